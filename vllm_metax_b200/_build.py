@@ -1,0 +1,115 @@
+"""In-tree build of the native extensions for sm_100a.
+
+Two shared objects are produced next to this file:
+
+* ``_b200_C.so``            - CUDA kernels + ``torch.ops.b200`` bindings
+* ``cumem_allocator.so``    - sleep-mode VMM allocator (CPython module, driver API)
+
+Every ``.cu`` is compiled with ``-gencode arch=compute_100a,code=sm_100a`` by a
+direct ``nvcc`` call (cross-compiles without a GPU); objects are rebuilt only
+when their source or a header is newer.  ``python -m vllm_metax_b200._build``
+builds from the command line.
+
+Parity: the reference drives CMake from setup.py (setup.py:82-262) for the three
+targets of CMakeLists.txt:181-686; a plain incremental nvcc driver is enough here.
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import os
+import subprocess
+import sys
+import sysconfig
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+CSRC = ROOT / "csrc"
+OBJ = ROOT / "_obj"
+LIB = ROOT / "_b200_C.so"
+CUMEM_LIB = ROOT / "cumem_allocator.so"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo", "--use_fast_math",
+    "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-DNDEBUG",
+]
+
+
+def _cuda_home() -> str:
+    return os.environ.get("CUDA_HOME", "/usr/local/cuda")
+
+
+def _newer(src_paths, target: Path) -> bool:
+    if not target.exists():
+        return True
+    t = target.stat().st_mtime
+    return any(Path(p).stat().st_mtime > t for p in src_paths)
+
+
+def _run(cmd: list[str]) -> None:
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("build step failed:\n" + " ".join(cmd) + "\n" + r.stdout + r.stderr)
+
+
+def sources() -> list[Path]:
+    return sorted(CSRC.glob("*.cu"))
+
+
+def build(verbose: bool = False, force: bool = False) -> Path:
+    import torch
+    from torch.utils.cpp_extension import include_paths, library_paths
+
+    OBJ.mkdir(exist_ok=True)
+    headers = list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh"))
+    nvcc = os.path.join(_cuda_home(), "bin", "nvcc")
+    jobs = []
+    objs = []
+    for src in sources():
+        obj = OBJ / (src.stem + ".o")
+        objs.append(obj)
+        if force or _newer([src, *headers], obj):
+            jobs.append([nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)])
+    bind_src = CSRC / "bindings.cpp"
+    bind_obj = OBJ / "bindings.o"
+    objs.append(bind_obj)
+    inc = []
+    for p in include_paths(device_type="cuda") if "device_type" in include_paths.__code__.co_varnames else include_paths(cuda=True):
+        inc += ["-I", p]
+    inc += ["-I", os.path.join(_cuda_home(), "include"), "-I", sysconfig.get_paths()["include"]]
+    cxx_abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+    if force or _newer([bind_src, *headers], bind_obj):
+        jobs.append(["g++", "-std=c++17", "-O2", "-fPIC", f"-D_GLIBCXX_USE_CXX11_ABI={cxx_abi}",
+                     "-DTORCH_EXTENSION_NAME=_b200_C", *inc, "-I", str(CSRC), "-c", str(bind_src), "-o", str(bind_obj)])
+    if jobs:
+        workers = int(os.environ.get("MAX_JOBS", "0")) or min(8, os.cpu_count() or 4)
+        with cf.ThreadPoolExecutor(workers) as ex:
+            for fut in [ex.submit(_run, j) for j in jobs]:
+                fut.result()
+        if verbose:
+            print(f"[b200 build] compiled {len(jobs)} translation units")
+    if force or jobs or not LIB.exists():
+        libdirs = []
+        for p in library_paths(device_type="cuda") if "device_type" in library_paths.__code__.co_varnames else library_paths(cuda=True):
+            libdirs += ["-L", p, f"-Wl,-rpath,{p}"]
+        _run(["g++", "-shared", "-o", str(LIB), *map(str, objs), *libdirs, "-L", os.path.join(_cuda_home(), "lib64"),
+              "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-lcudart"])
+    build_cumem(verbose=verbose, force=force)
+    return LIB
+
+
+def build_cumem(verbose: bool = False, force: bool = False) -> Path | None:
+    src = CSRC / "cumem_allocator.cpp"
+    if not src.exists():
+        return None
+    if force or _newer([src], CUMEM_LIB):
+        inc = ["-I", os.path.join(_cuda_home(), "include"), "-I", sysconfig.get_paths()["include"]]
+        _run(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", *inc, str(src), "-o", str(CUMEM_LIB),
+              "-L", os.path.join(_cuda_home(), "lib64"), "-L", os.path.join(_cuda_home(), "lib64", "stubs"), "-lcuda"])
+        if verbose:
+            print("[b200 build] built cumem_allocator")
+    return CUMEM_LIB
+
+
+if __name__ == "__main__":
+    build(verbose=True, force="--force" in sys.argv)
+    print(LIB)

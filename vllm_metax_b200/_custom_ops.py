@@ -1,0 +1,496 @@
+"""Python entry points of every op: CUDA kernels on GPU tensors, PyTorch reference on CPU.
+
+There is exactly one GPU implementation per op (the hand-written sm_100a kernel in
+``csrc/``); the PyTorch implementation in ``ops/reference.py`` is the oracle and the
+CPU execution path.  On a GPU tensor a missing native library is an error - nothing
+falls back silently.
+
+Parity: vllm_metax/_custom_ops.py:55-264 (the ops the reference adds or changes) plus
+the upstream ``vllm._custom_ops`` wrappers it relies on for everything else.
+"""
+from __future__ import annotations
+
+import os
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+from . import envs
+from .ops import reference as ref
+
+_LIB = Path(__file__).resolve().parent / "_b200_C.so"
+_loaded = False
+
+ACT_CODES = {"silu": 0, "gelu": 1, "gelu_tanh": 2, "fatrelu": 3, "relu2": 4, "mul_silu": 5, "swigluoai": 6,
+             "swiglustep": 7, "gelu_new": 8, "gelu_fast": 9, "gelu_quick": 10}
+CACHE_KIND = {"same": 0, "fp8_static": 1, "int8_dyn": 2, "fp8_dyn": 3}
+
+
+def load_native(build_if_missing: bool = True) -> bool:
+    """Load ``_b200_C.so`` (building it in-tree when absent and allowed)."""
+    global _loaded
+    if _loaded:
+        return True
+    if not _LIB.exists():
+        if not build_if_missing or envs.B200_USE_PREBUILT_KERNELS:
+            return False
+        from ._build import build
+
+        build()
+    torch.ops.load_library(str(_LIB))
+    _loaded = True
+    return True
+
+
+def native_loaded() -> bool:
+    return _loaded
+
+
+def _use_cuda(t: torch.Tensor) -> bool:
+    if not t.is_cuda or envs.B200_FORCE_REFERENCE_OPS:
+        return False
+    if not _loaded and not load_native():
+        raise RuntimeError("CUDA tensor given but the native library _b200_C.so is not built; "
+                           "run `python -m vllm_metax_b200._build`")
+    return True
+
+
+def kernel_status(device: int = 0) -> dict:
+    """Read (and clear) the device status word bounded waits and index checks report into."""
+    if not _loaded:
+        return {"code": 0}
+    w = torch.ops.b200.get_status(device)
+    vals = w.tolist()
+    if vals[0] != 0:
+        w.zero_()
+    return {"code": vals[0], "where": vals[1], "expected": vals[2], "observed": vals[3]}
+
+
+def check_kernel_status(device: int = 0) -> None:
+    st = kernel_status(device)
+    if st["code"] != 0:
+        names = {1: "wait timeout", 2: "index out of range", 3: "bad shape"}
+        raise RuntimeError(f"kernel reported {names.get(st['code'], st['code'])} at site {st['where']} "
+                           f"(expected {st['expected']}, observed {st['observed']})")
+
+
+# --------------------------------------------------------------------------- GEMM
+def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+         residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+         force_bn: int = 0) -> torch.Tensor:
+    """``a [M,K] @ w [N,K]^T (+bias) (+residual)``."""
+    if _use_cuda(a) and a.dtype in (torch.bfloat16, torch.float16):
+        if out is None:
+            out = torch.empty(a.shape[0], w.shape[0], dtype=a.dtype, device=a.device)
+        if envs.B200_TCGEN05_GEMM:
+            torch.ops.b200.gemm(out, a, w, bias, residual, force_bn)
+        else:  # debug switch only: library GEMM
+            torch.addmm(bias, a, w.t(), out=out) if bias is not None else torch.mm(a, w.t(), out=out)
+            if residual is not None:
+                out.add_(residual)
+        return out
+    y = ref.gemm(a, w, bias)
+    if residual is not None:
+        y = (y.float() + residual.float()).to(a.dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+# --------------------------------------------------------------------------- norms
+def rms_norm(x, weight, eps, out=None, gemma: bool = False):
+    if _use_cuda(x):
+        out = torch.empty_like(x) if out is None else out
+        torch.ops.b200.rms_norm(out, x, weight, eps, gemma)
+        return out
+    y = ref.gemma_rms_norm(x, weight, eps) if gemma else ref.rms_norm(x, weight, eps)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def fused_add_rms_norm(x, residual, weight, eps, gemma: bool = False):
+    """In place: ``residual += x``; ``x = rmsnorm(residual)``.  Returns ``(x, residual)``."""
+    if _use_cuda(x):
+        torch.ops.b200.fused_add_rms_norm(x, residual, weight, eps, gemma)
+        return x, residual
+    r = (x.float() + residual.float()).to(x.dtype)
+    y = ref.gemma_rms_norm(r, weight, eps) if gemma else ref.rms_norm(r, weight, eps)
+    x.copy_(y)
+    residual.copy_(r)
+    return x, residual
+
+
+def head_rms_norm(x, weight, eps, heads: int, head_dim: int):
+    """Per-head RMSNorm in place over the first ``heads*head_dim`` columns of ``x [T, *]``."""
+    if _use_cuda(x):
+        torch.ops.b200.head_rms_norm(x, weight, eps, heads, head_dim)
+        return x
+    T = x.shape[0]
+    v = x[:, : heads * head_dim].reshape(T, heads, head_dim)
+    x[:, : heads * head_dim] = ref.rms_norm(v, weight, eps).reshape(T, -1)
+    return x
+
+
+def rms_norm_static_fp8_quant(x, weight, scale, eps, residual=None):
+    if _use_cuda(x):
+        out = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+        torch.ops.b200.rms_norm_quant(out, None, scale, x, residual, weight, eps, 0, 0, False, 0.0)
+        return out
+    if residual is not None:
+        y, r = ref.fused_add_rms_norm(x, residual, weight, eps)
+        residual.copy_(r)
+        return ref.static_scaled_fp8_quant(y, scale)
+    return ref.rms_norm_static_fp8_quant(x, weight, scale, eps)
+
+
+def rms_norm_dynamic_per_token_quant(x, weight, eps, quant_dtype=torch.float8_e4m3fn, residual=None, scale_ub=None):
+    if _use_cuda(x):
+        out = torch.empty(x.shape, dtype=quant_dtype, device=x.device)
+        scales = torch.empty(*x.shape[:-1], 1, dtype=torch.float32, device=x.device)
+        torch.ops.b200.rms_norm_quant(out, scales, None, x, residual, weight, eps,
+                                      2 if quant_dtype == torch.int8 else 1, 0, False, scale_ub or 0.0)
+        return out, scales
+    q, s, r = ref.rms_norm_dynamic_per_token_quant(x, weight, eps, quant_dtype, residual, scale_ub)
+    if residual is not None:
+        residual.copy_(r)
+    return q, s
+
+
+def rms_norm_per_block_quant(x, weight, eps, group_size=128, residual=None, ue8m0=False):
+    if _use_cuda(x):
+        out = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+        scales = torch.empty(*x.shape[:-1], x.shape[-1] // group_size, dtype=torch.float32, device=x.device)
+        torch.ops.b200.rms_norm_quant(out, scales, None, x, residual, weight, eps, 3, group_size, ue8m0, 0.0)
+        return out, scales
+    q, s, r = ref.rms_norm_per_block_quant(x, weight, eps, group_size, residual, ue8m0)
+    if residual is not None:
+        residual.copy_(r)
+    return q, s
+
+
+# --------------------------------------------------------------------------- rope / cache
+def _cache_kind(kv_cache, kv_scales) -> int:
+    if kv_cache.dtype == torch.int8:
+        return CACHE_KIND["int8_dyn"]
+    if kv_cache.dtype == torch.float8_e4m3fn:
+        return CACHE_KIND["fp8_dyn"] if kv_scales is not None else CACHE_KIND["fp8_static"]
+    return CACHE_KIND["same"]
+
+
+def rotary_embedding(positions, q, k, head_size, cos_sin_cache, is_neox=True, rot_offset=0, inverse=False):
+    """In-place RoPE on ``q [T, Hq*D]`` and optionally ``k [T, Hk*D]``."""
+    if _use_cuda(q):
+        torch.ops.b200.rope_and_cache(positions, q, k, None, cos_sin_cache, head_size, q.shape[-1] // head_size,
+                                      0 if k is None else k.shape[-1] // head_size, is_neox, rot_offset, inverse,
+                                      None, None, None, 0, 1.0, 1.0)
+        return q, k
+    qo, ko = ref.rotary_embedding(positions, q, k, head_size, cos_sin_cache, is_neox, rot_offset, inverse)
+    q.copy_(qo)
+    if k is not None:
+        k.copy_(ko)
+    return q, k
+
+
+def reshape_and_cache(key, value, kv_cache, slot_mapping, kv_scales=None, k_scale=1.0, v_scale=1.0):
+    """Scatter ``key/value [T, Hkv, D]`` (or ``[T, Hkv*D]``) into the paged cache."""
+    if _use_cuda(key):
+        D = kv_cache.shape[-1]
+        torch.ops.b200.rope_and_cache(None, None, key, value, None, D, 0, kv_cache.shape[3], True, 0, False, kv_cache,
+                                      kv_scales, slot_mapping, _cache_kind(kv_cache, kv_scales), k_scale, v_scale)
+        return
+    H, D = kv_cache.shape[3], kv_cache.shape[4]
+    ref.reshape_and_cache(key.reshape(-1, H, D), value.reshape(-1, H, D), kv_cache, slot_mapping, kv_scales, k_scale, v_scale)
+
+
+def rope_and_cache(positions, q, k, v, head_size, cos_sin_cache, is_neox, kv_cache, slot_mapping, kv_scales=None,
+                   k_scale=1.0, v_scale=1.0, rot_offset=0):
+    """RoPE on q, k in place and write (k, v) into the paged cache - one kernel on GPU."""
+    if _use_cuda(q):
+        torch.ops.b200.rope_and_cache(positions, q, k, v, cos_sin_cache, head_size, q.shape[-1] // head_size,
+                                      k.shape[-1] // head_size, is_neox, rot_offset, False, kv_cache, kv_scales,
+                                      slot_mapping, _cache_kind(kv_cache, kv_scales), k_scale, v_scale)
+        return
+    rotary_embedding(positions, q, k, head_size, cos_sin_cache, is_neox, rot_offset)
+    reshape_and_cache(k, v, kv_cache, slot_mapping, kv_scales, k_scale, v_scale)
+
+
+def copy_blocks(kv_caches, src_to_dst: torch.Tensor):
+    if kv_caches and _use_cuda(kv_caches[0]):
+        pairs = src_to_dst.to(torch.int64).contiguous()
+        for c in kv_caches:
+            torch.ops.b200.copy_blocks(c, pairs)
+        return
+    ref.copy_blocks(kv_caches, src_to_dst)
+
+
+def swap_blocks(src, dst, src_to_dst):
+    """Block copies between a device cache and a (pinned) host cache; one async copy per block."""
+    for s, d in src_to_dst.tolist():
+        dst[d].copy_(src[s], non_blocking=True)
+
+
+def concat_and_cache_mla(kv_c, k_pe, mla_cache, slot_mapping):
+    if _use_cuda(kv_c):
+        torch.ops.b200.concat_and_cache_mla(kv_c, k_pe, mla_cache, slot_mapping)
+        return
+    ref.concat_and_cache_mla(kv_c, k_pe, mla_cache, slot_mapping)
+
+
+def indexer_k_quant_and_cache(k, idx_cache, slot_mapping, block_size: int, ue8m0: bool = False):
+    """Parity: vllm_metax/_custom_ops.py:137-149."""
+    if _use_cuda(k):
+        torch.ops.b200.indexer_k_quant_and_cache(k, idx_cache, slot_mapping, block_size, ue8m0)
+        return
+    ref.indexer_k_quant_and_cache(k, idx_cache.view(idx_cache.shape[0], -1), slot_mapping, ue8m0=ue8m0)
+
+
+# --------------------------------------------------------------------------- activations
+def act_and_mul(x, act: str = "silu", out=None, p0: float = 0.0, p1: float = 0.0):
+    if _use_cuda(x):
+        d = x.shape[-1] // 2
+        out = torch.empty(*x.shape[:-1], d, dtype=x.dtype, device=x.device) if out is None else out
+        if act == "swigluoai":
+            p0, p1 = p0 or 1.702, p1 or 7.0
+        if act == "swiglustep":
+            p1 = p1 or 7.0
+        torch.ops.b200.act_and_mul(out, x, ACT_CODES[act], p0, p1)
+        return out
+    if act == "mul_silu":
+        y = ref.mul_and_silu(x)
+    elif act == "swigluoai":
+        y = ref.swigluoai_and_mul(x, p0 or 1.702, p1 or 7.0)
+    elif act == "swiglustep":
+        y = ref.swiglustep_and_mul(x, p1 or 7.0)
+    elif act == "fatrelu":
+        y = ref.act_and_mul(x, act, threshold=p0)
+    else:
+        y = ref.act_and_mul(x, act)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def silu_and_mul(x, out=None):
+    return act_and_mul(x, "silu", out)
+
+
+def activation(x, act: str):
+    if _use_cuda(x):
+        out = torch.empty_like(x)
+        torch.ops.b200.activation(out, x.contiguous(), ACT_CODES[act], 0.0)
+        return out
+    return ref.activation(x, act)
+
+
+def silu_and_mul_quant(x, scale):
+    if _use_cuda(x):
+        out = torch.empty(*x.shape[:-1], x.shape[-1] // 2, dtype=torch.float8_e4m3fn, device=x.device)
+        torch.ops.b200.act_and_mul_quant(out, None, scale, x.contiguous(), 0, 0.0, 0.0, 0, False)
+        return out
+    return ref.silu_and_mul_quant(x, scale)
+
+
+def silu_and_mul_per_block_quant(x, group_size=128, ue8m0=False, act: str = "silu"):
+    if _use_cuda(x):
+        d = x.shape[-1] // 2
+        out = torch.empty(*x.shape[:-1], d, dtype=torch.float8_e4m3fn, device=x.device)
+        scales = torch.empty(*x.shape[:-1], d // group_size, dtype=torch.float32, device=x.device)
+        torch.ops.b200.act_and_mul_quant(out, scales, None, x.contiguous(), ACT_CODES[act], 0.0, 7.0, group_size, ue8m0)
+        return out, scales
+    y = ref.swiglustep_and_mul(x) if act == "swiglustep" else ref.silu_and_mul(x)
+    return ref.per_token_group_quant_fp8(y, group_size, ue8m0=ue8m0)
+
+
+# --------------------------------------------------------------------------- attention
+_decode_ws: dict = {}
+
+
+def _decode_workspace(device, numel: int) -> torch.Tensor:
+    ws = _decode_ws.get(device)
+    if ws is None or ws.numel() < numel:
+        ws = torch.empty(max(numel, 1 << 20), dtype=torch.float32, device=device)
+        _decode_ws[device] = ws
+    return ws
+
+
+def decode_num_splits(batch: int, num_kv_heads: int, max_seq_len: int, row_tiles: int = 1, sms: int = 148) -> int:
+    """Enough KV splits to give every SM a CTA, never finer than 256 tokens per split."""
+    ctas = max(1, batch * num_kv_heads * row_tiles)
+    if ctas >= sms:
+        return 1
+    want = (2 * sms + ctas - 1) // ctas
+    return max(1, min(want, max(1, max_seq_len // 256), 32))
+
+
+def paged_attention_decode(q, kv_cache, block_table, seq_lens, scale, *, out=None, kv_scales=None,
+                           query_start_loc=None, max_q_len: int = 1, window: int = -1, softcap: float = 0.0,
+                           sinks=None, lse_out=None, num_splits: int = 0, max_seq_len: int = 0, k_scale=1.0,
+                           v_scale=1.0, causal=True, workspace=None):
+    """Decode attention over the paged cache; ``q [T, Hq, D]``."""
+    if _use_cuda(q):
+        out = torch.empty(q.shape[0], q.shape[1], kv_cache.shape[-1], dtype=q.dtype, device=q.device) if out is None else out
+        B = seq_lens.shape[0]
+        Hkv = kv_cache.shape[3]
+        if num_splits <= 0:
+            g = q.shape[1] // Hkv
+            num_splits = decode_num_splits(B, Hkv, max_seq_len or 4096, (max_q_len * g + 15) // 16)
+        ws = workspace
+        if num_splits > 1 and ws is None:
+            ws = _decode_workspace(q.device, num_splits * q.shape[0] * q.shape[1] * (q.shape[2] + 1))
+        torch.ops.b200.paged_attention_decode(out, q, kv_cache, kv_scales, block_table, seq_lens, query_start_loc,
+                                              scale, window, softcap, sinks, lse_out, ws, num_splits, B, max_q_len,
+                                              k_scale, v_scale, causal)
+        return out
+    B = seq_lens.shape[0]
+    qsl = query_start_loc if query_start_loc is not None else torch.arange(B + 1, dtype=torch.int32, device=q.device)
+    res = ref.paged_attention(q, kv_cache, block_table, seq_lens, qsl, scale, kv_scales=kv_scales, window=window,
+                              softcap=softcap, sinks=sinks, k_scale=k_scale, v_scale=v_scale, causal=causal,
+                              return_lse=lse_out is not None)
+    if lse_out is not None:
+        res, lse = res
+        lse_out.copy_(lse)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+def paged_attention_prefill(q, kv_cache, block_table, seq_lens, query_start_loc, scale, *, out=None, kv_scales=None,
+                            max_q_len: int = 0, window: int = -1, softcap: float = 0.0, sinks=None, lse_out=None,
+                            k_scale=1.0, v_scale=1.0, causal=True, max_seq_len: int = 0):
+    """Varlen prefill / chunked-prefill attention reading K, V from the paged cache."""
+    if _use_cuda(q):
+        out = torch.empty(q.shape[0], q.shape[1], kv_cache.shape[-1], dtype=q.dtype, device=q.device) if out is None else out
+        B = seq_lens.shape[0]
+        D = q.shape[-1]
+        if kv_cache.dtype == q.dtype and D in (64, 128) and kv_scales is None:
+            torch.ops.b200.attention_prefill(out, q, kv_cache, None, block_table, seq_lens, query_start_loc, None,
+                                             scale, window, softcap, sinks, lse_out, B, max_q_len or q.shape[0], causal)
+        else:
+            # quantised caches / other head sizes: the split-KV kernel handles any query length in 16-row tiles
+            paged_attention_decode(q, kv_cache, block_table, seq_lens, scale, out=out, kv_scales=kv_scales,
+                                   query_start_loc=query_start_loc, max_q_len=max_q_len or q.shape[0], window=window,
+                                   softcap=softcap, sinks=sinks, lse_out=lse_out, num_splits=1, k_scale=k_scale,
+                                   v_scale=v_scale, causal=causal)
+        return out
+    res = ref.paged_attention(q, kv_cache, block_table, seq_lens, query_start_loc, scale, kv_scales=kv_scales,
+                              window=window, softcap=softcap, sinks=sinks, k_scale=k_scale, v_scale=v_scale,
+                              causal=causal, return_lse=lse_out is not None)
+    if lse_out is not None:
+        res, lse = res
+        lse_out.copy_(lse)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+def varlen_attention(q, k, v, cu_seqlens_q, cu_seqlens_k, scale, *, out=None, max_q_len: int = 0, causal=True,
+                     window: int = -1, softcap: float = 0.0, sinks=None, lse_out=None):
+    """Ragged attention over contiguous ``k [Tk,Hkv,Dqk]``, ``v [Tk,Hkv,Dv]`` (MLA prefill, ViT)."""
+    if _use_cuda(q):
+        out = torch.empty(q.shape[0], q.shape[1], v.shape[-1], dtype=q.dtype, device=q.device) if out is None else out
+        B = cu_seqlens_q.shape[0] - 1
+        torch.ops.b200.attention_prefill(out, q, k, v, None, None, cu_seqlens_q, cu_seqlens_k, scale, window, softcap,
+                                         sinks, lse_out, B, max_q_len or q.shape[0], causal)
+        return out
+    T, Hq, _ = q.shape
+    res = torch.zeros(T, Hq, v.shape[-1], dtype=torch.float32, device=q.device)
+    lse_all = torch.full((Hq, T), float("-inf"), dtype=torch.float32, device=q.device)
+    cq, ck = cu_seqlens_q.tolist(), cu_seqlens_k.tolist()
+    for b in range(len(cq) - 1):
+        if cq[b + 1] <= cq[b]:
+            continue
+        lq, lk = cq[b + 1] - cq[b], ck[b + 1] - ck[b]
+        o, lse = ref.attention_core(q[cq[b]:cq[b + 1]].float(), k[ck[b]:ck[b + 1]].float(), v[ck[b]:ck[b + 1]].float(),
+                                    scale, causal_offset=(lk - lq) if causal else None, window=window,
+                                    softcap=softcap, sinks=sinks)
+        res[cq[b]:cq[b + 1]] = o
+        lse_all[:, cq[b]:cq[b + 1]] = lse
+    if lse_out is not None:
+        lse_out.copy_(lse_all)
+    res = res.to(q.dtype)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+# --------------------------------------------------------------------------- sampling
+def argmax(logits, out=None):
+    if _use_cuda(logits):
+        out = torch.empty(logits.shape[0], dtype=torch.int64, device=logits.device) if out is None else out
+        torch.ops.b200.argmax(out, logits)
+        return out
+    r = logits.float().argmax(dim=-1)
+    if out is not None:
+        out.copy_(r)
+        return out
+    return r
+
+
+def sample(logits, temperature, top_k=None, top_p=None, min_p=None, uniform=None, out=None):
+    if _use_cuda(logits):
+        out = torch.empty(logits.shape[0], dtype=torch.int64, device=logits.device) if out is None else out
+        if uniform is None:
+            uniform = torch.rand(logits.shape[0], dtype=torch.float32, device=logits.device)
+        torch.ops.b200.sample(out, logits, temperature, top_k, top_p, min_p, uniform)
+        return out
+    r = ref.sample(logits, temperature, top_k, top_p, min_p, uniform=uniform)
+    if out is not None:
+        out.copy_(r)
+        return out
+    return r
+
+
+def apply_penalties(logits, prompt_mask, output_counts, rep, presence, frequency):
+    """In place.  ``prompt_mask``/``output_counts`` are int32 ``[B, V]``.  Parity: csrc/sampler.cu:14."""
+    if _use_cuda(logits):
+        torch.ops.b200.apply_penalties(logits, prompt_mask, output_counts, rep, presence, frequency)
+        return logits
+    lf = logits
+    if rep is not None:
+        pm = prompt_mask.bool() if prompt_mask is not None else torch.zeros_like(logits, dtype=torch.bool)
+        om = output_counts > 0 if output_counts is not None else torch.zeros_like(logits, dtype=torch.bool)
+        lf = ref.apply_repetition_penalties(lf, pm, om, rep)
+    if output_counts is not None and (presence is not None or frequency is not None):
+        z = torch.zeros(logits.shape[0], device=logits.device)
+        lf = ref.apply_penalties(lf, output_counts, presence if presence is not None else z,
+                                 frequency if frequency is not None else z)
+    logits.copy_(lf)
+    return logits
+
+
+def advance_step(input_ids, positions, seq_lens, slot_mapping, sampled, block_table, block_size, batch,
+                 token_log=None, log_col: int = 0):
+    if _use_cuda(input_ids):
+        torch.ops.b200.advance_step(input_ids, positions, seq_lens, slot_mapping, sampled, block_table, block_size,
+                                    batch, token_log, log_col)
+        return
+    input_ids[:batch] = sampled[:batch]
+    if token_log is not None:
+        token_log[:batch, log_col] = sampled[:batch]
+    positions[:batch] += 1
+    seq_lens[:batch] = (positions[:batch] + 1).to(seq_lens.dtype)
+    pos = positions[:batch]
+    blk = block_table[torch.arange(batch), (pos // block_size).long()].long()
+    slot_mapping[:batch] = blk * block_size + pos % block_size
+
+
+def embedding(table, ids, out=None, vocab_start: int = 0):
+    if _use_cuda(table) and table.dtype in (torch.bfloat16, torch.float16):
+        out = torch.empty(ids.numel(), table.shape[1], dtype=table.dtype, device=table.device) if out is None else out
+        torch.ops.b200.embedding(out, table, ids, vocab_start)
+        return out
+    local = ids - vocab_start
+    ok = (local >= 0) & (local < table.shape[0])
+    y = table[local.clamp(0, table.shape[0] - 1)] * ok[:, None].to(table.dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y

@@ -1,0 +1,208 @@
+"""Configuration objects of the standalone engine.
+
+``ModelConfig`` mirrors the fields of a HuggingFace ``config.json`` that the
+model classes read (Llama / Qwen3 / Qwen3-MoE / DeepSeek-V2/V3/V3.2), so a
+checkpoint directory and a hand-written dict are interchangeable.
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass, field
+from typing import Any, Optional
+
+import torch
+
+_DTYPES = {"float32": torch.float32, "fp32": torch.float32, "float16": torch.float16, "half": torch.float16,
+           "bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "auto": None}
+
+
+def resolve_dtype(d) -> Optional[torch.dtype]:
+    if isinstance(d, torch.dtype) or d is None:
+        return d
+    return _DTYPES[str(d)]
+
+
+@dataclass
+class ModelConfig:
+    architecture: str = "LlamaForCausalLM"
+    vocab_size: int = 32000
+    hidden_size: int = 4096
+    intermediate_size: int = 11008
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: Optional[int] = None
+    head_dim: Optional[int] = None
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    rope_scaling: Optional[dict] = None
+    max_position_embeddings: int = 8192
+    tie_word_embeddings: bool = False
+    hidden_act: str = "silu"
+    attention_bias: bool = False
+    mlp_bias: bool = False
+    qk_norm: bool = False                      # Qwen3: per-head RMSNorm on q and k
+    sliding_window: Optional[int] = None
+    # ---- MoE -----------------------------------------------------------
+    num_experts: int = 0                       # routed experts (0 = dense)
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    n_shared_experts: int = 0
+    first_k_dense_replace: int = 0
+    moe_layer_freq: int = 1
+    scoring_func: str = "softmax"              # softmax | sigmoid | sqrtsoftplus
+    n_group: int = 1
+    topk_group: int = 1
+    routed_scaling_factor: float = 1.0
+    topk_method: str = "greedy"                # greedy | noaux_tc | group_limited_greedy
+    # ---- MLA (DeepSeek) -------------------------------------------------
+    q_lora_rank: Optional[int] = None
+    kv_lora_rank: int = 0
+    qk_nope_head_dim: int = 0
+    qk_rope_head_dim: int = 0
+    v_head_dim: int = 0
+    # ---- DSA indexer (DeepSeek-V3.2) --------------------------------------
+    index_n_heads: int = 0
+    index_head_dim: int = 128
+    index_topk: int = 0
+    # ---- MTP ----------------------------------------------------------------
+    num_nextn_predict_layers: int = 0
+    # ---- numerics / quantisation ----------------------------------------
+    dtype: torch.dtype = torch.bfloat16
+    quantization: Optional[str] = None         # None | fp8 | w8a8_int8 | awq | gptq | ...
+    quant_config: dict = field(default_factory=dict)
+    model_path: Optional[str] = None
+    seed: int = 0
+    eos_token_id: Optional[int] = None
+
+    def __post_init__(self):
+        if self.num_key_value_heads is None:
+            self.num_key_value_heads = self.num_attention_heads
+        if self.head_dim is None:
+            self.head_dim = self.hidden_size // self.num_attention_heads
+        self.dtype = resolve_dtype(self.dtype) or torch.bfloat16
+
+    @property
+    def is_mla(self) -> bool:
+        return self.kv_lora_rank > 0
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    @property
+    def has_indexer(self) -> bool:
+        return self.index_topk > 0
+
+    def layer_is_moe(self, i: int) -> bool:
+        return self.is_moe and i >= self.first_k_dense_replace and (i % max(self.moe_layer_freq, 1) == 0)
+
+    @classmethod
+    def from_hf_dict(cls, d: dict, **overrides: Any) -> "ModelConfig":
+        archs = d.get("architectures") or ["LlamaForCausalLM"]
+        arch = archs[0]
+        kw: dict[str, Any] = dict(
+            architecture=arch,
+            vocab_size=d.get("vocab_size", 32000),
+            hidden_size=d["hidden_size"],
+            intermediate_size=d.get("intermediate_size", 4 * d["hidden_size"]),
+            num_hidden_layers=d["num_hidden_layers"],
+            num_attention_heads=d["num_attention_heads"],
+            num_key_value_heads=d.get("num_key_value_heads"),
+            head_dim=d.get("head_dim"),
+            rms_norm_eps=d.get("rms_norm_eps", 1e-5),
+            rope_theta=d.get("rope_theta", 10000.0),
+            rope_scaling=d.get("rope_scaling"),
+            max_position_embeddings=d.get("max_position_embeddings", 8192),
+            tie_word_embeddings=d.get("tie_word_embeddings", False),
+            hidden_act=d.get("hidden_act", "silu"),
+            attention_bias=d.get("attention_bias", False) or ("Qwen2" in arch),
+            mlp_bias=d.get("mlp_bias", False),
+            qk_norm="Qwen3" in arch,
+            sliding_window=d.get("sliding_window") if d.get("use_sliding_window", True) else None,
+            num_experts=d.get("num_experts", d.get("n_routed_experts", d.get("num_local_experts", 0))) or 0,
+            num_experts_per_tok=d.get("num_experts_per_tok", 0) or 0,
+            moe_intermediate_size=d.get("moe_intermediate_size", 0) or 0,
+            norm_topk_prob=d.get("norm_topk_prob", True),
+            n_shared_experts=d.get("n_shared_experts", 0) or 0,
+            first_k_dense_replace=d.get("first_k_dense_replace", 0) or 0,
+            moe_layer_freq=d.get("moe_layer_freq", 1) or 1,
+            scoring_func=d.get("scoring_func", "softmax"),
+            n_group=d.get("n_group", 1) or 1,
+            topk_group=d.get("topk_group", 1) or 1,
+            routed_scaling_factor=d.get("routed_scaling_factor", 1.0) or 1.0,
+            topk_method=d.get("topk_method", "greedy"),
+            q_lora_rank=d.get("q_lora_rank"),
+            kv_lora_rank=d.get("kv_lora_rank", 0) or 0,
+            qk_nope_head_dim=d.get("qk_nope_head_dim", 0) or 0,
+            qk_rope_head_dim=d.get("qk_rope_head_dim", 0) or 0,
+            v_head_dim=d.get("v_head_dim", 0) or 0,
+            index_n_heads=d.get("index_n_heads", 0) or 0,
+            index_head_dim=d.get("index_head_dim", 128) or 128,
+            index_topk=d.get("index_topk", 0) or 0,
+            num_nextn_predict_layers=d.get("num_nextn_predict_layers", 0) or 0,
+            dtype=d.get("torch_dtype", d.get("dtype", "bfloat16")),
+            eos_token_id=(d.get("eos_token_id")[0] if isinstance(d.get("eos_token_id"), list) else d.get("eos_token_id")),
+        )
+        qc = d.get("quantization_config")
+        if qc:
+            kw["quantization"] = qc.get("quant_method")
+            kw["quant_config"] = qc
+        kw.update(overrides)
+        return cls(**kw)
+
+    @classmethod
+    def from_pretrained(cls, path: str, **overrides: Any) -> "ModelConfig":
+        with open(os.path.join(path, "config.json")) as f:
+            d = json.load(f)
+        return cls.from_hf_dict(d, model_path=path, **overrides)
+
+
+@dataclass
+class CacheConfig:
+    block_size: int = 64
+    num_gpu_blocks: Optional[int] = None       # None: derived from gpu_memory_utilization
+    gpu_memory_utilization: float = 0.88
+    kv_cache_dtype: str = "auto"               # auto | bfloat16 | float16 | fp8 | int8_per_token_head | fp8_per_token_head | fp8_ds_mla
+    enable_prefix_caching: bool = False
+    swap_space_gb: float = 0.0
+
+
+@dataclass
+class ParallelConfig:
+    tensor_parallel_size: int = 1
+    pipeline_parallel_size: int = 1
+    data_parallel_size: int = 1
+    enable_expert_parallel: bool = False
+    decode_context_parallel_size: int = 1
+    use_sequence_parallel_moe: bool = False
+    all2all_backend: str = "fused_nvlink"      # fused_nvlink | allgather_reducescatter | naive
+
+    @property
+    def world_size(self) -> int:
+        return self.tensor_parallel_size * self.pipeline_parallel_size
+
+
+@dataclass
+class SchedulerConfig:
+    max_num_seqs: int = 256
+    max_num_batched_tokens: int = 8192
+    max_model_len: int = 4096
+    enable_chunked_prefill: bool = True
+    # Number of decode iterations run back to back on the device (device-side
+    # advance of positions/slots) before the host looks at the sampled tokens.
+    num_scheduler_steps: int = 1
+    policy: str = "fcfs"
+
+
+@dataclass
+class EngineConfig:
+    model: ModelConfig
+    cache: CacheConfig = field(default_factory=CacheConfig)
+    parallel: ParallelConfig = field(default_factory=ParallelConfig)
+    scheduler: SchedulerConfig = field(default_factory=SchedulerConfig)
+    device: str = "cuda"
+    enforce_eager: bool = False
+    load_format: str = "auto"                  # auto | dummy | safetensors | sharded_state
+    additional_config: dict = field(default_factory=dict)

@@ -1,0 +1,397 @@
+// torch.ops.b200.* : adapts torch tensors to the torch-free launchers in ops.h.
+// Every op writes into caller-provided tensors (no allocation here), so the ops can
+// be captured in CUDA graphs.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+#include <torch/types.h>
+
+#include "ops.h"
+
+namespace {
+
+using at::Tensor;
+using c10::optional;
+
+inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+inline int dtype_code(const Tensor& t) {
+  switch (t.scalar_type()) {
+    case at::kBFloat16: return 0;
+    case at::kHalf: return 1;
+    case at::kFloat: return 2;
+    default: TORCH_CHECK(false, "unsupported dtype ", t.scalar_type());
+  }
+}
+inline int dtype16(const Tensor& t) {
+  const int c = dtype_code(t);
+  TORCH_CHECK(c < 2, "expected a bf16 / fp16 tensor");
+  return c;
+}
+template <typename T = void>
+inline T* ptr(const optional<Tensor>& t) {
+  return t.has_value() && t->defined() ? reinterpret_cast<T*>(t->data_ptr()) : nullptr;
+}
+
+// One status word per device, zero-initialised on first use.
+Tensor& status_tensor(int device) {
+  static std::vector<Tensor> words(64);
+  if (!words[device].defined())
+    words[device] = torch::zeros({4}, torch::dtype(torch::kInt32).device(torch::kCUDA, device));
+  return words[device];
+}
+inline void* status_ptr(const Tensor& any) { return status_tensor(any.get_device()).data_ptr(); }
+
+Tensor get_status(int64_t device) { return status_tensor((int)device); }
+
+// ------------------------------------------------------------------ GEMM
+void gemm(Tensor& out, const Tensor& a, const Tensor& w, const optional<Tensor>& bias,
+          const optional<Tensor>& residual, int64_t force_bn) {
+  TORCH_CHECK(a.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm expects 2-D tensors");
+  TORCH_CHECK(a.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1, "inner dims must be contiguous");
+  const int M = a.size(0), K = a.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K && out.size(0) == M && out.size(1) == N, "gemm shape mismatch");
+  TORCH_CHECK(K % 8 == 0 && a.stride(0) % 8 == 0 && w.stride(0) % 8 == 0 && out.stride(0) % 8 == 0,
+              "gemm: K and row pitches must be multiples of 8 elements");
+  TORCH_CHECK(a.scalar_type() == w.scalar_type() && a.scalar_type() == out.scalar_type(), "gemm dtype mismatch");
+  int ldr = 0;
+  if (residual.has_value()) {
+    TORCH_CHECK(residual->stride(1) == 1 && residual->size(0) == M && residual->size(1) == N);
+    ldr = residual->stride(0);
+  }
+  const c10::cuda::CUDAGuard guard(a.device());
+  b200::gemm_tn(a.data_ptr(), w.data_ptr(), out.data_ptr(), ptr(bias), ptr(residual), M, N, K, a.stride(0),
+                w.stride(0), out.stride(0), ldr, dtype16(a), cur_stream(), status_ptr(a), (int)force_bn);
+}
+
+// ------------------------------------------------------------------ norms
+void rms_norm(Tensor& out, const Tensor& x, const Tensor& weight, double eps, bool gemma) {
+  const int hidden = x.size(-1);
+  const int tokens = x.numel() / hidden;
+  const c10::cuda::CUDAGuard guard(x.device());
+  b200::rms_norm(out.data_ptr(), x.data_ptr(), nullptr, weight.data_ptr(), (float)eps, tokens, hidden,
+                 x.dim() >= 2 ? x.stride(-2) : hidden, out.dim() >= 2 ? out.stride(-2) : hidden, dtype16(x),
+                 gemma ? 1 : 0, cur_stream());
+}
+void fused_add_rms_norm(Tensor& x, Tensor& residual, const Tensor& weight, double eps, bool gemma) {
+  const int hidden = x.size(-1);
+  const int tokens = x.numel() / hidden;
+  TORCH_CHECK(residual.is_contiguous(), "residual must be contiguous");
+  const c10::cuda::CUDAGuard guard(x.device());
+  b200::rms_norm(x.data_ptr(), x.data_ptr(), residual.data_ptr(), weight.data_ptr(), (float)eps, tokens, hidden,
+                 x.dim() >= 2 ? x.stride(-2) : hidden, x.dim() >= 2 ? x.stride(-2) : hidden, dtype16(x),
+                 gemma ? 1 : 0, cur_stream());
+}
+void head_rms_norm(Tensor& x, const Tensor& weight, double eps, int64_t heads, int64_t head_dim) {
+  // x: [T, >= heads*head_dim] view whose first heads*head_dim columns are normalised per head
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(head_dim % 32 == 0 && head_dim <= 256);
+  b200::head_rms_norm(x.data_ptr(), weight.data_ptr(), (float)eps, x.size(0), heads, head_dim, x.stride(0), dtype16(x),
+                      cur_stream());
+}
+void rms_norm_quant(Tensor& out_q, const optional<Tensor>& scale_out, const optional<Tensor>& scale_in,
+                    const Tensor& x, const optional<Tensor>& residual, const Tensor& weight, double eps, int64_t qmode,
+                    int64_t group, bool ue8m0, double scale_ub) {
+  const int hidden = x.size(-1);
+  const int tokens = x.numel() / hidden;
+  TORCH_CHECK(x.is_contiguous() && out_q.is_contiguous());
+  const c10::cuda::CUDAGuard guard(x.device());
+  b200::rms_norm_quant(out_q.data_ptr(), ptr<float>(scale_out), ptr<float>(scale_in), x.data_ptr(), ptr(residual),
+                       weight.data_ptr(), (float)eps, tokens, hidden, dtype16(x), qmode, group, ue8m0, (float)scale_ub,
+                       cur_stream());
+}
+
+// ------------------------------------------------------------------ rope / cache
+void rope_and_cache(const optional<Tensor>& positions, const optional<Tensor>& q, const optional<Tensor>& k,
+                    const optional<Tensor>& v, const optional<Tensor>& cos_sin, int64_t head_dim, int64_t num_q,
+                    int64_t num_kv, bool is_neox, int64_t rot_offset, bool inverse, const optional<Tensor>& kv_cache,
+                    const optional<Tensor>& kv_scales, const optional<Tensor>& slot_mapping, int64_t cache_kind,
+                    double k_scale, double v_scale) {
+  const Tensor& any = q.has_value() ? *q : *k;
+  const int tokens = any.size(0);
+  int rot = 0;
+  if (cos_sin.has_value()) {
+    TORCH_CHECK(cos_sin->scalar_type() == at::kFloat && cos_sin->is_contiguous(), "cos_sin cache must be f32");
+    rot = cos_sin->size(-1);
+  }
+  int block_size = 0;
+  int64_t num_slots = 0;
+  if (kv_cache.has_value()) {
+    TORCH_CHECK(kv_cache->dim() == 5 && kv_cache->is_contiguous(), "kv cache must be [nb,2,bs,Hkv,D] contiguous");
+    block_size = kv_cache->size(2);
+    num_slots = kv_cache->size(0) * block_size;
+    TORCH_CHECK(slot_mapping.has_value() && slot_mapping->scalar_type() == at::kLong);
+  }
+  if (positions.has_value()) TORCH_CHECK(positions->scalar_type() == at::kLong);
+  TORCH_CHECK(head_dim <= 576);
+  const c10::cuda::CUDAGuard guard(any.device());
+  b200::rope_and_cache(ptr<int64_t>(positions), ptr(q), ptr(k), ptr(v), ptr<float>(cos_sin), rot, head_dim,
+                       q.has_value() ? num_q : 0, num_kv, q.has_value() ? q->stride(0) : 0,
+                       k.has_value() ? k->stride(0) : 0, v.has_value() ? v->stride(0) : 0, is_neox, rot_offset, inverse,
+                       ptr(kv_cache), ptr<float>(kv_scales), ptr<int64_t>(slot_mapping), block_size, num_slots,
+                       cache_kind, (float)k_scale, (float)v_scale, tokens, dtype16(any), status_ptr(any), cur_stream());
+}
+void copy_blocks(Tensor& cache, const Tensor& pairs) {
+  TORCH_CHECK(pairs.scalar_type() == at::kLong && pairs.is_contiguous() && cache.is_contiguous());
+  const int64_t block_bytes = cache.stride(0) * cache.element_size();
+  TORCH_CHECK(block_bytes % 16 == 0);
+  const c10::cuda::CUDAGuard guard(cache.device());
+  b200::copy_blocks(cache.data_ptr(), pairs.data_ptr<int64_t>(), pairs.size(0), block_bytes, cur_stream());
+}
+void concat_and_cache_mla(const Tensor& kv_c, const Tensor& k_pe, Tensor& cache, const Tensor& slot_mapping) {
+  const bool rec = cache.scalar_type() == at::kByte;
+  const int rank = kv_c.size(-1), rope = k_pe.size(-1);
+  if (rec) TORCH_CHECK(rank == 512 && rope == 64 && cache.size(-1) == 656, "fp8_ds_mla needs 512+64 and 656-byte records");
+  const int64_t num_slots = cache.size(0) * cache.size(1);
+  const c10::cuda::CUDAGuard guard(kv_c.device());
+  b200::concat_and_cache_mla(kv_c.data_ptr(), k_pe.data_ptr(), cache.data_ptr(), slot_mapping.data_ptr<int64_t>(),
+                             kv_c.size(0), rank, rope, kv_c.stride(0), k_pe.stride(0), num_slots, rec, dtype16(kv_c),
+                             status_ptr(kv_c), cur_stream());
+}
+void indexer_k_quant_and_cache(const Tensor& k, Tensor& cache, const Tensor& slot_mapping, int64_t block_size,
+                               bool ue8m0) {
+  const int hd = k.size(-1);
+  TORCH_CHECK(hd % 32 == 0 && hd <= 128 && cache.scalar_type() == at::kByte);
+  const int64_t num_slots = cache.size(0) * block_size;
+  const c10::cuda::CUDAGuard guard(k.device());
+  b200::indexer_k_quant_and_cache(k.data_ptr(), cache.data_ptr(), slot_mapping.data_ptr<int64_t>(), k.size(0), hd,
+                                  block_size, num_slots, k.stride(0), ue8m0, dtype16(k), status_ptr(k), cur_stream());
+}
+
+// ------------------------------------------------------------------ activations
+void act_and_mul(Tensor& out, const Tensor& x, int64_t act, double p0, double p1) {
+  const int d = x.size(-1) / 2;
+  const int tokens = x.numel() / x.size(-1);
+  const c10::cuda::CUDAGuard guard(x.device());
+  b200::act_and_mul(out.data_ptr(), x.data_ptr(), tokens, d, x.dim() >= 2 ? x.stride(-2) : 2 * d,
+                    out.dim() >= 2 ? out.stride(-2) : d, act, (float)p0, (float)p1, dtype16(x), cur_stream());
+}
+void activation(Tensor& out, const Tensor& x, int64_t act, double p0) {
+  TORCH_CHECK(x.is_contiguous() && out.is_contiguous());
+  const c10::cuda::CUDAGuard guard(x.device());
+  b200::activation(out.data_ptr(), x.data_ptr(), x.numel(), act, (float)p0, dtype16(x), cur_stream());
+}
+void act_and_mul_quant(Tensor& out_q, const optional<Tensor>& scale_out, const optional<Tensor>& scale_in,
+                       const Tensor& x, int64_t act, double p0, double p1, int64_t group, bool ue8m0) {
+  TORCH_CHECK(x.is_contiguous() && out_q.is_contiguous());
+  const int d = x.size(-1) / 2;
+  const int tokens = x.numel() / x.size(-1);
+  const c10::cuda::CUDAGuard guard(x.device());
+  b200::act_and_mul_quant(out_q.data_ptr(), ptr<float>(scale_out), ptr<float>(scale_in), x.data_ptr(), tokens, d, act,
+                          (float)p0, (float)p1, group, ue8m0, dtype16(x), cur_stream());
+}
+
+// ------------------------------------------------------------------ attention
+int64_t kv_kind_of(const Tensor& cache, bool has_scales) {
+  if (cache.scalar_type() == at::kChar) return 1;
+  if (cache.scalar_type() == at::kFloat8_e4m3fn) return has_scales ? 2 : 3;
+  return 0;
+}
+
+void paged_attention_decode(Tensor& out, const Tensor& q, const Tensor& kv_cache, const optional<Tensor>& kv_scales,
+                            const Tensor& block_table, const Tensor& seq_lens,
+                            const optional<Tensor>& query_start_loc, double scale, int64_t window, double softcap,
+                            const optional<Tensor>& sinks, const optional<Tensor>& lse_out,
+                            const optional<Tensor>& workspace, int64_t num_splits, int64_t batch, int64_t max_q_len,
+                            double k_scale, double v_scale, bool causal) {
+  TORCH_CHECK(q.dim() == 3 && q.stride(2) == 1 && q.stride(1) == q.size(2), "q must be [T, Hq, D] with packed heads");
+  TORCH_CHECK(kv_cache.dim() == 5 && kv_cache.is_contiguous());
+  TORCH_CHECK(block_table.scalar_type() == at::kInt && seq_lens.scalar_type() == at::kInt);
+  TORCH_CHECK(out.is_contiguous());
+  b200::DecodeParams p{};
+  const int T = q.size(0), Hq = q.size(1), D = q.size(2);
+  p.out = out.data_ptr();
+  p.q = q.data_ptr();
+  p.q_stride = q.stride(0);
+  p.kv_cache = kv_cache.data_ptr();
+  p.kv_scales = ptr<float>(kv_scales);
+  p.block_table = block_table.data_ptr<int>();
+  p.seq_lens = seq_lens.data_ptr<int>();
+  p.query_start_loc = ptr<int>(query_start_loc);
+  p.sinks = ptr<float>(sinks);
+  p.lse_out = ptr<float>(lse_out);
+  p.num_q_heads = Hq;
+  p.num_kv_heads = kv_cache.size(3);
+  p.block_size = kv_cache.size(2);
+  p.max_blocks = block_table.size(1);
+  p.num_blocks = kv_cache.size(0);
+  p.num_splits = std::max<int64_t>(1, num_splits);
+  p.total_tokens = T;
+  p.scale = (float)scale;
+  p.softcap = (float)softcap;
+  p.k_scale = (float)k_scale;
+  p.v_scale = (float)v_scale;
+  p.window = (int)window;
+  p.causal = causal;
+  TORCH_CHECK(p.block_size % 16 == 0, "block_size must be a multiple of 16");
+  if (p.num_splits > 1) {
+    TORCH_CHECK(workspace.has_value(), "split-KV decode needs a workspace");
+    const int64_t need = p.num_splits * (int64_t)T * Hq * (D + 1);
+    TORCH_CHECK(workspace->scalar_type() == at::kFloat && workspace->numel() >= need, "decode workspace too small");
+    p.part_out = workspace->data_ptr<float>();
+    p.part_lse = p.part_out + p.num_splits * (int64_t)T * Hq * D;
+  }
+  p.status = reinterpret_cast<b200::StatusWord*>(status_ptr(q));
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int rc = b200::paged_attention_decode(p, D, kv_kind_of(kv_cache, kv_scales.has_value()), dtype16(q), batch,
+                                              max_q_len, cur_stream());
+  TORCH_CHECK(rc == 0, "paged_attention_decode: unsupported head_dim ", D);
+}
+
+void attention_prefill(Tensor& out, const Tensor& q, const Tensor& k_src, const optional<Tensor>& v_src,
+                       const optional<Tensor>& block_table, const optional<Tensor>& seq_lens,
+                       const Tensor& query_start_loc, const optional<Tensor>& kv_start_loc, double scale,
+                       int64_t window, double softcap, const optional<Tensor>& sinks,
+                       const optional<Tensor>& lse_out, int64_t batch, int64_t max_q_len, bool causal) {
+  TORCH_CHECK(q.dim() == 3 && q.stride(2) == 1 && q.stride(1) == q.size(2));
+  b200::PrefillParams p{};
+  const int T = q.size(0), Hq = q.size(1), DQK = q.size(2);
+  const bool paged = block_table.has_value();
+  int Hkv, DV;
+  int64_t total_kv = 0, ks = 0, vs = 0;
+  const void* kptr = k_src.data_ptr();
+  const void* vptr = nullptr;
+  if (paged) {
+    TORCH_CHECK(k_src.dim() == 5 && k_src.is_contiguous(), "paged mode expects the [nb,2,bs,Hkv,D] cache");
+    TORCH_CHECK(k_src.scalar_type() == q.scalar_type(), "tcgen05 prefill needs a 16-bit cache of the query dtype");
+    Hkv = k_src.size(3);
+    DV = k_src.size(4);
+    p.block_size = k_src.size(2);
+    p.num_blocks = k_src.size(0);
+    p.max_blocks = block_table->size(1);
+    p.block_table = block_table->data_ptr<int>();
+    p.seq_lens = seq_lens->data_ptr<int>();
+    TORCH_CHECK(p.block_size % 16 == 0 && (128 % p.block_size == 0 || p.block_size % 128 == 0),
+                "block_size must be 16/32/64 or a multiple of 128");
+    vptr = kptr;
+  } else {
+    TORCH_CHECK(v_src.has_value() && kv_start_loc.has_value());
+    TORCH_CHECK(k_src.dim() == 3 && k_src.stride(2) == 1 && k_src.stride(1) == k_src.size(2));
+    TORCH_CHECK(v_src->dim() == 3 && v_src->stride(2) == 1 && v_src->stride(1) == v_src->size(2));
+    Hkv = k_src.size(1);
+    DV = v_src->size(2);
+    total_kv = k_src.size(0);
+    ks = k_src.stride(0);
+    vs = v_src->stride(0);
+    vptr = v_src->data_ptr();
+    p.kv_start_loc = kv_start_loc->data_ptr<int>();
+  }
+  p.out = out.data_ptr();
+  p.lse_out = ptr<float>(lse_out);
+  p.query_start_loc = query_start_loc.data_ptr<int>();
+  p.sinks = ptr<float>(sinks);
+  p.num_q_heads = Hq;
+  p.num_kv_heads = Hkv;
+  const int g = Hq / Hkv;
+  p.gp = (128 % g == 0) ? g : 1;
+  p.total_q = T;
+  p.scale = (float)scale;
+  p.softcap = (float)softcap;
+  p.window = (int)window;
+  p.causal = causal;
+  p.paged = paged;
+  p.status = reinterpret_cast<b200::StatusWord*>(status_ptr(q));
+  TORCH_CHECK(out.is_contiguous() && out.size(-1) == DV);
+  TORCH_CHECK(q.stride(0) % 8 == 0, "q token stride must be a multiple of 8 elements");
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int rc = b200::attention_prefill(p, q.data_ptr(), q.stride(0), kptr, vptr, ks, vs, total_kv, DQK, DV,
+                                         dtype16(q), batch, max_q_len, cur_stream());
+  TORCH_CHECK(rc == 0, "attention_prefill: unsupported head dims ", DQK, "/", DV);
+}
+
+// ------------------------------------------------------------------ sampling
+void argmax(Tensor& out, const Tensor& logits) {
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && out.scalar_type() == at::kLong);
+  const c10::cuda::CUDAGuard guard(logits.device());
+  b200::argmax(out.data_ptr<int64_t>(), logits.data_ptr(), logits.size(0), logits.size(1), logits.stride(0),
+               dtype_code(logits), cur_stream());
+}
+void sample(Tensor& out, const Tensor& logits, const Tensor& temperature, const optional<Tensor>& top_k,
+            const optional<Tensor>& top_p, const optional<Tensor>& min_p, const Tensor& uniform) {
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && out.scalar_type() == at::kLong);
+  const c10::cuda::CUDAGuard guard(logits.device());
+  b200::sample(out.data_ptr<int64_t>(), logits.data_ptr(), logits.size(0), logits.size(1), logits.stride(0),
+               temperature.data_ptr<float>(), ptr<int>(top_k), ptr<float>(top_p), ptr<float>(min_p),
+               uniform.data_ptr<float>(), dtype_code(logits), cur_stream());
+}
+void apply_penalties(Tensor& logits, const optional<Tensor>& prompt_mask, const optional<Tensor>& output_counts,
+                     const optional<Tensor>& rep, const optional<Tensor>& presence,
+                     const optional<Tensor>& frequency) {
+  const c10::cuda::CUDAGuard guard(logits.device());
+  b200::apply_penalties(logits.data_ptr(), ptr<int>(prompt_mask), ptr<int>(output_counts), ptr<float>(rep),
+                        ptr<float>(presence), ptr<float>(frequency), logits.size(0), logits.size(1), logits.stride(0),
+                        dtype_code(logits), cur_stream());
+}
+void advance_step(Tensor& input_ids, Tensor& positions, Tensor& seq_lens, Tensor& slot_mapping, const Tensor& sampled,
+                  const Tensor& block_table, int64_t block_size, int64_t batch, const optional<Tensor>& token_log,
+                  int64_t log_col) {
+  const c10::cuda::CUDAGuard guard(input_ids.device());
+  b200::advance_step(input_ids.data_ptr<int64_t>(), positions.data_ptr<int64_t>(), seq_lens.data_ptr<int>(),
+                     slot_mapping.data_ptr<int64_t>(), sampled.data_ptr<int64_t>(), block_table.data_ptr<int>(),
+                     block_table.size(1), block_size, batch, ptr<int64_t>(token_log), log_col,
+                     token_log.has_value() ? token_log->stride(0) : 0, cur_stream());
+}
+void embedding(Tensor& out, const Tensor& table, const Tensor& ids, int64_t vocab_start) {
+  TORCH_CHECK(table.is_contiguous() && out.is_contiguous() && ids.scalar_type() == at::kLong);
+  TORCH_CHECK(table.size(1) % 8 == 0);
+  const c10::cuda::CUDAGuard guard(table.device());
+  b200::embedding(out.data_ptr(), table.data_ptr(), ids.data_ptr<int64_t>(), ids.numel(), table.size(1), table.size(0),
+                  vocab_start, dtype16(table), cur_stream());
+}
+
+}  // namespace
+
+TORCH_LIBRARY(b200, m) {
+  m.def("get_status(int device) -> Tensor", &get_status);
+  m.def("gemm(Tensor(a!) out, Tensor a, Tensor w, Tensor? bias, Tensor? residual, int force_bn) -> ()", &gemm);
+  m.def("rms_norm(Tensor(a!) out, Tensor x, Tensor weight, float eps, bool gemma) -> ()", &rms_norm);
+  m.def("fused_add_rms_norm(Tensor(a!) x, Tensor(b!) residual, Tensor weight, float eps, bool gemma) -> ()",
+        &fused_add_rms_norm);
+  m.def("head_rms_norm(Tensor(a!) x, Tensor weight, float eps, int heads, int head_dim) -> ()", &head_rms_norm);
+  m.def(
+      "rms_norm_quant(Tensor(a!) out_q, Tensor(b!)? scale_out, Tensor? scale_in, Tensor x, Tensor(c!)? residual, "
+      "Tensor weight, float eps, int qmode, int group, bool ue8m0, float scale_ub) -> ()",
+      &rms_norm_quant);
+  m.def(
+      "rope_and_cache(Tensor? positions, Tensor(a!)? q, Tensor(b!)? k, Tensor? v, Tensor? cos_sin, int head_dim, "
+      "int num_q, int num_kv, bool is_neox, int rot_offset, bool inverse, Tensor(c!)? kv_cache, "
+      "Tensor(d!)? kv_scales, Tensor? slot_mapping, int cache_kind, float k_scale, float v_scale) -> ()",
+      &rope_and_cache);
+  m.def("copy_blocks(Tensor(a!) cache, Tensor pairs) -> ()", &copy_blocks);
+  m.def("concat_and_cache_mla(Tensor kv_c, Tensor k_pe, Tensor(a!) cache, Tensor slot_mapping) -> ()",
+        &concat_and_cache_mla);
+  m.def(
+      "indexer_k_quant_and_cache(Tensor k, Tensor(a!) cache, Tensor slot_mapping, int block_size, bool ue8m0) -> ()",
+      &indexer_k_quant_and_cache);
+  m.def("act_and_mul(Tensor(a!) out, Tensor x, int act, float p0, float p1) -> ()", &act_and_mul);
+  m.def("activation(Tensor(a!) out, Tensor x, int act, float p0) -> ()", &activation);
+  m.def(
+      "act_and_mul_quant(Tensor(a!) out_q, Tensor(b!)? scale_out, Tensor? scale_in, Tensor x, int act, float p0, "
+      "float p1, int group, bool ue8m0) -> ()",
+      &act_and_mul_quant);
+  m.def(
+      "paged_attention_decode(Tensor(a!) out, Tensor q, Tensor kv_cache, Tensor? kv_scales, Tensor block_table, "
+      "Tensor seq_lens, Tensor? query_start_loc, float scale, int window, float softcap, Tensor? sinks, "
+      "Tensor(b!)? lse_out, Tensor(c!)? workspace, int num_splits, int batch, int max_q_len, float k_scale, "
+      "float v_scale, bool causal) -> ()",
+      &paged_attention_decode);
+  m.def(
+      "attention_prefill(Tensor(a!) out, Tensor q, Tensor k_src, Tensor? v_src, Tensor? block_table, "
+      "Tensor? seq_lens, Tensor query_start_loc, Tensor? kv_start_loc, float scale, int window, float softcap, "
+      "Tensor? sinks, Tensor(b!)? lse_out, int batch, int max_q_len, bool causal) -> ()",
+      &attention_prefill);
+  m.def("argmax(Tensor(a!) out, Tensor logits) -> ()", &argmax);
+  m.def(
+      "sample(Tensor(a!) out, Tensor logits, Tensor temperature, Tensor? top_k, Tensor? top_p, Tensor? min_p, "
+      "Tensor uniform) -> ()",
+      &sample);
+  m.def(
+      "apply_penalties(Tensor(a!) logits, Tensor? prompt_mask, Tensor? output_counts, Tensor? rep, Tensor? presence, "
+      "Tensor? frequency) -> ()",
+      &apply_penalties);
+  m.def(
+      "advance_step(Tensor(a!) input_ids, Tensor(b!) positions, Tensor(c!) seq_lens, Tensor(d!) slot_mapping, "
+      "Tensor sampled, Tensor block_table, int block_size, int batch, Tensor(e!)? token_log, int log_col) -> ()",
+      &advance_step);
+  m.def("embedding(Tensor(a!) out, Tensor table, Tensor ids, int vocab_start) -> ()", &embedding);
+}

@@ -1,0 +1,99 @@
+// Host-callable launchers of every CUDA kernel in this library.  The .cu files are
+// free of torch headers; bindings.cpp adapts torch tensors to these entry points.
+// dtype codes: 0 = bf16, 1 = fp16, 2 = fp32.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "status.h"
+
+namespace b200 {
+
+struct DecodeParams {
+  void* out;                 // [T, Hq, D] (T dtype)
+  float* part_out;           // [splits, T, Hq, D]
+  float* part_lse;           // [splits, T, Hq]
+  const void* q;             // [T, Hq, D] with token stride q_stride (elements)
+  const void* kv_cache;
+  const float* kv_scales;    // kinds 1, 2
+  const int* block_table;    // [B, max_blocks]
+  const int* seq_lens;       // [B]
+  const int* query_start_loc;  // [B+1] or null (one token per sequence)
+  const float* sinks;        // [Hq] or null
+  float* lse_out;            // [Hq, T] or null (natural-log LSE of the final result)
+  int64_t q_stride;
+  int num_q_heads, num_kv_heads, block_size, max_blocks, num_splits, total_tokens;
+  int64_t num_blocks;
+  float scale, softcap, k_scale, v_scale;
+  int window;                // <=0: none
+  int causal;
+  StatusWord* status;
+};
+
+struct PrefillParams {
+  void* out;                     // [T, Hq, DV]
+  float* lse_out;                // [Hq, T] or null
+  const int* block_table;        // [B, max_blocks] (paged) or null
+  const int* seq_lens;           // [B] kv length (paged) ; contiguous: derived from kv_start_loc
+  const int* query_start_loc;    // [B+1]
+  const int* kv_start_loc;       // [B+1] (contiguous mode) or null
+  const float* sinks;            // [Hq] or null
+  int num_q_heads, num_kv_heads, gp;  // gp: heads packed per tile (divides 128)
+  int block_size, max_blocks;
+  int64_t num_blocks;
+  int total_q;
+  float scale, softcap;
+  int window, causal, paged;
+  StatusWord* status;
+};
+
+// ---- gemm_tcgen05.cu
+void gemm_tn(const void* A, const void* W, void* C, const void* bias, const void* residual, int M, int N, int K,
+             int lda, int ldw, int ldc, int ldr, int dtype, cudaStream_t stream, void* status, int force_bn);
+// ---- norm.cu
+void rms_norm(void* out, void* x, void* residual, const void* weight, float eps, int tokens, int hidden,
+              int64_t x_stride, int64_t out_stride, int dtype, int mode, cudaStream_t stream);
+void head_rms_norm(void* x, const void* weight, float eps, int tokens, int heads, int head_dim, int64_t token_stride,
+                   int dtype, cudaStream_t stream);
+void rms_norm_quant(void* out_q, float* scale_out, const float* scale_in, const void* x, void* residual,
+                    const void* weight, float eps, int tokens, int hidden, int dtype, int qmode, int group, int ue8m0,
+                    float scale_ub, cudaStream_t stream);
+// ---- rope_cache.cu
+void rope_and_cache(const int64_t* positions, void* q, void* k, const void* v, const float* cos_sin, int rot,
+                    int head_dim, int num_q, int num_kv, int64_t q_stride, int64_t k_stride, int64_t v_stride,
+                    int is_neox, int rot_offset, int inverse, void* kv_cache, float* kv_scales,
+                    const int64_t* slot_mapping, int block_size, int64_t num_slots, int cache_kind, float k_scale,
+                    float v_scale, int tokens, int dtype, void* status, cudaStream_t stream);
+void copy_blocks(void* cache, const int64_t* pairs, int num_pairs, int64_t block_bytes, cudaStream_t stream);
+void concat_and_cache_mla(const void* kv_c, const void* k_pe, void* cache, const int64_t* slot_mapping, int tokens,
+                          int rank, int rope, int64_t kvc_stride, int64_t kpe_stride, int64_t num_slots,
+                          int fp8_record, int dtype, void* status, cudaStream_t stream);
+void indexer_k_quant_and_cache(const void* k, void* cache, const int64_t* slot_mapping, int tokens, int head_dim,
+                               int block_size, int64_t num_slots, int64_t k_stride, int ue8m0, int dtype, void* status,
+                               cudaStream_t stream);
+// ---- activation.cu
+void act_and_mul(void* out, const void* x, int tokens, int d, int64_t x_stride, int64_t out_stride, int act, float p0,
+                 float p1, int dtype, cudaStream_t stream);
+void activation(void* out, const void* x, int64_t n, int act, float p0, int dtype, cudaStream_t stream);
+void act_and_mul_quant(void* out_q, float* scale_out, const float* scale_in, const void* x, int tokens, int d, int act,
+                       float p0, float p1, int group, int ue8m0, int dtype, cudaStream_t stream);
+// ---- attention
+int paged_attention_decode(const DecodeParams& p, int head_dim, int kv_kind, int dtype, int batch, int max_q_len,
+                           cudaStream_t stream);
+int attention_prefill(const PrefillParams& p, const void* q, int64_t q_stride, const void* k_src, const void* v_src,
+                      int64_t k_tok_stride, int64_t v_tok_stride, int64_t total_kv, int dqk, int dv, int dtype,
+                      int batch, int max_q_len, cudaStream_t stream);
+// ---- sampling.cu
+void argmax(int64_t* out, const void* logits, int rows, int vocab, int64_t stride, int dtype, cudaStream_t stream);
+void sample(int64_t* out, const void* logits, int rows, int vocab, int64_t stride, const float* temperature,
+            const int* top_k, const float* top_p, const float* min_p, const float* uniform, int dtype,
+            cudaStream_t stream);
+void apply_penalties(void* logits, const int* prompt_mask, const int* output_counts, const float* rep,
+                     const float* presence, const float* frequency, int rows, int vocab, int64_t stride, int dtype,
+                     cudaStream_t stream);
+void advance_step(int64_t* input_ids, int64_t* positions, int* seq_lens, int64_t* slot_mapping, const int64_t* sampled,
+                  const int* block_table, int max_blocks, int block_size, int batch, int64_t* token_log, int log_col,
+                  int log_stride, cudaStream_t stream);
+void embedding(void* out, const void* table, const int64_t* ids, int tokens, int hidden, int64_t vocab,
+               int64_t vocab_start, int dtype, cudaStream_t stream);
+
+}  // namespace b200

@@ -1,0 +1,245 @@
+"""``LLMEngine`` (step loop) and ``LLM`` (offline ``generate`` API).
+
+``LLM(model=<config | path | dict>, ...)`` mirrors the call a vLLM user makes:
+``llm.generate(prompts, sampling_params)`` returns one ``RequestOutput`` per prompt with
+token ids, text (when a tokenizer is available), finish reason and per-request timing
+(TTFT / TPOT).  Sleep / wake, pause / resume and profiling hooks are exposed the way the
+reference's examples use them (examples/features/{sleep,pause_resume,profiling}).
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from typing import Any, Iterable, Optional, Sequence, Union
+
+import torch
+
+from ..config import CacheConfig, EngineConfig, ModelConfig, ParallelConfig, SchedulerConfig
+from .block_manager import KVCacheManager
+from .model_runner import ModelRunner
+from .sampling_params import (CompletionOutput, Request, RequestMetrics, RequestOutput, RequestStatus,
+                              SamplingParams)
+from .scheduler import Scheduler
+
+
+class EngineDeadError(RuntimeError):
+    """Raised to every caller once a step failed; the engine refuses further work."""
+
+
+class LLMEngine:
+    def __init__(self, cfg: EngineConfig, tokenizer=None):
+        self.cfg = cfg
+        self.tokenizer = tokenizer
+        self.runner = ModelRunner(cfg)
+        nb = self.runner.determine_num_blocks()
+        self.runner.init_kv_cache(nb)
+        self.kv = KVCacheManager(nb, cfg.cache.block_size, cfg.cache.enable_prefix_caching)
+        self.scheduler = Scheduler(cfg.scheduler, self.kv)
+        self.runner.capture_graphs()
+        self._ids = itertools.count()
+        self.dead: Optional[BaseException] = None
+        self.requests: dict[str, Request] = {}
+        self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0}
+        self.step_hooks: list = []
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
+                    request_id: Optional[str] = None, prompt: Optional[str] = None,
+                    arrival_time: Optional[float] = None) -> str:
+        if self.dead is not None:
+            raise EngineDeadError(str(self.dead))
+        rid = request_id or f"req-{next(self._ids)}"
+        req = Request(rid, list(prompt_token_ids), params or SamplingParams(), self.cfg.model.eos_token_id, prompt,
+                      arrival_time)
+        self.scheduler.add_request(req)
+        self.requests[rid] = req
+        return rid
+
+    def abort_request(self, request_id: str) -> bool:
+        self.requests.pop(request_id, None)
+        return self.scheduler.abort(request_id)
+
+    def has_unfinished_requests(self) -> bool:
+        return self.scheduler.has_unfinished()
+
+    # ------------------------------------------------------------------ stepping
+    def step(self) -> list[Request]:
+        """One scheduler iteration; returns the requests that finished in it."""
+        if self.dead is not None:
+            raise EngineDeadError(str(self.dead))
+        so = self.scheduler.schedule()
+        if so.is_empty:
+            if self.scheduler.has_unfinished() and not self.scheduler.paused:
+                raise RuntimeError("scheduler made no progress: KV cache too small for the waiting request")
+            return []
+        try:
+            for hook in self.step_hooks:
+                hook("before", self.stats["steps"])
+            sampled = self.runner.execute(so)
+            for hook in self.step_hooks:
+                hook("after", self.stats["steps"])
+        except BaseException as e:  # a failed step poisons the engine (memory is released)
+            self.dead = e
+            self._release_all()
+            raise EngineDeadError(f"engine step failed: {e!r}") from e
+        now = time.perf_counter()
+        finished = self.scheduler.update(so, sampled, now)
+        self.stats["steps"] += 1
+        self.stats["decode_tokens"] += so.num_decode
+        self.stats["prefill_tokens"] += so.num_tokens - so.num_decode
+        self.stats["preemptions"] = self.scheduler.num_preemptions
+        for r in finished:
+            self.requests.pop(r.request_id, None)
+        return finished
+
+    def _release_all(self) -> None:
+        for r in list(self.scheduler.running) + list(self.scheduler.waiting):
+            self.kv.free(r)
+        self.scheduler.running.clear()
+        self.scheduler.waiting.clear()
+
+    def make_output(self, r: Request) -> RequestOutput:
+        text = None
+        if self.tokenizer is not None:
+            text = self.tokenizer.decode(r.output_token_ids, skip_special_tokens=True)
+        reason = {RequestStatus.FINISHED_STOPPED: "stop", RequestStatus.FINISHED_LENGTH: "length",
+                  RequestStatus.FINISHED_ABORTED: "abort"}.get(r.status)
+        return RequestOutput(r.request_id, r.prompt, r.prompt_token_ids,
+                             [CompletionOutput(0, list(r.output_token_ids), text, reason)], r.status.finished,
+                             RequestMetrics(r.arrival_time, r.first_token_time, r.finish_time, list(r.token_times)),
+                             r.num_cached_tokens)
+
+
+def _resolve_model(model: Union[str, dict, ModelConfig], **overrides) -> tuple[ModelConfig, Any]:
+    tokenizer = None
+    if isinstance(model, ModelConfig):
+        mc = model
+        for k, v in overrides.items():
+            setattr(mc, k, v)
+        mc.__post_init__()
+    elif isinstance(model, dict):
+        mc = ModelConfig.from_hf_dict(model, **overrides) if "hidden_size" in model and "architectures" in model \
+            else ModelConfig(**{**model, **overrides})
+    else:
+        mc = ModelConfig.from_pretrained(model, **overrides)
+        try:
+            from transformers import AutoTokenizer
+
+            tokenizer = AutoTokenizer.from_pretrained(model)
+        except Exception:
+            tokenizer = None
+    return mc, tokenizer
+
+
+class LLM:
+    """Offline inference entry point.
+
+    >>> llm = LLM(model_config, tensor_parallel_size=1, max_model_len=2048)
+    >>> outs = llm.generate([[1, 2, 3]], SamplingParams(max_tokens=8))
+    """
+
+    def __init__(self, model: Union[str, dict, ModelConfig], *, tensor_parallel_size: int = 1,
+                 pipeline_parallel_size: int = 1, data_parallel_size: int = 1, enable_expert_parallel: bool = False,
+                 dtype: Any = None, quantization: Optional[str] = None, kv_cache_dtype: str = "auto",
+                 block_size: int = 64, max_model_len: int = 4096, max_num_seqs: int = 256,
+                 max_num_batched_tokens: int = 8192, gpu_memory_utilization: float = 0.88,
+                 num_gpu_blocks: Optional[int] = None, enable_prefix_caching: bool = False,
+                 enable_chunked_prefill: bool = True, enforce_eager: bool = False, device: Optional[str] = None,
+                 load_format: str = "auto", seed: int = 0, tokenizer: Any = None, enable_sleep_mode: bool = False,
+                 additional_config: Optional[dict] = None):
+        overrides = {"seed": seed}
+        if dtype is not None:
+            overrides["dtype"] = dtype
+        if quantization is not None:
+            overrides["quantization"] = quantization
+        mc, tok = _resolve_model(model, **overrides)
+        if device is None:
+            device = "cuda" if torch.cuda.is_available() else "cpu"
+        cfg = EngineConfig(
+            model=mc,
+            cache=CacheConfig(block_size=block_size, num_gpu_blocks=num_gpu_blocks,
+                              gpu_memory_utilization=gpu_memory_utilization, kv_cache_dtype=kv_cache_dtype,
+                              enable_prefix_caching=enable_prefix_caching),
+            parallel=ParallelConfig(tensor_parallel_size, pipeline_parallel_size, data_parallel_size,
+                                    enable_expert_parallel),
+            scheduler=SchedulerConfig(max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens,
+                                      max_model_len=max_model_len, enable_chunked_prefill=enable_chunked_prefill),
+            device=device, enforce_eager=enforce_eager, load_format=load_format,
+            additional_config=additional_config or {})
+        self.config = cfg
+        self.engine = LLMEngine(cfg, tokenizer or tok)
+        self.tokenizer = self.engine.tokenizer
+
+    # ------------------------------------------------------------------ generate
+    def _to_ids(self, p) -> tuple[list[int], Optional[str]]:
+        if isinstance(p, str):
+            if self.tokenizer is None:
+                raise ValueError("text prompt given but no tokenizer is available")
+            return self.tokenizer.encode(p), p
+        if isinstance(p, dict):
+            if "prompt_token_ids" in p:
+                return list(p["prompt_token_ids"]), p.get("prompt")
+            return self._to_ids(p["prompt"])
+        return list(p), None
+
+    def generate(self, prompts: Union[str, Sequence], sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
+                 use_tqdm: bool = False) -> list[RequestOutput]:
+        if isinstance(prompts, str) or (prompts and isinstance(prompts[0], int)):
+            prompts = [prompts]
+        n = len(prompts)
+        if sampling_params is None or isinstance(sampling_params, SamplingParams):
+            sps = [sampling_params or SamplingParams()] * n
+        else:
+            sps = list(sampling_params)
+        now = time.perf_counter()
+        order = []
+        reqs: dict[str, Request] = {}
+        for p, sp in zip(prompts, sps):
+            ids, text = self._to_ids(p)
+            import copy
+
+            rid = self.engine.add_request(ids, copy.copy(sp), prompt=text, arrival_time=now)
+            order.append(rid)
+            reqs[rid] = self.engine.requests[rid]
+        done: dict[str, Request] = {}
+        while len(done) < n:
+            for r in self.engine.step():
+                if r.request_id in reqs:
+                    done[r.request_id] = r
+            if not self.engine.has_unfinished_requests() and len(done) < n:
+                break
+        return [self.engine.make_output(reqs[rid]) for rid in order]
+
+    # ------------------------------------------------------------------ control surface
+    def pause_generation(self) -> None:
+        self.engine.scheduler.pause()
+
+    def resume_generation(self) -> None:
+        self.engine.scheduler.resume()
+
+    def sleep(self, level: int = 1) -> None:
+        from ..device_allocator.cumem import get_mem_allocator_instance
+
+        get_mem_allocator_instance().sleep(("weights",) if level == 1 else tuple())
+
+    def wake_up(self, tags: Optional[list[str]] = None) -> None:
+        from ..device_allocator.cumem import get_mem_allocator_instance
+
+        get_mem_allocator_instance().wake_up(tags)
+
+    def start_profile(self, trace_dir: str = "./b200_trace") -> None:
+        self._prof = torch.profiler.profile(
+            activities=[torch.profiler.ProfilerActivity.CPU] +
+                       ([torch.profiler.ProfilerActivity.CUDA] if torch.cuda.is_available() else []),
+            on_trace_ready=torch.profiler.tensorboard_trace_handler(trace_dir))
+        self._prof.start()
+
+    def stop_profile(self) -> None:
+        if getattr(self, "_prof", None) is not None:
+            self._prof.stop()
+            self._prof = None
+
+    def get_metrics(self) -> dict:
+        e = self.engine
+        return {**e.stats, "kv_cache_usage": e.kv.usage, "num_running": len(e.scheduler.running),
+                "num_waiting": len(e.scheduler.waiting)}

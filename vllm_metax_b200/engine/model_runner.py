@@ -1,0 +1,308 @@
+"""Executes one scheduler step on this rank's GPU.
+
+Responsibilities: own the model and the paged KV cache, turn a ``SchedulerOutput`` into
+flat device inputs (one pinned staging buffer, one H2D copy per step), run the model
+(eager for prefill / mixed batches, CUDA-graph replay for pure-decode batches at
+bucketed batch sizes), sample, and read the sampled tokens back.
+
+Every rank of a TP group runs the same runner on the same scheduler decisions (SPMD),
+so no broadcast of inputs is needed; logits are all-gathered and sampling is
+deterministic, which keeps ranks in lock step.
+
+Parity: replaces upstream GPUModelRunner for the standalone engine (the reference patches
+its batch reordering, vllm_metax/patch/performance/speculative_decode_perf.py:115-155, which
+the scheduler here does natively).
+"""
+from __future__ import annotations
+
+import time
+from typing import Optional
+
+import numpy as np
+import torch
+
+from .. import _custom_ops as ops
+from .. import envs
+from ..attention.metadata import AttentionMetadata, ForwardContext, set_forward_context
+from ..config import EngineConfig
+from ..layers.attention import PagedGQABackend
+from ..parallel import state as ps
+from .loader import build_model
+from .scheduler import SchedulerOutput
+
+
+def _graph_buckets(max_seqs: int) -> list[int]:
+    b = [1, 2, 4, 8]
+    b += list(range(16, 129, 16))
+    b += list(range(160, 513, 32))
+    return [x for x in b if x <= max_seqs] + ([max_seqs] if max_seqs not in b else [])
+
+
+class ModelRunner:
+    def __init__(self, cfg: EngineConfig):
+        self.cfg = cfg
+        par = cfg.parallel
+        ps.init_distributed(par.tensor_parallel_size, par.pipeline_parallel_size, par.data_parallel_size,
+                            par.decode_context_parallel_size, device=cfg.device)
+        if cfg.device == "cuda":
+            self.device = torch.device("cuda", ps.local_rank() if torch.cuda.device_count() > 1 else 0)
+            torch.cuda.set_device(self.device)
+            if not ops.load_native():
+                raise RuntimeError("native library missing on a GPU box; run python -m vllm_metax_b200._build")
+        else:
+            self.device = torch.device("cpu")
+        self.is_cuda = self.device.type == "cuda"
+        torch.manual_seed(cfg.model.seed)
+        with torch.no_grad():
+            self.model = build_model(cfg, self.device)
+        self.block_size = cfg.cache.block_size
+        sc = cfg.scheduler
+        self.max_tokens = max(sc.max_num_batched_tokens, sc.max_num_seqs)
+        self.max_seqs = sc.max_num_seqs
+        self.max_blocks_per_seq = (sc.max_model_len + self.block_size - 1) // self.block_size
+        self.kv_caches: list = []
+        self.num_blocks = 0
+        self._alloc_inputs()
+        self.graphs: dict[int, tuple] = {}
+        self.use_graphs = self.is_cuda and not cfg.enforce_eager and envs.B200_CUDA_GRAPHS
+        self.launch_count = 0
+        self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count if self.is_cuda else 1
+
+    # ------------------------------------------------------------------ buffers
+    def _alloc_inputs(self) -> None:
+        dev, T, B, MB = self.device, self.max_tokens, self.max_seqs, self.max_blocks_per_seq
+        # one int64 staging area: [input_ids T | positions T | slot_mapping T] and one int32 area
+        self.n64 = 3 * T
+        self.n32 = (B + 1) + B + B * MB + (B + 1)
+        pin = self.is_cuda
+        self.h64 = torch.zeros(self.n64, dtype=torch.int64, pin_memory=pin)
+        self.h32 = torch.zeros(self.n32, dtype=torch.int32, pin_memory=pin)
+        self.d64 = torch.zeros(self.n64, dtype=torch.int64, device=dev)
+        self.d32 = torch.zeros(self.n32, dtype=torch.int32, device=dev)
+        self.h64_np, self.h32_np = self.h64.numpy(), self.h32.numpy()
+        self.input_ids = self.d64[:T]
+        self.positions = self.d64[T:2 * T]
+        self.slot_mapping = self.d64[2 * T:3 * T]
+        o = 0
+        self.query_start_loc = self.d32[o:o + B + 1]; o += B + 1
+        self.seq_lens = self.d32[o:o + B]; o += B
+        self.block_table = self.d32[o:o + B * MB].view(B, MB); o += B * MB
+        self.prefill_qsl = self.d32[o:o + B + 1]
+        self.sampled = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.sampled_host = torch.zeros(B, dtype=torch.int64, pin_memory=pin)
+        self.sample_idx = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.sample_idx_host = torch.zeros(B, dtype=torch.int64, pin_memory=pin)
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    def kv_bytes_per_block(self) -> int:
+        spec = self.model.kv_cache_spec()
+        n = self.model.num_kv_layers()
+        from ..layers.attention import KV_DTYPES
+
+        if spec["kind"] == "gqa":
+            dt = KV_DTYPES[self.cfg.cache.kv_cache_dtype] or self.cfg.model.dtype
+            per = 2 * self.block_size * spec["num_kv_heads"] * spec["head_size"] * torch.empty((), dtype=dt).element_size()
+            if self.cfg.cache.kv_cache_dtype.endswith("per_token_head"):
+                per += 2 * self.block_size * spec["num_kv_heads"] * 4
+            return per * n
+        return self.model.kv_bytes_per_block(self.block_size, self.cfg.cache.kv_cache_dtype)
+
+    def determine_num_blocks(self) -> int:
+        c = self.cfg.cache
+        if c.num_gpu_blocks:
+            return c.num_gpu_blocks
+        if not self.is_cuda:
+            return 512
+        torch.cuda.synchronize()
+        free, total = torch.cuda.mem_get_info(self.device)
+        budget = free - int(total * (1.0 - c.gpu_memory_utilization)) - (6 << 30)  # activation head-room
+        n = max(16, budget // self.kv_bytes_per_block())
+        want = self.max_seqs * self.max_blocks_per_seq
+        return int(min(n, max(want, 64)))
+
+    def init_kv_cache(self, num_blocks: int) -> None:
+        self.num_blocks = num_blocks
+        spec = self.model.kv_cache_spec()
+        if spec["kind"] == "gqa":
+            self.kv_caches = [
+                PagedGQABackend.allocate(num_blocks, self.block_size, spec["num_kv_heads"], spec["head_size"],
+                                         self.cfg.model.dtype, self.cfg.cache.kv_cache_dtype, self.device)
+                for _ in range(self.model.num_kv_layers())]
+        else:
+            self.kv_caches = self.model.allocate_kv_cache(num_blocks, self.block_size, self.cfg.cache.kv_cache_dtype,
+                                                          self.device)
+
+    # ------------------------------------------------------------------ input prep
+    def _prepare(self, so: SchedulerOutput, pad_to: int = 0):
+        T_, B_, MB = self.max_tokens, self.max_seqs, self.max_blocks_per_seq
+        ids, pos, slots = self.h64_np[:T_], self.h64_np[T_:2 * T_], self.h64_np[2 * T_:3 * T_]
+        o = 0
+        qsl = self.h32_np[o:o + B_ + 1]; o += B_ + 1
+        sl = self.h32_np[o:o + B_]; o += B_
+        bt = self.h32_np[o:o + B_ * MB].reshape(B_, MB); o += B_ * MB
+        pqsl = self.h32_np[o:o + B_ + 1]
+        bs = self.block_size
+        t = 0
+        qsl[0] = 0
+        max_q = max_seq = 0
+        sample_rows = []
+        sample_reqs = []
+        for i, s in enumerate(so.scheduled):
+            r = s.request
+            n, p0 = s.num_new_tokens, s.start_pos
+            if n == 1:
+                ids[t] = r.token_at(p0)
+                pos[t] = p0
+                slots[t] = r.block_ids[p0 // bs] * bs + p0 % bs
+            else:
+                toks = r.all_token_ids[p0:p0 + n] if r.output_token_ids else r.prompt_token_ids[p0:p0 + n]
+                ids[t:t + n] = toks
+                ar = np.arange(p0, p0 + n)
+                pos[t:t + n] = ar
+                blk = np.asarray(r.block_ids, dtype=np.int64)
+                slots[t:t + n] = blk[ar // bs] * bs + ar % bs
+            t += n
+            qsl[i + 1] = t
+            sl[i] = p0 + n
+            nb = len(r.block_ids)
+            bt[i, :nb] = r.block_ids
+            max_q = max(max_q, n)
+            max_seq = max(max_seq, p0 + n)
+            if s.samples:
+                sample_rows.append(t - 1)
+                sample_reqs.append(r)
+        B = len(so.scheduled)
+        nd = so.num_decode
+        if pad_to > B:  # graph padding: dummy decodes that write nowhere and read block 0
+            for i in range(B, pad_to):
+                ids[t] = 0; pos[t] = 0; slots[t] = -1
+                t += 1
+                qsl[i + 1] = t
+                sl[i] = 1
+                bt[i, 0] = 0
+            B_eff, nd_eff = pad_to, pad_to
+        else:
+            B_eff, nd_eff = B, nd
+        pqsl[: B_eff - nd_eff + 1] = qsl[nd_eff:B_eff + 1] - qsl[nd_eff]
+        T = t
+        # one H2D per staging area (only the used prefix of each segment)
+        if self.is_cuda:
+            for seg in range(3):
+                self.d64[seg * T_: seg * T_ + T].copy_(self.h64[seg * T_: seg * T_ + T], non_blocking=True)
+            n32 = (B_ + 1) + B_ + B_eff * MB
+            self.d32[:n32].copy_(self.h32[:n32], non_blocking=True)
+            o2 = (B_ + 1) + B_ + B_ * MB
+            self.d32[o2:o2 + B_eff + 1].copy_(self.h32[o2:o2 + B_eff + 1], non_blocking=True)
+            self.h2d_bytes += 3 * T * 8 + (n32 + B_eff + 1) * 4
+        else:
+            self.d64.copy_(self.h64)
+            self.d32.copy_(self.h32)
+        md = AttentionMetadata(
+            num_tokens=T, num_reqs=B_eff, num_decodes=nd_eff, num_decode_tokens=nd_eff,
+            query_start_loc=self.query_start_loc[:B_eff + 1], seq_lens=self.seq_lens[:B_eff],
+            block_table=self.block_table[:B_eff], slot_mapping=self.slot_mapping[:T], max_query_len=max_q,
+            max_seq_len=max_seq, block_size=bs, prefill_query_start_loc=self.prefill_qsl[:B_eff - nd_eff + 1],
+            max_prefill_query_len=max_q if B_eff > nd_eff else 0)
+        return md, T, sample_rows, sample_reqs
+
+    # ------------------------------------------------------------------ execution
+    def _forward(self, md: AttentionMetadata, T: int):
+        ctx = ForwardContext(md, self.kv_caches, self.positions[:T])
+        with set_forward_context(ctx):
+            return self.model(self.input_ids[:T], self.positions[:T])
+
+    def _decode_splits(self, batch: int) -> int:
+        spec = self.model.kv_cache_spec()
+        if spec["kind"] != "gqa":
+            return 1
+        return ops.decode_num_splits(batch, spec["num_kv_heads"], self.cfg.scheduler.max_model_len, 1, self.sms)
+
+    def _capture(self, bucket: int):
+        """Capture a pure-decode step of `bucket` sequences: model -> logits -> arg-max."""
+        md = AttentionMetadata(
+            num_tokens=bucket, num_reqs=bucket, num_decodes=bucket, num_decode_tokens=bucket,
+            query_start_loc=self.query_start_loc[:bucket + 1], seq_lens=self.seq_lens[:bucket],
+            block_table=self.block_table[:bucket], slot_mapping=self.slot_mapping[:bucket], max_query_len=1,
+            max_seq_len=self.cfg.scheduler.max_model_len, block_size=self.block_size,
+            prefill_query_start_loc=self.prefill_qsl[:1], max_prefill_query_len=0)
+        md.decode_num_splits = self._decode_splits(bucket)
+        spec = self.model.kv_cache_spec()
+        if md.decode_num_splits > 1 and spec["kind"] == "gqa":
+            hq = spec["num_kv_heads"] * (self.cfg.model.num_attention_heads // self.cfg.model.num_key_value_heads)
+            md.decode_workspace = torch.empty(md.decode_num_splits * bucket * hq * (spec["head_size"] + 1),
+                                              dtype=torch.float32, device=self.device)
+        # safe dummy inputs for warm-up
+        self.seq_lens[:bucket].fill_(1)
+        self.slot_mapping[:bucket].fill_(-1)
+        self.block_table[:bucket].zero_()
+        self.positions[:bucket].zero_()
+        self.input_ids[:bucket].zero_()
+        stream = torch.cuda.Stream(self.device)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                h = self._forward(md, bucket)
+                logits = self.model.compute_logits(h)
+                ops.argmax(logits, self.sampled[:bucket])
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            h = self._forward(md, bucket)
+            logits = self.model.compute_logits(h)
+            ops.argmax(logits, self.sampled[:bucket])
+        self.graphs[bucket] = (g, logits, md)
+
+    def capture_graphs(self, buckets: Optional[list[int]] = None) -> None:
+        if not self.use_graphs:
+            return
+        if ps.get_pp_group().world_size > 1:
+            self.use_graphs = False
+            return
+        self.buckets = buckets or _graph_buckets(self.max_seqs)
+        with torch.no_grad():
+            for b in sorted(self.buckets, reverse=True):
+                self._capture(b)
+        ops.check_kernel_status(self.device.index or 0)
+
+    @torch.no_grad()
+    def execute(self, so: SchedulerOutput) -> dict[str, int]:
+        B = len(so.scheduled)
+        pure_decode = so.num_decode == B and B > 0
+        bucket = 0
+        if self.use_graphs and pure_decode and self.graphs:
+            bucket = next((b for b in self.buckets if b >= B), 0)
+        md, T, rows, reqs = self._prepare(so, pad_to=bucket)
+        all_greedy = all(r.params.greedy and not r.params.needs_penalties for r in reqs)
+        n = len(rows)
+        if bucket:
+            g, logits, _ = self.graphs[bucket]
+            g.replay()
+            if all_greedy:
+                tokens_dev = self.sampled[:B]
+            else:
+                tokens_dev = self._sample(logits[:B], reqs)
+        else:
+            h = self._forward(md, T)
+            if isinstance(h, dict):  # non-last pipeline stage
+                return {}
+            if n == 0:
+                return {}
+            if n == T:
+                hs = h
+            else:
+                self.sample_idx_host[:n] = torch.as_tensor(rows)
+                self.sample_idx[:n].copy_(self.sample_idx_host[:n], non_blocking=True)
+                hs = h.index_select(0, self.sample_idx[:n])
+            logits = self.model.compute_logits(hs)
+            tokens_dev = ops.argmax(logits, self.sampled[:n]) if all_greedy else self._sample(logits, reqs)
+        self.sampled_host[:n].copy_(tokens_dev[:n], non_blocking=False)
+        self.d2h_bytes += n * 8
+        toks = self.sampled_host[:n].tolist()
+        return {r.request_id: tok for r, tok in zip(reqs, toks)}
+
+    def _sample(self, logits: torch.Tensor, reqs) -> torch.Tensor:
+        from .sampler import sample_batch
+
+        return sample_batch(logits, reqs, self.sampled[:len(reqs)])

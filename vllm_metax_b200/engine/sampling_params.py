@@ -1,0 +1,150 @@
+"""Per-request sampling parameters and request/output records."""
+from __future__ import annotations
+
+import enum
+import time
+from dataclasses import dataclass, field
+from typing import Optional
+
+
+@dataclass
+class SamplingParams:
+    max_tokens: int = 16
+    temperature: float = 0.0
+    top_k: int = 0
+    top_p: float = 1.0
+    min_p: float = 0.0
+    repetition_penalty: float = 1.0
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    seed: Optional[int] = None
+    ignore_eos: bool = False
+    stop_token_ids: list[int] = field(default_factory=list)
+    min_tokens: int = 0
+    logprobs: Optional[int] = None
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature <= 0.0
+
+    @property
+    def needs_penalties(self) -> bool:
+        return self.repetition_penalty != 1.0 or self.presence_penalty != 0.0 or self.frequency_penalty != 0.0
+
+
+class RequestStatus(enum.Enum):
+    WAITING = 0
+    RUNNING = 1
+    PREEMPTED = 2
+    FINISHED_STOPPED = 3
+    FINISHED_LENGTH = 4
+    FINISHED_ABORTED = 5
+
+    @property
+    def finished(self) -> bool:
+        return self.value >= 3
+
+
+class Request:
+    """One generation request and its mutable decoding state."""
+
+    __slots__ = ("request_id", "prompt_token_ids", "params", "output_token_ids", "status", "block_ids",
+                 "num_computed_tokens", "arrival_time", "first_token_time", "finish_time", "token_times",
+                 "eos_token_id", "num_cached_tokens", "logprobs", "prompt", "_hashes")
+
+    def __init__(self, request_id: str, prompt_token_ids: list[int], params: SamplingParams,
+                 eos_token_id: Optional[int] = None, prompt: Optional[str] = None,
+                 arrival_time: Optional[float] = None):
+        self.request_id = request_id
+        self.prompt_token_ids = list(prompt_token_ids)
+        self.params = params
+        self.output_token_ids: list[int] = []
+        self.status = RequestStatus.WAITING
+        self.block_ids: list[int] = []
+        self.num_computed_tokens = 0           # tokens whose KV is in the cache
+        self.num_cached_tokens = 0             # prefix-cache hits
+        self.arrival_time = time.perf_counter() if arrival_time is None else arrival_time
+        self.first_token_time: Optional[float] = None
+        self.finish_time: Optional[float] = None
+        self.token_times: list[float] = []
+        self.eos_token_id = eos_token_id
+        self.logprobs: list = []
+        self.prompt = prompt
+        self._hashes: list[int] = []
+
+    @property
+    def num_prompt_tokens(self) -> int:
+        return len(self.prompt_token_ids)
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.prompt_token_ids) + len(self.output_token_ids)
+
+    @property
+    def all_token_ids(self) -> list[int]:
+        return self.prompt_token_ids + self.output_token_ids
+
+    def token_at(self, i: int) -> int:
+        n = len(self.prompt_token_ids)
+        return self.prompt_token_ids[i] if i < n else self.output_token_ids[i - n]
+
+    @property
+    def is_prefill(self) -> bool:
+        """True while the prompt (plus outputs kept across a preemption) is not fully cached."""
+        return self.num_computed_tokens < self.num_tokens - 1 or not self.output_token_ids
+
+    def append_token(self, tok: int, now: float) -> None:
+        self.output_token_ids.append(tok)
+        self.token_times.append(now)
+        if self.first_token_time is None:
+            self.first_token_time = now
+
+    def check_stop(self) -> None:
+        p = self.params
+        n_out = len(self.output_token_ids)
+        last = self.output_token_ids[-1] if n_out else None
+        if n_out >= p.min_tokens and last is not None:
+            if (not p.ignore_eos and self.eos_token_id is not None and last == self.eos_token_id) or \
+                    last in p.stop_token_ids:
+                self.status = RequestStatus.FINISHED_STOPPED
+                return
+        if n_out >= p.max_tokens:
+            self.status = RequestStatus.FINISHED_LENGTH
+
+
+@dataclass
+class CompletionOutput:
+    index: int
+    token_ids: list[int]
+    text: Optional[str]
+    finish_reason: Optional[str]
+    logprobs: Optional[list] = None
+
+
+@dataclass
+class RequestMetrics:
+    arrival_time: float
+    first_token_time: Optional[float]
+    finish_time: Optional[float]
+    token_times: list[float]
+
+    @property
+    def ttft(self) -> Optional[float]:
+        return None if self.first_token_time is None else self.first_token_time - self.arrival_time
+
+    @property
+    def tpot(self) -> Optional[float]:
+        if self.finish_time is None or self.first_token_time is None or len(self.token_times) < 2:
+            return None
+        return (self.token_times[-1] - self.first_token_time) / (len(self.token_times) - 1)
+
+
+@dataclass
+class RequestOutput:
+    request_id: str
+    prompt: Optional[str]
+    prompt_token_ids: list[int]
+    outputs: list[CompletionOutput]
+    finished: bool
+    metrics: RequestMetrics
+    num_cached_tokens: int = 0

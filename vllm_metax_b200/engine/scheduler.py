@@ -1,0 +1,170 @@
+"""Continuous-batching scheduler with chunked prefill and recompute preemption.
+
+Every call to ``schedule`` produces one batch under two budgets: at most
+``max_num_seqs`` requests and ``max_num_batched_tokens`` new tokens.  Running
+requests go first (decodes need one token each), then waiting requests are
+admitted while blocks and budget last; a prompt that does not fit the token
+budget is split into chunks.  When the pool runs dry the most recently admitted
+running request is preempted: its blocks are freed and it re-enters the waiting
+queue to be recomputed.  Batches are ordered decode-first so the attention
+backend can split the flat token buffer into a decode slice and a prefill slice
+(same idea as the batch reordering at
+vllm_metax/patch/performance/speculative_decode_perf.py:29-112).
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+
+from ..config import SchedulerConfig
+from .block_manager import KVCacheManager
+from .sampling_params import Request, RequestStatus
+
+
+@dataclass
+class ScheduledRequest:
+    request: Request
+    num_new_tokens: int            # tokens fed to the model this step
+    start_pos: int                 # position of the first fed token
+    samples: bool                  # whether logits of the last fed token are sampled
+
+    @property
+    def is_decode(self) -> bool:
+        return self.num_new_tokens == 1 and self.samples and len(self.request.output_token_ids) > 0
+
+
+@dataclass
+class SchedulerOutput:
+    scheduled: list[ScheduledRequest] = field(default_factory=list)
+    num_decode: int = 0
+    preempted: list[Request] = field(default_factory=list)
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(s.num_new_tokens for s in self.scheduled)
+
+    @property
+    def is_empty(self) -> bool:
+        return not self.scheduled
+
+
+class Scheduler:
+    def __init__(self, cfg: SchedulerConfig, kv: KVCacheManager):
+        self.cfg = cfg
+        self.kv = kv
+        self.waiting: deque[Request] = deque()
+        self.running: list[Request] = []
+        self.paused = False
+        self.num_preemptions = 0
+
+    # ------------------------------------------------------------------ queue ops
+    def add_request(self, req: Request) -> None:
+        if req.num_prompt_tokens + req.params.max_tokens > self.cfg.max_model_len:
+            req.params.max_tokens = max(1, self.cfg.max_model_len - req.num_prompt_tokens)
+        if req.num_prompt_tokens >= self.cfg.max_model_len:
+            raise ValueError(f"prompt of {req.num_prompt_tokens} tokens exceeds max_model_len {self.cfg.max_model_len}")
+        self.waiting.append(req)
+
+    def abort(self, request_id: str) -> bool:
+        for q in (self.running, self.waiting):
+            for r in list(q):
+                if r.request_id == request_id:
+                    q.remove(r)
+                    self.kv.free(r)
+                    r.status = RequestStatus.FINISHED_ABORTED
+                    return True
+        return False
+
+    def has_unfinished(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def pause(self) -> None:
+        self.paused = True
+
+    def resume(self) -> None:
+        self.paused = False
+
+    # ------------------------------------------------------------------ scheduling
+    def _preempt_one(self, out: SchedulerOutput, keep: Request) -> bool:
+        for victim in reversed(self.running):
+            if victim is keep:
+                continue
+            self.running.remove(victim)
+            out.scheduled = [s for s in out.scheduled if s.request is not victim]
+            self.kv.free(victim)
+            victim.num_computed_tokens = 0
+            victim.status = RequestStatus.PREEMPTED
+            self.waiting.appendleft(victim)
+            out.preempted.append(victim)
+            self.num_preemptions += 1
+            return True
+        return False
+
+    def schedule(self) -> SchedulerOutput:
+        out = SchedulerOutput()
+        if self.paused:
+            return out
+        budget = self.cfg.max_num_batched_tokens
+        # ---- running requests (decode, or the next chunk of a long prefill)
+        for req in list(self.running):
+            if req not in self.running or budget <= 0:
+                continue
+            remaining = req.num_tokens - req.num_computed_tokens
+            n = min(remaining, budget)
+            if not self.cfg.enable_chunked_prefill and n < remaining:
+                continue
+            ok = True
+            while not self.kv.can_allocate(req, n):
+                if not self._preempt_one(out, keep=req):
+                    ok = False
+                    break
+            if not ok:
+                continue
+            self.kv.allocate(req, n)
+            out.scheduled.append(ScheduledRequest(req, n, req.num_computed_tokens, n == remaining))
+            budget -= n
+        # ---- admit waiting requests
+        while self.waiting and budget > 0 and len(self.running) < self.cfg.max_num_seqs and not out.preempted:
+            req = self.waiting[0]
+            self.kv.try_prefix_hit(req)
+            remaining = req.num_tokens - req.num_computed_tokens
+            n = min(remaining, budget)
+            if not self.cfg.enable_chunked_prefill and n < remaining:
+                if not out.scheduled and remaining > self.cfg.max_num_batched_tokens:
+                    raise ValueError("prompt longer than max_num_batched_tokens and chunked prefill is off")
+                break
+            if not self.kv.can_allocate(req, n):
+                if req.block_ids:  # drop the prefix-cache references taken above
+                    self.kv.free(req)
+                    req.num_computed_tokens = 0
+                    req.num_cached_tokens = 0
+                break
+            self.waiting.popleft()
+            self.kv.allocate(req, n)
+            req.status = RequestStatus.RUNNING
+            self.running.append(req)
+            out.scheduled.append(ScheduledRequest(req, n, req.num_computed_tokens, n == remaining))
+            budget -= n
+        # ---- decode-first order
+        dec = [s for s in out.scheduled if s.is_decode]
+        pre = [s for s in out.scheduled if not s.is_decode]
+        out.scheduled = dec + pre
+        out.num_decode = len(dec)
+        return out
+
+    def update(self, out: SchedulerOutput, sampled: dict[str, int], now: float) -> list[Request]:
+        """Advance request state after the model ran; returns requests that finished."""
+        finished = []
+        for s in out.scheduled:
+            req = s.request
+            req.num_computed_tokens += s.num_new_tokens
+            self.kv.commit(req)
+            if s.samples:
+                req.append_token(sampled[req.request_id], now)
+                req.check_stop()
+                if req.status.finished:
+                    req.finish_time = now
+                    self.running.remove(req)
+                    self.kv.free(req)
+                    finished.append(req)
+        return finished

@@ -1,0 +1,115 @@
+"""Environment-variable flag system, evaluated lazily on attribute access.
+
+Every flag is declared once in ``environment_variables`` with a resolver that
+parses ``os.environ`` at the moment the attribute is read, so tests and launch
+scripts can flip a flag after import.  ``override_env`` rewrites both the
+resolver and ``os.environ`` and logs the reason, and can forward the override
+to ``vllm.envs`` when vLLM is importable.
+
+Parity: vllm_metax/envs.py:27-109 (table), :113-149 (override_vllm_env),
+:152-167 (module ``__getattr__``/``__dir__``).
+"""
+from __future__ import annotations
+
+import logging
+import os
+from typing import Any, Callable
+
+logger = logging.getLogger(__name__)
+
+
+def _flag(name: str, default: str) -> Callable[[], bool]:
+    return lambda: os.environ.get(name, default).strip().lower() in ("1", "true", "yes", "on")
+
+
+def _int(name: str, default: int) -> Callable[[], int]:
+    return lambda: int(os.environ.get(name, str(default)))
+
+
+def _str(name: str, default: str | None) -> Callable[[], str | None]:
+    return lambda: os.environ.get(name, default)
+
+
+environment_variables: dict[str, Callable[[], Any]] = {
+    # ---- build time -------------------------------------------------------
+    "B200_TARGET_DEVICE": _str("B200_TARGET_DEVICE", "cuda"),
+    "MAX_JOBS": _str("MAX_JOBS", None),
+    "NVCC_THREADS": _str("NVCC_THREADS", None),
+    "CMAKE_BUILD_TYPE": _str("CMAKE_BUILD_TYPE", None),
+    "VERBOSE": _flag("VERBOSE", "0"),
+    "CUDA_HOME": _str("CUDA_HOME", "/usr/local/cuda"),
+    # Path of a specific libnccl.so for the ctypes NCCL binding (None: torch's).
+    "B200_NCCL_SO_PATH": _str("B200_NCCL_SO_PATH", None),
+    # When 1 the native extension must already be built in-tree; never JIT.
+    "B200_USE_PREBUILT_KERNELS": _flag("B200_USE_PREBUILT_KERNELS", "0"),
+    # ---- runtime: kernel selection ---------------------------------------
+    # Hand-written tcgen05 GEMM on dense linears (0 = cuBLAS, debug only).
+    "B200_TCGEN05_GEMM": _flag("B200_TCGEN05_GEMM", "1"),
+    # Grouped tcgen05 GEMM for experts (0 = per-expert loop, debug only).
+    "B200_GROUPED_MOE_GEMM": _flag("B200_GROUPED_MOE_GEMM", "1"),
+    # Fused GEMM + in-kernel NVLink all-reduce + residual + RMSNorm.
+    "B200_FUSED_TP_COLLECTIVES": _flag("B200_FUSED_TP_COLLECTIVES", "1"),
+    # Pack topk weights/ids/scales into one tensor for the AG/RS dispatch.
+    "B200_OPTIMIZED_DP_ALL2ALL": _flag("B200_OPTIMIZED_DP_ALL2ALL", "1"),
+    # Run prefill and decode slices of a mixed batch through separate kernels.
+    "B200_ATTN_SPLIT_FORWARD": _flag("B200_ATTN_SPLIT_FORWARD", "1"),
+    # Token chunk for the fused-MoE expert pipeline.
+    "B200_FUSED_MOE_CHUNK_SIZE": _int("B200_FUSED_MOE_CHUNK_SIZE", 16384),
+    "B200_SUPPORTS_FP8": _flag("B200_SUPPORTS_FP8", "1"),
+    # fp8 weights with bf16 activations (weight-only) for block-scaled linears.
+    "B200_USE_FP8_WO_A": _flag("B200_USE_FP8_WO_A", "0"),
+    "B200_USE_FUSED_GROUPED_TOPK": _flag("B200_USE_FUSED_GROUPED_TOPK", "1"),
+    "B200_USE_CUDA_SAMPLER": _flag("B200_USE_CUDA_SAMPLER", "1"),
+    # CUDA-graph capture of decode steps.
+    "B200_CUDA_GRAPHS": _flag("B200_CUDA_GRAPHS", "1"),
+    # In-kernel bounds checks on every indexed access (slot mapping, block
+    # tables, expert ids); failures land in a device status word.
+    "B200_KERNEL_BOUNDS_CHECK": _flag("B200_KERNEL_BOUNDS_CHECK", "0"),
+    # Iteration budget of device-side waits on peer flags before giving up.
+    "B200_PEER_WAIT_ITERS": _int("B200_PEER_WAIT_ITERS", 20_000_000),
+    # Use NVLS multimem instructions in fused collectives when available.
+    "B200_USE_MULTIMEM": _flag("B200_USE_MULTIMEM", "0"),
+    # ---- debug -------------------------------------------------------------
+    "B200_FORCE_REFERENCE_OPS": _flag("B200_FORCE_REFERENCE_OPS", "0"),
+    "B200_PRECISION_DUMP_DIR": _str("B200_PRECISION_DUMP_DIR", None),
+    "B200_LOG_LEVEL": _str("B200_LOG_LEVEL", "INFO"),
+}
+
+_overrides: dict[str, tuple[Any, str]] = {}
+
+
+def override_env(name: str, value: Any, reason: str, *, forward_to_vllm: bool = False) -> None:
+    """Force ``name`` to ``value`` for this process and record why.
+
+    The value is written to ``os.environ`` (so child processes inherit it) and
+    the resolver is replaced.  With ``forward_to_vllm`` the same is done to
+    ``vllm.envs.environment_variables`` if vLLM is importable.
+    """
+    sval = "1" if value is True else "0" if value is False else str(value)
+    old = os.environ.get(name)
+    os.environ[name] = sval
+    environment_variables[name] = (lambda v=value: v)
+    _overrides[name] = (value, reason)
+    logger.info("env override %s: %r -> %r (%s)", name, old, sval, reason)
+    if forward_to_vllm:
+        try:
+            import vllm.envs as venvs  # type: ignore
+
+            if hasattr(venvs, "environment_variables"):
+                venvs.environment_variables[name] = (lambda v=value: v)
+        except Exception:  # pragma: no cover - vLLM optional
+            pass
+
+
+def overrides() -> dict[str, tuple[Any, str]]:
+    return dict(_overrides)
+
+
+def __getattr__(name: str) -> Any:
+    if name in environment_variables:
+        return environment_variables[name]()
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+
+
+def __dir__() -> list[str]:
+    return list(environment_variables.keys())

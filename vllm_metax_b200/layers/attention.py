@@ -1,0 +1,97 @@
+"""The GQA attention layer: fused RoPE + KV-cache write, then the split forward
+(decode slice -> split-KV decode kernel, prefill slice -> tcgen05 varlen kernel).
+
+One backend (``PAGED_GQA``) replaces the reference's FLASH_ATTN / TRITON_ATTN /
+FLASHINFER family for decoder self-attention: bf16/fp16 caches, fp8 caches with a
+static scale, and int8 / fp8 caches with per-(token, head) scales
+(``int8_per_token_head``) all run through the same two kernels.  The split of a
+mixed batch into a decode slice and a prefill slice follows
+vllm_metax/v1/attention/backends/flash_attn.py:1302-1355 (VLLM_METAX_ENABLE_FA_SPLIT_FORWARD).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from .. import _custom_ops as ops
+from ..attention.metadata import get_forward_context
+
+KV_DTYPES = {
+    "auto": None, "bfloat16": torch.bfloat16, "float16": torch.float16, "fp8": torch.float8_e4m3fn,
+    "fp8_e4m3": torch.float8_e4m3fn, "int8_per_token_head": torch.int8, "fp8_per_token_head": torch.float8_e4m3fn,
+}
+
+
+class PagedGQABackend:
+    name = "PAGED_GQA"
+    supported_head_sizes = (64, 128, 256)
+    supported_kv_cache_dtypes = tuple(KV_DTYPES)
+
+    @staticmethod
+    def get_kv_cache_shape(num_blocks: int, block_size: int, num_kv_heads: int, head_size: int):
+        return (num_blocks, 2, block_size, num_kv_heads, head_size)
+
+    @staticmethod
+    def get_scale_shape(num_blocks: int, block_size: int, num_kv_heads: int):
+        return (num_blocks, 2, block_size, num_kv_heads)
+
+    @staticmethod
+    def supported_block_sizes():
+        return (16, 32, 64, 128, 256)
+
+    @staticmethod
+    def allocate(num_blocks, block_size, num_kv_heads, head_size, model_dtype, kv_cache_dtype: str, device):
+        dt = KV_DTYPES[kv_cache_dtype] or model_dtype
+        cache = torch.zeros(PagedGQABackend.get_kv_cache_shape(num_blocks, block_size, num_kv_heads, head_size),
+                            dtype=dt, device=device)
+        scales = None
+        if kv_cache_dtype.endswith("per_token_head"):
+            scales = torch.ones(PagedGQABackend.get_scale_shape(num_blocks, block_size, num_kv_heads),
+                                dtype=torch.float32, device=device)
+        return (cache, scales)
+
+
+class Attention(nn.Module):
+    def __init__(self, num_heads: int, head_size: int, scale: float, num_kv_heads: int, layer_idx: int,
+                 sliding_window: Optional[int] = None, softcap: float = 0.0, sinks: Optional[torch.Tensor] = None,
+                 k_scale: float = 1.0, v_scale: float = 1.0):
+        super().__init__()
+        self.num_heads, self.head_size, self.scale, self.num_kv_heads = num_heads, head_size, scale, num_kv_heads
+        self.layer_idx = layer_idx
+        self.window = sliding_window or -1
+        self.softcap = softcap
+        self.sinks = sinks
+        self.k_scale, self.v_scale = k_scale, v_scale
+
+    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, positions: Optional[torch.Tensor] = None,
+                rope=None) -> torch.Tensor:
+        """``q [T, Hq*D]``, ``k, v [T, Hkv*D]`` (views into the qkv GEMM output are fine).
+        With ``rope`` given, RoPE is applied inside the cache-write kernel."""
+        ctx = get_forward_context()
+        md = ctx.attn_metadata
+        kv_cache, kv_scales = ctx.kv_caches[self.layer_idx]
+        T = q.shape[0]
+        if rope is not None:
+            ops.rope_and_cache(positions, q, k, v, self.head_size, rope.cos_sin_cache, rope.is_neox, kv_cache,
+                               md.slot_mapping, kv_scales, self.k_scale, self.v_scale)
+        else:
+            ops.reshape_and_cache(k, v, kv_cache, md.slot_mapping, kv_scales, self.k_scale, self.v_scale)
+        q3 = q.reshape(T, self.num_heads, self.head_size)
+        if not q3.is_contiguous() and q3.stride(1) != self.head_size:
+            q3 = q3.contiguous()
+        out = torch.empty(T, self.num_heads, self.head_size, dtype=q.dtype, device=q.device)
+        nd, ndt = md.num_decodes, md.num_decode_tokens
+        if nd > 0:
+            ops.paged_attention_decode(q3[:ndt], kv_cache, md.block_table[:nd], md.seq_lens[:nd], self.scale,
+                                       out=out[:ndt], kv_scales=kv_scales, window=self.window, softcap=self.softcap,
+                                       sinks=self.sinks, num_splits=md.decode_num_splits, max_seq_len=md.max_seq_len,
+                                       k_scale=self.k_scale, v_scale=self.v_scale, workspace=md.decode_workspace)
+        if md.num_prefills > 0:
+            ops.paged_attention_prefill(q3[ndt:], kv_cache, md.block_table[nd:], md.seq_lens[nd:],
+                                        md.prefill_query_start_loc, self.scale, out=out[ndt:], kv_scales=kv_scales,
+                                        max_q_len=md.max_prefill_query_len, window=self.window, softcap=self.softcap,
+                                        sinks=self.sinks, k_scale=self.k_scale, v_scale=self.v_scale,
+                                        max_seq_len=md.max_seq_len)
+        return out.reshape(T, self.num_heads * self.head_size)

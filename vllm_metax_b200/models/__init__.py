@@ -1,0 +1,44 @@
+"""Model registry: HF architecture name -> (module, class), resolved lazily.
+
+Parity: vllm_metax/models/__init__.py:6-38 registers the DeepSeek V2/V3/V3.2/V4, GLM-MoE-DSA
+and MTP architectures with vLLM's ModelRegistry; every other architecture of the
+reference's supported-models table runs through upstream model code.  Here the registry
+also holds the dense / MoE families the benchmark configurations name.
+"""
+from __future__ import annotations
+
+import importlib
+
+_MODELS: dict[str, tuple[str, str]] = {
+    "LlamaForCausalLM": ("llama", "LlamaForCausalLM"),
+    "MistralForCausalLM": ("llama", "MistralForCausalLM"),
+    "Qwen2ForCausalLM": ("llama", "Qwen2ForCausalLM"),
+    "Qwen3ForCausalLM": ("llama", "Qwen3ForCausalLM"),
+    "Qwen3MoeForCausalLM": ("qwen3_moe", "Qwen3MoeForCausalLM"),
+    "Qwen2MoeForCausalLM": ("qwen3_moe", "Qwen3MoeForCausalLM"),
+    "MixtralForCausalLM": ("qwen3_moe", "MixtralForCausalLM"),
+    "DeepseekV2ForCausalLM": ("deepseek_v2", "DeepseekV2ForCausalLM"),
+    "DeepseekV3ForCausalLM": ("deepseek_v2", "DeepseekV3ForCausalLM"),
+    "DeepseekV32ForCausalLM": ("deepseek_v2", "DeepseekV32ForCausalLM"),
+    "GlmMoeDsaForCausalLM": ("deepseek_v2", "GlmMoeDsaForCausalLM"),
+    "DeepSeekMTPModel": ("deepseek_mtp", "DeepSeekMTP"),
+    "DeepseekV4ForCausalLM": ("deepseek_v4", "DeepseekV4ForCausalLM"),
+    "DeepSeekV4MTPModel": ("deepseek_v4", "DeepSeekV4MTP"),
+    "Step3p5MTP": ("step3p5_mtp", "Step3p5MTP"),
+}
+
+
+def register_model(arch: str, module: str, cls: str) -> None:
+    _MODELS[arch] = (module, cls)
+
+
+def supported_architectures() -> list[str]:
+    return sorted(_MODELS)
+
+
+def get_model_class(arch: str):
+    if arch not in _MODELS:
+        raise ValueError(f"unknown architecture {arch!r}; known: {supported_architectures()}")
+    mod, cls = _MODELS[arch]
+    m = importlib.import_module(mod if "." in mod else f"{__name__}.{mod}")
+    return getattr(m, cls)

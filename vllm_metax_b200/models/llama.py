@@ -1,0 +1,203 @@
+"""Llama-family dense decoder (Llama 2/3, Mistral, Qwen2, Qwen3) on the B200 kernels.
+
+Layer data flow (all in flat ``[T, hidden]`` token-major tensors):
+
+    (h, res) = fused_add_rms_norm(h, res)            one kernel
+    qkv      = tcgen05 GEMM
+    RoPE(q,k) + KV-cache write                        one kernel (per-head q/k norm before it for Qwen3)
+    attn     = decode kernel | tcgen05 prefill kernel
+    h        = o_proj GEMM  (+ TP all-reduce)
+    (h, res) = fused_add_rms_norm(h, res)
+    h        = down( silu(gate) * up )                2 GEMMs + 1 activation kernel (+ TP all-reduce)
+
+Architecture names follow HF ``config.json``; checkpoints load from HF safetensors with
+the usual q/k/v and gate/up stacking.
+"""
+from __future__ import annotations
+
+from typing import Iterable, Optional
+
+import torch
+import torch.nn as nn
+
+from .. import _custom_ops as ops
+from ..config import ModelConfig
+from ..layers.attention import Attention
+from ..layers.basic import ParallelLMHead, RMSNorm, SiluAndMul, VocabParallelEmbedding, get_rope
+from ..layers.linear import MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear
+from ..parallel import state as ps
+from ..quantization import get_linear_method
+
+
+class LlamaMLP(nn.Module):
+    def __init__(self, cfg: ModelConfig, intermediate_size: int, prefix: str, reduce_results: bool = True):
+        super().__init__()
+        qm = lambda name: get_linear_method(cfg, f"{prefix}.{name}")
+        self.gate_up_proj = MergedColumnParallelLinear(cfg.hidden_size, [intermediate_size] * 2, cfg.mlp_bias,
+                                                       cfg.dtype, qm("gate_up_proj"), prefix=f"{prefix}.gate_up_proj")
+        self.down_proj = RowParallelLinear(intermediate_size, cfg.hidden_size, cfg.mlp_bias, cfg.dtype,
+                                           qm("down_proj"), reduce_results=reduce_results, prefix=f"{prefix}.down_proj")
+        self.act = SiluAndMul()
+
+    def forward(self, x):
+        return self.down_proj(self.act(self.gate_up_proj(x)))
+
+
+class LlamaAttention(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, prefix: str):
+        super().__init__()
+        tp = ps.tp_size()
+        self.head_dim = cfg.head_dim
+        self.total_heads, self.total_kv = cfg.num_attention_heads, cfg.num_key_value_heads
+        qm = lambda name: get_linear_method(cfg, f"{prefix}.{name}")
+        self.qkv_proj = QKVParallelLinear(cfg.hidden_size, self.head_dim, self.total_heads, self.total_kv,
+                                          cfg.attention_bias, cfg.dtype, qm("qkv_proj"), prefix=f"{prefix}.qkv_proj")
+        self.num_heads, self.num_kv_heads = self.qkv_proj.num_heads, self.qkv_proj.num_kv_heads
+        self.q_size, self.kv_size = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
+        self.o_proj = RowParallelLinear(self.total_heads * self.head_dim, cfg.hidden_size, False, cfg.dtype,
+                                        qm("o_proj"), prefix=f"{prefix}.o_proj")
+        self.rope = get_rope(self.head_dim, self.head_dim, cfg.max_position_embeddings, cfg.rope_theta, True,
+                             cfg.rope_scaling)
+        self.qk_norm = cfg.qk_norm
+        if cfg.qk_norm:
+            self.q_norm = RMSNorm(self.head_dim, cfg.rms_norm_eps, cfg.dtype)
+            self.k_norm = RMSNorm(self.head_dim, cfg.rms_norm_eps, cfg.dtype)
+        self.attn = Attention(self.num_heads, self.head_dim, self.head_dim ** -0.5, self.num_kv_heads, layer_idx,
+                              sliding_window=cfg.sliding_window)
+
+    def forward(self, positions, h):
+        qkv = self.qkv_proj(h)
+        q = qkv[:, : self.q_size]
+        k = qkv[:, self.q_size: self.q_size + self.kv_size]
+        v = qkv[:, self.q_size + self.kv_size:]
+        if self.qk_norm:
+            ops.head_rms_norm(q, self.q_norm.weight, self.q_norm.eps, self.num_heads, self.head_dim)
+            ops.head_rms_norm(k, self.k_norm.weight, self.k_norm.eps, self.num_kv_heads, self.head_dim)
+        a = self.attn(q, k, v, positions, self.rope)
+        return self.o_proj(a)
+
+
+class LlamaDecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, prefix: str):
+        super().__init__()
+        self.self_attn = LlamaAttention(cfg, layer_idx, f"{prefix}.self_attn")
+        self.mlp = LlamaMLP(cfg, cfg.intermediate_size, f"{prefix}.mlp")
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype)
+
+    def forward(self, positions, h, residual):
+        if residual is None:
+            residual = h
+            h = self.input_layernorm(h)
+        else:
+            h, residual = self.input_layernorm(h, residual)
+        h = self.self_attn(positions, h)
+        h, residual = self.post_attention_layernorm(h, residual)
+        h = self.mlp(h)
+        return h, residual
+
+
+class LlamaModel(nn.Module):
+    layer_cls = LlamaDecoderLayer
+
+    def __init__(self, cfg: ModelConfig, prefix: str = "model"):
+        super().__init__()
+        self.cfg = cfg
+        pp = ps.get_pp_group()
+        n = cfg.num_hidden_layers
+        per = (n + pp.world_size - 1) // pp.world_size
+        self.start_layer = pp.rank_in_group * per
+        self.end_layer = min(n, self.start_layer + per)
+        self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype) if pp.is_first_rank else None
+        self.layers = nn.ModuleDict({str(i): self.layer_cls(cfg, i - self.start_layer, f"{prefix}.layers.{i}")
+                                     for i in range(self.start_layer, self.end_layer)})
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype) if pp.is_last_rank else None
+
+    def forward(self, input_ids, positions, intermediate: Optional[dict] = None):
+        if self.embed_tokens is not None:
+            h, residual = self.embed_tokens(input_ids), None
+        else:
+            h, residual = intermediate["hidden_states"], intermediate["residual"]
+        for i in range(self.start_layer, self.end_layer):
+            h, residual = self.layers[str(i)](positions, h, residual)
+        if self.norm is None:
+            return {"hidden_states": h, "residual": residual}
+        h, _ = self.norm(h, residual)
+        return h
+
+
+class LlamaForCausalLM(nn.Module):
+    model_cls = LlamaModel
+    stacked_params = [("qkv_proj", "q_proj", "q"), ("qkv_proj", "k_proj", "k"), ("qkv_proj", "v_proj", "v"),
+                      ("gate_up_proj", "gate_proj", 0), ("gate_up_proj", "up_proj", 1)]
+
+    def __init__(self, cfg: ModelConfig):
+        super().__init__()
+        self.cfg = cfg
+        self.model = self.model_cls(cfg)
+        pp = ps.get_pp_group()
+        self.lm_head = None
+        if pp.is_last_rank:
+            if cfg.tie_word_embeddings and self.model.embed_tokens is not None:
+                self.lm_head = self.model.embed_tokens
+                self.lm_head.__class__ = ParallelLMHead
+            else:
+                self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, cfg.dtype)
+
+    # ---- engine interface ---------------------------------------------------
+    def num_kv_layers(self) -> int:
+        return self.model.end_layer - self.model.start_layer
+
+    def kv_cache_spec(self) -> dict:
+        a = next(iter(self.model.layers.values())).self_attn
+        return {"kind": "gqa", "num_kv_heads": a.num_kv_heads, "head_size": a.head_dim}
+
+    def forward(self, input_ids, positions, intermediate=None):
+        return self.model(input_ids, positions, intermediate)
+
+    def compute_logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        return self.lm_head.logits(hidden)
+
+    # ---- weights -------------------------------------------------------------
+    def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]) -> set[str]:
+        params = dict(self.named_parameters())
+        modules = dict(self.named_modules())
+        loaded: set[str] = set()
+        for name, w in weights:
+            if "rotary_emb.inv_freq" in name:
+                continue
+            if name.startswith("lm_head.") and self.cfg.tie_word_embeddings:
+                continue
+            target, shard = name, None
+            for fused, part, sid in self.stacked_params:
+                if f".{part}." in name:
+                    target, shard = name.replace(part, fused), sid
+                    break
+            if target not in params:
+                continue  # other pipeline stage, or unused tensor
+            p = params[target]
+            mod = modules[target.rsplit(".", 1)[0]]
+            loader = getattr(mod, "weight_loader", None)
+            if loader is not None:
+                loader(p, w, shard)
+            else:
+                p.data.copy_(w.reshape(p.shape))
+            loaded.add(target)
+        for m in self.modules():
+            qm = getattr(m, "quant_method", None)
+            if qm is not None and hasattr(qm, "process_weights_after_loading"):
+                qm.process_weights_after_loading(m)
+        return loaded
+
+
+# Same graph, different config flags (bias on qkv for Qwen2, per-head q/k norm for Qwen3).
+class Qwen2ForCausalLM(LlamaForCausalLM):
+    pass
+
+
+class Qwen3ForCausalLM(LlamaForCausalLM):
+    pass
+
+
+class MistralForCausalLM(LlamaForCausalLM):
+    pass

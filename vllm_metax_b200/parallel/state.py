@@ -1,0 +1,262 @@
+"""Process-group bookkeeping: one process per GPU, NCCL for device collectives, Gloo for control.
+
+World layout (rank = pp * tp_size + tp): TP ranks are adjacent so that on one
+NVSwitch box a TP group is any aligned run of GPUs.  EP reuses the TP*DP ranks
+(experts are sharded over the same processes that shard attention heads), DCP
+subdivides TP.  With world_size == 1 every group is a trivial ``Group`` whose
+collectives are identities, so model code never branches on "is distributed".
+
+Parity: the reference inherits vllm.distributed.parallel_state (_TP/_PP/_DP/_EP/_DCP)
+and plugs ``MacaCommunicator`` into GroupCoordinator
+(vllm_metax/distributed/device_communicators/cuda_communicator.py:19-62).
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+class Group:
+    """A communicator over ``ranks`` (global ranks); wraps a torch ProcessGroup."""
+
+    def __init__(self, ranks: Sequence[int], rank: int, device_pg=None, cpu_pg=None, name: str = ""):
+        self.ranks = list(ranks)
+        self.world_size = len(self.ranks)
+        self.rank_in_group = self.ranks.index(rank) if rank in self.ranks else -1
+        self.device_pg = device_pg
+        self.cpu_pg = cpu_pg
+        self.name = name
+
+    # ---- collectives -----------------------------------------------------
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self.world_size == 1:
+            return x
+        dist.all_reduce(x, group=self._pg(x))
+        return x
+
+    def all_gather(self, x: torch.Tensor, dim: int = -1) -> torch.Tensor:
+        if self.world_size == 1:
+            return x
+        if dim < 0:
+            dim += x.dim()
+        out = torch.empty((self.world_size,) + tuple(x.shape), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x.contiguous(), group=self._pg(x))
+        out = out.movedim(0, dim)
+        shp = list(x.shape)
+        shp[dim] *= self.world_size
+        return out.reshape(shp)
+
+    def all_gatherv(self, x: torch.Tensor, sizes: Sequence[int]) -> torch.Tensor:
+        """Concatenate dim-0 shards of differing length (``sizes[r]`` rows from rank r)."""
+        if self.world_size == 1:
+            return x
+        mx = max(sizes)
+        pad = torch.zeros((mx,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        pad[: x.shape[0]] = x
+        out = torch.empty((self.world_size, mx) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, pad, group=self._pg(x))
+        return torch.cat([out[r, : sizes[r]] for r in range(self.world_size)], dim=0)
+
+    def reduce_scatter(self, x: torch.Tensor, dim: int = 0) -> torch.Tensor:
+        if self.world_size == 1:
+            return x
+        xm = x.movedim(dim, 0).contiguous()
+        out = torch.empty((xm.shape[0] // self.world_size,) + tuple(xm.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.reduce_scatter_tensor(out, xm, group=self._pg(x))
+        return out.movedim(0, dim)
+
+    def reduce_scatterv(self, x: torch.Tensor, sizes: Sequence[int]) -> torch.Tensor:
+        if self.world_size == 1:
+            return x
+        mx = max(sizes)
+        buf = torch.zeros((self.world_size, mx) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        off = 0
+        for r, s in enumerate(sizes):
+            buf[r, :s] = x[off: off + s]
+            off += s
+        out = torch.empty((mx,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.reduce_scatter_tensor(out, buf, group=self._pg(x))
+        return out[: sizes[self.rank_in_group]]
+
+    def broadcast(self, x: torch.Tensor, src: int = 0) -> torch.Tensor:
+        if self.world_size > 1:
+            dist.broadcast(x, src=self.ranks[src], group=self._pg(x))
+        return x
+
+    def send(self, x: torch.Tensor, dst: int) -> None:
+        dist.send(x, dst=self.ranks[dst], group=self._pg(x))
+
+    def recv(self, x: torch.Tensor, src: int) -> torch.Tensor:
+        dist.recv(x, src=self.ranks[src], group=self._pg(x))
+        return x
+
+    def all_gather_object(self, obj):
+        if self.world_size == 1:
+            return [obj]
+        out = [None] * self.world_size
+        dist.all_gather_object(out, obj, group=self.cpu_pg)
+        return out
+
+    def barrier(self) -> None:
+        if self.world_size > 1:
+            dist.barrier(group=self.cpu_pg)
+
+    def _pg(self, x: torch.Tensor):
+        return self.device_pg if x.is_cuda else self.cpu_pg
+
+    @property
+    def is_first_rank(self) -> bool:
+        return self.rank_in_group == 0
+
+    @property
+    def is_last_rank(self) -> bool:
+        return self.rank_in_group == self.world_size - 1
+
+
+@dataclass
+class _State:
+    rank: int = 0
+    world_size: int = 1
+    local_rank: int = 0
+    tp: Optional[Group] = None
+    pp: Optional[Group] = None
+    dp: Optional[Group] = None
+    ep: Optional[Group] = None
+    dcp: Optional[Group] = None
+    world: Optional[Group] = None
+    initialized: bool = False
+
+
+_S = _State()
+
+
+def _trivial(name: str) -> Group:
+    return Group([0], 0, name=name)
+
+
+def init_distributed(tensor_parallel_size: int = 1, pipeline_parallel_size: int = 1, data_parallel_size: int = 1,
+                     decode_context_parallel_size: int = 1, backend: Optional[str] = None,
+                     device: Optional[str] = None) -> None:
+    """Create the process groups.  Reads RANK / WORLD_SIZE / LOCAL_RANK / MASTER_* from the environment."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", str(rank)))
+    _S.rank, _S.world_size, _S.local_rank = rank, world, local_rank
+    if world == 1:
+        _S.tp = _trivial("tp"); _S.pp = _trivial("pp"); _S.dp = _trivial("dp"); _S.ep = _trivial("ep")
+        _S.dcp = _trivial("dcp"); _S.world = _trivial("world")
+        _S.initialized = True
+        return
+    use_cuda = (device or "cuda") == "cuda" and torch.cuda.is_available()
+    if use_cuda:
+        torch.cuda.set_device(local_rank)
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+        be = backend or ("cpu:gloo,cuda:nccl" if use_cuda else "gloo")
+        kw = {}
+        if use_cuda:
+            kw["device_id"] = torch.device("cuda", local_rank)
+        dist.init_process_group(backend=be, rank=rank, world_size=world, **kw)
+    tp, pp, dp = tensor_parallel_size, pipeline_parallel_size, data_parallel_size
+    assert tp * pp * dp == world, f"tp*pp*dp = {tp * pp * dp} != world size {world}"
+
+    def make(groups: list[list[int]], name: str) -> Group:
+        mine = None
+        for ranks in groups:
+            if len(ranks) == 1:
+                g = Group(ranks, rank, name=name) if rank in ranks else None
+            else:
+                dpg = dist.new_group(ranks, backend="nccl") if use_cuda else None
+                cpg = dist.new_group(ranks, backend="gloo")
+                g = Group(ranks, rank, dpg if use_cuda else cpg, cpg, name) if rank in ranks else None
+            if g is not None:
+                mine = g
+        return mine
+
+    # rank = (dp_idx * pp + pp_idx) * tp + tp_idx
+    tp_groups = [[(d * pp + p) * tp + t for t in range(tp)] for d in range(dp) for p in range(pp)]
+    pp_groups = [[(d * pp + p) * tp + t for p in range(pp)] for d in range(dp) for t in range(tp)]
+    dp_groups = [[(d * pp + p) * tp + t for d in range(dp)] for p in range(pp) for t in range(tp)]
+    ep_groups = [[(d * pp + p) * tp + t for d in range(dp) for t in range(tp)] for p in range(pp)]
+    _S.tp = make(tp_groups, "tp")
+    _S.pp = make(pp_groups, "pp")
+    _S.dp = make(dp_groups, "dp")
+    _S.ep = make(ep_groups, "ep")
+    dcp = decode_context_parallel_size
+    if dcp > 1:
+        assert tp % dcp == 0
+        dcp_groups = [g[i: i + dcp] for g in tp_groups for i in range(0, tp, dcp)]
+        _S.dcp = make(dcp_groups, "dcp")
+    else:
+        _S.dcp = Group([rank], rank, name="dcp")
+    _S.world = Group(list(range(world)), rank, dist.group.WORLD, dist.new_group(list(range(world)), backend="gloo"), "world")
+    _S.initialized = True
+
+
+def ensure_initialized() -> None:
+    if not _S.initialized:
+        init_distributed()
+
+
+def destroy() -> None:
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    global _S
+    _S.__init__()
+
+
+def get_tp_group() -> Group:
+    ensure_initialized(); return _S.tp
+
+
+def get_pp_group() -> Group:
+    ensure_initialized(); return _S.pp
+
+
+def get_dp_group() -> Group:
+    ensure_initialized(); return _S.dp
+
+
+def get_ep_group() -> Group:
+    ensure_initialized(); return _S.ep
+
+
+def get_dcp_group() -> Group:
+    ensure_initialized(); return _S.dcp
+
+
+def get_world_group() -> Group:
+    ensure_initialized(); return _S.world
+
+
+def tp_rank() -> int:
+    return get_tp_group().rank_in_group
+
+
+def tp_size() -> int:
+    return get_tp_group().world_size
+
+
+def global_rank() -> int:
+    return _S.rank
+
+
+def local_rank() -> int:
+    return _S.local_rank
+
+
+def tensor_model_parallel_all_reduce(x):
+    return get_tp_group().all_reduce(x)
+
+
+def tensor_model_parallel_all_gather(x, dim=-1):
+    return get_tp_group().all_gather(x, dim)
+
+
+def tensor_model_parallel_reduce_scatter(x, dim=0):
+    return get_tp_group().reduce_scatter(x, dim)
