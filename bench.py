@@ -1,0 +1,208 @@
+#!/usr/bin/env python
+"""Headline benchmark: output tokens/s of Llama-3.1-8B serving on N GPUs of one node.
+
+Workload (the reference's `vllm bench serve --dataset-name random --ignore-eos` recipe at the
+shape named for this build): 256 concurrent requests, each 1024 uniform-random input tokens
+and 128 forced output tokens, bf16, random-init weights, TP = N.
+
+One *step* is one full pass over that workload (prefill of all requests + 127 decode
+iterations).  Two measurements per run:
+
+* ``value``  - device-resident replay (`StaticWorkload`): inputs staged on the GPU, decode as
+  CUDA-graph replays with a device-side advance kernel; CUDA-event time, max over ranks.
+* ``e2e``    - the same workload through the public API (`LLM.generate`): host scheduler,
+  per-step pinned-memory H2D of the step inputs and D2H of the sampled tokens.
+
+`python bench.py --gpus N --steps K --warmup W`; for N > 1 launch under torchrun.
+`--impl reference` reports that the reference cannot be installed on this machine.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+MODEL = dict(architecture="LlamaForCausalLM", vocab_size=128256, hidden_size=4096, intermediate_size=14336,
+             num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-5,
+             rope_theta=500000.0, max_position_embeddings=8192)
+NUM_REQS, IN_LEN, OUT_LEN = 256, 1024, 128
+PREFILL_TOKENS = 8192
+BLOCK_SIZE = 128
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+
+    def start(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-lms", "200", "-i", str(self.gpu)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.p = None
+
+    def stop(self) -> dict:
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except Exception:
+            self.p.kill()
+        self.f.flush()
+        self.f.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.f.read().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, parts[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        os.unlink(self.f.name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--num-reqs", type=int, default=NUM_REQS)
+    ap.add_argument("--in-len", type=int, default=IN_LEN)
+    ap.add_argument("--out-len", type=int, default=OUT_LEN)
+    ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"],
+                    help="debug only; the reported config names the full model")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable":
+                              "reference needs the MACA SDK (cmake_maca, +metax torch, mcoplib) and setuptools_scm; "
+                              "pip install --no-index of /root/reference fails at metadata generation on this image"}))
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from vllm_metax_b200 import LLM, ModelConfig, SamplingParams
+    from vllm_metax_b200 import _custom_ops as ops
+    from vllm_metax_b200.engine.static_workload import StaticWorkload
+    from vllm_metax_b200.parallel import state as ps
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    assert world == args.gpus, f"launch with torchrun --nproc-per-node {args.gpus} (WORLD_SIZE={world})"
+    model = dict(MODEL, num_hidden_layers=args.layers)
+    N, P, O = args.num_reqs, args.in_len, args.out_len
+    llm = LLM(ModelConfig(**model, dtype=torch.bfloat16), tensor_parallel_size=args.gpus, block_size=BLOCK_SIZE,
+              max_model_len=P + O + BLOCK_SIZE, max_num_seqs=N, max_num_batched_tokens=PREFILL_TOKENS,
+              num_gpu_blocks=N * ((P + O + BLOCK_SIZE - 1) // BLOCK_SIZE) + 8, device="cuda")
+    runner = llm.engine.runner
+    dev = runner.device
+
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[dev.index])
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---------------------------------------------------------------- device-resident measurement
+    wl = StaticWorkload(runner, N, P, O, PREFILL_TOKENS)
+    wl.capture()
+    for _ in range(args.warmup):
+        wl.run()
+    barrier()
+    sampler = ClockSampler(dev.index or 0)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches = 0
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        launches += wl.run()
+    ev1.record()
+    barrier()
+    dev_ms = max_over_ranks(ev0.elapsed_time(ev1))
+    clocks = sampler.stop() if rank == 0 else {}
+    ops.check_kernel_status(dev.index or 0)
+    out_tokens = args.steps * N * O
+    value = out_tokens / (dev_ms / 1e3)
+
+    # ---------------------------------------------------------------- end to end through LLM.generate
+    g = torch.Generator().manual_seed(1)
+    prompts_host = torch.randint(0, model["vocab_size"], (N, P), generator=g).pin_memory()
+    prompts = prompts_host.tolist()
+    sp = SamplingParams(max_tokens=O, temperature=0.0, ignore_eos=True)
+    for _ in range(min(args.warmup, 1) or 1):
+        llm.generate(prompts, sp)
+    barrier()
+    runner.h2d_bytes = runner.d2h_bytes = 0
+    ttfts, tpots = [], []
+    t0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        outs = llm.generate(prompts, sp)
+        ttfts += [o.metrics.ttft for o in outs]
+        tpots += [o.metrics.tpot for o in outs]
+        assert all(len(o.outputs[0].token_ids) == O for o in outs)
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3))
+    e2e_value = out_tokens / (e2e_ms / 1e3)
+    ops.check_kernel_status(dev.index or 0)
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": "output tok/s (Llama-3.1-8B, 256 req x 1024 in / 128 out, device-timed, max over ranks)",
+            "value": round(value, 1), "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(dev_ms / args.steps, 2), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "impl": "ours",
+            "config": {"model": "Llama-3.1-8B" if args.layers == 32 else f"Llama-3.1-8B[{args.layers} layers, debug]",
+                       "global_batch": N, "seq_len": P, "output_len": O, "parallelism": f"tp{args.gpus}",
+                       "block_size": BLOCK_SIZE, "prefill_tokens_per_step": PREFILL_TOKENS,
+                       "l2": "inputs larger than L2 (16 GB weights + KV streamed every iteration)",
+                       "step": "one pass over the whole workload (prefill + decode of all requests)"},
+            "clocks": clocks,
+            "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "ms_per_step": round(e2e_ms / args.steps, 2),
+                    "h2d_bytes_per_step": runner.h2d_bytes // args.steps,
+                    "d2h_bytes_per_step": runner.d2h_bytes // args.steps,
+                    "p50_ttft_ms": round(statistics.median(ttfts) * 1e3, 2),
+                    "p50_tpot_ms": round(statistics.median(tpots) * 1e3, 3)},
+            "gpu_launches": launches,
+        }))
+    if world > 1:
+        ps.destroy()
+
+
+if __name__ == "__main__":
+    main()

@@ -47,12 +47,31 @@ def native_loaded() -> bool:
     return _loaded
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Number of native kernel launches issued through this module so far (graph replays are
+    accounted by their owners: launches counted during capture x replays)."""
+    return _launches
+
+
+_force_ref = None
+_tc_gemm = None
+
+
 def _use_cuda(t: torch.Tensor) -> bool:
-    if not t.is_cuda or envs.B200_FORCE_REFERENCE_OPS:
+    global _launches, _force_ref
+    if not t.is_cuda:
+        return False
+    if _force_ref is None:
+        _force_ref = bool(envs.B200_FORCE_REFERENCE_OPS)
+    if _force_ref:
         return False
     if not _loaded and not load_native():
         raise RuntimeError("CUDA tensor given but the native library _b200_C.so is not built; "
                            "run `python -m vllm_metax_b200._build`")
+    _launches += 1
     return True
 
 
@@ -83,7 +102,10 @@ def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
     if _use_cuda(a) and a.dtype in (torch.bfloat16, torch.float16):
         if out is None:
             out = torch.empty(a.shape[0], w.shape[0], dtype=a.dtype, device=a.device)
-        if envs.B200_TCGEN05_GEMM:
+        global _tc_gemm
+        if _tc_gemm is None:
+            _tc_gemm = bool(envs.B200_TCGEN05_GEMM)
+        if _tc_gemm:
             torch.ops.b200.gemm(out, a, w, bias, residual, force_bn)
         else:  # debug switch only: library GEMM
             torch.addmm(bias, a, w.t(), out=out) if bias is not None else torch.mm(a, w.t(), out=out)

@@ -248,7 +248,9 @@ class ModelRunner:
         torch.cuda.current_stream().wait_stream(stream)
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=stream):
+        if getattr(self, "_graph_pool", None) is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        with torch.cuda.graph(g, pool=self._graph_pool, stream=stream):
             h = self._forward(md, bucket)
             logits = self.model.compute_logits(h)
             ops.argmax(logits, self.sampled[:bucket])
