@@ -25,7 +25,7 @@ namespace b200 {
 
 constexpr int kDecWarps = 4;
 constexpr int kDecTile = 16;    // tokens per tile
-template <int D> __host__ __device__ constexpr int dec_stages() { return D <= 128 ? 4 : 3; }
+template <int D> __host__ __device__ constexpr int dec_stages() { return 3; }  // D <= 128: ~100 KB per CTA, two CTAs per SM
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
   const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
@@ -96,7 +96,7 @@ struct DecSmem {
 };
 
 template <typename T, int D, int KIND>
-__global__ void __launch_bounds__(kDecWarps * 32) paged_decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kDecWarps * 32, (D <= 128 ? 2 : 1)) paged_decode_kernel(const DecodeParams p) {
   using S = DecSmem<D, KIND>;
   constexpr int CPR = D / 8;  // 16-byte chunks per converted row
   constexpr int kDecStages = dec_stages<D>();
@@ -316,11 +316,16 @@ __global__ void __launch_bounds__(kDecWarps * 32) paged_decode_kernel(const Deco
       rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 2);
       l_run[h] = l_run[h] * corr[h] + rs[h];
     }
-    // ---- O = O * corr + P V
+    // ---- O = O * corr + P V  (the rescale is skipped when no row of the warp raised its max)
+    const bool rescale = __any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f);
+    if (rescale) {
+#pragma unroll
+      for (int nd = 0; nd < D / 8; ++nd) {
+        o[nd][0] *= corr[0]; o[nd][1] *= corr[0]; o[nd][2] *= corr[1]; o[nd][3] *= corr[1];
+      }
+    }
 #pragma unroll
     for (int nd = 0; nd < D / 8; nd += 2) {
-      o[nd][0] *= corr[0]; o[nd][1] *= corr[0]; o[nd][2] *= corr[1]; o[nd][3] *= corr[1];
-      o[nd + 1][0] *= corr[0]; o[nd + 1][1] *= corr[0]; o[nd + 1][2] *= corr[1]; o[nd + 1][3] *= corr[1];
       uint32_t vf[4];
       const int mat = lane >> 3;
       const int r = (mat & 1) * 8 + (lane & 7);

@@ -298,9 +298,12 @@ static void gemm_dispatch(const void* A, const void* W, void* C, const void* bia
   }
   int bn = force_bn;
   if (bn <= 0) {
+    // Every N tile re-reads the whole A panel from L2, so narrow tiles only pay off while the
+    // grid would otherwise leave most SMs idle; 128 is the floor once M spans a full tile.
     const int mt = ceil_div(M, kBM);
     bn = 256;
-    while (bn > 32 && mt * ceil_div(N, bn) < sms) bn >>= 1;
+    while (bn > 128 && mt * ceil_div(N, bn) < sms) bn >>= 1;
+    while (bn > 32 && mt * ceil_div(N, bn) < sms / 4) bn >>= 1;
   }
   if (bn >= 256)
     launch_cfg<T, 256, 4, false>(A, M, lda, W, N, ldw, C, bias, residual, K, ldc, ldr, stream, status);

@@ -1,0 +1,153 @@
+"""Kernel micro-benchmarks at serving shapes (CUDA events, L2 flushed between iterations).
+
+    python -m vllm_metax_b200.utils.microbench --op all
+    python -m vllm_metax_b200.utils.microbench --op gemm --m 8192 --n 6144 --k 4096 --iters 3
+
+Each op reports its median time and the achieved TFLOP/s or GB/s; ``--compare`` adds the
+library kernel (cuBLAS) time for GEMMs.  With few ``--iters`` and a single ``--op`` the
+command doubles as the small case for an ``ncu`` capture of that kernel.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from .. import _custom_ops as ops
+from ..ops import reference as ref
+
+DEV = "cuda"
+
+
+class Timer:
+    def __init__(self, iters: int, warmup: int):
+        self.iters, self.warmup = iters, warmup
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+
+    def __call__(self, fn) -> float:
+        for _ in range(self.warmup):
+            fn()
+        ts = []
+        for _ in range(self.iters):
+            self.flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        ts.sort()
+        return ts[len(ts) // 2]
+
+
+def paged_cache(B, L, Hkv, D, bs, dtype=torch.bfloat16):
+    nblk = (L + bs - 1) // bs
+    total = B * nblk + 1
+    cache = torch.randn(total, 2, bs, Hkv, D, device=DEV, dtype=torch.float32).to(dtype)
+    bt = torch.randperm(B * nblk, device=DEV).to(torch.int32).view(B, nblk)
+    return cache, bt
+
+
+def bench_gemm(t: Timer, M, N, K, compare: bool, force_bn: int = 0) -> dict:
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.02
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    ms = t(lambda: ops.gemm(a, w, out=out, force_bn=force_bn))
+    r = {"ms": round(ms, 4), "tflops": round(2 * M * N * K / ms / 1e9, 1),
+         "gbs": round((M * K + N * K + M * N) * 2 / ms / 1e6, 1)}
+    if compare:
+        mc = t(lambda: torch.mm(a, w.t(), out=out))
+        r["cublas_ms"] = round(mc, 4)
+        r["cublas_tflops"] = round(2 * M * N * K / mc / 1e9, 1)
+    return r
+
+
+def bench_prefill(t: Timer, B, L, Hq, Hkv, D, bs) -> dict:
+    cache, bt = paged_cache(B, L, Hkv, D, bs)
+    q = torch.randn(B * L, Hq, D, device=DEV, dtype=torch.bfloat16)
+    qsl = torch.arange(B + 1, device=DEV, dtype=torch.int32) * L
+    sl = torch.full((B,), L, device=DEV, dtype=torch.int32)
+    out = torch.empty_like(q)
+    ms = t(lambda: ops.paged_attention_prefill(q, cache, bt, sl, qsl, D ** -0.5, out=out, max_q_len=L))
+    return {"ms": round(ms, 4), "tflops": round(4 * B * L * L / 2 * Hq * D / ms / 1e9, 1)}
+
+
+def bench_decode(t: Timer, B, L, Hq, Hkv, D, bs, kv="bf16") -> dict:
+    cache, bt = paged_cache(B, L, Hkv, D, bs)
+    scales = None
+    eb = 2
+    if kv == "int8":
+        cache = (cache.float() * 40).round().clamp(-127, 127).to(torch.int8)
+        scales = torch.rand(cache.shape[:-1], device=DEV) * 0.02 + 0.01
+        eb = 1
+    q = torch.randn(B, Hq, D, device=DEV, dtype=torch.bfloat16)
+    sl = torch.full((B,), L, device=DEV, dtype=torch.int32)
+    out = torch.empty_like(q)
+    ms = t(lambda: ops.paged_attention_decode(q, cache, bt, sl, D ** -0.5, out=out, kv_scales=scales, max_seq_len=L))
+    return {"ms": round(ms, 4), "gbs": round(B * L * Hkv * D * eb * 2 / ms / 1e6, 1)}
+
+
+def bench_elementwise(t: Timer, T, H, I) -> dict:
+    res = {}
+    x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16)
+    r = torch.randn_like(x)
+    w = torch.ones(H, device=DEV, dtype=torch.bfloat16)
+    ms = t(lambda: ops.fused_add_rms_norm(x, r, w, 1e-5))
+    res["add_rmsnorm"] = {"ms": round(ms, 4), "gbs": round(T * H * 2 * 4 / ms / 1e6, 1)}
+    g = torch.randn(T, 2 * I, device=DEV, dtype=torch.bfloat16)
+    o = torch.empty(T, I, device=DEV, dtype=torch.bfloat16)
+    ms = t(lambda: ops.silu_and_mul(g, o))
+    res["silu_mul"] = {"ms": round(ms, 4), "gbs": round(T * I * 2 * 3 / ms / 1e6, 1)}
+    qkv = torch.randn(T, 6144, device=DEV, dtype=torch.bfloat16)
+    pos = torch.arange(T, device=DEV) % 1024
+    cs = ref.build_rope_cache(128, 2048, 500000.0).to(DEV)
+    kvc = torch.zeros(T // 128 + 1, 2, 128, 8, 128, device=DEV, dtype=torch.bfloat16)
+    slots = torch.arange(T, device=DEV)
+    ms = t(lambda: ops.rope_and_cache(pos, qkv[:, :4096], qkv[:, 4096:5120], qkv[:, 5120:], 128, cs, True, kvc, slots))
+    res["rope_cache"] = {"ms": round(ms, 4), "gbs": round((T * 5120 * 2 * 2 + T * 2048 * 2 + T * 2048 * 2) / ms / 1e6, 1)}
+    return res
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="all", choices=["all", "gemm", "prefill", "decode", "elementwise"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=6144)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--force-bn", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--seq", type=int, default=1100)
+    ap.add_argument("--kv", default="bf16")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--compare", action="store_true")
+    a = ap.parse_args()
+    ops.load_native()
+    t = Timer(a.iters, a.warmup)
+    res = {}
+    H, I, V = 4096, 14336, 128256
+    if a.op == "gemm":
+        res[f"gemm_{a.m}x{a.n}x{a.k}"] = bench_gemm(t, a.m, a.n, a.k, a.compare, a.force_bn)
+    if a.op == "all":
+        for M in (8192, 256):
+            for name, (N, K) in {"qkv": (6144, H), "o": (H, H), "gate_up": (2 * I, H), "down": (H, I),
+                                 "lm_head": (V, H)}.items():
+                if name == "lm_head" and M > 256:
+                    continue
+                res[f"gemm_{name}_M{M}"] = bench_gemm(t, M, N, K, True)
+    if a.op in ("all", "prefill"):
+        res["attn_prefill_8x1024"] = bench_prefill(t, 8, 1024, 32, 8, 128, 128)
+    if a.op in ("all", "decode"):
+        res[f"attn_decode_{a.batch}x{a.seq}_{a.kv}"] = bench_decode(t, a.batch, a.seq, 32, 8, 128, 128, a.kv)
+    if a.op in ("all", "elementwise"):
+        for T in (8192, 256):
+            for k, v in bench_elementwise(t, T, H, I).items():
+                res[f"{k}_T{T}"] = v
+    torch.cuda.synchronize()
+    ops.check_kernel_status(0)
+    print(json.dumps(res, indent=1))
+
+
+if __name__ == "__main__":
+    main()
