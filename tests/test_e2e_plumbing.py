@@ -44,7 +44,7 @@ def plain_forward(model, ids):
         x = x + a @ lyr.self_attn.o_proj.weight.float().t()
         h = norm(x, lyr.post_attention_layernorm.weight)
         gu = h @ lyr.mlp.gate_up_proj.weight.float().t()
-        g, u = gu.chunk(2, -1)
+        g, u = gu[:, 0::2], gu[:, 1::2]   # gate / up rows are stored interleaved
         x = x + (torch.nn.functional.silu(g) * u) @ lyr.mlp.down_proj.weight.float().t()
     x = norm(x, model.model.norm.weight)
     return x @ model.lm_head.weight.float().t()[:, : cfg.vocab_size]

@@ -421,3 +421,27 @@ def test_penalties_and_advance_and_embedding():
     assert sl.tolist() == [2, 17, 18, 33, 102]
     exp = [int(bt[i, p // bs]) * bs + p % bs for i, p in enumerate([1, 16, 17, 32, 101])]
     assert slots.tolist() == exp
+
+
+@pytest.mark.parametrize("M", [5, 48, 256, 1000])
+def test_gemm_fused_silu_gate_epilogue(M):
+    K, I = 1024, 1408
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(2 * I, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    got = ops.gemm_silu_mul(a, w)
+    want = ops.gemm_silu_mul(a.cpu(), w.cpu()).to(DEV)
+    assert got.shape == (M, I)
+    assert cos_diff(got, want) < 1e-4
+    torch.testing.assert_close(got.float(), want.float(), rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 512, 256), (1024, 1536, 4096), (1000, 1288, 520), (8192, 6144, 4096)])
+def test_gemm_cta_pair(M, N, K):
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    want = a.float() @ w.float().t() + bias.float() + res.float()
+    got = ops.gemm(a, w, bias, res, force_bn=512)
+    assert (got.float() - want).abs().max() / want.abs().max() < 1.5e-2
+    assert cos_diff(got, want) < 1e-5

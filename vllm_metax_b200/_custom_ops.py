@@ -106,7 +106,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
         if _tc_gemm is None:
             _tc_gemm = bool(envs.B200_TCGEN05_GEMM)
         if _tc_gemm:
-            torch.ops.b200.gemm(out, a, w, bias, residual, force_bn)
+            torch.ops.b200.gemm(out, a, w, bias, residual, force_bn, 0)
         else:  # debug switch only: library GEMM
             torch.addmm(bias, a, w.t(), out=out) if bias is not None else torch.mm(a, w.t(), out=out)
             if residual is not None:
@@ -119,6 +119,24 @@ def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
         out.copy_(y)
         return out
     return y
+
+
+def gemm_silu_mul(a: torch.Tensor, w_interleaved: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Gated MLP first half in one kernel: ``w_interleaved [2I, K]`` holds (gate_j, up_j) in rows
+    (2j, 2j+1); returns ``silu(a @ gate^T) * (a @ up^T)`` of shape ``[M, I]`` - the activation is
+    applied in the GEMM epilogue, so the ``[M, 2I]`` intermediate never reaches memory."""
+    if _use_cuda(a) and a.dtype in (torch.bfloat16, torch.float16):
+        if out is None:
+            out = torch.empty(a.shape[0], w_interleaved.shape[0] // 2, dtype=a.dtype, device=a.device)
+        torch.ops.b200.gemm(out, a, w_interleaved, bias, None, 0, 1)
+        return out
+    y = ref.gemm(a, w_interleaved, bias)
+    r = (torch.nn.functional.silu(y[:, 0::2].float()) * y[:, 1::2].float()).to(a.dtype)
+    if out is not None:
+        out.copy_(r)
+        return out
+    return r
 
 
 # --------------------------------------------------------------------------- norms

@@ -6,6 +6,8 @@
 #include <torch/library.h>
 #include <torch/types.h>
 
+#include <cstdlib>
+
 #include "ops.h"
 
 namespace {
@@ -46,11 +48,12 @@ Tensor get_status(int64_t device) { return status_tensor((int)device); }
 
 // ------------------------------------------------------------------ GEMM
 void gemm(Tensor& out, const Tensor& a, const Tensor& w, const optional<Tensor>& bias,
-          const optional<Tensor>& residual, int64_t force_bn) {
+          const optional<Tensor>& residual, int64_t force_bn, int64_t epi) {
   TORCH_CHECK(a.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm expects 2-D tensors");
   TORCH_CHECK(a.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1, "inner dims must be contiguous");
   const int M = a.size(0), K = a.size(1), N = w.size(0);
-  TORCH_CHECK(w.size(1) == K && out.size(0) == M && out.size(1) == N, "gemm shape mismatch");
+  TORCH_CHECK(w.size(1) == K && out.size(0) == M && out.size(1) == (epi == 1 ? N / 2 : N), "gemm shape mismatch");
+  TORCH_CHECK(epi == 0 || (!residual.has_value() && N % 16 == 0), "gated epilogue: no residual, N % 16 == 0");
   TORCH_CHECK(K % 8 == 0 && a.stride(0) % 8 == 0 && w.stride(0) % 8 == 0 && out.stride(0) % 8 == 0,
               "gemm: K and row pitches must be multiples of 8 elements");
   TORCH_CHECK(a.scalar_type() == w.scalar_type() && a.scalar_type() == out.scalar_type(), "gemm dtype mismatch");
@@ -60,8 +63,19 @@ void gemm(Tensor& out, const Tensor& a, const Tensor& w, const optional<Tensor>&
     ldr = residual->stride(0);
   }
   const c10::cuda::CUDAGuard guard(a.device());
+  // CTA-pair (cta_group::2) kernel for large problems: at least one 256 x 256 tile per pair of SMs.
+  static const bool pair_default = [] {
+    const char* e = std::getenv("B200_GEMM_PAIR");
+    return e == nullptr || std::atoi(e) != 0;
+  }();
+  const int64_t pair_tiles = ((M + 255) / 256) * (int64_t)((N + 255) / 256);
+  if (force_bn == 512 || (force_bn == 0 && pair_default && M >= 512 && pair_tiles >= 64)) {
+    b200::gemm_tn_pair(a.data_ptr(), w.data_ptr(), out.data_ptr(), ptr(bias), ptr(residual), M, N, K, a.stride(0),
+                       w.stride(0), out.stride(0), ldr, dtype16(a), cur_stream(), status_ptr(a), (int)epi);
+    return;
+  }
   b200::gemm_tn(a.data_ptr(), w.data_ptr(), out.data_ptr(), ptr(bias), ptr(residual), M, N, K, a.stride(0),
-                w.stride(0), out.stride(0), ldr, dtype16(a), cur_stream(), status_ptr(a), (int)force_bn);
+                w.stride(0), out.stride(0), ldr, dtype16(a), cur_stream(), status_ptr(a), (int)force_bn, (int)epi);
 }
 
 // ------------------------------------------------------------------ norms
@@ -343,7 +357,7 @@ void embedding(Tensor& out, const Tensor& table, const Tensor& ids, int64_t voca
 
 TORCH_LIBRARY(b200, m) {
   m.def("get_status(int device) -> Tensor", &get_status);
-  m.def("gemm(Tensor(a!) out, Tensor a, Tensor w, Tensor? bias, Tensor? residual, int force_bn) -> ()", &gemm);
+  m.def("gemm(Tensor(a!) out, Tensor a, Tensor w, Tensor? bias, Tensor? residual, int force_bn, int epi) -> ()", &gemm);
   m.def("rms_norm(Tensor(a!) out, Tensor x, Tensor weight, float eps, bool gemma) -> ()", &rms_norm);
   m.def("fused_add_rms_norm(Tensor(a!) x, Tensor(b!) residual, Tensor weight, float eps, bool gemma) -> ()",
         &fused_add_rms_norm);

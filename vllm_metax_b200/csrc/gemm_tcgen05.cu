@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(192, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA,   // 128-row operand
                const __grid_constant__ CUtensorMap tmB,   // BN-row operand
                T* __restrict__ C, const T* __restrict__ bias, const T* __restrict__ residual,
-               int rows_a, int rows_b, int K, int ldc, int ldr, StatusWord* status) {
+               int rows_a, int rows_b, int K, int ldc, int ldr, int epi, StatusWord* status) {
   using L = GemmSmemLayout<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -183,7 +183,32 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA,   // 128-row operand
         const int cb0 = tb * BN + c;  // first index in the BN-row operand
         if constexpr (!SWAP) {
           // row = token (ra), columns = output features cb0..cb0+CH
-          if (ra < rows_a) {
+          if (ra < rows_a && epi == 1) {
+            // columns hold interleaved (gate, up) pairs: out[:, j] = silu(gate_j) * up_j
+            T* dst = C + (size_t)ra * ldc + (cb0 >> 1);
+#pragma unroll
+            for (int v = 0; v < CH / 8; ++v) {
+              const int col = cb0 + v * 8;
+              if (col + 8 <= rows_b) {
+                float f[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[v * 8 + i]);
+                if (bias) {
+                  float b[8];
+                  unpack8<T>(*reinterpret_cast<const uint4*>(bias + col), b);
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) f[i] += b[i];
+                }
+                T o4[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float g = to_f(from_f<T>(f[2 * i])), u = to_f(from_f<T>(f[2 * i + 1]));
+                  o4[i] = from_f<T>(g / (1.f + __expf(-g)) * u);
+                }
+                *reinterpret_cast<uint2*>(dst + v * 4) = *reinterpret_cast<const uint2*>(o4);
+              }
+            }
+          } else if (ra < rows_a) {
             T* dst = C + (size_t)ra * ldc + cb0;
             const T* res = residual ? residual + (size_t)ra * ldr + cb0 : nullptr;
 #pragma unroll
@@ -220,8 +245,18 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA,   // 128-row operand
           }
         } else {
           // row = output feature (ra), columns = tokens cb0..cb0+CH; C is [tokens, features]
-          if (ra < rows_a) {
-            const float bv = bias ? to_f(bias[ra]) : 0.f;
+          const float bv = (bias && ra < rows_a) ? to_f(bias[ra]) : 0.f;
+          if (epi == 1) {
+            // lanes hold interleaved (gate, up) features: even lane = gate, odd lane = up
+#pragma unroll
+            for (int i = 0; i < CH; ++i) {
+              const int tok = cb0 + i;
+              const float g = to_f(from_f<T>(__uint_as_float(r[i]) + bv));
+              const float u = __shfl_down_sync(0xffffffffu, g, 1);
+              if ((lane & 1) == 0 && ra < rows_a && tok < rows_b)
+                C[(size_t)tok * ldc + (ra >> 1)] = from_f<T>(g / (1.f + __expf(-g)) * u);
+            }
+          } else if (ra < rows_a) {
 #pragma unroll
             for (int i = 0; i < CH; ++i) {
               const int tok = cb0 + i;
@@ -260,7 +295,7 @@ static int num_sms() {
 
 template <typename T, int BN, int STAGES, bool SWAP>
 static void launch_cfg(const void* a_op, int rows_a, int lda, const void* b_op, int rows_b, int ldb, void* C,
-                       const void* bias, const void* residual, int K, int ldc, int ldr, cudaStream_t stream,
+                       const void* bias, const void* residual, int K, int ldc, int ldr, int epi, cudaStream_t stream,
                        StatusWord* status) {
   using L = GemmSmemLayout<BN, STAGES>;
   static_assert(L::kDynSmem <= 232448, "shared memory budget exceeded");
@@ -277,23 +312,23 @@ static void launch_cfg(const void* a_op, int rows_a, int lda, const void* b_op, 
   const int tiles = ceil_div(rows_a, kBM) * ceil_div(rows_b, BN);
   const int grid = tiles < num_sms() ? tiles : num_sms();
   kern<<<grid, 192, L::kDynSmem, stream>>>(tmA, tmB, reinterpret_cast<T*>(C), reinterpret_cast<const T*>(bias),
-                                           reinterpret_cast<const T*>(residual), rows_a, rows_b, K, ldc, ldr, status);
+                                           reinterpret_cast<const T*>(residual), rows_a, rows_b, K, ldc, ldr, epi, status);
 }
 
 template <typename T>
 static void gemm_dispatch(const void* A, const void* W, void* C, const void* bias, const void* residual, int M, int N,
-                          int K, int lda, int ldw, int ldc, int ldr, cudaStream_t stream, StatusWord* status,
+                          int K, int lda, int ldw, int ldc, int ldr, int epi, cudaStream_t stream, StatusWord* status,
                           int force_bn) {
   const int sms = num_sms();
   if (M <= 64 && force_bn <= 0 || force_bn < 0) {
     // swap-AB: weight rows on the 128-row MMA operand, tokens on the N operand
     const int bn = (force_bn < 0) ? -force_bn : (M <= 16 ? 16 : (M <= 32 ? 32 : 64));
     if (bn == 16)
-      launch_cfg<T, 16, 8, true>(W, N, ldw, A, M, lda, C, bias, residual, K, ldc, ldr, stream, status);
+      launch_cfg<T, 16, 8, true>(W, N, ldw, A, M, lda, C, bias, residual, K, ldc, ldr, epi, stream, status);
     else if (bn == 32)
-      launch_cfg<T, 32, 8, true>(W, N, ldw, A, M, lda, C, bias, residual, K, ldc, ldr, stream, status);
+      launch_cfg<T, 32, 8, true>(W, N, ldw, A, M, lda, C, bias, residual, K, ldc, ldr, epi, stream, status);
     else
-      launch_cfg<T, 64, 8, true>(W, N, ldw, A, M, lda, C, bias, residual, K, ldc, ldr, stream, status);
+      launch_cfg<T, 64, 8, true>(W, N, ldw, A, M, lda, C, bias, residual, K, ldc, ldr, epi, stream, status);
     return;
   }
   int bn = force_bn;
@@ -306,24 +341,25 @@ static void gemm_dispatch(const void* A, const void* W, void* C, const void* bia
     while (bn > 32 && mt * ceil_div(N, bn) < sms / 4) bn >>= 1;
   }
   if (bn >= 256)
-    launch_cfg<T, 256, 4, false>(A, M, lda, W, N, ldw, C, bias, residual, K, ldc, ldr, stream, status);
+    launch_cfg<T, 256, 4, false>(A, M, lda, W, N, ldw, C, bias, residual, K, ldc, ldr, epi, stream, status);
   else if (bn == 128)
-    launch_cfg<T, 128, 6, false>(A, M, lda, W, N, ldw, C, bias, residual, K, ldc, ldr, stream, status);
+    launch_cfg<T, 128, 6, false>(A, M, lda, W, N, ldw, C, bias, residual, K, ldc, ldr, epi, stream, status);
   else if (bn == 64)
-    launch_cfg<T, 64, 8, false>(A, M, lda, W, N, ldw, C, bias, residual, K, ldc, ldr, stream, status);
+    launch_cfg<T, 64, 8, false>(A, M, lda, W, N, ldw, C, bias, residual, K, ldc, ldr, epi, stream, status);
   else
-    launch_cfg<T, 32, 8, false>(A, M, lda, W, N, ldw, C, bias, residual, K, ldc, ldr, stream, status);
+    launch_cfg<T, 32, 8, false>(A, M, lda, W, N, ldw, C, bias, residual, K, ldc, ldr, epi, stream, status);
 }
 
+// epi: 0 = plain, 1 = SiLU-gate epilogue over interleaved (gate, up) output features (C is [M, N/2]).
 // dtype: 0 = bf16, 1 = fp16.  force_bn: 0 = heuristic, >0 = that BN without swap, <0 = swap with |BN| tokens.
 void gemm_tn(const void* A, const void* W, void* C, const void* bias, const void* residual, int M, int N, int K,
-             int lda, int ldw, int ldc, int ldr, int dtype, cudaStream_t stream, void* status, int force_bn) {
+             int lda, int ldw, int ldc, int ldr, int dtype, cudaStream_t stream, void* status, int force_bn, int epi) {
   if (M <= 0 || N <= 0) return;
   if (dtype == 0)
-    gemm_dispatch<__nv_bfloat16>(A, W, C, bias, residual, M, N, K, lda, ldw, ldc, ldr, stream,
+    gemm_dispatch<__nv_bfloat16>(A, W, C, bias, residual, M, N, K, lda, ldw, ldc, ldr, epi, stream,
                                  reinterpret_cast<StatusWord*>(status), force_bn);
   else
-    gemm_dispatch<__half>(A, W, C, bias, residual, M, N, K, lda, ldw, ldc, ldr, stream,
+    gemm_dispatch<__half>(A, W, C, bias, residual, M, N, K, lda, ldw, ldc, ldr, epi, stream,
                           reinterpret_cast<StatusWord*>(status), force_bn);
 }
 

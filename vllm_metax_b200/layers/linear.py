@@ -127,6 +127,36 @@ class MergedColumnParallelLinear(ColumnParallelLinear):
         param.data.narrow(out_dim, off // scale, max(per // scale, 1)).copy_(src)
 
 
+class GateUpSiluLinear(LinearBase):
+    """``silu(x W_gate^T) * (x W_up^T)`` as ONE tcgen05 GEMM with the activation in its epilogue.
+
+    The (column-parallel) gate and up shards are stored row-interleaved - row ``2j`` is
+    ``gate_j``, row ``2j+1`` is ``up_j`` - so every accumulator tile holds matching pairs.
+    Unquantised weights only; quantised checkpoints use ``MergedColumnParallelLinear`` + the
+    activation kernel.
+    """
+
+    def __init__(self, in_features: int, intermediate_size: int, dtype=torch.bfloat16, prefix: str = ""):
+        super().__init__(in_features, 2 * intermediate_size, False, dtype, None, prefix)
+        self.tp = ps.tp_size()
+        assert intermediate_size % self.tp == 0
+        self.inter_local = intermediate_size // self.tp
+        self._make(in_features, 2 * self.inter_local, False)
+
+    def weight_loader(self, param, loaded, shard_id=None):
+        r, n = ps.tp_rank(), self.inter_local
+        if shard_id is None:  # merged [gate; up] on disk
+            full = loaded.shape[0] // 2
+            self.weight_loader(param, loaded[:full], 0)
+            self.weight_loader(param, loaded[full:], 1)
+            return
+        param.data[int(shard_id)::2].copy_(loaded.narrow(0, r * n, n))
+
+    def forward(self, x):
+        x2, lead = self._x2d(x)
+        return ops.gemm_silu_mul(x2, self.weight).reshape(*lead, -1)
+
+
 class QKVParallelLinear(ColumnParallelLinear):
     """Fused q/k/v projection; KV heads are replicated when there are fewer than TP ranks."""
 

@@ -24,7 +24,7 @@ from .. import _custom_ops as ops
 from ..config import ModelConfig
 from ..layers.attention import Attention
 from ..layers.basic import ParallelLMHead, RMSNorm, SiluAndMul, VocabParallelEmbedding, get_rope
-from ..layers.linear import MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear
+from ..layers.linear import GateUpSiluLinear, MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear
 from ..parallel import state as ps
 from ..quantization import get_linear_method
 
@@ -33,13 +33,21 @@ class LlamaMLP(nn.Module):
     def __init__(self, cfg: ModelConfig, intermediate_size: int, prefix: str, reduce_results: bool = True):
         super().__init__()
         qm = lambda name: get_linear_method(cfg, f"{prefix}.{name}")
-        self.gate_up_proj = MergedColumnParallelLinear(cfg.hidden_size, [intermediate_size] * 2, cfg.mlp_bias,
-                                                       cfg.dtype, qm("gate_up_proj"), prefix=f"{prefix}.gate_up_proj")
+        self.fused_act = qm("gate_up_proj") is None and not cfg.mlp_bias and cfg.hidden_act == "silu"
+        if self.fused_act:
+            self.gate_up_proj = GateUpSiluLinear(cfg.hidden_size, intermediate_size, cfg.dtype,
+                                                 prefix=f"{prefix}.gate_up_proj")
+        else:
+            self.gate_up_proj = MergedColumnParallelLinear(cfg.hidden_size, [intermediate_size] * 2, cfg.mlp_bias,
+                                                           cfg.dtype, qm("gate_up_proj"),
+                                                           prefix=f"{prefix}.gate_up_proj")
         self.down_proj = RowParallelLinear(intermediate_size, cfg.hidden_size, cfg.mlp_bias, cfg.dtype,
                                            qm("down_proj"), reduce_results=reduce_results, prefix=f"{prefix}.down_proj")
         self.act = SiluAndMul()
 
     def forward(self, x):
+        if self.fused_act:
+            return self.down_proj(self.gate_up_proj(x))
         return self.down_proj(self.act(self.gate_up_proj(x)))
 
 
