@@ -1,0 +1,119 @@
+"""Multi-GPU tests (one process per GPU, NCCL + peer memory).  Skipped with fewer than 2 GPUs."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _launch(fn, world, *args, timeout=300):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29800 + (os.getpid() % 150)
+    procs = [ctx.Process(target=_entry, args=(fn, r, world, port, q) + args) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = q.get(timeout=timeout)
+    for p in procs:
+        p.join(timeout=120)
+    assert res == "ok", res
+    assert all(p.exitcode == 0 for p in procs)
+
+
+def _entry(fn, rank, world, port, q, *args):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    try:
+        fn(rank, world, *args)
+        if rank == 0:
+            q.put("ok")
+    except BaseException as e:
+        import traceback
+
+        if rank == 0:
+            q.put("rank0 failed: " + "".join(traceback.format_exception(e))[-3000:])
+        raise
+
+
+def _fused_ar_worker(rank, world):
+    from vllm_metax_b200 import _custom_ops as ops
+    from vllm_metax_b200.ops import reference as ref
+    from vllm_metax_b200.parallel import state as ps
+    from vllm_metax_b200.parallel.fused_collectives import FusedRowParallelNorm, rows_per_rank
+
+    ps.init_distributed(tensor_parallel_size=world)
+    dev = torch.device("cuda", rank)
+    g = ps.get_tp_group()
+    H, K = 2048, 512
+    fused = FusedRowParallelNorm(g, dev, 1024, H, torch.bfloat16)
+    gen = torch.Generator().manual_seed(0)          # same stream on every rank
+    for it, T in enumerate((5, 256, 1000, 130, 1024)):
+        xs = [torch.randn(T, K, generator=gen).to(torch.bfloat16) for _ in range(world)]
+        ws = [(torch.randn(H, K, generator=gen) * 0.05).to(torch.bfloat16) for _ in range(world)]
+        res_full = torch.randn(T, H, generator=gen).to(torch.bfloat16)
+        nw = torch.randn(H, generator=gen).to(torch.bfloat16)
+        rpr = rows_per_rank(T, world)
+        res = torch.zeros(rpr, H, dtype=torch.bfloat16, device=dev)
+        n_mine = max(0, min(rpr, T - rank * rpr))
+        res[:n_mine] = res_full[rank * rpr: rank * rpr + n_mine].to(dev)
+        add = it != 0
+        out = fused(xs[rank].to(dev), ws[rank].to(dev), res, nw.to(dev), 1e-5, add_residual=add)
+        torch.cuda.synchronize()
+        ops.check_kernel_status(rank)
+        # oracle in fp32 (partials rounded to bf16 as on the wire)
+        total = sum((xs[r].float() @ ws[r].float().t()).to(torch.bfloat16).float() for r in range(world))
+        if add:
+            total = total + res_full.float()
+        new_res = total.to(torch.bfloat16)
+        want = ref.rms_norm(new_res, nw, 1e-5)
+        torch.testing.assert_close(out.float().cpu(), want.float(), rtol=3e-2, atol=3e-2)
+        torch.testing.assert_close(res[:n_mine].float().cpu(), new_res[rank * rpr: rank * rpr + n_mine].float(),
+                                   rtol=2e-2, atol=2e-2)
+        g.barrier()
+    ps.destroy()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_fused_gemm_allreduce_norm_2gpu():
+    _launch(_fused_ar_worker, 2)
+
+
+def _tp_engine_worker(rank, world, fused):
+    os.environ["B200_FUSED_TP_COLLECTIVES"] = "1" if fused else "0"
+    from vllm_metax_b200 import LLM, ModelConfig, SamplingParams
+    from vllm_metax_b200 import _custom_ops as ops
+    from vllm_metax_b200.parallel import state as ps
+
+    cfg = ModelConfig(architecture="LlamaForCausalLM", vocab_size=2048, hidden_size=1024, intermediate_size=2816,
+                      num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+                      max_position_embeddings=1024, dtype=torch.bfloat16, seed=0)
+    llm = LLM(cfg, device="cuda", tensor_parallel_size=world, block_size=64, max_model_len=512, max_num_seqs=8,
+              max_num_batched_tokens=1024, num_gpu_blocks=128)
+    assert llm.engine.runner.fused_tp == fused
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (100, 33, 200)]
+    outs = llm.generate(prompts, SamplingParams(max_tokens=16, ignore_eos=True))
+    assert all(len(o.outputs[0].token_ids) == 16 for o in outs)
+    torch.cuda.synchronize()
+    ops.check_kernel_status(rank)
+    # every rank must have sampled the same tokens (SPMD lock step)
+    toks = torch.tensor([o.outputs[0].token_ids for o in outs], device="cuda")
+    gathered = ps.get_tp_group().all_gather(toks[None], 0)
+    assert bool((gathered == toks[None]).all())
+    ps.destroy()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("fused", [False, True])
+def test_tp2_engine_generates(fused):
+    _launch(_tp_engine_worker, 2, fused)

@@ -7,7 +7,10 @@
 #include <torch/types.h>
 
 #include <cstdlib>
+#include <cstring>
+#include <tuple>
 
+#include "comm_params.h"
 #include "ops.h"
 
 namespace {
@@ -353,10 +356,79 @@ void embedding(Tensor& out, const Tensor& table, const Tensor& ids, int64_t voca
                   vocab_start, dtype16(table), cur_stream());
 }
 
+
+// ------------------------------------------------------------------ symmetric (peer-mapped) memory
+// A plain cudaMalloc allocation whose IPC handle can be opened by the other ranks of the node.
+std::tuple<Tensor, Tensor> symm_alloc(int64_t nbytes, int64_t device) {
+  const c10::cuda::CUDAGuard guard((c10::DeviceIndex)device);
+  void* p = nullptr;
+  TORCH_CHECK(cudaMalloc(&p, (size_t)nbytes) == cudaSuccess, "symm_alloc: cudaMalloc of ", nbytes, " bytes failed");
+  TORCH_CHECK(cudaMemset(p, 0, (size_t)nbytes) == cudaSuccess);
+  cudaIpcMemHandle_t h;
+  TORCH_CHECK(cudaIpcGetMemHandle(&h, p) == cudaSuccess, "cudaIpcGetMemHandle failed");
+  Tensor handle = torch::empty({(int64_t)sizeof(h)}, torch::kUInt8);
+  std::memcpy(handle.data_ptr(), &h, sizeof(h));
+  Tensor buf = torch::from_blob(p, {nbytes}, [](void* q) { cudaFree(q); },
+                                torch::dtype(torch::kUInt8).device(torch::kCUDA, (c10::DeviceIndex)device));
+  return {buf, handle};
+}
+int64_t symm_open(const Tensor& handle, int64_t device) {
+  const c10::cuda::CUDAGuard guard((c10::DeviceIndex)device);
+  cudaIpcMemHandle_t h;
+  TORCH_CHECK(handle.numel() == (int64_t)sizeof(h));
+  std::memcpy(&h, handle.data_ptr(), sizeof(h));
+  void* p = nullptr;
+  const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  TORCH_CHECK(e == cudaSuccess, "cudaIpcOpenMemHandle failed: ", cudaGetErrorString(e));
+  return reinterpret_cast<int64_t>(p);
+}
+void symm_close(int64_t ptr) { cudaIpcCloseMemHandle(reinterpret_cast<void*>(ptr)); }
+
+// x [T, K_local], w [H, K_local]; ptrs: CPU int64 [4, tp] = recv / counters / flags / out base per rank.
+void gemm_ar_norm(const Tensor& x, const Tensor& w, Tensor& residual, const Tensor& norm_weight, double eps,
+                  const Tensor& ptrs, int64_t tp, int64_t rank, int64_t rows_per_rank, int64_t rows_cap,
+                  int64_t rb_cap, Tensor& local_sync, bool add_residual, int64_t wait_cycles) {
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 && x.size(1) == w.size(1));
+  TORCH_CHECK(tp >= 1 && tp <= b200::kMaxRanks && ptrs.dim() == 2 && ptrs.size(0) == 4 && ptrs.size(1) >= tp);
+  TORCH_CHECK(!ptrs.is_cuda() && ptrs.scalar_type() == at::kLong && residual.is_contiguous());
+  TORCH_CHECK(x.size(1) % 8 == 0 && x.stride(0) % 8 == 0 && w.stride(0) % 8 == 0);
+  b200::FusedArParams p{};
+  p.T = x.size(0); p.H = w.size(0); p.K = x.size(1);
+  p.tp = tp; p.rank = rank; p.rows_per_rank = rows_per_rank;
+  p.rows_cap = rows_cap; p.rb_cap = rb_cap;
+  TORCH_CHECK(rows_per_rank <= rows_cap && (p.T + 127) / 128 <= rb_cap, "fused all-reduce workspace too small");
+  const int64_t* pp = ptrs.data_ptr<int64_t>();
+  const int64_t st = ptrs.stride(0);
+  for (int r = 0; r < tp; ++r) {
+    p.recv[r] = reinterpret_cast<void*>(pp[0 * st + r]);
+    p.counters[r] = reinterpret_cast<uint32_t*>(pp[1 * st + r]);
+    p.flags[r] = reinterpret_cast<uint32_t*>(pp[2 * st + r]);
+    p.out[r] = reinterpret_cast<void*>(pp[3 * st + r]);
+  }
+  p.residual = residual.data_ptr();
+  p.norm_weight = norm_weight.data_ptr();
+  p.eps = (float)eps;
+  p.add_residual = add_residual;
+  p.local_sync = reinterpret_cast<uint32_t*>(local_sync.data_ptr());
+  p.wait_cycles = wait_cycles;
+  p.status = reinterpret_cast<b200::StatusWord*>(status_ptr(x));
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int rc = b200::gemm_ar_norm(p, x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), dtype16(x), cur_stream());
+  TORCH_CHECK(rc == 0, "gemm_ar_norm: hidden size ", p.H, " not supported");
+}
+
 }  // namespace
 
 TORCH_LIBRARY(b200, m) {
   m.def("get_status(int device) -> Tensor", &get_status);
+  m.def("symm_alloc(int nbytes, int device) -> (Tensor, Tensor)", &symm_alloc);
+  m.def("symm_open(Tensor handle, int device) -> int", &symm_open);
+  m.def("symm_close(int ptr) -> ()", &symm_close);
+  m.def(
+      "gemm_ar_norm(Tensor x, Tensor w, Tensor(a!) residual, Tensor norm_weight, float eps, Tensor ptrs, int tp, "
+      "int rank, int rows_per_rank, int rows_cap, int rb_cap, Tensor(b!) local_sync, bool add_residual, "
+      "int wait_cycles) -> ()",
+      &gemm_ar_norm);
   m.def("gemm(Tensor(a!) out, Tensor a, Tensor w, Tensor? bias, Tensor? residual, int force_bn, int epi) -> ()", &gemm);
   m.def("rms_norm(Tensor(a!) out, Tensor x, Tensor weight, float eps, bool gemma) -> ()", &rms_norm);
   m.def("fused_add_rms_norm(Tensor(a!) x, Tensor(b!) residual, Tensor weight, float eps, bool gemma) -> ()",

@@ -1,0 +1,34 @@
+// Parameter blocks of the fused compute + collective kernels (host- and device-visible).
+#pragma once
+#include <stdint.h>
+
+#include "status.h"
+
+namespace b200 {
+
+constexpr int kMaxRanks = 8;
+
+struct FusedArParams {
+  // problem: partial[T, H] = A[T, K] . W[H, K]^T on every rank; rows are owned in contiguous
+  // chunks of rows_per_rank.
+  int T, H, K;
+  int tp, rank, rows_per_rank;
+  // symmetric buffers, one pointer per rank (index = rank that OWNS the memory)
+  void* recv[kMaxRanks];          // [tp (source)][rows_per_rank_cap][H] 16-bit partial rows
+  uint32_t* counters[kMaxRanks];  // [2 (parity)][num_row_blocks_cap] arrivals per 128-row block
+  uint32_t* flags[kMaxRanks];     // [tp] epoch written by each source when its pushes are complete
+  void* out[kMaxRanks];           // [T_cap, H] normalised hidden states (all-gathered result)
+  int rows_cap;                   // rows_per_rank_cap (stride of recv's source dimension)
+  int rb_cap;                     // num_row_blocks_cap
+  // local tensors
+  void* residual;                 // [rows_per_rank, H] this rank's shard of the residual stream (in/out)
+  const void* norm_weight;        // [H]
+  float eps;
+  int add_residual;               // 0: residual_out = reduced sum (first use), 1: residual += sum
+  uint32_t* local_sync;           // [4] local scratch: [0] CTAs done, [1] last finished epoch (the call's
+                                  // epoch is that + 1; its low bit selects the counter set)
+  long long wait_cycles;          // budget of every flag wait
+  StatusWord* status;
+};
+
+}  // namespace b200

@@ -98,4 +98,9 @@ void advance_step(int64_t* input_ids, int64_t* positions, int* seq_lens, int64_t
 void embedding(void* out, const void* table, const int64_t* ids, int tokens, int hidden, int64_t vocab,
                int64_t vocab_start, int dtype, cudaStream_t stream);
 
+// ---- comm_gemm_ar_norm.cu (FusedArParams: comm_params.h)
+struct FusedArParams;
+int gemm_ar_norm(const FusedArParams& p, const void* A, int lda, const void* W, int ldw, int dtype,
+                 cudaStream_t stream);
+
 }  // namespace b200

@@ -63,10 +63,24 @@ class ModelRunner:
         self.kv_caches: list = []
         self.num_blocks = 0
         self._alloc_inputs()
+        self._enable_fused_tp()
         self.graphs: dict[int, tuple] = {}
         self.use_graphs = self.is_cuda and not cfg.enforce_eager and envs.B200_CUDA_GRAPHS
         self.launch_count = 0
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count if self.is_cuda else 1
+
+    def _enable_fused_tp(self) -> None:
+        """Swap the row-parallel linears + all-reduce + add-norm of a TP model for the fused NVLink kernel."""
+        inner = getattr(self.model, "model", None)
+        self.fused_tp = False
+        if (ps.tp_size() == 1 or ps.get_pp_group().world_size > 1 or not envs.B200_FUSED_TP_COLLECTIVES
+                or inner is None or not hasattr(inner, "forward_fused_tp") or self.cfg.model.quantization):
+            return
+        from ..parallel.fused_collectives import get_fused_row_parallel
+
+        inner.fused_ar = get_fused_row_parallel(ps.get_tp_group(), self.device, self.max_tokens,
+                                                self.cfg.model.hidden_size, self.cfg.model.dtype)
+        self.fused_tp = True
 
     # ------------------------------------------------------------------ buffers
     def _alloc_inputs(self) -> None:

@@ -45,10 +45,12 @@ class LlamaMLP(nn.Module):
                                            qm("down_proj"), reduce_results=reduce_results, prefix=f"{prefix}.down_proj")
         self.act = SiluAndMul()
 
+    def activation(self, x):
+        """Everything up to (not including) down_proj."""
+        return self.gate_up_proj(x) if self.fused_act else self.act(self.gate_up_proj(x))
+
     def forward(self, x):
-        if self.fused_act:
-            return self.down_proj(self.gate_up_proj(x))
-        return self.down_proj(self.act(self.gate_up_proj(x)))
+        return self.down_proj(self.activation(x))
 
 
 class LlamaAttention(nn.Module):
@@ -73,7 +75,8 @@ class LlamaAttention(nn.Module):
         self.attn = Attention(self.num_heads, self.head_dim, self.head_dim ** -0.5, self.num_kv_heads, layer_idx,
                               sliding_window=cfg.sliding_window)
 
-    def forward(self, positions, h):
+    def attention(self, positions, h):
+        """Everything up to (not including) o_proj: ``[T, local_heads * head_dim]``."""
         qkv = self.qkv_proj(h)
         q = qkv[:, : self.q_size]
         k = qkv[:, self.q_size: self.q_size + self.kv_size]
@@ -81,8 +84,10 @@ class LlamaAttention(nn.Module):
         if self.qk_norm:
             ops.head_rms_norm(q, self.q_norm.weight, self.q_norm.eps, self.num_heads, self.head_dim)
             ops.head_rms_norm(k, self.k_norm.weight, self.k_norm.eps, self.num_kv_heads, self.head_dim)
-        a = self.attn(q, k, v, positions, self.rope)
-        return self.o_proj(a)
+        return self.attn(q, k, v, positions, self.rope)
+
+    def forward(self, positions, h):
+        return self.o_proj(self.attention(positions, h))
 
 
 class LlamaDecoderLayer(nn.Module):
@@ -121,7 +126,33 @@ class LlamaModel(nn.Module):
                                      for i in range(self.start_layer, self.end_layer)})
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype) if pp.is_last_rank else None
 
+    def forward_fused_tp(self, input_ids, positions):
+        """Tensor-parallel forward with every row-parallel linear fused with its all-reduce, the residual
+        add and the following RMSNorm (``parallel/fused_collectives.py``).  The residual stream is
+        sharded by token rows; hidden states between kernels are the all-gathered normalised rows."""
+        fused = self.fused_ar
+        tp, rank = ps.tp_size(), ps.tp_rank()
+        h = self.embed_tokens(input_ids)
+        T = h.shape[0]
+        rpr = (T + tp - 1) // tp
+        res = torch.zeros(rpr, h.shape[1], dtype=h.dtype, device=h.device)
+        n_mine = max(0, min(rpr, T - rank * rpr))
+        if n_mine:
+            res[:n_mine] = h[rank * rpr: rank * rpr + n_mine]
+        layers = [self.layers[str(i)] for i in range(self.start_layer, self.end_layer)]
+        x = layers[0].input_layernorm(h)
+        for i, lyr in enumerate(layers):
+            a = lyr.self_attn.attention(positions, x)
+            x = fused(a, lyr.self_attn.o_proj.weight, res, lyr.post_attention_layernorm.weight,
+                      lyr.post_attention_layernorm.eps)
+            m = lyr.mlp.activation(x)
+            nxt = layers[i + 1].input_layernorm if i + 1 < len(layers) else self.norm
+            x = fused(m, lyr.mlp.down_proj.weight, res, nxt.weight, nxt.eps)
+        return x
+
     def forward(self, input_ids, positions, intermediate: Optional[dict] = None):
+        if getattr(self, "fused_ar", None) is not None:
+            return self.forward_fused_tp(input_ids, positions)
         if self.embed_tokens is not None:
             h, residual = self.embed_tokens(input_ids), None
         else:

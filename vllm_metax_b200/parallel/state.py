@@ -43,9 +43,10 @@ class Group:
             return x
         if dim < 0:
             dim += x.dim()
-        out = torch.empty((self.world_size,) + tuple(x.shape), dtype=x.dtype, device=x.device)
-        dist.all_gather_into_tensor(out, x.contiguous(), group=self._pg(x))
-        out = out.movedim(0, dim)
+        xc = x.contiguous() if x.dim() else x.reshape(1)
+        flat = torch.empty((self.world_size * xc.shape[0],) + tuple(xc.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(flat, xc, group=self._pg(x))
+        out = flat.view((self.world_size,) + tuple(x.shape)).movedim(0, dim)
         shp = list(x.shape)
         shp[dim] *= self.world_size
         return out.reshape(shp)
@@ -57,15 +58,20 @@ class Group:
         mx = max(sizes)
         pad = torch.zeros((mx,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
         pad[: x.shape[0]] = x
-        out = torch.empty((self.world_size, mx) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
-        dist.all_gather_into_tensor(out, pad, group=self._pg(x))
+        flat = torch.empty((self.world_size * mx,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(flat, pad, group=self._pg(x))
+        out = flat.view((self.world_size, mx) + tuple(x.shape[1:]))
         return torch.cat([out[r, : sizes[r]] for r in range(self.world_size)], dim=0)
 
     def reduce_scatter(self, x: torch.Tensor, dim: int = 0) -> torch.Tensor:
         if self.world_size == 1:
             return x
         xm = x.movedim(dim, 0).contiguous()
-        out = torch.empty((xm.shape[0] // self.world_size,) + tuple(xm.shape[1:]), dtype=x.dtype, device=x.device)
+        n = xm.shape[0] // self.world_size
+        if not x.is_cuda:  # Gloo has no reduce-scatter
+            dist.all_reduce(xm, group=self.cpu_pg)
+            return xm[self.rank_in_group * n:(self.rank_in_group + 1) * n].movedim(0, dim)
+        out = torch.empty((n,) + tuple(xm.shape[1:]), dtype=x.dtype, device=x.device)
         dist.reduce_scatter_tensor(out, xm, group=self._pg(x))
         return out.movedim(0, dim)
 
