@@ -201,7 +201,17 @@ def main() -> None:
             "gpu_launches": launches,
         }))
     if world > 1:
+        # release captured graphs before the communicators they reference, and never let a slow
+        # NCCL teardown keep a finished benchmark alive
+        import threading
+
+        sys.stdout.flush()
+        threading.Timer(30.0, lambda: os._exit(0)).start()
+        wl.graph = None
+        runner.graphs.clear()
+        torch.cuda.synchronize()
         ps.destroy()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -16,10 +16,15 @@ def _ngpu():
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
-def _launch(fn, world, *args, timeout=300):
+_PORT_SEQ = 0
+
+
+def _launch(fn, world, *args, timeout=150):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29800 + (os.getpid() % 150)
+    global _PORT_SEQ
+    _PORT_SEQ += 1
+    port = 29800 + (os.getpid() % 100) * 8 + _PORT_SEQ      # a fresh rendezvous port per launch
     procs = [ctx.Process(target=_entry, args=(fn, r, world, port, q) + args) for r in range(world)]
     for p in procs:
         p.start()
@@ -33,16 +38,35 @@ def _launch(fn, world, *args, timeout=300):
 def _entry(fn, rank, world, port, q, *args):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port))
+    import faulthandler
+
+    os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
+    fh = open(os.path.join(ROOT, "gpurun_out", f"stack_{fn.__name__}_r{rank}.txt"), "w")
+    faulthandler.dump_traceback_later(100, file=fh)      # where is a stuck rank? (diagnosis only)
     try:
         fn(rank, world, *args)
         if rank == 0:
             q.put("ok")
+        faulthandler.cancel_dump_traceback_later()
+        _shutdown()
     except BaseException as e:
         import traceback
 
         if rank == 0:
             q.put("rank0 failed: " + "".join(traceback.format_exception(e))[-3000:])
         raise
+
+
+def _shutdown():
+    """Tear the process groups down; never let a slow NCCL teardown outlive the test."""
+    import threading
+
+    from vllm_metax_b200.parallel import state as ps
+
+    threading.Timer(20.0, lambda: os._exit(0)).start()
+    torch.cuda.synchronize()
+    ps.destroy()
+    os._exit(0)
 
 
 def _fused_ar_worker(rank, world):
@@ -80,7 +104,6 @@ def _fused_ar_worker(rank, world):
         torch.testing.assert_close(res[:n_mine].float().cpu(), new_res[rank * rpr: rank * rpr + n_mine].float(),
                                    rtol=2e-2, atol=2e-2)
         g.barrier()
-    ps.destroy()
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
@@ -110,7 +133,7 @@ def _tp_engine_worker(rank, world, fused):
     toks = torch.tensor([o.outputs[0].token_ids for o in outs], device="cuda")
     gathered = ps.get_tp_group().all_gather(toks[None], 0)
     assert bool((gathered == toks[None]).all())
-    ps.destroy()
+    llm.engine.runner.graphs.clear()
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
