@@ -534,3 +534,144 @@ def embedding(table, ids, out=None, vocab_start: int = 0):
         out.copy_(y)
         return out
     return y
+
+
+# --------------------------------------------------------------------------- MoE routing / shuffling
+_GATING_MODE = {"softmax": 0, "sigmoid": 1, "sqrtsoftplus": 2}
+
+
+def topk_gating(gating, topk: int, renormalize: bool, scoring: str = "softmax", bias=None, scale: float = 1.0):
+    """Fused score + top-k (+ renorm, scale).  Returns ``(weights f32 [T,k], ids int32 [T,k])``.
+    Parity: torch.ops._moe_C.topk_softmax / topk_sigmoid / topk_softplus_sqrt."""
+    if _use_cuda(gating):
+        T = gating.shape[0]
+        w = torch.empty(T, topk, dtype=torch.float32, device=gating.device)
+        ids = torch.empty(T, topk, dtype=torch.int32, device=gating.device)
+        torch.ops.b200.topk_gating(w, ids, gating.contiguous(), bias, _GATING_MODE[scoring], renormalize, scale)
+        return w, ids
+    if scoring == "softmax":
+        w, ids = ref.topk_softmax(gating, topk, renormalize, bias)
+    elif scoring == "sigmoid":
+        w, ids = ref.topk_sigmoid(gating, topk, renormalize, bias)
+    else:
+        return ref.topk_softplus_sqrt(gating, topk, renormalize, bias, scale)
+    return w * scale, ids
+
+
+def grouped_topk(gating, topk: int, renormalize: bool, num_expert_group: int, topk_group: int,
+                 scoring_func: str = "sigmoid", bias=None, routed_scaling_factor: float = 1.0):
+    """Parity: vllm_metax/_custom_ops.py:206-238 (grouped_topk)."""
+    if _use_cuda(gating):
+        T = gating.shape[0]
+        w = torch.empty(T, topk, dtype=torch.float32, device=gating.device)
+        ids = torch.empty(T, topk, dtype=torch.int32, device=gating.device)
+        torch.ops.b200.grouped_topk(w, ids, gating.contiguous(), None if bias is None else bias.float(),
+                                    num_expert_group, topk_group, scoring_func == "sigmoid", renormalize,
+                                    routed_scaling_factor)
+        return w, ids
+    return ref.grouped_topk(gating, topk, renormalize, num_expert_group, topk_group, scoring_func, bias,
+                            routed_scaling_factor)
+
+
+def moe_align_block_size(topk_ids, block_size: int, num_experts: int, expert_map=None, want_inverse: bool = False):
+    """Expert-sort (token, k) pairs with per-expert padding to ``block_size``.
+
+    Returns ``(sorted_token_ids, block_expert_ids, num_tokens_post_padded[, inverse positions])``; padding
+    entries of ``sorted_token_ids`` hold ``numel``.  With ``expert_map`` (global -> local id or -1) pairs
+    routed to other ranks are dropped (their inverse position is -1)."""
+    numel = topk_ids.numel()
+    max_pad = numel + num_experts * (block_size - 1)
+    max_pad = (max_pad + block_size - 1) // block_size * block_size
+    if _use_cuda(topk_ids):
+        dev = topk_ids.device
+        sorted_ids = torch.empty(max_pad, dtype=torch.int32, device=dev)
+        block_expert = torch.empty(max_pad // block_size, dtype=torch.int32, device=dev)
+        total = torch.empty(1, dtype=torch.int32, device=dev)
+        inv = torch.empty(numel, dtype=torch.int32, device=dev) if want_inverse else None
+        torch.ops.b200.moe_align(sorted_ids, block_expert, total, inv, topk_ids.contiguous(), expert_map, num_experts,
+                                 block_size)
+        return (sorted_ids, block_expert, total, inv) if want_inverse else (sorted_ids, block_expert, total)
+    ids = topk_ids.reshape(-1).long()
+    if expert_map is not None:
+        ids = expert_map.long()[ids]
+    keep = ids >= 0
+    flat = torch.where(keep, ids, torch.full_like(ids, num_experts))
+    counts = torch.bincount(flat, minlength=num_experts + 1)[:num_experts]
+    padded = (counts + block_size - 1) // block_size * block_size
+    starts = torch.cumsum(padded, 0) - padded
+    sorted_ids = torch.full((max_pad,), numel, dtype=torch.int32)
+    block_expert = torch.full((max_pad // block_size,), -1, dtype=torch.int32)
+    inv = torch.full((numel,), -1, dtype=torch.int32)
+    order = torch.argsort(flat, stable=True)
+    order = order[flat[order] < num_experts]
+    se = flat[order]
+    cstarts = torch.cumsum(counts, 0) - counts
+    pos = starts[se] + (torch.arange(order.numel()) - cstarts[se])
+    sorted_ids[pos] = order.to(torch.int32)
+    inv[order] = pos.to(torch.int32)
+    be = torch.repeat_interleave(torch.arange(num_experts), padded // block_size)
+    block_expert[: be.numel()] = be.to(torch.int32)
+    total = padded.sum().to(torch.int32).reshape(1)
+    return (sorted_ids, block_expert, total, inv) if want_inverse else (sorted_ids, block_expert, total)
+
+
+def moe_gather(x, sorted_ids, total_padded, topk: int):
+    """Rows of ``x [T,H]`` in expert-sorted order, zero rows for padding: ``[max_padded, H]``."""
+    if _use_cuda(x):
+        out = torch.empty(sorted_ids.numel(), x.shape[1], dtype=x.dtype, device=x.device)
+        torch.ops.b200.moe_gather(out, x.contiguous(), sorted_ids, total_padded, topk)
+        return out
+    numel = x.shape[0] * topk
+    sid = sorted_ids.long()
+    valid = sid < numel
+    out = torch.zeros(sid.numel(), x.shape[1], dtype=x.dtype)
+    out[valid] = x[sid[valid] // topk]
+    return out
+
+
+def gemm_grouped(a, w, block_expert, total_padded, epi: int = 0):
+    """Per-row-block expert GEMM: ``a [R, K]`` (R multiple of 128), ``w [E, N, K]`` -> ``[R, N]`` (``N/2`` with the
+    SiLU-gate epilogue over row-interleaved gate/up weights)."""
+    if _use_cuda(a):
+        n_out = w.shape[1] // 2 if epi == 1 else w.shape[1]
+        out = torch.empty(a.shape[0], n_out, dtype=a.dtype, device=a.device)
+        torch.ops.b200.gemm_grouped(out, a, w, block_expert, total_padded, epi)
+        return out
+    R = a.shape[0]
+    nblk = R // 128
+    n_out = w.shape[1] // 2 if epi == 1 else w.shape[1]
+    out = torch.zeros(R, n_out, dtype=a.dtype)
+    valid_blocks = int(total_padded.item()) // 128
+    for b in range(min(nblk, valid_blocks)):
+        e = int(block_expert[b])
+        if e < 0:
+            continue
+        y = ref.gemm(a[b * 128:(b + 1) * 128], w[e])
+        if epi == 1:
+            y = (torch.nn.functional.silu(y[:, 0::2].float()) * y[:, 1::2].float()).to(a.dtype)
+        out[b * 128:(b + 1) * 128] = y
+    return out
+
+
+def moe_combine(y, weights, inv_pos, tokens: int, shared=None):
+    """``out[t] = sum_k weights[t,k] * y[inv_pos[t,k]] (+ shared[t])``."""
+    if _use_cuda(y):
+        out = torch.empty(tokens, y.shape[1], dtype=y.dtype, device=y.device)
+        torch.ops.b200.moe_combine(out, y, weights.contiguous(), inv_pos, shared)
+        return out
+    topk = weights.shape[1]
+    ip = inv_pos.reshape(tokens, topk).long()
+    ok = ip >= 0
+    g = y[ip.clamp(min=0)].float() * (weights.float() * ok)[..., None]
+    out = g.sum(dim=1)
+    if shared is not None:
+        out = out + shared.float()
+    return out.to(y.dtype)
+
+
+def moe_sum(x):
+    if _use_cuda(x):
+        out = torch.empty(x.shape[0], x.shape[2], dtype=x.dtype, device=x.device)
+        torch.ops.b200.moe_sum(out, x.contiguous())
+        return out
+    return ref.moe_sum(x)

@@ -357,6 +357,63 @@ void embedding(Tensor& out, const Tensor& table, const Tensor& ids, int64_t voca
 }
 
 
+// ------------------------------------------------------------------ MoE
+void topk_gating(Tensor& weights, Tensor& ids, const Tensor& gating, const optional<Tensor>& bias, int64_t mode,
+                 bool renorm, double scale) {
+  TORCH_CHECK(gating.dim() == 2 && gating.is_contiguous() && gating.size(1) <= 1024 && ids.size(1) <= 32);
+  TORCH_CHECK(weights.scalar_type() == at::kFloat && ids.scalar_type() == at::kInt);
+  const c10::cuda::CUDAGuard guard(gating.device());
+  b200::topk_gating(weights.data_ptr<float>(), ids.data_ptr<int>(), gating.data_ptr(), ptr<float>(bias),
+                    gating.size(0), gating.size(1), ids.size(1), mode, renorm, (float)scale, dtype_code(gating),
+                    cur_stream());
+}
+void grouped_topk(Tensor& weights, Tensor& ids, const Tensor& gating, const optional<Tensor>& bias, int64_t n_group,
+                  int64_t topk_group, bool sigmoid, bool renorm, double scale) {
+  TORCH_CHECK(gating.dim() == 2 && gating.is_contiguous() && gating.size(1) <= 1024 && ids.size(1) <= 32);
+  TORCH_CHECK(n_group <= 32 && gating.size(1) % n_group == 0);
+  const c10::cuda::CUDAGuard guard(gating.device());
+  b200::grouped_topk(weights.data_ptr<float>(), ids.data_ptr<int>(), gating.data_ptr(), ptr<float>(bias),
+                     gating.size(0), gating.size(1), ids.size(1), n_group, topk_group, sigmoid, renorm, (float)scale,
+                     dtype_code(gating), cur_stream());
+}
+void moe_align(Tensor& sorted_ids, Tensor& block_expert, Tensor& total_padded, const optional<Tensor>& inv_pos,
+               const Tensor& topk_ids, const optional<Tensor>& expert_map, int64_t experts, int64_t block) {
+  TORCH_CHECK(topk_ids.scalar_type() == at::kInt && topk_ids.is_contiguous());
+  TORCH_CHECK(sorted_ids.numel() % block == 0 && block_expert.numel() >= sorted_ids.numel() / block);
+  const c10::cuda::CUDAGuard guard(topk_ids.device());
+  b200::moe_align(sorted_ids.data_ptr<int>(), block_expert.data_ptr<int>(), total_padded.data_ptr<int>(),
+                  ptr<int>(inv_pos), topk_ids.data_ptr<int>(), ptr<int>(expert_map), topk_ids.numel(), experts, block,
+                  sorted_ids.numel(), cur_stream());
+}
+void moe_gather(Tensor& out, const Tensor& x, const Tensor& sorted_ids, const Tensor& total_padded, int64_t topk) {
+  TORCH_CHECK(x.is_contiguous() && out.is_contiguous() && x.size(1) % 8 == 0);
+  const c10::cuda::CUDAGuard guard(x.device());
+  b200::moe_gather(out.data_ptr(), x.data_ptr(), sorted_ids.data_ptr<int>(), total_padded.data_ptr<int>(),
+                   out.size(0), x.size(0) * topk, topk, x.size(1), dtype16(x), cur_stream());
+}
+void moe_combine(Tensor& out, const Tensor& y, const Tensor& weights, const Tensor& inv_pos,
+                 const optional<Tensor>& shared) {
+  TORCH_CHECK(y.is_contiguous() && out.is_contiguous() && weights.scalar_type() == at::kFloat);
+  const c10::cuda::CUDAGuard guard(y.device());
+  b200::moe_combine(out.data_ptr(), y.data_ptr(), weights.data_ptr<float>(), inv_pos.data_ptr<int>(), ptr(shared),
+                    out.size(0), weights.size(1), out.size(1), dtype16(y), cur_stream());
+}
+void moe_sum(Tensor& out, const Tensor& in) {
+  TORCH_CHECK(in.dim() == 3 && in.is_contiguous() && out.is_contiguous());
+  const c10::cuda::CUDAGuard guard(in.device());
+  b200::moe_sum(out.data_ptr(), in.data_ptr(), in.size(0), in.size(1), in.size(2), dtype16(in), cur_stream());
+}
+void gemm_grouped(Tensor& out, const Tensor& a, const Tensor& w, const Tensor& block_expert,
+                  const Tensor& total_padded, int64_t epi) {
+  TORCH_CHECK(a.dim() == 2 && w.dim() == 3 && a.stride(1) == 1 && w.is_contiguous() && out.stride(1) == 1);
+  TORCH_CHECK(a.size(0) % 128 == 0 && a.size(1) == w.size(2) && a.size(1) % 8 == 0 && a.stride(0) % 8 == 0);
+  TORCH_CHECK(out.size(0) == a.size(0) && out.size(1) == (epi == 1 ? w.size(1) / 2 : w.size(1)));
+  const c10::cuda::CUDAGuard guard(a.device());
+  b200::gemm_grouped(a.data_ptr(), a.size(0), a.stride(0), w.data_ptr(), w.size(0), w.size(1), w.size(2),
+                     out.data_ptr(), out.stride(0), block_expert.data_ptr<int>(), total_padded.data_ptr<int>(), epi,
+                     dtype16(a), cur_stream(), status_ptr(a));
+}
+
 // ------------------------------------------------------------------ symmetric (peer-mapped) memory
 // A plain cudaMalloc allocation whose IPC handle can be opened by the other ranks of the node.
 std::tuple<Tensor, Tensor> symm_alloc(int64_t nbytes, int64_t device) {
@@ -421,6 +478,13 @@ void gemm_ar_norm(const Tensor& x, const Tensor& w, Tensor& residual, const Tens
 
 TORCH_LIBRARY(b200, m) {
   m.def("get_status(int device) -> Tensor", &get_status);
+  m.def("topk_gating(Tensor(a!) weights, Tensor(b!) ids, Tensor gating, Tensor? bias, int mode, bool renorm, float scale) -> ()", &topk_gating);
+  m.def("grouped_topk(Tensor(a!) weights, Tensor(b!) ids, Tensor gating, Tensor? bias, int n_group, int topk_group, bool sigmoid, bool renorm, float scale) -> ()", &grouped_topk);
+  m.def("moe_align(Tensor(a!) sorted_ids, Tensor(b!) block_expert, Tensor(c!) total_padded, Tensor(d!)? inv_pos, Tensor topk_ids, Tensor? expert_map, int experts, int block) -> ()", &moe_align);
+  m.def("moe_gather(Tensor(a!) out, Tensor x, Tensor sorted_ids, Tensor total_padded, int topk) -> ()", &moe_gather);
+  m.def("moe_combine(Tensor(a!) out, Tensor y, Tensor weights, Tensor inv_pos, Tensor? shared) -> ()", &moe_combine);
+  m.def("moe_sum(Tensor(a!) out, Tensor inp) -> ()", &moe_sum);
+  m.def("gemm_grouped(Tensor(a!) out, Tensor a, Tensor w, Tensor block_expert, Tensor total_padded, int epi) -> ()", &gemm_grouped);
   m.def("symm_alloc(int nbytes, int device) -> (Tensor, Tensor)", &symm_alloc);
   m.def("symm_open(Tensor handle, int device) -> int", &symm_open);
   m.def("symm_close(int ptr) -> ()", &symm_close);

@@ -98,6 +98,21 @@ void advance_step(int64_t* input_ids, int64_t* positions, int* seq_lens, int64_t
 void embedding(void* out, const void* table, const int64_t* ids, int tokens, int hidden, int64_t vocab,
                int64_t vocab_start, int dtype, cudaStream_t stream);
 
+// ---- moe.cu / gemm_grouped_tcgen05.cu
+void topk_gating(float* weights, int* ids, const void* gating, const float* bias, int tokens, int experts, int topk,
+                 int mode, int renorm, float scale, int dtype, cudaStream_t stream);
+void grouped_topk(float* weights, int* ids, const void* gating, const float* bias, int tokens, int experts, int topk,
+                  int n_group, int topk_group, int sigmoid, int renorm, float scale, int dtype, cudaStream_t stream);
+void moe_align(int* sorted_ids, int* block_expert, int* total_padded, int* inv_pos, const int* topk_ids,
+               const int* expert_map, int numel, int experts, int block, int max_padded, cudaStream_t stream);
+void moe_gather(void* out, const void* x, const int* sorted_ids, const int* total_padded, int max_padded, int numel,
+                int topk, int hidden, int dtype, cudaStream_t stream);
+void moe_combine(void* out, const void* y, const float* weights, const int* inv_pos, const void* shared, int tokens,
+                 int topk, int hidden, int dtype, cudaStream_t stream);
+void moe_sum(void* out, const void* in, int tokens, int topk, int hidden, int dtype, cudaStream_t stream);
+void gemm_grouped(const void* A, int max_rows, int lda, const void* W, int E, int N, int K, void* C, int ldc,
+                  const int* block_expert, const int* total_padded, int epi, int dtype, cudaStream_t stream,
+                  void* status);
 // ---- comm_gemm_ar_norm.cu (FusedArParams: comm_params.h)
 struct FusedArParams;
 int gemm_ar_norm(const FusedArParams& p, const void* A, int lda, const void* W, int ldw, int dtype,

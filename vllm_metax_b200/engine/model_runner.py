@@ -74,7 +74,8 @@ class ModelRunner:
         inner = getattr(self.model, "model", None)
         self.fused_tp = False
         if (ps.tp_size() == 1 or ps.get_pp_group().world_size > 1 or not envs.B200_FUSED_TP_COLLECTIVES
-                or inner is None or not hasattr(inner, "forward_fused_tp") or self.cfg.model.quantization):
+                or inner is None or not hasattr(inner, "forward_fused_tp")
+                or not getattr(inner, "supports_fused_tp", True) or self.cfg.model.quantization):
             return
         from ..parallel.fused_collectives import get_fused_row_parallel
 
