@@ -675,3 +675,97 @@ def moe_sum(x):
         torch.ops.b200.moe_sum(out, x.contiguous())
         return out
     return ref.moe_sum(x)
+
+
+# --------------------------------------------------------------------------- quantisation
+def per_token_group_quant_fp8(x, group_size: int = 128, ue8m0: bool = False, column_major_scales: bool = False,
+                              eps: float = 1e-10):
+    """1 x group dynamic e4m3 quantisation: ``(q, scales [.., K/g])`` (scales ``[K/g, rows]`` if column-major)."""
+    if _use_cuda(x):
+        xc = x.contiguous()
+        K = xc.shape[-1]
+        rows = xc.numel() // K
+        q = torch.empty(xc.shape, dtype=torch.float8_e4m3fn, device=x.device)
+        shape = (K // group_size, rows) if column_major_scales else (*xc.shape[:-1], K // group_size)
+        s = torch.empty(shape, dtype=torch.float32, device=x.device)
+        torch.ops.b200.per_token_group_quant(q, s, xc, group_size, ue8m0, column_major_scales, eps)
+        return q, s
+    q, s = ref.per_token_group_quant_fp8(x, group_size, eps, ue8m0)
+    return (q, s.reshape(-1, s.shape[-1]).t().contiguous()) if column_major_scales else (q, s)
+
+
+def per_token_group_quant_int8(x, group_size: int = 128, eps: float = 1e-10):
+    if _use_cuda(x):
+        xc = x.contiguous()
+        q = torch.empty(xc.shape, dtype=torch.int8, device=x.device)
+        s = torch.empty(*xc.shape[:-1], xc.shape[-1] // group_size, dtype=torch.float32, device=x.device)
+        torch.ops.b200.per_token_group_quant(q, s, xc, group_size, False, False, eps)
+        return q, s
+    return ref.per_token_group_quant_int8(x, group_size, eps)
+
+
+def scaled_fp8_quant(x, scale=None, use_per_token_if_dynamic: bool = False, scale_ub=None):
+    """Static (``scale`` given), dynamic per-tensor, or dynamic per-token fp8 quantisation."""
+    if _use_cuda(x):
+        xc = x.contiguous()
+        q = torch.empty(xc.shape, dtype=torch.float8_e4m3fn, device=x.device)
+        if scale is not None:
+            torch.ops.b200.scaled_fp8_quant(q, scale, xc, 0, 0.0)
+            return q, scale
+        if use_per_token_if_dynamic:
+            s = torch.empty(*xc.shape[:-1], 1, dtype=torch.float32, device=x.device)
+            torch.ops.b200.scaled_fp8_quant(q, s, xc, 1, scale_ub or 0.0)
+            return q, s
+        s = (xc.abs().max().float() / 448.0).clamp(min=1e-12).reshape(1)
+        torch.ops.b200.scaled_fp8_quant(q, s, xc, 0, 0.0)
+        return q, s
+    if scale is not None:
+        return ref.static_scaled_fp8_quant(x, scale), scale
+    if use_per_token_if_dynamic:
+        return ref.dynamic_per_token_scaled_fp8_quant(x, scale_ub)
+    return ref.dynamic_scaled_fp8_quant(x)
+
+
+def scaled_int8_quant(x, scale=None, azp=None, symmetric: bool = True):
+    """Returns ``(q, scale, azp_or_None)``.  Parity: vllm_metax patch utils._int8_quantize -> scaled_int8_quant."""
+    if _use_cuda(x):
+        xc = x.contiguous()
+        q = torch.empty(xc.shape, dtype=torch.int8, device=x.device)
+        if scale is not None:
+            torch.ops.b200.scaled_int8_quant(q, scale, azp, xc, 0 if symmetric else 1)
+            return q, scale, azp
+        s = torch.empty(*xc.shape[:-1], 1, dtype=torch.float32, device=x.device)
+        z = None if symmetric else torch.empty(*xc.shape[:-1], 1, dtype=torch.int32, device=x.device)
+        torch.ops.b200.scaled_int8_quant(q, s, z, xc, 2 if symmetric else 3)
+        return q, s, z
+    return ref.scaled_int8_quant(x, scale, azp, symmetric)
+
+
+def merge_attn_states(prefix_out, prefix_lse, suffix_out, suffix_lse, want_lse: bool = False):
+    if _use_cuda(prefix_out):
+        out = torch.empty_like(prefix_out)
+        lse = torch.empty_like(prefix_lse) if want_lse else None
+        torch.ops.b200.merge_attn_states(out, lse, prefix_out.contiguous(), prefix_lse.contiguous(),
+                                         suffix_out.contiguous(), suffix_lse.contiguous())
+        return (out, lse) if want_lse else out
+    out, lse = ref.merge_attn_states(prefix_out, prefix_lse, suffix_out, suffix_lse)
+    return (out, lse) if want_lse else out
+
+
+def fp8_block_scaled_mm(aq, a_scale, wq, w_scale, out_dtype=torch.bfloat16, block_expert=None, total_padded=None):
+    """Block-scaled fp8 GEMM (1x128 activation scales, 128x128 weight scales); grouped when ``wq`` is 3-D."""
+    if _use_cuda(aq):
+        n = wq.shape[-2]
+        out = torch.empty(aq.shape[0], n, dtype=out_dtype, device=aq.device)
+        torch.ops.b200.gemm_fp8_blockscale(out, aq, a_scale.contiguous(), wq, w_scale.contiguous(), block_expert,
+                                           total_padded)
+        return out
+    if wq.dim() == 2:
+        return ref.fp8_block_scaled_mm(aq, a_scale, wq, w_scale, out_dtype)
+    out = torch.zeros(aq.shape[0], wq.shape[1], dtype=out_dtype)
+    for b in range(int(total_padded.item()) // 128):
+        e = int(block_expert[b])
+        if e >= 0:
+            sl = slice(b * 128, (b + 1) * 128)
+            out[sl] = ref.fp8_block_scaled_mm(aq[sl], a_scale[sl], wq[e], w_scale[e], out_dtype)
+    return out

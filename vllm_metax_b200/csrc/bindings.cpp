@@ -414,6 +414,55 @@ void gemm_grouped(Tensor& out, const Tensor& a, const Tensor& w, const Tensor& b
                      dtype16(a), cur_stream(), status_ptr(a));
 }
 
+// ------------------------------------------------------------------ quantisation
+void per_token_group_quant(Tensor& q, Tensor& scales, const Tensor& x, int64_t group, bool ue8m0, bool col_major,
+                           double eps) {
+  TORCH_CHECK(x.is_contiguous() && q.is_contiguous() && (group == 64 || group == 128 || group == 256));
+  const int K = x.size(-1);
+  TORCH_CHECK(K % group == 0);
+  const c10::cuda::CUDAGuard guard(x.device());
+  b200::per_token_group_quant(q.data_ptr(), scales.data_ptr<float>(), x.data_ptr(), x.numel() / K, K, group,
+                              q.scalar_type() == at::kChar, ue8m0, col_major, (float)eps, dtype16(x), cur_stream());
+}
+void scaled_fp8_quant(Tensor& q, Tensor& scale, const Tensor& x, int64_t mode, double scale_ub) {
+  TORCH_CHECK(x.is_contiguous() && q.is_contiguous());
+  const int K = x.size(-1);
+  const c10::cuda::CUDAGuard guard(x.device());
+  b200::scaled_fp8_quant(q.data_ptr(), scale.data_ptr<float>(), x.data_ptr(), x.numel() / K, K, mode, (float)scale_ub,
+                         dtype16(x), cur_stream());
+}
+void scaled_int8_quant(Tensor& q, Tensor& scale, const optional<Tensor>& azp, const Tensor& x, int64_t mode) {
+  TORCH_CHECK(x.is_contiguous() && q.is_contiguous());
+  const int K = x.size(-1);
+  const c10::cuda::CUDAGuard guard(x.device());
+  b200::scaled_int8_quant(q.data_ptr(), scale.data_ptr<float>(), ptr<int>(azp), x.data_ptr(), x.numel() / K, K, mode,
+                          dtype16(x), cur_stream());
+}
+void merge_attn_states(Tensor& out, const optional<Tensor>& out_lse, const Tensor& p_out, const Tensor& p_lse,
+                       const Tensor& s_out, const Tensor& s_lse) {
+  TORCH_CHECK(p_out.is_contiguous() && s_out.is_contiguous() && out.is_contiguous() && p_out.size(2) % 8 == 0);
+  TORCH_CHECK(p_lse.is_contiguous() && s_lse.is_contiguous());
+  const c10::cuda::CUDAGuard guard(p_out.device());
+  b200::merge_attn_states(out.data_ptr(), ptr<float>(out_lse), p_out.data_ptr(), p_lse.data_ptr<float>(),
+                          s_out.data_ptr(), s_lse.data_ptr<float>(), p_out.size(0), p_out.size(1), p_out.size(2),
+                          dtype16(p_out), cur_stream());
+}
+void gemm_fp8_blockscale(Tensor& out, const Tensor& a, const Tensor& a_scale, const Tensor& w, const Tensor& w_scale,
+                         const optional<Tensor>& block_expert, const optional<Tensor>& total_padded) {
+  const bool grouped = w.dim() == 3;
+  TORCH_CHECK(a.dim() == 2 && a.stride(1) == 1 && w.is_contiguous() && a_scale.is_contiguous() && w_scale.is_contiguous());
+  TORCH_CHECK(a.element_size() == 1 && w.element_size() == 1 && a.size(1) % 128 == 0 && a.stride(0) % 16 == 0);
+  const int M = a.size(0), K = a.size(1);
+  const int E = grouped ? w.size(0) : 1, N = grouped ? w.size(1) : w.size(0);
+  TORCH_CHECK(w.size(-1) == K && out.size(0) == M && out.size(1) == N && out.stride(1) == 1);
+  TORCH_CHECK(a_scale.size(-1) == K / 128 && w_scale.size(-1) == K / 128 && w_scale.size(-2) == (N + 127) / 128);
+  if (grouped) TORCH_CHECK(block_expert.has_value() && total_padded.has_value() && M % 128 == 0);
+  const c10::cuda::CUDAGuard guard(a.device());
+  b200::gemm_fp8_blockscale(a.data_ptr(), M, a.stride(0), w.data_ptr(), E, N, K, out.data_ptr(), out.stride(0),
+                            a_scale.data_ptr<float>(), w_scale.data_ptr<float>(), ptr<int>(block_expert),
+                            ptr<int>(total_padded), grouped, dtype16(out), cur_stream(), status_ptr(a));
+}
+
 // ------------------------------------------------------------------ symmetric (peer-mapped) memory
 // A plain cudaMalloc allocation whose IPC handle can be opened by the other ranks of the node.
 std::tuple<Tensor, Tensor> symm_alloc(int64_t nbytes, int64_t device) {
@@ -485,6 +534,11 @@ TORCH_LIBRARY(b200, m) {
   m.def("moe_combine(Tensor(a!) out, Tensor y, Tensor weights, Tensor inv_pos, Tensor? shared) -> ()", &moe_combine);
   m.def("moe_sum(Tensor(a!) out, Tensor inp) -> ()", &moe_sum);
   m.def("gemm_grouped(Tensor(a!) out, Tensor a, Tensor w, Tensor block_expert, Tensor total_padded, int epi) -> ()", &gemm_grouped);
+  m.def("per_token_group_quant(Tensor(a!) q, Tensor(b!) scales, Tensor x, int group, bool ue8m0, bool col_major, float eps) -> ()", &per_token_group_quant);
+  m.def("scaled_fp8_quant(Tensor(a!) q, Tensor(b!) scale, Tensor x, int mode, float scale_ub) -> ()", &scaled_fp8_quant);
+  m.def("scaled_int8_quant(Tensor(a!) q, Tensor(b!) scale, Tensor(c!)? azp, Tensor x, int mode) -> ()", &scaled_int8_quant);
+  m.def("merge_attn_states(Tensor(a!) out, Tensor(b!)? out_lse, Tensor p_out, Tensor p_lse, Tensor s_out, Tensor s_lse) -> ()", &merge_attn_states);
+  m.def("gemm_fp8_blockscale(Tensor(a!) out, Tensor a, Tensor a_scale, Tensor w, Tensor w_scale, Tensor? block_expert, Tensor? total_padded) -> ()", &gemm_fp8_blockscale);
   m.def("symm_alloc(int nbytes, int device) -> (Tensor, Tensor)", &symm_alloc);
   m.def("symm_open(Tensor handle, int device) -> int", &symm_open);
   m.def("symm_close(int ptr) -> ()", &symm_close);

@@ -113,6 +113,18 @@ void moe_sum(void* out, const void* in, int tokens, int topk, int hidden, int dt
 void gemm_grouped(const void* A, int max_rows, int lda, const void* W, int E, int N, int K, void* C, int ldc,
                   const int* block_expert, const int* total_padded, int epi, int dtype, cudaStream_t stream,
                   void* status);
+// ---- quant.cu / gemm_fp8_blockscale.cu
+void per_token_group_quant(void* q, float* scales, const void* x, int64_t rows, int K, int group, int int8, int ue8m0,
+                           int col_major, float eps, int dtype, cudaStream_t stream);
+void scaled_fp8_quant(void* q, float* scale, const void* x, int64_t rows, int K, int mode, float scale_ub, int dtype,
+                      cudaStream_t stream);
+void scaled_int8_quant(void* q, float* scale, int* azp, const void* x, int64_t rows, int K, int mode, int dtype,
+                       cudaStream_t stream);
+void merge_attn_states(void* out, float* out_lse, const void* p_out, const float* p_lse, const void* s_out,
+                       const float* s_lse, int tokens, int heads, int D, int dtype, cudaStream_t stream);
+void gemm_fp8_blockscale(const void* A, int M, int lda, const void* W, int E, int N, int K, void* C, int ldc,
+                         const float* a_scale, const float* w_scale, const int* block_expert,
+                         const int* total_padded, int grouped, int out_dtype, cudaStream_t stream, void* status);
 // ---- comm_gemm_ar_norm.cu (FusedArParams: comm_params.h)
 struct FusedArParams;
 int gemm_ar_norm(const FusedArParams& p, const void* A, int lda, const void* W, int ldw, int dtype,
