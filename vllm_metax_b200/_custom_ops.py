@@ -769,3 +769,62 @@ def fp8_block_scaled_mm(aq, a_scale, wq, w_scale, out_dtype=torch.bfloat16, bloc
             sl = slice(b * 128, (b + 1) * 128)
             out[sl] = ref.fp8_block_scaled_mm(aq[sl], a_scale[sl], wq[e], w_scale[e], out_dtype)
     return out
+
+
+# --------------------------------------------------------------------------- MLA
+def mla_decode(q, mla_cache, block_table, seq_lens, scale, *, query_start_loc=None, topk_indices=None, out=None,
+               lse_out=None, num_splits: int = 0, max_seq_len: int = 0):
+    """Absorbed MLA over the latent cache (dense, or sparse with ``topk_indices [T, topk]``).
+    ``q [T, H, 576]`` -> ``[T, H, 512]``."""
+    if _use_cuda(q):
+        T, H, _ = q.shape
+        out = torch.empty(T, H, 512, dtype=q.dtype, device=q.device) if out is None else out
+        if num_splits <= 0:
+            ctas = T * ((H + 15) // 16)
+            kv = topk_indices.shape[1] if topk_indices is not None else (max_seq_len or 4096)
+            num_splits = 1 if ctas >= 148 else max(1, min((296 + ctas - 1) // ctas, kv // 256, 16))
+        ws = _decode_workspace(q.device, num_splits * T * H * 513) if num_splits > 1 else None
+        torch.ops.b200.mla_decode(out, q, mla_cache, block_table, seq_lens, query_start_loc, topk_indices, scale,
+                                  lse_out, ws, num_splits)
+        return out
+    res, lse = ref.mla_decode(q, mla_cache, block_table, seq_lens, scale, query_start_loc=query_start_loc,
+                              topk_indices=topk_indices)
+    if lse_out is not None:
+        lse_out.copy_(lse)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+# --------------------------------------------------------------------------- DSA indexer
+def top_k_per_row(logits, k: int, row_len=None):
+    """Indices of the k largest finite entries per row (-1 padded, unordered).
+    Parity: vllm_metax/_custom_ops.py:170-203 (top_k_per_row / top_k_per_row_decode)."""
+    if _use_cuda(logits):
+        out = torch.empty(logits.shape[0], k, dtype=torch.int32, device=logits.device)
+        torch.ops.b200.topk_per_row(out, logits, row_len, logits.shape[1])
+        return out
+    if row_len is not None:
+        n = torch.arange(logits.shape[1])[None, :]
+        logits = logits.masked_fill(n >= row_len[:, None], float("-inf"))
+    return ref.top_k_per_row(logits, k)
+
+
+def indexer_topk(q_fp8, weights, idx_cache, block_table, seq_lens, query_start_loc, topk: int, block_size: int,
+                 max_seq_len: int = 0, return_logits: bool = False):
+    """fp8 index logits of every new token against its request's cached keys, then top-k.
+    Returns int32 ``[T, topk]`` per-request positions (-1 = none)."""
+    if _use_cuda(q_fp8):
+        T = q_fp8.shape[0]
+        L = max(int(max_seq_len), 1)
+        Lp = (L + 1023) // 1024 * 1024
+        logits = torch.empty(T, Lp, dtype=torch.float32, device=q_fp8.device)
+        qb = q_fp8 if q_fp8.dtype == torch.float8_e4m3fn else q_fp8.to(torch.float8_e4m3fn)
+        torch.ops.b200.indexer_logits(logits, qb.contiguous(), weights.float().contiguous(), idx_cache, block_table,
+                                      seq_lens, query_start_loc, block_size, L)
+        _ = _use_cuda(q_fp8)  # second kernel of the op (launch accounting)
+        out = torch.empty(T, topk, dtype=torch.int32, device=q_fp8.device)
+        torch.ops.b200.topk_per_row(out, logits, None, Lp)
+        return (out, logits) if return_logits else out
+    return ref.sparse_attn_indexer(q_fp8.float(), weights, idx_cache, block_table, seq_lens, query_start_loc, topk)

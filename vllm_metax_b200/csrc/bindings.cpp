@@ -463,6 +463,65 @@ void gemm_fp8_blockscale(Tensor& out, const Tensor& a, const Tensor& a_scale, co
                             ptr<int>(total_padded), grouped, dtype16(out), cur_stream(), status_ptr(a));
 }
 
+// ------------------------------------------------------------------ MLA
+void mla_decode(Tensor& out, const Tensor& q, const Tensor& cache, const Tensor& block_table, const Tensor& seq_lens,
+                const optional<Tensor>& query_start_loc, const optional<Tensor>& topk_indices, double scale,
+                const optional<Tensor>& lse_out, const optional<Tensor>& workspace, int64_t num_splits) {
+  TORCH_CHECK(q.dim() == 3 && q.size(2) == 576 && q.stride(2) == 1 && q.stride(1) == 576);
+  TORCH_CHECK(cache.is_contiguous() && cache.dim() == 3 && out.is_contiguous() && out.size(2) == 512);
+  const bool rec = cache.scalar_type() == at::kByte;
+  TORCH_CHECK(rec ? cache.size(2) == 656 : (cache.size(2) == 576 && cache.scalar_type() == q.scalar_type()));
+  b200::MlaDecodeParams p{};
+  p.out = out.data_ptr();
+  p.lse_out = ptr<float>(lse_out);
+  p.q = q.data_ptr();
+  p.q_stride = q.stride(0);
+  p.cache = cache.data_ptr();
+  p.block_table = block_table.data_ptr<int>();
+  p.seq_lens = seq_lens.data_ptr<int>();
+  p.query_start_loc = ptr<int>(query_start_loc);
+  p.topk_indices = ptr<int>(topk_indices);
+  p.topk = topk_indices.has_value() ? topk_indices->size(1) : 0;
+  p.num_heads = q.size(1);
+  p.block_size = cache.size(1);
+  p.num_blocks = cache.size(0);
+  p.max_blocks = block_table.size(1);
+  p.num_splits = std::max<int64_t>(1, num_splits);
+  p.total_tokens = q.size(0);
+  p.batch = seq_lens.size(0);
+  p.scale = (float)scale;
+  if (p.num_splits > 1) {
+    const int64_t need = p.num_splits * (int64_t)p.total_tokens * p.num_heads * 513;
+    TORCH_CHECK(workspace.has_value() && workspace->numel() >= need, "mla_decode workspace too small");
+    p.part_out = workspace->data_ptr<float>();
+    p.part_lse = p.part_out + p.num_splits * (int64_t)p.total_tokens * p.num_heads * 512;
+  }
+  p.status = reinterpret_cast<b200::StatusWord*>(status_ptr(q));
+  const c10::cuda::CUDAGuard guard(q.device());
+  b200::mla_decode(p, rec, dtype16(q), cur_stream());
+}
+
+// ------------------------------------------------------------------ DSA indexer
+void indexer_logits(Tensor& logits, const Tensor& q, const Tensor& w, const Tensor& cache, const Tensor& block_table,
+                    const Tensor& seq_lens, const Tensor& query_start_loc, int64_t block_size, int64_t max_len) {
+  TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.is_contiguous() && q.element_size() == 1);
+  TORCH_CHECK(q.size(1) % 16 == 0 && q.size(1) <= 64 && w.is_contiguous() && w.scalar_type() == at::kFloat);
+  TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.stride(1) == 1 && logits.size(1) >= max_len);
+  TORCH_CHECK(cache.is_contiguous() && cache.scalar_type() == at::kByte);
+  const c10::cuda::CUDAGuard guard(q.device());
+  b200::indexer_logits(logits.data_ptr<float>(), logits.stride(0), q.data_ptr(), w.data_ptr<float>(), cache.data_ptr(),
+                       block_table.data_ptr<int>(), block_table.size(1), seq_lens.data_ptr<int>(),
+                       query_start_loc.data_ptr<int>(), q.size(0), seq_lens.size(0), q.size(1), block_size,
+                       cache.size(0), max_len, status_ptr(q), cur_stream());
+}
+void topk_per_row(Tensor& out, const Tensor& x, const optional<Tensor>& row_len, int64_t cols) {
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.scalar_type() == at::kFloat && out.is_contiguous());
+  TORCH_CHECK(out.scalar_type() == at::kInt && out.size(0) == x.size(0));
+  const c10::cuda::CUDAGuard guard(x.device());
+  b200::topk_per_row(out.data_ptr<int>(), x.data_ptr<float>(), x.stride(0), ptr<int>(row_len), x.size(0), cols,
+                     out.size(1), cur_stream());
+}
+
 // ------------------------------------------------------------------ symmetric (peer-mapped) memory
 // A plain cudaMalloc allocation whose IPC handle can be opened by the other ranks of the node.
 std::tuple<Tensor, Tensor> symm_alloc(int64_t nbytes, int64_t device) {
@@ -539,6 +598,9 @@ TORCH_LIBRARY(b200, m) {
   m.def("scaled_int8_quant(Tensor(a!) q, Tensor(b!) scale, Tensor(c!)? azp, Tensor x, int mode) -> ()", &scaled_int8_quant);
   m.def("merge_attn_states(Tensor(a!) out, Tensor(b!)? out_lse, Tensor p_out, Tensor p_lse, Tensor s_out, Tensor s_lse) -> ()", &merge_attn_states);
   m.def("gemm_fp8_blockscale(Tensor(a!) out, Tensor a, Tensor a_scale, Tensor w, Tensor w_scale, Tensor? block_expert, Tensor? total_padded) -> ()", &gemm_fp8_blockscale);
+  m.def("mla_decode(Tensor(a!) out, Tensor q, Tensor cache, Tensor block_table, Tensor seq_lens, Tensor? query_start_loc, Tensor? topk_indices, float scale, Tensor(b!)? lse_out, Tensor(c!)? workspace, int num_splits) -> ()", &mla_decode);
+  m.def("indexer_logits(Tensor(a!) logits, Tensor q, Tensor w, Tensor cache, Tensor block_table, Tensor seq_lens, Tensor query_start_loc, int block_size, int max_len) -> ()", &indexer_logits);
+  m.def("topk_per_row(Tensor(a!) out, Tensor x, Tensor? row_len, int cols) -> ()", &topk_per_row);
   m.def("symm_alloc(int nbytes, int device) -> (Tensor, Tensor)", &symm_alloc);
   m.def("symm_open(Tensor handle, int device) -> int", &symm_open);
   m.def("symm_close(int ptr) -> ()", &symm_close);

@@ -46,6 +46,24 @@ struct PrefillParams {
   StatusWord* status;
 };
 
+struct MlaDecodeParams {
+  void* out;                   // [T, H, 512]
+  float* lse_out;              // [H, T] or null
+  float* part_out;             // [splits, T, H, 512]
+  float* part_lse;             // [splits, T, H]
+  const void* q;               // [T, H, 576], token stride q_stride (elements)
+  const void* cache;           // latent cache (bf16 576 rows or 656-byte fp8 records)
+  const int* block_table;      // [B, max_blocks]
+  const int* seq_lens;         // [B]
+  const int* query_start_loc;  // [B+1] or null (one token per sequence)
+  const int* topk_indices;     // [T, topk] per-request positions (-1 = none) or null (dense)
+  int64_t q_stride;
+  int num_heads, block_size, max_blocks, num_splits, total_tokens, batch, topk;
+  int64_t num_blocks;
+  float scale;
+  StatusWord* status;
+};
+
 // ---- gemm_tcgen05.cu
 void gemm_tn(const void* A, const void* W, void* C, const void* bias, const void* residual, int M, int N, int K,
              int lda, int ldw, int ldc, int ldr, int dtype, cudaStream_t stream, void* status, int force_bn, int epi);
@@ -125,6 +143,15 @@ void merge_attn_states(void* out, float* out_lse, const void* p_out, const float
 void gemm_fp8_blockscale(const void* A, int M, int lda, const void* W, int E, int N, int K, void* C, int ldc,
                          const float* a_scale, const float* w_scale, const int* block_expert,
                          const int* total_padded, int grouped, int out_dtype, cudaStream_t stream, void* status);
+// ---- mla_decode.cu
+void mla_decode(const MlaDecodeParams& p, int fp8_records, int dtype, cudaStream_t stream);
+// ---- indexer.cu
+void indexer_logits(float* logits, int64_t logits_stride, const void* q, const float* w, const void* cache,
+                    const int* block_table, int max_blocks, const int* seq_lens, const int* query_start_loc,
+                    int tokens, int batch, int heads, int block_size, int64_t num_blocks, int max_len, void* status,
+                    cudaStream_t stream);
+void topk_per_row(int* out, const float* x, int64_t stride, const int* row_len, int rows, int cols, int k,
+                  cudaStream_t stream);
 // ---- comm_gemm_ar_norm.cu (FusedArParams: comm_params.h)
 struct FusedArParams;
 int gemm_ar_norm(const FusedArParams& p, const void* A, int lda, const void* W, int ldw, int dtype,

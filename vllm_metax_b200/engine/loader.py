@@ -40,6 +40,8 @@ def build_model(cfg: EngineConfig, device: torch.device) -> nn.Module:
             qm = getattr(m, "quant_method", None)
             if qm is not None and hasattr(qm, "process_weights_after_loading"):
                 qm.process_weights_after_loading(m)
+        if hasattr(model, "finalize_weights"):
+            model.finalize_weights()
     elif fmt == "safetensors":
         model.load_weights(iter_safetensors(cfg.model.model_path))
     elif fmt == "sharded_state":

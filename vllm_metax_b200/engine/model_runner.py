@@ -219,6 +219,8 @@ class ModelRunner:
             block_table=self.block_table[:B_eff], slot_mapping=self.slot_mapping[:T], max_query_len=max_q,
             max_seq_len=max_seq, block_size=bs, prefill_query_start_loc=self.prefill_qsl[:B_eff - nd_eff + 1],
             max_prefill_query_len=max_q if B_eff > nd_eff else 0)
+        # MLA: prefill requests without cached context may take the up-projected MHA path
+        md.extra["prefill_no_context"] = all(s.start_pos == 0 for s in so.scheduled[nd:])
         return md, T, sample_rows, sample_reqs
 
     # ------------------------------------------------------------------ execution
