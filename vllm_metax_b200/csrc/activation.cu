@@ -113,7 +113,7 @@ __global__ void act_and_mul_quant_kernel(uint8_t* __restrict__ out_q, float* __r
     }
     m = fmaxf(warp_max(m), 1e-10f);
     float s = m / 448.f;
-    if (ue8m0) s = exp2f(ceilf(log2f(s)));
+    if (ue8m0) s = ue8m0_ceil(s);
     if (lane == 0) scale_out[t * ngroups + g] = s;
     for (int j = 0; j < per; ++j) o[g * group + lane + 32 * j] = float_to_fp8_e4m3(y[j] / s);
   }

@@ -52,6 +52,14 @@ __device__ __forceinline__ uint8_t float_to_fp8_e4m3(float v) {
   return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
 }
 
+// Smallest power of two >= s (s > 0, normal): the value a ue8m0 scale can represent.
+__device__ __forceinline__ float ue8m0_ceil(float s) {
+  uint32_t u = __float_as_uint(s);
+  uint32_t e = u >> 23;
+  if (u & 0x7FFFFFu) ++e;
+  return __uint_as_float(e << 23);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

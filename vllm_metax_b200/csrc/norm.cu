@@ -136,7 +136,7 @@ __global__ void rms_norm_quant_kernel(uint8_t* __restrict__ out_q, float* __rest
       for (int i = lane; i < group; i += 32) m = fmaxf(m, fabsf(row[g * group + i]));
       m = fmaxf(warp_max(m), 1e-10f);
       float s = m / 448.f;
-      if (ue8m0) s = exp2f(ceilf(log2f(s)));
+      if (ue8m0) s = ue8m0_ceil(s);
       if (lane == 0) scale_out[t * ngroups + g] = s;
       for (int i = lane; i < group; i += 32) oq[g * group + i] = float_to_fp8_e4m3(row[g * group + i] / s);
     }

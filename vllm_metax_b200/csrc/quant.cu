@@ -31,7 +31,7 @@ __global__ void per_token_group_quant_kernel(uint8_t* __restrict__ q, float* __r
   }
   m = fmaxf(warp_max(m), eps);
   float s = m / (int8 ? 127.f : 448.f);
-  if (ue8m0) s = exp2f(ceilf(log2f(s)));
+  if (ue8m0) s = ue8m0_ceil(s);
   if (lane == 0) scales[col_major_scales ? (int64_t)g * rows + row : row * ngroups + g] = s;
   uint8_t* dst = q + row * K + (int64_t)g * group;
   const float inv = 1.f / s;

@@ -257,7 +257,7 @@ __global__ void indexer_k_quant_and_cache_kernel(const T* __restrict__ k, uint8_
   }
   m = warp_max(m);
   float sc = fmaxf(m / 448.f, 1e-10f);
-  if (ue8m0) sc = exp2f(ceilf(log2f(sc)));
+  if (ue8m0) sc = ue8m0_ceil(sc);
   const int64_t blk = slot / block_size;
   const int off = (int)(slot % block_size);
   uint8_t* bbase = cache + blk * (int64_t)block_size * (head_dim + 4);
