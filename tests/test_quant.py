@@ -137,3 +137,72 @@ def test_fp8_moe_method_gpu(kernel_status_ok):
     w, ids = ops.topk_gating(logits.cpu(), k, True)
     want = ref.fused_experts(x.cpu().float(), w13, w2, w, ids)
     assert cos_diff(got, want) < 5e-3
+
+
+def test_scaled_mm_reference_matches_dequant_cpu():
+    torch.manual_seed(0)
+    M, N, K = 7, 48, 64
+    x = torch.randn(M, K)
+    w = torch.randn(N, K) * 0.1
+    wq = torch.clamp((w / (w.abs().amax(1, keepdim=True) / 127)).round(), -128, 127).to(torch.int8)
+    ws = (w.abs().amax(1) / 127)
+    # asymmetric per-token activations
+    mx, mn = x.amax(1), x.amin(1)
+    s = (mx - mn) / 255
+    zp = torch.round(-128 - mn / s).int()
+    xq = torch.clamp((x / s[:, None]).round() + zp[:, None], -128, 127).to(torch.int8)
+    adj = wq.int().sum(1).int()
+    out = ops.scaled_mm(xq, wq, s, ws, torch.float32, azp=zp, azp_adj=adj)
+    assert cos_diff(out, x @ w.t()) < 2e-3
+
+
+@gpu
+@pytest.mark.parametrize("M,N,K", [(3, 256, 128), (200, 1536, 1024), (1000, 4096, 4096), (129, 2112, 7168)])
+@pytest.mark.parametrize("kind", ["int8", "int8_azp", "fp8"])
+def test_scaled_mm_gpu(M, N, K, kind, kernel_status_ok):
+    torch.manual_seed(1)
+    dev = "cuda"
+    bias = (torch.randn(N, device=dev) * 0.1).bfloat16()
+    if kind == "fp8":
+        aq = (torch.randn(M, K, device=dev)).to(torch.float8_e4m3fn)
+        wq = (torch.randn(N, K, device=dev)).to(torch.float8_e4m3fn)
+        a_s = torch.rand(M, device=dev) * 0.1 + 0.01
+        w_s = torch.rand(N, device=dev) * 0.1 + 0.01
+        out = ops.scaled_mm(aq, wq, a_s, w_s, torch.bfloat16, bias=bias)
+        want = ref.scaled_mm(aq.cpu(), wq.cpu(), a_s.cpu(), w_s.cpu(), torch.float32, bias=bias.cpu())
+        assert cos_diff(out, want) < 1e-4
+        return
+    aq = torch.randint(-128, 128, (M, K), device=dev, dtype=torch.int8)
+    wq = torch.randint(-128, 128, (N, K), device=dev, dtype=torch.int8)
+    a_s = torch.rand(M, device=dev) * 1e-2 + 1e-3
+    w_s = torch.rand(N, device=dev) * 1e-2 + 1e-3
+    azp = adj = None
+    if kind == "int8_azp":
+        azp = torch.randint(-20, 20, (M,), device=dev, dtype=torch.int32)
+        adj = wq.int().sum(1).int()
+    out = ops.scaled_mm(aq, wq, a_s, w_s, torch.bfloat16, azp=azp, azp_adj=adj, bias=bias)
+    want = ref.scaled_mm(aq.cpu(), wq.cpu(), a_s.cpu(), w_s.cpu(), torch.float32, None if azp is None else azp.cpu(),
+                         None if adj is None else adj.cpu(), bias.cpu())
+    # integer accumulation is exact: only the bf16 rounding of the result differs
+    torch.testing.assert_close(out.float().cpu(), want, rtol=1e-2, atol=1e-2 * float(want.abs().max()))
+    assert cos_diff(out, want) < 1e-5
+
+
+@gpu
+def test_scaled_mm_grouped_gpu(kernel_status_ok):
+    torch.manual_seed(2)
+    dev = "cuda"
+    E, N, K, T, topk = 4, 512, 256, 77, 2
+    ids = torch.stack([torch.randperm(E, device=dev)[:topk] for _ in range(T)]).int()
+    sorted_ids, block_expert, total_padded = ops.moe_align_block_size(ids, 128, E)
+    rows = sorted_ids.numel()
+    aq = torch.randint(-128, 128, (rows, K), device=dev, dtype=torch.int8)
+    wq = torch.randint(-128, 128, (E, N, K), device=dev, dtype=torch.int8)
+    a_s = torch.rand(rows, device=dev) * 1e-2 + 1e-3
+    w_s = torch.rand(E, N, device=dev) * 1e-2 + 1e-3
+    out = ops.scaled_mm(aq, wq, a_s, w_s, torch.bfloat16, block_expert=block_expert, total_padded=total_padded)
+    want = ops.scaled_mm(aq.cpu(), wq.cpu(), a_s.cpu(), w_s.cpu(), torch.float32, block_expert=block_expert.cpu(),
+                         total_padded=total_padded.cpu())
+    n = int(total_padded.item())
+    valid = torch.repeat_interleave(block_expert[: n // 128].cpu() >= 0, 128)
+    assert cos_diff(out[:n].cpu()[valid], want[:n][valid]) < 1e-5

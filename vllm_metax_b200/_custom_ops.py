@@ -771,6 +771,75 @@ def fp8_block_scaled_mm(aq, a_scale, wq, w_scale, out_dtype=torch.bfloat16, bloc
     return out
 
 
+def scaled_mm(aq, wq, a_scale, w_scale, out_dtype=torch.bfloat16, *, azp=None, azp_adj=None, bias=None,
+              block_expert=None, total_padded=None):
+    """W8A8 GEMM ``out = a_scale * w_scale * (aq @ wq.T - azp * azp_adj) + bias``.
+
+    ``aq [M,K]`` and ``wq [N,K]`` (or ``[E,N,K]`` grouped over expert-sorted rows) are int8 or fp8 e4m3;
+    ``a_scale`` has 1 or M entries, ``w_scale`` 1 or N per expert.  ``azp_adj [N]`` int32 = column sums of
+    ``wq`` (times the zero point when that is per tensor, in which case ``azp`` is None); ``azp [M]`` int32 is
+    the per-token zero point.  Parity: cutlass_scaled_mm / cutlass_scaled_mm_azp / cutlass_moe_mm_w8a8,
+    vllm_metax/model_executor/layers/quantization/_python_api_ops.py:812-1105."""
+    if _use_cuda(aq):
+        out = torch.empty(aq.shape[0], wq.shape[-2], dtype=out_dtype, device=aq.device)
+        torch.ops.b200.scaled_mm(out, aq, wq, a_scale.float().reshape(-1).contiguous(),
+                                 w_scale.float().reshape(-1).contiguous(),
+                                 None if azp is None else azp.int().reshape(-1).contiguous(),
+                                 None if azp_adj is None else azp_adj.int().reshape(-1).contiguous(),
+                                 bias, block_expert, total_padded)
+        return out
+    if wq.dim() == 2:
+        return ref.scaled_mm(aq, wq, a_scale, w_scale, out_dtype, azp, azp_adj, bias)
+    out = torch.zeros(aq.shape[0], wq.shape[1], dtype=out_dtype)
+    ws = w_scale.float().reshape(wq.shape[0], -1)
+    for b in range(int(total_padded.item()) // 128):
+        e = int(block_expert[b])
+        if e >= 0:
+            sl = slice(b * 128, (b + 1) * 128)
+            asl = a_scale.reshape(-1)[sl] if a_scale.numel() > 1 else a_scale
+            out[sl] = ref.scaled_mm(aq[sl], wq[e], asl, ws[e], out_dtype)
+    return out
+
+
+def wna16_token_tile(rows_per_expert: int) -> int:
+    """Token tile (= moe_align block size) the weight-only GEMM uses for about this many rows per expert."""
+    m = max(int(rows_per_expert), 1)
+    return 16 if m <= 16 else 32 if m <= 32 else 64 if m <= 64 else 128
+
+
+def wna16_gemm(x, qweight, scales, zeros, bits: int, group: int, *, bias=None, block_expert=None, total_padded=None,
+               token_tile: int = 0, silu_gate: bool = False):
+    """``x [M,K] @ dequant(qweight)^T`` with 4/8-bit group-quantised weights in the canonical layout
+    (``quantization/wna16.py``); grouped over expert-sorted rows when ``qweight`` is 3-D.  ``silu_gate``
+    applies SiLU(gate) * up over interleaved output rows (output width N/2)."""
+    N = qweight.shape[-2]
+    if _use_cuda(x):
+        out = torch.empty(x.shape[0], N // 2 if silu_gate else N, dtype=x.dtype, device=x.device)
+        torch.ops.b200.wna16_gemm(out, x, qweight, scales, zeros, bits, group, bias, block_expert, total_padded,
+                                  token_tile, 1 if silu_gate else 0)
+        return out
+    from .quantization.wna16 import dequantize_canonical
+
+    def one(xs, q, s, z):
+        y = xs.float() @ dequantize_canonical(q, s, z, bits, group).to(x.dtype).float().t()
+        if bias is not None:
+            y = y + bias.float()
+        if silu_gate:
+            y = y.to(x.dtype).float()
+            y = torch.nn.functional.silu(y[:, 0::2]) * y[:, 1::2]
+        return y.to(x.dtype)
+
+    if qweight.dim() == 2:
+        return one(x, qweight, scales, zeros)
+    out = torch.zeros(x.shape[0], N // 2 if silu_gate else N, dtype=x.dtype)
+    for b in range(int(total_padded.item()) // token_tile):
+        e = int(block_expert[b])
+        if e >= 0:
+            sl = slice(b * token_tile, (b + 1) * token_tile)
+            out[sl] = one(x[sl], qweight[e], scales[e], zeros[e])
+    return out
+
+
 # --------------------------------------------------------------------------- MLA
 def mla_decode(q, mla_cache, block_table, seq_lens, scale, *, query_start_loc=None, topk_indices=None, out=None,
                lse_out=None, num_splits: int = 0, max_seq_len: int = 0):

@@ -463,6 +463,60 @@ void gemm_fp8_blockscale(Tensor& out, const Tensor& a, const Tensor& a_scale, co
                             ptr<int>(total_padded), grouped, dtype16(out), cur_stream(), status_ptr(a));
 }
 
+// kind is taken from the operand dtype: int8 -> kind::i8, anything else one byte wide -> e4m3
+void scaled_mm(Tensor& out, const Tensor& a, const Tensor& w, const Tensor& a_scale, const Tensor& w_scale,
+               const optional<Tensor>& azp, const optional<Tensor>& azp_adj, const optional<Tensor>& bias,
+               const optional<Tensor>& block_expert, const optional<Tensor>& total_padded) {
+  const bool grouped = w.dim() == 3;
+  TORCH_CHECK(a.dim() == 2 && a.stride(1) == 1 && w.is_contiguous() && a_scale.is_contiguous() && w_scale.is_contiguous());
+  TORCH_CHECK(a.element_size() == 1 && w.element_size() == 1 && a.size(1) % 16 == 0 && a.stride(0) % 16 == 0);
+  TORCH_CHECK(a_scale.scalar_type() == at::kFloat && w_scale.scalar_type() == at::kFloat);
+  const int M = a.size(0), K = a.size(1);
+  const int E = grouped ? w.size(0) : 1, N = grouped ? w.size(1) : w.size(0);
+  TORCH_CHECK(w.size(-1) == K && out.size(0) == M && out.size(1) == N && out.stride(1) == 1);
+  const int a_per_row = a_scale.numel() > 1;
+  TORCH_CHECK(!a_per_row || a_scale.numel() == M, "a_scale must have 1 or M entries");
+  const int w_per_col = w_scale.numel() > E;
+  TORCH_CHECK(w_per_col ? w_scale.numel() == (int64_t)E * N : w_scale.numel() == E, "w_scale must be per tensor or per channel");
+  if (azp.has_value()) TORCH_CHECK(azp->numel() == M && azp->scalar_type() == at::kInt && azp_adj.has_value());
+  if (azp_adj.has_value()) TORCH_CHECK(azp_adj->numel() == N && azp_adj->scalar_type() == at::kInt && !grouped);
+  if (bias.has_value()) TORCH_CHECK(bias->numel() == N && bias->scalar_type() == out.scalar_type() && !grouped);
+  if (grouped) TORCH_CHECK(block_expert.has_value() && total_padded.has_value() && M % 128 == 0);
+  const c10::cuda::CUDAGuard guard(a.device());
+  b200::gemm_scaled_mm(a.data_ptr(), M, a.stride(0), w.data_ptr(), E, N, K, out.data_ptr(), out.stride(0),
+                       a_scale.data_ptr<float>(), a_per_row, w_scale.data_ptr<float>(), w_per_col, ptr<int>(azp),
+                       ptr<int>(azp_adj), bias.has_value() ? bias->data_ptr() : nullptr, ptr<int>(block_expert),
+                       ptr<int>(total_padded), grouped, a.scalar_type() == at::kChar ? 0 : 1, dtype16(out),
+                       cur_stream(), status_ptr(a));
+}
+
+// Weight-only quantised GEMM; q [(E,) N, K*bits/8] uint8, scales / zeros [(E,) K/group, N] in a's dtype.
+void wna16_gemm(Tensor& out, const Tensor& a, const Tensor& q, const Tensor& scales, const optional<Tensor>& zeros,
+                int64_t bits, int64_t group, const optional<Tensor>& bias, const optional<Tensor>& block_expert,
+                const optional<Tensor>& total_padded, int64_t token_tile, int64_t epi) {
+  const bool grouped = q.dim() == 3;
+  TORCH_CHECK(a.dim() == 2 && a.stride(1) == 1 && a.stride(0) % 8 == 0 && q.is_contiguous() && scales.is_contiguous());
+  TORCH_CHECK(bits == 4 || bits == 8);
+  const int M = a.size(0), K = a.size(1);
+  const int E = grouped ? q.size(0) : 1, N = q.size(-2);
+  TORCH_CHECK(q.size(-1) * 8 == K * bits && K % 64 == 0 && group >= 32 && K % group == 0 && group % 32 == 0);
+  TORCH_CHECK(scales.scalar_type() == a.scalar_type() && scales.size(-1) == N && scales.size(-2) == K / group);
+  if (zeros.has_value()) TORCH_CHECK(zeros->scalar_type() == a.scalar_type() && zeros->sizes() == scales.sizes() && zeros->is_contiguous());
+  TORCH_CHECK(out.size(0) == M && out.size(1) == (epi == 1 ? N / 2 : N) && out.stride(1) == 1);
+  if (bias.has_value()) TORCH_CHECK(bias->numel() == N && bias->scalar_type() == a.scalar_type());
+  const c10::cuda::CUDAGuard guard(a.device());
+  int bn = token_tile > 0 ? (int)token_tile : b200::gemm_wna16_token_tile(M);
+  if (grouped) TORCH_CHECK(block_expert.has_value() && total_padded.has_value() && token_tile > 0 && M % bn == 0);
+  int splits = (grouped || epi != 0) ? 1 : b200::gemm_wna16_splits(M, N, K, bn);
+  Tensor partial;
+  if (splits > 1) partial = at::empty({splits, M, N}, a.options().dtype(at::kFloat));
+  b200::gemm_wna16(a.data_ptr(), M, a.stride(0), q.data_ptr(), scales.data_ptr(),
+                   zeros.has_value() ? zeros->data_ptr() : nullptr, E, N, K, group, bits, out.data_ptr(), out.stride(0),
+                   bias.has_value() ? bias->data_ptr() : nullptr, splits > 1 ? partial.data_ptr<float>() : nullptr,
+                   splits, ptr<int>(block_expert), ptr<int>(total_padded), grouped, bn, epi, dtype16(a), cur_stream(),
+                   status_ptr(a));
+}
+
 // ------------------------------------------------------------------ MLA
 void mla_decode(Tensor& out, const Tensor& q, const Tensor& cache, const Tensor& block_table, const Tensor& seq_lens,
                 const optional<Tensor>& query_start_loc, const optional<Tensor>& topk_indices, double scale,
@@ -598,6 +652,8 @@ TORCH_LIBRARY(b200, m) {
   m.def("scaled_int8_quant(Tensor(a!) q, Tensor(b!) scale, Tensor(c!)? azp, Tensor x, int mode) -> ()", &scaled_int8_quant);
   m.def("merge_attn_states(Tensor(a!) out, Tensor(b!)? out_lse, Tensor p_out, Tensor p_lse, Tensor s_out, Tensor s_lse) -> ()", &merge_attn_states);
   m.def("gemm_fp8_blockscale(Tensor(a!) out, Tensor a, Tensor a_scale, Tensor w, Tensor w_scale, Tensor? block_expert, Tensor? total_padded) -> ()", &gemm_fp8_blockscale);
+  m.def("scaled_mm(Tensor(a!) out, Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor? azp, Tensor? azp_adj, Tensor? bias, Tensor? block_expert, Tensor? total_padded) -> ()", &scaled_mm);
+  m.def("wna16_gemm(Tensor(a!) out, Tensor a, Tensor q, Tensor scales, Tensor? zeros, int bits, int group, Tensor? bias, Tensor? block_expert, Tensor? total_padded, int token_tile, int epi) -> ()", &wna16_gemm);
   m.def("mla_decode(Tensor(a!) out, Tensor q, Tensor cache, Tensor block_table, Tensor seq_lens, Tensor? query_start_loc, Tensor? topk_indices, float scale, Tensor(b!)? lse_out, Tensor(c!)? workspace, int num_splits) -> ()", &mla_decode);
   m.def("indexer_logits(Tensor(a!) logits, Tensor q, Tensor w, Tensor cache, Tensor block_table, Tensor seq_lens, Tensor query_start_loc, int block_size, int max_len) -> ()", &indexer_logits);
   m.def("topk_per_row(Tensor(a!) out, Tensor x, Tensor? row_len, int cols) -> ()", &topk_per_row);

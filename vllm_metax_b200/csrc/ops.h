@@ -143,6 +143,18 @@ void merge_attn_states(void* out, float* out_lse, const void* p_out, const float
 void gemm_fp8_blockscale(const void* A, int M, int lda, const void* W, int E, int N, int K, void* C, int ldc,
                          const float* a_scale, const float* w_scale, const int* block_expert,
                          const int* total_padded, int grouped, int out_dtype, cudaStream_t stream, void* status);
+// ---- gemm_scaled_mm.cu
+void gemm_scaled_mm(const void* A, int M, int lda, const void* W, int E, int N, int K, void* C, int ldc,
+                    const float* a_scale, int a_per_row, const float* w_scale, int w_per_col, const int* azp,
+                    const int* azp_adj, const void* bias, const int* block_expert, const int* total_padded,
+                    int grouped, int kind, int out_dtype, cudaStream_t stream, void* status);
+// ---- gemm_wna16_tcgen05.cu
+int gemm_wna16_token_tile(int M);
+int gemm_wna16_splits(int M, int N, int K, int bn);
+void gemm_wna16(const void* A, int M, int lda, const void* Q, const void* scales, const void* zeros, int E, int N,
+                int K, int group, int bits, void* C, int ldc, const void* bias, float* partial, int splits,
+                const int* block_expert, const int* total_padded, int grouped, int token_tile, int epi, int dtype,
+                cudaStream_t stream, void* status);
 // ---- mla_decode.cu
 void mla_decode(const MlaDecodeParams& p, int fp8_records, int dtype, cudaStream_t stream);
 // ---- indexer.cu

@@ -69,6 +69,7 @@ environment_variables: dict[str, Callable[[], Any]] = {
     "B200_PEER_WAIT_ITERS": _int("B200_PEER_WAIT_ITERS", 20_000_000),
     # Use NVLS multimem instructions in fused collectives when available.
     "B200_USE_MULTIMEM": _flag("B200_USE_MULTIMEM", "0"),
+    "B200_PP_DISABLE_ALLGATHER": _flag("B200_PP_DISABLE_ALLGATHER", "0"),
     # ---- debug -------------------------------------------------------------
     "B200_FORCE_REFERENCE_OPS": _flag("B200_FORCE_REFERENCE_OPS", "0"),
     "B200_PRECISION_DUMP_DIR": _str("B200_PRECISION_DUMP_DIR", None),

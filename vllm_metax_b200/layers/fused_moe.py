@@ -108,6 +108,17 @@ class FusedMoE(nn.Module):
         else:
             param.data[e].copy_(loaded)
 
+    def load_expert_tensor(self, expert_id: int, shard: str, suffix: str, loaded: torch.Tensor) -> bool:
+        """Checkpoint tensors that have no one-to-one parameter (packed weight-only formats): the quant
+        method converts them.  Returns False when the tensor is not consumed."""
+        qm = self.quant_method
+        if qm is None or not hasattr(qm, "load_expert_tensor"):
+            return False
+        lo = self.ep_rank * self.num_local
+        if lo <= expert_id < lo + self.num_local:
+            qm.load_expert_tensor(self, expert_id - lo, shard, suffix, loaded)
+        return True
+
     # ---- forward ------------------------------------------------------------------
     def route(self, router_logits: torch.Tensor):
         bias = self.e_score_correction_bias

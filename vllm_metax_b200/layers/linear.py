@@ -65,12 +65,20 @@ class LinearBase(nn.Module):
         return x.reshape(-1, x.shape[-1]), x.shape[:-1]
 
 
+def _expand_scalar(param, loaded: torch.Tensor, rows: int) -> torch.Tensor:
+    """A per-tensor scale stored for a per-channel parameter: give every one of ``rows`` channels the value."""
+    if getattr(param, "expand_scalar", False) and loaded.numel() == 1:
+        return loaded.reshape(1, 1).expand(rows, 1)
+    return loaded.reshape(-1, 1) if getattr(param, "expand_scalar", False) and loaded.dim() == 1 else loaded
+
+
 class ReplicatedLinear(LinearBase):
     def __init__(self, in_features, out_features, bias=False, dtype=torch.bfloat16, quant_method=None, prefix=""):
         super().__init__(in_features, out_features, bias, dtype, quant_method, prefix)
         self._make(in_features, out_features, bias)
 
     def weight_loader(self, param: torch.Tensor, loaded: torch.Tensor, shard_id=None) -> None:
+        loaded = _expand_scalar(param, loaded, self.out_features)
         param.data.copy_(loaded.reshape(param.shape))
 
     def forward(self, x):
@@ -91,6 +99,7 @@ class ColumnParallelLinear(LinearBase):
         r = ps.tp_rank()
         out_dim = getattr(param, "output_dim", 0)
         n = param.shape[out_dim]
+        loaded = _expand_scalar(param, loaded, self.out_features)
         param.data.copy_(loaded.narrow(out_dim, r * n, n))
 
     def forward(self, x):
@@ -112,6 +121,7 @@ class MergedColumnParallelLinear(ColumnParallelLinear):
     def weight_loader(self, param, loaded, shard_id=None):
         out_dim = getattr(param, "output_dim", 0)
         scale = getattr(param, "block_n", 1)  # block-scale tensors cover `block_n` output rows per entry
+        loaded = _expand_scalar(param, loaded, sum(self.output_sizes) if shard_id is None else self.output_sizes[shard_id])
         if shard_id is None:  # already merged on disk
             per = [s // self.tp for s in self.output_sizes]
             off_src = off_dst = 0
@@ -187,9 +197,10 @@ class QKVParallelLinear(ColumnParallelLinear):
         kv_sz = self.num_kv_heads * self.head_size
         offs = {"q": 0, "k": q_sz, "v": q_sz + kv_sz}
         sizes = {"q": q_sz, "k": kv_sz, "v": kv_sz}
+        tq = self.total_num_heads * self.head_size
+        tkv = self.total_num_kv_heads * self.head_size
+        loaded = _expand_scalar(param, loaded, tq + 2 * tkv if shard_id is None else (tq if shard_id == "q" else tkv))
         if shard_id is None:
-            tq = self.total_num_heads * self.head_size
-            tkv = self.total_num_kv_heads * self.head_size
             for sid, src_off in (("q", 0), ("k", tq), ("v", tq + tkv)):
                 tot = tq if sid == "q" else tkv
                 self.weight_loader(param, loaded.narrow(out_dim, src_off // scale, max(tot // scale, 1)), sid)
@@ -212,7 +223,8 @@ class RowParallelLinear(LinearBase):
 
     def weight_loader(self, param, loaded, shard_id=None):
         in_dim = getattr(param, "input_dim", 1)
-        if param.dim() <= in_dim:  # per-output-channel vectors are replicated
+        loaded = _expand_scalar(param, loaded, self.out_features)
+        if param.dim() <= in_dim or getattr(param, "expand_scalar", False):  # per-output-channel values are replicated
             param.data.copy_(loaded.reshape(param.shape))
             return
         n = param.shape[in_dim]

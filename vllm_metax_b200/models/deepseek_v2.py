@@ -286,6 +286,8 @@ class DeepseekV2ForCausalLM(nn.Module):
                     if pname in params:
                         modules[mod_name].weight_loader(params[pname], w, eid, shard)
                         loaded.add(pname)
+                    elif modules[mod_name].load_expert_tensor(eid, shard, suffix, w):
+                        loaded.add(name)
                 continue
             name = name.replace("mlp.gate.e_score_correction_bias", "mlp.experts.e_score_correction_bias")
             # q_a_proj + kv_a_proj_with_mqa -> fused_qkv_a_proj (rows stacked)

@@ -103,6 +103,8 @@ class Qwen3MoeForCausalLM(LlamaForCausalLM):
             shard = _SHARD[proj]
             pname = f"{mod_name}.{'w2' if shard == 'w2' else 'w13'}_{suffix}"
             if pname not in params:
+                if modules[mod_name].load_expert_tensor(eid, shard, suffix, w):
+                    loaded.add(name)
                 continue
             modules[mod_name].weight_loader(params[pname], w, eid, shard)
             loaded.add(pname)

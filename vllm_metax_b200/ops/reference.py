@@ -917,3 +917,15 @@ def selective_scan_fwd(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta
     if z is not None:
         y = y * F.silu(z.float())
     return y.to(u.dtype), h
+
+
+def scaled_mm(aq, wq, a_scale, w_scale, out_dtype=torch.bfloat16, azp=None, azp_adj=None, bias=None):
+    """fp32 oracle of the W8A8 GEMM (int8 or fp8 operands, per-token / per-channel scales, optional azp)."""
+    acc = aq.float() @ wq.float().t()
+    if azp_adj is not None:
+        adj = azp_adj.float().reshape(1, -1)
+        acc = acc - (azp.float().reshape(-1, 1) * adj if azp is not None else adj)
+    out = acc * a_scale.float().reshape(-1, 1) * w_scale.float().reshape(1, -1)
+    if bias is not None:
+        out = out + bias.float()
+    return out.to(out_dtype)

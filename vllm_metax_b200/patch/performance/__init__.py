@@ -1,0 +1,2 @@
+"""Patches that only change speed."""
+from . import grouped_topk_router, speculative_decode_perf  # noqa: F401
