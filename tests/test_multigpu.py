@@ -140,3 +140,50 @@ def _tp_engine_worker(rank, world, fused):
 @pytest.mark.parametrize("fused", [False, True])
 def test_tp2_engine_generates(fused):
     _launch(_tp_engine_worker, 2, fused)
+
+
+def _moe_a2a_worker(rank, world, quant):
+    from vllm_metax_b200 import _custom_ops as ops
+    from vllm_metax_b200.layers.fused_moe import reference_moe
+    from vllm_metax_b200.parallel import state as ps
+    from vllm_metax_b200.parallel.all2all import NvlinkAll2AllManager, run_experts_a2a
+
+    ps.init_distributed(tensor_parallel_size=world)
+    dev = torch.device("cuda", rank)
+    g = ps.get_tp_group()
+    E, H, I, topk = 8, 512, 256, 2
+    mgr = NvlinkAll2AllManager(g, 64 + world, H, topk, E, torch.bfloat16, dev, quant_fp8=quant)
+    gen = torch.Generator().manual_seed(11)         # same stream on every rank
+    w13 = (torch.randn(E, 2 * I, H, generator=gen) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=gen) * 0.05).to(torch.bfloat16)
+    el = E // world
+    w13_l, w2_l = w13[rank * el:(rank + 1) * el].to(dev), w2[rank * el:(rank + 1) * el].to(dev)
+
+    def experts(a, a_scale, block_expert, total):
+        if a_scale is not None:      # fp8 rows + 1x128 scales -> back to bf16 for the bf16 expert weights
+            a = (a.view(torch.float8_e4m3fn).float() * a_scale.repeat_interleave(128, dim=1)).to(torch.bfloat16)
+        h = ops.gemm_grouped(a, w13_l, block_expert, total, epi=1)
+        return ops.gemm_grouped(h, w2_l, block_expert, total)
+
+    for step, T in enumerate((7, 64, 1, 33)):       # several steps: epochs, slot reuse, different sizes per step
+        xs = [(torch.randn(T + r, H, generator=gen) * 0.5).to(torch.bfloat16) for r in range(world)]
+        ids = [torch.stack([torch.randperm(E, generator=gen)[:topk] for _ in range(T + r)]).int() for r in range(world)]
+        wts = [torch.rand(T + r, topk, generator=gen) for r in range(world)]
+        shareds = [(torch.randn(T + r, H, generator=gen) * 0.1).to(torch.bfloat16) for r in range(world)]
+        shared = shareds[rank] if step % 2 else None
+        got = run_experts_a2a(mgr, xs[rank].to(dev), wts[rank].to(dev), ids[rank].to(dev), experts,
+                              None if shared is None else shared.to(dev))
+        torch.cuda.synchronize()
+        ops.check_kernel_status(rank)
+        want = reference_moe(xs[rank].float(), w13.float(), w2.float(), wts[rank], ids[rank].long())
+        if shared is not None:
+            want = want + shared.float()
+        err = 1.0 - float(torch.nn.functional.cosine_similarity(got.float().cpu().flatten(), want.flatten(), dim=0))
+        assert err < (3e-3 if quant else 3e-4), (step, err)
+        g.barrier()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("quant", [False, True])
+def test_moe_nvlink_all2all_2gpu(quant):
+    _launch(_moe_a2a_worker, 2, quant)

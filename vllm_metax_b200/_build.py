@@ -103,8 +103,8 @@ def build_cumem(verbose: bool = False, force: bool = False) -> Path | None:
         return None
     if force or _newer([src], CUMEM_LIB):
         inc = ["-I", os.path.join(_cuda_home(), "include"), "-I", sysconfig.get_paths()["include"]]
-        _run(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", *inc, str(src), "-o", str(CUMEM_LIB),
-              "-L", os.path.join(_cuda_home(), "lib64"), "-L", os.path.join(_cuda_home(), "lib64", "stubs"), "-lcuda"])
+        # the driver is dlopen'ed at first use: no link-time dependency on libcuda
+        _run(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", *inc, str(src), "-o", str(CUMEM_LIB), "-ldl"])
         if verbose:
             print("[b200 build] built cumem_allocator")
     return CUMEM_LIB

@@ -636,9 +636,76 @@ void gemm_ar_norm(const Tensor& x, const Tensor& w, Tensor& residual, const Tens
   TORCH_CHECK(rc == 0, "gemm_ar_norm: hidden size ", p.H, " not supported");
 }
 
+// ptrs: int64 CPU tensor [8, ep] = recv_x, recv_scale, recv_ids, recv_src, recv_count, disp_flag, comb_x, comb_flag
+static b200::MoeA2aParams a2a_params(const Tensor& ptrs, int64_t ep, int64_t rank, int64_t experts_per_rank, int64_t H,
+                                     int64_t topk, int64_t T, int64_t cap, bool quant, Tensor& local_sync,
+                                     int64_t wait_cycles, const Tensor& any) {
+  TORCH_CHECK(ep >= 1 && ep <= b200::kMaxRanks && ptrs.dim() == 2 && ptrs.size(0) == 8 && ptrs.size(1) >= ep);
+  TORCH_CHECK(!ptrs.is_cuda() && ptrs.scalar_type() == at::kLong && H % 8 == 0 && (!quant || H % 128 == 0));
+  TORCH_CHECK(local_sync.numel() >= 8 + ep && local_sync.element_size() == 4);
+  b200::MoeA2aParams p{};
+  p.ep = ep; p.rank = rank; p.experts_per_rank = experts_per_rank; p.H = H; p.topk = topk; p.T = T; p.cap = cap;
+  p.quant = quant;
+  const int64_t* pp = ptrs.data_ptr<int64_t>();
+  const int64_t st = ptrs.stride(0);
+  for (int r = 0; r < ep; ++r) {
+    p.recv_x[r] = reinterpret_cast<void*>(pp[0 * st + r]);
+    p.recv_scale[r] = reinterpret_cast<float*>(pp[1 * st + r]);
+    p.recv_ids[r] = reinterpret_cast<int*>(pp[2 * st + r]);
+    p.recv_src[r] = reinterpret_cast<int*>(pp[3 * st + r]);
+    p.recv_count[r] = reinterpret_cast<uint32_t*>(pp[4 * st + r]);
+    p.disp_flag[r] = reinterpret_cast<uint32_t*>(pp[5 * st + r]);
+    p.comb_x[r] = reinterpret_cast<void*>(pp[6 * st + r]);
+    p.comb_flag[r] = reinterpret_cast<uint32_t*>(pp[7 * st + r]);
+  }
+  p.local_sync = reinterpret_cast<uint32_t*>(local_sync.data_ptr());
+  p.wait_cycles = wait_cycles;
+  p.status = reinterpret_cast<b200::StatusWord*>(status_ptr(any));
+  return p;
+}
+
+void moe_a2a_dispatch(const Tensor& x, const Tensor& topk_ids, const Tensor& ptrs, int64_t ep, int64_t rank,
+                      int64_t experts_per_rank, int64_t cap, bool quant, Tensor& local_sync, int64_t wait_cycles) {
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && topk_ids.is_contiguous() && topk_ids.scalar_type() == at::kInt);
+  TORCH_CHECK(topk_ids.size(0) == x.size(0));
+  auto p = a2a_params(ptrs, ep, rank, experts_per_rank, x.size(1), topk_ids.size(1), x.size(0), cap, quant, local_sync,
+                      wait_cycles, x);
+  const c10::cuda::CUDAGuard guard(x.device());
+  b200::moe_a2a_dispatch(p, x.data_ptr(), topk_ids.data_ptr<int>(), dtype16(x), cur_stream());
+}
+
+void moe_a2a_combine(Tensor& out, const Tensor& y, const Tensor& inv_pos, const Tensor& topk_w, const Tensor& topk_ids,
+                     const optional<Tensor>& shared_out, const Tensor& ptrs, int64_t ep, int64_t rank,
+                     int64_t experts_per_rank, int64_t cap, Tensor& local_sync, int64_t wait_cycles) {
+  TORCH_CHECK(y.dim() == 2 && y.is_contiguous() && out.is_contiguous() && out.size(1) == y.size(1));
+  TORCH_CHECK(inv_pos.numel() == ep * cap && inv_pos.scalar_type() == at::kInt && topk_w.scalar_type() == at::kFloat);
+  TORCH_CHECK(topk_w.is_contiguous() && topk_ids.is_contiguous() && topk_ids.scalar_type() == at::kInt);
+  TORCH_CHECK(topk_w.size(0) == out.size(0) && out.scalar_type() == y.scalar_type());
+  if (shared_out.has_value()) TORCH_CHECK(shared_out->is_contiguous() && shared_out->sizes() == out.sizes());
+  auto p = a2a_params(ptrs, ep, rank, experts_per_rank, y.size(1), topk_ids.size(1), out.size(0), cap, false,
+                      local_sync, wait_cycles, y);
+  const c10::cuda::CUDAGuard guard(y.device());
+  b200::moe_a2a_combine(p, y.data_ptr(), inv_pos.data_ptr<int>(), out.data_ptr(), topk_w.data_ptr<float>(),
+                        topk_ids.data_ptr<int>(), shared_out.has_value() ? shared_out->data_ptr() : nullptr,
+                        dtype16(y), cur_stream());
+}
+
+// dst[i] = src[idx[i]] for i < count[0] (rows of any dtype whose byte width is a multiple of 16)
+void gather_rows(Tensor& dst, const Tensor& src, const Tensor& idx, const Tensor& count) {
+  TORCH_CHECK(dst.is_contiguous() && src.is_contiguous() && dst.dim() == 2 && src.dim() == 2);
+  const int64_t row_bytes = src.size(1) * src.element_size();
+  TORCH_CHECK(row_bytes % 16 == 0 && dst.size(1) * dst.element_size() == row_bytes && idx.numel() >= dst.size(0));
+  const c10::cuda::CUDAGuard guard(src.device());
+  b200::gather_rows(dst.data_ptr(), src.data_ptr(), idx.data_ptr<int>(), count.data_ptr<int>(), dst.size(0),
+                    src.size(0), row_bytes, cur_stream());
+}
+
 }  // namespace
 
 TORCH_LIBRARY(b200, m) {
+  m.def("moe_a2a_dispatch(Tensor x, Tensor topk_ids, Tensor ptrs, int ep, int rank, int experts_per_rank, int cap, bool quant, Tensor(a!) local_sync, int wait_cycles) -> ()", &moe_a2a_dispatch);
+  m.def("moe_a2a_combine(Tensor(a!) out, Tensor y, Tensor inv_pos, Tensor topk_w, Tensor topk_ids, Tensor? shared_out, Tensor ptrs, int ep, int rank, int experts_per_rank, int cap, Tensor(b!) local_sync, int wait_cycles) -> ()", &moe_a2a_combine);
+  m.def("gather_rows(Tensor(a!) dst, Tensor src, Tensor idx, Tensor count) -> ()", &gather_rows);
   m.def("get_status(int device) -> Tensor", &get_status);
   m.def("topk_gating(Tensor(a!) weights, Tensor(b!) ids, Tensor gating, Tensor? bias, int mode, bool renorm, float scale) -> ()", &topk_gating);
   m.def("grouped_topk(Tensor(a!) weights, Tensor(b!) ids, Tensor gating, Tensor? bias, int n_group, int topk_group, bool sigmoid, bool renorm, float scale) -> ()", &grouped_topk);

@@ -41,6 +41,8 @@ struct Driver {
   CUresult (*ctxGetCurrent)(CUcontext*);
   CUresult (*devicePrimaryCtxRetain)(CUcontext*, CUdevice);
   CUresult (*ctxSetCurrent)(CUcontext);
+  CUresult (*memcpyDtoH)(void*, CUdeviceptr, size_t);
+  CUresult (*memcpyHtoD)(CUdeviceptr, const void*, size_t);
   bool loaded = false;
 };
 
@@ -81,7 +83,8 @@ bool load_driver() {
             sym(lib, "cuMemGetAllocationGranularity", g_drv.memGetAllocationGranularity) &&
             sym(lib, "cuGetErrorString", g_drv.getErrorString) && sym(lib, "cuCtxGetCurrent", g_drv.ctxGetCurrent) &&
             sym(lib, "cuDevicePrimaryCtxRetain", g_drv.devicePrimaryCtxRetain) &&
-            sym(lib, "cuCtxSetCurrent", g_drv.ctxSetCurrent);
+            sym(lib, "cuCtxSetCurrent", g_drv.ctxSetCurrent) && sym(lib, "cuMemcpyDtoH_v2", g_drv.memcpyDtoH) &&
+            sym(lib, "cuMemcpyHtoD_v2", g_drv.memcpyHtoD);
   if (!ok) g_last_error = "CUDA driver lacks the virtual memory management entry points";
   g_drv.loaded = ok;
   return ok;
@@ -288,6 +291,30 @@ PyObject* py_restore(PyObject*, PyObject* args) {
   Py_RETURN_NONE;
 }
 
+// copy(ptr, host_ptr, nbytes, to_host): synchronous copy between an allocation and host memory
+PyObject* py_copy(PyObject*, PyObject* args) {
+  unsigned long long dev, host, n;
+  int to_host;
+  if (!PyArg_ParseTuple(args, "KKKp", &dev, &host, &n, &to_host)) return nullptr;
+  bool ok = true;
+  if (g_fake) {
+    if (to_host) std::memcpy(reinterpret_cast<void*>(host), reinterpret_cast<void*>(dev), n);
+    else std::memcpy(reinterpret_cast<void*>(dev), reinterpret_cast<void*>(host), n);
+  } else {
+    Py_BEGIN_ALLOW_THREADS
+    std::lock_guard<std::mutex> lk(g_mu);
+    ok = load_driver() &&
+         (to_host ? check(g_drv.memcpyDtoH(reinterpret_cast<void*>(host), (CUdeviceptr)dev, n), "cuMemcpyDtoH")
+                  : check(g_drv.memcpyHtoD((CUdeviceptr)dev, reinterpret_cast<const void*>(host), n), "cuMemcpyHtoD"));
+    Py_END_ALLOW_THREADS
+  }
+  if (!ok) {
+    PyErr_SetString(PyExc_RuntimeError, g_last_error.c_str());
+    return nullptr;
+  }
+  Py_RETURN_NONE;
+}
+
 PyObject* py_stats(PyObject*, PyObject*) {
   std::lock_guard<std::mutex> lk(g_mu);
   unsigned long long mapped = 0, reserved = 0;
@@ -308,6 +335,7 @@ PyMethodDef kMethods[] = {
     {"allocations", py_allocations, METH_NOARGS, "[(ptr, size, device, tag, mapped)]"},
     {"release", py_release, METH_VARARGS, "drop the physical memory behind ptr"},
     {"restore", py_restore, METH_VARARGS, "back ptr with fresh physical memory"},
+    {"copy", py_copy, METH_VARARGS, "copy(ptr, host_ptr, nbytes, to_host)"},
     {"stats", py_stats, METH_NOARGS, "byte counters"},
     {nullptr, nullptr, 0, nullptr}};
 

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include "status.h"
+#include "comm_params.h"
 
 namespace b200 {
 
@@ -155,6 +156,12 @@ void gemm_wna16(const void* A, int M, int lda, const void* Q, const void* scales
                 int K, int group, int bits, void* C, int ldc, const void* bias, float* partial, int splits,
                 const int* block_expert, const int* total_padded, int grouped, int token_tile, int epi, int dtype,
                 cudaStream_t stream, void* status);
+// ---- comm_moe_a2a.cu
+void moe_a2a_dispatch(const MoeA2aParams& p, const void* x, const int* topk_ids, int dtype, cudaStream_t stream);
+void moe_a2a_combine(const MoeA2aParams& p, const void* y, const int* inv_pos, void* out, const float* topk_w,
+                     const int* topk_ids, const void* shared_out, int dtype, cudaStream_t stream);
+void gather_rows(void* dst, const void* src, const int* idx, const int* count, int max_rows, int limit, int row_bytes,
+                 cudaStream_t stream);
 // ---- mla_decode.cu
 void mla_decode(const MlaDecodeParams& p, int fp8_records, int dtype, cudaStream_t stream);
 // ---- indexer.cu

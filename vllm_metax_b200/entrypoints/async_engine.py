@@ -1,0 +1,161 @@
+"""Asynchronous front of ``LLMEngine`` for serving: one background thread steps the engine, request
+coroutines receive incremental outputs through per-request queues.
+
+The engine thread is the only code that touches the scheduler / model runner; producers hand requests
+over through a lock-protected inbox, so no engine state is shared with the event loop.  A failed step
+marks the engine dead: every in-flight and every later request receives ``EngineDeadError``.
+Parity: the role of vLLM's AsyncLLM / EngineCore client that the reference serves through
+(``vllm serve`` with the platform plugin, SURVEY call stack 3.2).
+"""
+from __future__ import annotations
+
+import asyncio
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import AsyncIterator, Optional, Sequence
+
+from ..engine.llm import LLM, EngineDeadError
+from ..engine.sampling_params import SamplingParams
+
+
+@dataclass
+class StreamChunk:
+    request_id: str
+    new_token_ids: list[int]
+    token_ids: list[int]
+    text: Optional[str]
+    finished: bool
+    finish_reason: Optional[str] = None
+    prompt_tokens: int = 0
+    error: Optional[BaseException] = None
+    ttft: Optional[float] = None
+
+
+@dataclass
+class _Stream:
+    queue: asyncio.Queue
+    loop: asyncio.AbstractEventLoop
+    sent: int = 0
+    t_arrival: float = field(default_factory=time.perf_counter)
+    t_first: Optional[float] = None
+
+
+class AsyncLLM:
+    def __init__(self, llm: LLM):
+        self.llm = llm
+        self.engine = llm.engine
+        self._inbox: list[tuple] = []
+        self._aborts: list[str] = []
+        self._lock = threading.Lock()
+        self._wake = threading.Event()
+        self._streams: dict[str, _Stream] = {}
+        self._stop = False
+        self._seq = 0
+        self.metrics = {"requests_total": 0, "requests_finished": 0, "requests_aborted": 0, "generated_tokens": 0,
+                        "prompt_tokens": 0, "ttft_sum": 0.0, "ttft_count": 0}
+        self._thread = threading.Thread(target=self._run, name="b200-engine", daemon=True)
+        self._thread.start()
+
+    # ------------------------------------------------------------------ engine thread
+    def _post(self, st: _Stream, chunk: StreamChunk) -> None:
+        st.loop.call_soon_threadsafe(st.queue.put_nowait, chunk)
+
+    def _fail_all(self, err: BaseException) -> None:
+        for rid, st in list(self._streams.items()):
+            self._post(st, StreamChunk(rid, [], [], None, True, "error", error=err))
+        self._streams.clear()
+
+    def _run(self) -> None:
+        eng = self.engine
+        while not self._stop:
+            with self._lock:
+                inbox, self._inbox = self._inbox, []
+                aborts, self._aborts = self._aborts, []
+            for rid in aborts:
+                eng.abort_request(rid)
+                st = self._streams.pop(rid, None)
+                if st is not None:
+                    self.metrics["requests_aborted"] += 1
+                    self._post(st, StreamChunk(rid, [], [], None, True, "abort"))
+            for rid, ids, params, prompt, st in inbox:
+                try:
+                    eng.add_request(ids, params, request_id=rid, prompt=prompt)
+                    self._streams[rid] = st
+                    self.metrics["requests_total"] += 1
+                    self.metrics["prompt_tokens"] += len(ids)
+                except BaseException as e:
+                    self._post(st, StreamChunk(rid, [], [], None, True, "error", error=e))
+            if not eng.has_unfinished_requests() or eng.scheduler.paused:
+                self._wake.wait(timeout=0.05)
+                self._wake.clear()
+                continue
+            try:
+                finished = eng.step()
+            except BaseException as e:
+                self._fail_all(e if isinstance(e, EngineDeadError) else EngineDeadError(repr(e)))
+                continue
+            now = time.perf_counter()
+            done = {r.request_id: r for r in finished}
+            for rid, st in list(self._streams.items()):
+                r = done.get(rid) or eng.requests.get(rid)
+                if r is None:
+                    continue
+                n = len(r.output_token_ids)
+                fin = rid in done
+                if n == st.sent and not fin:
+                    continue
+                if st.t_first is None and n > 0:
+                    st.t_first = now
+                    self.metrics["ttft_sum"] += now - st.t_arrival
+                    self.metrics["ttft_count"] += 1
+                new = list(r.output_token_ids[st.sent:n])
+                self.metrics["generated_tokens"] += len(new)
+                st.sent = n
+                out = eng.make_output(r) if fin else None
+                text = out.outputs[0].text if out is not None else (
+                    eng.tokenizer.decode(r.output_token_ids, skip_special_tokens=True) if eng.tokenizer else None)
+                self._post(st, StreamChunk(rid, new, list(r.output_token_ids), text, fin,
+                                           out.outputs[0].finish_reason if out else None, len(r.prompt_token_ids),
+                                           ttft=None if st.t_first is None else st.t_first - st.t_arrival))
+                if fin:
+                    self.metrics["requests_finished"] += 1
+                    del self._streams[rid]
+
+    # ------------------------------------------------------------------ coroutine API
+    async def generate(self, prompt_token_ids: Sequence[int], params: SamplingParams, request_id: Optional[str] = None,
+                       prompt: Optional[str] = None) -> AsyncIterator[StreamChunk]:
+        if self.engine.dead is not None:
+            raise EngineDeadError(str(self.engine.dead))
+        loop = asyncio.get_running_loop()
+        with self._lock:
+            self._seq += 1
+            rid = request_id or f"cmpl-{self._seq}"
+            st = _Stream(asyncio.Queue(), loop)
+            self._inbox.append((rid, list(prompt_token_ids), params, prompt, st))
+        self._wake.set()
+        try:
+            while True:
+                chunk: StreamChunk = await st.queue.get()
+                if chunk.error is not None:
+                    raise chunk.error
+                yield chunk
+                if chunk.finished:
+                    return
+        except (asyncio.CancelledError, GeneratorExit):
+            self.abort(rid)
+            raise
+
+    def abort(self, request_id: str) -> None:
+        with self._lock:
+            self._aborts.append(request_id)
+        self._wake.set()
+
+    def shutdown(self) -> None:
+        self._stop = True
+        self._wake.set()
+        self._thread.join(timeout=5)
+
+    @property
+    def is_dead(self) -> bool:
+        return self.engine.dead is not None

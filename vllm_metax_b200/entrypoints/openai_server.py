@@ -1,0 +1,229 @@
+"""OpenAI-compatible HTTP server over ``AsyncLLM``.
+
+Routes: ``/v1/models``, ``/v1/completions``, ``/v1/chat/completions`` (streaming through server-sent
+events), ``/tokenize``, ``/detokenize``, ``/health``, ``/metrics`` (Prometheus text), and the control
+plane the RLHF / benchmark harnesses use: ``/sleep``, ``/wake_up``, ``/is_sleeping``, ``/pause``,
+``/resume``, ``/collective_rpc``-free by design (SPMD ranks run the same server code).
+Parity: the reference is served by ``vllm serve`` (OpenAI API server + ``vllm bench serve`` client,
+BASELINE methodology); sampling defaults follow patch/enhancement/chores/bench_serve_args.py:284-292
+(temperature 0 unless the request sets one).
+"""
+import json
+import time
+import uuid
+from typing import Any, Optional
+
+from ..engine.llm import EngineDeadError
+from ..engine.sampling_params import SamplingParams
+from .async_engine import AsyncLLM
+
+
+def sampling_from_request(body: dict, default_max_tokens: int = 16) -> SamplingParams:
+    stop = body.get("stop")
+    if isinstance(stop, str):
+        stop = [stop]
+    kw: dict[str, Any] = dict(
+        max_tokens=int(body.get("max_tokens") or body.get("max_completion_tokens") or default_max_tokens),
+        temperature=float(body.get("temperature", 0.0) or 0.0),
+        top_p=float(body.get("top_p", 1.0) or 1.0),
+        top_k=int(body.get("top_k", 0) or 0),
+        min_p=float(body.get("min_p", 0.0) or 0.0),
+        repetition_penalty=float(body.get("repetition_penalty", 1.0) or 1.0),
+        presence_penalty=float(body.get("presence_penalty", 0.0) or 0.0),
+        frequency_penalty=float(body.get("frequency_penalty", 0.0) or 0.0),
+        ignore_eos=bool(body.get("ignore_eos", False)),
+        seed=body.get("seed"),
+    )
+    if stop:
+        kw["stop"] = list(stop)
+    if body.get("stop_token_ids"):
+        kw["stop_token_ids"] = list(body["stop_token_ids"])
+    fields = getattr(SamplingParams, "__dataclass_fields__", None)
+    if fields is not None:
+        kw = {k: v for k, v in kw.items() if k in fields}
+    return SamplingParams(**kw)
+
+
+def render_chat(tokenizer, messages: list[dict], add_generation_prompt: bool = True) -> str:
+    if tokenizer is not None and getattr(tokenizer, "chat_template", None):
+        return tokenizer.apply_chat_template(messages, tokenize=False, add_generation_prompt=add_generation_prompt)
+    text = "".join(f"<|{m.get('role', 'user')}|>\n{m.get('content', '')}\n" for m in messages)
+    return text + ("<|assistant|>\n" if add_generation_prompt else "")
+
+
+def prometheus_text(allm: AsyncLLM) -> str:
+    m, st = allm.metrics, allm.engine.stats
+    kv = allm.engine.kv
+    lines = []
+
+    def g(name, val, typ="gauge", help_=""):
+        lines.append(f"# HELP b200:{name} {help_}")
+        lines.append(f"# TYPE b200:{name} {typ}")
+        lines.append(f"b200:{name} {val}")
+
+    g("num_requests_running", len(allm.engine.scheduler.running), help_="requests in the running queue")
+    g("num_requests_waiting", len(allm.engine.scheduler.waiting), help_="requests waiting for admission")
+    g("request_success_total", m["requests_finished"], "counter", "finished requests")
+    g("request_aborted_total", m["requests_aborted"], "counter", "aborted requests")
+    g("prompt_tokens_total", m["prompt_tokens"], "counter", "prompt tokens received")
+    g("generation_tokens_total", m["generated_tokens"], "counter", "tokens generated")
+    g("engine_steps_total", st["steps"], "counter", "scheduler iterations")
+    g("num_preemptions_total", st["preemptions"], "counter", "preempted requests")
+    g("time_to_first_token_seconds_sum", m["ttft_sum"], "counter", "sum of TTFT")
+    g("time_to_first_token_seconds_count", m["ttft_count"], "counter", "TTFT samples")
+    usage = getattr(kv, "usage", None)
+    if callable(usage):
+        g("kv_cache_usage_perc", usage(), help_="fraction of KV blocks in use")
+    return "\n".join(lines) + "\n"
+
+
+def build_app(allm: AsyncLLM, served_model_name: str = "b200-model"):
+    from fastapi import FastAPI, Request
+    from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+
+    app = FastAPI(title="vllm_metax_b200 OpenAI-compatible server")
+    tok = allm.engine.tokenizer
+    llm = allm.llm
+    state = {"sleeping": False}
+
+    def encode(prompt) -> tuple[list[int], Optional[str]]:
+        if isinstance(prompt, list) and prompt and isinstance(prompt[0], int):
+            return list(prompt), None
+        if isinstance(prompt, list) and len(prompt) == 1:
+            prompt = prompt[0]
+            if isinstance(prompt, list):
+                return list(prompt), None
+        if not isinstance(prompt, str):
+            raise ValueError("prompt must be a string or a list of token ids")
+        if tok is None:
+            raise ValueError("text prompt given but the server has no tokenizer; send token ids")
+        return tok.encode(prompt), prompt
+
+    def err(status: int, msg: str, typ: str = "invalid_request_error"):
+        return JSONResponse({"error": {"message": msg, "type": typ, "code": status}}, status_code=status)
+
+    @app.get("/health")
+    async def health():
+        return PlainTextResponse("", status_code=503 if allm.is_dead else 200)
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": served_model_name, "object": "model", "owned_by": "b200",
+                                            "max_model_len": llm.engine.cfg.scheduler.max_model_len}]}
+
+    @app.get("/metrics")
+    async def metrics():
+        return PlainTextResponse(prometheus_text(allm))
+
+    @app.post("/tokenize")
+    async def tokenize(req: Request):
+        body = await req.json()
+        if tok is None:
+            return err(400, "no tokenizer")
+        ids = tok.encode(body.get("prompt", ""))
+        return {"tokens": ids, "count": len(ids), "max_model_len": llm.engine.cfg.scheduler.max_model_len}
+
+    @app.post("/detokenize")
+    async def detokenize(req: Request):
+        body = await req.json()
+        if tok is None:
+            return err(400, "no tokenizer")
+        return {"prompt": tok.decode(body.get("tokens", []))}
+
+    @app.post("/sleep")
+    async def sleep(level: int = 1):
+        llm.sleep(level)
+        state["sleeping"] = True
+        return {"status": "sleeping", "level": level}
+
+    @app.post("/wake_up")
+    async def wake_up(req: Request):
+        tags = req.query_params.getlist("tags") or None
+        llm.wake_up(tags)
+        state["sleeping"] = False
+        return {"status": "awake"}
+
+    @app.get("/is_sleeping")
+    async def is_sleeping():
+        return {"is_sleeping": state["sleeping"]}
+
+    @app.post("/pause")
+    async def pause():
+        llm.pause_generation()
+        return {"status": "paused"}
+
+    @app.post("/resume")
+    async def resume():
+        llm.resume_generation()
+        return {"status": "running"}
+
+    async def run_one(ids, prompt, params, rid):
+        last = None
+        async for chunk in allm.generate(ids, params, rid, prompt):
+            last = chunk
+        return last
+
+    def usage(prompt_tokens: int, completion_tokens: int) -> dict:
+        return {"prompt_tokens": prompt_tokens, "completion_tokens": completion_tokens,
+                "total_tokens": prompt_tokens + completion_tokens}
+
+    async def serve(body: dict, chat: bool):
+        try:
+            if chat:
+                text = render_chat(tok, body.get("messages") or [])
+                ids, prompt = encode(text)
+            else:
+                ids, prompt = encode(body.get("prompt", ""))
+            params = sampling_from_request(body, default_max_tokens=16 if not chat else 256)
+        except Exception as e:
+            return err(400, str(e))
+        if len(ids) + params.max_tokens > llm.engine.cfg.scheduler.max_model_len:
+            return err(400, f"prompt ({len(ids)}) + max_tokens ({params.max_tokens}) exceeds max_model_len")
+        rid = ("chatcmpl-" if chat else "cmpl-") + uuid.uuid4().hex[:16]
+        created = int(time.time())
+        obj = "chat.completion" if chat else "text_completion"
+        if not body.get("stream"):
+            try:
+                last = await run_one(ids, prompt, params, rid)
+            except EngineDeadError as e:
+                return err(500, str(e), "engine_dead")
+            text = last.text if last.text is not None else ""
+            choice = ({"index": 0, "message": {"role": "assistant", "content": text}, "finish_reason": last.finish_reason}
+                      if chat else {"index": 0, "text": text, "token_ids": last.token_ids, "logprobs": None,
+                                    "finish_reason": last.finish_reason})
+            return {"id": rid, "object": obj, "created": created, "model": served_model_name, "choices": [choice],
+                    "usage": usage(len(ids), len(last.token_ids))}
+
+        async def sse():
+            prev = ""
+            ntok = 0
+            try:
+                async for chunk in allm.generate(ids, params, rid, prompt):
+                    cur = chunk.text if chunk.text is not None else ""
+                    delta, prev = cur[len(prev):] if cur.startswith(prev) else cur, cur
+                    ntok = len(chunk.token_ids)
+                    if chat:
+                        ch = {"index": 0, "delta": {"content": delta}, "finish_reason": chunk.finish_reason}
+                    else:
+                        ch = {"index": 0, "text": delta, "token_ids": chunk.new_token_ids,
+                              "finish_reason": chunk.finish_reason}
+                    yield "data: " + json.dumps({"id": rid, "object": obj + (".chunk" if chat else ""), "created": created,
+                                                 "model": served_model_name, "choices": [ch]}) + "\n\n"
+                if (body.get("stream_options") or {}).get("include_usage"):
+                    yield "data: " + json.dumps({"id": rid, "object": obj, "created": created, "model": served_model_name,
+                                                 "choices": [], "usage": usage(len(ids), ntok)}) + "\n\n"
+            except EngineDeadError as e:
+                yield "data: " + json.dumps({"error": {"message": str(e), "type": "engine_dead", "code": 500}}) + "\n\n"
+            yield "data: [DONE]\n\n"
+
+        return StreamingResponse(sse(), media_type="text/event-stream")
+
+    @app.post("/v1/completions")
+    async def completions(req: Request):
+        return await serve(await req.json(), chat=False)
+
+    @app.post("/v1/chat/completions")
+    async def chat_completions(req: Request):
+        return await serve(await req.json(), chat=True)
+
+    return app
