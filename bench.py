@@ -153,6 +153,7 @@ def main() -> None:
     dev_ms = max_over_ranks(ev0.elapsed_time(ev1))
     clocks = sampler.stop() if rank == 0 else {}
     ops.check_kernel_status(dev.index or 0)
+    phases = wl.phase_ms()
     out_tokens = args.steps * N * O
     value = out_tokens / (dev_ms / 1e3)
 
@@ -191,7 +192,8 @@ def main() -> None:
                        "global_batch": N, "seq_len": P, "output_len": O, "parallelism": f"tp{args.gpus}",
                        "block_size": BLOCK_SIZE, "prefill_tokens_per_step": PREFILL_TOKENS,
                        "l2": "inputs larger than L2 (16 GB weights + KV streamed every iteration)",
-                       "step": "one pass over the whole workload (prefill + decode of all requests)"},
+                       "step": "one pass over the whole workload (prefill + decode of all requests)",
+                       "last_pass_phases_rank0": phases},
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "ms_per_step": round(e2e_ms / args.steps, 2),
                     "h2d_bytes_per_step": runner.h2d_bytes // args.steps,

@@ -187,3 +187,32 @@ def _moe_a2a_worker(rank, world, quant):
 @pytest.mark.parametrize("quant", [False, True])
 def test_moe_nvlink_all2all_2gpu(quant):
     _launch(_moe_a2a_worker, 2, quant)
+
+
+def _ag_gemm_worker(rank, world):
+    from vllm_metax_b200 import _custom_ops as ops
+    from vllm_metax_b200.parallel import state as ps
+    from vllm_metax_b200.parallel.fused_collectives import AllGatherGemm
+
+    ps.init_distributed(tensor_parallel_size=world)
+    dev = torch.device("cuda", rank)
+    g = ps.get_tp_group()
+    K = 1024
+    ag = AllGatherGemm(g, dev, 1024, K, torch.bfloat16)
+    gen = torch.Generator().manual_seed(21)
+    for rows, N in ((128, 256), (1024, 768), (384, 3584), (1024, 200)):
+        xs = [(torch.randn(rows, K, generator=gen) * 0.5).to(torch.bfloat16) for _ in range(world)]
+        w = (torch.randn(N, K, generator=gen) * 0.05).to(torch.bfloat16)
+        bias = (torch.randn(N, generator=gen) * 0.1).to(torch.bfloat16)
+        ag.x_shard(rows).copy_(xs[rank].to(dev))
+        out = ag(rows, w.to(dev), bias.to(dev))
+        torch.cuda.synchronize()
+        ops.check_kernel_status(rank)
+        want = torch.cat(xs, 0).float() @ w.float().t() + bias.float()
+        torch.testing.assert_close(out.float().cpu(), want, rtol=2e-2, atol=2e-2)
+        g.barrier()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_allgather_gemm_2gpu():
+    _launch(_ag_gemm_worker, 2)

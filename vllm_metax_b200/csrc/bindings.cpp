@@ -636,6 +636,35 @@ void gemm_ar_norm(const Tensor& x, const Tensor& w, Tensor& residual, const Tens
   TORCH_CHECK(rc == 0, "gemm_ar_norm: hidden size ", p.H, " not supported");
 }
 
+// ptrs: int64 CPU tensor [3, tp] = x_shard, xready, done (per owning rank)
+void ag_gemm(Tensor& out, const Tensor& w, const optional<Tensor>& bias, const Tensor& ptrs, Tensor& gathered,
+             Tensor& ready, Tensor& sync, int64_t tp, int64_t rank, int64_t rows_per_rank, int64_t wait_cycles) {
+  TORCH_CHECK(w.dim() == 2 && w.stride(1) == 1 && w.stride(0) % 8 == 0 && out.dim() == 2 && out.stride(1) == 1);
+  TORCH_CHECK(tp >= 1 && tp <= b200::kMaxRanks && ptrs.dim() == 2 && ptrs.size(0) == 3 && ptrs.size(1) >= tp);
+  TORCH_CHECK(!ptrs.is_cuda() && ptrs.scalar_type() == at::kLong && gathered.is_contiguous());
+  b200::AgGemmParams p{};
+  p.rows_per_rank = rows_per_rank; p.N = w.size(0); p.K = w.size(1); p.tp = tp; p.rank = rank; p.ldc = out.stride(0);
+  TORCH_CHECK(out.size(0) == tp * rows_per_rank && out.size(1) == p.N && gathered.numel() >= tp * rows_per_rank * p.K);
+  TORCH_CHECK(ready.numel() >= tp * rows_per_rank / 128 && sync.numel() >= 3 && rows_per_rank % 128 == 0 && p.K % 64 == 0);
+  const int64_t* pp = ptrs.data_ptr<int64_t>();
+  const int64_t st = ptrs.stride(0);
+  for (int r = 0; r < tp; ++r) {
+    p.x_shard[r] = reinterpret_cast<void*>(pp[0 * st + r]);
+    p.xready[r] = reinterpret_cast<uint32_t*>(pp[1 * st + r]);
+    p.done[r] = reinterpret_cast<uint32_t*>(pp[2 * st + r]);
+  }
+  p.gathered = gathered.data_ptr();
+  p.ready = reinterpret_cast<uint32_t*>(ready.data_ptr());
+  p.sync = reinterpret_cast<uint32_t*>(sync.data_ptr());
+  p.wait_cycles = wait_cycles;
+  p.status = reinterpret_cast<b200::StatusWord*>(status_ptr(w));
+  if (bias.has_value()) TORCH_CHECK(bias->numel() == p.N && bias->scalar_type() == w.scalar_type());
+  const c10::cuda::CUDAGuard guard(w.device());
+  const int rc = b200::ag_gemm(p, w.data_ptr(), w.stride(0), out.data_ptr(), bias.has_value() ? bias->data_ptr() : nullptr,
+                               dtype16(w), cur_stream());
+  TORCH_CHECK(rc == 0, "ag_gemm: rows per rank must be a multiple of 128");
+}
+
 // ptrs: int64 CPU tensor [8, ep] = recv_x, recv_scale, recv_ids, recv_src, recv_count, disp_flag, comb_x, comb_flag
 static b200::MoeA2aParams a2a_params(const Tensor& ptrs, int64_t ep, int64_t rank, int64_t experts_per_rank, int64_t H,
                                      int64_t topk, int64_t T, int64_t cap, bool quant, Tensor& local_sync,
@@ -705,6 +734,7 @@ void gather_rows(Tensor& dst, const Tensor& src, const Tensor& idx, const Tensor
 TORCH_LIBRARY(b200, m) {
   m.def("moe_a2a_dispatch(Tensor x, Tensor topk_ids, Tensor ptrs, int ep, int rank, int experts_per_rank, int cap, bool quant, Tensor(a!) local_sync, int wait_cycles) -> ()", &moe_a2a_dispatch);
   m.def("moe_a2a_combine(Tensor(a!) out, Tensor y, Tensor inv_pos, Tensor topk_w, Tensor topk_ids, Tensor? shared_out, Tensor ptrs, int ep, int rank, int experts_per_rank, int cap, Tensor(b!) local_sync, int wait_cycles) -> ()", &moe_a2a_combine);
+  m.def("ag_gemm(Tensor(a!) out, Tensor w, Tensor? bias, Tensor ptrs, Tensor(b!) gathered, Tensor(c!) ready, Tensor(d!) sync, int tp, int rank, int rows_per_rank, int wait_cycles) -> ()", &ag_gemm);
   m.def("gather_rows(Tensor(a!) dst, Tensor src, Tensor idx, Tensor count) -> ()", &gather_rows);
   m.def("get_status(int device) -> Tensor", &get_status);
   m.def("topk_gating(Tensor(a!) weights, Tensor(b!) ids, Tensor gating, Tensor? bias, int mode, bool renorm, float scale) -> ()", &topk_gating);

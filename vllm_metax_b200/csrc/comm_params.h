@@ -31,6 +31,19 @@ struct FusedArParams {
   StatusWord* status;
 };
 
+// All-gather -> GEMM (comm_ag_gemm.cu): C[tp*R, N] = concat_r(X_r[R, K]) . W[N, K]^T.
+struct AgGemmParams {
+  int rows_per_rank, N, K, tp, rank, ldc;
+  void* x_shard[kMaxRanks];        // [rows_per_rank, K] 16-bit, contiguous (symmetric)
+  uint32_t* xready[kMaxRanks];     // [tp] epoch written by each source: "my shard may be pulled"
+  uint32_t* done[kMaxRanks];       // [1] pulls completed on the owner's shard (monotonic counter)
+  void* gathered;                  // local [tp*rows_per_rank, K]
+  uint32_t* ready;                 // local [tp*rows_per_rank/128] epoch per landed row block
+  uint32_t* sync;                  // local [3]: last finished epoch, CTAs-left counter, pulls expected so far
+  long long wait_cycles;
+  StatusWord* status;
+};
+
 // Expert-parallel all-to-all (comm_moe_a2a.cu).  Pointer arrays are indexed by the rank that OWNS the memory.
 struct MoeA2aParams {
   int ep, rank, experts_per_rank, H, topk, T, cap, quant;

@@ -156,6 +156,9 @@ void gemm_wna16(const void* A, int M, int lda, const void* Q, const void* scales
                 int K, int group, int bits, void* C, int ldc, const void* bias, float* partial, int splits,
                 const int* block_expert, const int* total_padded, int grouped, int token_tile, int epi, int dtype,
                 cudaStream_t stream, void* status);
+// ---- comm_ag_gemm.cu
+int ag_gemm_copiers(int tp, int rows_per_rank);
+int ag_gemm(const AgGemmParams& p, const void* W, int ldw, void* C, const void* bias, int dtype, cudaStream_t stream);
 // ---- comm_moe_a2a.cu
 void moe_a2a_dispatch(const MoeA2aParams& p, const void* x, const int* topk_ids, int dtype, cudaStream_t stream);
 void moe_a2a_combine(const MoeA2aParams& p, const void* y, const int* inv_pos, void* out, const float* topk_w,

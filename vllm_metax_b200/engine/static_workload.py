@@ -51,6 +51,7 @@ class StaticWorkload:
             last = (qsl[1:] - 1).long()
             self.prefill_steps.append((s0, k, self.tokens[s0:s0 + k].reshape(-1), positions, md, last))
         self.graph = None
+        self.phase_events = None     # [start, prefill done, decode done] of the latest run()
 
     # ------------------------------------------------------------------ decode graph
     def capture(self) -> None:
@@ -104,6 +105,13 @@ class StaticWorkload:
         r.slot_mapping[:N] = blk * bs + self.P % bs
         r.input_ids[:N] = self.first
 
+    def phase_ms(self) -> dict:
+        """Device time of the prefill and decode parts of the latest ``run()`` (call after a synchronize)."""
+        ev = self.phase_events
+        if not ev:
+            return {}
+        return {"prefill_ms": round(ev[0].elapsed_time(ev[1]), 2), "decode_ms": round(ev[1].elapsed_time(ev[2]), 2)}
+
     # ------------------------------------------------------------------ the timed body
     @torch.no_grad()
     def run(self) -> int:
@@ -111,6 +119,11 @@ class StaticWorkload:
         number of kernels launched."""
         r = self.r
         before = ops.launch_count()
+        if self.phase_events is None and torch.cuda.is_available():
+            self.phase_events = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        ev = self.phase_events
+        if ev:
+            ev[0].record()
         for s0, k, ids, positions, md, last in self.prefill_steps:
             ctx = ForwardContext(md, r.kv_caches, positions)
             with set_forward_context(ctx):
@@ -120,7 +133,11 @@ class StaticWorkload:
         self._reset_decode_inputs()
         self.token_log[:, 0] = self.first
         launches = ops.launch_count() - before
+        if ev:
+            ev[1].record()
         for i in range(1, self.O):
             self.graph.replay()
             self.token_log[:, i] = r.sampled[: self.N]
+        if ev:
+            ev[2].record()
         return launches + (self.O - 1) * self.launches_per_replay

@@ -101,3 +101,59 @@ def get_fused_row_parallel(group: Group, device: torch.device, max_tokens: int, 
         cur = FusedRowParallelNorm(group, device, max_tokens, hidden, dtype)
         _SHARED[key] = cur
     return cur
+
+
+class AllGatherGemm:
+    """``concat_r(x_r) @ W^T`` for row-sharded activations as ONE kernel per rank (``csrc/comm_ag_gemm.cu``):
+    remote row blocks stream in over NVLink (once each) while the tensor cores already work on the local
+    shard.  ``x_shard()`` is the symmetric input buffer the producing op writes into.
+
+    On CPU tensors the same contract is met with an all-gather + matmul (host-side tests)."""
+
+    def __init__(self, group: Group, device: torch.device, max_rows_per_rank: int, k: int, dtype: torch.dtype):
+        self.group, self.device, self.k, self.dtype = group, device, k, dtype
+        self.tp, self.rank = group.world_size, group.rank_in_group
+        self.rows_cap = (max_rows_per_rank + 127) // 128 * 128
+        self.cuda = device.type == "cuda"
+        if not self.cuda:
+            self._x = torch.zeros(self.rows_cap, k, dtype=dtype)
+            return
+        esz = torch.empty((), dtype=dtype).element_size()
+        n_x = self.rows_cap * k * esz
+        self.ws = SymmWorkspace(group, n_x + 3 * SymmWorkspace.ALIGN + 4096, device)
+        r_x, r_ready, r_done = self.ws.region("ag_x", n_x), self.ws.region("ag_xready", 64), self.ws.region("ag_done", 64)
+        self._x = self.ws.local(r_x, dtype, (self.rows_cap, k))
+        self.ws.local(r_ready, torch.int32, (16,)).zero_()
+        self.ws.local(r_done, torch.int32, (16,)).zero_()
+        self.ptrs = torch.tensor([self.ws.peer_ptrs(r_x), self.ws.peer_ptrs(r_ready), self.ws.peer_ptrs(r_done)],
+                                 dtype=torch.int64)
+        self.gathered = torch.empty(self.tp * self.rows_cap, k, dtype=dtype, device=device)
+        self.ready = torch.zeros(self.tp * self.rows_cap // 128 + 1, dtype=torch.int32, device=device)
+        self.sync = torch.zeros(4, dtype=torch.int32, device=device)
+        self.wait_cycles = int(envs.B200_PEER_WAIT_ITERS) * 200
+        torch.cuda.synchronize(device)
+        group.barrier()
+
+    def x_shard(self, rows: int) -> torch.Tensor:
+        """The first ``rows`` (multiple of 128) rows of this rank's symmetric input buffer."""
+        assert rows % 128 == 0 and rows <= self.rows_cap
+        return self._x[:rows]
+
+    def __call__(self, rows: int, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``rows`` = rows per rank (same on every rank, multiple of 128); returns ``[tp*rows, N]``."""
+        if not self.cuda:
+            x_all = self.group.all_gather(self._x[:rows], 0) if self.tp > 1 else self._x[:rows]
+            y = x_all.float() @ w.float().t()
+            if bias is not None:
+                y = y + bias.float()
+            return y.to(self.dtype)
+        out = torch.empty(self.tp * rows, w.shape[0], dtype=self.dtype, device=self.device)
+        # the shard buffer is [rows_cap, K] on every rank; with rows < rows_cap the kernel still addresses row
+        # blocks relative to each shard's base, and the gathered buffer is indexed with `rows` per rank
+        torch.ops.b200.ag_gemm(out, w, bias, self.ptrs, self.gathered, self.ready, self.sync, self.tp, self.rank,
+                               rows, self.wait_cycles)
+        return out
+
+    def close(self) -> None:
+        if self.cuda:
+            self.ws.close()
