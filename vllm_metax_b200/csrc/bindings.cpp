@@ -636,6 +636,116 @@ void gemm_ar_norm(const Tensor& x, const Tensor& w, Tensor& residual, const Tens
   TORCH_CHECK(rc == 0, "gemm_ar_norm: hidden size ", p.H, " not supported");
 }
 
+// ------------------------------------------------------------------ small / fused kernels
+void small_gemm(Tensor& out, const Tensor& a, const Tensor& w, const optional<Tensor>& bias) {
+  TORCH_CHECK(a.dim() == 2 && w.dim() == 2 && a.stride(1) == 1 && w.stride(1) == 1 && a.size(1) == w.size(1));
+  TORCH_CHECK(out.size(0) == a.size(0) && out.size(1) == w.size(0) && out.stride(1) == 1 && w.scalar_type() == a.scalar_type());
+  const bool f32 = out.scalar_type() == at::kFloat;
+  TORCH_CHECK(f32 || out.scalar_type() == a.scalar_type());
+  if (bias.has_value()) TORCH_CHECK(bias->numel() == w.size(0) && bias->scalar_type() == a.scalar_type());
+  const c10::cuda::CUDAGuard guard(a.device());
+  const int rc = b200::small_gemm(out.data_ptr(), a.data_ptr(), w.data_ptr(), bias.has_value() ? bias->data_ptr() : nullptr,
+                                  a.size(0), w.size(0), a.size(1), a.stride(0), w.stride(0), out.stride(0), dtype16(a),
+                                  f32 ? 1 : 0, cur_stream());
+  TORCH_CHECK(rc == 0, "small_gemm: needs M <= 32, K % 32 == 0 and 16-byte aligned rows (rc=", rc, ")");
+}
+
+void fused_qk_norm_rope(Tensor& qkv, const Tensor& q_weight, const Tensor& k_weight, const Tensor& cos_sin,
+                        const Tensor& positions, int64_t hq, int64_t hk, int64_t hv, int64_t head_dim, bool is_neox,
+                        double eps, bool gemma) {
+  TORCH_CHECK(qkv.dim() == 2 && qkv.is_contiguous() && qkv.size(1) == (hq + hk + hv) * head_dim);
+  TORCH_CHECK(cos_sin.scalar_type() == at::kFloat && cos_sin.is_contiguous() && positions.scalar_type() == at::kLong);
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  const int rc = b200::fused_qk_norm_rope(qkv.data_ptr(), q_weight.data_ptr(), k_weight.data_ptr(),
+                                          cos_sin.data_ptr<float>(), positions.data_ptr<int64_t>(), qkv.size(0), hq, hk,
+                                          hv, head_dim, cos_sin.size(1), is_neox, (float)eps, gemma, dtype16(qkv),
+                                          cur_stream());
+  TORCH_CHECK(rc == 0, "fused_qk_norm_rope: unsupported head_dim / rotary_dim");
+}
+
+void mla_rope_and_cache(Tensor& q_pe, Tensor& k_pe, const Tensor& kv_c, Tensor& cache, const Tensor& cos_sin,
+                        const Tensor& positions, const Tensor& slot_mapping, bool is_neox) {
+  TORCH_CHECK(q_pe.dim() == 3 && q_pe.size(2) == 64 && q_pe.stride(2) == 1 && q_pe.stride(1) == 64);
+  TORCH_CHECK(k_pe.size(-1) == 64 && k_pe.stride(-1) == 1 && kv_c.size(-1) == 512 && kv_c.stride(-1) == 1);
+  TORCH_CHECK(cache.is_contiguous() && cache.size(-1) == 576 && cache.scalar_type() == q_pe.scalar_type());
+  TORCH_CHECK(cos_sin.scalar_type() == at::kFloat && cos_sin.size(1) == 64 && cos_sin.is_contiguous());
+  const c10::cuda::CUDAGuard guard(q_pe.device());
+  b200::mla_rope_and_cache(q_pe.data_ptr(), k_pe.data_ptr(), kv_c.data_ptr(), cache.data_ptr(), cos_sin.data_ptr<float>(),
+                           positions.data_ptr<int64_t>(), slot_mapping.data_ptr<int64_t>(), q_pe.size(0), q_pe.size(1),
+                           q_pe.stride(0), k_pe.stride(0), kv_c.stride(0), is_neox, cache.numel() / 576, dtype16(q_pe),
+                           cur_stream());
+}
+
+void concat_mla_q(Tensor& out, const Tensor& nope, const Tensor& pe) {
+  TORCH_CHECK(out.is_contiguous() && out.size(-1) == 576 && nope.size(-1) == 512 && pe.size(-1) == 64);
+  TORCH_CHECK(nope.dim() == 3 && pe.dim() == 3 && nope.stride(2) == 1 && pe.stride(2) == 1);
+  TORCH_CHECK(nope.stride(0) == nope.size(1) * nope.stride(1) && pe.stride(0) == pe.size(1) * pe.stride(1));
+  const c10::cuda::CUDAGuard guard(out.device());
+  b200::concat_mla_q(out.data_ptr(), nope.data_ptr(), pe.data_ptr(), nope.size(0) * nope.size(1), nope.stride(1),
+                     pe.stride(1), dtype16(out), cur_stream());
+}
+
+void permute_cols(Tensor& out, const Tensor& a, const Tensor& perm) {
+  TORCH_CHECK(a.dim() == 2 && a.stride(1) == 1 && out.is_contiguous() && perm.scalar_type() == at::kInt);
+  TORCH_CHECK(out.size(0) == a.size(0) && out.size(1) == perm.numel());
+  const c10::cuda::CUDAGuard guard(a.device());
+  b200::permute_cols(out.data_ptr(), a.data_ptr(), perm.data_ptr<int>(), a.size(0), perm.numel(), a.stride(0),
+                     dtype16(a), cur_stream());
+}
+
+void gather_mla_cache(Tensor& dst, const Tensor& cache, const Tensor& block_table, const Tensor& cu_seq_lens,
+                      const optional<Tensor>& seq_starts) {
+  TORCH_CHECK(dst.is_contiguous() && dst.size(1) == 576 && cache.is_contiguous() && cache.dim() == 3);
+  const bool rec = cache.scalar_type() == at::kByte;
+  TORCH_CHECK(rec ? cache.size(2) == 656 : (cache.size(2) == 576 && cache.scalar_type() == dst.scalar_type()));
+  const c10::cuda::CUDAGuard guard(dst.device());
+  b200::gather_mla_cache(dst.data_ptr(), cache.data_ptr(), block_table.data_ptr<int>(), cu_seq_lens.data_ptr<int>(),
+                         ptr<int>(seq_starts), cu_seq_lens.numel() - 1, block_table.size(1), cache.size(1), dst.size(0),
+                         rec, dtype16(dst), cur_stream());
+}
+
+void gather_indexer_k(Tensor& dst_k, Tensor& dst_s, const Tensor& cache, const Tensor& block_table,
+                      const Tensor& cu_seq_lens, int64_t block_size) {
+  TORCH_CHECK(dst_k.is_contiguous() && dst_k.size(1) == 128 && dst_k.element_size() == 1 && dst_s.scalar_type() == at::kFloat);
+  TORCH_CHECK(cache.is_contiguous() && cache.scalar_type() == at::kByte);
+  const c10::cuda::CUDAGuard guard(dst_k.device());
+  b200::gather_indexer_k(dst_k.data_ptr(), dst_s.data_ptr<float>(), cache.data_ptr(), block_table.data_ptr<int>(),
+                         cu_seq_lens.data_ptr<int>(), cu_seq_lens.numel() - 1, block_table.size(1), block_size,
+                         dst_k.size(0), cur_stream());
+}
+
+// u / delta / z / out: [dim, tokens] with query_start_loc, or [batch, dim, L]; B / C: [groups, dstate, tokens] or
+// [batch, groups, dstate, L]; state fp32 [slots, dim, dstate].
+void selective_scan(Tensor& out, const Tensor& u, const Tensor& delta, const Tensor& A, const Tensor& B, const Tensor& C,
+                    const optional<Tensor>& D, const optional<Tensor>& z, const optional<Tensor>& delta_bias,
+                    bool delta_softplus, Tensor& state, const optional<Tensor>& query_start_loc,
+                    const optional<Tensor>& cache_indices, const optional<Tensor>& has_initial_state, int64_t pad_slot) {
+  TORCH_CHECK(u.is_contiguous() && delta.is_contiguous() && B.is_contiguous() && C.is_contiguous() && out.is_contiguous());
+  TORCH_CHECK(A.scalar_type() == at::kFloat && A.is_contiguous() && state.scalar_type() == at::kFloat && state.is_contiguous());
+  const bool varlen = query_start_loc.has_value();
+  b200::ScanParams p{};
+  p.u = u.data_ptr(); p.delta = delta.data_ptr(); p.out = out.data_ptr();
+  p.z = z.has_value() ? z->data_ptr() : nullptr;
+  p.A = A.data_ptr<float>(); p.B = B.data_ptr(); p.C = C.data_ptr();
+  p.D = ptr<float>(D); p.delta_bias = ptr<float>(delta_bias);
+  p.state = state.data_ptr<float>();
+  p.query_start_loc = ptr<int>(query_start_loc);
+  p.cache_indices = ptr<int>(cache_indices);
+  p.has_initial_state = has_initial_state.has_value() ? has_initial_state->data_ptr<uint8_t>() : nullptr;
+  p.dim = A.size(0); p.dstate = A.size(1);
+  if (varlen) {
+    TORCH_CHECK(u.dim() == 2 && B.dim() == 3);
+    p.batch = query_start_loc->numel() - 1; p.total_tokens = u.size(1); p.seqlen = 0; p.groups = B.size(0);
+  } else {
+    TORCH_CHECK(u.dim() == 3 && B.dim() == 4);
+    p.batch = u.size(0); p.seqlen = u.size(2); p.total_tokens = 0; p.groups = B.size(1);
+  }
+  p.softplus = delta_softplus; p.pad_slot = pad_slot;
+  const int dt = u.scalar_type() == at::kFloat ? 2 : dtype16(u);
+  const c10::cuda::CUDAGuard guard(u.device());
+  TORCH_CHECK(b200::selective_scan_fwd(p, dt, cur_stream()) == 0, "selective_scan: unsupported dstate / dim");
+}
+
 // ptrs: int64 CPU tensor [3, tp] = x_shard, xready, done (per owning rank)
 void ag_gemm(Tensor& out, const Tensor& w, const optional<Tensor>& bias, const Tensor& ptrs, Tensor& gathered,
              Tensor& ready, Tensor& sync, int64_t tp, int64_t rank, int64_t rows_per_rank, int64_t wait_cycles) {
@@ -735,6 +845,14 @@ TORCH_LIBRARY(b200, m) {
   m.def("moe_a2a_dispatch(Tensor x, Tensor topk_ids, Tensor ptrs, int ep, int rank, int experts_per_rank, int cap, bool quant, Tensor(a!) local_sync, int wait_cycles) -> ()", &moe_a2a_dispatch);
   m.def("moe_a2a_combine(Tensor(a!) out, Tensor y, Tensor inv_pos, Tensor topk_w, Tensor topk_ids, Tensor? shared_out, Tensor ptrs, int ep, int rank, int experts_per_rank, int cap, Tensor(b!) local_sync, int wait_cycles) -> ()", &moe_a2a_combine);
   m.def("ag_gemm(Tensor(a!) out, Tensor w, Tensor? bias, Tensor ptrs, Tensor(b!) gathered, Tensor(c!) ready, Tensor(d!) sync, int tp, int rank, int rows_per_rank, int wait_cycles) -> ()", &ag_gemm);
+  m.def("small_gemm(Tensor(a!) out, Tensor a, Tensor w, Tensor? bias) -> ()", &small_gemm);
+  m.def("fused_qk_norm_rope(Tensor(a!) qkv, Tensor q_weight, Tensor k_weight, Tensor cos_sin, Tensor positions, int hq, int hk, int hv, int head_dim, bool is_neox, float eps, bool gemma) -> ()", &fused_qk_norm_rope);
+  m.def("mla_rope_and_cache(Tensor(a!) q_pe, Tensor(b!) k_pe, Tensor kv_c, Tensor(c!) cache, Tensor cos_sin, Tensor positions, Tensor slot_mapping, bool is_neox) -> ()", &mla_rope_and_cache);
+  m.def("concat_mla_q(Tensor(a!) out, Tensor nope, Tensor pe) -> ()", &concat_mla_q);
+  m.def("permute_cols(Tensor(a!) out, Tensor a, Tensor perm) -> ()", &permute_cols);
+  m.def("gather_mla_cache(Tensor(a!) dst, Tensor cache, Tensor block_table, Tensor cu_seq_lens, Tensor? seq_starts) -> ()", &gather_mla_cache);
+  m.def("gather_indexer_k(Tensor(a!) dst_k, Tensor(b!) dst_s, Tensor cache, Tensor block_table, Tensor cu_seq_lens, int block_size) -> ()", &gather_indexer_k);
+  m.def("selective_scan(Tensor(a!) out, Tensor u, Tensor delta, Tensor A, Tensor B, Tensor C, Tensor? D, Tensor? z, Tensor? delta_bias, bool delta_softplus, Tensor(b!) state, Tensor? query_start_loc, Tensor? cache_indices, Tensor? has_initial_state, int pad_slot) -> ()", &selective_scan);
   m.def("gather_rows(Tensor(a!) dst, Tensor src, Tensor idx, Tensor count) -> ()", &gather_rows);
   m.def("get_status(int device) -> Tensor", &get_status);
   m.def("topk_gating(Tensor(a!) weights, Tensor(b!) ids, Tensor gating, Tensor? bias, int mode, bool renorm, float scale) -> ()", &topk_gating);

@@ -156,6 +156,40 @@ void gemm_wna16(const void* A, int M, int lda, const void* Q, const void* scales
                 int K, int group, int bits, void* C, int ldc, const void* bias, float* partial, int splits,
                 const int* block_expert, const int* total_padded, int grouped, int token_tile, int epi, int dtype,
                 cudaStream_t stream, void* status);
+// ---- small_gemm.cu
+int small_gemm(void* C, const void* A, const void* W, const void* bias, int M, int N, int K, int lda, int ldw, int ldc,
+               int dtype, int out_kind, cudaStream_t stream);
+// ---- fused_misc.cu
+int fused_qk_norm_rope(void* qkv, const void* q_weight, const void* k_weight, const float* cos_sin,
+                       const int64_t* positions, int tokens, int hq, int hk, int hv, int head_dim, int rot, int is_neox,
+                       float eps, int gemma, int dtype, cudaStream_t stream);
+void mla_rope_and_cache(void* q_pe, void* k_pe, const void* kv_c, void* cache, const float* cos_sin,
+                        const int64_t* positions, const int64_t* slots, int tokens, int heads, int64_t q_tok_stride,
+                        int64_t kpe_stride, int64_t kvc_stride, int is_neox, int64_t num_slots, int dtype,
+                        cudaStream_t stream);
+void concat_mla_q(void* out, const void* nope, const void* pe, int64_t rows, int64_t nope_stride, int64_t pe_stride,
+                  int dtype, cudaStream_t stream);
+void permute_cols(void* out, const void* a, const int* perm, int64_t rows, int cols, int64_t lda, int dtype,
+                  cudaStream_t stream);
+void gather_mla_cache(void* dst, const void* cache, const int* block_table, const int* cu_seq_lens,
+                      const int* seq_starts, int batch, int max_blocks, int block_size, int max_total, int records,
+                      int dtype, cudaStream_t stream);
+void gather_indexer_k(void* dst_k, float* dst_s, const void* cache, const int* block_table, const int* cu_seq_lens,
+                      int batch, int max_blocks, int block_size, int max_total, cudaStream_t stream);
+// ---- mamba_scan.cu
+struct ScanParams {
+  const void* u; const void* delta; const void* z; void* out;
+  const float* A;                 // [dim, dstate]
+  const void* B; const void* C;   // [(batch,) groups, dstate, tokens]
+  const float* D;                 // [dim] or null
+  const float* delta_bias;        // [dim] or null
+  float* state;                   // [slots, dim, dstate] fp32
+  const int* query_start_loc;     // [batch+1] or null (dense layout)
+  const int* cache_indices;       // [batch] or null (slot = b)
+  const uint8_t* has_initial_state;  // [batch] or null (no initial state)
+  int batch, dim, dstate, groups, seqlen, total_tokens, softplus, pad_slot;
+};
+int selective_scan_fwd(const ScanParams& p, int dtype, cudaStream_t stream);
 // ---- comm_ag_gemm.cu
 int ag_gemm_copiers(int tp, int rows_per_rank);
 int ag_gemm(const AgGemmParams& p, const void* W, int ldw, void* C, const void* bias, int dtype, cudaStream_t stream);
