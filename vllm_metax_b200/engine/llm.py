@@ -41,6 +41,10 @@ class LLMEngine:
         self.requests: dict[str, Request] = {}
         self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0}
         self.step_hooks: list = []
+        from .spec_decode import SpeculativeConfig, make_proposer
+
+        self.spec_config = SpeculativeConfig.from_dict((cfg.additional_config or {}).get("speculative_config"))
+        self.proposer = make_proposer(self.spec_config, self)
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
@@ -84,6 +88,8 @@ class LLMEngine:
             raise EngineDeadError(f"engine step failed: {e!r}") from e
         now = time.perf_counter()
         finished = self.scheduler.update(so, sampled, now)
+        if self.proposer is not None:
+            self._propose_drafts(so, sampled)
         self.stats["steps"] += 1
         self.stats["decode_tokens"] += so.num_decode
         self.stats["prefill_tokens"] += so.num_tokens - so.num_decode
@@ -91,6 +97,29 @@ class LLMEngine:
         for r in finished:
             self.requests.pop(r.request_id, None)
         return finished
+
+    def _propose_drafts(self, so, sampled=None) -> None:
+        """Attach draft tokens to the requests that will decode next step."""
+        self.stats["draft_tokens"] = self.scheduler.num_draft_tokens
+        self.stats["accepted_tokens"] = self.scheduler.num_accepted_tokens
+        if hasattr(self.proposer, "after_step"):       # model-based proposers draft the whole batch at once
+            self.proposer.after_step(so, sampled or {})
+            return
+        k = self.spec_config.num_speculative_tokens
+        for s in so.scheduled:
+            r = s.request
+            if r.status.finished or not r.output_token_ids or r.num_computed_tokens != r.num_tokens - 1:
+                continue
+            room = min(k, r.params.max_tokens - len(r.output_token_ids) - 1)
+            if room <= 0:
+                continue
+            if hasattr(self.proposer, "propose_for_request"):
+                drafts = self.proposer.propose_for_request(r, room)
+            else:
+                drafts = self.proposer.propose(r.all_token_ids)
+            r.spec_token_ids = [int(t) for t in drafts[:room]]
+        self.stats["draft_tokens"] = self.scheduler.num_draft_tokens
+        self.stats["accepted_tokens"] = self.scheduler.num_accepted_tokens
 
     def _release_all(self) -> None:
         for r in list(self.scheduler.running) + list(self.scheduler.waiting):
@@ -146,7 +175,7 @@ class LLM:
                  num_gpu_blocks: Optional[int] = None, enable_prefix_caching: bool = False,
                  enable_chunked_prefill: bool = True, enforce_eager: bool = False, device: Optional[str] = None,
                  load_format: str = "auto", seed: int = 0, tokenizer: Any = None, enable_sleep_mode: bool = False,
-                 additional_config: Optional[dict] = None):
+                 additional_config: Optional[dict] = None, speculative_config: Optional[dict] = None):
         overrides = {"seed": seed}
         if dtype is not None:
             overrides["dtype"] = dtype
@@ -165,7 +194,8 @@ class LLM:
             scheduler=SchedulerConfig(max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens,
                                       max_model_len=max_model_len, enable_chunked_prefill=enable_chunked_prefill),
             device=device, enforce_eager=enforce_eager, load_format=load_format,
-            additional_config=additional_config or {})
+            additional_config=dict(additional_config or {}, **({"speculative_config": speculative_config}
+                                                                if speculative_config else {})))
         self.config = cfg
         self.engine = LLMEngine(cfg, tokenizer or tok)
         self.tokenizer = self.engine.tokenizer

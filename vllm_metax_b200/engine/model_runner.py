@@ -103,10 +103,11 @@ class ModelRunner:
         self.seq_lens = self.d32[o:o + B]; o += B
         self.block_table = self.d32[o:o + B * MB].view(B, MB); o += B * MB
         self.prefill_qsl = self.d32[o:o + B + 1]
-        self.sampled = torch.zeros(B, dtype=torch.int64, device=dev)
-        self.sampled_host = torch.zeros(B, dtype=torch.int64, pin_memory=pin)
-        self.sample_idx = torch.zeros(B, dtype=torch.int64, device=dev)
-        self.sample_idx_host = torch.zeros(B, dtype=torch.int64, pin_memory=pin)
+        S = max(B, T)        # with draft tokens every fed position of a request is sampled
+        self.sampled = torch.zeros(S, dtype=torch.int64, device=dev)
+        self.sampled_host = torch.zeros(S, dtype=torch.int64, pin_memory=pin)
+        self.sample_idx = torch.zeros(S, dtype=torch.int64, device=dev)
+        self.sample_idx_host = torch.zeros(S, dtype=torch.int64, pin_memory=pin)
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
@@ -171,7 +172,10 @@ class ModelRunner:
                 pos[t] = p0
                 slots[t] = r.block_ids[p0 // bs] * bs + p0 % bs
             else:
-                toks = r.all_token_ids[p0:p0 + n] if r.output_token_ids else r.prompt_token_ids[p0:p0 + n]
+                if s.num_spec:
+                    toks = (r.all_token_ids + r.spec_token_ids[: s.num_spec])[p0:p0 + n]
+                else:
+                    toks = r.all_token_ids[p0:p0 + n] if r.output_token_ids else r.prompt_token_ids[p0:p0 + n]
                 ids[t:t + n] = toks
                 ar = np.arange(p0, p0 + n)
                 pos[t:t + n] = ar
@@ -185,8 +189,9 @@ class ModelRunner:
             max_q = max(max_q, n)
             max_seq = max(max_seq, p0 + n)
             if s.samples:
-                sample_rows.append(t - 1)
-                sample_reqs.append(r)
+                for row in range(t - 1 - s.num_spec, t):      # drafts: every fed position is verified
+                    sample_rows.append(row)
+                    sample_reqs.append(r)
         B = len(so.scheduled)
         nd = so.num_decode
         if pad_to > B:  # graph padding: dummy decodes that write nowhere and read block 0
@@ -304,6 +309,8 @@ class ModelRunner:
                 tokens_dev = self._sample(logits[:B], reqs)
         else:
             h = self._forward(md, T)
+            if getattr(self, "keep_hidden", False):
+                self.last_step = (h, md, T)      # draft proposers read the step's hidden states
             if isinstance(h, dict):  # non-last pipeline stage
                 return {}
             if n == 0:
@@ -319,7 +326,17 @@ class ModelRunner:
         self.sampled_host[:n].copy_(tokens_dev[:n], non_blocking=False)
         self.d2h_bytes += n * 8
         toks = self.sampled_host[:n].tolist()
-        return {r.request_id: tok for r, tok in zip(reqs, toks)}
+        out: dict = {}
+        for r, tok in zip(reqs, toks):
+            if r.request_id in out:                 # several verified positions of one request, in order
+                prev = out[r.request_id]
+                out[r.request_id] = (prev if isinstance(prev, list) else [prev]) + [tok]
+            else:
+                out[r.request_id] = tok
+        for s in so.scheduled:                      # a drafted request always reports a list
+            if s.num_spec and s.samples and not isinstance(out.get(s.request.request_id), list):
+                out[s.request.request_id] = [out[s.request.request_id]]
+        return out
 
     def _sample(self, logits: torch.Tensor, reqs) -> torch.Tensor:
         from .sampler import sample_batch

@@ -50,7 +50,7 @@ class Request:
 
     __slots__ = ("request_id", "prompt_token_ids", "params", "output_token_ids", "status", "block_ids",
                  "num_computed_tokens", "arrival_time", "first_token_time", "finish_time", "token_times",
-                 "eos_token_id", "num_cached_tokens", "logprobs", "prompt", "_hashes")
+                 "eos_token_id", "num_cached_tokens", "logprobs", "prompt", "_hashes", "spec_token_ids")
 
     def __init__(self, request_id: str, prompt_token_ids: list[int], params: SamplingParams,
                  eos_token_id: Optional[int] = None, prompt: Optional[str] = None,
@@ -71,6 +71,7 @@ class Request:
         self.logprobs: list = []
         self.prompt = prompt
         self._hashes: list[int] = []
+        self.spec_token_ids: list[int] = []     # draft tokens to verify in the next step (speculative decoding)
 
     @property
     def num_prompt_tokens(self) -> int:

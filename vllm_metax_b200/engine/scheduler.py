@@ -27,6 +27,7 @@ class ScheduledRequest:
     num_new_tokens: int            # tokens fed to the model this step
     start_pos: int                 # position of the first fed token
     samples: bool                  # whether logits of the last fed token are sampled
+    num_spec: int = 0              # trailing draft tokens among the fed ones (their logits are verified)
 
     @property
     def is_decode(self) -> bool:
@@ -56,6 +57,8 @@ class Scheduler:
         self.running: list[Request] = []
         self.paused = False
         self.num_preemptions = 0
+        self.num_draft_tokens = 0
+        self.num_accepted_tokens = 0
 
     # ------------------------------------------------------------------ queue ops
     def add_request(self, req: Request) -> None:
@@ -110,7 +113,10 @@ class Scheduler:
             if req not in self.running or budget <= 0:
                 continue
             remaining = req.num_tokens - req.num_computed_tokens
-            n = min(remaining, budget)
+            k = len(req.spec_token_ids) if remaining == 1 and req.output_token_ids else 0
+            if k and (budget < 1 + k or req.num_tokens + k > self.cfg.max_model_len):
+                req.spec_token_ids, k = [], 0       # no room to verify drafts this step
+            n = min(remaining, budget) + k
             if not self.cfg.enable_chunked_prefill and n < remaining:
                 continue
             ok = True
@@ -121,7 +127,7 @@ class Scheduler:
             if not ok:
                 continue
             self.kv.allocate(req, n)
-            out.scheduled.append(ScheduledRequest(req, n, req.num_computed_tokens, n == remaining))
+            out.scheduled.append(ScheduledRequest(req, n, req.num_computed_tokens, n == remaining + k, k))
             budget -= n
         # ---- admit waiting requests
         while self.waiting and budget > 0 and len(self.running) < self.cfg.max_num_seqs and not out.preempted:
@@ -157,10 +163,37 @@ class Scheduler:
         finished = []
         for s in out.scheduled:
             req = s.request
+            if s.num_spec:
+                # lossless verification of deterministic drafts: the target token of every fed position was
+                # sampled; drafts are kept while they equal it, the first mismatch (or the token after the last
+                # draft) is the step's own token.  KV of rejected positions is recomputed later.
+                targets = sampled[req.request_id]
+                drafts = req.spec_token_ids[: s.num_spec]
+                acc = 0
+                while acc < s.num_spec and drafts[acc] == targets[acc]:
+                    acc += 1
+                self.num_draft_tokens += s.num_spec
+                self.num_accepted_tokens += acc
+                req.spec_token_ids = []
+                req.num_computed_tokens += 1 + acc
+                self.kv.commit(req)
+                for tok in targets[: acc + 1]:
+                    req.append_token(int(tok), now)
+                    req.check_stop()
+                    if req.status.finished:
+                        break
+                if req.status.finished:
+                    req.num_computed_tokens = min(req.num_computed_tokens, req.num_tokens)
+                    req.finish_time = now
+                    self.running.remove(req)
+                    self.kv.free(req)
+                    finished.append(req)
+                continue
             req.num_computed_tokens += s.num_new_tokens
             self.kv.commit(req)
             if s.samples:
-                req.append_token(sampled[req.request_id], now)
+                tok = sampled[req.request_id]
+                req.append_token(int(tok[0]) if isinstance(tok, (list, tuple)) else tok, now)
                 req.check_stop()
                 if req.status.finished:
                     req.finish_time = now
