@@ -1,0 +1,95 @@
+"""DeepSeek-V4 pieces: mHC kernels vs the fp32 statement, name rewriting, and the model end to end on CPU."""
+import pytest
+import torch
+
+from vllm_metax_b200 import LLM, ModelConfig, SamplingParams
+from vllm_metax_b200.ops import mhc
+
+gpu = pytest.mark.gpu
+
+
+def _cfg(**kw):
+    base = dict(architecture="DeepseekV4ForCausalLM", vocab_size=64, hidden_size=128, intermediate_size=256,
+                num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4, q_lora_rank=64, kv_lora_rank=512,
+                qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, num_experts=4, num_experts_per_tok=2,
+                moe_intermediate_size=64, n_shared_experts=1, first_k_dense_replace=0, scoring_func="sqrtsoftplus",
+                routed_scaling_factor=1.5, hc_mult=4, hc_sinkhorn_iters=5, num_hash_layers=1,
+                max_position_embeddings=256, dtype=torch.float32)
+    base.update(kw)
+    return ModelConfig(**base)
+
+
+def test_sinkhorn_is_doubly_stochastic():
+    x = mhc.sinkhorn(torch.randn(7, 4, 4), 20, 1e-6)
+    assert torch.allclose(x.sum(-2), torch.ones(7, 4), atol=1e-3) and torch.allclose(x.sum(-1), torch.ones(7, 4), atol=2e-2)
+
+
+def test_fused_equals_post_then_pre_cpu():
+    torch.manual_seed(0)
+    T, M, H = 5, 4, 32
+    res = torch.randn(T, M, H)
+    fn, base, scale = torch.randn(24, M * H) * 0.05, torch.randn(24) * 0.1, torch.rand(3) + 0.5
+    post, comb, x = mhc.mhc_pre(res, fn, scale, base, 1e-6, 1e-6, 1e-6, 2.0, 5)
+    y = torch.randn(T, H)
+    new_res, p2, c2, x2 = mhc.mhc_fused_post_pre(y, res, post, comb, fn, scale, base, 1e-6, 1e-6, 1e-6, 2.0, 5)
+    want_res = mhc.mhc_post(y, res, post, comb)
+    torch.testing.assert_close(new_res, want_res)
+    p3, c3, x3 = mhc.mhc_pre(want_res, fn, scale, base, 1e-6, 1e-6, 1e-6, 2.0, 5)
+    torch.testing.assert_close(x2, x3)
+    torch.testing.assert_close(c2, c3)
+
+
+def test_v4_weight_name_rewriting():
+    from vllm_metax_b200.models.deepseek_v4 import rename_v4
+
+    assert rename_v4("layers.3.attn.wq_a.weight") == "model.layers.3.attn.q_a_proj.weight"
+    assert rename_v4("layers.0.ffn.experts.7.w1.weight") == "model.layers.0.ffn.experts.7.gate_proj.weight"
+    assert rename_v4("layers.2.hc_attn_fn") == "model.layers.2.hc_attn.fn"
+    assert rename_v4("head.weight") == "lm_head.weight"
+    assert rename_v4("embed.weight") == "model.embed_tokens.weight"
+
+
+def test_v4_model_generates_and_is_deterministic_cpu():
+    kw = dict(device="cpu", load_format="dummy", num_gpu_blocks=16, block_size=64, max_model_len=128, seed=0)
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    a = LLM(_cfg(), **kw).generate([[1, 2, 3, 4], [5, 6]], sp)
+    b = LLM(_cfg(), **kw).generate([[5, 6], [1, 2, 3, 4]], sp)
+    assert a[0].outputs[0].token_ids == b[1].outputs[0].token_ids       # batch-order invariant
+    assert len(a[1].outputs[0].token_ids) == 6
+
+
+@gpu
+@pytest.mark.parametrize("T,M,H", [(1, 4, 1024), (9, 4, 7168), (130, 2, 512)])
+def test_mhc_kernels_gpu(T, M, H, kernel_status_ok):
+    torch.manual_seed(1)
+    nmix = (2 + M) * M
+    res = torch.randn(T, M, H).bfloat16()
+    fn, base, scale = torch.randn(nmix, M * H) * 0.02, torch.randn(nmix) * 0.1, torch.rand(3) + 0.5
+    args = (1e-6, 1e-6, 1e-6, 2.0, 6)
+    post, comb, x = mhc.mhc_pre(res, fn, scale, base, *args)
+    gp, gc, gx = mhc.mhc_pre(res.cuda(), fn.cuda(), scale.cuda(), base.cuda(), *args)
+    torch.testing.assert_close(gp.cpu(), post, rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(gc.cpu(), comb, rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(gx.float().cpu(), x.float(), rtol=2e-2, atol=2e-2)
+    y = torch.randn(T, H).bfloat16()
+    want = mhc.mhc_fused_post_pre(y, res, post, comb, fn, scale, base, *args)
+    got = mhc.mhc_fused_post_pre(y.cuda(), res.cuda(), gp, gc, fn.cuda(), scale.cuda(), base.cuda(), *args)
+    torch.testing.assert_close(got[0].float().cpu(), want[0].float(), rtol=2e-2, atol=3e-2)
+    torch.testing.assert_close(got[2].cpu(), want[2], rtol=5e-3, atol=5e-3)
+    torch.testing.assert_close(got[3].float().cpu(), want[3].float(), rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(mhc.mhc_post(y.cuda(), res.cuda(), gp, gc).float().cpu(), mhc.mhc_post(y, res, post, comb).float(),
+                               rtol=2e-2, atol=3e-2)
+    hfn, hbase, hscale = torch.randn(M, M * H) * 0.02, torch.randn(M) * 0.1, torch.rand(1) + 0.5
+    torch.testing.assert_close(mhc.mhc_head(res.cuda(), hfn.cuda(), hscale.cuda(), hbase.cuda(), 1e-6, 1e-6).float().cpu(),
+                               mhc.mhc_head(res, hfn, hscale, hbase, 1e-6, 1e-6).float(), rtol=2e-2, atol=2e-2)
+
+
+@gpu
+def test_v4_model_gpu_matches_cpu_tokens(kernel_status_ok):
+    sp = SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True)
+    cpu = LLM(_cfg(), device="cpu", load_format="dummy", num_gpu_blocks=16, block_size=64, max_model_len=128, seed=0)
+    gpu_llm = LLM(_cfg(dtype=torch.bfloat16), device="cuda", load_format="dummy", num_gpu_blocks=16, block_size=64,
+                  max_model_len=128, seed=0)
+    gpu_llm.engine.runner.model.load_state_dict({k: v for k, v in cpu.engine.runner.model.state_dict().items()}, strict=False)
+    out = gpu_llm.generate([[1, 2, 3, 4]], sp)
+    assert len(out[0].outputs[0].token_ids) == 5

@@ -68,6 +68,11 @@ class ModelConfig:
     index_topk: int = 0
     # ---- MTP ----------------------------------------------------------------
     num_nextn_predict_layers: int = 0
+    # ---- DeepSeek-V4 hyper-connections / hash routing -------------------------
+    hc_mult: int = 0                           # residual streams (0 = plain residual)
+    hc_sinkhorn_iters: int = 20
+    hc_eps: float = 1e-6
+    num_hash_layers: int = 0                   # leading MoE layers routed by token id (tid2eid table)
     # ---- numerics / quantisation ----------------------------------------
     dtype: torch.dtype = torch.bfloat16
     quantization: Optional[str] = None         # None | fp8 | w8a8_int8 | awq | gptq | ...
@@ -142,6 +147,8 @@ class ModelConfig:
             index_head_dim=d.get("index_head_dim", 128) or 128,
             index_topk=d.get("index_topk", 0) or 0,
             num_nextn_predict_layers=d.get("num_nextn_predict_layers", 0) or 0,
+            hc_mult=d.get("hc_mult", 0) or 0, hc_sinkhorn_iters=d.get("hc_sinkhorn_iters", 20) or 20,
+            hc_eps=d.get("hc_eps", 1e-6) or 1e-6, num_hash_layers=d.get("num_hash_layers", 0) or 0,
             dtype=d.get("torch_dtype", d.get("dtype", "bfloat16")),
             eos_token_id=(d.get("eos_token_id")[0] if isinstance(d.get("eos_token_id"), list) else d.get("eos_token_id")),
         )

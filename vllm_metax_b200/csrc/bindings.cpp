@@ -746,6 +746,42 @@ void selective_scan(Tensor& out, const Tensor& u, const Tensor& delta, const Ten
   TORCH_CHECK(b200::selective_scan_fwd(p, dt, cur_stream()) == 0, "selective_scan: unsupported dstate / dim");
 }
 
+// mHC pre (optionally fused with the previous sub-layer's post).  residual [T, M, H]; fn fp32 [mix, M*H].
+void mhc_pre(Tensor& x_out, const optional<Tensor>& post_out, const optional<Tensor>& comb_out, const Tensor& residual,
+             const optional<Tensor>& residual_out, const optional<Tensor>& y, const optional<Tensor>& post_in,
+             const optional<Tensor>& comb_in, const Tensor& fn, const Tensor& scale, const Tensor& base, double rms_eps,
+             double pre_eps, double sinkhorn_eps, double post_mult, int64_t iters, bool head) {
+  TORCH_CHECK(residual.dim() == 3 && residual.is_contiguous() && fn.scalar_type() == at::kFloat && fn.is_contiguous());
+  b200::MhcParams p{};
+  p.T = residual.size(0); p.M = residual.size(1); p.H = residual.size(2);
+  const int nmix = head ? p.M : 2 * p.M + p.M * p.M;
+  TORCH_CHECK(fn.size(0) == nmix && fn.size(1) == (int64_t)p.M * p.H && base.numel() == nmix && scale.numel() >= (head ? 1 : 3));
+  TORCH_CHECK(scale.scalar_type() == at::kFloat && base.scalar_type() == at::kFloat && x_out.is_contiguous());
+  const bool fused = y.has_value();
+  if (fused) TORCH_CHECK(residual_out.has_value() && post_in.has_value() && comb_in.has_value() && y->is_contiguous() &&
+                         residual_out->is_contiguous() && residual_out->data_ptr() != residual.data_ptr());
+  if (!head) TORCH_CHECK(post_out.has_value() && comb_out.has_value());
+  p.residual = residual.data_ptr();
+  p.residual_out = fused ? residual_out->data_ptr() : nullptr;
+  p.y = fused ? y->data_ptr() : nullptr;
+  p.post_in = ptr<float>(post_in); p.comb_in = ptr<float>(comb_in);
+  p.fn = fn.data_ptr<float>(); p.scale = scale.data_ptr<float>(); p.base = base.data_ptr<float>();
+  p.post_out = ptr<float>(post_out); p.comb_out = ptr<float>(comb_out);
+  p.x_out = x_out.data_ptr();
+  p.iters = iters; p.head = head;
+  p.rms_eps = rms_eps; p.pre_eps = pre_eps; p.sinkhorn_eps = sinkhorn_eps; p.post_mult = post_mult;
+  const c10::cuda::CUDAGuard guard(residual.device());
+  TORCH_CHECK(b200::mhc_pre(p, fused, dtype16(residual), cur_stream()) == 0, "mhc_pre: unsupported stream count");
+}
+
+void mhc_post(Tensor& out, const Tensor& y, const Tensor& residual, const Tensor& post, const Tensor& comb) {
+  TORCH_CHECK(residual.dim() == 3 && residual.is_contiguous() && y.is_contiguous() && out.is_contiguous());
+  TORCH_CHECK(post.scalar_type() == at::kFloat && comb.scalar_type() == at::kFloat && residual.size(1) <= 4);
+  const c10::cuda::CUDAGuard guard(residual.device());
+  b200::mhc_post(out.data_ptr(), y.data_ptr(), residual.data_ptr(), post.data_ptr<float>(), comb.data_ptr<float>(),
+                 residual.size(0), residual.size(1), residual.size(2), dtype16(residual), cur_stream());
+}
+
 // ptrs: int64 CPU tensor [3, tp] = x_shard, xready, done (per owning rank)
 void ag_gemm(Tensor& out, const Tensor& w, const optional<Tensor>& bias, const Tensor& ptrs, Tensor& gathered,
              Tensor& ready, Tensor& sync, int64_t tp, int64_t rank, int64_t rows_per_rank, int64_t wait_cycles) {
@@ -845,6 +881,8 @@ TORCH_LIBRARY(b200, m) {
   m.def("moe_a2a_dispatch(Tensor x, Tensor topk_ids, Tensor ptrs, int ep, int rank, int experts_per_rank, int cap, bool quant, Tensor(a!) local_sync, int wait_cycles) -> ()", &moe_a2a_dispatch);
   m.def("moe_a2a_combine(Tensor(a!) out, Tensor y, Tensor inv_pos, Tensor topk_w, Tensor topk_ids, Tensor? shared_out, Tensor ptrs, int ep, int rank, int experts_per_rank, int cap, Tensor(b!) local_sync, int wait_cycles) -> ()", &moe_a2a_combine);
   m.def("ag_gemm(Tensor(a!) out, Tensor w, Tensor? bias, Tensor ptrs, Tensor(b!) gathered, Tensor(c!) ready, Tensor(d!) sync, int tp, int rank, int rows_per_rank, int wait_cycles) -> ()", &ag_gemm);
+  m.def("mhc_pre(Tensor(a!) x_out, Tensor(b!)? post_out, Tensor(c!)? comb_out, Tensor residual, Tensor(d!)? residual_out, Tensor? y, Tensor? post_in, Tensor? comb_in, Tensor fn, Tensor scale, Tensor base, float rms_eps, float pre_eps, float sinkhorn_eps, float post_mult, int iters, bool head) -> ()", &mhc_pre);
+  m.def("mhc_post(Tensor(a!) out, Tensor y, Tensor residual, Tensor post, Tensor comb) -> ()", &mhc_post);
   m.def("small_gemm(Tensor(a!) out, Tensor a, Tensor w, Tensor? bias) -> ()", &small_gemm);
   m.def("fused_qk_norm_rope(Tensor(a!) qkv, Tensor q_weight, Tensor k_weight, Tensor cos_sin, Tensor positions, int hq, int hk, int hv, int head_dim, bool is_neox, float eps, bool gemma) -> ()", &fused_qk_norm_rope);
   m.def("mla_rope_and_cache(Tensor(a!) q_pe, Tensor(b!) k_pe, Tensor kv_c, Tensor(c!) cache, Tensor cos_sin, Tensor positions, Tensor slot_mapping, bool is_neox) -> ()", &mla_rope_and_cache);

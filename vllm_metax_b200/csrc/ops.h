@@ -190,6 +190,25 @@ struct ScanParams {
   int batch, dim, dstate, groups, seqlen, total_tokens, softplus, pad_slot;
 };
 int selective_scan_fwd(const ScanParams& p, int dtype, cudaStream_t stream);
+// ---- mhc.cu
+struct MhcParams {
+  const void* residual;   // [T, M, H] (input streams)
+  void* residual_out;     // fused: new streams [T, M, H] (a different buffer than residual)
+  const void* y;          // fused: sub-layer output [T, H]
+  const float* post_in;   // fused: [T, M]
+  const float* comb_in;   // fused: [T, M, M]
+  const float* fn;        // [mix, M*H]
+  const float* scale;     // [3] (head: [1])
+  const float* base;      // [mix]
+  float* post_out;        // [T, M]
+  float* comb_out;        // [T, M, M]
+  void* x_out;            // [T, H]
+  int T, M, H, iters, head;
+  float rms_eps, pre_eps, sinkhorn_eps, post_mult;
+};
+int mhc_pre(const MhcParams& p, int fused, int dtype, cudaStream_t stream);
+void mhc_post(void* out, const void* y, const void* res, const float* post, const float* comb, int tokens, int M, int H,
+              int dtype, cudaStream_t stream);
 // ---- comm_ag_gemm.cu
 int ag_gemm_copiers(int tp, int rows_per_rank);
 int ag_gemm(const AgGemmParams& p, const void* W, int ldw, void* C, const void* bias, int dtype, cudaStream_t stream);
