@@ -87,8 +87,8 @@ def test_mhc_kernels_gpu(T, M, H, kernel_status_ok):
 @gpu
 def test_v4_model_gpu_matches_cpu_tokens(kernel_status_ok):
     sp = SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True)
-    cpu = LLM(_cfg(), device="cpu", load_format="dummy", num_gpu_blocks=16, block_size=64, max_model_len=128, seed=0)
-    gpu_llm = LLM(_cfg(dtype=torch.bfloat16), device="cuda", load_format="dummy", num_gpu_blocks=16, block_size=64,
+    cpu = LLM(_cfg(num_experts=8), device="cpu", load_format="dummy", num_gpu_blocks=16, block_size=64, max_model_len=128, seed=0)
+    gpu_llm = LLM(_cfg(num_experts=8, dtype=torch.bfloat16), device="cuda", load_format="dummy", num_gpu_blocks=16, block_size=64,
                   max_model_len=128, seed=0)
     gpu_llm.engine.runner.model.load_state_dict({k: v for k, v in cpu.engine.runner.model.state_dict().items()}, strict=False)
     out = gpu_llm.generate([[1, 2, 3, 4]], sp)

@@ -77,6 +77,21 @@ void gemm(Tensor& out, const Tensor& a, const Tensor& w, const optional<Tensor>&
                        w.stride(0), out.stride(0), ldr, dtype16(a), cur_stream(), status_ptr(a), (int)epi);
     return;
   }
+  // cluster split-K for medium M with too few tiles to cover the GPU (force_bn 1002 / 1004 pins the split count)
+  static const bool splitk_default = [] {
+    const char* e = std::getenv("B200_GEMM_SPLITK");
+    return e == nullptr || std::atoi(e) != 0;
+  }();
+  static int sms = 0;
+  if (sms == 0) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, a.get_device());
+  int splits = 1;
+  if (force_bn == 1002 || force_bn == 1004) splits = (int)force_bn - 1000;
+  else if (force_bn == 0 && splitk_default && M > 64 && M <= 1024) splits = b200::gemm_splitk_choice(M, N, K, sms);
+  if (splits > 1) {
+    b200::gemm_tn_splitk(a.data_ptr(), w.data_ptr(), out.data_ptr(), ptr(bias), ptr(residual), M, N, K, a.stride(0),
+                         w.stride(0), out.stride(0), ldr, dtype16(a), cur_stream(), status_ptr(a), (int)epi, splits);
+    return;
+  }
   b200::gemm_tn(a.data_ptr(), w.data_ptr(), out.data_ptr(), ptr(bias), ptr(residual), M, N, K, a.stride(0),
                 w.stride(0), out.stride(0), ldr, dtype16(a), cur_stream(), status_ptr(a), (int)force_bn, (int)epi);
 }

@@ -70,6 +70,11 @@ void gemm_tn(const void* A, const void* W, void* C, const void* bias, const void
              int lda, int ldw, int ldc, int ldr, int dtype, cudaStream_t stream, void* status, int force_bn, int epi);
 void gemm_tn_pair(const void* A, const void* W, void* C, const void* bias, const void* residual, int M, int N, int K,
                   int lda, int ldw, int ldc, int ldr, int dtype, cudaStream_t stream, void* status, int epi);
+// ---- gemm_splitk_tcgen05.cu
+int gemm_splitk_choice(int M, int N, int K, int sms);
+void gemm_tn_splitk(const void* A, const void* W, void* C, const void* bias, const void* residual, int M, int N, int K,
+                    int lda, int ldw, int ldc, int ldr, int dtype, cudaStream_t stream, void* status, int epi,
+                    int splits);
 // ---- norm.cu
 void rms_norm(void* out, void* x, void* residual, const void* weight, float eps, int tokens, int hidden,
               int64_t x_stride, int64_t out_stride, int dtype, int mode, cudaStream_t stream);
