@@ -797,6 +797,15 @@ void mhc_post(Tensor& out, const Tensor& y, const Tensor& residual, const Tensor
                  residual.size(0), residual.size(1), residual.size(2), dtype16(residual), cur_stream());
 }
 
+// copy `src` (a local tensor) to the raw device address `dst_ptr` (typically a peer-mapped buffer)
+void p2p_copy(int64_t dst_ptr, const Tensor& src, int64_t ctas, int64_t mode) {
+  TORCH_CHECK(src.is_contiguous() && ctas >= 1 && ctas <= 1024);
+  const size_t n = (size_t)src.numel() * src.element_size();
+  TORCH_CHECK(n % (mode == 0 ? 16 : 16384) == 0, "p2p_copy: size granularity");
+  const c10::cuda::CUDAGuard guard(src.device());
+  b200::p2p_copy(reinterpret_cast<void*>(dst_ptr), src.data_ptr(), n, (int)ctas, (int)mode, status_ptr(src), cur_stream());
+}
+
 // ptrs: int64 CPU tensor [3, tp] = x_shard, xready, done (per owning rank)
 void ag_gemm(Tensor& out, const Tensor& w, const optional<Tensor>& bias, const Tensor& ptrs, Tensor& gathered,
              Tensor& ready, Tensor& sync, int64_t tp, int64_t rank, int64_t rows_per_rank, int64_t wait_cycles) {
@@ -906,6 +915,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("gather_mla_cache(Tensor(a!) dst, Tensor cache, Tensor block_table, Tensor cu_seq_lens, Tensor? seq_starts) -> ()", &gather_mla_cache);
   m.def("gather_indexer_k(Tensor(a!) dst_k, Tensor(b!) dst_s, Tensor cache, Tensor block_table, Tensor cu_seq_lens, int block_size) -> ()", &gather_indexer_k);
   m.def("selective_scan(Tensor(a!) out, Tensor u, Tensor delta, Tensor A, Tensor B, Tensor C, Tensor? D, Tensor? z, Tensor? delta_bias, bool delta_softplus, Tensor(b!) state, Tensor? query_start_loc, Tensor? cache_indices, Tensor? has_initial_state, int pad_slot) -> ()", &selective_scan);
+  m.def("p2p_copy(int dst_ptr, Tensor src, int ctas, int mode) -> ()", &p2p_copy);
   m.def("gather_rows(Tensor(a!) dst, Tensor src, Tensor idx, Tensor count) -> ()", &gather_rows);
   m.def("get_status(int device) -> Tensor", &get_status);
   m.def("topk_gating(Tensor(a!) weights, Tensor(b!) ids, Tensor gating, Tensor? bias, int mode, bool renorm, float scale) -> ()", &topk_gating);

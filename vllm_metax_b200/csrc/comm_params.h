@@ -25,6 +25,7 @@ struct FusedArParams {
   const void* norm_weight;        // [H]
   float eps;
   int add_residual;               // 0: residual_out = reduced sum (first use), 1: residual += sum
+  int rows_per_gap;               // rows an epilogue warp may reduce between two tiles (set by the launcher)
   uint32_t* local_sync;           // [4] local scratch: [0] CTAs done, [1] last finished epoch (the call's
                                   // epoch is that + 1; its low bit selects the counter set)
   long long wait_cycles;          // budget of every flag wait

@@ -214,6 +214,8 @@ struct MhcParams {
 int mhc_pre(const MhcParams& p, int fused, int dtype, cudaStream_t stream);
 void mhc_post(void* out, const void* y, const void* res, const float* post, const float* comb, int tokens, int M, int H,
               int dtype, cudaStream_t stream);
+// ---- p2p_copy.cu
+void p2p_copy(void* dst, const void* src, size_t nbytes, int ctas, int mode, void* status, cudaStream_t stream);
 // ---- comm_ag_gemm.cu
 int ag_gemm_copiers(int tp, int rows_per_rank);
 int ag_gemm(const AgGemmParams& p, const void* W, int ldw, void* C, const void* bias, int dtype, cudaStream_t stream);

@@ -305,7 +305,10 @@ class WNA16MoEMethod:
 
     def apply(self, layer, x, topk_weights, topk_ids, shared_out=None):
         T, topk = x.shape[0], topk_ids.shape[1]
-        tile = ops.wna16_token_tile(T * topk // max(layer.num_local, 1))
+        from ..layers.moe_configs import try_get_optimal_moe_config
+
+        # tuned (or heuristic) row-block size: small per-expert batches waste less of a tile
+        tile = int(try_get_optimal_moe_config(T, layer.num_local, self.inter, self.hidden, topk, "w4a16")["token_tile"])
         sorted_ids, block_expert, total, inv = ops.moe_align_block_size(topk_ids, tile, layer.num_local,
                                                                         layer.expert_map, want_inverse=True)
         a = ops.moe_gather(x, sorted_ids, total, topk)
