@@ -216,3 +216,67 @@ def _ag_gemm_worker(rank, world):
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_allgather_gemm_2gpu():
     _launch(_ag_gemm_worker, 2)
+
+
+def _custom_ar_worker(rank, world):
+    from vllm_metax_b200 import _custom_ops as ops
+    from vllm_metax_b200.parallel import state as ps
+    from vllm_metax_b200.parallel.custom_allreduce import CrossRankRMSNorm, CustomAllReduce
+
+    ps.init_distributed(tensor_parallel_size=world)
+    dev = torch.device("cuda", rank)
+    g = ps.get_tp_group()
+    car = CustomAllReduce(g, dev, max_bytes=4 << 20)
+    gen = torch.Generator().manual_seed(1)
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        for n in (8, 4096, 100_000 * 8, (4 << 20) // 4):
+            for mode in (1, 2, 0):
+                parts = [torch.randn(n, generator=gen).to(dtype) for _ in range(world)]
+                want = sum(p.float() for p in parts)
+                x = parts[rank].to(dev)
+                out = torch.empty_like(x)
+                car.all_reduce(x, out=out, mode=mode)
+                torch.cuda.synchronize()
+                ops.check_kernel_status(rank)
+                tol = 1e-5 if dtype == torch.float32 else 2e-2
+                torch.testing.assert_close(out.float().cpu(), want.to(dtype).float(), rtol=tol, atol=tol)
+                car.all_reduce(x, mode=mode)                      # in place
+                torch.cuda.synchronize()
+                assert torch.equal(x, out)
+    # through the group, including a size that must stay on NCCL
+    car.attach()
+    for n in (1024, (8 << 20)):
+        parts = [torch.randn(n, generator=gen).to(torch.bfloat16) for _ in range(world)]
+        x = parts[rank].to(dev)
+        g.all_reduce(x)
+        torch.cuda.synchronize()
+        torch.testing.assert_close(x.float().cpu(), sum(p.float() for p in parts), rtol=2e-2, atol=2e-2)
+    car.close()
+
+    # RMSNorm over a hidden dimension split across ranks; token counts go down and up again so that stale slots of
+    # an earlier, larger call would be noticed
+    rms = CrossRankRMSNorm(g, dev, max_tokens=512)
+    Hq, Hk = 768, 128
+    for T in (300, 7, 512, 1, 300, 300):
+        qs = [torch.randn(T, Hq, generator=gen).to(torch.bfloat16) for _ in range(world)]
+        ks = [torch.randn(T, Hk, generator=gen).to(torch.bfloat16) for _ in range(world)]
+        wq = torch.randn(world, Hq, generator=gen).to(torch.bfloat16)
+        wk = torch.randn(world, Hk, generator=gen).to(torch.bfloat16)
+        oq, ok_ = rms(qs[rank].to(dev), wq[rank].to(dev), 1e-6, ks[rank].to(dev), wk[rank].to(dev))
+        torch.cuda.synchronize()
+        ops.check_kernel_status(rank)
+        for o, xs, w, H in ((oq, qs, wq, Hq), (ok_, ks, wk, Hk)):
+            full = torch.cat([x.float() for x in xs], dim=1)
+            inv = torch.rsqrt(full.pow(2).mean(-1, keepdim=True) + 1e-6)
+            want = xs[rank].float() * inv * w[rank].float()
+            torch.testing.assert_close(o.float().cpu(), want, rtol=2e-2, atol=2e-2)
+        o1, none = rms(qs[rank].to(dev), wq[rank].to(dev), 1e-6)     # single-tensor form
+        assert none is None
+        torch.cuda.synchronize()
+        torch.testing.assert_close(o1.float(), oq.float(), rtol=0, atol=0)
+    rms.close()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_custom_allreduce_and_reduce_rms_2gpu():
+    _launch(_custom_ar_worker, 2)

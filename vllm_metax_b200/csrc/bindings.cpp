@@ -806,6 +806,65 @@ void p2p_copy(int64_t dst_ptr, const Tensor& src, int64_t ctas, int64_t mode) {
   b200::p2p_copy(reinterpret_cast<void*>(dst_ptr), src.data_ptr(), n, (int)ctas, (int)mode, status_ptr(src), cur_stream());
 }
 
+// ptrs: int64 CPU tensor [4, tp] = recv, gather, flag1, flag2 (per owning rank)
+void custom_allreduce(Tensor& out, const Tensor& inp, const Tensor& ptrs, int64_t tp, int64_t rank, int64_t cap_bytes,
+                      int64_t max_ctas, Tensor& local_sync, int64_t mode, int64_t wait_cycles) {
+  TORCH_CHECK(inp.is_contiguous() && out.is_contiguous() && inp.scalar_type() == out.scalar_type() &&
+              inp.numel() == out.numel());
+  TORCH_CHECK(tp >= 1 && tp <= b200::kMaxRanks && ptrs.dim() == 2 && ptrs.size(0) == 4 && ptrs.size(1) >= tp);
+  TORCH_CHECK(!ptrs.is_cuda() && ptrs.scalar_type() == at::kLong && local_sync.numel() >= 2);
+  b200::CustomArParams p{};
+  p.tp = tp; p.rank = rank; p.n_bytes = (long long)inp.numel() * inp.element_size(); p.cap_bytes = cap_bytes;
+  p.max_ctas = max_ctas;
+  const int64_t* pp = ptrs.data_ptr<int64_t>();
+  const int64_t st = ptrs.stride(0);
+  for (int r = 0; r < tp; ++r) {
+    p.recv[r] = reinterpret_cast<void*>(pp[0 * st + r]);
+    p.gather[r] = reinterpret_cast<void*>(pp[1 * st + r]);
+    p.flag1[r] = reinterpret_cast<uint32_t*>(pp[2 * st + r]);
+    p.flag2[r] = reinterpret_cast<uint32_t*>(pp[3 * st + r]);
+  }
+  p.local_sync = reinterpret_cast<uint32_t*>(local_sync.data_ptr());
+  p.wait_cycles = wait_cycles;
+  p.status = reinterpret_cast<b200::StatusWord*>(status_ptr(inp));
+  const int dt = inp.scalar_type() == at::kBFloat16 ? 0 : inp.scalar_type() == at::kHalf ? 1
+               : inp.scalar_type() == at::kFloat ? 2 : -1;
+  const c10::cuda::CUDAGuard guard(inp.device());
+  const int rc = b200::custom_allreduce(p, inp.data_ptr(), out.data_ptr(), dt, (int)mode, cur_stream());
+  TORCH_CHECK(rc == 0, "custom_allreduce: payload must be bf16/fp16/fp32, a multiple of 16 bytes and fit the buffers");
+}
+
+// slots_ptrs: int64 CPU tensor [tp]; x / w / out: one or two tensors (q and k) normalised over the hidden
+// dimension of ALL ranks
+void reduce_rms(Tensor& out0, const Tensor& x0, const Tensor& w0, const optional<Tensor>& out1,
+                const optional<Tensor>& x1, const optional<Tensor>& w1, double eps, const Tensor& slots_ptrs,
+                int64_t tp, int64_t rank, int64_t t_cap, Tensor& local_sync, int64_t wait_cycles) {
+  TORCH_CHECK(x0.dim() == 2 && x0.stride(1) == 1 && out0.dim() == 2 && out0.stride(1) == 1 &&
+              out0.stride(0) == x0.stride(0) && w0.numel() == x0.size(1) && w0.scalar_type() == x0.scalar_type());
+  TORCH_CHECK(tp >= 1 && tp <= b200::kMaxRanks && !slots_ptrs.is_cuda() && slots_ptrs.numel() >= tp &&
+              local_sync.numel() >= 5);
+  b200::ReduceRmsParams p{};
+  p.tp = tp; p.rank = rank; p.T = x0.size(0); p.n_tensors = x1.has_value() ? 2 : 1;
+  p.x[0] = x0.data_ptr(); p.w[0] = w0.data_ptr(); p.out[0] = out0.data_ptr(); p.H[0] = x0.size(1); p.ld[0] = x0.stride(0);
+  if (x1.has_value()) {
+    TORCH_CHECK(out1.has_value() && w1.has_value() && x1->dim() == 2 && x1->size(0) == x0.size(0) && x1->stride(1) == 1 &&
+                out1->stride(0) == x1->stride(0) && out1->stride(1) == 1 && w1->numel() == x1->size(1) &&
+                x1->scalar_type() == x0.scalar_type() && w1->scalar_type() == x0.scalar_type());
+    p.x[1] = x1->data_ptr(); p.w[1] = w1->data_ptr(); p.out[1] = out1->data_ptr(); p.H[1] = x1->size(1);
+    p.ld[1] = x1->stride(0);
+  }
+  p.eps = (float)eps;
+  const int64_t* pp = slots_ptrs.data_ptr<int64_t>();
+  for (int r = 0; r < tp; ++r) p.slots[r] = reinterpret_cast<float*>(pp[r]);
+  p.t_cap = t_cap;
+  p.local_sync = reinterpret_cast<uint32_t*>(local_sync.data_ptr());
+  p.wait_cycles = wait_cycles;
+  p.status = reinterpret_cast<b200::StatusWord*>(status_ptr(x0));
+  const c10::cuda::CUDAGuard guard(x0.device());
+  const int rc = b200::reduce_rms(p, dtype16(x0), cur_stream());
+  TORCH_CHECK(rc == 0, "reduce_rms: widths and pitches must be multiples of 8 and T must fit the slot arrays");
+}
+
 // ptrs: int64 CPU tensor [3, tp] = x_shard, xready, done (per owning rank)
 void ag_gemm(Tensor& out, const Tensor& w, const optional<Tensor>& bias, const Tensor& ptrs, Tensor& gathered,
              Tensor& ready, Tensor& sync, int64_t tp, int64_t rank, int64_t rows_per_rank, int64_t wait_cycles) {
@@ -904,6 +963,8 @@ void gather_rows(Tensor& dst, const Tensor& src, const Tensor& idx, const Tensor
 TORCH_LIBRARY(b200, m) {
   m.def("moe_a2a_dispatch(Tensor x, Tensor topk_ids, Tensor ptrs, int ep, int rank, int experts_per_rank, int cap, bool quant, Tensor(a!) local_sync, int wait_cycles) -> ()", &moe_a2a_dispatch);
   m.def("moe_a2a_combine(Tensor(a!) out, Tensor y, Tensor inv_pos, Tensor topk_w, Tensor topk_ids, Tensor? shared_out, Tensor ptrs, int ep, int rank, int experts_per_rank, int cap, Tensor(b!) local_sync, int wait_cycles) -> ()", &moe_a2a_combine);
+  m.def("custom_allreduce(Tensor(a!) out, Tensor inp, Tensor ptrs, int tp, int rank, int cap_bytes, int max_ctas, Tensor(b!) local_sync, int mode, int wait_cycles) -> ()", &custom_allreduce);
+  m.def("reduce_rms(Tensor(a!) out0, Tensor x0, Tensor w0, Tensor(b!)? out1, Tensor? x1, Tensor? w1, float eps, Tensor slots_ptrs, int tp, int rank, int t_cap, Tensor(c!) local_sync, int wait_cycles) -> ()", &reduce_rms);
   m.def("ag_gemm(Tensor(a!) out, Tensor w, Tensor? bias, Tensor ptrs, Tensor(b!) gathered, Tensor(c!) ready, Tensor(d!) sync, int tp, int rank, int rows_per_rank, int wait_cycles) -> ()", &ag_gemm);
   m.def("mhc_pre(Tensor(a!) x_out, Tensor(b!)? post_out, Tensor(c!)? comb_out, Tensor residual, Tensor(d!)? residual_out, Tensor? y, Tensor? post_in, Tensor? comb_in, Tensor fn, Tensor scale, Tensor base, float rms_eps, float pre_eps, float sinkhorn_eps, float post_mult, int iters, bool head) -> ()", &mhc_pre);
   m.def("mhc_post(Tensor(a!) out, Tensor y, Tensor residual, Tensor post, Tensor comb) -> ()", &mhc_post);

@@ -40,7 +40,7 @@ using namespace ptx;
 constexpr int kArBM = 128, kArBN = 256, kArBK = 64, kArStages = 4;   // 48 KB per stage
 
 struct ArPushMaps {
-  CUtensorMap recv[kMaxRanks];   // this rank's slice of every owner's receive buffer: [rows_cap, H], box 128 x 64, SW128
+  CUtensorMap recv[kMaxRanks];   // every owner's receive buffer as [tp * rows_cap, H] rows, box 128 x 64, SW128
 };
 
 struct ArSmem {
@@ -72,6 +72,10 @@ gemm_ar_norm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int num_n = ceil_div(p.H, kArBN);
   const int num_tiles = num_rb * num_n;
   const int num_k = ceil_div(p.K, kArBK);
+  // Split-K for small token counts: a work unit is (tile, K range); every range lands in a receive slot of its
+  // own, so the owner's row reduction sums tp * ksplit partials instead of tp.
+  const int num_units = num_tiles * p.ksplit;
+  const int k_per = ceil_div(num_k, p.ksplit);
   constexpr uint32_t kTmemCols = 2 * kArBN;
   // The call's epoch lives in device memory (local_sync[1] holds the last finished epoch) so that a
   // CUDA-graph replay of this launch still advances it; every rank issues the same call sequence.
@@ -107,11 +111,13 @@ gemm_ar_norm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+        const int tile = unit / p.ksplit, ks = unit - tile * p.ksplit;
         const int rb = tile / num_n, tn = tile % num_n;     // row-block-major, the same order on every rank
-        for (int kb = 0; kb < num_k; ++kb) {
+        const int kb1 = min(num_k, (ks + 1) * k_per);
+        for (int kb = ks * k_per; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
-            report_status(p.status, kWaitTimeout, 70, tile, kb);
+            report_status(p.status, kWaitTimeout, 70, unit, kb);
             ok = false;
             break;
           }
@@ -131,17 +137,18 @@ gemm_ar_norm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int stage = 0, it = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++it) {
         const int acc = it & 1;
         if (!mbar_wait(&tmem_empty[acc], ((it >> 1) & 1) ^ 1)) {
-          report_status(p.status, kWaitTimeout, 71, tile, acc);
+          report_status(p.status, kWaitTimeout, 71, unit, acc);
           break;
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * kArBN;
-        for (int kb = 0; kb < num_k; ++kb) {
+        const int ks = unit % p.ksplit, kb0 = ks * k_per, kb1 = min(num_k, kb0 + k_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase)) {
-            report_status(p.status, kWaitTimeout, 72, tile, kb);
+            report_status(p.status, kWaitTimeout, 72, unit, kb);
             ok = false;
             break;
           }
@@ -150,7 +157,7 @@ gemm_ar_norm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const uint64_t da = make_smem_desc_sw128(sa), db = make_smem_desc_sw128(sa + L::kABytes);
 #pragma unroll
           for (int k = 0; k < kArBK / 16; ++k)
-            umma_f16_ss(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_ss(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb != kb0 || k != 0) ? 1u : 0u);
           umma_commit(&empty_bar[stage]);
           if (++stage == kArStages) { stage = 0; phase ^= 1; }
         }
@@ -163,7 +170,8 @@ gemm_ar_norm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int etid = threadIdx.x - 64;  // 0..127 within the epilogue group
     const int my_row0 = p.rank * p.rows_per_rank;
     const int my_rows = max(0, min(p.rows_per_rank, p.T - my_row0));
-    const uint32_t expected = (uint32_t)(p.tp * num_n);
+    const uint32_t expected = (uint32_t)(p.tp * num_n * p.ksplit);
+    const int num_src = p.tp * p.ksplit;
     const T* recv_mine = reinterpret_cast<const T*>(p.recv[p.rank]);
     T* residual = reinterpret_cast<T*>(p.residual);
     const T* nw = reinterpret_cast<const T*>(p.norm_weight);
@@ -209,20 +217,20 @@ gemm_ar_norm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
             for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
           }
-          for (int s0 = 0; s0 < p.tp; s0 += 4) {
+          for (int s0 = 0; s0 < num_src; s0 += 4) {
             uint4 raw[4][4];
 #pragma unroll
             for (int q = 0; q < 4; ++q)
 #pragma unroll
               for (int j = 0; j < 4; ++j)
-                if (s0 + q < p.tp && live[j])
-                  raw[q][j] = __ldcg(reinterpret_cast<const uint4*>(recv_mine + ((size_t)(s0 + q) * p.rows_cap + lr) * p.H) +
+                if (s0 + q < num_src && live[j])
+                  raw[q][j] = __ldcg(reinterpret_cast<const uint4*>(recv_mine + ((size_t)(s0 + q) * p.slot_rows + lr) * p.H) +
                                      v0 + j * 128 + etid);
 #pragma unroll
             for (int q = 0; q < 4; ++q)
 #pragma unroll
               for (int j = 0; j < 4; ++j)
-                if (s0 + q < p.tp && live[j]) {
+                if (s0 + q < num_src && live[j]) {
                   float f[8];
                   unpack8<T>(raw[q][j], f);
 #pragma unroll
@@ -302,11 +310,13 @@ gemm_ar_norm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
     int it = 0;
     int prev_rb = -1, prev_owner = 0;   // TMA push: the tile whose arrival is not yet published
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+    for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, ++it) {
+      const int tile = unit / p.ksplit;
+      const int slot = p.rank * p.ksplit + (unit - tile * p.ksplit);   // receive slot of this (source, K range)
       const int rb = tile / num_n, tn = tile % num_n;
       const int acc = it & 1;
       if (!mbar_wait(&tmem_full[acc], (it >> 1) & 1)) {
-        report_status(p.status, kWaitTimeout, 73, tile, acc);
+        report_status(p.status, kWaitTimeout, 73, unit, acc);
         break;
       }
       tc_fence_after_sync();
@@ -315,7 +325,7 @@ gemm_ar_norm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const int row = quarter * 32 + lane;                   // row inside the tile
         uint8_t* stg = smem + L::kPushStage;
         const int owner = (rb * kArBM) / p.rows_per_rank;
-        const int lr0 = rb * kArBM - owner * p.rows_per_rank;
+        const int lr0 = slot * p.slot_rows + rb * kArBM - owner * p.rows_per_rank;   // row in the owner's buffer
 #pragma unroll 1
         for (int h = 0; h < kArBN / 128; ++h) {                // the tile leaves in 128-column halves
           if (etid == 0) tma_store_wait_read<0>();              // earlier stores have read the stage
@@ -362,7 +372,7 @@ gemm_ar_norm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const bool row_ok = gr < p.T;
         const int owner = row_ok ? gr / p.rows_per_rank : 0;
         const int lr = gr - owner * p.rows_per_rank;
-        T* dst_row = reinterpret_cast<T*>(p.recv[owner]) + ((size_t)p.rank * p.rows_cap + lr) * p.H;
+        T* dst_row = reinterpret_cast<T*>(p.recv[owner]) + ((size_t)slot * p.slot_rows + lr) * p.H;
 #pragma unroll 1
         for (int c = 0; c < kArBN; c += 32) {
           uint32_t r[32];
@@ -444,12 +454,35 @@ static void launch_ar(const FusedArParams& p, const void* A, int lda, const void
   // may reduce between two tiles
   static const int env_push = [] { const char* e = std::getenv("B200_AR_TMA_PUSH"); return e ? std::atoi(e) : 1; }();
   static const int env_gap = [] { const char* e = std::getenv("B200_AR_ROWS_PER_GAP"); return e ? std::atoi(e) : 4; }();
+  static const int env_split = [] { const char* e = std::getenv("B200_AR_KSPLIT"); return e ? std::atoi(e) : 0; }();
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  // Split-K while the tiles alone leave SMs idle: every K range keeps >= 4 k-blocks, no range is empty, and the
+  // tp * ksplit receive slots fit the buffer sized for tp sources of rows_cap rows.
+  const int num_tiles = ((p.T + kArBM - 1) / kArBM) * ((p.H + kArBN - 1) / kArBN);
+  const int num_k = (p.K + kArBK - 1) / kArBK;
+  auto split_ok = [&](int s) {
+    const int per = (num_k + s - 1) / s;
+    return per * (s - 1) < num_k && ((p.rows_cap / s) & ~7) >= p.rows_per_rank;
+  };
+  int ksplit = 1;
+  if (env_split > 0) {
+    ksplit = env_split;
+  } else {
+    while (ksplit < 8 && num_tiles * ksplit * 2 <= sms && num_k / (ksplit * 2) >= 4) ksplit *= 2;
+  }
+  while (ksplit > 1 && !split_ok(ksplit)) --ksplit;
+  // TMA tensor stores push whole 128-row boxes: every box must stay inside one owner's slot
   const bool tma_push = env_push != 0 && p.rows_per_rank % kArBM == 0 && p.H % 64 == 0;
   ArPushMaps maps;
   for (int r = 0; r < kMaxRanks; ++r) {
     const int o = r < p.tp ? r : p.rank;
-    const char* base = reinterpret_cast<const char*>(p.recv[o]) + (size_t)p.rank * p.rows_cap * p.H * 2;
-    maps.recv[r] = make_tmap_2d(base, dt, 2, tma_push ? p.rows_cap : 8, p.H, p.H, tma_push ? kArBM : 8, 64);
+    maps.recv[r] = make_tmap_2d(p.recv[o], dt, 2, tma_push ? (uint64_t)p.tp * p.rows_cap : 8, p.H, p.H,
+                                tma_push ? kArBM : 8, 64);
   }
   auto kern = tma_push ? gemm_ar_norm_kernel<T, true> : gemm_ar_norm_kernel<T, false>;
   static bool set[2] = {false, false};
@@ -457,14 +490,10 @@ static void launch_ar(const FusedArParams& p, const void* A, int lda, const void
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ArSmem::kDyn);
     set[tma_push] = true;
   }
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  }
   FusedArParams q = p;
   q.rows_per_gap = env_gap;
+  q.ksplit = ksplit;
+  q.slot_rows = ksplit == 1 ? p.rows_cap : ((p.rows_cap / ksplit) & ~7);
   // the whole grid must be co-resident (CTAs wait on peers, never on each other)
   kern<<<sms, 192, ArSmem::kDyn, stream>>>(tmA, tmB, maps, q);
 }

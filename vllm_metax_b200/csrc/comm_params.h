@@ -26,6 +26,8 @@ struct FusedArParams {
   float eps;
   int add_residual;               // 0: residual_out = reduced sum (first use), 1: residual += sum
   int rows_per_gap;               // rows an epilogue warp may reduce between two tiles (set by the launcher)
+  int ksplit;                     // K is cut into this many ranges, each a work unit of its own (set by the launcher)
+  int slot_rows;                  // rows between two (source, K-range) slots of recv: rows_cap / ksplit, multiple of 8
   uint32_t* local_sync;           // [4] local scratch: [0] CTAs done, [1] last finished epoch (the call's
                                   // epoch is that + 1; its low bit selects the counter set)
   long long wait_cycles;          // budget of every flag wait
@@ -57,6 +59,39 @@ struct MoeA2aParams {
   void* comb_x[kMaxRanks];          // [pairs_cap][H] 16-bit
   uint32_t* comb_flag[kMaxRanks];   // [ep] combine epoch per source
   uint32_t* local_sync;             // [0] ticket, [1] dispatch epoch, [2] combine epoch, [8+r] send counters
+  long long wait_cycles;
+  StatusWord* status;
+};
+
+// Stand-alone all-reduce over peer memory (comm_allreduce.cu).  Pointer arrays are indexed by the rank that OWNS
+// the memory.
+struct CustomArParams {
+  int tp, rank;
+  long long n_bytes;                // payload, multiple of 16
+  long long cap_bytes;              // stride of one (parity, source) slot of recv and of one parity half of gather
+  void* recv[kMaxRanks];            // [2 parity][tp source][cap_bytes] pushed inputs (one-shot) or segments (two-shot)
+  void* gather[kMaxRanks];          // [2 parity][cap_bytes] reduced segments written by their owners (two-shot)
+  uint32_t* flag1[kMaxRanks];       // [tp source][max_ctas] epoch per pushing CTA
+  uint32_t* flag2[kMaxRanks];       // [tp source][max_ctas] epoch per CTA after its reduced segment is out
+  int max_ctas;
+  uint32_t* local_sync;             // [0] ticket, [1] last finished epoch
+  long long wait_cycles;
+  StatusWord* status;
+};
+
+// Cross-rank RMSNorm over a hidden dimension that is split across ranks (comm_allreduce.cu): the per-token sums of
+// squares travel as 4-byte values whose arrival is their own flag (-0.0 = "not yet written").
+struct ReduceRmsParams {
+  int tp, rank, T, n_tensors;       // up to two tensors (q and k) per launch
+  const void* x[2];
+  const void* w[2];
+  void* out[2];
+  int H[2];                         // local width of each tensor (multiple of 8)
+  int ld[2];                        // row pitch of x / out in elements
+  float eps;
+  float* slots[kMaxRanks];          // [3 buffers][2 tensors][tp source][t_cap]
+  int t_cap;
+  uint32_t* local_sync;             // [0] ticket, [1] calls finished, [2 + b] tokens of the last call that used buffer b
   long long wait_cycles;
   StatusWord* status;
 };

@@ -225,6 +225,9 @@ void moe_a2a_combine(const MoeA2aParams& p, const void* y, const int* inv_pos, v
                      const int* topk_ids, const void* shared_out, int dtype, cudaStream_t stream);
 void gather_rows(void* dst, const void* src, const int* idx, const int* count, int max_rows, int limit, int row_bytes,
                  cudaStream_t stream);
+// ---- comm_allreduce.cu
+int custom_allreduce(const CustomArParams& p, const void* in, void* out, int dtype, int mode, cudaStream_t stream);
+int reduce_rms(const ReduceRmsParams& p, int dtype, cudaStream_t stream);
 // ---- mla_decode.cu
 void mla_decode(const MlaDecodeParams& p, int fp8_records, int dtype, cudaStream_t stream);
 // ---- indexer.cu

@@ -45,6 +45,9 @@ class LLMEngine:
 
         self.spec_config = SpeculativeConfig.from_dict((cfg.additional_config or {}).get("speculative_config"))
         self.proposer = make_proposer(self.spec_config, self)
+        from ..parallel.liveness import RankLiveness
+
+        self.liveness = RankLiveness.from_default_group()     # None in a single-process engine
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
@@ -77,6 +80,8 @@ class LLMEngine:
                 raise RuntimeError("scheduler made no progress: KV cache too small for the waiting request")
             return []
         try:
+            if self.liveness is not None:
+                self.liveness.check()          # a peer whose step raised: stop before launching work that waits for it
             for hook in self.step_hooks:
                 hook("before", self.stats["steps"])
             sampled = self.runner.execute(so)
@@ -84,6 +89,8 @@ class LLMEngine:
                 hook("after", self.stats["steps"])
         except BaseException as e:  # a failed step poisons the engine (memory is released)
             self.dead = e
+            if self.liveness is not None:
+                self.liveness.announce_failure(repr(e))
             self._release_all()
             raise EngineDeadError(f"engine step failed: {e!r}") from e
         now = time.perf_counter()

@@ -73,6 +73,13 @@ class ModelRunner:
         """Swap the row-parallel linears + all-reduce + add-norm of a TP model for the fused NVLink kernel."""
         inner = getattr(self.model, "model", None)
         self.fused_tp = False
+        self.custom_ar = None
+        if ps.tp_size() > 1 and self.is_cuda and envs.B200_CUSTOM_ALLREDUCE:
+            from ..parallel.custom_allreduce import CustomAllReduce
+
+            # small reductions (decode steps, MoE outputs, logits pieces) skip NCCL's launch + protocol latency
+            self.custom_ar = CustomAllReduce(ps.get_tp_group(), self.device, envs.B200_CUSTOM_ALLREDUCE_MAX_BYTES)
+            self.custom_ar.attach()
         if (ps.tp_size() == 1 or ps.get_pp_group().world_size > 1 or not envs.B200_FUSED_TP_COLLECTIVES
                 or inner is None or not hasattr(inner, "forward_fused_tp")
                 or not getattr(inner, "supports_fused_tp", True) or self.cfg.model.quantization):

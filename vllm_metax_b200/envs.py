@@ -70,6 +70,10 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # Use NVLS multimem instructions in fused collectives when available.
     "B200_USE_MULTIMEM": _flag("B200_USE_MULTIMEM", "0"),
     "B200_PP_DISABLE_ALLGATHER": _flag("B200_PP_DISABLE_ALLGATHER", "0"),
+    # Peer-store all-reduce kernel for tensor-parallel reductions up to B200_CUSTOM_ALLREDUCE_MAX_BYTES
+    # (larger messages stay on NCCL).
+    "B200_CUSTOM_ALLREDUCE": _flag("B200_CUSTOM_ALLREDUCE", "1"),
+    "B200_CUSTOM_ALLREDUCE_MAX_BYTES": _int("B200_CUSTOM_ALLREDUCE_MAX_BYTES", 8 << 20),
     # ---- debug -------------------------------------------------------------
     "B200_FORCE_REFERENCE_OPS": _flag("B200_FORCE_REFERENCE_OPS", "0"),
     "B200_PRECISION_DUMP_DIR": _str("B200_PRECISION_DUMP_DIR", None),

@@ -30,11 +30,15 @@ class Group:
         self.device_pg = device_pg
         self.cpu_pg = cpu_pg
         self.name = name
+        self.custom_allreduce = None     # parallel.custom_allreduce.CustomAllReduce once attached
 
     # ---- collectives -----------------------------------------------------
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         if self.world_size == 1:
             return x
+        car = self.custom_allreduce
+        if car is not None and car.supports(x):
+            return car.all_reduce(x)
         dist.all_reduce(x, group=self._pg(x))
         return x
 
@@ -144,6 +148,15 @@ def _trivial(name: str) -> Group:
     return Group([0], 0, name=name)
 
 
+def _pg_timeout():
+    """Collective timeout from B200_PG_TIMEOUT_S (seconds): a short value turns a peer that never joins a
+    collective into an error on the waiting ranks instead of a long stall."""
+    import datetime
+
+    v = os.environ.get("B200_PG_TIMEOUT_S")
+    return datetime.timedelta(seconds=float(v)) if v else None
+
+
 def init_distributed(tensor_parallel_size: int = 1, pipeline_parallel_size: int = 1, data_parallel_size: int = 1,
                      decode_context_parallel_size: int = 1, backend: Optional[str] = None,
                      device: Optional[str] = None) -> None:
@@ -167,6 +180,8 @@ def init_distributed(tensor_parallel_size: int = 1, pipeline_parallel_size: int 
         kw = {}
         if use_cuda:
             kw["device_id"] = torch.device("cuda", local_rank)
+        if _pg_timeout() is not None:
+            kw["timeout"] = _pg_timeout()
         dist.init_process_group(backend=be, rank=rank, world_size=world, **kw)
     tp, pp, dp = tensor_parallel_size, pipeline_parallel_size, data_parallel_size
     assert tp * pp * dp == world, f"tp*pp*dp = {tp * pp * dp} != world size {world}"
@@ -177,8 +192,9 @@ def init_distributed(tensor_parallel_size: int = 1, pipeline_parallel_size: int 
             if len(ranks) == 1:
                 g = Group(ranks, rank, name=name) if rank in ranks else None
             else:
-                dpg = dist.new_group(ranks, backend="nccl") if use_cuda else None
-                cpg = dist.new_group(ranks, backend="gloo")
+                tkw = {"timeout": _pg_timeout()} if _pg_timeout() is not None else {}
+                dpg = dist.new_group(ranks, backend="nccl", **tkw) if use_cuda else None
+                cpg = dist.new_group(ranks, backend="gloo", **tkw)
                 g = Group(ranks, rank, dpg if use_cuda else cpg, cpg, name) if rank in ranks else None
             if g is not None:
                 mine = g
