@@ -93,3 +93,57 @@ def test_v4_model_gpu_matches_cpu_tokens(kernel_status_ok):
     gpu_llm.engine.runner.model.load_state_dict({k: v for k, v in cpu.engine.runner.model.state_dict().items()}, strict=False)
     out = gpu_llm.generate([[1, 2, 3, 4]], sp)
     assert len(out[0].outputs[0].token_ids) == 5
+
+
+# ------------------------------------------------------------------------------- latent-cache records
+def _record_case(device, T=37, Hq=5, hq_pad=8, block_size=16, n_insert=33):
+    from vllm_metax_b200.ops import v4_cache as vc
+
+    g = torch.Generator().manual_seed(3)
+    q = (torch.randn(T, Hq, 512, generator=g) * 2).to(torch.bfloat16).to(device)
+    kv = (torch.randn(T, 512, generator=g) * torch.logspace(-3, 2, 512)).to(torch.bfloat16).to(device)
+    pos = torch.randint(0, 300, (T,), generator=g).to(device)
+    ang = torch.arange(300)[:, None].float() * (1.0 / 10000 ** (torch.arange(32).float() / 32))[None]
+    cos_sin = torch.cat([ang.cos(), ang.sin()], -1).to(device)
+    slots = torch.randperm(4 * block_size, generator=g)[:n_insert]
+    slots[5] = -1
+    cache = vc.alloc_cache(4, block_size, device)
+    return vc, q, kv, pos, cos_sin, slots.to(device), cache, hq_pad, block_size
+
+
+def test_v4_records_reference_round_trip():
+    vc, q, kv, pos, cos_sin, slots, cache, hq_pad, bs = _record_case("cpu")
+    q_out = vc.qnorm_rope_kv_insert(q, kv, cache, slots, pos, cos_sin, 1e-6, bs, hq_pad)
+    assert q_out.shape == (37, hq_pad, 512) and q_out[:, 5:].abs().max() == 0
+    # normalised heads have unit RMS (RoPE is a rotation)
+    torch.testing.assert_close(q_out[:, :5].float().pow(2).mean(-1), torch.ones(37, 5), rtol=2e-2, atol=2e-2)
+    back = vc.gather_dequant(cache, slots, bs).float()
+    rows = cos_sin[pos[: slots.numel()]]
+    want = torch.cat([kv[: slots.numel(), :448].float(), vc._rope_interleaved(kv[: slots.numel(), 448:].float(), rows)], -1)
+    live = slots >= 0
+    assert back[~live].abs().max() == 0
+    # e4m3 with a power-of-two scale per 64 values: 3 mantissa bits -> relative error up to 2^-4 of the block maximum
+    err = (back[live] - want[live]).abs().view(-1, 8, 64).amax(-1)
+    ref = want[live].abs().view(-1, 8, 64).amax(-1).clamp_min(1e-4)
+    assert (err / ref).max() < 0.07
+    torch.testing.assert_close(back[live][:, 448:], want[live][:, 448:].to(torch.bfloat16).float(), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.gpu
+def test_v4_records_kernel_matches_reference():
+    vc, q, kv, pos, cos_sin, slots, cache, hq_pad, bs = _record_case("cuda")
+    # q as a view with padded pitches, as it comes out of a fused projection
+    q_wide = torch.zeros(q.shape[0], q.shape[1], 520, dtype=q.dtype, device="cuda")
+    q_wide[..., :512] = q
+    q_out = vc.qnorm_rope_kv_insert(q_wide[..., :512], kv, cache, slots, pos, cos_sin, 1e-6, bs, hq_pad)
+    cache_ref = vc.alloc_cache(4, bs, "cpu")
+    q_ref = vc.qnorm_rope_kv_insert_ref(q.cpu(), kv.cpu(), cache_ref, slots.cpu(), pos.cpu(), cos_sin.cpu(), 1e-6, bs, hq_pad)
+    torch.testing.assert_close(q_out.float().cpu(), q_ref.float(), rtol=2e-2, atol=2e-2)
+    got = vc.gather_dequant(cache, slots, bs).float().cpu()
+    want = vc.gather_dequant_ref(cache_ref, slots.cpu(), bs).float()
+    # identical scales except where an amax sits on a power-of-two boundary; compare dequantised values
+    torch.testing.assert_close(got, want, rtol=0.13, atol=1e-3)
+    same = (cache.cpu() == cache_ref).float().mean()
+    assert same > 0.98, same
+    # the kernel's own reader agrees with the PyTorch reader on the kernel's bytes
+    torch.testing.assert_close(got, vc.gather_dequant_ref(cache.cpu(), slots.cpu(), bs).float(), rtol=0, atol=0)

@@ -169,3 +169,74 @@ def test_selective_scan_gpu(n, g, dtype, kernel_status_ok):
     assert cos_diff(got, want) < (1e-6 if dtype == torch.float32 else 1e-4)
     torch.testing.assert_close(gst.cpu()[[4, 0, 2]], wst[[4, 0, 2]], rtol=tol, atol=tol)
     assert torch.equal(gst.cpu()[[1, 3]], st0[[1, 3]])
+
+
+# ----------------------------------------------------------------------------- whole-row norm + RoPE + inserts
+def _m3_case(dtype, T=21, hq=6, hk=2, niq=3, bs=16, nb=4, n_insert=18):
+    g = torch.Generator().manual_seed(11)
+    width = (hq + 2 * hk + niq + 1) * 128
+    qkv = torch.randn(T, width, generator=g).to(dtype)
+    ws = [(torch.randn(128, generator=g) * 0.1).to(dtype) for _ in range(4)]
+    cs = _cos_sin(256, 64)
+    pos = torch.randint(0, 256, (T,), generator=g)
+    slots = torch.randperm(nb * bs, generator=g)[:n_insert]
+    slots[3] = -1
+    return qkv, ws, cs, pos, slots, (hq, hk, niq, bs, nb)
+
+
+def test_qkv_norm_rope_insert_cpu_consistency():
+    qkv, ws, cs, pos, slots, (hq, hk, niq, bs, nb) = _m3_case(torch.float32)
+    before = qkv.clone()
+    kv_cache = torch.zeros(nb, 2, bs, hk, 128)
+    idx_cache = torch.zeros(nb * bs, 128)
+    q_out, iq_out = X.qkv_norm_rope_insert(qkv, pos, slots, cs, hq, hk, ws[0], ws[1], kv_cache, niq, True, ws[2], ws[3],
+                                           idx_cache)
+    assert q_out.shape == (21, hq, 128) and iq_out.shape == (21, niq, 128)
+    # same math as the in-place q/k op on the leading [q | k | v] part
+    part = before[:, : (hq + 2 * hk) * 128].clone()
+    X.fused_qk_norm_rope(part, ws[0], ws[1], cs, pos, hq, hk, hk, 128, True, 1e-6, gemma=True)
+    torch.testing.assert_close(q_out.reshape(21, -1), part[:, : hq * 128])
+    torch.testing.assert_close(qkv[:, hq * 128: (hq + hk) * 128], part[:, hq * 128: (hq + hk) * 128])
+    assert torch.equal(qkv[:, (hq + hk) * 128:], before[:, (hq + hk) * 128:])       # v and index parts untouched
+    for t, s in enumerate(slots.tolist()):
+        if s < 0:
+            continue
+        blk, p = divmod(s, bs)
+        torch.testing.assert_close(kv_cache[blk, 0, p].reshape(-1), qkv[t, hq * 128: (hq + hk) * 128])
+        torch.testing.assert_close(kv_cache[blk, 1, p].reshape(-1), before[t, (hq + hk) * 128: (hq + 2 * hk) * 128])
+    untouched = torch.ones(nb * bs, dtype=torch.bool)
+    untouched[slots[slots >= 0]] = False
+    assert idx_cache[untouched].abs().max() == 0 and idx_cache[~untouched].abs().min(dim=1).values.max() > 0
+
+
+@gpu
+@pytest.mark.parametrize("fp8_idx", [False, True])
+def test_qkv_norm_rope_insert_gpu(fp8_idx, kernel_status_ok):
+    qkv, ws, cs, pos, slots, (hq, hk, niq, bs, nb) = _m3_case(torch.bfloat16)
+    idt = torch.uint8 if fp8_idx else torch.bfloat16
+    kv_ref, idx_ref = torch.zeros(nb, 2, bs, hk, 128), torch.zeros(nb * bs, 128, dtype=torch.uint8 if fp8_idx else torch.float32)
+    qkv_ref = qkv.float().clone()
+    q_ref, iq_ref = X.qkv_norm_rope_insert(qkv_ref, pos, slots, cs, hq, hk, ws[0].float(), ws[1].float(), kv_ref, niq, True,
+                                           ws[2].float(), ws[3].float(), idx_ref, index_fp8=fp8_idx)
+    kv = torch.zeros(nb, 2, bs, hk, 128, dtype=torch.bfloat16, device="cuda")
+    idx = torch.zeros(nb * bs, 128, dtype=idt, device="cuda")
+    wide = torch.zeros(qkv.shape[0], qkv.shape[1] + 64, dtype=torch.bfloat16, device="cuda")     # padded row pitch
+    wide[:, : qkv.shape[1]] = qkv.cuda()
+    view = wide[:, : qkv.shape[1]]
+    q_out, iq_out = X.qkv_norm_rope_insert(view, pos.cuda(), slots.cuda(), cs.cuda(), hq, hk, ws[0].cuda(), ws[1].cuda(), kv,
+                                           niq, True, ws[2].cuda(), ws[3].cuda(), idx, index_fp8=fp8_idx)
+    tol = dict(rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(q_out.float().cpu(), q_ref, **tol)
+    torch.testing.assert_close(view.float().cpu(), qkv_ref, **tol)
+    torch.testing.assert_close(kv.float().cpu(), kv_ref, **tol)
+
+    def f(x):
+        return x.view(torch.float8_e4m3fn).float() if fp8_idx else x.float()
+
+    torch.testing.assert_close(f(iq_out.cpu()), f(iq_ref), rtol=0.14 if fp8_idx else 3e-2, atol=3e-2)
+    torch.testing.assert_close(f(idx.cpu()), f(idx_ref), rtol=0.14 if fp8_idx else 3e-2, atol=3e-2)
+    # dense layer form: no index heads, no cache (profiling run)
+    q2, none = X.qkv_norm_rope_insert(qkv[:, : (hq + 2 * hk) * 128].cuda().contiguous(), pos.cuda(), slots.cuda()[:0], cs.cuda(),
+                                      hq, hk, ws[0].cuda(), ws[1].cuda())
+    assert none is None
+    torch.testing.assert_close(q2.float().cpu(), q_ref, **tol)

@@ -678,6 +678,51 @@ void fused_qk_norm_rope(Tensor& qkv, const Tensor& q_weight, const Tensor& k_wei
   TORCH_CHECK(rc == 0, "fused_qk_norm_rope: unsupported head_dim / rotary_dim");
 }
 
+// qkv [T, (hq + 2 hk + niq + has_ik) * 128]; kv_cache [blocks, 2, block_size, hk, 128]; idx_cache [slots, 128]
+void qkv_norm_rope_insert(Tensor& qkv, Tensor& q_out, const optional<Tensor>& iq_out, const optional<Tensor>& kv_cache,
+                          const optional<Tensor>& idx_cache, const optional<Tensor>& q_w, const optional<Tensor>& k_w,
+                          const optional<Tensor>& iq_w, const optional<Tensor>& ik_w, const Tensor& cos_sin,
+                          const Tensor& positions, const Tensor& slot_mapping, int64_t hq, int64_t hk, int64_t niq,
+                          bool has_ik, bool is_neox, double eps, bool gemma) {
+  const int64_t width = (hq + 2 * hk + niq + (has_ik ? 1 : 0)) * 128;
+  TORCH_CHECK(qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.size(1) == width && qkv.stride(0) % 4 == 0);
+  TORCH_CHECK(q_out.is_contiguous() && q_out.numel() == qkv.size(0) * hq * 128 && q_out.scalar_type() == qkv.scalar_type());
+  TORCH_CHECK(cos_sin.scalar_type() == at::kFloat && cos_sin.is_contiguous() && positions.scalar_type() == at::kLong &&
+              slot_mapping.scalar_type() == at::kLong && positions.numel() >= qkv.size(0) &&
+              slot_mapping.numel() <= qkv.size(0));
+  bool idx_fp8 = false;
+  if (niq > 0) {
+    TORCH_CHECK(iq_out.has_value() && iq_out->is_contiguous() && iq_out->numel() == qkv.size(0) * niq * 128);
+    idx_fp8 = iq_out->element_size() == 1;
+  }
+  int64_t block_size = 1, num_slots = 0;
+  if (kv_cache.has_value()) {
+    TORCH_CHECK(kv_cache->dim() == 5 && kv_cache->is_contiguous() && kv_cache->size(1) == 2 && kv_cache->size(3) == hk &&
+                kv_cache->size(4) == 128 && kv_cache->scalar_type() == qkv.scalar_type());
+    block_size = kv_cache->size(2);
+    num_slots = kv_cache->size(0) * block_size;
+  }
+  if (has_ik && idx_cache.has_value()) {
+    TORCH_CHECK(idx_cache->is_contiguous() && idx_cache->size(-1) == 128 && (idx_cache->element_size() == 1) == idx_fp8);
+    const int64_t n = idx_cache->numel() / 128;
+    num_slots = kv_cache.has_value() ? std::min(num_slots, n) : n;
+  }
+  auto wp = [&](const optional<Tensor>& w) -> const void* {
+    if (!w.has_value()) return nullptr;
+    TORCH_CHECK(w->numel() == 128 && w->scalar_type() == qkv.scalar_type() && w->is_contiguous());
+    return w->data_ptr();
+  };
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  const int rc = b200::qkv_norm_rope_insert(
+      qkv.data_ptr(), qkv.stride(0), wp(q_w), wp(k_w), wp(iq_w), wp(ik_w), cos_sin.data_ptr<float>(),
+      positions.data_ptr<int64_t>(), slot_mapping.data_ptr<int64_t>(), q_out.data_ptr(),
+      iq_out.has_value() ? iq_out->data_ptr() : nullptr, kv_cache.has_value() ? kv_cache->data_ptr() : nullptr,
+      has_ik && idx_cache.has_value() ? idx_cache->data_ptr() : nullptr, (int)qkv.size(0), (int)slot_mapping.numel(),
+      (int)hq, (int)hk, (int)niq, has_ik ? 1 : 0, kv_cache.has_value() ? 1 : 0, (int)cos_sin.size(1), is_neox, gemma,
+      idx_fp8, (int)block_size, num_slots, (float)eps, dtype16(qkv), cur_stream());
+  TORCH_CHECK(rc == 0, "qkv_norm_rope_insert: unsupported rotary width");
+}
+
 void mla_rope_and_cache(Tensor& q_pe, Tensor& k_pe, const Tensor& kv_c, Tensor& cache, const Tensor& cos_sin,
                         const Tensor& positions, const Tensor& slot_mapping, bool is_neox) {
   TORCH_CHECK(q_pe.dim() == 3 && q_pe.size(2) == 64 && q_pe.stride(2) == 1 && q_pe.stride(1) == 64);
@@ -804,6 +849,39 @@ void p2p_copy(int64_t dst_ptr, const Tensor& src, int64_t ctas, int64_t mode) {
   TORCH_CHECK(n % (mode == 0 ? 16 : 16384) == 0, "p2p_copy: size granularity");
   const c10::cuda::CUDAGuard guard(src.device());
   b200::p2p_copy(reinterpret_cast<void*>(dst_ptr), src.data_ptr(), n, (int)ctas, (int)mode, status_ptr(src), cur_stream());
+}
+
+// DeepSeek-V4 records: q [T, Hq, 512] bf16 (any token / head pitch), kv [T, 512] bf16, q_out [T, Hq_pad, 512],
+// cache uint8 [blocks, block_stride >= block_size * 584], cos_sin fp32 [max_pos, 64]
+void v4_qnorm_rope_kv_insert(Tensor& q_out, Tensor& cache, const Tensor& q, const Tensor& kv, const Tensor& slot_mapping,
+                             const Tensor& positions, const Tensor& cos_sin, double eps, int64_t block_size) {
+  TORCH_CHECK(q.dim() == 3 && q.size(2) == 512 && q.stride(2) == 1 && q.scalar_type() == at::kBFloat16);
+  TORCH_CHECK(kv.dim() == 2 && kv.size(1) == 512 && kv.stride(1) == 1 && kv.scalar_type() == at::kBFloat16 &&
+              kv.size(0) == q.size(0));
+  TORCH_CHECK(q_out.dim() == 3 && q_out.is_contiguous() && q_out.size(0) == q.size(0) && q_out.size(1) >= q.size(1) &&
+              q_out.size(2) == 512 && q_out.scalar_type() == at::kBFloat16);
+  TORCH_CHECK(q.stride(0) % 8 == 0 && q.stride(1) % 8 == 0 && kv.stride(0) % 8 == 0, "rows must be 16-byte aligned");
+  TORCH_CHECK(cache.dim() == 2 && cache.element_size() == 1 && cache.stride(1) == 1 &&
+              cache.stride(0) >= block_size * 584 && cache.stride(0) % 16 == 0 && block_size % 2 == 0);
+  TORCH_CHECK(slot_mapping.scalar_type() == at::kLong && positions.scalar_type() == at::kLong &&
+              slot_mapping.is_contiguous() && positions.is_contiguous() && positions.numel() >= q.size(0) &&
+              slot_mapping.numel() <= q.size(0));
+  TORCH_CHECK(cos_sin.scalar_type() == at::kFloat && cos_sin.dim() == 2 && cos_sin.size(1) == 64 && cos_sin.is_contiguous());
+  const c10::cuda::CUDAGuard guard(q.device());
+  b200::v4_qnorm_rope_kv_insert(q.data_ptr(), q.stride(0), q.stride(1), kv.data_ptr(), kv.stride(0), q_out.data_ptr(),
+                                cache.data_ptr(), cache.stride(0), slot_mapping.data_ptr<int64_t>(),
+                                positions.data_ptr<int64_t>(), cos_sin.data_ptr<float>(), (int)q.size(0),
+                                (int)slot_mapping.numel(), (int)q.size(1), (int)q_out.size(1), (int)block_size,
+                                (float)eps, cur_stream());
+}
+
+void v4_gather_dequant(Tensor& dst, const Tensor& cache, const Tensor& slots, int64_t block_size) {
+  TORCH_CHECK(dst.dim() == 2 && dst.size(1) == 512 && dst.is_contiguous() && dst.scalar_type() == at::kBFloat16);
+  TORCH_CHECK(cache.dim() == 2 && cache.element_size() == 1 && cache.stride(1) == 1 && cache.stride(0) >= block_size * 584);
+  TORCH_CHECK(slots.scalar_type() == at::kLong && slots.is_contiguous() && slots.numel() == dst.size(0));
+  const c10::cuda::CUDAGuard guard(dst.device());
+  b200::v4_gather_dequant(dst.data_ptr(), cache.data_ptr(), cache.stride(0), slots.data_ptr<int64_t>(), (int)dst.size(0),
+                          (int)block_size, cur_stream());
 }
 
 // ptrs: int64 CPU tensor [4, tp] = recv, gather, flag1, flag2 (per owning rank)
@@ -963,12 +1041,15 @@ void gather_rows(Tensor& dst, const Tensor& src, const Tensor& idx, const Tensor
 TORCH_LIBRARY(b200, m) {
   m.def("moe_a2a_dispatch(Tensor x, Tensor topk_ids, Tensor ptrs, int ep, int rank, int experts_per_rank, int cap, bool quant, Tensor(a!) local_sync, int wait_cycles) -> ()", &moe_a2a_dispatch);
   m.def("moe_a2a_combine(Tensor(a!) out, Tensor y, Tensor inv_pos, Tensor topk_w, Tensor topk_ids, Tensor? shared_out, Tensor ptrs, int ep, int rank, int experts_per_rank, int cap, Tensor(b!) local_sync, int wait_cycles) -> ()", &moe_a2a_combine);
+  m.def("v4_qnorm_rope_kv_insert(Tensor(a!) q_out, Tensor(b!) cache, Tensor q, Tensor kv, Tensor slot_mapping, Tensor positions, Tensor cos_sin, float eps, int block_size) -> ()", &v4_qnorm_rope_kv_insert);
+  m.def("v4_gather_dequant(Tensor(a!) dst, Tensor cache, Tensor slots, int block_size) -> ()", &v4_gather_dequant);
   m.def("custom_allreduce(Tensor(a!) out, Tensor inp, Tensor ptrs, int tp, int rank, int cap_bytes, int max_ctas, Tensor(b!) local_sync, int mode, int wait_cycles) -> ()", &custom_allreduce);
   m.def("reduce_rms(Tensor(a!) out0, Tensor x0, Tensor w0, Tensor(b!)? out1, Tensor? x1, Tensor? w1, float eps, Tensor slots_ptrs, int tp, int rank, int t_cap, Tensor(c!) local_sync, int wait_cycles) -> ()", &reduce_rms);
   m.def("ag_gemm(Tensor(a!) out, Tensor w, Tensor? bias, Tensor ptrs, Tensor(b!) gathered, Tensor(c!) ready, Tensor(d!) sync, int tp, int rank, int rows_per_rank, int wait_cycles) -> ()", &ag_gemm);
   m.def("mhc_pre(Tensor(a!) x_out, Tensor(b!)? post_out, Tensor(c!)? comb_out, Tensor residual, Tensor(d!)? residual_out, Tensor? y, Tensor? post_in, Tensor? comb_in, Tensor fn, Tensor scale, Tensor base, float rms_eps, float pre_eps, float sinkhorn_eps, float post_mult, int iters, bool head) -> ()", &mhc_pre);
   m.def("mhc_post(Tensor(a!) out, Tensor y, Tensor residual, Tensor post, Tensor comb) -> ()", &mhc_post);
   m.def("small_gemm(Tensor(a!) out, Tensor a, Tensor w, Tensor? bias) -> ()", &small_gemm);
+  m.def("qkv_norm_rope_insert(Tensor(a!) qkv, Tensor(b!) q_out, Tensor(c!)? iq_out, Tensor(d!)? kv_cache, Tensor(e!)? idx_cache, Tensor? q_w, Tensor? k_w, Tensor? iq_w, Tensor? ik_w, Tensor cos_sin, Tensor positions, Tensor slot_mapping, int hq, int hk, int niq, bool has_ik, bool is_neox, float eps, bool gemma) -> ()", &qkv_norm_rope_insert);
   m.def("fused_qk_norm_rope(Tensor(a!) qkv, Tensor q_weight, Tensor k_weight, Tensor cos_sin, Tensor positions, int hq, int hk, int hv, int head_dim, bool is_neox, float eps, bool gemma) -> ()", &fused_qk_norm_rope);
   m.def("mla_rope_and_cache(Tensor(a!) q_pe, Tensor(b!) k_pe, Tensor kv_c, Tensor(c!) cache, Tensor cos_sin, Tensor positions, Tensor slot_mapping, bool is_neox) -> ()", &mla_rope_and_cache);
   m.def("concat_mla_q(Tensor(a!) out, Tensor nope, Tensor pe) -> ()", &concat_mla_q);

@@ -1,6 +1,9 @@
 // Small fused memory-bound kernels:
 //   fused_qk_norm_rope        per-head RMSNorm(q), RMSNorm(k) + RoPE (NeoX / GPT-J, partial rotary) in place
 //                             on the packed qkv GEMM output - one warp per (token, head)
+//   qkv_norm_rope_insert      the same for a whole [q | k | v | index_q | index_k] row, with q / index_q gathered into
+//                             contiguous outputs and k, v, index_k written into their paged caches (head_dim 128;
+//                             fused_minimax_m3_qknorm_rope_kv_insert_kernel.cu:262-480 of the reference)
 //   mla_rope_and_cache        RoPE on q_pe / k_pe + insert [kv_c | k_pe] into the bf16 MLA cache, one pass
 //   concat_mla_q              q_out[T,H,576] = [ql_nope(512) | q_pe(64)]
 //   permute_cols              out[:, j] = a[:, perm[j]]   (GPTQ act-order activation gather)
@@ -187,6 +190,169 @@ __global__ void gather_indexer_k_kernel(uint8_t* __restrict__ dst_k, float* __re
   const uint8_t* base = cache + (size_t)blk * block_size * 132;
   if (lane < 8) reinterpret_cast<uint4*>(dst_k + (size_t)gw * 128)[lane] = reinterpret_cast<const uint4*>(base + off * 128)[lane];
   if (lane == 8) dst_s[gw] = reinterpret_cast<const float*>(base + block_size * 128)[off];
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Norm + RoPE + cache inserts of a whole attention input row in one launch (head_dim 128, 4 dims per lane).
+// Row of `qkv`: [q (hq) | k (hk) | v (hk) | index_q (niq) | index_k (1)] x 128; one warp per (token, slot):
+//   q, index_q   RMSNorm (gemma form, skipped when the weight is null) + partial RoPE -> q_out / iq_out, contiguous
+//                [T, heads, 128] so that the attention kernel can address them with a flat tensor map
+//   k            norm + RoPE, written back in place and into the K plane of the paged cache
+//   v            copied into the V plane
+//   index_k      norm + RoPE -> index cache row of the token's slot
+// iq_out and the index cache are 16-bit or e4m3 bytes (direct saturating cast: normalised values are O(1)).
+// Tokens at or beyond `insert_tokens` and negative slots get no cache rows.
+template <typename T>
+__device__ __forceinline__ void norm_rope4(float (&v)[4], const T* w, const float* cs, int rot, int is_neox, float eps,
+                                           int gemma, int lane) {
+  if (w != nullptr) {
+    float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / 128.f + eps);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = to_f(from_f<T>(v[i] * inv * (to_f(w[lane * 4 + i]) + (gemma ? 1.f : 0.f))));
+  }
+  if (rot <= 0) return;
+  const int half = rot >> 1;
+  if (is_neox) {
+    const int dl = half / 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = lane * 4 + i;
+      const bool lo = idx < half;
+      const float other = __shfl_sync(0xffffffffu, v[i], (lo ? lane + dl : lane - dl) & 31);
+      if (idx < rot) {
+        const int j = lo ? idx : idx - half;
+        const float c = cs[j], s = cs[half + j];
+        v[i] = lo ? v[i] * c - other * s : v[i] * c + other * s;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; i += 2) {
+      const int idx = lane * 4 + i;
+      if (idx < rot) {
+        const float c = cs[idx >> 1], s = cs[half + (idx >> 1)];
+        const float x = v[i], y = v[i + 1];
+        v[i] = x * c - y * s;
+        v[i + 1] = y * c + x * s;
+      }
+    }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store4(T* p, const float (&v)[4]) {
+  T o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o[i] = from_f<T>(v[i]);
+  *reinterpret_cast<uint2*>(p) = *reinterpret_cast<const uint2*>(o);
+}
+__device__ __forceinline__ void store4_fp8(uint8_t* p, const float (&v)[4]) {
+  uint32_t w = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) w |= (uint32_t)float_to_fp8_e4m3(fminf(fmaxf(v[i], -448.f), 448.f)) << (8 * i);
+  *reinterpret_cast<uint32_t*>(p) = w;
+}
+
+struct QkvInsertParams {
+  int tokens, insert_tokens, hq, hk, niq, has_ik, insert_v;
+  int rot, is_neox, gemma, idx_fp8, block_size;
+  float eps;
+  int64_t row_stride;          // elements between two rows of qkv
+  int64_t num_slots;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+qkv_norm_rope_insert_kernel(const QkvInsertParams p, T* __restrict__ qkv, const T* __restrict__ q_w,
+                            const T* __restrict__ k_w, const T* __restrict__ iq_w, const T* __restrict__ ik_w,
+                            const float* __restrict__ cos_sin, const int64_t* __restrict__ positions,
+                            const int64_t* __restrict__ slot_mapping, T* __restrict__ q_out, void* __restrict__ iq_out,
+                            T* __restrict__ kv_cache, void* __restrict__ idx_cache) {
+  const int lane = threadIdx.x & 31;
+  const int v_slots = p.insert_v ? p.hk : 0;
+  const int slots = p.hq + p.hk + v_slots + p.niq + p.has_ik;
+  const int64_t gw = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (gw >= (int64_t)p.tokens * slots) return;
+  const int t = (int)(gw / slots);
+  int s = (int)(gw % slots);
+  T* row = qkv + (int64_t)t * p.row_stride;
+  const float* cs = cos_sin + (size_t)positions[t] * p.rot;
+  const int64_t slot = t < p.insert_tokens ? slot_mapping[t] : -1;
+  const bool can_insert = slot >= 0 && slot < p.num_slots;
+  const int64_t blk = can_insert ? slot / p.block_size : 0, pos = can_insert ? slot % p.block_size : 0;
+  float v[4];
+  auto load = [&](const T* src) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(src + lane * 4);
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = to_f(e[i]);
+  };
+  if (s < p.hq) {                                                   // ---- q
+    load(row + (int64_t)s * 128);
+    norm_rope4<T>(v, q_w, cs, p.rot, p.is_neox, p.eps, p.gemma, lane);
+    store4<T>(q_out + ((int64_t)t * p.hq + s) * 128 + lane * 4, v);
+    return;
+  }
+  s -= p.hq;
+  if (s < p.hk) {                                                   // ---- k
+    T* src = row + (int64_t)(p.hq + s) * 128;
+    load(src);
+    norm_rope4<T>(v, k_w, cs, p.rot, p.is_neox, p.eps, p.gemma, lane);
+    store4<T>(src + lane * 4, v);
+    if (can_insert && kv_cache != nullptr)
+      store4<T>(kv_cache + (((blk * 2 + 0) * p.block_size + pos) * p.hk + s) * 128 + lane * 4, v);
+    return;
+  }
+  s -= p.hk;
+  if (s < v_slots) {                                                // ---- v
+    if (!can_insert) return;
+    load(row + (int64_t)(p.hq + p.hk + s) * 128);
+    store4<T>(kv_cache + (((blk * 2 + 1) * p.block_size + pos) * p.hk + s) * 128 + lane * 4, v);
+    return;
+  }
+  s -= v_slots;
+  const int64_t idx_base = (int64_t)(p.hq + 2 * p.hk) * 128;       // index_q / index_k follow q | k | v
+  if (s < p.niq) {                                                  // ---- index_q
+    load(row + idx_base + (int64_t)s * 128);
+    norm_rope4<T>(v, iq_w, cs, p.rot, p.is_neox, p.eps, p.gemma, lane);
+    const int64_t o = ((int64_t)t * p.niq + s) * 128 + lane * 4;
+    if (p.idx_fp8) store4_fp8(static_cast<uint8_t*>(iq_out) + o, v);
+    else store4<T>(static_cast<T*>(iq_out) + o, v);
+    return;
+  }
+  // ---- index_k
+  load(row + idx_base + (int64_t)p.niq * 128);
+  norm_rope4<T>(v, ik_w, cs, p.rot, p.is_neox, p.eps, p.gemma, lane);
+  if (!can_insert || idx_cache == nullptr) return;
+  const int64_t o = slot * 128 + lane * 4;
+  if (p.idx_fp8) store4_fp8(static_cast<uint8_t*>(idx_cache) + o, v);
+  else store4<T>(static_cast<T*>(idx_cache) + o, v);
+}
+
+// Returns 0, or 1 for an unsupported rotary width.
+int qkv_norm_rope_insert(void* qkv, int64_t row_stride, const void* q_w, const void* k_w, const void* iq_w,
+                         const void* ik_w, const float* cos_sin, const int64_t* positions, const int64_t* slot_mapping,
+                         void* q_out, void* iq_out, void* kv_cache, void* idx_cache, int tokens, int insert_tokens, int hq,
+                         int hk, int niq, int has_ik, int insert_v, int rot, int is_neox, int gemma, int idx_fp8,
+                         int block_size, int64_t num_slots, float eps, int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (rot > 128 || (rot & 1) || (is_neox && rot > 0 && ((rot / 2) % 4))) return 1;
+  QkvInsertParams p{tokens, insert_tokens, hq, hk, niq, has_ik, insert_v, rot, is_neox, gemma, idx_fp8, block_size,
+                    eps, row_stride, num_slots};
+  const int64_t warps = (int64_t)tokens * (hq + hk + (insert_v ? hk : 0) + niq + has_ik);
+  const unsigned blocks = (unsigned)((warps + 7) / 8);
+  if (dtype == 0)
+    qkv_norm_rope_insert_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
+        p, (__nv_bfloat16*)qkv, (const __nv_bfloat16*)q_w, (const __nv_bfloat16*)k_w, (const __nv_bfloat16*)iq_w,
+        (const __nv_bfloat16*)ik_w, cos_sin, positions, slot_mapping, (__nv_bfloat16*)q_out, iq_out,
+        (__nv_bfloat16*)kv_cache, idx_cache);
+  else
+    qkv_norm_rope_insert_kernel<__half><<<blocks, 256, 0, stream>>>(
+        p, (__half*)qkv, (const __half*)q_w, (const __half*)k_w, (const __half*)iq_w, (const __half*)ik_w, cos_sin,
+        positions, slot_mapping, (__half*)q_out, iq_out, (__half*)kv_cache, idx_cache);
+  return 0;
 }
 
 // ---------------------------------------------------------------------------------------------------------

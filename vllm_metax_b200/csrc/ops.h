@@ -165,6 +165,11 @@ void gemm_wna16(const void* A, int M, int lda, const void* Q, const void* scales
 int small_gemm(void* C, const void* A, const void* W, const void* bias, int M, int N, int K, int lda, int ldw, int ldc,
                int dtype, int out_kind, cudaStream_t stream);
 // ---- fused_misc.cu
+int qkv_norm_rope_insert(void* qkv, int64_t row_stride, const void* q_w, const void* k_w, const void* iq_w,
+                         const void* ik_w, const float* cos_sin, const int64_t* positions, const int64_t* slot_mapping,
+                         void* q_out, void* iq_out, void* kv_cache, void* idx_cache, int tokens, int insert_tokens, int hq,
+                         int hk, int niq, int has_ik, int insert_v, int rot, int is_neox, int gemma, int idx_fp8,
+                         int block_size, int64_t num_slots, float eps, int dtype, cudaStream_t stream);
 int fused_qk_norm_rope(void* qkv, const void* q_weight, const void* k_weight, const float* cos_sin,
                        const int64_t* positions, int tokens, int hq, int hk, int hv, int head_dim, int rot, int is_neox,
                        float eps, int gemma, int dtype, cudaStream_t stream);
@@ -225,6 +230,13 @@ void moe_a2a_combine(const MoeA2aParams& p, const void* y, const int* inv_pos, v
                      const int* topk_ids, const void* shared_out, int dtype, cudaStream_t stream);
 void gather_rows(void* dst, const void* src, const int* idx, const int* count, int max_rows, int limit, int row_bytes,
                  cudaStream_t stream);
+// ---- v4_cache.cu
+void v4_qnorm_rope_kv_insert(const void* q_in, int64_t q_stride_t, int64_t q_stride_h, const void* kv, int64_t kv_stride,
+                             void* q_out, void* cache, int64_t block_stride, const int64_t* slot_mapping,
+                             const int64_t* positions, const float* cos_sin, int tokens, int insert_tokens, int hq,
+                             int hq_pad, int block_size, float eps, cudaStream_t stream);
+void v4_gather_dequant(void* dst, const void* cache, int64_t block_stride, const int64_t* slots, int n, int block_size,
+                       cudaStream_t stream);
 // ---- comm_allreduce.cu
 int custom_allreduce(const CustomArParams& p, const void* in, void* out, int dtype, int mode, cudaStream_t stream);
 int reduce_rms(const ReduceRmsParams& p, int dtype, cudaStream_t stream);

@@ -64,6 +64,66 @@ def fused_qk_norm_rope(qkv: torch.Tensor, q_weight, k_weight, cos_sin_cache, pos
     return qkv
 
 
+def qkv_norm_rope_insert(qkv: torch.Tensor, positions, slot_mapping, cos_sin_cache, num_q: int, num_kv: int,
+                         q_weight=None, k_weight=None, kv_cache=None, num_index_q: int = 0, index_k: bool = False,
+                         index_q_weight=None, index_k_weight=None, index_cache=None, index_fp8: bool = False,
+                         is_neox: bool = True, eps: float = 1e-6, gemma: bool = True):
+    """One pass over ``qkv [T, (Hq + 2 Hkv + Niq + index_k) * 128]`` (MiniMax-M3 layout): per-head (gemma) RMSNorm +
+    partial RoPE of q, k, index_q, index_k; ``q`` / ``index_q`` are returned as contiguous ``[T, H, 128]``; k (also
+    rewritten in place) and v go into ``kv_cache [blocks, 2, block_size, Hkv, 128]``, index_k into
+    ``index_cache [slots, 128]`` at ``slot_mapping`` (shorter than T: the tail gets no cache rows; negative slots are
+    skipped).  ``index_fp8`` stores index_q / index_k as e4m3 bytes (direct saturating cast).
+    Returns ``(q_out, index_q_out or None)``."""
+    T, D = qkv.shape[0], 128
+    if _cuda(qkv):
+        q_out = torch.empty(T, num_q, D, dtype=qkv.dtype, device=qkv.device)
+        iq_out = None
+        if num_index_q:
+            iq_out = torch.empty(T, num_index_q, D, dtype=torch.uint8 if index_fp8 else qkv.dtype, device=qkv.device)
+        torch.ops.b200.qkv_norm_rope_insert(qkv, q_out, iq_out, kv_cache, index_cache if index_k else None, q_weight,
+                                            k_weight, index_q_weight, index_k_weight, cos_sin_cache,
+                                            positions.long().contiguous(), slot_mapping.long().contiguous(), num_q,
+                                            num_kv, num_index_q, index_k, is_neox, eps, gemma)
+        return q_out, iq_out
+    norm = ref.gemma_rms_norm if gemma else ref.rms_norm
+
+    def nr(x, w):                                    # x [T, h, 128]
+        h = x.shape[1]
+        y = norm(x, w, eps) if w is not None else x
+        y, _ = ref.rotary_embedding(positions[:T], y.reshape(T, h * D), None, D, cos_sin_cache, is_neox)
+        return y.reshape(T, h, D)
+
+    def fp8(x):
+        return x.float().clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8)
+
+    o = 0
+    q = qkv[:, o: o + num_q * D].reshape(T, num_q, D); o += num_q * D
+    k = qkv[:, o: o + num_kv * D].reshape(T, num_kv, D); ko = o; o += num_kv * D
+    v = qkv[:, o: o + num_kv * D].reshape(T, num_kv, D); o += num_kv * D
+    q_out = nr(q, q_weight).contiguous()
+    k_out = nr(k, k_weight)
+    qkv[:, ko: ko + num_kv * D] = k_out.reshape(T, -1)
+    iq_out = ik_out = None
+    if num_index_q:
+        iq = nr(qkv[:, o: o + num_index_q * D].reshape(T, num_index_q, D), index_q_weight)
+        iq_out = fp8(iq) if index_fp8 else iq.contiguous()
+        o += num_index_q * D
+    if index_k:
+        ik_out = nr(qkv[:, o: o + D].reshape(T, 1, D), index_k_weight)[:, 0]
+    n = slot_mapping.numel()
+    for t in range(n):
+        s = int(slot_mapping[t])
+        if s < 0:
+            continue
+        if kv_cache is not None:
+            blk, pos = divmod(s, kv_cache.shape[2])
+            kv_cache[blk, 0, pos] = k_out[t]
+            kv_cache[blk, 1, pos] = v[t]
+        if index_k and index_cache is not None:
+            index_cache.view(-1, D)[s] = fp8(ik_out[t]) if index_fp8 else ik_out[t]
+    return q_out, iq_out
+
+
 def mla_rope_and_cache(q_pe, k_pe, kv_c, mla_cache, cos_sin_cache, positions, slot_mapping, is_neox: bool = False):
     """RoPE on ``q_pe [T,H,64]`` / ``k_pe [T,64]`` in place + insert ``[kv_c | k_pe]`` into the bf16 MLA cache."""
     if _cuda(q_pe):
