@@ -972,11 +972,12 @@ void ag_gemm(Tensor& out, const Tensor& w, const optional<Tensor>& bias, const T
   TORCH_CHECK(rc == 0, "ag_gemm: rows per rank must be a multiple of 128");
 }
 
-// ptrs: int64 CPU tensor [8, ep] = recv_x, recv_scale, recv_ids, recv_src, recv_count, disp_flag, comb_x, comb_flag
+// ptrs: int64 CPU tensor [9, ep] = recv_x, recv_scale, recv_ids, recv_src, recv_count, disp_flag, comb_x, comb_flag,
+// recv_w
 static b200::MoeA2aParams a2a_params(const Tensor& ptrs, int64_t ep, int64_t rank, int64_t experts_per_rank, int64_t H,
                                      int64_t topk, int64_t T, int64_t cap, bool quant, Tensor& local_sync,
                                      int64_t wait_cycles, const Tensor& any) {
-  TORCH_CHECK(ep >= 1 && ep <= b200::kMaxRanks && ptrs.dim() == 2 && ptrs.size(0) == 8 && ptrs.size(1) >= ep);
+  TORCH_CHECK(ep >= 1 && ep <= b200::kMaxRanks && ptrs.dim() == 2 && ptrs.size(0) == 9 && ptrs.size(1) >= ep);
   TORCH_CHECK(!ptrs.is_cuda() && ptrs.scalar_type() == at::kLong && H % 8 == 0 && (!quant || H % 128 == 0));
   TORCH_CHECK(local_sync.numel() >= 8 + ep && local_sync.element_size() == 4);
   b200::MoeA2aParams p{};
@@ -993,6 +994,7 @@ static b200::MoeA2aParams a2a_params(const Tensor& ptrs, int64_t ep, int64_t ran
     p.disp_flag[r] = reinterpret_cast<uint32_t*>(pp[5 * st + r]);
     p.comb_x[r] = reinterpret_cast<void*>(pp[6 * st + r]);
     p.comb_flag[r] = reinterpret_cast<uint32_t*>(pp[7 * st + r]);
+    p.recv_w[r] = reinterpret_cast<float*>(pp[8 * st + r]);
   }
   p.local_sync = reinterpret_cast<uint32_t*>(local_sync.data_ptr());
   p.wait_cycles = wait_cycles;
@@ -1000,47 +1002,48 @@ static b200::MoeA2aParams a2a_params(const Tensor& ptrs, int64_t ep, int64_t ran
   return p;
 }
 
-void moe_a2a_dispatch(const Tensor& x, const Tensor& topk_ids, const Tensor& ptrs, int64_t ep, int64_t rank,
-                      int64_t experts_per_rank, int64_t cap, bool quant, Tensor& local_sync, int64_t wait_cycles) {
+void moe_a2a_dispatch(const Tensor& x, const Tensor& topk_ids, const Tensor& topk_w, const Tensor& ptrs, int64_t ep,
+                      int64_t rank, int64_t experts_per_rank, int64_t cap, bool quant, Tensor& local_sync,
+                      int64_t wait_cycles) {
   TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && topk_ids.is_contiguous() && topk_ids.scalar_type() == at::kInt);
-  TORCH_CHECK(topk_ids.size(0) == x.size(0));
+  TORCH_CHECK(topk_ids.size(0) == x.size(0) && topk_w.is_contiguous() && topk_w.scalar_type() == at::kFloat &&
+              topk_w.sizes() == topk_ids.sizes() && x.size(0) <= cap);
   auto p = a2a_params(ptrs, ep, rank, experts_per_rank, x.size(1), topk_ids.size(1), x.size(0), cap, quant, local_sync,
                       wait_cycles, x);
   const c10::cuda::CUDAGuard guard(x.device());
-  b200::moe_a2a_dispatch(p, x.data_ptr(), topk_ids.data_ptr<int>(), dtype16(x), cur_stream());
+  b200::moe_a2a_dispatch(p, x.data_ptr(), topk_ids.data_ptr<int>(), topk_w.data_ptr<float>(), dtype16(x), cur_stream());
 }
 
-void moe_a2a_combine(Tensor& out, const Tensor& y, const Tensor& inv_pos, const Tensor& topk_w, const Tensor& topk_ids,
-                     const optional<Tensor>& shared_out, const Tensor& ptrs, int64_t ep, int64_t rank,
-                     int64_t experts_per_rank, int64_t cap, Tensor& local_sync, int64_t wait_cycles) {
-  TORCH_CHECK(y.dim() == 2 && y.is_contiguous() && out.is_contiguous() && out.size(1) == y.size(1));
-  TORCH_CHECK(inv_pos.numel() == ep * cap && inv_pos.scalar_type() == at::kInt && topk_w.scalar_type() == at::kFloat);
-  TORCH_CHECK(topk_w.is_contiguous() && topk_ids.is_contiguous() && topk_ids.scalar_type() == at::kInt);
-  TORCH_CHECK(topk_w.size(0) == out.size(0) && out.scalar_type() == y.scalar_type());
+// y [ep*cap, H]: weighted partial sums of the received tokens, one row per receive slot
+void moe_a2a_combine(Tensor& out, const Tensor& y, const Tensor& topk_ids, const optional<Tensor>& shared_out,
+                     const Tensor& ptrs, int64_t ep, int64_t rank, int64_t experts_per_rank, int64_t cap,
+                     Tensor& local_sync, int64_t wait_cycles) {
+  TORCH_CHECK(y.dim() == 2 && y.is_contiguous() && y.size(0) == ep * cap && out.is_contiguous() && out.size(1) == y.size(1));
+  TORCH_CHECK(topk_ids.is_contiguous() && topk_ids.scalar_type() == at::kInt && topk_ids.size(0) == out.size(0) &&
+              out.scalar_type() == y.scalar_type() && out.size(0) <= cap);
   if (shared_out.has_value()) TORCH_CHECK(shared_out->is_contiguous() && shared_out->sizes() == out.sizes());
   auto p = a2a_params(ptrs, ep, rank, experts_per_rank, y.size(1), topk_ids.size(1), out.size(0), cap, false,
                       local_sync, wait_cycles, y);
   const c10::cuda::CUDAGuard guard(y.device());
-  b200::moe_a2a_combine(p, y.data_ptr(), inv_pos.data_ptr<int>(), out.data_ptr(), topk_w.data_ptr<float>(),
-                        topk_ids.data_ptr<int>(), shared_out.has_value() ? shared_out->data_ptr() : nullptr,
-                        dtype16(y), cur_stream());
+  b200::moe_a2a_combine(p, y.data_ptr(), out.data_ptr(), topk_ids.data_ptr<int>(),
+                        shared_out.has_value() ? shared_out->data_ptr() : nullptr, dtype16(y), cur_stream());
 }
 
-// dst[i] = src[idx[i]] for i < count[0] (rows of any dtype whose byte width is a multiple of 16)
-void gather_rows(Tensor& dst, const Tensor& src, const Tensor& idx, const Tensor& count) {
+// dst[i] = src[idx[i] / div] for i < count[0] (rows of any dtype whose byte width is a multiple of 16)
+void gather_rows(Tensor& dst, const Tensor& src, const Tensor& idx, const Tensor& count, int64_t div) {
   TORCH_CHECK(dst.is_contiguous() && src.is_contiguous() && dst.dim() == 2 && src.dim() == 2);
   const int64_t row_bytes = src.size(1) * src.element_size();
   TORCH_CHECK(row_bytes % 16 == 0 && dst.size(1) * dst.element_size() == row_bytes && idx.numel() >= dst.size(0));
   const c10::cuda::CUDAGuard guard(src.device());
   b200::gather_rows(dst.data_ptr(), src.data_ptr(), idx.data_ptr<int>(), count.data_ptr<int>(), dst.size(0),
-                    src.size(0), row_bytes, cur_stream());
+                    src.size(0), row_bytes, (int)div, cur_stream());
 }
 
 }  // namespace
 
 TORCH_LIBRARY(b200, m) {
-  m.def("moe_a2a_dispatch(Tensor x, Tensor topk_ids, Tensor ptrs, int ep, int rank, int experts_per_rank, int cap, bool quant, Tensor(a!) local_sync, int wait_cycles) -> ()", &moe_a2a_dispatch);
-  m.def("moe_a2a_combine(Tensor(a!) out, Tensor y, Tensor inv_pos, Tensor topk_w, Tensor topk_ids, Tensor? shared_out, Tensor ptrs, int ep, int rank, int experts_per_rank, int cap, Tensor(b!) local_sync, int wait_cycles) -> ()", &moe_a2a_combine);
+  m.def("moe_a2a_dispatch(Tensor x, Tensor topk_ids, Tensor topk_w, Tensor ptrs, int ep, int rank, int experts_per_rank, int cap, bool quant, Tensor(a!) local_sync, int wait_cycles) -> ()", &moe_a2a_dispatch);
+  m.def("moe_a2a_combine(Tensor(a!) out, Tensor y, Tensor topk_ids, Tensor? shared_out, Tensor ptrs, int ep, int rank, int experts_per_rank, int cap, Tensor(b!) local_sync, int wait_cycles) -> ()", &moe_a2a_combine);
   m.def("v4_qnorm_rope_kv_insert(Tensor(a!) q_out, Tensor(b!) cache, Tensor q, Tensor kv, Tensor slot_mapping, Tensor positions, Tensor cos_sin, float eps, int block_size) -> ()", &v4_qnorm_rope_kv_insert);
   m.def("v4_gather_dequant(Tensor(a!) dst, Tensor cache, Tensor slots, int block_size) -> ()", &v4_gather_dequant);
   m.def("custom_allreduce(Tensor(a!) out, Tensor inp, Tensor ptrs, int tp, int rank, int cap_bytes, int max_ctas, Tensor(b!) local_sync, int mode, int wait_cycles) -> ()", &custom_allreduce);
@@ -1058,7 +1061,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("gather_indexer_k(Tensor(a!) dst_k, Tensor(b!) dst_s, Tensor cache, Tensor block_table, Tensor cu_seq_lens, int block_size) -> ()", &gather_indexer_k);
   m.def("selective_scan(Tensor(a!) out, Tensor u, Tensor delta, Tensor A, Tensor B, Tensor C, Tensor? D, Tensor? z, Tensor? delta_bias, bool delta_softplus, Tensor(b!) state, Tensor? query_start_loc, Tensor? cache_indices, Tensor? has_initial_state, int pad_slot) -> ()", &selective_scan);
   m.def("p2p_copy(int dst_ptr, Tensor src, int ctas, int mode) -> ()", &p2p_copy);
-  m.def("gather_rows(Tensor(a!) dst, Tensor src, Tensor idx, Tensor count) -> ()", &gather_rows);
+  m.def("gather_rows(Tensor(a!) dst, Tensor src, Tensor idx, Tensor count, int div) -> ()", &gather_rows);
   m.def("get_status(int device) -> Tensor", &get_status);
   m.def("topk_gating(Tensor(a!) weights, Tensor(b!) ids, Tensor gating, Tensor? bias, int mode, bool renorm, float scale) -> ()", &topk_gating);
   m.def("grouped_topk(Tensor(a!) weights, Tensor(b!) ids, Tensor gating, Tensor? bias, int n_group, int topk_group, bool sigmoid, bool renorm, float scale) -> ()", &grouped_topk);

@@ -49,14 +49,15 @@ struct AgGemmParams {
 
 // Expert-parallel all-to-all (comm_moe_a2a.cu).  Pointer arrays are indexed by the rank that OWNS the memory.
 struct MoeA2aParams {
-  int ep, rank, experts_per_rank, H, topk, T, cap, quant;
+  int ep, rank, experts_per_rank, H, topk, T, cap, quant;   // cap: tokens one source may send to one destination
   void* recv_x[kMaxRanks];          // [ep*cap][H] 16-bit rows, or e4m3 rows when quant
   float* recv_scale[kMaxRanks];     // [ep*cap][H/128] (quant only)
-  int* recv_ids[kMaxRanks];         // [ep*cap] local expert id, -1 = empty slot
-  int* recv_src[kMaxRanks];         // [ep*cap] pair index (t*topk + k) at the source
+  int* recv_ids[kMaxRanks];         // [ep*cap][topk] local expert ids of the token, -1 = not on this rank / empty slot
+  float* recv_w[kMaxRanks];         // [ep*cap][topk] routing weights (0 where the id is -1)
+  int* recv_src[kMaxRanks];         // [ep*cap] token index at the source
   uint32_t* recv_count[kMaxRanks];  // [ep] rows pushed by each source
   uint32_t* disp_flag[kMaxRanks];   // [ep] dispatch epoch per source
-  void* comb_x[kMaxRanks];          // [pairs_cap][H] 16-bit
+  void* comb_x[kMaxRanks];          // [ep (rank that computed)][cap][H] 16-bit partial sums
   uint32_t* comb_flag[kMaxRanks];   // [ep] combine epoch per source
   uint32_t* local_sync;             // [0] ticket, [1] dispatch epoch, [2] combine epoch, [8+r] send counters
   long long wait_cycles;

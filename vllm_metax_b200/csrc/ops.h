@@ -225,11 +225,12 @@ void p2p_copy(void* dst, const void* src, size_t nbytes, int ctas, int mode, voi
 int ag_gemm_copiers(int tp, int rows_per_rank);
 int ag_gemm(const AgGemmParams& p, const void* W, int ldw, void* C, const void* bias, int dtype, cudaStream_t stream);
 // ---- comm_moe_a2a.cu
-void moe_a2a_dispatch(const MoeA2aParams& p, const void* x, const int* topk_ids, int dtype, cudaStream_t stream);
-void moe_a2a_combine(const MoeA2aParams& p, const void* y, const int* inv_pos, void* out, const float* topk_w,
-                     const int* topk_ids, const void* shared_out, int dtype, cudaStream_t stream);
+void moe_a2a_dispatch(const MoeA2aParams& p, const void* x, const int* topk_ids, const float* topk_w, int dtype,
+                      cudaStream_t stream);
+void moe_a2a_combine(const MoeA2aParams& p, const void* y, void* out, const int* topk_ids, const void* shared_out,
+                     int dtype, cudaStream_t stream);
 void gather_rows(void* dst, const void* src, const int* idx, const int* count, int max_rows, int limit, int row_bytes,
-                 cudaStream_t stream);
+                 int div, cudaStream_t stream);
 // ---- v4_cache.cu
 void v4_qnorm_rope_kv_insert(const void* q_in, int64_t q_stride_t, int64_t q_stride_h, const void* kv, int64_t kv_stride,
                              void* q_out, void* cache, int64_t block_stride, const int64_t* slot_mapping,

@@ -79,7 +79,12 @@ class AgRsAll2AllManager:
 
 # ----------------------------------------------------------------------------- NVLink kernels
 class NvlinkAll2AllManager:
-    REGIONS = ("recv_x", "recv_scale", "recv_ids", "recv_src", "recv_count", "disp_flag", "comb_x", "comb_flag")
+    """Dispatch / combine by peer stores (``csrc/comm_moe_a2a.cu``).  A token is sent once per destination RANK
+    with its top-k list rewritten for that rank, so the receiver runs the ordinary local fused-MoE path on
+    ``(recv_x, recv_ids, recv_w)`` and returns one partial sum per received token."""
+
+    REGIONS = ("recv_x", "recv_scale", "recv_ids", "recv_src", "recv_count", "disp_flag", "comb_x", "comb_flag",
+               "recv_w")
 
     def __init__(self, group: Group, max_tokens_per_rank: int, hidden: int, topk: int, num_experts: int,
                  dtype: torch.dtype, device: torch.device, quant_fp8: bool = False, workspace=None):
@@ -90,14 +95,13 @@ class NvlinkAll2AllManager:
         self.H, self.topk, self.E_local = hidden, topk, num_experts // self.ep
         self.dtype, self.device, self.quant = dtype, device, quant_fp8
         self.max_tokens = max_tokens_per_rank
-        # worst case every pair of a source goes to one destination
-        self.cap = max_tokens_per_rank * min(topk, self.E_local)
+        self.cap = max_tokens_per_rank               # a source sends a token to a destination at most once
         slots = self.ep * self.cap
         esz = 1 if quant_fp8 else 2
         sizes = {
             "recv_x": slots * hidden * esz, "recv_scale": slots * (hidden // 128) * 4 if quant_fp8 else 16,
-            "recv_ids": slots * 4, "recv_src": slots * 4, "recv_count": 64, "disp_flag": 64,
-            "comb_x": max_tokens_per_rank * topk * hidden * 2, "comb_flag": 64,
+            "recv_ids": slots * topk * 4, "recv_w": slots * topk * 4, "recv_src": slots * 4, "recv_count": 64,
+            "disp_flag": 64, "comb_x": slots * hidden * 2, "comb_flag": 64,
         }
         total = sum((v + 1023) // 1024 * 1024 for v in sizes.values()) + 4096
         self.ws = workspace or SymmWorkspace(group, total, device)
@@ -105,28 +109,32 @@ class NvlinkAll2AllManager:
         self.ptrs = torch.tensor([self.ws.peer_ptrs(self.reg[k]) for k in self.REGIONS], dtype=torch.int64)
         self.recv_x = self.ws.local(self.reg["recv_x"], torch.uint8 if quant_fp8 else dtype, (slots, hidden))
         self.recv_scale = self.ws.local(self.reg["recv_scale"], torch.float32, (slots, hidden // 128)) if quant_fp8 else None
-        self.recv_ids = self.ws.local(self.reg["recv_ids"], torch.int32, (slots,))
+        self.recv_ids = self.ws.local(self.reg["recv_ids"], torch.int32, (slots, topk))
+        self.recv_w = self.ws.local(self.reg["recv_w"], torch.float32, (slots, topk))
         self.recv_ids.fill_(-1)
+        self.recv_w.zero_()
         for k in ("recv_count", "disp_flag", "comb_flag"):
             self.ws.local(self.reg[k], torch.int32, (16,)).zero_()
         self.local_sync = torch.zeros(32, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
         group.barrier()
 
-    def dispatch(self, x: torch.Tensor, topk_ids: torch.Tensor):
-        """Push this rank's (token, k) pairs; returns the receive views ``(recv_x, recv_scale, recv_ids)``."""
+    def dispatch(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor):
+        """Push this rank's tokens to the ranks that own their experts; returns the receive views
+        ``(recv_x [ep*cap, H], recv_scale, recv_ids [ep*cap, topk], recv_w [ep*cap, topk])`` (empty slots: ids -1)."""
         assert x.shape[0] <= self.max_tokens and x.shape[1] == self.H and x.dtype == self.dtype
-        torch.ops.b200.moe_a2a_dispatch(x.contiguous(), topk_ids.int().contiguous(), self.ptrs, self.ep, self.rank,
-                                        self.E_local, self.cap, self.quant, self.local_sync, WAIT_CYCLES)
-        return self.recv_x, self.recv_scale, self.recv_ids
+        torch.ops.b200.moe_a2a_dispatch(x.contiguous(), topk_ids.int().contiguous(), topk_weights.float().contiguous(),
+                                        self.ptrs, self.ep, self.rank, self.E_local, self.cap, self.quant,
+                                        self.local_sync, WAIT_CYCLES)
+        return self.recv_x, self.recv_scale, self.recv_ids, self.recv_w
 
-    def combine(self, y: torch.Tensor, inv_pos: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
+    def combine(self, y_tok: torch.Tensor, topk_ids: torch.Tensor,
                 shared_out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """``y`` = expert outputs in expert-sorted order, ``inv_pos [ep*cap]`` = row of each receive slot."""
+        """``y_tok [ep*cap, H]`` = weighted partial sum of every receive slot -> this rank's tokens, summed over the
+        ranks that computed a part of them (+ ``shared_out``)."""
         out = torch.empty(topk_ids.shape[0], self.H, dtype=self.dtype, device=self.device)
-        torch.ops.b200.moe_a2a_combine(out, y.contiguous(), inv_pos, topk_weights.float().contiguous(),
-                                       topk_ids.int().contiguous(), shared_out, self.ptrs, self.ep, self.rank,
-                                       self.E_local, self.cap, self.local_sync, WAIT_CYCLES)
+        torch.ops.b200.moe_a2a_combine(out, y_tok.contiguous(), topk_ids.int().contiguous(), shared_out, self.ptrs,
+                                       self.ep, self.rank, self.E_local, self.cap, self.local_sync, WAIT_CYCLES)
         return out
 
     def close(self) -> None:
@@ -135,18 +143,19 @@ class NvlinkAll2AllManager:
 
 def run_experts_a2a(mgr: NvlinkAll2AllManager, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
                     experts_fn: Callable, shared_out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """dispatch -> align -> gather -> ``experts_fn(a, a_scale, block_expert, total)`` -> combine.
+    """dispatch -> align -> gather -> ``experts_fn(a, a_scale, block_expert, total)`` -> weighted sum per received
+    token -> combine.
 
     ``experts_fn`` maps expert-sorted rows ``a [padded, H]`` (bf16, or fp8 with ``a_scale``) to outputs of the same
     row count (the two grouped GEMMs and the activation)."""
-    recv_x, recv_scale, recv_ids = mgr.dispatch(x, topk_ids)
-    sorted_ids, block_expert, total, inv = ops.moe_align_block_size(recv_ids.view(-1, 1), 128, mgr.E_local, None,
-                                                                    want_inverse=True)
+    recv_x, recv_scale, recv_ids, recv_w = mgr.dispatch(x, topk_weights, topk_ids)
+    sorted_ids, block_expert, total, inv = ops.moe_align_block_size(recv_ids, 128, mgr.E_local, None, want_inverse=True)
     a = torch.empty(sorted_ids.numel(), recv_x.shape[1], dtype=recv_x.dtype, device=recv_x.device)
-    torch.ops.b200.gather_rows(a, recv_x, sorted_ids, total)
+    torch.ops.b200.gather_rows(a, recv_x, sorted_ids, total, mgr.topk)
     a_scale = None
     if recv_scale is not None:
         a_scale = torch.empty(sorted_ids.numel(), recv_scale.shape[1], dtype=torch.float32, device=recv_x.device)
-        torch.ops.b200.gather_rows(a_scale, recv_scale, sorted_ids, total)
+        torch.ops.b200.gather_rows(a_scale, recv_scale, sorted_ids, total, mgr.topk)
     y = experts_fn(a, a_scale, block_expert, total)
-    return mgr.combine(y, inv, topk_weights, topk_ids, shared_out)
+    y_tok = ops.moe_combine(y, recv_w, inv, recv_ids.shape[0], None)
+    return mgr.combine(y_tok, topk_ids, shared_out)
