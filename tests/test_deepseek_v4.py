@@ -147,3 +147,62 @@ def test_v4_records_kernel_matches_reference():
     assert same > 0.98, same
     # the kernel's own reader agrees with the PyTorch reader on the kernel's bytes
     torch.testing.assert_close(got, vc.gather_dequant_ref(cache.cpu(), slots.cpu(), bs).float(), rtol=0, atol=0)
+
+
+def _cs64(n=300):
+    ang = torch.arange(n)[:, None].float() * (1.0 / 10000 ** (torch.arange(32).float() / 32))[None]
+    return torch.cat([ang.cos(), ang.sin()], -1)
+
+
+def test_v4_inv_rope_undoes_the_insert_rotation():
+    from vllm_metax_b200.ops import v4_cache as vc
+
+    g = torch.Generator().manual_seed(5)
+    T, H = 9, 4
+    x = torch.randn(T, H, 512, generator=g)
+    pos = torch.randint(0, 300, (T,), generator=g)
+    cs = _cs64()
+    rot = torch.cat([x[..., :448], vc._rope_interleaved(x[..., 448:], cs[pos][:, None, :])], -1)
+    back = vc.inv_rope(rot, pos, cs, n_groups=2)
+    assert back.shape == (T, 2, 2 * 512)
+    torch.testing.assert_close(back.reshape(T, H, 512), x, rtol=1e-5, atol=1e-5)
+
+
+def test_v4_indexer_q_reference_contract():
+    from vllm_metax_b200.ops import v4_cache as vc
+
+    g = torch.Generator().manual_seed(6)
+    T, H = 7, 3
+    q = torch.randn(T, H, 128, generator=g)
+    w = torch.randn(T, H, generator=g)
+    pos = torch.randint(0, 300, (T,), generator=g)
+    q8, w_out = vc.indexer_q_rope_int8_quant(pos, q, _cs64(), w, 0.5, 0.25)
+    assert q8.dtype == torch.int8 and q8.abs().max() == 127
+    # q8 * folded weight reproduces (rotated q) * w * softmax_scale * head_scale
+    want = torch.cat([q[..., :64], vc._rope_interleaved(q[..., 64:], _cs64()[pos][:, None, :])], -1)
+    got = q8.float() * (w_out / (w * 0.125))[..., None]
+    torch.testing.assert_close(got, want, rtol=0, atol=float(want.abs().max()) / 127 + 1e-2)
+
+
+@pytest.mark.gpu
+def test_v4_inv_rope_and_indexer_q_kernels():
+    from vllm_metax_b200.ops import v4_cache as vc
+
+    g = torch.Generator().manual_seed(7)
+    T, H = 45, 8
+    cs = _cs64()
+    pos = torch.randint(0, 300, (T,), generator=g)
+    o = torch.randn(T, H, 512, generator=g).to(torch.bfloat16)
+    wide = torch.zeros(T, H, 528, dtype=torch.bfloat16, device="cuda")
+    wide[..., :512] = o.cuda()
+    got = vc.inv_rope(wide[..., :512], pos.cuda(), cs.cuda(), n_groups=4)
+    want = vc.inv_rope(o, pos, cs, n_groups=4)
+    assert got.shape == want.shape
+    torch.testing.assert_close(got.float().cpu(), want.float(), rtol=2e-2, atol=2e-2)
+    q = torch.randn(T, H, 128, generator=g).to(torch.bfloat16)
+    w = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    q8, w_out = vc.indexer_q_rope_int8_quant(pos.cuda(), q.cuda(), cs.cuda(), w.cuda(), 0.5, 0.25)
+    q8_ref, w_ref = vc.indexer_q_rope_int8_quant(pos, q, cs, w, 0.5, 0.25)
+    torch.testing.assert_close(w_out.cpu(), w_ref, rtol=1e-2, atol=1e-5)
+    assert (q8.cpu().int() - q8_ref.int()).abs().max() <= 1
+    assert (q8.cpu() == q8_ref).float().mean() > 0.97

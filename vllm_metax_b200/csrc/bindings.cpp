@@ -884,6 +884,37 @@ void v4_gather_dequant(Tensor& dst, const Tensor& cache, const Tensor& slots, in
                           (int)block_size, cur_stream());
 }
 
+// o [T, H, 512] -> out [G, T, (H / G) * 512] with the rope dims rotated back
+void v4_inv_rope(Tensor& out, const Tensor& o, const Tensor& positions, const Tensor& cos_sin, int64_t n_groups) {
+  TORCH_CHECK(o.dim() == 3 && o.size(2) == 512 && o.stride(2) == 1 && o.stride(0) % 8 == 0 && o.stride(1) % 8 == 0);
+  TORCH_CHECK(n_groups >= 1 && o.size(1) % n_groups == 0 && out.is_contiguous() && out.numel() == o.numel() &&
+              out.scalar_type() == o.scalar_type());
+  TORCH_CHECK(positions.scalar_type() == at::kLong && positions.is_contiguous() && positions.numel() >= o.size(0));
+  TORCH_CHECK(cos_sin.scalar_type() == at::kFloat && cos_sin.dim() == 2 && cos_sin.size(1) == 64 && cos_sin.is_contiguous());
+  const c10::cuda::CUDAGuard guard(o.device());
+  b200::v4_inv_rope(out.data_ptr(), o.data_ptr(), o.stride(0), o.stride(1), positions.data_ptr<int64_t>(),
+                    cos_sin.data_ptr<float>(), (int)o.size(0), (int)o.size(1), (int)(o.size(1) / n_groups), dtype16(o),
+                    cur_stream());
+}
+
+// q [T, H, 128] -> q8 int8 [T, H, 128], w_out f32 [T, H] = weights * q_scale * softmax_scale * head_scale
+void v4_indexer_q(Tensor& q8, Tensor& w_out, const Tensor& q, const Tensor& weights, const Tensor& positions,
+                  const Tensor& cos_sin, double softmax_scale, double head_scale) {
+  TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.stride(2) == 1 && q.stride(0) % 4 == 0 && q.stride(1) % 4 == 0);
+  TORCH_CHECK(q8.is_contiguous() && q8.element_size() == 1 && q8.numel() == q.numel());
+  TORCH_CHECK(w_out.is_contiguous() && w_out.scalar_type() == at::kFloat && w_out.numel() == q.size(0) * q.size(1));
+  TORCH_CHECK(weights.dim() == 2 && weights.size(0) == q.size(0) && weights.size(1) == q.size(1) &&
+              weights.stride(1) == 1 && weights.scalar_type() == q.scalar_type());
+  TORCH_CHECK(positions.scalar_type() == at::kLong && positions.is_contiguous() && positions.numel() >= q.size(0));
+  TORCH_CHECK(cos_sin.scalar_type() == at::kFloat && cos_sin.dim() == 2 && cos_sin.is_contiguous() &&
+              cos_sin.size(1) % 4 == 0 && cos_sin.size(1) <= 128);
+  const c10::cuda::CUDAGuard guard(q.device());
+  b200::v4_indexer_q(q8.data_ptr(), w_out.data_ptr<float>(), q.data_ptr(), q.stride(0), q.stride(1), weights.data_ptr(),
+                     weights.stride(0), positions.data_ptr<int64_t>(), cos_sin.data_ptr<float>(), (int)q.size(0),
+                     (int)q.size(1), (int)cos_sin.size(1), (float)softmax_scale, (float)head_scale, dtype16(q),
+                     cur_stream());
+}
+
 // ptrs: int64 CPU tensor [4, tp] = recv, gather, flag1, flag2 (per owning rank)
 void custom_allreduce(Tensor& out, const Tensor& inp, const Tensor& ptrs, int64_t tp, int64_t rank, int64_t cap_bytes,
                       int64_t max_ctas, Tensor& local_sync, int64_t mode, int64_t wait_cycles) {
@@ -1046,6 +1077,8 @@ TORCH_LIBRARY(b200, m) {
   m.def("moe_a2a_combine(Tensor(a!) out, Tensor y, Tensor topk_ids, Tensor? shared_out, Tensor ptrs, int ep, int rank, int experts_per_rank, int cap, Tensor(b!) local_sync, int wait_cycles) -> ()", &moe_a2a_combine);
   m.def("v4_qnorm_rope_kv_insert(Tensor(a!) q_out, Tensor(b!) cache, Tensor q, Tensor kv, Tensor slot_mapping, Tensor positions, Tensor cos_sin, float eps, int block_size) -> ()", &v4_qnorm_rope_kv_insert);
   m.def("v4_gather_dequant(Tensor(a!) dst, Tensor cache, Tensor slots, int block_size) -> ()", &v4_gather_dequant);
+  m.def("v4_inv_rope(Tensor(a!) out, Tensor o, Tensor positions, Tensor cos_sin, int n_groups) -> ()", &v4_inv_rope);
+  m.def("v4_indexer_q(Tensor(a!) q8, Tensor(b!) w_out, Tensor q, Tensor weights, Tensor positions, Tensor cos_sin, float softmax_scale, float head_scale) -> ()", &v4_indexer_q);
   m.def("custom_allreduce(Tensor(a!) out, Tensor inp, Tensor ptrs, int tp, int rank, int cap_bytes, int max_ctas, Tensor(b!) local_sync, int mode, int wait_cycles) -> ()", &custom_allreduce);
   m.def("reduce_rms(Tensor(a!) out0, Tensor x0, Tensor w0, Tensor(b!)? out1, Tensor? x1, Tensor? w1, float eps, Tensor slots_ptrs, int tp, int rank, int t_cap, Tensor(c!) local_sync, int wait_cycles) -> ()", &reduce_rms);
   m.def("ag_gemm(Tensor(a!) out, Tensor w, Tensor? bias, Tensor ptrs, Tensor(b!) gathered, Tensor(c!) ready, Tensor(d!) sync, int tp, int rank, int rows_per_rank, int wait_cycles) -> ()", &ag_gemm);

@@ -238,6 +238,11 @@ void v4_qnorm_rope_kv_insert(const void* q_in, int64_t q_stride_t, int64_t q_str
                              int hq_pad, int block_size, float eps, cudaStream_t stream);
 void v4_gather_dequant(void* dst, const void* cache, int64_t block_stride, const int64_t* slots, int n, int block_size,
                        cudaStream_t stream);
+void v4_inv_rope(void* out, const void* o, int64_t o_stride_t, int64_t o_stride_h, const int64_t* positions,
+                 const float* cos_sin, int tokens, int heads, int hpg, int dtype, cudaStream_t stream);
+void v4_indexer_q(void* q8, float* w_out, const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* weights,
+                  int64_t w_stride, const int64_t* positions, const float* cos_sin, int tokens, int heads, int rot,
+                  float softmax_scale, float head_scale, int dtype, cudaStream_t stream);
 // ---- comm_allreduce.cu
 int custom_allreduce(const CustomArParams& p, const void* in, void* out, int dtype, int mode, cudaStream_t stream);
 int reduce_rms(const ReduceRmsParams& p, int dtype, cudaStream_t stream);

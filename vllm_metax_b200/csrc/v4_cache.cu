@@ -13,6 +13,10 @@
 //       slot == Hq_padded   record(slot_mapping[t]) = quant(rope(kv[t]))      (skipped for t >= insert tokens, slot < 0)
 //     RoPE is the interleaved (GPT-J) form on dims [448, 512) with an fp32 cos|sin table row per position.
 //   v4_gather_dequant         dst[i] = bf16(record(slots[i])), slots < 0 -> zeros.
+//   v4_inv_rope               attention output: inverse RoPE on the rope dims + regrouping of the heads for the grouped
+//                             output projection (vllm_metax/models/deepseek_v4/ops/fused_inv_rope_quant.py:9-166)
+//   v4_indexer_q              indexer query: RoPE + per-(token, head) int8 quantisation, scale folded into the head
+//                             weights (vllm_metax/models/deepseek_v4/ops/fused_indexer_q.py:36-205)
 // Memory-bound elementwise work: every global access is a 16-byte vector, one pass over the data.
 // Covers csrc/libtorch_stable/fused_deepseek_v4_qnorm_rope_kv_insert_kernel.cu:165-480 of the reference and the
 // read side of its _gather_k_cache_kernel (vllm_metax/models/deepseek_v4/ops/cache_utils.py:7).
@@ -163,6 +167,121 @@ v4_gather_dequant_kernel(__nv_bfloat16* __restrict__ dst, const uint8_t* __restr
 #pragma unroll
     for (int k = 0; k < 4; ++k) e[4 * j + k] = fp8_e4m3_to_float((uint8_t)(wds[j] >> (8 * k))) * scale;
   v4_store16(out, e);
+}
+
+// Attention output -> o_proj input: the rope dims of every head are rotated BACK (inverse of the interleaved
+// RoPE) and the heads are regrouped [T, G * hpg, 512] -> [G, T, hpg * 512] for the grouped output projection.
+template <typename T>
+__global__ void __launch_bounds__(256)
+v4_inv_rope_kernel(T* __restrict__ out, const T* __restrict__ o, int64_t o_stride_t, int64_t o_stride_h,
+                   const int64_t* __restrict__ positions, const float* __restrict__ cos_sin, int tokens, int heads,
+                   int hpg) {
+  const int lane = threadIdx.x & 31;
+  const int64_t w = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (int64_t)tokens * heads) return;
+  const int t = (int)(w / heads), h = (int)(w % heads);
+  const int d0 = lane * 16;
+  const T* src = o + (int64_t)t * o_stride_t + (int64_t)h * o_stride_h + d0;
+  uint4 a = reinterpret_cast<const uint4*>(src)[0], b = reinterpret_cast<const uint4*>(src)[1];
+  if (d0 >= kV4Nope) {
+    float e[16], x[8], y[8];
+    unpack8<T>(a, x);
+    unpack8<T>(b, y);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { e[i] = x[i]; e[8 + i] = y[i]; }
+    const float* row = cos_sin + positions[t] * kV4Rope;
+    const int p0 = (d0 - kV4Nope) >> 1;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float c = row[p0 + i], s = row[32 + p0 + i];
+      const float u = e[2 * i], v = e[2 * i + 1];
+      e[2 * i] = u * c + v * s;
+      e[2 * i + 1] = v * c - u * s;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { x[i] = e[i]; y[i] = e[8 + i]; }
+    a = pack8<T>(x);
+    b = pack8<T>(y);
+  }
+  const int g = h / hpg, hi = h % hpg;
+  T* dst = out + ((int64_t)g * tokens + t) * ((int64_t)hpg * kV4Head) + (int64_t)hi * kV4Head + d0;
+  reinterpret_cast<uint4*>(dst)[0] = a;
+  reinterpret_cast<uint4*>(dst)[1] = b;
+}
+
+// Indexer query: interleaved RoPE on the last `rot` dims of every 128-wide head, symmetric int8 quantisation with
+// one scale per (token, head) (round half away from zero), and the scale folded into the head weight:
+// w_out = w * q_scale * softmax_scale * head_scale, so the logits kernel needs no per-head dequantisation.
+template <typename T>
+__global__ void __launch_bounds__(256)
+v4_indexer_q_kernel(int8_t* __restrict__ q8, float* __restrict__ w_out, const T* __restrict__ q, int64_t q_stride_t,
+                    int64_t q_stride_h, const T* __restrict__ weights, int64_t w_stride,
+                    const int64_t* __restrict__ positions, const float* __restrict__ cos_sin, int tokens, int heads,
+                    int rot, float softmax_scale, float head_scale) {
+  const int lane = threadIdx.x & 31;
+  const int64_t w = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (int64_t)tokens * heads) return;
+  const int t = (int)(w / heads), h = (int)(w % heads);
+  const int d0 = lane * 4, nope = 128 - rot;
+  const uint2 raw = *reinterpret_cast<const uint2*>(q + (int64_t)t * q_stride_t + (int64_t)h * q_stride_h + d0);
+  const T* e = reinterpret_cast<const T*>(&raw);
+  float v[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = to_f(e[i]);
+  if (d0 >= nope) {
+    const float* row = cos_sin + positions[t] * rot;
+    const int half = rot >> 1, p0 = (d0 - nope) >> 1;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float c = row[p0 + i], s = row[half + p0 + i];
+      const float x = v[2 * i], y = v[2 * i + 1];
+      v[2 * i] = __bfloat162float(__float2bfloat16_rn(x * c - y * s));       // the unfused path materialises bf16
+      v[2 * i + 1] = __bfloat162float(__float2bfloat16_rn(y * c + x * s));
+    }
+  }
+  float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  m = warp_max(m);
+  const float scale = m > 0.f ? m / 127.f : 1.f;
+  uint32_t pk = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float r = v[i] / scale;
+    float qv = r >= 0.f ? floorf(r + 0.5f) : ceilf(r - 0.5f);
+    qv = fminf(fmaxf(qv, -127.f), 127.f);
+    pk |= (uint32_t)(uint8_t)(int8_t)(int)qv << (8 * i);
+  }
+  *reinterpret_cast<uint32_t*>(q8 + ((int64_t)t * heads + h) * 128 + d0) = pk;
+  if (lane == 0)
+    w_out[(int64_t)t * heads + h] = to_f(weights[(int64_t)t * w_stride + h]) * scale * softmax_scale * head_scale;
+}
+
+void v4_inv_rope(void* out, const void* o, int64_t o_stride_t, int64_t o_stride_h, const int64_t* positions,
+                 const float* cos_sin, int tokens, int heads, int hpg, int dtype, cudaStream_t stream) {
+  const int64_t warps = (int64_t)tokens * heads;
+  if (warps <= 0) return;
+  const unsigned blocks = (unsigned)((warps + 7) / 8);
+  if (dtype == 0)
+    v4_inv_rope_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)o, o_stride_t,
+                                                                  o_stride_h, positions, cos_sin, tokens, heads, hpg);
+  else
+    v4_inv_rope_kernel<__half><<<blocks, 256, 0, stream>>>((__half*)out, (const __half*)o, o_stride_t, o_stride_h,
+                                                           positions, cos_sin, tokens, heads, hpg);
+}
+
+void v4_indexer_q(void* q8, float* w_out, const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* weights,
+                  int64_t w_stride, const int64_t* positions, const float* cos_sin, int tokens, int heads, int rot,
+                  float softmax_scale, float head_scale, int dtype, cudaStream_t stream) {
+  const int64_t warps = (int64_t)tokens * heads;
+  if (warps <= 0) return;
+  const unsigned blocks = (unsigned)((warps + 7) / 8);
+  if (dtype == 0)
+    v4_indexer_q_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
+        (int8_t*)q8, w_out, (const __nv_bfloat16*)q, q_stride_t, q_stride_h, (const __nv_bfloat16*)weights, w_stride,
+        positions, cos_sin, tokens, heads, rot, softmax_scale, head_scale);
+  else
+    v4_indexer_q_kernel<__half><<<blocks, 256, 0, stream>>>((int8_t*)q8, w_out, (const __half*)q, q_stride_t, q_stride_h,
+                                                            (const __half*)weights, w_stride, positions, cos_sin, tokens,
+                                                            heads, rot, softmax_scale, head_scale);
 }
 
 void v4_qnorm_rope_kv_insert(const void* q_in, int64_t q_stride_t, int64_t q_stride_h, const void* kv, int64_t kv_stride,

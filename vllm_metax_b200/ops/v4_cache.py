@@ -106,3 +106,55 @@ def gather_dequant(cache, slots, block_size: int):
     ops._launches += 1
     torch.ops.b200.v4_gather_dequant(out, cache, slots.long().contiguous(), block_size)
     return out
+
+
+def inv_rope(o: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor, n_groups: int) -> torch.Tensor:
+    """Attention output ``o [T, H, 512]`` -> ``[T, n_groups, (H / n_groups) * 512]`` with the rope dims of every head
+    rotated back (inverse interleaved RoPE); storage is group-major (``[G, T, d]``, returned transposed) so that
+    each group's slab feeds one GEMM of the grouped output projection."""
+    T, H, _ = o.shape
+    hpg = H // n_groups
+    if o.is_cuda:
+        from .. import _custom_ops as ops
+
+        ops.load_native()
+        out = torch.empty(n_groups, T, hpg * HEAD, dtype=o.dtype, device=o.device)
+        ops._launches += 1
+        torch.ops.b200.v4_inv_rope(out, o, positions.long().contiguous(), cos_sin, n_groups)
+        return out.transpose(0, 1)
+    rows = cos_sin[positions[:T]].float()[:, None, :]
+    cos, sin = rows[..., :32], rows[..., 32:]
+    x = o.float()
+    a, b = x[..., NOPE::2], x[..., NOPE + 1::2]
+    rot = torch.stack((a * cos + b * sin, b * cos - a * sin), dim=-1).flatten(-2)
+    y = torch.cat([x[..., :NOPE], rot], -1).to(o.dtype)
+    return y.reshape(T, n_groups, hpg * HEAD)
+
+
+def indexer_q_rope_int8_quant(positions, index_q, cos_sin, index_weights, softmax_scale: float, head_scale: float):
+    """``index_q [T, H, 128]``: interleaved RoPE on the last ``cos_sin.shape[1]`` dims, int8 quantisation with one scale
+    per (token, head); returns ``(q_int8 [T, H, 128], weights_out [T, H] f32)`` with
+    ``weights_out = index_weights * q_scale * softmax_scale * head_scale``."""
+    T, H, D = index_q.shape
+    if index_q.is_cuda:
+        from .. import _custom_ops as ops
+
+        ops.load_native()
+        q8 = torch.empty(T, H, D, dtype=torch.int8, device=index_q.device)
+        w_out = torch.empty(T, H, dtype=torch.float32, device=index_q.device)
+        ops._launches += 1
+        torch.ops.b200.v4_indexer_q(q8, w_out, index_q, index_weights, positions.long().contiguous(), cos_sin,
+                                    softmax_scale, head_scale)
+        return q8, w_out
+    rot = cos_sin.shape[1]
+    rows = cos_sin[positions[:T]].float()[:, None, :]
+    cos, sin = rows[..., : rot // 2], rows[..., rot // 2:]
+    x = index_q.float()
+    a, b = x[..., D - rot::2], x[..., D - rot + 1::2]
+    r = torch.stack((a * cos - b * sin, b * cos + a * sin), dim=-1).flatten(-2).to(torch.bfloat16).float()
+    x = torch.cat([x[..., : D - rot], r], -1)
+    amax = x.abs().amax(-1, keepdim=True)
+    scale = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax))
+    v = x / scale
+    q8 = torch.where(v >= 0, torch.floor(v + 0.5), torch.ceil(v - 0.5)).clamp(-127, 127).to(torch.int8)
+    return q8, index_weights.float() * scale[..., 0] * softmax_scale * head_scale
