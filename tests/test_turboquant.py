@@ -1,0 +1,119 @@
+"""TurboQuant KV cache: the fp32 statement on CPU (error bounds of the format) and the CUDA kernels against it."""
+import math
+import os
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from vllm_metax_b200.ops import turboquant as tq  # noqa: E402
+
+gpu = pytest.mark.gpu
+NAMES = list(tq.PRESETS)
+
+
+def test_formats():
+    f = tq.TqFormat.from_name("turboquant_4bit_nc")
+    assert (f.kbits, f.vbits, f.nc, f.slot_bytes) == (4, 4, True, 144)
+    assert tq.TqFormat.from_name("turboquant_3bit_nc").slot_bytes == 112
+    assert tq.TqFormat.from_name("turboquant_k8v4").slot_bytes == 208
+    assert tq.TqFormat.from_name("turboquant_4bit_nc").compression > 3.5
+    assert tq.is_turboquant("turboquant_k3v4_nc") and not tq.is_turboquant("fp8") and not tq.is_turboquant(None)
+    with pytest.raises(ValueError):
+        tq.TqFormat.from_name("turboquant_2bit")
+    h = tq.hadamard()
+    torch.testing.assert_close(h @ h, torch.eye(128), rtol=0, atol=1e-5)
+    torch.testing.assert_close(h, h.t())
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_reference_error_bounds(name):
+    fmt = tq.TqFormat.from_name(name)
+    g = torch.Generator().manual_seed(0)
+    k = torch.randn(64, 2, 128, generator=g) * 3
+    v = torch.randn(64, 2, 128, generator=g)
+    kh, vh = tq.quant_dequant_ref(k, v, fmt)
+    cos = torch.nn.functional.cosine_similarity(kh, k, dim=-1)
+    assert cos.min() > {8: 0.995, 4: 0.98, 3: 0.95}[fmt.kbits]
+    if fmt.nc:      # the reconstructed key keeps its length
+        torch.testing.assert_close(kh.norm(dim=-1), k.norm(dim=-1), rtol=2e-3, atol=1e-3)
+    step = (v.amax(-1) - v.amin(-1)) / ((1 << fmt.vbits) - 1)
+    assert ((vh - v).abs().amax(-1) <= step * 0.51 + 2e-2).all()
+
+
+def test_cpu_ops_round_trip():
+    fmt = tq.TqFormat.from_name("turboquant_4bit_nc")
+    g = torch.Generator().manual_seed(1)
+    cache = tq.alloc_cache(4, 16, 2, fmt, "cpu")
+    lens = [5, 33]
+    bt = torch.tensor([[2, -1, -1], [1, 3, 0]], dtype=torch.int32)
+    ks, vs = [], []
+    for b, L in enumerate(lens):
+        k = torch.randn(L, 2 * 128, generator=g)
+        v = torch.randn(L, 2 * 128, generator=g)
+        slots = tq._slots_of(bt[b], L, 16)
+        tq.store(k, v, cache, slots, fmt)
+        ks.append(k.reshape(L, 2, 128))
+        vs.append(v.reshape(L, 2, 128))
+    q = torch.randn(2, 8, 128, generator=g)
+    got = tq.decode_attention(q, cache, bt, torch.tensor(lens), 0.09, fmt)
+    exact = tq.decode_attention_ref(q, ks, vs, torch.tensor(lens), 0.09)
+    assert torch.nn.functional.cosine_similarity(got.flatten(), exact.flatten(), dim=0) > 0.97
+
+
+def _case(fmt, B=3, hkv=2, G=4, bs=16, lens=(1, 70, 333)):
+    g = torch.Generator().manual_seed(2)
+    nb = sum((L + bs - 1) // bs for L in lens) + 2
+    perm = torch.randperm(nb, generator=g)
+    mb = max((L + bs - 1) // bs for L in lens)
+    bt = torch.zeros(B, mb, dtype=torch.int32)
+    used = 0
+    ks, vs, slots = [], [], []
+    for b, L in enumerate(lens):
+        n = (L + bs - 1) // bs
+        bt[b, :n] = perm[used: used + n].int()
+        used += n
+        ks.append((torch.randn(L, hkv * 128, generator=g) * 2).to(torch.bfloat16))
+        vs.append(torch.randn(L, hkv * 128, generator=g).to(torch.bfloat16))
+        slots.append(tq._slots_of(bt[b], L, bs))
+    q = torch.randn(B, hkv * G, 128, generator=g).to(torch.bfloat16)
+    return nb, bs, hkv, bt, ks, vs, slots, q
+
+
+@gpu
+@pytest.mark.parametrize("name", NAMES)
+def test_store_dequant_decode_kernels(name):
+    fmt = tq.TqFormat.from_name(name)
+    nb, bs, hkv, bt, ks, vs, slots, q = _case(fmt)
+    cache = tq.alloc_cache(nb, bs, hkv, fmt, "cuda")
+    assert cache.shape[-1] == torch.ops.b200.tq_slot_bytes(fmt.kbits, fmt.vbits)
+    k_all, v_all, s_all = torch.cat(ks), torch.cat(vs), torch.cat(slots)
+    s_in = s_all.clone()
+    s_in[3] = -1                                     # a skipped token
+    wide = torch.zeros(k_all.shape[0], k_all.shape[1] + 64, dtype=torch.bfloat16, device="cuda")
+    wide[:, : k_all.shape[1]] = k_all.cuda()
+    tq.store(wide[:, : k_all.shape[1]], v_all.cuda(), cache, s_in.cuda(), fmt)
+    kd, vd = tq.dequant(cache, s_all.cuda(), fmt)
+    k_ref, v_ref = tq.quant_dequant_ref(k_all.reshape(-1, hkv, 128), v_all.reshape(-1, hkv, 128), fmt)
+    assert kd[3].abs().max() == 0 and vd[3].abs().max() == 0
+    keep = torch.ones(s_all.numel(), dtype=torch.bool)
+    keep[3] = False
+    # a coordinate that sits on a level boundary may fall either way: compare vectors, not codes
+    cos = torch.nn.functional.cosine_similarity(kd.float().cpu()[keep], k_ref[keep], dim=-1)
+    assert cos.min() > 0.995, cos.min()
+    torch.testing.assert_close(vd.float().cpu()[keep], v_ref[keep], rtol=2e-2, atol=8e-2)
+    # decode: the kernel against attention over the kernel's own dequantised rows
+    tq.store(k_all.cuda(), v_all.cuda(), cache, s_all.cuda(), fmt)
+    kd, vd = tq.dequant(cache, s_all.cuda(), fmt, torch.bfloat16)
+    lens = torch.tensor([k.shape[0] for k in ks])
+    offs = [0] + lens.cumsum(0).tolist()
+    kh = [kd[offs[b]: offs[b + 1]].float().cpu() for b in range(len(ks))]
+    vh = [vd[offs[b]: offs[b + 1]].float().cpu() for b in range(len(ks))]
+    want = tq.decode_attention_ref(q.float(), kh, vh, lens, 1 / math.sqrt(128))
+    for splits in (1, 3):
+        got = tq.decode_attention(q.cuda(), cache, bt.cuda(), lens.cuda(), 1 / math.sqrt(128), fmt, num_splits=splits)
+        torch.testing.assert_close(got.float().cpu(), want, rtol=3e-2, atol=3e-2)
+    torch.cuda.synchronize()

@@ -884,6 +884,61 @@ void v4_gather_dequant(Tensor& dst, const Tensor& cache, const Tensor& slots, in
                           (int)block_size, cur_stream());
 }
 
+// TurboQuant cache: uint8 [blocks, block_size, kv_heads, slot_bytes]; k, v [T, kv_heads * 128] (any row pitch)
+int64_t tq_slot_bytes(int64_t kbits, int64_t vbits) { return b200::tq_slot_bytes((int)kbits, (int)vbits); }
+
+void tq_store(Tensor& cache, const Tensor& k, const Tensor& v, const Tensor& slot_mapping, int64_t kbits, int64_t vbits,
+              bool nc) {
+  TORCH_CHECK(cache.dim() == 4 && cache.is_contiguous() && cache.element_size() == 1 &&
+              cache.size(3) == b200::tq_slot_bytes((int)kbits, (int)vbits));
+  const int64_t heads = cache.size(2);
+  TORCH_CHECK(k.dim() == 2 && v.dim() == 2 && k.size(1) == heads * 128 && v.size(1) == heads * 128 && k.stride(1) == 1 &&
+              v.stride(1) == 1 && k.stride(0) % 4 == 0 && v.stride(0) % 4 == 0 && k.scalar_type() == v.scalar_type());
+  TORCH_CHECK(slot_mapping.scalar_type() == at::kLong && slot_mapping.is_contiguous() && slot_mapping.numel() <= k.size(0));
+  const c10::cuda::CUDAGuard guard(k.device());
+  const int rc = b200::tq_store(cache.data_ptr(), k.data_ptr(), v.data_ptr(), k.stride(0), v.stride(0),
+                                slot_mapping.data_ptr<int64_t>(), (int)slot_mapping.numel(), (int)heads,
+                                cache.size(0) * cache.size(1), (int)kbits, (int)vbits, nc, dtype16(k), cur_stream());
+  TORCH_CHECK(rc == 0, "tq_store: unsupported bit widths");
+}
+
+void tq_dequant(Tensor& k_out, Tensor& v_out, const Tensor& cache, const Tensor& slots, int64_t kbits, int64_t vbits,
+                bool nc) {
+  TORCH_CHECK(cache.dim() == 4 && cache.is_contiguous() && cache.size(3) == b200::tq_slot_bytes((int)kbits, (int)vbits));
+  const int64_t heads = cache.size(2), rows = slots.numel();
+  TORCH_CHECK(k_out.is_contiguous() && v_out.is_contiguous() && k_out.numel() == rows * heads * 128 &&
+              v_out.numel() == k_out.numel() && k_out.scalar_type() == v_out.scalar_type());
+  TORCH_CHECK(slots.scalar_type() == at::kLong && slots.is_contiguous());
+  const c10::cuda::CUDAGuard guard(cache.device());
+  const int rc = b200::tq_dequant(k_out.data_ptr(), v_out.data_ptr(), cache.data_ptr(), slots.data_ptr<int64_t>(),
+                                  (int)rows, (int)heads, (int)kbits, (int)vbits, nc, dtype16(k_out), cur_stream());
+  TORCH_CHECK(rc == 0, "tq_dequant: unsupported bit widths");
+}
+
+// q [B, Hq, 128] (one query token per sequence); workspace f32 [splits * B * Hq * 129] when splits > 1
+void tq_decode(Tensor& out, const Tensor& q, const Tensor& cache, const Tensor& block_table, const Tensor& seq_lens,
+               const optional<Tensor>& workspace, double scale, int64_t splits, int64_t kbits, int64_t vbits, bool nc) {
+  TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.stride(2) == 1 && q.stride(1) == 128 && q.stride(0) % 4 == 0);
+  TORCH_CHECK(out.is_contiguous() && out.sizes() == q.sizes() && out.scalar_type() == q.scalar_type());
+  TORCH_CHECK(cache.dim() == 4 && cache.is_contiguous() && cache.size(3) == b200::tq_slot_bytes((int)kbits, (int)vbits));
+  TORCH_CHECK(block_table.dim() == 2 && block_table.is_contiguous() && block_table.scalar_type() == at::kInt &&
+              block_table.size(0) >= q.size(0) && seq_lens.scalar_type() == at::kInt && seq_lens.numel() >= q.size(0));
+  const int64_t B = q.size(0), hq = q.size(1), hkv = cache.size(2);
+  TORCH_CHECK(hq % hkv == 0 && splits >= 1);
+  float* part = nullptr;
+  if (splits > 1) {
+    TORCH_CHECK(workspace.has_value() && workspace->scalar_type() == at::kFloat && workspace->is_contiguous() &&
+                workspace->numel() >= splits * B * hq * 129);
+    part = workspace->data_ptr<float>();
+  }
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int rc = b200::tq_decode(out.data_ptr(), part, part ? part + splits * B * hq * 128 : nullptr, q.data_ptr(),
+                                 q.stride(0), cache.data_ptr(), block_table.data_ptr<int>(), (int)block_table.size(1),
+                                 seq_lens.data_ptr<int>(), (int)B, (int)hq, (int)hkv, (int)cache.size(1), cache.size(0),
+                                 (int)splits, (float)scale, (int)kbits, (int)vbits, nc, dtype16(q), cur_stream());
+  TORCH_CHECK(rc == 0, "tq_decode: unsupported format or GQA group (1, 2, 4, 8)");
+}
+
 // o [T, H, 512] -> out [G, T, (H / G) * 512] with the rope dims rotated back
 void v4_inv_rope(Tensor& out, const Tensor& o, const Tensor& positions, const Tensor& cos_sin, int64_t n_groups) {
   TORCH_CHECK(o.dim() == 3 && o.size(2) == 512 && o.stride(2) == 1 && o.stride(0) % 8 == 0 && o.stride(1) % 8 == 0);
@@ -1077,6 +1132,10 @@ TORCH_LIBRARY(b200, m) {
   m.def("moe_a2a_combine(Tensor(a!) out, Tensor y, Tensor topk_ids, Tensor? shared_out, Tensor ptrs, int ep, int rank, int experts_per_rank, int cap, Tensor(b!) local_sync, int wait_cycles) -> ()", &moe_a2a_combine);
   m.def("v4_qnorm_rope_kv_insert(Tensor(a!) q_out, Tensor(b!) cache, Tensor q, Tensor kv, Tensor slot_mapping, Tensor positions, Tensor cos_sin, float eps, int block_size) -> ()", &v4_qnorm_rope_kv_insert);
   m.def("v4_gather_dequant(Tensor(a!) dst, Tensor cache, Tensor slots, int block_size) -> ()", &v4_gather_dequant);
+  m.def("tq_slot_bytes(int kbits, int vbits) -> int", &tq_slot_bytes);
+  m.def("tq_store(Tensor(a!) cache, Tensor k, Tensor v, Tensor slot_mapping, int kbits, int vbits, bool nc) -> ()", &tq_store);
+  m.def("tq_dequant(Tensor(a!) k_out, Tensor(b!) v_out, Tensor cache, Tensor slots, int kbits, int vbits, bool nc) -> ()", &tq_dequant);
+  m.def("tq_decode(Tensor(a!) out, Tensor q, Tensor cache, Tensor block_table, Tensor seq_lens, Tensor? workspace, float scale, int splits, int kbits, int vbits, bool nc) -> ()", &tq_decode);
   m.def("v4_inv_rope(Tensor(a!) out, Tensor o, Tensor positions, Tensor cos_sin, int n_groups) -> ()", &v4_inv_rope);
   m.def("v4_indexer_q(Tensor(a!) q8, Tensor(b!) w_out, Tensor q, Tensor weights, Tensor positions, Tensor cos_sin, float softmax_scale, float head_scale) -> ()", &v4_indexer_q);
   m.def("custom_allreduce(Tensor(a!) out, Tensor inp, Tensor ptrs, int tp, int rank, int cap_bytes, int max_ctas, Tensor(b!) local_sync, int mode, int wait_cycles) -> ()", &custom_allreduce);

@@ -243,6 +243,15 @@ void v4_inv_rope(void* out, const void* o, int64_t o_stride_t, int64_t o_stride_
 void v4_indexer_q(void* q8, float* w_out, const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* weights,
                   int64_t w_stride, const int64_t* positions, const float* cos_sin, int tokens, int heads, int rot,
                   float softmax_scale, float head_scale, int dtype, cudaStream_t stream);
+// ---- tq_cache.cu (TurboQuant KV cache, head_dim 128)
+int tq_slot_bytes(int kbits, int vbits);
+int tq_store(void* cache, const void* k, const void* v, int64_t k_stride, int64_t v_stride, const int64_t* slot_mapping,
+             int tokens, int heads, int64_t num_slots, int kbits, int vbits, int nc, int dtype, cudaStream_t stream);
+int tq_dequant(void* k_out, void* v_out, const void* cache, const int64_t* slots, int rows, int heads, int kbits, int vbits,
+               int nc, int dtype, cudaStream_t stream);
+int tq_decode(void* out, float* part_out, float* part_lse, const void* q, int64_t q_stride, const void* cache,
+              const int* block_table, int max_blocks, const int* seq_lens, int batch, int hq, int hkv, int block_size,
+              int64_t num_blocks, int splits, float scale, int kbits, int vbits, int nc, int dtype, cudaStream_t stream);
 // ---- comm_allreduce.cu
 int custom_allreduce(const CustomArParams& p, const void* in, void* out, int dtype, int mode, cudaStream_t stream);
 int reduce_rms(const ReduceRmsParams& p, int dtype, cudaStream_t stream);

@@ -9,6 +9,9 @@ NVLink bytes per GPU / measured link bandwidth:
 * ``gemm_ar_norm``   GEMM -> reduce-scatter -> residual + RMSNorm -> all-gather (o_proj and down_proj shapes)
                      baseline: tcgen05 GEMM + NCCL all-reduce + fused add-RMSNorm kernel
 * ``ag_gemm``        all-gather -> column-parallel GEMM; baseline: NCCL all-gather + GEMM
+* ``allreduce``      stand-alone one-shot / two-shot peer-store all-reduce against NCCL (32 KiB .. 8 MiB)
+* ``reduce_rms``     cross-rank q/k RMSNorm (4-byte partial sums as their own flags) against torch ops + NCCL
+* ``peer_copy``      (``--p2p``) raw bandwidth of the push primitives into the next rank's memory
 * ``moe_a2a``        expert-parallel dispatch + combine (bf16 and fp8 on the wire) around an identity expert
                      baseline: all-gather of tokens + reduce-scatter of outputs (NCCL)
 Rank 0 prints one JSON object.
@@ -57,6 +60,7 @@ def main() -> None:
     ap.add_argument("--inter", type=int, default=14336)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--skip-moe", action="store_true")
+    ap.add_argument("--p2p", action="store_true", help="also measure raw peer-copy bandwidth")
     a = ap.parse_args()
 
     from vllm_metax_b200 import _custom_ops as ops
@@ -127,6 +131,55 @@ def main() -> None:
                                                       "speedup_vs_nccl": round(t_b / t_f, 2)}
         ops.check_kernel_status(dev.index or 0)
         ag.close()
+
+    # ---- stand-alone all-reduce (one-shot / two-shot peer stores) against NCCL, small to medium messages
+    if world > 1:
+        from vllm_metax_b200.parallel.custom_allreduce import CrossRankRMSNorm, CustomAllReduce
+
+        car = CustomAllReduce(g, dev, 8 << 20)
+        for nbytes in (32 << 10, 512 << 10, 2 << 20, 8 << 20):
+            y = torch.randn(nbytes // 2, dtype=bf, device=dev)
+            t1 = timed(lambda: car.all_reduce(y, mode=1), a.iters, pg)
+            t2 = timed(lambda: car.all_reduce(y, mode=2), a.iters, pg)
+            tn = timed(lambda: dist.all_reduce(y, group=pg), a.iters, pg)
+            link = 2.0 * nbytes * (world - 1) / world / (LINK_GBS * 1e9) * 1e3
+            res[f"allreduce_{nbytes >> 10}KiB"] = {"one_shot_ms": round(t1, 4), "two_shot_ms": round(t2, 4),
+                                                  "nccl_ms": round(tn, 4), "link_roofline_ms": round(link, 5)}
+        ops.check_kernel_status(dev.index or 0)
+        car.close()
+        rms = CrossRankRMSNorm(g, dev, 8192)
+        for T in (256, 8192):
+            q = torch.randn(T, 6144 // world, dtype=bf, device=dev)
+            k = torch.randn(T, 1024 // world if world <= 8 else 128, dtype=bf, device=dev)
+            wq, wk = torch.ones(q.shape[1], dtype=bf, device=dev), torch.ones(k.shape[1], dtype=bf, device=dev)
+            t_f = timed(lambda: rms(q, wq, 1e-6, k, wk), a.iters, pg)
+
+            def baseline():
+                ss = torch.stack([q.float().pow(2).sum(-1), k.float().pow(2).sum(-1)])
+                dist.all_reduce(ss, group=pg)
+                return (q * torch.rsqrt(ss[0] / 6144 + 1e-6)[:, None].to(bf) * wq,
+                        k * torch.rsqrt(ss[1] / 1024 + 1e-6)[:, None].to(bf) * wk)
+
+            t_b = timed(baseline, a.iters, pg)
+            res[f"reduce_rms_qk_T{T}"] = {"fused_ms": round(t_f, 4), "torch_nccl_baseline_ms": round(t_b, 4)}
+        ops.check_kernel_status(dev.index or 0)
+        rms.close()
+
+    # ---- raw peer-copy bandwidth of the push primitives (plain 16-byte stores, bulk stores), per CTA count
+    if world > 1 and a.p2p:
+        from vllm_metax_b200.parallel.symm_mem import SymmWorkspace
+
+        n = 64 << 20
+        ws = SymmWorkspace(g, n + 4096, dev)
+        reg = ws.region("buf", n)
+        peer = ws.peer_ptrs(reg)[(rank + 1) % world]
+        src = torch.randint(0, 255, (n,), dtype=torch.uint8, device=dev)
+        for mode, name in ((0, "st16"), (1, "bulk")):
+            for ctas in (8, 32, 148):
+                t = timed(lambda: torch.ops.b200.p2p_copy(peer, src, ctas, mode), 5, pg)
+                res[f"peer_copy_{name}_ctas{ctas}_GBs"] = round(n / t / 1e6, 1)
+        ops.check_kernel_status(dev.index or 0)
+        ws.close()
 
     # ---- expert-parallel dispatch + combine (identity experts: measures the exchange itself)
     if not a.skip_moe and world > 1:
