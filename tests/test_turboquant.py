@@ -117,3 +117,44 @@ def test_store_dequant_decode_kernels(name):
         got = tq.decode_attention(q.cuda(), cache, bt.cuda(), lens.cuda(), 1 / math.sqrt(128), fmt, num_splits=splits)
         torch.testing.assert_close(got.float().cpu(), want, rtol=3e-2, atol=3e-2)
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("name", ["turboquant_k8v4", "turboquant_4bit_nc"])
+def test_engine_runs_with_turboquant_cache(name):
+    """The whole engine on CPU with a compressed cache: chunked prefill (context read back through the
+    de-quantiser), decode from the slots, preemption-free run to the end."""
+    from vllm_metax_b200 import LLM, ModelConfig, SamplingParams
+
+    cfg = ModelConfig(architecture="LlamaForCausalLM", vocab_size=512, hidden_size=256, intermediate_size=512,
+                      num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=1, head_dim=128,
+                      max_position_embeddings=256, dtype=torch.float32, seed=0)
+    kw = dict(device="cpu", block_size=16, max_model_len=128, max_num_seqs=4, max_num_batched_tokens=32, num_gpu_blocks=32)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (40, 9)]       # 40 > 32: chunked prefill
+    sp = SamplingParams(max_tokens=6, ignore_eos=True)
+    base = LLM(cfg, **kw).generate(prompts, sp)
+    llm = LLM(cfg, kv_cache_dtype=name, **kw)
+    cache, fmt = llm.engine.runner.kv_caches[0]
+    assert cache.dtype == torch.uint8 and cache.shape[-1] == fmt.slot_bytes
+    outs = llm.generate(prompts, sp)
+    assert [len(o.outputs[0].token_ids) for o in outs] == [6, 6]
+    if name == "turboquant_k8v4":       # fp8 keys / 4-bit values barely move a greedy first token
+        assert outs[0].outputs[0].token_ids[0] == base[0].outputs[0].token_ids[0]
+
+
+@gpu
+def test_engine_runs_with_turboquant_cache_gpu():
+    from vllm_metax_b200 import LLM, ModelConfig, SamplingParams
+    from vllm_metax_b200 import _custom_ops as ops
+
+    cfg = ModelConfig(architecture="LlamaForCausalLM", vocab_size=1024, hidden_size=512, intermediate_size=1024,
+                      num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+                      max_position_embeddings=512, dtype=torch.bfloat16, seed=0)
+    llm = LLM(cfg, device="cuda", kv_cache_dtype="turboquant_4bit_nc", block_size=16, max_model_len=256, max_num_seqs=4,
+              max_num_batched_tokens=64, num_gpu_blocks=64)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (100, 9, 33)]
+    outs = llm.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
+    assert [len(o.outputs[0].token_ids) for o in outs] == [12, 12, 12]
+    torch.cuda.synchronize()
+    ops.check_kernel_status(0)

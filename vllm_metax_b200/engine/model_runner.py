@@ -124,6 +124,11 @@ class ModelRunner:
         from ..layers.attention import KV_DTYPES
 
         if spec["kind"] == "gqa":
+            from ..ops import turboquant as tq
+
+            if tq.is_turboquant(self.cfg.cache.kv_cache_dtype):
+                slot = tq.TqFormat.from_name(self.cfg.cache.kv_cache_dtype).slot_bytes
+                return self.block_size * spec["num_kv_heads"] * slot * n
             dt = KV_DTYPES[self.cfg.cache.kv_cache_dtype] or self.cfg.model.dtype
             per = 2 * self.block_size * spec["num_kv_heads"] * spec["head_size"] * torch.empty((), dtype=dt).element_size()
             if self.cfg.cache.kv_cache_dtype.endswith("per_token_head"):

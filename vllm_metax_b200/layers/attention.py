@@ -17,6 +17,7 @@ import torch.nn as nn
 
 from .. import _custom_ops as ops
 from ..attention.metadata import get_forward_context
+from ..ops import turboquant as tq
 
 KV_DTYPES = {
     "auto": None, "bfloat16": torch.bfloat16, "float16": torch.float16, "fp8": torch.float8_e4m3fn,
@@ -43,6 +44,11 @@ class PagedGQABackend:
 
     @staticmethod
     def allocate(num_blocks, block_size, num_kv_heads, head_size, model_dtype, kv_cache_dtype: str, device):
+        if tq.is_turboquant(kv_cache_dtype):
+            # combined K+V slots; the second element carries the format instead of a scale tensor
+            assert head_size == tq.D, "TurboQuant caches are built for head_dim 128"
+            fmt = tq.TqFormat.from_name(kv_cache_dtype)
+            return (tq.alloc_cache(num_blocks, block_size, num_kv_heads, fmt, device), fmt)
         dt = KV_DTYPES[kv_cache_dtype] or model_dtype
         cache = torch.zeros(PagedGQABackend.get_kv_cache_shape(num_blocks, block_size, num_kv_heads, head_size),
                             dtype=dt, device=device)
@@ -73,6 +79,8 @@ class Attention(nn.Module):
         md = ctx.attn_metadata
         kv_cache, kv_scales = ctx.kv_caches[self.layer_idx]
         T = q.shape[0]
+        if isinstance(kv_scales, tq.TqFormat):
+            return self._forward_turboquant(q, k, v, positions, rope, md, kv_cache, kv_scales)
         if rope is not None:
             ops.rope_and_cache(positions, q, k, v, self.head_size, rope.cos_sin_cache, rope.is_neox, kv_cache,
                                md.slot_mapping, kv_scales, self.k_scale, self.v_scale)
@@ -94,4 +102,38 @@ class Attention(nn.Module):
                                         max_q_len=md.max_prefill_query_len, window=self.window, softcap=self.softcap,
                                         sinks=self.sinks, k_scale=self.k_scale, v_scale=self.v_scale,
                                         max_seq_len=md.max_seq_len)
+        return out.reshape(T, self.num_heads * self.head_size)
+
+    def _forward_turboquant(self, q, k, v, positions, rope, md, cache, fmt) -> torch.Tensor:
+        """TurboQuant cache: RoPE, quantising store, then decode rows straight from the compressed slots and prefill
+        rows against the de-quantised context (the cache is the only source of K / V, so a chunk sees its own keys
+        through the same quantiser as every later step will).  Mirrors the split of
+        vllm_metax/v1/attention/backends/turboquant_attn.py:286-942."""
+        T = q.shape[0]
+        if rope is not None:
+            ops.rotary_embedding(positions, q, k, self.head_size, rope.cos_sin_cache, rope.is_neox)
+        tq.store(k, v, cache, md.slot_mapping[:T], fmt)
+        q3 = q.reshape(T, self.num_heads, self.head_size)
+        if not q3.is_contiguous():
+            q3 = q3.contiguous()
+        out = torch.empty(T, self.num_heads, self.head_size, dtype=q.dtype, device=q.device)
+        nd, ndt = md.num_decodes, md.num_decode_tokens
+        if nd > 0 and ndt == nd:
+            tq.decode_attention(q3[:nd], cache, md.block_table[:nd], md.seq_lens[:nd], self.scale, fmt, out=out[:nd])
+            first = nd
+        else:
+            first = 0                   # multi-token decode rows (speculative drafts) take the prefill route
+        if first < md.num_reqs:
+            bs = cache.shape[1]
+            lens = md.seq_lens[first: md.num_reqs].cpu()
+            qsl = md.query_start_loc[first: md.num_reqs + 1]
+            t0 = 0 if first == 0 else ndt
+            slots = torch.cat([tq._slots_of(md.block_table[first + i], int(L), bs) for i, L in enumerate(lens.tolist())])
+            kd, vd = tq.dequant(cache, slots, fmt, q.dtype)
+            cu_k = torch.zeros(lens.numel() + 1, dtype=torch.int32)
+            cu_k[1:] = lens.cumsum(0)
+            cu_q = (qsl - qsl[0]).int()
+            ops.varlen_attention(q3[t0:], kd, vd, cu_q, cu_k.to(q.device), self.scale, out=out[t0:],
+                                 max_q_len=md.max_query_len, causal=True, window=self.window, softcap=self.softcap,
+                                 sinks=self.sinks)
         return out.reshape(T, self.num_heads * self.head_size)
