@@ -104,7 +104,11 @@ def test_store_dequant_decode_kernels(name):
     # a coordinate that sits on a level boundary may fall either way: compare vectors, not codes
     cos = torch.nn.functional.cosine_similarity(kd.float().cpu()[keep], k_ref[keep], dim=-1)
     assert cos.min() > 0.995, cos.min()
-    torch.testing.assert_close(vd.float().cpu()[keep], v_ref[keep], rtol=2e-2, atol=8e-2)
+    # values: identical up to a code that sits exactly between two levels (one step apart, a handful of elements)
+    dv = (vd.float().cpu()[keep] - v_ref[keep]).abs()
+    step = ((v_ref[keep].amax(-1) - v_ref[keep].amin(-1)) / ((1 << fmt.vbits) - 1))[..., None]
+    assert (dv <= step * 1.05 + 8e-2).all()
+    assert (dv > 8e-2).float().mean() < 1e-3
     # decode: the kernel against attention over the kernel's own dequantised rows
     tq.store(k_all.cuda(), v_all.cuda(), cache, s_all.cuda(), fmt)
     kd, vd = tq.dequant(cache, s_all.cuda(), fmt, torch.bfloat16)

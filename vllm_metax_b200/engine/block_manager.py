@@ -57,6 +57,12 @@ class BlockPool:
             if self.ref[bid] == 0:
                 self.free[bid] = None
 
+    def reset_prefix_cache(self) -> None:
+        """Forget every cached prefix (the weights changed: cached K/V no longer match).  Blocks in use keep their
+        contents for their current owners but can no longer be hit by new requests."""
+        self.block_of_hash.clear()
+        self.hash_of = [None] * self.num_blocks
+
     # ------------------------------------------------------------------ prefix cache
     @staticmethod
     def chain_hash(parent: Optional[int], tokens: tuple) -> int:
@@ -112,6 +118,13 @@ class KVCacheManager:
     def __init__(self, num_blocks: int, block_size: int, enable_prefix_caching: bool = False):
         self.pool = BlockPool(num_blocks, block_size, enable_prefix_caching)
         self.block_size = block_size
+
+    @property
+    def enable_prefix_caching(self) -> bool:
+        return self.pool.enable_prefix_caching
+
+    def reset_prefix_cache(self) -> None:
+        self.pool.reset_prefix_cache()
 
     def blocks_needed(self, req: Request, num_new_tokens: int) -> int:
         total = req.num_computed_tokens + num_new_tokens

@@ -56,6 +56,8 @@ class LLMEngine:
         if self.dead is not None:
             raise EngineDeadError(str(self.dead))
         rid = request_id or f"req-{next(self._ids)}"
+        if params is not None and (params.constrained or params.guided_regex is not None or params.guided_json is not None):
+            params.prepare(self.tokenizer)
         req = Request(rid, list(prompt_token_ids), params or SamplingParams(), self.cfg.model.eos_token_id, prompt,
                       arrival_time)
         self.scheduler.add_request(req)
@@ -246,6 +248,123 @@ class LLM:
             if not self.engine.has_unfinished_requests() and len(done) < n:
                 break
         return [self.engine.make_output(reqs[rid]) for rid in order]
+
+    # ------------------------------------------------------------------ chat / pooling / scoring
+    def chat(self, messages, sampling_params: Optional[SamplingParams] = None,
+             add_generation_prompt: bool = True) -> list[RequestOutput]:
+        """``messages``: one conversation (list of ``{"role", "content"}``) or a list of conversations.  Uses the
+        tokenizer's chat template when it has one, else a plain ``role: content`` transcript."""
+        if messages and isinstance(messages[0], dict):
+            messages = [messages]
+        prompts = []
+        for conv in messages:
+            tok = self.tokenizer
+            if tok is not None and getattr(tok, "chat_template", None):
+                prompts.append(tok.apply_chat_template(conv, tokenize=False, add_generation_prompt=add_generation_prompt))
+            else:
+                text = "".join(f"{m['role']}: {m['content']}\n" for m in conv)
+                prompts.append(text + ("assistant:" if add_generation_prompt else ""))
+        return self.generate(prompts, sampling_params)
+
+    def _run_capturing(self, prompts, visit) -> None:
+        """Prefill ``prompts`` (one generated token each) and hand ``visit(index, hidden_rows, is_last_chunk)`` the
+        final-layer hidden states of every prompt chunk as it is computed."""
+        runner = self.engine.runner
+        ids = [self._to_ids(p)[0] for p in prompts]
+        rid_to_idx = {}
+        for i, t in enumerate(ids):
+            rid_to_idx[self.engine.add_request(t, SamplingParams(max_tokens=1, ignore_eos=True))] = i
+        prev_keep, orig = getattr(runner, "keep_hidden", False), runner.execute
+        runner.keep_hidden = True
+
+        def execute(so):
+            out = orig(so)
+            h, md, _ = runner.last_step
+            qsl = md.query_start_loc[: len(so.scheduled) + 1].tolist()
+            for j, s in enumerate(so.scheduled):
+                i = rid_to_idx.get(s.request.request_id)
+                if i is not None and not isinstance(h, dict):
+                    last = s.start_pos + s.num_new_tokens >= len(s.request.prompt_token_ids)
+                    visit(i, h[qsl[j]: qsl[j + 1]], last)
+            return out
+
+        runner.execute = execute
+        use_graphs, runner.use_graphs = runner.use_graphs, False      # every step must expose its hidden states
+        try:
+            while any(r in self.engine.requests for r in rid_to_idx):
+                self.engine.step()
+        finally:
+            runner.execute, runner.keep_hidden, runner.use_graphs = orig, prev_keep, use_graphs
+
+    def embed(self, prompts: Union[str, Sequence], pooling: str = "last", normalize: bool = True) -> torch.Tensor:
+        """Sentence embeddings ``[n, hidden]`` (fp32, on CPU): the final hidden state of the last prompt token
+        (``pooling="last"``) or the mean over all prompt tokens (``"mean"``)."""
+        if isinstance(prompts, str) or (prompts and isinstance(prompts[0], int)):
+            prompts = [prompts]
+        assert pooling in ("last", "mean")
+        n = len(prompts)
+        acc: list = [None] * n
+        cnt = [0] * n
+
+        def visit(i, rows, is_last):
+            rows = rows.float()
+            if pooling == "last":
+                if is_last:
+                    acc[i] = rows[-1].cpu()
+            else:
+                part = rows.sum(0).cpu()
+                acc[i] = part if acc[i] is None else acc[i] + part
+                cnt[i] += rows.shape[0]
+
+        self._run_capturing(prompts, visit)
+        e = torch.stack([a if pooling == "last" else a / max(1, c) for a, c in zip(acc, cnt)])
+        return torch.nn.functional.normalize(e, dim=-1) if normalize else e
+
+    encode = embed
+
+    def score(self, text_1: Union[str, Sequence], text_2: Union[str, Sequence], pooling: str = "last") -> list[float]:
+        """Cosine similarity of the embeddings of ``text_1`` (one prompt, or one per pair) and every ``text_2``."""
+        one = isinstance(text_1, str) or (text_1 and isinstance(text_1[0], int))
+        a = self.embed([text_1] if one else text_1, pooling)
+        many = not (isinstance(text_2, str) or (text_2 and isinstance(text_2[0], int)))
+        b = self.embed(text_2 if many else [text_2], pooling)
+        if a.shape[0] == 1:
+            a = a.expand(b.shape[0], -1)
+        return (a * b).sum(-1).tolist()
+
+    def classify(self, prompts: Union[str, Sequence], class_token_ids: Sequence[int]) -> torch.Tensor:
+        """Zero-shot classification: the next-token distribution restricted to one token per class,
+        ``[n, len(class_token_ids)]`` probabilities."""
+        if isinstance(prompts, str) or (prompts and isinstance(prompts[0], int)):
+            prompts = [prompts]
+        model = self.engine.runner.model
+        ids = torch.tensor(list(class_token_ids), dtype=torch.long)
+        out: list = [None] * len(prompts)
+
+        def visit(i, rows, is_last):
+            if is_last:
+                logits = model.compute_logits(rows[-1:]).float()[0].cpu()
+                out[i] = torch.softmax(logits[ids], -1)
+
+        self._run_capturing(prompts, visit)
+        return torch.stack(out)
+
+    # ------------------------------------------------------------------ weight sync (RLHF loops)
+    def update_weights(self, named_tensors) -> int:
+        """Load new values for (a subset of) the model's weights from ``(hf_name, tensor)`` pairs through the model's
+        own loader (fused / sharded parameters are handled as at start-up).  Returns the number of tensors consumed.
+        Captured CUDA graphs stay valid: parameters are updated in place."""
+        model = self.engine.runner.model
+        pairs = list(named_tensors.items() if isinstance(named_tensors, dict) else named_tensors)
+        with torch.no_grad():
+            model.load_weights(iter(pairs))
+        if self.engine.kv.enable_prefix_caching:
+            self.engine.kv.reset_prefix_cache()
+        return len(pairs)
+
+    def collective_rpc(self, method: str, args: tuple = (), kwargs: Optional[dict] = None):
+        """Call ``method`` on this rank's model runner (every rank of an SPMD engine makes the same call)."""
+        return [getattr(self.engine.runner, method)(*args, **(kwargs or {}))]
 
     # ------------------------------------------------------------------ control surface
     def pause_generation(self) -> None:

@@ -310,7 +310,7 @@ class ModelRunner:
         if self.use_graphs and pure_decode and self.graphs:
             bucket = next((b for b in self.buckets if b >= B), 0)
         md, T, rows, reqs = self._prepare(so, pad_to=bucket)
-        all_greedy = all(r.params.greedy and not r.params.needs_penalties for r in reqs)
+        all_greedy = all(r.params.greedy and not r.params.needs_penalties and not r.params.constrained for r in reqs)
         n = len(rows)
         if bucket:
             g, logits, _ = self.graphs[bucket]

@@ -37,6 +37,10 @@ def forget(request_id: str) -> None:
 def sample_batch(logits: torch.Tensor, reqs, out: torch.Tensor) -> torch.Tensor:
     dev = logits.device
     B, V = logits.shape
+    if any(r.params.constrained for r in reqs):
+        from .structured import apply_constraints
+
+        logits = apply_constraints(logits, reqs)
     if any(r.params.needs_penalties for r in reqs):
         logits = logits.float() if logits.dtype != torch.float32 else logits.clone()
         counts = torch.zeros(B, V, dtype=torch.int32)

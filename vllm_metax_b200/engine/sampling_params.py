@@ -22,6 +22,26 @@ class SamplingParams:
     stop_token_ids: list[int] = field(default_factory=list)
     min_tokens: int = 0
     logprobs: Optional[int] = None
+    # constrained decoding (engine/structured.py)
+    allowed_token_ids: Optional[list[int]] = None
+    logit_bias: Optional[dict] = None
+    guided_choice: Optional[list] = None        # alternatives: token-id lists, or strings with a tokenizer attached
+    guided_regex: Optional[str] = None
+    guided_json: Optional[object] = None
+
+    def prepare(self, tokenizer=None) -> "SamplingParams":
+        """Resolve the constraint once per request (builds the token trie of ``guided_choice``)."""
+        if self.guided_regex is not None or self.guided_json is not None:
+            raise NotImplementedError("guided_regex / guided_json are not built; use guided_choice or allowed_token_ids")
+        if self.guided_choice is not None and getattr(self, "_trie", None) is None:
+            from .structured import TokenTrie, resolve_choices
+
+            self._trie = TokenTrie(resolve_choices(self.guided_choice, tokenizer))
+        return self
+
+    @property
+    def constrained(self) -> bool:
+        return bool(self.allowed_token_ids) or bool(self.logit_bias) or self.guided_choice is not None
 
     @property
     def greedy(self) -> bool:
@@ -104,6 +124,10 @@ class Request:
         p = self.params
         n_out = len(self.output_token_ids)
         last = self.output_token_ids[-1] if n_out else None
+        trie = getattr(p, "_trie", None)
+        if trie is not None and n_out and trie.complete(self.output_token_ids):
+            self.status = RequestStatus.FINISHED_STOPPED
+            return
         if n_out >= p.min_tokens and last is not None:
             if (not p.ignore_eos and self.eos_token_id is not None and last == self.eos_token_id) or \
                     last in p.stop_token_ids:
