@@ -33,8 +33,12 @@ def export_hf_checkpoint(model, path):
             for n, t in (("q_proj", q), ("k_proj", k), ("v_proj", v)):
                 out[name.replace("qkv_proj", n)] = t.contiguous()
         elif "gate_up_proj" in name:
-            out[name.replace("gate_up_proj", "gate_proj")] = w[0::2].contiguous()
-            out[name.replace("gate_up_proj", "up_proj")] = w[1::2].contiguous()
+            if type(model.get_submodule(name.rsplit(".", 1)[0])).__name__ == "GateUpSiluLinear":   # rows interleaved
+                g_, u_ = w[0::2], w[1::2]
+            else:                                                                                   # [gate | up] halves
+                g_, u_ = w[: w.shape[0] // 2], w[w.shape[0] // 2:]
+            out[name.replace("gate_up_proj", "gate_proj")] = g_.contiguous()
+            out[name.replace("gate_up_proj", "up_proj")] = u_.contiguous()
         elif name.endswith("embed_tokens.weight") or name.startswith("lm_head"):
             out[name] = w[: cfg.vocab_size].contiguous()
         else:

@@ -79,6 +79,10 @@ class ModelConfig:
     quant_config: dict = field(default_factory=dict)
     model_path: Optional[str] = None
     seed: int = 0
+    # multi-LoRA serving (lora/): slots resident at once and the largest adapter rank
+    enable_lora: bool = False
+    max_loras: int = 4
+    max_lora_rank: int = 64
     eos_token_id: Optional[int] = None
 
     def __post_init__(self):

@@ -78,7 +78,8 @@ class BlockPool:
             if toks is None:
                 toks = req.all_token_ids
             i = len(hs)
-            hs.append(self.chain_hash(hs[-1] if hs else None, tuple(toks[i * bs:(i + 1) * bs])))
+            root = None if req.lora_request is None else ("lora", req.lora_request.lora_int_id)   # K/V depend on the adapter
+            hs.append(self.chain_hash(hs[-1] if hs else root, tuple(toks[i * bs:(i + 1) * bs])))
         return hs[:nfull]
 
     def match_prefix(self, req: Request) -> list[int]:

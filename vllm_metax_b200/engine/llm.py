@@ -52,7 +52,7 @@ class LLMEngine:
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
                     request_id: Optional[str] = None, prompt: Optional[str] = None,
-                    arrival_time: Optional[float] = None) -> str:
+                    arrival_time: Optional[float] = None, lora_request=None) -> str:
         if self.dead is not None:
             raise EngineDeadError(str(self.dead))
         rid = request_id or f"req-{next(self._ids)}"
@@ -60,6 +60,10 @@ class LLMEngine:
             params.prepare(self.tokenizer)
         req = Request(rid, list(prompt_token_ids), params or SamplingParams(), self.cfg.model.eos_token_id, prompt,
                       arrival_time)
+        if lora_request is not None:
+            if getattr(self.runner, "lora", None) is None:
+                raise ValueError("the engine was built without enable_lora=True")
+            req.lora_request = lora_request
         self.scheduler.add_request(req)
         self.requests[rid] = req
         return rid
@@ -184,8 +188,11 @@ class LLM:
                  num_gpu_blocks: Optional[int] = None, enable_prefix_caching: bool = False,
                  enable_chunked_prefill: bool = True, enforce_eager: bool = False, device: Optional[str] = None,
                  load_format: str = "auto", seed: int = 0, tokenizer: Any = None, enable_sleep_mode: bool = False,
-                 additional_config: Optional[dict] = None, speculative_config: Optional[dict] = None):
+                 additional_config: Optional[dict] = None, speculative_config: Optional[dict] = None,
+                 enable_lora: bool = False, max_loras: int = 4, max_lora_rank: int = 64):
         overrides = {"seed": seed}
+        if enable_lora:
+            overrides.update(enable_lora=True, max_loras=max_loras, max_lora_rank=max_lora_rank)
         if dtype is not None:
             overrides["dtype"] = dtype
         if quantization is not None:
@@ -222,7 +229,8 @@ class LLM:
         return list(p), None
 
     def generate(self, prompts: Union[str, Sequence], sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
-                 use_tqdm: bool = False) -> list[RequestOutput]:
+                 use_tqdm: bool = False, lora_request=None) -> list[RequestOutput]:
+        """``lora_request``: one ``LoRARequest`` for all prompts, or a list with one entry (or None) per prompt."""
         if isinstance(prompts, str) or (prompts and isinstance(prompts[0], int)):
             prompts = [prompts]
         n = len(prompts)
@@ -233,11 +241,12 @@ class LLM:
         now = time.perf_counter()
         order = []
         reqs: dict[str, Request] = {}
-        for p, sp in zip(prompts, sps):
+        loras = lora_request if isinstance(lora_request, (list, tuple)) else [lora_request] * n
+        for p, sp, lr in zip(prompts, sps, loras):
             ids, text = self._to_ids(p)
             import copy
 
-            rid = self.engine.add_request(ids, copy.copy(sp), prompt=text, arrival_time=now)
+            rid = self.engine.add_request(ids, copy.copy(sp), prompt=text, arrival_time=now, lora_request=lr)
             order.append(rid)
             reqs[rid] = self.engine.requests[rid]
         done: dict[str, Request] = {}

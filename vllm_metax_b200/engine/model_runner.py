@@ -55,6 +55,11 @@ class ModelRunner:
         torch.manual_seed(cfg.model.seed)
         with torch.no_grad():
             self.model = build_model(cfg, self.device)
+        self.lora = None
+        if cfg.model.enable_lora:
+            from ..lora import LoRAManager
+
+            self.lora = LoRAManager(self.model, cfg.model.max_loras, cfg.model.max_lora_rank, self.device, cfg.model.dtype)
         self.block_size = cfg.cache.block_size
         sc = cfg.scheduler
         self.max_tokens = max(sc.max_num_batched_tokens, sc.max_num_seqs)
@@ -82,7 +87,8 @@ class ModelRunner:
             self.custom_ar.attach()
         if (ps.tp_size() == 1 or ps.get_pp_group().world_size > 1 or not envs.B200_FUSED_TP_COLLECTIVES
                 or inner is None or not hasattr(inner, "forward_fused_tp")
-                or not getattr(inner, "supports_fused_tp", True) or self.cfg.model.quantization):
+                or not getattr(inner, "supports_fused_tp", True) or self.cfg.model.quantization
+                or self.cfg.model.enable_lora):
             return
         from ..parallel.fused_collectives import get_fused_row_parallel
 
@@ -307,7 +313,8 @@ class ModelRunner:
         B = len(so.scheduled)
         pure_decode = so.num_decode == B and B > 0
         bucket = 0
-        if self.use_graphs and pure_decode and self.graphs:
+        use_lora = self._route_lora(so)
+        if self.use_graphs and pure_decode and self.graphs and not use_lora:      # adapter rows are gathered by index
             bucket = next((b for b in self.buckets if b >= B), 0)
         md, T, rows, reqs = self._prepare(so, pad_to=bucket)
         all_greedy = all(r.params.greedy and not r.params.needs_penalties and not r.params.constrained for r in reqs)
@@ -349,6 +356,22 @@ class ModelRunner:
             if s.num_spec and s.samples and not isinstance(out.get(s.request.request_id), list):
                 out[s.request.request_id] = [out[s.request.request_id]]
         return out
+
+    def _route_lora(self, so: SchedulerOutput) -> bool:
+        """Make the adapters of this step resident and tell the hooks which rows use which slot."""
+        if self.lora is None:
+            return False
+        wanted = {s.request.lora_request.lora_int_id for s in so.scheduled if s.request.lora_request is not None}
+        if not wanted:
+            self.lora.set_batch(None)
+            return False
+        rows: list = []
+        for s in so.scheduled:
+            lr = s.request.lora_request
+            slot = -1 if lr is None else self.lora.activate(lr, in_use=wanted)
+            rows.extend([slot] * s.num_new_tokens)
+        self.lora.set_batch(rows)
+        return True
 
     def _sample(self, logits: torch.Tensor, reqs) -> torch.Tensor:
         from .sampler import sample_batch

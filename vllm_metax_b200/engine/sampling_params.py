@@ -70,7 +70,7 @@ class Request:
 
     __slots__ = ("request_id", "prompt_token_ids", "params", "output_token_ids", "status", "block_ids",
                  "num_computed_tokens", "arrival_time", "first_token_time", "finish_time", "token_times",
-                 "eos_token_id", "num_cached_tokens", "logprobs", "prompt", "_hashes", "spec_token_ids")
+                 "eos_token_id", "num_cached_tokens", "logprobs", "prompt", "_hashes", "spec_token_ids", "lora_request")
 
     def __init__(self, request_id: str, prompt_token_ids: list[int], params: SamplingParams,
                  eos_token_id: Optional[int] = None, prompt: Optional[str] = None,
@@ -91,6 +91,7 @@ class Request:
         self.logprobs: list = []
         self.prompt = prompt
         self._hashes: list[int] = []
+        self.lora_request = None               # lora.LoRARequest of the adapter this request runs with
         self.spec_token_ids: list[int] = []     # draft tokens to verify in the next step (speculative decoding)
 
     @property

@@ -33,7 +33,7 @@ class LlamaMLP(nn.Module):
     def __init__(self, cfg: ModelConfig, intermediate_size: int, prefix: str, reduce_results: bool = True):
         super().__init__()
         qm = lambda name: get_linear_method(cfg, f"{prefix}.{name}")
-        self.fused_act = qm("gate_up_proj") is None and not cfg.mlp_bias and cfg.hidden_act == "silu"
+        self.fused_act = qm("gate_up_proj") is None and not cfg.mlp_bias and cfg.hidden_act == "silu" and not cfg.enable_lora
         if self.fused_act:
             self.gate_up_proj = GateUpSiluLinear(cfg.hidden_size, intermediate_size, cfg.dtype,
                                                  prefix=f"{prefix}.gate_up_proj")
