@@ -100,7 +100,7 @@ def _fused_ar_worker(rank, world):
             total = total + res_full.float()
         new_res = total.to(torch.bfloat16)
         want = ref.rms_norm(new_res, nw, 1e-5)
-        torch.testing.assert_close(out.float().cpu(), want.float(), rtol=3e-2, atol=3e-2)
+        torch.testing.assert_close(out.float().cpu(), want.float(), rtol=3e-2, atol=5e-2)   # split-K rounds every K range to bf16
         torch.testing.assert_close(res[:n_mine].float().cpu(), new_res[rank * rpr: rank * rpr + n_mine].float(),
                                    rtol=2e-2, atol=2e-2)
         g.barrier()
@@ -113,6 +113,7 @@ def test_fused_gemm_allreduce_norm_2gpu():
 
 def _tp_engine_worker(rank, world, fused):
     os.environ["B200_FUSED_TP_COLLECTIVES"] = "1" if fused else "0"
+    os.environ["B200_FUSED_TP_MIN_TOKENS"] = "0"          # the small test batches must still take the fused kernel
     from vllm_metax_b200 import LLM, ModelConfig, SamplingParams
     from vllm_metax_b200 import _custom_ops as ops
     from vllm_metax_b200.parallel import state as ps

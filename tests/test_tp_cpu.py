@@ -51,7 +51,8 @@ def export_hf_checkpoint(model, path):
 
 def _worker(rank, world, port, path, prompts, fused, q):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
-                      MASTER_PORT=str(port), B200_FUSED_TP_COLLECTIVES="1" if fused else "0")
+                      MASTER_PORT=str(port), B200_FUSED_TP_COLLECTIVES="1" if fused else "0",
+                      B200_FUSED_TP_MIN_TOKENS="0")
     try:
         _worker_body(rank, world, path, prompts, fused, q)
     except BaseException as e:  # surface the failure to the parent instead of letting it time out

@@ -94,6 +94,7 @@ class ModelRunner:
 
         inner.fused_ar = get_fused_row_parallel(ps.get_tp_group(), self.device, self.max_tokens,
                                                 self.cfg.model.hidden_size, self.cfg.model.dtype)
+        inner.fused_min_tokens = envs.B200_FUSED_TP_MIN_TOKENS
         self.fused_tp = True
 
     # ------------------------------------------------------------------ buffers

@@ -151,7 +151,9 @@ class LlamaModel(nn.Module):
         return x
 
     def forward(self, input_ids, positions, intermediate: Optional[dict] = None):
-        if getattr(self, "fused_ar", None) is not None:
+        # large token counts: GEMM + reduce + norm as one NVLink kernel; small ones (decode steps): the split-K GEMMs
+        # of the single-GPU path + the peer-store all-reduce are faster than a 128x256-tile kernel on a few tiles
+        if getattr(self, "fused_ar", None) is not None and input_ids.shape[0] >= getattr(self, "fused_min_tokens", 0):
             return self.forward_fused_tp(input_ids, positions)
         if self.embed_tokens is not None:
             h, residual = self.embed_tokens(input_ids), None
