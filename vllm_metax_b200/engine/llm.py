@@ -48,6 +48,50 @@ class LLMEngine:
         from ..parallel.liveness import RankLiveness
 
         self.liveness = RankLiveness.from_default_group()     # None in a single-process engine
+        from ..kv_transfer import KVTransferConfig, make_connector
+
+        self.kv_connector = make_connector(
+            KVTransferConfig.from_dict((cfg.additional_config or {}).get("kv_transfer_config")), self.runner)
+        if self.kv_connector is not None and self.kv_connector.config.is_consumer:
+            self.scheduler.external_kv = self._load_external_kv
+
+    # ------------------------------------------------------------------ KV transfer (disaggregated prefill)
+    @staticmethod
+    def _kv_salt(req: Request):
+        return None if req.lora_request is None else ("lora", req.lora_request.lora_int_id)
+
+    def _load_external_kv(self, req: Request) -> None:
+        """Before admission: pull the blocks another engine published for this prompt.  Whatever cannot be loaded
+        (missing or corrupt block, no free blocks) is simply recomputed."""
+        c, bs = self.kv_connector, self.cfg.cache.block_size
+        toks = req.prompt_token_ids
+        limit = ((len(toks) - 1) // bs) * bs                       # at least one prompt token is always computed
+        have = req.num_computed_tokens
+        n = min(c.lookup(toks[:limit], self._kv_salt(req)), limit)
+        need = n // bs - len(req.block_ids)
+        if n <= have or need > self.kv.pool.num_free:
+            return
+        req.block_ids.extend(self.kv.pool.allocate(need))
+        got = c.load(toks, req.block_ids, n, self._kv_salt(req), first_block=have // bs)
+        if got < n:                                                # recompute from the first bad block on
+            keep = max(got, have) // bs
+            self.kv.pool.release(req.block_ids[keep:])
+            del req.block_ids[keep:]
+            self.stats["kv_load_failures"] = self.stats.get("kv_load_failures", 0) + 1
+        req.num_computed_tokens = max(have, got)
+        req.num_cached_tokens = req.num_computed_tokens
+        self.stats["kv_external_tokens"] = self.stats.get("kv_external_tokens", 0) + max(0, got - have)
+
+    def _publish_kv(self, so) -> None:
+        """After the forward pass, before finished requests give their blocks back: publish the full blocks of
+        every prompt whose prefill completed in this step."""
+        c, bs = self.kv_connector, self.cfg.cache.block_size
+        for s in so.scheduled:
+            r = s.request
+            if not r.output_token_ids and s.start_pos + s.num_new_tokens >= len(r.prompt_token_ids):
+                n = (len(r.prompt_token_ids) // bs) * bs
+                if n:
+                    c.save(r.prompt_token_ids, r.block_ids, n, self._kv_salt(r))
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
@@ -99,6 +143,8 @@ class LLMEngine:
                 self.liveness.announce_failure(repr(e))
             self._release_all()
             raise EngineDeadError(f"engine step failed: {e!r}") from e
+        if self.kv_connector is not None and self.kv_connector.config.is_producer:
+            self._publish_kv(so)
         now = time.perf_counter()
         finished = self.scheduler.update(so, sampled, now)
         if self.proposer is not None:
@@ -189,7 +235,8 @@ class LLM:
                  enable_chunked_prefill: bool = True, enforce_eager: bool = False, device: Optional[str] = None,
                  load_format: str = "auto", seed: int = 0, tokenizer: Any = None, enable_sleep_mode: bool = False,
                  additional_config: Optional[dict] = None, speculative_config: Optional[dict] = None,
-                 enable_lora: bool = False, max_loras: int = 4, max_lora_rank: int = 64):
+                 enable_lora: bool = False, max_loras: int = 4, max_lora_rank: int = 64,
+                 kv_transfer_config: Optional[dict] = None):
         overrides = {"seed": seed}
         if enable_lora:
             overrides.update(enable_lora=True, max_loras=max_loras, max_lora_rank=max_lora_rank)
@@ -210,8 +257,9 @@ class LLM:
             scheduler=SchedulerConfig(max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens,
                                       max_model_len=max_model_len, enable_chunked_prefill=enable_chunked_prefill),
             device=device, enforce_eager=enforce_eager, load_format=load_format,
-            additional_config=dict(additional_config or {}, **({"speculative_config": speculative_config}
-                                                                if speculative_config else {})))
+            additional_config=dict(additional_config or {},
+                                   **({"speculative_config": speculative_config} if speculative_config else {}),
+                                   **({"kv_transfer_config": kv_transfer_config} if kv_transfer_config else {})))
         self.config = cfg
         self.engine = LLMEngine(cfg, tokenizer or tok)
         self.tokenizer = self.engine.tokenizer

@@ -56,6 +56,7 @@ class Scheduler:
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []
         self.paused = False
+        self.external_kv = None            # callable(req): attach externally published KV blocks before admission
         self.num_preemptions = 0
         self.num_draft_tokens = 0
         self.num_accepted_tokens = 0
@@ -133,6 +134,8 @@ class Scheduler:
         while self.waiting and budget > 0 and len(self.running) < self.cfg.max_num_seqs and not out.preempted:
             req = self.waiting[0]
             self.kv.try_prefix_hit(req)
+            if self.external_kv is not None and not req.output_token_ids:
+                self.external_kv(req)              # KV published by another engine (disaggregated prefill)
             remaining = req.num_tokens - req.num_computed_tokens
             n = min(remaining, budget)
             if not self.cfg.enable_chunked_prefill and n < remaining:

@@ -270,6 +270,16 @@ class B200PlatformBase(Platform):
         return True
 
     @classmethod
+    def get_default_ir_op_priority(cls, vllm_config):
+        """Kernel-provider order for vLLM's IR ops: this package's CUDA ops (registered under the ``vllm_c``
+        provider name through the custom-op registry) first, the native PyTorch lowering as the fall-back
+        (vllm_metax/platform.py:666-688)."""
+        from vllm.config.kernel import IrOpPriorityConfig
+
+        default = ["vllm_c", "native"]
+        return IrOpPriorityConfig.with_default(default, rms_norm=default, fused_add_rms_norm=default)
+
+    @classmethod
     def get_punica_wrapper(cls) -> str:
         return "vllm.lora.punica_wrapper.punica_gpu.PunicaWrapperGPU"
 
