@@ -16,6 +16,11 @@ def _ngpu():
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
+def _world():
+    """Ranks per test: 2, or B200_TEST_WORLD (4 / 8) to confirm the kernels at a larger world size."""
+    return max(2, min(int(os.environ.get("B200_TEST_WORLD", "2")), _ngpu() or 2))
+
+
 _PORT_SEQ = 0
 
 
@@ -108,7 +113,7 @@ def _fused_ar_worker(rank, world):
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_fused_gemm_allreduce_norm_2gpu():
-    _launch(_fused_ar_worker, 2)
+    _launch(_fused_ar_worker, _world())
 
 
 def _tp_engine_worker(rank, world, fused):
@@ -280,4 +285,4 @@ def _custom_ar_worker(rank, world):
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_custom_allreduce_and_reduce_rms_2gpu():
-    _launch(_custom_ar_worker, 2)
+    _launch(_custom_ar_worker, _world())

@@ -13,7 +13,8 @@ NVLink bytes per GPU / measured link bandwidth:
 * ``reduce_rms``     cross-rank q/k RMSNorm (4-byte partial sums as their own flags) against torch ops + NCCL
 * ``peer_copy``      (``--p2p``) raw bandwidth of the push primitives into the next rank's memory
 * ``moe_a2a``        expert-parallel dispatch + combine (bf16 and fp8 on the wire) around an identity expert
-                     baseline: all-gather of tokens + reduce-scatter of outputs (NCCL)
+                     baseline: all-gather of tokens / ids / weights, the same align + gather + weighted-sum kernels
+                     on all tokens, reduce-scatter of the partial sums (NCCL)
 Rank 0 prints one JSON object.
 """
 from __future__ import annotations
@@ -192,22 +193,42 @@ def main() -> None:
                 ids = torch.stack([torch.randperm(E, generator=gen)[:topk] for _ in range(T)]).int().to(dev)
                 wts = torch.rand(T, topk, device=dev)
 
+                y_buf: dict = {}
+
                 def identity(arows, a_scale, block_expert, total):
-                    if a_scale is not None:
-                        return arows.view(torch.float8_e4m3fn).to(bf)
-                    return arows
+                    # stands for the grouped GEMMs: fp8 rows would feed the fp8 GEMM as they are, so the timing
+                    # must not include a conversion - hand back a bf16 buffer of the right shape
+                    if a_scale is None:
+                        return arows
+                    if arows.shape[0] not in y_buf:
+                        y_buf[arows.shape[0]] = torch.zeros(arows.shape[0], Hm, dtype=bf, device=dev)
+                    return y_buf[arows.shape[0]]
 
                 t_f = timed(lambda: run_experts_a2a(mgr, x, wts, ids, identity), a.iters, pg)
+                # baseline = the all-gather / reduce-scatter manager's path: every rank receives ALL tokens, keeps the
+                # pairs of its own experts (same align / gather / weighted-sum kernels), reduce-scatters the partial sums
                 allx = torch.empty(world * T, Hm, dtype=bf, device=dev)
+                all_ids = torch.empty(world * T, topk, dtype=torch.int32, device=dev)
+                all_w = torch.empty(world * T, topk, dtype=torch.float32, device=dev)
                 out = torch.empty(T, Hm, dtype=bf, device=dev)
+                el = E // world
+                emap = torch.full((E,), -1, dtype=torch.int32, device=dev)
+                emap[rank * el:(rank + 1) * el] = torch.arange(el, dtype=torch.int32, device=dev)
 
                 def baseline():
                     dist.all_gather_into_tensor(allx, x, group=pg)
-                    dist.reduce_scatter_tensor(out, allx, group=pg)
+                    dist.all_gather_into_tensor(all_ids, ids, group=pg)
+                    dist.all_gather_into_tensor(all_w, wts, group=pg)
+                    sorted_ids, block_expert, total, inv = ops.moe_align_block_size(all_ids, 128, el, emap, want_inverse=True)
+                    arows = ops.moe_gather(allx, sorted_ids, total, topk)
+                    part = ops.moe_combine(arows, all_w, inv, world * T, None)
+                    dist.reduce_scatter_tensor(out, part, group=pg)
 
                 t_b = timed(baseline, a.iters, pg)
-                per_dir = T * topk * Hm * (1 if quant else 2) * (world - 1) / world
-                link_ms = (per_dir + T * topk * Hm * 2 * (world - 1) / world) / (LINK_GBS * 1e9) * 1e3
+                # rows that really cross NVLink: one per (token, remote rank owning one of its experts), both ways
+                dst = ids // el
+                remote = sum(int(((dst == r).any(dim=1)).sum()) for r in range(world) if r != rank)
+                link_ms = remote * Hm * ((1 if quant else 2) + 2) / (LINK_GBS * 1e9) * 1e3
                 res[f"moe_a2a_T{T}_{'fp8' if quant else 'bf16'}"] = {
                     "fused_ms": round(t_f, 4), "nccl_agrs_baseline_ms": round(t_b, 4), "link_roofline_ms": round(link_ms, 4),
                     "of_roofline": round(link_ms / t_f, 3), "speedup_vs_nccl": round(t_b / t_f, 2)}
