@@ -89,3 +89,48 @@ def test_too_long_prompt_is_rejected(client_app):
     pytest.importorskip("httpx")
     code, text = _call(app, "POST", "/v1/completions", {"prompt": [1] * 250, "max_tokens": 50})
     assert code == 400 and "max_model_len" in text
+
+
+def test_constrained_and_unknown_model(client_app):
+    allm, app = client_app
+    pytest.importorskip("httpx")
+    body = {"prompt": "pick", "max_tokens": 8, "guided_choice": [[10, 11], [12]], "model": "toy"}
+    code, text = _call(app, "POST", "/v1/completions", body)
+    out = json.loads(text)
+    assert code == 200 and out["choices"][0]["token_ids"] in ([10, 11], [12]) and out["choices"][0]["finish_reason"] == "stop"
+    body = {"prompt": "pick", "max_tokens": 5, "ignore_eos": True, "allowed_token_ids": [7, 8]}
+    code, text = _call(app, "POST", "/v1/completions", body)
+    assert code == 200 and set(json.loads(text)["choices"][0]["token_ids"]) <= {7, 8}
+    code, _ = _call(app, "POST", "/v1/completions", {"prompt": "x", "guided_regex": "a+"})
+    assert code == 400
+    code, text = _call(app, "POST", "/v1/completions", {"prompt": "x", "model": "no-such-adapter"})
+    assert code == 404 and "not served" in text
+
+
+def test_lora_adapter_selected_by_model_name():
+    pytest.importorskip("httpx")
+    from vllm_metax_b200.lora import LoRARequest
+
+    cfg = ModelConfig(architecture="LlamaForCausalLM", vocab_size=256, hidden_size=64, intermediate_size=128,
+                      num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                      max_position_embeddings=256, dtype=torch.float32)
+    llm = LLM(cfg, device="cpu", load_format="dummy", num_gpu_blocks=64, block_size=16, max_model_len=256,
+              tokenizer=ToyTokenizer(), seed=0, enable_lora=True, max_loras=2, max_lora_rank=4)
+    g = torch.Generator().manual_seed(0)
+    t = {}
+    for i in range(2):
+        stem = f"base_model.model.model.layers.{i}.self_attn.q_proj"
+        t[stem + ".lora_A.weight"] = torch.randn(4, 64, generator=g)
+        t[stem + ".lora_B.weight"] = torch.randn(64, 4, generator=g)
+    allm = AsyncLLM(llm)
+    try:
+        app = build_app(allm, "toy", {"tuned": LoRARequest("tuned", 1, tensors=t, config={"lora_alpha": 8})})
+        code, text = _call(app, "GET", "/v1/models")
+        assert [m["id"] for m in json.loads(text)["data"]] == ["toy", "tuned"]
+        req = {"prompt": "hello there", "max_tokens": 8, "ignore_eos": True}
+        base = json.loads(_call(app, "POST", "/v1/completions", dict(req, model="toy"))[1])["choices"][0]["token_ids"]
+        tuned = json.loads(_call(app, "POST", "/v1/completions", dict(req, model="tuned"))[1])["choices"][0]["token_ids"]
+        assert len(tuned) == 8 and tuned != base
+        assert llm.engine.runner.lora.list_adapters() == [1]
+    finally:
+        allm.shutdown()

@@ -104,6 +104,8 @@ class LLMEngine:
             params.prepare(self.tokenizer)
         req = Request(rid, list(prompt_token_ids), params or SamplingParams(), self.cfg.model.eos_token_id, prompt,
                       arrival_time)
+        if lora_request is None and params is not None:
+            lora_request = getattr(params, "_lora_request", None)      # set by front ends that only pass params through
         if lora_request is not None:
             if getattr(self.runner, "lora", None) is None:
                 raise ValueError("the engine was built without enable_lora=True")

@@ -32,6 +32,12 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--enforce-eager", action="store_true")
     s.add_argument("--device", default="cuda")
     s.add_argument("--seed", type=int, default=0)
+    s.add_argument("--enable-lora", action="store_true")
+    s.add_argument("--max-loras", type=int, default=4)
+    s.add_argument("--max-lora-rank", type=int, default=64)
+    s.add_argument("--lora-modules", nargs="*", default=[], metavar="NAME=PATH", help="PEFT adapters served under NAME")
+    s.add_argument("--kv-transfer-config", default=None, help="JSON, e.g. '{\"kv_connector\": \"SharedStorageConnector\", "
+                   "\"kv_role\": \"kv_producer\", \"kv_connector_extra_config\": {\"shared_storage_path\": \"/dev/shm/kv\"}}'")
     b = sub.add_parser("bench", help="offline throughput / latency run (same engine, no HTTP)")
     b.add_argument("model")
     b.add_argument("--num-prompts", type=int, default=64)
@@ -63,6 +69,10 @@ def make_llm(args):
                  "enable_prefix_caching", "enable_sleep_mode", "enforce_eager", "kv_cache_dtype", "seed"):
         if hasattr(args, name):
             kw[name] = getattr(args, name)
+    if getattr(args, "enable_lora", False):
+        kw.update(enable_lora=True, max_loras=args.max_loras, max_lora_rank=args.max_lora_rank)
+    if getattr(args, "kv_transfer_config", None):
+        kw["kv_transfer_config"] = json.loads(args.kv_transfer_config)
     if hasattr(args, "dtype"):
         kw["dtype"] = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32}[args.dtype]
     return LLM(_model_arg(args.model), **kw)
@@ -104,7 +114,10 @@ def main(argv=None) -> int:
     llm = make_llm(args)
     if ps.global_rank() != 0:
         raise SystemExit("tensor-parallel serving runs the HTTP front on rank 0 only; start ranks with torchrun")
-    app = build_app(AsyncLLM(llm), args.served_model_name or str(args.model))
+    from ..lora import LoRARequest
+
+    loras = {n: LoRARequest(n, i + 1, p) for i, (n, p) in enumerate(m.split("=", 1) for m in args.lora_modules)}
+    app = build_app(AsyncLLM(llm), args.served_model_name or str(args.model), loras)
     uvicorn.run(app, host=args.host, port=args.port, log_level="info")
     return 0
 

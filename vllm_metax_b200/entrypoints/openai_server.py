@@ -38,6 +38,17 @@ def sampling_from_request(body: dict, default_max_tokens: int = 16) -> SamplingP
         kw["stop"] = list(stop)
     if body.get("stop_token_ids"):
         kw["stop_token_ids"] = list(body["stop_token_ids"])
+    so = body.get("structured_outputs") or {}
+    choice = body.get("guided_choice") or so.get("choice")
+    if choice:
+        kw["guided_choice"] = list(choice)
+    for name in ("guided_regex", "guided_json"):
+        if body.get(name) is not None or so.get(name[7:]) is not None:
+            kw[name] = body.get(name) if body.get(name) is not None else so.get(name[7:])
+    if body.get("allowed_token_ids"):
+        kw["allowed_token_ids"] = [int(t) for t in body["allowed_token_ids"]]
+    if body.get("logit_bias"):
+        kw["logit_bias"] = {int(k): float(v) for k, v in body["logit_bias"].items()}
     fields = getattr(SamplingParams, "__dataclass_fields__", None)
     if fields is not None:
         kw = {k: v for k, v in kw.items() if k in fields}
@@ -77,7 +88,9 @@ def prometheus_text(allm: AsyncLLM) -> str:
     return "\n".join(lines) + "\n"
 
 
-def build_app(allm: AsyncLLM, served_model_name: str = "b200-model"):
+def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_modules: Optional[dict] = None):
+    """``lora_modules``: adapter name -> ``LoRARequest``; a request whose ``model`` field names one runs with it."""
+    lora_modules = dict(lora_modules or {})
     from fastapi import FastAPI, Request
     from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
@@ -108,8 +121,10 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model"):
 
     @app.get("/v1/models")
     async def models():
-        return {"object": "list", "data": [{"id": served_model_name, "object": "model", "owned_by": "b200",
-                                            "max_model_len": llm.engine.cfg.scheduler.max_model_len}]}
+        base = {"id": served_model_name, "object": "model", "owned_by": "b200",
+                "max_model_len": llm.engine.cfg.scheduler.max_model_len}
+        adapters = [{"id": n, "object": "model", "owned_by": "b200", "parent": served_model_name} for n in lora_modules]
+        return {"object": "list", "data": [base] + adapters}
 
     @app.get("/metrics")
     async def metrics():
@@ -175,6 +190,13 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model"):
             else:
                 ids, prompt = encode(body.get("prompt", ""))
             params = sampling_from_request(body, default_max_tokens=16 if not chat else 256)
+            if params.guided_regex is not None or params.guided_json is not None:
+                raise NotImplementedError("guided_regex / guided_json are not built; use guided_choice")
+            model_name = body.get("model")
+            if model_name in lora_modules:
+                params._lora_request = lora_modules[model_name]
+            elif model_name not in (None, "", served_model_name):
+                return err(404, f"model {model_name!r} is not served (adapters: {sorted(lora_modules)})", "model_not_found")
         except Exception as e:
             return err(400, str(e))
         if len(ids) + params.max_tokens > llm.engine.cfg.scheduler.max_model_len:
