@@ -92,3 +92,29 @@ def test_mtp_spec_decode_matches_plain_greedy_cpu():
     for a, b in zip(plain, spec):
         assert a.outputs[0].token_ids == b.outputs[0].token_ids
     assert llm.engine.scheduler.num_draft_tokens > 0
+
+
+def test_eagle_spec_decode_matches_plain_greedy_cpu():
+    """An EAGLE head (random here, so few drafts are accepted) must never change the greedy output; drafts are
+    proposed every step and the head shares the target's embedding and language-model head."""
+    from tests.test_e2e_plumbing import tiny_cfg
+
+    kw = dict(device="cpu", num_gpu_blocks=64, block_size=16, max_model_len=128, max_num_batched_tokens=32)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (5, 40, 17)]      # 40 > 32: chunked prefill
+    sp = SamplingParams(max_tokens=12, temperature=0.0, ignore_eos=True)
+    plain = LLM(tiny_cfg(), **kw).generate(prompts, sp)
+    llm = LLM(tiny_cfg(), speculative_config={"method": "eagle", "num_speculative_tokens": 1}, **kw)
+    head = llm.engine.proposer.module
+    assert type(head).__name__ == "EagleLlamaForCausalLM" and head.fc.weight.shape == (256, 512)
+    assert head.embed_tokens is llm.engine.runner.model.model.embed_tokens and head.lm_head is llm.engine.runner.model.lm_head
+    spec = llm.generate(prompts, sp)
+    for a, b in zip(plain, spec):
+        assert a.outputs[0].token_ids == b.outputs[0].token_ids
+    assert llm.engine.scheduler.num_draft_tokens > 0
+    # published EAGLE checkpoints name their tensors fc.* / layers.0.* (with or without a model. prefix)
+    names = {"fc.weight": torch.zeros(256, 512), "fc.bias": torch.zeros(256),
+             "model.layers.0.self_attn.q_proj.weight": torch.zeros(256, 256),
+             "layers.0.mlp.down_proj.weight": torch.zeros(256, 512)}
+    assert head.load_weights(names.items()) == {"fc.weight", "fc.bias", "layers.0.self_attn.qkv_proj.weight",
+                                                "layers.0.mlp.down_proj.weight"}

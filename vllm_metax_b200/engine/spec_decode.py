@@ -25,10 +25,12 @@ from typing import Optional, Sequence
 
 @dataclass
 class SpeculativeConfig:
-    method: str = "ngram"                  # "ngram" | "mtp"
+    method: str = "ngram"                  # "ngram" | "mtp" | "eagle"
     num_speculative_tokens: int = 4
     prompt_lookup_max: int = 4
     prompt_lookup_min: int = 1
+    model: object = None                   # eagle: draft checkpoint directory, config dict or ModelConfig
+    own_embeddings: bool = False           # eagle: keep the draft's own embedding / head instead of the target's
 
     @classmethod
     def from_dict(cls, d: Optional[dict]) -> Optional["SpeculativeConfig"]:
@@ -74,4 +76,17 @@ def make_proposer(cfg: Optional[SpeculativeConfig], engine=None):
         from ..models.deepseek_mtp import MTPProposer
 
         return MTPProposer(cfg, engine)
+    if cfg.method == "eagle":
+        import copy
+
+        from ..models.deepseek_mtp import MTPProposer
+
+        if cfg.model is None:                                   # a one-layer head with the target's dimensions
+            draft = copy.copy(engine.cfg.model)
+            draft.num_hidden_layers = 1
+        else:
+            from .llm import _resolve_model
+
+            draft, _ = _resolve_model(cfg.model, dtype=engine.cfg.model.dtype)
+        return MTPProposer(cfg, engine, architecture="EagleLlamaForCausalLM", draft_model=draft)
     raise ValueError(f"unknown speculative method {cfg.method!r}")

@@ -25,6 +25,7 @@ _MODELS: dict[str, tuple[str, str]] = {
     "DeepseekV4ForCausalLM": ("deepseek_v4", "DeepseekV4ForCausalLM"),
     "DeepSeekV4MTPModel": ("deepseek_v4", "DeepSeekV4MTP"),
     "Step3p5MTP": ("step3p5_mtp", "Step3p5MTP"),
+    "EagleLlamaForCausalLM": ("eagle", "EagleLlamaForCausalLM"),
 }
 
 

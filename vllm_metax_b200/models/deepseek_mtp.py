@@ -121,7 +121,9 @@ class MTPProposer:
     """Draft proposer over a ``DeepSeekMTP`` module.  ``after_step`` is called by the engine once the target
     step's tokens are known."""
 
-    def __init__(self, cfg, engine):
+    def __init__(self, cfg, engine, architecture: str = "DeepSeekMTPModel", draft_model=None):
+        """``architecture`` names the draft module class; ``draft_model`` (a ``ModelConfig``) replaces the copy of the
+        target's configuration when the draft has its own (EAGLE heads)."""
         import copy
 
         from ..engine.loader import build_model
@@ -130,9 +132,11 @@ class MTPProposer:
         self.engine = engine
         runner = engine.runner
         ecfg = copy.copy(engine.cfg)
-        ecfg.model = copy.copy(engine.cfg.model)
-        ecfg.model.architecture = "DeepSeekMTPModel"
+        ecfg.model = copy.copy(draft_model if draft_model is not None else engine.cfg.model)
+        ecfg.model.architecture = architecture
         self.module = build_model(ecfg, runner.device)
+        if hasattr(self.module, "share_with_target") and not getattr(cfg, "own_embeddings", False):
+            self.module.share_with_target(runner.model)
         self.kv_caches = self.module.allocate_kv_cache(runner.num_blocks, runner.block_size, ecfg.cache.kv_cache_dtype,
                                                        runner.device)
         runner.use_graphs = False          # the proposer needs the hidden states of every step
