@@ -1,0 +1,101 @@
+"""Regex- and JSON-schema-guided decoding with a character-level toy tokenizer: whatever the (random) model prefers,
+the decoded output must match the pattern."""
+import json
+import os
+import sys
+
+import pytest
+import regex
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from tests.test_e2e_plumbing import tiny_cfg  # noqa: E402
+
+KW = dict(device="cpu", block_size=16, max_model_len=256, max_num_seqs=8, max_num_batched_tokens=64, num_gpu_blocks=64)
+CHARS = [chr(c) for c in range(32, 127)]
+
+
+class CharTokenizer:
+    """Token i < 95 is one printable ASCII character; a few multi-character tokens follow; the rest decode to ''."""
+    chat_template = None
+    multi = ['{"', '":', '", "', "true", "false", "null", "12", '"}', "ab"]
+
+    def piece(self, t):
+        if t < len(CHARS):
+            return CHARS[t]
+        if t - len(CHARS) < len(self.multi):
+            return self.multi[t - len(CHARS)]
+        return ""
+
+    def encode(self, text, add_special_tokens=True):
+        return [CHARS.index(c) for c in text]
+
+    def decode(self, ids, skip_special_tokens=True):
+        return "".join(self.piece(int(t)) for t in ids)
+
+
+def test_schema_to_regex_subset():
+    from vllm_metax_b200.engine.structured import schema_to_regex
+
+    rx = schema_to_regex({"type": "object", "properties": {
+        "name": {"type": "string"}, "age": {"type": "integer"}, "ok": {"type": "boolean"},
+        "tags": {"type": "array", "items": {"enum": ["a", "b"]}, "maxItems": 2}}})
+    good = ['{"name": "x y", "age": 3, "ok": true, "tags": ["a", "b"]}', '{"name":"","age":-12,"ok":false,"tags":[]}']
+    bad = ['{"name": 1, "age": 3, "ok": true, "tags": []}', '{"name":"x","age":3,"ok":true,"tags":["a","b","a"]}',
+           '{"age":3,"name":"x","ok":true,"tags":[]}']
+    assert all(regex.fullmatch(rx, g) for g in good) and not any(regex.fullmatch(rx, b) for b in bad)
+    assert all(json.loads(g) for g in good)
+    with pytest.raises(NotImplementedError):
+        schema_to_regex({"anyOf": []})
+
+
+@pytest.fixture(scope="module")
+def llm():
+    from vllm_metax_b200 import LLM
+
+    return LLM(tiny_cfg(), tokenizer=CharTokenizer(), **KW)
+
+
+@pytest.mark.parametrize("temperature", [0.0, 0.9])
+def test_guided_regex(llm, temperature):
+    from vllm_metax_b200 import SamplingParams
+
+    pattern = r"(yes|no), [0-9]{3}-[a-c]+!"
+    sp = SamplingParams(max_tokens=40, temperature=temperature, seed=1, guided_regex=pattern)
+    outs = llm.generate(["Q: ok?", "Q: sure?", "x"], sp)
+    for o in outs:
+        assert regex.fullmatch(pattern, o.outputs[0].text), o.outputs[0].text
+        assert o.outputs[0].finish_reason == "stop"
+
+
+def test_guided_json(llm):
+    from vllm_metax_b200 import SamplingParams
+
+    schema = {"type": "object", "properties": {"city": {"enum": ["Paris", "Rome"]}, "n": {"enum": [1, 22, 333]},
+                                               "ok": {"type": "boolean"}}}
+    outs = llm.generate(["a", "bb"], SamplingParams(max_tokens=60, guided_json=schema))
+    for o in outs:
+        doc = json.loads(o.outputs[0].text)
+        assert set(doc) == {"city", "n", "ok"} and doc["city"] in ("Paris", "Rome") and doc["n"] in (1, 22, 333)
+    # unbounded parts (an integer of any length): a run cut off by max_tokens is still a prefix of a valid document
+    from vllm_metax_b200.engine.structured import schema_to_regex
+
+    schema = {"type": "object", "properties": {"n": {"type": "integer"}, "s": {"type": "string"}}}
+    o = llm.generate(["c"], SamplingParams(max_tokens=30, guided_json=schema))[0].outputs[0]
+    assert regex.fullmatch(schema_to_regex(schema), o.text, partial=True), o.text
+    # the multi-character tokens are usable too (the guide works on decoded text, not on single characters)
+    from vllm_metax_b200.engine.structured import RegexGuide
+
+    g = RegexGuide(r'\{"k":true\}', CharTokenizer())
+    row = torch.zeros(1024)
+    row[95] = 5.0                                    # token '{"' has the best logit and is a valid start
+    assert g.allowed([], row, None)[0] == 95
+
+
+def test_guided_needs_tokenizer():
+    from vllm_metax_b200 import LLM, SamplingParams
+
+    with pytest.raises(ValueError):
+        LLM(tiny_cfg(), **KW).generate([[1, 2]], SamplingParams(guided_regex="a+"))

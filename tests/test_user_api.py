@@ -48,7 +48,7 @@ def test_guided_choice_and_allowed_tokens(llm):
     # a large bias on one token wins the arg-max
     outs = llm.generate(prompts[:1], SamplingParams(max_tokens=3, ignore_eos=True, logit_bias={123: 1e4}))
     assert outs[0].outputs[0].token_ids == [123, 123, 123]
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(ValueError):                       # text-level guidance needs a tokenizer
         llm.generate(prompts[:1], SamplingParams(guided_regex="a+"))
 
 

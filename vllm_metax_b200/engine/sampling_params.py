@@ -31,8 +31,11 @@ class SamplingParams:
 
     def prepare(self, tokenizer=None) -> "SamplingParams":
         """Resolve the constraint once per request (builds the token trie of ``guided_choice``)."""
-        if self.guided_regex is not None or self.guided_json is not None:
-            raise NotImplementedError("guided_regex / guided_json are not built; use guided_choice or allowed_token_ids")
+        if (self.guided_regex is not None or self.guided_json is not None) and getattr(self, "_guide", None) is None:
+            from .structured import RegexGuide, schema_to_regex
+
+            pattern = self.guided_regex if self.guided_regex is not None else schema_to_regex(self.guided_json)
+            self._guide = RegexGuide(pattern, tokenizer)
         if self.guided_choice is not None and getattr(self, "_trie", None) is None:
             from .structured import TokenTrie, resolve_choices
 
@@ -41,7 +44,8 @@ class SamplingParams:
 
     @property
     def constrained(self) -> bool:
-        return bool(self.allowed_token_ids) or bool(self.logit_bias) or self.guided_choice is not None
+        return (bool(self.allowed_token_ids) or bool(self.logit_bias) or self.guided_choice is not None
+                or self.guided_regex is not None or self.guided_json is not None)
 
     @property
     def greedy(self) -> bool:
@@ -128,6 +132,10 @@ class Request:
         trie = getattr(p, "_trie", None)
         if trie is not None and n_out and trie.complete(self.output_token_ids):
             self.status = RequestStatus.FINISHED_STOPPED
+            return
+        guide = getattr(p, "_guide", None)
+        if guide is not None and n_out and self.eos_token_id is None and guide.is_complete(guide.text(self.output_token_ids)):
+            self.status = RequestStatus.FINISHED_STOPPED      # no end-of-sequence token to ask for: first full match ends
             return
         if n_out >= p.min_tokens and last is not None:
             if (not p.ignore_eos and self.eos_token_id is not None and last == self.eos_token_id) or \

@@ -8,9 +8,14 @@
   preemption and recomputation without bookkeeping.  The request stops as soon as it has produced a complete
   alternative.
 
-Regular-expression and JSON-schema guidance need a character-level automaton intersected with the vocabulary; they
-are not built (``guided_regex`` / ``guided_json`` raise).  Parity: the structured-outputs examples of the reference
-(examples/features/structured_outputs in its tree) run on upstream's backends.
+* ``guided_regex`` / ``guided_json`` - the decoded output must match a regular expression (a JSON schema is first
+  turned into one, for the subset in ``schema_to_regex``).  Instead of intersecting an automaton with the whole
+  vocabulary, the guide tests candidates lazily: tokens are visited in descending logit order and kept when
+  ``prefix + piece`` is still a partial match, until enough valid candidates are found.  Greedy decoding is exact
+  (the best valid token is always found); sampling draws from the valid part of the top candidates.  Needs a
+  tokenizer (token pieces come from ``decode``) and the ``regex`` package (partial matching).
+Parity: the structured-outputs examples of the reference (examples/features/structured_outputs in its tree) run on
+upstream's backends.
 """
 from __future__ import annotations
 
@@ -66,6 +71,112 @@ def resolve_choices(choices, tokenizer) -> list[list[int]]:
     return out
 
 
+# ---------------------------------------------------------------------------------------------- regex / JSON
+_JSON_WS = r"[ \n]?"
+_JSON_STRING = r'"(?:[^"\\\x00-\x1f]|\\["\\/bfnrt])*"'
+_JSON_NUMBER = r"-?(?:0|[1-9][0-9]*)(?:\.[0-9]+)?(?:[eE][+-]?[0-9]+)?"
+_JSON_INT = r"-?(?:0|[1-9][0-9]*)"
+
+
+def schema_to_regex(schema) -> str:
+    """Regular expression for the JSON documents of a schema: ``type`` string / integer / number / boolean / null,
+    ``enum`` / ``const``, ``array`` (``items``, optional ``minItems`` / ``maxItems``), ``object`` with ``properties``
+    (all listed properties, in order - ``required`` is treated as "all").  Anything else raises."""
+    import json
+    import re
+
+    if isinstance(schema, str):
+        schema = json.loads(schema)
+    if "enum" in schema:
+        return "(?:" + "|".join(re.escape(json.dumps(v)) for v in schema["enum"]) + ")"
+    if "const" in schema:
+        return re.escape(json.dumps(schema["const"]))
+    t = schema.get("type")
+    if t == "string":
+        return _JSON_STRING
+    if t == "integer":
+        return _JSON_INT
+    if t == "number":
+        return _JSON_NUMBER
+    if t == "boolean":
+        return "(?:true|false)"
+    if t == "null":
+        return "null"
+    if t == "array":
+        item = schema_to_regex(schema.get("items", {"type": "string"}))
+        lo, hi = int(schema.get("minItems", 0)), schema.get("maxItems")
+        more = f"(?:,{_JSON_WS}{item})"
+        if hi is None:
+            rest = more + ("*" if lo <= 1 else f"{{{lo - 1},}}")
+        else:
+            rest = more + f"{{{max(lo - 1, 0)},{max(int(hi) - 1, 0)}}}"
+        body = f"{item}{rest}"
+        return rf"\[{_JSON_WS}(?:{body}){'' if lo > 0 else '?'}{_JSON_WS}\]"
+    if t == "object":
+        props = schema.get("properties") or {}
+        if not props:
+            return r"\{" + _JSON_WS + r"\}"
+        parts = [re.escape(json.dumps(k)) + ":" + _JSON_WS + schema_to_regex(v) for k, v in props.items()]
+        return r"\{" + _JSON_WS + ("," + _JSON_WS).join(parts) + _JSON_WS + r"\}"
+    raise NotImplementedError(f"JSON schema construct not supported for guided decoding: {schema!r}")
+
+
+class RegexGuide:
+    """Lazy candidate filter for one pattern (shared by the requests that use it)."""
+
+    BATCHES = (32, 256, 2048)
+
+    def __init__(self, pattern: str, tokenizer):
+        import regex
+
+        if tokenizer is None:
+            raise ValueError("guided_regex / guided_json need a tokenizer")
+        self.rx = regex.compile(pattern)
+        self.tok = tokenizer
+        self._piece: dict[int, str] = {}
+
+    def piece(self, tok: int) -> str:
+        p = self._piece.get(tok)
+        if p is None:
+            p = self.tok.decode([tok])
+            self._piece[tok] = p
+        return p
+
+    def text(self, output_ids) -> str:
+        return self.tok.decode(list(output_ids)) if output_ids else ""
+
+    def is_complete(self, text: str) -> bool:
+        return self.rx.fullmatch(text) is not None
+
+    def viable(self, text: str) -> bool:
+        return self.rx.fullmatch(text, partial=True) is not None
+
+    def allowed(self, output_ids, logits_row: torch.Tensor, eos: Optional[int], want: int = 1) -> list[int]:
+        """At least ``want`` valid next tokens (fewer only when the vocabulary has fewer), best logits first;
+        the end-of-sequence token is valid exactly when the text so far matches the whole pattern."""
+        text = self.text(output_ids)
+        out: list[int] = []
+        if eos is not None and self.is_complete(text):
+            out.append(int(eos))
+        V = logits_row.numel()
+        order = None
+        seen = 0
+        for n in self.BATCHES + (V,):
+            n = min(n, V)
+            if order is None or n > len(order):
+                order = torch.topk(logits_row, n).indices.tolist()
+            for t in order[seen:n]:
+                if t == eos:
+                    continue
+                p = self.piece(t)
+                if p and "\ufffd" not in p and self.viable(text + p):
+                    out.append(t)
+            seen = n
+            if len(out) >= want or n == V:
+                break
+        return out
+
+
 def constraint_of(req) -> Optional[list[int]]:
     """Allowed token ids for the request's next step, or None when it is unconstrained."""
     p = req.params
@@ -88,7 +199,8 @@ def apply_constraints(logits: torch.Tensor, reqs) -> torch.Tensor:
     for i, r in enumerate(reqs):
         p = r.params
         allowed = constraint_of(r)
-        if allowed is None and not p.logit_bias:
+        guide = getattr(p, "_guide", None)
+        if allowed is None and not p.logit_bias and guide is None:
             continue
         if not touched:
             logits = logits.float().clone()
@@ -97,6 +209,16 @@ def apply_constraints(logits: torch.Tensor, reqs) -> torch.Tensor:
             idx = torch.tensor(list(p.logit_bias.keys()), dtype=torch.long, device=logits.device)
             val = torch.tensor(list(p.logit_bias.values()), dtype=torch.float32, device=logits.device)
             logits[i].index_add_(0, idx, val)
+        if guide is not None:
+            row = logits[i].detach().float().cpu()
+            if allowed is not None:                      # combine with an allow-list / choice trie
+                mask = torch.full_like(row, float("-inf"))
+                mask[torch.tensor(allowed, dtype=torch.long)] = 0.0
+                row = row + mask
+            ok = guide.allowed(r.output_token_ids, row, r.eos_token_id, want=1 if p.greedy else 16)
+            if not ok and r.eos_token_id is not None:
+                ok = [r.eos_token_id]                    # dead end: nothing extends the text - stop
+            allowed = ok
         if allowed is not None:
             keep = torch.tensor(allowed, dtype=torch.long, device=logits.device)
             row = torch.full_like(logits[i], float("-inf"))

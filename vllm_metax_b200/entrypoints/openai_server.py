@@ -190,8 +190,6 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
             else:
                 ids, prompt = encode(body.get("prompt", ""))
             params = sampling_from_request(body, default_max_tokens=16 if not chat else 256)
-            if params.guided_regex is not None or params.guided_json is not None:
-                raise NotImplementedError("guided_regex / guided_json are not built; use guided_choice")
             model_name = body.get("model")
             if model_name in lora_modules:
                 params._lora_request = lora_modules[model_name]
