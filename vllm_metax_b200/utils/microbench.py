@@ -109,9 +109,54 @@ def bench_elementwise(t: Timer, T, H, I) -> dict:
     return res
 
 
+def bench_quant(t, M: int, N: int, K: int) -> dict:
+    """Quantised GEMMs at one shape (TFLOP/s over 2 M N K) and the TurboQuant decode kernel (bytes of compressed
+    cache streamed per second)."""
+    from ..ops import turboquant as tq
+    from ..quantization import wna16 as W
+
+    res = {}
+    flops = 2.0 * M * N * K
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    # fp8, 1x128 activation scales and 128x128 weight scales
+    aq, a_s = ops.per_token_group_quant_fp8(x, 128)
+    wq = w.to(torch.float8_e4m3fn)
+    w_s = torch.ones(N // 128, K // 128, device=DEV, dtype=torch.float32)
+    ms = t(lambda: ops.fp8_block_scaled_mm(aq, a_s, wq, w_s))
+    res["fp8_blockscale"] = {"ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1)}
+    # W8A8 int8, per-token / per-channel scales
+    a8 = torch.randint(-127, 127, (M, K), device=DEV, dtype=torch.int8)
+    w8 = torch.randint(-127, 127, (N, K), device=DEV, dtype=torch.int8)
+    sa = torch.rand(M, device=DEV) * 0.01
+    sw = torch.rand(N, device=DEV) * 0.01
+    ms = t(lambda: ops.scaled_mm(a8, w8, sa, sw))
+    res["w8a8_int8"] = {"ms": round(ms, 4), "tops": round(flops / ms / 1e9, 1)}
+    ms = t(lambda: ops.scaled_mm(aq.view(torch.float8_e4m3fn), wq, sa, sw))
+    res["w8a8_fp8"] = {"ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1)}
+    # W4A16 (group 128, symmetric): a weight stream at small M
+    qv, sg, _ = W.quantize_weight(w.float().cpu(), 4, 128, sym=True)
+    qc, sc, zc = (v.to(DEV) for v in W.canonical_from_values(qv, sg, None, 4, torch.bfloat16))
+    ms = t(lambda: ops.wna16_gemm(x, qc, sc, zc, 4, 128))
+    res["w4a16"] = {"ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
+                    "weight_gbs": round(N * K / 2 / ms / 1e6, 1)}
+    # TurboQuant decode: 256 sequences x 1100 tokens, 32 / 8 heads
+    fmt = tq.TqFormat.from_name("turboquant_4bit_nc")
+    B, L, bs = 256, 1100, 128
+    nb = B * ((L + bs - 1) // bs)
+    cache = torch.randint(0, 255, (nb, bs, 8, fmt.slot_bytes), device=DEV, dtype=torch.uint8)
+    cache[..., fmt.k_bytes + fmt.v_bytes:] = 0          # finite norms / scales (fp16 zero)
+    bt = torch.arange(nb, device=DEV, dtype=torch.int32).view(B, -1)
+    sl = torch.full((B,), L, device=DEV, dtype=torch.int32)
+    qd = torch.randn(B, 32, 128, device=DEV, dtype=torch.bfloat16)
+    ms = t(lambda: tq.decode_attention(qd, cache, bt, sl, 0.088, fmt))
+    res["turboquant_decode_256x1100"] = {"ms": round(ms, 4), "gbs": round(B * L * 8 * fmt.slot_bytes / ms / 1e6, 1)}
+    return res
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "gemm", "prefill", "decode", "elementwise"])
+    ap.add_argument("--op", default="all", choices=["all", "gemm", "prefill", "decode", "elementwise", "quant"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
@@ -136,6 +181,8 @@ def main() -> None:
                 if name == "lm_head" and M > 256:
                     continue
                 res[f"gemm_{name}_M{M}"] = bench_gemm(t, M, N, K, True)
+    if a.op == "quant":
+        res[f"quant_{a.m}x{a.n}x{a.k}"] = bench_quant(t, a.m, a.n, a.k)
     if a.op in ("all", "prefill"):
         res["attn_prefill_8x1024"] = bench_prefill(t, 8, 1024, 32, 8, 128, 128)
     if a.op in ("all", "decode"):
