@@ -12,9 +12,8 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", required=True)
     ap.add_argument("--dp", type=int, default=2)
-    ap.add_argument("--tp", type=int, default=1)
     a = ap.parse_args()
-    llm = DataParallelLLM(a.model, data_parallel_size=a.dp, devices_per_replica=a.tp, tensor_parallel_size=a.tp)
+    llm = DataParallelLLM(a.model, data_parallel_size=a.dp)
     prompts = [f"Question {i}: what is {i} squared?" for i in range(64)]
     outs = llm.generate(prompts, SamplingParams(max_tokens=32))
     print("replica of each prompt:", llm.last_assignment)

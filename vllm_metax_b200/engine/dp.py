@@ -5,7 +5,9 @@ box - its own device or tensor-parallel group of devices) behind one front that 
     outs = llm.generate(prompts, sampling_params)                    # internal load balancing
     outs = llm.generate(prompts, sampling_params, dp_rank=2)         # external: the caller picks the replica
 
-Every replica is a child process running an ordinary ``LLM``; requests and results travel over pipes.  Balancing
+Every replica is a child process running an ordinary single-GPU ``LLM``; requests and results travel over pipes.
+(Tensor-parallel replicas are torchrun groups of their own: start one server per group and balance externally, e.g.
+by ``dp_rank`` from the caller's side.)  Balancing
 is by outstanding work (prompt tokens + tokens still to generate), which is what the replicas' schedulers are
 bound by.  A replica that dies turns the calls routed to it into ``EngineDeadError``; the others keep serving.
 Parity: the data-parallel deployments the reference's tests drive (tests/v1/test_internal_lb_dp.py,
