@@ -100,7 +100,7 @@ def main() -> None:
         if rank == 0:
             print(json.dumps({"impl": "reference", "unavailable":
                               "reference needs the MACA SDK (cmake_maca, +metax torch, mcoplib) and setuptools_scm; "
-                              "pip install --no-index of /root/reference fails at metadata generation on this image"}))
+                              "its offline pip install fails at metadata generation on this image"}))
         return
 
     import torch

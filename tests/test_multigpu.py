@@ -45,8 +45,11 @@ def _entry(fn, rank, world, port, q, *args):
                       MASTER_PORT=str(port))
     import faulthandler
 
-    os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-    fh = open(os.path.join(ROOT, "gpurun_out", f"stack_{fn.__name__}_r{rank}.txt"), "w")
+    import tempfile
+
+    diag = os.environ.get("B200_TEST_DIAG_DIR", tempfile.gettempdir())      # where a stuck rank leaves its stack
+    os.makedirs(diag, exist_ok=True)
+    fh = open(os.path.join(diag, f"stack_{fn.__name__}_r{rank}.txt"), "w")
     faulthandler.dump_traceback_later(100, file=fh)      # where is a stuck rank? (diagnosis only)
     try:
         fn(rank, world, *args)
