@@ -884,6 +884,31 @@ void v4_gather_dequant(Tensor& dst, const Tensor& cache, const Tensor& slots, in
                           (int)block_size, cur_stream());
 }
 
+// q, k [T, Hq, 128], v [T, Hv, 128], g / beta f32 [T, Hv], state f32 [slots, Hv, 128, 128] (in / out)
+void gdn_recurrent(Tensor& out, Tensor& state, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& g,
+                   const Tensor& beta, const Tensor& query_start_loc, const optional<Tensor>& state_idx,
+                   const optional<Tensor>& has_initial, double scale, bool l2norm) {
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3 && q.stride(2) == 1 && k.stride(2) == 1 && v.stride(2) == 1);
+  TORCH_CHECK(q.stride(1) == q.size(2) && k.stride(1) == k.size(2) && v.stride(1) == v.size(2) && k.sizes() == q.sizes());
+  const int64_t T = q.size(0), hq = q.size(1), hv = v.size(1);
+  TORCH_CHECK(v.size(0) == T && out.is_contiguous() && out.sizes() == v.sizes() && out.scalar_type() == q.scalar_type());
+  TORCH_CHECK(g.is_contiguous() && beta.is_contiguous() && g.scalar_type() == at::kFloat && beta.scalar_type() == at::kFloat &&
+              g.numel() == T * hv && beta.numel() == T * hv);
+  TORCH_CHECK(state.is_contiguous() && state.scalar_type() == at::kFloat && state.dim() == 4 && state.size(1) == hv);
+  TORCH_CHECK(query_start_loc.scalar_type() == at::kInt && query_start_loc.is_contiguous());
+  const int64_t B = query_start_loc.numel() - 1;
+  if (state_idx.has_value()) TORCH_CHECK(state_idx->scalar_type() == at::kInt && state_idx->numel() >= B);
+  if (has_initial.has_value()) TORCH_CHECK(has_initial->scalar_type() == at::kInt && has_initial->numel() >= B);
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int rc = b200::gdn_recurrent(out.data_ptr(), state.data_ptr<float>(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                     g.data_ptr<float>(), beta.data_ptr<float>(), query_start_loc.data_ptr<int>(),
+                                     state_idx.has_value() ? state_idx->data_ptr<int>() : nullptr, (int)B, (int)hq, (int)hv,
+                                     (int)q.size(2), (int)v.size(2), q.stride(0), k.stride(0), v.stride(0), (float)scale,
+                                     l2norm, has_initial.has_value() ? has_initial->data_ptr<int>() : nullptr,
+                                     dtype16(q), cur_stream());
+  TORCH_CHECK(rc == 0, "gdn_recurrent: head sizes must be 128 and value heads a multiple of q/k heads");
+}
+
 // TurboQuant cache: uint8 [blocks, block_size, kv_heads, slot_bytes]; k, v [T, kv_heads * 128] (any row pitch)
 int64_t tq_slot_bytes(int64_t kbits, int64_t vbits) { return b200::tq_slot_bytes((int)kbits, (int)vbits); }
 
@@ -1132,6 +1157,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("moe_a2a_combine(Tensor(a!) out, Tensor y, Tensor topk_ids, Tensor? shared_out, Tensor ptrs, int ep, int rank, int experts_per_rank, int cap, Tensor(b!) local_sync, int wait_cycles) -> ()", &moe_a2a_combine);
   m.def("v4_qnorm_rope_kv_insert(Tensor(a!) q_out, Tensor(b!) cache, Tensor q, Tensor kv, Tensor slot_mapping, Tensor positions, Tensor cos_sin, float eps, int block_size) -> ()", &v4_qnorm_rope_kv_insert);
   m.def("v4_gather_dequant(Tensor(a!) dst, Tensor cache, Tensor slots, int block_size) -> ()", &v4_gather_dequant);
+  m.def("gdn_recurrent(Tensor(a!) out, Tensor(b!) state, Tensor q, Tensor k, Tensor v, Tensor g, Tensor beta, Tensor query_start_loc, Tensor? state_idx, Tensor? has_initial, float scale, bool l2norm) -> ()", &gdn_recurrent);
   m.def("tq_slot_bytes(int kbits, int vbits) -> int", &tq_slot_bytes);
   m.def("tq_store(Tensor(a!) cache, Tensor k, Tensor v, Tensor slot_mapping, int kbits, int vbits, bool nc) -> ()", &tq_store);
   m.def("tq_dequant(Tensor(a!) k_out, Tensor(b!) v_out, Tensor cache, Tensor slots, int kbits, int vbits, bool nc) -> ()", &tq_dequant);

@@ -243,6 +243,11 @@ void v4_inv_rope(void* out, const void* o, int64_t o_stride_t, int64_t o_stride_
 void v4_indexer_q(void* q8, float* w_out, const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* weights,
                   int64_t w_stride, const int64_t* positions, const float* cos_sin, int tokens, int heads, int rot,
                   float softmax_scale, float head_scale, int dtype, cudaStream_t stream);
+// ---- gdn.cu
+int gdn_recurrent(void* out, float* state, const void* q, const void* k, const void* v, const float* g, const float* beta,
+                  const int* query_start_loc, const int* state_idx, int batch, int hq, int hv, int dk, int dv,
+                  int64_t q_stride, int64_t k_stride, int64_t v_stride, float scale, int l2norm,
+                  const int* has_initial, int dtype, cudaStream_t stream);
 // ---- tq_cache.cu (TurboQuant KV cache, head_dim 128)
 int tq_slot_bytes(int kbits, int vbits);
 int tq_store(void* cache, const void* k, const void* v, int64_t k_stride, int64_t v_stride, const int64_t* slot_mapping,

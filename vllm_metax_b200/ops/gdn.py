@@ -1,0 +1,64 @@
+"""Gated delta rule linear attention (``csrc/gdn.cu``) with its fp32 PyTorch statement.
+
+    S <- exp(g_t) S;   u = beta_t (v_t - S^T k_t);   S <- S + k_t u^T;   o_t = S^T (scale q_t)
+
+``q, k [T, Hq, 128]``, ``v [T, Hv, 128]`` (``Hv`` a multiple of ``Hq``), ``g, beta [T, Hv]``; sequences are given by
+``query_start_loc``; ``state [slots, Hv, 128, 128]`` (fp32) is read where ``has_initial_state`` says so and always
+written back at ``state_indices`` (negative index: no state is kept).
+Parity: ``ChunkGatedDeltaRule`` / the fused recurrent decode step of the GDN blocks
+(vllm_metax/registry/custom_ops/layers/mamba/qwen_gdn_linear_attn.py:16-88).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+
+def gated_delta_rule_ref(q, k, v, g, beta, query_start_loc, state=None, state_indices=None, has_initial_state=None,
+                         scale: Optional[float] = None, l2norm: bool = True):
+    T, Hq, Dk = q.shape
+    Hv, Dv = v.shape[1], v.shape[2]
+    scale = Dk ** -0.5 if scale is None else scale
+    qf, kf, vf = q.float(), k.float(), v.float()
+    if l2norm:
+        qf = qf * torch.rsqrt(qf.pow(2).sum(-1, keepdim=True) + 1e-6)
+        kf = kf * torch.rsqrt(kf.pow(2).sum(-1, keepdim=True) + 1e-6)
+    rep = Hv // Hq
+    qf, kf = qf.repeat_interleave(rep, 1) * scale, kf.repeat_interleave(rep, 1)
+    out = torch.zeros(T, Hv, Dv)
+    qsl = query_start_loc.tolist()
+    for b in range(len(qsl) - 1):
+        slot = int(state_indices[b]) if state_indices is not None else -1
+        use = slot >= 0 and state is not None and (has_initial_state is None or bool(has_initial_state[b]))
+        S = state[slot].float().clone() if use else torch.zeros(Hv, Dk, Dv)
+        for t in range(qsl[b], qsl[b + 1]):
+            S = S * torch.exp(g[t].float())[:, None, None]
+            u = beta[t].float()[:, None] * (vf[t] - torch.einsum("hkv,hk->hv", S, kf[t]))
+            S = S + torch.einsum("hk,hv->hkv", kf[t], u)
+            out[t] = torch.einsum("hkv,hk->hv", S, qf[t])
+        if slot >= 0 and state is not None:
+            state[slot] = S.to(state.dtype)
+    return out.to(q.dtype)
+
+
+def gated_delta_rule(q, k, v, g, beta, query_start_loc, state=None, state_indices=None, has_initial_state=None,
+                     scale: Optional[float] = None, l2norm: bool = True):
+    """Output ``[T, Hv, 128]``; ``state`` is updated in place."""
+    if not q.is_cuda:
+        return gated_delta_rule_ref(q, k, v, g, beta, query_start_loc, state, state_indices, has_initial_state, scale, l2norm)
+    from .. import _custom_ops as ops
+
+    ops.load_native()
+    Hv = v.shape[1]
+    if state is None:
+        state = torch.zeros(1, Hv, 128, 128, dtype=torch.float32, device=q.device)
+        state_indices = None
+    out = torch.empty_like(v)
+    ops._launches += 1
+    torch.ops.b200.gdn_recurrent(
+        out, state, q, k, v, g.float().contiguous(), beta.float().contiguous(), query_start_loc.int().contiguous(),
+        None if state_indices is None else state_indices.int().contiguous(),
+        None if has_initial_state is None else has_initial_state.int().contiguous(),
+        q.shape[-1] ** -0.5 if scale is None else scale, l2norm)
+    return out

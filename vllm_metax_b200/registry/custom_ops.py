@@ -4,7 +4,8 @@ One table drives the registration: (upstream module, class name, forward_oot).  
 subclass of the upstream layer whose ``forward_oot`` calls ``vllm_metax_b200._custom_ops``; vLLM picks it
 up through ``CustomOp.register_oot`` when the platform is out-of-tree.
 Parity: vllm_metax/registry/custom_ops/activation.py:17-73 (ten activations), layernorm.py:6-20
-(RMSNorm, GemmaRMSNorm, RMSNormGated), layers/rotary_embedding, layers/minimax_rms_norm.
+(RMSNorm, GemmaRMSNorm, RMSNormGated), layers/attention/mm_encoder_attention.py:17-122,
+layers/mamba/qwen_gdn_linear_attn.py:16-88, layers/minimax_rms_norm/rms_norm_tp.py:22-59.
 """
 from __future__ import annotations
 
@@ -66,6 +67,54 @@ def _rms_norm_gated(self, x: torch.Tensor, z: Optional[torch.Tensor] = None) -> 
     return y
 
 
+def _mm_encoder_attention(self, query, key, value, cu_seqlens=None, max_seqlen=None, sequence_lengths=None):
+    """Vision-encoder attention on the non-causal tcgen05 varlen kernel."""
+    from ..layers.mm_encoder_attention import encoder_attention
+
+    hs = self.head_size
+    q = query.reshape(*query.shape[:-1], -1, hs) if query.shape[-1] != hs else query
+    k = key.reshape(*key.shape[:-1], -1, hs) if key.shape[-1] != hs else key
+    v = value.reshape(*value.shape[:-1], -1, hs) if value.shape[-1] != hs else value
+    out = encoder_attention(q, k, v, cu_seqlens, None if max_seqlen is None else int(max_seqlen), getattr(self, "scale", None))
+    return out.reshape(query.shape) if query.shape[-1] != hs else out
+
+
+def _chunk_gated_delta_rule(self, q, k, v, g, beta, initial_state, output_final_state, cu_seqlens=None,
+                            chunk_indices=None, chunk_offsets=None, use_qk_l2norm_in_kernel=True, core_attn_out=None):
+    """GDN prefill on the recurrent kernel: ``q, k [1, T, H, 128]``, ``initial_state [N, Hv, 128, 128]``."""
+    from ..ops.gdn import gated_delta_rule
+
+    T = q.shape[-3]
+    q3, k3, v3 = (t.reshape(T, t.shape[-2], t.shape[-1]) for t in (q, k, v))
+    qsl = cu_seqlens if cu_seqlens is not None else torch.tensor([0, T], dtype=torch.int32, device=q.device)
+    n = qsl.numel() - 1
+    state = initial_state.float().contiguous() if initial_state is not None else \
+        torch.zeros(n, v3.shape[1], q3.shape[-1], v3.shape[-1], dtype=torch.float32, device=q.device)
+    idx = torch.arange(n, dtype=torch.int32, device=q.device)
+    o = gated_delta_rule(q3, k3, v3, g.reshape(T, -1), beta.reshape(T, -1), qsl, state, idx, None, None,
+                         use_qk_l2norm_in_kernel).reshape(v.shape)
+    if core_attn_out is not None:
+        core_attn_out.copy_(o.reshape(core_attn_out.shape))
+        o = core_attn_out
+    return o, (state if output_final_state else None)
+
+
+def _minimax_rms_norm_tp(self, x: torch.Tensor, *args, **kwargs):
+    """RMSNorm over a hidden dimension split across the TP ranks: only per-token sums of squares cross NVLink."""
+    from ..parallel import state as ps
+    from ..parallel.custom_allreduce import CrossRankRMSNorm
+
+    eps = float(getattr(self, "variance_epsilon", getattr(self, "eps", 1e-6)))
+    x2 = x.reshape(-1, x.shape[-1])
+    if getattr(self, "tp_world", 1) == 1 or not getattr(ps._S, "initialized", False):
+        return ops.rms_norm(x2, self.weight.data.to(x.dtype), eps).reshape(x.shape)
+    rms = getattr(self, "_b200_rms", None)
+    if rms is None or rms.t_cap < x2.shape[0]:
+        rms = CrossRankRMSNorm(ps.get_tp_group(), x.device, max(x2.shape[0], 8192))
+        self._b200_rms = rms
+    return rms(x2.contiguous(), self.weight.data.to(x.dtype), eps)[0].reshape(x.shape)
+
+
 _TABLE = [
     ("vllm.model_executor.layers.activation", "SiluAndMul", _gated("silu")),
     ("vllm.model_executor.layers.activation", "MulAndSilu", _gated("mul_silu")),
@@ -80,6 +129,9 @@ _TABLE = [
     ("vllm.model_executor.layers.layernorm", "RMSNorm", _rms_norm(False)),
     ("vllm.model_executor.layers.layernorm", "GemmaRMSNorm", _rms_norm(True)),
     ("vllm.model_executor.layers.layernorm", "RMSNormGated", _rms_norm_gated),
+    ("vllm.model_executor.layers.attention.mm_encoder_attention", "MMEncoderAttention", _mm_encoder_attention),
+    ("vllm.model_executor.layers.mamba.gdn.qwen_gdn_linear_attn", "ChunkGatedDeltaRule", _chunk_gated_delta_rule),
+    ("vllm.model_executor.layers.mamba.linear_attn", "MiniMaxText01RMSNormTP", _minimax_rms_norm_tp),
 ]
 
 
