@@ -280,12 +280,13 @@ def concat_and_cache_mla(kv_c, k_pe, mla_cache, slot_mapping):
     ref.concat_and_cache_mla(kv_c, k_pe, mla_cache, slot_mapping)
 
 
-def indexer_k_quant_and_cache(k, idx_cache, slot_mapping, block_size: int, ue8m0: bool = False):
-    """Parity: vllm_metax/_custom_ops.py:137-149."""
+def indexer_k_quant_and_cache(k, idx_cache, slot_mapping, block_size: int, ue8m0: bool = False, int8: bool = False):
+    """e4m3 keys (V3.2) or int8 keys (V4, ``int8=True``) + one f32 scale per token.
+    Parity: vllm_metax/_custom_ops.py:137-149."""
     if _use_cuda(k):
-        torch.ops.b200.indexer_k_quant_and_cache(k, idx_cache, slot_mapping, block_size, ue8m0)
+        torch.ops.b200.indexer_k_quant_and_cache(k, idx_cache, slot_mapping, block_size, ue8m0, int8)
         return
-    ref.indexer_k_quant_and_cache(k, idx_cache.view(idx_cache.shape[0], -1), slot_mapping, ue8m0=ue8m0)
+    ref.indexer_k_quant_and_cache(k, idx_cache.view(idx_cache.shape[0], -1), slot_mapping, ue8m0=ue8m0, int8=int8)
 
 
 # --------------------------------------------------------------------------- activations
@@ -882,18 +883,21 @@ def top_k_per_row(logits, k: int, row_len=None):
 
 def indexer_topk(q_fp8, weights, idx_cache, block_table, seq_lens, query_start_loc, topk: int, block_size: int,
                  max_seq_len: int = 0, return_logits: bool = False):
-    """fp8 index logits of every new token against its request's cached keys, then top-k.
+    """Index logits of every new token against its request's cached keys, then top-k.  ``q_fp8`` is e4m3, or int8
+    (the V4 indexer: queries from ``ops.v4_cache.indexer_q_rope_int8_quant``, keys written with ``int8=True``).
     Returns int32 ``[T, topk]`` per-request positions (-1 = none)."""
     if _use_cuda(q_fp8):
         T = q_fp8.shape[0]
         L = max(int(max_seq_len), 1)
         Lp = (L + 1023) // 1024 * 1024
         logits = torch.empty(T, Lp, dtype=torch.float32, device=q_fp8.device)
-        qb = q_fp8 if q_fp8.dtype == torch.float8_e4m3fn else q_fp8.to(torch.float8_e4m3fn)
+        i8 = q_fp8.dtype == torch.int8
+        qb = q_fp8 if (i8 or q_fp8.dtype == torch.float8_e4m3fn) else q_fp8.to(torch.float8_e4m3fn)
         torch.ops.b200.indexer_logits(logits, qb.contiguous(), weights.float().contiguous(), idx_cache, block_table,
-                                      seq_lens, query_start_loc, block_size, L)
+                                      seq_lens, query_start_loc, block_size, L, i8)
         _ = _use_cuda(q_fp8)  # second kernel of the op (launch accounting)
         out = torch.empty(T, topk, dtype=torch.int32, device=q_fp8.device)
         torch.ops.b200.topk_per_row(out, logits, None, Lp)
         return (out, logits) if return_logits else out
-    return ref.sparse_attn_indexer(q_fp8.float(), weights, idx_cache, block_table, seq_lens, query_start_loc, topk)
+    return ref.sparse_attn_indexer(q_fp8.float(), weights, idx_cache, block_table, seq_lens, query_start_loc, topk,
+                                   int8=q_fp8.dtype == torch.int8)

@@ -181,13 +181,13 @@ void concat_and_cache_mla(const Tensor& kv_c, const Tensor& k_pe, Tensor& cache,
                              status_ptr(kv_c), cur_stream());
 }
 void indexer_k_quant_and_cache(const Tensor& k, Tensor& cache, const Tensor& slot_mapping, int64_t block_size,
-                               bool ue8m0) {
+                               bool ue8m0, bool int8) {
   const int hd = k.size(-1);
   TORCH_CHECK(hd % 32 == 0 && hd <= 128 && cache.scalar_type() == at::kByte);
   const int64_t num_slots = cache.size(0) * block_size;
   const c10::cuda::CUDAGuard guard(k.device());
   b200::indexer_k_quant_and_cache(k.data_ptr(), cache.data_ptr(), slot_mapping.data_ptr<int64_t>(), k.size(0), hd,
-                                  block_size, num_slots, k.stride(0), ue8m0, dtype16(k), status_ptr(k), cur_stream());
+                                  block_size, num_slots, k.stride(0), ue8m0, dtype16(k), status_ptr(k), cur_stream(), int8 ? 1 : 0);
 }
 
 // ------------------------------------------------------------------ activations
@@ -572,7 +572,8 @@ void mla_decode(Tensor& out, const Tensor& q, const Tensor& cache, const Tensor&
 
 // ------------------------------------------------------------------ DSA indexer
 void indexer_logits(Tensor& logits, const Tensor& q, const Tensor& w, const Tensor& cache, const Tensor& block_table,
-                    const Tensor& seq_lens, const Tensor& query_start_loc, int64_t block_size, int64_t max_len) {
+                    const Tensor& seq_lens, const Tensor& query_start_loc, int64_t block_size, int64_t max_len,
+                    bool int8) {
   TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.is_contiguous() && q.element_size() == 1);
   TORCH_CHECK(q.size(1) % 16 == 0 && q.size(1) <= 64 && w.is_contiguous() && w.scalar_type() == at::kFloat);
   TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.stride(1) == 1 && logits.size(1) >= max_len);
@@ -581,7 +582,7 @@ void indexer_logits(Tensor& logits, const Tensor& q, const Tensor& w, const Tens
   b200::indexer_logits(logits.data_ptr<float>(), logits.stride(0), q.data_ptr(), w.data_ptr<float>(), cache.data_ptr(),
                        block_table.data_ptr<int>(), block_table.size(1), seq_lens.data_ptr<int>(),
                        query_start_loc.data_ptr<int>(), q.size(0), seq_lens.size(0), q.size(1), block_size,
-                       cache.size(0), max_len, status_ptr(q), cur_stream());
+                       cache.size(0), max_len, status_ptr(q), cur_stream(), int8 ? 1 : 0);
 }
 void topk_per_row(Tensor& out, const Tensor& x, const optional<Tensor>& row_len, int64_t cols) {
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.scalar_type() == at::kFloat && out.is_contiguous());
@@ -1196,7 +1197,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("scaled_mm(Tensor(a!) out, Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor? azp, Tensor? azp_adj, Tensor? bias, Tensor? block_expert, Tensor? total_padded) -> ()", &scaled_mm);
   m.def("wna16_gemm(Tensor(a!) out, Tensor a, Tensor q, Tensor scales, Tensor? zeros, int bits, int group, Tensor? bias, Tensor? block_expert, Tensor? total_padded, int token_tile, int epi) -> ()", &wna16_gemm);
   m.def("mla_decode(Tensor(a!) out, Tensor q, Tensor cache, Tensor block_table, Tensor seq_lens, Tensor? query_start_loc, Tensor? topk_indices, float scale, Tensor(b!)? lse_out, Tensor(c!)? workspace, int num_splits) -> ()", &mla_decode);
-  m.def("indexer_logits(Tensor(a!) logits, Tensor q, Tensor w, Tensor cache, Tensor block_table, Tensor seq_lens, Tensor query_start_loc, int block_size, int max_len) -> ()", &indexer_logits);
+  m.def("indexer_logits(Tensor(a!) logits, Tensor q, Tensor w, Tensor cache, Tensor block_table, Tensor seq_lens, Tensor query_start_loc, int block_size, int max_len, bool int8) -> ()", &indexer_logits);
   m.def("topk_per_row(Tensor(a!) out, Tensor x, Tensor? row_len, int cols) -> ()", &topk_per_row);
   m.def("symm_alloc(int nbytes, int device) -> (Tensor, Tensor)", &symm_alloc);
   m.def("symm_open(Tensor handle, int device) -> int", &symm_open);
@@ -1224,7 +1225,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("concat_and_cache_mla(Tensor kv_c, Tensor k_pe, Tensor(a!) cache, Tensor slot_mapping) -> ()",
         &concat_and_cache_mla);
   m.def(
-      "indexer_k_quant_and_cache(Tensor k, Tensor(a!) cache, Tensor slot_mapping, int block_size, bool ue8m0) -> ()",
+      "indexer_k_quant_and_cache(Tensor k, Tensor(a!) cache, Tensor slot_mapping, int block_size, bool ue8m0, bool int8) -> ()",
       &indexer_k_quant_and_cache);
   m.def("act_and_mul(Tensor(a!) out, Tensor x, int act, float p0, float p1) -> ()", &act_and_mul);
   m.def("activation(Tensor(a!) out, Tensor x, int act, float p0) -> ()", &activation);

@@ -1,6 +1,6 @@
 // DeepSeek-V3.2 sparse-attention indexer.
 //   indexer_logits   logits[t, n] = k_scale[n] * sum_h w[t, h] * relu(q[t, h, :] . k[n, :])  for the keys of
-//                    token t's own request visible to it (n < limit[t]); -inf elsewhere.  q and k are e4m3;
+//                    token t's own request visible to it (n < limit[t]); -inf elsewhere.  q and k are e4m3 (or int8);
 //                    the products run on m16n8k16 MMAs after an exact fp8 -> bf16 widening, one warp per 16
 //                    index heads, 32 keys per step read straight from the paged, block-planar key cache.
 //   topk_per_row     indices of the k largest finite entries of every row (radix select: four 8-bit
@@ -30,7 +30,7 @@ __global__ void indexer_logits_kernel(float* __restrict__ logits, int64_t logits
                                       const int* __restrict__ block_table, int max_blocks,
                                       const int* __restrict__ seq_lens, const int* __restrict__ query_start_loc,
                                       int batch, int heads, int block_size, int64_t num_blocks, int keys_per_cta,
-                                      StatusWord* status) {
+                                      StatusWord* status, int kind) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ int s_seq, s_lim;
   __shared__ float s_sum[kIdxKeys];
@@ -64,7 +64,7 @@ __global__ void indexer_logits_kernel(float* __restrict__ logits, int64_t logits
     const uint8_t* bb = reinterpret_cast<const uint8_t*>(&b8);
     float f[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) f[j] = fp8_e4m3_to_float(bb[j]);
+    for (int j = 0; j < 8; ++j) f[j] = kind == 1 ? (float)(int8_t)bb[j] : fp8_e4m3_to_float(bb[j]);   // both exact in bf16
     *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(qs) + r * 256 + ((c ^ (r & 7)) * 16)) = pack8<__nv_bfloat16>(f);
   }
   __syncthreads();
@@ -95,7 +95,7 @@ __global__ void indexer_logits_kernel(float* __restrict__ logits, int64_t logits
         const uint2 b8 = *reinterpret_cast<const uint2*>(src);
         const uint8_t* bb = reinterpret_cast<const uint8_t*>(&b8);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = fp8_e4m3_to_float(bb[j]);
+        for (int j = 0; j < 8; ++j) f[j] = kind == 1 ? (float)(int8_t)bb[j] : fp8_e4m3_to_float(bb[j]);   // both exact in bf16
         if (c == 0)
           s_scale[r] = *reinterpret_cast<const float*>(cache + page * blk_bytes + (int64_t)block_size * kIdxD +
                                                        (n % block_size) * 4);
@@ -219,14 +219,14 @@ topk_per_row_kernel(int* __restrict__ out, const float* __restrict__ x, int64_t 
 void indexer_logits(float* logits, int64_t logits_stride, const void* q, const float* w, const void* cache,
                     const int* block_table, int max_blocks, const int* seq_lens, const int* query_start_loc,
                     int tokens, int batch, int heads, int block_size, int64_t num_blocks, int max_len, void* status,
-                    cudaStream_t stream) {
+                    cudaStream_t stream, int kind) {
   if (tokens <= 0 || max_len <= 0) return;
   const int keys_per_cta = 1024;
   dim3 grid(tokens, ceil_div(max_len, keys_per_cta));
   const size_t sm = (size_t)(heads + kIdxKeys) * kIdxD * 2;
   indexer_logits_kernel<<<grid, 32 * (heads / 16), sm, stream>>>(
       logits, logits_stride, (const uint8_t*)q, w, (const uint8_t*)cache, block_table, max_blocks, seq_lens,
-      query_start_loc, batch, heads, block_size, num_blocks, keys_per_cta, (StatusWord*)status);
+      query_start_loc, batch, heads, block_size, num_blocks, keys_per_cta, (StatusWord*)status, kind);
 }
 
 void topk_per_row(int* out, const float* x, int64_t stride, const int* row_len, int rows, int cols, int k,

@@ -95,7 +95,7 @@ void concat_and_cache_mla(const void* kv_c, const void* k_pe, void* cache, const
                           int fp8_record, int dtype, void* status, cudaStream_t stream);
 void indexer_k_quant_and_cache(const void* k, void* cache, const int64_t* slot_mapping, int tokens, int head_dim,
                                int block_size, int64_t num_slots, int64_t k_stride, int ue8m0, int dtype, void* status,
-                               cudaStream_t stream);
+                               cudaStream_t stream, int kind = 0);
 // ---- activation.cu
 void act_and_mul(void* out, const void* x, int tokens, int d, int64_t x_stride, int64_t out_stride, int act, float p0,
                  float p1, int dtype, cudaStream_t stream);
@@ -266,7 +266,7 @@ void mla_decode(const MlaDecodeParams& p, int fp8_records, int dtype, cudaStream
 void indexer_logits(float* logits, int64_t logits_stride, const void* q, const float* w, const void* cache,
                     const int* block_table, int max_blocks, const int* seq_lens, const int* query_start_loc,
                     int tokens, int batch, int heads, int block_size, int64_t num_blocks, int max_len, void* status,
-                    cudaStream_t stream);
+                    cudaStream_t stream, int kind = 0);   // kind 1: int8 queries and keys
 void topk_per_row(int* out, const float* x, int64_t stride, const int* row_len, int rows, int cols, int k,
                   cudaStream_t stream);
 // ---- comm_gemm_ar_norm.cu (FusedArParams: comm_params.h)

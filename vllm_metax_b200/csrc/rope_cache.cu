@@ -237,7 +237,7 @@ template <typename T>
 __global__ void indexer_k_quant_and_cache_kernel(const T* __restrict__ k, uint8_t* __restrict__ cache,
                                                  const int64_t* __restrict__ slot_mapping, int head_dim,
                                                  int block_size, int64_t num_slots, int64_t k_stride, int ue8m0,
-                                                 int tokens, StatusWord* status) {
+                                                 int tokens, StatusWord* status, int kind) {
   const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (gw >= tokens) return;
@@ -256,29 +256,32 @@ __global__ void indexer_k_quant_and_cache_kernel(const T* __restrict__ k, uint8_
     m = fmaxf(m, fabsf(x[i]));
   }
   m = warp_max(m);
-  float sc = fmaxf(m / 448.f, 1e-10f);
+  // kind 0: e4m3 keys (scale = amax / 448); kind 1: int8 keys (scale = amax / 127, round to nearest)
+  float sc = fmaxf(m / (kind == 1 ? 127.f : 448.f), 1e-10f);
   if (ue8m0) sc = ue8m0_ceil(sc);
   const int64_t blk = slot / block_size;
   const int off = (int)(slot % block_size);
   uint8_t* bbase = cache + blk * (int64_t)block_size * (head_dim + 4);
   uint8_t* dst = bbase + (int64_t)off * head_dim;
-  for (int i = 0; i < per; ++i) dst[lane * per + i] = float_to_fp8_e4m3(x[i] / sc);
+  for (int i = 0; i < per; ++i)
+    dst[lane * per + i] = kind == 1 ? (uint8_t)(int8_t)max(-127, min(127, __float2int_rn(x[i] / sc)))
+                                    : float_to_fp8_e4m3(x[i] / sc);
   if (lane == 0) reinterpret_cast<float*>(bbase + (int64_t)block_size * head_dim)[off] = sc;
 }
 void indexer_k_quant_and_cache(const void* k, void* cache, const int64_t* slot_mapping, int tokens, int head_dim,
                                int block_size, int64_t num_slots, int64_t k_stride, int ue8m0, int dtype, void* status,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, int kind) {
   if (tokens <= 0) return;
   const int th = 256;
   const int blocks = ceil_div(tokens * 32, th);
   if (dtype == 0)
     indexer_k_quant_and_cache_kernel<__nv_bfloat16><<<blocks, th, 0, stream>>>(
         (const __nv_bfloat16*)k, (uint8_t*)cache, slot_mapping, head_dim, block_size, num_slots, k_stride, ue8m0,
-        tokens, (StatusWord*)status);
+        tokens, (StatusWord*)status, kind);
   else
     indexer_k_quant_and_cache_kernel<__half><<<blocks, th, 0, stream>>>((const __half*)k, (uint8_t*)cache,
                                                                         slot_mapping, head_dim, block_size, num_slots,
-                                                                        k_stride, ue8m0, tokens, (StatusWord*)status);
+                                                                        k_stride, ue8m0, tokens, (StatusWord*)status, kind);
 }
 
 }  // namespace b200

@@ -614,7 +614,8 @@ def concat_mla_q(ql_nope, q_pe):
 
 
 # --------------------------------------------------------------------------- DSA indexer
-def indexer_k_quant_and_cache(k, idx_cache, slot_mapping, quant_block: int = 128, ue8m0: bool = False):
+def indexer_k_quant_and_cache(k, idx_cache, slot_mapping, quant_block: int = 128, ue8m0: bool = False,
+                              int8: bool = False):
     """Quantise indexer keys ``k [T,128]`` to e4m3 + one f32 scale and insert into the
     block-planar cache ``uint8 [nb, bs*(128+4)]``.  Ref: cache_kernels.cu:545-605."""
     nb = idx_cache.shape[0]
@@ -625,10 +626,13 @@ def indexer_k_quant_and_cache(k, idx_cache, slot_mapping, quant_block: int = 128
     slots = slot_mapping[valid].long()
     b, o = slots // bs, slots % bs
     x = k[valid].float()
-    scale = (x.abs().amax(dim=-1) / FP8_MAX).clamp(min=1e-10)
+    scale = (x.abs().amax(dim=-1) / (127.0 if int8 else FP8_MAX)).clamp(min=1e-10)
     if ue8m0:
         scale = _ue8m0_round(scale)
-    q = to_fp8(x / scale[:, None]).view(torch.uint8)
+    if int8:      # V4 indexer: int8 keys, same block-planar layout
+        q = torch.round(x / scale[:, None]).clamp(-127, 127).to(torch.int8).view(torch.uint8)
+    else:
+        q = to_fp8(x / scale[:, None]).view(torch.uint8)
     sb = scale.float().contiguous().view(torch.uint8).reshape(-1, 4)
     cols = o[:, None] * D + torch.arange(D, device=k.device)[None]
     flat[b[:, None], cols] = q
@@ -636,14 +640,14 @@ def indexer_k_quant_and_cache(k, idx_cache, slot_mapping, quant_block: int = 128
     flat[b[:, None], scols] = sb
 
 
-def gather_indexer_k(idx_cache, block_table_row, kv_len, D: int = 128):
+def gather_indexer_k(idx_cache, block_table_row, kv_len, D: int = 128, int8: bool = False):
     """Returns fp32 ``(k_q [L,128] (dequantised values *without* scale), scale [L])``."""
     nb = idx_cache.shape[0]
     flat = idx_cache.reshape(nb, -1)
     bs = flat.shape[1] // (D + 4)
     nblk = (kv_len + bs - 1) // bs
     blk = flat[block_table_row[:nblk].long()]
-    kq = blk[:, : bs * D].contiguous().view(FP8_DTYPE).float().reshape(nblk * bs, D)[:kv_len]
+    kq = blk[:, : bs * D].contiguous().view(torch.int8 if int8 else FP8_DTYPE).float().reshape(nblk * bs, D)[:kv_len]
     sc = blk[:, bs * D:].contiguous().view(torch.float32).reshape(nblk * bs)[:kv_len]
     return kq, sc
 
@@ -674,7 +678,8 @@ def top_k_per_row(logits, k: int):
     return idx.to(torch.int32)
 
 
-def sparse_attn_indexer(q_fp8, weights, idx_cache, block_table, seq_lens, query_start_loc, topk: int):
+def sparse_attn_indexer(q_fp8, weights, idx_cache, block_table, seq_lens, query_start_loc, topk: int,
+                        int8: bool = False):
     """Full indexer: for every new token, top-k cache positions of its own request.
 
     ``q_fp8 [T,Hi,128]`` (already quantised values as float/fp8), ``weights [T,Hi]`` with the
@@ -688,7 +693,7 @@ def sparse_attn_indexer(q_fp8, weights, idx_cache, block_table, seq_lens, query_
         s0, s1 = qsl[b], qsl[b + 1]
         if s1 <= s0:
             continue
-        kq, sc = gather_indexer_k(idx_cache, block_table[b], sl[b])
+        kq, sc = gather_indexer_k(idx_cache, block_table[b], sl[b], int8=int8)
         Lq = s1 - s0
         ke = sl[b] - Lq + 1 + torch.arange(Lq, device=q_fp8.device)
         ks = torch.zeros_like(ke)
