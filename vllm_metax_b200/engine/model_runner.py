@@ -84,7 +84,13 @@ class ModelRunner:
 
             # small reductions (decode steps, MoE outputs, logits pieces) skip NCCL's launch + protocol latency
             self.custom_ar = CustomAllReduce(ps.get_tp_group(), self.device, envs.B200_CUSTOM_ALLREDUCE_MAX_BYTES)
-            self.custom_ar.attach()
+            if self.custom_ar.self_test():          # checked once against the library all-reduce at this world size
+                self.custom_ar.attach()
+            else:
+                import warnings
+
+                warnings.warn("peer-store all-reduce failed its start-up check; tensor-parallel reductions stay on NCCL")
+                self.custom_ar = None
         if (ps.tp_size() == 1 or ps.get_pp_group().world_size > 1 or not envs.B200_FUSED_TP_COLLECTIVES
                 or inner is None or not hasattr(inner, "forward_fused_tp")
                 or not getattr(inner, "supports_fused_tp", True) or self.cfg.model.quantization

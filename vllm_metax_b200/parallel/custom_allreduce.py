@@ -68,6 +68,33 @@ class CustomAllReduce:
                                         self.local_sync, mode, self.wait_cycles)
         return out
 
+    def self_test(self) -> bool:
+        """Both modes against the library all-reduce on a small and a medium message; every rank gets the same
+        verdict (the comparison result is itself reduced).  A failed or timed-out kernel leaves the context usable:
+        the waits are bounded and only set the status word, which is cleared here."""
+        if not self.cuda:
+            return True
+        import torch.distributed as dist
+
+        ok = True
+        gen = torch.Generator(device="cpu").manual_seed(1234 + self.rank)
+        for n in (4096, min(self.max_bytes // 2, 1 << 20)):
+            x = torch.randn(n, generator=gen).to(self.device, torch.bfloat16)
+            want = x.clone()
+            dist.all_reduce(want, group=self.group.device_pg)
+            for mode in (1, 2):
+                got = torch.empty_like(x)
+                self.all_reduce(x, out=got, mode=mode)
+                ok = ok and bool(torch.allclose(got.float(), want.float(), rtol=3e-2, atol=3e-2))
+        torch.cuda.synchronize(self.device)
+        try:
+            ops.check_kernel_status(self.device.index or 0)
+        except RuntimeError:
+            ok = False
+        flag = torch.tensor([1 if ok else 0], device=self.device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group.device_pg)
+        return bool(flag.item())
+
     def attach(self) -> None:
         """Make ``group.all_reduce`` use this object for eligible CUDA tensors."""
         self.group.custom_allreduce = self
