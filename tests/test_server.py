@@ -134,3 +134,66 @@ def test_lora_adapter_selected_by_model_name():
         assert llm.engine.runner.lora.list_adapters() == [1]
     finally:
         allm.shutdown()
+
+
+def test_tracing_and_latency_histograms():
+    """One span per finished request reaches an OTLP/HTTP collector (a fake one here), continuing the caller's
+    trace; /metrics exposes the latency histograms."""
+    pytest.importorskip("httpx")
+    import http.server
+    import threading
+
+    from vllm_metax_b200.utils.observability import Histogram, RequestTracer, parse_traceparent
+
+    got = []
+
+    class Collector(http.server.BaseHTTPRequestHandler):
+        def do_POST(self):
+            got.append((self.path, json.loads(self.rfile.read(int(self.headers["Content-Length"])))))
+            self.send_response(200)
+            self.end_headers()
+
+        def log_message(self, *a):
+            pass
+
+    srv = http.server.HTTPServer(("127.0.0.1", 0), Collector)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    cfg = ModelConfig(architecture="LlamaForCausalLM", vocab_size=256, hidden_size=64, intermediate_size=128,
+                      num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                      max_position_embeddings=256, dtype=torch.float32)
+    llm = LLM(cfg, device="cpu", load_format="dummy", num_gpu_blocks=64, block_size=16, max_model_len=256,
+              tokenizer=ToyTokenizer(), seed=0)
+    tracer = RequestTracer.from_endpoint(f"http://127.0.0.1:{srv.server_port}", "toy")
+    allm = AsyncLLM(llm, tracer)
+    try:
+        app = build_app(allm, "toy")
+
+        async def go():
+            import httpx
+
+            async with httpx.AsyncClient(transport=httpx.ASGITransport(app=app), base_url="http://test") as c:
+                tp = "00-0af7651916cd43dd8448eb211c80319c-b7ad6b7169203331-01"
+                r = await c.post("/v1/completions", json={"prompt": "hello", "max_tokens": 5, "ignore_eos": True},
+                                 headers={"traceparent": tp})
+                m = await c.get("/metrics")
+                return r.status_code, m.text
+
+        code, metrics = asyncio.run(go())
+        assert code == 200
+        tracer.exporter.flush()
+        assert got and got[0][0] == "/v1/traces"
+        span = got[0][1]["resourceSpans"][0]["scopeSpans"][0]["spans"][0]
+        assert span["traceId"] == "0af7651916cd43dd8448eb211c80319c" and span["parentSpanId"] == "b7ad6b7169203331"
+        attrs = {a["key"]: a["value"] for a in span["attributes"]}
+        assert attrs["gen_ai.usage.completion_tokens"]["intValue"] == "5"
+        assert "gen_ai.latency.time_to_first_token" in attrs and "gen_ai.latency.e2e" in attrs
+        assert 'b200:time_to_first_token_seconds_bucket{le="+Inf"} 1' in metrics
+        assert "b200:inter_token_latency_seconds_count 4" in metrics and "b200:e2e_request_latency_seconds_sum" in metrics
+    finally:
+        allm.shutdown()
+        srv.shutdown()
+    assert parse_traceparent("garbage") == (None, None)
+    h = Histogram("x", "h", (1.0, 2.0))
+    for v in (0.5, 1.5, 3.0):
+        h.observe(v)
+    assert 'x_bucket{le="2.0"} 2' in h.render("") and 'x_bucket{le="+Inf"} 3' in h.render("")

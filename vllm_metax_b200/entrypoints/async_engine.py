@@ -39,12 +39,21 @@ class _Stream:
     sent: int = 0
     t_arrival: float = field(default_factory=time.perf_counter)
     t_first: Optional[float] = None
+    t_last: Optional[float] = None                 # time of the previous token batch (inter-token latency)
+    wall_arrival: float = field(default_factory=time.time)
+    traceparent: Optional[str] = None
+    params: Optional[SamplingParams] = None
 
 
 class AsyncLLM:
-    def __init__(self, llm: LLM):
+    def __init__(self, llm: LLM, tracer=None):
+        """``tracer``: a ``utils.observability.RequestTracer`` (one span per finished request) or None."""
+        from ..utils.observability import latency_histograms
+
         self.llm = llm
         self.engine = llm.engine
+        self.tracer = tracer
+        self.histograms = latency_histograms()
         self._inbox: list[tuple] = []
         self._aborts: list[str] = []
         self._lock = threading.Lock()
@@ -109,6 +118,12 @@ class AsyncLLM:
                     st.t_first = now
                     self.metrics["ttft_sum"] += now - st.t_arrival
                     self.metrics["ttft_count"] += 1
+                    self.histograms["ttft"].observe(now - st.t_arrival)
+                elif n > st.sent and st.t_last is not None:
+                    for _ in range(n - st.sent):
+                        self.histograms["itl"].observe((now - st.t_last) / (n - st.sent))
+                if n > st.sent:
+                    st.t_last = now
                 new = list(r.output_token_ids[st.sent:n])
                 self.metrics["generated_tokens"] += len(new)
                 st.sent = n
@@ -120,18 +135,24 @@ class AsyncLLM:
                                            ttft=None if st.t_first is None else st.t_first - st.t_arrival))
                 if fin:
                     self.metrics["requests_finished"] += 1
+                    self.histograms["e2e"].observe(now - st.t_arrival)
+                    if self.tracer is not None:
+                        self.tracer.finish(rid, arrival_wall=st.wall_arrival, t_arrival=st.t_arrival, t_first=st.t_first,
+                                           t_end=now, prompt_tokens=len(r.prompt_token_ids), completion_tokens=n,
+                                           params=st.params, finish_reason=out.outputs[0].finish_reason,
+                                           traceparent=st.traceparent, cached_tokens=r.num_cached_tokens)
                     del self._streams[rid]
 
     # ------------------------------------------------------------------ coroutine API
     async def generate(self, prompt_token_ids: Sequence[int], params: SamplingParams, request_id: Optional[str] = None,
-                       prompt: Optional[str] = None) -> AsyncIterator[StreamChunk]:
+                       prompt: Optional[str] = None, traceparent: Optional[str] = None) -> AsyncIterator[StreamChunk]:
         if self.engine.dead is not None:
             raise EngineDeadError(str(self.engine.dead))
         loop = asyncio.get_running_loop()
         with self._lock:
             self._seq += 1
             rid = request_id or f"cmpl-{self._seq}"
-            st = _Stream(asyncio.Queue(), loop)
+            st = _Stream(asyncio.Queue(), loop, traceparent=traceparent, params=params)
             self._inbox.append((rid, list(prompt_token_ids), params, prompt, st))
         self._wake.set()
         try:

@@ -32,6 +32,7 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--enforce-eager", action="store_true")
     s.add_argument("--device", default="cuda")
     s.add_argument("--seed", type=int, default=0)
+    s.add_argument("--otlp-traces-endpoint", default=None, help="OTLP/HTTP collector, e.g. http://localhost:4318")
     s.add_argument("--enable-lora", action="store_true")
     s.add_argument("--max-loras", type=int, default=4)
     s.add_argument("--max-lora-rank", type=int, default=64)
@@ -117,7 +118,10 @@ def main(argv=None) -> int:
     from ..lora import LoRARequest
 
     loras = {n: LoRARequest(n, i + 1, p) for i, (n, p) in enumerate(m.split("=", 1) for m in args.lora_modules)}
-    app = build_app(AsyncLLM(llm), args.served_model_name or str(args.model), loras)
+    from ..utils.observability import RequestTracer
+
+    name = args.served_model_name or str(args.model)
+    app = build_app(AsyncLLM(llm, RequestTracer.from_endpoint(args.otlp_traces_endpoint, name)), name, loras)
     uvicorn.run(app, host=args.host, port=args.port, log_level="info")
     return 0
 

@@ -85,6 +85,8 @@ def prometheus_text(allm: AsyncLLM) -> str:
     usage = getattr(kv, "usage", None)
     if callable(usage):
         g("kv_cache_usage_perc", usage(), help_="fraction of KV blocks in use")
+    for h in getattr(allm, "histograms", {}).values():
+        lines.append(h.render())
     return "\n".join(lines) + "\n"
 
 
@@ -172,9 +174,9 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
         llm.resume_generation()
         return {"status": "running"}
 
-    async def run_one(ids, prompt, params, rid):
+    async def run_one(ids, prompt, params, rid, traceparent=None):
         last = None
-        async for chunk in allm.generate(ids, params, rid, prompt):
+        async for chunk in allm.generate(ids, params, rid, prompt, traceparent):
             last = chunk
         return last
 
@@ -182,7 +184,7 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
         return {"prompt_tokens": prompt_tokens, "completion_tokens": completion_tokens,
                 "total_tokens": prompt_tokens + completion_tokens}
 
-    async def serve(body: dict, chat: bool):
+    async def serve(body: dict, chat: bool, traceparent: Optional[str] = None):
         try:
             if chat:
                 text = render_chat(tok, body.get("messages") or [])
@@ -204,7 +206,7 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
         obj = "chat.completion" if chat else "text_completion"
         if not body.get("stream"):
             try:
-                last = await run_one(ids, prompt, params, rid)
+                last = await run_one(ids, prompt, params, rid, traceparent)
             except EngineDeadError as e:
                 return err(500, str(e), "engine_dead")
             text = last.text if last.text is not None else ""
@@ -218,7 +220,7 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
             prev = ""
             ntok = 0
             try:
-                async for chunk in allm.generate(ids, params, rid, prompt):
+                async for chunk in allm.generate(ids, params, rid, prompt, traceparent):
                     cur = chunk.text if chunk.text is not None else ""
                     delta, prev = cur[len(prev):] if cur.startswith(prev) else cur, cur
                     ntok = len(chunk.token_ids)
@@ -240,10 +242,10 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
 
     @app.post("/v1/completions")
     async def completions(req: Request):
-        return await serve(await req.json(), chat=False)
+        return await serve(await req.json(), chat=False, traceparent=req.headers.get("traceparent"))
 
     @app.post("/v1/chat/completions")
     async def chat_completions(req: Request):
-        return await serve(await req.json(), chat=True)
+        return await serve(await req.json(), chat=True, traceparent=req.headers.get("traceparent"))
 
     return app
