@@ -256,8 +256,15 @@ class ModelRunner:
     # ------------------------------------------------------------------ execution
     def _forward(self, md: AttentionMetadata, T: int):
         ctx = ForwardContext(md, self.kv_caches, self.positions[:T])
-        with set_forward_context(ctx):
-            return self.model(self.input_ids[:T], self.positions[:T])
+        nvtx = self.is_cuda and envs.B200_NVTX
+        if nvtx:      # a named range per step in Nsight timelines: tokens, decode / prefill split
+            torch.cuda.nvtx.range_push(f"forward T={T} decodes={md.num_decodes} prefills={md.num_prefills}")
+        try:
+            with set_forward_context(ctx):
+                return self.model(self.input_ids[:T], self.positions[:T])
+        finally:
+            if nvtx:
+                torch.cuda.nvtx.range_pop()
 
     def _decode_splits(self, batch: int) -> int:
         spec = self.model.kv_cache_spec()

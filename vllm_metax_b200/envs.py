@@ -76,6 +76,8 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # (larger messages stay on NCCL).
     "B200_CUSTOM_ALLREDUCE": _flag("B200_CUSTOM_ALLREDUCE", "1"),
     "B200_CUSTOM_ALLREDUCE_MAX_BYTES": _int("B200_CUSTOM_ALLREDUCE_MAX_BYTES", 8 << 20),
+    # NVTX range around every forward pass (Nsight Systems / Compute timelines).
+    "B200_NVTX": _flag("B200_NVTX", "0"),
     # ---- debug -------------------------------------------------------------
     "B200_FORCE_REFERENCE_OPS": _flag("B200_FORCE_REFERENCE_OPS", "0"),
     "B200_PRECISION_DUMP_DIR": _str("B200_PRECISION_DUMP_DIR", None),
