@@ -200,3 +200,42 @@ def test_deepseek_v32_gpu_tracks_cpu(kernel_status_ok):
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (150, 60)]
     lockstep(cpu, gl, prompts, steps=4, tol=3e-2)
+
+
+@gpu
+def test_indexer_bf16_variant_gpu(kernel_status_ok):
+    """Unquantised indexer: bf16 queries against a bf16 key cache, same logits / top-k contract."""
+    bs, Hi = 64, 32
+    lens, qlens = [200, 700], [3, 1]
+    g = torch.Generator().manual_seed(3)
+    nblk = [(l + bs - 1) // bs for l in lens]
+    total = sum(nblk) + 1
+    bt = torch.zeros(2, max(nblk), dtype=torch.int32)
+    perm = torch.randperm(total, generator=g)
+    bt[0, : nblk[0]] = perm[: nblk[0]].int()
+    bt[1, : nblk[1]] = perm[nblk[0]: nblk[0] + nblk[1]].int()
+    cache = torch.zeros(total, bs, 128, dtype=torch.bfloat16)
+    for b in range(2):
+        k = torch.randn(lens[b], 128, generator=g).bfloat16()
+        pos = torch.arange(lens[b])
+        cache.view(-1, 128)[bt[b].long()[pos // bs] * bs + pos % bs] = k
+    T = sum(qlens)
+    q = torch.randn(T, Hi, 128, generator=g).bfloat16()
+    w = torch.randn(T, Hi, generator=g) * 0.1
+    sl = torch.tensor(lens, dtype=torch.int32)
+    qsl = torch.tensor([0, 3, 4], dtype=torch.int32)
+    got, logits = ops.indexer_topk(q.cuda(), w.cuda(), cache.cuda(), bt.cuda(), sl.cuda(), qsl.cuda(), 64, bs,
+                                   max_seq_len=max(lens), return_logits=True)
+    want = ref.sparse_attn_indexer(q.float(), w, cache, bt, sl, qsl, 64, bf16=True)
+    t = 0
+    for b in range(2):
+        kq = cache[bt[b][: nblk[b]].long()].reshape(-1, 128)[: lens[b]].float()
+        for i in range(qlens[b]):
+            lim = lens[b] - qlens[b] + i + 1
+            lg = ref.mqa_logits(q[t:t + 1].float(), kq, torch.ones(lens[b]), w[t:t + 1], torch.tensor([0]), torch.tensor([lim]))[0]
+            mine = logits[t, : lens[b]].cpu()
+            fin = torch.isfinite(lg)
+            assert bool((torch.isfinite(mine) == fin).all())
+            torch.testing.assert_close(mine[fin], lg[fin], rtol=2e-2, atol=5e-2)
+            assert set(got[t].cpu().tolist()) - {-1} == set(want[t].tolist()) - {-1} or lim > 64
+            t += 1

@@ -892,7 +892,11 @@ def indexer_topk(q_fp8, weights, idx_cache, block_table, seq_lens, query_start_l
         Lp = (L + 1023) // 1024 * 1024
         logits = torch.empty(T, Lp, dtype=torch.float32, device=q_fp8.device)
         i8 = q_fp8.dtype == torch.int8
-        qb = q_fp8 if (i8 or q_fp8.dtype == torch.float8_e4m3fn) else q_fp8.to(torch.float8_e4m3fn)
+        if q_fp8.dtype == torch.bfloat16:        # unquantised indexer: ``idx_cache`` is bf16 [blocks, block_size, 128]
+            qb = q_fp8
+            idx_cache = idx_cache.view(torch.uint8).reshape(idx_cache.shape[0], -1)
+        else:
+            qb = q_fp8 if (i8 or q_fp8.dtype == torch.float8_e4m3fn) else q_fp8.to(torch.float8_e4m3fn)
         torch.ops.b200.indexer_logits(logits, qb.contiguous(), weights.float().contiguous(), idx_cache, block_table,
                                       seq_lens, query_start_loc, block_size, L, i8)
         _ = _use_cuda(q_fp8)  # second kernel of the op (launch accounting)
@@ -900,4 +904,4 @@ def indexer_topk(q_fp8, weights, idx_cache, block_table, seq_lens, query_start_l
         torch.ops.b200.topk_per_row(out, logits, None, Lp)
         return (out, logits) if return_logits else out
     return ref.sparse_attn_indexer(q_fp8.float(), weights, idx_cache, block_table, seq_lens, query_start_loc, topk,
-                                   int8=q_fp8.dtype == torch.int8)
+                                   int8=q_fp8.dtype == torch.int8, bf16=q_fp8.dtype == torch.bfloat16)

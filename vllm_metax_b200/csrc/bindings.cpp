@@ -574,7 +574,8 @@ void mla_decode(Tensor& out, const Tensor& q, const Tensor& cache, const Tensor&
 void indexer_logits(Tensor& logits, const Tensor& q, const Tensor& w, const Tensor& cache, const Tensor& block_table,
                     const Tensor& seq_lens, const Tensor& query_start_loc, int64_t block_size, int64_t max_len,
                     bool int8) {
-  TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.is_contiguous() && q.element_size() == 1);
+  const bool bf16 = q.scalar_type() == at::kBFloat16;      // unquantised indexer: bf16 queries, bf16 key cache
+  TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.is_contiguous() && (q.element_size() == 1 || bf16));
   TORCH_CHECK(q.size(1) % 16 == 0 && q.size(1) <= 64 && w.is_contiguous() && w.scalar_type() == at::kFloat);
   TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.stride(1) == 1 && logits.size(1) >= max_len);
   TORCH_CHECK(cache.is_contiguous() && cache.scalar_type() == at::kByte);
@@ -582,7 +583,7 @@ void indexer_logits(Tensor& logits, const Tensor& q, const Tensor& w, const Tens
   b200::indexer_logits(logits.data_ptr<float>(), logits.stride(0), q.data_ptr(), w.data_ptr<float>(), cache.data_ptr(),
                        block_table.data_ptr<int>(), block_table.size(1), seq_lens.data_ptr<int>(),
                        query_start_loc.data_ptr<int>(), q.size(0), seq_lens.size(0), q.size(1), block_size,
-                       cache.size(0), max_len, status_ptr(q), cur_stream(), int8 ? 1 : 0);
+                       cache.size(0), max_len, status_ptr(q), cur_stream(), bf16 ? 2 : (int8 ? 1 : 0));
 }
 void topk_per_row(Tensor& out, const Tensor& x, const optional<Tensor>& row_len, int64_t cols) {
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.scalar_type() == at::kFloat && out.is_contiguous());

@@ -57,9 +57,15 @@ __global__ void indexer_logits_kernel(float* __restrict__ logits, int64_t logits
   // q tile: heads x 128 bf16, swizzled rows of 256 bytes
   __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem);
   __nv_bfloat16* ks = qs + heads * kIdxD;
-  const uint8_t* qt = q + (int64_t)t * heads * kIdxD;
+  const int esz = kind == 2 ? 2 : 1;                 // kind 2: bf16 queries and keys, no scales
+  const uint8_t* qt = q + (int64_t)t * heads * kIdxD * esz;
   for (int i = threadIdx.x; i < heads * 16; i += blockDim.x) {
     const int r = i >> 4, c = i & 15;
+    if (kind == 2) {
+      *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(qs) + r * 256 + ((c ^ (r & 7)) * 16)) =
+          *reinterpret_cast<const uint4*>(qt + r * 256 + c * 16);
+      continue;
+    }
     const uint2 b8 = *reinterpret_cast<const uint2*>(qt + r * kIdxD + c * 8);
     const uint8_t* bb = reinterpret_cast<const uint8_t*>(&b8);
     float f[8];
@@ -78,7 +84,7 @@ __global__ void indexer_logits_kernel(float* __restrict__ logits, int64_t logits
   const float wA = w[(int64_t)t * heads + warp * 16 + (lane >> 2)];
   const float wB = w[(int64_t)t * heads + warp * 16 + (lane >> 2) + 8];
   const int* btab = block_table + (int64_t)seq * max_blocks;
-  const int64_t blk_bytes = (int64_t)block_size * (kIdxD + 4);
+  const int64_t blk_bytes = kind == 2 ? (int64_t)block_size * kIdxD * 2 : (int64_t)block_size * (kIdxD + 4);
 
   for (int base = n0; base < n1; base += kIdxKeys) {
     // load + widen 32 keys
@@ -91,6 +97,12 @@ __global__ void indexer_logits_kernel(float* __restrict__ logits, int64_t logits
       if (n < n1) {
         int page = btab[n / block_size];
         if (page < 0 || page >= num_blocks) { report_status(status, kBadIndex, 97, (int)num_blocks, page); page = 0; }
+        if (kind == 2) {
+          *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(ks) + r * 256 + ((c ^ (r & 7)) * 16)) =
+              *reinterpret_cast<const uint4*>(cache + page * blk_bytes + (int64_t)(n % block_size) * 256 + c * 16);
+          if (c == 0) s_scale[r] = 1.f;
+          continue;
+        }
         const uint8_t* src = cache + page * blk_bytes + (int64_t)(n % block_size) * kIdxD + c * 8;
         const uint2 b8 = *reinterpret_cast<const uint2*>(src);
         const uint8_t* bb = reinterpret_cast<const uint8_t*>(&b8);

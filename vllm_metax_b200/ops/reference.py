@@ -679,7 +679,7 @@ def top_k_per_row(logits, k: int):
 
 
 def sparse_attn_indexer(q_fp8, weights, idx_cache, block_table, seq_lens, query_start_loc, topk: int,
-                        int8: bool = False):
+                        int8: bool = False, bf16: bool = False):
     """Full indexer: for every new token, top-k cache positions of its own request.
 
     ``q_fp8 [T,Hi,128]`` (already quantised values as float/fp8), ``weights [T,Hi]`` with the
@@ -693,7 +693,12 @@ def sparse_attn_indexer(q_fp8, weights, idx_cache, block_table, seq_lens, query_
         s0, s1 = qsl[b], qsl[b + 1]
         if s1 <= s0:
             continue
-        kq, sc = gather_indexer_k(idx_cache, block_table[b], sl[b], int8=int8)
+        if bf16:      # unquantised keys: bf16 [blocks, block_size, 128], no scales
+            nblk = (sl[b] + idx_cache.shape[1] - 1) // idx_cache.shape[1]
+            kq = idx_cache[block_table[b][:nblk].long()].reshape(-1, idx_cache.shape[-1])[: sl[b]].float()
+            sc = torch.ones(sl[b], device=kq.device)
+        else:
+            kq, sc = gather_indexer_k(idx_cache, block_table[b], sl[b], int8=int8)
         Lq = s1 - s0
         ke = sl[b] - Lq + 1 + torch.arange(Lq, device=q_fp8.device)
         ks = torch.zeros_like(ke)
