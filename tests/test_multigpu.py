@@ -289,3 +289,43 @@ def _custom_ar_worker(rank, world):
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_custom_allreduce_and_reduce_rms_2gpu():
     _launch(_custom_ar_worker, _world())
+
+
+def _moe_layer_a2a_worker(rank, world):
+    """FusedMoE with B200_MOE_A2A=1 (sequence-parallel dispatch / combine) against the fp32 MoE oracle."""
+    os.environ["B200_MOE_A2A"] = "1"
+    from vllm_metax_b200 import _custom_ops as ops
+    from vllm_metax_b200.layers.fused_moe import FusedMoE, reference_moe
+    from vllm_metax_b200.parallel import state as ps
+
+    ps.init_distributed(tensor_parallel_size=world)
+    dev = torch.device("cuda", rank)
+    E, H, I, topk = 8, 512, 256, 2
+    gen = torch.Generator().manual_seed(21)
+    w13 = (torch.randn(E, 2 * I, H, generator=gen) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=gen) * 0.05).to(torch.bfloat16)
+    with torch.device(dev):
+        moe = FusedMoE(E, topk, H, I, dtype=torch.bfloat16, renormalize=True)
+    el = E // world
+    moe.w13_weight.data.copy_(w13[rank * el:(rank + 1) * el])
+    moe.w2_weight.data.copy_(w2[rank * el:(rank + 1) * el])
+    for T in (37, 1, 200, 64):
+        x = (torch.randn(T, H, generator=gen) * 0.5).to(torch.bfloat16)
+        logits = torch.randn(T, E, generator=gen)
+        shared = (torch.randn(T, H, generator=gen) * 0.1).to(torch.bfloat16) if T == 200 else None
+        got = moe(x.to(dev), logits.to(dev), None if shared is None else (shared / world).to(dev))
+        torch.cuda.synchronize()
+        ops.check_kernel_status(rank)
+        from vllm_metax_b200.ops import reference as ref
+
+        tw, ti = ref.topk_softmax(logits, topk, True)
+        want = reference_moe(x.float(), w13.float(), w2.float(), tw, ti.long())
+        if shared is not None:
+            want = want + shared.float()
+        err = 1.0 - float(torch.nn.functional.cosine_similarity(got.float().cpu().flatten(), want.flatten(), dim=0))
+        assert got.shape == (T, H) and err < 5e-4, (T, err)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_fused_moe_sequence_parallel_a2a_2gpu():
+    _launch(_moe_layer_a2a_worker, 2)

@@ -51,6 +51,8 @@ environment_variables: dict[str, Callable[[], Any]] = {
     "B200_FUSED_TP_COLLECTIVES": _flag("B200_FUSED_TP_COLLECTIVES", "1"),
     # Steps with fewer tokens than this use GEMM + peer-store all-reduce + add-norm instead of the fused kernel.
     "B200_FUSED_TP_MIN_TOKENS": _int("B200_FUSED_TP_MIN_TOKENS", 1024),
+    # Sequence-parallel MoE through the NVLink dispatch / combine kernels instead of experts-on-all-tokens + all-reduce.
+    "B200_MOE_A2A": _flag("B200_MOE_A2A", "0"),
     # Pack topk weights/ids/scales into one tensor for the AG/RS dispatch.
     "B200_OPTIMIZED_DP_ALL2ALL": _flag("B200_OPTIMIZED_DP_ALL2ALL", "1"),
     # Run prefill and decode slices of a mixed batch through separate kernels.

@@ -32,6 +32,7 @@ import torch
 import torch.nn as nn
 
 from .. import _custom_ops as ops
+from .. import envs
 from ..ops import reference as ref
 from ..parallel import state as ps
 from .linear import ReplicatedLinear
@@ -128,8 +129,43 @@ class FusedMoE(nn.Module):
         return ops.topk_gating(router_logits, self.top_k, self.renormalize, self.scoring_func, bias,
                                self.routed_scaling_factor)
 
+    def _forward_a2a(self, x: torch.Tensor, router_logits: torch.Tensor,
+                     shared_out: Optional[torch.Tensor]) -> torch.Tensor:
+        """Sequence-parallel MoE over the NVLink dispatch / combine kernels: every rank routes its own 1/ep of the
+        tokens, rows travel once to the ranks that own their experts, partial sums come back, and the finished rows
+        are all-gathered - instead of every rank running its experts on all tokens and all-reducing ``[T, H]``
+        (the reference's sequence-parallel MoE region, models/deepseek_v2.py:1286-1316, with its all2all managers)."""
+        from ..parallel.all2all import NvlinkAll2AllManager, run_experts_a2a
+
+        g = ps.get_tp_group()
+        T, H = x.shape
+        per = (T + self.ep - 1) // self.ep
+        sizes = [max(0, min(per, T - r * per)) for r in range(self.ep)]
+        lo, n = self.ep_rank * per, sizes[self.ep_rank]
+        mgr = getattr(self, "_a2a", None)
+        if mgr is None or mgr.max_tokens < per:
+            if mgr is not None:
+                mgr.close()
+            cap = max(per, 64)
+            mgr = NvlinkAll2AllManager(g, cap, H, self.top_k, self.num_experts, x.dtype, x.device)
+            self._a2a = mgr
+        w, ids = self.route(router_logits[lo: lo + n])
+
+        def experts(a, a_scale, block_expert, total):
+            h = ops.gemm_grouped(a, self.w13_weight, block_expert, total, epi=1)
+            return ops.gemm_grouped(h, self.w2_weight, block_expert, total)
+
+        mine = run_experts_a2a(mgr, x[lo: lo + n].contiguous(), w, ids, experts)
+        y = g.all_gatherv(mine, sizes)
+        if shared_out is not None:       # shared experts are tensor-parallel: their partial sums still need the reduction
+            y = y + (ps.tensor_model_parallel_all_reduce(shared_out) if self.reduce_results else shared_out)
+        return y
+
     def forward(self, x: torch.Tensor, router_logits: torch.Tensor,
                 shared_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if (self.ep > 1 and self.quant_method is None and self.reduce_results and x.is_cuda
+                and envs.B200_MOE_A2A):
+            return self._forward_a2a(x, router_logits, shared_out)
         w, ids = self.route(router_logits)
         if self.quant_method is not None:
             y = self.quant_method.apply(self, x, w, ids, shared_out)
