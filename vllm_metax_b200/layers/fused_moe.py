@@ -149,7 +149,11 @@ class FusedMoE(nn.Module):
             cap = max(per, 64)
             mgr = NvlinkAll2AllManager(g, cap, H, self.top_k, self.num_experts, x.dtype, x.device)
             self._a2a = mgr
-        w, ids = self.route(router_logits[lo: lo + n])
+        if n > 0:
+            w, ids = self.route(router_logits[lo: lo + n])
+        else:           # fewer tokens than ranks: this rank only serves its experts
+            w = torch.empty(0, self.top_k, dtype=torch.float32, device=x.device)
+            ids = torch.empty(0, self.top_k, dtype=torch.int32, device=x.device)
 
         def experts(a, a_scale, block_expert, total):
             h = ops.gemm_grouped(a, self.w13_weight, block_expert, total, epi=1)
