@@ -63,17 +63,28 @@ def bench_gemm(t: Timer, M, N, K, compare: bool, force_bn: int = 0) -> dict:
     return r
 
 
-def bench_prefill(t: Timer, B, L, Hq, Hkv, D, bs) -> dict:
+def bench_prefill(t: Timer, B, L, Hq, Hkv, D, bs, compare: bool = False) -> dict:
     cache, bt = paged_cache(B, L, Hkv, D, bs)
     q = torch.randn(B * L, Hq, D, device=DEV, dtype=torch.bfloat16)
     qsl = torch.arange(B + 1, device=DEV, dtype=torch.int32) * L
     sl = torch.full((B,), L, device=DEV, dtype=torch.int32)
     out = torch.empty_like(q)
     ms = t(lambda: ops.paged_attention_prefill(q, cache, bt, sl, qsl, D ** -0.5, out=out, max_q_len=L))
-    return {"ms": round(ms, 4), "tflops": round(4 * B * L * L / 2 * Hq * D / ms / 1e9, 1)}
+    res = {"ms": round(ms, 4), "tflops": round(4 * B * L * L / 2 * Hq * D / ms / 1e9, 1)}
+    if compare:      # the attention library installed on the box, same problem (contiguous K / V)
+        try:
+            from flash_attn import flash_attn_varlen_func
+
+            k = torch.randn(B * L, Hkv, D, device=DEV, dtype=torch.bfloat16)
+            v = torch.randn_like(k)
+            lib = t(lambda: flash_attn_varlen_func(q, k, v, qsl, qsl, L, L, causal=True))
+            res["flash_attn_ms"] = round(lib, 4)
+        except Exception as e:  # noqa: BLE001
+            res["flash_attn_ms"] = f"unavailable: {type(e).__name__}"
+    return res
 
 
-def bench_decode(t: Timer, B, L, Hq, Hkv, D, bs, kv="bf16") -> dict:
+def bench_decode(t: Timer, B, L, Hq, Hkv, D, bs, kv="bf16", compare: bool = False) -> dict:
     cache, bt = paged_cache(B, L, Hkv, D, bs)
     scales = None
     eb = 2
@@ -85,7 +96,17 @@ def bench_decode(t: Timer, B, L, Hq, Hkv, D, bs, kv="bf16") -> dict:
     sl = torch.full((B,), L, device=DEV, dtype=torch.int32)
     out = torch.empty_like(q)
     ms = t(lambda: ops.paged_attention_decode(q, cache, bt, sl, D ** -0.5, out=out, kv_scales=scales, max_seq_len=L))
-    return {"ms": round(ms, 4), "gbs": round(B * L * Hkv * D * eb * 2 / ms / 1e6, 1)}
+    res = {"ms": round(ms, 4), "gbs": round(B * L * Hkv * D * eb * 2 / ms / 1e6, 1)}
+    if compare and kv == "bf16":
+        try:
+            from flash_attn import flash_attn_with_kvcache
+
+            kc, vc = cache[:, 0].contiguous(), cache[:, 1].contiguous()        # [blocks, block_size, Hkv, D]
+            lib = t(lambda: flash_attn_with_kvcache(q.unsqueeze(1), kc, vc, cache_seqlens=sl, block_table=bt, causal=True))
+            res["flash_attn_ms"] = round(lib, 4)
+        except Exception as e:  # noqa: BLE001
+            res["flash_attn_ms"] = f"unavailable: {type(e).__name__}"
+    return res
 
 
 def bench_elementwise(t: Timer, T, H, I) -> dict:
@@ -184,9 +205,9 @@ def main() -> None:
     if a.op == "quant":
         res[f"quant_{a.m}x{a.n}x{a.k}"] = bench_quant(t, a.m, a.n, a.k)
     if a.op in ("all", "prefill"):
-        res["attn_prefill_8x1024"] = bench_prefill(t, 8, 1024, 32, 8, 128, 128)
+        res["attn_prefill_8x1024"] = bench_prefill(t, 8, 1024, 32, 8, 128, 128, a.compare)
     if a.op in ("all", "decode"):
-        res[f"attn_decode_{a.batch}x{a.seq}_{a.kv}"] = bench_decode(t, a.batch, a.seq, 32, 8, 128, 128, a.kv)
+        res[f"attn_decode_{a.batch}x{a.seq}_{a.kv}"] = bench_decode(t, a.batch, a.seq, 32, 8, 128, 128, a.kv, a.compare)
     if a.op in ("all", "elementwise"):
         for T in (8192, 256):
             for k, v in bench_elementwise(t, T, H, I).items():
