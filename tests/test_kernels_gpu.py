@@ -445,3 +445,34 @@ def test_gemm_cta_pair(M, N, K):
     got = ops.gemm(a, w, bias, res, force_bn=512)
     assert (got.float() - want).abs().max() / want.abs().max() < 1.5e-2
     assert cos_diff(got, want) < 1e-5
+
+
+@gpu
+@pytest.mark.parametrize("D", [64, 128])
+def test_alibi_bias_in_prefill_and_decode(D, kernel_status_ok):
+    """ALiBi slopes: score += slope[h] * (kv position - query position), both attention kernels."""
+    torch.manual_seed(9)
+    Hq, Hkv, bs = 8, 2, 16
+    lens, qlens = [70, 33, 130], [70, 1, 17]          # fresh prefill, decode, chunked prefill
+    B = len(lens)
+    nblk = [(l + bs - 1) // bs for l in lens]
+    bt = torch.zeros(B, max(nblk), dtype=torch.int32)
+    perm = torch.randperm(sum(nblk) + 1)
+    o = 0
+    for b in range(B):
+        bt[b, : nblk[b]] = perm[o:o + nblk[b]].int()
+        o += nblk[b]
+    cache = torch.randn(sum(nblk) + 1, 2, bs, Hkv, D).bfloat16()
+    q = torch.randn(sum(qlens), Hq, D).bfloat16()
+    slopes = torch.tensor([2.0 ** (-(i + 1)) for i in range(Hq)])
+    sl = torch.tensor(lens, dtype=torch.int32)
+    qsl = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32)
+    want = ref.paged_attention(q.float(), cache.float(), bt, sl, qsl, D ** -0.5, alibi_slopes=slopes)
+    plain = ref.paged_attention(q.float(), cache.float(), bt, sl, qsl, D ** -0.5)
+    assert (want - plain).abs().max() > 1e-2          # the bias matters in this case
+    got_p = ops.paged_attention_prefill(q.cuda(), cache.cuda(), bt.cuda(), sl.cuda(), qsl.cuda(), D ** -0.5,
+                                        max_q_len=max(qlens), alibi_slopes=slopes.cuda())
+    torch.testing.assert_close(got_p.float().cpu(), want, rtol=3e-2, atol=3e-2)
+    got_d = ops.paged_attention_decode(q.cuda(), cache.cuda(), bt.cuda(), sl.cuda(), D ** -0.5, query_start_loc=qsl.cuda(),
+                                       max_q_len=max(qlens), max_seq_len=max(lens), alibi_slopes=slopes.cuda())
+    torch.testing.assert_close(got_d.float().cpu(), want, rtol=3e-2, atol=3e-2)

@@ -371,8 +371,9 @@ def decode_num_splits(batch: int, num_kv_heads: int, max_seq_len: int, row_tiles
 def paged_attention_decode(q, kv_cache, block_table, seq_lens, scale, *, out=None, kv_scales=None,
                            query_start_loc=None, max_q_len: int = 1, window: int = -1, softcap: float = 0.0,
                            sinks=None, lse_out=None, num_splits: int = 0, max_seq_len: int = 0, k_scale=1.0,
-                           v_scale=1.0, causal=True, workspace=None):
-    """Decode attention over the paged cache; ``q [T, Hq, D]``."""
+                           v_scale=1.0, causal=True, workspace=None, alibi_slopes=None):
+    """Decode attention over the paged cache; ``q [T, Hq, D]``.  ``alibi_slopes [Hq]`` (f32) adds
+    ``slope * (kv position - query position)`` to the scores."""
     if _use_cuda(q):
         out = torch.empty(q.shape[0], q.shape[1], kv_cache.shape[-1], dtype=q.dtype, device=q.device) if out is None else out
         B = seq_lens.shape[0]
@@ -385,13 +386,13 @@ def paged_attention_decode(q, kv_cache, block_table, seq_lens, scale, *, out=Non
             ws = _decode_workspace(q.device, num_splits * q.shape[0] * q.shape[1] * (q.shape[2] + 1))
         torch.ops.b200.paged_attention_decode(out, q, kv_cache, kv_scales, block_table, seq_lens, query_start_loc,
                                               scale, window, softcap, sinks, lse_out, ws, num_splits, B, max_q_len,
-                                              k_scale, v_scale, causal)
+                                              k_scale, v_scale, causal, alibi_slopes)
         return out
     B = seq_lens.shape[0]
     qsl = query_start_loc if query_start_loc is not None else torch.arange(B + 1, dtype=torch.int32, device=q.device)
     res = ref.paged_attention(q, kv_cache, block_table, seq_lens, qsl, scale, kv_scales=kv_scales, window=window,
                               softcap=softcap, sinks=sinks, k_scale=k_scale, v_scale=v_scale, causal=causal,
-                              return_lse=lse_out is not None)
+                              return_lse=lse_out is not None, alibi_slopes=alibi_slopes)
     if lse_out is not None:
         res, lse = res
         lse_out.copy_(lse)
@@ -403,7 +404,7 @@ def paged_attention_decode(q, kv_cache, block_table, seq_lens, scale, *, out=Non
 
 def paged_attention_prefill(q, kv_cache, block_table, seq_lens, query_start_loc, scale, *, out=None, kv_scales=None,
                             max_q_len: int = 0, window: int = -1, softcap: float = 0.0, sinks=None, lse_out=None,
-                            k_scale=1.0, v_scale=1.0, causal=True, max_seq_len: int = 0):
+                            k_scale=1.0, v_scale=1.0, causal=True, max_seq_len: int = 0, alibi_slopes=None):
     """Varlen prefill / chunked-prefill attention reading K, V from the paged cache."""
     if _use_cuda(q):
         out = torch.empty(q.shape[0], q.shape[1], kv_cache.shape[-1], dtype=q.dtype, device=q.device) if out is None else out
@@ -411,17 +412,18 @@ def paged_attention_prefill(q, kv_cache, block_table, seq_lens, query_start_loc,
         D = q.shape[-1]
         if kv_cache.dtype == q.dtype and D in (64, 128) and kv_scales is None:
             torch.ops.b200.attention_prefill(out, q, kv_cache, None, block_table, seq_lens, query_start_loc, None,
-                                             scale, window, softcap, sinks, lse_out, B, max_q_len or q.shape[0], causal)
+                                             scale, window, softcap, sinks, lse_out, B, max_q_len or q.shape[0], causal,
+                                             alibi_slopes)
         else:
             # quantised caches / other head sizes: the split-KV kernel handles any query length in 16-row tiles
             paged_attention_decode(q, kv_cache, block_table, seq_lens, scale, out=out, kv_scales=kv_scales,
                                    query_start_loc=query_start_loc, max_q_len=max_q_len or q.shape[0], window=window,
                                    softcap=softcap, sinks=sinks, lse_out=lse_out, num_splits=1, k_scale=k_scale,
-                                   v_scale=v_scale, causal=causal)
+                                   v_scale=v_scale, causal=causal, alibi_slopes=alibi_slopes)
         return out
     res = ref.paged_attention(q, kv_cache, block_table, seq_lens, query_start_loc, scale, kv_scales=kv_scales,
                               window=window, softcap=softcap, sinks=sinks, k_scale=k_scale, v_scale=v_scale,
-                              causal=causal, return_lse=lse_out is not None)
+                              causal=causal, return_lse=lse_out is not None, alibi_slopes=alibi_slopes)
     if lse_out is not None:
         res, lse = res
         lse_out.copy_(lse)

@@ -157,6 +157,9 @@ __global__ void __launch_bounds__(kDecWarps * 32, (D <= 128 ? 2 : 1)) paged_deco
   const int limA = row_limit(rA), limB = row_limit(rB);
   const int loA = (p.window > 0) ? max(0, limA - p.window) : 0;
   const int loB = (p.window > 0) ? max(0, limB - p.window) : 0;
+  // ALiBi: bias = slope[head of the row] * (kv position - query position), in log2 units like the scores
+  const float alA = (p.alibi_slopes && rA < rows_total) ? p.alibi_slopes[hk * g + rA % g] * 1.4426950408889634f : 0.f;
+  const float alB = (p.alibi_slopes && rB < rows_total) ? p.alibi_slopes[hk * g + rB % g] * 1.4426950408889634f : 0.f;
 
   const float sm_scale_log2 = p.scale * 1.4426950408889634f * ((KIND == 3) ? p.k_scale : 1.f);
   float m_run[2] = {-INFINITY, -INFINITY};
@@ -275,6 +278,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, (D <= 128 ? 2 : 1)) paged_deco
           v *= sm_scale_log2;
         }
         const int lim = half ? limB : limA, lo = half ? loB : loA;
+        v += (half ? alB : alA) * (float)(col - (lim - 1));
         if (col >= lim || col < lo) v = -INFINITY;
         s[nt][e] = v;
         mx[half] = fmaxf(mx[half], v);

@@ -263,8 +263,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     for (int i = 0; i < DV; ++i) o_reg[i] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
-    auto fx = [&](float s) -> float {
-      return (p.softcap > 0.f) ? p.softcap * tanhf(s * p.scale / p.softcap) * 1.4426950408889634f : s * sl2;
+    const float alibi2 = (p.alibi_slopes && row_valid) ? p.alibi_slopes[hq] * 1.4426950408889634f : 0.f;
+    auto fx = [&](float s, int col) -> float {
+      const float base = (p.softcap > 0.f) ? p.softcap * tanhf(s * p.scale / p.softcap) * 1.4426950408889634f : s * sl2;
+      return base + alibi2 * (float)(col - pos);     // ALiBi bias (0 without slopes)
     };
     for (int j = 0; j < n_tiles; ++j) {
       const int st = j & 1;
@@ -286,7 +288,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float s = fx(__uint_as_float(v[i]));
+          float s = fx(__uint_as_float(v[i]), t0 + c + i);
           if (need_mask) {
             const int col = t0 + c + i;
             if (col >= lim || col < lo) s = -INFINITY;
@@ -328,7 +330,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         float pv[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float s = fx(__uint_as_float(v[i]));
+          float s = fx(__uint_as_float(v[i]), t0 + c + i);
           if (need_mask) {
             const int col = t0 + c + i;
             if (col >= lim || col < lo) s = -INFINITY;

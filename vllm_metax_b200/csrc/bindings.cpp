@@ -225,7 +225,7 @@ void paged_attention_decode(Tensor& out, const Tensor& q, const Tensor& kv_cache
                             const optional<Tensor>& query_start_loc, double scale, int64_t window, double softcap,
                             const optional<Tensor>& sinks, const optional<Tensor>& lse_out,
                             const optional<Tensor>& workspace, int64_t num_splits, int64_t batch, int64_t max_q_len,
-                            double k_scale, double v_scale, bool causal) {
+                            double k_scale, double v_scale, bool causal, const optional<Tensor>& alibi_slopes) {
   TORCH_CHECK(q.dim() == 3 && q.stride(2) == 1 && q.stride(1) == q.size(2), "q must be [T, Hq, D] with packed heads");
   TORCH_CHECK(kv_cache.dim() == 5 && kv_cache.is_contiguous());
   TORCH_CHECK(block_table.scalar_type() == at::kInt && seq_lens.scalar_type() == at::kInt);
@@ -241,6 +241,7 @@ void paged_attention_decode(Tensor& out, const Tensor& q, const Tensor& kv_cache
   p.seq_lens = seq_lens.data_ptr<int>();
   p.query_start_loc = ptr<int>(query_start_loc);
   p.sinks = ptr<float>(sinks);
+  p.alibi_slopes = ptr<float>(alibi_slopes);
   p.lse_out = ptr<float>(lse_out);
   p.num_q_heads = Hq;
   p.num_kv_heads = kv_cache.size(3);
@@ -274,9 +275,11 @@ void attention_prefill(Tensor& out, const Tensor& q, const Tensor& k_src, const 
                        const optional<Tensor>& block_table, const optional<Tensor>& seq_lens,
                        const Tensor& query_start_loc, const optional<Tensor>& kv_start_loc, double scale,
                        int64_t window, double softcap, const optional<Tensor>& sinks,
-                       const optional<Tensor>& lse_out, int64_t batch, int64_t max_q_len, bool causal) {
+                       const optional<Tensor>& lse_out, int64_t batch, int64_t max_q_len, bool causal,
+                       const optional<Tensor>& alibi_slopes) {
   TORCH_CHECK(q.dim() == 3 && q.stride(2) == 1 && q.stride(1) == q.size(2));
   b200::PrefillParams p{};
+  p.alibi_slopes = ptr<float>(alibi_slopes);
   const int T = q.size(0), Hq = q.size(1), DQK = q.size(2);
   const bool paged = block_table.has_value();
   int Hkv, DV;
@@ -1238,12 +1241,12 @@ TORCH_LIBRARY(b200, m) {
       "paged_attention_decode(Tensor(a!) out, Tensor q, Tensor kv_cache, Tensor? kv_scales, Tensor block_table, "
       "Tensor seq_lens, Tensor? query_start_loc, float scale, int window, float softcap, Tensor? sinks, "
       "Tensor(b!)? lse_out, Tensor(c!)? workspace, int num_splits, int batch, int max_q_len, float k_scale, "
-      "float v_scale, bool causal) -> ()",
+      "float v_scale, bool causal, Tensor? alibi_slopes=None) -> ()",
       &paged_attention_decode);
   m.def(
       "attention_prefill(Tensor(a!) out, Tensor q, Tensor k_src, Tensor? v_src, Tensor? block_table, "
       "Tensor? seq_lens, Tensor query_start_loc, Tensor? kv_start_loc, float scale, int window, float softcap, "
-      "Tensor? sinks, Tensor(b!)? lse_out, int batch, int max_q_len, bool causal) -> ()",
+      "Tensor? sinks, Tensor(b!)? lse_out, int batch, int max_q_len, bool causal, Tensor? alibi_slopes=None) -> ()",
       &attention_prefill);
   m.def("argmax(Tensor(a!) out, Tensor logits) -> ()", &argmax);
   m.def(

@@ -20,6 +20,7 @@ struct DecodeParams {
   const int* seq_lens;       // [B]
   const int* query_start_loc;  // [B+1] or null (one token per sequence)
   const float* sinks;        // [Hq] or null
+  const float* alibi_slopes; // [Hq] or null: score += slope * (kv position - query position)
   float* lse_out;            // [Hq, T] or null (natural-log LSE of the final result)
   int64_t q_stride;
   int num_q_heads, num_kv_heads, block_size, max_blocks, num_splits, total_tokens;
@@ -38,6 +39,7 @@ struct PrefillParams {
   const int* query_start_loc;    // [B+1]
   const int* kv_start_loc;       // [B+1] (contiguous mode) or null
   const float* sinks;            // [Hq] or null
+  const float* alibi_slopes;     // [Hq] or null
   int num_q_heads, num_kv_heads, gp;  // gp: heads packed per tile (divides 128)
   int block_size, max_blocks;
   int64_t num_blocks;

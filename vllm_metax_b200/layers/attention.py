@@ -62,8 +62,9 @@ class PagedGQABackend:
 class Attention(nn.Module):
     def __init__(self, num_heads: int, head_size: int, scale: float, num_kv_heads: int, layer_idx: int,
                  sliding_window: Optional[int] = None, softcap: float = 0.0, sinks: Optional[torch.Tensor] = None,
-                 k_scale: float = 1.0, v_scale: float = 1.0):
+                 k_scale: float = 1.0, v_scale: float = 1.0, alibi_slopes: Optional[torch.Tensor] = None):
         super().__init__()
+        self.alibi_slopes = alibi_slopes           # f32 [num_heads] (Bloom / MPT / Baichuan-13B style position bias)
         self.num_heads, self.head_size, self.scale, self.num_kv_heads = num_heads, head_size, scale, num_kv_heads
         self.layer_idx = layer_idx
         self.window = sliding_window or -1
@@ -95,13 +96,14 @@ class Attention(nn.Module):
             ops.paged_attention_decode(q3[:ndt], kv_cache, md.block_table[:nd], md.seq_lens[:nd], self.scale,
                                        out=out[:ndt], kv_scales=kv_scales, window=self.window, softcap=self.softcap,
                                        sinks=self.sinks, num_splits=md.decode_num_splits, max_seq_len=md.max_seq_len,
-                                       k_scale=self.k_scale, v_scale=self.v_scale, workspace=md.decode_workspace)
+                                       k_scale=self.k_scale, v_scale=self.v_scale, workspace=md.decode_workspace,
+                                       alibi_slopes=self.alibi_slopes)
         if md.num_prefills > 0:
             ops.paged_attention_prefill(q3[ndt:], kv_cache, md.block_table[nd:], md.seq_lens[nd:],
                                         md.prefill_query_start_loc, self.scale, out=out[ndt:], kv_scales=kv_scales,
                                         max_q_len=md.max_prefill_query_len, window=self.window, softcap=self.softcap,
                                         sinks=self.sinks, k_scale=self.k_scale, v_scale=self.v_scale,
-                                        max_seq_len=md.max_seq_len)
+                                        max_seq_len=md.max_seq_len, alibi_slopes=self.alibi_slopes)
         return out.reshape(T, self.num_heads * self.head_size)
 
     def _forward_turboquant(self, q, k, v, positions, rope, md, cache, fmt) -> torch.Tensor:
