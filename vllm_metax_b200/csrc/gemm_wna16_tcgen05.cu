@@ -187,7 +187,20 @@ gemm_wna16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const int n = min(tw * kWqBM + r, p.N - 1);
       const T* Se = S + (size_t)e * ngroups * p.N + n;
       const T* Ze = Z ? Z + (size_t)e * ngroups * p.N + n : nullptr;
+      // scales / zero points of a k-step are fetched one step ahead, so their global-memory latency overlaps the
+      // wait for the stage and the conversion of the previous step instead of sitting in front of the arithmetic
+      T sc_cur[2], zc_cur[2], sc_nxt[2], zc_nxt[2];
+      auto fetch = [&](int kb, T (&sc)[2], T (&zc)[2]) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int g = min((kb * kWqBK + h * 32) / p.group, ngroups - 1);
+          sc[h] = Se[(size_t)g * p.N];
+          zc[h] = Ze ? Ze[(size_t)g * p.N] : from_f<T>(BITS == 4 ? (std::is_same<T, __half>::value ? 1032.f : 136.f) : 128.f);
+        }
+      };
+      if (kb0 < kb1) fetch(kb0, sc_cur, zc_cur);
       for (int kb = kb0; kb < kb1; ++kb) {
+        if (kb + 1 < kb1) fetch(kb + 1, sc_nxt, zc_nxt);
         if (!mbar_wait(&full_bar[stage], phase)) {
           report_status(status, kWaitTimeout, 123, tile, kb);
           ok = false;
@@ -198,10 +211,9 @@ gemm_wna16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const uint4* src = reinterpret_cast<const uint4*>(sq + r * L::kPackedRow);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {   // 32 k values per half
-          const int g = min((kb * kWqBK + h * 32) / p.group, ngroups - 1);
-          const T sc = Se[(size_t)g * p.N];
+          const T sc = sc_cur[h];
           if constexpr (BITS == 4) {
-            const T zc = Ze ? Ze[(size_t)g * p.N] : from_f<T>(std::is_same<T, __half>::value ? 1032.f : 136.f);
+            const T zc = zc_cur[h];
             T2 s2, z2;
             s2.x = sc; s2.y = sc; z2.x = zc; z2.y = zc;
             const uint4 q = src[h];
@@ -219,7 +231,7 @@ gemm_wna16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
               *reinterpret_cast<uint4*>(sa + ((chunk ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
             }
           } else {
-            const float sf = to_f(sc), zf = Ze ? to_f(Ze[(size_t)g * p.N]) : 128.f;
+            const float sf = to_f(sc), zf = to_f(zc_cur[h]);
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
               const uint4 q = src[h * 2 + u];   // 16 bytes = 16 k values = two 16-byte output chunks
@@ -238,6 +250,8 @@ gemm_wna16_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         fence_proxy_async();          // generic-proxy stores -> visible to the tensor core's async proxy
         mbar_arrive(&ready_bar[stage]);
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) { sc_cur[h] = sc_nxt[h]; zc_cur[h] = zc_nxt[h]; }
       }
     }
   } else {
