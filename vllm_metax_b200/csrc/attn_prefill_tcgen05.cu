@@ -47,7 +47,7 @@ struct PfSmem {
   static constexpr int kV = kK + 2 * kKBytes;        // 2 stages
   static constexpr int kP = kV + 2 * kVBytes;
   static constexpr int kBar = kP + kPBytes;
-  static constexpr int kNumBars = 1 + 2 + 2 + 2 + 2 + 2 + 2 + 1 + 1;
+  static constexpr int kNumBars = 1 + 2 + 2 + 2 + 2 + 2 + 2 + 1 + 1 + 3;   // + row-exchange barriers
   static constexpr int kTotal = kBar + kNumBars * 8 + 16;
   static constexpr int kDyn = kTotal + 1024;
 };
@@ -65,7 +65,7 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128_mn(uint32_t smem_addr, 
 }
 
 template <typename T, int DQK, int DV, int BN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const PrefillParams p) {
   using L = PfSmem<DQK, DV, BN>;
@@ -83,6 +83,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* s_empty = bars + 11;  // [2]
   uint64_t* p_full = bars + 13;
   uint64_t* o_full = bars + 14;
+  uint64_t* x_bar = bars + 15;    // [3] the two threads of a row exchange max (per tile, alternating) and sum
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -118,9 +119,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 128);
+      mbar_init(&s_empty[i], 256);
     }
-    mbar_init(p_full, 128);
+    mbar_init(p_full, 256);
+    for (int i = 0; i < 3; ++i) mbar_init(&x_bar[i], 256);
     mbar_init(o_full, 1);
     fence_mbar_init();
     prefetch_tensormap(&tmQ);
@@ -247,8 +249,16 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
     }
   } else {
-    // ------------------------------------------------------------ softmax / output (warps 2..5)
+    // ------------------------------------------------------------ softmax / output (warps 2..9)
+    // Two threads per tile row: warps 2..5 take the first half of a tile's key columns and of the value
+    // dimension, warps 6..9 the second half (a warp reaches the TMEM lanes of quarter warp % 4, any columns).
+    // The row maximum is exchanged through shared memory once per tile; the row sums are added at the end.
+    constexpr int HC = BN / 2, HD = DV / 2;
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int c_lo = half * HC, d_lo = half * HD;
+    __shared__ float s_xmax[2][2][kPfBM];
+    __shared__ float s_xsum[2][kPfBM];
     const int r = quarter * 32 + lane;              // tile row
     const int tok = tok0 + r / p.gp;                // token within the sequence
     const int hq = h0 + r % p.gp;
@@ -258,9 +268,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int lo = (p.window > 0) ? max(0, lim - p.window) : 0;
     const float sl2 = p.scale * 1.4426950408889634f;
     const uint32_t lane_base = ((uint32_t)(quarter * 32)) << 16;
-    float o_reg[DV];
+    float o_reg[HD];
 #pragma unroll
-    for (int i = 0; i < DV; ++i) o_reg[i] = 0.f;
+    for (int i = 0; i < HD; ++i) o_reg[i] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     const float alibi2 = (p.alibi_slopes && row_valid) ? p.alibi_slopes[hq] * 1.4426950408889634f : 0.f;
@@ -282,7 +292,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       // pass 1: row max
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
+      for (int c = c_lo; c < c_lo + HC; c += 32) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(tmem_S[st] + lane_base + c, v);
         tmem_ld_wait();
@@ -296,6 +306,15 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           mx = fmaxf(mx, s);
         }
       }
+      // the other half of the row: buffers alternate per tile, so one barrier per tile is enough
+      s_xmax[j & 1][half][r] = mx;
+      mbar_arrive(&x_bar[j & 1]);
+      if (!mbar_wait(&x_bar[j & 1], (j >> 1) & 1)) {      // bounded like every other wait
+        report_status(p.status, kWaitTimeout, 53, j, half);
+        ok = false;
+        break;
+      }
+      mx = fmaxf(mx, s_xmax[j & 1][half ^ 1][r]);
       const float m_new = fmaxf(m_run, mx);
       const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
       const float corr = exp2f(m_run - m_safe);
@@ -309,21 +328,21 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         tc_fence_after_sync();
 #pragma unroll
-        for (int c = 0; c < DV; c += 32) {
+        for (int c = 0; c < HD; c += 32) {
           uint32_t v[32];
-          tmem_ld_32x32b_x32(tmem_O + lane_base + c, v);
+          tmem_ld_32x32b_x32(tmem_O + lane_base + d_lo + c, v);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o_reg[c + i] += __uint_as_float(v[i]);
         }
       }
 #pragma unroll
-      for (int i = 0; i < DV; ++i) o_reg[i] *= corr;
+      for (int i = 0; i < HD; ++i) o_reg[i] *= corr;
       l_run *= corr;
       // pass 2: P = exp2(S - m) -> shared memory (bf16, K-major, 128B swizzle)
       float rs = 0.f;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
+      for (int c = c_lo; c < c_lo + HC; c += 32) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(tmem_S[st] + lane_base + c, v);
         tmem_ld_wait();
@@ -364,29 +383,35 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       } else {
         tc_fence_after_sync();
 #pragma unroll
-        for (int c = 0; c < DV; c += 32) {
+        for (int c = 0; c < HD; c += 32) {
           uint32_t v[32];
-          tmem_ld_32x32b_x32(tmem_O + lane_base + c, v);
+          tmem_ld_32x32b_x32(tmem_O + lane_base + d_lo + c, v);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o_reg[c + i] += __uint_as_float(v[i]);
         }
       }
     }
+    s_xsum[half][r] = l_run;
+    mbar_arrive(&x_bar[2]);
+    if (ok && !mbar_wait(&x_bar[2], 0)) {
+      report_status(p.status, kWaitTimeout, 54, 0, half);
+      ok = false;
+    }
     if (row_valid && ok) {
-      float l_tot = l_run;
+      float l_tot = l_run + s_xsum[half ^ 1][r];
       const float m_safe = (m_run == -INFINITY) ? 0.f : m_run;
       if (p.sinks) l_tot += exp2f(p.sinks[hq] * 1.4426950408889634f - m_safe);
       const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-      T* dst = reinterpret_cast<T*>(p.out) + ((int64_t)(q_begin + tok) * p.num_q_heads + hq) * DV;
+      T* dst = reinterpret_cast<T*>(p.out) + ((int64_t)(q_begin + tok) * p.num_q_heads + hq) * DV + d_lo;
 #pragma unroll
-      for (int c = 0; c < DV; c += 8) {
+      for (int c = 0; c < HD; c += 8) {
         float f[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) f[i] = o_reg[c + i] * inv;
         *reinterpret_cast<uint4*>(dst + c) = pack8<T>(f);
       }
-      if (p.lse_out)
+      if (p.lse_out && half == 0)
         p.lse_out[(int64_t)hq * p.total_q + q_begin + tok] =
             l_tot > 0.f ? (m_safe * 0.6931471805599453f + logf(l_tot)) : -INFINITY;
     }
@@ -404,7 +429,7 @@ static void launch_prefill(const PrefillParams& p, const void* q, int64_t q_stri
                            const void* v_src, int64_t kv_tok_stride_k, int64_t kv_tok_stride_v, int64_t total_kv,
                            int batch, int max_q_len, cudaStream_t stream) {
   using L = PfSmem<DQK, DV, BN>;
-  static_assert(L::kDyn <= 232448, "shared memory budget exceeded");
+  static_assert(L::kDyn + 3072 <= 232448, "shared memory budget exceeded (dynamic + the static row-exchange arrays)");
   const CUtensorMapDataType dt =
       std::is_same<T, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   // Q: [T, Hq, DQK], box [128/gp tokens, gp heads, 64]
@@ -439,7 +464,7 @@ static void launch_prefill(const PrefillParams& p, const void* q, int64_t q_stri
   }
   const int toks_per_tile = kPfBM / p.gp;
   dim3 grid(ceil_div(max_q_len, toks_per_tile), p.num_q_heads / p.gp, batch);
-  kern<<<grid, 192, L::kDyn, stream>>>(tmQ, tmK, tmV, p);
+  kern<<<grid, 320, L::kDyn, stream>>>(tmQ, tmK, tmV, p);
 }
 
 // Returns 0 on success, -1 when the head sizes are not supported by this kernel.
