@@ -393,8 +393,10 @@ int gemm_wna16_token_tile(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 6
 int gemm_wna16_splits(int M, int N, int K, int bn) {
   const int tiles = ceil_div(N, kWqBM) * ceil_div(M, bn);
   const int num_k = ceil_div(K, kWqBK);
-  int s = 1;
-  while (s < 8 && tiles * s * 2 <= wq_sms() && num_k / (s * 2) >= 8) s *= 2;
+  // as many K ranges as fill one wave of SMs (any count, not only powers of two), each at least 8 k-steps long
+  int s = wq_sms() / (tiles > 0 ? tiles : 1);
+  s = s < 1 ? 1 : (s > 8 ? 8 : s);
+  while (s > 1 && num_k / s < 8) --s;
   return s;
 }
 
