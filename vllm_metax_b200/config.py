@@ -23,6 +23,51 @@ def resolve_dtype(d) -> Optional[torch.dtype]:
     return _DTYPES[str(d)]
 
 
+def _canonical_hf_keys(d: dict) -> dict:
+    """Copy of a HF ``config.json`` dict with the spellings older / non-Llama architectures use mapped onto the
+    Llama-style keys the rest of the parser reads (GPT-2 era ``n_embd`` / ``n_head`` / ``n_layer``, MPT ``d_model``,
+    Falcon / BigCode multi-query flags, ``rope_parameters`` of recent transformers releases)."""
+    d = dict(d)
+
+    def alias(key, *others):
+        if d.get(key) is None:
+            for o in others:
+                if d.get(o) is not None:
+                    d[key] = d[o]
+                    return
+
+    arch = (d.get("architectures") or [""])[0]
+    alias("hidden_size", "n_embd", "d_model")
+    alias("num_attention_heads", "n_head", "n_heads")
+    alias("num_hidden_layers", "n_layer", "n_layers", "num_layers")
+    alias("rms_norm_eps", "layer_norm_eps", "layer_norm_epsilon", "layernorm_epsilon")
+    alias("max_position_embeddings", "n_positions", "max_seq_len", "seq_length")
+    alias("intermediate_size", "ffn_hidden_size", "n_inner")
+    if d.get("intermediate_size") is None and d.get("expansion_ratio") and d.get("hidden_size"):
+        d["intermediate_size"] = int(d["expansion_ratio"] * d["hidden_size"])
+    rp = d.get("rope_parameters")
+    if isinstance(rp, dict):
+        if d.get("rope_theta") is None and rp.get("rope_theta") is not None:
+            d["rope_theta"] = rp["rope_theta"]
+        if d.get("rope_scaling") is None and rp.get("rope_type", "default") not in (None, "default"):
+            d["rope_scaling"] = rp
+        if d.get("partial_rotary_factor") is None and rp.get("partial_rotary_factor") is not None:
+            d["partial_rotary_factor"] = rp["partial_rotary_factor"]
+    alias("rope_theta", "rotary_emb_base")
+    alias("partial_rotary_factor", "rotary_pct")
+    if d.get("num_key_value_heads") is None:
+        if "Falcon" in arch:
+            if d.get("new_decoder_architecture"):
+                d["num_key_value_heads"] = d.get("num_kv_heads") or d.get("num_attention_heads")
+            elif d.get("multi_query", True):
+                d["num_key_value_heads"] = 1
+        elif "GPTBigCode" in arch and d.get("multi_query", True):
+            d["num_key_value_heads"] = 1
+        elif d.get("multi_query_group_num") is not None and d.get("multi_query_attention", True):
+            d["num_key_value_heads"] = d["multi_query_group_num"]
+    return d
+
+
 @dataclass
 class ModelConfig:
     architecture: str = "LlamaForCausalLM"
@@ -84,6 +129,9 @@ class ModelConfig:
     max_loras: int = 4
     max_lora_rank: int = 64
     eos_token_id: Optional[int] = None
+    partial_rotary_factor: float = 1.0         # fraction of each head that is rotated (GPT-NeoX, GLM: < 1)
+    rope_is_neox: bool = True                  # False: GPT-J style (adjacent pairs), e.g. GLM / ChatGLM
+    hf_config: dict = field(default_factory=dict, repr=False)   # raw config.json for architecture-specific keys
 
     def __post_init__(self):
         if self.num_key_value_heads is None:
@@ -109,9 +157,13 @@ class ModelConfig:
 
     @classmethod
     def from_hf_dict(cls, d: dict, **overrides: Any) -> "ModelConfig":
+        raw, d = d, _canonical_hf_keys(d)
         archs = d.get("architectures") or ["LlamaForCausalLM"]
         arch = archs[0]
         kw: dict[str, Any] = dict(
+            hf_config=dict(raw),
+            partial_rotary_factor=float(d.get("partial_rotary_factor", 1.0) or 1.0),
+            rope_is_neox=bool(d.get("rope_is_neox", True)),
             architecture=arch,
             vocab_size=d.get("vocab_size", 32000),
             hidden_size=d["hidden_size"],

@@ -261,10 +261,32 @@ class ModelRunner:
             torch.cuda.nvtx.range_push(f"forward T={T} decodes={md.num_decodes} prefills={md.num_prefills}")
         try:
             with set_forward_context(ctx):
-                return self.model(self.input_ids[:T], self.positions[:T])
+                pp = ps.get_pp_group()
+                if pp.world_size == 1:
+                    return self.model(self.input_ids[:T], self.positions[:T])
+                inter = None if pp.is_first_rank else self._pp_recv(pp, T)
+                out = self.model(self.input_ids[:T], self.positions[:T], inter)
+                if isinstance(out, dict):
+                    self._pp_send(pp, out)
+                return out
         finally:
             if nvtx:
                 torch.cuda.nvtx.range_pop()
+
+    # Pipeline stages exchange one tensor per step: [parts, T, hidden] with parts = hidden states (+ the residual
+    # stream for pre-norm models).  Every stage runs the same scheduler, so shapes need no handshake.
+    def _pp_parts(self) -> int:
+        return 2 if getattr(self.model, "pp_residual", True) else 1
+
+    def _pp_send(self, pp, out: dict) -> None:
+        h, r = out["hidden_states"], out.get("residual")
+        parts = [h] if self._pp_parts() == 1 else [h, r if r is not None else torch.zeros_like(h)]
+        pp.send(torch.stack(parts).contiguous(), pp.rank_in_group + 1)
+
+    def _pp_recv(self, pp, T: int) -> dict:
+        buf = torch.empty(self._pp_parts(), T, self.cfg.model.hidden_size, dtype=self.cfg.model.dtype, device=self.device)
+        pp.recv(buf, pp.rank_in_group - 1)
+        return {"hidden_states": buf[0], "residual": buf[1] if buf.shape[0] > 1 else None}
 
     def _decode_splits(self, batch: int) -> int:
         spec = self.model.kv_cache_spec()
@@ -344,18 +366,24 @@ class ModelRunner:
             h = self._forward(md, T)
             if getattr(self, "keep_hidden", False):
                 self.last_step = (h, md, T)      # draft proposers read the step's hidden states
-            if isinstance(h, dict):  # non-last pipeline stage
-                return {}
             if n == 0:
                 return {}
-            if n == T:
-                hs = h
+            pp = ps.get_pp_group()
+            if isinstance(h, dict):  # non-last pipeline stage: the last stage samples and shares the tokens
+                tokens_dev = pp.broadcast(self.sampled[:n], src=pp.world_size - 1)
             else:
-                self.sample_idx_host[:n] = torch.as_tensor(rows)
-                self.sample_idx[:n].copy_(self.sample_idx_host[:n], non_blocking=True)
-                hs = h.index_select(0, self.sample_idx[:n])
-            logits = self.model.compute_logits(hs)
-            tokens_dev = ops.argmax(logits, self.sampled[:n]) if all_greedy else self._sample(logits, reqs)
+                if n == T:
+                    hs = h
+                else:
+                    self.sample_idx_host[:n] = torch.as_tensor(rows)
+                    self.sample_idx[:n].copy_(self.sample_idx_host[:n], non_blocking=True)
+                    hs = h.index_select(0, self.sample_idx[:n])
+                logits = self.model.compute_logits(hs)
+                tokens_dev = ops.argmax(logits, self.sampled[:n]) if all_greedy else self._sample(logits, reqs)
+                if pp.world_size > 1:
+                    if tokens_dev.data_ptr() != self.sampled.data_ptr():
+                        self.sampled[:n].copy_(tokens_dev[:n])
+                    tokens_dev = pp.broadcast(self.sampled[:n], src=pp.world_size - 1)
         self.sampled_host[:n].copy_(tokens_dev[:n], non_blocking=False)
         self.d2h_bytes += n * 8
         toks = self.sampled_host[:n].tolist()

@@ -26,6 +26,15 @@ _MODELS: dict[str, tuple[str, str]] = {
     "DeepSeekV4MTPModel": ("deepseek_v4", "DeepSeekV4MTP"),
     "Step3p5MTP": ("step3p5_mtp", "Step3p5MTP"),
     "EagleLlamaForCausalLM": ("eagle", "EagleLlamaForCausalLM"),
+    # LayerNorm + plain-MLP decoders (rotary, ALiBi or learned positions)
+    "GPTNeoXForCausalLM": ("gpt", "GPTNeoXForCausalLM"),
+    "FalconForCausalLM": ("gpt", "FalconForCausalLM"),
+    "RWForCausalLM": ("gpt", "FalconForCausalLM"),
+    "BloomForCausalLM": ("gpt", "BloomForCausalLM"),
+    "MPTForCausalLM": ("gpt", "MPTForCausalLM"),
+    "MptForCausalLM": ("gpt", "MPTForCausalLM"),
+    "GPTBigCodeForCausalLM": ("gpt", "GPTBigCodeForCausalLM"),
+    "GPT2LMHeadModel": ("gpt", "GPT2LMHeadModel"),
 }
 
 
