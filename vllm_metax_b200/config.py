@@ -53,6 +53,10 @@ def _canonical_hf_keys(d: dict) -> dict:
             d["rope_scaling"] = rp
         if d.get("partial_rotary_factor") is None and rp.get("partial_rotary_factor") is not None:
             d["partial_rotary_factor"] = rp["partial_rotary_factor"]
+    alias("head_dim", "kv_channels")
+    if "ChatGLM" in arch and d.get("padded_vocab_size"):
+        d["vocab_size"] = d["padded_vocab_size"]
+    alias("vocab_size", "padded_vocab_size")
     alias("rope_theta", "rotary_emb_base")
     alias("partial_rotary_factor", "rotary_pct")
     if d.get("num_key_value_heads") is None:
@@ -86,6 +90,7 @@ class ModelConfig:
     hidden_act: str = "silu"
     attention_bias: bool = False
     mlp_bias: bool = False
+    attention_out_bias: bool = False           # bias on o_proj too (Llama-style ``attention_bias``, InternLM ``bias``)
     qk_norm: bool = False                      # Qwen3: per-head RMSNorm on q and k
     sliding_window: Optional[int] = None
     # ---- MoE -----------------------------------------------------------
@@ -94,6 +99,9 @@ class ModelConfig:
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
     n_shared_experts: int = 0
+    shared_expert_intermediate_size: int = 0   # Qwen2-MoE: one gated shared expert of this width (0: n_shared * moe width)
+    decoder_sparse_step: int = 1               # Qwen MoE: layer i is sparse when (i + 1) % step == 0 ...
+    mlp_only_layers: tuple = ()                # ... and i is not listed here
     first_k_dense_replace: int = 0
     moe_layer_freq: int = 1
     scoring_func: str = "softmax"              # softmax | sigmoid | sqrtsoftplus
@@ -130,6 +138,7 @@ class ModelConfig:
     max_lora_rank: int = 64
     eos_token_id: Optional[int] = None
     partial_rotary_factor: float = 1.0         # fraction of each head that is rotated (GPT-NeoX, GLM: < 1)
+    use_alibi: bool = False                    # ALiBi slopes instead of rotary embeddings (Baichuan 13B)
     rope_is_neox: bool = True                  # False: GPT-J style (adjacent pairs), e.g. GLM / ChatGLM
     hf_config: dict = field(default_factory=dict, repr=False)   # raw config.json for architecture-specific keys
 
@@ -153,13 +162,18 @@ class ModelConfig:
         return self.index_topk > 0
 
     def layer_is_moe(self, i: int) -> bool:
-        return self.is_moe and i >= self.first_k_dense_replace and (i % max(self.moe_layer_freq, 1) == 0)
+        if not self.is_moe or i in self.mlp_only_layers or (i + 1) % max(self.decoder_sparse_step, 1) != 0:
+            return False
+        return i >= self.first_k_dense_replace and (i % max(self.moe_layer_freq, 1) == 0)
 
     @classmethod
     def from_hf_dict(cls, d: dict, **overrides: Any) -> "ModelConfig":
         raw, d = d, _canonical_hf_keys(d)
         archs = d.get("architectures") or ["LlamaForCausalLM"]
         arch = archs[0]
+        # DeepSeek-V3 lineage: sigmoid scores + bias-corrected grouped top-k even when the config (HF-native exports)
+        # does not spell it out
+        v3_routing = any(t in arch for t in ("DeepseekV3", "DeepseekV32", "GlmMoeDsa", "DeepseekV4", "Glm4Moe"))
         kw: dict[str, Any] = dict(
             hf_config=dict(raw),
             partial_rotary_factor=float(d.get("partial_rotary_factor", 1.0) or 1.0),
@@ -178,22 +192,28 @@ class ModelConfig:
             max_position_embeddings=d.get("max_position_embeddings", 8192),
             tie_word_embeddings=d.get("tie_word_embeddings", False),
             hidden_act=d.get("hidden_act", "silu"),
-            attention_bias=d.get("attention_bias", False) or ("Qwen2" in arch),
+            attention_bias=bool(d.get("attention_bias", False) or d.get("bias", False) or d.get("add_qkv_bias", False)
+                                or d.get("qkv_bias", False) or ("Qwen2" in arch) or arch == "QWenLMHeadModel"),
+            attention_out_bias=bool((d.get("attention_bias", False) and "Qwen" not in arch and "Glm" not in arch
+                                     and "GLM" not in arch) or (d.get("bias", False) and "InternLM" in arch)),
             mlp_bias=d.get("mlp_bias", False),
             qk_norm="Qwen3" in arch,
             sliding_window=d.get("sliding_window") if d.get("use_sliding_window", True) else None,
             num_experts=d.get("num_experts", d.get("n_routed_experts", d.get("num_local_experts", 0))) or 0,
             num_experts_per_tok=d.get("num_experts_per_tok", 0) or 0,
-            moe_intermediate_size=d.get("moe_intermediate_size", 0) or 0,
+            moe_intermediate_size=d.get("moe_intermediate_size") or d.get("intermediate_size", 0) or 0,
+            shared_expert_intermediate_size=d.get("shared_expert_intermediate_size", 0) or 0,
+            decoder_sparse_step=d.get("decoder_sparse_step", 1) or 1,
+            mlp_only_layers=tuple(d.get("mlp_only_layers") or ()),
             norm_topk_prob=d.get("norm_topk_prob", True),
-            n_shared_experts=d.get("n_shared_experts", 0) or 0,
+            n_shared_experts=d.get("n_shared_experts", 0) or (1 if d.get("shared_expert_intermediate_size") else 0),
             first_k_dense_replace=d.get("first_k_dense_replace", 0) or 0,
             moe_layer_freq=d.get("moe_layer_freq", 1) or 1,
-            scoring_func=d.get("scoring_func", "softmax"),
+            scoring_func=d.get("scoring_func", "sigmoid" if v3_routing else "softmax"),
             n_group=d.get("n_group", 1) or 1,
             topk_group=d.get("topk_group", 1) or 1,
             routed_scaling_factor=d.get("routed_scaling_factor", 1.0) or 1.0,
-            topk_method=d.get("topk_method", "greedy"),
+            topk_method=d.get("topk_method", "noaux_tc" if v3_routing else "greedy"),
             q_lora_rank=d.get("q_lora_rank"),
             kv_lora_rank=d.get("kv_lora_rank", 0) or 0,
             qk_nope_head_dim=d.get("qk_nope_head_dim", 0) or 0,

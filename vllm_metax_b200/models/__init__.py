@@ -26,6 +26,20 @@ _MODELS: dict[str, tuple[str, str]] = {
     "DeepSeekV4MTPModel": ("deepseek_v4", "DeepSeekV4MTP"),
     "Step3p5MTP": ("step3p5_mtp", "Step3p5MTP"),
     "EagleLlamaForCausalLM": ("eagle", "EagleLlamaForCausalLM"),
+    # the Llama graph under other names / checkpoint dialects
+    "AquilaForCausalLM": ("llama_family", "AquilaForCausalLM"),
+    "AquilaModel": ("llama_family", "AquilaForCausalLM"),
+    "InternLMForCausalLM": ("llama_family", "InternLMForCausalLM"),
+    "InternLM2ForCausalLM": ("llama_family", "InternLM2ForCausalLM"),
+    "InternLM3ForCausalLM": ("llama_family", "InternLM3ForCausalLM"),
+    "Ernie4_5ForCausalLM": ("llama_family", "Ernie4_5ForCausalLM"),
+    "BaichuanForCausalLM": ("llama_family", "BaichuanForCausalLM"),
+    "BaiChuanForCausalLM": ("llama_family", "BaiChuanForCausalLM"),
+    "QWenLMHeadModel": ("llama_family", "QWenLMHeadModel"),
+    "GlmForCausalLM": ("llama_family", "GlmForCausalLM"),
+    "Glm4ForCausalLM": ("llama_family", "Glm4ForCausalLM"),
+    "ChatGLMModel": ("llama_family", "ChatGLMModel"),
+    "ChatGLMForConditionalGeneration": ("llama_family", "ChatGLMModel"),
     # LayerNorm + plain-MLP decoders (rotary, ALiBi or learned positions)
     "GPTNeoXForCausalLM": ("gpt", "GPTNeoXForCausalLM"),
     "FalconForCausalLM": ("gpt", "FalconForCausalLM"),

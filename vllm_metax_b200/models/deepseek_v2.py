@@ -46,7 +46,7 @@ class DeepseekV2MoE(nn.Module):
         noaux = cfg.topk_method == "noaux_tc"
         self.experts = FusedMoE(cfg.num_experts, cfg.num_experts_per_tok, cfg.hidden_size, cfg.moe_intermediate_size,
                                 cfg.dtype, renormalize=cfg.norm_topk_prob, scoring_func=cfg.scoring_func,
-                                use_grouped_topk=cfg.n_group > 1 or noaux, num_expert_group=cfg.n_group,
+                                use_grouped_topk=(cfg.n_group > 1 and cfg.topk_method != "greedy") or noaux, num_expert_group=cfg.n_group,
                                 topk_group=cfg.topk_group, routed_scaling_factor=cfg.routed_scaling_factor,
                                 e_score_correction_bias=noaux, reduce_results=False,
                                 quant_method=get_moe_method(cfg, f"{prefix}.experts"), prefix=f"{prefix}.experts")
@@ -327,7 +327,7 @@ class DeepseekV2ForCausalLM(nn.Module):
                 continue
             mod = modules[target.rsplit(".", 1)[0]]
             loader = getattr(mod, "weight_loader", None)
-            if loader is not None:
+            if loader is not None and not target.endswith("e_score_correction_bias"):
                 loader(p, w, shard)
             else:
                 p.data.copy_(w.reshape(p.shape))

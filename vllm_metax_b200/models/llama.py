@@ -15,6 +15,7 @@ the usual q/k/v and gate/up stacking.
 """
 from __future__ import annotations
 
+import re
 from typing import Iterable, Optional
 
 import torch
@@ -64,16 +65,24 @@ class LlamaAttention(nn.Module):
                                           cfg.attention_bias, cfg.dtype, qm("qkv_proj"), prefix=f"{prefix}.qkv_proj")
         self.num_heads, self.num_kv_heads = self.qkv_proj.num_heads, self.qkv_proj.num_kv_heads
         self.q_size, self.kv_size = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
-        self.o_proj = RowParallelLinear(self.total_heads * self.head_dim, cfg.hidden_size, False, cfg.dtype,
-                                        qm("o_proj"), prefix=f"{prefix}.o_proj")
-        self.rope = get_rope(self.head_dim, self.head_dim, cfg.max_position_embeddings, cfg.rope_theta, True,
-                             cfg.rope_scaling)
+        self.o_proj = RowParallelLinear(self.total_heads * self.head_dim, cfg.hidden_size, cfg.attention_out_bias,
+                                        cfg.dtype, qm("o_proj"), prefix=f"{prefix}.o_proj")
+        self.rope = get_rope(self.head_dim, int(self.head_dim * cfg.partial_rotary_factor), cfg.max_position_embeddings,
+                             cfg.rope_theta, cfg.rope_is_neox, cfg.rope_scaling)
         self.qk_norm = cfg.qk_norm
         if cfg.qk_norm:
             self.q_norm = RMSNorm(self.head_dim, cfg.rms_norm_eps, cfg.dtype)
             self.k_norm = RMSNorm(self.head_dim, cfg.rms_norm_eps, cfg.dtype)
+        slopes = None
+        if cfg.use_alibi:                              # Baichuan-13B style: linear position bias instead of rotary
+            from .gpt import alibi_slopes
+
+            r = ps.tp_rank()
+            slopes = alibi_slopes(self.total_heads)[r * self.num_heads: (r + 1) * self.num_heads].contiguous()
+            slopes = slopes.to(torch.empty(0).device)
+            self.rope = None
         self.attn = Attention(self.num_heads, self.head_dim, self.head_dim ** -0.5, self.num_kv_heads, layer_idx,
-                              sliding_window=cfg.sliding_window)
+                              sliding_window=cfg.sliding_window, alibi_slopes=slopes)
 
     def attention(self, positions, h):
         """Everything up to (not including) o_proj: ``[T, local_heads * head_dim]``."""
@@ -116,6 +125,8 @@ class LlamaModel(nn.Module):
     def __init__(self, cfg: ModelConfig, prefix: str = "model"):
         super().__init__()
         self.cfg = cfg
+        if cfg.attention_out_bias or cfg.mlp_bias:     # the fused GEMM + reduce + norm kernel has no bias operand
+            self.supports_fused_tp = False
         pp = ps.get_pp_group()
         n = cfg.num_hidden_layers
         per = (n + pp.world_size - 1) // pp.world_size
@@ -171,6 +182,24 @@ class LlamaForCausalLM(nn.Module):
     model_cls = LlamaModel
     stacked_params = [("qkv_proj", "q_proj", "q"), ("qkv_proj", "k_proj", "k"), ("qkv_proj", "v_proj", "v"),
                       ("gate_up_proj", "gate_proj", 0), ("gate_up_proj", "up_proj", 1)]
+    # Checkpoint dialects of the same graph: (regex, replacement) pairs applied to every tensor name, and the row order
+    # of a qkv tensor that is already fused on disk ("concat": q | k | v; "grouped": per kv head its q heads, k, v).
+    renames: list = []
+    fused_qkv_layout = "concat"
+
+    def _fused_qkv_rows(self, w: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
+        H, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        if self.fused_qkv_layout != "grouped" or w.shape[0] != (H + 2 * Hkv) * D:
+            return w
+        g, tail = H // Hkv, w.shape[1:]
+        x = w.reshape(Hkv, g + 2, D, *tail)
+        return torch.cat([x[:, :g].reshape(H * D, *tail), x[:, g].reshape(Hkv * D, *tail),
+                          x[:, g + 1].reshape(Hkv * D, *tail)], 0)
+
+    def transform_weight(self, name: str, w: torch.Tensor) -> torch.Tensor:
+        """Hook for dialects that store a tensor differently (called with the renamed name)."""
+        return w
 
     def __init__(self, cfg: ModelConfig):
         super().__init__()
@@ -205,10 +234,15 @@ class LlamaForCausalLM(nn.Module):
         modules = dict(self.named_modules())
         loaded: set[str] = set()
         for name, w in weights:
-            if "rotary_emb.inv_freq" in name:
+            if "rotary_emb.inv_freq" in name or "rotary_pos_emb.inv_freq" in name:
                 continue
+            for pat, rep in self.renames:
+                name = re.sub(pat, rep, name)
             if name.startswith("lm_head.") and self.cfg.tie_word_embeddings:
                 continue
+            w = self.transform_weight(name, w)
+            if ".qkv_proj." in name:
+                w = self._fused_qkv_rows(w)
             target, shard = name, None
             for fused, part, sid in self.stacked_params:
                 if f".{part}." in name:

@@ -30,13 +30,24 @@ class SparseMoeBlock(nn.Module):
                                 cfg.dtype, renormalize=cfg.norm_topk_prob, scoring_func="softmax",
                                 reduce_results=False, quant_method=get_moe_method(cfg, f"{prefix}.experts"),
                                 prefix=f"{prefix}.experts")
-        self.shared_expert = None
+        self.shared_expert = self.shared_expert_gate = None
         if cfg.n_shared_experts:
-            self.shared_expert = LlamaMLP(cfg, cfg.moe_intermediate_size * cfg.n_shared_experts,
-                                          f"{prefix}.shared_expert", reduce_results=False)
+            width = cfg.shared_expert_intermediate_size or cfg.moe_intermediate_size * cfg.n_shared_experts
+            self.shared_expert = LlamaMLP(cfg, width, f"{prefix}.shared_expert", reduce_results=False)
+            if cfg.shared_expert_intermediate_size:      # Qwen2-MoE: sigmoid(x . w) scales the shared expert per token
+                self.shared_expert_gate = ReplicatedLinear(cfg.hidden_size, 1, False, cfg.dtype,
+                                                           prefix=f"{prefix}.shared_expert_gate")
+
+    def _shared(self, x):
+        if self.shared_expert is None:
+            return None
+        y = self.shared_expert(x)
+        if self.shared_expert_gate is not None:
+            y = (torch.sigmoid(torch.nn.functional.linear(x, self.shared_expert_gate.weight).float()) * y.float()).to(y.dtype)
+        return y
 
     def forward(self, x):
-        shared = self.shared_expert(x) if self.shared_expert is not None else None
+        shared = self._shared(x)
         y = self.experts(x, self.gate(x), shared)
         from ..parallel import state as ps
 
@@ -46,8 +57,7 @@ class SparseMoeBlock(nn.Module):
 
     def partial(self, x):
         """Un-reduced output (for the fused reduce + norm path)."""
-        shared = self.shared_expert(x) if self.shared_expert is not None else None
-        return self.experts(x, self.gate(x), shared)
+        return self.experts(x, self.gate(x), self._shared(x))
 
 
 class MoeDecoderLayer(nn.Module):
