@@ -102,3 +102,84 @@ def test_encoder_attention_gpu(D):
     q, k, v = (torch.randn(T, H, D, generator=g).to(torch.bfloat16) for _ in range(3))
     out = MMEncoderAttention(H, D)(q.cuda(), k.cuda(), v.cuda(), cu.cuda(), max(lens))
     torch.testing.assert_close(out.float().cpu(), _vit_ref(q, k, v, cu, D ** -0.5), rtol=3e-2, atol=3e-2)
+
+
+# ------------------------------------------------------------------------------------------ short causal convolution
+def _conv_case(dtype, seed=0, C=384, K=4, lens=(5, 1, 70, 2)):
+    g_ = torch.Generator().manual_seed(seed)
+    T = sum(lens)
+    x = torch.randn(T, C + 64, generator=g_).to(dtype)[:, :C]            # row pitch larger than C
+    w = (torch.randn(C, K, generator=g_) * 0.5).to(dtype)
+    bias = (torch.randn(C, generator=g_) * 0.1).to(dtype)
+    qsl = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    state = torch.randn(6, K - 1, C, generator=g_).to(dtype)
+    idx = torch.tensor([4, 1, 0, 5], dtype=torch.int32)
+    has = torch.tensor([1, 1, 0, 1], dtype=torch.int32)
+    return x, w, bias, qsl, state, idx, has
+
+
+def test_causal_conv1d_reference_is_a_streaming_convolution():
+    """Feeding a sequence in pieces through the carry gives the same outputs as feeding it at once."""
+    from vllm_metax_b200.ops.gdn import causal_conv1d
+
+    x, w, bias, *_ = _conv_case(torch.float32, lens=(40,))
+    one = torch.tensor([0], dtype=torch.int32)
+    whole = causal_conv1d(x, w, bias, torch.zeros(1, 3, x.shape[1]), torch.tensor([0, 40], dtype=torch.int32), one,
+                          torch.tensor([0], dtype=torch.int32))
+    st = torch.zeros(1, 3, x.shape[1])
+    parts, pos = [], 0
+    for n in (1, 2, 17, 1, 19):
+        parts.append(causal_conv1d(x[pos:pos + n], w, bias, st, torch.tensor([0, n], dtype=torch.int32), one,
+                                   torch.tensor([1 if pos else 0], dtype=torch.int32)))
+        pos += n
+    torch.testing.assert_close(torch.cat(parts), whole, atol=1e-5, rtol=1e-5)
+    # and against torch's own depthwise convolution
+    ref = torch.nn.functional.conv1d(x.t()[None], w[:, None], bias, padding=3, groups=x.shape[1])[0, :, :40].t()
+    torch.testing.assert_close(whole, torch.nn.functional.silu(ref), atol=1e-5, rtol=1e-5)
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("K", [2, 4])
+def test_causal_conv1d_kernel_matches_reference(dtype, K):
+    from vllm_metax_b200.ops.gdn import causal_conv1d, causal_conv1d_ref
+
+    x, w, bias, qsl, state, idx, has = _conv_case(dtype, K=K)
+    st_ref = state.clone()
+    want = causal_conv1d_ref(x, w, bias, st_ref, qsl, idx, has)
+    st = state.cuda()
+    got = causal_conv1d(x.cuda(), w.cuda(), bias.cuda(), st, qsl.cuda(), idx.cuda(), has.cuda())
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    torch.testing.assert_close(got.float().cpu(), want.float(), atol=tol, rtol=tol)
+    torch.testing.assert_close(st.float().cpu(), st_ref.float(), atol=0, rtol=0)          # carries are copies of inputs
+    # no carry: every sequence starts from zeros and nothing is written back
+    got2 = causal_conv1d(x.cuda(), w.cuda(), None, None, qsl.cuda(), None, None, silu=False)
+    want2 = causal_conv1d_ref(x, w, None, None, qsl, None, None, silu=False)
+    torch.testing.assert_close(got2.float().cpu(), want2.float(), atol=tol, rtol=tol)
+
+
+@gpu
+def test_qwen3_next_engine_on_gpu_graphs_match_eager():
+    """Hybrid model end to end on the GPU kernels (delta-rule head size 128, attention head size 128): decode steps
+    replayed from CUDA graphs must give the tokens of the eager run, with requests spread over several state slots."""
+    from vllm_metax_b200 import LLM, SamplingParams
+    from vllm_metax_b200.config import ModelConfig
+
+    hf = dict(architectures=["Qwen3NextForCausalLM"], vocab_size=1024, hidden_size=256, num_hidden_layers=4,
+              num_attention_heads=4, num_key_value_heads=2, head_dim=128, max_position_embeddings=512,
+              intermediate_size=512, moe_intermediate_size=128, shared_expert_intermediate_size=128, num_experts=8,
+              num_experts_per_tok=2, linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=128,
+              linear_value_head_dim=128, linear_conv_kernel_dim=4, norm_topk_prob=True, torch_dtype="bfloat16")
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (37, 5, 130, 64, 9)]
+    sp = SamplingParams(max_tokens=12, temperature=0.0, ignore_eos=True)
+    outs = []
+    for eager in (True, False):
+        llm = LLM(ModelConfig.from_hf_dict(hf, seed=3), max_model_len=256, max_num_seqs=4, max_num_batched_tokens=128,
+                  num_gpu_blocks=64, enforce_eager=eager, load_format="dummy")
+        outs.append([list(o.outputs[0].token_ids) for o in llm.generate(prompts, sp)])
+        assert not llm.engine.runner.state_slots
+        del llm
+        torch.cuda.empty_cache()
+    assert outs[0] == outs[1]
+    assert all(len(t) == 12 for t in outs[0])

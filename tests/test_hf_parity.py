@@ -35,6 +35,19 @@ CASES = {
                     dict(BASE, intermediate_size=256, moe_intermediate_size=64, n_routed_experts=8, num_experts_per_tok=2,
                          n_shared_experts=1, n_group=2, topk_group=1, first_k_dense_replace=1, q_lora_rank=48,
                          kv_lora_rank=512, qk_nope_head_dim=32, qk_rope_head_dim=64, v_head_dim=32, num_key_value_heads=4)),
+    "glm4_moe": ("Glm4MoeConfig", "Glm4MoeForCausalLM",
+                 dict(BASE, intermediate_size=256, moe_intermediate_size=64, n_routed_experts=8, num_experts_per_tok=2,
+                      n_shared_experts=1, n_group=2, topk_group=1, first_k_dense_replace=1, num_key_value_heads=2,
+                      head_dim=32, use_qk_norm=True)),
+    "ernie4_5_moe": ("Ernie4_5_MoeConfig", "Ernie4_5_MoeForCausalLM",
+                     dict(BASE, intermediate_size=256, moe_intermediate_size=64, moe_num_experts=8, moe_k=2,
+                          moe_num_shared_experts=1, moe_layer_start_index=1, num_key_value_heads=2)),
+    "qwen3_next_hybrid": ("Qwen3NextConfig", "Qwen3NextForCausalLM",
+                          dict(vocab_size=512, hidden_size=128, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+                               head_dim=32, max_position_embeddings=256, intermediate_size=256, moe_intermediate_size=64,
+                               shared_expert_intermediate_size=64, num_experts=8, num_experts_per_tok=2,
+                               linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=16,
+                               linear_value_head_dim=16, linear_conv_kernel_dim=4, norm_topk_prob=True)),
     "neox": ("GPTNeoXConfig", "GPTNeoXForCausalLM", dict(BASE, intermediate_size=256)),
     "neox_sequential": ("GPTNeoXConfig", "GPTNeoXForCausalLM",
                         dict(BASE, intermediate_size=256, use_parallel_residual=False, rotary_pct=0.5)),
@@ -65,11 +78,14 @@ def test_matches_hugging_face(case, tmp_path):
         for p in hf.parameters():          # default inits leave norms at 1 / biases at 0, and logits nearly flat
             if p.dim() == 1:
                 p.add_(0.1 * torch.randn_like(p))
-            elif "moe" not in case and "mixtral" not in case and "deepseek" not in case:
+            elif "moe" not in case and "mixtral" not in case and "deepseek" not in case and "qwen3_next" not in case:
                 p.mul_(3.0)                # (routers stay at their init scale: near-ties flip experts in fp32)
         for n, b in hf.named_buffers():
-            if n.endswith("e_score_correction_bias"):     # DeepSeek-V3 routing bias: a buffer, zero at init
+            if n.endswith("e_score_correction_bias"):     # DeepSeek-V3 / GLM-4.5 routing bias: a buffer, zero at init
                 b.add_(0.05 * torch.randn_like(b))
+        for n, p in hf.named_parameters():
+            if n.endswith("e_score_correction_bias"):     # Ernie keeps it as a [1, E] parameter
+                p.copy_(0.02 * torch.randn_like(p))
     hf.save_pretrained(str(tmp_path))
     llm = LLM(str(tmp_path), dtype="float32", device="cpu", max_model_len=128, num_gpu_blocks=16, block_size=16)
     got_h = llm.embed(PROMPTS, pooling="mean", normalize=False)
@@ -243,3 +259,30 @@ def test_baichuan_13b_alibi(tmp_path):
         x = x + (torch.nn.functional.silu(h @ t["mlp.gate_proj.weight"].T) * (h @ t["mlp.up_proj.weight"].T)) @ t["mlp.down_proj.weight"].T
     want = rms(x, sd["model.norm.weight"]).mean(0)
     torch.testing.assert_close(got, want, atol=2e-4, rtol=2e-4)
+
+
+def test_qwen3_next_state_carry_across_chunks_and_batches(tmp_path):
+    """The recurrent state and the convolution carry must survive chunked prefill (8 tokens per step here), batched
+    decode with requests joining at different times, and slot reuse after a request finishes."""
+    from vllm_metax_b200 import LLM, SamplingParams
+
+    cfg_cls, model_cls, kw = CASES["qwen3_next_hybrid"]
+    torch.manual_seed(2)
+    hf = getattr(tf, model_cls)(getattr(tf, cfg_cls)(**kw)).eval().float()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.dim() == 1:
+                p.add_(0.1 * torch.randn_like(p))
+    hf.save_pretrained(str(tmp_path))
+    llm = LLM(str(tmp_path), dtype="float32", device="cpu", max_model_len=128, num_gpu_blocks=32, block_size=16,
+              max_num_batched_tokens=8, max_num_seqs=2, enable_prefix_caching=True)      # prefix caching is refused
+    assert not llm.engine.kv.enable_prefix_caching
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (19, 5, 27, 11)]  # 4 requests, 2 slots
+    outs = llm.generate(prompts, SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True))
+    for ids, o in zip(prompts, outs):
+        with torch.no_grad():
+            want = hf.generate(torch.tensor([ids]), max_new_tokens=6, do_sample=False, eos_token_id=None,
+                               pad_token_id=0)[0, len(ids):].tolist()
+        assert list(o.outputs[0].token_ids) == want
+    assert not llm.engine.runner.state_slots and len(llm.engine.runner.free_state_slots) == 2

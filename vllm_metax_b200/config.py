@@ -54,6 +54,11 @@ def _canonical_hf_keys(d: dict) -> dict:
         if d.get("partial_rotary_factor") is None and rp.get("partial_rotary_factor") is not None:
             d["partial_rotary_factor"] = rp["partial_rotary_factor"]
     alias("head_dim", "kv_channels")
+    alias("num_experts", "moe_num_experts")                    # Ernie-4.5-MoE spellings
+    alias("num_experts_per_tok", "moe_k")
+    alias("n_shared_experts", "moe_num_shared_experts")
+    alias("first_k_dense_replace", "moe_layer_start_index")
+    alias("moe_layer_freq", "moe_layer_interval")
     if "ChatGLM" in arch and d.get("padded_vocab_size"):
         d["vocab_size"] = d["padded_vocab_size"]
     alias("vocab_size", "padded_vocab_size")
@@ -197,7 +202,7 @@ class ModelConfig:
             attention_out_bias=bool((d.get("attention_bias", False) and "Qwen" not in arch and "Glm" not in arch
                                      and "GLM" not in arch) or (d.get("bias", False) and "InternLM" in arch)),
             mlp_bias=d.get("mlp_bias", False),
-            qk_norm="Qwen3" in arch,
+            qk_norm=("Qwen3" in arch) or bool(d.get("use_qk_norm", False)),
             sliding_window=d.get("sliding_window") if d.get("use_sliding_window", True) else None,
             num_experts=d.get("num_experts", d.get("n_routed_experts", d.get("num_local_experts", 0))) or 0,
             num_experts_per_tok=d.get("num_experts_per_tok", 0) or 0,

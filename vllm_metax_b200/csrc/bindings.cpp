@@ -914,6 +914,34 @@ void gdn_recurrent(Tensor& out, Tensor& state, const Tensor& q, const Tensor& k,
   TORCH_CHECK(rc == 0, "gdn_recurrent: head sizes must be 128 and value heads a multiple of q/k heads");
 }
 
+// x [T, C] (row pitch free), w [C, K], state [slots, K-1, C] (in / out), all of one dtype (bf16 / fp16 / fp32)
+void causal_conv1d(Tensor& out, const Tensor& x, const Tensor& w, const optional<Tensor>& bias,
+                   const optional<Tensor>& state, const Tensor& query_start_loc, const optional<Tensor>& state_idx,
+                   const optional<Tensor>& has_initial, bool silu) {
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && out.is_contiguous() && out.sizes() == x.sizes() &&
+              out.scalar_type() == x.scalar_type());
+  const int64_t T = x.size(0), C = x.size(1), K = w.size(1);
+  TORCH_CHECK(w.dim() == 2 && w.size(0) == C && w.is_contiguous() && w.scalar_type() == x.scalar_type());
+  if (bias.has_value()) TORCH_CHECK(bias->is_contiguous() && bias->numel() == C && bias->scalar_type() == x.scalar_type());
+  TORCH_CHECK(query_start_loc.scalar_type() == at::kInt && query_start_loc.is_contiguous());
+  const int64_t B = query_start_loc.numel() - 1;
+  if (state.has_value()) {
+    TORCH_CHECK(state_idx.has_value(), "a carry needs state indices");
+    TORCH_CHECK(state->is_contiguous() && state->dim() == 3 && state->size(1) == K - 1 && state->size(2) == C &&
+                state->scalar_type() == x.scalar_type());
+  }
+  if (state_idx.has_value()) TORCH_CHECK(state_idx->scalar_type() == at::kInt && state_idx->numel() >= B);
+  if (has_initial.has_value()) TORCH_CHECK(has_initial->scalar_type() == at::kInt && has_initial->numel() >= B);
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int rc = b200::causal_conv1d(out.data_ptr(), x.data_ptr(), x.stride(0), w.data_ptr(),
+                                     bias.has_value() ? bias->data_ptr() : nullptr,
+                                     state.has_value() ? state->data_ptr() : nullptr, query_start_loc.data_ptr<int>(),
+                                     state_idx.has_value() ? state_idx->data_ptr<int>() : nullptr,
+                                     has_initial.has_value() ? has_initial->data_ptr<int>() : nullptr, (int)B, (int)T,
+                                     (int)C, (int)K, silu ? 1 : 0, dtype_code(x), cur_stream());
+  TORCH_CHECK(rc == 0, "causal_conv1d: kernel width must be 2..8");
+}
+
 // TurboQuant cache: uint8 [blocks, block_size, kv_heads, slot_bytes]; k, v [T, kv_heads * 128] (any row pitch)
 int64_t tq_slot_bytes(int64_t kbits, int64_t vbits) { return b200::tq_slot_bytes((int)kbits, (int)vbits); }
 
@@ -1162,6 +1190,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("moe_a2a_combine(Tensor(a!) out, Tensor y, Tensor topk_ids, Tensor? shared_out, Tensor ptrs, int ep, int rank, int experts_per_rank, int cap, Tensor(b!) local_sync, int wait_cycles) -> ()", &moe_a2a_combine);
   m.def("v4_qnorm_rope_kv_insert(Tensor(a!) q_out, Tensor(b!) cache, Tensor q, Tensor kv, Tensor slot_mapping, Tensor positions, Tensor cos_sin, float eps, int block_size) -> ()", &v4_qnorm_rope_kv_insert);
   m.def("v4_gather_dequant(Tensor(a!) dst, Tensor cache, Tensor slots, int block_size) -> ()", &v4_gather_dequant);
+  m.def("causal_conv1d(Tensor(a!) out, Tensor x, Tensor w, Tensor? bias, Tensor(b!)? state, Tensor query_start_loc, Tensor? state_idx, Tensor? has_initial, bool silu) -> ()", &causal_conv1d);
   m.def("gdn_recurrent(Tensor(a!) out, Tensor(b!) state, Tensor q, Tensor k, Tensor v, Tensor g, Tensor beta, Tensor query_start_loc, Tensor? state_idx, Tensor? has_initial, float scale, bool l2norm) -> ()", &gdn_recurrent);
   m.def("tq_slot_bytes(int kbits, int vbits) -> int", &tq_slot_bytes);
   m.def("tq_store(Tensor(a!) cache, Tensor k, Tensor v, Tensor slot_mapping, int kbits, int vbits, bool nc) -> ()", &tq_store);

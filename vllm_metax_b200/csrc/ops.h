@@ -250,6 +250,10 @@ int gdn_recurrent(void* out, float* state, const void* q, const void* k, const v
                   const int* query_start_loc, const int* state_idx, int batch, int hq, int hv, int dk, int dv,
                   int64_t q_stride, int64_t k_stride, int64_t v_stride, float scale, int l2norm,
                   const int* has_initial, int dtype, cudaStream_t stream);
+// ---- causal_conv1d.cu (depthwise causal convolution over ragged batches with a per-sequence carry)
+int causal_conv1d(void* out, const void* x, int64_t x_stride, const void* w, const void* bias, void* state,
+                  const int* query_start_loc, const int* state_idx, const int* has_init, int batch, int tokens,
+                  int channels, int K, int silu, int dtype, cudaStream_t stream);
 // ---- tq_cache.cu (TurboQuant KV cache, head_dim 128)
 int tq_slot_bytes(int kbits, int vbits);
 int tq_store(void* cache, const void* k, const void* v, int64_t k_stride, int64_t v_stride, const int64_t* slot_mapping,

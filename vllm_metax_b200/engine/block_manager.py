@@ -157,6 +157,8 @@ class KVCacheManager:
     def free(self, req: Request) -> None:
         self.pool.release(req.block_ids)
         req.block_ids = []
+        for hook in getattr(self, "on_free", ()):     # e.g. the runner's recurrent-state slots
+            hook(req)
 
     @property
     def num_free_blocks(self) -> int:

@@ -33,7 +33,9 @@ class LLMEngine:
         self.runner = ModelRunner(cfg)
         nb = self.runner.determine_num_blocks()
         self.runner.init_kv_cache(nb)
-        self.kv = KVCacheManager(nb, cfg.cache.block_size, cfg.cache.enable_prefix_caching)
+        prefix_ok = getattr(self.runner.model, "supports_prefix_caching", True)
+        self.kv = KVCacheManager(nb, cfg.cache.block_size, cfg.cache.enable_prefix_caching and prefix_ok)
+        self.kv.on_free = [self.runner.release_request]
         self.scheduler = Scheduler(cfg.scheduler, self.kv)
         self.runner.capture_graphs()
         self._ids = itertools.count()

@@ -68,6 +68,7 @@ class ModelRunner:
         self.kv_caches: list = []
         self.num_blocks = 0
         self._alloc_inputs()
+        self._alloc_state_slots()
         self._enable_fused_tp()
         self.graphs: dict[int, tuple] = {}
         self.use_graphs = self.is_cuda and not cfg.enforce_eager and envs.B200_CUDA_GRAPHS
@@ -174,6 +175,47 @@ class ModelRunner:
             self.kv_caches = self.model.allocate_kv_cache(num_blocks, self.block_size, self.cfg.cache.kv_cache_dtype,
                                                           self.device)
 
+    # ------------------------------------------------------------------ per-request recurrent state (hybrid models)
+    def _alloc_state_slots(self) -> None:
+        """Models with recurrent layers (gated delta rule, short convolutions) keep one state slot per running request
+        next to the paged KV cache.  Slot ``max_seqs`` is scratch: CUDA-graph padding rows read and write it."""
+        self.state_slots: Optional[dict] = None
+        if not hasattr(self.model, "allocate_state"):
+            return
+        B = self.max_seqs
+        self.state_bytes = self.model.allocate_state(B + 1, self.device)
+        self.state_slots = {}
+        self.free_state_slots = list(range(B - 1, -1, -1))
+        pin = self.is_cuda
+        self.state_host = torch.zeros(2 * B, dtype=torch.int32, pin_memory=pin)
+        self.state_dev = torch.zeros(2 * B, dtype=torch.int32, device=self.device)
+        self.state_dev[:B].fill_(B)
+
+    def release_request(self, req) -> None:
+        """Called when a request gives its KV blocks back (finished, aborted or preempted for re-computation)."""
+        if self.state_slots is not None:
+            slot = self.state_slots.pop(req.request_id, None)
+            if slot is not None:
+                self.free_state_slots.append(slot)
+
+    def _state_metadata(self, so: SchedulerOutput, md: AttentionMetadata, B_eff: int) -> None:
+        B = self.max_seqs
+        h = self.state_host.numpy()
+        for i, s in enumerate(so.scheduled):
+            rid = s.request.request_id
+            slot = self.state_slots.get(rid)
+            if slot is None:
+                slot = self.state_slots[rid] = self.free_state_slots.pop()
+            h[i] = slot
+            h[B + i] = 1 if s.start_pos > 0 else 0
+        n = len(so.scheduled)
+        h[n:B_eff] = B
+        h[B + n: B + B_eff] = 0
+        self.state_dev[:B_eff].copy_(self.state_host[:B_eff], non_blocking=True)
+        self.state_dev[B: B + B_eff].copy_(self.state_host[B: B + B_eff], non_blocking=True)
+        md.extra["state_indices"] = self.state_dev[:B_eff]
+        md.extra["state_has_init"] = self.state_dev[B: B + B_eff]
+
     # ------------------------------------------------------------------ input prep
     def _prepare(self, so: SchedulerOutput, pad_to: int = 0):
         T_, B_, MB = self.max_tokens, self.max_seqs, self.max_blocks_per_seq
@@ -251,6 +293,8 @@ class ModelRunner:
             max_prefill_query_len=max_q if B_eff > nd_eff else 0)
         # MLA: prefill requests without cached context may take the up-projected MHA path
         md.extra["prefill_no_context"] = all(s.start_pos == 0 for s in so.scheduled[nd:])
+        if self.state_slots is not None:
+            self._state_metadata(so, md, B_eff)
         return md, T, sample_rows, sample_reqs
 
     # ------------------------------------------------------------------ execution
@@ -303,6 +347,12 @@ class ModelRunner:
             max_seq_len=self.cfg.scheduler.max_model_len, block_size=self.block_size,
             prefill_query_start_loc=self.prefill_qsl[:1], max_prefill_query_len=0)
         md.decode_num_splits = self._decode_splits(bucket)
+        if self.state_slots is not None:      # warm-up and capture run on the scratch slot
+            B = self.max_seqs
+            self.state_dev[:bucket].fill_(B)
+            self.state_dev[B: B + bucket].zero_()
+            md.extra["state_indices"] = self.state_dev[:bucket]
+            md.extra["state_has_init"] = self.state_dev[B: B + bucket]
         spec = self.model.kv_cache_spec()
         if md.decode_num_splits > 1 and spec["kind"] == "gqa":
             hq = spec["num_kv_heads"] * (self.cfg.model.num_attention_heads // self.cfg.model.num_key_value_heads)

@@ -93,8 +93,13 @@ class FusedMoE(nn.Module):
             self.expert_map = None
 
     # ---- weights ----------------------------------------------------------------
-    def weight_loader(self, param: torch.Tensor, loaded: torch.Tensor, expert_id: int, shard: str) -> None:
-        """``shard`` in {w1 (gate), w3 (up), w2 (down)}; ``expert_id`` is global."""
+    def weight_loader(self, param: torch.Tensor, loaded: torch.Tensor, expert_id: Optional[int] = None,
+                      shard: Optional[str] = None) -> None:
+        """``shard`` in {w1 (gate), w3 (up), w2 (down)}; ``expert_id`` is global.  Without an expert id the tensor is a
+        per-layer one (the routing bias) and is copied as is."""
+        if expert_id is None:
+            param.data.copy_(loaded.reshape(param.shape))
+            return
         lo = self.ep_rank * self.num_local
         if not (lo <= expert_id < lo + self.num_local):
             return

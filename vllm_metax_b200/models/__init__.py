@@ -40,6 +40,10 @@ _MODELS: dict[str, tuple[str, str]] = {
     "Glm4ForCausalLM": ("llama_family", "Glm4ForCausalLM"),
     "ChatGLMModel": ("llama_family", "ChatGLMModel"),
     "ChatGLMForConditionalGeneration": ("llama_family", "ChatGLMModel"),
+    "Qwen3NextForCausalLM": ("qwen3_next", "Qwen3NextForCausalLM"),
+    "Glm4MoeForCausalLM": ("moe_family", "Glm4MoeForCausalLM"),
+    "DeepseekForCausalLM": ("moe_family", "DeepseekForCausalLM"),
+    "Ernie4_5_MoeForCausalLM": ("moe_family", "Ernie4_5_MoeForCausalLM"),
     # LayerNorm + plain-MLP decoders (rotary, ALiBi or learned positions)
     "GPTNeoXForCausalLM": ("gpt", "GPTNeoXForCausalLM"),
     "FalconForCausalLM": ("gpt", "FalconForCausalLM"),

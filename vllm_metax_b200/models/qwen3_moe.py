@@ -61,12 +61,14 @@ class SparseMoeBlock(nn.Module):
 
 
 class MoeDecoderLayer(nn.Module):
+    moe_block_cls = SparseMoeBlock
+
     def __init__(self, cfg: ModelConfig, layer_idx: int, prefix: str):
         super().__init__()
         abs_idx = int(prefix.rsplit(".", 1)[1])
         self.self_attn = LlamaAttention(cfg, layer_idx, f"{prefix}.self_attn")
         if cfg.layer_is_moe(abs_idx):
-            self.mlp = SparseMoeBlock(cfg, f"{prefix}.mlp")
+            self.mlp = self.moe_block_cls(cfg, f"{prefix}.mlp")
         else:
             self.mlp = LlamaMLP(cfg, cfg.intermediate_size, f"{prefix}.mlp")
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype)

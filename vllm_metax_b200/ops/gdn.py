@@ -62,3 +62,49 @@ def gated_delta_rule(q, k, v, g, beta, query_start_loc, state=None, state_indice
         None if has_initial_state is None else has_initial_state.int().contiguous(),
         q.shape[-1] ** -0.5 if scale is None else scale, l2norm)
     return out
+
+
+# ------------------------------------------------------------------------------------------ short causal convolution
+def causal_conv1d_ref(x, w, bias=None, state=None, query_start_loc=None, state_indices=None, has_initial_state=None,
+                      silu: bool = True):
+    """fp32 statement of ``csrc/causal_conv1d.cu``: ``x [T, C]``, ``w [C, K]``, ``state [slots, K-1, C]`` (oldest first,
+    updated in place)."""
+    T, C = x.shape
+    K = w.shape[1]
+    out = torch.empty(T, C, dtype=torch.float32)
+    qsl = query_start_loc.tolist()
+    wf = w.float()
+    for b in range(len(qsl) - 1):
+        s, e = qsl[b], qsl[b + 1]
+        if e <= s:
+            continue
+        slot = int(state_indices[b]) if state_indices is not None else -1
+        use = slot >= 0 and state is not None and (has_initial_state is None or bool(has_initial_state[b]))
+        carry = state[slot].float() if use else torch.zeros(K - 1, C)
+        ext = torch.cat([carry, x[s:e].float()], 0)                     # [K-1 + n, C]
+        win = ext.unfold(0, K, 1)                                       # [n, C, K]
+        y = (win * wf[None]).sum(-1)
+        if bias is not None:
+            y = y + bias.float()
+        out[s:e] = torch.nn.functional.silu(y) if silu else y
+        if slot >= 0 and state is not None:
+            state[slot] = ext[-(K - 1):].to(state.dtype)
+    return out.to(x.dtype)
+
+
+def causal_conv1d(x, w, bias=None, state=None, query_start_loc=None, state_indices=None, has_initial_state=None,
+                  silu: bool = True):
+    """Depthwise causal convolution (+ SiLU) over a ragged batch; the last ``K-1`` inputs of every sequence are carried
+    in ``state`` between steps.  Parity: the ``causal_conv1d_fn`` / ``causal_conv1d_update`` pair the reference's GDN
+    layer calls (vllm_metax/registry/custom_ops/layers/mamba/qwen_gdn_linear_attn.py:8-10)."""
+    if not x.is_cuda:
+        return causal_conv1d_ref(x, w, bias, state, query_start_loc, state_indices, has_initial_state, silu)
+    from .. import _custom_ops as ops
+
+    ops.load_native()
+    out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    ops._launches += 2 if state is not None else 1
+    torch.ops.b200.causal_conv1d(out, x, w.contiguous(), bias, state, query_start_loc.int().contiguous(),
+                                 None if state_indices is None else state_indices.int().contiguous(),
+                                 None if has_initial_state is None else has_initial_state.int().contiguous(), silu)
+    return out
