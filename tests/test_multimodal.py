@@ -1,0 +1,81 @@
+"""Vision-language path: CLIP tower + projector + text decoder against Hugging Face's LLaVA (tiny random checkpoint,
+fp32, CPU), image features merged at the placeholder rows across chunked prefill, prefix-cache keys salted by image."""
+import pytest
+import torch
+
+tf = pytest.importorskip("transformers")
+
+IMG_TOK = 500
+
+
+def _hf_llava(tmp_path):
+    torch.manual_seed(0)
+    vc = tf.CLIPVisionConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4,
+                             image_size=28, patch_size=14, projection_dim=32)
+    tc = tf.LlamaConfig(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2, max_position_embeddings=256)
+    c = tf.LlavaConfig(vision_config=vc, text_config=tc, image_token_index=IMG_TOK, vision_feature_layer=-2,
+                       vision_feature_select_strategy="default", image_seq_length=4)
+    hf = tf.LlavaForConditionalGeneration(c).eval().float()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.dim() == 1:
+                p.add_(0.1 * torch.randn_like(p))
+            else:
+                p.mul_(3.0)
+    hf.save_pretrained(str(tmp_path))
+    return hf
+
+
+def _want(hf, ids, pixels, n=6):
+    with torch.no_grad():
+        out = hf.generate(input_ids=torch.tensor([ids]), pixel_values=pixels, max_new_tokens=n, do_sample=False,
+                          eos_token_id=None, pad_token_id=0)
+    return out[0, len(ids):].tolist()
+
+
+@pytest.mark.parametrize("chunk", [64, 5])
+def test_llava_matches_hugging_face(tmp_path, chunk):
+    from vllm_metax_b200 import LLM, SamplingParams
+
+    hf = _hf_llava(tmp_path)
+    llm = LLM(str(tmp_path), dtype="float32", device="cpu", max_model_len=128, num_gpu_blocks=32, block_size=16,
+              max_num_batched_tokens=chunk, enable_prefix_caching=True)
+    g = torch.Generator().manual_seed(1)
+    img_a, img_b = torch.randn(1, 3, 28, 28, generator=g), torch.randn(1, 3, 28, 28, generator=g)
+    two = torch.cat([img_a, img_b])
+    expanded = [5, 9] + [IMG_TOK] * 4 + [33, 100, 7, 8, 200, 31, 2, 17, 45, 301, 77, 12]          # 4 tokens per image
+    short = [5, 9, IMG_TOK, 33, 100, 7, 8, 200, 31, 2, 17, 45, 301, 77, 12]                       # one placeholder per image
+    double = [3] + [IMG_TOK] * 4 + [40, 41] + [IMG_TOK] * 4 + [60, 61, 62]
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    outs = llm.generate([
+        {"prompt_token_ids": expanded, "multi_modal_data": {"image": img_a}},
+        {"prompt_token_ids": short, "multi_modal_data": {"image": img_b}},          # same text, other image
+        {"prompt_token_ids": double, "multi_modal_data": {"pixel_values": two}},
+        {"prompt_token_ids": [5, 9, 33, 100, 7]},                                     # text only, same batch
+    ], sp)
+    got = [list(o.outputs[0].token_ids) for o in outs]
+    assert got[0] == _want(hf, expanded, img_a)
+    assert got[1] == _want(hf, expanded, img_b)
+    assert got[2] == _want(hf, double, two)
+    with torch.no_grad():
+        text = hf.generate(input_ids=torch.tensor([[5, 9, 33, 100, 7]]), max_new_tokens=6, do_sample=False,
+                           eos_token_id=None, pad_token_id=0)[0, 5:].tolist()
+    assert got[3] == text
+    # the same prompt with another image must not reuse the first image's cached blocks (and gives its own answer)
+    again = llm.generate([{"prompt_token_ids": expanded, "multi_modal_data": {"image": img_b}}], sp)
+    assert list(again[0].outputs[0].token_ids) == got[1]
+
+
+def test_placeholder_count_is_checked(tmp_path):
+    from vllm_metax_b200 import LLM, SamplingParams
+
+    _hf_llava(tmp_path)
+    llm = LLM(str(tmp_path), dtype="float32", device="cpu", max_model_len=128, num_gpu_blocks=16, block_size=16)
+    with pytest.raises(ValueError, match="placeholder"):
+        llm.generate([{"prompt_token_ids": [1, 2, 3], "multi_modal_data": {"image": torch.zeros(1, 3, 28, 28)}}],
+                     SamplingParams(max_tokens=2))
+    img = torch.randint(0, 255, (3, 50, 40), dtype=torch.uint8)          # raw image: resized + normalised here
+    out = llm.generate([{"prompt_token_ids": [1, IMG_TOK, 3], "multi_modal_data": {"image": img}}],
+                       SamplingParams(max_tokens=2, ignore_eos=True))
+    assert len(out[0].outputs[0].token_ids) == 2

@@ -74,3 +74,14 @@ def set_forward_context(ctx: ForwardContext):
         yield
     finally:
         _CTX = prev
+
+
+def merge_multimodal_embeddings(h: torch.Tensor) -> torch.Tensor:
+    """Overwrite the rows of image / audio placeholder tokens with the encoder's projected features (called by the text
+    decoders right after their embedding lookup; a no-op for text-only steps).  The runner lists the rows of this
+    step's chunk in ``extra["mm_rows"]`` and their features, in the same order, in ``extra["mm_embeds"]``."""
+    ctx = _CTX
+    md = ctx.attn_metadata if ctx is not None else None
+    if md is None or "mm_embeds" not in md.extra:
+        return h
+    return h.index_copy_(0, md.extra["mm_rows"], md.extra["mm_embeds"].to(h.dtype))

@@ -173,7 +173,11 @@ class ModelConfig:
 
     @classmethod
     def from_hf_dict(cls, d: dict, **overrides: Any) -> "ModelConfig":
-        raw, d = d, _canonical_hf_keys(d)
+        raw = d
+        if isinstance(d.get("text_config"), dict):     # vision-language wrappers: the decoder's fields live one level down
+            d = dict(d["text_config"], architectures=d.get("architectures"),
+                     **{k: d[k] for k in ("quantization_config", "torch_dtype", "dtype") if k in d and k not in d["text_config"]})
+        d = _canonical_hf_keys(d)
         archs = d.get("architectures") or ["LlamaForCausalLM"]
         arch = archs[0]
         # DeepSeek-V3 lineage: sigmoid scores + bias-corrected grouped top-k even when the config (HF-native exports)

@@ -79,6 +79,8 @@ class BlockPool:
                 toks = req.all_token_ids
             i = len(hs)
             root = None if req.lora_request is None else ("lora", req.lora_request.lora_int_id)   # K/V depend on the adapter
+            if getattr(req, "mm_hash", None) is not None:                                         # ... and on the images
+                root = (root, "mm", req.mm_hash)
             hs.append(self.chain_hash(hs[-1] if hs else root, tuple(toks[i * bs:(i + 1) * bs])))
         return hs[:nfull]
 

@@ -60,7 +60,8 @@ class LLMEngine:
     # ------------------------------------------------------------------ KV transfer (disaggregated prefill)
     @staticmethod
     def _kv_salt(req: Request):
-        return None if req.lora_request is None else ("lora", req.lora_request.lora_int_id)
+        salt = None if req.lora_request is None else ("lora", req.lora_request.lora_int_id)
+        return salt if req.mm_hash is None else (salt, "mm", req.mm_hash)
 
     def _load_external_kv(self, req: Request) -> None:
         """Before admission: pull the blocks another engine published for this prompt.  Whatever cannot be loaded
@@ -98,14 +99,19 @@ class LLMEngine:
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
                     request_id: Optional[str] = None, prompt: Optional[str] = None,
-                    arrival_time: Optional[float] = None, lora_request=None) -> str:
+                    arrival_time: Optional[float] = None, lora_request=None, multi_modal_data: Optional[dict] = None) -> str:
         if self.dead is not None:
             raise EngineDeadError(str(self.dead))
         rid = request_id or f"req-{next(self._ids)}"
+        mm = None
+        if multi_modal_data:
+            prompt_token_ids, mm = self.runner.encode_multimodal(list(prompt_token_ids), multi_modal_data)
         if params is not None and (params.constrained or params.guided_regex is not None or params.guided_json is not None):
             params.prepare(self.tokenizer)
         req = Request(rid, list(prompt_token_ids), params or SamplingParams(), self.cfg.model.eos_token_id, prompt,
                       arrival_time)
+        if mm is not None:
+            req.mm_embeds, req.mm_positions, req.mm_hash = mm
         if lora_request is None and params is not None:
             lora_request = getattr(params, "_lora_request", None)      # set by front ends that only pass params through
         if lora_request is not None:
@@ -298,7 +304,9 @@ class LLM:
             ids, text = self._to_ids(p)
             import copy
 
-            rid = self.engine.add_request(ids, copy.copy(sp), prompt=text, arrival_time=now, lora_request=lr)
+            mm = p.get("multi_modal_data") if isinstance(p, dict) else None       # {"image": tensor | PIL | list}
+            rid = self.engine.add_request(ids, copy.copy(sp), prompt=text, arrival_time=now, lora_request=lr,
+                                          multi_modal_data=mm)
             order.append(rid)
             reqs[rid] = self.engine.requests[rid]
         done: dict[str, Request] = {}

@@ -216,6 +216,58 @@ class ModelRunner:
         md.extra["state_indices"] = self.state_dev[:B_eff]
         md.extra["state_has_init"] = self.state_dev[B: B + B_eff]
 
+    # ------------------------------------------------------------------ multimodal inputs
+    @torch.no_grad()
+    def encode_multimodal(self, prompt_token_ids: list, mm: dict):
+        """Run the model's encoder on a request's images and line the features up with the prompt's placeholder tokens.
+
+        ``mm["image"]``: one image or a list of them (PIL, ``[3, H, W]`` tensors) or pre-processed ``pixel_values
+        [n, 3, S, S]``.  The prompt holds either one placeholder token per image (expanded here to the encoder's token
+        count) or the already expanded run.  Returns ``(token ids, (features [N, hidden], positions [N], hash))``."""
+        import hashlib
+
+        model = self.model
+        if not getattr(model, "is_multimodal", False):
+            raise ValueError(f"{self.cfg.model.architecture} takes no multi-modal inputs")
+        imgs = mm.get("pixel_values", mm.get("image"))
+        if isinstance(imgs, torch.Tensor) and imgs.dim() == 4:
+            pixels = imgs
+        else:
+            if not isinstance(imgs, (list, tuple)):
+                imgs = [imgs]
+            pixels = torch.stack([model.preprocess(im) for im in imgs])
+        feats = model.embed_multimodal(pixels.to(self.device))              # [n, per, hidden]
+        n, per, hid = feats.shape
+        tok = model.image_token_id
+        count = sum(1 for t in prompt_token_ids if t == tok)
+        if count == n and per > 1:
+            ids = []
+            for t in prompt_token_ids:
+                ids.extend([tok] * per if t == tok else [t])
+        elif count == n * per:
+            ids = prompt_token_ids
+        else:
+            raise ValueError(f"prompt has {count} image placeholder tokens for {n} image(s) of {per} tokens each")
+        pos = np.asarray([i for i, t in enumerate(ids) if t == tok], dtype=np.int64)
+        digest = hashlib.sha256(pixels.detach().float().cpu().numpy().tobytes()).hexdigest()[:16]
+        return ids, (feats.reshape(n * per, hid), pos, digest)
+
+    def _multimodal_rows(self, so: SchedulerOutput, md: AttentionMetadata) -> None:
+        """Rows of this step's flat batch that are placeholder tokens, with their features in the same order."""
+        rows, parts, t = [], [], 0
+        for s in so.scheduled:
+            r = s.request
+            if r.mm_embeds is not None and s.start_pos < r.mm_positions[-1] + 1:
+                lo = int(np.searchsorted(r.mm_positions, s.start_pos))
+                hi = int(np.searchsorted(r.mm_positions, s.start_pos + s.num_new_tokens))
+                if hi > lo:
+                    rows.append(r.mm_positions[lo:hi] - s.start_pos + t)
+                    parts.append(r.mm_embeds[lo:hi])
+            t += s.num_new_tokens
+        if rows:
+            md.extra["mm_rows"] = torch.from_numpy(np.concatenate(rows)).to(self.device)
+            md.extra["mm_embeds"] = torch.cat(parts) if len(parts) > 1 else parts[0]
+
     # ------------------------------------------------------------------ input prep
     def _prepare(self, so: SchedulerOutput, pad_to: int = 0):
         T_, B_, MB = self.max_tokens, self.max_seqs, self.max_blocks_per_seq
@@ -295,6 +347,8 @@ class ModelRunner:
         md.extra["prefill_no_context"] = all(s.start_pos == 0 for s in so.scheduled[nd:])
         if self.state_slots is not None:
             self._state_metadata(so, md, B_eff)
+        if getattr(self.model, "is_multimodal", False):
+            self._multimodal_rows(so, md)
         return md, T, sample_rows, sample_reqs
 
     # ------------------------------------------------------------------ execution

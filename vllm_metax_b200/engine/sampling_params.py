@@ -74,7 +74,7 @@ class Request:
 
     __slots__ = ("request_id", "prompt_token_ids", "params", "output_token_ids", "status", "block_ids",
                  "num_computed_tokens", "arrival_time", "first_token_time", "finish_time", "token_times",
-                 "eos_token_id", "num_cached_tokens", "logprobs", "prompt", "_hashes", "spec_token_ids", "lora_request")
+                 "eos_token_id", "num_cached_tokens", "logprobs", "prompt", "_hashes", "spec_token_ids", "lora_request", "mm_embeds", "mm_positions", "mm_hash")
 
     def __init__(self, request_id: str, prompt_token_ids: list[int], params: SamplingParams,
                  eos_token_id: Optional[int] = None, prompt: Optional[str] = None,
@@ -96,6 +96,9 @@ class Request:
         self.prompt = prompt
         self._hashes: list[int] = []
         self.lora_request = None               # lora.LoRARequest of the adapter this request runs with
+        self.mm_embeds = None                  # [n, hidden] encoder features for the prompt's placeholder tokens ...
+        self.mm_positions = None               # ... and the (sorted) prompt positions they replace
+        self.mm_hash = None                    # content hash of the request's images (salts the prefix-cache keys)
         self.spec_token_ids: list[int] = []     # draft tokens to verify in the next step (speculative decoding)
 
     @property

@@ -40,6 +40,7 @@ _MODELS: dict[str, tuple[str, str]] = {
     "Glm4ForCausalLM": ("llama_family", "Glm4ForCausalLM"),
     "ChatGLMModel": ("llama_family", "ChatGLMModel"),
     "ChatGLMForConditionalGeneration": ("llama_family", "ChatGLMModel"),
+    "LlavaForConditionalGeneration": ("llava", "LlavaForConditionalGeneration"),
     "Qwen3NextForCausalLM": ("qwen3_next", "Qwen3NextForCausalLM"),
     "Glm4MoeForCausalLM": ("moe_family", "Glm4MoeForCausalLM"),
     "DeepseekForCausalLM": ("moe_family", "DeepseekForCausalLM"),

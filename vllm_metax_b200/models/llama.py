@@ -23,6 +23,7 @@ import torch.nn as nn
 
 from .. import _custom_ops as ops
 from ..config import ModelConfig
+from ..attention.metadata import merge_multimodal_embeddings
 from ..layers.attention import Attention
 from ..layers.basic import ParallelLMHead, RMSNorm, SiluAndMul, VocabParallelEmbedding, get_rope
 from ..layers.linear import GateUpSiluLinear, MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear
@@ -143,7 +144,7 @@ class LlamaModel(nn.Module):
         sharded by token rows; hidden states between kernels are the all-gathered normalised rows."""
         fused = self.fused_ar
         tp, rank = ps.tp_size(), ps.tp_rank()
-        h = self.embed_tokens(input_ids)
+        h = merge_multimodal_embeddings(self.embed_tokens(input_ids))
         T = h.shape[0]
         rpr = (T + tp - 1) // tp
         res = torch.zeros(rpr, h.shape[1], dtype=h.dtype, device=h.device)
@@ -167,7 +168,7 @@ class LlamaModel(nn.Module):
         if getattr(self, "fused_ar", None) is not None and input_ids.shape[0] >= getattr(self, "fused_min_tokens", 0):
             return self.forward_fused_tp(input_ids, positions)
         if self.embed_tokens is not None:
-            h, residual = self.embed_tokens(input_ids), None
+            h, residual = merge_multimodal_embeddings(self.embed_tokens(input_ids)), None
         else:
             h, residual = intermediate["hidden_states"], intermediate["residual"]
         for i in range(self.start_layer, self.end_layer):
