@@ -3,7 +3,7 @@
 ``get_linear_method(cfg, prefix)`` returns the ``LinearMethodBase`` for the linear layer
 at ``prefix`` (``None`` = unquantised bf16 tcgen05 GEMM).  Names follow the reference's
 supported list (vllm_metax/platform.py:177-189): awq, gptq, compressed-tensors, fp8,
-moe_wna16 (+ w8a8 int8 through compressed-tensors).
+moe_wna16 (+ w8a8 int8 through compressed-tensors), mxfp4 / nvfp4 (weight-only, expanded at load).
 """
 from __future__ import annotations
 
@@ -34,7 +34,7 @@ def _ensure_loaded():
     _loaded = True
     import importlib
 
-    for mod in ("fp8", "int8", "wna16"):
+    for mod in ("fp8", "int8", "wna16", "fp4"):
         try:
             importlib.import_module(f"{__name__}.{mod}")
         except ModuleNotFoundError:
