@@ -99,3 +99,40 @@ def test_guided_needs_tokenizer():
 
     with pytest.raises(ValueError):
         LLM(tiny_cfg(), **KW).generate([[1, 2]], SamplingParams(guided_regex="a+"))
+
+
+def test_schema_to_regex_optional_refs_alternatives():
+    """``required`` decides which properties may be left out; ``$ref`` / ``anyOf`` / type lists / formats expand."""
+    import regex
+
+    from vllm_metax_b200.engine.structured import schema_to_regex
+
+    def ok(schema, doc):
+        return regex.fullmatch(schema_to_regex(schema), doc) is not None
+
+    s = {"type": "object", "required": ["b"],
+         "properties": {"a": {"type": "integer"}, "b": {"type": "string"}, "c": {"type": "boolean"}}}
+    assert ok(s, '{"b": "x"}') and ok(s, '{"a": 1, "b": "x"}') and ok(s, '{"a": 1, "b": "x", "c": true}')
+    assert ok(s, '{"b": "x", "c": false}')
+    assert not ok(s, '{"a": 1}') and not ok(s, '{"a": 1, "c": true}') and not ok(s, '{"b": "x",}')
+    none_required = dict(s, required=[])
+    assert ok(none_required, "{}") and ok(none_required, '{"c": true}') and ok(none_required, '{"a": 1, "c": true}')
+    assert not ok(none_required, '{"c": true, "a": 1}')                       # listed order is kept
+    people = {"$defs": {"P": {"type": "object", "properties": {
+        "name": {"type": "string"}, "age": {"anyOf": [{"type": "integer"}, {"type": "null"}]}}}},
+        "type": "array", "items": {"$ref": "#/$defs/P"}, "minItems": 1}
+    assert ok(people, '[{"name": "a", "age": null}, {"name": "b", "age": 3}]') and not ok(people, "[]")
+    misc = {"type": "object", "properties": {"id": {"type": "string", "format": "uuid"},
+                                             "t": {"type": ["string", "null"], "maxLength": 3},
+                                             "tags": {"type": "array", "items": {}}}}
+    assert ok(misc, '{"id": "123e4567-e89b-12d3-a456-426614174000", "t": "abc", "tags": [1, "x", {"k": 2}]}')
+    assert ok(misc, '{"id": "123e4567-e89b-12d3-a456-426614174000", "t": null, "tags": []}')
+    assert not ok(misc, '{"id": "123e4567-e89b-12d3-a456-426614174000", "t": "abcd", "tags": []}')
+    assert ok({"type": "string", "pattern": "^[a-z]+\\d$"}, '"abc1"') and not ok({"type": "string", "pattern": "^[a-z]+\\d$"}, '"abc"')
+    assert ok({}, '{"a": [1, 2], "b": {"c": null}}')
+    tree = {"$defs": {"N": {"type": "object", "properties": {"v": {"type": "integer"},
+                                                                "kids": {"type": "array", "items": {"$ref": "#/$defs/N"}}},
+                            "required": ["v"]}}, "$ref": "#/$defs/N"}
+    import pytest as _pytest
+    with _pytest.raises(NotImplementedError):           # unbounded recursion is refused, not silently truncated
+        schema_to_regex(tree)

@@ -78,21 +78,92 @@ _JSON_NUMBER = r"-?(?:0|[1-9][0-9]*)(?:\.[0-9]+)?(?:[eE][+-]?[0-9]+)?"
 _JSON_INT = r"-?(?:0|[1-9][0-9]*)"
 
 
-def schema_to_regex(schema) -> str:
-    """Regular expression for the JSON documents of a schema: ``type`` string / integer / number / boolean / null,
-    ``enum`` / ``const``, ``array`` (``items``, optional ``minItems`` / ``maxItems``), ``object`` with ``properties``
-    (all listed properties, in order - ``required`` is treated as "all").  Anything else raises."""
+_FORMATS = {
+    "date-time": r'"\d{4}-\d{2}-\d{2}T\d{2}:\d{2}:\d{2}(?:\.\d+)?(?:Z|[+-]\d{2}:\d{2})"',
+    "date": r'"\d{4}-\d{2}-\d{2}"',
+    "time": r'"\d{2}:\d{2}:\d{2}(?:\.\d+)?(?:Z|[+-]\d{2}:\d{2})?"',
+    "uuid": r'"[0-9a-fA-F]{8}-[0-9a-fA-F]{4}-[0-9a-fA-F]{4}-[0-9a-fA-F]{4}-[0-9a-fA-F]{12}"',
+}
+_STR_CHAR = r'(?:[^"\\\x00-\x1f]|\\["\\/bfnrt]|\\u[0-9a-fA-F]{4})'
+
+
+def _any_json(depth: int) -> str:
+    """Any JSON value with containers nested at most ``depth`` levels (schemas that leave a value open)."""
+    scalar = f"(?:{_JSON_STRING}|{_JSON_NUMBER}|true|false|null)"
+    if depth <= 0:
+        return scalar
+    inner = _any_json(depth - 1)
+    arr = rf"\[{_JSON_WS}(?:{inner}(?:,{_JSON_WS}{inner})*)?{_JSON_WS}\]"
+    member = f"{_JSON_STRING}:{_JSON_WS}{inner}"
+    obj = rf"\{{{_JSON_WS}(?:{member}(?:,{_JSON_WS}{member})*)?{_JSON_WS}\}}"
+    return f"(?:{scalar}|{arr}|{obj})"
+
+
+def schema_to_regex(schema, _root=None, _depth: int = 0) -> str:
+    """Regular expression for the JSON documents of a schema.
+
+    Supported: ``type`` (one or a list of) string / integer / number / boolean / null / array / object; ``enum`` /
+    ``const``; ``anyOf`` / ``oneOf`` (alternation) and single-element ``allOf``; local ``$ref`` into ``$defs`` /
+    ``definitions`` (recursive schemas are unrolled three levels); strings with ``minLength`` / ``maxLength`` /
+    ``pattern`` / ``format`` (date-time, date, time, uuid); arrays with ``items`` / ``prefixItems`` / ``minItems`` /
+    ``maxItems``; objects with ``properties`` in their listed order, where ``required`` (when present) says which may be
+    left out - without a ``required`` list every listed property is produced; an object or schema that leaves its
+    content open accepts any JSON value nested up to two levels.  Anything else raises."""
     import json
     import re
 
     if isinstance(schema, str):
         schema = json.loads(schema)
+    root = schema if _root is None else _root
+    if schema is True or schema == {}:
+        return _any_json(2)
+    rec = lambda sub: schema_to_regex(sub, root, _depth)
+    if "$ref" in schema:
+        ref = schema["$ref"]
+        if not ref.startswith("#/"):
+            raise NotImplementedError(f"only local $ref is supported: {ref!r}")
+        if _depth >= 3:
+            raise NotImplementedError("recursive $ref deeper than three levels")
+        node = root
+        for part in ref[2:].split("/"):
+            node = node[part.replace("~1", "/").replace("~0", "~")]
+        return schema_to_regex(node, root, _depth + 1)
+    for key in ("anyOf", "oneOf"):
+        if key in schema:
+            alts = []
+            for sub in schema[key]:
+                try:
+                    alts.append(rec(sub))
+                except NotImplementedError:
+                    if _depth < 3:
+                        raise
+            if not alts:
+                raise NotImplementedError("no usable alternative")
+            return "(?:" + "|".join(alts) + ")"
+    if "allOf" in schema:
+        if len(schema["allOf"]) != 1:
+            raise NotImplementedError("allOf with several sub-schemas")
+        return rec(schema["allOf"][0])
     if "enum" in schema:
         return "(?:" + "|".join(re.escape(json.dumps(v)) for v in schema["enum"]) + ")"
     if "const" in schema:
         return re.escape(json.dumps(schema["const"]))
     t = schema.get("type")
+    if isinstance(t, list):
+        return "(?:" + "|".join(rec(dict(schema, type=one)) for one in t) + ")"
+    if t is None and "properties" in schema:
+        t = "object"
     if t == "string":
+        if "format" in schema and schema["format"] in _FORMATS:
+            return _FORMATS[schema["format"]]
+        if "pattern" in schema:
+            pat = schema["pattern"]
+            pat = pat[1:] if pat.startswith("^") else pat
+            pat = pat[:-1] if pat.endswith("$") and not pat.endswith("\\$") else pat
+            return f'"(?:{pat})"'
+        if "minLength" in schema or "maxLength" in schema:
+            lo, hi = int(schema.get("minLength", 0)), schema.get("maxLength")
+            return f'"{_STR_CHAR}{{{lo},{"" if hi is None else int(hi)}}}"'
         return _JSON_STRING
     if t == "integer":
         return _JSON_INT
@@ -103,7 +174,10 @@ def schema_to_regex(schema) -> str:
     if t == "null":
         return "null"
     if t == "array":
-        item = schema_to_regex(schema.get("items", {"type": "string"}))
+        if "prefixItems" in schema:
+            items = [rec(sub) for sub in schema["prefixItems"]]
+            return rf"\[{_JSON_WS}" + f",{_JSON_WS}".join(items) + rf"{_JSON_WS}\]"
+        item = rec(schema["items"]) if schema.get("items") not in (None, True) else _any_json(1)
         lo, hi = int(schema.get("minItems", 0)), schema.get("maxItems")
         more = f"(?:,{_JSON_WS}{item})"
         if hi is None:
@@ -115,9 +189,30 @@ def schema_to_regex(schema) -> str:
     if t == "object":
         props = schema.get("properties") or {}
         if not props:
-            return r"\{" + _JSON_WS + r"\}"
-        parts = [re.escape(json.dumps(k)) + ":" + _JSON_WS + schema_to_regex(v) for k, v in props.items()]
-        return r"\{" + _JSON_WS + ("," + _JSON_WS).join(parts) + _JSON_WS + r"\}"
+            if schema.get("additionalProperties") in (None, False) and "additionalProperties" in schema:
+                return r"\{" + _JSON_WS + r"\}"
+            extra = schema.get("additionalProperties")
+            val = rec(extra) if isinstance(extra, dict) and extra else _any_json(1)
+            member = f"{_JSON_STRING}:{_JSON_WS}{val}"
+            return rf"\{{{_JSON_WS}(?:{member}(?:,{_JSON_WS}{member})*)?{_JSON_WS}\}}"
+        names = list(props)
+        subs = [re.escape(json.dumps(k)) + ":" + _JSON_WS + rec(v) for k, v in props.items()]
+        required = set(schema["required"]) if "required" in schema else set(names)
+        sep = "," + _JSON_WS
+        if any(n in required for n in names):
+            last = max(i for i, n in enumerate(names) if n in required)
+            body = ""
+            for i, (n, sub) in enumerate(zip(names, subs)):
+                piece = sub + sep if i < last else (sep + sub if i > last else sub)
+                body += piece if n in required else f"(?:{piece})?"
+        else:       # every property optional: pick which one comes first, earlier ones absent, later ones optional
+            alts = []
+            for i, sub in enumerate(subs):
+                alts.append(sub + "".join(f"(?:{sep}{later})?" for later in subs[i + 1:]))
+            body = "(?:" + "|".join(alts) + ")?"
+        return r"\{" + _JSON_WS + body + _JSON_WS + r"\}"
+    if t is None:
+        return _any_json(2)
     raise NotImplementedError(f"JSON schema construct not supported for guided decoding: {schema!r}")
 
 
