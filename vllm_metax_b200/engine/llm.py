@@ -34,7 +34,7 @@ class LLMEngine:
         nb = self.runner.determine_num_blocks()
         self.runner.init_kv_cache(nb)
         prefix_ok = getattr(self.runner.model, "supports_prefix_caching", True)
-        self.kv = KVCacheManager(nb, cfg.cache.block_size, cfg.cache.enable_prefix_caching and prefix_ok)
+        self.kv = KVCacheManager(nb, self.runner.virt_bs, cfg.cache.enable_prefix_caching and prefix_ok)
         self.kv.on_free = [self.runner.release_request]
         self.scheduler = Scheduler(cfg.scheduler, self.kv)
         self.runner.capture_graphs()
@@ -246,7 +246,7 @@ class LLM:
                  load_format: str = "auto", seed: int = 0, tokenizer: Any = None, enable_sleep_mode: bool = False,
                  additional_config: Optional[dict] = None, speculative_config: Optional[dict] = None,
                  enable_lora: bool = False, max_loras: int = 4, max_lora_rank: int = 64,
-                 kv_transfer_config: Optional[dict] = None):
+                 kv_transfer_config: Optional[dict] = None, decode_context_parallel_size: int = 1):
         overrides = {"seed": seed}
         if enable_lora:
             overrides.update(enable_lora=True, max_loras=max_loras, max_lora_rank=max_lora_rank)
@@ -263,7 +263,7 @@ class LLM:
                               gpu_memory_utilization=gpu_memory_utilization, kv_cache_dtype=kv_cache_dtype,
                               enable_prefix_caching=enable_prefix_caching),
             parallel=ParallelConfig(tensor_parallel_size, pipeline_parallel_size, data_parallel_size,
-                                    enable_expert_parallel),
+                                    enable_expert_parallel, decode_context_parallel_size),
             scheduler=SchedulerConfig(max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens,
                                       max_model_len=max_model_len, enable_chunked_prefill=enable_chunked_prefill),
             device=device, enforce_eager=enforce_eager, load_format=load_format,

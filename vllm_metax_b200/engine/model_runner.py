@@ -64,7 +64,19 @@ class ModelRunner:
         sc = cfg.scheduler
         self.max_tokens = max(sc.max_num_batched_tokens, sc.max_num_seqs)
         self.max_seqs = sc.max_num_seqs
-        self.max_blocks_per_seq = (sc.max_model_len + self.block_size - 1) // self.block_size
+        # decode context parallel: a scheduler block of block_size * dcp tokens is block_size slots on every rank of the
+        # DCP group (token p lives on rank p % dcp, at local index p // dcp)
+        self.dcp = ps.get_dcp_group().world_size
+        self.dcp_rank = ps.get_dcp_group().rank_in_group
+        self.virt_bs = self.block_size * self.dcp
+        if self.dcp > 1:
+            m = cfg.model
+            reps = ps.tp_size() // m.num_key_value_heads if m.num_key_value_heads < ps.tp_size() else 1
+            if m.is_mla or reps % self.dcp != 0:
+                raise ValueError("decode context parallelism needs a GQA model whose KV heads are replicated over at "
+                                 f"least dcp tensor-parallel ranks (kv heads {m.num_key_value_heads}, tp {ps.tp_size()}, "
+                                 f"dcp {self.dcp})")
+        self.max_blocks_per_seq = (sc.max_model_len + self.virt_bs - 1) // self.virt_bs
         self.kv_caches: list = []
         self.num_blocks = 0
         self._alloc_inputs()
@@ -278,6 +290,8 @@ class ModelRunner:
         bt = self.h32_np[o:o + B_ * MB].reshape(B_, MB); o += B_ * MB
         pqsl = self.h32_np[o:o + B_ + 1]
         bs = self.block_size
+        d, dr, vbs = self.dcp, self.dcp_rank, self.virt_bs
+        ctx_local = []
         t = 0
         qsl[0] = 0
         max_q = max_seq = 0
@@ -286,7 +300,15 @@ class ModelRunner:
         for i, s in enumerate(so.scheduled):
             r = s.request
             n, p0 = s.num_new_tokens, s.start_pos
-            if n == 1:
+            if d > 1:
+                ids[t:t + n] = ((r.all_token_ids + r.spec_token_ids[: s.num_spec])[p0:p0 + n] if s.num_spec
+                                else r.all_token_ids[p0:p0 + n])
+                ar = np.arange(p0, p0 + n)
+                pos[t:t + n] = ar
+                blk = np.asarray(r.block_ids, dtype=np.int64)
+                slots[t:t + n] = np.where(ar % d == dr, blk[ar // vbs] * bs + (ar % vbs) // d, -1)
+                ctx_local.append(max(0, (p0 - dr + d - 1) // d))
+            elif n == 1:
                 ids[t] = r.token_at(p0)
                 pos[t] = p0
                 slots[t] = r.block_ids[p0 // bs] * bs + p0 % bs
@@ -302,7 +324,7 @@ class ModelRunner:
                 slots[t:t + n] = blk[ar // bs] * bs + ar % bs
             t += n
             qsl[i + 1] = t
-            sl[i] = p0 + n
+            sl[i] = p0 + n if d == 1 else max(0, (p0 + n - dr + d - 1) // d)     # tokens in THIS rank's cache
             nb = len(r.block_ids)
             bt[i, :nb] = r.block_ids
             max_q = max(max_q, n)
@@ -345,6 +367,10 @@ class ModelRunner:
             max_prefill_query_len=max_q if B_eff > nd_eff else 0)
         # MLA: prefill requests without cached context may take the up-projected MHA path
         md.extra["prefill_no_context"] = all(s.start_pos == 0 for s in so.scheduled[nd:])
+        if d > 1:
+            ctx_local += [0] * (B_eff - len(ctx_local))
+            md.extra["dcp_ctx_lens"] = torch.tensor(ctx_local, dtype=torch.int32).to(self.device, non_blocking=True)
+            md.extra["dcp_any_context"] = any(s.start_pos > 0 for s in so.scheduled[nd:])
         if self.state_slots is not None:
             self._state_metadata(so, md, B_eff)
         if getattr(self.model, "is_multimodal", False):
@@ -401,6 +427,9 @@ class ModelRunner:
             max_seq_len=self.cfg.scheduler.max_model_len, block_size=self.block_size,
             prefill_query_start_loc=self.prefill_qsl[:1], max_prefill_query_len=0)
         md.decode_num_splits = self._decode_splits(bucket)
+        if self.dcp > 1:                      # decode rows of the captured step take the context-parallel path
+            md.extra["dcp_ctx_lens"] = torch.zeros(bucket, dtype=torch.int32, device=self.device)
+            md.extra["dcp_any_context"] = False
         if self.state_slots is not None:      # warm-up and capture run on the scratch slot
             B = self.max_seqs
             self.state_dev[:bucket].fill_(B)

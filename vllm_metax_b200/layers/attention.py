@@ -82,6 +82,8 @@ class Attention(nn.Module):
         T = q.shape[0]
         if isinstance(kv_scales, tq.TqFormat):
             return self._forward_turboquant(q, k, v, positions, rope, md, kv_cache, kv_scales)
+        if "dcp_ctx_lens" in md.extra:
+            return self._forward_dcp(q, k, v, positions, rope, md, kv_cache, kv_scales)
         if rope is not None:
             ops.rope_and_cache(positions, q, k, v, self.head_size, rope.cos_sin_cache, rope.is_neox, kv_cache,
                                md.slot_mapping, kv_scales, self.k_scale, self.v_scale)
@@ -105,6 +107,78 @@ class Attention(nn.Module):
                                         sinks=self.sinks, k_scale=self.k_scale, v_scale=self.v_scale,
                                         max_seq_len=md.max_seq_len, alibi_slopes=self.alibi_slopes)
         return out.reshape(T, self.num_heads * self.head_size)
+
+    def _forward_dcp(self, q, k, v, positions, rope, md, kv_cache, kv_scales) -> torch.Tensor:
+        """Decode context parallel: this rank's cache holds every dcp-th token of each sequence (the slot mapping is
+        -1 for the others).  Decode rows: all-gather q over the group's heads, attend the local shard, combine the
+        partial outputs by their log-sum-exp and keep this rank's heads.  Prefill rows: causal attention over the
+        chunk's own fresh K / V (every rank has them - its KV heads are replicated over the group) merged with the
+        same gather / local / combine pass over the cached context, which needs no mask because all of it precedes
+        the chunk.  Mirrors vllm_metax/v1/attention/backends/flash_attn.py:1450-1610."""
+        from ..parallel import dcp
+        from ..parallel import state as ps
+
+        g = ps.get_dcp_group()
+        d = g.world_size
+        T, H, D = q.shape[0], self.num_heads, self.head_size
+        if rope is not None:
+            ops.rope_and_cache(positions, q, k, v, D, rope.cos_sin_cache, rope.is_neox, kv_cache, md.slot_mapping,
+                               kv_scales, self.k_scale, self.v_scale)
+        else:
+            ops.reshape_and_cache(k, v, kv_cache, md.slot_mapping, kv_scales, self.k_scale, self.v_scale)
+        q3 = q.reshape(T, H, D)
+        out = torch.empty(T, H, D, dtype=q.dtype, device=q.device)
+        nd, ndt = md.num_decodes, md.num_decode_tokens
+        common = dict(kv_scales=kv_scales, window=self.window, softcap=self.softcap, k_scale=self.k_scale,
+                      v_scale=self.v_scale, alibi_slopes=None)
+        assert self.alibi_slopes is None and self.sinks is None, "ALiBi / sinks are not combined with DCP"
+
+        def masked(o, lse, empty_rows):           # rows whose local shard is empty contribute nothing
+            lse = torch.where(empty_rows[None, :], torch.full_like(lse, float("-inf")), lse)
+            return torch.where(empty_rows[:, None, None], torch.zeros_like(o), o), lse.t().contiguous()
+
+        if nd > 0:
+            lens = md.seq_lens[:nd]
+
+            def attend_decode(q_all):
+                o = torch.empty(ndt, H * d, D, dtype=q.dtype, device=q.device)
+                lse = torch.empty(H * d, ndt, dtype=torch.float32, device=q.device)
+                ops.paged_attention_decode(q_all, kv_cache, md.block_table[:nd], lens.clamp_min(1), self.scale, out=o,
+                                           lse_out=lse, num_splits=md.decode_num_splits, max_seq_len=md.max_seq_len,
+                                           workspace=md.decode_workspace, **common)
+                return masked(o, lse, lens == 0)
+
+            out[:ndt] = dcp.decode_attention(q3[:ndt].contiguous(), attend_decode, g)
+        if md.num_prefills > 0:
+            Tp = T - ndt
+            cu = md.prefill_query_start_loc
+            Hkv = self.num_kv_heads
+            qp = q3[ndt:].contiguous()
+            kp = k[ndt:].reshape(Tp, Hkv, D).contiguous()
+            vp = v[ndt:].reshape(Tp, Hkv, D).contiguous()
+            o_self = torch.empty(Tp, H, D, dtype=q.dtype, device=q.device)
+            lse_self = torch.empty(H, Tp, dtype=torch.float32, device=q.device)
+            ops.varlen_attention(qp, kp, vp, cu, cu, self.scale, out=o_self, max_q_len=md.max_prefill_query_len,
+                                 causal=True, window=self.window, softcap=self.softcap, lse_out=lse_self)
+            if md.extra["dcp_any_context"]:
+                ctx = md.extra["dcp_ctx_lens"][nd:]
+                qlens = (cu[1:] - cu[:-1]).long()
+                empty_tok = torch.repeat_interleave(ctx == 0, qlens, output_size=Tp)
+
+                def attend_context(q_all):
+                    o = torch.empty(Tp, H * d, D, dtype=q.dtype, device=q.device)
+                    lse = torch.empty(H * d, Tp, dtype=torch.float32, device=q.device)
+                    ops.paged_attention_prefill(q_all, kv_cache, md.block_table[nd:], ctx.clamp_min(1), cu, self.scale,
+                                                out=o, lse_out=lse, max_q_len=md.max_prefill_query_len, causal=False,
+                                                max_seq_len=md.max_seq_len, **{k_: v_ for k_, v_ in common.items()
+                                                                               if k_ != "window"})
+                    return masked(o, lse, empty_tok)
+
+                o_ctx, lse_ctx = dcp.decode_attention(qp, attend_context, g, return_lse=True)
+                out[ndt:] = ops.merge_attn_states(o_ctx, lse_ctx.t().contiguous(), o_self, lse_self)
+            else:
+                out[ndt:] = o_self
+        return out.reshape(T, H * D)
 
     def _forward_turboquant(self, q, k, v, positions, rope, md, cache, fmt) -> torch.Tensor:
         """TurboQuant cache: RoPE, quantising store, then decode rows straight from the compressed slots and prefill
