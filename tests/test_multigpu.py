@@ -329,3 +329,79 @@ def _moe_layer_a2a_worker(rank, world):
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_fused_moe_sequence_parallel_a2a_2gpu():
     _launch(_moe_layer_a2a_worker, 2)
+
+
+# ---- pipeline parallel and decode context parallel through the engine ------------------------------------------
+def _pp_dcp_cfg(kv_heads):
+    from vllm_metax_b200 import ModelConfig
+
+    return ModelConfig(architecture="LlamaForCausalLM", vocab_size=2048, hidden_size=1024, intermediate_size=2816,
+                       num_hidden_layers=4, num_attention_heads=8, num_key_value_heads=kv_heads, head_dim=128,
+                       max_position_embeddings=1024, dtype=torch.bfloat16, seed=0)
+
+
+def _pp_dcp_prompts():
+    g = torch.Generator().manual_seed(9)
+    return [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (100, 33, 300, 1)]
+
+
+def _single_gpu_tokens(kv_heads):
+    from vllm_metax_b200 import LLM, SamplingParams
+
+    llm = LLM(_pp_dcp_cfg(kv_heads), device="cuda", block_size=64, max_model_len=512, max_num_seqs=8,
+              max_num_batched_tokens=128, num_gpu_blocks=64)
+    toks = [list(o.outputs[0].token_ids) for o in llm.generate(_pp_dcp_prompts(), SamplingParams(max_tokens=12, ignore_eos=True))]
+    llm.engine.runner.graphs.clear()
+    del llm
+    torch.cuda.empty_cache()
+    return toks
+
+
+def _pp_engine_worker(rank, world, want):
+    os.environ["B200_FUSED_TP_COLLECTIVES"] = "0"
+    from vllm_metax_b200 import LLM, SamplingParams
+    from vllm_metax_b200 import _custom_ops as ops
+
+    llm = LLM(_pp_dcp_cfg(2), device="cuda", pipeline_parallel_size=world, block_size=64, max_model_len=512, max_num_seqs=8,
+              max_num_batched_tokens=128, num_gpu_blocks=64)
+    assert llm.engine.runner.model.num_kv_layers() == 4 // world
+    outs = llm.generate(_pp_dcp_prompts(), SamplingParams(max_tokens=12, ignore_eos=True))
+    torch.cuda.synchronize()
+    ops.check_kernel_status(rank)
+    got = [list(o.outputs[0].token_ids) for o in outs]
+    assert got == want, (rank, got, want)       # same kernels in the same order: bit-identical to one GPU
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_pp2_engine_matches_single_gpu():
+    want = _single_gpu_tokens(2)
+    _launch(_pp_engine_worker, 2, want, timeout=240)
+
+
+def _dcp_engine_worker(rank, world, want):
+    os.environ["B200_FUSED_TP_COLLECTIVES"] = "0"
+    from vllm_metax_b200 import LLM, SamplingParams
+    from vllm_metax_b200 import _custom_ops as ops
+    from vllm_metax_b200.parallel import state as ps
+
+    llm = LLM(_pp_dcp_cfg(1), device="cuda", tensor_parallel_size=world, decode_context_parallel_size=world, block_size=64,
+              max_model_len=512, max_num_seqs=8, max_num_batched_tokens=128, num_gpu_blocks=64)
+    assert llm.engine.runner.dcp == world
+    outs = llm.generate(_pp_dcp_prompts(), SamplingParams(max_tokens=12, ignore_eos=True))
+    torch.cuda.synchronize()
+    ops.check_kernel_status(rank)
+    got = [list(o.outputs[0].token_ids) for o in outs]
+    toks = torch.tensor(got, device="cuda")
+    gathered = ps.get_tp_group().all_gather(toks[None], 0)
+    assert bool((gathered == toks[None]).all())                               # ranks in lock step
+    # other reduction order than one GPU (bf16): first tokens agree, the rest mostly
+    assert [g_[0] for g_ in got] == [w[0] for w in want], (got, want)
+    same = sum(a == b for g_, w in zip(got, want) for a, b in zip(g_, w))
+    assert same >= 0.75 * sum(len(w) for w in want), (got, want)
+    llm.engine.runner.graphs.clear()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_dcp2_engine_close_to_single_gpu():
+    want = _single_gpu_tokens(1)
+    _launch(_dcp_engine_worker, 2, want, timeout=240)
