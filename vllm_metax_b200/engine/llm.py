@@ -218,6 +218,11 @@ def _resolve_model(model: Union[str, dict, ModelConfig], **overrides) -> tuple[M
     elif isinstance(model, dict):
         mc = ModelConfig.from_hf_dict(model, **overrides) if "hidden_size" in model and "architectures" in model \
             else ModelConfig(**{**model, **overrides})
+    elif isinstance(model, str) and model.endswith(".gguf"):       # llama.cpp single-file checkpoint
+        from .gguf import config_from_gguf, read_gguf
+
+        meta, infos, _ = read_gguf(model)
+        mc = ModelConfig.from_hf_dict(config_from_gguf(meta, infos), model_path=model, **overrides)
     else:
         mc = ModelConfig.from_pretrained(model, **overrides)
         try:

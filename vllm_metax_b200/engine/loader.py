@@ -85,6 +85,11 @@ def hash_name(name: str) -> int:
 
 
 def iter_safetensors(path: str) -> Iterator[tuple[str, torch.Tensor]]:
+    if path.endswith(".gguf"):
+        from .gguf import iter_gguf
+
+        yield from iter_gguf(path, torch.float32)       # parameters cast on copy
+        return
     from safetensors import safe_open
 
     index = os.path.join(path, "model.safetensors.index.json")

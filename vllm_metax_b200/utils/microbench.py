@@ -175,9 +175,42 @@ def bench_quant(t, M: int, N: int, K: int) -> dict:
     return res
 
 
+def bench_linear_attention(t: Timer) -> dict:
+    """Qwen3-Next linear-attention layer shapes (16 k heads, 32 v heads of 128; convolution over 8192 channels, width 4):
+    one prefill chunk of 8192 tokens in 8 sequences and a decode step of 256 sequences."""
+    from ..ops import gdn
+
+    Hk, Hv, D, K = 16, 32, 128, 4
+    C = 2 * Hk * D + Hv * D
+    out = {}
+    for name, lens in (("prefill_8x1024", [1024] * 8), ("decode_256", [1] * 256)):
+        T, B = sum(lens), len(lens)
+        qsl = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+        idx = torch.arange(B, dtype=torch.int32, device=DEV)
+        has = torch.ones(B, dtype=torch.int32, device=DEV)
+        x = torch.randn(T, C, device=DEV, dtype=torch.bfloat16)
+        w = torch.randn(C, K, device=DEV, dtype=torch.bfloat16) * 0.3
+        cstate = torch.zeros(B, K - 1, C, device=DEV, dtype=torch.bfloat16)
+        ms = t(lambda: gdn.causal_conv1d(x, w, None, cstate, qsl, idx, has))
+        byt = 2 * T * C * 2 + 2 * B * (K - 1) * C * 2
+        out[f"causal_conv1d_{name}"] = {"ms": round(ms, 4), "gbs": round(byt / ms / 1e6, 1)}
+        q = torch.randn(T, Hk, D, device=DEV, dtype=torch.bfloat16)
+        k = torch.randn(T, Hk, D, device=DEV, dtype=torch.bfloat16)
+        v = torch.randn(T, Hv, D, device=DEV, dtype=torch.bfloat16)
+        g = -torch.rand(T, Hv, device=DEV) * 0.3
+        beta = torch.rand(T, Hv, device=DEV)
+        state = torch.zeros(B, Hv, D, D, device=DEV, dtype=torch.float32)
+        ms = t(lambda: gdn.gated_delta_rule(q, k, v, g, beta, qsl, state, idx, has))
+        byt = 2 * B * Hv * D * D * 4 + T * (2 * Hk + 2 * Hv) * D * 2
+        # per token and v head: decay (D*D), S^T k (2 D*D), rank-1 update (2 D*D), S^T q (2 D*D)
+        out[f"gated_delta_rule_{name}"] = {"ms": round(ms, 4), "gbs": round(byt / ms / 1e6, 1),
+                                            "gflops": round(7 * T * Hv * D * D / ms / 1e6, 1)}
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "gemm", "prefill", "decode", "elementwise", "quant"])
+    ap.add_argument("--op", default="all", choices=["all", "gemm", "prefill", "decode", "elementwise", "quant", "linear_attention"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
@@ -208,6 +241,8 @@ def main() -> None:
         res["attn_prefill_8x1024"] = bench_prefill(t, 8, 1024, 32, 8, 128, 128, a.compare)
     if a.op in ("all", "decode"):
         res[f"attn_decode_{a.batch}x{a.seq}_{a.kv}"] = bench_decode(t, a.batch, a.seq, 32, 8, 128, 128, a.kv, a.compare)
+    if a.op == "linear_attention":
+        res.update(bench_linear_attention(t))
     if a.op in ("all", "elementwise"):
         for T in (8192, 256):
             for k, v in bench_elementwise(t, T, H, I).items():
