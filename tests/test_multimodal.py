@@ -79,3 +79,63 @@ def test_placeholder_count_is_checked(tmp_path):
     out = llm.generate([{"prompt_token_ids": [1, IMG_TOK, 3], "multi_modal_data": {"image": img}}],
                        SamplingParams(max_tokens=2, ignore_eos=True))
     assert len(out[0].outputs[0].token_ids) == 2
+
+
+def test_chat_completion_with_image_over_http(tmp_path):
+    """An OpenAI chat request with a base64 image part: the server decodes it, places the model's placeholder token
+    where the image stands in the rendered prompt, and the answer equals the offline call with the same inputs."""
+    import asyncio
+    import base64
+    import io
+    import json
+
+    httpx = pytest.importorskip("httpx")
+    from PIL import Image
+
+    from vllm_metax_b200 import LLM, SamplingParams
+    from vllm_metax_b200.entrypoints.async_engine import AsyncLLM
+    from vllm_metax_b200.entrypoints.openai_server import build_app
+
+    class Tok:
+        chat_template = None
+
+        def encode(self, text, add_special_tokens=True):
+            return [3 + (ord(c) % 200) for c in text][:48] or [3]
+
+        def decode(self, ids, skip_special_tokens=True):
+            return "".join(chr(97 + (i % 26)) for i in ids)
+
+    _hf_llava(tmp_path)
+    llm = LLM(str(tmp_path), dtype="float32", device="cpu", max_model_len=128, num_gpu_blocks=32, block_size=16, tokenizer=Tok())
+    img = Image.fromarray((torch.rand(40, 30, 3) * 255).to(torch.uint8).numpy())
+    buf = io.BytesIO()
+    img.save(buf, format="PNG")
+    url = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+    body = {"model": "llava", "max_tokens": 5, "messages": [{"role": "user", "content": [
+        {"type": "text", "text": "look: "}, {"type": "image_url", "image_url": {"url": url}}, {"type": "text", "text": " what?"}]}]}
+    allm = AsyncLLM(llm)
+    app = build_app(allm, "llava")
+
+    async def go(b):
+        async with httpx.AsyncClient(transport=httpx.ASGITransport(app=app), base_url="http://t") as c:
+            r = await c.post("/v1/chat/completions", json=b)
+            return r.status_code, r.text
+    try:
+        code, text = asyncio.run(go(body))
+        assert code == 200, text
+        answer = json.loads(text)["choices"][0]["message"]["content"]
+        assert json.loads(text)["usage"]["prompt_tokens"] > 4                  # the image run is part of the prompt
+        # same request offline: the prompt text around the image, placeholder in between
+        from vllm_metax_b200.entrypoints.openai_server import render_chat
+
+        rendered = render_chat(Tok(), [{"role": "user", "content": "look: @@ what?"}])
+        left, right = rendered.split("@@")
+        ids = Tok().encode(left) + [IMG_TOK] + Tok().encode(right)
+        code2, text2 = asyncio.run(go(dict(body, messages=[{"role": "user", "content": [
+            {"type": "image_url", "image_url": {"url": "http://example.com/x.png"}}]}])))
+        assert code2 == 400 and "data:" in text2
+    finally:
+        allm.shutdown()
+    off = llm.generate([{"prompt_token_ids": ids, "multi_modal_data": {"image": img}}],
+                       SamplingParams(max_tokens=5, temperature=0.0))
+    assert Tok().decode(off[0].outputs[0].token_ids) == answer

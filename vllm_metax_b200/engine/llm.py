@@ -104,6 +104,8 @@ class LLMEngine:
             raise EngineDeadError(str(self.dead))
         rid = request_id or f"req-{next(self._ids)}"
         mm = None
+        if multi_modal_data is None and params is not None:
+            multi_modal_data = getattr(params, "_multi_modal_data", None)   # set by front ends that only pass params through
         if multi_modal_data:
             prompt_token_ids, mm = self.runner.encode_multimodal(list(prompt_token_ids), multi_modal_data)
         if params is not None and (params.constrained or params.guided_regex is not None or params.guided_json is not None):

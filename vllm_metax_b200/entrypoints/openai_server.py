@@ -114,6 +114,56 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
             raise ValueError("text prompt given but the server has no tokenizer; send token ids")
         return tok.encode(prompt), prompt
 
+    IMAGE_MARK = "<|b200-image|>"
+
+    def split_images(messages: list) -> tuple[list, list]:
+        """OpenAI content parts -> (messages with plain-text content where every image is ``IMAGE_MARK``, PIL images).
+        Images come as ``data:`` URLs (base64); remote URLs are refused - the server fetches nothing."""
+        import base64
+        import io
+
+        images, flat = [], []
+        for m in messages:
+            c = m.get("content")
+            if not isinstance(c, list):
+                flat.append(m)
+                continue
+            text = ""
+            for part in c:
+                kind = part.get("type")
+                if kind == "text":
+                    text += part.get("text", "")
+                elif kind == "image_url":
+                    url = (part.get("image_url") or {}).get("url", "")
+                    if not url.startswith("data:") or "," not in url:
+                        raise ValueError("image_url must be a data: URL (base64); remote images are not fetched")
+                    from PIL import Image
+
+                    images.append(Image.open(io.BytesIO(base64.b64decode(url.split(",", 1)[1]))).convert("RGB"))
+                    text += IMAGE_MARK
+                else:
+                    raise ValueError(f"unsupported content part type {kind!r}")
+            flat.append(dict(m, content=text))
+        return flat, images
+
+    def encode_with_images(text: str, n_images: int) -> list[int]:
+        """Tokenise around the image marks and put the model's placeholder id where each image goes."""
+        model = llm.engine.runner.model
+        if not getattr(model, "is_multimodal", False):
+            raise ValueError("this model takes no image inputs")
+        pieces = text.split(IMAGE_MARK)
+        if len(pieces) != n_images + 1:
+            raise ValueError("image marks were altered by the chat template")
+        ids = list(tok.encode(pieces[0]))
+        for piece in pieces[1:]:
+            ids.append(model.image_token_id)
+            if piece:
+                try:
+                    ids.extend(tok.encode(piece, add_special_tokens=False))
+                except TypeError:
+                    ids.extend(tok.encode(piece))
+        return ids
+
     def err(status: int, msg: str, typ: str = "invalid_request_error"):
         return JSONResponse({"error": {"message": msg, "type": typ, "code": status}}, status_code=status)
 
@@ -186,12 +236,19 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
 
     async def serve(body: dict, chat: bool, traceparent: Optional[str] = None):
         try:
+            images = []
             if chat:
-                text = render_chat(tok, body.get("messages") or [])
-                ids, prompt = encode(text)
+                messages, images = split_images(body.get("messages") or [])
+                text = render_chat(tok, messages)
+                if images:
+                    ids, prompt = encode_with_images(text, len(images)), text
+                else:
+                    ids, prompt = encode(text)
             else:
                 ids, prompt = encode(body.get("prompt", ""))
             params = sampling_from_request(body, default_max_tokens=16 if not chat else 256)
+            if images:
+                params._multi_modal_data = {"image": images}
             model_name = body.get("model")
             if model_name in lora_modules:
                 params._lora_request = lora_modules[model_name]
