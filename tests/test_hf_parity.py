@@ -286,3 +286,26 @@ def test_qwen3_next_state_carry_across_chunks_and_batches(tmp_path):
                                pad_token_id=0)[0, len(ids):].tolist()
         assert list(o.outputs[0].token_ids) == want
     assert not llm.engine.runner.state_slots and len(llm.engine.runner.free_state_slots) == 2
+
+
+def test_qwen3_next_recomputes_state_after_preemption(tmp_path):
+    """With too few KV blocks for the batch a request is preempted and later re-computed from scratch; its recurrent
+    state must restart from zero in a fresh slot."""
+    from vllm_metax_b200 import LLM, SamplingParams
+
+    cfg_cls, model_cls, kw = CASES["qwen3_next_hybrid"]
+    torch.manual_seed(4)
+    hf = getattr(tf, model_cls)(getattr(tf, cfg_cls)(**kw)).eval().float()
+    hf.save_pretrained(str(tmp_path))
+    llm = LLM(str(tmp_path), dtype="float32", device="cpu", max_model_len=64, num_gpu_blocks=7, block_size=8,
+              max_num_batched_tokens=32, max_num_seqs=3)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (14, 15, 13)]
+    outs = llm.generate(prompts, SamplingParams(max_tokens=12, temperature=0.0, ignore_eos=True))
+    assert llm.engine.scheduler.num_preemptions > 0
+    for ids, o in zip(prompts, outs):
+        with torch.no_grad():
+            want = hf.generate(torch.tensor([ids]), max_new_tokens=12, do_sample=False, eos_token_id=None,
+                               pad_token_id=0)[0, len(ids):].tolist()
+        assert list(o.outputs[0].token_ids) == want
+    assert not llm.engine.runner.state_slots

@@ -139,3 +139,32 @@ def test_chat_completion_with_image_over_http(tmp_path):
     off = llm.generate([{"prompt_token_ids": ids, "multi_modal_data": {"image": img}}],
                        SamplingParams(max_tokens=5, temperature=0.0))
     assert Tok().decode(off[0].outputs[0].token_ids) == answer
+
+
+def test_internvl_matches_hugging_face(tmp_path):
+    """InternViT tower (layer scale, no pre-norm) + pixel-shuffle + LayerNorm projector over a Qwen2 decoder."""
+    from vllm_metax_b200 import LLM, SamplingParams
+
+    torch.manual_seed(0)
+    vc = tf.InternVLVisionConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                                 image_size=[56, 56], patch_size=[14, 14])
+    tc = tf.Qwen2Config(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2, max_position_embeddings=256)
+    c = tf.InternVLConfig(vision_config=vc, text_config=tc, image_token_id=IMG_TOK, image_seq_length=4)
+    hf = tf.InternVLForConditionalGeneration(c).eval().float()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.dim() == 1:
+                p.add_(0.1 * torch.randn_like(p))
+            else:
+                p.mul_(3.0)
+    hf.save_pretrained(str(tmp_path))
+    llm = LLM(str(tmp_path), dtype="float32", device="cpu", max_model_len=128, num_gpu_blocks=32, block_size=16,
+              max_num_batched_tokens=6)
+    assert llm.engine.runner.model.tokens_per_image == 4            # 4 x 4 patches folded 2 x 2
+    g = torch.Generator().manual_seed(2)
+    img = torch.randn(1, 3, 56, 56, generator=g)
+    ids = [5, 9] + [IMG_TOK] * 4 + [33, 100, 7, 8, 200, 31, 2]
+    out = llm.generate([{"prompt_token_ids": [5, 9, IMG_TOK, 33, 100, 7, 8, 200, 31, 2], "multi_modal_data": {"image": img}}],
+                       SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True))
+    assert list(out[0].outputs[0].token_ids) == _want(hf, ids, img)

@@ -746,9 +746,10 @@ def scaled_int8_quant(x, scale=None, azp=None, symmetric: bool = True):
 
 def merge_attn_states(prefix_out, prefix_lse, suffix_out, suffix_lse, want_lse: bool = False):
     if _use_cuda(prefix_out):
+        prefix_out, prefix_lse = prefix_out.contiguous(), prefix_lse.contiguous()     # (empty_like keeps odd strides)
         out = torch.empty_like(prefix_out)
         lse = torch.empty_like(prefix_lse) if want_lse else None
-        torch.ops.b200.merge_attn_states(out, lse, prefix_out.contiguous(), prefix_lse.contiguous(),
+        torch.ops.b200.merge_attn_states(out, lse, prefix_out, prefix_lse,
                                          suffix_out.contiguous(), suffix_lse.contiguous())
         return (out, lse) if want_lse else out
     out, lse = ref.merge_attn_states(prefix_out, prefix_lse, suffix_out, suffix_lse)

@@ -202,7 +202,8 @@ class ModelConfig:
             tie_word_embeddings=d.get("tie_word_embeddings", False),
             hidden_act=d.get("hidden_act", "silu"),
             attention_bias=bool(d.get("attention_bias", False) or d.get("bias", False) or d.get("add_qkv_bias", False)
-                                or d.get("qkv_bias", False) or ("Qwen2" in arch) or arch == "QWenLMHeadModel"),
+                                or d.get("qkv_bias", False) or ("Qwen2" in arch) or arch == "QWenLMHeadModel"
+                                or d.get("model_type") == "qwen2"),
             attention_out_bias=bool((d.get("attention_bias", False) and "Qwen" not in arch and "Glm" not in arch
                                      and "GLM" not in arch) or (d.get("bias", False) and "InternLM" in arch)),
             mlp_bias=d.get("mlp_bias", False),

@@ -41,6 +41,7 @@ _MODELS: dict[str, tuple[str, str]] = {
     "ChatGLMModel": ("llama_family", "ChatGLMModel"),
     "ChatGLMForConditionalGeneration": ("llama_family", "ChatGLMModel"),
     "LlavaForConditionalGeneration": ("llava", "LlavaForConditionalGeneration"),
+    "InternVLForConditionalGeneration": ("internvl", "InternVLForConditionalGeneration"),
     "Qwen3NextForCausalLM": ("qwen3_next", "Qwen3NextForCausalLM"),
     "Glm4MoeForCausalLM": ("moe_family", "Glm4MoeForCausalLM"),
     "DeepseekForCausalLM": ("moe_family", "DeepseekForCausalLM"),

@@ -80,6 +80,7 @@ class ClipVisionTower(nn.Module):
 
 class LlavaForConditionalGeneration(nn.Module):
     is_multimodal = True
+    qkv_pattern = r"(vision_tower\.layers\.\d+)\.self_attn\.([qkv])_proj\.(weight|bias)$"
     renames = [(r"^model\.language_model\.model\.", "language_model.model."),
                (r"^model\.language_model\.(?!model\.|lm_head\.)", "language_model.model."),
                (r"^lm_head\.", "language_model.lm_head."),
@@ -166,12 +167,12 @@ class LlavaForConditionalGeneration(nn.Module):
             if name.startswith("language_model."):
                 text.append((name[len("language_model."):], w))
                 continue
-            m = re.match(r"(vision_tower\.layers\.\d+)\.self_attn\.([qkv])_proj\.(weight|bias)$", name)
+            m = re.match(self.qkv_pattern, name)
             if m:                                   # q, k, v of a vision layer are fused into one GEMM
                 if int(m.group(1).rsplit(".", 1)[1]) < len(self.vision_tower.layers):
                     qkv.setdefault((m.group(1), m.group(3)), {})[m.group(2)] = w
                 continue
-            if name == "vision_tower.patch_embedding":
+            if name in ("vision_tower.patch_embedding", "vision_tower.patch_weight"):
                 w = w.reshape(w.shape[0], -1)
             if name in params:
                 params[name].data.copy_(w.reshape(params[name].shape))
@@ -180,5 +181,10 @@ class LlavaForConditionalGeneration(nn.Module):
             target = f"{layer}.qkv_proj.{kind}"
             params[target].data.copy_(torch.cat([parts["q"], parts["k"], parts["v"]], 0))
             loaded.add(target)
-        loaded |= {f"language_model.{n}" for n in self.language_model.load_weights(text)}
+        got = self.language_model.load_weights(text)
+        lm = self.language_model
+        if "lm_head.weight" not in got and getattr(lm, "lm_head", None) is not None and lm.lm_head is not lm.model.embed_tokens:
+            # wrappers that tie the head at the top level save no lm_head tensor whatever the decoder's own flag says
+            lm.lm_head.weight.data.copy_(lm.model.embed_tokens.weight.data)
+        loaded |= {f"language_model.{n}" for n in got}
         return loaded
