@@ -378,15 +378,19 @@ def test_pp2_engine_matches_single_gpu():
     _launch(_pp_engine_worker, 2, want, timeout=240)
 
 
-def _dcp_engine_worker(rank, world, want):
+def _dcp_engine_worker(rank, world, dcp, path):
+    """TP2 with one KV head (replicated on both ranks): with dcp = 1 the tokens are written to ``path``; with dcp = 2
+    (same sharded weights, the cache split by position) they are compared with that file."""
     os.environ["B200_FUSED_TP_COLLECTIVES"] = "0"
+    import json
+
     from vllm_metax_b200 import LLM, SamplingParams
     from vllm_metax_b200 import _custom_ops as ops
     from vllm_metax_b200.parallel import state as ps
 
-    llm = LLM(_pp_dcp_cfg(1), device="cuda", tensor_parallel_size=world, decode_context_parallel_size=world, block_size=64,
+    llm = LLM(_pp_dcp_cfg(1), device="cuda", tensor_parallel_size=world, decode_context_parallel_size=dcp, block_size=64,
               max_model_len=512, max_num_seqs=8, max_num_batched_tokens=128, num_gpu_blocks=64)
-    assert llm.engine.runner.dcp == world
+    assert llm.engine.runner.dcp == dcp
     outs = llm.generate(_pp_dcp_prompts(), SamplingParams(max_tokens=12, ignore_eos=True))
     torch.cuda.synchronize()
     ops.check_kernel_status(rank)
@@ -394,14 +398,21 @@ def _dcp_engine_worker(rank, world, want):
     toks = torch.tensor(got, device="cuda")
     gathered = ps.get_tp_group().all_gather(toks[None], 0)
     assert bool((gathered == toks[None]).all())                               # ranks in lock step
-    # other reduction order than one GPU (bf16): first tokens agree, the rest mostly
+    llm.engine.runner.graphs.clear()
+    if dcp == 1:
+        if rank == 0:
+            with open(path, "w") as f:
+                json.dump(got, f)
+        return
+    want = json.load(open(path))
+    # other reduction order than the unsplit cache (bf16): first tokens agree, the rest mostly
     assert [g_[0] for g_ in got] == [w[0] for w in want], (got, want)
     same = sum(a == b for g_, w in zip(got, want) for a, b in zip(g_, w))
     assert same >= 0.75 * sum(len(w) for w in want), (got, want)
-    llm.engine.runner.graphs.clear()
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-def test_dcp2_engine_close_to_single_gpu():
-    want = _single_gpu_tokens(1)
-    _launch(_dcp_engine_worker, 2, want, timeout=240)
+def test_dcp2_engine_close_to_unsplit_cache(tmp_path):
+    path = str(tmp_path / "tp2_tokens.json")
+    _launch(_dcp_engine_worker, 2, 1, path, timeout=240)
+    _launch(_dcp_engine_worker, 2, 2, path, timeout=240)

@@ -47,6 +47,12 @@ class LLMEngine:
 
         self.spec_config = SpeculativeConfig.from_dict((cfg.additional_config or {}).get("speculative_config"))
         self.proposer = make_proposer(self.spec_config, self)
+        if self.proposer is not None:
+            from ..parallel import state as ps
+
+            if ps.get_pp_group().world_size > 1 or self.runner.dcp > 1 or self.runner.state_slots is not None:
+                raise ValueError("speculative decoding is not combined with pipeline parallel, decode context parallel "
+                                 "or recurrent-state (hybrid) models")
         from ..parallel.liveness import RankLiveness
 
         self.liveness = RankLiveness.from_default_group()     # None in a single-process engine
