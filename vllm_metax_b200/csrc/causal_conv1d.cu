@@ -8,8 +8,9 @@
 // state[slot, K-1, C] (oldest first) and is rewritten by a second kernel once the outputs are done, so a decode step
 // (one token) and a prefill chunk (thousands) go through the same two launches.
 //
-// Grid of the forward kernel: (C / 128, ceil(T / kTokPerCta)); threads along channels so every load is coalesced; each
-// CTA locates its first token's sequence by binary search and walks forward across sequence boundaries.
+// Grid of the forward kernel: (C / 128, ceil(T / kTokPerCta)); threads along channels so every load is coalesced; the
+// first 32 threads of a CTA look up each token's sequence (binary search) into shared memory, so the token loop has
+// no data-dependent control flow beyond uniform branches and can be unrolled.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -35,27 +36,40 @@ __global__ void conv1d_fwd_kernel(T* __restrict__ out, const T* __restrict__ x, 
                                   const int* __restrict__ qsl, const int* __restrict__ state_idx,
                                   const int* __restrict__ has_init, int batch, int tokens, int channels, int K,
                                   int silu) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  // per token of this CTA's chunk: first token of its sequence, and the carry slot to read (-1: zeros)
+  __shared__ int s_start[kTokPerCta];
+  __shared__ int s_slot[kTokPerCta];
   const int t0 = blockIdx.y * kTokPerCta;
-  if (c >= channels || t0 >= tokens) return;
   const int t1 = min(tokens, t0 + kTokPerCta);
+  if (threadIdx.x < kTokPerCta) {
+    const int t = t0 + threadIdx.x;
+    int start = -1, slot = -1;
+    if (t < t1 && t < qsl[batch]) {
+      int lo = 0, hi = batch - 1;               // largest s with qsl[s] <= t
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (qsl[mid] <= t) lo = mid; else hi = mid - 1;
+      }
+      start = qsl[lo];
+      const int sl = state_idx ? state_idx[lo] : -1;
+      if (sl >= 0 && state != nullptr && (has_init == nullptr || has_init[lo] != 0)) slot = sl;
+    }
+    s_start[threadIdx.x] = start;               // -1: padding row after the last sequence, nothing is written
+    s_slot[threadIdx.x] = slot;
+  }
+  __syncthreads();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
   float wr[kMaxK];
 #pragma unroll
   for (int j = 0; j < kMaxK; ++j) wr[j] = j < K ? ld(w + (int64_t)c * K + j) : 0.f;
   const float b = bias ? ld(bias + c) : 0.f;
-  // sequence of the first token: largest s with qsl[s] <= t0
-  int lo = 0, hi = batch - 1;
-  while (lo < hi) {
-    const int mid = (lo + hi + 1) >> 1;
-    if (qsl[mid] <= t0) lo = mid; else hi = mid - 1;
-  }
-  int s = lo;
-  for (int t = t0; t < t1; ++t) {
-    while (s + 1 < batch && qsl[s + 1] <= t) ++s;
-    if (t >= qsl[batch]) break;                     // padding rows after the last sequence
-    const int start = qsl[s];
-    const int slot = state_idx ? state_idx[s] : -1;
-    const bool carry = slot >= 0 && state != nullptr && (has_init == nullptr || has_init[s] != 0);
+#pragma unroll 4
+  for (int i = 0; i < kTokPerCta; ++i) {
+    const int t = t0 + i;
+    const int start = s_start[i];
+    if (t >= t1 || start < 0) continue;
+    const int slot = s_slot[i];
     float acc = b;
 #pragma unroll
     for (int j = 0; j < kMaxK; ++j) {
@@ -64,7 +78,7 @@ __global__ void conv1d_fwd_kernel(T* __restrict__ out, const T* __restrict__ x, 
       float v = 0.f;
       if (src >= start) {
         v = ld(x + (int64_t)src * x_stride + c);
-      } else if (carry) {
+      } else if (slot >= 0) {
         const int back = start - src;               // 1 .. K-1 tokens before the sequence's first new token
         v = ld(state + ((int64_t)slot * (K - 1) + (K - 1 - back)) * channels + c);
       }
