@@ -48,6 +48,9 @@ CASES = {
                                shared_expert_intermediate_size=64, num_experts=8, num_experts_per_tok=2,
                                linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=16,
                                linear_value_head_dim=16, linear_conv_kernel_dim=4, norm_topk_prob=True)),
+    "mamba": ("MambaConfig", "MambaForCausalLM",
+              dict(vocab_size=512, hidden_size=64, state_size=8, num_hidden_layers=2, conv_kernel=4, expand=2,
+                   time_step_rank=8, pad_token_id=0, bos_token_id=1, eos_token_id=2)),
     "neox": ("GPTNeoXConfig", "GPTNeoXForCausalLM", dict(BASE, intermediate_size=256)),
     "neox_sequential": ("GPTNeoXConfig", "GPTNeoXForCausalLM",
                         dict(BASE, intermediate_size=256, use_parallel_residual=False, rotary_pct=0.5)),

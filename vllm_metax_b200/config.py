@@ -39,6 +39,8 @@ def _canonical_hf_keys(d: dict) -> dict:
     arch = (d.get("architectures") or [""])[0]
     alias("hidden_size", "n_embd", "d_model")
     alias("num_attention_heads", "n_head", "n_heads")
+    if d.get("num_attention_heads") is None and d.get("model_type") == "mamba":
+        d["num_attention_heads"] = 1                          # attention-free
     alias("num_hidden_layers", "n_layer", "n_layers", "num_layers")
     alias("rms_norm_eps", "layer_norm_eps", "layer_norm_epsilon", "layernorm_epsilon")
     alias("max_position_embeddings", "n_positions", "max_seq_len", "seq_length")

@@ -171,7 +171,7 @@ class ModelRunner:
         torch.cuda.synchronize()
         free, total = torch.cuda.mem_get_info(self.device)
         budget = free - int(total * (1.0 - c.gpu_memory_utilization)) - (6 << 30)  # activation head-room
-        n = max(16, budget // self.kv_bytes_per_block())
+        n = max(16, budget // max(1, self.kv_bytes_per_block()))          # attention-free models: blocks only meter length
         want = self.max_seqs * self.max_blocks_per_seq
         return int(min(n, max(want, 64)))
 
