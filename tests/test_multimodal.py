@@ -168,3 +168,61 @@ def test_internvl_matches_hugging_face(tmp_path):
     out = llm.generate([{"prompt_token_ids": [5, 9, IMG_TOK, 33, 100, 7, 8, 200, 31, 2], "multi_modal_data": {"image": img}}],
                        SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True))
     assert list(out[0].outputs[0].token_ids) == _want(hf, ids, img)
+
+
+def test_internvl_chat_original_export(tmp_path):
+    """The original InternVL tensor names (fused ``attn.qkv``, ``ls1`` / ``ls2``, ``mlp1.*``, ``llm_config``) load onto
+    the same graph: a Hugging Face InternVL model rewritten into that dialect must give the Hugging Face answer."""
+    import json
+
+    from safetensors.torch import save_file
+
+    from vllm_metax_b200 import LLM, SamplingParams
+
+    torch.manual_seed(3)
+    vc = tf.InternVLVisionConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                                 image_size=[56, 56], patch_size=[14, 14], attention_bias=True)
+    tc = tf.Qwen2Config(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2, max_position_embeddings=256, tie_word_embeddings=False)
+    hf = tf.InternVLForConditionalGeneration(tf.InternVLConfig(vision_config=vc, text_config=tc, image_token_id=IMG_TOK,
+                                                               image_seq_length=4, tie_word_embeddings=False)).eval().float()
+    with torch.no_grad():
+        for p in hf.parameters():
+            p.add_(0.1 * torch.randn_like(p)) if p.dim() == 1 else p.mul_(3.0)
+    sd, out = hf.state_dict(), {}
+    for k, v in sd.items():
+        if k.startswith("model.language_model."):
+            out["language_model.model." + k[len("model.language_model."):]] = v
+        elif k == "lm_head.weight":
+            out["language_model.lm_head.weight"] = v
+        elif k.startswith("model.multi_modal_projector."):
+            n = k[len("model.multi_modal_projector."):]
+            out["mlp1." + n.replace("layer_norm", "0").replace("linear_1", "1").replace("linear_2", "3")] = v
+        elif k.startswith("model.vision_tower.embeddings."):
+            n = k.rsplit(".", 1)[1] if "patch_embeddings" in k else k[len("model.vision_tower.embeddings."):]
+            name = {"cls_token": "class_embedding", "position_embeddings": "position_embedding", "weight": "patch_embedding.weight",
+                    "bias": "patch_embedding.bias"}[n]
+            out["vision_model.embeddings." + name] = v
+    for i in range(2):
+        pre, dst = f"model.vision_tower.encoder.layer.{i}.", f"vision_model.encoder.layers.{i}."
+        for kind in ("weight", "bias"):
+            out[dst + f"attn.qkv.{kind}"] = torch.cat([sd[pre + f"attention.{x}_proj.{kind}"] for x in "qkv"], 0)
+            out[dst + f"attn.proj.{kind}"] = sd[pre + f"attention.projection_layer.{kind}"]
+            out[dst + f"norm1.{kind}"] = sd[pre + f"layernorm_before.{kind}"]
+            out[dst + f"norm2.{kind}"] = sd[pre + f"layernorm_after.{kind}"]
+            out[dst + f"mlp.fc1.{kind}"] = sd[pre + f"mlp.fc1.{kind}"]
+            out[dst + f"mlp.fc2.{kind}"] = sd[pre + f"mlp.fc2.{kind}"]
+        out[dst + "ls1"], out[dst + "ls2"] = sd[pre + "lambda_1"], sd[pre + "lambda_2"]
+    save_file({k: v.contiguous() for k, v in out.items()}, str(tmp_path / "model.safetensors"))
+    cfg = {"architectures": ["InternVLChatModel"], "downsample_ratio": 0.5, "select_layer": -1, "img_context_token_id": IMG_TOK,
+           "vision_config": {"hidden_size": 64, "intermediate_size": 128, "num_hidden_layers": 2, "num_attention_heads": 4,
+                             "image_size": 56, "patch_size": 14, "qkv_bias": True, "hidden_act": "gelu", "layer_norm_eps": 1e-6,
+                             "norm_type": "layer_norm"},
+           "llm_config": dict(tc.to_dict(), architectures=["Qwen2ForCausalLM"]), "torch_dtype": "float32"}
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    llm = LLM(str(tmp_path), dtype="float32", device="cpu", max_model_len=128, num_gpu_blocks=32, block_size=16)
+    img = torch.randn(1, 3, 56, 56, generator=torch.Generator().manual_seed(4))
+    ids = [5, 9] + [IMG_TOK] * 4 + [33, 100, 7, 8, 200, 31, 2]
+    got = llm.generate([{"prompt_token_ids": ids, "multi_modal_data": {"image": img}}],
+                       SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True))
+    assert list(got[0].outputs[0].token_ids) == _want(hf, ids, img)

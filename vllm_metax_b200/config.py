@@ -176,6 +176,9 @@ class ModelConfig:
     @classmethod
     def from_hf_dict(cls, d: dict, **overrides: Any) -> "ModelConfig":
         raw = d
+        if isinstance(d.get("llm_config"), dict) and "text_config" not in d:      # InternVL's original export
+            d = dict(d, text_config=d["llm_config"])
+            raw = d
         if isinstance(d.get("text_config"), dict):     # vision-language wrappers: the decoder's fields live one level down
             d = dict(d["text_config"], architectures=d.get("architectures"),
                      **{k: d[k] for k in ("quantization_config", "torch_dtype", "dtype") if k in d and k not in d["text_config"]})

@@ -42,6 +42,7 @@ _MODELS: dict[str, tuple[str, str]] = {
     "ChatGLMForConditionalGeneration": ("llama_family", "ChatGLMModel"),
     "LlavaForConditionalGeneration": ("llava", "LlavaForConditionalGeneration"),
     "InternVLForConditionalGeneration": ("internvl", "InternVLForConditionalGeneration"),
+    "InternVLChatModel": ("internvl", "InternVLChatModel"),
     "MambaForCausalLM": ("mamba", "MambaForCausalLM"),
     "Qwen3NextForCausalLM": ("qwen3_next", "Qwen3NextForCausalLM"),
     "Glm4MoeForCausalLM": ("moe_family", "Glm4MoeForCausalLM"),

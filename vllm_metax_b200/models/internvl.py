@@ -143,3 +143,31 @@ class InternVLForConditionalGeneration(LlavaForConditionalGeneration):
         mean = torch.tensor([0.485, 0.456, 0.406]).view(3, 1, 1)
         std = torch.tensor([0.229, 0.224, 0.225]).view(3, 1, 1)
         return (x - mean) / std
+
+
+class InternVLChatModel(InternVLForConditionalGeneration):
+    """The original InternVL export (``vision_model.*`` with fused ``attn.qkv``, ``ls1`` / ``ls2``, ``mlp1.{0,1,3}``,
+    ``llm_config``): the same graph under other names.  The image-context token is a tokenizer entry there, so its id
+    comes from ``img_context_token_id`` in the config when present (default: ``<IMG_CONTEXT>`` of the Qwen2 tokenizer)."""
+    renames = [(r"^language_model\.lm_head\.", "language_model.lm_head."),
+               (r"^vision_model\.embeddings\.class_embedding$", "vision_tower.cls_token"),
+               (r"^vision_model\.embeddings\.position_embedding$", "vision_tower.position_embeddings"),
+               (r"^vision_model\.embeddings\.patch_embedding\.weight$", "vision_tower.patch_weight"),
+               (r"^vision_model\.embeddings\.patch_embedding\.bias$", "vision_tower.patch_bias"),
+               (r"^vision_model\.encoder\.layers\.", "vision_tower.layers."),
+               (r"\.attn\.qkv\.", ".qkv_proj."), (r"\.attn\.proj\.", ".projection_layer."),
+               (r"\.ls1$", ".lambda_1"), (r"\.ls2$", ".lambda_2"),
+               (r"\.norm1\.", ".layernorm_before."), (r"\.norm2\.", ".layernorm_after."), (r"\.mlp\.fc([12])\.", r".fc\1."),
+               (r"^mlp1\.0\.", "multi_modal_projector.layer_norm."), (r"^mlp1\.1\.", "multi_modal_projector.linear_1."),
+               (r"^mlp1\.3\.", "multi_modal_projector.linear_2.")]
+
+    def __init__(self, cfg: ModelConfig):
+        hf = cfg.hf_config
+        vc = dict(hf["vision_config"])
+        vc.setdefault("attention_bias", bool(vc.get("qkv_bias", True)))
+        vc.setdefault("use_qk_norm", bool(vc.get("qk_normalization", False)))
+        hf = dict(hf, vision_config=vc, vision_feature_layer=hf.get("select_layer", -1),
+                  image_token_id=hf.get("img_context_token_id", hf.get("image_token_id", 151667)))
+        hf.setdefault("text_config", hf.get("llm_config", {}))
+        cfg.hf_config = hf
+        super().__init__(cfg)
