@@ -52,18 +52,6 @@ struct PfSmem {
   static constexpr int kDyn = kTotal + 1024;
 };
 
-// MN-major SW128 descriptor: 64-element (128-byte) chunks along MN are `lbo_bytes` apart,
-// 8-row groups along K are 1024 bytes apart.
-__device__ __forceinline__ uint64_t make_smem_desc_sw128_mn(uint32_t smem_addr, uint32_t lbo_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-
 template <typename T, int DQK, int DV, int BN>
 __global__ void __launch_bounds__(320, 1)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,

@@ -77,6 +77,35 @@ void gemm(Tensor& out, const Tensor& a, const Tensor& w, const optional<Tensor>&
                        w.stride(0), out.stride(0), ldr, dtype16(a), cur_stream(), status_ptr(a), (int)epi);
     return;
   }
+  // stream-K over CTA pairs for skinny problems: decode batches and narrow tensor-parallel shards (force_bn 2000
+  // pins it).  Its scratch (partial tiles + arrival counters) is allocated once per device and stream-ordered
+  // use is assumed, like every other op of this library.
+  static const bool streamk_default = [] {
+    const char* e = std::getenv("B200_GEMM_STREAMK");
+    return e == nullptr || std::atoi(e) != 0;
+  }();
+  {
+    static int sms_k[64] = {};
+    const int dev = a.get_device();
+    if (sms_k[dev] == 0) cudaDeviceGetAttribute(&sms_k[dev], cudaDevAttrMultiProcessorCount, dev);
+    const int64_t tiles = ((M + 255) / 256) * (int64_t)((N + 255) / 256);
+    if (force_bn == 2000 || (force_bn == 0 && streamk_default && M <= 1024 && tiles <= 2 * sms_k[dev])) {
+      // leaked on purpose: destroying CUDA tensors from static destructors can outlive the allocator
+      static Tensor* ws = new Tensor[64];
+      static Tensor* counters = new Tensor[64];
+      if (!ws[dev].defined()) {
+        ws[dev] = torch::empty({(int64_t)(b200::gemm_streamk_workspace_bytes(sms_k[dev]) / 4)},
+                               a.options().dtype(at::kFloat));
+        counters[dev] = torch::zeros({2 * (int64_t)b200::gemm_streamk_max_tiles()}, a.options().dtype(at::kInt));
+      }
+      const int rc = b200::gemm_tn_streamk(a.data_ptr(), w.data_ptr(), out.data_ptr(), ptr(bias), ptr(residual), M, N,
+                                           K, a.stride(0), w.stride(0), out.stride(0), ldr, dtype16(a), cur_stream(),
+                                           status_ptr(a), (int)epi, ws[dev].data_ptr<float>(),
+                                           counters[dev].data_ptr<int>(), sms_k[dev]);
+      if (rc == 0) return;
+      TORCH_CHECK(force_bn != 2000, "gemm: shape outside the stream-K kernel's scratch");
+    }
+  }
   // cluster split-K for medium M with too few tiles to cover the GPU (force_bn 1002 / 1004 pins the split count)
   static const bool splitk_default = [] {
     const char* e = std::getenv("B200_GEMM_SPLITK");
@@ -329,8 +358,16 @@ void attention_prefill(Tensor& out, const Tensor& q, const Tensor& k_src, const 
   TORCH_CHECK(out.is_contiguous() && out.size(-1) == DV);
   TORCH_CHECK(q.stride(0) % 8 == 0, "q token stride must be a multiple of 8 elements");
   const c10::cuda::CUDAGuard guard(q.device());
-  const int rc = b200::attention_prefill(p, q.data_ptr(), q.stride(0), kptr, vptr, ks, vs, total_kv, DQK, DV,
-                                         dtype16(q), batch, max_q_len, cur_stream());
+  // B200_ATTN_PREFILL_SINGLE=1 selects the one-tile-per-CTA kernel (P through shared memory)
+  static const bool single_tile = [] {
+    const char* e = std::getenv("B200_ATTN_PREFILL_SINGLE");
+    return e != nullptr && std::atoi(e) != 0;
+  }();
+  const int rc = single_tile
+                     ? b200::attention_prefill(p, q.data_ptr(), q.stride(0), kptr, vptr, ks, vs, total_kv, DQK, DV,
+                                               dtype16(q), batch, max_q_len, cur_stream())
+                     : b200::attention_prefill_pp(p, q.data_ptr(), q.stride(0), kptr, vptr, ks, vs, total_kv, DQK, DV,
+                                                  dtype16(q), batch, max_q_len, cur_stream());
   TORCH_CHECK(rc == 0, "attention_prefill: unsupported head dims ", DQK, "/", DV);
 }
 

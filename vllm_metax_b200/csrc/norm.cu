@@ -67,6 +67,55 @@ __global__ void rms_norm_kernel(T* __restrict__ out, T* __restrict__ x, T* __res
     o[i] = from_f<T>(to_f(row[i]) * inv * (to_f(weight[i]) + wadd));
 }
 
+// Register-resident variant for rows of 128 * VPT vectors (hidden = 1024 * VPT elements): every thread issues
+// all of its 16-byte loads before the first use, keeps the row in registers between the two passes and writes
+// once; the only shared-memory traffic is the block reduction.
+template <typename T, bool ADD_RESIDUAL, int VPT>
+__global__ void __launch_bounds__(128)
+rms_norm_reg_kernel(T* __restrict__ out, T* __restrict__ x, T* __restrict__ residual, const T* __restrict__ weight,
+                    float eps, int hidden, int64_t x_stride, int64_t out_stride, int mode) {
+  __shared__ float red[32];
+  const int64_t t = blockIdx.x;
+  const uint4* xin = reinterpret_cast<const uint4*>(x + t * x_stride);
+  uint4* res = ADD_RESIDUAL ? reinterpret_cast<uint4*>(residual + t * (int64_t)hidden) : nullptr;
+  uint4 xv[VPT], rv[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) xv[i] = xin[threadIdx.x + i * 128];
+  if (ADD_RESIDUAL) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) rv[i] = res[threadIdx.x + i * 128];
+  }
+  float f[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    unpack8<T>(xv[i], f[i]);
+    if (ADD_RESIDUAL) {
+      float r[8];
+      unpack8<T>(rv[i], r);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[i][e] += r[e];
+      const uint4 packed = pack8<T>(f[i]);
+      res[threadIdx.x + i * 128] = packed;
+      unpack8<T>(packed, f[i]);  // the norm sees the rounded residual
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += f[i][e] * f[i][e];
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+  const float wadd = (mode & kNormGemma) ? 1.f : 0.f;
+  uint4* o = reinterpret_cast<uint4*>(out + t * out_stride);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    float w[8];
+    unpack8<T>(reinterpret_cast<const uint4*>(weight)[threadIdx.x + i * 128], w);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[i][e] = f[i][e] * inv * (w[e] + wadd);
+    o[threadIdx.x + i * 128] = pack8<T>(f[i]);
+  }
+}
+
 // Per-head RMSNorm over the last dim (head_dim <= 256): one warp per (token, head).
 template <typename T>
 __global__ void head_rms_norm_kernel(T* __restrict__ x, const T* __restrict__ weight, float eps, int num_rows,
@@ -179,6 +228,23 @@ static int norm_threads(int hidden, int tokens) {
 template <typename T>
 static void rms_norm_t(void* out, void* x, void* residual, const void* weight, float eps, int tokens, int hidden,
                        int64_t x_stride, int64_t out_stride, int mode, cudaStream_t stream) {
+  const bool vec_ok = hidden % 1024 == 0 && x_stride % 8 == 0 && out_stride % 8 == 0 && tokens >= 32 &&
+                      ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(x) |
+                        reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(weight)) & 15) == 0;
+  const int vpt = hidden / 1024;
+  if (vec_ok && (vpt == 1 || vpt == 2 || vpt == 4 || vpt == 8)) {
+#define REG(ADD, V)                                                                                                \
+  rms_norm_reg_kernel<T, ADD, V><<<tokens, 128, 0, stream>>>((T*)out, (T*)x, (T*)residual, (const T*)weight, eps,  \
+                                                             hidden, x_stride, out_stride, mode)
+#define REGV(ADD)                                                                                                  \
+  do {                                                                                                             \
+    if (vpt == 1) REG(ADD, 1); else if (vpt == 2) REG(ADD, 2); else if (vpt == 4) REG(ADD, 4); else REG(ADD, 8);   \
+  } while (0)
+    if (residual) REGV(true); else REGV(false);
+#undef REGV
+#undef REG
+    return;
+  }
   const int th = norm_threads(hidden, tokens);
   const size_t sm = (size_t)hidden * sizeof(T);
   if (residual)

@@ -70,6 +70,12 @@ struct MlaDecodeParams {
 // ---- gemm_tcgen05.cu
 void gemm_tn(const void* A, const void* W, void* C, const void* bias, const void* residual, int M, int N, int K,
              int lda, int ldw, int ldc, int ldr, int dtype, cudaStream_t stream, void* status, int force_bn, int epi);
+// gemm_streamk_tcgen05.cu: swap-AB CTA-pair stream-K for skinny problems (scratch supplied by the caller)
+size_t gemm_streamk_workspace_bytes(int sms);
+int gemm_streamk_max_tiles();
+int gemm_tn_streamk(const void* A, const void* W, void* C, const void* bias, const void* residual, int M, int N, int K,
+                    int lda, int ldw, int ldc, int ldr, int dtype, cudaStream_t stream, void* status, int epi,
+                    float* ws, int* counters, int sms);
 void gemm_tn_pair(const void* A, const void* W, void* C, const void* bias, const void* residual, int M, int N, int K,
                   int lda, int ldw, int ldc, int ldr, int dtype, cudaStream_t stream, void* status, int epi);
 // ---- gemm_splitk_tcgen05.cu
@@ -108,6 +114,10 @@ void act_and_mul_quant(void* out_q, float* scale_out, const float* scale_in, con
 int paged_attention_decode(const DecodeParams& p, int head_dim, int kv_kind, int dtype, int batch, int max_q_len,
                            cudaStream_t stream);
 int attention_prefill(const PrefillParams& p, const void* q, int64_t q_stride, const void* k_src, const void* v_src,
+                      int64_t k_tok_stride, int64_t v_tok_stride, int64_t total_kv, int dqk, int dv, int dtype,
+                      int batch, int max_q_len, cudaStream_t stream);
+// attn_prefill_pingpong.cu: two query tiles per CTA, P and O resident in TMEM
+int attention_prefill_pp(const PrefillParams& p, const void* q, int64_t q_stride, const void* k_src, const void* v_src,
                       int64_t k_tok_stride, int64_t v_tok_stride, int64_t total_kv, int dqk, int dv, int dtype,
                       int batch, int max_q_len, cudaStream_t stream);
 // ---- sampling.cu

@@ -137,12 +137,93 @@ rope_and_cache_kernel(const int64_t* __restrict__ positions, T* __restrict__ q, 
   }
 }
 
+// Vector path for the common serving case: NeoX pairing over the whole head (rot == head_dim), cache of the
+// activation dtype.  One thread owns the 16-byte vector at offset 8j of a head and its rotation partner at
+// head_dim/2 + 8j, so every load and store is a full 16-byte access and eight neighbouring threads cover a
+// 128-byte line; q and k are rotated in place, k and v go to their cache slot in the same pass.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_and_cache_vec_kernel(const int64_t* __restrict__ positions, T* __restrict__ q, T* __restrict__ k,
+                          const T* __restrict__ v, const float* __restrict__ cos_sin, int head_dim, int num_q,
+                          int num_kv, int64_t q_stride, int64_t k_stride, int64_t v_stride, int inverse,
+                          T* __restrict__ kv_cache, const int64_t* __restrict__ slot_mapping, int block_size,
+                          int64_t num_slots, int tokens, StatusWord* status) {
+  const int per_head = head_dim >> 4;                       // (vector, partner) items per head
+  const int heads_total = num_q + 2 * num_kv;
+  const int items = heads_total * per_head;
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= (int64_t)tokens * items) return;
+  const int t = (int)(gid / items);
+  const int it = (int)(gid % items);
+  const int h = it / per_head, j = it % per_head;
+  const int half = head_dim >> 1;
+  const bool is_q = h < num_q;
+  const bool is_k = !is_q && h < num_q + num_kv;
+  const int hh = is_q ? h : (is_k ? h - num_q : h - num_q - num_kv);
+  T* src = is_q ? q + t * q_stride + (int64_t)hh * head_dim
+                : (is_k ? k + t * k_stride + (int64_t)hh * head_dim
+                        : const_cast<T*>(v) + t * v_stride + (int64_t)hh * head_dim);
+  uint4 a = *reinterpret_cast<const uint4*>(src + 8 * j);
+  uint4 b = *reinterpret_cast<const uint4*>(src + half + 8 * j);
+  if (is_q || is_k) {
+    const float* cs = cos_sin + positions[t] * (int64_t)head_dim;
+    const float4 c0 = *reinterpret_cast<const float4*>(cs + 8 * j), c1 = *reinterpret_cast<const float4*>(cs + 8 * j + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(cs + half + 8 * j),
+                 s1 = *reinterpret_cast<const float4*>(cs + half + 8 * j + 4);
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    float x1[8], x2[8], o1[8], o2[8];
+    unpack8<T>(a, x1);
+    unpack8<T>(b, x2);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float sg = inverse ? -sn[i] : sn[i];
+      o1[i] = x1[i] * c[i] - x2[i] * sg;
+      o2[i] = x2[i] * c[i] + x1[i] * sg;
+    }
+    a = pack8<T>(o1);
+    b = pack8<T>(o2);
+    *reinterpret_cast<uint4*>(src + 8 * j) = a;
+    *reinterpret_cast<uint4*>(src + half + 8 * j) = b;
+  }
+  if (is_q || kv_cache == nullptr) return;
+  const int64_t slot = slot_mapping[t];
+  if (slot < 0) return;
+  if (slot >= num_slots) {
+    report_status(status, kBadIndex, 10, (int)num_slots, (int)slot);
+    return;
+  }
+  const int64_t blk = slot / block_size;
+  const int off = (int)(slot % block_size);
+  T* dst = kv_cache + ((((blk * 2 + (is_k ? 0 : 1)) * block_size + off) * num_kv + hh) * (int64_t)head_dim);
+  *reinterpret_cast<uint4*>(dst + 8 * j) = a;
+  *reinterpret_cast<uint4*>(dst + half + 8 * j) = b;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 void rope_and_cache(const int64_t* positions, void* q, void* k, const void* v, const float* cos_sin, int rot,
                     int head_dim, int num_q, int num_kv, int64_t q_stride, int64_t k_stride, int64_t v_stride,
                     int is_neox, int rot_offset, int inverse, void* kv_cache, float* kv_scales,
                     const int64_t* slot_mapping, int block_size, int64_t num_slots, int cache_kind, float k_scale,
                     float v_scale, int tokens, int dtype, void* status, cudaStream_t stream) {
   if (tokens <= 0) return;
+  if (is_neox && rot == head_dim && rot_offset == 0 && head_dim % 16 == 0 && positions && q && k && v && cos_sin &&
+      (kv_cache == nullptr || cache_kind == kCacheSame) && q_stride % 8 == 0 && k_stride % 8 == 0 &&
+      v_stride % 8 == 0 && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(kv_cache) && aligned16(cos_sin)) {
+    const int64_t items = (int64_t)tokens * (num_q + 2 * num_kv) * (head_dim / 16);
+    const int blocks_v = (int)((items + 255) / 256);
+    if (dtype == 0)
+      rope_and_cache_vec_kernel<__nv_bfloat16><<<blocks_v, 256, 0, stream>>>(
+          positions, (__nv_bfloat16*)q, (__nv_bfloat16*)k, (const __nv_bfloat16*)v, cos_sin, head_dim, num_q, num_kv,
+          q_stride, k_stride, v_stride, inverse, (__nv_bfloat16*)kv_cache, slot_mapping, block_size, num_slots, tokens,
+          (StatusWord*)status);
+    else
+      rope_and_cache_vec_kernel<__half><<<blocks_v, 256, 0, stream>>>(
+          positions, (__half*)q, (__half*)k, (const __half*)v, cos_sin, head_dim, num_q, num_kv, q_stride, k_stride,
+          v_stride, inverse, (__half*)kv_cache, slot_mapping, block_size, num_slots, tokens, (StatusWord*)status);
+    return;
+  }
   const int64_t warps = (int64_t)tokens * (num_q + 2 * num_kv);
   const int blocks = (int)((warps + kRopeWarps - 1) / kRopeWarps);
   if (dtype == 0)

@@ -130,6 +130,27 @@ def bench_elementwise(t: Timer, T, H, I) -> dict:
     return res
 
 
+def bench_skinny(t: Timer) -> dict:
+    """Decode-batch GEMMs of Llama-3.1-8B at TP 1 and TP 8 shard sizes: the stream-K CTA-pair kernel (force_bn 2000)
+    against the cluster split-K kernel (1004), the plain 128-wide tile kernel (128) and cuBLAS."""
+    H, I = 4096, 14336
+    res = {}
+    for tp in (1, 8):
+        shapes = {"qkv": (6144 // tp, H), "o": (H, H // tp), "gate_up": (2 * I // tp, H), "down": (H, I // tp)}
+        for M in (32, 256):
+            for name, (N, K) in shapes.items():
+                a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+                w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.02
+                out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+                row = {}
+                for label, fb in (("streamk", 2000), ("splitk4", 1004), ("tile128", 128 if M > 64 else -32)):
+                    row[label + "_ms"] = round(t(lambda: ops.gemm(a, w, out=out, force_bn=fb)), 4)
+                row["cublas_ms"] = round(t(lambda: torch.mm(a, w.t(), out=out)), 4)
+                row["weights_gbs_streamk"] = round(N * K * 2 / row["streamk_ms"] / 1e6, 1)
+                res[f"tp{tp}_{name}_M{M}_{N}x{K}"] = row
+    return res
+
+
 def bench_quant(t, M: int, N: int, K: int) -> dict:
     """Quantised GEMMs at one shape (TFLOP/s over 2 M N K) and the TurboQuant decode kernel (bytes of compressed
     cache streamed per second)."""
@@ -210,7 +231,7 @@ def bench_linear_attention(t: Timer) -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "gemm", "prefill", "decode", "elementwise", "quant", "linear_attention"])
+    ap.add_argument("--op", default="all", choices=["all", "gemm", "prefill", "decode", "elementwise", "quant", "linear_attention", "skinny"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
@@ -243,6 +264,8 @@ def main() -> None:
         res[f"attn_decode_{a.batch}x{a.seq}_{a.kv}"] = bench_decode(t, a.batch, a.seq, 32, 8, 128, 128, a.kv, a.compare)
     if a.op == "linear_attention":
         res.update(bench_linear_attention(t))
+    if a.op == "skinny":
+        res.update(bench_skinny(t))
     if a.op in ("all", "elementwise"):
         for T in (8192, 256):
             for k, v in bench_elementwise(t, T, H, I).items():
