@@ -154,6 +154,8 @@ def main() -> None:
     clocks = sampler.stop() if rank == 0 else {}
     ops.check_kernel_status(dev.index or 0)
     phases = wl.phase_ms()
+    # outside the timed region: the fused NVLink path against the library collectives on the same ranks
+    tp_check = wl.collective_check() if world > 1 else None
     out_tokens = args.steps * N * O
     value = out_tokens / (dev_ms / 1e3)
 
@@ -201,6 +203,7 @@ def main() -> None:
                     "p50_ttft_ms": round(statistics.median(ttfts) * 1e3, 2),
                     "p50_tpot_ms": round(statistics.median(tpots) * 1e3, 3)},
             "gpu_launches": launches,
+            **({"tp_check": tp_check} if tp_check is not None else {}),
         }))
     if world > 1:
         # release captured graphs before the communicators they reference, and never let a slow

@@ -77,7 +77,8 @@ def _shutdown():
     os._exit(0)
 
 
-def _fused_ar_worker(rank, world):
+def _fused_ar_worker(rank, world, kernel="split"):
+    os.environ["B200_FUSED_TP_KERNEL"] = kernel
     from vllm_metax_b200 import _custom_ops as ops
     from vllm_metax_b200.ops import reference as ref
     from vllm_metax_b200.parallel import state as ps
@@ -87,9 +88,12 @@ def _fused_ar_worker(rank, world):
     dev = torch.device("cuda", rank)
     g = ps.get_tp_group()
     H, K = 2048, 512
-    fused = FusedRowParallelNorm(g, dev, 1024, H, torch.bfloat16)
+    fused = FusedRowParallelNorm(g, dev, 4096, H, torch.bfloat16)
+    assert fused.kernel == kernel
+    ok, why = fused.self_test()
+    assert ok, why
     gen = torch.Generator().manual_seed(0)          # same stream on every rank
-    for it, T in enumerate((5, 256, 1000, 130, 1024)):
+    for it, T in enumerate((5, 256, 1000, 130, 1024, 3000, 1, 4096)):
         xs = [torch.randn(T, K, generator=gen).to(torch.bfloat16) for _ in range(world)]
         ws = [(torch.randn(H, K, generator=gen) * 0.05).to(torch.bfloat16) for _ in range(world)]
         res_full = torch.randn(T, H, generator=gen).to(torch.bfloat16)
@@ -115,11 +119,12 @@ def _fused_ar_worker(rank, world):
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-def test_fused_gemm_allreduce_norm_2gpu():
-    _launch(_fused_ar_worker, _world())
+@pytest.mark.parametrize("kernel", ["split", "mono"])
+def test_fused_gemm_allreduce_norm_2gpu(kernel):
+    _launch(_fused_ar_worker, _world(), kernel)
 
 
-def _tp_engine_worker(rank, world, fused):
+def _tp_engine_worker(rank, world, fused, want=None):
     os.environ["B200_FUSED_TP_COLLECTIVES"] = "1" if fused else "0"
     os.environ["B200_FUSED_TP_MIN_TOKENS"] = "0"          # the small test batches must still take the fused kernel
     from vllm_metax_b200 import LLM, ModelConfig, SamplingParams
@@ -143,12 +148,37 @@ def _tp_engine_worker(rank, world, fused):
     gathered = ps.get_tp_group().all_gather(toks[None], 0)
     assert bool((gathered == toks[None]).all())
     llm.engine.runner.graphs.clear()
+    if want is not None:
+        # against ONE GPU on the same weights: another reduction order (bf16), so the first tokens agree and the
+        # rest mostly; a wrong-but-consistent collective would agree on neither
+        got = [list(o.outputs[0].token_ids) for o in outs]
+        assert [g_[0] for g_ in got] == [w[0] for w in want], (got, want)
+        same = sum(a == b for g_, w in zip(got, want) for a, b in zip(g_, w))
+        assert same >= 0.7 * sum(len(w) for w in want), (got, want)
+
+
+def _tp_single_gpu_tokens():
+    from vllm_metax_b200 import LLM, ModelConfig, SamplingParams
+
+    cfg = ModelConfig(architecture="LlamaForCausalLM", vocab_size=2048, hidden_size=1024, intermediate_size=2816,
+                      num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+                      max_position_embeddings=1024, dtype=torch.bfloat16, seed=0)
+    llm = LLM(cfg, device="cuda", block_size=64, max_model_len=512, max_num_seqs=8, max_num_batched_tokens=1024,
+              num_gpu_blocks=128)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (100, 33, 200)]
+    toks = [list(o.outputs[0].token_ids) for o in llm.generate(prompts, SamplingParams(max_tokens=16, ignore_eos=True))]
+    llm.engine.runner.graphs.clear()
+    del llm
+    torch.cuda.empty_cache()
+    return toks
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("fused", [False, True])
 def test_tp2_engine_generates(fused):
-    _launch(_tp_engine_worker, 2, fused)
+    want = _tp_single_gpu_tokens()
+    _launch(_tp_engine_worker, _world() if fused else 2, fused, want)
 
 
 def _moe_a2a_worker(rank, world, quant):

@@ -50,6 +50,28 @@ inline void* status_ptr(const Tensor& any) { return status_tensor(any.get_device
 Tensor get_status(int64_t device) { return status_tensor((int)device); }
 
 // ------------------------------------------------------------------ GEMM
+// Scratch of the stream-K GEMM (partial tiles + arrival counters): allocated once per device, stream-ordered use.
+struct StkScratch {
+  float* ws;
+  int* counters;
+  int sms;
+};
+static StkScratch stk_scratch(const Tensor& like) {
+  // leaked on purpose: destroying CUDA tensors from static destructors can outlive the allocator
+  static Tensor* ws = new Tensor[64];
+  static Tensor* counters = new Tensor[64];
+  static int sms_k[64] = {};
+  const int dev = like.get_device();
+  TORCH_CHECK(dev >= 0 && dev < 64);
+  if (sms_k[dev] == 0) cudaDeviceGetAttribute(&sms_k[dev], cudaDevAttrMultiProcessorCount, dev);
+  if (!ws[dev].defined()) {
+    ws[dev] = torch::empty({(int64_t)(b200::gemm_streamk_workspace_bytes(sms_k[dev]) / 4)},
+                           like.options().dtype(at::kFloat));
+    counters[dev] = torch::zeros({2 * (int64_t)b200::gemm_streamk_max_tiles()}, like.options().dtype(at::kInt));
+  }
+  return {ws[dev].data_ptr<float>(), counters[dev].data_ptr<int>(), sms_k[dev]};
+}
+
 void gemm(Tensor& out, const Tensor& a, const Tensor& w, const optional<Tensor>& bias,
           const optional<Tensor>& residual, int64_t force_bn, int64_t epi) {
   TORCH_CHECK(a.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm expects 2-D tensors");
@@ -85,23 +107,14 @@ void gemm(Tensor& out, const Tensor& a, const Tensor& w, const optional<Tensor>&
     return e == nullptr || std::atoi(e) != 0;
   }();
   {
-    static int sms_k[64] = {};
-    const int dev = a.get_device();
-    if (sms_k[dev] == 0) cudaDeviceGetAttribute(&sms_k[dev], cudaDevAttrMultiProcessorCount, dev);
+    StkScratch sk = stk_scratch(a);
     const int64_t tiles = ((M + 255) / 256) * (int64_t)((N + 255) / 256);
-    if (force_bn == 2000 || (force_bn == 0 && streamk_default && M <= 1024 && tiles <= 2 * sms_k[dev])) {
-      // leaked on purpose: destroying CUDA tensors from static destructors can outlive the allocator
-      static Tensor* ws = new Tensor[64];
-      static Tensor* counters = new Tensor[64];
-      if (!ws[dev].defined()) {
-        ws[dev] = torch::empty({(int64_t)(b200::gemm_streamk_workspace_bytes(sms_k[dev]) / 4)},
-                               a.options().dtype(at::kFloat));
-        counters[dev] = torch::zeros({2 * (int64_t)b200::gemm_streamk_max_tiles()}, a.options().dtype(at::kInt));
-      }
+    // measured inside replayed graphs: with up to 64 tokens the partial tiles are small and streaming over all SMs
+    // wins; at 256 tokens the 128 KB partials make the fix-up cost more than the balanced stream saves
+    if (force_bn == 2000 || (force_bn == 0 && streamk_default && M <= 64 && K >= 1024 && tiles <= 2 * sk.sms)) {
       const int rc = b200::gemm_tn_streamk(a.data_ptr(), w.data_ptr(), out.data_ptr(), ptr(bias), ptr(residual), M, N,
                                            K, a.stride(0), w.stride(0), out.stride(0), ldr, dtype16(a), cur_stream(),
-                                           status_ptr(a), (int)epi, ws[dev].data_ptr<float>(),
-                                           counters[dev].data_ptr<int>(), sms_k[dev]);
+                                           status_ptr(a), (int)epi, sk.ws, sk.counters, sk.sms);
       if (rc == 0) return;
       TORCH_CHECK(force_bn != 2000, "gemm: shape outside the stream-K kernel's scratch");
     }
@@ -693,6 +706,68 @@ void gemm_ar_norm(const Tensor& x, const Tensor& w, Tensor& residual, const Tens
   TORCH_CHECK(rc == 0, "gemm_ar_norm: hidden size ", p.H, " not supported");
 }
 
+// Row-parallel GEMM whose output rows go straight into the owning rank's receive slot (NVLink peer stores from the
+// GEMM epilogue).  ptrs: CPU int64 [>= 2, tp] = recv / flag1 base per rank; local_sync: int32 [4] on the device.
+void gemm_row_scatter(const Tensor& x, const Tensor& w, const Tensor& ptrs, int64_t tp, int64_t rank,
+                      int64_t rows_per_rank, int64_t rows_cap, Tensor& local_sync) {
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 && x.size(1) == w.size(1));
+  TORCH_CHECK(tp >= 1 && tp <= b200::kMaxRanks && ptrs.dim() == 2 && ptrs.size(0) >= 2 && ptrs.size(1) >= tp);
+  TORCH_CHECK(!ptrs.is_cuda() && ptrs.scalar_type() == at::kLong);
+  TORCH_CHECK(x.size(1) % 8 == 0 && x.stride(0) % 8 == 0 && w.stride(0) % 8 == 0 && w.size(0) % 8 == 0);
+  const int M = x.size(0), N = w.size(0), K = x.size(1);
+  TORCH_CHECK(rows_per_rank >= 1 && rows_per_rank <= rows_cap && rows_per_rank * tp >= M,
+              "gemm_row_scatter: receive slots too small");
+  b200::RowScatter sc{};
+  sc.tp = tp; sc.src_rank = rank; sc.rows_per_rank = rows_per_rank; sc.rows_cap = rows_cap;
+  const int64_t* pp = ptrs.data_ptr<int64_t>();
+  const int64_t st = ptrs.stride(0);
+  for (int r = 0; r < tp; ++r) {
+    sc.recv[r] = reinterpret_cast<void*>(pp[0 * st + r]);
+    sc.flag[r] = reinterpret_cast<uint32_t*>(pp[1 * st + r]);
+  }
+  sc.local_sync = reinterpret_cast<uint32_t*>(local_sync.data_ptr());
+  const c10::cuda::CUDAGuard guard(x.device());
+  if (M <= 64) {   // few tokens: stream over all SMs; otherwise CTA-pair tiles
+    StkScratch sk = stk_scratch(x);
+    const int rc = b200::gemm_tn_streamk(x.data_ptr(), w.data_ptr(), nullptr, nullptr, nullptr, M, N, K, x.stride(0),
+                                         w.stride(0), N, 0, dtype16(x), cur_stream(), status_ptr(x), 0, sk.ws,
+                                         sk.counters, sk.sms, &sc);
+    if (rc == 0) return;
+  }
+  b200::gemm_tn_pair(x.data_ptr(), w.data_ptr(), nullptr, nullptr, nullptr, M, N, K, x.stride(0), w.stride(0), N, 0,
+                     dtype16(x), cur_stream(), status_ptr(x), 0, &sc);
+}
+
+// Reduce + residual + RMSNorm + all-gather over the slots filled by gemm_row_scatter.
+// ptrs: CPU int64 [4, tp] = recv / flag1 / flag2 / out base per rank.
+void ar_norm_gather(Tensor& residual, const Tensor& norm_weight, double eps, const Tensor& ptrs, int64_t T, int64_t H,
+                    int64_t tp, int64_t rank, int64_t rows_per_rank, int64_t rows_cap, Tensor& local_sync,
+                    bool add_residual, int64_t wait_cycles) {
+  TORCH_CHECK(tp >= 1 && tp <= b200::kMaxRanks && ptrs.dim() == 2 && ptrs.size(0) == 4 && ptrs.size(1) >= tp);
+  TORCH_CHECK(!ptrs.is_cuda() && ptrs.scalar_type() == at::kLong && residual.is_contiguous());
+  TORCH_CHECK(residual.size(-1) == H && norm_weight.numel() == H && residual.size(0) >= rows_per_rank);
+  b200::ArNormParams p{};
+  p.T = T; p.H = H; p.tp = tp; p.rank = rank; p.rows_per_rank = rows_per_rank; p.rows_cap = rows_cap;
+  const int64_t* pp = ptrs.data_ptr<int64_t>();
+  const int64_t st = ptrs.stride(0);
+  for (int r = 0; r < tp; ++r) {
+    p.recv[r] = reinterpret_cast<void*>(pp[0 * st + r]);
+    p.flag1[r] = reinterpret_cast<uint32_t*>(pp[1 * st + r]);
+    p.flag2[r] = reinterpret_cast<uint32_t*>(pp[2 * st + r]);
+    p.out[r] = reinterpret_cast<void*>(pp[3 * st + r]);
+  }
+  p.residual = residual.data_ptr();
+  p.norm_weight = norm_weight.data_ptr();
+  p.eps = (float)eps;
+  p.add_residual = add_residual;
+  p.local_sync = reinterpret_cast<uint32_t*>(local_sync.data_ptr());
+  p.wait_cycles = wait_cycles;
+  p.status = reinterpret_cast<b200::StatusWord*>(status_ptr(residual));
+  const c10::cuda::CUDAGuard guard(residual.device());
+  const int rc = b200::ar_norm_gather(p, dtype16(residual), cur_stream());
+  TORCH_CHECK(rc == 0, "ar_norm_gather: hidden size ", H, " / dtype not supported");
+}
+
 // ------------------------------------------------------------------ small / fused kernels
 void small_gemm(Tensor& out, const Tensor& a, const Tensor& w, const optional<Tensor>& bias) {
   TORCH_CHECK(a.dim() == 2 && w.dim() == 2 && a.stride(1) == 1 && w.stride(1) == 1 && a.size(1) == w.size(1));
@@ -1272,6 +1347,14 @@ TORCH_LIBRARY(b200, m) {
   m.def("symm_alloc(int nbytes, int device) -> (Tensor, Tensor)", &symm_alloc);
   m.def("symm_open(Tensor handle, int device) -> int", &symm_open);
   m.def("symm_close(int ptr) -> ()", &symm_close);
+  m.def(
+      "gemm_row_scatter(Tensor x, Tensor w, Tensor ptrs, int tp, int rank, int rows_per_rank, int rows_cap, "
+      "Tensor(a!) local_sync) -> ()",
+      &gemm_row_scatter);
+  m.def(
+      "ar_norm_gather(Tensor(a!) residual, Tensor norm_weight, float eps, Tensor ptrs, int T, int H, int tp, int rank, "
+      "int rows_per_rank, int rows_cap, Tensor(b!) local_sync, bool add_residual, int wait_cycles) -> ()",
+      &ar_norm_gather);
   m.def(
       "gemm_ar_norm(Tensor x, Tensor w, Tensor(a!) residual, Tensor norm_weight, float eps, Tensor ptrs, int tp, "
       "int rank, int rows_per_rank, int rows_cap, int rb_cap, Tensor(b!) local_sync, bool add_residual, "

@@ -34,6 +34,33 @@ struct FusedArParams {
   StatusWord* status;
 };
 
+// Row scatter of a GEMM's output (gemm_pair_tcgen05.cu, gemm_streamk_tcgen05.cu): output row r belongs to rank
+// r / rows_per_rank and is stored into that rank's receive slot for this source, over NVLink when the owner is a
+// peer.  tp == 0 switches the scatter off.  When the last CTA of the launch has finished, flag[d][src_rank] on every
+// rank d is set to the call's epoch (local_sync[1] + 1, kept in device memory so that graph replays advance it).
+struct RowScatter {
+  int tp, src_rank, rows_per_rank, rows_cap;
+  void* recv[kMaxRanks];          // [tp (source)][rows_cap][ld] 16-bit rows, indexed by the OWNING rank
+  uint32_t* flag[kMaxRanks];      // [tp] push epoch per source, indexed by the owning rank
+  uint32_t* local_sync;           // [0] CTA ticket, [1] last finished push epoch
+};
+
+// Reduce + residual + RMSNorm + all-gather over the slots a RowScatter GEMM filled (comm_ar_norm.cu).
+struct ArNormParams {
+  int T, H, tp, rank, rows_per_rank, rows_cap;
+  void* recv[kMaxRanks];          // as in RowScatter
+  uint32_t* flag1[kMaxRanks];     // [tp] push epochs (written by the GEMMs)
+  uint32_t* flag2[kMaxRanks];     // [tp] gather epochs (written by this kernel)
+  void* out[kMaxRanks];           // [T_cap, H] normalised rows on every rank
+  void* residual;                 // [rows_per_rank, H] this rank's shard of the residual stream (in/out)
+  const void* norm_weight;        // [H]
+  float eps;
+  int add_residual;
+  uint32_t* local_sync;           // [2] CTA ticket, [3] last finished epoch of this kernel
+  long long wait_cycles;
+  StatusWord* status;
+};
+
 // All-gather -> GEMM (comm_ag_gemm.cu): C[tp*R, N] = concat_r(X_r[R, K]) . W[N, K]^T.
 struct AgGemmParams {
   int rows_per_rank, N, K, tp, rank, ldc;

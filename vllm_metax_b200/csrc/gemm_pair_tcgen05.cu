@@ -18,7 +18,7 @@
 // Clusters are persistent (74 on a 148-SM part) and walk tiles M-fastest so that
 // concurrently running pairs share W tiles in L2.
 #include <type_traits>
-#include "common.cuh"
+#include "comm_fused.cuh"
 #include "gemm_epilogue.cuh"
 #include "ptx_sm100.cuh"
 #include "tma_host.h"
@@ -44,7 +44,7 @@ template <typename T>
 __global__ void __launch_bounds__(192, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  T* __restrict__ C, const T* __restrict__ bias, const T* __restrict__ residual, int M, int N, int K,
-                 int ldc, int ldr, int epi, StatusWord* status) {
+                 int ldc, int ldr, int epi, StatusWord* status, const __grid_constant__ RowScatter sc) {
   using L = PairSmem;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -170,7 +170,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         uint32_t r[32];
         tmem_ld_32x32b_x32(taddr + c, r);
         tmem_ld_wait();
-        if (row < M) store_row_segment<T, 32>(r, row, tn * kPairBN + c, N, C, ldc, bias, residual, ldr, epi);
+        if (row < M) {
+          if (sc.tp > 0) {
+            // the row goes to the receive slot of the rank that owns it (a peer store over NVLink for d != me)
+            const int owner = row / sc.rows_per_rank;
+            store_row_segment<T, 32>(r, sc.src_rank * sc.rows_cap + (row - owner * sc.rows_per_rank),
+                                     tn * kPairBN + c, N, reinterpret_cast<T*>(sc.recv[owner]), ldc, bias, nullptr, 0,
+                                     epi);
+          } else {
+            store_row_segment<T, 32>(r, row, tn * kPairBN + c, N, C, ldc, bias, residual, ldr, epi);
+          }
+        }
       }
       tc_fence_before_sync();
       mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
@@ -184,11 +194,25 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_after_sync();
     tmem_dealloc_pair(tmem_base, kTmemCols);
   }
+  if (sc.tp > 0 && threadIdx.x == 0) {
+    // every store of this CTA is ordered before the fence by the barrier above; the last CTA of the launch
+    // tells every owner that this source's rows have landed
+    __threadfence_system();
+    const uint32_t ticket = atomicAdd(&sc.local_sync[0], 1u);
+    if (ticket == gridDim.x - 1) {
+      __threadfence_system();
+      const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(sc.local_sync + 1) + 1u;
+      for (int d = 0; d < sc.tp; ++d) st_release_sys(sc.flag[d] + sc.src_rank, epoch);
+      sc.local_sync[0] = 0;
+      sc.local_sync[1] = epoch;
+    }
+  }
 }
 
 template <typename T>
 static void launch_pair(const void* A, const void* W, void* C, const void* bias, const void* residual, int M, int N,
-                        int K, int lda, int ldw, int ldc, int ldr, int epi, cudaStream_t stream, StatusWord* status) {
+                        int K, int lda, int ldw, int ldc, int ldr, int epi, cudaStream_t stream, StatusWord* status,
+                        const RowScatter& sc) {
   const CUtensorMapDataType dt =
       std::is_same<T, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap tmA = make_tmap_2d(A, dt, 2, M, K, lda, 128, kPairBK);
@@ -221,18 +245,21 @@ static void launch_pair(const void* A, const void* W, void* C, const void* bias,
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaLaunchKernelEx(&cfg, kern, tmA, tmB, reinterpret_cast<T*>(C), reinterpret_cast<const T*>(bias),
-                     reinterpret_cast<const T*>(residual), M, N, K, ldc, ldr, epi, status);
+                     reinterpret_cast<const T*>(residual), M, N, K, ldc, ldr, epi, status, sc);
 }
 
 void gemm_tn_pair(const void* A, const void* W, void* C, const void* bias, const void* residual, int M, int N, int K,
-                  int lda, int ldw, int ldc, int ldr, int dtype, cudaStream_t stream, void* status, int epi) {
+                  int lda, int ldw, int ldc, int ldr, int dtype, cudaStream_t stream, void* status, int epi,
+                  const RowScatter* scatter) {
   if (M <= 0 || N <= 0) return;
+  RowScatter sc{};
+  if (scatter) sc = *scatter;
   if (dtype == 0)
     launch_pair<__nv_bfloat16>(A, W, C, bias, residual, M, N, K, lda, ldw, ldc, ldr, epi, stream,
-                               reinterpret_cast<StatusWord*>(status));
+                               reinterpret_cast<StatusWord*>(status), sc);
   else
     launch_pair<__half>(A, W, C, bias, residual, M, N, K, lda, ldw, ldc, ldr, epi, stream,
-                        reinterpret_cast<StatusWord*>(status));
+                        reinterpret_cast<StatusWord*>(status), sc);
 }
 
 }  // namespace b200

@@ -18,7 +18,7 @@
 // All mbarrier waits are bounded.  Replaces the library GEMM behind every unquantised linear layer at decode
 // batch sizes (torch.nn.functional.linear in the reference's model files).
 #include <type_traits>
-#include "common.cuh"
+#include "comm_fused.cuh"
 #include "ptx_sm100.cuh"
 #include "tma_host.h"
 #include "ops.h"
@@ -30,6 +30,7 @@ constexpr int kStkBW = 256;           // weight rows per pair tile (128 per CTA)
 constexpr int kStkBT = 256;           // tokens per tile at most
 constexpr int kStkBK = 64;
 constexpr int kStkStages = 6;
+constexpr int kStkMaxContrib = 8;      // partials that may meet in one tile (host plan keeps to it)
 constexpr int kStkSlotFloats = 2 * kStkBT * 128;   // one partial tile: [cta][token column][128 lanes]
 
 struct StkSmem {
@@ -65,7 +66,7 @@ __global__ void __launch_bounds__(192, 1)
 gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                     T* __restrict__ C, const T* __restrict__ bias, const T* __restrict__ residual, const StkShape sh,
                     int ldc, int ldr, int epi, float* __restrict__ ws, int* __restrict__ counters,
-                    StatusWord* status) {
+                    StatusWord* status, const __grid_constant__ RowScatter sc) {
   using L = StkSmem;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -227,31 +228,96 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           if (epi_tid == 0) counters[tile * 2 + (int)rank] = 0;   // ready for the next launch
         }
       }
-      if (finish) {
+      if (finish && !complete) {
+        // Every partial of this tile half (this pair's own included) sits in scratch as [token column][lane].
+        // The 128 epilogue threads walk it flat, four lanes (= four output features) per float4, with the loads
+        // of every contributor and of four units in flight together; contributors are added in pair order, so
+        // the result does not depend on who arrived last.
+        const int n = min(c_last - c_first + 1, kStkMaxContrib);
+        if (c_last - c_first + 1 > kStkMaxContrib) report_status(status, kBadIndex, 174, kStkMaxContrib, c_last - c_first + 1);
+        const float* src[kStkMaxContrib];
+#pragma unroll
+        for (int k = 0; k < kStkMaxContrib; ++k) {
+          const int cc = c_first + (k < n ? k : 0);
+          const int which = stk_unit_start(units, sh.clusters, cc) > tile_u0 ? 0 : 1;
+          src[k] = ws + (size_t)(cc * 2 + which) * kStkSlotFloats + (size_t)rank * (kStkBT * 128);
+        }
+        const int units4 = sh.TN * 32;                       // float4 units of this CTA's half tile
+        const int feat0 = tw * kStkBW + (int)rank * 128;
+#pragma unroll 1
+        for (int u0 = epi_tid; u0 < units4; u0 += 4 * 128) {
+          float4 v[kStkMaxContrib][4];
+#pragma unroll
+          for (int k = 0; k < kStkMaxContrib; ++k)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int u = u0 + q * 128;
+              v[k][q] = (k < n && u < units4) ? __ldcg(reinterpret_cast<const float4*>(src[k]) + u)
+                                              : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int u = u0 + q * 128;
+            if (u >= units4) break;
+            float4 a = v[0][q];
+#pragma unroll
+            for (int k = 1; k < kStkMaxContrib; ++k) {
+              if (k < n) { a.x += v[k][q].x; a.y += v[k][q].y; a.z += v[k][q].z; a.w += v[k][q].w; }
+            }
+            const int col = u >> 5, l4 = (u & 31) << 2;
+            const int tok = tt * kStkBT + col, ra = feat0 + l4;
+            if (tok >= sh.M || ra >= sh.N) continue;
+            float f[4] = {a.x, a.y, a.z, a.w};
+            if (bias) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) if (ra + e < sh.N) f[e] += to_f(bias[ra + e]);
+            }
+            T* crow;
+            if (sc.tp > 0) {
+              const int owner = tok / sc.rows_per_rank;
+              crow = reinterpret_cast<T*>(sc.recv[owner]) +
+                     (size_t)(sc.src_rank * sc.rows_cap + tok - owner * sc.rows_per_rank) * ldc;
+            } else {
+              crow = C + (size_t)tok * ldc;
+            }
+            if (epi == 1) {
+              // interleaved (gate, up) features: two outputs per four lanes
+              T o2[2];
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const float g = to_f(from_f<T>(f[2 * e])), up = to_f(from_f<T>(f[2 * e + 1]));
+                o2[e] = from_f<T>(g / (1.f + __expf(-g)) * up);
+              }
+              if (ra + 3 < sh.N) *reinterpret_cast<uint32_t*>(crow + (ra >> 1)) = *reinterpret_cast<const uint32_t*>(o2);
+              else if (ra + 1 < sh.N) crow[ra >> 1] = o2[0];
+            } else {
+              if (residual && sc.tp == 0) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) if (ra + e < sh.N) f[e] += to_f(residual[(size_t)tok * ldr + ra + e]);
+              }
+              if (ra + 3 < sh.N) {
+                T o4[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) o4[e] = from_f<T>(f[e]);
+                *reinterpret_cast<uint2*>(crow + ra) = *reinterpret_cast<const uint2*>(o4);
+              } else {
+                for (int e = 0; e < 4 && ra + e < sh.N; ++e) crow[ra + e] = from_f<T>(f[e]);
+              }
+            }
+          }
+        }
+      } else if (finish) {
         const int ra = tw * kStkBW + (int)rank * 128 + row;  // output feature of this lane
         const bool ra_ok = ra < sh.N;
         const float bv = (bias && ra_ok) ? to_f(bias[ra]) : 0.f;
 #pragma unroll 1
         for (int c = 0; c < sh.TN; c += 16) {
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(taddr + c, r);
+          tmem_ld_wait();
           float a[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) a[i] = 0.f;
-          // partials are added in pair order whoever arrives last: the result does not depend on timing
-          for (int cc = c_first; cc <= c_last; ++cc) {
-            if (cc == cluster_id) {
-              uint32_t r[16];
-              tmem_ld_32x32b_x16(taddr + c, r);
-              tmem_ld_wait();
-#pragma unroll
-              for (int i = 0; i < 16; ++i) a[i] += __uint_as_float(r[i]);
-            } else {
-              const int which = stk_unit_start(units, sh.clusters, cc) > tile_u0 ? 0 : 1;
-              const float* src =
-                  ws + (size_t)(cc * 2 + which) * kStkSlotFloats + (size_t)rank * (kStkBT * 128) + row;
-#pragma unroll
-              for (int i = 0; i < 16; ++i) a[i] += __ldcg(src + (c + i) * 128);
-            }
-          }
+          for (int i = 0; i < 16; ++i) a[i] = __uint_as_float(r[i]);
           const int tok0 = tt * kStkBT + c;
           if (epi == 1) {
             // lanes hold interleaved (gate, up) features: even lane = gate, odd lane = up
@@ -268,8 +334,15 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
               const int tok = tok0 + i;
               if (tok < sh.M) {
                 float f = a[i] + bv;
-                if (residual) f += to_f(residual[(size_t)tok * ldr + ra]);
-                C[(size_t)tok * ldc + ra] = from_f<T>(f);
+                if (sc.tp > 0) {
+                  // the token's row lives in the receive slot of the rank that owns it
+                  const int owner = tok / sc.rows_per_rank;
+                  reinterpret_cast<T*>(sc.recv[owner])[(size_t)(sc.src_rank * sc.rows_cap + tok -
+                                                                 owner * sc.rows_per_rank) * ldc + ra] = from_f<T>(f);
+                } else {
+                  if (residual) f += to_f(residual[(size_t)tok * ldr + ra]);
+                  C[(size_t)tok * ldc + ra] = from_f<T>(f);
+                }
               }
             }
           }
@@ -287,6 +360,18 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     tc_fence_after_sync();
     tmem_dealloc_pair(tmem_base, kTmemCols);
   }
+  if (sc.tp > 0 && threadIdx.x == 0) {
+    // the last CTA of the launch tells every owner that this source's rows have landed
+    __threadfence_system();
+    const uint32_t ticket = atomicAdd(&sc.local_sync[0], 1u);
+    if (ticket == gridDim.x - 1) {
+      __threadfence_system();
+      const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(sc.local_sync + 1) + 1u;
+      for (int d = 0; d < sc.tp; ++d) st_release_sys(sc.flag[d] + sc.src_rank, epoch);
+      sc.local_sync[0] = 0;
+      sc.local_sync[1] = epoch;
+    }
+  }
 }
 
 // How the (tile, k-block) space is shared out for a problem; clusters == 0: not a stream-K shape.
@@ -300,7 +385,7 @@ static StkShape stk_plan(int M, int N, int K, int sms) {
   const long long tiles = (long long)sh.num_t * sh.num_w;
   const long long units = tiles * sh.num_k;
   long long c = sms / 2;
-  if (c > 8 * tiles) c = 8 * tiles;          // at most ~8 partials meet in one tile
+  if (c > 6 * tiles) c = 6 * tiles;          // keeps the partials that meet in one tile within kStkMaxContrib
   if (c > units / 4) c = units / 4;          // at least 4 k-blocks per pair
   if (c < 1) c = 1;
   sh.clusters = (int)c;
@@ -313,7 +398,7 @@ int gemm_streamk_max_tiles() { return 8192; }
 template <typename T>
 static void launch_stk(const void* A, const void* W, void* C, const void* bias, const void* residual,
                        const StkShape& sh, int lda, int ldw, int ldc, int ldr, int epi, float* ws, int* counters,
-                       cudaStream_t stream, StatusWord* status) {
+                       cudaStream_t stream, StatusWord* status, const RowScatter& sc) {
   const CUtensorMapDataType dt =
       std::is_same<T, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap tmW = make_tmap_2d(W, dt, 2, sh.N, sh.K, ldw, 128, kStkBK);
@@ -339,22 +424,24 @@ static void launch_stk(const void* A, const void* W, void* C, const void* bias, 
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaLaunchKernelEx(&cfg, kern, tmW, tmX, reinterpret_cast<T*>(C), reinterpret_cast<const T*>(bias),
-                     reinterpret_cast<const T*>(residual), sh, ldc, ldr, epi, ws, counters, status);
+                     reinterpret_cast<const T*>(residual), sh, ldc, ldr, epi, ws, counters, status, sc);
 }
 
 // Returns 0 when launched, -1 when the shape is outside what the scratch buffers cover.
 // `ws` must hold gemm_streamk_workspace_bytes(sms) bytes, `counters` 2 * gemm_streamk_max_tiles() zeroed ints.
 int gemm_tn_streamk(const void* A, const void* W, void* C, const void* bias, const void* residual, int M, int N, int K,
                     int lda, int ldw, int ldc, int ldr, int dtype, cudaStream_t stream, void* status, int epi,
-                    float* ws, int* counters, int sms) {
+                    float* ws, int* counters, int sms, const RowScatter* scatter) {
   if (M <= 0 || N <= 0) return 0;
+  RowScatter sc{};
+  if (scatter) sc = *scatter;
   const StkShape sh = stk_plan(M, N, K, sms);
   if ((long long)sh.num_t * sh.num_w > gemm_streamk_max_tiles() || K <= 0) return -1;
   StatusWord* st = reinterpret_cast<StatusWord*>(status);
   if (dtype == 0)
-    launch_stk<__nv_bfloat16>(A, W, C, bias, residual, sh, lda, ldw, ldc, ldr, epi, ws, counters, stream, st);
+    launch_stk<__nv_bfloat16>(A, W, C, bias, residual, sh, lda, ldw, ldc, ldr, epi, ws, counters, stream, st, sc);
   else
-    launch_stk<__half>(A, W, C, bias, residual, sh, lda, ldw, ldc, ldr, epi, ws, counters, stream, st);
+    launch_stk<__half>(A, W, C, bias, residual, sh, lda, ldw, ldc, ldr, epi, ws, counters, stream, st, sc);
   return 0;
 }
 

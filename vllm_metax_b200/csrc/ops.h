@@ -75,9 +75,12 @@ size_t gemm_streamk_workspace_bytes(int sms);
 int gemm_streamk_max_tiles();
 int gemm_tn_streamk(const void* A, const void* W, void* C, const void* bias, const void* residual, int M, int N, int K,
                     int lda, int ldw, int ldc, int ldr, int dtype, cudaStream_t stream, void* status, int epi,
-                    float* ws, int* counters, int sms);
+                    float* ws, int* counters, int sms, const struct RowScatter* scatter = nullptr);
 void gemm_tn_pair(const void* A, const void* W, void* C, const void* bias, const void* residual, int M, int N, int K,
-                  int lda, int ldw, int ldc, int ldr, int dtype, cudaStream_t stream, void* status, int epi);
+                  int lda, int ldw, int ldc, int ldr, int dtype, cudaStream_t stream, void* status, int epi,
+                  const struct RowScatter* scatter = nullptr);
+// ---- comm_ar_norm.cu
+int ar_norm_gather(const ArNormParams& p, int dtype, cudaStream_t stream);
 // ---- gemm_splitk_tcgen05.cu
 int gemm_splitk_choice(int M, int N, int K, int sms);
 void gemm_tn_splitk(const void* A, const void* W, void* C, const void* bias, const void* residual, int M, int N, int K,

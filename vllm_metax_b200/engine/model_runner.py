@@ -97,12 +97,14 @@ class ModelRunner:
 
             # small reductions (decode steps, MoE outputs, logits pieces) skip NCCL's launch + protocol latency
             self.custom_ar = CustomAllReduce(ps.get_tp_group(), self.device, envs.B200_CUSTOM_ALLREDUCE_MAX_BYTES)
-            if self.custom_ar.self_test():          # checked once against the library all-reduce at this world size
+            ok, why = self.custom_ar.self_test()    # checked once against an fp32 sum at this world size
+            if ok:
                 self.custom_ar.attach()
             else:
                 import warnings
 
-                warnings.warn("peer-store all-reduce failed its start-up check; tensor-parallel reductions stay on NCCL")
+                warnings.warn(f"peer-store all-reduce failed its start-up check ({why}); "
+                              "tensor-parallel reductions stay on NCCL")
                 self.custom_ar = None
         if (ps.tp_size() == 1 or ps.get_pp_group().world_size > 1 or not envs.B200_FUSED_TP_COLLECTIVES
                 or inner is None or not hasattr(inner, "forward_fused_tp")
@@ -111,9 +113,18 @@ class ModelRunner:
             return
         from ..parallel.fused_collectives import get_fused_row_parallel
 
-        inner.fused_ar = get_fused_row_parallel(ps.get_tp_group(), self.device, self.max_tokens,
-                                                self.cfg.model.hidden_size, self.cfg.model.dtype)
-        inner.fused_min_tokens = envs.B200_FUSED_TP_MIN_TOKENS
+        fused = get_fused_row_parallel(ps.get_tp_group(), self.device, self.max_tokens,
+                                       self.cfg.model.hidden_size, self.cfg.model.dtype)
+        ok, why = fused.self_test()                 # same verdict on every rank
+        if not ok:
+            import warnings
+
+            warnings.warn(f"fused row-parallel path failed its start-up check ({why}); "
+                          "row-parallel layers use GEMM + all-reduce + add-norm")
+            return
+        inner.fused_ar = fused
+        # the split path serves every step size; the single-kernel path only pays off on large steps
+        inner.fused_min_tokens = envs.B200_FUSED_TP_MIN_TOKENS if fused.kernel == "mono" else 0
         self.fused_tp = True
 
     # ------------------------------------------------------------------ buffers

@@ -112,6 +112,49 @@ class StaticWorkload:
             return {}
         return {"prefill_ms": round(ev[0].elapsed_time(ev[1]), 2), "decode_ms": round(ev[1].elapsed_time(ev[2]), 2)}
 
+    # ------------------------------------------------------------------ correctness probe of the fused collectives
+    @torch.no_grad()
+    def collective_check(self) -> dict:
+        """One prefill chunk and one decode step, each run twice on the same ranks and the same cache: through the
+        fused NVLink path the benchmark times, and through plain GEMMs + the library all-reduce.  Returns the
+        cosine distance and the largest absolute difference of the final hidden states (the two paths add the
+        partial sums in different orders, in 16-bit, so they agree closely but not bit for bit)."""
+        from ..parallel import state as ps
+
+        r = self.r
+        inner = getattr(r.model, "model", None)
+        group = ps.get_tp_group()
+        if group.world_size == 1 or inner is None:
+            return {}
+        saved = (getattr(inner, "fused_ar", None), getattr(group, "custom_allreduce", None))
+
+        def fwd(ids, positions, md):
+            ctx = ForwardContext(md, r.kv_caches, positions)
+            with set_forward_context(ctx):
+                return r.model(ids, positions).float().clone()
+
+        def both(ids, positions, md):
+            a = fwd(ids, positions, md)
+            inner.fused_ar, group.custom_allreduce = None, None
+            try:
+                b = fwd(ids, positions, md)
+            finally:
+                inner.fused_ar, group.custom_allreduce = saved
+            cos = 1.0 - float(torch.dot(a.flatten(), b.flatten()) / (a.norm() * b.norm() + 1e-12))
+            return cos, float((a - b).abs().max()), float(b.abs().max())
+
+        _, _, ids, positions, md, _ = self.prefill_steps[0]
+        p_cos, p_abs, p_ref = both(ids, positions, md)
+        self._reset_decode_inputs()
+        N = self.N
+        d_cos, d_abs, d_ref = both(r.input_ids[:N], r.positions[:N], self.decode_md)
+        torch.cuda.synchronize()
+        ok = p_cos < 2e-3 and d_cos < 2e-3
+        return {"fused_path": bool(saved[0] is not None), "peer_allreduce": bool(saved[1] is not None),
+                "prefill_tokens": int(ids.shape[0]), "cos_diff": round(max(p_cos, d_cos), 6),
+                "max_abs": round(max(p_abs, d_abs), 4), "ref_max_abs": round(max(p_ref, d_ref), 3),
+                "decode_cos_diff": round(d_cos, 6), "ok": bool(ok)}
+
     # ------------------------------------------------------------------ the timed body
     @torch.no_grad()
     def run(self) -> int:

@@ -38,41 +38,32 @@ environment_variables: dict[str, Callable[[], Any]] = {
     "CMAKE_BUILD_TYPE": _str("CMAKE_BUILD_TYPE", None),
     "VERBOSE": _flag("VERBOSE", "0"),
     "CUDA_HOME": _str("CUDA_HOME", "/usr/local/cuda"),
-    # Path of a specific libnccl.so for the ctypes NCCL binding (None: torch's).
-    "B200_NCCL_SO_PATH": _str("B200_NCCL_SO_PATH", None),
     # When 1 the native extension must already be built in-tree; never JIT.
     "B200_USE_PREBUILT_KERNELS": _flag("B200_USE_PREBUILT_KERNELS", "0"),
     # ---- runtime: kernel selection ---------------------------------------
     # Hand-written tcgen05 GEMM on dense linears (0 = cuBLAS, debug only).
     "B200_TCGEN05_GEMM": _flag("B200_TCGEN05_GEMM", "1"),
-    # Grouped tcgen05 GEMM for experts (0 = per-expert loop, debug only).
-    "B200_GROUPED_MOE_GEMM": _flag("B200_GROUPED_MOE_GEMM", "1"),
     # Fused GEMM + in-kernel NVLink all-reduce + residual + RMSNorm.
     "B200_FUSED_TP_COLLECTIVES": _flag("B200_FUSED_TP_COLLECTIVES", "1"),
-    # Steps with fewer tokens than this use GEMM + peer-store all-reduce + add-norm instead of the fused kernel.
+    # Which fused row-parallel path runs: "split" = GEMM with NVLink row-scatter epilogue + one reduce / norm /
+    # all-gather kernel (every step size), "mono" = the single 128x256-tile kernel (steps of at least
+    # B200_FUSED_TP_MIN_TOKENS tokens; GEMM + peer-store all-reduce + add-norm below).
+    "B200_FUSED_TP_KERNEL": _str("B200_FUSED_TP_KERNEL", "split"),
     "B200_FUSED_TP_MIN_TOKENS": _int("B200_FUSED_TP_MIN_TOKENS", 1024),
+    # Stream-K CTA-pair GEMM for skinny problems (read by the native GEMM dispatcher; 0 = tile / split-K kernels).
+    "B200_GEMM_STREAMK": _flag("B200_GEMM_STREAMK", "1"),
+    # One query tile per CTA in the prefill attention kernel (read by the native dispatcher; debug only).
+    "B200_ATTN_PREFILL_SINGLE": _flag("B200_ATTN_PREFILL_SINGLE", "0"),
     # Sequence-parallel MoE through the NVLink dispatch / combine kernels instead of experts-on-all-tokens + all-reduce.
     "B200_MOE_A2A": _flag("B200_MOE_A2A", "0"),
     # Pack topk weights/ids/scales into one tensor for the AG/RS dispatch.
     "B200_OPTIMIZED_DP_ALL2ALL": _flag("B200_OPTIMIZED_DP_ALL2ALL", "1"),
-    # Run prefill and decode slices of a mixed batch through separate kernels.
-    "B200_ATTN_SPLIT_FORWARD": _flag("B200_ATTN_SPLIT_FORWARD", "1"),
-    # Token chunk for the fused-MoE expert pipeline.
-    "B200_FUSED_MOE_CHUNK_SIZE": _int("B200_FUSED_MOE_CHUNK_SIZE", 16384),
     "B200_SUPPORTS_FP8": _flag("B200_SUPPORTS_FP8", "1"),
-    # fp8 weights with bf16 activations (weight-only) for block-scaled linears.
-    "B200_USE_FP8_WO_A": _flag("B200_USE_FP8_WO_A", "0"),
     "B200_USE_FUSED_GROUPED_TOPK": _flag("B200_USE_FUSED_GROUPED_TOPK", "1"),
-    "B200_USE_CUDA_SAMPLER": _flag("B200_USE_CUDA_SAMPLER", "1"),
     # CUDA-graph capture of decode steps.
     "B200_CUDA_GRAPHS": _flag("B200_CUDA_GRAPHS", "1"),
-    # In-kernel bounds checks on every indexed access (slot mapping, block
-    # tables, expert ids); failures land in a device status word.
-    "B200_KERNEL_BOUNDS_CHECK": _flag("B200_KERNEL_BOUNDS_CHECK", "0"),
     # Iteration budget of device-side waits on peer flags before giving up.
     "B200_PEER_WAIT_ITERS": _int("B200_PEER_WAIT_ITERS", 20_000_000),
-    # Use NVLS multimem instructions in fused collectives when available.
-    "B200_USE_MULTIMEM": _flag("B200_USE_MULTIMEM", "0"),
     "B200_PP_DISABLE_ALLGATHER": _flag("B200_PP_DISABLE_ALLGATHER", "0"),
     # Peer-store all-reduce kernel for tensor-parallel reductions up to B200_CUSTOM_ALLREDUCE_MAX_BYTES
     # (larger messages stay on NCCL).

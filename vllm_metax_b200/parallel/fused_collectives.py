@@ -2,9 +2,16 @@
 
 ``FusedRowParallelNorm`` is the tensor-parallel row-parallel linear (o_proj / down_proj) fused
 with everything that follows it: GEMM -> reduce-scatter into the owning rank -> residual add
--> RMSNorm -> all-gather of the normalised rows, as ONE kernel per rank
-(``csrc/comm_gemm_ar_norm.cu``).  It replaces GEMM + NCCL all-reduce + fused_add_rms_norm
-(the reference's path C1 -> K12, and its quick-reduce / minimax_reduce_rms special cases).
+-> RMSNorm -> all-gather of the normalised rows.  Two implementations share one workspace:
+
+``split`` (default)  the CTA-pair GEMM (prefill chunks) or the stream-K GEMM (decode batches) stores each output
+                     row from its epilogue straight into the owning rank's receive slot over NVLink while the
+                     tensor cores work on the next tile; ONE more kernel (``csrc/comm_ar_norm.cu``) then reduces,
+                     adds the residual, normalises and all-gathers.  Two launches, no library collective.
+``mono``             one kernel per rank for all of it (``csrc/comm_gemm_ar_norm.cu``, 128 x 256 single-CTA tiles).
+
+Both replace GEMM + NCCL all-reduce + fused_add_rms_norm (the reference's path C1 -> K12, and its
+quick-reduce / minimax_reduce_rms special cases).
 
 The residual stream is kept sharded by token rows between calls: rank r owns rows
 ``[r * rows_per_rank, (r + 1) * rows_per_rank)`` of the step's ``T`` tokens.
@@ -39,6 +46,7 @@ class FusedRowParallelNorm:
         self.rows_cap = (rows_per_rank(max_tokens, self.tp) + 7) // 8 * 8
         self.rb_cap = (max_tokens + 127) // 128 + 1
         self.cuda = device.type == "cuda"
+        self.kernel = (envs.B200_FUSED_TP_KERNEL or "split").lower()
         if not self.cuda:
             return
         esz = torch.empty((), dtype=dtype).element_size()
@@ -46,15 +54,23 @@ class FusedRowParallelNorm:
         n_out = max_tokens * hidden * esz
         n_cnt = 2 * self.rb_cap * 4
         n_flag = 64
-        self.ws = SymmWorkspace(group, n_recv + n_out + n_cnt + n_flag + 8 * SymmWorkspace.ALIGN, device)
+        self.ws = SymmWorkspace(group, n_recv + n_out + n_cnt + 3 * n_flag + 12 * SymmWorkspace.ALIGN, device)
         r_recv = self.ws.region("recv", n_recv)
         r_cnt = self.ws.region("counters", n_cnt)
         r_flag = self.ws.region("flags", n_flag)
         r_out = self.ws.region("out", n_out)
+        # flags of the split path: push epochs (written by the scatter GEMMs) and gather epochs
+        r_f1, r_f2 = self.ws.region("push_flags", 64), self.ws.region("gather_flags", 64)
+        self.ws.local(r_f1, torch.int32, (16,)).zero_()
+        self.ws.local(r_f2, torch.int32, (16,)).zero_()
         self.out = self.ws.local(r_out, dtype, (max_tokens, hidden))
         self.ptrs = torch.tensor([self.ws.peer_ptrs(r_recv), self.ws.peer_ptrs(r_cnt), self.ws.peer_ptrs(r_flag),
                                   self.ws.peer_ptrs(r_out)], dtype=torch.int64)
+        self.ptrs_scatter = torch.tensor([self.ws.peer_ptrs(r_recv), self.ws.peer_ptrs(r_f1)], dtype=torch.int64)
+        self.ptrs_gather = torch.tensor([self.ws.peer_ptrs(r_recv), self.ws.peer_ptrs(r_f1), self.ws.peer_ptrs(r_f2),
+                                         self.ws.peer_ptrs(r_out)], dtype=torch.int64)
         self.local_sync = torch.zeros(4, dtype=torch.int32, device=device)
+        self.local_sync_split = torch.zeros(4, dtype=torch.int32, device=device)
         self.wait_cycles = int(envs.B200_PEER_WAIT_ITERS) * 200  # iteration budget expressed in SM cycles
         torch.cuda.synchronize(device)
         group.barrier()
@@ -68,10 +84,18 @@ class FusedRowParallelNorm:
         rpr = rows_per_rank(T, self.tp)
         if self.cuda:
             assert T <= self.max_tokens
-            ops._launches += 1
-            torch.ops.b200.gemm_ar_norm(x, weight, residual_shard, norm_weight, eps, self.ptrs, self.tp, self.rank,
-                                        rpr, self.rows_cap, self.rb_cap, self.local_sync, add_residual,
-                                        self.wait_cycles)
+            if self.kernel == "mono":
+                ops._launches += 1
+                torch.ops.b200.gemm_ar_norm(x, weight, residual_shard, norm_weight, eps, self.ptrs, self.tp, self.rank,
+                                            rpr, self.rows_cap, self.rb_cap, self.local_sync, add_residual,
+                                            self.wait_cycles)
+                return self.out[:T]
+            ops._launches += 2
+            torch.ops.b200.gemm_row_scatter(x, weight, self.ptrs_scatter, self.tp, self.rank, rpr, self.rows_cap,
+                                            self.local_sync_split)
+            torch.ops.b200.ar_norm_gather(residual_shard, norm_weight, eps, self.ptrs_gather, T, self.hidden, self.tp,
+                                          self.rank, rpr, self.rows_cap, self.local_sync_split, add_residual,
+                                          self.wait_cycles)
             return self.out[:T]
         # CPU ranks: same contract through plain collectives
         part = ref.gemm(x, weight, out_dtype=torch.float32)
@@ -88,6 +112,49 @@ class FusedRowParallelNorm:
         if normed.shape[0] < rpr:
             normed = torch.cat([normed, normed.new_zeros(rpr - normed.shape[0], normed.shape[1])])
         return self.group.all_gather(normed.contiguous(), 0)[:T]
+
+
+    def self_test(self, tokens=(8, 300)) -> tuple[bool, str]:
+        """Runs the fused path on random data at this world size and compares it with an fp32 statement of the same
+        contract built from all-gathered inputs.  Returns (ok, reason); the verdict is the same on every rank.  A
+        failed or timed-out kernel leaves the context usable (bounded waits set the status word, cleared here)."""
+        if not self.cuda or self.tp == 1:
+            return True, ""
+        import torch.distributed as dist
+
+        ok, why = True, ""
+        K = 256
+        gen = torch.Generator(device="cpu").manual_seed(4321)
+        for T in tokens:
+            T = min(T, self.max_tokens)
+            # same generator on every rank: rank r uses slice r, and knows everybody's inputs
+            xs = torch.randn(self.tp, T, K, generator=gen).to(self.device, self.dtype)
+            wsl = (torch.randn(self.tp, self.hidden, K, generator=gen) * 0.05).to(self.device, self.dtype)
+            res_full = torch.randn(self.tp * rows_per_rank(T, self.tp), self.hidden, generator=gen).to(self.device, self.dtype)
+            nw = torch.randn(self.hidden, generator=gen).to(self.device, self.dtype)
+            rpr = rows_per_rank(T, self.tp)
+            res = res_full[self.rank * rpr:(self.rank + 1) * rpr].clone()
+            got = self(xs[self.rank].contiguous(), wsl[self.rank].contiguous(), res, nw, 1e-5).float().clone()
+            part = sum((xs[r].float() @ wsl[r].float().t()).to(self.dtype).float() for r in range(self.tp))
+            new_res = (part + res_full[:T].float()).to(self.dtype)
+            want = ref.rms_norm(new_res, nw, 1e-5).float()
+            torch.cuda.synchronize(self.device)
+            err = float((got - want).abs().max())
+            lim = 0.06 * max(1.0, float(want.abs().max()))
+            n_mine = max(0, min(rpr, T - self.rank * rpr))
+            err_res = float((res[:n_mine].float() - new_res[self.rank * rpr:self.rank * rpr + n_mine].float()).abs().max()) if n_mine else 0.0
+            if not (err <= lim and err_res <= lim):
+                ok, why = False, f"numeric mismatch at T={T}: out {err:.3g}, residual {err_res:.3g} (limit {lim:.3g})"
+        try:
+            ops.check_kernel_status(self.device.index or 0)
+        except RuntimeError as e:
+            ok, why = False, f"kernel status: {e}"
+        flag = torch.tensor([1 if ok else 0], device=self.device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group.device_pg)
+        all_ok = bool(flag.item())
+        if not all_ok and ok:
+            why = "another rank failed the check"
+        return all_ok, why
 
 
 _SHARED: dict = {}

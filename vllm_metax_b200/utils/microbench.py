@@ -130,22 +130,53 @@ def bench_elementwise(t: Timer, T, H, I) -> dict:
     return res
 
 
+def graph_ms(calls: list, replays: int = 7) -> float:
+    """Device time per call of a list of launches replayed from ONE CUDA graph (no host launch gaps: the way a
+    decode step runs).  The caller rotates the calls over enough distinct operands to exceed L2."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for c in calls:
+            c()
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for c in calls:
+            c()
+    ts = []
+    for _ in range(replays):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) / len(calls))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
 def bench_skinny(t: Timer) -> dict:
     """Decode-batch GEMMs of Llama-3.1-8B at TP 1 and TP 8 shard sizes: the stream-K CTA-pair kernel (force_bn 2000)
-    against the cluster split-K kernel (1004), the plain 128-wide tile kernel (128) and cuBLAS."""
+    against the cluster split-K kernel (1004), the plain 128-wide tile kernel (128) and cuBLAS.  Times are per launch
+    inside a replayed CUDA graph (how decode steps run), weights rotating through more copies than L2 holds."""
     H, I = 4096, 14336
     res = {}
     for tp in (1, 8):
         shapes = {"qkv": (6144 // tp, H), "o": (H, H // tp), "gate_up": (2 * I // tp, H), "down": (H, I // tp)}
         for M in (32, 256):
             for name, (N, K) in shapes.items():
+                # weights rotate over enough copies to exceed L2 (126 MB); one graph replays 4 rounds of them
+                R = max(2, min(24, (300 << 20) // (N * K * 2) + 1))
                 a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
-                w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.02
+                ws = [torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(R)]
                 out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
                 row = {}
                 for label, fb in (("streamk", 2000), ("splitk4", 1004), ("tile128", 128 if M > 64 else -32)):
-                    row[label + "_ms"] = round(t(lambda: ops.gemm(a, w, out=out, force_bn=fb)), 4)
-                row["cublas_ms"] = round(t(lambda: torch.mm(a, w.t(), out=out)), 4)
+                    calls = [(lambda w=w, fb=fb: ops.gemm(a, w, out=out, force_bn=fb)) for _ in range(4) for w in ws]
+                    row[label + "_ms"] = round(graph_ms(calls), 4)
+                calls = [(lambda w=w: torch.mm(a, w.t(), out=out)) for _ in range(4) for w in ws]
+                row["cublas_ms"] = round(graph_ms(calls), 4)
                 row["weights_gbs_streamk"] = round(N * K * 2 / row["streamk_ms"] / 1e6, 1)
                 res[f"tp{tp}_{name}_M{M}_{N}x{K}"] = row
     return res

@@ -61,6 +61,7 @@ def main() -> None:
     ap.add_argument("--inter", type=int, default=14336)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--skip-moe", action="store_true")
+    ap.add_argument("--only", default="", help="comma list of sections: row,ag,allreduce,moe (default: all)")
     ap.add_argument("--p2p", action="store_true", help="also measure raw peer-copy bandwidth")
     a = ap.parse_args()
 
@@ -78,17 +79,23 @@ def main() -> None:
     H, I = a.hidden, a.inter
     res: dict = {"world": world}
     bf = torch.bfloat16
+    only = set(x for x in a.only.split(",") if x)
+    want = lambda sec: not only or sec in only      # noqa: E731
     fused = FusedRowParallelNorm(g, dev, max(a.tokens), H, bf)
     nw = torch.ones(H, dtype=bf, device=dev)
 
-    for T in a.tokens:
+    for T in (a.tokens if want("row") else []):
         for name, K in (("o_proj", H // world), ("down_proj", I // world)):
             x = torch.randn(T, K, dtype=bf, device=dev)
             w = torch.randn(H, K, dtype=bf, device=dev) * 0.02
             rpr = rows_per_rank(T, world)
             shard = torch.zeros(rpr, H, dtype=bf, device=dev)
             full_res = torch.zeros(T, H, dtype=bf, device=dev)
+            fused.kernel = "split"     # GEMM with row-scatter epilogue + reduce / norm / all-gather kernel
             t_f = timed(lambda: fused(x, w, shard, nw, 1e-5, add_residual=True), a.iters, pg)
+            fused.kernel = "mono"      # the single-kernel variant
+            t_m = timed(lambda: fused(x, w, shard, nw, 1e-5, add_residual=True), a.iters, pg)
+            fused.kernel = "split"
 
             def baseline():
                 y = ops.gemm(x, w)
@@ -100,13 +107,14 @@ def main() -> None:
             # bytes this GPU sends: partial rows to their owners (reduce-scatter) + its normalised rows to every peer
             link = 2.0 * (T * H * 2) * (world - 1) / world
             r = roof_ms(flops, link)
-            res[f"gemm_ar_norm_{name}_T{T}"] = {"fused_ms": round(t_f, 4), "nccl_baseline_ms": round(t_b, 4),
+            res[f"gemm_ar_norm_{name}_T{T}"] = {"fused_ms": round(t_f, 4), "single_kernel_ms": round(t_m, 4),
+                                               "nccl_baseline_ms": round(t_b, 4),
                                                "roofline_ms": round(r, 4), "of_roofline": round(r / t_f, 3),
                                                "speedup_vs_nccl": round(t_b / t_f, 2)}
         ops.check_kernel_status(dev.index or 0)
 
     # ---- all-gather -> GEMM (qkv-like and gate_up-like column shards)
-    for T in a.tokens:
+    for T in (a.tokens if want("ag") else []):
         rows = (T // world + 127) // 128 * 128
         if rows == 0:
             continue
@@ -134,7 +142,7 @@ def main() -> None:
         ag.close()
 
     # ---- stand-alone all-reduce (one-shot / two-shot peer stores) against NCCL, small to medium messages
-    if world > 1:
+    if world > 1 and want("allreduce"):
         from vllm_metax_b200.parallel.custom_allreduce import CrossRankRMSNorm, CustomAllReduce
 
         car = CustomAllReduce(g, dev, 8 << 20)
@@ -183,7 +191,7 @@ def main() -> None:
         ws.close()
 
     # ---- expert-parallel dispatch + combine (identity experts: measures the exchange itself)
-    if not a.skip_moe and world > 1:
+    if not a.skip_moe and world > 1 and want("moe"):
         E, topk, Hm = 32 * world, 8, 7168
         for T in (128, 1024):
             for quant in (False, True):
