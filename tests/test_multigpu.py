@@ -114,7 +114,7 @@ def _fused_ar_worker(rank, world, kernel="split"):
         want = ref.rms_norm(new_res, nw, 1e-5)
         torch.testing.assert_close(out.float().cpu(), want.float(), rtol=3e-2, atol=5e-2)   # split-K rounds every K range to bf16
         torch.testing.assert_close(res[:n_mine].float().cpu(), new_res[rank * rpr: rank * rpr + n_mine].float(),
-                                   rtol=2e-2, atol=2e-2)
+                                   rtol=3e-2, atol=3e-2)
         g.barrier()
 
 
@@ -124,22 +124,17 @@ def test_fused_gemm_allreduce_norm_2gpu(kernel):
     _launch(_fused_ar_worker, _world(), kernel)
 
 
-def _tp_engine_worker(rank, world, fused, want=None):
+def _tp_engine_worker(rank, world, fused, path, want=None):
     os.environ["B200_FUSED_TP_COLLECTIVES"] = "1" if fused else "0"
     os.environ["B200_FUSED_TP_MIN_TOKENS"] = "0"          # the small test batches must still take the fused kernel
-    from vllm_metax_b200 import LLM, ModelConfig, SamplingParams
+    from vllm_metax_b200 import LLM, SamplingParams
     from vllm_metax_b200 import _custom_ops as ops
     from vllm_metax_b200.parallel import state as ps
 
-    cfg = ModelConfig(architecture="LlamaForCausalLM", vocab_size=2048, hidden_size=1024, intermediate_size=2816,
-                      num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
-                      max_position_embeddings=1024, dtype=torch.bfloat16, seed=0)
-    llm = LLM(cfg, device="cuda", tensor_parallel_size=world, block_size=64, max_model_len=512, max_num_seqs=8,
-              max_num_batched_tokens=1024, num_gpu_blocks=128)
+    llm = LLM(path, device="cuda", dtype="bfloat16", tensor_parallel_size=world, block_size=64, max_model_len=512,
+              max_num_seqs=8, max_num_batched_tokens=1024, num_gpu_blocks=128)
     assert llm.engine.runner.fused_tp == fused
-    g = torch.Generator().manual_seed(5)
-    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (100, 33, 200)]
-    outs = llm.generate(prompts, SamplingParams(max_tokens=16, ignore_eos=True))
+    outs = llm.generate(_tp_prompts(), SamplingParams(max_tokens=16, ignore_eos=True))
     assert all(len(o.outputs[0].token_ids) == 16 for o in outs)
     torch.cuda.synchronize()
     ops.check_kernel_status(rank)
@@ -149,25 +144,36 @@ def _tp_engine_worker(rank, world, fused, want=None):
     assert bool((gathered == toks[None]).all())
     llm.engine.runner.graphs.clear()
     if want is not None:
-        # against ONE GPU on the same weights: another reduction order (bf16), so the first tokens agree and the
+        # against ONE GPU on the same checkpoint: another reduction order (bf16), so the first tokens agree and the
         # rest mostly; a wrong-but-consistent collective would agree on neither
         got = [list(o.outputs[0].token_ids) for o in outs]
         assert [g_[0] for g_ in got] == [w[0] for w in want], (got, want)
-        same = sum(a == b for g_, w in zip(got, want) for a, b in zip(g_, w))
-        assert same >= 0.7 * sum(len(w) for w in want), (got, want)
+        # once one token differs the continuations part ways, so count the common prefixes
+        prefix = [next((i for i, (a, b) in enumerate(zip(g_, w)) if a != b), len(w)) for g_, w in zip(got, want)]
+        assert min(prefix) >= 2 and sum(prefix) >= 3 * len(want), (prefix, got, want)
 
 
-def _tp_single_gpu_tokens():
-    from vllm_metax_b200 import LLM, ModelConfig, SamplingParams
-
-    cfg = ModelConfig(architecture="LlamaForCausalLM", vocab_size=2048, hidden_size=1024, intermediate_size=2816,
-                      num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
-                      max_position_embeddings=1024, dtype=torch.bfloat16, seed=0)
-    llm = LLM(cfg, device="cuda", block_size=64, max_model_len=512, max_num_seqs=8, max_num_batched_tokens=1024,
-              num_gpu_blocks=128)
+def _tp_prompts():
     g = torch.Generator().manual_seed(5)
-    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (100, 33, 200)]
-    toks = [list(o.outputs[0].token_ids) for o in llm.generate(prompts, SamplingParams(max_tokens=16, ignore_eos=True))]
+    return [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (100, 33, 200)]
+
+
+def _tp_checkpoint(path):
+    """A small random Llama checkpoint in Hugging Face format, so that one GPU and the TP ranks load the same weights."""
+    tf = pytest.importorskip("transformers")
+    torch.manual_seed(0)
+    cfg = tf.LlamaConfig(vocab_size=2048, hidden_size=1024, intermediate_size=2816, num_hidden_layers=3,
+                         num_attention_heads=8, num_key_value_heads=2, head_dim=128, max_position_embeddings=1024,
+                         rms_norm_eps=1e-5, tie_word_embeddings=False)
+    tf.LlamaForCausalLM(cfg).save_pretrained(path)
+
+
+def _tp_single_gpu_tokens(path):
+    from vllm_metax_b200 import LLM, SamplingParams
+
+    llm = LLM(path, device="cuda", dtype="bfloat16", block_size=64, max_model_len=512, max_num_seqs=8,
+              max_num_batched_tokens=1024, num_gpu_blocks=128)
+    toks = [list(o.outputs[0].token_ids) for o in llm.generate(_tp_prompts(), SamplingParams(max_tokens=16, ignore_eos=True))]
     llm.engine.runner.graphs.clear()
     del llm
     torch.cuda.empty_cache()
@@ -176,9 +182,11 @@ def _tp_single_gpu_tokens():
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("fused", [False, True])
-def test_tp2_engine_generates(fused):
-    want = _tp_single_gpu_tokens()
-    _launch(_tp_engine_worker, _world() if fused else 2, fused, want)
+def test_tp2_engine_generates(fused, tmp_path):
+    path = str(tmp_path)
+    _tp_checkpoint(path)
+    want = _tp_single_gpu_tokens(path)
+    _launch(_tp_engine_worker, _world() if fused else 2, fused, path, want, timeout=240)
 
 
 def _moe_a2a_worker(rank, world, quant):

@@ -22,6 +22,47 @@
 
 namespace b200 {
 
+// every source's pushes for this call have landed (bounded); returns false after a timeout
+__device__ __forceinline__ bool arn_wait_pushes(const ArNormParams& p, uint32_t epoch, int* s_ok) {
+  if (threadIdx.x == 0) *s_ok = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < p.tp) {
+    uint32_t seen = 0;
+    if (!wait_flag_ge(p.flag1[p.rank] + threadIdx.x, epoch, p.wait_cycles, &seen)) {
+      report_status(p.status, kWaitTimeout, 180, (int)epoch, (int)seen);
+      *s_ok = 0;
+    }
+  }
+  __syncthreads();
+  return *s_ok != 0;
+}
+
+// close: the last CTA publishes "my rows are in your output buffer" and waits for every owner's
+__device__ __forceinline__ void arn_close(const ArNormParams& p, uint32_t epoch, int* s_ok) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const uint32_t ticket = atomicAdd(&p.local_sync[2], 1u);
+    *s_ok = (ticket == gridDim.x - 1) ? 2 : 0;
+  }
+  __syncthreads();
+  if (*s_ok == 2) {
+    if ((int)threadIdx.x < p.tp) {
+      __threadfence_system();
+      st_release_sys(p.flag2[threadIdx.x] + p.rank, epoch);
+      uint32_t seen = 0;
+      if (!wait_flag_ge(p.flag2[p.rank] + threadIdx.x, epoch, p.wait_cycles, &seen))
+        report_status(p.status, kWaitTimeout, 181, (int)epoch, (int)seen);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      p.local_sync[2] = 0;
+      p.local_sync[3] = epoch;
+    }
+  }
+}
+
+// General widths: the summed row is staged in shared memory between the two passes.
 template <typename T>
 __global__ void __launch_bounds__(256)
 ar_norm_gather_kernel(const ArNormParams p) {
@@ -32,19 +73,7 @@ ar_norm_gather_kernel(const ArNormParams p) {
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(p.local_sync + 3) + 1u;
   const int my_rows = max(0, min(p.rows_per_rank, p.T - p.rank * p.rows_per_rank));
   const int nvec = p.H >> 3;
-
-  // every source's pushes for this call have landed
-  if (threadIdx.x == 0) s_ok = 1;
-  __syncthreads();
-  if ((int)threadIdx.x < p.tp) {
-    uint32_t seen = 0;
-    if (!wait_flag_ge(p.flag1[p.rank] + threadIdx.x, epoch, p.wait_cycles, &seen)) {
-      report_status(p.status, kWaitTimeout, 180, (int)epoch, (int)seen);
-      s_ok = 0;
-    }
-  }
-  __syncthreads();
-  const bool ok = s_ok != 0;
+  const bool ok = arn_wait_pushes(p, epoch, &s_ok);
 
   const char* mine = static_cast<const char*>(p.recv[p.rank]);
   const size_t slot_bytes = (size_t)p.rows_cap * p.H * sizeof(T);
@@ -90,29 +119,80 @@ ar_norm_gather_kernel(const ArNormParams p) {
     }
     __syncthreads();                                 // `row` and `red` are rewritten by the next row
   }
+  arn_close(p, epoch, &s_ok);
+}
 
-  // close: last CTA publishes "my rows are in your output buffer" and waits for every owner's
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence_system();
-    const uint32_t ticket = atomicAdd(&p.local_sync[2], 1u);
-    s_ok = (ticket == gridDim.x - 1) ? 2 : 0;
-  }
-  __syncthreads();
-  if (s_ok == 2) {
-    if ((int)threadIdx.x < p.tp) {
-      __threadfence_system();
-      st_release_sys(p.flag2[threadIdx.x] + p.rank, epoch);
-      uint32_t seen = 0;
-      if (!wait_flag_ge(p.flag2[p.rank] + threadIdx.x, epoch, p.wait_cycles, &seen))
-        report_status(p.status, kWaitTimeout, 181, (int)epoch, (int)seen);
+// Rows of 128 * VPT vectors (H = 1024 * VPT): 128 threads per row, every load of the row - all sources and the
+// residual - in flight before the first use, the summed row kept in registers between the two passes.
+template <typename T, int VPT>
+__global__ void __launch_bounds__(128)
+ar_norm_gather_reg_kernel(const ArNormParams p) {
+  __shared__ float red[32];
+  __shared__ int s_ok;
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(p.local_sync + 3) + 1u;
+  const int my_rows = max(0, min(p.rows_per_rank, p.T - p.rank * p.rows_per_rank));
+  const bool ok = arn_wait_pushes(p, epoch, &s_ok);
+
+  const char* mine = static_cast<const char*>(p.recv[p.rank]);
+  const size_t slot_bytes = (size_t)p.rows_cap * p.H * sizeof(T);
+  for (int r = blockIdx.x; r < my_rows && ok; r += gridDim.x) {
+    const size_t row_off = (size_t)r * p.H * sizeof(T);
+    uint4* res = reinterpret_cast<uint4*>(static_cast<T*>(p.residual) + (size_t)r * p.H);
+    uint4 part[kMaxRanks][VPT], rv[VPT];
+#pragma unroll
+    for (int s = 0; s < kMaxRanks; ++s)
+#pragma unroll
+      for (int i = 0; i < VPT; ++i)
+        part[s][i] = s < p.tp ? __ldcg(reinterpret_cast<const uint4*>(mine + s * slot_bytes + row_off) + threadIdx.x + i * 128)
+                              : make_uint4(0, 0, 0, 0);
+    if (p.add_residual) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) rv[i] = res[threadIdx.x + i * 128];
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      p.local_sync[2] = 0;
-      p.local_sync[3] = epoch;
+    float f[VPT][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[i][e] = 0.f;
+#pragma unroll
+      for (int s = 0; s < kMaxRanks; ++s) {
+        if (s < p.tp) {                              // rank order: the same bits whoever owns the row
+          float g[8];
+          unpack8<T>(part[s][i], g);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[i][e] += g[e];
+        }
+      }
+      if (p.add_residual) {
+        float g[8];
+        unpack8<T>(rv[i], g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[i][e] += g[e];
+      }
+      const uint4 packed = pack8<T>(f[i]);
+      res[threadIdx.x + i * 128] = packed;
+      unpack8<T>(packed, f[i]);                      // the norm sees the rounded residual
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += f[i][e] * f[i][e];
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)p.H + p.eps);
+    const size_t grow = (size_t)(p.rank * p.rows_per_rank + r) * p.H;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      float w[8];
+      unpack8<T>(reinterpret_cast<const uint4*>(p.norm_weight)[threadIdx.x + i * 128], w);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[i][e] = f[i][e] * inv * w[e];
+      const uint4 y = pack8<T>(f[i]);
+      for (int d = 0; d < p.tp; ++d) {
+        const int dst = (p.rank + d) % p.tp;
+        reinterpret_cast<uint4*>(static_cast<T*>(p.out[dst]) + grow)[threadIdx.x + i * 128] = y;
+      }
     }
   }
+  arn_close(p, epoch, &s_ok);
 }
 
 // Returns 0, -1 (H not a multiple of 8 / too wide for the row stage), -2 (bad dtype).
@@ -125,20 +205,25 @@ int ar_norm_gather(const ArNormParams& p, int dtype, cudaStream_t stream) {
   if (dev < 0 || dev >= 64) return -1;
   if (sms[dev] == 0) cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
   const int my_rows_max = p.rows_per_rank;
-  int grid = my_rows_max < 4 * sms[dev] ? my_rows_max : 4 * sms[dev];
+  int grid = my_rows_max < 8 * sms[dev] ? my_rows_max : 8 * sms[dev];
   grid = grid < 1 ? 1 : grid;
   const size_t sm = (size_t)p.H * 2;
-  if (dtype == 0) {
-    if (sm > 48 * 1024)
-      cudaFuncSetAttribute(ar_norm_gather_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-    ar_norm_gather_kernel<__nv_bfloat16><<<grid, 256, sm, stream>>>(p);
-  } else if (dtype == 1) {
-    if (sm > 48 * 1024)
-      cudaFuncSetAttribute(ar_norm_gather_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-    ar_norm_gather_kernel<__half><<<grid, 256, sm, stream>>>(p);
-  } else {
-    return -2;
-  }
+  const int vpt = p.H % 1024 == 0 ? p.H / 1024 : 0;
+#define B200_ARN(T)                                                                                               \
+  do {                                                                                                            \
+    if (vpt == 1) ar_norm_gather_reg_kernel<T, 1><<<grid, 128, 0, stream>>>(p);                                   \
+    else if (vpt == 2) ar_norm_gather_reg_kernel<T, 2><<<grid, 128, 0, stream>>>(p);                              \
+    else if (vpt == 4) ar_norm_gather_reg_kernel<T, 4><<<grid, 128, 0, stream>>>(p);                              \
+    else {                                                                                                        \
+      if (sm > 48 * 1024)                                                                                         \
+        cudaFuncSetAttribute(ar_norm_gather_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);     \
+      ar_norm_gather_kernel<T><<<grid, 256, sm, stream>>>(p);                                                     \
+    }                                                                                                             \
+  } while (0)
+  if (dtype == 0) B200_ARN(__nv_bfloat16);
+  else if (dtype == 1) B200_ARN(__half);
+  else return -2;
+#undef B200_ARN
   return 0;
 }
 

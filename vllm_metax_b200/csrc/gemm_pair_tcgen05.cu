@@ -17,6 +17,7 @@
 //   tmem_empty[a]  lives in the leader; 256 epilogue threads (both CTAs) arrive on it
 // Clusters are persistent (74 on a 148-SM part) and walk tiles M-fastest so that
 // concurrently running pairs share W tiles in L2.
+#include <cstdlib>
 #include <type_traits>
 #include "comm_fused.cuh"
 #include "gemm_epilogue.cuh"
@@ -29,23 +30,37 @@ using namespace ptx;
 constexpr int kPairBM = 256;          // tile rows (128 per CTA)
 constexpr int kPairBN = 256;          // tile cols (128 W rows loaded per CTA)
 constexpr int kPairBK = 64;
-constexpr int kPairStages = 6;
 
+constexpr int kPairRowPitch = kPairBN * 2 + 16;   // staged output row: 512 B + 16 B so that 8 rows hit 32 banks
+
+// STAGES-deep operand ring; BULK adds a row-major staging tile for the bulk-store epilogue.
+template <int STAGES, bool BULK>
 struct PairSmem {
   static constexpr int kABytes = 128 * kPairBK * 2;
   static constexpr int kBBytes = 128 * kPairBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;             // per CTA
-  static constexpr int kBarOffset = kPairStages * kStageBytes;
-  static constexpr int kTotal = kBarOffset + (2 * kPairStages + 4) * 8 + 16;
+  static constexpr int kOutStage = STAGES * kStageBytes;
+  static constexpr int kBarOffset = kOutStage + (BULK ? 128 * kPairRowPitch : 0);
+  static constexpr int kTotal = kBarOffset + (2 * STAGES + 4) * 8 + 16;
   static constexpr int kDyn = kTotal + 1024;
 };
 
-template <typename T>
+// 1-D bulk copy shared -> global (16-byte aligned, size a multiple of 16); completion tracked by bulk groups.
+__device__ __forceinline__ void bulk_store_1d(void* gdst, const void* ssrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(ssrc)), "r"(bytes)
+               : "memory");
+}
+
+// BULK epilogue (used with the row scatter): a thread converts its output row of the tile into shared memory and
+// sends it as ONE bulk copy of up to 512 bytes, so rows that cross NVLink travel as large writes instead of
+// 16-byte stores.
+template <typename T, int STAGES, bool BULK>
 __global__ void __launch_bounds__(192, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  T* __restrict__ C, const T* __restrict__ bias, const T* __restrict__ residual, int M, int N, int K,
                  int ldc, int ldr, int epi, StatusWord* status, const __grid_constant__ RowScatter sc) {
-  using L = PairSmem;
+  using L = PairSmem<STAGES, BULK>;
+  constexpr int kPairStages = STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
@@ -165,6 +180,47 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after_sync();
       const int row = tm * kPairBM + (int)rank * 128 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kPairBN;
+      if constexpr (BULK) {
+        uint8_t* my_row = smem + L::kOutStage + (quarter * 32 + lane) * kPairRowPitch;
+        tma_store_wait_read<0>();                  // this thread's previous row has left shared memory
+#pragma unroll 1
+        for (int c = 0; c < kPairBN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            float f[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[v * 8 + i]);
+            if (bias && tn * kPairBN + c + v * 8 + 8 <= N) {
+              float b[8];
+              unpack8<T>(*reinterpret_cast<const uint4*>(bias + tn * kPairBN + c + v * 8), b);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) f[i] += b[i];
+            }
+            *reinterpret_cast<uint4*>(my_row + (c + v * 8) * 2) = pack8<T>(f);
+          }
+        }
+        // accumulators are in shared memory: the tensor core may reuse the buffer while the row travels
+        tc_fence_before_sync();
+        mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
+        const int col0 = tn * kPairBN;
+        const int ncols = min(kPairBN, N - col0);
+        if (row < M && ncols > 0) {
+          T* drow;
+          if (sc.tp > 0) {
+            const int owner = row / sc.rows_per_rank;
+            drow = reinterpret_cast<T*>(sc.recv[owner]) +
+                   (size_t)(sc.src_rank * sc.rows_cap + (row - owner * sc.rows_per_rank)) * ldc;
+          } else {
+            drow = C + (size_t)row * ldc;
+          }
+          fence_proxy_async();                     // my generic-proxy writes are visible to the bulk copy
+          bulk_store_1d(drow + col0, my_row, (uint32_t)ncols * 2);
+        }
+        tma_store_commit();
+      } else {
 #pragma unroll 1
       for (int c = 0; c < kPairBN; c += 32) {
         uint32_t r[32];
@@ -184,9 +240,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_before_sync();
       mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
+      }
     }
   }
 
+  if constexpr (BULK) {
+    if (warp >= 2) tma_store_wait<0>();          // every row of this thread has been written out
+  }
   tc_fence_before_sync();
   __syncthreads();
   cluster_sync();                                // no CTA leaves while its peer may still touch it
@@ -209,7 +269,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
-template <typename T>
+template <typename T, int STAGES, bool BULK>
 static void launch_pair(const void* A, const void* W, void* C, const void* bias, const void* residual, int M, int N,
                         int K, int lda, int ldw, int ldc, int ldr, int epi, cudaStream_t stream, StatusWord* status,
                         const RowScatter& sc) {
@@ -217,25 +277,28 @@ static void launch_pair(const void* A, const void* W, void* C, const void* bias,
       std::is_same<T, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap tmA = make_tmap_2d(A, dt, 2, M, K, lda, 128, kPairBK);
   CUtensorMap tmB = make_tmap_2d(W, dt, 2, N, K, ldw, 128, kPairBK);
-  auto kern = gemm_pair_kernel<T>;
-  static bool set = false;
-  if (!set) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::kDyn);
-    set = true;
+  using L = PairSmem<STAGES, BULK>;
+  static_assert(L::kDyn <= 232448, "shared memory budget exceeded");
+  auto kern = gemm_pair_kernel<T, STAGES, BULK>;
+  // kernel attributes and SM counts are per device
+  static bool set[64] = {};
+  static int sms_dev[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev = dev < 0 || dev >= 64 ? 0 : dev;
+  if (!set[dev]) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDyn);
+    set[dev] = true;
   }
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  }
+  if (sms_dev[dev] == 0) cudaDeviceGetAttribute(&sms_dev[dev], cudaDevAttrMultiProcessorCount, dev);
+  const int sms = sms_dev[dev];
   const int tiles = ceil_div(M, kPairBM) * ceil_div(N, kPairBN);
   int clusters = sms / 2;
   if (tiles < clusters) clusters = tiles;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * clusters, 1, 1);
   cfg.blockDim = dim3(192, 1, 1);
-  cfg.dynamicSmemBytes = PairSmem::kDyn;
+  cfg.dynamicSmemBytes = L::kDyn;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -254,12 +317,21 @@ void gemm_tn_pair(const void* A, const void* W, void* C, const void* bias, const
   if (M <= 0 || N <= 0) return;
   RowScatter sc{};
   if (scatter) sc = *scatter;
-  if (dtype == 0)
-    launch_pair<__nv_bfloat16>(A, W, C, bias, residual, M, N, K, lda, ldw, ldc, ldr, epi, stream,
-                               reinterpret_cast<StatusWord*>(status), sc);
-  else
-    launch_pair<__half>(A, W, C, bias, residual, M, N, K, lda, ldw, ldc, ldr, epi, stream,
-                        reinterpret_cast<StatusWord*>(status), sc);
+  StatusWord* st = reinterpret_cast<StatusWord*>(status);
+  // scattered rows leave as bulk copies (B200_SCATTER_BULK=0: plain 16-byte stores, for comparison)
+  static const bool bulk_default = [] {
+    const char* e = std::getenv("B200_SCATTER_BULK");
+    return e == nullptr || std::atoi(e) != 0;
+  }();
+  const bool bulk = sc.tp > 0 && bulk_default && epi == 0 && residual == nullptr && N % 8 == 0 && ldc % 8 == 0;
+#define B200_PAIR(T)                                                                                              \
+  do {                                                                                                            \
+    if (bulk) launch_pair<T, 4, true>(A, W, C, bias, residual, M, N, K, lda, ldw, ldc, ldr, epi, stream, st, sc);  \
+    else launch_pair<T, 6, false>(A, W, C, bias, residual, M, N, K, lda, ldw, ldc, ldr, epi, stream, st, sc);      \
+  } while (0)
+  if (dtype == 0) B200_PAIR(__nv_bfloat16);
+  else B200_PAIR(__half);
+#undef B200_PAIR
 }
 
 }  // namespace b200

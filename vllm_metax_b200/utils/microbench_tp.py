@@ -103,12 +103,21 @@ def main() -> None:
                 ops.fused_add_rms_norm(y, full_res, nw, 1e-5)
 
             t_b = timed(baseline, a.iters, pg)
+            # the two launches of the split path on their own, and the same GEMM with an ordinary local epilogue
+            t_g = timed(lambda: torch.ops.b200.gemm_row_scatter(x, w, fused.ptrs_scatter, world, rank, rpr,
+                                                                 fused.rows_cap, fused.local_sync_split), a.iters, pg)
+            t_n = timed(lambda: torch.ops.b200.ar_norm_gather(shard, nw, 1e-5, fused.ptrs_gather, T, H, world, rank,
+                                                               rpr, fused.rows_cap, fused.local_sync_split, True,
+                                                               fused.wait_cycles), a.iters, pg)
+            y_loc = torch.empty(T, H, dtype=bf, device=dev)
+            t_l = timed(lambda: ops.gemm(x, w, out=y_loc), a.iters, pg)
             flops = 2.0 * T * H * K
             # bytes this GPU sends: partial rows to their owners (reduce-scatter) + its normalised rows to every peer
             link = 2.0 * (T * H * 2) * (world - 1) / world
             r = roof_ms(flops, link)
             res[f"gemm_ar_norm_{name}_T{T}"] = {"fused_ms": round(t_f, 4), "single_kernel_ms": round(t_m, 4),
-                                               "nccl_baseline_ms": round(t_b, 4),
+                                               "nccl_baseline_ms": round(t_b, 4), "scatter_gemm_ms": round(t_g, 4),
+                                               "reduce_norm_gather_ms": round(t_n, 4), "local_gemm_ms": round(t_l, 4),
                                                "roofline_ms": round(r, 4), "of_roofline": round(r / t_f, 3),
                                                "speedup_vs_nccl": round(t_b / t_f, 2)}
         ops.check_kernel_status(dev.index or 0)
