@@ -113,8 +113,9 @@ def _fused_ar_worker(rank, world, kernel="split"):
         new_res = total.to(torch.bfloat16)
         want = ref.rms_norm(new_res, nw, 1e-5)
         torch.testing.assert_close(out.float().cpu(), want.float(), rtol=3e-2, atol=5e-2)   # split-K rounds every K range to bf16
+        # one 16-bit rounding per partial (tp of them, times the K ranges of the single-kernel path) around |x| ~ 4
         torch.testing.assert_close(res[:n_mine].float().cpu(), new_res[rank * rpr: rank * rpr + n_mine].float(),
-                                   rtol=3e-2, atol=3e-2)
+                                   rtol=3e-2, atol=2e-2 + 5e-3 * world)
         g.barrier()
 
 

@@ -182,6 +182,63 @@ def bench_skinny(t: Timer) -> dict:
     return res
 
 
+def bench_decode_layer(tp: int, batch: int = 256, ctx: int = 1100) -> dict:
+    """Every launch of one Llama-3.1-8B decoder layer at a decode step of `batch` sequences, at the shard sizes of
+    tensor-parallel degree `tp` (row-parallel GEMMs with a local epilogue), each timed inside a replayed CUDA graph
+    with operands rotating through more copies than L2 holds.  Shows where a decode step's time goes."""
+    H, I, D = 4096, 14336, 128
+    hq, hkv = 32 // tp, max(1, 8 // tp)
+    bf = torch.bfloat16
+    res = {}
+
+    def rot(nbytes):
+        return max(2, min(16, (300 << 20) // max(1, nbytes) + 1))
+
+    def gemm_row(name, N, K, silu=False):
+        R = rot(N * K * 2)
+        a = torch.randn(batch, K, device=DEV, dtype=bf)
+        ws = [torch.randn(N, K, device=DEV, dtype=bf) * 0.02 for _ in range(R)]
+        if silu:
+            calls = [(lambda w=w: ops.gemm_silu_mul(a, w)) for _ in range(3) for w in ws]
+        else:
+            out = torch.empty(batch, N, device=DEV, dtype=bf)
+            calls = [(lambda w=w: ops.gemm(a, w, out=out)) for _ in range(3) for w in ws]
+        ours = graph_ms(calls)
+        out2 = torch.empty(batch, N, device=DEV, dtype=bf)
+        lib = graph_ms([(lambda w=w: torch.mm(a, w.t(), out=out2)) for _ in range(3) for w in ws])
+        res[name] = {"ms": round(ours, 4), "cublas_ms": round(lib, 4), "weights_gbs": round(N * K * 2 / ours / 1e6, 1)}
+
+    gemm_row("qkv_gemm", (hq + 2 * hkv) * D, H)
+    gemm_row("o_gemm", H, hq * D)
+    gemm_row("gate_up_silu_gemm", 2 * I // tp, H, silu=True)
+    gemm_row("down_gemm", H, I // tp)
+    # norm (+ residual)
+    x = torch.randn(batch, H, device=DEV, dtype=bf)
+    r = torch.randn_like(x)
+    w = torch.ones(H, device=DEV, dtype=bf)
+    res["add_rmsnorm"] = {"ms": round(graph_ms([lambda: ops.fused_add_rms_norm(x, r, w, 1e-5)] * 20), 4)}
+    # rope + cache write
+    qkv = torch.randn(batch, (hq + 2 * hkv) * D, device=DEV, dtype=bf)
+    pos = torch.full((batch,), ctx, device=DEV)
+    cs = ref.build_rope_cache(D, 2048, 500000.0).to(DEV)
+    nblk = (ctx + 127) // 128
+    caches = [torch.randn(batch * nblk + 1, 2, 128, hkv, D, device=DEV, dtype=bf) for _ in range(rot(batch * nblk * 2 * 128 * hkv * D * 2))]
+    slots = torch.arange(batch, device=DEV) * nblk * 128 + ctx - 1
+    q_, k_, v_ = qkv[:, :hq * D], qkv[:, hq * D:(hq + hkv) * D], qkv[:, (hq + hkv) * D:]
+    res["rope_cache"] = {"ms": round(graph_ms([(lambda c=c: ops.rope_and_cache(pos, q_, k_, v_, D, cs, True, c, slots))
+                                               for _ in range(5) for c in caches]), 4)}
+    # decode attention
+    bt = torch.arange(batch * nblk, device=DEV, dtype=torch.int32).view(batch, nblk)
+    sl = torch.full((batch,), ctx, device=DEV, dtype=torch.int32)
+    qd = torch.randn(batch, hq, D, device=DEV, dtype=bf)
+    od = torch.empty_like(qd)
+    att = graph_ms([(lambda c=c: ops.paged_attention_decode(qd, c, bt, sl, D ** -0.5, out=od, max_seq_len=ctx))
+                    for _ in range(3) for c in caches])
+    res["attn_decode"] = {"ms": round(att, 4), "kv_gbs": round(batch * ctx * hkv * D * 2 * 2 / att / 1e6, 1)}
+    res["layer_total_ms"] = round(sum(v["ms"] for v in res.values()) + res["add_rmsnorm"]["ms"], 4)
+    return res
+
+
 def bench_quant(t, M: int, N: int, K: int) -> dict:
     """Quantised GEMMs at one shape (TFLOP/s over 2 M N K) and the TurboQuant decode kernel (bytes of compressed
     cache streamed per second)."""
@@ -262,7 +319,7 @@ def bench_linear_attention(t: Timer) -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "gemm", "prefill", "decode", "elementwise", "quant", "linear_attention", "skinny"])
+    ap.add_argument("--op", default="all", choices=["all", "gemm", "prefill", "decode", "elementwise", "quant", "linear_attention", "skinny", "decode_layer"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
@@ -297,6 +354,9 @@ def main() -> None:
         res.update(bench_linear_attention(t))
     if a.op == "skinny":
         res.update(bench_skinny(t))
+    if a.op == "decode_layer":
+        for tp in (1, 8):
+            res[f"decode_layer_tp{tp}_b{a.batch}"] = bench_decode_layer(tp, a.batch, a.seq)
     if a.op in ("all", "elementwise"):
         for T in (8192, 256):
             for k, v in bench_elementwise(t, T, H, I).items():
