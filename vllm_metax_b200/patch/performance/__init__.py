@@ -1,2 +1,2 @@
 """Patches that only change speed."""
-from . import grouped_topk_router, speculative_decode_perf  # noqa: F401
+from . import grouped_topk_router, speculative_decode_perf, unquantized_gemm  # noqa: F401

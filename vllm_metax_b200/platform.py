@@ -159,6 +159,10 @@ class B200PlatformBase(Platform):
         from . import _custom_ops
 
         _custom_ops.load_native()
+        # the kernel names upstream layers bind at construction time, on this package's kernels
+        from .registry.c_namespace import define_c_ops
+
+        define_c_ops()
 
     # ------------------------------------------------------------------ attention
     @classmethod
@@ -215,6 +219,24 @@ class B200PlatformBase(Platform):
             cache_config.block_size = 64
         model_config = getattr(vllm_config, "model_config", None)
         compilation = getattr(vllm_config, "compilation_config", None)
+        if compilation is not None and _HAVE_VLLM:
+            # This platform's hot path is hand-written kernels behind torch custom ops, not a tracing compiler:
+            # the model runs as written (no Dynamo / Inductor pass) and decode steps are captured as whole CUDA
+            # graphs, which the attention metadata builder supports for uniform decode batches.
+            try:
+                from vllm.config.compilation import CompilationMode, CUDAGraphMode
+
+                enforce_eager = bool(getattr(model_config := getattr(vllm_config, "model_config", None),
+                                             "enforce_eager", False))
+                if getattr(compilation, "mode", None) not in (None, CompilationMode.NONE):
+                    compilation.mode = CompilationMode.NONE
+                if enforce_eager:
+                    compilation.cudagraph_mode = CUDAGraphMode.NONE
+                elif getattr(compilation, "cudagraph_mode", None) in (None, CUDAGraphMode.PIECEWISE,
+                                                                      CUDAGraphMode.FULL_AND_PIECEWISE):
+                    compilation.cudagraph_mode = CUDAGraphMode.FULL_DECODE_ONLY
+            except ImportError:      # older config layout: leave vLLM's defaults
+                pass
         if compilation is not None:
             ops_list = getattr(compilation, "_attention_ops", None)
             if isinstance(ops_list, list):

@@ -115,7 +115,34 @@ def _minimax_rms_norm_tp(self, x: torch.Tensor, *args, **kwargs):
     return rms(x2.contiguous(), self.weight.data.to(x.dtype), eps)[0].reshape(x.shape)
 
 
+def _rotary(self, positions: torch.Tensor, query: torch.Tensor, key: Optional[torch.Tensor] = None, *args, **kwargs):
+    """RoPE in place on this package's kernel (NeoX or interleaved pairing, partial rotary widths)."""
+    offsets = args[0] if args else kwargs.get("offsets")
+    if offsets is not None or kwargs.get("inverse", False):
+        return self.forward_native(positions, query, key, *args, **kwargs)
+    from .c_namespace import fp32_cos_sin
+
+    T = positions.numel()
+    q2 = query.view(T, -1)
+    k2 = key.view(T, -1) if key is not None else None
+    ops.rotary_embedding(positions.reshape(-1), q2, k2, int(self.head_size), fp32_cos_sin(self.cos_sin_cache),
+                         bool(self.is_neox_style))
+    return query, key
+
+
+def _rotary_native(self, *args, **kwargs):
+    """Multi-axis position schemes (M-RoPE, XD-RoPE) keep upstream's tensor formulation."""
+    return self.forward_native(*args, **kwargs)
+
+
 _TABLE = [
+    ("vllm.model_executor.layers.rotary_embedding.base", "RotaryEmbedding", _rotary),
+    ("vllm.model_executor.layers.rotary_embedding.llama3_rope", "Llama3RotaryEmbedding", _rotary),
+    ("vllm.model_executor.layers.rotary_embedding.linear_scaling_rope", "LinearScalingRotaryEmbedding", _rotary),
+    ("vllm.model_executor.layers.rotary_embedding.yarn_scaling_rope", "YaRNScalingRotaryEmbedding", _rotary),
+    ("vllm.model_executor.layers.rotary_embedding.deepseek_scaling_rope", "DeepseekScalingRotaryEmbedding", _rotary_native),
+    ("vllm.model_executor.layers.rotary_embedding.mrope", "MRotaryEmbedding", _rotary_native),
+    ("vllm.model_executor.layers.rotary_embedding.xdrope", "XDRotaryEmbedding", _rotary_native),
     ("vllm.model_executor.layers.activation", "SiluAndMul", _gated("silu")),
     ("vllm.model_executor.layers.activation", "MulAndSilu", _gated("mul_silu")),
     ("vllm.model_executor.layers.activation", "GeluAndMul", None),           # approximate flag read at call
