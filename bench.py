@@ -3,7 +3,8 @@
 
 Workload (the reference's `vllm bench serve --dataset-name random --ignore-eos` recipe at the
 shape named for this build): 256 concurrent requests, each 1024 uniform-random input tokens
-and 128 forced output tokens, bf16, random-init weights, TP = N.
+and 128 forced output tokens, bf16, random-init weights, TP = N.  `--config` selects one of the
+other serving configurations (`qwen3moe`, `dsv32`, `llama70b_int8kv`); the output line names it.
 
 One *step* is one full pass over that workload (prefill of all requests + 127 decode
 iterations).  Two measurements per run:
@@ -27,12 +28,44 @@ import sys
 import tempfile
 import time
 
-MODEL = dict(architecture="LlamaForCausalLM", vocab_size=128256, hidden_size=4096, intermediate_size=14336,
-             num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-5,
-             rope_theta=500000.0, max_position_embeddings=8192)
-NUM_REQS, IN_LEN, OUT_LEN = 256, 1024, 128
-PREFILL_TOKENS = 8192
 BLOCK_SIZE = 128
+
+# The serving configurations named for this build (random-init weights, uniform-random prompt tokens).
+# `model` holds ModelConfig fields; `workload` = (requests, input tokens, output tokens); `prefill_tokens` = tokens
+# per prefill step of the device-resident replay; `llm` = extra LLM(...) arguments.
+CONFIGS = {
+    "llama8b": dict(
+        label="Llama-3.1-8B", parallelism="tp",
+        model=dict(architecture="LlamaForCausalLM", vocab_size=128256, hidden_size=4096, intermediate_size=14336,
+                   num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                   rms_norm_eps=1e-5, rope_theta=500000.0, max_position_embeddings=8192),
+        workload=(256, 1024, 128), prefill_tokens=8192, llm={}),
+    "qwen3moe": dict(
+        label="Qwen3-30B-A3B-style MoE (128 experts, top-8)", parallelism="ep",
+        model=dict(architecture="Qwen3MoeForCausalLM", vocab_size=151936, hidden_size=2048, intermediate_size=6144,
+                   num_hidden_layers=48, num_attention_heads=32, num_key_value_heads=4, head_dim=128,
+                   rms_norm_eps=1e-6, rope_theta=1000000.0, max_position_embeddings=40960, qk_norm=True,
+                   num_experts=128, num_experts_per_tok=8, moe_intermediate_size=768, norm_topk_prob=True),
+        workload=(512, 2048, 256), prefill_tokens=8192, llm={}),
+    "dsv32": dict(
+        label="DeepSeek-V3.2-style MLA + DSA, block-scaled fp8", parallelism="tp+ep",
+        model=dict(architecture="DeepseekV32ForCausalLM", vocab_size=129280, hidden_size=7168, intermediate_size=18432,
+                   num_hidden_layers=61, num_attention_heads=128, num_key_value_heads=128, rms_norm_eps=1e-6,
+                   rope_theta=10000.0, max_position_embeddings=163840, q_lora_rank=1536, kv_lora_rank=512,
+                   qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, first_k_dense_replace=3,
+                   num_experts=256, num_experts_per_tok=8, moe_intermediate_size=2048, n_shared_experts=1,
+                   scoring_func="sigmoid", n_group=8, topk_group=4, routed_scaling_factor=2.5, topk_method="noaux_tc",
+                   norm_topk_prob=True, index_n_heads=64, index_head_dim=128, index_topk=2048, quantization="fp8",
+                   quant_config={"quant_method": "fp8", "weight_block_size": [128, 128]}),
+        workload=(128, 8192, 512), prefill_tokens=8192, llm=dict(kv_cache_dtype="fp8_ds_mla"),
+        dtype="fp8 e4m3 block-scaled weights (128x128), bf16 activations"),
+    "llama70b_int8kv": dict(
+        label="Llama-3.1-70B, int8 KV cache (per-token-per-head scales)", parallelism="tp",
+        model=dict(architecture="LlamaForCausalLM", vocab_size=128256, hidden_size=8192, intermediate_size=28672,
+                   num_hidden_layers=80, num_attention_heads=64, num_key_value_heads=8, head_dim=128,
+                   rms_norm_eps=1e-5, rope_theta=500000.0, max_position_embeddings=131072),
+        workload=(32, 32768, 1024), prefill_tokens=8192, llm=dict(kv_cache_dtype="int8")),
+}
 
 
 class ClockSampler:
@@ -88,12 +121,20 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--num-reqs", type=int, default=NUM_REQS)
-    ap.add_argument("--in-len", type=int, default=IN_LEN)
-    ap.add_argument("--out-len", type=int, default=OUT_LEN)
-    ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"],
-                    help="debug only; the reported config names the full model")
+    ap.add_argument("--config", default="llama8b", choices=sorted(CONFIGS),
+                    help="serving configuration (default: the headline Llama-3.1-8B workload)")
+    ap.add_argument("--num-reqs", type=int, default=0, help="debug only: override the configuration's request count")
+    ap.add_argument("--in-len", type=int, default=0)
+    ap.add_argument("--out-len", type=int, default=0)
+    ap.add_argument("--layers", type=int, default=0, help="debug only; a reduced model is named as such in the output")
     args = ap.parse_args()
+    conf = CONFIGS[args.config]
+    MODEL = conf["model"]
+    args.num_reqs = args.num_reqs or conf["workload"][0]
+    args.in_len = args.in_len or conf["workload"][1]
+    args.out_len = args.out_len or conf["workload"][2]
+    args.layers = args.layers or MODEL["num_hidden_layers"]
+    PREFILL_TOKENS = conf["prefill_tokens"]
 
     rank = int(os.environ.get("RANK", "0"))
     if args.impl == "reference":
@@ -117,7 +158,7 @@ def main() -> None:
     N, P, O = args.num_reqs, args.in_len, args.out_len
     llm = LLM(ModelConfig(**model, dtype=torch.bfloat16), tensor_parallel_size=args.gpus, block_size=BLOCK_SIZE,
               max_model_len=P + O + BLOCK_SIZE, max_num_seqs=N, max_num_batched_tokens=PREFILL_TOKENS,
-              num_gpu_blocks=N * ((P + O + BLOCK_SIZE - 1) // BLOCK_SIZE) + 8, device="cuda")
+              num_gpu_blocks=N * ((P + O + BLOCK_SIZE - 1) // BLOCK_SIZE) + 8, device="cuda", **conf["llm"])
     runner = llm.engine.runner
     dev = runner.device
 
@@ -185,15 +226,18 @@ def main() -> None:
 
     if rank == 0:
         print(json.dumps({
-            "metric": "output tok/s (Llama-3.1-8B, 256 req x 1024 in / 128 out, device-timed, max over ranks)",
+            "metric": f"output tok/s ({conf['label']}, {N} req x {P} in / {O} out, device-timed, max over ranks)",
             "value": round(value, 1), "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(dev_ms / args.steps, 2), "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "scaling": "strong", "vs_baseline": None, "dtype": conf.get("dtype", "bf16"), "data": "synthetic",
             "impl": "ours",
-            "config": {"model": "Llama-3.1-8B" if args.layers == 32 else f"Llama-3.1-8B[{args.layers} layers, debug]",
-                       "global_batch": N, "seq_len": P, "output_len": O, "parallelism": f"tp{args.gpus}",
+            "config": {"name": args.config,
+                       "model": conf["label"] if args.layers == MODEL["num_hidden_layers"]
+                       else f"{conf['label']}[{args.layers} layers, debug]",
+                       "global_batch": N, "seq_len": P, "output_len": O,
+                       "parallelism": "+".join(f"{x}{args.gpus}" for x in conf["parallelism"].split("+")),
                        "block_size": BLOCK_SIZE, "prefill_tokens_per_step": PREFILL_TOKENS,
-                       "l2": "inputs larger than L2 (16 GB weights + KV streamed every iteration)",
+                       "l2": "inputs larger than L2 (weights + KV cache streamed every iteration)",
                        "step": "one pass over the whole workload (prefill + decode of all requests)",
                        "last_pass_phases_rank0": phases},
             "clocks": clocks,

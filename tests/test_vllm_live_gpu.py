@@ -113,3 +113,70 @@ def test_vllm_llm_generate_on_b200_platform(tmp_path, eager):
     assert [t[0] for t in toks] == [w[0] for w in want], (toks, want)
     prefix = [next((i for i, (a, b) in enumerate(zip(t, w)) if a != b), len(w)) for t, w in zip(toks, want)]
     assert min(prefix) >= 2 and sum(prefix) >= 3 * len(want), (prefix, toks, want)
+
+
+def _tokenizer(path: str) -> None:
+    """A word-level tokenizer over the checkpoint's 2048 ids with a trivial chat template (no download needed)."""
+    tokenizers = pytest.importorskip("tokenizers")
+    vocab = {f"w{i}": i for i in range(2048)}
+    tok = tokenizers.Tokenizer(tokenizers.models.WordLevel(vocab, unk_token="w0"))
+    tok.pre_tokenizer = tokenizers.pre_tokenizers.Whitespace()
+    fast = tf.PreTrainedTokenizerFast(tokenizer_object=tok, unk_token="w0", eos_token="w1", bos_token="w2", pad_token="w3")
+    fast.chat_template = "{% for m in messages %}{{ m['content'] }} {% endfor %}"
+    fast.save_pretrained(path)
+
+
+def test_vllm_serve_chat_round_trip(tmp_path):
+    """``vllm serve`` on the plugin platform answers one /v1/chat/completions request."""
+    import socket
+    import time
+    import urllib.request
+
+    path = str(tmp_path)
+    _checkpoint(path, "llama")
+    _tokenizer(path)
+    write_dist_info(path)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ)
+    env["PYTHONPATH"] = os.pathsep.join([path, ROOT, env.get("PYTHONPATH", "")])
+    env.update(VLLM_PLUGINS="b200,b200_out_of_tree,b200_models", VLLM_LOGGING_LEVEL="INFO", TOKENIZERS_PARALLELISM="false")
+    log = open(os.path.join(path, "serve.log"), "w")
+    proc = subprocess.Popen([sys.executable, "-m", "vllm.entrypoints.openai.api_server", "--model", path,
+                             "--served-model-name", "tiny", "--dtype", "bfloat16", "--max-model-len", "512",
+                             "--gpu-memory-utilization", "0.25", "--host", "127.0.0.1", "--port", str(port),
+                             "--max-num-seqs", "8"], env=env, stdout=log, stderr=subprocess.STDOUT)
+    try:
+        deadline = time.time() + 600
+        up = False
+        while time.time() < deadline and proc.poll() is None:
+            try:
+                urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=2)
+                up = True
+                break
+            except Exception:
+                time.sleep(2)
+        assert up, open(os.path.join(path, "serve.log")).read()[-6000:]
+        body = json.dumps({"model": "tiny", "messages": [{"role": "user", "content": "w5 w17 w200 w33"}],
+                           "max_tokens": 8, "temperature": 0}).encode()
+        req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/chat/completions", data=body,
+                                     headers={"Content-Type": "application/json"})
+        resp = json.loads(urllib.request.urlopen(req, timeout=120).read())
+        assert resp["choices"][0]["message"]["content"] is not None
+        assert resp["usage"]["completion_tokens"] == 8
+        record = os.environ.get("B200_VLLM_LIVE_LOG")
+        if record:
+            with open(record + ".serve.json", "w") as f:
+                json.dump(resp, f, indent=1)
+    finally:
+        proc.terminate()
+        try:
+            proc.wait(timeout=30)
+        except subprocess.TimeoutExpired:
+            proc.kill()
+        log.close()
+        record = os.environ.get("B200_VLLM_LIVE_LOG")
+        if record:
+            with open(record + ".serve.log", "w") as f:
+                f.write(open(os.path.join(path, "serve.log")).read()[-30000:])

@@ -768,6 +768,13 @@ void ar_norm_gather(Tensor& residual, const Tensor& norm_weight, double eps, con
   TORCH_CHECK(rc == 0, "ar_norm_gather: hidden size ", H, " / dtype not supported");
 }
 
+// A tensor over the same storage that does not keep it alive: CUDA-graph wrappers hold their captured outputs this
+// way so that the graph's memory pool, not Python references, owns the buffers (upstream's ``weak_ref_tensor``).
+Tensor weak_ref_tensor(const Tensor& t) {
+  TORCH_CHECK(t.is_cuda(), "weak_ref_tensor expects a CUDA tensor");
+  return torch::from_blob(t.data_ptr(), t.sizes(), t.strides(), t.options());
+}
+
 // ------------------------------------------------------------------ small / fused kernels
 void small_gemm(Tensor& out, const Tensor& a, const Tensor& w, const optional<Tensor>& bias) {
   TORCH_CHECK(a.dim() == 2 && w.dim() == 2 && a.stride(1) == 1 && w.stride(1) == 1 && a.size(1) == w.size(1));
@@ -1411,4 +1418,5 @@ TORCH_LIBRARY(b200, m) {
       "Tensor sampled, Tensor block_table, int block_size, int batch, Tensor(e!)? token_log, int log_col) -> ()",
       &advance_step);
   m.def("embedding(Tensor(a!) out, Tensor table, Tensor ids, int vocab_start) -> ()", &embedding);
+  m.def("weak_ref_tensor(Tensor input) -> Tensor", &weak_ref_tensor);
 }

@@ -86,10 +86,19 @@ def _reshape_and_cache_flash(key, value, key_cache, value_cache, slot_mapping, k
     raise NotImplementedError("this platform's attention backend writes the cache itself")
 
 
+def _apply_repetition_penalties(logits, prompt_mask, output_mask, repetition_penalties):
+    pen = torch.where(prompt_mask | output_mask, repetition_penalties.unsqueeze(1).to(logits.dtype),
+                      torch.ones((), dtype=logits.dtype, device=logits.device))
+    logits.mul_(torch.where(logits > 0, 1.0 / pen, pen))
+
+
 def define_c_ops() -> list[str]:
     """Define the missing names (idempotent).  Returns the fully qualified names this call or an earlier one defined."""
     if _LIBS:
-        return DEFINED
+        _define(lib, "_C", "apply_repetition_penalties_(Tensor! logits, Tensor prompt_mask, Tensor output_mask, "
+            "Tensor repetition_penalties) -> ()", _apply_repetition_penalties)
+    _define(lib, "_C", "weak_ref_tensor(Tensor input) -> Tensor", lambda t: torch.ops.b200.weak_ref_tensor(t))
+    return DEFINED
     lib = torch.library.Library("_C", "FRAGMENT")
     _LIBS.append(lib)
     for op, act in (("silu_and_mul", "silu"), ("mul_and_silu", "mul_silu"), ("gelu_and_mul", "gelu"),
@@ -109,4 +118,7 @@ def define_c_ops() -> list[str]:
             _fused_add_rms_norm)
     _define(lib, "_C", "rotary_embedding(Tensor positions, Tensor! query, Tensor!? key, int head_size, "
             "Tensor cos_sin_cache, bool is_neox) -> ()", _rotary_embedding)
+    _define(lib, "_C", "apply_repetition_penalties_(Tensor! logits, Tensor prompt_mask, Tensor output_mask, "
+            "Tensor repetition_penalties) -> ()", _apply_repetition_penalties)
+    _define(lib, "_C", "weak_ref_tensor(Tensor input) -> Tensor", lambda t: torch.ops.b200.weak_ref_tensor(t))
     return DEFINED
