@@ -420,8 +420,9 @@ B200Platform = _autodetect()
 # this module in every process).
 if _HAVE_VLLM:
     for _name, _val, _why in (
-        ("VLLM_USE_FLASHINFER_SAMPLER", "0", "sampling runs on this package's kernels"),
-        ("VLLM_ENGINE_READY_TIMEOUT_S", "7200", "first start compiles / captures graphs"),
+        # typed as vllm.envs returns them (the override replaces vLLM's parser for the name)
+        ("VLLM_USE_FLASHINFER_SAMPLER", False, "sampling runs on this package's kernels"),
+        ("VLLM_ENGINE_READY_TIMEOUT_S", 7200, "first start compiles / captures graphs"),
         ("VLLM_FLOAT32_MATMUL_PRECISION", "high", "fp32 matmuls may use tf32"),
     ):
         if _name not in os.environ:

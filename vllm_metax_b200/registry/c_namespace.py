@@ -95,10 +95,7 @@ def _apply_repetition_penalties(logits, prompt_mask, output_mask, repetition_pen
 def define_c_ops() -> list[str]:
     """Define the missing names (idempotent).  Returns the fully qualified names this call or an earlier one defined."""
     if _LIBS:
-        _define(lib, "_C", "apply_repetition_penalties_(Tensor! logits, Tensor prompt_mask, Tensor output_mask, "
-            "Tensor repetition_penalties) -> ()", _apply_repetition_penalties)
-    _define(lib, "_C", "weak_ref_tensor(Tensor input) -> Tensor", lambda t: torch.ops.b200.weak_ref_tensor(t))
-    return DEFINED
+        return DEFINED
     lib = torch.library.Library("_C", "FRAGMENT")
     _LIBS.append(lib)
     for op, act in (("silu_and_mul", "silu"), ("mul_and_silu", "mul_silu"), ("gelu_and_mul", "gelu"),
