@@ -49,8 +49,11 @@ llm = LLM(path, dtype="bfloat16", max_model_len=512, gpu_memory_utilization=0.25
           max_num_seqs=8, seed=0)
 outs = llm.generate([{"prompt_token_ids": p} for p in prompts], SamplingParams(max_tokens=12, temperature=0.0, ignore_eos=True))
 from vllm_metax_b200 import _custom_ops as ops
+from vllm.model_executor.custom_op import op_registry_oot
+moe = op_registry_oot.get("UnquantizedFusedMoEMethod")
 res = {"platform": type(current_platform).__name__, "module": type(current_platform).__module__,
-       "tokens": [list(o.outputs[0].token_ids) for o in outs], "launches": ops.launch_count()}
+       "tokens": [list(o.outputs[0].token_ids) for o in outs], "launches": ops.launch_count(),
+       "moe_method": moe.__name__ if moe is not None else ""}
 json.dump(res, open(out, "w"))
 """
 
@@ -62,6 +65,12 @@ def _checkpoint(path: str, kind: str) -> list:
                              num_attention_heads=8, num_key_value_heads=2, head_dim=128, max_position_embeddings=1024,
                              rms_norm_eps=1e-5, tie_word_embeddings=False)
         tf.LlamaForCausalLM(cfg).save_pretrained(path)
+    elif kind == "qwen3_moe":
+        cfg = tf.Qwen3MoeConfig(vocab_size=2048, hidden_size=1024, intermediate_size=2048, num_hidden_layers=2,
+                                num_attention_heads=8, num_key_value_heads=2, head_dim=128, max_position_embeddings=1024,
+                                rms_norm_eps=1e-6, tie_word_embeddings=False, num_experts=8, num_experts_per_tok=2,
+                                moe_intermediate_size=512, decoder_sparse_step=1, norm_topk_prob=True, mlp_only_layers=[])
+        tf.Qwen3MoeForCausalLM(cfg).save_pretrained(path)
     else:
         raise ValueError(kind)
     g = torch.Generator().manual_seed(5)
@@ -109,6 +118,20 @@ def test_vllm_llm_generate_on_b200_platform(tmp_path, eager):
     got = run_vllm_child(path, eager, os.environ.get("B200_VLLM_LIVE_LOG"))
     assert got["platform"].endswith("B200Platform") and got["module"] == "vllm_metax_b200.platform", got
     assert got["launches"] > 0, "no kernel of this package ran under vLLM"
+    toks = got["tokens"]
+    assert [t[0] for t in toks] == [w[0] for w in want], (toks, want)
+    prefix = [next((i for i, (a, b) in enumerate(zip(t, w)) if a != b), len(w)) for t, w in zip(toks, want)]
+    assert min(prefix) >= 2 and sum(prefix) >= 3 * len(want), (prefix, toks, want)
+
+
+def test_vllm_moe_runs_on_grouped_gemms(tmp_path):
+    """A Qwen3-MoE checkpoint under upstream vLLM: the experts run through this package's FusedMoE method."""
+    path = str(tmp_path)
+    prompts = _checkpoint(path, "qwen3_moe")
+    want = _standalone_tokens(path, prompts)
+    got = run_vllm_child(path, True, os.environ.get("B200_VLLM_LIVE_LOG"))
+    assert got["platform"].endswith("B200Platform"), got
+    assert got.get("moe_method", "").startswith("B200"), got
     toks = got["tokens"]
     assert [t[0] for t in toks] == [w[0] for w in want], (toks, want)
     prefix = [next((i for i, (a, b) in enumerate(zip(t, w)) if a != b), len(w)) for t, w in zip(toks, want)]

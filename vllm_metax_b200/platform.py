@@ -166,6 +166,17 @@ class B200PlatformBase(Platform):
 
     # ------------------------------------------------------------------ attention
     @classmethod
+    def _late_registrations(cls) -> None:
+        """Registrations that need upstream modules which cannot be imported while vLLM itself is still importing."""
+        if _HAVE_VLLM:
+            try:
+                from .registry.fused_moe_method import ensure_registered
+
+                ensure_registered()
+            except Exception:  # registry layout differs between vLLM versions
+                pass
+
+    @classmethod
     def get_valid_backends(cls, attn_selector_config, device_capability=None) -> list[str]:
         use_mla = bool(getattr(attn_selector_config, "use_mla", False))
         use_sparse = bool(getattr(attn_selector_config, "use_sparse", False))
@@ -173,6 +184,7 @@ class B200PlatformBase(Platform):
 
     @classmethod
     def get_attn_backend_cls(cls, selected_backend, attn_selector_config, num_heads: Optional[int] = None) -> str:
+        cls._late_registrations()
         use_mla = bool(getattr(attn_selector_config, "use_mla", False))
         use_sparse = bool(getattr(attn_selector_config, "use_sparse", False))
         if selected_backend is not None:
@@ -211,6 +223,7 @@ class B200PlatformBase(Platform):
 
     @classmethod
     def check_and_update_config(cls, vllm_config: "VllmConfig") -> None:
+        cls._late_registrations()
         parallel_config = vllm_config.parallel_config
         if getattr(parallel_config, "worker_cls", "auto") == "auto":
             parallel_config.worker_cls = "vllm.v1.worker.gpu_worker.Worker"

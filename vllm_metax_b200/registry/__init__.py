@@ -9,4 +9,4 @@ except Exception:  # pragma: no cover
     HAVE_VLLM = False
 
 if HAVE_VLLM:
-    from . import custom_ops, linear_kernels, quant_config  # noqa: F401
+    from . import custom_ops, fused_moe_method, linear_kernels, quant_config  # noqa: F401
