@@ -367,20 +367,48 @@ def test_argmax_and_greedy_sample():
     assert torch.equal(ops.sample(logits, t, None, None, None, u), logits.float().argmax(-1))
 
 
+def _topk_then_topp_keep(probs, k, p):
+    """Upstream's order: top-k, renormalise over the kept tokens, then top-p.  Returns (sorted ids, keep mask by rank,
+    renormalised probabilities by rank)."""
+    sp, si = probs.sort(-1, descending=True)
+    V = probs.shape[-1]
+    in_k = torch.arange(V, device=probs.device)[None] < k
+    pk = torch.where(in_k, sp, torch.zeros_like(sp))
+    pk = pk / pk.sum(-1, keepdim=True)
+    keep = in_k & ((pk.cumsum(-1) - pk) < p)
+    final = torch.where(keep, pk, torch.zeros_like(pk))
+    return si, keep, final / final.sum(-1, keepdim=True)
+
+
 def test_sample_respects_topk_topp():
     V = 5000
-    logits = torch.randn(64, V, device=DEV) * 3
+    logits = torch.randn(64, V, device=DEV)
     temp = torch.full((64,), 0.8, device=DEV)
-    top_k = torch.full((64,), 20, device=DEV, dtype=torch.int32)
+    top_k = torch.full((64,), 50, device=DEV, dtype=torch.int32)
     top_p = torch.full((64,), 0.9, device=DEV)
-    probs = torch.softmax(logits / 0.8, -1)
-    sp, si = probs.sort(-1, descending=True)
-    keep = (torch.arange(V, device=DEV)[None] < 20) & ((sp.cumsum(-1) - sp) < 0.9)
+    si, keep, _ = _topk_then_topp_keep(torch.softmax(logits / 0.8, -1), 50, 0.9)
     for trial in range(8):
         u = torch.rand(64, device=DEV)
         tok = ops.sample(logits, temp, top_k, top_p, None, u)
         rank = (si == tok[:, None]).float().argmax(-1)
         assert bool(keep.gather(1, rank[:, None]).all())
+
+
+def test_sample_topk_then_topp_distribution():
+    """With both cuts active the kept set is the one of the sort-based oracle (top-p over the renormalised top-k
+    distribution), and tokens are drawn in proportion inside it."""
+    V, n = 64, 16384
+    row = torch.randn(1, V, device=DEV)
+    logits = row.repeat(n, 1)
+    temp = torch.ones(n, device=DEV)
+    si, keep, final = _topk_then_topp_keep(torch.softmax(row, -1), 16, 0.8)
+    tok = ops.sample(logits, temp, torch.full((n,), 16, device=DEV, dtype=torch.int32),
+                     torch.full((n,), 0.8, device=DEV), None, torch.rand(n, device=DEV))
+    emp = torch.bincount(tok, minlength=V).float() / n
+    want = torch.zeros(V, device=DEV)
+    want[si[0]] = final[0]
+    assert float(emp[want == 0].sum()) == 0.0
+    assert (emp - want).abs().max() < 0.03
 
 
 def test_sample_distribution_matches():

@@ -55,8 +55,12 @@ def _call(fn, q, cache, bt, sl, splits):
     B, Hq, D = q.shape
     torch.cuda.synchronize()
     n_alloc = torch.cuda.memory_stats()["allocation.all.allocated"]
+    free_before = torch.cuda.mem_get_info()[0]
     rc = _raw(fn, out, q, cache, bt, sl, splits)
-    assert torch.cuda.memory_stats()["allocation.all.allocated"] == n_alloc  # the call allocated nothing
+    torch.cuda.synchronize()
+    # the call allocated nothing: neither through torch's caching allocator nor behind its back (driver view)
+    assert torch.cuda.memory_stats()["allocation.all.allocated"] == n_alloc
+    assert torch.cuda.mem_get_info()[0] >= free_before
     return rc, out
 
 
@@ -81,6 +85,12 @@ def test_noalloc_decode_matches_regular_op_twice():
         a, b = got.float().flatten(), want.float().flatten()
         assert 1.0 - float(torch.dot(a, b) / (a.norm() * b.norm())) < 2e-4
         torch.testing.assert_close(got.float(), want.float(), rtol=3e-2, atol=3e-2)
+        # and against the fp32 PyTorch statement of paged attention, not only against the same kernel
+        from vllm_metax_b200.ops import reference as ref
+
+        qsl = torch.arange(len(lens) + 1, dtype=torch.int32, device="cuda")
+        oracle = ref.paged_attention(q, cache, bt, sl, qsl, q.shape[-1] ** -0.5)
+        torch.testing.assert_close(got.float(), oracle.float(), rtol=3e-2, atol=3e-2)
 
 
 def test_noalloc_decode_rejects_oversized_request():
@@ -96,3 +106,25 @@ def test_noalloc_decode_rejects_oversized_request():
     assert rc == 0
     want = ops.paged_attention_decode(q, cache, bt, sl, D ** -0.5, num_splits=2)
     torch.testing.assert_close(got.float(), want.float(), rtol=3e-2, atol=3e-2)
+
+
+def test_noalloc_decode_rejects_bad_sizes_before_launching():
+    """Sizes an embedder could get wrong are refused with a negative code; nothing is launched for them."""
+    ops, lib, fn = _load()
+    q, cache, bt, sl = _case(3, [40] * 2)
+    out = torch.empty_like(q)
+    B, Hq, D = q.shape
+    good = dict(batch=B, hq=Hq, hkv=cache.shape[3], d=D, bs=cache.shape[2], mb=bt.shape[1], nb=cache.shape[0])
+
+    def call(**over):
+        a = dict(good, **over)
+        return fn(out.data_ptr(), q.data_ptr(), cache.data_ptr(), None, bt.data_ptr(), sl.data_ptr(), a["batch"], a["hq"],
+                  a["hkv"], a["d"], a["bs"], a["mb"], a["nb"], 2, D ** -0.5, 0, 0, torch.cuda.current_stream().cuda_stream)
+
+    for bad in (dict(bs=0), dict(bs=-16), dict(bs=24), dict(mb=0), dict(nb=0), dict(hq=0), dict(hkv=0), dict(d=96),
+                dict(d=0), dict(batch=-1), dict(hq=Hq + 1)):
+        assert call(**bad) < 0, bad
+        assert lib.b200_noalloc_last_error() != b""
+    assert call() == 0
+    torch.cuda.synchronize()
+    ops.check_kernel_status(0)

@@ -112,7 +112,13 @@ __global__ void __launch_bounds__(kDecWarps * 32, (D <= 128 ? 2 : 1)) paged_deco
   const int hk = blockIdx.x / row_tiles;
   const int row0 = (blockIdx.x % row_tiles) * 16;
   if (q_len <= 0 || row0 >= rows_total) return;
-  const int kv_len = p.seq_lens[b];
+  int kv_len = p.seq_lens[b];
+  // a length the block table cannot hold would index past its row: record it and attend to what the row covers
+  const long long kv_cap = (long long)p.max_blocks * p.block_size;
+  if (kv_len < 0 || kv_len > kv_cap) {
+    report_status(p.status, kBadIndex, 21, (int)(kv_cap > 0x7fffffff ? 0x7fffffff : kv_cap), kv_len);
+    kv_len = kv_len < 0 ? 0 : (int)kv_cap;
+  }
   // tiles of this split
   const int tiles_total = (kv_len + kDecTile - 1) / kDecTile;
   const int tiles_per_split = (tiles_total + p.num_splits - 1) / p.num_splits;
@@ -427,11 +433,8 @@ template <typename T, int D, int KIND>
 static void launch_decode(const DecodeParams& p, int batch, int max_q_len, cudaStream_t stream) {
   using S = DecSmem<D, KIND>;
   auto kern = paged_decode_kernel<T, D, KIND>;
-  static bool set = false;
-  if (!set) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
-    set = true;
-  }
+  // a per-device attribute of the kernel: set on every launch (cheap) rather than once per process
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
   const int g = p.num_q_heads / p.num_kv_heads;
   const int row_tiles = ceil_div(max_q_len * g, 16);
   dim3 grid(p.num_kv_heads * row_tiles, batch, p.num_splits);

@@ -445,11 +445,8 @@ static void launch_prefill(const PrefillParams& p, const void* q, int64_t q_stri
     tmV = make_tmap_nd(v_src, dt, 3, vd, vs, kb, CU_TENSOR_MAP_SWIZZLE_128B);
   }
   auto kern = attn_prefill_kernel<T, DQK, DV, BN>;
-  static bool set = false;
-  if (!set) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDyn);
-    set = true;
-  }
+  // a per-device attribute of the kernel: set on every launch (cheap) rather than once per process
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDyn);
   const int toks_per_tile = kPfBM / p.gp;
   dim3 grid(ceil_div(max_q_len, toks_per_tile), p.num_q_heads / p.gp, batch);
   kern<<<grid, 320, L::kDyn, stream>>>(tmQ, tmK, tmV, p);

@@ -299,11 +299,8 @@ static void launch_ag(const AgGemmParams& p, const void* W, int ldw, void* C, co
   m.local_ld = make_tmap_2d(p.x_shard[p.rank], dt, 2, p.rows_per_rank, p.K, p.K, kAgBM, kAgBK, true);
   m.w = make_tmap_2d(W, dt, 2, p.N, p.K, ldw, BN, kAgBK, true);
   auto kern = ag_gemm_kernel<T, BN, STAGES>;
-  static bool set = false;
-  if (!set) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDyn);
-    set = true;
-  }
+  // a per-device attribute of the kernel: set on every launch (cheap) rather than once per process
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDyn);
   static int sms = 0;
   if (sms == 0) {
     int dev = 0;

@@ -1,8 +1,9 @@
 // Shared pieces of the fused compute + collective kernels: parameter blocks, system-scope
 // flag primitives with bounded waits.
 //
-// All cross-GPU traffic is plain peer loads/stores on IPC-mapped buffers over NVLink (no NCCL
-// call, no TMA from peer memory).  Every wait on a value another GPU writes is bounded by an
+// Cross-GPU traffic goes over NVLink to IPC-mapped buffers as plain peer loads / stores, bulk copies and
+// TMA tensor stores from shared memory, and plain (never cluster-multicast) TMA loads of peer rows; no NCCL call
+// and no library kernel is ever handed peer memory.  Every wait on a value another GPU writes is bounded by an
 // SM-clock budget; on expiry the waiter records {site, expected, observed} in the status word
 // and carries on without the data, so a missing peer can never hang the GPU - the host turns the
 // status into an exception.

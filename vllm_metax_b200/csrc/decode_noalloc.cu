@@ -49,10 +49,16 @@ extern "C" int b200_paged_decode_noalloc(void* out, const void* q, const void* k
                                          void* stream) {
   g_err[0] = 0;
   if (!out || !q || !kv_cache || !block_table || !seq_lens) return fail(-1, "null tensor pointer");
-  if (batch <= 0) return 0;
+  // every size is checked before anything is computed from it or launched: the pointers come from an embedder
+  if (head_dim != 64 && head_dim != 128 && head_dim != 256) return fail(-5, "unsupported head_dim (64, 128 and 256 are built)");
+  if (num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads != 0)
+    return fail(-1, "num_q_heads must be a positive multiple of num_kv_heads");
+  if (block_size <= 0 || block_size % 16 != 0) return fail(-1, "block_size must be a positive multiple of 16");
+  if (max_blocks <= 0) return fail(-1, "max_blocks must be positive");
+  if (num_blocks <= 0) return fail(-1, "num_blocks must be positive");
+  if (batch < 0) return fail(-1, "batch must not be negative");
+  if (batch == 0) return 0;
   if (num_splits < 1) num_splits = 1;
-  if (num_kv_heads <= 0 || num_q_heads % num_kv_heads != 0) return fail(-1, "num_q_heads must be a multiple of num_kv_heads");
-  if (block_size % 16 != 0) return fail(-1, "block_size must be a multiple of 16");
   if (cache_dtype != 0 && kv_scales == nullptr) return fail(-1, "quantised caches need kv_scales");
   if (dtype != 0 && dtype != 1) return fail(-1, "dtype must be 0 (bf16) or 1 (fp16)");
   const uint64_t need = (uint64_t)num_splits * (uint64_t)batch * (uint64_t)num_q_heads * (uint64_t)(head_dim + 1);

@@ -36,6 +36,8 @@ extern "C" {
 // block_table  [batch, max_blocks] int32, seq_lens [batch] int32
 // dtype        0 = bf16, 1 = fp16;  head_dim in {64, 128, 256};  num_splits >= 1
 // stream       a cudaStream_t (NULL = legacy default stream)
+// Every size is validated before anything is launched (head_dim, head counts, block_size, max_blocks, num_blocks);
+// sequence lengths beyond max_blocks * block_size are clamped by the kernel.
 // Returns 0 on success, a negative code otherwise.
 int b200_paged_decode_noalloc(void* out, const void* q, const void* kv_cache, const float* kv_scales,
                               const int* block_table, const int* seq_lens, int batch, int num_q_heads,

@@ -212,11 +212,8 @@ static void launch_f8(const void* A, int M, int lda, const void* W, int E, int N
     tmW = make_tmap_2d(W, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, kF8BN, kF8BK);
   }
   auto kern = gemm_fp8_kernel<T, GROUPED>;
-  static bool set = false;
-  if (!set) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, F8Smem::kDyn);
-    set = true;
-  }
+  // a per-device attribute of the kernel: set on every launch (cheap) rather than once per process
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, F8Smem::kDyn);
   static int sms = 0;
   if (sms == 0) {
     int dev = 0;

@@ -179,11 +179,8 @@ static void launch_grouped(const void* A, int max_rows, int lda, const void* W, 
   uint32_t wb[3] = {(uint32_t)kGgBK, (uint32_t)BN, 1};
   CUtensorMap tmW = make_tmap_nd(W, dt, 3, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B);
   auto kern = gemm_grouped_kernel<T, BN, STAGES>;
-  static bool set = false;
-  if (!set) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDyn);
-    set = true;
-  }
+  // a per-device attribute of the kernel: set on every launch (cheap) rather than once per process
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDyn);
   static int sms = 0;
   if (sms == 0) {
     int dev = 0;

@@ -247,11 +247,8 @@ static void launch_sm(const void* A, int lda, const void* W, int E, void* C, con
     tmW = make_tmap_2d(W, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.N, p.K, p.K, BN, kSmBK);
   }
   auto kern = scaled_mm_kernel<T, BN, STAGES, INT8, GROUPED>;
-  static bool set = false;
-  if (!set) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDyn);
-    set = true;
-  }
+  // a per-device attribute of the kernel: set on every launch (cheap) rather than once per process
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDyn);
   const int tiles = ceil_div(p.M, kSmBM) * ceil_div(p.N, BN);
   const int grid = tiles < sm_count() ? (tiles < 1 ? 1 : tiles) : sm_count();
   kern<<<grid, 192, L::kDyn, stream>>>(tmA, tmW, reinterpret_cast<T*>(C), p, status);

@@ -202,11 +202,8 @@ static void launch_sk(const void* A, const void* W, void* C, const void* bias, c
   CUtensorMap tmA = make_tmap_2d(A, dt, 2, M, K, lda, kSkBM, kSkBK);
   CUtensorMap tmB = make_tmap_2d(W, dt, 2, N, K, ldw, kSkBN, kSkBK);
   auto kern = gemm_splitk_kernel<T>;
-  static bool set = false;
-  if (!set) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SkSmem::kDyn);
-    set = true;
-  }
+  // a per-device attribute of the kernel: set on every launch (cheap) rather than once per process
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SkSmem::kDyn);
   const int tiles = ceil_div(M, kSkBM) * ceil_div(N, kSkBN);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(tiles * splits, 1, 1);

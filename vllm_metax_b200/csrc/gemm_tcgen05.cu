@@ -304,11 +304,8 @@ static void launch_cfg(const void* a_op, int rows_a, int lda, const void* b_op, 
   CUtensorMap tmA = make_tmap_2d(a_op, dt, 2, rows_a, K, lda, kBM, kBK);
   CUtensorMap tmB = make_tmap_2d(b_op, dt, 2, rows_b, K, ldb, BN, kBK);
   auto kern = gemm_tn_kernel<T, BN, STAGES, SWAP>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynSmem);
-    attr_set = true;
-  }
+  // a per-device attribute of the kernel: set on every launch (cheap) rather than once per process
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynSmem);
   const int tiles = ceil_div(rows_a, kBM) * ceil_div(rows_b, BN);
   const int grid = tiles < num_sms() ? tiles : num_sms();
   kern<<<grid, 192, L::kDynSmem, stream>>>(tmA, tmB, reinterpret_cast<T*>(C), reinterpret_cast<const T*>(bias),

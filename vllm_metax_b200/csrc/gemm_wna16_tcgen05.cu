@@ -359,11 +359,8 @@ static void launch_wq(const void* A, int lda, const void* Q, int E, void* C, WqA
       std::is_same<T, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap tmX = make_tmap_2d(A, dt, 2, p.M, p.K, lda, BN, kWqBK);
   auto kern = gemm_wna16_kernel<T, BN, STAGES, BITS, GROUPED>;
-  static bool set = false;
-  if (!set) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDyn);
-    set = true;
-  }
+  // a per-device attribute of the kernel: set on every launch (cheap) rather than once per process
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDyn);
   const int tiles = ceil_div(p.N, kWqBM) * ceil_div(p.M, BN);
   int gx = wq_sms() / p.splits;
   gx = gx < 1 ? 1 : gx;

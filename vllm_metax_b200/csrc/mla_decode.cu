@@ -369,11 +369,8 @@ __global__ void mla_split_reduce_kernel(T* __restrict__ out, float* __restrict__
 template <typename T, bool FP8>
 static void launch_mla(const MlaDecodeParams& p, cudaStream_t stream) {
   auto kern = mla_decode_kernel<T, FP8>;
-  static bool set = false;
-  if (!set) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, MlaSmem::kTotal);
-    set = true;
-  }
+  // a per-device attribute of the kernel: set on every launch (cheap) rather than once per process
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, MlaSmem::kTotal);
   dim3 grid((p.num_heads + 15) / 16, p.total_tokens, p.num_splits);
   kern<<<grid, kMlaWarps * 32, MlaSmem::kTotal, stream>>>(p);
   if (p.num_splits > 1)

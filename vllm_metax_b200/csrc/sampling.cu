@@ -88,34 +88,42 @@ sample_kernel(int64_t* __restrict__ out, const T* __restrict__ logits, int vocab
   const float tp = top_p ? top_p[b] : 1.f;
   const float mp = min_p ? min_p[b] : 0.f;
   float thr = 0.f;  // keep p_i >= thr
-  if (k < vocab || tp < 1.f) {
-    // largest threshold tau such that count(p >= tau) <= k ... found by bisection on tau:
-    // keep-set(tau) shrinks as tau grows.  We need the smallest keep-set that satisfies BOTH
-    // "at most k tokens" and "mass before the last kept token < top_p" -> the largest tau whose
-    // keep-set still has mass >= min(top_p, mass of top-k set).
-    float lo = 0.f, hi = inv_z;  // invariant: keep-set(lo) is acceptable-or-too-big, keep-set(hi) = {max tokens}
+  // Same order as upstream's sampler: top-k first, then top-p over the distribution RENORMALISED to the top-k set
+  // (the smallest set of its leading tokens whose share of the top-k mass reaches top_p).  Both cuts are
+  // thresholds on p_i, found by bisection (keep-set(tau) = {p_i >= tau} shrinks as tau grows).
+  float mass_k = 1.f;
+  if (k < vocab) {
+    float lo = 0.f, hi = inv_z * 1.0000002f + 1e-30f;   // count(lo) = vocab >= k, count(hi) = 0
     for (int it = 0; it < 32; ++it) {
       const float mid = 0.5f * (lo + hi);
-      float cnt = 0.f, mass = 0.f;
-      for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float pi = __expf((to_f(row[i]) - gmax) * inv_t) * inv_z;
-        if (pi >= mid) { cnt += 1.f; mass += pi; }
-      }
+      float cnt = 0.f;
+      for (int i = threadIdx.x; i < vocab; i += blockDim.x)
+        if (__expf((to_f(row[i]) - gmax) * inv_t) * inv_z >= mid) cnt += 1.f;
       cnt = block_sum(cnt, red);
-      mass = block_sum(mass, red);
-      // too big a set if it has more than k tokens, or if dropping to this set still covers top_p
-      const bool can_shrink = (cnt > (float)k) || (mass >= tp);
-      if (can_shrink) lo = mid; else hi = mid;
+      if (cnt >= (float)k) lo = mid; else hi = mid;      // lo converges to the k-th largest probability
     }
-    // `lo` keeps a set with mass >= tp (or > k tokens at float resolution); use the set at lo unless it
-    // violates k, in which case hi (first set within k) is used.
-    float cnt = 0.f;
+    thr = lo;
+    float m = 0.f;
     for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
       const float pi = __expf((to_f(row[i]) - gmax) * inv_t) * inv_z;
-      if (pi >= lo) cnt += 1.f;
+      if (pi >= thr) m += pi;
     }
-    cnt = block_sum(cnt, red);
-    thr = (cnt > (float)k) ? hi : lo;
+    mass_k = block_sum(m, red);
+  }
+  if (tp < 1.f) {
+    const float need = tp * mass_k;
+    float lo = thr, hi = inv_z * 1.0000002f + 1e-30f;    // mass(lo) = mass_k >= need, mass(hi) = 0
+    for (int it = 0; it < 32; ++it) {
+      const float mid = 0.5f * (lo + hi);
+      float m = 0.f;
+      for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float pi = __expf((to_f(row[i]) - gmax) * inv_t) * inv_z;
+        if (pi >= mid) m += pi;
+      }
+      m = block_sum(m, red);
+      if (m >= need) lo = mid; else hi = mid;            // largest tau whose keep-set still covers top_p
+    }
+    thr = lo;
   }
   thr = fmaxf(thr, mp * inv_z);
   // mass of kept set

@@ -5,7 +5,7 @@ The engine thread is the only code that touches the scheduler / model runner; pr
 over through a lock-protected inbox, so no engine state is shared with the event loop.  A failed step
 marks the engine dead: every in-flight and every later request receives ``EngineDeadError``.
 Parity: the role of vLLM's AsyncLLM / EngineCore client that the reference serves through
-(``vllm serve`` with the platform plugin, SURVEY call stack 3.2).
+(``vllm serve`` with the platform plugin).
 """
 from __future__ import annotations
 

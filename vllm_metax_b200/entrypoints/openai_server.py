@@ -5,7 +5,7 @@ events), ``/tokenize``, ``/detokenize``, ``/health``, ``/metrics`` (Prometheus t
 plane the RLHF / benchmark harnesses use: ``/sleep``, ``/wake_up``, ``/is_sleeping``, ``/pause``,
 ``/resume``, ``/collective_rpc``-free by design (SPMD ranks run the same server code).
 Parity: the reference is served by ``vllm serve`` (OpenAI API server + ``vllm bench serve`` client,
-BASELINE methodology); sampling defaults follow patch/enhancement/chores/bench_serve_args.py:284-292
+tools/batched_test/bench_sweep.sh:3-14); sampling defaults follow patch/enhancement/chores/bench_serve_args.py:284-292
 (temperature 0 unless the request sets one).
 """
 import json

@@ -873,7 +873,10 @@ def sample(logits, temperature, top_k, top_p, min_p=None, generators=None, unifo
         k = torch.where(top_k <= 0, torch.full_like(top_k, V), top_k)[:, None]
         keep &= torch.arange(V, device=logits.device)[None, :] < k
     if top_p is not None:
-        keep &= (cum - sp) < top_p.float()[:, None]
+        # upstream's order: top-p is taken over the distribution renormalised to the top-k set
+        spk = sp * keep
+        spk = spk / spk.sum(dim=-1, keepdim=True)
+        keep &= (torch.cumsum(spk, dim=-1) - spk) < top_p.float()[:, None]
     if min_p is not None:
         keep &= sp >= (min_p.float()[:, None] * sp[:, :1])
     keep[:, 0] = True

@@ -5,7 +5,7 @@
 Runs the workload under ``torch.profiler`` (CUDA activities), groups device kernels by name and prints count,
 total / mean time and share - the quick "where does a step go" view.  ``LLM.start_profile`` / ``stop_profile``
 write a full trace for TensorBoard; this prints the summary without leaving the terminal.
-Parity: the reference's profiling docs (docs/developing/msprobe, vllm's torch-profiler hooks): SURVEY 5.1.
+Parity: the reference's profiling docs (docs/developing/msprobe, the torch-profiler hooks of upstream vLLM).
 """
 from __future__ import annotations
 
