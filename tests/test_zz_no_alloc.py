@@ -31,6 +31,10 @@ def _load():
     fn.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int] * 6 + [ctypes.c_int64, ctypes.c_int, ctypes.c_float,
                                                                 ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
     lib.b200_noalloc_last_error.restype = ctypes.c_char_p
+    # set-up call (first on the device): symbol address, shared-memory limit, driver-side module load
+    q, cache, bt, sl = _case(99, [20, 40])
+    assert _raw(fn, torch.empty_like(q), q, cache, bt, sl, 2) == 0
+    torch.cuda.synchronize()
     return ops, lib, fn
 
 
@@ -58,7 +62,9 @@ def _call(fn, q, cache, bt, sl, splits):
     free_before = torch.cuda.mem_get_info()[0]
     rc = _raw(fn, out, q, cache, bt, sl, splits)
     torch.cuda.synchronize()
-    # the call allocated nothing: neither through torch's caching allocator nor behind its back (driver view)
+    # the call allocated nothing: neither through torch's caching allocator nor behind its back (driver view).
+    # The very first use of the library on a device makes the driver load its kernels and the 16 MiB array
+    # (lazy module loading) - that one-time set-up is done by the warm-up call in _load().
     assert torch.cuda.memory_stats()["allocation.all.allocated"] == n_alloc
     assert torch.cuda.mem_get_info()[0] >= free_before
     return rc, out

@@ -17,8 +17,10 @@
 //     earlier in the same call - but the array does keep the previous call's contents.
 //
 // The first call on each device looks the array's device address up (the name is only a
-// host-side handle, not a device pointer) and raises the kernel's shared-memory limit; make
-// that first call outside any stream capture.  No call allocates or frees anything.
+// host-side handle, not a device pointer) and raises the kernel's shared-memory limit; with
+// CUDA's lazy module loading it is also the moment the driver places the kernels and the
+// array on that device.  Make that first call outside any stream capture.  No call allocates
+// or frees anything through cudaMalloc / cudaFree or an allocating library routine.
 #pragma once
 #include <stdint.h>
 

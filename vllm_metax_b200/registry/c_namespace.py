@@ -92,6 +92,45 @@ def _apply_repetition_penalties(logits, prompt_mask, output_mask, repetition_pen
     logits.mul_(torch.where(logits > 0, 1.0 / pen, pen))
 
 
+def _topk(scoring: str):
+    def fn(topk_weights, topk_ids, token_expert_indices, gating_output, renormalize=False, bias=None):
+        T, k = topk_weights.shape
+        w, ids = ops.topk_gating(gating_output.reshape(T, -1), k, bool(renormalize), scoring,
+                                 None if bias is None else bias.float())
+        topk_weights.copy_(w)
+        topk_ids.copy_(ids)
+        if token_expert_indices is not None and token_expert_indices.numel():
+            # the position of every (token, choice) pair in choice-major order, as upstream's kernel fills it
+            token_expert_indices.copy_(torch.arange(k, device=ids.device, dtype=token_expert_indices.dtype)[None, :] * T
+                                       + torch.arange(T, device=ids.device, dtype=token_expert_indices.dtype)[:, None])
+
+    return fn
+
+
+def _grouped_topk(scores, num_expert_group, topk_group, topk, renormalize, routed_scaling_factor, bias, scoring_func=0):
+    if int(scoring_func) == 1:      # `scores` are logits: sigmoid + bias + group-limited top-k in one kernel
+        return ops.grouped_topk(scores, int(topk), bool(renormalize), int(num_expert_group), int(topk_group),
+                                "sigmoid", bias, float(routed_scaling_factor))
+    # already-activated scores: the same selection in tensor ops (bias steers the choice, not the weights)
+    T, E = scores.shape
+    sc = scores.float()
+    choice = sc + bias.float()[None, :]
+    grp = choice.view(T, num_expert_group, -1)
+    gscore = grp.topk(2, dim=-1).values.sum(-1) if grp.shape[-1] >= 2 else grp.max(-1).values
+    gidx = gscore.topk(topk_group, dim=-1).indices
+    gmask = torch.zeros_like(gscore).scatter_(1, gidx, 1.0)
+    mask = gmask[:, :, None].expand_as(grp).reshape(T, E)
+    ids = choice.masked_fill(mask == 0, float("-inf")).topk(topk, dim=-1).indices
+    w = sc.gather(1, ids)
+    if renormalize:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return w * float(routed_scaling_factor), ids.to(torch.int32)
+
+
+def _moe_sum(inp, out):
+    torch.sum(inp, dim=1, out=out)
+
+
 def define_c_ops() -> list[str]:
     """Define the missing names (idempotent).  Returns the fully qualified names this call or an earlier one defined."""
     if _LIBS:
@@ -118,4 +157,13 @@ def define_c_ops() -> list[str]:
     _define(lib, "_C", "apply_repetition_penalties_(Tensor! logits, Tensor prompt_mask, Tensor output_mask, "
             "Tensor repetition_penalties) -> ()", _apply_repetition_penalties)
     _define(lib, "_C", "weak_ref_tensor(Tensor input) -> Tensor", lambda t: torch.ops.b200.weak_ref_tensor(t))
+    # routing ops of the MoE namespace (upstream's router calls them by name)
+    moe = torch.library.Library("_moe_C", "FRAGMENT")
+    _LIBS.append(moe)
+    for op, scoring in (("topk_softmax", "softmax"), ("topk_sigmoid", "sigmoid")):
+        _define(moe, "_moe_C", f"{op}(Tensor! topk_weights, Tensor! topk_indices, Tensor! token_expert_indices, "
+                "Tensor gating_output, bool renormalize, Tensor? bias) -> ()", _topk(scoring))
+    _define(moe, "_moe_C", "grouped_topk(Tensor scores, int n_group, int topk_group, int topk, bool renormalize, "
+            "float routed_scaling_factor, Tensor bias, int scoring_func) -> (Tensor, Tensor)", _grouped_topk)
+    _define(moe, "_moe_C", "moe_sum(Tensor input, Tensor! output) -> ()", _moe_sum)
     return DEFINED

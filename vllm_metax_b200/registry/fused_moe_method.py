@@ -32,6 +32,10 @@ def _build_class():
     class B200UnquantizedFusedMoEMethod(_Upstream):
         """Registered under upstream's name, so every unquantised ``FusedMoE`` layer is built with it."""
 
+        @property
+        def is_monolithic(self) -> bool:
+            return False        # routing stays with upstream's router; this method is handed (weights, ids)
+
         def process_weights_after_loading(self, layer: torch.nn.Module) -> None:
             super().process_weights_after_loading(layer)
             # (also after a weight update: the loader rewrites w13 in checkpoint order, in place)
