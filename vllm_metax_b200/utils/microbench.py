@@ -239,6 +239,88 @@ def bench_decode_layer(tp: int, batch: int = 256, ctx: int = 1100) -> dict:
     return res
 
 
+def bench_configs(t: Timer) -> dict:
+    """Kernels that carry the MoE / MLA / long-context serving configurations, at per-rank shapes of an 8-way
+    expert- / tensor-parallel deployment (and the unsharded shape where it fits): grouped expert GEMMs in bf16 and
+    block-scaled fp8, absorbed MLA decode (dense and sparse, bf16 rows and 656-byte fp8 records), the sparse-attention
+    indexer (logits + top-k), paged decode over an int8 cache at 32 k tokens of context."""
+    res = {}
+    bf = torch.bfloat16
+    # ---- grouped expert GEMMs: (label, local experts, hidden, expert FFN), 8192 routed pairs per rank
+    for label, E, H, I in (("qwen3_30b_ep8", 16, 2048, 768), ("dsv3_ep8", 32, 7168, 2048)):
+        pairs = 8192
+        ids = torch.randint(0, E, (pairs, 1), device=DEV, dtype=torch.int32)
+        sorted_ids, block_expert, total, _ = ops.moe_align_block_size(ids, 128, E, None, want_inverse=True)
+        R = sorted_ids.shape[0]
+        a = torch.randn(R, H, device=DEV, dtype=bf)
+        w13 = torch.randn(E, 2 * I, H, device=DEV, dtype=bf) * 0.02
+        w2 = torch.randn(E, H, I, device=DEV, dtype=bf) * 0.02
+        h = torch.randn(R, I, device=DEV, dtype=bf)
+        ms1 = t(lambda: ops.gemm_grouped(a, w13, block_expert, total, epi=1))
+        ms2 = t(lambda: ops.gemm_grouped(h, w2, block_expert, total, epi=0))
+        res[f"grouped_bf16_{label}_w13"] = {"ms": round(ms1, 4), "tflops": round(2 * pairs * 2 * I * H / ms1 / 1e9, 1)}
+        res[f"grouped_bf16_{label}_w2"] = {"ms": round(ms2, 4), "tflops": round(2 * pairs * I * H / ms2 / 1e9, 1)}
+        aq, a_s = ops.per_token_group_quant_fp8(a, 128)
+        w13q = w13.to(torch.float8_e4m3fn)
+        ws13 = torch.ones(E, 2 * I // 128, H // 128, device=DEV, dtype=torch.float32)
+        ms3 = t(lambda: ops.fp8_block_scaled_mm(aq, a_s, w13q, ws13, block_expert=block_expert, total_padded=total))
+        res[f"grouped_fp8_blockscale_{label}_w13"] = {"ms": round(ms3, 4),
+                                                      "tflops": round(2 * pairs * 2 * I * H / ms3 / 1e9, 1)}
+        del a, w13, w2, h, aq, w13q
+    # ---- routing: 8192 tokens, 256 experts, sigmoid grouped top-8 (DeepSeek) and 128 experts softmax top-8 (Qwen3)
+    g256 = torch.randn(8192, 256, device=DEV, dtype=torch.float32)
+    bias = torch.zeros(256, device=DEV)
+    res["grouped_topk_8192x256"] = {"ms": round(t(lambda: ops.grouped_topk(g256, 8, True, 8, 4, "sigmoid", bias, 2.5)), 4)}
+    g128 = torch.randn(8192, 128, device=DEV, dtype=torch.float32)
+    res["topk_softmax_8192x128"] = {"ms": round(t(lambda: ops.topk_gating(g128, 8, True, "softmax")), 4)}
+    # ---- absorbed MLA decode: batch 128 x 8192 tokens of context, 16 heads (TP 8) and 128 heads
+    B, L, bs = 128, 8192, 64
+    nblk = L // bs
+    bt = torch.arange(B * nblk, device=DEV, dtype=torch.int32).view(B, nblk)
+    sl = torch.full((B,), L, device=DEV, dtype=torch.int32)
+    cache_bf = torch.randn(B * nblk, bs, 576, device=DEV, dtype=bf)
+    cache_f8 = torch.randint(0, 120, (B * nblk, bs, 656), device=DEV, dtype=torch.uint8)
+    cache_f8[..., 512:528] = torch.tensor([0, 0, 128, 60] * 4, device=DEV, dtype=torch.uint8)   # scales = 2^-7 (f32)
+    for H in (16, 128):
+        q = torch.randn(B, H, 576, device=DEV, dtype=bf) * 0.1
+        for name, cache, rec in (("bf16", cache_bf, 1152), ("fp8_records", cache_f8, 656)):
+            ms = t(lambda: ops.mla_decode(q, cache, bt, sl, 0.07, max_seq_len=L))
+            res[f"mla_decode_{name}_h{H}_b{B}x{L}"] = {"ms": round(ms, 4), "cache_gbs": round(B * L * rec / ms / 1e6, 1),
+                                                       "tflops": round(2 * B * H * L * (576 + 512) / ms / 1e9, 1)}
+        # sparse (top-k 2048 positions per token)
+        topk = torch.stack([torch.randperm(L, device=DEV)[:2048] for _ in range(4)]).to(torch.int32).repeat(B // 4, 1)
+        ms = t(lambda: ops.mla_decode(q, cache_f8, bt, sl, 0.07, topk_indices=topk, max_seq_len=L))
+        res[f"mla_sparse_decode_fp8_h{H}_b{B}_top2048"] = {"ms": round(ms, 4),
+                                                            "cache_gbs": round(B * 2048 * 656 / ms / 1e6, 1)}
+    # sparse prefill: 1024 new tokens of one request with 8192 tokens of context, 16 heads
+    qp = torch.randn(1024, 16, 576, device=DEV, dtype=bf) * 0.1
+    qsl = torch.tensor([0, 1024], device=DEV, dtype=torch.int32)
+    topk_p = torch.stack([torch.randperm(L, device=DEV)[:2048] for _ in range(8)]).to(torch.int32).repeat(128, 1)
+    ms = t(lambda: ops.mla_decode(qp, cache_f8, bt[:1], sl[:1], 0.07, query_start_loc=qsl, topk_indices=topk_p,
+                                  max_seq_len=L))
+    res["mla_sparse_prefill_fp8_h16_1024tok_top2048"] = {"ms": round(ms, 4),
+                                                          "tflops": round(2 * 1024 * 16 * 2048 * 1088 / ms / 1e9, 1)}
+    del cache_bf, cache_f8
+    # ---- indexer: 64 heads x 128, fp8 keys (132 bytes per token), logits + top-2048
+    for Lk, T in ((8192, 1024), (32768, 256)):
+        nb = Lk // bs
+        idx_cache = torch.randint(0, 100, (nb, bs * 132), device=DEV, dtype=torch.uint8)
+        idx_cache.view(nb, bs * 132)[:, bs * 128:] = torch.tensor([0, 0, 128, 60], device=DEV, dtype=torch.uint8).repeat(bs)
+        qi = (torch.randn(T, 64, 128, device=DEV) * 0.5).to(torch.float8_e4m3fn)
+        wts = torch.rand(T, 64, device=DEV)
+        bti = torch.arange(nb, device=DEV, dtype=torch.int32).view(1, nb)
+        sli = torch.tensor([Lk], device=DEV, dtype=torch.int32)
+        qsli = torch.tensor([0, T], device=DEV, dtype=torch.int32)
+        ms = t(lambda: ops.indexer_topk(qi, wts, idx_cache, bti, sli, qsli, 2048, bs, max_seq_len=Lk))
+        res[f"indexer_logits_topk_T{T}_L{Lk}"] = {"ms": round(ms, 4),
+                                                  "tflops": round(2 * T * 64 * Lk * 128 / ms / 1e9, 1)}
+    # ---- paged decode over an int8 cache: 32 sequences x 32768 tokens, 8 q / 1 kv head (TP 8) and 64 / 8
+    for Hq, Hkv in ((8, 1), (64, 8)):
+        res[f"attn_decode_int8kv_32x32768_h{Hq}"] = bench_decode(t, 32, 32768, Hq, Hkv, 128, 128, "int8")
+        res[f"attn_decode_bf16kv_32x32768_h{Hq}"] = bench_decode(t, 32, 32768, Hq, Hkv, 128, 128, "bf16")
+    return res
+
+
 def bench_quant(t, M: int, N: int, K: int) -> dict:
     """Quantised GEMMs at one shape (TFLOP/s over 2 M N K) and the TurboQuant decode kernel (bytes of compressed
     cache streamed per second)."""
@@ -319,7 +401,7 @@ def bench_linear_attention(t: Timer) -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "gemm", "prefill", "decode", "elementwise", "quant", "linear_attention", "skinny", "decode_layer"])
+    ap.add_argument("--op", default="all", choices=["all", "gemm", "prefill", "decode", "elementwise", "quant", "linear_attention", "skinny", "decode_layer", "configs"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
@@ -354,6 +436,8 @@ def main() -> None:
         res.update(bench_linear_attention(t))
     if a.op == "skinny":
         res.update(bench_skinny(t))
+    if a.op == "configs":
+        res.update(bench_configs(t))
     if a.op == "decode_layer":
         for tp in (1, 8):
             res[f"decode_layer_tp{tp}_b{a.batch}"] = bench_decode_layer(tp, a.batch, a.seq)
