@@ -78,6 +78,9 @@ def _shutdown():
 
 
 def _fused_ar_worker(rank, world, kernel="split"):
+    if kernel == "split_peer_stores":          # the split path without the NVLink multicast gather
+        os.environ["B200_USE_MULTIMEM"] = "0"
+        kernel = "split"
     os.environ["B200_FUSED_TP_KERNEL"] = kernel
     from vllm_metax_b200 import _custom_ops as ops
     from vllm_metax_b200.ops import reference as ref
@@ -120,7 +123,7 @@ def _fused_ar_worker(rank, world, kernel="split"):
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("kernel", ["split", "mono"])
+@pytest.mark.parametrize("kernel", ["split", "split_peer_stores", "mono"])
 def test_fused_gemm_allreduce_norm_2gpu(kernel):
     _launch(_fused_ar_worker, _world(), kernel)
 

@@ -742,7 +742,7 @@ void gemm_row_scatter(const Tensor& x, const Tensor& w, const Tensor& ptrs, int6
 // ptrs: CPU int64 [4, tp] = recv / flag1 / flag2 / out base per rank.
 void ar_norm_gather(Tensor& residual, const Tensor& norm_weight, double eps, const Tensor& ptrs, int64_t T, int64_t H,
                     int64_t tp, int64_t rank, int64_t rows_per_rank, int64_t rows_cap, Tensor& local_sync,
-                    bool add_residual, int64_t wait_cycles) {
+                    bool add_residual, int64_t wait_cycles, int64_t out_multicast_ptr) {
   TORCH_CHECK(tp >= 1 && tp <= b200::kMaxRanks && ptrs.dim() == 2 && ptrs.size(0) == 4 && ptrs.size(1) >= tp);
   TORCH_CHECK(!ptrs.is_cuda() && ptrs.scalar_type() == at::kLong && residual.is_contiguous());
   TORCH_CHECK(residual.size(-1) == H && norm_weight.numel() == H && residual.size(0) >= rows_per_rank);
@@ -756,6 +756,7 @@ void ar_norm_gather(Tensor& residual, const Tensor& norm_weight, double eps, con
     p.flag2[r] = reinterpret_cast<uint32_t*>(pp[2 * st + r]);
     p.out[r] = reinterpret_cast<void*>(pp[3 * st + r]);
   }
+  p.out_mc = reinterpret_cast<void*>(out_multicast_ptr);
   p.residual = residual.data_ptr();
   p.norm_weight = norm_weight.data_ptr();
   p.eps = (float)eps;
@@ -1360,7 +1361,8 @@ TORCH_LIBRARY(b200, m) {
       &gemm_row_scatter);
   m.def(
       "ar_norm_gather(Tensor(a!) residual, Tensor norm_weight, float eps, Tensor ptrs, int T, int H, int tp, int rank, "
-      "int rows_per_rank, int rows_cap, Tensor(b!) local_sync, bool add_residual, int wait_cycles) -> ()",
+      "int rows_per_rank, int rows_cap, Tensor(b!) local_sync, bool add_residual, int wait_cycles, "
+      "int out_multicast_ptr=0) -> ()",
       &ar_norm_gather);
   m.def(
       "gemm_ar_norm(Tensor x, Tensor w, Tensor(a!) residual, Tensor norm_weight, float eps, Tensor ptrs, int tp, "

@@ -7,7 +7,9 @@
 //   reduce   my rows: sum of the tp partial rows in rank order (bit-identical on every rank whoever computes it),
 //            + my shard of the residual stream -> new residual (kept sharded by rows between calls)
 //   norm     RMSNorm of the row
-//   gather   the normalised row is stored into EVERY rank's output buffer (peer stores over NVLink)
+//   gather   the normalised row is stored into EVERY rank's output buffer: one multimem.st per 16 bytes when the
+//            buffers are mapped as an NVLink multicast object (the switch replicates it: 1/tp of the bytes leave
+//            the GPU), else one peer store per rank
 //   close    the last CTA raises flag2[d][me] on every rank d and waits (bounded) for flag2[me][o] of every owner
 //            o, so when the kernel has finished on a rank, that rank's output buffer is complete and every peer
 //            has finished reading the receive slots of this call.
@@ -21,6 +23,13 @@
 #include "ops.h"
 
 namespace b200 {
+
+// One 16-byte store that the NVSwitch replicates into every rank's copy of a multicast-mapped buffer.
+__device__ __forceinline__ void multimem_st_u4(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
 
 // every source's pushes for this call have landed (bounded); returns false after a timeout
 __device__ __forceinline__ bool arn_wait_pushes(const ArNormParams& p, uint32_t epoch, int* s_ok) {
@@ -112,9 +121,13 @@ ar_norm_gather_kernel(const ArNormParams p) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) f[i] = f[i] * inv * w[i];
       const uint4 y = pack8<T>(f);
-      for (int d = 0; d < p.tp; ++d) {
-        const int dst = (p.rank + d) % p.tp;         // start with the local copy, spread the peers
-        reinterpret_cast<uint4*>(static_cast<T*>(p.out[dst]) + grow)[v] = y;
+      if (p.out_mc) {
+        multimem_st_u4(reinterpret_cast<uint4*>(static_cast<T*>(p.out_mc) + grow) + v, y);
+      } else {
+        for (int d = 0; d < p.tp; ++d) {
+          const int dst = (p.rank + d) % p.tp;       // start with the local copy, spread the peers
+          reinterpret_cast<uint4*>(static_cast<T*>(p.out[dst]) + grow)[v] = y;
+        }
       }
     }
     __syncthreads();                                 // `row` and `red` are rewritten by the next row
@@ -186,9 +199,13 @@ ar_norm_gather_reg_kernel(const ArNormParams p) {
 #pragma unroll
       for (int e = 0; e < 8; ++e) f[i][e] = f[i][e] * inv * w[e];
       const uint4 y = pack8<T>(f[i]);
-      for (int d = 0; d < p.tp; ++d) {
-        const int dst = (p.rank + d) % p.tp;
-        reinterpret_cast<uint4*>(static_cast<T*>(p.out[dst]) + grow)[threadIdx.x + i * 128] = y;
+      if (p.out_mc) {
+        multimem_st_u4(reinterpret_cast<uint4*>(static_cast<T*>(p.out_mc) + grow) + threadIdx.x + i * 128, y);
+      } else {
+        for (int d = 0; d < p.tp; ++d) {
+          const int dst = (p.rank + d) % p.tp;
+          reinterpret_cast<uint4*>(static_cast<T*>(p.out[dst]) + grow)[threadIdx.x + i * 128] = y;
+        }
       }
     }
   }

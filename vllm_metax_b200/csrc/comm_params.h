@@ -52,6 +52,8 @@ struct ArNormParams {
   uint32_t* flag1[kMaxRanks];     // [tp] push epochs (written by the GEMMs)
   uint32_t* flag2[kMaxRanks];     // [tp] gather epochs (written by this kernel)
   void* out[kMaxRanks];           // [T_cap, H] normalised rows on every rank
+  void* out_mc;                   // the same buffers as ONE NVLink multicast address (multimem.st reaches every
+                                  // rank's copy through the switch), or null: one peer store per rank
   void* residual;                 // [rows_per_rank, H] this rank's shard of the residual stream (in/out)
   const void* norm_weight;        // [H]
   float eps;

@@ -151,6 +151,7 @@ class StaticWorkload:
         torch.cuda.synchronize()
         ok = p_cos < 2e-3 and d_cos < 2e-3
         return {"fused_path": bool(saved[0] is not None), "peer_allreduce": bool(saved[1] is not None),
+                "multicast_gather": bool(getattr(saved[0], "out_mc", 0)),
                 "prefill_tokens": int(ids.shape[0]), "cos_diff": round(max(p_cos, d_cos), 6),
                 "max_abs": round(max(p_abs, d_abs), 4), "ref_max_abs": round(max(p_ref, d_ref), 3),
                 "decode_cos_diff": round(d_cos, 6), "ok": bool(ok)}

@@ -62,6 +62,9 @@ environment_variables: dict[str, Callable[[], Any]] = {
     "B200_USE_FUSED_GROUPED_TOPK": _flag("B200_USE_FUSED_GROUPED_TOPK", "1"),
     # CUDA-graph capture of decode steps.
     "B200_CUDA_GRAPHS": _flag("B200_CUDA_GRAPHS", "1"),
+    # All-gather leg of the fused row-parallel path through an NVLink multicast mapping (one multimem.st, replicated
+    # by the switch) when torch's symmetric memory can provide one; 0 = one peer store per rank.
+    "B200_USE_MULTIMEM": _flag("B200_USE_MULTIMEM", "1"),
     # Iteration budget of device-side waits on peer flags before giving up.
     "B200_PEER_WAIT_ITERS": _int("B200_PEER_WAIT_ITERS", 20_000_000),
     "B200_PP_DISABLE_ALLGATHER": _flag("B200_PP_DISABLE_ALLGATHER", "0"),

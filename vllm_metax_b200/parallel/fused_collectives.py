@@ -71,9 +71,40 @@ class FusedRowParallelNorm:
                                          self.ws.peer_ptrs(r_out)], dtype=torch.int64)
         self.local_sync = torch.zeros(4, dtype=torch.int32, device=device)
         self.local_sync_split = torch.zeros(4, dtype=torch.int32, device=device)
+        self.out_mc = 0
+        self._ipc_out, self._ipc_ptrs_gather = self.out, self.ptrs_gather
+        if envs.B200_USE_MULTIMEM and self.tp > 1:
+            self._try_multicast_out(n_out, dtype, max_tokens, hidden, r_recv, r_f1, r_f2)
         self.wait_cycles = int(envs.B200_PEER_WAIT_ITERS) * 200  # iteration budget expressed in SM cycles
         torch.cuda.synchronize(device)
         group.barrier()
+
+    def _try_multicast_out(self, n_out, dtype, max_tokens, hidden, r_recv, r_f1, r_f2) -> None:
+        """Puts the all-gathered output buffer into torch's symmetric memory, which binds the ranks' copies to ONE
+        NVLink multicast address when the fabric supports it: the gather kernel then issues a single
+        ``multimem.st`` per 16 bytes and the NVSwitch replicates it (1/tp of the bytes leave the GPU).  Any failure
+        keeps the IPC buffer and the per-rank peer stores."""
+        try:
+            import torch.distributed._symmetric_memory as symm
+
+            buf = symm.empty(n_out, dtype=torch.uint8, device=self.device)
+            hdl = symm.rendezvous(buf, self.group.device_pg)
+            mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+            ptrs = [int(p) for p in hdl.buffer_ptrs]
+            if mc == 0 or len(ptrs) != self.tp:
+                return
+            self._mc_buf, self._mc_hdl = buf, hdl
+            self.out = buf.view(dtype).view(max_tokens, hidden)
+            self.out_mc = mc
+            self.ptrs_gather = torch.tensor([self.ws.peer_ptrs(r_recv), self.ws.peer_ptrs(r_f1),
+                                             self.ws.peer_ptrs(r_f2), ptrs], dtype=torch.int64)
+        except Exception:      # no multicast support in this torch build / driver / fabric
+            self.out_mc = 0
+
+    def disable_multicast(self) -> None:
+        """Back to the IPC output buffer and per-rank peer stores (start-up check failed with multicast on)."""
+        self.out_mc = 0
+        self.out, self.ptrs_gather = self._ipc_out, self._ipc_ptrs_gather
 
     def __call__(self, x: torch.Tensor, weight: torch.Tensor, residual_shard: torch.Tensor,
                  norm_weight: torch.Tensor, eps: float, add_residual: bool = True) -> torch.Tensor:
@@ -95,7 +126,7 @@ class FusedRowParallelNorm:
                                             self.local_sync_split)
             torch.ops.b200.ar_norm_gather(residual_shard, norm_weight, eps, self.ptrs_gather, T, self.hidden, self.tp,
                                           self.rank, rpr, self.rows_cap, self.local_sync_split, add_residual,
-                                          self.wait_cycles)
+                                          self.wait_cycles, self.out_mc)
             return self.out[:T]
         # CPU ranks: same contract through plain collectives
         part = ref.gemm(x, weight, out_dtype=torch.float32)

@@ -83,6 +83,7 @@ def main() -> None:
     want = lambda sec: not only or sec in only      # noqa: E731
     fused = FusedRowParallelNorm(g, dev, max(a.tokens), H, bf)
     nw = torch.ones(H, dtype=bf, device=dev)
+    res["multicast_gather"] = bool(fused.out_mc)
 
     for T in (a.tokens if want("row") else []):
         for name, K in (("o_proj", H // world), ("down_proj", I // world)):
@@ -108,7 +109,7 @@ def main() -> None:
                                                                  fused.rows_cap, fused.local_sync_split), a.iters, pg)
             t_n = timed(lambda: torch.ops.b200.ar_norm_gather(shard, nw, 1e-5, fused.ptrs_gather, T, H, world, rank,
                                                                rpr, fused.rows_cap, fused.local_sync_split, True,
-                                                               fused.wait_cycles), a.iters, pg)
+                                                               fused.wait_cycles, fused.out_mc), a.iters, pg)
             y_loc = torch.empty(T, H, dtype=bf, device=dev)
             t_l = timed(lambda: ops.gemm(x, w, out=y_loc), a.iters, pg)
             flops = 2.0 * T * H * K
