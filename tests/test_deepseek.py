@@ -89,7 +89,7 @@ def _mla_case(lens, qlens, H, bs, fp8, seed=0):
 
 
 @gpu
-@pytest.mark.parametrize("H", [16, 128, 8])
+@pytest.mark.parametrize("H", [16, 128, 8, 32, 48])
 @pytest.mark.parametrize("fp8", [False, True])
 @pytest.mark.parametrize("splits", [1, 3])
 def test_mla_decode_gpu(H, fp8, splits, kernel_status_ok):

@@ -853,7 +853,9 @@ def mla_decode(q, mla_cache, block_table, seq_lens, scale, *, query_start_loc=No
         T, H, _ = q.shape
         out = torch.empty(T, H, 512, dtype=q.dtype, device=q.device) if out is None else out
         if num_splits <= 0:
-            ctas = T * ((H + 15) // 16)
+            # heads per CTA as chosen by the kernel launcher (csrc/mla_decode.cu:mla_decode_heads_per_cta)
+            hpc = 16 if H <= 16 else (32 if (H <= 32 or mla_cache.dtype == torch.uint8) else 64)
+            ctas = T * ((H + hpc - 1) // hpc)
             kv = topk_indices.shape[1] if topk_indices is not None else (max_seq_len or 4096)
             num_splits = 1 if ctas >= 148 else max(1, min((296 + ctas - 1) // ctas, kv // 256, 16))
         ws = _decode_workspace(q.device, num_splits * T * H * 513) if num_splits > 1 else None

@@ -18,6 +18,7 @@
 // Cache layout [num_blocks, 2, block_size, num_kv_heads, D]; block_size % 16 == 0.
 // Replaces flash_attn_with_kvcache (vllm_metax/v1/attention/backends/flash_attn.py:1339-1355)
 // and the Triton unified_attention int8 path (triton_attn.py:688-725).
+#include <type_traits>
 #include "common.cuh"
 #include "ops.h"
 
@@ -77,6 +78,24 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   return (uint32_t)(*reinterpret_cast<uint16_t*>(&lo)) | ((uint32_t)(*reinterpret_cast<uint16_t*>(&hi)) << 16);
 }
 
+
+// Eight int8 values -> eight bf16 values without the conversion unit: a byte b (as b ^ 0x80 = b + 128, unsigned)
+// dropped into the mantissa of 2^23 gives the float 8388608 + b + 128; subtracting 8388736 leaves b exactly, and a
+// float holding an integer of at most 8 significant bits has zero low mantissa bits, so its upper half IS the bf16.
+__device__ __forceinline__ uint4 int8x8_to_bf16x8(const uint2 raw) {
+  const uint32_t w[2] = {raw.x ^ 0x80808080u, raw.y ^ 0x80808080u};
+  uint32_t out[4];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float f[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      f[i] = __uint_as_float(__byte_perm(w[h], 0x4B000000u, 0x7540 + i)) - 8388736.f;
+    out[2 * h] = __byte_perm(__float_as_uint(f[0]), __float_as_uint(f[1]), 0x7632);
+    out[2 * h + 1] = __byte_perm(__float_as_uint(f[2]), __float_as_uint(f[3]), 0x7632);
+  }
+  return make_uint4(out[0], out[1], out[2], out[3]);
+}
 
 template <int D, int KIND>
 struct DecSmem {
@@ -239,11 +258,17 @@ __global__ void __launch_bounds__(kDecWarps * 32, (D <= 128 ? 2 : 1)) paged_deco
         for (int idx = lane; idx < kDecTile * CPR; idx += 32) {
           const int r = idx / CPR, c = idx % CPR;
           const uint2 raw = *reinterpret_cast<const uint2*>(st + kv * S::kRawTile + r * S::kRawRow + c * 8);
-          const uint8_t* rb = reinterpret_cast<const uint8_t*>(&raw);
-          float f[8];
+          uint4 packed;
+          if constexpr (KIND == 1 && std::is_same<T, __nv_bfloat16>::value) {
+            packed = int8x8_to_bf16x8(raw);           // integer ALU only: no conversion-unit instruction
+          } else {
+            const uint8_t* rb = reinterpret_cast<const uint8_t*>(&raw);
+            float f[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) f[i] = (KIND == 1) ? (float)(int8_t)rb[i] : fp8_e4m3_to_float(rb[i]);
-          *reinterpret_cast<uint4*>(conv + kv * S::kTileBytes + r * S::kRowBytes + ((c ^ (r & 7)) * 16)) = pack8<T>(f);
+            for (int i = 0; i < 8; ++i) f[i] = (KIND == 1) ? (float)(int8_t)rb[i] : fp8_e4m3_to_float(rb[i]);
+            packed = pack8<T>(f);
+          }
+          *reinterpret_cast<uint4*>(conv + kv * S::kTileBytes + r * S::kRowBytes + ((c ^ (r & 7)) * 16)) = packed;
         }
       }
       if constexpr (KIND == 1 || KIND == 2) {

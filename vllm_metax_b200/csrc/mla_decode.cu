@@ -8,12 +8,10 @@
 // Dense: token t of sequence b sees cache positions < seq_len - q_len + i + 1.
 // Sparse (DeepSeek sparse attention): only the positions listed in topk_indices[t, :] (-1 = none).
 //
-// One CTA = one query token x 16 heads (one m16 MMA row tile).  The 4 warps share a 3-stage
-// cp.async ring of 16-token latent tiles; for each tile the QK^T contraction (576 = 36 k-steps)
-// is split four ways and summed through shared memory, every warp then runs the same online
-// softmax and multiplies P into ITS 128 of the 512 value columns - the value operand is the
-// first 512 columns of the very tile that served as K, read with ldmatrix.trans.
-// With 16 heads per rank (TP8 of 128 heads) the kernel is HBM-bound like GQA decode.
+// One CTA = one query token x 16 / 32 / 64 heads x one KV split; 8 warps walk 64-token latent tiles through a
+// two-slot cp.async ring (see the kernel's comment for the division of work).  The latent rows of a token are
+// read once per CTA, so the more heads a CTA covers the less cache traffic; with 16 heads per rank (TP 8 of 128
+// heads) the kernel is a stream over the cache like GQA decode.
 // Replaces flash_mla_with_kvcache / flash_mla_sparse_fwd / the Triton split-KV MLA decode
 // (vllm_metax/v1/attention/backends/mla/flashmla.py:339-349, flashmla_sparse.py:973-1084,
 // ops/triton_decode_attention.py:72-825).
@@ -22,10 +20,9 @@
 
 namespace b200 {
 
-constexpr int kMlaD = 576, kMlaDV = 512, kMlaTile = 16, kMlaStages = 3, kMlaWarps = 4;
+constexpr int kMlaD = 576, kMlaDV = 512;
 constexpr int kMlaRowBytes = kMlaD * 2;          // 1152
 constexpr int kMlaCPR = kMlaRowBytes / 16;       // 72 chunks per row
-constexpr int kMlaTileBytes = kMlaTile * kMlaRowBytes;
 constexpr int kMlaRecBytes = 656;
 
 __device__ __forceinline__ void mla_cp16(void* smem, const void* gmem, bool valid) {
@@ -63,24 +60,42 @@ __device__ __forceinline__ uint32_t mla_pack2(float a, float b) {
   return (uint32_t)(*reinterpret_cast<uint16_t*>(&lo)) | ((uint32_t)(*reinterpret_cast<uint16_t*>(&hi)) << 16);
 }
 
-struct MlaSmem {
-  static constexpr int kQ = 0;                                   // 16 x 1152
-  static constexpr int kRing = kQ + kMlaTileBytes;               // stages x tile (bf16, swizzled)
-  static constexpr int kRaw = kRing + kMlaStages * kMlaTileBytes;  // fp8 records staging: stages x 16 x 656
-  static constexpr int kRawBytes = kMlaStages * kMlaTile * kMlaRecBytes;
-  static constexpr int kSPart = kRaw + kRawBytes;                // 4 x 256 floats
-  static constexpr int kTotal = kSPart + kMlaWarps * 256 * 4 + 64;
+constexpr int kMlaTok = 64;                       // latent rows per tile
+constexpr int kMlaThreads = 256;                  // 8 warps: warp w owns tile tokens [8w, 8w+8) and output columns [64w, 64w+64)
+constexpr int kMlaTileB = kMlaTok * kMlaRowBytes; // 72 KB
+
+// Shared-memory plan for MT m16 row tiles (16 * MT heads per CTA).
+template <int MT, bool FP8>
+struct MlaSmem2 {
+  static constexpr int kQ = 0;                                        // 16 MT x 1152, swizzled
+  static constexpr int kQBytes = 16 * MT * kMlaRowBytes;
+  static constexpr int kRawStage = kMlaTok * kMlaRecBytes;            // fp8 records of one tile
+  static constexpr int kRing = kQ + kQBytes;                          // 2 stages: bf16 tiles, or raw records when FP8
+  static constexpr int kRingBytes = 2 * (FP8 ? kRawStage : kMlaTileB);
+  static constexpr int kConv = kRing + kRingBytes;                    // FP8: the dequantised tile
+  static constexpr int kConvBytes = FP8 ? kMlaTileB : 0;
+  static constexpr int kP = kConv + kConvBytes;                       // 16 MT rows x 64 tokens, 16-bit, swizzled
+  static constexpr int kPBytes = 16 * MT * kMlaTok * 2;
+  static constexpr int kMax = kP + kPBytes;                           // [8 warps][16 MT] row maxima, later row sums
+  static constexpr int kMaxBytes = 8 * 16 * MT * 4;
+  static constexpr int kPos = kMax + kMaxBytes;                       // [2][64] cache position of every tile row
+  static constexpr int kTotal = kPos + 2 * kMlaTok * 4 + 16;
 };
 
-// FP8: cache rows are 656-byte records that are dequantised into the bf16 ring.
-template <typename T, bool FP8>
-__global__ void __launch_bounds__(kMlaWarps * 32)
+// One CTA = one query token x 16 MT heads x one KV split.  Per 64-token tile: every warp multiplies ALL of the CTA's
+// rows with ITS 8 tokens over the full 576-wide contraction (no cross-warp reduction of partial scores), the row
+// maxima are exchanged through shared memory, P goes to shared memory once, and every warp multiplies P into ITS 64
+// of the 512 value columns - the value operand is the first 512 columns of the very tile that served as K
+// (ldmatrix.trans).  Four CTA barriers per 64 tokens; the latent rows of a token are read once per 16 MT heads.
+template <typename T, bool FP8, int MT>
+__global__ void __launch_bounds__(kMlaThreads, 1)
 mla_decode_kernel(const MlaDecodeParams p) {
+  using S = MlaSmem2<MT, FP8>;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ int s_seq, s_lim;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.y;
-  const int h0 = blockIdx.x * 16;
+  const int h0 = blockIdx.x * 16 * MT;
   const int split = blockIdx.z;
   if (threadIdx.x == 0) {
     // sequence of token t: last b with query_start_loc[b] <= t
@@ -101,19 +116,22 @@ mla_decode_kernel(const MlaDecodeParams p) {
   __syncthreads();
   const int seq = s_seq, lim = s_lim;
   const int n_entries = p.topk_indices ? p.topk : lim;     // logical kv list length
-  const int tiles_total = (n_entries + kMlaTile - 1) / kMlaTile;
+  const int tiles_total = (n_entries + kMlaTok - 1) / kMlaTok;
   const int tiles_per_split = (tiles_total + p.num_splits - 1) / p.num_splits;
   const int tile_begin = split * tiles_per_split;
   const int tile_end = min(tiles_total, tile_begin + tiles_per_split);
   const int* btab = p.block_table + (int64_t)seq * p.max_blocks;
   const int* idx_row = p.topk_indices ? p.topk_indices + (int64_t)t * p.topk : nullptr;
-  uint8_t* q_smem = smem + MlaSmem::kQ;
-  float* s_part = reinterpret_cast<float*>(smem + MlaSmem::kSPart);
+  uint8_t* q_smem = smem + S::kQ;
+  uint8_t* p_smem = smem + S::kP;
+  float* s_max = reinterpret_cast<float*>(smem + S::kMax);
+  int* s_pos = reinterpret_cast<int*>(smem + S::kPos);
+  const long long kv_cap = (long long)p.max_blocks * p.block_size;
 
-  // ---- Q rows (heads h0..h0+15 of token t), swizzled
+  // ---- Q rows (heads h0 .. h0 + 16 MT - 1 of token t), swizzled; rows beyond the head count are zero
   {
     const T* qb = reinterpret_cast<const T*>(p.q) + (int64_t)t * p.q_stride;
-    for (int i = threadIdx.x; i < 16 * kMlaCPR; i += blockDim.x) {
+    for (int i = threadIdx.x; i < 16 * MT * kMlaCPR; i += blockDim.x) {
       const int r = i / kMlaCPR, c = i % kMlaCPR;
       uint4 v = make_uint4(0, 0, 0, 0);
       if (h0 + r < p.num_heads) v = *reinterpret_cast<const uint4*>(qb + (int64_t)(h0 + r) * kMlaD + c * 8);
@@ -121,67 +139,66 @@ mla_decode_kernel(const MlaDecodeParams p) {
     }
   }
 
-  // position of entry e of the kv list, or -1
+  // cache position of entry e of the kv list, or -1 (beyond the list, masked by causality, or a bad index)
   auto pos_of = [&](int e) -> int {
     if (e >= n_entries) return -1;
-    if (!idx_row) return e;
-    const int v = idx_row[e];
-    return (v >= 0 && v < lim) ? v : -1;
+    int v = e;
+    if (idx_row) v = idx_row[e];
+    return (v >= 0 && v < lim && v < kv_cap) ? v : -1;
   };
-  auto issue = [&](int tile, int stage) {
+  // positions of tile `tile` into s_pos[slot] (threads 0..63), then - after a barrier - issue_rows copies them
+  auto stage_positions = [&](int tile, int slot) {
+    if (threadIdx.x < kMlaTok) s_pos[slot * kMlaTok + threadIdx.x] = tile < tile_end ? pos_of(tile * kMlaTok + threadIdx.x) : -1;
+  };
+  auto issue_rows = [&](int tile, int slot) {
     if (tile >= tile_end) return;
     const uint8_t* cache = reinterpret_cast<const uint8_t*>(p.cache);
-    if (!FP8) {
-      uint8_t* dst = smem + MlaSmem::kRing + stage * kMlaTileBytes;
-      for (int i = threadIdx.x; i < kMlaTile * kMlaCPR; i += blockDim.x) {
-        const int r = i / kMlaCPR, c = i % kMlaCPR;
-        const int pos = pos_of(tile * kMlaTile + r);
-        const uint8_t* src = cache;
-        if (pos >= 0) {
-          int page = btab[pos / p.block_size];
-          if (page < 0 || page >= p.num_blocks) { report_status(p.status, kBadIndex, 95, (int)p.num_blocks, page); page = 0; }
-          src = cache + ((int64_t)page * p.block_size + pos % p.block_size) * kMlaRowBytes + c * 16;
-        }
-        mla_cp16(dst + r * kMlaRowBytes + ((c ^ (r & 7)) * 16), src, pos >= 0);
+    constexpr int CH = FP8 ? 41 : kMlaCPR;                   // 16-byte chunks per stored row
+    constexpr int RB = FP8 ? kMlaRecBytes : kMlaRowBytes;
+    uint8_t* dst = smem + S::kRing + slot * (FP8 ? S::kRawStage : kMlaTileB);
+    for (int i = threadIdx.x; i < kMlaTok * CH; i += blockDim.x) {
+      const int r = i / CH, c = i % CH;
+      const int pos = s_pos[slot * kMlaTok + r];
+      const uint8_t* src = cache;
+      if (pos >= 0) {
+        int page = btab[pos / p.block_size];
+        if (page < 0 || page >= p.num_blocks) { report_status(p.status, kBadIndex, 95, (int)p.num_blocks, page); page = 0; }
+        src = cache + ((int64_t)page * p.block_size + pos % p.block_size) * RB + c * 16;
       }
-    } else {
-      uint8_t* dst = smem + MlaSmem::kRaw + stage * (kMlaTile * kMlaRecBytes);
-      for (int i = threadIdx.x; i < kMlaTile * 41; i += blockDim.x) {
-        const int r = i / 41, c = i % 41;
-        const int pos = pos_of(tile * kMlaTile + r);
-        const uint8_t* src = cache;
-        if (pos >= 0) {
-          int page = btab[pos / p.block_size];
-          if (page < 0 || page >= p.num_blocks) { report_status(p.status, kBadIndex, 96, (int)p.num_blocks, page); page = 0; }
-          src = cache + ((int64_t)page * p.block_size + pos % p.block_size) * kMlaRecBytes + c * 16;
-        }
-        mla_cp16(dst + r * kMlaRecBytes + c * 16, src, pos >= 0);
-      }
+      const int dc = FP8 ? c : (c ^ (r & 7));
+      mla_cp16(dst + r * RB + dc * 16, src, pos >= 0);
     }
   };
 
   const float sl2 = p.scale * 1.4426950408889634f;
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-  float o[16][4];
+  float m_run[MT][2], l_run[MT][2];
+  float o[MT][8][4];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-
+  for (int mt = 0; mt < MT; ++mt) {
+    m_run[mt][0] = m_run[mt][1] = -INFINITY;
+    l_run[mt][0] = l_run[mt][1] = 0.f;
 #pragma unroll
-  for (int s = 0; s < kMlaStages - 1; ++s) {
-    issue(tile_begin + s, s);
-    asm volatile("cp.async.commit_group;" ::: "memory");
+    for (int i = 0; i < 8; ++i) o[mt][i][0] = o[mt][i][1] = o[mt][i][2] = o[mt][i][3] = 0.f;
   }
-  int stage = 0;
-  for (int tile = tile_begin; tile < tile_end; ++tile) {
-    issue(tile + kMlaStages - 1, (stage + kMlaStages - 1) % kMlaStages);
+
+  stage_positions(tile_begin, 0);
+  __syncthreads();
+  issue_rows(tile_begin, 0);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  int slot = 0;
+  for (int tile = tile_begin; tile < tile_end; ++tile, slot ^= 1) {
+    stage_positions(tile + 1, slot ^ 1);
+    __syncthreads();                       // positions visible; the other slot and P / s_max are free again
+    issue_rows(tile + 1, slot ^ 1);
     asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group %0;" ::"n"(kMlaStages - 1) : "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncthreads();
-    uint8_t* kt = smem + MlaSmem::kRing + stage * kMlaTileBytes;
+    const uint8_t* kt = smem + S::kRing + slot * kMlaTileB;
     if (FP8) {
-      // dequantise the 16 records of this stage into the swizzled bf16 tile
-      const uint8_t* raw = smem + MlaSmem::kRaw + stage * (kMlaTile * kMlaRecBytes);
-      for (int i = threadIdx.x; i < kMlaTile * kMlaCPR; i += blockDim.x) {
+      // dequantise the 64 records of this slot into the swizzled 16-bit tile
+      const uint8_t* raw = smem + S::kRing + slot * S::kRawStage;
+      uint8_t* conv = smem + S::kConv;
+      for (int i = threadIdx.x; i < kMlaTok * kMlaCPR; i += blockDim.x) {
         const int r = i / kMlaCPR, c = i % kMlaCPR;
         const uint8_t* rec = raw + r * kMlaRecBytes;
         uint4 outv;
@@ -200,149 +217,159 @@ mla_decode_kernel(const MlaDecodeParams p) {
           for (int j = 0; j < 8; ++j) f[j] = __bfloat162float(pe[j]);
           outv = pack8<T>(f);
         }
-        *reinterpret_cast<uint4*>(kt + r * kMlaRowBytes + ((c ^ (r & 7)) * 16)) = outv;
+        *reinterpret_cast<uint4*>(conv + r * kMlaRowBytes + ((c ^ (r & 7)) * 16)) = outv;
       }
       __syncthreads();
+      kt = conv;
     }
-    // ---- partial S over this warp's 9 k-steps
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    // ---- S[rows, my 8 tokens] over the whole contraction: 18 pairs of k-steps
+    float sc[MT][4];
 #pragma unroll
-    for (int kk = 0; kk < 9; ++kk) {
-      const int ks = warp * 9 + kk;
-      const int mat = lane >> 3;
-      uint32_t qf[4], kf[4];
-      {
-        const int r = (mat & 1) * 8 + (lane & 7), c = 2 * ks + (mat >> 1);
-        mla_ldm(qf, q_smem + r * kMlaRowBytes + ((c ^ (r & 7)) * 16));
-      }
-      {
-        const int r = (mat >> 1) * 8 + (lane & 7), c = 2 * ks + (mat & 1);
-        mla_ldm(kf, kt + r * kMlaRowBytes + ((c ^ (r & 7)) * 16));
-      }
-      mla_mma<T>(s[0], qf, kf[0], kf[1]);
-      mla_mma<T>(s[1], qf, kf[2], kf[3]);
-    }
+    for (int mt = 0; mt < MT; ++mt) sc[mt][0] = sc[mt][1] = sc[mt][2] = sc[mt][3] = 0.f;
     {
-      float* mine = s_part + warp * 256;
-      const int ra = lane >> 2, c0 = 2 * (lane & 3);
+      const int mat = lane >> 3;
+      const int kr = warp * 8 + (lane & 7);                  // my token row of the tile
+#pragma unroll 2
+      for (int kp = 0; kp < 18; ++kp) {
+        uint32_t kf[4];
+        {
+          const int c = 4 * kp + mat;                         // chunks 4kp .. 4kp+3 = two k-steps
+          mla_ldm(kf, kt + kr * kMlaRowBytes + ((c ^ (kr & 7)) * 16));
+        }
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-        mine[ra * 16 + nt * 8 + c0] = s[nt][0];
-        mine[ra * 16 + nt * 8 + c0 + 1] = s[nt][1];
-        mine[(ra + 8) * 16 + nt * 8 + c0] = s[nt][2];
-        mine[(ra + 8) * 16 + nt * 8 + c0 + 1] = s[nt][3];
+        for (int half = 0; half < 2; ++half) {
+          const int ks = 2 * kp + half;
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            uint32_t qf[4];
+            const int r = mt * 16 + (mat & 1) * 8 + (lane & 7), c = 2 * ks + (mat >> 1);
+            mla_ldm(qf, q_smem + r * kMlaRowBytes + ((c ^ (r & 7)) * 16));
+            mla_mma<T>(sc[mt], qf, kf[2 * half], kf[2 * half + 1]);
+          }
+        }
+      }
+    }
+    // ---- mask, row maxima of my 8 tokens -> shared memory
+    const int ra = lane >> 2, c0 = 2 * (lane & 3);
+    const bool ok0 = s_pos[slot * kMlaTok + warp * 8 + c0] >= 0, ok1 = s_pos[slot * kMlaTok + warp * 8 + c0 + 1] >= 0;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      sc[mt][0] = ok0 ? sc[mt][0] * sl2 : -INFINITY;
+      sc[mt][1] = ok1 ? sc[mt][1] * sl2 : -INFINITY;
+      sc[mt][2] = ok0 ? sc[mt][2] * sl2 : -INFINITY;
+      sc[mt][3] = ok1 ? sc[mt][3] * sl2 : -INFINITY;
+      float ma = fmaxf(sc[mt][0], sc[mt][1]), mb = fmaxf(sc[mt][2], sc[mt][3]);
+      ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, 1));
+      ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, 2));
+      mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 1));
+      mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 2));
+      if ((lane & 3) == 0) {
+        s_max[warp * 16 * MT + mt * 16 + ra] = ma;
+        s_max[warp * 16 * MT + mt * 16 + ra + 8] = mb;
       }
     }
     __syncthreads();
-    {
-      const int ra = lane >> 2, c0 = 2 * (lane & 3);
+    // ---- online softmax with the tile-wide maximum; P (16-bit) -> shared memory
+    float corr[MT][2];
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
-        for (int w = 0; w < kMlaWarps; ++w) {
-          const float* pw = s_part + w * 256;
-          a0 += pw[ra * 16 + nt * 8 + c0];
-          a1 += pw[ra * 16 + nt * 8 + c0 + 1];
-          a2 += pw[(ra + 8) * 16 + nt * 8 + c0];
-          a3 += pw[(ra + 8) * 16 + nt * 8 + c0 + 1];
-        }
-        s[nt][0] = a0; s[nt][1] = a1; s[nt][2] = a2; s[nt][3] = a3;
+      for (int h = 0; h < 2; ++h) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) mx = fmaxf(mx, s_max[w * 16 * MT + mt * 16 + ra + 8 * h]);
+        const float mnew = fmaxf(m_run[mt][h], mx);
+        const float msafe = (mnew == -INFINITY) ? 0.f : mnew;
+        corr[mt][h] = exp2f(m_run[mt][h] - msafe);
+        m_run[mt][h] = mnew;
+        const float p0 = exp2f(sc[mt][2 * h] - msafe), p1 = exp2f(sc[mt][2 * h + 1] - msafe);
+        l_run[mt][h] = l_run[mt][h] * corr[mt][h] + p0 + p1;   // this thread's tokens only; summed at the end
+        const int r = mt * 16 + ra + 8 * h;
+        // row r, tokens 8 warp + c0, c0 + 1: 16-byte chunk `warp` of the row, swizzled
+        *reinterpret_cast<uint32_t*>(p_smem + r * (kMlaTok * 2) + ((warp ^ (r & 7)) * 16) + c0 * 2) = mla_pack2<T>(p0, p1);
       }
     }
-    // ---- mask + online softmax (identical in all four warps)
-    float mx[2] = {-INFINITY, -INFINITY};
+    __syncthreads();
+    // ---- O[:, 64 warp .. 64 warp + 64) = O * corr + P . V  (4 k-steps of 16 tokens)
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int col = nt * 8 + 2 * (lane & 3) + (e & 1);
-        float v = s[nt][e] * sl2;
-        if (pos_of(tile * kMlaTile + col) < 0) v = -INFINITY;
-        s[nt][e] = v;
-        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      for (int nd = 0; nd < 8; ++nd) {
+        o[mt][nd][0] *= corr[mt][0]; o[mt][nd][1] *= corr[mt][0];
+        o[mt][nd][2] *= corr[mt][1]; o[mt][nd][3] *= corr[mt][1];
       }
-    float corr[2], msafe[2];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-      const float mnew = fmaxf(m_run[h], mx[h]);
-      msafe[h] = (mnew == -INFINITY) ? 0.f : mnew;
-      corr[h] = exp2f(m_run[h] - msafe[h]);
-      m_run[h] = mnew;
-    }
-    float rs[2] = {0.f, 0.f};
-    uint32_t pf[4];
-    {
-      float pv[2][4];
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          pv[nt][e] = exp2f(s[nt][e] - msafe[e >> 1]);
-          rs[e >> 1] += pv[nt][e];
-        }
-      pf[0] = mla_pack2<T>(pv[0][0], pv[0][1]);
-      pf[1] = mla_pack2<T>(pv[0][2], pv[0][3]);
-      pf[2] = mla_pack2<T>(pv[1][0], pv[1][1]);
-      pf[3] = mla_pack2<T>(pv[1][2], pv[1][3]);
-    }
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 1);
-      rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 2);
-      l_run[h] = l_run[h] * corr[h] + rs[h];
-    }
-    // ---- O[:, 128w .. 128w+128) = O * corr + P . V
-#pragma unroll
-    for (int nd = 0; nd < 16; nd += 2) {
-      o[nd][0] *= corr[0]; o[nd][1] *= corr[0]; o[nd][2] *= corr[1]; o[nd][3] *= corr[1];
-      o[nd + 1][0] *= corr[0]; o[nd + 1][1] *= corr[0]; o[nd + 1][2] *= corr[1]; o[nd + 1][3] *= corr[1];
-      uint32_t vf[4];
+    for (int kk = 0; kk < 4; ++kk) {
+      uint32_t pf[MT][4];
       const int mat = lane >> 3;
-      const int r = (mat & 1) * 8 + (lane & 7);
-      const int c = warp * 16 + nd + (mat >> 1);
-      mla_ldm_t(vf, kt + r * kMlaRowBytes + ((c ^ (r & 7)) * 16));
-      mla_mma<T>(o[nd], pf, vf[0], vf[1]);
-      mla_mma<T>(o[nd + 1], pf, vf[2], vf[3]);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        const int r = mt * 16 + (mat & 1) * 8 + (lane & 7), c = 2 * kk + (mat >> 1);
+        mla_ldm(pf[mt], p_smem + r * (kMlaTok * 2) + ((c ^ (r & 7)) * 16));
+      }
+#pragma unroll
+      for (int nd = 0; nd < 8; nd += 2) {
+        uint32_t vf[4];
+        const int r = kk * 16 + (mat & 1) * 8 + (lane & 7);
+        const int c = warp * 8 + nd + (mat >> 1);
+        mla_ldm_t(vf, kt + r * kMlaRowBytes + ((c ^ (r & 7)) * 16));
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          mla_mma<T>(o[mt][nd], pf[mt], vf[0], vf[1]);
+          mla_mma<T>(o[mt][nd + 1], pf[mt], vf[2], vf[3]);
+        }
+      }
     }
-    __syncthreads();   // everyone is done with this ring slot and with s_part
-    stage = (stage + 1) % kMlaStages;
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 
-  // ---- write out (normalised) or the split partials
+  // ---- row sums over the 8 warps (quad first), then the normalised output or the split partials
+  __syncthreads();
   const int ra = lane >> 2;
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int r = ra + half * 8;
-    const int h = h0 + r;
-    if (h >= p.num_heads) continue;
-    const float L = l_run[half];
-    const float Ms = (m_run[half] == -INFINITY) ? 0.f : m_run[half];
-    const float inv = L > 0.f ? 1.f / L : 0.f;
-    const float lse = L > 0.f ? Ms * 0.6931471805599453f + logf(L) : -INFINITY;
-    if (p.num_splits == 1) {
-      T* dst = reinterpret_cast<T*>(p.out) + ((int64_t)t * p.num_heads + h) * kMlaDV + warp * 128;
+  for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-      for (int nd = 0; nd < 16; ++nd) {
-        const int col = nd * 8 + 2 * (lane & 3);
-        *reinterpret_cast<uint32_t*>(dst + col) = mla_pack2<T>(o[nd][half * 2] * inv, o[nd][half * 2 + 1] * inv);
-      }
-      if (warp == 0 && (lane & 3) == 0 && p.lse_out) p.lse_out[(int64_t)h * p.total_tokens + t] = lse;
-    } else {
-      const int64_t prow = ((int64_t)split * p.total_tokens + t) * p.num_heads + h;
-      float* dst = p.part_out + prow * kMlaDV + warp * 128;
-#pragma unroll
-      for (int nd = 0; nd < 16; ++nd) {
-        const int col = nd * 8 + 2 * (lane & 3);
-        dst[col] = o[nd][half * 2] * inv;
-        dst[col + 1] = o[nd][half * 2 + 1] * inv;
-      }
-      if (warp == 0 && (lane & 3) == 0) p.part_lse[prow] = lse;
+    for (int h = 0; h < 2; ++h) {
+      float l = l_run[mt][h];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      if ((lane & 3) == 0) s_max[warp * 16 * MT + mt * 16 + ra + 8 * h] = l;
     }
-  }
+  __syncthreads();
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = mt * 16 + ra + half * 8;
+      const int h = h0 + r;
+      if (h >= p.num_heads) continue;
+      float L = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) L += s_max[w * 16 * MT + r];
+      const float Ms = (m_run[mt][half] == -INFINITY) ? 0.f : m_run[mt][half];
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      const float lse = L > 0.f ? Ms * 0.6931471805599453f + logf(L) : -INFINITY;
+      if (p.num_splits == 1) {
+        T* dst = reinterpret_cast<T*>(p.out) + ((int64_t)t * p.num_heads + h) * kMlaDV + warp * 64;
+#pragma unroll
+        for (int nd = 0; nd < 8; ++nd) {
+          const int col = nd * 8 + 2 * (lane & 3);
+          *reinterpret_cast<uint32_t*>(dst + col) =
+              mla_pack2<T>(o[mt][nd][half * 2] * inv, o[mt][nd][half * 2 + 1] * inv);
+        }
+        if (warp == 0 && (lane & 3) == 0 && p.lse_out) p.lse_out[(int64_t)h * p.total_tokens + t] = lse;
+      } else {
+        const int64_t prow = ((int64_t)split * p.total_tokens + t) * p.num_heads + h;
+        float* dst = p.part_out + prow * kMlaDV + warp * 64;
+#pragma unroll
+        for (int nd = 0; nd < 8; ++nd) {
+          const int col = nd * 8 + 2 * (lane & 3);
+          dst[col] = o[mt][nd][half * 2] * inv;
+          dst[col + 1] = o[mt][nd][half * 2 + 1] * inv;
+        }
+        if (warp == 0 && (lane & 3) == 0) p.part_lse[prow] = lse;
+      }
+    }
 }
 
 template <typename T>
@@ -366,13 +393,33 @@ __global__ void mla_split_reduce_kernel(T* __restrict__ out, float* __restrict__
     lse_out[(row % heads) * (int64_t)total_tokens + row / heads] = L > 0.f ? Ms + logf(L) : -INFINITY;
 }
 
+template <typename T, bool FP8, int MT>
+static void launch_mla_mt(const MlaDecodeParams& p, cudaStream_t stream) {
+  using S = MlaSmem2<MT, FP8>;
+  static_assert(S::kTotal <= 232448, "shared memory budget exceeded");
+  auto kern = mla_decode_kernel<T, FP8, MT>;
+  // a per-device attribute of the kernel: set on every launch (cheap) rather than once per process
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+  dim3 grid((p.num_heads + 16 * MT - 1) / (16 * MT), p.total_tokens, p.num_splits);
+  kern<<<grid, kMlaThreads, S::kTotal, stream>>>(p);
+}
+
+// Heads per CTA: the latent rows are re-read once per 16 MT heads, so as many heads as shared memory allows.
+int mla_decode_heads_per_cta(int num_heads, int fp8_records) {
+  if (num_heads <= 16) return 16;
+  if (num_heads <= 32 || fp8_records) return 32;
+  return 64;
+}
+
 template <typename T, bool FP8>
 static void launch_mla(const MlaDecodeParams& p, cudaStream_t stream) {
-  auto kern = mla_decode_kernel<T, FP8>;
-  // a per-device attribute of the kernel: set on every launch (cheap) rather than once per process
-  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, MlaSmem::kTotal);
-  dim3 grid((p.num_heads + 15) / 16, p.total_tokens, p.num_splits);
-  kern<<<grid, kMlaWarps * 32, MlaSmem::kTotal, stream>>>(p);
+  const int hpc = mla_decode_heads_per_cta(p.num_heads, FP8 ? 1 : 0);
+  if (hpc == 16) launch_mla_mt<T, FP8, 1>(p, stream);
+  else if (hpc == 32) launch_mla_mt<T, FP8, 2>(p, stream);
+  else {
+    if constexpr (FP8) launch_mla_mt<T, true, 2>(p, stream);
+    else launch_mla_mt<T, false, 4>(p, stream);
+  }
   if (p.num_splits > 1)
     mla_split_reduce_kernel<T><<<(unsigned)((int64_t)p.total_tokens * p.num_heads), 256, 0, stream>>>(
         (T*)p.out, p.lse_out, p.part_out, p.part_lse, p.num_splits, p.total_tokens, p.num_heads);
