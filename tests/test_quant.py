@@ -157,7 +157,7 @@ def test_scaled_mm_reference_matches_dequant_cpu():
 
 
 @gpu
-@pytest.mark.parametrize("M,N,K", [(3, 256, 128), (200, 1536, 1024), (1000, 4096, 4096), (129, 2112, 7168)])
+@pytest.mark.parametrize("M,N,K", [(3, 256, 128), (200, 1536, 1024), (1000, 4096, 4096), (129, 2112, 7168), (2048, 4352, 1024)])
 @pytest.mark.parametrize("kind", ["int8", "int8_azp", "fp8"])
 def test_scaled_mm_gpu(M, N, K, kind, kernel_status_ok):
     torch.manual_seed(1)

@@ -94,7 +94,9 @@ void gemm(Tensor& out, const Tensor& a, const Tensor& w, const optional<Tensor>&
     return e == nullptr || std::atoi(e) != 0;
   }();
   const int64_t pair_tiles = ((M + 255) / 256) * (int64_t)((N + 255) / 256);
-  if (force_bn == 512 || (force_bn == 0 && pair_default && M >= 512 && pair_tiles >= 64)) {
+  // (a full 256-token decode batch against a wide weight, e.g. gate_up, already gives every CTA pair a tile)
+  if (force_bn == 512 || (force_bn == 0 && pair_default && ((M >= 512 && pair_tiles >= 64) ||
+                                                             (M >= 256 && pair_tiles >= 96)))) {
     b200::gemm_tn_pair(a.data_ptr(), w.data_ptr(), out.data_ptr(), ptr(bias), ptr(residual), M, N, K, a.stride(0),
                        w.stride(0), out.stride(0), ldr, dtype16(a), cur_stream(), status_ptr(a), (int)epi);
     return;
