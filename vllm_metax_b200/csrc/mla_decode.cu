@@ -78,7 +78,7 @@ struct MlaSmem2 {
   static constexpr int kPBytes = 16 * MT * kMlaTok * 2;
   static constexpr int kMax = kP + kPBytes;                           // [8 warps][16 MT] row maxima, later row sums
   static constexpr int kMaxBytes = 8 * 16 * MT * 4;
-  static constexpr int kPos = kMax + kMaxBytes;                       // [2][64] cache position of every tile row
+  static constexpr int kPos = kMax + kMaxBytes;                       // [2][64] cache row of every tile row, -1 = masked
   static constexpr int kTotal = kPos + 2 * kMlaTok * 4 + 16;
 };
 
@@ -146,9 +146,19 @@ mla_decode_kernel(const MlaDecodeParams p) {
     if (idx_row) v = idx_row[e];
     return (v >= 0 && v < lim && v < kv_cap) ? v : -1;
   };
-  // positions of tile `tile` into s_pos[slot] (threads 0..63), then - after a barrier - issue_rows copies them
+  // cache rows (page * block_size + offset, or -1) of the entries of tile `tile` into s_pos[slot] (threads 0..63:
+  // one page-table lookup per row); after a barrier issue_rows copies the rows 16 bytes at a time
   auto stage_positions = [&](int tile, int slot) {
-    if (threadIdx.x < kMlaTok) s_pos[slot * kMlaTok + threadIdx.x] = tile < tile_end ? pos_of(tile * kMlaTok + threadIdx.x) : -1;
+    if (threadIdx.x < kMlaTok) {
+      const int pos = tile < tile_end ? pos_of(tile * kMlaTok + threadIdx.x) : -1;
+      int row = -1;
+      if (pos >= 0) {
+        const int page = btab[pos / p.block_size];
+        if (page < 0 || page >= p.num_blocks) report_status(p.status, kBadIndex, 95, (int)p.num_blocks, page);
+        else row = page * p.block_size + pos % p.block_size;
+      }
+      s_pos[slot * kMlaTok + threadIdx.x] = row;
+    }
   };
   auto issue_rows = [&](int tile, int slot) {
     if (tile >= tile_end) return;
@@ -158,15 +168,9 @@ mla_decode_kernel(const MlaDecodeParams p) {
     uint8_t* dst = smem + S::kRing + slot * (FP8 ? S::kRawStage : kMlaTileB);
     for (int i = threadIdx.x; i < kMlaTok * CH; i += blockDim.x) {
       const int r = i / CH, c = i % CH;
-      const int pos = s_pos[slot * kMlaTok + r];
-      const uint8_t* src = cache;
-      if (pos >= 0) {
-        int page = btab[pos / p.block_size];
-        if (page < 0 || page >= p.num_blocks) { report_status(p.status, kBadIndex, 95, (int)p.num_blocks, page); page = 0; }
-        src = cache + ((int64_t)page * p.block_size + pos % p.block_size) * RB + c * 16;
-      }
+      const int row = s_pos[slot * kMlaTok + r];
       const int dc = FP8 ? c : (c ^ (r & 7));
-      mla_cp16(dst + r * RB + dc * 16, src, pos >= 0);
+      mla_cp16(dst + r * RB + dc * 16, cache + (row >= 0 ? (int64_t)row * RB + c * 16 : 0), row >= 0);
     }
   };
 
@@ -223,9 +227,13 @@ mla_decode_kernel(const MlaDecodeParams p) {
       kt = conv;
     }
     // ---- S[rows, my 8 tokens] over the whole contraction: 18 pairs of k-steps
-    float sc[MT][4];
+    // (two accumulator chains per row tile - even / odd k-steps - so consecutive MMAs do not wait on each other)
+    float sc[MT][4], sc2[MT][4];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) sc[mt][0] = sc[mt][1] = sc[mt][2] = sc[mt][3] = 0.f;
+    for (int mt = 0; mt < MT; ++mt) {
+      sc[mt][0] = sc[mt][1] = sc[mt][2] = sc[mt][3] = 0.f;
+      sc2[mt][0] = sc2[mt][1] = sc2[mt][2] = sc2[mt][3] = 0.f;
+    }
     {
       const int mat = lane >> 3;
       const int kr = warp * 8 + (lane & 7);                  // my token row of the tile
@@ -244,10 +252,15 @@ mla_decode_kernel(const MlaDecodeParams p) {
             uint32_t qf[4];
             const int r = mt * 16 + (mat & 1) * 8 + (lane & 7), c = 2 * ks + (mat >> 1);
             mla_ldm(qf, q_smem + r * kMlaRowBytes + ((c ^ (r & 7)) * 16));
-            mla_mma<T>(sc[mt], qf, kf[2 * half], kf[2 * half + 1]);
+            if (half == 0) mla_mma<T>(sc[mt], qf, kf[0], kf[1]);
+            else mla_mma<T>(sc2[mt], qf, kf[2], kf[3]);
           }
         }
       }
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc[mt][e] += sc2[mt][e];
     }
     // ---- mask, row maxima of my 8 tokens -> shared memory
     const int ra = lane >> 2, c0 = 2 * (lane & 3);
