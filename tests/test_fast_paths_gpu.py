@@ -154,3 +154,40 @@ def test_rope_and_cache_vector_path_llama_shape():
     torch.testing.assert_close(q, wq, rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(k, wk, rtol=2e-2, atol=2e-2)
     assert cos_diff(cache.float(), wcache.float()) < 1e-4
+
+
+# ------------------------------------------------------------------ expert alignment and greedy argmax at serving sizes
+@pytest.mark.parametrize("T,topk,E,block,mapped", [(8192, 8, 128, 128, False), (8192, 8, 128, 128, True),
+                                                   (256, 8, 256, 128, False), (3, 2, 8, 16, False),
+                                                   (1000, 6, 160, 64, True), (4100, 1, 512, 128, False)])
+def test_moe_align_matches_stable_sort(T, topk, E, block, mapped):
+    g = torch.Generator().manual_seed(T + E)
+    ids = torch.randint(0, E, (T, topk), generator=g, dtype=torch.int32)
+    emap, local = None, E
+    if mapped:
+        local = E // 4
+        emap = torch.full((E,), -1, dtype=torch.int32)
+        emap[local: 2 * local] = torch.arange(local, dtype=torch.int32)
+    want = ops.moe_align_block_size(ids, block, local, emap, want_inverse=True)
+    got = ops.moe_align_block_size(ids.to(DEV), block, local, None if emap is None else emap.to(DEV), want_inverse=True)
+    total = int(want[2])
+    assert int(got[2]) == total
+    assert torch.equal(got[0][:total].cpu(), want[0][:total])
+    assert torch.equal(got[1][: total // block].cpu(), want[1][: total // block])
+    assert torch.equal(got[3].cpu(), want[3])
+
+
+@pytest.mark.parametrize("rows,vocab", [(1, 151936), (8, 151936), (37, 128256), (256, 128256), (300, 32000), (5, 1000)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_argmax_split_rows(rows, vocab, dtype):
+    logits = torch.randn(rows, vocab, device=DEV, dtype=dtype)
+    hot = torch.randint(0, vocab, (rows,), device=DEV)
+    logits[torch.arange(rows, device=DEV), hot] = 50.0
+    assert torch.equal(ops.argmax(logits), hot)
+    assert torch.equal(ops.argmax(logits), hot)          # the row tickets were reset
+    # ties go to the lowest index; rows that start off a 16-byte boundary take the scalar path
+    wide = torch.zeros(rows, vocab + 3, device=DEV, dtype=dtype)
+    view = wide[:, 3:]
+    view[:, vocab // 2] = 1.0
+    view[:, vocab - 1] = 1.0
+    assert torch.equal(ops.argmax(view), torch.full((rows,), vocab // 2, device=DEV))

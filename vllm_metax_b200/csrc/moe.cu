@@ -185,68 +185,101 @@ __global__ void grouped_topk_kernel(float* __restrict__ weights, int* __restrict
 }
 
 // ---------------------------------------------------------------- align
-// Single CTA (1024 threads): histogram -> padded prefix -> stable placement.  numel = tokens * topk.
-// expert_map (optional): global expert id -> local id or -1 (pairs routed elsewhere are dropped).
-__global__ void __launch_bounds__(1024)
+// Single CTA (1024 threads = 32 warps): warp w owns the w-th contiguous segment of the (token, k) pairs.
+//   1. per-warp histograms in shared memory            hist[w][e]
+//   2. per expert: exclusive prefix over the warps, then the padded expert starts
+//   3. each warp walks its segment 32 pairs at a time; lanes that hold the same expert find each other with
+//      match.any, so the placement is stable (pair order is kept inside an expert) and every pair is read twice.
+// numel = tokens * topk.  expert_map (optional): global expert id -> local id or -1 (pairs routed elsewhere are
+// dropped and get inv_pos = -1).
+constexpr int kAlignWarps = 32;
+
+__device__ __forceinline__ int align_expert_of(const int* __restrict__ topk_ids, const int* __restrict__ expert_map,
+                                               int i, int numel, int experts) {
+  if (i >= numel) return -1;
+  int e = topk_ids[i];
+  if (expert_map) e = (e >= 0) ? expert_map[e] : -1;
+  return (e >= 0 && e < experts) ? e : -1;
+}
+
+__global__ void __launch_bounds__(kAlignWarps * 32)
 moe_align_kernel(int* __restrict__ sorted_ids, int* __restrict__ block_expert, int* __restrict__ total_padded,
                  int* __restrict__ inv_pos, const int* __restrict__ topk_ids, const int* __restrict__ expert_map,
                  int numel, int experts, int block, int max_padded) {
   extern __shared__ int sm[];
-  int* counts = sm;                 // [experts]
-  int* starts = sm + experts;       // [experts + 1] padded starts
-  int* cursor = starts + experts + 1;
-  for (int e = threadIdx.x; e < experts; e += blockDim.x) { counts[e] = 0; cursor[e] = 0; }
-  __syncthreads();
-  for (int i = threadIdx.x; i < numel; i += blockDim.x) {
-    int e = topk_ids[i];
-    if (expert_map) e = (e >= 0) ? expert_map[e] : -1;
-    if (e >= 0 && e < experts) atomicAdd(&counts[e], 1);
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int acc = 0;
-    for (int e = 0; e < experts; ++e) {
-      starts[e] = acc;
-      acc += (counts[e] + block - 1) / block * block;
-    }
-    starts[experts] = acc;
-    *total_padded = acc;
-  }
-  __syncthreads();
-  const int total = starts[experts];
-  for (int i = threadIdx.x; i < max_padded; i += blockDim.x) sorted_ids[i] = numel;   // padding marker
+  int* hist = sm;                                   // [kAlignWarps][experts] counts, then write cursors
+  int* starts = sm + kAlignWarps * experts;         // [experts + 1] padded starts
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seg = ((numel + kAlignWarps - 1) / kAlignWarps + 127) / 128 * 128;   // pairs per warp, 4 x 32 per trip
+  const int lo = warp * seg, hi = min(numel, lo + seg);
+  for (int i = threadIdx.x; i < kAlignWarps * experts; i += blockDim.x) hist[i] = 0;
+  // padding marker everywhere first; real pairs overwrite it in step 3
+  for (int i = threadIdx.x; i < max_padded; i += blockDim.x) sorted_ids[i] = numel;
   for (int b = threadIdx.x; b < max_padded / block; b += blockDim.x) block_expert[b] = -1;
   __syncthreads();
-  for (int e = threadIdx.x; e < experts; e += blockDim.x)
-    for (int b = starts[e] / block; b < starts[e + 1] / block; ++b) block_expert[b] = e;
-  // stable placement: one warp per expert scans the pairs in order (ballot-based compaction)
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  for (int e = warp; e < experts; e += nw) {
-    int base = starts[e];
-    for (int i0 = 0; i0 < numel; i0 += 32) {
-      const int i = i0 + lane;
-      int ee = -1;
-      if (i < numel) {
-        ee = topk_ids[i];
-        if (expert_map) ee = (ee >= 0) ? expert_map[ee] : -1;
+  int* mine = hist + warp * experts;
+  for (int i0 = lo; i0 < hi; i0 += 128) {
+    int e[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) e[j] = align_expert_of(topk_ids, expert_map, i0 + j * 32 + lane, hi, experts);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (e[j] >= 0) atomicAdd(&mine[e[j]], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {      // exclusive prefix over the warps, per expert
+    int acc = 0;
+    for (int w = 0; w < kAlignWarps; ++w) {
+      const int c = hist[w * experts + e];
+      hist[w * experts + e] = acc;
+      acc += c;
+    }
+    starts[e + 1] = (acc + block - 1) / block * block;           // padded count for now
+  }
+  __syncthreads();
+  if (warp == 0) {                                               // inclusive scan of the padded counts
+    int carry = 0;
+    for (int e0 = 0; e0 < experts; e0 += 32) {
+      const int e = e0 + lane;
+      int v = (e < experts) ? starts[e + 1] : 0;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, v, d);
+        if (lane >= d) v += o;
       }
-      const unsigned m = __ballot_sync(0xffffffffu, ee == e);
-      if (ee == e) {
-        const int pos = base + __popc(m & ((1u << lane) - 1u));
+      if (e < experts) starts[e + 1] = carry + v;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+    if (lane == 0) { starts[0] = 0; *total_padded = carry; }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    for (int b = starts[e] / block; b < starts[e + 1] / block; ++b) block_expert[b] = e;
+    const int s0 = starts[e];
+    for (int w = 0; w < kAlignWarps; ++w) hist[w * experts + e] += s0;
+  }
+  __syncthreads();
+  for (int i0 = lo; i0 < hi; i0 += 128) {
+    int e[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) e[j] = align_expert_of(topk_ids, expert_map, i0 + j * 32 + lane, hi, experts);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = i0 + j * 32 + lane;
+      const unsigned peers = __match_any_sync(0xffffffffu, e[j]);
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      if (e[j] >= 0) {
+        const int pos = mine[e[j]] + rank;
         sorted_ids[pos] = i;
         if (inv_pos) inv_pos[i] = pos;
+      } else if (inv_pos && i < hi) {
+        inv_pos[i] = -1;
       }
-      base += __popc(m);
+      __syncwarp();
+      if (e[j] >= 0 && rank == 0) mine[e[j]] += __popc(peers);
+      __syncwarp();
     }
   }
-  if (inv_pos) {
-    for (int i = threadIdx.x; i < numel; i += blockDim.x) {
-      int e = topk_ids[i];
-      if (expert_map) e = (e >= 0) ? expert_map[e] : -1;
-      if (e < 0 || e >= experts) inv_pos[i] = -1;
-    }
-  }
-  (void)total;
 }
 
 template <typename T>
@@ -325,8 +358,9 @@ void grouped_topk(float* weights, int* ids, const void* gating, const float* bia
 
 void moe_align(int* sorted_ids, int* block_expert, int* total_padded, int* inv_pos, const int* topk_ids,
                const int* expert_map, int numel, int experts, int block, int max_padded, cudaStream_t stream) {
-  const size_t sm = (size_t)(3 * experts + 1) * sizeof(int);
-  moe_align_kernel<<<1, 1024, sm, stream>>>(sorted_ids, block_expert, total_padded, inv_pos, topk_ids, expert_map,
+  const size_t sm = (size_t)(kAlignWarps * experts + experts + 1) * sizeof(int);
+  if (sm > 48 * 1024) cudaFuncSetAttribute(moe_align_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+  moe_align_kernel<<<1, kAlignWarps * 32, sm, stream>>>(sorted_ids, block_expert, total_padded, inv_pos, topk_ids, expert_map,
                                             numel, experts, block, max_padded);
 }
 

@@ -14,37 +14,90 @@
 
 namespace b200 {
 
+// Greedy token: each row is cut into `splits` slices, one CTA per (row, slice), read as 16-byte vectors where the row
+// allows it.  With one slice the CTA writes the token; otherwise it leaves (value, index) in device scratch and the
+// last slice of the row to arrive (a ticket per row, reset by that CTA) picks the winner - ties go to the lower index
+// at every level, so the answer does not depend on the split.  The scratch is per device and shared by all launches:
+// argmax calls on one device must be stream-ordered.
+constexpr int kArgmaxMaxSplits = 16;
+constexpr int kArgmaxScratchRows = 4096;
+static __device__ float g_argmax_val[kArgmaxScratchRows * kArgmaxMaxSplits];
+static __device__ int g_argmax_idx[kArgmaxScratchRows * kArgmaxMaxSplits];
+static __device__ unsigned g_argmax_ticket[kArgmaxScratchRows];
+
+__device__ __forceinline__ void argmax_take(float& best, int& bi, float v, int i) {
+  if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+}
+
 template <typename T>
-__global__ void argmax_kernel(int64_t* __restrict__ out, const T* __restrict__ logits, int vocab, int64_t stride) {
+__global__ void __launch_bounds__(512)
+argmax_kernel(int64_t* __restrict__ out, const T* __restrict__ logits, int vocab, int64_t stride, int splits) {
   __shared__ float sv[32];
   __shared__ int si[32];
-  const T* row = logits + (int64_t)blockIdx.x * stride;
+  __shared__ bool s_last;
+  const int r = blockIdx.x, sp = blockIdx.y;
+  const T* row = logits + (int64_t)r * stride;
+  constexpr int V = 16 / sizeof(T);
+  const int per = ((vocab + splits - 1) / splits + V - 1) / V * V;
+  const int lo = sp * per, hi = min(vocab, lo + per);
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = to_f(row[i]);
-    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    const int nvec = (hi - lo) / V;
+    const uint4* rv = reinterpret_cast<const uint4*>(row + lo);
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      const uint4 u = rv[v];
+      const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+      for (int j = 0; j < V; ++j) argmax_take(best, bi, to_f(e[j]), lo + v * V + j);
+    }
+    for (int i = lo + nvec * V + threadIdx.x; i < hi; i += blockDim.x) argmax_take(best, bi, to_f(row[i]), i);
+  } else {
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) argmax_take(best, bi, to_f(row[i]), i);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, o);
     const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    argmax_take(best, bi, ov, oi);
   }
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   if (lane == 0) { sv[w] = best; si[w] = bi; }
   __syncthreads();
-  if (w == 0) {
-    const int nw = blockDim.x >> 5;
-    best = lane < nw ? sv[lane] : -INFINITY;
-    bi = lane < nw ? si[lane] : 0x7fffffff;
+  if (w != 0) return;
+  const int nw = blockDim.x >> 5;
+  best = lane < nw ? sv[lane] : -INFINITY;
+  bi = lane < nw ? si[lane] : 0x7fffffff;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-    }
-    if (lane == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    argmax_take(best, bi, ov, oi);
+  }
+  if (splits == 1) {
+    if (lane == 0) out[r] = (bi == 0x7fffffff) ? 0 : bi;
+    return;
+  }
+  if (lane == 0) {
+    g_argmax_val[r * kArgmaxMaxSplits + sp] = best;
+    g_argmax_idx[r * kArgmaxMaxSplits + sp] = bi;
+    __threadfence();
+    s_last = atomicAdd(&g_argmax_ticket[r], 1u) == (unsigned)(splits - 1);
+  }
+  __syncwarp();
+  if (!s_last) return;
+  __threadfence();
+  best = lane < splits ? __ldcg(&g_argmax_val[r * kArgmaxMaxSplits + lane]) : -INFINITY;
+  bi = lane < splits ? __ldcg(&g_argmax_idx[r * kArgmaxMaxSplits + lane]) : 0x7fffffff;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    argmax_take(best, bi, ov, oi);
+  }
+  if (lane == 0) {
+    out[r] = (bi == 0x7fffffff) ? 0 : bi;
+    g_argmax_ticket[r] = 0;
   }
 }
 
@@ -230,9 +283,16 @@ __global__ void embedding_kernel(T* __restrict__ out, const T* __restrict__ tabl
 
 void argmax(int64_t* out, const void* logits, int rows, int vocab, int64_t stride, int dtype, cudaStream_t stream) {
   if (rows <= 0) return;
-  if (dtype == 0) argmax_kernel<__nv_bfloat16><<<rows, 1024, 0, stream>>>(out, (const __nv_bfloat16*)logits, vocab, stride);
-  else if (dtype == 1) argmax_kernel<__half><<<rows, 1024, 0, stream>>>(out, (const __half*)logits, vocab, stride);
-  else argmax_kernel<float><<<rows, 1024, 0, stream>>>(out, (const float*)logits, vocab, stride);
+  int splits = 1;
+  if (rows <= kArgmaxScratchRows && rows < 296) {
+    splits = (592 + rows - 1) / rows;
+    if (splits > kArgmaxMaxSplits) splits = kArgmaxMaxSplits;
+    while (splits > 1 && vocab / splits < 4096) --splits;
+  }
+  const dim3 grid(rows, splits);
+  if (dtype == 0) argmax_kernel<__nv_bfloat16><<<grid, 512, 0, stream>>>(out, (const __nv_bfloat16*)logits, vocab, stride, splits);
+  else if (dtype == 1) argmax_kernel<__half><<<grid, 512, 0, stream>>>(out, (const __half*)logits, vocab, stride, splits);
+  else argmax_kernel<float><<<grid, 512, 0, stream>>>(out, (const float*)logits, vocab, stride, splits);
 }
 
 void sample(int64_t* out, const void* logits, int rows, int vocab, int64_t stride, const float* temperature,
