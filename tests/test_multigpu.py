@@ -420,7 +420,20 @@ def test_pp2_engine_matches_single_gpu():
     _launch(_pp_engine_worker, 2, want, timeout=240)
 
 
-def _dcp_engine_worker(rank, world, dcp, path):
+def _dcp_mla_cfg(sparse):
+    from vllm_metax_b200 import ModelConfig
+
+    kw = dict(architecture="DeepseekV32ForCausalLM", index_n_heads=16, index_head_dim=128, index_topk=64) if sparse \
+        else dict(architecture="DeepseekV3ForCausalLM")
+    return ModelConfig(vocab_size=2048, hidden_size=1024, intermediate_size=2048, num_hidden_layers=3,
+                       num_attention_heads=32, q_lora_rank=256, kv_lora_rank=512, qk_nope_head_dim=128,
+                       qk_rope_head_dim=64, v_head_dim=128, num_experts=8, num_experts_per_tok=2,
+                       moe_intermediate_size=256, n_shared_experts=1, first_k_dense_replace=1, scoring_func="sigmoid",
+                       n_group=4, topk_group=2, topk_method="noaux_tc", routed_scaling_factor=2.5, norm_topk_prob=True,
+                       max_position_embeddings=1024, dtype=torch.bfloat16, seed=0, **kw)
+
+
+def _dcp_engine_worker(rank, world, dcp, path, model="llama"):
     """TP2 with one KV head (replicated on both ranks): with dcp = 1 the tokens are written to ``path``; with dcp = 2
     (same sharded weights, the cache split by position) they are compared with that file."""
     os.environ["B200_FUSED_TP_COLLECTIVES"] = "0"
@@ -430,7 +443,8 @@ def _dcp_engine_worker(rank, world, dcp, path):
     from vllm_metax_b200 import _custom_ops as ops
     from vllm_metax_b200.parallel import state as ps
 
-    llm = LLM(_pp_dcp_cfg(1), device="cuda", tensor_parallel_size=world, decode_context_parallel_size=dcp, block_size=64,
+    cfg = _pp_dcp_cfg(1) if model == "llama" else _dcp_mla_cfg(model == "mla_sparse")
+    llm = LLM(cfg, device="cuda", tensor_parallel_size=world, decode_context_parallel_size=dcp, block_size=64,
               max_model_len=512, max_num_seqs=8, max_num_batched_tokens=128, num_gpu_blocks=64)
     assert llm.engine.runner.dcp == dcp
     outs = llm.generate(_pp_dcp_prompts(), SamplingParams(max_tokens=12, ignore_eos=True))
@@ -454,7 +468,10 @@ def _dcp_engine_worker(rank, world, dcp, path):
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-def test_dcp2_engine_close_to_unsplit_cache(tmp_path):
+@pytest.mark.parametrize("model", ["llama", "mla", "mla_sparse"])
+def test_dcp2_engine_close_to_unsplit_cache(tmp_path, model):
+    """GQA with a replicated KV head, MLA (latent cache interleaved over the ranks) and MLA with the sparse indexer
+    (local top-k, merged over the group)."""
     path = str(tmp_path / "tp2_tokens.json")
-    _launch(_dcp_engine_worker, 2, 1, path, timeout=240)
-    _launch(_dcp_engine_worker, 2, 2, path, timeout=240)
+    _launch(_dcp_engine_worker, 2, 1, path, model, timeout=240)
+    _launch(_dcp_engine_worker, 2, 2, path, model, timeout=240)

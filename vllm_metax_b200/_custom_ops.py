@@ -909,4 +909,5 @@ def indexer_topk(q_fp8, weights, idx_cache, block_table, seq_lens, query_start_l
         torch.ops.b200.topk_per_row(out, logits, None, Lp)
         return (out, logits) if return_logits else out
     return ref.sparse_attn_indexer(q_fp8.float(), weights, idx_cache, block_table, seq_lens, query_start_loc, topk,
-                                   int8=q_fp8.dtype == torch.int8, bf16=q_fp8.dtype == torch.bfloat16)
+                                   int8=q_fp8.dtype == torch.int8, bf16=q_fp8.dtype == torch.bfloat16,
+                                   return_logits=return_logits)

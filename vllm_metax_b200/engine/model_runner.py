@@ -71,11 +71,14 @@ class ModelRunner:
         self.virt_bs = self.block_size * self.dcp
         if self.dcp > 1:
             m = cfg.model
+            # GQA: the KV heads of a DCP group must be replicas of one another.  MLA: the latent cache is the same on
+            # every tensor-parallel rank, so any dcp that divides tp works.
             reps = ps.tp_size() // m.num_key_value_heads if m.num_key_value_heads < ps.tp_size() else 1
-            if m.is_mla or reps % self.dcp != 0:
+            if not m.is_mla and reps % self.dcp != 0:
                 raise ValueError("decode context parallelism needs a GQA model whose KV heads are replicated over at "
                                  f"least dcp tensor-parallel ranks (kv heads {m.num_key_value_heads}, tp {ps.tp_size()}, "
-                                 f"dcp {self.dcp})")
+                                 f"dcp {self.dcp}), or an MLA model")
+        self.dcp_per_token = self.dcp > 1 and cfg.model.is_mla
         self.max_blocks_per_seq = (sc.max_model_len + self.virt_bs - 1) // self.virt_bs
         self.kv_caches: list = []
         self.num_blocks = 0
@@ -310,6 +313,7 @@ class ModelRunner:
         bs = self.block_size
         d, dr, vbs = self.dcp, self.dcp_rank, self.virt_bs
         ctx_local = []
+        vis_local, tok_req = [], []
         t = 0
         qsl[0] = 0
         max_q = max_seq = 0
@@ -326,6 +330,9 @@ class ModelRunner:
                 blk = np.asarray(r.block_ids, dtype=np.int64)
                 slots[t:t + n] = np.where(ar % d == dr, blk[ar // vbs] * bs + (ar % vbs) // d, -1)
                 ctx_local.append(max(0, (p0 - dr + d - 1) // d))
+                if self.dcp_per_token:      # MLA: cache entries of this rank that token p may see, (p - dr + d) // d
+                    vis_local.append((ar - dr + d) // d)
+                    tok_req.append(np.full(n, i, dtype=np.int64))
             elif n == 1:
                 ids[t] = r.token_at(p0)
                 pos[t] = p0
@@ -389,6 +396,11 @@ class ModelRunner:
             ctx_local += [0] * (B_eff - len(ctx_local))
             md.extra["dcp_ctx_lens"] = torch.tensor(ctx_local, dtype=torch.int32).to(self.device, non_blocking=True)
             md.extra["dcp_any_context"] = any(s.start_pos > 0 for s in so.scheduled[nd:])
+            if self.dcp_per_token and vis_local and T > B_eff:      # steps with multi-token requests only
+                vis = np.concatenate(vis_local + [np.ones(T - sum(len(v) for v in vis_local), dtype=np.int64)])
+                req = np.concatenate(tok_req + [np.arange(B, B + T - sum(len(v) for v in tok_req), dtype=np.int64)])
+                md.extra["dcp_vis_lens"] = torch.from_numpy(vis.astype(np.int32)).to(self.device, non_blocking=True)
+                md.extra["dcp_token_req"] = torch.from_numpy(req).to(self.device, non_blocking=True)
         if self.state_slots is not None:
             self._state_metadata(so, md, B_eff)
         if getattr(self.model, "is_multimodal", False):

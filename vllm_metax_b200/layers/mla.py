@@ -79,6 +79,8 @@ class MLAAttention(nn.Module):
         cache = ctx.kv_caches[self.layer_idx]["mla"]
         T, H = q.shape[0], self.num_heads
         ops.concat_and_cache_mla(kv_c, k_pe, cache, md.slot_mapping)
+        if "dcp_ctx_lens" in md.extra:
+            return self._forward_dcp(q, kv_c, k_pe, kv_b_proj, topk_indices, md, cache)
         nd, ndt = md.num_decodes, md.num_decode_tokens
         pure_prefill = md.extra.get("prefill_no_context", False) and topk_indices is None and kv_b_proj is not None
         out = torch.empty(T, H, self.v_head, dtype=q.dtype, device=q.device)
@@ -92,6 +94,57 @@ class MLAAttention(nn.Module):
                                  max_seq_len=md.max_seq_len)
             out[:mqa_end] = torch.bmm(lat.transpose(0, 1), self.W_UV).transpose(0, 1)
         if pure_prefill and T > ndt:
+            kv = kv_b_proj(kv_c[ndt:]).view(T - ndt, H, self.qk_nope + self.v_head)
+            k = torch.cat([kv[..., : self.qk_nope], k_pe[ndt:, None, :].expand(-1, H, -1)], dim=-1).contiguous()
+            v = kv[..., self.qk_nope:].contiguous()
+            qsl = md.prefill_query_start_loc
+            ops.varlen_attention(q[ndt:].contiguous(), k, v, qsl, qsl, self.scale, out=out[ndt:],
+                                 max_q_len=md.max_prefill_query_len, causal=True)
+        return out.reshape(T, H * self.v_head)
+
+    def _forward_dcp(self, q, kv_c, k_pe, kv_b_proj, topk_indices, md, cache) -> torch.Tensor:
+        """Decode context parallel: the latent cache of a sequence is spread over the DCP group (position p on rank
+        p % dcp, the slot mapping is -1 elsewhere).  The absorbed queries of all the group's heads are gathered, every
+        rank attends its shard, and the partial outputs are combined by their log-sum-exp and scattered back over
+        heads (``parallel/dcp.py``).  A step with multi-token requests treats every token as a request of its own
+        whose length is the number of local entries it may see, which makes the causal mask exact on an interleaved
+        shard; ``topk_indices`` (global positions from the DCP indexer) are reduced to the local ones.
+        Mirrors vllm_metax/model_executor/layers/attention/mla_attention.py:858-899, 2142-2297."""
+        from ..parallel import dcp
+        from ..parallel import state as ps
+
+        g = ps.get_dcp_group()
+        d, r = g.world_size, g.rank_in_group
+        T, H = q.shape[0], self.num_heads
+        nd, ndt = md.num_decodes, md.num_decode_tokens
+        pure_prefill = md.extra.get("prefill_no_context", False) and topk_indices is None and kv_b_proj is not None
+        out = torch.empty(T, H, self.v_head, dtype=q.dtype, device=q.device)
+        mqa_end = ndt if pure_prefill else T
+        if mqa_end > 0:
+            if "dcp_vis_lens" in md.extra:
+                lens = md.extra["dcp_vis_lens"][:mqa_end]
+                table = md.block_table[md.extra["dcp_token_req"][:mqa_end]]
+            else:                                   # one token per request
+                lens, table = md.seq_lens[:mqa_end], md.block_table[:mqa_end]
+            local_idx = None
+            if topk_indices is not None:
+                ti = topk_indices[:mqa_end]
+                local_idx = torch.where((ti >= 0) & (ti % d == r), ti // d, torch.full_like(ti, -1)).contiguous()
+                empty = (local_idx >= 0).sum(1) == 0
+            else:
+                empty = lens == 0
+            qa = self._absorb_q(q[:mqa_end])
+
+            def attend(q_all):
+                lse = torch.empty(H * d, mqa_end, dtype=torch.float32, device=q.device)
+                o = ops.mla_decode(q_all, cache, table, lens.clamp_min(1), self.scale, topk_indices=local_idx,
+                                   lse_out=lse, max_seq_len=md.max_seq_len)
+                lse = torch.where(empty[None, :], torch.full_like(lse, float("-inf")), lse)
+                return torch.where(empty[:, None, None], torch.zeros_like(o), o), lse.t().contiguous()
+
+            lat = dcp.decode_attention(qa, attend, g)
+            out[:mqa_end] = torch.bmm(lat.transpose(0, 1), self.W_UV).transpose(0, 1)
+        if pure_prefill and T > ndt:               # fresh chunks see only their own keys: no communication
             kv = kv_b_proj(kv_c[ndt:]).view(T - ndt, H, self.qk_nope + self.v_head)
             k = torch.cat([kv[..., : self.qk_nope], k_pe[ndt:, None, :].expand(-1, H, -1)], dim=-1).contiguous()
             v = kv[..., self.qk_nope:].contiguous()
@@ -115,5 +168,35 @@ def sparse_attn_indexer(q_fp8: torch.Tensor, weights: torch.Tensor, k: torch.Ten
     """
     md = get_forward_context().attn_metadata
     ops.indexer_k_quant_and_cache(k, idx_cache, md.slot_mapping, block_size)
+    if "dcp_ctx_lens" in md.extra:
+        return _sparse_attn_indexer_dcp(q_fp8, weights, idx_cache, topk, block_size, md)
     return ops.indexer_topk(q_fp8, weights, idx_cache, md.block_table, md.seq_lens, md.query_start_loc, topk,
                             block_size, max_seq_len=md.max_seq_len)
+
+
+def _sparse_attn_indexer_dcp(q_fp8, weights, idx_cache, topk: int, block_size: int, md) -> torch.Tensor:
+    """Indexer under decode context parallelism: every rank scores the index keys of its shard (token = request, length
+    = visible local entries), keeps its top-k with their logits, and the group's candidates are merged into the global
+    top-k.  Returns GLOBAL positions.  Mirrors registry/custom_ops/layers/sparse_attn_indexer/fp8.py:241-249."""
+    from ..parallel import state as ps
+
+    g = ps.get_dcp_group()
+    d, r = g.world_size, g.rank_in_group
+    T = q_fp8.shape[0]
+    if "dcp_vis_lens" in md.extra:
+        lens = md.extra["dcp_vis_lens"][:T]
+        table = md.block_table[md.extra["dcp_token_req"][:T]]
+    else:
+        lens, table = md.seq_lens[:T], md.block_table[:T]
+    qsl = torch.arange(T + 1, dtype=torch.int32, device=q_fp8.device)
+    local_max = (md.max_seq_len + d - 1) // d
+    idx, logits = ops.indexer_topk(q_fp8, weights, idx_cache, table, lens.clamp_min(1), qsl, topk, block_size,
+                                   max_seq_len=local_max, return_logits=True)
+    ok = (idx >= 0) & (lens > 0)[:, None]
+    vals = torch.where(ok, logits.gather(1, idx.clamp_min(0).long()), torch.full_like(idx, float("-inf"), dtype=torch.float32))
+    pos = torch.where(ok, idx * d + r, torch.full_like(idx, -1))
+    all_vals = g.all_gather(vals.contiguous(), 1)                 # [T, d * topk]
+    all_pos = g.all_gather(pos.contiguous(), 1)
+    top = torch.topk(all_vals, topk, dim=1)
+    sel = all_pos.gather(1, top.indices)
+    return torch.where(torch.isfinite(top.values), sel, torch.full_like(sel, -1)).to(torch.int32).contiguous()

@@ -679,7 +679,7 @@ def top_k_per_row(logits, k: int):
 
 
 def sparse_attn_indexer(q_fp8, weights, idx_cache, block_table, seq_lens, query_start_loc, topk: int,
-                        int8: bool = False, bf16: bool = False):
+                        int8: bool = False, bf16: bool = False, return_logits: bool = False):
     """Full indexer: for every new token, top-k cache positions of its own request.
 
     ``q_fp8 [T,Hi,128]`` (already quantised values as float/fp8), ``weights [T,Hi]`` with the
@@ -689,6 +689,8 @@ def sparse_attn_indexer(q_fp8, weights, idx_cache, block_table, seq_lens, query_
     T = q_fp8.shape[0]
     out = torch.full((T, topk), -1, dtype=torch.int32, device=q_fp8.device)
     qsl, sl = query_start_loc.tolist(), seq_lens.tolist()
+    all_logits = (torch.full((T, max(sl + [1])), float("-inf"), dtype=torch.float32, device=q_fp8.device)
+                  if return_logits else None)
     for b in range(len(sl)):
         s0, s1 = qsl[b], qsl[b + 1]
         if s1 <= s0:
@@ -704,7 +706,9 @@ def sparse_attn_indexer(q_fp8, weights, idx_cache, block_table, seq_lens, query_
         ks = torch.zeros_like(ke)
         lg = mqa_logits(q_fp8[s0:s1], kq, sc, weights[s0:s1], ks, ke)
         out[s0:s1] = top_k_per_row(lg, topk)
-    return out
+        if all_logits is not None:
+            all_logits[s0:s1, : lg.shape[1]] = lg
+    return (out, all_logits) if return_logits else out
 
 
 # --------------------------------------------------------------------------- MoE routing
