@@ -127,6 +127,10 @@ def main() -> None:
     ap.add_argument("--in-len", type=int, default=0)
     ap.add_argument("--out-len", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="debug only; a reduced model is named as such in the output")
+    ap.add_argument("--pp", type=int, default=1,
+                    help="pipeline stages (the other gpus / pp ranks of a stage are tensor parallel); the value is then "
+                         "the end-to-end number through LLM.generate, device-timed, because the device-resident "
+                         "workload driver is tensor-parallel only")
     args = ap.parse_args()
     conf = CONFIGS[args.config]
     MODEL = conf["model"]
@@ -156,7 +160,9 @@ def main() -> None:
     assert world == args.gpus, f"launch with torchrun --nproc-per-node {args.gpus} (WORLD_SIZE={world})"
     model = dict(MODEL, num_hidden_layers=args.layers)
     N, P, O = args.num_reqs, args.in_len, args.out_len
-    llm = LLM(ModelConfig(**model, dtype=torch.bfloat16), tensor_parallel_size=args.gpus, block_size=BLOCK_SIZE,
+    assert args.gpus % args.pp == 0
+    llm = LLM(ModelConfig(**model, dtype=torch.bfloat16), tensor_parallel_size=args.gpus // args.pp,
+              pipeline_parallel_size=args.pp, block_size=BLOCK_SIZE,
               max_model_len=P + O + BLOCK_SIZE, max_num_seqs=N, max_num_batched_tokens=PREFILL_TOKENS,
               num_gpu_blocks=N * ((P + O + BLOCK_SIZE - 1) // BLOCK_SIZE) + 8, device="cuda", **conf["llm"])
     runner = llm.engine.runner
@@ -175,39 +181,43 @@ def main() -> None:
         return float(t.item())
 
     # ---------------------------------------------------------------- device-resident measurement
-    wl = StaticWorkload(runner, N, P, O, PREFILL_TOKENS)
-    wl.capture()
-    for _ in range(args.warmup):
-        wl.run()
-    barrier()
-    sampler = ClockSampler(dev.index or 0)
-    if rank == 0:
-        sampler.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches = 0
-    barrier()
-    ev0.record()
-    for _ in range(args.steps):
-        launches += wl.run()
-    ev1.record()
-    barrier()
-    dev_ms = max_over_ranks(ev0.elapsed_time(ev1))
-    clocks = sampler.stop() if rank == 0 else {}
-    ops.check_kernel_status(dev.index or 0)
-    phases = wl.phase_ms()
-    # outside the timed region: the fused NVLink path against the library collectives on the same ranks
-    tp_check = wl.collective_check() if world > 1 else None
     out_tokens = args.steps * N * O
-    value = out_tokens / (dev_ms / 1e3)
+    sampler = ClockSampler(dev.index or 0)
+    launches, phases, tp_check, dev_ms = 0, {}, None, 0.0
+    if args.pp == 1:
+        wl = StaticWorkload(runner, N, P, O, PREFILL_TOKENS)
+        wl.capture()
+        for _ in range(args.warmup):
+            wl.run()
+        barrier()
+        if rank == 0:
+            sampler.start()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        ev0.record()
+        for _ in range(args.steps):
+            launches += wl.run()
+        ev1.record()
+        barrier()
+        dev_ms = max_over_ranks(ev0.elapsed_time(ev1))
+        clocks = sampler.stop() if rank == 0 else {}
+        ops.check_kernel_status(dev.index or 0)
+        phases = wl.phase_ms()
+        # outside the timed region: the fused NVLink path against the library collectives on the same ranks
+        tp_check = wl.collective_check() if world > 1 else None
+        value = out_tokens / (dev_ms / 1e3)
 
     # ---------------------------------------------------------------- end to end through LLM.generate
     g = torch.Generator().manual_seed(1)
     prompts_host = torch.randint(0, model["vocab_size"], (N, P), generator=g).pin_memory()
     prompts = prompts_host.tolist()
     sp = SamplingParams(max_tokens=O, temperature=0.0, ignore_eos=True)
-    for _ in range(min(args.warmup, 1) or 1):
+    for _ in range((min(args.warmup, 1) or 1) if args.pp == 1 else args.warmup):
         llm.generate(prompts, sp)
     barrier()
+    if args.pp > 1 and rank == 0:
+        sampler.start()
+    l0 = ops.launch_count()
     runner.h2d_bytes = runner.d2h_bytes = 0
     ttfts, tpots = [], []
     t0 = time.perf_counter()
@@ -223,6 +233,10 @@ def main() -> None:
     e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3))
     e2e_value = out_tokens / (e2e_ms / 1e3)
     ops.check_kernel_status(dev.index or 0)
+    if args.pp > 1:          # no device-resident driver for pipeline stages: the end-to-end run is the measurement
+        clocks = sampler.stop() if rank == 0 else {}
+        dev_ms, value, launches = e2e_ms, e2e_value, ops.launch_count() - l0
+        phases = {"note": "timed through LLM.generate", "max_inflight": llm.engine.stats.get("max_inflight", 0)}
 
     if rank == 0:
         print(json.dumps({
@@ -235,7 +249,8 @@ def main() -> None:
                        "model": conf["label"] if args.layers == MODEL["num_hidden_layers"]
                        else f"{conf['label']}[{args.layers} layers, debug]",
                        "global_batch": N, "seq_len": P, "output_len": O,
-                       "parallelism": "+".join(f"{x}{args.gpus}" for x in conf["parallelism"].split("+")),
+                       "parallelism": "+".join(f"{x}{args.gpus // args.pp}" for x in conf["parallelism"].split("+"))
+                       + (f"+pp{args.pp}" if args.pp > 1 else ""),
                        "block_size": BLOCK_SIZE, "prefill_tokens_per_step": PREFILL_TOKENS,
                        "l2": "inputs larger than L2 (weights + KV cache streamed every iteration)",
                        "step": "one pass over the whole workload (prefill + decode of all requests)",

@@ -1,5 +1,7 @@
 """Pipeline parallel on CPU ranks (gloo): stage 0 sends [hidden | residual] to stage 1, the last stage samples and
-broadcasts the tokens; outputs must equal the single-process run of the same checkpoint."""
+broadcasts the tokens; outputs must equal the single-process run of the same checkpoint.  Overlapped mode keeps one
+step per stage in flight (asynchronous transfers, requests of a launched step are not scheduled again until its
+tokens are back); lock-step mode runs one step at a time."""
 import os
 import sys
 
@@ -23,23 +25,25 @@ def _params(tp):
     return [SamplingParams(max_tokens=8, ignore_eos=True), mid, SamplingParams(max_tokens=5, ignore_eos=True)]
 
 
-def _worker(rank, world, port, path, prompts, tp, q):
+def _worker(rank, world, port, path, prompts, tp, overlap, q):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
-                      MASTER_PORT=str(port), B200_FUSED_TP_COLLECTIVES="0")
+                      MASTER_PORT=str(port), B200_FUSED_TP_COLLECTIVES="0", B200_PP_OVERLAP="1" if overlap else "0")
     try:
         from vllm_metax_b200 import LLM, SamplingParams
 
         llm = LLM(path, device="cpu", tensor_parallel_size=tp, pipeline_parallel_size=world // tp, block_size=16,
                   max_model_len=128, max_num_seqs=8, max_num_batched_tokens=64, num_gpu_blocks=64, dtype=torch.float32)
         outs = llm.generate(prompts, _params(tp))
+        # overlapped: one step per stage was in flight at some point (disjoint request sets); lock-step: never
+        assert llm.engine.stats.get("max_inflight", 0) == (world // tp if overlap else 0), llm.engine.stats
         q.put((rank, [o.outputs[0].token_ids for o in outs]))
     except BaseException as e:
         q.put((rank, repr(e)))
         raise
 
 
-@pytest.mark.parametrize("world,tp", [(2, 1), (4, 2)])
-def test_pipeline_parallel_matches_single_process(tmp_path, world, tp):
+@pytest.mark.parametrize("world,tp,overlap", [(2, 1, True), (2, 1, False), (4, 2, True)])
+def test_pipeline_parallel_matches_single_process(tmp_path, world, tp, overlap):
     from vllm_metax_b200 import LLM, SamplingParams
 
     kw = dict(device="cpu", block_size=16, max_model_len=128, max_num_seqs=8, max_num_batched_tokens=64, num_gpu_blocks=64)
@@ -56,7 +60,7 @@ def test_pipeline_parallel_matches_single_process(tmp_path, world, tp):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = 29900 + (os.getpid() % 80) + world
-    procs = [ctx.Process(target=_worker, args=(r, world, port, path, prompts, tp, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, path, prompts, tp, overlap, q)) for r in range(world)]
     for p in procs:
         p.start()
     got = dict(q.get(timeout=240) for _ in range(world))

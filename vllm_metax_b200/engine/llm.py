@@ -43,6 +43,17 @@ class LLMEngine:
         self.requests: dict[str, Request] = {}
         self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0}
         self.step_hooks: list = []
+        # pipeline parallel: as many steps in flight as there are stages (B200_PP_OVERLAP=0: lock-step)
+        import collections
+
+        from .. import envs
+        from ..parallel import state as ps_
+
+        pp_size = ps_.get_pp_group().world_size
+        self.pipeline_depth = pp_size if (pp_size > 1 and envs.B200_PP_OVERLAP) else 1
+        self._inflight: collections.deque = collections.deque()
+        if self.pipeline_depth > 1:
+            self.scheduler.max_seqs_per_step = max(1, -(-cfg.scheduler.max_num_seqs // self.pipeline_depth))
         from .spec_decode import SpeculativeConfig, make_proposer
 
         self.spec_config = SpeculativeConfig.from_dict((cfg.additional_config or {}).get("speculative_config"))
@@ -142,6 +153,8 @@ class LLMEngine:
         """One scheduler iteration; returns the requests that finished in it."""
         if self.dead is not None:
             raise EngineDeadError(str(self.dead))
+        if self.pipeline_depth > 1:
+            return self._step_pipelined()
         so = self.scheduler.schedule()
         if so.is_empty:
             if self.scheduler.has_unfinished() and not self.scheduler.paused:
@@ -167,6 +180,49 @@ class LLMEngine:
         finished = self.scheduler.update(so, sampled, now)
         if self.proposer is not None:
             self._propose_drafts(so, sampled)
+        self.stats["steps"] += 1
+        self.stats["decode_tokens"] += so.num_decode
+        self.stats["prefill_tokens"] += so.num_tokens - so.num_decode
+        self.stats["preemptions"] = self.scheduler.num_preemptions
+        for r in finished:
+            self.requests.pop(r.request_id, None)
+        return finished
+
+    def _step_pipelined(self) -> list[Request]:
+        """Pipeline parallel with one step per stage in flight: launch steps over disjoint request sets until the
+        pipeline is full, then take the oldest step's tokens.  Every stage runs this loop on the same scheduler
+        state, so all of them launch the same steps in the same order."""
+        try:
+            if self.liveness is not None:
+                self.liveness.check()
+            while len(self._inflight) < self.pipeline_depth:
+                so = self.scheduler.schedule()
+                if so.is_empty:
+                    break
+                self.scheduler.mark_in_flight(so)
+                for hook in self.step_hooks:
+                    hook("before", self.stats["steps"] + len(self._inflight))
+                self._inflight.append((so, self.runner.execute_async(so)))
+                self.stats["max_inflight"] = max(self.stats.get("max_inflight", 0), len(self._inflight))
+            if not self._inflight:
+                if self.scheduler.has_unfinished() and not self.scheduler.paused:
+                    raise RuntimeError("scheduler made no progress: KV cache too small for the waiting request")
+                return []
+            so, pending = self._inflight.popleft()
+            sampled = pending.result()
+            for hook in self.step_hooks:
+                hook("after", self.stats["steps"])
+        except BaseException as e:
+            self.dead = e
+            if self.liveness is not None:
+                self.liveness.announce_failure(repr(e))
+            self._inflight.clear()
+            self.scheduler.in_flight.clear()
+            self._release_all()
+            raise EngineDeadError(f"engine step failed: {e!r}") from e
+        if self.kv_connector is not None and self.kv_connector.config.is_producer:
+            self._publish_kv(so)
+        finished = self.scheduler.update(so, sampled, time.perf_counter())
         self.stats["steps"] += 1
         self.stats["decode_tokens"] += so.num_decode
         self.stats["prefill_tokens"] += so.num_tokens - so.num_decode

@@ -79,6 +79,16 @@ class ModelRunner:
                                  f"least dcp tensor-parallel ranks (kv heads {m.num_key_value_heads}, tp {ps.tp_size()}, "
                                  f"dcp {self.dcp}), or an MLA model")
         self.dcp_per_token = self.dcp > 1 and cfg.model.is_mla
+        # pipeline parallel with overlapped steps: asynchronous stage-to-stage transfers and one token buffer per
+        # step in flight
+        import collections
+
+        self._pp_async = ps.get_pp_group().world_size > 1 and envs.B200_PP_OVERLAP
+        self._pp_sends: collections.deque = collections.deque()
+        self._pp_next = 0
+        self._prep_done = None
+        self._pp_copy_stream = None
+        self._pp_host = None
         self.max_blocks_per_seq = (sc.max_model_len + self.virt_bs - 1) // self.virt_bs
         self.kv_caches: list = []
         self.num_blocks = 0
@@ -159,6 +169,8 @@ class ModelRunner:
         self.prefill_qsl = self.d32[o:o + B + 1]
         S = max(B, T)        # with draft tokens every fed position of a request is sampled
         self.sampled = torch.zeros(S, dtype=torch.int64, device=dev)
+        self._pp_slots = [torch.zeros(S, dtype=torch.int64, device=dev)
+                          for _ in range(2 * ps.get_pp_group().world_size)] if self._pp_async else []
         self.sampled_host = torch.zeros(S, dtype=torch.int64, pin_memory=pin)
         self.sample_idx = torch.zeros(S, dtype=torch.int64, device=dev)
         self.sample_idx_host = torch.zeros(S, dtype=torch.int64, pin_memory=pin)
@@ -435,11 +447,20 @@ class ModelRunner:
     def _pp_send(self, pp, out: dict) -> None:
         h, r = out["hidden_states"], out.get("residual")
         parts = [h] if self._pp_parts() == 1 else [h, r if r is not None else torch.zeros_like(h)]
-        pp.send(torch.stack(parts).contiguous(), pp.rank_in_group + 1)
+        buf = torch.stack(parts).contiguous()
+        if self._pp_async:      # the transfer runs beside the next step's forward; the buffer lives until it is done
+            self._pp_sends.append((pp.isend(buf, pp.rank_in_group + 1), buf))
+            while len(self._pp_sends) > 2 * pp.world_size:
+                self._pp_sends.popleft()[0].wait()
+        else:
+            pp.send(buf, pp.rank_in_group + 1)
 
     def _pp_recv(self, pp, T: int) -> dict:
         buf = torch.empty(self._pp_parts(), T, self.cfg.model.hidden_size, dtype=self.cfg.model.dtype, device=self.device)
-        pp.recv(buf, pp.rank_in_group - 1)
+        if self._pp_async:
+            pp.irecv(buf, pp.rank_in_group - 1).wait()
+        else:
+            pp.recv(buf, pp.rank_in_group - 1)
         return {"hidden_states": buf[0], "residual": buf[1] if buf.shape[0] > 1 else None}
 
     def _decode_splits(self, batch: int) -> int:
@@ -562,6 +583,43 @@ class ModelRunner:
                 out[s.request.request_id] = [out[s.request.request_id]]
         return out
 
+    # ------------------------------------------------------------------ pipelined steps
+    @torch.no_grad()
+    def execute_async(self, so: SchedulerOutput) -> "PendingStep":
+        """Launch one step without waiting for its tokens (pipeline parallel with one step per stage in flight).
+        This stage's share of the step is enqueued - receive from the previous stage, forward, send to the next, or
+        sample on the last stage - and the token broadcast from the last stage is started; ``PendingStep.result()``
+        waits for it.  Steps launched back to back must hold disjoint requests (the scheduler's ``in_flight`` set).
+        Upstream keeps ``pipeline_parallel_size`` batches in its executor queue the same way; the reference model
+        files only mark the stage boundaries (vllm_metax/models/deepseek_v2.py:1364-1386, 1473-1494)."""
+        pp = ps.get_pp_group()
+        if self.is_cuda and self._prep_done is not None:
+            self._prep_done.synchronize()          # the previous step's H2D copies have read the pinned staging area
+        self._route_lora(so)
+        md, T, rows, reqs = self._prepare(so)
+        if self.is_cuda:
+            self._prep_done = torch.cuda.Event()
+            self._prep_done.record()
+        all_greedy = all(r.params.greedy and not r.params.needs_penalties and not r.params.constrained for r in reqs)
+        n = len(rows)
+        h = self._forward(md, T)
+        if n == 0:
+            return PendingStep(self, None, None, [], 0)
+        slot = self._pp_slots[self._pp_next % len(self._pp_slots)]
+        self._pp_next += 1
+        if not isinstance(h, dict):
+            if n == T:
+                hs = h
+            else:
+                idx = torch.as_tensor(rows, dtype=torch.int64)
+                hs = h.index_select(0, idx.to(self.device, non_blocking=False))
+            logits = self.model.compute_logits(hs)
+            tokens = ops.argmax(logits, slot[:n]) if all_greedy else self._sample(logits, reqs)
+            if tokens.data_ptr() != slot.data_ptr():
+                slot[:n].copy_(tokens[:n])
+        work = pp.broadcast_async(slot[:n], src=pp.world_size - 1) if pp.world_size > 1 else None
+        return PendingStep(self, work, slot, reqs, n)
+
     def _route_lora(self, so: SchedulerOutput) -> bool:
         """Make the adapters of this step resident and tell the hooks which rows use which slot."""
         if self.lora is None:
@@ -582,3 +640,41 @@ class ModelRunner:
         from .sampler import sample_batch
 
         return sample_batch(logits, reqs, self.sampled[:len(reqs)])
+
+
+class PendingStep:
+    """Tokens of a launched step: ``result()`` waits for the last stage's broadcast and returns ``{request id: token}``
+    (a list per request where several positions were sampled)."""
+
+    def __init__(self, runner: ModelRunner, work, slot, reqs, n: int):
+        self.runner, self.work, self.slot, self.reqs, self.n = runner, work, slot, reqs, n
+
+    def result(self) -> dict:
+        if self.n == 0:
+            return {}
+        if self.slot.is_cuda:
+            # on a side stream: the host must not wait for the NEXT step's kernels, which are already queued on the
+            # compute stream behind this step's
+            r = self.runner
+            if r._pp_copy_stream is None:
+                r._pp_copy_stream = torch.cuda.Stream(device=r.device)
+                r._pp_host = torch.zeros(self.slot.numel(), dtype=torch.int64, pin_memory=True)
+            with torch.cuda.stream(r._pp_copy_stream):
+                if self.work is not None:
+                    self.work.wait()
+                r._pp_host[: self.n].copy_(self.slot[: self.n], non_blocking=True)
+            r._pp_copy_stream.synchronize()
+            host = r._pp_host[: self.n]
+        else:
+            if self.work is not None:
+                self.work.wait()
+            host = self.slot[: self.n]
+        self.runner.d2h_bytes += self.n * 8
+        out: dict = {}
+        for r, tok in zip(self.reqs, host.tolist()):
+            if r.request_id in out:
+                prev = out[r.request_id]
+                out[r.request_id] = (prev if isinstance(prev, list) else [prev]) + [tok]
+            else:
+                out[r.request_id] = tok
+        return out

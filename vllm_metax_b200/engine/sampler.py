@@ -12,7 +12,6 @@ import torch
 
 from .. import _custom_ops as ops
 
-_rngs: dict[str, random.Random] = {}
 _global_rng = random.Random(0)
 
 
@@ -22,16 +21,18 @@ def seed_global(seed: int) -> None:
 
 
 def _uniform_for(req) -> float:
+    """A seeded request draws from its own stream, kept on the request (two engines in one process, or a reused
+    request id, never share one)."""
     if req.params.seed is None:
         return _global_rng.random()
-    rng = _rngs.get(req.request_id)
+    rng = getattr(req, "_sample_rng", None)
     if rng is None:
-        rng = _rngs[req.request_id] = random.Random(req.params.seed)
+        rng = req._sample_rng = random.Random(req.params.seed)
     return rng.random()
 
 
 def forget(request_id: str) -> None:
-    _rngs.pop(request_id, None)
+    """Kept for callers of earlier versions: the streams live on the requests and need no clean-up."""
 
 
 def sample_batch(logits: torch.Tensor, reqs, out: torch.Tensor) -> torch.Tensor:

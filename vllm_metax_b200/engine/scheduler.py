@@ -57,6 +57,10 @@ class Scheduler:
         self.running: list[Request] = []
         self.paused = False
         self.external_kv = None            # callable(req): attach externally published KV blocks before admission
+        # pipelined engine: requests of steps that were launched but whose tokens are not back yet.  They are not
+        # scheduled again, not pre-empted, and an abort only marks them (their blocks are in use by the device).
+        self.in_flight: set[str] = set()
+        self.max_seqs_per_step = cfg.max_num_seqs
         self.num_preemptions = 0
         self.num_draft_tokens = 0
         self.num_accepted_tokens = 0
@@ -73,6 +77,9 @@ class Scheduler:
         for q in (self.running, self.waiting):
             for r in list(q):
                 if r.request_id == request_id:
+                    if request_id in self.in_flight:       # freed by update() when its step comes back
+                        r.status = RequestStatus.FINISHED_ABORTED
+                        return True
                     q.remove(r)
                     self.kv.free(r)
                     r.status = RequestStatus.FINISHED_ABORTED
@@ -91,7 +98,7 @@ class Scheduler:
     # ------------------------------------------------------------------ scheduling
     def _preempt_one(self, out: SchedulerOutput, keep: Request) -> bool:
         for victim in reversed(self.running):
-            if victim is keep:
+            if victim is keep or victim.request_id in self.in_flight:
                 continue
             self.running.remove(victim)
             out.scheduled = [s for s in out.scheduled if s.request is not victim]
@@ -110,8 +117,11 @@ class Scheduler:
             return out
         budget = self.cfg.max_num_batched_tokens
         # ---- running requests (decode, or the next chunk of a long prefill)
+        cap = self.max_seqs_per_step
         for req in list(self.running):
-            if req not in self.running or budget <= 0:
+            if req not in self.running or budget <= 0 or len(out.scheduled) >= cap:
+                continue
+            if req.request_id in self.in_flight:
                 continue
             remaining = req.num_tokens - req.num_computed_tokens
             k = len(req.spec_token_ids) if remaining == 1 and req.output_token_ids else 0
@@ -131,7 +141,8 @@ class Scheduler:
             out.scheduled.append(ScheduledRequest(req, n, req.num_computed_tokens, n == remaining + k, k))
             budget -= n
         # ---- admit waiting requests
-        while self.waiting and budget > 0 and len(self.running) < self.cfg.max_num_seqs and not out.preempted:
+        while (self.waiting and budget > 0 and len(self.running) < self.cfg.max_num_seqs and not out.preempted
+               and len(out.scheduled) < cap):
             req = self.waiting[0]
             self.kv.try_prefix_hit(req)
             if self.external_kv is not None and not req.output_token_ids:
@@ -161,11 +172,20 @@ class Scheduler:
         out.num_decode = len(dec)
         return out
 
+    def mark_in_flight(self, out: SchedulerOutput) -> None:
+        self.in_flight.update(s.request.request_id for s in out.scheduled)
+
     def update(self, out: SchedulerOutput, sampled: dict[str, int], now: float) -> list[Request]:
         """Advance request state after the model ran; returns requests that finished."""
         finished = []
         for s in out.scheduled:
             req = s.request
+            self.in_flight.discard(req.request_id)
+            if req.status == RequestStatus.FINISHED_ABORTED:       # aborted while its step was in flight
+                if req in self.running:
+                    self.running.remove(req)
+                    self.kv.free(req)
+                continue
             if s.num_spec:
                 # lossless verification of deterministic drafts: the target token of every fed position was
                 # sampled; drafts are kept while they equal it, the first mismatch (or the token after the last

@@ -50,6 +50,8 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # B200_FUSED_TP_MIN_TOKENS tokens; GEMM + peer-store all-reduce + add-norm below).
     "B200_FUSED_TP_KERNEL": _str("B200_FUSED_TP_KERNEL", "split"),
     "B200_FUSED_TP_MIN_TOKENS": _int("B200_FUSED_TP_MIN_TOKENS", 1024),
+    # Pipeline parallel: keep one step per stage in flight (disjoint request sets) instead of running lock-step.
+    "B200_PP_OVERLAP": _flag("B200_PP_OVERLAP", "1"),
     # Stream-K CTA-pair GEMM for skinny problems (read by the native GEMM dispatcher; 0 = tile / split-K kernels).
     "B200_GEMM_STREAMK": _flag("B200_GEMM_STREAMK", "1"),
     # One query tile per CTA in the prefill attention kernel (read by the native dispatcher; debug only).
@@ -63,8 +65,9 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # CUDA-graph capture of decode steps.
     "B200_CUDA_GRAPHS": _flag("B200_CUDA_GRAPHS", "1"),
     # All-gather leg of the fused row-parallel path through an NVLink multicast mapping (one multimem.st, replicated
-    # by the switch) when torch's symmetric memory can provide one; 0 = one peer store per rank.
-    "B200_USE_MULTIMEM": _flag("B200_USE_MULTIMEM", "1"),
+    # by the switch) when torch's symmetric memory can provide one.  0 = one peer store per rank, 1 = multicast at 4
+    # ranks and more (at 2 ranks it saves no bytes and measured 10 % slower), 2 = multicast at any world size.
+    "B200_USE_MULTIMEM": _int("B200_USE_MULTIMEM", 1),
     # Iteration budget of device-side waits on peer flags before giving up.
     "B200_PEER_WAIT_ITERS": _int("B200_PEER_WAIT_ITERS", 20_000_000),
     "B200_PP_DISABLE_ALLGATHER": _flag("B200_PP_DISABLE_ALLGATHER", "0"),

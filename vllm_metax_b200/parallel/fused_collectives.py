@@ -73,7 +73,8 @@ class FusedRowParallelNorm:
         self.local_sync_split = torch.zeros(4, dtype=torch.int32, device=device)
         self.out_mc = 0
         self._ipc_out, self._ipc_ptrs_gather = self.out, self.ptrs_gather
-        if envs.B200_USE_MULTIMEM and self.tp > 1:
+        mm = int(envs.B200_USE_MULTIMEM)
+        if (mm >= 2 or (mm == 1 and self.tp >= 4)) and self.tp > 1 and self.kernel != "mono":   # "mono" gathers through self.ptrs
             self._try_multicast_out(n_out, dtype, max_tokens, hidden, r_recv, r_f1, r_f2)
         self.wait_cycles = int(envs.B200_PEER_WAIT_ITERS) * 200  # iteration budget expressed in SM cycles
         torch.cuda.synchronize(device)

@@ -97,6 +97,16 @@ class Group:
             dist.broadcast(x, src=self.ranks[src], group=self._pg(x))
         return x
 
+    def broadcast_async(self, x: torch.Tensor, src: int = 0):
+        """Start a broadcast; the returned work's ``wait()`` orders the current stream (NCCL) or the host (Gloo) after it."""
+        return dist.broadcast(x, src=self.ranks[src], group=self._pg(x), async_op=True)
+
+    def isend(self, x: torch.Tensor, dst: int):
+        return dist.isend(x, dst=self.ranks[dst], group=self._pg(x))
+
+    def irecv(self, x: torch.Tensor, src: int):
+        return dist.irecv(x, src=self.ranks[src], group=self._pg(x))
+
     def send(self, x: torch.Tensor, dst: int) -> None:
         dist.send(x, dst=self.ranks[dst], group=self._pg(x))
 
