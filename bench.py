@@ -271,7 +271,8 @@ def main() -> None:
 
         sys.stdout.flush()
         threading.Timer(30.0, lambda: os._exit(0)).start()
-        wl.graph = None
+        if args.pp == 1:
+            wl.graph = None
         runner.graphs.clear()
         torch.cuda.synchronize()
         ps.destroy()

@@ -335,11 +335,13 @@ def test_custom_allreduce_and_reduce_rms_2gpu():
     _launch(_custom_ar_worker, _world())
 
 
-def _moe_layer_a2a_worker(rank, world):
-    """FusedMoE with B200_MOE_A2A=1 (sequence-parallel dispatch / combine) against the fp32 MoE oracle."""
+def _moe_layer_a2a_worker(rank, world, fp8=False):
+    """FusedMoE with B200_MOE_A2A=1 (sequence-parallel dispatch / combine) against the fp32 MoE oracle; with ``fp8``
+    the experts are block-scaled e4m3 and the tokens travel quantised (one scale per 128 channels)."""
     os.environ["B200_MOE_A2A"] = "1"
     from vllm_metax_b200 import _custom_ops as ops
     from vllm_metax_b200.layers.fused_moe import FusedMoE, reference_moe
+    from vllm_metax_b200.ops import reference as ref
     from vllm_metax_b200.parallel import state as ps
 
     ps.init_distributed(tensor_parallel_size=world)
@@ -348,11 +350,28 @@ def _moe_layer_a2a_worker(rank, world):
     gen = torch.Generator().manual_seed(21)
     w13 = (torch.randn(E, 2 * I, H, generator=gen) * 0.05).to(torch.bfloat16)
     w2 = (torch.randn(E, H, I, generator=gen) * 0.05).to(torch.bfloat16)
-    with torch.device(dev):
-        moe = FusedMoE(E, topk, H, I, dtype=torch.bfloat16, renormalize=True)
     el = E // world
-    moe.w13_weight.data.copy_(w13[rank * el:(rank + 1) * el])
-    moe.w2_weight.data.copy_(w2[rank * el:(rank + 1) * el])
+    mine = slice(rank * el, (rank + 1) * el)
+    if fp8:
+        from vllm_metax_b200.quantization.fp8 import Fp8MoEMethod
+
+        def quant(w):
+            Eb, N, K = w.shape
+            wb = w.float().reshape(Eb, N // 128, 128, K // 128, 128)
+            sc = wb.abs().amax(dim=(2, 4)) / 448.0
+            return (wb / sc[:, :, None, :, None]).reshape(Eb, N, K).to(torch.float8_e4m3fn), sc.float()
+
+        with torch.device(dev):
+            moe = FusedMoE(E, topk, H, I, dtype=torch.bfloat16, renormalize=True, quant_method=Fp8MoEMethod())
+        q13, s13 = quant(w13[mine])
+        q2, s2 = quant(w2[mine])
+        moe.w13_weight.data.copy_(q13); moe.w13_weight_scale_inv.data.copy_(s13)
+        moe.w2_weight.data.copy_(q2); moe.w2_weight_scale_inv.data.copy_(s2)
+    else:
+        with torch.device(dev):
+            moe = FusedMoE(E, topk, H, I, dtype=torch.bfloat16, renormalize=True)
+        moe.w13_weight.data.copy_(w13[mine])
+        moe.w2_weight.data.copy_(w2[mine])
     for T in (37, 1, 200, 64):
         x = (torch.randn(T, H, generator=gen) * 0.5).to(torch.bfloat16)
         logits = torch.randn(T, E, generator=gen)
@@ -360,19 +379,22 @@ def _moe_layer_a2a_worker(rank, world):
         got = moe(x.to(dev), logits.to(dev), None if shared is None else (shared / world).to(dev))
         torch.cuda.synchronize()
         ops.check_kernel_status(rank)
-        from vllm_metax_b200.ops import reference as ref
-
+        assert getattr(moe, "_a2a", None) is not None and moe._a2a.quant == fp8      # the dispatch path ran
         tw, ti = ref.topk_softmax(logits, topk, True)
-        want = reference_moe(x.float(), w13.float(), w2.float(), tw, ti.long())
+        if fp8:      # the fp8 method keeps [gate rows | up rows]
+            want = ref.fused_experts(x.float(), w13.float(), w2.float(), tw, ti)
+        else:
+            want = reference_moe(x.float(), w13.float(), w2.float(), tw, ti.long())
         if shared is not None:
             want = want + shared.float()
         err = 1.0 - float(torch.nn.functional.cosine_similarity(got.float().cpu().flatten(), want.flatten(), dim=0))
-        assert got.shape == (T, H) and err < 5e-4, (T, err)
+        assert got.shape == (T, H) and err < (5e-3 if fp8 else 5e-4), (T, err)
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-def test_fused_moe_sequence_parallel_a2a_2gpu():
-    _launch(_moe_layer_a2a_worker, 2)
+@pytest.mark.parametrize("fp8", [False, True])
+def test_fused_moe_sequence_parallel_a2a_2gpu(fp8):
+    _launch(_moe_layer_a2a_worker, 2, fp8)
 
 
 # ---- pipeline parallel and decode context parallel through the engine ------------------------------------------

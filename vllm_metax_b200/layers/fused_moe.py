@@ -147,12 +147,14 @@ class FusedMoE(nn.Module):
         per = (T + self.ep - 1) // self.ep
         sizes = [max(0, min(per, T - r * per)) for r in range(self.ep)]
         lo, n = self.ep_rank * per, sizes[self.ep_rank]
+        qm = self.quant_method
+        wire_fp8 = bool(getattr(qm, "a2a_wire_fp8", False))
         mgr = getattr(self, "_a2a", None)
         if mgr is None or mgr.max_tokens < per:
             if mgr is not None:
                 mgr.close()
             cap = max(per, 64)
-            mgr = NvlinkAll2AllManager(g, cap, H, self.top_k, self.num_experts, x.dtype, x.device)
+            mgr = NvlinkAll2AllManager(g, cap, H, self.top_k, self.num_experts, x.dtype, x.device, quant_fp8=wire_fp8)
             self._a2a = mgr
         if n > 0:
             w, ids = self.route(router_logits[lo: lo + n])
@@ -161,6 +163,8 @@ class FusedMoE(nn.Module):
             ids = torch.empty(0, self.top_k, dtype=torch.int32, device=x.device)
 
         def experts(a, a_scale, block_expert, total):
+            if qm is not None:
+                return qm.apply_sorted(self, a, a_scale, block_expert, total)
             h = ops.gemm_grouped(a, self.w13_weight, block_expert, total, epi=1)
             return ops.gemm_grouped(h, self.w2_weight, block_expert, total)
 
@@ -172,8 +176,8 @@ class FusedMoE(nn.Module):
 
     def forward(self, x: torch.Tensor, router_logits: torch.Tensor,
                 shared_out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        if (self.ep > 1 and self.quant_method is None and self.reduce_results and x.is_cuda
-                and envs.B200_MOE_A2A):
+        if (self.ep > 1 and (self.quant_method is None or hasattr(self.quant_method, "apply_sorted"))
+                and self.reduce_results and x.is_cuda and envs.B200_MOE_A2A and x.shape[1] % 128 == 0):
             return self._forward_a2a(x, router_logits, shared_out)
         w, ids = self.route(router_logits)
         if self.quant_method is not None:

@@ -86,6 +86,22 @@ class Fp8MoEMethod:
         return ops.moe_combine(y, topk_weights, inv, T, shared_out)
 
 
+    # Sequence-parallel MoE over the NVLink dispatch / combine kernels: tokens travel as e4m3 rows with one scale per
+    # 128 channels (the dispatch kernel quantises them), so the rows this rank receives feed the first grouped GEMM
+    # without another quantisation pass.
+    a2a_wire_fp8 = True
+
+    def apply_sorted(self, layer, a, a_scale, block_expert, total):
+        """Expert MLPs on expert-sorted rows that arrive quantised: ``a [padded, H]`` e4m3 bytes, ``a_scale
+        [padded, H / 128]``.  Mirrors the reference's masked / batched expert path behind its low-latency dispatch
+        (model_executor/layers/fused_moe/experts/batched_deep_gemm_moe.py:248-329)."""
+        dt = self.dtype
+        aq = a.view(torch.float8_e4m3fn) if a.dtype == torch.uint8 else a
+        h = ops.fp8_block_scaled_mm(aq, a_scale, layer.w13_weight, layer.w13_weight_scale_inv, dt, block_expert, total)
+        hq, h_s = ops.silu_and_mul_per_block_quant(h, BLOCK)
+        return ops.fp8_block_scaled_mm(hq, h_s, layer.w2_weight, layer.w2_weight_scale_inv, dt, block_expert, total)
+
+
 class Fp8Config:
     """``quantization_config`` of an fp8 checkpoint: ``{"quant_method": "fp8", "weight_block_size": [128, 128],
     "activation_scheme": "dynamic"}``.  Layers listed in ``ignored_layers`` / not matching stay bf16."""
