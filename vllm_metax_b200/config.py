@@ -133,6 +133,11 @@ class ModelConfig:
     hc_sinkhorn_iters: int = 20
     hc_eps: float = 1e-6
     num_hash_layers: int = 0                   # leading MoE layers routed by token id (tid2eid table)
+    # ---- DeepSeek-V4 attention: one shared 512-wide K = V vector per token, a sliding window of raw vectors plus a
+    # ratio-c compressed cache (per layer: 0 / 1 = window only, 4 = compressed + top-k indexer, 128 = compressed, dense)
+    compress_ratios: Optional[list] = None     # None = V3.2-style latent attention without compression
+    o_lora_rank: int = 0                       # grouped low-rank output projection (wo_a / wo_b)
+    o_groups: int = 1
     # ---- numerics / quantisation ----------------------------------------
     dtype: torch.dtype = torch.bfloat16
     quantization: Optional[str] = None         # None | fp8 | w8a8_int8 | awq | gptq | ...
@@ -240,6 +245,8 @@ class ModelConfig:
             num_nextn_predict_layers=d.get("num_nextn_predict_layers", 0) or 0,
             hc_mult=d.get("hc_mult", 0) or 0, hc_sinkhorn_iters=d.get("hc_sinkhorn_iters", 20) or 20,
             hc_eps=d.get("hc_eps", 1e-6) or 1e-6, num_hash_layers=d.get("num_hash_layers", 0) or 0,
+            compress_ratios=d.get("compress_ratios"), o_lora_rank=d.get("o_lora_rank", 0) or 0,
+            o_groups=d.get("o_groups", 1) or 1,
             dtype=d.get("torch_dtype", d.get("dtype", "bfloat16")),
             eos_token_id=(d.get("eos_token_id")[0] if isinstance(d.get("eos_token_id"), list) else d.get("eos_token_id")),
         )

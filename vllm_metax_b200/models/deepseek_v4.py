@@ -10,10 +10,12 @@ What is V4-specific here:
   token-id hash table (``tid2eid``) picks the experts while the gate only supplies the weights;
 * the output head mixes the streams once more (``hc_head``) before the final norm.
 
-Attention runs on this package's latent (MLA) attention with the DSA top-k indexer.  The reference's V4 attention
-additionally keeps a ratio-c COMPRESSED latent cache next to a sliding window (``models/deepseek_v4/compressor.py``,
-``attention.py:100-373``, 584-byte cache records); that cache manager is not part of this module - every token's
-latent is cached uncompressed - so long-context memory use is that of V3.2, not of V4.
+Attention: with ``compress_ratios`` in the config the layers run ``layers/v4_attention.py`` (shared 512-wide K = V
+vector, sliding window of raw vectors + ratio-c compressed cache with its compressor state, indexer on the ratio-4
+layers, attention sink, grouped low-rank output projection).  The raw vectors of all positions stay in the paged
+cache (only the last ``sliding_window`` of them are read), so the window's memory saving is not realised yet.
+Without ``compress_ratios`` (configs written for the V3.2-style path) the layers run the latent attention of
+``deepseek_v2.py`` with the DSA indexer.
 
 Checkpoint names of the V4 release (``layers.N.attn.wq_a`` ...) are rewritten onto the module tree below.
 Parity: vllm_metax/models/deepseek_v4/model.py:70-1367 (DeepseekV4MLP, DeepseekV4MoE :478-724 routing,
@@ -32,6 +34,7 @@ from ..config import ModelConfig
 from ..layers.basic import ParallelLMHead, RMSNorm, VocabParallelEmbedding
 from ..layers.fused_moe import FusedMoE
 from ..layers.linear import ReplicatedLinear
+from ..layers.v4_attention import DeepseekV4Attention
 from ..ops import mhc
 from ..parallel import state as ps
 from ..quantization import get_moe_method
@@ -112,7 +115,8 @@ class DeepseekV4DecoderLayer(nn.Module):
         super().__init__()
         abs_idx = int(prefix.rsplit(".", 1)[1])
         self.cfg = cfg
-        self.attn = DeepseekV2MLAAttention(cfg, kv_index, f"{prefix}.attn")
+        self.attn = (DeepseekV4Attention(cfg, kv_index, f"{prefix}.attn") if cfg.compress_ratios is not None
+                     else DeepseekV2MLAAttention(cfg, kv_index, f"{prefix}.attn"))
         self.ffn = DeepseekV4MoE(cfg, abs_idx, f"{prefix}.ffn") if cfg.layer_is_moe(abs_idx) else \
             LlamaMLP(cfg, cfg.intermediate_size, f"{prefix}.ffn")
         self.attn_norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.dtype)
@@ -188,25 +192,82 @@ def rename_v4(name: str) -> str:
     return name
 
 
+# checkpoint tensors that are stored apart and live in one fused parameter here: (fused, part, which half)
+_V4_STACKED = (("compressor.fused_wkv_wgate", "compressor.wkv", 0), ("compressor.fused_wkv_wgate", "compressor.wgate", 1),
+               ("attn.fused_wqa_wkv", "attn.wq_a", 0), ("attn.fused_wqa_wkv", "attn.wkv", 1))
+
+
 class DeepseekV4ForCausalLM(DeepseekV2ForCausalLM):
     def __init__(self, cfg: ModelConfig):
         nn.Module.__init__(self)
         self.cfg = cfg
         self.model = DeepseekV4Model(cfg)
         self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, cfg.dtype)
+        self.v4_attention = cfg.compress_ratios is not None
+        if self.v4_attention:
+            # compressor accumulators are per request and cannot be rebuilt from a cached prefix
+            self.supports_prefix_caching = False
+            self.allocate_state = self._allocate_state
+
+    # ---- caches of the V4 attention layers ---------------------------------------------------------------------
+    def _attn_layers(self):
+        return [self.model.layers[str(i)].attn for i in range(self.cfg.num_hidden_layers)]
+
+    def kv_cache_spec(self) -> dict:
+        return {"kind": "v4"} if self.v4_attention else super().kv_cache_spec()
+
+    def kv_bytes_per_block(self, block_size: int, kv_cache_dtype: str) -> int:
+        if not self.v4_attention:
+            return super().kv_bytes_per_block(block_size, kv_cache_dtype)
+        elem = torch.empty((), dtype=self.cfg.dtype).element_size()
+        return sum(a.bytes_per_block(block_size, elem) for a in self._attn_layers())
+
+    def allocate_kv_cache(self, num_blocks, block_size, kv_cache_dtype, device):
+        if not self.v4_attention:
+            return super().allocate_kv_cache(num_blocks, block_size, kv_cache_dtype, device)
+        if kv_cache_dtype not in ("auto", "bfloat16", "float16", "float32"):
+            raise ValueError("the V4 attention path keeps its caches in the model dtype")
+        return [a.allocate_kv_cache(num_blocks, block_size, self.cfg.dtype, device) for a in self._attn_layers()]
+
+    def _allocate_state(self, slots: int, device) -> int:
+        return sum(a.allocate_state(slots, device) for a in self._attn_layers())
+
+    def _load_v4_attn(self, name: str, w: torch.Tensor, params: dict, modules: dict) -> str:
+        """One tensor of a V4 attention block (``layers.N.attn...``) by its release name."""
+        if not name.startswith("model."):
+            name = "model." + name
+        for fused, part, half in _V4_STACKED:
+            if f".{part}." in name:
+                target = name.replace(part, fused)
+                p = params[target]
+                off = 0 if half == 0 else p.shape[0] - w.shape[0]
+                p.data[off: off + w.shape[0]].copy_(w)
+                return target
+        p = params[name]
+        loader = getattr(modules[name.rsplit(".", 1)[0]], "weight_loader", None)
+        if loader is not None:
+            loader(p, w, None)
+        else:
+            p.data.copy_(w.reshape(p.shape))
+        return name
 
     def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]) -> set[str]:
         buffers = dict(self.named_buffers())
+        params, modules = dict(self.named_parameters()), dict(self.named_modules())
+        direct: set = set()
 
         def mapped():
             for name, w in weights:
+                if self.v4_attention and ".attn." in name:
+                    direct.add(self._load_v4_attn(name, w, params, modules))
+                    continue
                 name = rename_v4(name).replace(".ffn.experts.", ".ffn.experts.").replace(".mlp.", ".ffn.")
                 if name.endswith(".tid2eid") and name in buffers:
                     buffers[name].copy_(w.to(torch.int32))
                     continue
                 yield name, w
 
-        return super().load_weights(mapped())
+        return super().load_weights(mapped()) | direct
 
 
 class DeepSeekV4MTP(DeepSeekMTP):
