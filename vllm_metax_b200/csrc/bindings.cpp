@@ -771,6 +771,34 @@ void ar_norm_gather(Tensor& residual, const Tensor& norm_weight, double eps, con
   TORCH_CHECK(rc == 0, "ar_norm_gather: hidden size ", H, " / dtype not supported");
 }
 
+// All-reduce + residual + RMSNorm through the NVSwitch.  The four addresses lie inside one multicast-mapped symmetric
+// buffer (flag_local: this rank's own copy of the flag words).
+void nvls_ar_norm(Tensor& residual, const Tensor& norm_weight, double eps, int64_t partial_mc, int64_t out_mc,
+                  int64_t flag_mc, int64_t flag_local, int64_t T, int64_t H, int64_t tp, int64_t rank,
+                  int64_t rows_per_rank, Tensor& local_sync, bool add_residual, int64_t wait_cycles) {
+  TORCH_CHECK(tp >= 2 && tp <= b200::kMaxRanks && residual.is_contiguous() && residual.is_cuda());
+  TORCH_CHECK(residual.size(-1) == H && norm_weight.numel() == H && residual.size(0) >= rows_per_rank);
+  TORCH_CHECK(partial_mc != 0 && out_mc != 0 && flag_mc != 0 && flag_local != 0 && (partial_mc & 15) == 0 &&
+              (out_mc & 15) == 0, "nvls_ar_norm needs a multicast mapping");
+  TORCH_CHECK(local_sync.is_cuda() && local_sync.scalar_type() == at::kInt && local_sync.numel() >= 2);
+  b200::NvlsArNormParams p{};
+  p.T = T; p.H = H; p.tp = tp; p.rank = rank; p.rows_per_rank = rows_per_rank;
+  p.partial_mc = reinterpret_cast<const void*>(partial_mc);
+  p.out_mc = reinterpret_cast<void*>(out_mc);
+  p.flag_mc = reinterpret_cast<uint32_t*>(flag_mc);
+  p.flag_local = reinterpret_cast<const uint32_t*>(flag_local);
+  p.residual = residual.data_ptr();
+  p.norm_weight = norm_weight.data_ptr();
+  p.eps = (float)eps;
+  p.add_residual = add_residual;
+  p.local_sync = reinterpret_cast<uint32_t*>(local_sync.data_ptr());
+  p.wait_cycles = wait_cycles;
+  p.status = reinterpret_cast<b200::StatusWord*>(status_ptr(residual));
+  const c10::cuda::CUDAGuard guard(residual.device());
+  const int rc = b200::nvls_ar_norm(p, dtype16(residual), cur_stream());
+  TORCH_CHECK(rc == 0, "nvls_ar_norm: hidden size ", H, " / dtype not supported");
+}
+
 // A tensor over the same storage that does not keep it alive: CUDA-graph wrappers hold their captured outputs this
 // way so that the graph's memory pool, not Python references, owns the buffers (upstream's ``weak_ref_tensor``).
 Tensor weak_ref_tensor(const Tensor& t) {
@@ -1366,6 +1394,11 @@ TORCH_LIBRARY(b200, m) {
       "int rows_per_rank, int rows_cap, Tensor(b!) local_sync, bool add_residual, int wait_cycles, "
       "int out_multicast_ptr=0) -> ()",
       &ar_norm_gather);
+  m.def(
+      "nvls_ar_norm(Tensor(a!) residual, Tensor norm_weight, float eps, int partial_mc, int out_mc, int flag_mc, "
+      "int flag_local, int T, int H, int tp, int rank, int rows_per_rank, Tensor(b!) local_sync, bool add_residual, "
+      "int wait_cycles) -> ()",
+      &nvls_ar_norm);
   m.def(
       "gemm_ar_norm(Tensor x, Tensor w, Tensor(a!) residual, Tensor norm_weight, float eps, Tensor ptrs, int tp, "
       "int rank, int rows_per_rank, int rows_cap, int rb_cap, Tensor(b!) local_sync, bool add_residual, "

@@ -63,6 +63,23 @@ struct ArNormParams {
   StatusWord* status;
 };
 
+// All-reduce + residual + RMSNorm through the switch (comm_nvls_ar_norm.cu).  `*_mc` are addresses inside ONE
+// multicast mapping of a symmetric buffer; `flag_local` is this rank's own copy of the two flag words.
+struct NvlsArNormParams {
+  int T, H, tp, rank, rows_per_rank;
+  const void* partial_mc;         // [T_cap, H] the GEMM outputs of all ranks behind one address (multimem.ld_reduce)
+  void* out_mc;                   // [T_cap, H] normalised rows, written on every rank (multimem.st)
+  uint32_t* flag_mc;              // [2] arrival counters (multimem.red.add)
+  const uint32_t* flag_local;     // [2] this rank's copy of them (polled)
+  void* residual;                 // [rows_per_rank, H] this rank's shard of the residual stream (in/out)
+  const void* norm_weight;        // [H]
+  float eps;
+  int add_residual;
+  uint32_t* local_sync;           // [0] CTA ticket, [1] number of finished calls
+  long long wait_cycles;
+  StatusWord* status;
+};
+
 // All-gather -> GEMM (comm_ag_gemm.cu): C[tp*R, N] = concat_r(X_r[R, K]) . W[N, K]^T.
 struct AgGemmParams {
   int rows_per_rank, N, K, tp, rank, ldc;

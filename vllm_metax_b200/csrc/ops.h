@@ -81,6 +81,7 @@ void gemm_tn_pair(const void* A, const void* W, void* C, const void* bias, const
                   const struct RowScatter* scatter = nullptr);
 // ---- comm_ar_norm.cu
 int ar_norm_gather(const ArNormParams& p, int dtype, cudaStream_t stream);
+int nvls_ar_norm(const NvlsArNormParams& p, int dtype, cudaStream_t stream);
 // ---- gemm_splitk_tcgen05.cu
 int gemm_splitk_choice(int M, int N, int K, int sms);
 void gemm_tn_splitk(const void* A, const void* W, void* C, const void* bias, const void* residual, int M, int N, int K,

@@ -129,6 +129,13 @@ class ModelRunner:
         fused = get_fused_row_parallel(ps.get_tp_group(), self.device, self.max_tokens,
                                        self.cfg.model.hidden_size, self.cfg.model.dtype)
         ok, why = fused.self_test()                 # same verdict on every rank
+        if not ok and fused.nvls is not None:
+            import warnings
+
+            warnings.warn(f"fused row-parallel path failed its start-up check with the in-switch reduction ({why}); "
+                          "retrying with the peer-store kernels at every step size")
+            fused.disable_nvls()
+            ok, why = fused.self_test()
         if not ok and fused.out_mc:
             import warnings
 

@@ -152,6 +152,7 @@ class StaticWorkload:
         ok = p_cos < 2e-3 and d_cos < 2e-3
         return {"fused_path": bool(saved[0] is not None), "peer_allreduce": bool(saved[1] is not None),
                 "multicast_gather": bool(getattr(saved[0], "out_mc", 0)),
+                "nvls_reduce_max_tokens": (saved[0].nvls_max_tokens if getattr(saved[0], "nvls", None) is not None else 0),
                 "prefill_tokens": int(ids.shape[0]), "cos_diff": round(max(p_cos, d_cos), 6),
                 "max_abs": round(max(p_abs, d_abs), 4), "ref_max_abs": round(max(p_ref, d_ref), 3),
                 "decode_cos_diff": round(d_cos, 6), "ok": bool(ok)}

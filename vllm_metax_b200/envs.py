@@ -68,6 +68,9 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # by the switch) when torch's symmetric memory can provide one.  0 = one peer store per rank, 1 = multicast at 4
     # ranks and more (at 2 ranks it saves no bytes and measured 10 % slower), 2 = multicast at any world size.
     "B200_USE_MULTIMEM": _int("B200_USE_MULTIMEM", 1),
+    # Steps of at most this many tokens take the in-switch all-reduce + norm kernel (multimem.ld_reduce) after a plain
+    # local GEMM; larger steps take the scatter GEMM + reduce / gather kernels.  0 = never.
+    "B200_NVLS_AR_MAX_TOKENS": _int("B200_NVLS_AR_MAX_TOKENS", 1024),
     # Iteration budget of device-side waits on peer flags before giving up.
     "B200_PEER_WAIT_ITERS": _int("B200_PEER_WAIT_ITERS", 20_000_000),
     "B200_PP_DISABLE_ALLGATHER": _flag("B200_PP_DISABLE_ALLGATHER", "0"),

@@ -77,6 +77,10 @@ class FusedRowParallelNorm:
         if (mm >= 2 or (mm == 1 and self.tp >= 4)) and self.tp > 1 and self.kernel != "mono":   # "mono" gathers through self.ptrs
             self._try_multicast_out(n_out, dtype, max_tokens, hidden, r_recv, r_f1, r_f2)
         self.wait_cycles = int(envs.B200_PEER_WAIT_ITERS) * 200  # iteration budget expressed in SM cycles
+        self.nvls = None
+        self.nvls_max_tokens = min(int(envs.B200_NVLS_AR_MAX_TOKENS), max_tokens)
+        if mm >= 1 and self.tp > 1 and self.kernel != "mono" and self.nvls_max_tokens > 0:
+            self._try_nvls(dtype, hidden)
         torch.cuda.synchronize(device)
         group.barrier()
 
@@ -102,6 +106,36 @@ class FusedRowParallelNorm:
         except Exception:      # no multicast support in this torch build / driver / fabric
             self.out_mc = 0
 
+    def _try_nvls(self, dtype, hidden) -> None:
+        """Small steps (decode batches): a plain local GEMM into a multicast-mapped buffer, then ONE kernel that
+        reduces through the switch (``multimem.ld_reduce``), adds the residual, normalises and writes every rank's
+        output (``multimem.st``) - ``csrc/comm_nvls_ar_norm.cu``.  Needs torch symmetric memory with a multicast
+        handle; without one the peer-store path serves every size."""
+        try:
+            import torch.distributed._symmetric_memory as symm
+
+            esz = torch.empty((), dtype=dtype).element_size()
+            n_buf = (self.nvls_max_tokens * hidden * esz + 1023) // 1024 * 1024
+            buf = symm.empty(2 * n_buf + 1024, dtype=torch.uint8, device=self.device)
+            buf.zero_()
+            hdl = symm.rendezvous(buf, self.group.device_pg)
+            mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+            if mc == 0:
+                return
+            self.nvls = {
+                "buf": buf, "hdl": hdl, "mc": mc,
+                "partial": buf[:n_buf].view(dtype)[: self.nvls_max_tokens * hidden].view(self.nvls_max_tokens, hidden),
+                "out": buf[n_buf: 2 * n_buf].view(dtype)[: self.nvls_max_tokens * hidden].view(self.nvls_max_tokens, hidden),
+                "partial_mc": mc, "out_mc": mc + n_buf, "flag_mc": mc + 2 * n_buf,
+                "flag_local": buf.data_ptr() + 2 * n_buf,
+                "sync": torch.zeros(4, dtype=torch.int32, device=self.device),
+            }
+        except Exception:      # no multicast support in this torch build / driver / fabric
+            self.nvls = None
+
+    def disable_nvls(self) -> None:
+        self.nvls = None
+
     def disable_multicast(self) -> None:
         """Back to the IPC output buffer and per-rank peer stores (start-up check failed with multicast on)."""
         self.out_mc = 0
@@ -122,6 +156,14 @@ class FusedRowParallelNorm:
                                             rpr, self.rows_cap, self.rb_cap, self.local_sync, add_residual,
                                             self.wait_cycles)
                 return self.out[:T]
+            nv = self.nvls
+            if nv is not None and T <= self.nvls_max_tokens:
+                ops._launches += 2
+                torch.ops.b200.gemm(nv["partial"][:T], x, weight, None, None, 0, 0)
+                torch.ops.b200.nvls_ar_norm(residual_shard, norm_weight, eps, nv["partial_mc"], nv["out_mc"],
+                                            nv["flag_mc"], nv["flag_local"], T, self.hidden, self.tp, self.rank, rpr,
+                                            nv["sync"], add_residual, self.wait_cycles)
+                return nv["out"][:T]
             ops._launches += 2
             torch.ops.b200.gemm_row_scatter(x, weight, self.ptrs_scatter, self.tp, self.rank, rpr, self.rows_cap,
                                             self.local_sync_split)
@@ -146,7 +188,7 @@ class FusedRowParallelNorm:
         return self.group.all_gather(normed.contiguous(), 0)[:T]
 
 
-    def self_test(self, tokens=(8, 300)) -> tuple[bool, str]:
+    def self_test(self, tokens=(8, 300, 2100)) -> tuple[bool, str]:
         """Runs the fused path on random data at this world size and compares it with an fp32 statement of the same
         contract built from all-gathered inputs.  Returns (ok, reason); the verdict is the same on every rank.  A
         failed or timed-out kernel leaves the context usable (bounded waits set the status word, cleared here)."""

@@ -50,6 +50,38 @@ def timed(fn, iters: int, group) -> float:
     return float(t.item())
 
 
+def graph_timed(fn, group, calls: int = 16, replays: int = 5) -> float:
+    """ms per call inside a replayed CUDA graph of ``calls`` back-to-back calls (how decode steps run: no host
+    launch gaps between the kernels), median over ``replays``, max over ranks."""
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier(group=group)
+    g = torch.cuda.CUDAGraph()
+    st = torch.cuda.Stream()
+    st.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(st):
+        with torch.cuda.graph(g, stream=st):
+            for _ in range(calls):
+                fn()
+    torch.cuda.synchronize()
+    ts = []
+    for i in range(replays + 2):
+        dist.barrier(group=group)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= 2:
+            ts.append(e0.elapsed_time(e1) / calls)
+    t = torch.tensor([statistics.median(ts)], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    del g
+    return float(t.item())
+
+
 def roof_ms(flops: float, link_bytes: float) -> float:
     return max(flops / (GEMM_PEAK_TFLOPS * 1e12), link_bytes / (LINK_GBS * 1e9)) * 1e3
 
@@ -84,6 +116,8 @@ def main() -> None:
     fused = FusedRowParallelNorm(g, dev, max(a.tokens), H, bf)
     nw = torch.ones(H, dtype=bf, device=dev)
     res["multicast_gather"] = bool(fused.out_mc)
+    res["nvls_reduce"] = fused.nvls is not None
+    res["nvls_max_tokens"] = fused.nvls_max_tokens if fused.nvls is not None else 0
 
     for T in (a.tokens if want("row") else []):
         for name, K in (("o_proj", H // world), ("down_proj", I // world)):
@@ -112,6 +146,22 @@ def main() -> None:
                                                                fused.wait_cycles, fused.out_mc), a.iters, pg)
             y_loc = torch.empty(T, H, dtype=bf, device=dev)
             t_l = timed(lambda: ops.gemm(x, w, out=y_loc), a.iters, pg)
+            extra = {}
+            nv = fused.nvls
+            if nv is not None and T <= fused.nvls_max_tokens:
+                # `fused_ms` above took the in-switch reduction; the peer-store kernels at the same size:
+                fused.nvls = None
+                extra["peer_store_path_ms"] = round(timed(lambda: fused(x, w, shard, nw, 1e-5, add_residual=True), a.iters, pg), 4)
+                fused.nvls = nv
+            if T <= 1024:      # launch-bound sizes: per-call time inside a replayed graph
+                extra["fused_in_graph_ms"] = round(graph_timed(lambda: fused(x, w, shard, nw, 1e-5, add_residual=True), pg), 4)
+                if nv is not None:
+                    fused.nvls = None
+                    extra["peer_store_path_in_graph_ms"] = round(
+                        graph_timed(lambda: fused(x, w, shard, nw, 1e-5, add_residual=True), pg), 4)
+                    fused.nvls = nv
+                extra["nccl_baseline_in_graph_ms"] = round(graph_timed(baseline, pg), 4)
+                extra["local_gemm_in_graph_ms"] = round(graph_timed(lambda: ops.gemm(x, w, out=y_loc), pg), 4)
             flops = 2.0 * T * H * K
             # bytes this GPU sends: partial rows to their owners (reduce-scatter) + its normalised rows to every peer
             link = 2.0 * (T * H * 2) * (world - 1) / world
@@ -120,7 +170,7 @@ def main() -> None:
                                                "nccl_baseline_ms": round(t_b, 4), "scatter_gemm_ms": round(t_g, 4),
                                                "reduce_norm_gather_ms": round(t_n, 4), "local_gemm_ms": round(t_l, 4),
                                                "roofline_ms": round(r, 4), "of_roofline": round(r / t_f, 3),
-                                               "speedup_vs_nccl": round(t_b / t_f, 2)}
+                                               "speedup_vs_nccl": round(t_b / t_f, 2), **extra}
         ops.check_kernel_status(dev.index or 0)
 
     # ---- all-gather -> GEMM (qkv-like and gate_up-like column shards)
