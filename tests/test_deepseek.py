@@ -123,9 +123,12 @@ def test_mla_sparse_decode_gpu(kernel_status_ok):
 
 @gpu
 @pytest.mark.parametrize("int8", [False, True])
-def test_indexer_logits_and_topk_gpu(int8, kernel_status_ok):
-    bs, Hi = 64, 64
-    lens, qlens = [300, 1500, 64], [5, 2, 64]
+@pytest.mark.parametrize("impl,bs,Hi,decode", [(1, 64, 64, False), (2, 64, 64, False), (2, 16, 32, False),
+                                               (2, 128, 64, False), (2, 64, 64, True), (2, 32, 64, True)])
+def test_indexer_logits_and_topk_gpu(int8, impl, bs, Hi, decode, kernel_status_ok):
+    """impl 1: the mma.sync kernel, impl 2: the tcgen05 kernel (``kind::f8f6f4`` / ``kind::i8``); ``decode``: one query
+    token per request, which the tcgen05 kernel serves with N = heads instead of 256."""
+    lens, qlens = ([300, 1500, 64, 129], [1, 1, 1, 1]) if decode else ([300, 1500, 64], [5, 2, 64])
     g = torch.Generator().manual_seed(0)
     B = len(lens)
     nblk = [(l + bs - 1) // bs for l in lens]
@@ -158,7 +161,7 @@ def test_indexer_logits_and_topk_gpu(int8, kernel_status_ok):
     qsl = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32)
     topk = 128
     got, logits = ops.indexer_topk(q.cuda(), w.cuda(), cache.cuda(), bt.cuda(), sl.cuda(), qsl.cuda(), topk, bs,
-                                   max_seq_len=max(lens), return_logits=True)
+                                   max_seq_len=max(lens), return_logits=True, max_query_len=max(qlens), impl=impl)
     # oracle logits per token
     t = 0
     for b in range(B):

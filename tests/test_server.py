@@ -197,3 +197,51 @@ def test_tracing_and_latency_histograms():
     for v in (0.5, 1.5, 3.0):
         h.observe(v)
     assert 'x_bucket{le="2.0"} 2' in h.render("") and 'x_bucket{le="+Inf"} 3' in h.render("")
+
+
+def test_logprobs_in_completions_and_chat(client_app):
+    allm, app = client_app
+    pytest.importorskip("httpx")
+    code, text = _call(app, "POST", "/v1/completions", {"model": "toy", "prompt": "hello", "max_tokens": 4, "logprobs": 2})
+    assert code == 200, text
+    lp = json.loads(text)["choices"][0]["logprobs"]
+    assert len(lp["tokens"]) == 4 and len(lp["token_logprobs"]) == 4 and all(len(t) <= 2 for t in lp["top_logprobs"])
+    assert all(v <= 0.0 for v in lp["token_logprobs"])
+    code, text = _call(app, "POST", "/v1/chat/completions", {"model": "toy", "messages": [{"role": "user", "content": "hi"}],
+                                                             "max_tokens": 3, "logprobs": True, "top_logprobs": 3})
+    assert code == 200, text
+    content = json.loads(text)["choices"][0]["logprobs"]["content"]
+    assert len(content) == 3 and all(len(c["top_logprobs"]) == 3 for c in content)
+    # greedy decoding: the sampled token is the most likely one
+    assert all(c["logprob"] == max(t["logprob"] for t in c["top_logprobs"]) for c in content)
+    code, text = _call(app, "POST", "/v1/completions", {"model": "toy", "prompt": "hello", "max_tokens": 2})
+    assert json.loads(text)["choices"][0]["logprobs"] is None
+
+
+def test_chat_with_tools_and_reasoning_parsers():
+    """A server started with parsers: a request with ``tools`` is rendered with the function list and answered with the
+    parsed message (the toy model writes no markup, so the answer stays content); ``tool_choice`` needs a parser."""
+    pytest.importorskip("httpx")
+    cfg = ModelConfig(architecture="LlamaForCausalLM", vocab_size=256, hidden_size=64, intermediate_size=128,
+                      num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                      max_position_embeddings=256, dtype=torch.float32)
+    llm = LLM(cfg, device="cpu", load_format="dummy", num_gpu_blocks=64, block_size=16, max_model_len=256,
+              tokenizer=ToyTokenizer(), seed=0)
+    allm = AsyncLLM(llm)
+    try:
+        app = build_app(allm, "toy", tool_call_parser="hermes", reasoning_parser="deepseek_r1")
+        tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {"type": "object", "properties": {}}}}]
+        body = {"model": "toy", "messages": [{"role": "user", "content": "weather?"}], "max_tokens": 4, "tools": tools}
+        code, text = _call(app, "POST", "/v1/chat/completions", body)
+        assert code == 200, text
+        msg = json.loads(text)["choices"][0]["message"]
+        assert msg["role"] == "assistant" and "tool_calls" not in msg and msg["content"]
+        code, text = _call(app, "POST", "/v1/chat/completions", dict(body, stream=True))
+        assert code == 200 and text.count("data: ") == 2 and "[DONE]" in text     # one parsed chunk + the terminator
+        plain = build_app(allm, "toy")
+        code, text = _call(plain, "POST", "/v1/chat/completions", dict(body, tool_choice="required"))
+        assert code == 400 and "tool-call-parser" in text
+        code, text = _call(plain, "POST", "/v1/chat/completions", dict(body, tool_choice={"type": "function", "function": {"name": "nope"}}))
+        assert code == 400 and "unknown function" in text
+    finally:
+        allm.shutdown()

@@ -887,7 +887,7 @@ def top_k_per_row(logits, k: int, row_len=None):
 
 
 def indexer_topk(q_fp8, weights, idx_cache, block_table, seq_lens, query_start_loc, topk: int, block_size: int,
-                 max_seq_len: int = 0, return_logits: bool = False):
+                 max_seq_len: int = 0, return_logits: bool = False, max_query_len: int = 0, impl: int = 0):
     """Index logits of every new token against its request's cached keys, then top-k.  ``q_fp8`` is e4m3, or int8
     (the V4 indexer: queries from ``ops.v4_cache.indexer_q_rope_int8_quant``, keys written with ``int8=True``).
     Returns int32 ``[T, topk]`` per-request positions (-1 = none)."""
@@ -903,7 +903,7 @@ def indexer_topk(q_fp8, weights, idx_cache, block_table, seq_lens, query_start_l
         else:
             qb = q_fp8 if (i8 or q_fp8.dtype == torch.float8_e4m3fn) else q_fp8.to(torch.float8_e4m3fn)
         torch.ops.b200.indexer_logits(logits, qb.contiguous(), weights.float().contiguous(), idx_cache, block_table,
-                                      seq_lens, query_start_loc, block_size, L, i8)
+                                      seq_lens, query_start_loc, block_size, L, i8, int(max_query_len), int(impl))
         _ = _use_cuda(q_fp8)  # second kernel of the op (launch accounting)
         out = torch.empty(T, topk, dtype=torch.int32, device=q_fp8.device)
         torch.ops.b200.topk_per_row(out, logits, None, Lp)

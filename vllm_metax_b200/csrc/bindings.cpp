@@ -628,13 +628,24 @@ void mla_decode(Tensor& out, const Tensor& q, const Tensor& cache, const Tensor&
 // ------------------------------------------------------------------ DSA indexer
 void indexer_logits(Tensor& logits, const Tensor& q, const Tensor& w, const Tensor& cache, const Tensor& block_table,
                     const Tensor& seq_lens, const Tensor& query_start_loc, int64_t block_size, int64_t max_len,
-                    bool int8) {
+                    bool int8, int64_t max_query_len, int64_t impl) {
+  // impl: 0 = tcgen05 kernel when it serves the shapes (8-bit operands, heads a multiple of 32), 1 = mma.sync kernel,
+  // 2 = tcgen05 kernel or an error
   const bool bf16 = q.scalar_type() == at::kBFloat16;      // unquantised indexer: bf16 queries, bf16 key cache
   TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.is_contiguous() && (q.element_size() == 1 || bf16));
   TORCH_CHECK(q.size(1) % 16 == 0 && q.size(1) <= 64 && w.is_contiguous() && w.scalar_type() == at::kFloat);
   TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.stride(1) == 1 && logits.size(1) >= max_len);
   TORCH_CHECK(cache.is_contiguous() && cache.scalar_type() == at::kByte);
   const c10::cuda::CUDAGuard guard(q.device());
+  if (impl != 1 && !bf16) {
+    const int rc = b200::indexer_logits_tc(logits.data_ptr<float>(), logits.stride(0), q.data_ptr(), w.data_ptr<float>(),
+                                           cache.data_ptr(), block_table.data_ptr<int>(), block_table.size(1),
+                                           seq_lens.data_ptr<int>(), query_start_loc.data_ptr<int>(), q.size(0),
+                                           seq_lens.size(0), q.size(1), block_size, cache.size(0), max_len,
+                                           max_query_len, status_ptr(q), cur_stream(), int8 ? 1 : 0);
+    if (rc == 0) return;
+    TORCH_CHECK(impl != 2, "indexer_logits: shapes not served by the tcgen05 kernel");
+  }
   b200::indexer_logits(logits.data_ptr<float>(), logits.stride(0), q.data_ptr(), w.data_ptr<float>(), cache.data_ptr(),
                        block_table.data_ptr<int>(), block_table.size(1), seq_lens.data_ptr<int>(),
                        query_start_loc.data_ptr<int>(), q.size(0), seq_lens.size(0), q.size(1), block_size,
@@ -1380,7 +1391,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("scaled_mm(Tensor(a!) out, Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor? azp, Tensor? azp_adj, Tensor? bias, Tensor? block_expert, Tensor? total_padded) -> ()", &scaled_mm);
   m.def("wna16_gemm(Tensor(a!) out, Tensor a, Tensor q, Tensor scales, Tensor? zeros, int bits, int group, Tensor? bias, Tensor? block_expert, Tensor? total_padded, int token_tile, int epi) -> ()", &wna16_gemm);
   m.def("mla_decode(Tensor(a!) out, Tensor q, Tensor cache, Tensor block_table, Tensor seq_lens, Tensor? query_start_loc, Tensor? topk_indices, float scale, Tensor(b!)? lse_out, Tensor(c!)? workspace, int num_splits) -> ()", &mla_decode);
-  m.def("indexer_logits(Tensor(a!) logits, Tensor q, Tensor w, Tensor cache, Tensor block_table, Tensor seq_lens, Tensor query_start_loc, int block_size, int max_len, bool int8) -> ()", &indexer_logits);
+  m.def("indexer_logits(Tensor(a!) logits, Tensor q, Tensor w, Tensor cache, Tensor block_table, Tensor seq_lens, Tensor query_start_loc, int block_size, int max_len, bool int8, int max_query_len, int impl) -> ()", &indexer_logits);
   m.def("topk_per_row(Tensor(a!) out, Tensor x, Tensor? row_len, int cols) -> ()", &topk_per_row);
   m.def("symm_alloc(int nbytes, int device) -> (Tensor, Tensor)", &symm_alloc);
   m.def("symm_open(Tensor handle, int device) -> int", &symm_open);

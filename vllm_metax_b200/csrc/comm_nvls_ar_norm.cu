@@ -54,6 +54,43 @@ __device__ __forceinline__ void nvls_st_16(void* mc_addr, const uint4& v) {
                : "memory");
 }
 
+// arrive (once per rank: the GEMM that filled `partial` finished before this launch started) and wait for all ranks
+__device__ __forceinline__ bool nvls_open(const NvlsArNormParams& p, uint32_t want, int* s_ok) {
+  if (threadIdx.x == 0) {
+    if (blockIdx.x == 0) {
+      __threadfence_system();
+      multimem_red_add_u32(p.flag_mc + 0, 1u);
+    }
+    uint32_t seen = 0;
+    *s_ok = 1;
+    if (!wait_flag_ge(p.flag_local + 0, want, p.wait_cycles, &seen)) {
+      report_status(p.status, kWaitTimeout, 190, (int)want, (int)seen);
+      *s_ok = 0;
+    }
+  }
+  __syncthreads();
+  return *s_ok != 0;
+}
+
+// last CTA: "my rows are in everybody's output buffer, and I no longer read anybody's partial sums"
+__device__ __forceinline__ void nvls_close(const NvlsArNormParams& p, uint32_t call, uint32_t want, bool ok) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const uint32_t ticket = atomicAdd(&p.local_sync[0], 1u);
+    if (ticket == gridDim.x - 1) {
+      __threadfence_system();
+      multimem_red_add_u32(p.flag_mc + 1, 1u);
+      uint32_t seen = 0;
+      if (ok && !wait_flag_ge(p.flag_local + 1, want, p.wait_cycles, &seen))
+        report_status(p.status, kWaitTimeout, 191, (int)want, (int)seen);
+      p.local_sync[0] = 0;
+      p.local_sync[1] = call;
+    }
+  }
+}
+
+// Any H that is a multiple of 8: vectors of a row are taken 128 at a time.
 template <typename T>
 __global__ void __launch_bounds__(128)
 nvls_ar_norm_kernel(const NvlsArNormParams p) {
@@ -63,22 +100,7 @@ nvls_ar_norm_kernel(const NvlsArNormParams p) {
   const uint32_t want = call * (uint32_t)p.tp;
   const int my_rows = max(0, min(p.rows_per_rank, p.T - p.rank * p.rows_per_rank));
   const int nvec = p.H >> 3;
-
-  // arrive (once per rank: the GEMM that filled `partial` finished before this launch started) and wait
-  if (threadIdx.x == 0) {
-    if (blockIdx.x == 0) {
-      __threadfence_system();
-      multimem_red_add_u32(p.flag_mc + 0, 1u);
-    }
-    uint32_t seen = 0;
-    s_ok = 1;
-    if (!wait_flag_ge(p.flag_local + 0, want, p.wait_cycles, &seen)) {
-      report_status(p.status, kWaitTimeout, 190, (int)want, (int)seen);
-      s_ok = 0;
-    }
-  }
-  __syncthreads();
-  const bool ok = s_ok != 0;
+  const bool ok = nvls_open(p, want, &s_ok);
 
   for (int r = blockIdx.x; r < my_rows && ok; r += gridDim.x) {
     const size_t grow = (size_t)(p.rank * p.rows_per_rank + r) * p.H;       // element offset of the row
@@ -113,22 +135,63 @@ nvls_ar_norm_kernel(const NvlsArNormParams p) {
     }
     __syncthreads();                                  // `red` is reused by the next row
   }
+  nvls_close(p, call, want, ok);
+}
 
-  // close
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence_system();
-    const uint32_t ticket = atomicAdd(&p.local_sync[0], 1u);
-    if (ticket == gridDim.x - 1) {
-      __threadfence_system();
-      multimem_red_add_u32(p.flag_mc + 1, 1u);
-      uint32_t seen = 0;
-      if (ok && !wait_flag_ge(p.flag_local + 1, want, p.wait_cycles, &seen))
-        report_status(p.status, kWaitTimeout, 191, (int)want, (int)seen);
-      p.local_sync[0] = 0;
-      p.local_sync[1] = call;
+// H = 1024 * VPT: every switch round trip of the row (and the residual loads) is in flight before the first use, and
+// the row stays in registers between the two passes.
+template <typename T, int VPT>
+__global__ void __launch_bounds__(128)
+nvls_ar_norm_reg_kernel(const NvlsArNormParams p) {
+  __shared__ float red[32];
+  __shared__ int s_ok;
+  const uint32_t call = *reinterpret_cast<volatile uint32_t*>(p.local_sync + 1) + 1u;
+  const uint32_t want = call * (uint32_t)p.tp;
+  const int my_rows = max(0, min(p.rows_per_rank, p.T - p.rank * p.rows_per_rank));
+  const bool ok = nvls_open(p, want, &s_ok);
+
+  for (int r = blockIdx.x; r < my_rows && ok; r += gridDim.x) {
+    const size_t grow = (size_t)(p.rank * p.rows_per_rank + r) * p.H;
+    const uint4* part = reinterpret_cast<const uint4*>(static_cast<const T*>(p.partial_mc) + grow);
+    uint4* res = reinterpret_cast<uint4*>(static_cast<T*>(p.residual) + (size_t)r * p.H);
+    uint4 sum[VPT], rv[VPT], wv[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) sum[i] = multimem_ld_reduce_16<T>(part + threadIdx.x + i * 128);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      rv[i] = p.add_residual ? res[threadIdx.x + i * 128] : make_uint4(0, 0, 0, 0);
+      wv[i] = reinterpret_cast<const uint4*>(p.norm_weight)[threadIdx.x + i * 128];
+    }
+    float f[VPT][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      unpack8<T>(sum[i], f[i]);
+      if (p.add_residual) {
+        float g[8];
+        unpack8<T>(rv[i], g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[i][e] += g[e];
+      }
+      const uint4 packed = pack8<T>(f[i]);
+      res[threadIdx.x + i * 128] = packed;
+      unpack8<T>(packed, f[i]);                       // the norm sees the rounded residual
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += f[i][e] * f[i][e];
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)p.H + p.eps);
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(p.out_mc) + grow);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      float w[8];
+      unpack8<T>(wv[i], w);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[i][e] = f[i][e] * inv * w[e];
+      nvls_st_16(dst + threadIdx.x + i * 128, pack8<T>(f[i]));
     }
   }
+  nvls_close(p, call, want, ok);
 }
 
 // Returns 0, -1 (H not a multiple of 8), -2 (bad dtype).
@@ -137,9 +200,19 @@ int nvls_ar_norm(const NvlsArNormParams& p, int dtype, cudaStream_t stream) {
   if ((p.H & 7) != 0) return -1;
   int grid = p.rows_per_rank < 1 ? 1 : p.rows_per_rank;
   if (grid > 1184) grid = 1184;                       // 8 CTAs of 128 threads on each of 148 SMs
-  if (dtype == 0) nvls_ar_norm_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(p);
-  else if (dtype == 1) nvls_ar_norm_kernel<__half><<<grid, 128, 0, stream>>>(p);
+  const int vpt = p.H % 1024 == 0 ? p.H / 1024 : 0;
+#define B200_NVLS(T)                                                                      \
+  do {                                                                                    \
+    if (vpt == 1) nvls_ar_norm_reg_kernel<T, 1><<<grid, 128, 0, stream>>>(p);             \
+    else if (vpt == 2) nvls_ar_norm_reg_kernel<T, 2><<<grid, 128, 0, stream>>>(p);        \
+    else if (vpt == 4) nvls_ar_norm_reg_kernel<T, 4><<<grid, 128, 0, stream>>>(p);        \
+    else if (vpt == 8) nvls_ar_norm_reg_kernel<T, 8><<<grid, 128, 0, stream>>>(p);        \
+    else nvls_ar_norm_kernel<T><<<grid, 128, 0, stream>>>(p);                             \
+  } while (0)
+  if (dtype == 0) B200_NVLS(__nv_bfloat16);
+  else if (dtype == 1) B200_NVLS(__half);
   else return -2;
+#undef B200_NVLS
   return 0;
 }
 

@@ -287,6 +287,11 @@ void indexer_logits(float* logits, int64_t logits_stride, const void* q, const f
                     const int* block_table, int max_blocks, const int* seq_lens, const int* query_start_loc,
                     int tokens, int batch, int heads, int block_size, int64_t num_blocks, int max_len, void* status,
                     cudaStream_t stream, int kind = 0);   // kind 1: int8 queries and keys
+// ---- indexer_tcgen05.cu: returns -1 when the shapes are not served (caller falls back to indexer_logits)
+int indexer_logits_tc(float* logits, int64_t logits_stride, const void* q, const float* w, const void* cache,
+                      const int* block_table, int max_blocks, const int* seq_lens, const int* query_start_loc,
+                      int tokens, int batch, int heads, int block_size, int64_t num_blocks, int max_len,
+                      int max_query_len, void* status, cudaStream_t stream, int kind);
 void topk_per_row(int* out, const float* x, int64_t stride, const int* row_len, int rows, int cols, int k,
                   cudaStream_t stream);
 // ---- comm_gemm_ar_norm.cu (FusedArParams: comm_params.h)

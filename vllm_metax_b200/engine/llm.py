@@ -267,7 +267,9 @@ class LLMEngine:
         reason = {RequestStatus.FINISHED_STOPPED: "stop", RequestStatus.FINISHED_LENGTH: "length",
                   RequestStatus.FINISHED_ABORTED: "abort"}.get(r.status)
         return RequestOutput(r.request_id, r.prompt, r.prompt_token_ids,
-                             [CompletionOutput(0, list(r.output_token_ids), text, reason)], r.status.finished,
+                             [CompletionOutput(0, list(r.output_token_ids), text, reason,
+                                               list(r.logprobs) if r.params.logprobs is not None else None)],
+                             r.status.finished,
                              RequestMetrics(r.arrival_time, r.first_token_time, r.finish_time, list(r.token_times)),
                              r.num_cached_tokens)
 

@@ -546,13 +546,15 @@ class ModelRunner:
         md, T, rows, reqs = self._prepare(so, pad_to=bucket)
         all_greedy = all(r.params.greedy and not r.params.needs_penalties and not r.params.constrained for r in reqs)
         n = len(rows)
+        logits = None
         if bucket:
             g, logits, _ = self.graphs[bucket]
             g.replay()
+            logits = logits[:B]
             if all_greedy:
                 tokens_dev = self.sampled[:B]
             else:
-                tokens_dev = self._sample(logits[:B], reqs)
+                tokens_dev = self._sample(logits, reqs)
         else:
             h = self._forward(md, T)
             if getattr(self, "keep_hidden", False):
@@ -578,6 +580,8 @@ class ModelRunner:
         self.sampled_host[:n].copy_(tokens_dev[:n], non_blocking=False)
         self.d2h_bytes += n * 8
         toks = self.sampled_host[:n].tolist()
+        if logits is not None and any(r.params.logprobs is not None for r in reqs):
+            self._record_logprobs(logits, reqs, toks)
         out: dict = {}
         for r, tok in zip(reqs, toks):
             if r.request_id in out:                 # several verified positions of one request, in order
@@ -642,6 +646,28 @@ class ModelRunner:
             rows.extend([slot] * s.num_new_tokens)
         self.lora.set_batch(rows)
         return True
+
+    def _record_logprobs(self, logits: torch.Tensor, reqs, toks: list) -> None:
+        """Log-probability of every sampled token and of the ``logprobs`` most likely ones, appended to
+        ``request.logprobs`` as ``{"token_id", "logprob", "top": [(token_id, logprob), ...]}`` (one entry per sampled
+        position).  Taken from the raw logits: the distribution before temperature, top-k / top-p and penalties."""
+        seen: dict = {}
+        for r in reqs:
+            seen[r.request_id] = seen.get(r.request_id, 0) + 1
+        # a request with several sampled positions in one step is verifying drafts: not combined with logprobs
+        rows = [i for i, r in enumerate(reqs) if r.params.logprobs is not None and seen[r.request_id] == 1]
+        if not rows:
+            return
+        idx = torch.as_tensor(rows, dtype=torch.int64, device=logits.device)
+        lp = torch.log_softmax(logits.index_select(0, idx).float(), dim=-1)
+        k = max(1, min(max(int(reqs[i].params.logprobs or 0) for i in rows), lp.shape[1]))
+        top_v, top_i = lp.topk(k, dim=-1)
+        chosen = lp.gather(1, torch.as_tensor([toks[i] for i in rows], dtype=torch.int64, device=logits.device)[:, None])
+        top_v, top_i, chosen = top_v.cpu().tolist(), top_i.cpu().tolist(), chosen[:, 0].cpu().tolist()
+        for j, i in enumerate(rows):
+            n = int(reqs[i].params.logprobs or 0)
+            reqs[i].logprobs.append({"token_id": int(toks[i]), "logprob": float(chosen[j]),
+                                     "top": [(int(t), float(v)) for t, v in zip(top_i[j][:n], top_v[j][:n])]})
 
     def _sample(self, logits: torch.Tensor, reqs) -> torch.Tensor:
         from .sampler import sample_batch

@@ -133,13 +133,20 @@ class StaticWorkload:
             with set_forward_context(ctx):
                 return r.model(ids, positions).float().clone()
 
+        counts = []
+
         def both(ids, positions, md):
+            from .. import _custom_ops as ops
+
+            n0 = ops.launch_count()
             a = fwd(ids, positions, md)
+            n1 = ops.launch_count()
             inner.fused_ar, group.custom_allreduce = None, None
             try:
                 b = fwd(ids, positions, md)
             finally:
                 inner.fused_ar, group.custom_allreduce = saved
+            counts.append((n1 - n0, ops.launch_count() - n1))        # the two paths launch different kernel counts
             cos = 1.0 - float(torch.dot(a.flatten(), b.flatten()) / (a.norm() * b.norm() + 1e-12))
             return cos, float((a - b).abs().max()), float(b.abs().max())
 
@@ -155,7 +162,7 @@ class StaticWorkload:
                 "nvls_reduce_max_tokens": (saved[0].nvls_max_tokens if getattr(saved[0], "nvls", None) is not None else 0),
                 "prefill_tokens": int(ids.shape[0]), "cos_diff": round(max(p_cos, d_cos), 6),
                 "max_abs": round(max(p_abs, d_abs), 4), "ref_max_abs": round(max(p_ref, d_ref), 3),
-                "decode_cos_diff": round(d_cos, 6), "ok": bool(ok)}
+                "decode_cos_diff": round(d_cos, 6), "launches_fused_vs_plain": counts, "ok": bool(ok)}
 
     # ------------------------------------------------------------------ the timed body
     @torch.no_grad()

@@ -30,6 +30,7 @@ class StreamChunk:
     prompt_tokens: int = 0
     error: Optional[BaseException] = None
     ttft: Optional[float] = None
+    logprobs: Optional[list] = None          # entries of the tokens so far (requests with ``logprobs``)
 
 
 @dataclass
@@ -132,7 +133,8 @@ class AsyncLLM:
                     eng.tokenizer.decode(r.output_token_ids, skip_special_tokens=True) if eng.tokenizer else None)
                 self._post(st, StreamChunk(rid, new, list(r.output_token_ids), text, fin,
                                            out.outputs[0].finish_reason if out else None, len(r.prompt_token_ids),
-                                           ttft=None if st.t_first is None else st.t_first - st.t_arrival))
+                                           ttft=None if st.t_first is None else st.t_first - st.t_arrival,
+                                           logprobs=list(r.logprobs) if r.params.logprobs is not None else None))
                 if fin:
                     self.metrics["requests_finished"] += 1
                     self.histograms["e2e"].observe(now - st.t_arrival)

@@ -34,6 +34,10 @@ def sampling_from_request(body: dict, default_max_tokens: int = 16) -> SamplingP
         ignore_eos=bool(body.get("ignore_eos", False)),
         seed=body.get("seed"),
     )
+    lp = body.get("logprobs")
+    if lp is True or (isinstance(lp, int) and not isinstance(lp, bool) and lp >= 0 and lp is not False):
+        # chat: ``logprobs: true`` + ``top_logprobs: n``; completions: ``logprobs: n``
+        kw["logprobs"] = int(body.get("top_logprobs") or 0) if lp is True else int(lp)
     if stop:
         kw["stop"] = list(stop)
     if body.get("stop_token_ids"):
@@ -55,9 +59,14 @@ def sampling_from_request(body: dict, default_max_tokens: int = 16) -> SamplingP
     return SamplingParams(**kw)
 
 
-def render_chat(tokenizer, messages: list[dict], add_generation_prompt: bool = True) -> str:
+def render_chat(tokenizer, messages: list[dict], add_generation_prompt: bool = True, tools: Optional[list] = None) -> str:
     if tokenizer is not None and getattr(tokenizer, "chat_template", None):
-        return tokenizer.apply_chat_template(messages, tokenize=False, add_generation_prompt=add_generation_prompt)
+        kw = {"tools": tools} if tools else {}
+        return tokenizer.apply_chat_template(messages, tokenize=False, add_generation_prompt=add_generation_prompt, **kw)
+    if tools:      # no template: list the functions in a system turn, Hermes style
+        listing = "\n".join(json.dumps(t.get("function", t)) for t in tools)
+        messages = [{"role": "system", "content": "You may call these functions by answering "
+                     "<tool_call>{\"name\": ..., \"arguments\": {...}}</tool_call>:\n" + listing}] + list(messages)
     text = "".join(f"<|{m.get('role', 'user')}|>\n{m.get('content', '')}\n" for m in messages)
     return text + ("<|assistant|>\n" if add_generation_prompt else "")
 
@@ -90,9 +99,42 @@ def prometheus_text(allm: AsyncLLM) -> str:
     return "\n".join(lines) + "\n"
 
 
-def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_modules: Optional[dict] = None):
-    """``lora_modules``: adapter name -> ``LoRARequest``; a request whose ``model`` field names one runs with it."""
+def format_logprobs(entries: Optional[list], tokenizer, chat: bool, start: int = 0):
+    """``request.logprobs`` entries -> the OpenAI ``logprobs`` object of a choice (chat or completions flavour)."""
+    if entries is None:
+        return None
+
+    def name(tid: int) -> str:
+        if tokenizer is None:
+            return f"token_id:{tid}"
+        return tokenizer.decode([tid])
+
+    if chat:
+        content = []
+        for e in entries[start:]:
+            tok = name(e["token_id"])
+            content.append({"token": tok, "logprob": e["logprob"], "bytes": list(tok.encode("utf-8", "replace")),
+                            "top_logprobs": [{"token": name(t), "logprob": v, "bytes": list(name(t).encode("utf-8", "replace"))}
+                                             for t, v in e["top"]]})
+        return {"content": content}
+    toks = [name(e["token_id"]) for e in entries[start:]]
+    offsets, o = [], 0
+    for t in toks:
+        offsets.append(o)
+        o += len(t)
+    return {"tokens": toks, "token_logprobs": [e["logprob"] for e in entries[start:]],
+            "top_logprobs": [{name(t): v for t, v in e["top"]} for e in entries[start:]], "text_offset": offsets}
+
+
+def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_modules: Optional[dict] = None,
+              tool_call_parser: Optional[str] = None, reasoning_parser: Optional[str] = None):
+    """``lora_modules``: adapter name -> ``LoRARequest``; a request whose ``model`` field names one runs with it.
+    ``tool_call_parser`` / ``reasoning_parser``: names from ``entrypoints/parsers.py``; with them chat answers carry
+    ``message.tool_calls`` / ``message.reasoning_content``."""
+    from .parsers import get_reasoning_parser, get_tool_parser, parse_chat_output
+
     lora_modules = dict(lora_modules or {})
+    tool_parser, think_parser = get_tool_parser(tool_call_parser), get_reasoning_parser(reasoning_parser)
     from fastapi import FastAPI, Request
     from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
@@ -237,9 +279,22 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
     async def serve(body: dict, chat: bool, traceparent: Optional[str] = None):
         try:
             images = []
+            tools = body.get("tools") if chat else None
+            tool_choice = body.get("tool_choice", "auto" if tools else "none")
+            forced_tool = None
+            if tools and tool_choice == "none":
+                tools = None
+            if tools and isinstance(tool_choice, dict):          # {"type": "function", "function": {"name": ...}}
+                forced_tool = (tool_choice.get("function") or {}).get("name")
+                spec = next((t.get("function", t) for t in tools if t.get("function", t).get("name") == forced_tool), None)
+                if spec is None:
+                    return err(400, f"tool_choice names an unknown function {forced_tool!r}")
+                body = dict(body, guided_json=spec.get("parameters") or {"type": "object"})   # the answer IS the arguments
+            if tools and tool_parser is None and forced_tool is None and tool_choice != "auto":
+                return err(400, "tool_choice needs the server to be started with --tool-call-parser")
             if chat:
                 messages, images = split_images(body.get("messages") or [])
-                text = render_chat(tok, messages)
+                text = render_chat(tok, messages, tools=tools)
                 if images:
                     ids, prompt = encode_with_images(text, len(images)), text
                 else:
@@ -267,24 +322,56 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
             except EngineDeadError as e:
                 return err(500, str(e), "engine_dead")
             text = last.text if last.text is not None else ""
-            choice = ({"index": 0, "message": {"role": "assistant", "content": text}, "finish_reason": last.finish_reason}
-                      if chat else {"index": 0, "text": text, "token_ids": last.token_ids, "logprobs": None,
-                                    "finish_reason": last.finish_reason})
+            if chat:
+                msg = parse_chat_output(text, tool_parser, think_parser, bool(tools), forced_tool)
+                message = {"role": "assistant", "content": msg.content}
+                if msg.reasoning_content is not None:
+                    message["reasoning_content"] = msg.reasoning_content
+                finish = last.finish_reason
+                if msg.tool_calls:
+                    message["tool_calls"] = [c.to_openai() for c in msg.tool_calls]
+                    finish = "tool_calls" if forced_tool is None else finish
+                choice = {"index": 0, "message": message, "finish_reason": finish,
+                          "logprobs": format_logprobs(last.logprobs, tok, True)}
+            else:
+                choice = {"index": 0, "text": text, "token_ids": last.token_ids,
+                          "logprobs": format_logprobs(last.logprobs, tok, False), "finish_reason": last.finish_reason}
             return {"id": rid, "object": obj, "created": created, "model": served_model_name, "choices": [choice],
                     "usage": usage(len(ids), len(last.token_ids))}
+
+        # with a tool or reasoning parser the markup has to be complete before it can be split, so such a stream
+        # carries the parsed message in its last chunk; plain chats stream token by token
+        parse_at_end = chat and (forced_tool is not None or think_parser is not None
+                                 or (tool_parser is not None and bool(tools)))
 
         async def sse():
             prev = ""
             ntok = 0
+            sent_lp = 0
             try:
                 async for chunk in allm.generate(ids, params, rid, prompt, traceparent):
                     cur = chunk.text if chunk.text is not None else ""
                     delta, prev = cur[len(prev):] if cur.startswith(prev) else cur, cur
                     ntok = len(chunk.token_ids)
-                    if chat:
-                        ch = {"index": 0, "delta": {"content": delta}, "finish_reason": chunk.finish_reason}
+                    lp = format_logprobs(chunk.logprobs, tok, chat, sent_lp)
+                    sent_lp = len(chunk.logprobs) if chunk.logprobs is not None else 0
+                    if parse_at_end:
+                        if not chunk.finished:
+                            continue
+                        msg = parse_chat_output(cur, tool_parser, think_parser, bool(tools), forced_tool)
+                        d = {"role": "assistant", "content": msg.content}
+                        if msg.reasoning_content is not None:
+                            d["reasoning_content"] = msg.reasoning_content
+                        finish = chunk.finish_reason
+                        if msg.tool_calls:
+                            d["tool_calls"] = [c.to_openai(i) for i, c in enumerate(msg.tool_calls)]
+                            finish = "tool_calls" if forced_tool is None else finish
+                        ch = {"index": 0, "delta": d, "finish_reason": finish,
+                              "logprobs": format_logprobs(chunk.logprobs, tok, True)}
+                    elif chat:
+                        ch = {"index": 0, "delta": {"content": delta}, "finish_reason": chunk.finish_reason, "logprobs": lp}
                     else:
-                        ch = {"index": 0, "text": delta, "token_ids": chunk.new_token_ids,
+                        ch = {"index": 0, "text": delta, "token_ids": chunk.new_token_ids, "logprobs": lp,
                               "finish_reason": chunk.finish_reason}
                     yield "data: " + json.dumps({"id": rid, "object": obj + (".chunk" if chat else ""), "created": created,
                                                  "model": served_model_name, "choices": [ch]}) + "\n\n"

@@ -314,6 +314,30 @@ def bench_configs(t: Timer) -> dict:
         ms = t(lambda: ops.indexer_topk(qi, wts, idx_cache, bti, sli, qsli, 2048, bs, max_seq_len=Lk))
         res[f"indexer_logits_topk_T{T}_L{Lk}"] = {"ms": round(ms, 4),
                                                   "tflops": round(2 * T * 64 * Lk * 128 / ms / 1e9, 1)}
+        # the two halves on their own, and the mma.sync logits kernel the tcgen05 one replaces
+        lg = torch.empty(T, Lk, device=DEV, dtype=torch.float32)
+        for name, impl in (("tcgen05", 2), ("mma_sync", 1)):
+            ms = t(lambda: torch.ops.b200.indexer_logits(lg, qi, wts, idx_cache, bti, sli, qsli, bs, Lk, False, 0, impl))
+            res[f"indexer_logits_only_{name}_T{T}_L{Lk}"] = {"ms": round(ms, 4),
+                                                             "tflops": round(2 * T * 64 * Lk * 128 / ms / 1e9, 1)}
+        out_k = torch.empty(T, 2048, device=DEV, dtype=torch.int32)
+        ms = t(lambda: torch.ops.b200.topk_per_row(out_k, lg, None, Lk))
+        res[f"topk_per_row_2048_T{T}_L{Lk}"] = {"ms": round(ms, 4), "gbs": round(T * Lk * 4 / ms / 1e6, 1)}
+    # decode: 128 requests x 1 token over 32768 cached keys each
+    nb = 128 * (32768 // bs)
+    idx_cache = torch.randint(0, 100, (nb, bs * 132), device=DEV, dtype=torch.uint8)
+    idx_cache.view(nb, bs * 132)[:, bs * 128:] = torch.tensor([0, 0, 128, 60], device=DEV, dtype=torch.uint8).repeat(bs)
+    qi = (torch.randn(128, 64, 128, device=DEV) * 0.5).to(torch.float8_e4m3fn)
+    wts = torch.rand(128, 64, device=DEV)
+    bti = torch.arange(nb, device=DEV, dtype=torch.int32).view(128, -1)
+    sli = torch.full((128,), 32768, device=DEV, dtype=torch.int32)
+    qsli = torch.arange(129, device=DEV, dtype=torch.int32)
+    lg = torch.empty(128, 32768, device=DEV, dtype=torch.float32)
+    for name, impl in (("tcgen05", 2), ("mma_sync", 1)):
+        ms = t(lambda: torch.ops.b200.indexer_logits(lg, qi, wts, idx_cache, bti, sli, qsli, bs, 32768, False, 1, impl))
+        res[f"indexer_logits_decode_{name}_b128_L32768"] = {"ms": round(ms, 4),
+                                                            "key_gbs": round(128 * 32768 * 132 / ms / 1e6, 1)}
+    del idx_cache
     # ---- paged decode over an int8 cache: 32 sequences x 32768 tokens, 8 q / 1 kv head (TP 8) and 64 / 8
     for Hq, Hkv in ((8, 1), (64, 8)):
         res[f"attn_decode_int8kv_32x32768_h{Hq}"] = bench_decode(t, 32, 32768, Hq, Hkv, 128, 128, "int8")
@@ -401,7 +425,7 @@ def bench_linear_attention(t: Timer) -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "gemm", "prefill", "decode", "elementwise", "quant", "linear_attention", "skinny", "decode_layer", "configs"])
+    ap.add_argument("--op", default="all", choices=["all", "gemm", "prefill", "decode", "elementwise", "quant", "linear_attention", "skinny", "decode_layer", "configs", "indexer"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
@@ -438,6 +462,19 @@ def main() -> None:
         res.update(bench_skinny(t))
     if a.op == "configs":
         res.update(bench_configs(t))
+    if a.op == "indexer":        # --m query tokens of one request against --n cached keys (fp8, 64 heads): logits only
+        T, Lk, bs = a.m, a.n, 64
+        nb = Lk // bs
+        idx_cache = torch.randint(0, 100, (nb, bs * 132), device=DEV, dtype=torch.uint8)
+        idx_cache.view(nb, bs * 132)[:, bs * 128:] = torch.tensor([0, 0, 128, 60], device=DEV, dtype=torch.uint8).repeat(bs)
+        qi = (torch.randn(T, 64, 128, device=DEV) * 0.5).to(torch.float8_e4m3fn)
+        wts = torch.rand(T, 64, device=DEV)
+        bti = torch.arange(nb, device=DEV, dtype=torch.int32).view(1, nb)
+        sli = torch.tensor([Lk], device=DEV, dtype=torch.int32)
+        qsli = torch.tensor([0, T], device=DEV, dtype=torch.int32)
+        lg = torch.empty(T, Lk, device=DEV, dtype=torch.float32)
+        ms = t(lambda: torch.ops.b200.indexer_logits(lg, qi, wts, idx_cache, bti, sli, qsli, bs, Lk, False, 0, 2))
+        res[f"indexer_logits_tcgen05_T{T}_L{Lk}"] = {"ms": round(ms, 4), "tflops": round(2 * T * 64 * Lk * 128 / ms / 1e9, 1)}
     if a.op == "decode_layer":
         for tp in (1, 8):
             res[f"decode_layer_tp{tp}_b{a.batch}"] = bench_decode_layer(tp, a.batch, a.seq)
