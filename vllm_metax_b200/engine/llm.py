@@ -51,6 +51,11 @@ class LLMEngine:
 
         pp_size = ps_.get_pp_group().world_size
         self.pipeline_depth = pp_size if (pp_size > 1 and envs.B200_PP_OVERLAP) else 1
+        # data-parallel replicas of a MoE model share their experts (DP attention + EP): they step in lock-step
+        self._dp_group = ps_.get_dp_group()
+        self.dp_sync = self._dp_group.world_size > 1 and cfg.model.is_moe
+        if self.dp_sync and pp_size > 1:
+            raise ValueError("data-parallel expert sharing is not combined with pipeline parallelism")
         self._inflight: collections.deque = collections.deque()
         if self.pipeline_depth > 1:
             self.scheduler.max_seqs_per_step = max(1, -(-cfg.scheduler.max_num_seqs // self.pipeline_depth))
@@ -156,6 +161,20 @@ class LLMEngine:
         if self.pipeline_depth > 1:
             return self._step_pipelined()
         so = self.scheduler.schedule()
+        if self.dp_sync:
+            # replicas whose experts span all of them step together: one without work runs a padding token through
+            # the model so that every rank joins the step's token exchanges
+            busy = self._dp_group.all_gather_object(not so.is_empty)
+            if not any(busy):
+                if self.scheduler.has_unfinished() and not self.scheduler.paused:
+                    raise RuntimeError("scheduler made no progress: KV cache too small for the waiting request")
+                return []
+            if so.is_empty:
+                if self.scheduler.has_unfinished() and not self.scheduler.paused:
+                    raise RuntimeError("scheduler made no progress: KV cache too small for the waiting request")
+                self.runner.execute_dummy()
+                self.stats["dp_padding_steps"] = self.stats.get("dp_padding_steps", 0) + 1
+                return []
         if so.is_empty:
             if self.scheduler.has_unfinished() and not self.scheduler.paused:
                 raise RuntimeError("scheduler made no progress: KV cache too small for the waiting request")
@@ -381,6 +400,13 @@ class LLM:
             order.append(rid)
             reqs[rid] = self.engine.requests[rid]
         done: dict[str, Request] = {}
+        if self.engine.dp_sync:
+            # keep stepping (padding steps once this replica is done) until every replica has finished its prompts
+            while any(self.engine._dp_group.all_gather_object(len(done) < n and self.engine.has_unfinished_requests())):
+                for r in self.engine.step():
+                    if r.request_id in reqs:
+                        done[r.request_id] = r
+            return [self.engine.make_output(reqs[rid]) for rid in order]
         while len(done) < n:
             for r in self.engine.step():
                 if r.request_id in reqs:

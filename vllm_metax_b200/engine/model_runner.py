@@ -63,6 +63,7 @@ class ModelRunner:
         self.block_size = cfg.cache.block_size
         sc = cfg.scheduler
         self.max_tokens = max(sc.max_num_batched_tokens, sc.max_num_seqs)
+        ps.set_max_tokens_per_step(self.max_tokens)
         self.max_seqs = sc.max_num_seqs
         # decode context parallel: a scheduler block of block_size * dcp tokens is block_size slots on every rank of the
         # DCP group (token p lives on rank p % dcp, at local index p // dcp)
@@ -593,6 +594,25 @@ class ModelRunner:
             if s.num_spec and s.samples and not isinstance(out.get(s.request.request_id), list):
                 out[s.request.request_id] = [out[s.request.request_id]]
         return out
+
+    @torch.no_grad()
+    def execute_dummy(self) -> None:
+        """One forward pass over a single padding token that writes no KV and samples nothing: a replica without work
+        still has to take part in the expert-parallel exchanges of the step the other replicas run."""
+        self.input_ids[:1].zero_()
+        self.positions[:1].zero_()
+        self.slot_mapping[:1].fill_(-1)
+        self.seq_lens[:1].fill_(1)
+        self.query_start_loc[:2].copy_(torch.tensor([0, 1], dtype=torch.int32))
+        self.block_table[:1].zero_()
+        self.prefill_qsl[:1].zero_()
+        md = AttentionMetadata(
+            num_tokens=1, num_reqs=1, num_decodes=1, num_decode_tokens=1, query_start_loc=self.query_start_loc[:2],
+            seq_lens=self.seq_lens[:1], block_table=self.block_table[:1], slot_mapping=self.slot_mapping[:1],
+            max_query_len=1, max_seq_len=1, block_size=self.block_size, prefill_query_start_loc=self.prefill_qsl[:1],
+            max_prefill_query_len=0)
+        md.extra["prefill_no_context"] = True
+        self._forward(md, 1)
 
     # ------------------------------------------------------------------ pipelined steps
     @torch.no_grad()

@@ -13,13 +13,22 @@ Data flow on one rank (bf16):
 Weights: ``w13 [E_local, 2I, H]`` with gate/up rows interleaved (row 2j = gate_j, 2j+1 = up_j),
 ``w2 [E_local, H, I]``.
 
-Expert parallelism: experts are sharded over the EP group (``E_local = E / ep``).  Tokens are
-replicated across the TP/EP ranks in this engine (SPMD, attention is tensor-parallel), so
-"dispatch" is a local filter - every rank gathers the pairs routed to ITS experts
-(``expert_map``) - and "combine" is a sum over ranks of the partial outputs, which is exactly the
-row-parallel reduction and is therefore fused with the residual add + RMSNorm in
-``parallel/fused_collectives.py`` (or falls back to an NCCL all-reduce).  Data-parallel
-attention (tokens differ per rank) goes through ``parallel/all2all.py``.
+Expert parallelism: experts are sharded over the EP group (``E_local = E / ep``).
+
+* One replica (``data_parallel_size == 1``): EP group = TP group.  Tokens are replicated across its ranks (SPMD,
+  attention is tensor-parallel), so by default "dispatch" is a local filter - every rank gathers the pairs routed
+  to ITS experts (``expert_map``) - and "combine" is a sum over ranks of the partial outputs, which is exactly the
+  row-parallel reduction (fused with the residual add + RMSNorm in ``parallel/fused_collectives.py``, or an
+  all-reduce).  With ``B200_MOE_A2A=1`` the layer instead runs sequence-parallel: every rank routes 1 / tp of the
+  tokens and the rows travel once over the NVLink dispatch / combine kernels.
+* Several replicas (``data_parallel_size > 1``, "DP attention + EP"): EP group = all dp x tp ranks.  Every replica
+  has its own tokens; each of its TP ranks routes a slice of them, the slices are exchanged over the EP group
+  (``parallel/all2all.py``: NVLink kernels, or all-gather / reduce-scatter on any backend), every rank runs its
+  experts on what it received, and the results travel back.  The engines of the replicas step in lock-step
+  (``engine/llm.py``) so that every rank takes part in every exchange.
+
+``forward_reduced`` picks the path and returns the complete output; ``forward`` is the local-filter path (partial
+sums when experts live on several ranks).
 
 Parity: vllm_metax/model_executor/layers/fused_moe/fused_moe.py:1960-2436 (fused_experts),
 experts/triton_moe.py:221-620, all2all_utils.py:34-126.
@@ -69,9 +78,11 @@ class FusedMoE(nn.Module):
         self.routed_scaling_factor = routed_scaling_factor
         self.reduce_results = reduce_results
         self.prefix = prefix
-        # experts are sharded over the TP group's ranks (TP == EP in this engine)
-        self.ep = ps.tp_size()
-        self.ep_rank = ps.tp_rank()
+        # experts are sharded over the EP group: the TP group of a single replica, all dp x tp ranks otherwise
+        self.dp = ps.get_dp_group().world_size
+        self.ep_group = ps.get_ep_group() if self.dp > 1 else ps.get_tp_group()
+        self.ep = self.ep_group.world_size
+        self.ep_rank = self.ep_group.rank_in_group
         assert num_experts % self.ep == 0, "number of experts must divide over the EP ranks"
         self.num_local = num_experts // self.ep
         self.quant_method = quant_method
@@ -134,51 +145,92 @@ class FusedMoE(nn.Module):
         return ops.topk_gating(router_logits, self.top_k, self.renormalize, self.scoring_func, bias,
                                self.routed_scaling_factor)
 
-    def _forward_a2a(self, x: torch.Tensor, router_logits: torch.Tensor,
-                     shared_out: Optional[torch.Tensor]) -> torch.Tensor:
-        """Sequence-parallel MoE over the NVLink dispatch / combine kernels: every rank routes its own 1/ep of the
-        tokens, rows travel once to the ranks that own their experts, partial sums come back, and the finished rows
-        are all-gathered - instead of every rank running its experts on all tokens and all-reducing ``[T, H]``
-        (the reference's sequence-parallel MoE region, models/deepseek_v2.py:1286-1316, with its all2all managers)."""
-        from ..parallel.all2all import NvlinkAll2AllManager, run_experts_a2a
-
-        g = ps.get_tp_group()
-        T, H = x.shape
-        per = (T + self.ep - 1) // self.ep
-        sizes = [max(0, min(per, T - r * per)) for r in range(self.ep)]
-        lo, n = self.ep_rank * per, sizes[self.ep_rank]
+    def _experts_sorted(self, a, a_scale, block_expert, total):
         qm = self.quant_method
-        wire_fp8 = bool(getattr(qm, "a2a_wire_fp8", False))
-        mgr = getattr(self, "_a2a", None)
-        if mgr is None or mgr.max_tokens < per:
-            if mgr is not None:
-                mgr.close()
-            cap = max(per, 64)
-            mgr = NvlinkAll2AllManager(g, cap, H, self.top_k, self.num_experts, x.dtype, x.device, quant_fp8=wire_fp8)
-            self._a2a = mgr
+        if qm is not None:
+            return qm.apply_sorted(self, a, a_scale, block_expert, total)
+        h = ops.gemm_grouped(a, self.w13_weight, block_expert, total, epi=1)
+        return ops.gemm_grouped(h, self.w2_weight, block_expert, total)
+
+    def _forward_sp(self, x: torch.Tensor, router_logits: torch.Tensor,
+                    shared_out: Optional[torch.Tensor]) -> torch.Tensor:
+        """Sequence-parallel MoE: every TP rank of a replica routes its own 1 / tp of the replica's tokens, rows travel
+        once to the EP ranks that own their experts, partial sums come back, and the finished rows are all-gathered
+        inside the replica - instead of every rank running its experts on all tokens and all-reducing ``[T, H]``.
+        With several replicas the exchange spans all of them (DP attention + EP).  The reference's sequence-parallel
+        MoE region (models/deepseek_v2.py:1273-1324) with its all2all managers
+        (distributed/device_communicators/all2all.py:20-218)."""
+        from ..parallel.all2all import AgRsAll2AllManager, NvlinkAll2AllManager, run_experts_a2a
+
+        tpg, epg = ps.get_tp_group(), self.ep_group
+        tp = tpg.world_size
+        T, H = x.shape
+        per = (T + tp - 1) // tp
+        sizes = [max(0, min(per, T - r * per)) for r in range(tp)]
+        lo, n = tpg.rank_in_group * per, sizes[tpg.rank_in_group]
         if n > 0:
             w, ids = self.route(router_logits[lo: lo + n])
         else:           # fewer tokens than ranks: this rank only serves its experts
             w = torch.empty(0, self.top_k, dtype=torch.float32, device=x.device)
             ids = torch.empty(0, self.top_k, dtype=torch.int32, device=x.device)
-
-        def experts(a, a_scale, block_expert, total):
+        mine_x = x[lo: lo + n].contiguous()
+        qm = self.quant_method
+        nvlink = (x.is_cuda and envs.B200_MOE_A2A and H % 128 == 0
+                  and (qm is None or hasattr(qm, "apply_sorted")))
+        if nvlink:
+            mgr = getattr(self, "_a2a", None)
+            # replicas step with different token counts: the receive slots are sized once, for the largest step
+            need = max(per, 64) if self.dp == 1 else max(64, -(-ps.max_tokens_per_step() // tp))
+            if mgr is None or mgr.max_tokens < need:
+                if mgr is not None:
+                    mgr.close()
+                mgr = NvlinkAll2AllManager(epg, need, H, self.top_k, self.num_experts, x.dtype, x.device,
+                                           quant_fp8=bool(getattr(qm, "a2a_wire_fp8", False)))
+                self._a2a = mgr
+            mine = run_experts_a2a(mgr, mine_x, w, ids, self._experts_sorted)
+        else:
+            mgr = getattr(self, "_agrs", None)
+            if mgr is None:
+                mgr = self._agrs = AgRsAll2AllManager(epg)
+            h_all, w_all, ids_all, _ = mgr.dispatch(mine_x, w, ids)
             if qm is not None:
-                return qm.apply_sorted(self, a, a_scale, block_expert, total)
-            h = ops.gemm_grouped(a, self.w13_weight, block_expert, total, epi=1)
-            return ops.gemm_grouped(h, self.w2_weight, block_expert, total)
-
-        mine = run_experts_a2a(mgr, x[lo: lo + n].contiguous(), w, ids, experts)
-        y = g.all_gatherv(mine, sizes)
+                part = qm.apply(self, h_all, w_all, ids_all.to(torch.int32), None)
+            else:
+                part = fused_experts(h_all, self.w13_weight, self.w2_weight, w_all, ids_all.to(torch.int32),
+                                     self.num_local, self.expert_map, None)
+            mine = mgr.combine(part)
+        y = tpg.all_gatherv(mine.contiguous(), sizes)
         if shared_out is not None:       # shared experts are tensor-parallel: their partial sums still need the reduction
-            y = y + (ps.tensor_model_parallel_all_reduce(shared_out) if self.reduce_results else shared_out)
+            y = y + ps.tensor_model_parallel_all_reduce(shared_out)
+        return y
+
+    def sequence_parallel(self, x: torch.Tensor) -> bool:
+        """Whether ``forward_reduced`` exchanges tokens (always with several replicas; opt-in inside one replica)."""
+        if self.ep == 1:
+            return False
+        if self.dp > 1:
+            return True
+        qm = self.quant_method
+        return bool(x.is_cuda and envs.B200_MOE_A2A and x.shape[1] % 128 == 0
+                    and (qm is None or hasattr(qm, "apply_sorted")))
+
+    def forward_reduced(self, x: torch.Tensor, router_logits: torch.Tensor,
+                        shared_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The complete MoE output on every rank of the replica, whichever path computes it."""
+        if self.sequence_parallel(x):
+            return self._forward_sp(x, router_logits, shared_out)
+        y = self.forward(x, router_logits, shared_out)
+        if ps.tp_size() > 1 and not (self.reduce_results and self.ep > 1):
+            y = ps.tensor_model_parallel_all_reduce(y)
         return y
 
     def forward(self, x: torch.Tensor, router_logits: torch.Tensor,
                 shared_out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        if (self.ep > 1 and (self.quant_method is None or hasattr(self.quant_method, "apply_sorted"))
-                and self.reduce_results and x.is_cuda and envs.B200_MOE_A2A and x.shape[1] % 128 == 0):
-            return self._forward_a2a(x, router_logits, shared_out)
+        """Local-filter path: this rank's experts on all of the replica's tokens (partial sums when ``ep > 1`` unless
+        ``reduce_results``).  Not usable with several replicas, whose tokens differ."""
+        assert self.dp == 1, "with data_parallel_size > 1 the experts need forward_reduced (tokens differ per replica)"
+        if self.reduce_results and self.sequence_parallel(x):
+            return self._forward_sp(x, router_logits, shared_out)
         w, ids = self.route(router_logits)
         if self.quant_method is not None:
             y = self.quant_method.apply(self, x, w, ids, shared_out)

@@ -57,10 +57,7 @@ class DeepseekV2MoE(nn.Module):
 
     def forward(self, x):
         shared = self.shared_experts(x) if self.shared_experts is not None else None
-        y = self.experts(x, self.gate(x).float(), shared)
-        if ps.tp_size() > 1:
-            y = ps.tensor_model_parallel_all_reduce(y)
-        return y
+        return self.experts.forward_reduced(x, self.gate(x).float(), shared)
 
 
 class Indexer(nn.Module):

@@ -93,7 +93,7 @@ class DeepseekV4MoE(nn.Module):
 
                 y = fused_experts(x, e.w13_weight, e.w2_weight, w, ids, e.num_local, e.expert_map, shared)
         else:
-            y = e(x, logits, shared)
+            return e.forward_reduced(x, logits, shared)
         if ps.tp_size() > 1:
             y = ps.tensor_model_parallel_all_reduce(y)
         return y

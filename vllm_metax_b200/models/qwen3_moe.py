@@ -47,13 +47,7 @@ class SparseMoeBlock(nn.Module):
         return y
 
     def forward(self, x):
-        shared = self._shared(x)
-        y = self.experts(x, self.gate(x), shared)
-        from ..parallel import state as ps
-
-        if ps.tp_size() > 1:
-            y = ps.tensor_model_parallel_all_reduce(y)
-        return y
+        return self.experts.forward_reduced(x, self.gate(x), self._shared(x))
 
     def partial(self, x):
         """Un-reduced output (for the fused reduce + norm path)."""

@@ -88,8 +88,11 @@ class Group:
         for r, s in enumerate(sizes):
             buf[r, :s] = x[off: off + s]
             off += s
+        if not x.is_cuda:  # Gloo has no reduce-scatter
+            dist.all_reduce(buf, group=self.cpu_pg)
+            return buf[self.rank_in_group, : sizes[self.rank_in_group]].contiguous()
         out = torch.empty((mx,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
-        dist.reduce_scatter_tensor(out, buf, group=self._pg(x))
+        dist.reduce_scatter_tensor(out, buf.view((self.world_size * mx,) + tuple(x.shape[1:])), group=self._pg(x))
         return out[: sizes[self.rank_in_group]]
 
     def broadcast(self, x: torch.Tensor, src: int = 0) -> torch.Tensor:
@@ -240,6 +243,20 @@ def destroy() -> None:
         dist.destroy_process_group()
     global _S
     _S.__init__()
+
+
+_MAX_TOKENS_PER_STEP = 8192
+
+
+def set_max_tokens_per_step(n: int) -> None:
+    """The scheduler's token budget of one step: collectively created buffers whose size must not depend on a
+    replica's current batch (the expert-parallel receive slots) are sized from it."""
+    global _MAX_TOKENS_PER_STEP
+    _MAX_TOKENS_PER_STEP = int(n)
+
+
+def max_tokens_per_step() -> int:
+    return _MAX_TOKENS_PER_STEP
 
 
 def get_tp_group() -> Group:
