@@ -65,3 +65,61 @@ def test_prefill_decode_split_and_failure_recovery(tmp_path):
     assert [o.num_cached_tokens for o in outs] == [48, 0, 0]
     assert again.engine.stats["kv_load_failures"] == 1 and again.engine.kv_connector.stats["load_failures"] == 1
     assert again.engine.kv.num_free_blocks == 64                       # nothing leaked on the failure path
+
+
+def test_network_connector_serves_blocks_over_tcp():
+    """Producer and consumer engines joined by the TCP connector (loopback): the consumer pulls the prompt blocks
+    from the producer's memory; a damaged blob and a vanished producer both end in recomputation, same tokens."""
+    from vllm_metax_b200 import LLM, SamplingParams
+    from vllm_metax_b200.kv_transfer.shared_storage import chain_hashes
+
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (100, 37, 16)]
+    sp = SamplingParams(max_tokens=8, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in LLM(tiny_cfg(), **KW).generate(prompts, sp)]
+
+    producer = LLM(tiny_cfg(), kv_transfer_config={"kv_connector": "NetworkKVConnector", "kv_role": "kv_producer",
+                                                   "kv_connector_extra_config": {"listen": "127.0.0.1:0"}}, **KW)
+    pc = producer.engine.kv_connector
+    producer.generate(prompts, SamplingParams(max_tokens=1, ignore_eos=True))
+    assert pc.stats["blocks_saved"] == 9 and pc.address.startswith("127.0.0.1:")
+
+    def consumer():
+        return LLM(tiny_cfg(), kv_transfer_config={"kv_connector": "NetworkKVConnector", "kv_role": "kv_consumer",
+                                                   "kv_connector_extra_config": {"peers": [pc.address], "timeout_s": 2}}, **KW)
+
+    c = consumer()
+    outs = c.generate(prompts, sp)
+    assert [o.outputs[0].token_ids for o in outs] == want
+    assert [o.num_cached_tokens for o in outs] == [96, 32, 0]
+    assert c.engine.kv_connector.stats["blocks_loaded"] == 8 and c.engine.kv_connector.stats["bytes_received"] > 0
+    c.engine.kv_connector.close()
+
+    # a blob damaged in the producer's store fails its checksum on the consumer: prefix kept, rest recomputed
+    h = chain_hashes(prompts[0], 16)[3]
+    blob = bytearray(pc.store.blobs[h])
+    blob[100:104] = b"\xff\xff\xff\xff"
+    pc.store.blobs[h] = bytes(blob)
+    c = consumer()
+    outs = c.generate(prompts, sp)
+    assert [o.outputs[0].token_ids for o in outs] == want
+    assert [o.num_cached_tokens for o in outs] == [48, 32, 0] and c.engine.stats["kv_load_failures"] == 1
+    c.engine.kv_connector.close()
+
+    # the producer goes away: lookups find nothing, everything is computed locally
+    pc.close()
+    c = consumer()
+    outs = c.generate(prompts, sp)
+    assert [o.outputs[0].token_ids for o in outs] == want and [o.num_cached_tokens for o in outs] == [0, 0, 0]
+
+
+def test_block_store_is_bounded_lru():
+    from vllm_metax_b200.kv_transfer.network import BlockStore
+
+    st = BlockStore(max_bytes=250)
+    for i in range(4):
+        st.put(f"h{i}", bytes(100))
+    assert not st.has("h0") and not st.has("h1") and st.has("h2") and st.has("h3") and st.size == 200
+    st.get("h2")
+    st.put("h4", bytes(100))
+    assert st.has("h2") and not st.has("h3")
