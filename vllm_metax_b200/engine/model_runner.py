@@ -167,6 +167,7 @@ class ModelRunner:
         self.d64 = torch.zeros(self.n64, dtype=torch.int64, device=dev)
         self.d32 = torch.zeros(self.n32, dtype=torch.int32, device=dev)
         self.h64_np, self.h32_np = self.h64.numpy(), self.h32.numpy()
+        self._bt_owner: list = [None] * B
         self.input_ids = self.d64[:T]
         self.positions = self.d64[T:2 * T]
         self.slot_mapping = self.d64[2 * T:3 * T]
@@ -332,6 +333,7 @@ class ModelRunner:
         pqsl = self.h32_np[o:o + B_ + 1]
         bs = self.block_size
         d, dr, vbs = self.dcp, self.dcp_rank, self.virt_bs
+        owners = self._bt_owner          # per staging row: (request, blocks already written), None = unknown
         ctx_local = []
         vis_local, tok_req = [], []
         t = 0
@@ -339,7 +341,37 @@ class ModelRunner:
         max_q = max_seq = 0
         sample_rows = []
         sample_reqs = []
+        # decode rows first (the scheduler's order): one token each, filled as whole arrays
+        nd_fast = 0
+        if d == 1 and so.num_decode and so.scheduled[so.num_decode - 1].num_new_tokens == 1 and all(
+                s.num_spec == 0 for s in so.scheduled[: so.num_decode]):
+            nd_fast = so.num_decode
+            dec = so.scheduled[:nd_fast]
+            p0s = [s.start_pos for s in dec]
+            ids[:nd_fast] = [s.request.token_at(p) for s, p in zip(dec, p0s)]
+            pos[:nd_fast] = p0s
+            slots[:nd_fast] = [s.request.block_ids[p // bs] * bs + p % bs for s, p in zip(dec, p0s)]
+            qsl[1:nd_fast + 1] = np.arange(1, nd_fast + 1, dtype=np.int32)
+            sl[:nd_fast] = np.asarray(p0s, dtype=np.int32) + 1
+            max_q, max_seq = 1, max(p0s) + 1
+            for i, s in enumerate(dec):
+                r = s.request
+                nb = len(r.block_ids)
+                own = owners[i]
+                if own is not None and own[0] is r and own[1] <= nb:
+                    if own[1] < nb:
+                        bt[i, own[1]:nb] = r.block_ids[own[1]:]
+                        owners[i] = (r, nb)
+                else:
+                    bt[i, :nb] = r.block_ids
+                    owners[i] = (r, nb)
+                if s.samples:
+                    sample_rows.append(i)
+                    sample_reqs.append(r)
+            t = nd_fast
         for i, s in enumerate(so.scheduled):
+            if i < nd_fast:
+                continue
             r = s.request
             n, p0 = s.num_new_tokens, s.start_pos
             if d > 1:
@@ -371,7 +403,14 @@ class ModelRunner:
             qsl[i + 1] = t
             sl[i] = p0 + n if d == 1 else max(0, (p0 + n - dr + d - 1) // d)     # tokens in THIS rank's cache
             nb = len(r.block_ids)
-            bt[i, :nb] = r.block_ids
+            own = owners[i]
+            if own is not None and own[0] is r and own[1] <= nb:      # same request in this row: only its new blocks
+                if own[1] < nb:
+                    bt[i, own[1]:nb] = r.block_ids[own[1]:]
+                    owners[i] = (r, nb)
+            else:
+                bt[i, :nb] = r.block_ids
+                owners[i] = (r, nb)
             max_q = max(max_q, n)
             max_seq = max(max_seq, p0 + n)
             if s.samples:
@@ -387,6 +426,7 @@ class ModelRunner:
                 qsl[i + 1] = t
                 sl[i] = 1
                 bt[i, 0] = 0
+                owners[i] = None
             B_eff, nd_eff = pad_to, pad_to
         else:
             B_eff, nd_eff = B, nd

@@ -119,7 +119,8 @@ class Scheduler:
         # ---- running requests (decode, or the next chunk of a long prefill)
         cap = self.max_seqs_per_step
         for req in list(self.running):
-            if req not in self.running or budget <= 0 or len(out.scheduled) >= cap:
+            # (a request pre-empted earlier in this pass is no longer running)
+            if budget <= 0 or len(out.scheduled) >= cap or (out.preempted and req.status == RequestStatus.PREEMPTED):
                 continue
             if req.request_id in self.in_flight:
                 continue
@@ -131,13 +132,15 @@ class Scheduler:
             if not self.cfg.enable_chunked_prefill and n < remaining:
                 continue
             ok = True
-            while not self.kv.can_allocate(req, n):
+            need = self.kv.blocks_needed(req, n)
+            while need > self.kv.pool.num_free:
                 if not self._preempt_one(out, keep=req):
                     ok = False
                     break
             if not ok:
                 continue
-            self.kv.allocate(req, n)
+            if need:
+                req.block_ids.extend(self.kv.pool.allocate(need))
             out.scheduled.append(ScheduledRequest(req, n, req.num_computed_tokens, n == remaining + k, k))
             budget -= n
         # ---- admit waiting requests

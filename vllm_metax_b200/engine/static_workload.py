@@ -134,12 +134,15 @@ class StaticWorkload:
                 return r.model(ids, positions).float().clone()
 
         counts = []
+        fused_calls = []
 
         def both(ids, positions, md):
             from .. import _custom_ops as ops
 
             n0 = ops.launch_count()
+            c0 = getattr(saved[0], "calls", 0)
             a = fwd(ids, positions, md)
+            fused_calls.append(getattr(saved[0], "calls", 0) - c0)
             n1 = ops.launch_count()
             inner.fused_ar, group.custom_allreduce = None, None
             try:
@@ -162,7 +165,7 @@ class StaticWorkload:
                 "nvls_reduce_max_tokens": (saved[0].nvls_max_tokens if getattr(saved[0], "nvls", None) is not None else 0),
                 "prefill_tokens": int(ids.shape[0]), "cos_diff": round(max(p_cos, d_cos), 6),
                 "max_abs": round(max(p_abs, d_abs), 4), "ref_max_abs": round(max(p_ref, d_ref), 3),
-                "decode_cos_diff": round(d_cos, 6), "launches_fused_vs_plain": counts, "ok": bool(ok)}
+                "decode_cos_diff": round(d_cos, 6), "launches_fused_vs_plain": counts, "fused_calls": fused_calls, "ok": bool(ok)}
 
     # ------------------------------------------------------------------ the timed body
     @torch.no_grad()

@@ -148,6 +148,7 @@ class FusedRowParallelNorm:
         symmetric output buffer, valid until the next call)."""
         T = x.shape[0]
         rpr = rows_per_rank(T, self.tp)
+        self.calls = getattr(self, "calls", 0) + 1
         if self.cuda:
             assert T <= self.max_tokens
             if self.kernel == "mono":
