@@ -51,6 +51,8 @@ class LLMEngine:
 
         pp_size = ps_.get_pp_group().world_size
         self.pipeline_depth = pp_size if (pp_size > 1 and envs.B200_PP_OVERLAP) else 1
+        self.overlap_scheduling = bool(envs.B200_OVERLAP_SCHEDULING) and pp_size == 1
+        self._next = None                  # (scheduler output, prepared inputs) of the step prepared ahead of time
         # data-parallel replicas of a MoE model share their experts (DP attention + EP): they step in lock-step
         self._dp_group = ps_.get_dp_group()
         self.dp_sync = self._dp_group.world_size > 1 and cfg.model.is_moe
@@ -160,6 +162,9 @@ class LLMEngine:
             raise EngineDeadError(str(self.dead))
         if self.pipeline_depth > 1:
             return self._step_pipelined()
+        if self._overlap_ok():
+            return self._step_overlapped()
+        self._next = None
         so = self.scheduler.schedule()
         if self.dp_sync:
             # replicas whose experts span all of them step together: one without work runs a padding token through
@@ -203,6 +208,58 @@ class LLMEngine:
         self.stats["decode_tokens"] += so.num_decode
         self.stats["prefill_tokens"] += so.num_tokens - so.num_decode
         self.stats["preemptions"] = self.scheduler.num_preemptions
+        for r in finished:
+            self.requests.pop(r.request_id, None)
+        return finished
+
+    def _overlap_ok(self) -> bool:
+        """Host work of the next step may run while the device computes this one: plain steps only (no drafts to
+        verify, no adapters to route, no recurrent state slots, no replicas or stages to keep in step, no KV
+        hand-over)."""
+        r = self.runner
+        return (self.overlap_scheduling and not self.scheduler.paused and self.proposer is None and not self.dp_sync
+                and self.kv_connector is None and r.state_slots is None and r.lora is None and r.dcp == 1
+                and not self.step_hooks and not getattr(r, "keep_hidden", False))
+
+    def _step_overlapped(self) -> list[Request]:
+        """One step with the host work of the NEXT step (scheduling, staging buffers) done while the device runs this
+        one.  The scheduler advances in two phases around it (``Scheduler.begin_step`` / ``finish_step``); a request
+        that turns out to have finished stays in the prepared step as a row that writes and returns nothing."""
+        sch, runner = self.scheduler, self.runner
+        if self._next is not None:
+            so, prep = self._next
+            self._next = None
+        else:
+            so = sch.schedule()
+            if so.is_empty:
+                if sch.has_unfinished() and not sch.paused:
+                    raise RuntimeError("scheduler made no progress: KV cache too small for the waiting request")
+                return []
+            prep = runner.prepare_step(so)
+        try:
+            if self.liveness is not None:
+                self.liveness.check()
+            launched = runner.launch_step(prep)
+            sch.begin_step(so)
+            so2 = sch.schedule()
+            prep2 = None if so2.is_empty else runner.prepare_step(so2)
+            sampled = launched.result()
+        except BaseException as e:
+            self.dead = e
+            if self.liveness is not None:
+                self.liveness.announce_failure(repr(e))
+            self._next = None
+            self._release_all()
+            raise EngineDeadError(f"engine step failed: {e!r}") from e
+        finished = sch.finish_step(so, sampled, time.perf_counter())
+        self._next = None if prep2 is None else (so2, prep2)
+        if prep2 is not None and all(s.request.status.finished for s in so2.scheduled):
+            self._next = None              # everything in the prepared step has just finished: nothing to run
+        self.stats["steps"] += 1
+        self.stats["decode_tokens"] += so.num_decode
+        self.stats["prefill_tokens"] += so.num_tokens - so.num_decode
+        self.stats["preemptions"] = sch.num_preemptions
+        self.stats["overlapped_steps"] = self.stats.get("overlapped_steps", 0) + (1 if prep2 is not None else 0)
         for r in finished:
             self.requests.pop(r.request_id, None)
         return finished

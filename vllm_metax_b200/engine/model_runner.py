@@ -323,7 +323,10 @@ class ModelRunner:
             md.extra["mm_embeds"] = torch.cat(parts) if len(parts) > 1 else parts[0]
 
     # ------------------------------------------------------------------ input prep
-    def _prepare(self, so: SchedulerOutput, pad_to: int = 0):
+    def _prepare(self, so: SchedulerOutput, pad_to: int = 0, copy: bool = True):
+        """Fills the pinned staging areas for ``so`` and (``copy``) sends them to the device.  With ``copy=False`` the
+        transfer is left to ``_submit_inputs`` - the step is being prepared while the device still runs the previous
+        one, and token ids that are not known yet are written by ``_refill_tokens`` first."""
         T_, B_, MB = self.max_tokens, self.max_seqs, self.max_blocks_per_seq
         ids, pos, slots = self.h64_np[:T_], self.h64_np[T_:2 * T_], self.h64_np[2 * T_:3 * T_]
         o = 0
@@ -432,18 +435,9 @@ class ModelRunner:
             B_eff, nd_eff = B, nd
         pqsl[: B_eff - nd_eff + 1] = qsl[nd_eff:B_eff + 1] - qsl[nd_eff]
         T = t
-        # one H2D per staging area (only the used prefix of each segment)
-        if self.is_cuda:
-            for seg in range(3):
-                self.d64[seg * T_: seg * T_ + T].copy_(self.h64[seg * T_: seg * T_ + T], non_blocking=True)
-            n32 = (B_ + 1) + B_ + B_eff * MB
-            self.d32[:n32].copy_(self.h32[:n32], non_blocking=True)
-            o2 = (B_ + 1) + B_ + B_ * MB
-            self.d32[o2:o2 + B_eff + 1].copy_(self.h32[o2:o2 + B_eff + 1], non_blocking=True)
-            self.h2d_bytes += 3 * T * 8 + (n32 + B_eff + 1) * 4
-        else:
-            self.d64.copy_(self.h64)
-            self.d32.copy_(self.h32)
+        self._staged = (T, B_eff)
+        if copy:
+            self._submit_inputs()
         md = AttentionMetadata(
             num_tokens=T, num_reqs=B_eff, num_decodes=nd_eff, num_decode_tokens=nd_eff,
             query_start_loc=self.query_start_loc[:B_eff + 1], seq_lens=self.seq_lens[:B_eff],
@@ -466,6 +460,92 @@ class ModelRunner:
         if getattr(self.model, "is_multimodal", False):
             self._multimodal_rows(so, md)
         return md, T, sample_rows, sample_reqs
+
+    def _submit_inputs(self) -> None:
+        """One H2D per staging area (only the used prefix of each segment)."""
+        T, B_eff = self._staged
+        T_, B_, MB = self.max_tokens, self.max_seqs, self.max_blocks_per_seq
+        if self.is_cuda:
+            for seg in range(3):
+                self.d64[seg * T_: seg * T_ + T].copy_(self.h64[seg * T_: seg * T_ + T], non_blocking=True)
+            n32 = (B_ + 1) + B_ + B_eff * MB
+            self.d32[:n32].copy_(self.h32[:n32], non_blocking=True)
+            o2 = (B_ + 1) + B_ + B_ * MB
+            self.d32[o2:o2 + B_eff + 1].copy_(self.h32[o2:o2 + B_eff + 1], non_blocking=True)
+            self.h2d_bytes += 3 * T * 8 + (n32 + B_eff + 1) * 4
+        else:
+            self.d64.copy_(self.h64)
+            self.d32.copy_(self.h32)
+
+    def _refill_tokens(self, so: SchedulerOutput) -> None:
+        """A step prepared ahead of time held provisional tokens: write the real ids of every row, and switch off the
+        cache writes of rows whose request has finished in the meantime (their results are dropped)."""
+        T_ = self.max_tokens
+        ids, slots = self.h64_np[:T_], self.h64_np[2 * T_:3 * T_]
+        t = 0
+        for s in so.scheduled:
+            r, n, p0 = s.request, s.num_new_tokens, s.start_pos
+            if r.status.finished:
+                s.zombie = True
+                slots[t:t + n] = -1
+                self.zombie_rows = getattr(self, "zombie_rows", 0) + 1
+            elif n == 1:
+                ids[t] = r.token_at(p0)
+            else:
+                ids[t:t + n] = r.all_token_ids[p0:p0 + n] if r.output_token_ids else r.prompt_token_ids[p0:p0 + n]
+            t += n
+
+    # ------------------------------------------------------------------ a step in two halves (overlapped host work)
+    def prepare_step(self, so: SchedulerOutput) -> dict:
+        """Host half of a step: batch shape, staging buffers, metadata.  Nothing is sent to the device."""
+        B = len(so.scheduled)
+        bucket = 0
+        if self.use_graphs and so.num_decode == B and B > 0 and self.graphs:
+            bucket = next((b for b in self.buckets if b >= B), 0)
+        if self.is_cuda and self._prep_done is not None:
+            self._prep_done.synchronize()          # the previous step's H2D copies have read the staging areas
+        md, T, rows, reqs = self._prepare(so, pad_to=bucket, copy=False)
+        return {"so": so, "md": md, "T": T, "rows": rows, "reqs": reqs, "bucket": bucket, "staged": self._staged}
+
+    @torch.no_grad()
+    def launch_step(self, prep: dict) -> "LaunchedStep":
+        """Device half: inputs, forward (graph replay for decode buckets), sampling, and the start of the token
+        read-back.  Returns without waiting for the device."""
+        so, md, T, rows, reqs, bucket = (prep[k] for k in ("so", "md", "T", "rows", "reqs", "bucket"))
+        self._refill_tokens(so)
+        self._staged = prep["staged"]
+        self._submit_inputs()
+        if self.is_cuda:
+            self._prep_done = torch.cuda.Event()
+            self._prep_done.record()
+        B, n = len(so.scheduled), len(rows)
+        all_greedy = all(r.params.greedy and not r.params.needs_penalties and not r.params.constrained for r in reqs)
+        logits = None
+        if bucket:
+            g, logits, _ = self.graphs[bucket]
+            g.replay()
+            logits = logits[:B]
+            tokens_dev = self.sampled[:B] if all_greedy else self._sample(logits, reqs)
+        else:
+            h = self._forward(md, T)
+            if n == 0:
+                return LaunchedStep(self, reqs, 0, None, None)
+            if n == T:
+                hs = h
+            else:
+                self.sample_idx_host[:n] = torch.as_tensor(rows)
+                self.sample_idx[:n].copy_(self.sample_idx_host[:n], non_blocking=True)
+                hs = h.index_select(0, self.sample_idx[:n])
+            logits = self.model.compute_logits(hs)
+            tokens_dev = ops.argmax(logits, self.sampled[:n]) if all_greedy else self._sample(logits, reqs)
+        self.sampled_host[:n].copy_(tokens_dev[:n], non_blocking=True)
+        done = None
+        if self.is_cuda:
+            done = torch.cuda.Event()
+            done.record()
+        self.d2h_bytes += n * 8
+        want_lp = any(r.params.logprobs is not None for r in reqs)
+        return LaunchedStep(self, reqs, n, done, logits if want_lp else None)
 
     # ------------------------------------------------------------------ execution
     def _forward(self, md: AttentionMetadata, T: int):
@@ -715,7 +795,8 @@ class ModelRunner:
         for r in reqs:
             seen[r.request_id] = seen.get(r.request_id, 0) + 1
         # a request with several sampled positions in one step is verifying drafts: not combined with logprobs
-        rows = [i for i, r in enumerate(reqs) if r.params.logprobs is not None and seen[r.request_id] == 1]
+        rows = [i for i, r in enumerate(reqs) if r.params.logprobs is not None and seen[r.request_id] == 1
+                and not r.status.finished]          # (a finished request's row was prepared ahead: nothing to record)
         if not rows:
             return
         idx = torch.as_tensor(rows, dtype=torch.int64, device=logits.device)
@@ -771,3 +852,20 @@ class PendingStep:
             else:
                 out[r.request_id] = tok
         return out
+
+
+class LaunchedStep:
+    """A step whose device work has been queued; ``result()`` waits for its tokens: ``{request id: token}``."""
+
+    def __init__(self, runner: ModelRunner, reqs, n: int, done, logits):
+        self.runner, self.reqs, self.n, self.done, self.logits = runner, reqs, n, done, logits
+
+    def result(self) -> dict:
+        if self.n == 0:
+            return {}
+        if self.done is not None:
+            self.done.synchronize()
+        toks = self.runner.sampled_host[: self.n].tolist()
+        if self.logits is not None:
+            self.runner._record_logprobs(self.logits, self.reqs, toks)
+        return {r.request_id: tok for r, tok in zip(self.reqs, toks)}

@@ -74,13 +74,14 @@ class Request:
 
     __slots__ = ("request_id", "prompt_token_ids", "params", "output_token_ids", "status", "block_ids",
                  "num_computed_tokens", "arrival_time", "first_token_time", "finish_time", "token_times",
-                 "eos_token_id", "num_cached_tokens", "logprobs", "prompt", "_hashes", "spec_token_ids", "lora_request", "mm_embeds", "mm_positions", "mm_hash", "_sample_rng")
+                 "eos_token_id", "num_cached_tokens", "logprobs", "prompt", "_hashes", "spec_token_ids", "lora_request", "mm_embeds", "mm_positions", "mm_hash", "_sample_rng", "finishing")
 
     def __init__(self, request_id: str, prompt_token_ids: list[int], params: SamplingParams,
                  eos_token_id: Optional[int] = None, prompt: Optional[str] = None,
                  arrival_time: Optional[float] = None):
         self.request_id = request_id
         self._sample_rng = None
+        self.finishing = False                 # its last token (by length) is being computed: not scheduled again
         self.prompt_token_ids = list(prompt_token_ids)
         self.params = params
         self.output_token_ids: list[int] = []

@@ -28,6 +28,7 @@ class ScheduledRequest:
     start_pos: int                 # position of the first fed token
     samples: bool                  # whether logits of the last fed token are sampled
     num_spec: int = 0              # trailing draft tokens among the fed ones (their logits are verified)
+    zombie: bool = False           # the request finished after this step was prepared: the row computes nothing kept
 
     @property
     def is_decode(self) -> bool:
@@ -122,7 +123,7 @@ class Scheduler:
             # (a request pre-empted earlier in this pass is no longer running)
             if budget <= 0 or len(out.scheduled) >= cap or (out.preempted and req.status == RequestStatus.PREEMPTED):
                 continue
-            if req.request_id in self.in_flight:
+            if req.request_id in self.in_flight or req.finishing:
                 continue
             remaining = req.num_tokens - req.num_computed_tokens
             k = len(req.spec_token_ids) if remaining == 1 and req.output_token_ids else 0
@@ -147,6 +148,8 @@ class Scheduler:
         while (self.waiting and budget > 0 and len(self.running) < self.cfg.max_num_seqs and not out.preempted
                and len(out.scheduled) < cap):
             req = self.waiting[0]
+            if req.finishing:          # pre-empted while its last token was in flight: nothing left to compute
+                break
             self.kv.try_prefix_hit(req)
             if self.external_kv is not None and not req.output_token_ids:
                 self.external_kv(req)              # KV published by another engine (disaggregated prefill)
@@ -174,6 +177,55 @@ class Scheduler:
         out.scheduled = dec + pre
         out.num_decode = len(dec)
         return out
+
+    # ------------------------------------------------------------------ two-phase update (overlapped host work)
+    # The engine may prepare step k + 1 on the host while the device still runs step k.  ``begin_step`` applies what
+    # step k changes without knowing its tokens (computed-token counts, a provisional output token per sampling
+    # request so that the next ``schedule`` sees a decode request); ``finish_step`` puts the real tokens in, checks
+    # the stop conditions and retires finished requests.  A request that finishes at step k may already sit in the
+    # prepared step k + 1: the engine marks that row (``ScheduledRequest.zombie``) and both phases skip it.
+    PROVISIONAL = -1
+
+    def begin_step(self, out: SchedulerOutput) -> None:
+        for s in out.scheduled:
+            req = s.request
+            if s.zombie:
+                continue
+            assert s.num_spec == 0, "draft verification needs the tokens: not used with overlapped host work"
+            req.num_computed_tokens += s.num_new_tokens
+            self.kv.commit(req)
+            if s.samples:
+                req.output_token_ids.append(self.PROVISIONAL)
+                if len(req.output_token_ids) >= req.params.max_tokens:
+                    req.finishing = True
+
+    def finish_step(self, out: SchedulerOutput, sampled: dict, now: float) -> list[Request]:
+        finished = []
+        for s in out.scheduled:
+            req = s.request
+            if s.zombie or not s.samples:
+                continue
+            tok = sampled[req.request_id]
+            req.output_token_ids[-1] = int(tok[0]) if isinstance(tok, (list, tuple)) else int(tok)
+            req.token_times.append(now)
+            if req.first_token_time is None:
+                req.first_token_time = now
+            req.finishing = False
+            if req.status == RequestStatus.FINISHED_ABORTED:
+                continue
+            req.check_stop()
+            if req.status.finished:
+                req.finish_time = now
+                if req in self.running:
+                    self.running.remove(req)
+                else:                       # pre-empted during the overlap window
+                    try:
+                        self.waiting.remove(req)
+                    except ValueError:
+                        pass
+                self.kv.free(req)
+                finished.append(req)
+        return finished
 
     def mark_in_flight(self, out: SchedulerOutput) -> None:
         self.in_flight.update(s.request.request_id for s in out.scheduled)

@@ -50,6 +50,8 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # B200_FUSED_TP_MIN_TOKENS tokens; GEMM + peer-store all-reduce + add-norm below).
     "B200_FUSED_TP_KERNEL": _str("B200_FUSED_TP_KERNEL", "split"),
     "B200_FUSED_TP_MIN_TOKENS": _int("B200_FUSED_TP_MIN_TOKENS", 1024),
+    # Prepare step k + 1 on the host (schedule, staging buffers) while the device runs step k; 0 = strictly in turn.
+    "B200_OVERLAP_SCHEDULING": _flag("B200_OVERLAP_SCHEDULING", "1"),
     # Pipeline parallel: keep one step per stage in flight (disjoint request sets) instead of running lock-step.
     "B200_PP_OVERLAP": _flag("B200_PP_OVERLAP", "1"),
     # Stream-K CTA-pair GEMM for skinny problems (read by the native GEMM dispatcher; 0 = tile / split-K kernels).
