@@ -566,3 +566,31 @@ def test_dp2_attention_shared_experts_2gpu(a2a, tmp_path):
     del llm
     torch.cuda.empty_cache()
     _launch(_dp_ep_worker, 2, a2a, path, want, timeout=300)
+
+
+# ---- prefill context parallel: two full copies split every prefill chunk ------------------------------------------
+def _pcp_engine_worker(rank, world, path, want):
+    os.environ["B200_FUSED_TP_COLLECTIVES"] = "0"
+    from vllm_metax_b200 import LLM, SamplingParams
+    from vllm_metax_b200 import _custom_ops as ops
+
+    llm = LLM(path, device="cuda", dtype="bfloat16", prefill_context_parallel_size=world, block_size=64,
+              max_model_len=512, max_num_seqs=8, max_num_batched_tokens=128, num_gpu_blocks=64)
+    assert llm.engine.runner.pcp == world
+    outs = llm.generate(_tp_prompts(), SamplingParams(max_tokens=16, ignore_eos=True))
+    torch.cuda.synchronize()
+    ops.check_kernel_status(rank)
+    got = [list(o.outputs[0].token_ids) for o in outs]
+    # each copy multiplies other token counts than one GPU (other GEMM shapes, bf16): first tokens agree, the rest mostly
+    assert [g_[0] for g_ in got] == [w[0] for w in want], (got, want)
+    prefix = [next((i for i, (a, b) in enumerate(zip(g_, w)) if a != b), len(w)) for g_, w in zip(got, want)]
+    assert min(prefix) >= 2 and sum(prefix) >= 3 * len(want), (prefix, got, want)
+    llm.engine.runner.graphs.clear()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_pcp2_engine_close_to_single_gpu(tmp_path):
+    path = str(tmp_path / "ckpt")
+    _tp_checkpoint(path)
+    want = _tp_single_gpu_tokens(path)
+    _launch(_pcp_engine_worker, 2, path, want, timeout=240)

@@ -1,0 +1,86 @@
+"""Prefill context parallelism on CPU ranks (gloo): two full copies of the model (each optionally tensor-parallel)
+split the tokens of every prefill chunk, exchange K / V in the attention layers and keep identical caches; the last
+copy samples.  Tokens must equal the single-process run across chunked prefill, mixed steps and decode."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from tests.test_e2e_plumbing import tiny_cfg  # noqa: E402
+from tests.test_tp_cpu import export_hf_checkpoint  # noqa: E402
+
+
+def test_slices_and_gathered_slots():
+    from vllm_metax_b200.engine.sampling_params import Request, SamplingParams
+    from vllm_metax_b200.engine.scheduler import ScheduledRequest, SchedulerOutput
+    from vllm_metax_b200.parallel.pcp import gathered_slots, local_view, sampling_requests, slice_bounds
+
+    assert [slice_bounds(10, 4, r) for r in range(4)] == [(0, 3), (3, 6), (6, 8), (8, 10)]
+    a = Request("a", list(range(30)), SamplingParams(max_tokens=4), None)
+    b = Request("b", list(range(9)), SamplingParams(max_tokens=4), None)
+    b.output_token_ids = [5]
+    a.block_ids, b.block_ids = [3, 1], [2]
+    so = SchedulerOutput(scheduled=[ScheduledRequest(b, 1, 9, True), ScheduledRequest(a, 11, 10, False)], num_decode=1)
+    v0, v1 = local_view(so, 2, 0), local_view(so, 2, 1)
+    assert [(s.request.request_id, s.start_pos, s.num_new_tokens) for s in v0.scheduled] == [("b", 9, 1), ("a", 10, 6)]
+    assert [(s.request.request_id, s.start_pos, s.num_new_tokens) for s in v1.scheduled] == [("b", 9, 1), ("a", 16, 5)]
+    assert v0.num_decode == 1 and [r.request_id for r in sampling_requests(so, 2)] == ["b"]
+    slots, sizes = gathered_slots(so, 2, 0, 16)
+    assert sizes == [7, 6]
+    # copy 0: its own decode row is written, copy 1's duplicate of it is not; chunk rows of both copies are
+    assert slots.tolist() == [2 * 16 + 9] + [3 * 16 + p for p in range(10, 16)] + [-1] + [1 * 16 + p - 16 for p in range(16, 21)]
+
+
+def _worker(rank, world, tp, port, path, prompts, q):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), B200_FUSED_TP_COLLECTIVES="0")
+    try:
+        from vllm_metax_b200 import LLM, SamplingParams
+
+        llm = LLM(path, device="cpu", tensor_parallel_size=tp, prefill_context_parallel_size=world // tp, block_size=16,
+                  max_model_len=256, max_num_seqs=4, max_num_batched_tokens=32, num_gpu_blocks=64, dtype=torch.float32)
+        assert llm.engine.runner.pcp == world // tp
+        sps = [SamplingParams(max_tokens=8, ignore_eos=True), SamplingParams(max_tokens=5, ignore_eos=True),
+               SamplingParams(max_tokens=8, ignore_eos=True, temperature=0.8, top_p=0.9, seed=5),
+               SamplingParams(max_tokens=3, ignore_eos=True)]
+        outs = llm.generate(prompts, sps)
+        q.put((rank, [o.outputs[0].token_ids for o in outs]))
+    except BaseException as e:
+        q.put((rank, repr(e)))
+        raise
+
+
+@pytest.mark.parametrize("world,tp", [(2, 1), (4, 2)])
+def test_pcp_matches_single_process(tmp_path, world, tp):
+    from vllm_metax_b200 import LLM, SamplingParams
+
+    kw = dict(device="cpu", block_size=16, max_model_len=256, max_num_seqs=4, max_num_batched_tokens=32, num_gpu_blocks=64)
+    ref_llm = LLM(tiny_cfg(), **kw)
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (21, 77, 1, 40)]
+    sps = [SamplingParams(max_tokens=8, ignore_eos=True), SamplingParams(max_tokens=5, ignore_eos=True),
+           SamplingParams(max_tokens=8, ignore_eos=True, temperature=0.8, top_p=0.9, seed=5) if tp == 1
+           else SamplingParams(max_tokens=8, ignore_eos=True),
+           SamplingParams(max_tokens=3, ignore_eos=True)]
+    want = [o.outputs[0].token_ids for o in ref_llm.generate(prompts, sps)]
+    path = str(tmp_path / "ckpt")
+    export_hf_checkpoint(ref_llm.engine.runner.model, path)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29150 + (os.getpid() % 120) + world
+    procs = [ctx.Process(target=_worker, args=(r, world, tp, port, path, prompts, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for r in range(world):
+        if tp == 1:
+            assert got[r] == want, (r, got[r], want)
+        else:      # tensor-parallel sums differ in the last bits: the seeded request is greedy in this case
+            assert got[r][0] == want[0] and got[r][1] == want[1] and got[r][3] == want[3], (r, got[r], want)

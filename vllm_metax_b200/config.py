@@ -281,6 +281,7 @@ class ParallelConfig:
     data_parallel_size: int = 1
     enable_expert_parallel: bool = False
     decode_context_parallel_size: int = 1
+    prefill_context_parallel_size: int = 1
     use_sequence_parallel_moe: bool = False
     all2all_backend: str = "fused_nvlink"      # fused_nvlink | allgather_reducescatter | naive
 

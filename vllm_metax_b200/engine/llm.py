@@ -68,7 +68,8 @@ class LLMEngine:
         if self.proposer is not None:
             from ..parallel import state as ps
 
-            if ps.get_pp_group().world_size > 1 or self.runner.dcp > 1 or self.runner.state_slots is not None:
+            if (ps.get_pp_group().world_size > 1 or self.runner.dcp > 1 or self.runner.pcp > 1
+                    or self.runner.state_slots is not None):
                 raise ValueError("speculative decoding is not combined with pipeline parallel, decode context parallel "
                                  "or recurrent-state (hybrid) models")
         from ..parallel.liveness import RankLiveness
@@ -218,7 +219,7 @@ class LLMEngine:
         hand-over)."""
         r = self.runner
         return (self.overlap_scheduling and not self.scheduler.paused and self.proposer is None and not self.dp_sync
-                and self.kv_connector is None and r.state_slots is None and r.lora is None and r.dcp == 1
+                and self.kv_connector is None and r.state_slots is None and r.lora is None and r.dcp == 1 and r.pcp == 1
                 and not self.step_hooks and not getattr(r, "keep_hidden", False))
 
     def _step_overlapped(self) -> list[Request]:
@@ -393,7 +394,8 @@ class LLM:
                  load_format: str = "auto", seed: int = 0, tokenizer: Any = None, enable_sleep_mode: bool = False,
                  additional_config: Optional[dict] = None, speculative_config: Optional[dict] = None,
                  enable_lora: bool = False, max_loras: int = 4, max_lora_rank: int = 64,
-                 kv_transfer_config: Optional[dict] = None, decode_context_parallel_size: int = 1):
+                 kv_transfer_config: Optional[dict] = None, decode_context_parallel_size: int = 1,
+                 prefill_context_parallel_size: int = 1):
         overrides = {"seed": seed}
         if enable_lora:
             overrides.update(enable_lora=True, max_loras=max_loras, max_lora_rank=max_lora_rank)
@@ -410,7 +412,8 @@ class LLM:
                               gpu_memory_utilization=gpu_memory_utilization, kv_cache_dtype=kv_cache_dtype,
                               enable_prefix_caching=enable_prefix_caching),
             parallel=ParallelConfig(tensor_parallel_size, pipeline_parallel_size, data_parallel_size,
-                                    enable_expert_parallel, decode_context_parallel_size),
+                                    enable_expert_parallel, decode_context_parallel_size,
+                                    prefill_context_parallel_size),
             scheduler=SchedulerConfig(max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens,
                                       max_model_len=max_model_len, enable_chunked_prefill=enable_chunked_prefill),
             device=device, enforce_eager=enforce_eager, load_format=load_format,

@@ -43,7 +43,8 @@ class ModelRunner:
         self.cfg = cfg
         par = cfg.parallel
         ps.init_distributed(par.tensor_parallel_size, par.pipeline_parallel_size, par.data_parallel_size,
-                            par.decode_context_parallel_size, device=cfg.device)
+                            par.decode_context_parallel_size, device=cfg.device,
+                            prefill_context_parallel_size=par.prefill_context_parallel_size)
         if cfg.device == "cuda":
             self.device = torch.device("cuda", ps.local_rank() if torch.cuda.device_count() > 1 else 0)
             torch.cuda.set_device(self.device)
@@ -80,6 +81,10 @@ class ModelRunner:
                                  f"least dcp tensor-parallel ranks (kv heads {m.num_key_value_heads}, tp {ps.tp_size()}, "
                                  f"dcp {self.dcp}), or an MLA model")
         self.dcp_per_token = self.dcp > 1 and cfg.model.is_mla
+        # prefill context parallel: full model copies that split the tokens of every prefill chunk (parallel/pcp.py)
+        self.pcp = ps.get_pcp_group().world_size
+        if self.pcp > 1 and (cfg.model.is_mla or self.dcp > 1):
+            raise ValueError("prefill context parallelism serves GQA models with an unsplit cache")
         # pipeline parallel with overlapped steps: asynchronous stage-to-stage transfers and one token buffer per
         # step in flight
         import collections
@@ -657,7 +662,41 @@ class ModelRunner:
         ops.check_kernel_status(self.device.index or 0)
 
     @torch.no_grad()
+    def _execute_pcp_sliced(self, so: SchedulerOutput) -> dict:
+        """A step with prefill chunks under prefill context parallelism: this copy runs its slice of every chunk (and
+        the small rows whole), the attention layers exchange K / V, the last copy samples and broadcasts."""
+        from ..parallel import pcp as P
+
+        g = ps.get_pcp_group()
+        n_c, r = g.world_size, g.rank_in_group
+        view = P.local_view(so, n_c, r)
+        slots_all, sizes = P.gathered_slots(so, n_c, r, self.block_size)
+        reqs_last = P.sampling_requests(so, n_c)
+        self._route_lora(view)
+        md, T, rows, reqs = self._prepare(view)
+        md.extra["pcp_slots_all"] = torch.from_numpy(slots_all).to(self.device, non_blocking=True)
+        md.extra["pcp_sizes"] = sizes
+        h = self._forward(md, T)
+        n = len(reqs_last)
+        if n == 0:
+            return {}
+        if r == n_c - 1:
+            assert [q.request_id for q in reqs] == [q.request_id for q in reqs_last]
+            hs = h if n == T else h.index_select(0, torch.as_tensor(rows, dtype=torch.int64).to(self.device))
+            logits = self.model.compute_logits(hs)
+            greedy = all(q.params.greedy and not q.params.needs_penalties and not q.params.constrained for q in reqs)
+            tokens = ops.argmax(logits, self.sampled[:n]) if greedy else self._sample(logits, reqs)
+            if tokens.data_ptr() != self.sampled.data_ptr():
+                self.sampled[:n].copy_(tokens[:n])
+        g.broadcast(self.sampled[:n], src=n_c - 1)
+        self.sampled_host[:n].copy_(self.sampled[:n], non_blocking=False)
+        self.d2h_bytes += n * 8
+        return {q.request_id: tok for q, tok in zip(reqs_last, self.sampled_host[:n].tolist())}
+
+    @torch.no_grad()
     def execute(self, so: SchedulerOutput) -> dict[str, int]:
+        if self.pcp > 1 and any(s.num_new_tokens >= self.pcp for s in so.scheduled):
+            return self._execute_pcp_sliced(so)
         B = len(so.scheduled)
         pure_decode = so.num_decode == B and B > 0
         bucket = 0
@@ -698,6 +737,10 @@ class ModelRunner:
                     if tokens_dev.data_ptr() != self.sampled.data_ptr():
                         self.sampled[:n].copy_(tokens_dev[:n])
                     tokens_dev = pp.broadcast(self.sampled[:n], src=pp.world_size - 1)
+        if self.pcp > 1:        # the copies ran the same rows; the last copy's tokens are the step's
+            if tokens_dev.data_ptr() != self.sampled.data_ptr():
+                self.sampled[:n].copy_(tokens_dev[:n])
+            tokens_dev = ps.get_pcp_group().broadcast(self.sampled[:n], src=self.pcp - 1)
         self.sampled_host[:n].copy_(tokens_dev[:n], non_blocking=False)
         self.d2h_bytes += n * 8
         toks = self.sampled_host[:n].tolist()

@@ -84,7 +84,18 @@ class Attention(nn.Module):
             return self._forward_turboquant(q, k, v, positions, rope, md, kv_cache, kv_scales)
         if "dcp_ctx_lens" in md.extra:
             return self._forward_dcp(q, k, v, positions, rope, md, kv_cache, kv_scales)
-        if rope is not None:
+        pcp_slots = md.extra.get("pcp_slots_all")
+        if pcp_slots is not None:
+            # prefill context parallel: this copy computed a slice of every chunk; the copies exchange their K / V
+            # rows and each writes all of them into its own (replicated) cache - parallel/pcp.py
+            from ..parallel import state as ps
+
+            if rope is not None:
+                ops.rotary_embedding(positions, q, k, self.head_size, rope.cos_sin_cache, rope.is_neox)
+            g, sizes = ps.get_pcp_group(), md.extra["pcp_sizes"]
+            k_all, v_all = g.all_gatherv(k.contiguous(), sizes), g.all_gatherv(v.contiguous(), sizes)
+            ops.reshape_and_cache(k_all, v_all, kv_cache, pcp_slots, kv_scales, self.k_scale, self.v_scale)
+        elif rope is not None:
             ops.rope_and_cache(positions, q, k, v, self.head_size, rope.cos_sin_cache, rope.is_neox, kv_cache,
                                md.slot_mapping, kv_scales, self.k_scale, self.v_scale)
         else:

@@ -150,6 +150,7 @@ class _State:
     dp: Optional[Group] = None
     ep: Optional[Group] = None
     dcp: Optional[Group] = None
+    pcp: Optional[Group] = None
     world: Optional[Group] = None
     initialized: bool = False
 
@@ -172,15 +173,17 @@ def _pg_timeout():
 
 def init_distributed(tensor_parallel_size: int = 1, pipeline_parallel_size: int = 1, data_parallel_size: int = 1,
                      decode_context_parallel_size: int = 1, backend: Optional[str] = None,
-                     device: Optional[str] = None) -> None:
-    """Create the process groups.  Reads RANK / WORLD_SIZE / LOCAL_RANK / MASTER_* from the environment."""
+                     device: Optional[str] = None, prefill_context_parallel_size: int = 1) -> None:
+    """Create the process groups.  Reads RANK / WORLD_SIZE / LOCAL_RANK / MASTER_* from the environment.
+    ``prefill_context_parallel_size`` adds an outer dimension of full (tensor-parallel) model copies that split the
+    tokens of every prefill chunk between them; it is not combined with pipeline or data parallelism."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", str(rank)))
     _S.rank, _S.world_size, _S.local_rank = rank, world, local_rank
     if world == 1:
         _S.tp = _trivial("tp"); _S.pp = _trivial("pp"); _S.dp = _trivial("dp"); _S.ep = _trivial("ep")
-        _S.dcp = _trivial("dcp"); _S.world = _trivial("world")
+        _S.dcp = _trivial("dcp"); _S.pcp = _trivial("pcp"); _S.world = _trivial("world")
         _S.initialized = True
         return
     use_cuda = (device or "cuda") == "cuda" and torch.cuda.is_available()
@@ -197,7 +200,9 @@ def init_distributed(tensor_parallel_size: int = 1, pipeline_parallel_size: int 
             kw["timeout"] = _pg_timeout()
         dist.init_process_group(backend=be, rank=rank, world_size=world, **kw)
     tp, pp, dp = tensor_parallel_size, pipeline_parallel_size, data_parallel_size
-    assert tp * pp * dp == world, f"tp*pp*dp = {tp * pp * dp} != world size {world}"
+    pcp = prefill_context_parallel_size
+    assert tp * pp * dp * pcp == world, f"tp*pp*dp*pcp = {tp * pp * dp * pcp} != world size {world}"
+    assert pcp == 1 or (pp == 1 and dp == 1), "prefill context parallelism is combined with tensor parallelism only"
 
     def make(groups: list[list[int]], name: str) -> Group:
         mine = None
@@ -213,15 +218,24 @@ def init_distributed(tensor_parallel_size: int = 1, pipeline_parallel_size: int 
                 mine = g
         return mine
 
-    # rank = (dp_idx * pp + pp_idx) * tp + tp_idx
+    # rank = (dp_idx * pp + pp_idx) * tp + tp_idx; with prefill context parallelism rank = pcp_idx * tp + tp_idx
+    if pcp > 1:
+        _S.pcp = make([[c * tp + t for c in range(pcp)] for t in range(tp)], "pcp")
+        dp = pcp            # the tensor-parallel groups below are cut out of the world the same way
+    else:
+        _S.pcp = Group([rank], rank, name="pcp")
     tp_groups = [[(d * pp + p) * tp + t for t in range(tp)] for d in range(dp) for p in range(pp)]
     pp_groups = [[(d * pp + p) * tp + t for p in range(pp)] for d in range(dp) for t in range(tp)]
     dp_groups = [[(d * pp + p) * tp + t for d in range(dp)] for p in range(pp) for t in range(tp)]
     ep_groups = [[(d * pp + p) * tp + t for d in range(dp) for t in range(tp)] for p in range(pp)]
     _S.tp = make(tp_groups, "tp")
     _S.pp = make(pp_groups, "pp")
-    _S.dp = make(dp_groups, "dp")
-    _S.ep = make(ep_groups, "ep")
+    if pcp > 1:             # the copies are not data-parallel replicas: they work on the same requests
+        _S.dp = Group([rank], rank, name="dp")
+        _S.ep = _S.tp
+    else:
+        _S.dp = make(dp_groups, "dp")
+        _S.ep = make(ep_groups, "ep")
     dcp = decode_context_parallel_size
     if dcp > 1:
         assert tp % dcp == 0
@@ -277,6 +291,10 @@ def get_ep_group() -> Group:
 
 def get_dcp_group() -> Group:
     ensure_initialized(); return _S.dcp
+
+
+def get_pcp_group() -> Group:
+    ensure_initialized(); return _S.pcp
 
 
 def get_world_group() -> Group:
