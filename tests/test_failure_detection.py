@@ -24,15 +24,15 @@ def test_forward_error_poisons_engine_and_releases_memory():
     eng = llm.engine
     free0 = eng.kv.num_free_blocks
     calls = {"n": 0}
-    real = eng.runner.execute
+    real = eng.runner._forward            # every step path (in-turn, overlapped, pipelined) runs the model through it
 
-    def flaky(so):
+    def flaky(md, T):
         calls["n"] += 1
         if calls["n"] == 3:
             raise RuntimeError("injected forward failure")
-        return real(so)
+        return real(md, T)
 
-    eng.runner.execute = flaky
+    eng.runner._forward = flaky
     with pytest.raises(EngineDeadError, match="injected forward failure"):
         llm.generate([[1, 2, 3, 4, 5]] * 3, SamplingParams(max_tokens=8, ignore_eos=True))
     assert eng.dead is not None
