@@ -81,6 +81,7 @@ class ModelRunner:
                                  f"least dcp tensor-parallel ranks (kv heads {m.num_key_value_heads}, tp {ps.tp_size()}, "
                                  f"dcp {self.dcp}), or an MLA model")
         self.dcp_per_token = self.dcp > 1 and cfg.model.is_mla
+        self.cascade = bool(envs.B200_CASCADE_ATTENTION) and cfg.cache.enable_prefix_caching and self.dcp == 1
         # prefill context parallel: full model copies that split the tokens of every prefill chunk (parallel/pcp.py)
         self.pcp = ps.get_pcp_group().world_size
         if self.pcp > 1 and (cfg.model.is_mla or self.dcp > 1):
@@ -451,6 +452,8 @@ class ModelRunner:
             max_prefill_query_len=max_q if B_eff > nd_eff else 0)
         # MLA: prefill requests without cached context may take the up-projected MHA path
         md.extra["prefill_no_context"] = all(s.start_pos == 0 for s in so.scheduled[nd:])
+        if self.cascade and B >= 2 and pad_to <= B:
+            self._cascade_metadata(so, md, T)
         if d > 1:
             ctx_local += [0] * (B_eff - len(ctx_local))
             md.extra["dcp_ctx_lens"] = torch.tensor(ctx_local, dtype=torch.int32).to(self.device, non_blocking=True)
@@ -465,6 +468,43 @@ class ModelRunner:
         if getattr(self.model, "is_multimodal", False):
             self._multimodal_rows(so, md)
         return md, T, sample_rows, sample_reqs
+
+    def _cascade_applies(self, so: SchedulerOutput) -> bool:
+        if len(so.scheduled) < 2:
+            return False
+        first = so.scheduled[0].request.block_ids
+        n = min(min(s.start_pos for s in so.scheduled) // self.block_size, len(first))
+        if n * self.block_size * (len(so.scheduled) - 1) < envs.B200_CASCADE_MIN_SAVED_TOKENS:
+            return False
+        return all(s.request.block_ids[:n] == first[:n] for s in so.scheduled[1:])
+
+    def _cascade_metadata(self, so: SchedulerOutput, md: AttentionMetadata, T: int) -> None:
+        """Leading cache blocks that ALL requests of the step share (the same physical blocks, from the prefix cache)
+        and that hold computed context: the attention layers read them once for the whole step."""
+        first = so.scheduled[0].request.block_ids
+        n = min(min(s.start_pos for s in so.scheduled) // self.block_size, len(first))
+        for s in so.scheduled[1:]:
+            ids = s.request.block_ids
+            k = 0
+            while k < n and ids[k] == first[k]:
+                k += 1
+            n = k
+            if n == 0:
+                return
+        tokens = n * self.block_size
+        if tokens * (len(so.scheduled) - 1) < envs.B200_CASCADE_MIN_SAVED_TOKENS:
+            return
+        md.extra["cascade_blocks"] = n
+        md.extra["cascade_seq_len"] = torch.tensor([tokens], dtype=torch.int32).to(self.device, non_blocking=True)
+        md.extra["cascade_qsl"] = torch.tensor([0, T], dtype=torch.int32).to(self.device, non_blocking=True)
+        # from the host staging arrays: the device copies of this step may not have been submitted yet
+        B_, MB, nb = self.max_seqs, self.max_blocks_per_seq, len(so.scheduled)
+        sl = self.h32_np[B_ + 1: 2 * B_ + 1]
+        bt = self.h32_np[2 * B_ + 1: 2 * B_ + 1 + B_ * MB].reshape(B_, MB)
+        md.extra["cascade_suffix_lens"] = torch.from_numpy(sl[:nb] - tokens).to(self.device, non_blocking=True)
+        md.extra["cascade_suffix_table"] = torch.from_numpy(np.ascontiguousarray(bt[:nb, n:])).to(self.device,
+                                                                                                non_blocking=True)
+        self.cascade_steps = getattr(self, "cascade_steps", 0) + 1
 
     def _submit_inputs(self) -> None:
         """One H2D per staging area (only the used prefix of each segment)."""
@@ -703,6 +743,8 @@ class ModelRunner:
         use_lora = self._route_lora(so)
         if self.use_graphs and pure_decode and self.graphs and not use_lora:      # adapter rows are gathered by index
             bucket = next((b for b in self.buckets if b >= B), 0)
+            if bucket and self.cascade and self._cascade_applies(so):
+                bucket = 0        # the shared prefix is worth more than the captured graph: this step runs eagerly
         md, T, rows, reqs = self._prepare(so, pad_to=bucket)
         all_greedy = all(r.params.greedy and not r.params.needs_penalties and not r.params.constrained for r in reqs)
         n = len(rows)

@@ -50,6 +50,10 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # B200_FUSED_TP_MIN_TOKENS tokens; GEMM + peer-store all-reduce + add-norm below).
     "B200_FUSED_TP_KERNEL": _str("B200_FUSED_TP_KERNEL", "split"),
     "B200_FUSED_TP_MIN_TOKENS": _int("B200_FUSED_TP_MIN_TOKENS", 1024),
+    # Cascade attention: requests of a step whose leading cache blocks are the same physical blocks (prefix cache)
+    # attend that prefix once for the whole step.  Taken when prefix_tokens * (requests - 1) reaches the threshold.
+    "B200_CASCADE_ATTENTION": _flag("B200_CASCADE_ATTENTION", "1"),
+    "B200_CASCADE_MIN_SAVED_TOKENS": _int("B200_CASCADE_MIN_SAVED_TOKENS", 131072),
     # Prepare step k + 1 on the host (schedule, staging buffers) while the device runs step k; 0 = strictly in turn.
     "B200_OVERLAP_SCHEDULING": _flag("B200_OVERLAP_SCHEDULING", "1"),
     # Pipeline parallel: keep one step per stage in flight (disjoint request sets) instead of running lock-step.

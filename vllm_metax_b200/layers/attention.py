@@ -105,6 +105,8 @@ class Attention(nn.Module):
             q3 = q3.contiguous()
         out = torch.empty(T, self.num_heads, self.head_size, dtype=q.dtype, device=q.device)
         nd, ndt = md.num_decodes, md.num_decode_tokens
+        if "cascade_blocks" in md.extra and self.window == -1 and self.alibi_slopes is None and self.sinks is None:
+            return self._forward_cascade(q3, out, md, kv_cache, kv_scales)
         if nd > 0:
             ops.paged_attention_decode(q3[:ndt], kv_cache, md.block_table[:nd], md.seq_lens[:nd], self.scale,
                                        out=out[:ndt], kv_scales=kv_scales, window=self.window, softcap=self.softcap,
@@ -118,6 +120,41 @@ class Attention(nn.Module):
                                         sinks=self.sinks, k_scale=self.k_scale, v_scale=self.v_scale,
                                         max_seq_len=md.max_seq_len, alibi_slopes=self.alibi_slopes)
         return out.reshape(T, self.num_heads * self.head_size)
+
+    def _forward_cascade(self, q3, out, md, kv_cache, kv_scales) -> torch.Tensor:
+        """Shared-prefix (cascade) attention: the leading ``cascade_blocks`` cache blocks are the same physical blocks
+        for every request of the step, so all of the step's query tokens attend them in ONE pass (one pseudo request,
+        no causal mask: the prefix precedes every query), every request attends the rest of its own context, and the
+        two partial results are merged by their log-sum-exps.  The prefix is read once per step instead of once per
+        request.  Mirrors the cascade path of vllm_metax/v1/attention/backends/flash_attn.py (``use_cascade_attention``
+        / ``cascade_attention``: prefix pass + suffix pass + ``merge_attn_states``)."""
+        T, H, D = q3.shape
+        dev = q3.device
+        n = md.extra["cascade_blocks"]
+        nd, ndt = md.num_decodes, md.num_decode_tokens
+        common = dict(kv_scales=kv_scales, softcap=self.softcap, k_scale=self.k_scale, v_scale=self.v_scale)
+        o_p = torch.empty(T, H, D, dtype=q3.dtype, device=dev)
+        lse_p = torch.empty(H, T, dtype=torch.float32, device=dev)
+        ops.paged_attention_prefill(q3, kv_cache, md.block_table[:1, :n].contiguous(), md.extra["cascade_seq_len"],
+                                    md.extra["cascade_qsl"], self.scale, out=o_p, lse_out=lse_p, max_q_len=T,
+                                    causal=False, max_seq_len=n * md.block_size, **common)
+        table, lens = md.extra["cascade_suffix_table"], md.extra["cascade_suffix_lens"]
+        o_s = torch.empty(T, H, D, dtype=q3.dtype, device=dev)
+        parts = []
+        if nd > 0:
+            lse_d = torch.empty(H, ndt, dtype=torch.float32, device=dev)
+            ops.paged_attention_decode(q3[:ndt], kv_cache, table[:nd], lens[:nd], self.scale, out=o_s[:ndt],
+                                       lse_out=lse_d, max_seq_len=md.max_seq_len, **common)
+            parts.append(lse_d)
+        if md.num_prefills > 0:
+            lse_f = torch.empty(H, T - ndt, dtype=torch.float32, device=dev)
+            ops.paged_attention_prefill(q3[ndt:], kv_cache, table[nd:], lens[nd:], md.prefill_query_start_loc, self.scale,
+                                        out=o_s[ndt:], lse_out=lse_f, max_q_len=md.max_prefill_query_len,
+                                        max_seq_len=md.max_seq_len, **common)
+            parts.append(lse_f)
+        lse_s = parts[0] if len(parts) == 1 else torch.cat(parts, dim=1)
+        out = ops.merge_attn_states(o_p, lse_p, o_s, lse_s.contiguous())
+        return out.reshape(T, H * D)
 
     def _forward_dcp(self, q, k, v, positions, rope, md, kv_cache, kv_scales) -> torch.Tensor:
         """Decode context parallel: this rank's cache holds every dcp-th token of each sequence (the slot mapping is
