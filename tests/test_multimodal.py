@@ -226,3 +226,111 @@ def test_internvl_chat_original_export(tmp_path):
     got = llm.generate([{"prompt_token_ids": ids, "multi_modal_data": {"image": img}}],
                        SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True))
     assert list(got[0].outputs[0].token_ids) == _want(hf, ids, img)
+
+
+# ------------------------------------------------------------------ Qwen2-VL: dynamic-resolution tower + M-RoPE
+QV_IMG, QV_START, QV_END = 500, 501, 502
+
+
+def _hf_qwen2vl(tmp_path):
+    torch.manual_seed(0)
+    c = tf.Qwen2VLConfig(
+        text_config=dict(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, max_position_embeddings=256, tie_word_embeddings=False,
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [4, 6, 6]}),
+        vision_config=dict(depth=2, embed_dim=64, hidden_size=128, num_heads=4, mlp_ratio=2, in_channels=3, patch_size=14,
+                           spatial_merge_size=2, temporal_patch_size=2),
+        image_token_id=QV_IMG, video_token_id=503, vision_start_token_id=QV_START, vision_end_token_id=QV_END)
+    hf = tf.Qwen2VLForConditionalGeneration(c).eval().float()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.dim() == 1:
+                p.add_(0.1 * torch.randn_like(p))
+            else:
+                p.mul_(2.0)
+    hf.save_pretrained(str(tmp_path))
+    return hf
+
+
+@pytest.mark.parametrize("chunk", [64, 7])
+def test_qwen2_vl_matches_hugging_face(tmp_path, chunk):
+    from vllm_metax_b200 import LLM, SamplingParams
+
+    hf = _hf_qwen2vl(tmp_path)
+    llm = LLM(str(tmp_path), dtype="float32", device="cpu", max_model_len=128, num_gpu_blocks=32, block_size=16,
+              max_num_batched_tokens=chunk)
+    assert llm.engine.runner.uses_mrope
+    g = torch.Generator().manual_seed(1)
+    grid_a, grid_b = (1, 4, 6), (1, 2, 4)                      # patches; 6 and 2 tokens after the 2 x 2 merge
+    pa, pb = torch.randn(24, 1176, generator=g), torch.randn(8, 1176, generator=g)
+    one = [5, 9, QV_START] + [QV_IMG] * 6 + [QV_END, 33, 100, 7, 8, 200, 31]
+    two = [3, QV_START] + [QV_IMG] * 6 + [QV_END, 40, QV_START] + [QV_IMG] * 2 + [QV_END, 60, 61, 62]
+    short = [5, 9, QV_START, QV_IMG, QV_END, 33, 100, 7, 8, 200, 31]          # one placeholder for the image
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    outs = llm.generate([
+        {"prompt_token_ids": one, "multi_modal_data": {"pixel_values": pa, "image_grid_thw": [grid_a]}},
+        {"prompt_token_ids": two, "multi_modal_data": {"pixel_values": torch.cat([pa, pb]), "image_grid_thw": [grid_a, grid_b]}},
+        {"prompt_token_ids": short, "multi_modal_data": {"pixel_values": pa, "image_grid_thw": [grid_a]}},
+        {"prompt_token_ids": [5, 9, 33, 100, 7]},
+    ], sp)
+    got = [list(o.outputs[0].token_ids) for o in outs]
+
+    def want(ids, pixels=None, grids=None):
+        kw = {} if pixels is None else dict(pixel_values=pixels, image_grid_thw=torch.tensor(grids))
+        with torch.no_grad():
+            out = hf.generate(input_ids=torch.tensor([ids]), max_new_tokens=6, do_sample=False, eos_token_id=None,
+                              pad_token_id=0, **kw)
+        return out[0, len(ids):].tolist()
+
+    assert got[0] == want(one, pa, [grid_a])
+    assert got[1] == want(two, torch.cat([pa, pb]), [grid_a, grid_b])
+    assert got[2] == got[0]
+    assert got[3] == want([5, 9, 33, 100, 7])
+
+
+def test_mrope_prompt_table():
+    from vllm_metax_b200.models.qwen2_vl import mrope_prompt_positions
+
+    ids = [1, 2, QV_IMG, QV_IMG, QV_IMG, QV_IMG, QV_IMG, QV_IMG, 3, 4]
+    pos, delta = mrope_prompt_positions(ids, [(1, 4, 6)], QV_IMG, 2)          # 2 x 3 merged grid
+    assert pos[:, :2].tolist() == [[0, 1]] * 3
+    assert pos[0, 2:8].tolist() == [2] * 6
+    assert pos[1, 2:8].tolist() == [2, 2, 2, 3, 3, 3] and pos[2, 2:8].tolist() == [2, 3, 4, 2, 3, 4]
+    assert pos[:, 8:].tolist() == [[5, 6]] * 3 and delta == 7 - 10
+
+
+def test_qwen2_5_vl_matches_hugging_face(tmp_path):
+    """Qwen2.5-VL: RMSNorm + SiLU-gated vision blocks, window attention with one full-attention block, RMSNorm merger."""
+    from vllm_metax_b200 import LLM, SamplingParams
+
+    torch.manual_seed(0)
+    c = tf.Qwen2_5_VLConfig(
+        text_config=dict(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, max_position_embeddings=256, tie_word_embeddings=False,
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [4, 6, 6]}),
+        vision_config=dict(depth=3, hidden_size=64, intermediate_size=96, out_hidden_size=128, num_heads=4, in_channels=3,
+                           patch_size=14, spatial_merge_size=2, temporal_patch_size=2, window_size=56,
+                           fullatt_block_indexes=[1]),
+        image_token_id=QV_IMG, video_token_id=503, vision_start_token_id=QV_START, vision_end_token_id=QV_END)
+    hf = tf.Qwen2_5_VLForConditionalGeneration(c).eval().float()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.dim() == 1:
+                p.add_(0.1 * torch.randn_like(p))
+            else:
+                p.mul_(2.0)
+    hf.save_pretrained(str(tmp_path))
+    llm = LLM(str(tmp_path), dtype="float32", device="cpu", max_model_len=128, num_gpu_blocks=32, block_size=16,
+              max_num_batched_tokens=64)
+    g = torch.Generator().manual_seed(1)
+    grid = (1, 6, 8)                                           # 3 x 4 merge units, windows of 2 x 2 units: ragged edges
+    px = torch.randn(48, 1176, generator=g)
+    ids = [5, 9, QV_START] + [QV_IMG] * 12 + [QV_END, 33, 100, 7, 8]
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    got = list(llm.generate([{"prompt_token_ids": ids, "multi_modal_data": {"pixel_values": px, "image_grid_thw": [grid]}}],
+                            sp)[0].outputs[0].token_ids)
+    with torch.no_grad():
+        out = hf.generate(input_ids=torch.tensor([ids]), pixel_values=px, image_grid_thw=torch.tensor([grid]),
+                          mm_token_type_ids=torch.tensor([[1 if t == QV_IMG else 0 for t in ids]]),
+                          max_new_tokens=6, do_sample=False, eos_token_id=None, pad_token_id=0)
+    assert got == out[0, len(ids):].tolist()

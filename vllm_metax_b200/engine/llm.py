@@ -138,7 +138,9 @@ class LLMEngine:
         req = Request(rid, list(prompt_token_ids), params or SamplingParams(), self.cfg.model.eos_token_id, prompt,
                       arrival_time)
         if mm is not None:
-            req.mm_embeds, req.mm_positions, req.mm_hash = mm
+            req.mm_embeds, req.mm_positions, req.mm_hash = mm[:3]
+            if len(mm) > 3 and mm[3]:
+                req.mrope_positions, req.mrope_delta = mm[3]["mrope_positions"], int(mm[3]["mrope_delta"])
         if lora_request is None and params is not None:
             lora_request = getattr(params, "_lora_request", None)      # set by front ends that only pass params through
         if lora_request is not None:
@@ -220,7 +222,7 @@ class LLMEngine:
         r = self.runner
         return (self.overlap_scheduling and not self.scheduler.paused and self.proposer is None and not self.dp_sync
                 and self.kv_connector is None and r.state_slots is None and r.lora is None and r.dcp == 1 and r.pcp == 1
-                and not self.step_hooks and not getattr(r, "keep_hidden", False))
+                and not self.step_hooks and not getattr(r, "keep_hidden", False) and not r.uses_mrope)
 
     def _step_overlapped(self) -> list[Request]:
         """One step with the host work of the NEXT step (scheduling, staging buffers) done while the device runs this

@@ -82,6 +82,7 @@ class ModelRunner:
                                  f"dcp {self.dcp}), or an MLA model")
         self.dcp_per_token = self.dcp > 1 and cfg.model.is_mla
         self.cascade = bool(envs.B200_CASCADE_ATTENTION) and cfg.cache.enable_prefix_caching and self.dcp == 1
+        self.uses_mrope = bool(getattr(self.model, "uses_mrope", False))
         # prefill context parallel: full model copies that split the tokens of every prefill chunk (parallel/pcp.py)
         self.pcp = ps.get_pcp_group().world_size
         if self.pcp > 1 and (cfg.model.is_mla or self.dcp > 1):
@@ -174,6 +175,7 @@ class ModelRunner:
         self.d32 = torch.zeros(self.n32, dtype=torch.int32, device=dev)
         self.h64_np, self.h32_np = self.h64.numpy(), self.h32.numpy()
         self._bt_owner: list = [None] * B
+        self.mrope_dev = torch.zeros(3, T, dtype=torch.int64, device=dev) if self.uses_mrope else None
         self.input_ids = self.d64[:T]
         self.positions = self.d64[T:2 * T]
         self.slot_mapping = self.d64[2 * T:3 * T]
@@ -289,6 +291,9 @@ class ModelRunner:
         model = self.model
         if not getattr(model, "is_multimodal", False):
             raise ValueError(f"{self.cfg.model.architecture} takes no multi-modal inputs")
+        if hasattr(model, "encode_request"):         # models with their own input layout (dynamic-resolution towers)
+            ids, triple, extras = model.encode_request(list(prompt_token_ids), mm, self.device)
+            return ids, (*triple, extras)
         imgs = mm.get("pixel_values", mm.get("image"))
         if isinstance(imgs, torch.Tensor) and imgs.dim() == 4:
             pixels = imgs
@@ -467,7 +472,33 @@ class ModelRunner:
             self._state_metadata(so, md, B_eff)
         if getattr(self.model, "is_multimodal", False):
             self._multimodal_rows(so, md)
+        if self.uses_mrope:
+            self._mrope_positions(so, md, T)
         return md, T, sample_rows, sample_reqs
+
+    def _mrope_positions(self, so: SchedulerOutput, md: AttentionMetadata, T: int) -> None:
+        """The three rotary position streams of this step's tokens (``[3, T]``, a static buffer so that captured decode
+        graphs read the current values): the request's prompt table where it has one, else position + offset."""
+        out = np.empty((3, T), dtype=np.int64)
+        t = 0
+        for s in so.scheduled:
+            r, n, p0 = s.request, s.num_new_tokens, s.start_pos
+            ar = np.arange(p0, p0 + n)
+            tab = r.mrope_positions
+            if tab is None:
+                out[:, t:t + n] = ar
+            else:
+                L = tab.shape[1]
+                k = max(0, min(n, L - p0))
+                if k:
+                    out[:, t:t + k] = tab[:, p0:p0 + k]
+                if k < n:
+                    out[:, t + k:t + n] = ar[k:] + r.mrope_delta
+            t += n
+        if t < T:                      # graph padding rows
+            out[:, t:] = 0
+        self.mrope_dev[:, :T].copy_(torch.from_numpy(out), non_blocking=False)
+        md.extra["mrope_positions"] = self.mrope_dev[:, :T]
 
     def _cascade_applies(self, so: SchedulerOutput) -> bool:
         if len(so.scheduled) < 2:
@@ -654,6 +685,8 @@ class ModelRunner:
         if self.dcp > 1:                      # decode rows of the captured step take the context-parallel path
             md.extra["dcp_ctx_lens"] = torch.zeros(bucket, dtype=torch.int32, device=self.device)
             md.extra["dcp_any_context"] = False
+        if self.uses_mrope:
+            md.extra["mrope_positions"] = self.mrope_dev[:, :bucket]
         if self.state_slots is not None:      # warm-up and capture run on the scratch slot
             B = self.max_seqs
             self.state_dev[:bucket].fill_(B)

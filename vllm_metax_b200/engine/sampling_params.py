@@ -74,7 +74,7 @@ class Request:
 
     __slots__ = ("request_id", "prompt_token_ids", "params", "output_token_ids", "status", "block_ids",
                  "num_computed_tokens", "arrival_time", "first_token_time", "finish_time", "token_times",
-                 "eos_token_id", "num_cached_tokens", "logprobs", "prompt", "_hashes", "spec_token_ids", "lora_request", "mm_embeds", "mm_positions", "mm_hash", "_sample_rng", "finishing")
+                 "eos_token_id", "num_cached_tokens", "logprobs", "prompt", "_hashes", "spec_token_ids", "lora_request", "mm_embeds", "mm_positions", "mm_hash", "_sample_rng", "finishing", "mrope_positions", "mrope_delta")
 
     def __init__(self, request_id: str, prompt_token_ids: list[int], params: SamplingParams,
                  eos_token_id: Optional[int] = None, prompt: Optional[str] = None,
@@ -82,6 +82,8 @@ class Request:
         self.request_id = request_id
         self._sample_rng = None
         self.finishing = False                 # its last token (by length) is being computed: not scheduled again
+        self.mrope_positions = None            # [3, prompt] multimodal rotary position streams (Qwen2-VL family) ...
+        self.mrope_delta = 0                   # ... and the offset of generated tokens' stream value from their position
         self.prompt_token_ids = list(prompt_token_ids)
         self.params = params
         self.output_token_ids: list[int] = []

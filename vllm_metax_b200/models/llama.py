@@ -94,6 +94,17 @@ class LlamaAttention(nn.Module):
         if self.qk_norm:
             ops.head_rms_norm(q, self.q_norm.weight, self.q_norm.eps, self.num_heads, self.head_dim)
             ops.head_rms_norm(k, self.k_norm.weight, self.k_norm.eps, self.num_kv_heads, self.head_dim)
+        sections = getattr(self, "mrope_section", None)
+        if sections is not None and self.rope is not None:
+            # multimodal rotary positions (Qwen2-VL family): three position streams, see models/qwen2_vl.py
+            from ..attention.metadata import get_forward_context
+            from .qwen2_vl import apply_mrope
+
+            pos3 = get_forward_context().attn_metadata.extra.get("mrope_positions")
+            if pos3 is None:
+                pos3 = positions[None, :].expand(3, -1)
+            q, k = apply_mrope(q, k, pos3, self.rope.cos_sin_cache, sections, self.head_dim)
+            return self.attn(q, k, v.contiguous(), positions, None)
         return self.attn(q, k, v, positions, self.rope)
 
     def forward(self, positions, h):

@@ -1,0 +1,380 @@
+"""Qwen2-VL: dynamic-resolution vision transformer + Qwen2 decoder with multimodal rotary positions (M-RoPE).
+
+Vision side (``Qwen2VisionTower``): the processor hands over flattened patches ``[N, 3 * 2 * 14 * 14]`` and one
+``(t, h, w)`` grid per image.  Patch embedding (the 3-D convolution is a linear map on a flattened patch), 2-D rotary
+positions (half of each head's rotary pairs turn with the patch row, half with its column; rows / columns are numbered
+in 2 x 2 merge-unit order, which is the order the patches arrive in), ``depth`` pre-LayerNorm blocks whose attention is
+bidirectional inside one temporal frame (varlen, non-causal), and the merger that concatenates every 2 x 2 unit and
+projects it to the decoder width: ``t * h * w / 4`` tokens per image.
+
+Decoder side: the rotary angle of frequency pair ``j`` is taken from one of THREE position streams (temporal, height,
+width) according to ``mrope_section`` - text tokens carry the same value in all three, image tokens their grid
+coordinates, and the text after an image continues from the largest coordinate used.  The engine keeps ordinary 1-D
+positions for the cache; the three streams travel as ``extra["mrope_positions"]`` (built per step by the model runner
+from the request's prompt table and its offset for generated tokens) and ``LlamaAttention`` applies them.
+
+Parity: Qwen2-VL / Qwen2.5-VL / Qwen3-VL rows of the reference's multimodal table (docs/models/supported_models.md:86-91),
+its ``MRotaryEmbedding`` registration (registry/custom_ops/layers/rotary_embedding/rotary_embedding.py:9-32) and ViT
+attention layer (registry/custom_ops/layers/attention/mm_encoder_attention.py:17-122).  Checked against Hugging Face's
+``Qwen2VLForConditionalGeneration`` in ``tests/test_multimodal.py``.
+"""
+from __future__ import annotations
+
+import hashlib
+import re
+from typing import Iterable
+
+import numpy as np
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import _custom_ops as ops
+from ..config import ModelConfig
+from ..layers.basic import LayerNorm
+from ..layers.linear import ReplicatedLinear
+from ..layers.mm_encoder_attention import encoder_attention
+
+
+def apply_mrope(q: torch.Tensor, k: torch.Tensor, pos3: torch.Tensor, cos_sin_cache: torch.Tensor, sections,
+                head_dim: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """NeoX rotation of ``q [T, Hq * D]`` / ``k [T, Hkv * D]`` where frequency pair j turns with position stream
+    ``section_of(j)`` of ``pos3 [3, T]``.  ``cos_sin_cache [max_pos, D]`` = ``[cos(D/2) | sin(D/2)]``."""
+    half = head_dim // 2
+    cs = cos_sin_cache.index_select(0, pos3.reshape(-1).long()).view(3, -1, head_dim).float()      # [3, T, D]
+    cos_parts, sin_parts, o = [], [], 0
+    for i, n in enumerate(sections):
+        cos_parts.append(cs[i, :, o:o + n])
+        sin_parts.append(cs[i, :, half + o: half + o + n])
+        o += n
+    assert o == half, "mrope_section must cover half of the head dimension"
+    cos, sin = torch.cat(cos_parts, -1)[:, None, :], torch.cat(sin_parts, -1)[:, None, :]            # [T, 1, D/2]
+
+    def rot(x):
+        T = x.shape[0]
+        x3 = x.reshape(T, -1, head_dim).float()
+        a, b = x3[..., :half], x3[..., half:]
+        return torch.cat([a * cos - b * sin, b * cos + a * sin], -1).to(x.dtype).reshape(T, -1)
+
+    return rot(q), rot(k)
+
+
+def mrope_prompt_positions(ids: list, grids: list, image_token_id: int, merge: int) -> tuple[np.ndarray, int]:
+    """``[3, len(ids)]`` position streams of a prompt whose images (in order) have the ``(t, h, w)`` patch grids
+    ``grids``, and the offset that turns the ordinary position of a generated token into its (common) stream value."""
+    pos = np.zeros((3, len(ids)), dtype=np.int64)
+    nxt, i, g = 0, 0, 0
+    while i < len(ids):
+        if ids[i] == image_token_id and g < len(grids):
+            t, h, w = grids[g]
+            gh, gw = h // merge, w // merge
+            n = t * gh * gw
+            tt = np.repeat(np.arange(t), gh * gw)
+            hh = np.tile(np.repeat(np.arange(gh), gw), t)
+            ww = np.tile(np.arange(gw), t * gh)
+            pos[:, i:i + n] = np.stack([tt, hh, ww]) + nxt
+            nxt += max(t, gh, gw)
+            i += n
+            g += 1
+        else:
+            pos[:, i] = nxt
+            nxt += 1
+            i += 1
+    return pos, nxt - len(ids)
+
+
+class Qwen2VisionBlock(nn.Module):
+    def __init__(self, dim: int, heads: int, mlp_dim: int, act: str, dtype):
+        super().__init__()
+        self.heads, self.hd = heads, dim // heads
+        self.norm1, self.norm2 = LayerNorm(dim, 1e-6, dtype), LayerNorm(dim, 1e-6, dtype)
+        self.qkv = ReplicatedLinear(dim, 3 * dim, True, dtype)
+        self.proj = ReplicatedLinear(dim, dim, True, dtype)
+        self.fc1, self.fc2 = ReplicatedLinear(dim, mlp_dim, True, dtype), ReplicatedLinear(mlp_dim, dim, True, dtype)
+        self.act = {"quick_gelu": "gelu_quick", "gelu": "gelu", "gelu_pytorch_tanh": "gelu_tanh"}.get(act, act)
+
+    def forward(self, x, cos, sin, cu, max_tokens: int):
+        N, dim = x.shape
+        qkv = self.qkv(self.norm1(x)).reshape(N, 3, self.heads, self.hd)
+        q, k, v = qkv[:, 0], qkv[:, 1], qkv[:, 2]
+
+        def rot(t):      # rotate-half over the whole head, angles [N, hd] = [row | col | row | col] quarters
+            tf_ = t.float()
+            a, b = tf_[..., : self.hd // 2], tf_[..., self.hd // 2:]
+            return (tf_ * cos[:, None, :] + torch.cat([-b, a], -1) * sin[:, None, :]).to(t.dtype)
+
+        a = encoder_attention(rot(q).contiguous(), rot(k).contiguous(), v.contiguous(), cu, max_tokens)
+        x = x + self.proj(a.reshape(N, dim))
+        return x + self.fc2(ops.activation(self.fc1(self.norm2(x)), self.act))
+
+
+class Qwen2VisionTower(nn.Module):
+    def __init__(self, vc: dict, dtype):
+        super().__init__()
+        self.embed, self.heads = vc["embed_dim"], vc["num_heads"]
+        self.patch, self.merge, self.tpatch = vc.get("patch_size", 14), vc.get("spatial_merge_size", 2), vc.get("temporal_patch_size", 2)
+        self.in_ch = vc.get("in_channels", 3)
+        self.patch_dim = self.in_ch * self.tpatch * self.patch * self.patch
+        self.patch_embed = ReplicatedLinear(self.patch_dim, self.embed, False, dtype)
+        mlp_dim = int(self.embed * vc.get("mlp_ratio", 4))
+        self.blocks = nn.ModuleList([Qwen2VisionBlock(self.embed, self.heads, mlp_dim, vc.get("hidden_act", "quick_gelu"), dtype)
+                                     for _ in range(vc["depth"])])
+        unit = self.embed * self.merge * self.merge
+        self.ln_q = LayerNorm(self.embed, 1e-6, dtype)
+        self.merger_fc1 = ReplicatedLinear(unit, unit, True, dtype)
+        self.merger_fc2 = ReplicatedLinear(unit, vc["hidden_size"], True, dtype)
+
+    def _angles(self, grids: list, device) -> torch.Tensor:
+        """``[N, head_dim / 2]``: per patch the angles of its row then of its column (quarter of the head each)."""
+        hd = self.embed // self.heads
+        dim = hd // 2
+        inv = 1.0 / (10000.0 ** (torch.arange(0, dim, 2, dtype=torch.float32, device=device) / dim))
+        m = self.merge
+        out = []
+        for t, h, w in grids:
+            hp = torch.arange(h, device=device)[:, None].expand(h, w).reshape(h // m, m, w // m, m).permute(0, 2, 1, 3).flatten()
+            wp = torch.arange(w, device=device)[None, :].expand(h, w).reshape(h // m, m, w // m, m).permute(0, 2, 1, 3).flatten()
+            ang = torch.cat([hp[:, None].float() * inv[None, :], wp[:, None].float() * inv[None, :]], -1)
+            out.append(ang.repeat(t, 1))
+        return torch.cat(out)
+
+    def forward(self, patches: torch.Tensor, grids: list) -> torch.Tensor:
+        """``patches [N, patch_dim]`` -> ``[N / merge^2, hidden_text]``."""
+        x = self.patch_embed(patches.to(self.patch_embed.weight.dtype))
+        ang = self._angles(grids, x.device)
+        emb = torch.cat([ang, ang], -1)
+        cos, sin = emb.cos(), emb.sin()
+        frames = [h * w for t, h, w in grids for _ in range(t)]
+        cu = torch.tensor([0] + list(np.cumsum(frames)), dtype=torch.int32, device=x.device)
+        for blk in self.blocks:
+            x = blk(x, cos, sin, cu, max(frames))
+        x = self.ln_q(x).reshape(-1, self.embed * self.merge * self.merge)
+        return self.merger_fc2(F.gelu(self.merger_fc1(x)))
+
+
+class Qwen2VLForConditionalGeneration(nn.Module):
+    is_multimodal = True
+    uses_mrope = True
+    renames = [(r"^model\.language_model\.", "language_model.model."), (r"^model\.visual\.", "visual."),
+               (r"^lm_head\.", "language_model.lm_head."), (r"^model\.(?!language_model|visual)", "language_model.model."),
+               (r"^visual\.patch_embed\.proj\.", "visual.patch_embed."),
+               (r"^visual\.blocks\.(\d+)\.attn\.", r"visual.blocks.\1."), (r"^visual\.blocks\.(\d+)\.mlp\.", r"visual.blocks.\1."),
+               (r"^visual\.merger\.ln_q\.", "visual.ln_q."), (r"^visual\.merger\.mlp\.0\.", "visual.merger_fc1."),
+               (r"^visual\.merger\.mlp\.2\.", "visual.merger_fc2.")]
+
+    def __init__(self, cfg: ModelConfig):
+        super().__init__()
+        from . import get_model_class
+
+        self.cfg = cfg
+        hf = cfg.hf_config
+        self.image_token_id = int(hf.get("image_token_id", 151655))
+        self.visual = Qwen2VisionTower(hf["vision_config"], cfg.dtype)
+        self.language_model = get_model_class("Qwen2ForCausalLM")(cfg)
+        tc = hf.get("text_config", hf)
+        rp = tc.get("rope_parameters") or tc.get("rope_scaling") or hf.get("rope_scaling") or {}
+        self.mrope_section = list(rp.get("mrope_section") or [cfg.head_dim // 2 - 2 * (cfg.head_dim // 6)] + [cfg.head_dim // 6] * 2)
+        for layer in self.language_model.model.layers.values():
+            layer.self_attn.mrope_section = self.mrope_section
+
+    # ---- multimodal interface -------------------------------------------------------------------------------------
+    def patchify(self, image) -> tuple[torch.Tensor, tuple]:
+        """A PIL image / ``[3, H, W]`` tensor -> ``(patches [N, patch_dim], (1, h, w))``: resized so that both sides
+        are multiples of ``patch * merge``, CLIP-normalised, one frame repeated over the temporal patch."""
+        v = self.visual
+        if not isinstance(image, torch.Tensor):
+            image = torch.from_numpy(np.asarray(image.convert("RGB"))).permute(2, 0, 1)
+        x = image.float() / (255.0 if image.dtype == torch.uint8 else 1.0)
+        unit = v.patch * v.merge
+        H = max(unit, round(x.shape[1] / unit) * unit)
+        W = max(unit, round(x.shape[2] / unit) * unit)
+        x = F.interpolate(x[None], size=(H, W), mode="bicubic", align_corners=False)[0].clamp(0, 1)
+        mean = torch.tensor([0.48145466, 0.4578275, 0.40821073]).view(3, 1, 1)
+        std = torch.tensor([0.26862954, 0.26130258, 0.27577711]).view(3, 1, 1)
+        x = ((x - mean) / std)[None].repeat(v.tpatch, 1, 1, 1)                       # [tp, 3, H, W]
+        gh, gw, m, p = H // v.patch, W // v.patch, v.merge, v.patch
+        x = x.reshape(1, v.tpatch, 3, gh // m, m, p, gw // m, m, p).permute(0, 3, 6, 4, 7, 2, 1, 5, 8)
+        return x.reshape(gh * gw, 3 * v.tpatch * p * p), (1, gh, gw)
+
+    @torch.no_grad()
+    def encode_request(self, prompt_token_ids: list, mm: dict, device):
+        """Everything the engine needs for one request: the prompt with its placeholder runs expanded, the projected
+        image features with the prompt positions they replace, a content hash, and the M-RoPE streams of the prompt."""
+        if "pixel_values" in mm:
+            patches, grids = mm["pixel_values"], [tuple(int(x) for x in g) for g in mm["image_grid_thw"]]
+        else:
+            imgs = mm["image"] if isinstance(mm["image"], (list, tuple)) else [mm["image"]]
+            pg = [self.patchify(im) for im in imgs]
+            patches, grids = torch.cat([p for p, _ in pg]), [g for _, g in pg]
+        feats = self.visual(patches.to(device), grids)
+        m2 = self.visual.merge ** 2
+        per = [t * h * w // m2 for t, h, w in grids]
+        tok = self.image_token_id
+        runs = [r for r in re.finditer(r"(?:%d,)+" % tok, ",".join(map(str, prompt_token_ids)) + ",")]
+        lens = [r.group(0).count(",") for r in runs]
+        if lens == per:
+            ids = list(prompt_token_ids)
+        elif len(lens) == len(per) and all(n == 1 for n in lens):          # one placeholder per image: expand
+            ids, g = [], 0
+            for t in prompt_token_ids:
+                if t == tok:
+                    ids.extend([tok] * per[g])
+                    g += 1
+                else:
+                    ids.append(t)
+        else:
+            raise ValueError(f"prompt has image placeholder runs of {lens} tokens for images of {per} tokens")
+        pos = np.asarray([i for i, t in enumerate(ids) if t == tok], dtype=np.int64)
+        digest = hashlib.sha256(patches.detach().float().cpu().numpy().tobytes()).hexdigest()[:16]
+        table, delta = mrope_prompt_positions(ids, grids, tok, self.visual.merge)
+        return ids, (feats, pos, digest), {"mrope_positions": table, "mrope_delta": delta}
+
+    # ---- engine interface: the text decoder's ---------------------------------------------------------------------
+    def num_kv_layers(self) -> int:
+        return self.language_model.num_kv_layers()
+
+    def kv_cache_spec(self) -> dict:
+        return self.language_model.kv_cache_spec()
+
+    def forward(self, input_ids, positions, intermediate=None):
+        return self.language_model(input_ids, positions, intermediate)
+
+    def compute_logits(self, hidden):
+        return self.language_model.compute_logits(hidden)
+
+    @property
+    def model(self):
+        return self.language_model.model
+
+    def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]) -> set[str]:
+        params = dict(self.named_parameters())
+        text, loaded = [], set()
+        for name, w in weights:
+            for pat, rep in self.renames:
+                name = re.sub(pat, rep, name)
+            if name.startswith("language_model."):
+                text.append((name[len("language_model."):], w))
+                continue
+            if name == "visual.patch_embed.weight":
+                w = w.reshape(w.shape[0], -1)                # Conv3d kernel [embed, 3, tp, p, p] -> linear
+            if name in params:
+                params[name].data.copy_(w.reshape(params[name].shape))
+                loaded.add(name)
+        loaded |= {"language_model." + n for n in self.language_model.load_weights(iter(text))}
+        return loaded
+
+
+# ------------------------------------------------------------------------------------------------ Qwen2.5-VL
+class Qwen25VisionBlock(nn.Module):
+    """RMSNorm, attention, SiLU-gated MLP (all linears with bias)."""
+
+    def __init__(self, dim: int, heads: int, inter: int, dtype):
+        super().__init__()
+        from ..layers.basic import RMSNorm
+
+        self.heads, self.hd = heads, dim // heads
+        self.norm1, self.norm2 = RMSNorm(dim, 1e-6, dtype), RMSNorm(dim, 1e-6, dtype)
+        self.qkv = ReplicatedLinear(dim, 3 * dim, True, dtype)
+        self.proj = ReplicatedLinear(dim, dim, True, dtype)
+        self.gate_proj = ReplicatedLinear(dim, inter, True, dtype)
+        self.up_proj = ReplicatedLinear(dim, inter, True, dtype)
+        self.down_proj = ReplicatedLinear(inter, dim, True, dtype)
+
+    def forward(self, x, cos, sin, cu, max_tokens: int):
+        N, dim = x.shape
+        qkv = self.qkv(self.norm1(x)).reshape(N, 3, self.heads, self.hd)
+
+        def rot(t):
+            tf_ = t.float()
+            a, b = tf_[..., : self.hd // 2], tf_[..., self.hd // 2:]
+            return (tf_ * cos[:, None, :] + torch.cat([-b, a], -1) * sin[:, None, :]).to(t.dtype)
+
+        a = encoder_attention(rot(qkv[:, 0]).contiguous(), rot(qkv[:, 1]).contiguous(), qkv[:, 2].contiguous(), cu, max_tokens)
+        x = x + self.proj(a.reshape(N, dim))
+        h = self.norm2(x)
+        return x + self.down_proj(F.silu(self.gate_proj(h)) * self.up_proj(h))
+
+
+class Qwen25VisionTower(Qwen2VisionTower):
+    """Qwen2.5-VL tower: most blocks attend inside windows of ``window_size`` pixels (merge units are reordered window
+    by window, the order is undone after the merger); the blocks listed in ``fullatt_block_indexes`` attend the frame."""
+
+    def __init__(self, vc: dict, dtype):
+        nn.Module.__init__(self)
+        from ..layers.basic import RMSNorm
+
+        self.embed, self.heads = vc["hidden_size"], vc["num_heads"]
+        self.patch, self.merge, self.tpatch = vc.get("patch_size", 14), vc.get("spatial_merge_size", 2), vc.get("temporal_patch_size", 2)
+        self.in_ch = vc.get("in_channels", vc.get("in_chans", 3))
+        self.patch_dim = self.in_ch * self.tpatch * self.patch * self.patch
+        self.window = vc.get("window_size", 112) // self.merge // self.patch          # merge units per window side
+        self.full_blocks = set(vc.get("fullatt_block_indexes", [7, 15, 23, 31]))
+        self.patch_embed = ReplicatedLinear(self.patch_dim, self.embed, False, dtype)
+        self.blocks = nn.ModuleList([Qwen25VisionBlock(self.embed, self.heads, vc["intermediate_size"], dtype)
+                                     for _ in range(vc["depth"])])
+        unit = self.embed * self.merge * self.merge
+        self.ln_q = RMSNorm(self.embed, 1e-6, dtype)
+        self.merger_fc1 = ReplicatedLinear(unit, unit, True, dtype)
+        self.merger_fc2 = ReplicatedLinear(unit, vc["out_hidden_size"], True, dtype)
+
+    def _windows(self, grids: list):
+        """Order of the merge units window by window, and the cumulative patch counts of the windows."""
+        order, cu, base, ws, m2 = [], [0], 0, self.window, self.merge * self.merge
+        for t, h, w in grids:
+            gh, gw = h // self.merge, w // self.merge
+            idx = torch.arange(t * gh * gw).reshape(t, gh, gw)
+            ph, pw = (ws - gh % ws) % ws, (ws - gw % ws) % ws
+            idx = F.pad(idx, (0, pw, 0, ph), value=-100)
+            nh, nw = (gh + ph) // ws, (gw + pw) // ws
+            idx = idx.reshape(t, nh, ws, nw, ws).permute(0, 1, 3, 2, 4).reshape(t, nh * nw, ws, ws)
+            lens = (idx != -100).sum([2, 3]).reshape(-1)
+            order.append(idx[idx != -100] + base)
+            for n in lens.tolist():
+                if n:
+                    cu.append(cu[-1] + n * m2)
+            base += t * gh * gw
+        return torch.cat(order), cu
+
+    def forward(self, patches: torch.Tensor, grids: list) -> torch.Tensor:
+        x = self.patch_embed(patches.to(self.patch_embed.weight.dtype))
+        dev = x.device
+        ang = self._angles(grids, dev)
+        order, cu_win = self._windows(grids)
+        order = order.to(dev)
+        m2 = self.merge * self.merge
+        N = x.shape[0]
+        x = x.reshape(N // m2, m2, -1)[order].reshape(N, -1)
+        ang = ang.reshape(N // m2, m2, -1)[order].reshape(N, -1)
+        emb = torch.cat([ang, ang], -1)
+        cos, sin = emb.cos(), emb.sin()
+        frames = [h * w for t, h, w in grids for _ in range(t)]
+        cu_full = torch.tensor([0] + list(np.cumsum(frames)), dtype=torch.int32, device=dev)
+        cu_w = torch.tensor(cu_win, dtype=torch.int32, device=dev)
+        max_w = max(b - a for a, b in zip(cu_win[:-1], cu_win[1:]))
+        for i, blk in enumerate(self.blocks):
+            if i in self.full_blocks:
+                x = blk(x, cos, sin, cu_full, max(frames))
+            else:
+                x = blk(x, cos, sin, cu_w, max_w)
+        x = self.ln_q(x).reshape(-1, self.embed * m2)
+        x = self.merger_fc2(F.gelu(self.merger_fc1(x)))
+        return x[torch.argsort(order)]
+
+
+class Qwen2_5_VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
+    renames = Qwen2VLForConditionalGeneration.renames
+
+    def __init__(self, cfg: ModelConfig):
+        nn.Module.__init__(self)
+        from . import get_model_class
+
+        self.cfg = cfg
+        hf = cfg.hf_config
+        self.image_token_id = int(hf.get("image_token_id", 151655))
+        self.visual = Qwen25VisionTower(hf["vision_config"], cfg.dtype)
+        self.language_model = get_model_class("Qwen2ForCausalLM")(cfg)
+        tc = hf.get("text_config", hf)
+        rp = tc.get("rope_parameters") or tc.get("rope_scaling") or hf.get("rope_scaling") or {}
+        self.mrope_section = list(rp.get("mrope_section") or [cfg.head_dim // 2 - 2 * (cfg.head_dim // 6)] + [cfg.head_dim // 6] * 2)
+        for layer in self.language_model.model.layers.values():
+            layer.self_attn.mrope_section = self.mrope_section
