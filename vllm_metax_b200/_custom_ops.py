@@ -846,9 +846,10 @@ def wna16_gemm(x, qweight, scales, zeros, bits: int, group: int, *, bias=None, b
 
 # --------------------------------------------------------------------------- MLA
 def mla_decode(q, mla_cache, block_table, seq_lens, scale, *, query_start_loc=None, topk_indices=None, out=None,
-               lse_out=None, num_splits: int = 0, max_seq_len: int = 0):
+               lse_out=None, num_splits: int = 0, max_seq_len: int = 0, impl: int = 0):
     """Absorbed MLA over the latent cache (dense, or sparse with ``topk_indices [T, topk]``).
-    ``q [T, H, 576]`` -> ``[T, H, 512]``."""
+    ``q [T, H, 576]`` -> ``[T, H, 512]``.  ``impl``: 0 = choose, 1 = mma.sync kernel, 2 = tcgen05 kernel (dense 16-bit
+    caches; csrc/mla_decode_tcgen05.cu) or fail."""
     if _use_cuda(q):
         T, H, _ = q.shape
         out = torch.empty(T, H, 512, dtype=q.dtype, device=q.device) if out is None else out
@@ -856,11 +857,13 @@ def mla_decode(q, mla_cache, block_table, seq_lens, scale, *, query_start_loc=No
             # heads per CTA as chosen by the kernel launcher (csrc/mla_decode.cu:mla_decode_heads_per_cta)
             hpc = 16 if H <= 16 else (32 if (H <= 32 or mla_cache.dtype == torch.uint8) else 64)
             ctas = T * ((H + hpc - 1) // hpc)
+            if impl != 1 and topk_indices is None and mla_cache.dtype != torch.uint8 and (impl == 2 or H >= 64):
+                ctas = 2 * T * ((H + 127) // 128)            # tcgen05 kernel: 128 heads x half the latent per CTA
             kv = topk_indices.shape[1] if topk_indices is not None else (max_seq_len or 4096)
             num_splits = 1 if ctas >= 148 else max(1, min((296 + ctas - 1) // ctas, kv // 256, 16))
         ws = _decode_workspace(q.device, num_splits * T * H * 513) if num_splits > 1 else None
         torch.ops.b200.mla_decode(out, q, mla_cache, block_table, seq_lens, query_start_loc, topk_indices, scale,
-                                  lse_out, ws, num_splits)
+                                  lse_out, ws, num_splits, impl)
         return out
     res, lse = ref.mla_decode(q, mla_cache, block_table, seq_lens, scale, query_start_loc=query_start_loc,
                               topk_indices=topk_indices)

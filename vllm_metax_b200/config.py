@@ -284,6 +284,13 @@ class ParallelConfig:
     prefill_context_parallel_size: int = 1
     use_sequence_parallel_moe: bool = False
     all2all_backend: str = "fused_nvlink"      # fused_nvlink | allgather_reducescatter | naive
+    # expert-parallel load balancing (parallel/eplb.py): redundant expert slots, re-placement every
+    # eplb_step_interval engine steps from the routing statistics of the last eplb_window steps
+    enable_eplb: bool = False
+    num_redundant_experts: int = 0
+    eplb_step_interval: int = 3000
+    eplb_window: int = 1000
+    eplb_log_balancedness: bool = False
 
     @property
     def world_size(self) -> int:

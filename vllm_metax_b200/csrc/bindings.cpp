@@ -590,7 +590,7 @@ void wna16_gemm(Tensor& out, const Tensor& a, const Tensor& q, const Tensor& sca
 // ------------------------------------------------------------------ MLA
 void mla_decode(Tensor& out, const Tensor& q, const Tensor& cache, const Tensor& block_table, const Tensor& seq_lens,
                 const optional<Tensor>& query_start_loc, const optional<Tensor>& topk_indices, double scale,
-                const optional<Tensor>& lse_out, const optional<Tensor>& workspace, int64_t num_splits) {
+                const optional<Tensor>& lse_out, const optional<Tensor>& workspace, int64_t num_splits, int64_t impl) {
   TORCH_CHECK(q.dim() == 3 && q.size(2) == 576 && q.stride(2) == 1 && q.stride(1) == 576);
   TORCH_CHECK(cache.is_contiguous() && cache.dim() == 3 && out.is_contiguous() && out.size(2) == 512);
   const bool rec = cache.scalar_type() == at::kByte;
@@ -622,7 +622,8 @@ void mla_decode(Tensor& out, const Tensor& q, const Tensor& cache, const Tensor&
   }
   p.status = reinterpret_cast<b200::StatusWord*>(status_ptr(q));
   const c10::cuda::CUDAGuard guard(q.device());
-  b200::mla_decode(p, rec, dtype16(q), cur_stream());
+  const int rc = b200::mla_decode(p, rec, dtype16(q), cur_stream(), (int)impl);
+  TORCH_CHECK(rc == 0, "mla_decode: the tcgen05 kernel was asked for (impl = 2) but does not serve this call");
 }
 
 // ------------------------------------------------------------------ DSA indexer
@@ -1390,7 +1391,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("gemm_fp8_blockscale(Tensor(a!) out, Tensor a, Tensor a_scale, Tensor w, Tensor w_scale, Tensor? block_expert, Tensor? total_padded) -> ()", &gemm_fp8_blockscale);
   m.def("scaled_mm(Tensor(a!) out, Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor? azp, Tensor? azp_adj, Tensor? bias, Tensor? block_expert, Tensor? total_padded) -> ()", &scaled_mm);
   m.def("wna16_gemm(Tensor(a!) out, Tensor a, Tensor q, Tensor scales, Tensor? zeros, int bits, int group, Tensor? bias, Tensor? block_expert, Tensor? total_padded, int token_tile, int epi) -> ()", &wna16_gemm);
-  m.def("mla_decode(Tensor(a!) out, Tensor q, Tensor cache, Tensor block_table, Tensor seq_lens, Tensor? query_start_loc, Tensor? topk_indices, float scale, Tensor(b!)? lse_out, Tensor(c!)? workspace, int num_splits) -> ()", &mla_decode);
+  m.def("mla_decode(Tensor(a!) out, Tensor q, Tensor cache, Tensor block_table, Tensor seq_lens, Tensor? query_start_loc, Tensor? topk_indices, float scale, Tensor(b!)? lse_out, Tensor(c!)? workspace, int num_splits, int impl=0) -> ()", &mla_decode);
   m.def("indexer_logits(Tensor(a!) logits, Tensor q, Tensor w, Tensor cache, Tensor block_table, Tensor seq_lens, Tensor query_start_loc, int block_size, int max_len, bool int8, int max_query_len, int impl) -> ()", &indexer_logits);
   m.def("topk_per_row(Tensor(a!) out, Tensor x, Tensor? row_len, int cols) -> ()", &topk_per_row);
   m.def("symm_alloc(int nbytes, int device) -> (Tensor, Tensor)", &symm_alloc);

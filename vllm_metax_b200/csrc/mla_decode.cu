@@ -433,18 +433,30 @@ static void launch_mla(const MlaDecodeParams& p, cudaStream_t stream) {
     if constexpr (FP8) launch_mla_mt<T, true, 2>(p, stream);
     else launch_mla_mt<T, false, 4>(p, stream);
   }
-  if (p.num_splits > 1)
-    mla_split_reduce_kernel<T><<<(unsigned)((int64_t)p.total_tokens * p.num_heads), 256, 0, stream>>>(
-        (T*)p.out, p.lse_out, p.part_out, p.part_lse, p.num_splits, p.total_tokens, p.num_heads);
 }
 
-void mla_decode(const MlaDecodeParams& p, int fp8_records, int dtype, cudaStream_t stream) {
-  if (p.total_tokens <= 0) return;
-  if (dtype == 0) {
-    if (fp8_records) launch_mla<__nv_bfloat16, true>(p, stream); else launch_mla<__nv_bfloat16, false>(p, stream);
-  } else {
-    if (fp8_records) launch_mla<__half, true>(p, stream); else launch_mla<__half, false>(p, stream);
+template <typename T>
+static void launch_mla_reduce(const MlaDecodeParams& p, cudaStream_t stream) {
+  mla_split_reduce_kernel<T><<<(unsigned)((int64_t)p.total_tokens * p.num_heads), 256, 0, stream>>>(
+      (T*)p.out, p.lse_out, p.part_out, p.part_lse, p.num_splits, p.total_tokens, p.num_heads);
+}
+
+int mla_decode(const MlaDecodeParams& p, int fp8_records, int dtype, cudaStream_t stream, int impl) {
+  if (p.total_tokens <= 0) return 0;
+  bool done = false;
+  if (impl != 1 && !fp8_records && (impl == 2 || p.num_heads >= 64)) done = mla_decode_tc(p, dtype, stream) == 0;
+  if (!done && impl == 2) return -1;
+  if (!done) {
+    if (dtype == 0) {
+      if (fp8_records) launch_mla<__nv_bfloat16, true>(p, stream); else launch_mla<__nv_bfloat16, false>(p, stream);
+    } else {
+      if (fp8_records) launch_mla<__half, true>(p, stream); else launch_mla<__half, false>(p, stream);
+    }
   }
+  if (p.num_splits > 1) {
+    if (dtype == 0) launch_mla_reduce<__nv_bfloat16>(p, stream); else launch_mla_reduce<__half>(p, stream);
+  }
+  return 0;
 }
 
 }  // namespace b200

@@ -281,7 +281,11 @@ int tq_decode(void* out, float* part_out, float* part_lse, const void* q, int64_
 int custom_allreduce(const CustomArParams& p, const void* in, void* out, int dtype, int mode, cudaStream_t stream);
 int reduce_rms(const ReduceRmsParams& p, int dtype, cudaStream_t stream);
 // ---- mla_decode.cu
-void mla_decode(const MlaDecodeParams& p, int fp8_records, int dtype, cudaStream_t stream);
+// impl: 0 = choose (tcgen05 kernel for dense 16-bit caches from 64 heads per rank up), 1 = mma.sync kernel,
+// 2 = tcgen05 kernel or fail.  Returns 0, or -1 when impl 2 was asked for and that kernel does not serve the call.
+int mla_decode(const MlaDecodeParams& p, int fp8_records, int dtype, cudaStream_t stream, int impl = 0);
+// ---- mla_decode_tcgen05.cu: 0 = launched, -1 = not served
+int mla_decode_tc(const MlaDecodeParams& p, int dtype, cudaStream_t stream);
 // ---- indexer.cu
 void indexer_logits(float* logits, int64_t logits_stride, const void* q, const float* w, const void* cache,
                     const int* block_table, int max_blocks, const int* seq_lens, const int* query_start_loc,

@@ -182,6 +182,7 @@ class LLMEngine:
                     raise RuntimeError("scheduler made no progress: KV cache too small for the waiting request")
                 self.runner.execute_dummy()
                 self.stats["dp_padding_steps"] = self.stats.get("dp_padding_steps", 0) + 1
+                self._eplb_step()
                 return []
         if so.is_empty:
             if self.scheduler.has_unfinished() and not self.scheduler.paused:
@@ -207,6 +208,7 @@ class LLMEngine:
         finished = self.scheduler.update(so, sampled, now)
         if self.proposer is not None:
             self._propose_drafts(so, sampled)
+        self._eplb_step()
         self.stats["steps"] += 1
         self.stats["decode_tokens"] += so.num_decode
         self.stats["prefill_tokens"] += so.num_tokens - so.num_decode
@@ -255,6 +257,7 @@ class LLMEngine:
             self._release_all()
             raise EngineDeadError(f"engine step failed: {e!r}") from e
         finished = sch.finish_step(so, sampled, time.perf_counter())
+        self._eplb_step()
         self._next = None if prep2 is None else (so2, prep2)
         if prep2 is not None and all(s.request.status.finished for s in so2.scheduled):
             self._next = None              # everything in the prepared step has just finished: nothing to run
@@ -302,6 +305,7 @@ class LLMEngine:
         if self.kv_connector is not None and self.kv_connector.config.is_producer:
             self._publish_kv(so)
         finished = self.scheduler.update(so, sampled, time.perf_counter())
+        self._eplb_step()
         self.stats["steps"] += 1
         self.stats["decode_tokens"] += so.num_decode
         self.stats["prefill_tokens"] += so.num_tokens - so.num_decode
@@ -309,6 +313,15 @@ class LLMEngine:
         for r in finished:
             self.requests.pop(r.request_id, None)
         return finished
+
+    def _eplb_step(self) -> None:
+        """Expert load balancing: one tick per executed step on every rank (the ranks of an EP group run the same
+        steps), between steps; every ``eplb_step_interval`` ticks the experts are re-placed (parallel/eplb.py)."""
+        e = self.runner.eplb
+        if e is not None and e.step():
+            self.stats["eplb_rearrangements"] = e.rearrangements
+            if e.last_balancedness is not None:
+                self.stats["eplb_balancedness_before"], self.stats["eplb_balancedness_after"] = e.last_balancedness
 
     def _propose_drafts(self, so, sampled=None) -> None:
         """Attach draft tokens to the requests that will decode next step."""
@@ -397,7 +410,8 @@ class LLM:
                  additional_config: Optional[dict] = None, speculative_config: Optional[dict] = None,
                  enable_lora: bool = False, max_loras: int = 4, max_lora_rank: int = 64,
                  kv_transfer_config: Optional[dict] = None, decode_context_parallel_size: int = 1,
-                 prefill_context_parallel_size: int = 1):
+                 prefill_context_parallel_size: int = 1, enable_eplb: bool = False, num_redundant_experts: int = 0,
+                 eplb_step_interval: int = 3000, eplb_window: int = 1000):
         overrides = {"seed": seed}
         if enable_lora:
             overrides.update(enable_lora=True, max_loras=max_loras, max_lora_rank=max_lora_rank)
@@ -415,7 +429,9 @@ class LLM:
                               enable_prefix_caching=enable_prefix_caching),
             parallel=ParallelConfig(tensor_parallel_size, pipeline_parallel_size, data_parallel_size,
                                     enable_expert_parallel, decode_context_parallel_size,
-                                    prefill_context_parallel_size),
+                                    prefill_context_parallel_size, enable_eplb=enable_eplb,
+                                    num_redundant_experts=num_redundant_experts,
+                                    eplb_step_interval=eplb_step_interval, eplb_window=eplb_window),
             scheduler=SchedulerConfig(max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens,
                                       max_model_len=max_model_len, enable_chunked_prefill=enable_chunked_prefill),
             device=device, enforce_eager=enforce_eager, load_format=load_format,

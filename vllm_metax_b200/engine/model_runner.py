@@ -54,8 +54,16 @@ class ModelRunner:
             self.device = torch.device("cpu")
         self.is_cuda = self.device.type == "cuda"
         torch.manual_seed(cfg.model.seed)
+        ps.set_eplb(par.enable_eplb, par.num_redundant_experts)
         with torch.no_grad():
             self.model = build_model(cfg, self.device)
+        self.eplb = None
+        if par.enable_eplb:
+            from ..layers.fused_moe import FusedMoE
+            from ..parallel.eplb import EplbState
+
+            moe = [m for m in self.model.modules() if isinstance(m, FusedMoE) and m.eplb]
+            self.eplb = EplbState(moe, par.eplb_step_interval, par.eplb_window, par.eplb_log_balancedness)
         self.lora = None
         if cfg.model.enable_lora:
             from ..lora import LoRAManager

@@ -83,8 +83,11 @@ class FusedMoE(nn.Module):
         self.ep_group = ps.get_ep_group() if self.dp > 1 else ps.get_tp_group()
         self.ep = self.ep_group.world_size
         self.ep_rank = self.ep_group.rank_in_group
-        assert num_experts % self.ep == 0, "number of experts must divide over the EP ranks"
-        self.num_local = num_experts // self.ep
+        # load balancing: num_physical = num_experts + redundant slots; hot experts live in several slots
+        self.eplb = ps.eplb_enabled()
+        self.num_physical = num_experts + (ps.num_redundant_experts() if self.eplb else 0)
+        assert self.num_physical % self.ep == 0, "number of expert slots must divide over the EP ranks"
+        self.num_local = self.num_physical // self.ep
         self.quant_method = quant_method
         if quant_method is not None:
             quant_method.create_weights(self, self.num_local, hidden_size, intermediate_size, dtype)
@@ -96,12 +99,73 @@ class FusedMoE(nn.Module):
         self.e_score_correction_bias = (nn.Parameter(torch.zeros(num_experts, dtype=torch.float32), requires_grad=False)
                                         if e_score_correction_bias else None)
         if self.ep > 1:
-            emap = torch.full((num_experts,), -1, dtype=torch.int32)
+            emap = torch.full((self.num_physical,), -1, dtype=torch.int32)
             lo = self.ep_rank * self.num_local
             emap[lo: lo + self.num_local] = torch.arange(self.num_local, dtype=torch.int32)
             self.register_buffer("expert_map", emap, persistent=False)
         else:
             self.expert_map = None
+        if self.eplb:
+            from ..parallel import eplb
+
+            phy2log = eplb.initial_placement(num_experts, self.num_physical)
+            l2p, cnt = eplb.build_maps(phy2log, num_experts, self.num_physical - num_experts + 1)
+            self.register_buffer("phy2log", phy2log.to(torch.int32), persistent=False)
+            self.register_buffer("log2phy", l2p, persistent=False)
+            self.register_buffer("logcnt", cnt, persistent=False)
+            self.register_buffer("expert_load", torch.zeros(num_experts, dtype=torch.int64), persistent=False)
+
+    # ---- load balancing ---------------------------------------------------------
+    _EPLB_BUFFERS = ("phy2log", "log2phy", "logcnt", "expert_load", "expert_map", "e_score_correction_bias")
+
+    def _local_slots(self, expert_id: int) -> list:
+        """Local slot indices that hold logical expert ``expert_id`` on this rank."""
+        lo = self.ep_rank * self.num_local
+        if not self.eplb:
+            return [expert_id - lo] if lo <= expert_id < lo + self.num_local else []
+        mine = self.phy2log[lo: lo + self.num_local].tolist()
+        return [i for i, e in enumerate(mine) if e == expert_id]
+
+    def expert_tensors(self) -> list:
+        """Every per-slot tensor of this layer (first dimension = local slots): what a re-placement moves."""
+        out = []
+        for name, t in list(self._parameters.items()) + list(self._buffers.items()):
+            if t is None or name in self._EPLB_BUFFERS:
+                continue
+            if t.dim() >= 1 and t.shape[0] == self.num_local:
+                out.append(t.data)
+        return out
+
+    def apply_placement(self, new_phy2log: torch.Tensor) -> int:
+        """Move expert weights to the slots ``new_phy2log [P]`` names and switch the routing maps; collective over the
+        EP group.  Returns the number of expert rows received from other ranks."""
+        from ..parallel import eplb
+
+        old = self.phy2log.cpu().to(torch.int64)
+        new = new_phy2log.to(torch.int64).cpu()
+        tensors = self.expert_tensors()
+        moved = 0
+        if self.ep > 1:
+            moved = eplb.rearrange_layer(tensors, old, new, self.ep_group.ranks, self.ep_rank,
+                                         group=self.ep_group._pg(tensors[0]))
+        else:
+            eplb.rearrange_layer(tensors, old, new, [0], 0)
+        l2p, cnt = eplb.build_maps(new, self.num_experts, self.log2phy.shape[1])
+        self.phy2log.copy_(new.to(torch.int32))
+        self.log2phy.copy_(l2p)
+        self.logcnt.copy_(cnt)
+        return moved
+
+    def _to_physical(self, ids: torch.Tensor) -> torch.Tensor:
+        """Logical expert ids ``[T, k]`` -> physical slots: the pairs of a replicated expert take its copies in turn
+        (by token index), and the logical load is counted for the next re-placement."""
+        flat = ids.reshape(-1).long()
+        self.expert_load.scatter_add_(0, flat, torch.ones_like(flat))
+        T, k = ids.shape
+        turn = torch.arange(T, device=ids.device).unsqueeze(1) + torch.arange(k, device=ids.device).unsqueeze(0)
+        cnt = self.logcnt[flat].view(T, k)
+        rep = turn % cnt
+        return self.log2phy[flat, rep.reshape(-1).long()].view(T, k).to(ids.dtype)
 
     # ---- weights ----------------------------------------------------------------
     def weight_loader(self, param: torch.Tensor, loaded: torch.Tensor, expert_id: Optional[int] = None,
@@ -111,19 +175,15 @@ class FusedMoE(nn.Module):
         if expert_id is None:
             param.data.copy_(loaded.reshape(param.shape))
             return
-        lo = self.ep_rank * self.num_local
-        if not (lo <= expert_id < lo + self.num_local):
-            return
-        e = expert_id - lo
-        if self.quant_method is not None and hasattr(self.quant_method, "load_expert_weight"):
-            self.quant_method.load_expert_weight(self, param, loaded, e, shard)
-            return
-        if shard == "w1":
-            param.data[e, 0::2].copy_(loaded)
-        elif shard == "w3":
-            param.data[e, 1::2].copy_(loaded)
-        else:
-            param.data[e].copy_(loaded)
+        for e in self._local_slots(expert_id):
+            if self.quant_method is not None and hasattr(self.quant_method, "load_expert_weight"):
+                self.quant_method.load_expert_weight(self, param, loaded, e, shard)
+            elif shard == "w1":
+                param.data[e, 0::2].copy_(loaded)
+            elif shard == "w3":
+                param.data[e, 1::2].copy_(loaded)
+            else:
+                param.data[e].copy_(loaded)
 
     def load_expert_tensor(self, expert_id: int, shard: str, suffix: str, loaded: torch.Tensor) -> bool:
         """Checkpoint tensors that have no one-to-one parameter (packed weight-only formats): the quant
@@ -131,19 +191,23 @@ class FusedMoE(nn.Module):
         qm = self.quant_method
         if qm is None or not hasattr(qm, "load_expert_tensor"):
             return False
-        lo = self.ep_rank * self.num_local
-        if lo <= expert_id < lo + self.num_local:
-            qm.load_expert_tensor(self, expert_id - lo, shard, suffix, loaded)
+        for e in self._local_slots(expert_id):
+            qm.load_expert_tensor(self, e, shard, suffix, loaded)
         return True
 
     # ---- forward ------------------------------------------------------------------
     def route(self, router_logits: torch.Tensor):
+        """``(weights, ids) [T, k]``; the ids name expert SLOTS (= experts unless load balancing replicates some)."""
         bias = self.e_score_correction_bias
         if self.use_grouped_topk:
-            return ops.grouped_topk(router_logits, self.top_k, self.renormalize, self.num_expert_group,
-                                    self.topk_group, self.scoring_func, bias, self.routed_scaling_factor)
-        return ops.topk_gating(router_logits, self.top_k, self.renormalize, self.scoring_func, bias,
-                               self.routed_scaling_factor)
+            w, ids = ops.grouped_topk(router_logits, self.top_k, self.renormalize, self.num_expert_group,
+                                      self.topk_group, self.scoring_func, bias, self.routed_scaling_factor)
+        else:
+            w, ids = ops.topk_gating(router_logits, self.top_k, self.renormalize, self.scoring_func, bias,
+                                     self.routed_scaling_factor)
+        if self.eplb:
+            ids = self._to_physical(ids)
+        return w, ids
 
     def _experts_sorted(self, a, a_scale, block_expert, total):
         qm = self.quant_method
@@ -184,7 +248,7 @@ class FusedMoE(nn.Module):
             if mgr is None or mgr.max_tokens < need:
                 if mgr is not None:
                     mgr.close()
-                mgr = NvlinkAll2AllManager(epg, need, H, self.top_k, self.num_experts, x.dtype, x.device,
+                mgr = NvlinkAll2AllManager(epg, need, H, self.top_k, self.num_physical, x.dtype, x.device,
                                            quant_fp8=bool(getattr(qm, "a2a_wire_fp8", False)))
                 self._a2a = mgr
             mine = run_experts_a2a(mgr, mine_x, w, ids, self._experts_sorted)

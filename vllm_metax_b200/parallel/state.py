@@ -273,6 +273,26 @@ def max_tokens_per_step() -> int:
     return _MAX_TOKENS_PER_STEP
 
 
+_NUM_REDUNDANT_EXPERTS = 0
+_EPLB_ENABLED = False
+
+
+def set_eplb(enabled: bool, num_redundant_experts: int = 0) -> None:
+    """Expert-parallel load balancing for the MoE layers built from now on: ``num_redundant_experts`` extra expert
+    slots over the EP group (parallel/eplb.py).  Set by the engine before the model is constructed."""
+    global _NUM_REDUNDANT_EXPERTS, _EPLB_ENABLED
+    _EPLB_ENABLED = bool(enabled)
+    _NUM_REDUNDANT_EXPERTS = int(num_redundant_experts) if enabled else 0
+
+
+def eplb_enabled() -> bool:
+    return _EPLB_ENABLED
+
+
+def num_redundant_experts() -> int:
+    return _NUM_REDUNDANT_EXPERTS
+
+
 def get_tp_group() -> Group:
     ensure_initialized(); return _S.tp
 

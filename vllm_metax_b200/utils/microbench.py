@@ -425,7 +425,7 @@ def bench_linear_attention(t: Timer) -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "gemm", "prefill", "decode", "elementwise", "quant", "linear_attention", "skinny", "decode_layer", "configs", "indexer"])
+    ap.add_argument("--op", default="all", choices=["all", "gemm", "prefill", "decode", "elementwise", "quant", "linear_attention", "skinny", "decode_layer", "configs", "indexer", "mla"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
@@ -462,6 +462,23 @@ def main() -> None:
         res.update(bench_skinny(t))
     if a.op == "configs":
         res.update(bench_configs(t))
+    if a.op == "mla":            # absorbed MLA decode, --batch requests x --seq cached tokens, bf16 cache: both kernels
+        B, L, bs = a.batch, a.seq, 64
+        nblk = (L + bs - 1) // bs
+        bt = torch.arange(B * nblk, device=DEV, dtype=torch.int32).view(B, nblk)
+        sl = torch.full((B,), L, device=DEV, dtype=torch.int32)
+        cache = torch.randn(B * nblk, bs, 576, device=DEV, dtype=torch.bfloat16)
+        for Hh in (128, 64, 16):
+            q = torch.randn(B, Hh, 576, device=DEV, dtype=torch.bfloat16) * 0.1
+            row = {}
+            for name, impl in (("mma_sync", 1), ("tcgen05", 2)):
+                ms = t(lambda: ops.mla_decode(q, cache, bt, sl, 0.07, max_seq_len=L, impl=impl))
+                row[name] = {"ms": round(ms, 4), "cache_gbs": round(B * L * 1152 / ms / 1e6, 1),
+                             "tflops": round(2 * B * Hh * L * (576 + 512) / ms / 1e9, 1)}
+            o1 = ops.mla_decode(q, cache, bt, sl, 0.07, max_seq_len=L, impl=1).float()
+            o2 = ops.mla_decode(q, cache, bt, sl, 0.07, max_seq_len=L, impl=2).float()
+            row["max_abs_diff"] = float((o1 - o2).abs().max())
+            res[f"mla_decode_bf16_h{Hh}_b{B}x{L}"] = row
     if a.op == "indexer":        # --m query tokens of one request against --n cached keys (fp8, 64 heads): logits only
         T, Lk, bs = a.m, a.n, 64
         nb = Lk // bs
