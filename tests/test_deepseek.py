@@ -104,27 +104,6 @@ def test_mla_decode_gpu(H, fp8, splits, kernel_status_ok):
 
 
 @gpu
-@pytest.mark.parametrize("H", [128, 16, 200])
-@pytest.mark.parametrize("splits", [1, 3])
-@pytest.mark.parametrize("bs,scale,dtype", [(64, 0.1, torch.bfloat16), (32, 1.5, torch.bfloat16),
-                                            (64, 0.1, torch.float16)])
-def test_mla_decode_tcgen05_gpu(H, splits, bs, scale, dtype, kernel_status_ok):
-    """The tcgen05 kernel (csrc/mla_decode_tcgen05.cu), forced, against the fp32 oracle: one and two head tiles,
-    fewer heads than a tile, lengths that end inside a tile / a page, several tokens per request, empty splits,
-    and a score scale at which row maxima keep growing (the accumulator rescale path)."""
-    q, cache, bt, sl, qsl = _mla_case([70, 300, 17, 1000, 33], [1, 3, 1, 2, 1], H, bs, False, seed=5)
-    q, cache = q.to(dtype), cache.to(dtype)
-    lse = torch.empty(H, q.shape[0], device="cuda")
-    got = ops.mla_decode(q.cuda(), cache.cuda(), bt.cuda(), sl.cuda(), scale, query_start_loc=qsl.cuda(), lse_out=lse,
-                         num_splits=splits, impl=2)
-    want, wlse = ref.mla_decode(q.float(), cache.float(), bt, sl, scale, query_start_loc=qsl)
-    a, b = got.float().cpu().flatten(), want.flatten()
-    assert torch.isfinite(a).all()
-    assert 1 - float(torch.dot(a, b) / (a.norm() * b.norm())) < (5e-4 if scale < 1 else 3e-3)
-    torch.testing.assert_close(lse.cpu(), wlse, rtol=2e-2, atol=3e-2)
-
-
-@gpu
 def test_mla_sparse_decode_gpu(kernel_status_ok):
     H, topk = 16, 64
     q, cache, bt, sl, qsl = _mla_case([200, 90, 500], [2, 1, 1], H, 64, True, seed=3)

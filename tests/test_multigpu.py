@@ -33,9 +33,17 @@ def _launch(fn, world, *args, timeout=150):
     procs = [ctx.Process(target=_entry, args=(fn, r, world, port, q) + args) for r in range(world)]
     for p in procs:
         p.start()
-    res = q.get(timeout=timeout)
-    for p in procs:
-        p.join(timeout=120)
+    try:
+        res = q.get(timeout=timeout)
+        for p in procs:
+            p.join(timeout=120)
+    finally:
+        # a rank that is stuck (waiting for a peer that failed) must not outlive the test: end exactly the
+        # processes started above
+        for p in procs:
+            if p.is_alive():
+                p.kill()
+                p.join(timeout=10)
     assert res == "ok", res
     assert all(p.exitcode == 0 for p in procs)
 

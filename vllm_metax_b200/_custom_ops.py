@@ -849,9 +849,12 @@ def mla_decode(q, mla_cache, block_table, seq_lens, scale, *, query_start_loc=No
                lse_out=None, num_splits: int = 0, max_seq_len: int = 0, impl: int = 0):
     """Absorbed MLA over the latent cache (dense, or sparse with ``topk_indices [T, topk]``).
     ``q [T, H, 576]`` -> ``[T, H, 512]``.  ``impl``: 0 = choose, 1 = mma.sync kernel, 2 = tcgen05 kernel (dense 16-bit
-    caches; csrc/mla_decode_tcgen05.cu) or fail."""
+    caches; csrc/mla_decode_tcgen05.cu) or fail.  "Choose" takes the tcgen05 kernel for 64 heads per rank or more only
+    with ``B200_MLA_TCGEN05=1``."""
     if _use_cuda(q):
         T, H, _ = q.shape
+        if impl == 0 and not envs.B200_MLA_TCGEN05:
+            impl = 1
         out = torch.empty(T, H, 512, dtype=q.dtype, device=q.device) if out is None else out
         if num_splits <= 0:
             # heads per CTA as chosen by the kernel launcher (csrc/mla_decode.cu:mla_decode_heads_per_cta)

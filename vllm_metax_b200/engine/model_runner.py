@@ -113,6 +113,11 @@ class ModelRunner:
         self._enable_fused_tp()
         self.graphs: dict[int, tuple] = {}
         self.use_graphs = self.is_cuda and not cfg.enforce_eager and envs.B200_CUDA_GRAPHS
+        # replicas that share their experts exchange tokens in every MoE layer with sizes agreed on the host, and
+        # their steps differ in shape (one decodes while another prefills): a replayed graph would skip the host
+        # handshake its peer is waiting in, so these engines run eagerly
+        if ps.get_dp_group().world_size > 1 and cfg.model.is_moe:
+            self.use_graphs = False
         self.launch_count = 0
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count if self.is_cuda else 1
 

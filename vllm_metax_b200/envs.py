@@ -54,6 +54,9 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # attend that prefix once for the whole step.  Taken when prefix_tokens * (requests - 1) reaches the threshold.
     "B200_CASCADE_ATTENTION": _flag("B200_CASCADE_ATTENTION", "1"),
     "B200_CASCADE_MIN_SAVED_TOKENS": _int("B200_CASCADE_MIN_SAVED_TOKENS", 131072),
+    # Absorbed-MLA decode on tcgen05 (csrc/mla_decode_tcgen05.cu) for dense 16-bit caches from 64 heads per rank up;
+    # 0 = the mma.sync kernel unless a call asks for the tcgen05 one.
+    "B200_MLA_TCGEN05": _flag("B200_MLA_TCGEN05", "0"),
     # Prepare step k + 1 on the host (schedule, staging buffers) while the device runs step k; 0 = strictly in turn.
     "B200_OVERLAP_SCHEDULING": _flag("B200_OVERLAP_SCHEDULING", "1"),
     # Pipeline parallel: keep one step per stage in flight (disjoint request sets) instead of running lock-step.
