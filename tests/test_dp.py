@@ -43,3 +43,38 @@ def test_data_parallel_front():
         assert [o.outputs[0].token_ids for o in dp.generate(prompts[:2], sp, dp_rank=1)] == want[:2]
     finally:
         dp.shutdown()
+
+
+def test_elastic_scaling_and_healing():
+    """Replicas are added and retired between calls, and a replica that died is restarted in place; results never
+    change."""
+    from vllm_metax_b200 import LLM, EngineDeadError, SamplingParams
+    from vllm_metax_b200.engine.dp import DataParallelLLM
+
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (40, 8, 30, 31, 9, 50)]
+    sp = SamplingParams(max_tokens=5, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in LLM(tiny_cfg(), **KW).generate(prompts, sp)]
+    dp = DataParallelLLM(tiny_cfg(), data_parallel_size=1, **KW)
+    try:
+        assert [o.outputs[0].token_ids for o in dp.generate(prompts, sp)] == want
+        assert dp.scale(3) == 3 and len(dp._procs) == 3
+        assert [o.outputs[0].token_ids for o in dp.generate(prompts, sp)] == want
+        assert set(dp.last_assignment) == {0, 1, 2}
+        retired = dp._procs[2]
+        assert dp.scale(2) == 2 and not retired.is_alive()
+        assert [o.outputs[0].token_ids for o in dp.generate(prompts, sp)] == want
+        assert set(dp.last_assignment) == {0, 1}
+        with pytest.raises(ValueError):
+            dp.scale(0)
+        assert dp.scale_events == [(1, 3), (3, 2)]
+        # a replica dies and is restarted with the same rank
+        dp._procs[1].terminate()
+        dp._procs[1].join(10)
+        with pytest.raises(EngineDeadError):
+            dp.generate(prompts, sp)
+        assert dp.heal() == [1]
+        assert [o.outputs[0].token_ids for o in dp.generate(prompts, sp)] == want
+        assert dp.heal() == []
+    finally:
+        dp.shutdown()

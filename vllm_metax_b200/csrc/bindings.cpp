@@ -1391,7 +1391,7 @@ TORCH_LIBRARY(b200, m) {
   m.def("gemm_fp8_blockscale(Tensor(a!) out, Tensor a, Tensor a_scale, Tensor w, Tensor w_scale, Tensor? block_expert, Tensor? total_padded) -> ()", &gemm_fp8_blockscale);
   m.def("scaled_mm(Tensor(a!) out, Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor? azp, Tensor? azp_adj, Tensor? bias, Tensor? block_expert, Tensor? total_padded) -> ()", &scaled_mm);
   m.def("wna16_gemm(Tensor(a!) out, Tensor a, Tensor q, Tensor scales, Tensor? zeros, int bits, int group, Tensor? bias, Tensor? block_expert, Tensor? total_padded, int token_tile, int epi) -> ()", &wna16_gemm);
-  m.def("mla_decode(Tensor(a!) out, Tensor q, Tensor cache, Tensor block_table, Tensor seq_lens, Tensor? query_start_loc, Tensor? topk_indices, float scale, Tensor(b!)? lse_out, Tensor(c!)? workspace, int num_splits, int impl=0) -> ()", &mla_decode);
+  m.def("mla_decode(Tensor(a!) out, Tensor q, Tensor cache, Tensor block_table, Tensor seq_lens, Tensor? query_start_loc, Tensor? topk_indices, float scale, Tensor(b!)? lse_out, Tensor(c!)? workspace, int num_splits, int impl=1) -> ()", &mla_decode);
   m.def("indexer_logits(Tensor(a!) logits, Tensor q, Tensor w, Tensor cache, Tensor block_table, Tensor seq_lens, Tensor query_start_loc, int block_size, int max_len, bool int8, int max_query_len, int impl) -> ()", &indexer_logits);
   m.def("topk_per_row(Tensor(a!) out, Tensor x, Tensor? row_len, int cols) -> ()", &topk_per_row);
   m.def("symm_alloc(int nbytes, int device) -> (Tensor, Tensor)", &symm_alloc);

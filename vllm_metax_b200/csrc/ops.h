@@ -283,7 +283,7 @@ int reduce_rms(const ReduceRmsParams& p, int dtype, cudaStream_t stream);
 // ---- mla_decode.cu
 // impl: 0 = choose (tcgen05 kernel for dense 16-bit caches from 64 heads per rank up), 1 = mma.sync kernel,
 // 2 = tcgen05 kernel or fail.  Returns 0, or -1 when impl 2 was asked for and that kernel does not serve the call.
-int mla_decode(const MlaDecodeParams& p, int fp8_records, int dtype, cudaStream_t stream, int impl = 0);
+int mla_decode(const MlaDecodeParams& p, int fp8_records, int dtype, cudaStream_t stream, int impl = 1);
 // ---- mla_decode_tcgen05.cu: 0 = launched, -1 = not served
 int mla_decode_tc(const MlaDecodeParams& p, int dtype, cudaStream_t stream);
 // ---- indexer.cu

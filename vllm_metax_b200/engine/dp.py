@@ -56,27 +56,104 @@ def _replica_main(rank: int, conn, model, kwargs: dict, visible: Optional[str]) 
 class DataParallelLLM:
     def __init__(self, model, data_parallel_size: int = 2, devices_per_replica: int = 1, **llm_kwargs):
         assert data_parallel_size >= 1
-        self.dp = data_parallel_size
-        ctx = mp.get_context("spawn")
-        self._conns, self._procs = [], []
-        self._load = [0] * self.dp
-        on_gpu = llm_kwargs.get("device", None) != "cpu"
-        for r in range(self.dp):
-            parent, child = ctx.Pipe()
-            visible = None
-            if on_gpu:
-                base = os.environ.get("CUDA_VISIBLE_DEVICES")
-                ids = base.split(",") if base else [str(i) for i in range(self.dp * devices_per_replica)]
-                visible = ",".join(ids[r * devices_per_replica:(r + 1) * devices_per_replica])
-            p = ctx.Process(target=_replica_main, args=(r, child, model, dict(llm_kwargs), visible), daemon=True)
-            p.start()
-            self._conns.append(parent)
-            self._procs.append(p)
-        for r, c in enumerate(self._conns):
-            state, info = c.recv()
+        self.dp = 0
+        self._model, self._kwargs, self._per = model, dict(llm_kwargs), devices_per_replica
+        self._ctx = mp.get_context("spawn")
+        self._conns, self._procs, self._load = [], [], []
+        self.scale_events: list = []
+        self._grow(data_parallel_size)
+
+    # ------------------------------------------------------------------ replicas
+    def _visible(self, r: int) -> Optional[str]:
+        if self._kwargs.get("device", None) == "cpu":
+            return None
+        base = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if base:
+            ids = base.split(",")
+        else:
+            ids = [str(i) for i in range((r + 1) * self._per)]
+        mine = ids[r * self._per:(r + 1) * self._per]
+        if len(mine) < self._per:
+            raise RuntimeError(f"no devices left for data-parallel replica {r} (visible: {ids})")
+        return ",".join(mine)
+
+    def _spawn(self, r: int):
+        parent, child = self._ctx.Pipe()
+        p = self._ctx.Process(target=_replica_main, args=(r, child, self._model, dict(self._kwargs), self._visible(r)),
+                              daemon=True)
+        p.start()
+        return parent, p
+
+    def _grow(self, new_size: int) -> None:
+        started = [(r,) + self._spawn(r) for r in range(self.dp, new_size)]      # all new replicas load at once
+        failed = None
+        for r, c, p in started:
+            try:
+                state, info = c.recv()
+            except EOFError:
+                state, info = "failed", "replica exited while starting"
             if state != "ready":
-                self.shutdown()
-                raise RuntimeError(f"data-parallel replica {r} failed to start: {info}")
+                failed = failed or f"data-parallel replica {r} failed to start: {info}"
+        if failed is not None:
+            for _, c, p in started:
+                self._stop_one(c, p)
+            if self.dp == 0:
+                raise RuntimeError(failed)
+            raise RuntimeError(failed + f" (still serving with {self.dp} replicas)")
+        for r, c, p in started:
+            self._conns.append(c)
+            self._procs.append(p)
+            self._load.append(0)
+        self.dp = new_size
+
+    @staticmethod
+    def _stop_one(c, p) -> None:
+        try:
+            c.send(("stop", None))
+        except (BrokenPipeError, OSError):
+            pass
+        p.join(timeout=10)
+        if p.is_alive():
+            p.terminate()
+            p.join(timeout=5)
+        c.close()
+
+    def scale(self, new_data_parallel_size: int) -> int:
+        """Elastic scaling between calls: start more replicas (they load the model in parallel while the existing
+        ones stay up) or retire the highest-numbered ones (their devices are free when this returns).  Calls are
+        synchronous, so no request is in flight on a replica that leaves.  Returns the new size.  The use case of
+        the reference's examples/ray_serving/elastic_ep/scale.py (``new_data_parallel_size``) for replicas that do
+        not share experts."""
+        n = int(new_data_parallel_size)
+        if n < 1:
+            raise ValueError("at least one replica must remain")
+        old = self.dp
+        if n > old:
+            self._grow(n)
+        elif n < old:
+            for r in range(old - 1, n - 1, -1):
+                self._stop_one(self._conns.pop(), self._procs.pop())
+                self._load.pop()
+            self.dp = n
+        if n != old:
+            self.scale_events.append((old, n))
+        return self.dp
+
+    def heal(self) -> list:
+        """Restart replicas whose process has died (same rank, same devices).  Returns the ranks restarted."""
+        dead = [r for r, p in enumerate(self._procs) if not p.is_alive()]
+        for r in dead:
+            self._conns[r].close()
+            c, p = self._spawn(r)
+            try:
+                state, info = c.recv()
+            except EOFError:
+                state, info = "failed", "replica exited while starting"
+            if state != "ready":
+                self._stop_one(c, p)
+                raise RuntimeError(f"data-parallel replica {r} failed to restart: {info}")
+            self._conns[r], self._procs[r], self._load[r] = c, p, 0
+        return dead
 
     # ------------------------------------------------------------------ balancing
     @staticmethod
@@ -162,6 +239,7 @@ class DataParallelLLM:
             p.join(timeout=10)
             if p.is_alive():
                 p.terminate()
+        self._conns, self._procs, self._load, self.dp = [], [], [], 0
 
     def __del__(self):
         try:
