@@ -1,0 +1,166 @@
+"""User-facing sampling parameters beyond the sampler itself: stop strings (with an incremental detokeniser that
+survives multi-token characters), ``include_stop_str_in_output``, ``bad_words``, ``n`` samples per prompt,
+``truncate_prompt_tokens`` - offline and through the OpenAI server."""
+import asyncio
+import json
+import os
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from tests.test_e2e_plumbing import tiny_cfg  # noqa: E402
+from tests.test_structured import CharTokenizer  # noqa: E402
+
+PRINTABLE = list(range(95))        # the character tokens of CharTokenizer
+
+
+def _sp(**kw):
+    """Seeded sampling over the printable tokens: varied text that a second run reproduces."""
+    from vllm_metax_b200 import SamplingParams
+
+    base = dict(max_tokens=30, temperature=1.0, seed=11, allowed_token_ids=PRINTABLE)
+    base.update(kw)
+    return SamplingParams(**base)
+
+
+KW = dict(device="cpu", block_size=16, max_model_len=256, max_num_seqs=8, max_num_batched_tokens=64, num_gpu_blocks=64)
+
+
+@pytest.fixture(scope="module")
+def llm():
+    from vllm_metax_b200 import LLM
+
+    return LLM(tiny_cfg(), tokenizer=CharTokenizer(), **KW)
+
+
+def test_stop_checker_waits_for_complete_characters():
+    from vllm_metax_b200.engine.sampling_params import StopStringChecker
+
+    class ByteTok:                      # one token per UTF-8 byte: a character is printable only when all bytes arrived
+        def decode(self, ids, skip_special_tokens=True):
+            return bytes(ids).decode("utf-8", errors="replace")
+
+    text = "aé中 END tail"
+    ids = list(text.encode("utf-8"))
+    ck = StopStringChecker(ByteTok(), ["END"], include=False)
+    hit_at = None
+    for i in range(1, len(ids) + 1):
+        if ck.step(ids[:i]) is not None:
+            hit_at = i
+            break
+    assert hit_at == len("aé中 END".encode("utf-8"))
+    assert ck.text == "aé中 " and "�" not in ck.text
+    ck2 = StopStringChecker(ByteTok(), ["END", "中"], include=True)
+    for i in range(1, len(ids) + 1):
+        if ck2.step(ids[:i]) is not None:
+            break
+    assert ck2.hit == "中" and ck2.text == "aé中"      # the earliest stop wins, kept in the text
+
+
+def test_stop_strings_end_generation_and_cut_the_text(llm):
+    from vllm_metax_b200 import SamplingParams
+
+    free = llm.generate(["Q: ok?"], _sp())[0].outputs[0]
+    assert len(free.text) >= 12 and len(set(free.text)) > 4
+    stop = free.text[6:9]                                   # a string the seeded continuation is known to contain
+    cut = free.text.index(stop)
+    got = llm.generate(["Q: ok?"], _sp(stop=[stop, "\x00never"]))[0].outputs[0]
+    assert got.finish_reason == "stop" and got.stop_reason == stop
+    assert got.text == free.text[:cut]
+    assert len(got.token_ids) < len(free.token_ids)
+    keep = llm.generate(["Q: ok?"], _sp(stop=[stop], include_stop_str_in_output=True))[0].outputs[0]
+    assert keep.text == free.text[:cut + len(stop)]
+    none = llm.generate(["Q: ok?"], _sp(stop=["\x00never"]))[0].outputs[0]
+    assert none.text == free.text and none.finish_reason == "length" and none.stop_reason is None
+
+
+def test_bad_words_never_appear(llm):
+    from vllm_metax_b200 import SamplingParams
+
+    free = llm.generate(["Q: ok?"], _sp(max_tokens=24))[0].outputs[0]
+    first = free.token_ids[0]
+    pair = free.token_ids[3:5]
+    got = llm.generate(["Q: ok?"], _sp(max_tokens=24, bad_words=[[first], pair]))[0].outputs[0]
+    assert first not in got.token_ids
+    assert all(got.token_ids[i:i + 2] != pair for i in range(len(got.token_ids) - 1))
+    word = free.text[2:4]
+    got = llm.generate(["Q: ok?"], _sp(max_tokens=24, bad_words=[word]))[0].outputs[0]
+    assert word not in got.text
+
+
+def test_n_samples_per_prompt(llm):
+    from vllm_metax_b200 import SamplingParams
+
+    outs = llm.generate(["Q: ok?", "x"], SamplingParams(max_tokens=12, temperature=1.0, seed=7, n=3))
+    assert len(outs) == 2 and all(len(o.outputs) == 3 for o in outs)
+    assert [c.index for c in outs[0].outputs] == [0, 1, 2]
+    assert len({tuple(c.token_ids) for c in outs[0].outputs}) > 1                  # independent samples
+    again = llm.generate(["Q: ok?"], SamplingParams(max_tokens=12, temperature=1.0, seed=7, n=3))[0]
+    assert [c.token_ids for c in again.outputs] == [c.token_ids for c in outs[0].outputs]     # seeded: reproducible
+    greedy = llm.generate(["Q: ok?"], SamplingParams(max_tokens=6, n=2))[0]
+    assert greedy.outputs[0].token_ids == greedy.outputs[1].token_ids
+
+
+def test_truncate_prompt_tokens(llm):
+    from vllm_metax_b200 import SamplingParams
+
+    long = "abcdefghijklmnopqrstuvwxyz"
+    a = llm.generate([long], SamplingParams(max_tokens=6, truncate_prompt_tokens=5))[0]
+    b = llm.generate([long[-5:]], SamplingParams(max_tokens=6))[0]
+    assert a.outputs[0].token_ids == b.outputs[0].token_ids and len(a.prompt_token_ids) == 5
+
+
+def _call(app, body, path="/v1/completions"):
+    import httpx
+
+    async def go():
+        transport = httpx.ASGITransport(app=app)
+        async with httpx.AsyncClient(transport=transport, base_url="http://test") as c:
+            r = await c.post(path, json=body)
+            return r.status_code, r.text
+    return asyncio.run(go())
+
+
+def test_server_stop_and_n(llm):
+    pytest.importorskip("httpx")
+    from vllm_metax_b200.entrypoints.async_engine import AsyncLLM
+    from vllm_metax_b200.entrypoints.openai_server import build_app, sampling_from_request
+
+    sp = sampling_from_request({"stop": "ab", "include_stop_str_in_output": True, "bad_words": ["x"], "min_tokens": 2})
+    assert sp.stop == ["ab"] and sp.include_stop_str_in_output and sp.bad_words == ["x"] and sp.min_tokens == 2
+    allm = AsyncLLM(llm)
+    try:
+        app = build_app(allm, "toy")
+        base = {"prompt": "Q: ok?", "max_tokens": 30, "temperature": 1.0, "seed": 11, "allowed_token_ids": PRINTABLE}
+        code, text = _call(app, base)
+        free = json.loads(text)["choices"][0]["text"]
+        stop = free[6:9]
+        code, text = _call(app, dict(base, stop=[stop]))
+        ch = json.loads(text)["choices"][0]
+        assert code == 200 and ch["text"] == free[:free.index(stop)] and ch["finish_reason"] == "stop"
+        code, text = _call(app, {"prompt": "Q: ok?", "max_tokens": 8, "n": 3, "temperature": 1.0, "seed": 3})
+        res = json.loads(text)
+        assert code == 200 and [c["index"] for c in res["choices"]] == [0, 1, 2]
+        assert res["usage"]["completion_tokens"] == 24
+        code, text = _call(app, {"prompt": "Q: ok?", "max_tokens": 8, "n": 2, "stream": True})
+        assert code == 400
+        # a stream never shows the beginning of a stop string that then completes
+        import httpx
+
+        async def stream():
+            transport = httpx.ASGITransport(app=app)
+            async with httpx.AsyncClient(transport=transport, base_url="http://test") as c:
+                async with c.stream("POST", "/v1/completions",
+                                    json=dict(base, stop=[stop], stream=True)) as r:
+                    parts = []
+                    async for line in r.aiter_lines():
+                        if line.startswith("data: ") and line != "data: [DONE]":
+                            parts.append(json.loads(line[6:])["choices"][0]["text"])
+                    return "".join(parts)
+        assert asyncio.run(stream()) == free[:free.index(stop)]
+    finally:
+        allm.shutdown()

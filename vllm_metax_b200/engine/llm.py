@@ -135,8 +135,17 @@ class LLMEngine:
             prompt_token_ids, mm = self.runner.encode_multimodal(list(prompt_token_ids), multi_modal_data)
         if params is not None and (params.constrained or params.guided_regex is not None or params.guided_json is not None):
             params.prepare(self.tokenizer)
+        if params is not None and params.truncate_prompt_tokens:
+            prompt_token_ids = list(prompt_token_ids)[-int(params.truncate_prompt_tokens):]
         req = Request(rid, list(prompt_token_ids), params or SamplingParams(), self.cfg.model.eos_token_id, prompt,
                       arrival_time)
+        if params is not None and params.stop:
+            if self.tokenizer is None:
+                raise ValueError("stop strings need a tokenizer (use stop_token_ids with token-id prompts)")
+            from .sampling_params import StopStringChecker
+
+            req.stop_checker = StopStringChecker(self.tokenizer, list(params.stop), params.include_stop_str_in_output,
+                                                 params.skip_special_tokens)
         if mm is not None:
             req.mm_embeds, req.mm_positions, req.mm_hash = mm[:3]
             if len(mm) > 3 and mm[3]:
@@ -354,13 +363,16 @@ class LLMEngine:
 
     def make_output(self, r: Request) -> RequestOutput:
         text = None
-        if self.tokenizer is not None:
-            text = self.tokenizer.decode(r.output_token_ids, skip_special_tokens=True)
+        if r.stop_checker is not None and r.stop_checker.hit is not None:
+            text = r.stop_checker.text             # cut at the stop string
+        elif self.tokenizer is not None:
+            text = self.tokenizer.decode(r.output_token_ids, skip_special_tokens=r.params.skip_special_tokens)
         reason = {RequestStatus.FINISHED_STOPPED: "stop", RequestStatus.FINISHED_LENGTH: "length",
                   RequestStatus.FINISHED_ABORTED: "abort"}.get(r.status)
         return RequestOutput(r.request_id, r.prompt, r.prompt_token_ids,
-                             [CompletionOutput(0, list(r.output_token_ids), text, reason,
-                                               list(r.logprobs) if r.params.logprobs is not None else None)],
+                             [CompletionOutput(r.sample_index, list(r.output_token_ids), text, reason,
+                                               list(r.logprobs) if r.params.logprobs is not None else None,
+                                               r.stop_reason)],
                              r.status.finished,
                              RequestMetrics(r.arrival_time, r.first_token_time, r.finish_time, list(r.token_times)),
                              r.num_cached_tokens)
@@ -465,33 +477,52 @@ class LLM:
         else:
             sps = list(sampling_params)
         now = time.perf_counter()
-        order = []
+        import copy
+
+        groups: list[list[str]] = []          # per prompt: the request ids of its sp.n samples
         reqs: dict[str, Request] = {}
         loras = lora_request if isinstance(lora_request, (list, tuple)) else [lora_request] * n
         for p, sp, lr in zip(prompts, sps, loras):
             ids, text = self._to_ids(p)
-            import copy
-
             mm = p.get("multi_modal_data") if isinstance(p, dict) else None       # {"image": tensor | PIL | list}
-            rid = self.engine.add_request(ids, copy.copy(sp), prompt=text, arrival_time=now, lora_request=lr,
-                                          multi_modal_data=mm)
-            order.append(rid)
-            reqs[rid] = self.engine.requests[rid]
+            k = max(1, int(getattr(sp, "n", 1) or 1))
+            rids = []
+            for i in range(k):
+                spi = copy.copy(sp)
+                if k > 1:       # independent samples of one prompt (they share its cached prefix when that is on)
+                    spi.n = 1
+                    spi.seed = None if sp.seed is None else sp.seed + i
+                rid = self.engine.add_request(ids, spi, prompt=text, arrival_time=now, lora_request=lr,
+                                              multi_modal_data=mm)
+                reqs[rid] = self.engine.requests[rid]
+                reqs[rid].sample_index = i
+                rids.append(rid)
+            groups.append(rids)
+        total = len(reqs)
+
+        def merged(rids: list[str]) -> RequestOutput:
+            outs = [self.engine.make_output(reqs[r]) for r in rids]
+            first = outs[0]
+            for o in outs[1:]:
+                first.outputs.extend(o.outputs)
+                first.finished = first.finished and o.finished
+            return first
+
         done: dict[str, Request] = {}
         if self.engine.dp_sync:
             # keep stepping (padding steps once this replica is done) until every replica has finished its prompts
-            while any(self.engine._dp_group.all_gather_object(len(done) < n and self.engine.has_unfinished_requests())):
+            while any(self.engine._dp_group.all_gather_object(len(done) < total and self.engine.has_unfinished_requests())):
                 for r in self.engine.step():
                     if r.request_id in reqs:
                         done[r.request_id] = r
-            return [self.engine.make_output(reqs[rid]) for rid in order]
-        while len(done) < n:
+            return [merged(g) for g in groups]
+        while len(done) < total:
             for r in self.engine.step():
                 if r.request_id in reqs:
                     done[r.request_id] = r
-            if not self.engine.has_unfinished_requests() and len(done) < n:
+            if not self.engine.has_unfinished_requests() and len(done) < total:
                 break
-        return [self.engine.make_output(reqs[rid]) for rid in order]
+        return [merged(g) for g in groups]
 
     # ------------------------------------------------------------------ chat / pooling / scoring
     def chat(self, messages, sampling_params: Optional[SamplingParams] = None,

@@ -22,6 +22,12 @@ class SamplingParams:
     stop_token_ids: list[int] = field(default_factory=list)
     min_tokens: int = 0
     logprobs: Optional[int] = None
+    n: int = 1                                  # completions per prompt (independent samples; seed + i when seeded)
+    stop: list = field(default_factory=list)    # stop STRINGS: generation ends when the output text contains one
+    include_stop_str_in_output: bool = False
+    bad_words: list = field(default_factory=list)   # strings (need a tokenizer) or token-id lists never to be produced
+    skip_special_tokens: bool = True
+    truncate_prompt_tokens: Optional[int] = None    # keep only the last k prompt tokens
     # constrained decoding (engine/structured.py)
     allowed_token_ids: Optional[list[int]] = None
     logit_bias: Optional[dict] = None
@@ -40,12 +46,37 @@ class SamplingParams:
             from .structured import TokenTrie, resolve_choices
 
             self._trie = TokenTrie(resolve_choices(self.guided_choice, tokenizer))
+        if self.bad_words and getattr(self, "_bad_seqs", None) is None:
+            seqs = []
+            for w in self.bad_words:
+                if isinstance(w, str):
+                    if tokenizer is None:
+                        raise ValueError("bad_words given as strings need a tokenizer")
+                    # a word is banned with and without a leading space (both tokenisations occur in running text)
+                    for form in (w, " " + w.lstrip()):
+                        ids = list(tokenizer.encode(form, add_special_tokens=False))
+                        if ids and ids not in seqs:
+                            seqs.append(ids)
+                else:
+                    ids = [int(t) for t in w]
+                    if ids and ids not in seqs:
+                        seqs.append(ids)
+            self._bad_seqs = seqs
         return self
+
+    def banned_next_tokens(self, output_token_ids: list) -> list:
+        """Tokens that would complete one of the ``bad_words`` sequences given what has been produced."""
+        out = []
+        for seq in getattr(self, "_bad_seqs", None) or ():
+            k = len(seq) - 1
+            if k == 0 or (len(output_token_ids) >= k and output_token_ids[-k:] == seq[:-1]):
+                out.append(seq[-1])
+        return out
 
     @property
     def constrained(self) -> bool:
         return (bool(self.allowed_token_ids) or bool(self.logit_bias) or self.guided_choice is not None
-                or self.guided_regex is not None or self.guided_json is not None)
+                or self.guided_regex is not None or self.guided_json is not None or bool(self.bad_words))
 
     @property
     def greedy(self) -> bool:
@@ -74,13 +105,18 @@ class Request:
 
     __slots__ = ("request_id", "prompt_token_ids", "params", "output_token_ids", "status", "block_ids",
                  "num_computed_tokens", "arrival_time", "first_token_time", "finish_time", "token_times",
-                 "eos_token_id", "num_cached_tokens", "logprobs", "prompt", "_hashes", "spec_token_ids", "lora_request", "mm_embeds", "mm_positions", "mm_hash", "_sample_rng", "finishing", "mrope_positions", "mrope_delta")
+                 "eos_token_id", "num_cached_tokens", "logprobs", "prompt", "_hashes", "spec_token_ids", "lora_request", "mm_embeds", "mm_positions", "mm_hash", "_sample_rng", "finishing", "mrope_positions", "mrope_delta", "stop_checker", "stop_reason",
+                 "parent_id", "sample_index")
 
     def __init__(self, request_id: str, prompt_token_ids: list[int], params: SamplingParams,
                  eos_token_id: Optional[int] = None, prompt: Optional[str] = None,
                  arrival_time: Optional[float] = None):
         self.request_id = request_id
         self._sample_rng = None
+        self.stop_checker = None               # StopStringChecker when params.stop is set and a tokenizer is attached
+        self.stop_reason = None                # the stop string / stop token id that ended the request
+        self.parent_id = None                  # n > 1: the id the samples are reported under ...
+        self.sample_index = 0                  # ... and this sample's index
         self.finishing = False                 # its last token (by length) is being computed: not scheduled again
         self.mrope_positions = None            # [3, prompt] multimodal rotary position streams (Qwen2-VL family) ...
         self.mrope_delta = 0                   # ... and the offset of generated tokens' stream value from their position
@@ -148,9 +184,61 @@ class Request:
             if (not p.ignore_eos and self.eos_token_id is not None and last == self.eos_token_id) or \
                     last in p.stop_token_ids:
                 self.status = RequestStatus.FINISHED_STOPPED
+                if last in p.stop_token_ids:
+                    self.stop_reason = last
                 return
+            if self.stop_checker is not None and last >= 0:
+                hit = self.stop_checker.step(self.output_token_ids)
+                if hit is not None:
+                    self.status = RequestStatus.FINISHED_STOPPED
+                    self.stop_reason = hit
+                    return
         if n_out >= p.max_tokens:
             self.status = RequestStatus.FINISHED_LENGTH
+
+
+class StopStringChecker:
+    """Incremental detokeniser + stop-string search for one request.  ``step`` is called after every new token with
+    the whole output; it decodes only the tokens since the last stable boundary (a token sequence can end inside a
+    multi-byte character, which decodes to U+FFFD until the rest arrives) and searches the tail of the text.  On a
+    hit, ``text`` is cut before the stop string (after it with ``include``)."""
+
+    def __init__(self, tokenizer, stops: list, include: bool = False, skip_special_tokens: bool = True):
+        self.tok, self.stops, self.include, self.skip = tokenizer, [s for s in stops if s], include, skip_special_tokens
+        self.max_len = max((len(s) for s in self.stops), default=0)
+        self.text = ""
+        self.prefix = 0          # tokens before this offset are fully emitted
+        self.read = 0            # tokens before this offset have been decoded as context
+        self.hit: Optional[str] = None
+
+    def _decode(self, ids) -> str:
+        return self.tok.decode(list(ids), skip_special_tokens=self.skip)
+
+    def step(self, output_token_ids: list) -> Optional[str]:
+        if self.hit is not None:
+            return self.hit
+        ids = output_token_ids
+        if len(ids) <= self.read:
+            return None
+        before = self._decode(ids[self.prefix:self.read]) if self.read > self.prefix else ""
+        now = self._decode(ids[self.prefix:])
+        if len(now) <= len(before) or now.endswith("\ufffd"):
+            return None                       # nothing printable yet (incomplete character): wait for more tokens
+        delta = now[len(before):]
+        self.prefix, self.read = self.read, len(ids)
+        start = max(0, len(self.text) - self.max_len + 1)
+        self.text += delta
+        best = None
+        for s in self.stops:
+            i = self.text.find(s, start)
+            if i >= 0 and (best is None or i < best[0]):
+                best = (i, s)
+        if best is None:
+            return None
+        i, s = best
+        self.text = self.text[: i + len(s)] if self.include else self.text[:i]
+        self.hit = s
+        return s
 
 
 @dataclass
@@ -160,6 +248,7 @@ class CompletionOutput:
     text: Optional[str]
     finish_reason: Optional[str]
     logprobs: Optional[list] = None
+    stop_reason: object = None            # the stop string or stop token id that ended the completion (None: EOS / length)
 
 
 @dataclass

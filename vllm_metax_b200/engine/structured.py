@@ -295,11 +295,14 @@ def apply_constraints(logits: torch.Tensor, reqs) -> torch.Tensor:
         p = r.params
         allowed = constraint_of(r)
         guide = getattr(p, "_guide", None)
-        if allowed is None and not p.logit_bias and guide is None:
+        banned = p.banned_next_tokens(r.output_token_ids) if getattr(p, "_bad_seqs", None) else []
+        if allowed is None and not p.logit_bias and guide is None and not banned:
             continue
         if not touched:
             logits = logits.float().clone()
             touched = True
+        if banned:                                       # bad_words: the token that would complete a banned sequence
+            logits[i][torch.tensor(banned, dtype=torch.long, device=logits.device)] = float("-inf")
         if p.logit_bias:
             idx = torch.tensor(list(p.logit_bias.keys()), dtype=torch.long, device=logits.device)
             val = torch.tensor(list(p.logit_bias.values()), dtype=torch.float32, device=logits.device)

@@ -129,8 +129,15 @@ class AsyncLLM:
                 self.metrics["generated_tokens"] += len(new)
                 st.sent = n
                 out = eng.make_output(r) if fin else None
-                text = out.outputs[0].text if out is not None else (
-                    eng.tokenizer.decode(r.output_token_ids, skip_special_tokens=True) if eng.tokenizer else None)
+                if out is not None:
+                    text = out.outputs[0].text
+                elif r.stop_checker is not None:
+                    # hold back what could still turn out to be the beginning of a stop string
+                    t, hold = r.stop_checker.text, r.stop_checker.max_len - 1
+                    text = t[: max(0, len(t) - hold)] if hold > 0 else t
+                else:
+                    text = (eng.tokenizer.decode(r.output_token_ids, skip_special_tokens=r.params.skip_special_tokens)
+                            if eng.tokenizer else None)
                 self._post(st, StreamChunk(rid, new, list(r.output_token_ids), text, fin,
                                            out.outputs[0].finish_reason if out else None, len(r.prompt_token_ids),
                                            ttft=None if st.t_first is None else st.t_first - st.t_arrival,

@@ -8,6 +8,7 @@ Parity: the reference is served by ``vllm serve`` (OpenAI API server + ``vllm be
 tools/batched_test/bench_sweep.sh:3-14); sampling defaults follow patch/enhancement/chores/bench_serve_args.py:284-292
 (temperature 0 unless the request sets one).
 """
+import asyncio
 import json
 import time
 import uuid
@@ -40,6 +41,16 @@ def sampling_from_request(body: dict, default_max_tokens: int = 16) -> SamplingP
         kw["logprobs"] = int(body.get("top_logprobs") or 0) if lp is True else int(lp)
     if stop:
         kw["stop"] = list(stop)
+    if body.get("include_stop_str_in_output"):
+        kw["include_stop_str_in_output"] = True
+    if body.get("bad_words"):
+        kw["bad_words"] = list(body["bad_words"])
+    if body.get("min_tokens"):
+        kw["min_tokens"] = int(body["min_tokens"])
+    if body.get("skip_special_tokens") is False:
+        kw["skip_special_tokens"] = False
+    if body.get("truncate_prompt_tokens"):
+        kw["truncate_prompt_tokens"] = int(body["truncate_prompt_tokens"])
     if body.get("stop_token_ids"):
         kw["stop_token_ids"] = list(body["stop_token_ids"])
     so = body.get("structured_outputs") or {}
@@ -316,11 +327,23 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
         rid = ("chatcmpl-" if chat else "cmpl-") + uuid.uuid4().hex[:16]
         created = int(time.time())
         obj = "chat.completion" if chat else "text_completion"
-        if not body.get("stream"):
-            try:
-                last = await run_one(ids, prompt, params, rid, traceparent)
-            except EngineDeadError as e:
-                return err(500, str(e), "engine_dead")
+        n_samples = max(1, int(body.get("n") or 1))
+        if n_samples > 1 and body.get("stream"):
+            return err(400, "n > 1 is served for non-streaming requests only")
+
+        def sample_params(i: int):
+            if n_samples == 1:
+                return params
+            import copy
+
+            p_i = copy.copy(params)                     # independent samples; a seeded request stays reproducible
+            p_i.seed = None if params.seed is None else params.seed + i
+            for extra in ("_multi_modal_data", "_lora_request"):
+                if hasattr(params, extra):
+                    setattr(p_i, extra, getattr(params, extra))
+            return p_i
+
+        def build_choice(i: int, last) -> dict:
             text = last.text if last.text is not None else ""
             if chat:
                 msg = parse_chat_output(text, tool_parser, think_parser, bool(tools), forced_tool)
@@ -331,13 +354,21 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
                 if msg.tool_calls:
                     message["tool_calls"] = [c.to_openai() for c in msg.tool_calls]
                     finish = "tool_calls" if forced_tool is None else finish
-                choice = {"index": 0, "message": message, "finish_reason": finish,
-                          "logprobs": format_logprobs(last.logprobs, tok, True)}
-            else:
-                choice = {"index": 0, "text": text, "token_ids": last.token_ids,
-                          "logprobs": format_logprobs(last.logprobs, tok, False), "finish_reason": last.finish_reason}
-            return {"id": rid, "object": obj, "created": created, "model": served_model_name, "choices": [choice],
-                    "usage": usage(len(ids), len(last.token_ids))}
+                return {"index": i, "message": message, "finish_reason": finish,
+                        "logprobs": format_logprobs(last.logprobs, tok, True)}
+            return {"index": i, "text": text, "token_ids": last.token_ids,
+                    "logprobs": format_logprobs(last.logprobs, tok, False), "finish_reason": last.finish_reason}
+
+        if not body.get("stream"):
+            try:
+                lasts = await asyncio.gather(*[
+                    run_one(ids, prompt, sample_params(i), rid if n_samples == 1 else f"{rid}-{i}", traceparent)
+                    for i in range(n_samples)])
+            except EngineDeadError as e:
+                return err(500, str(e), "engine_dead")
+            return {"id": rid, "object": obj, "created": created, "model": served_model_name,
+                    "choices": [build_choice(i, last) for i, last in enumerate(lasts)],
+                    "usage": usage(len(ids), sum(len(last.token_ids) for last in lasts))}
 
         # with a tool or reasoning parser the markup has to be complete before it can be split, so such a stream
         # carries the parsed message in its last chunk; plain chats stream token by token
