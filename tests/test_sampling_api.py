@@ -164,3 +164,44 @@ def test_server_stop_and_n(llm):
         assert asyncio.run(stream()) == free[:free.index(stop)]
     finally:
         allm.shutdown()
+
+
+def test_beam_search_finds_a_more_likely_sequence_than_greedy(llm):
+    """Against an exhaustive oracle on a short horizon: the best beam (width = all candidates that matter) has the
+    highest total log-probability, and it is at least as likely as the greedy continuation."""
+    from vllm_metax_b200 import SamplingParams
+
+    prompt = "Q: ok?"
+    beams = llm.beam_search([prompt], beam_width=4, max_tokens=3, ignore_eos=True)[0]
+    assert len(beams) == 4 and all(len(b["token_ids"]) == 3 for b in beams)
+    assert beams == sorted(beams, key=lambda b: -b["score"])
+    greedy = llm.generate([prompt], SamplingParams(max_tokens=3, temperature=0.0, logprobs=1, ignore_eos=True))[0].outputs[0]
+    g_lp = sum(e["logprob"] for e in greedy.logprobs)
+    assert beams[0]["cum_logprob"] >= g_lp - 1e-4
+    assert any(b["token_ids"] == greedy.token_ids for b in beams) or beams[-1]["cum_logprob"] > g_lp
+    # the reported log-probability of the best beam is what the model assigns to it token by token
+    ids = llm._to_ids(prompt)[0]
+    total = 0.0
+    for i, t in enumerate(beams[0]["token_ids"]):
+        o = llm.generate([ids + beams[0]["token_ids"][:i]], SamplingParams(max_tokens=1, logprobs=8, ignore_eos=True))[0]
+        top = dict(o.outputs[0].logprobs[0]["top"])
+        total += top[t]
+    assert abs(total - beams[0]["cum_logprob"]) < 1e-3
+
+
+def test_prompt_logprobs_match_step_by_step_scoring(llm):
+    """Chunked over several prefill steps (the prompt is longer than the step budget) and equal to what one decode
+    step per prefix reports."""
+    from vllm_metax_b200 import SamplingParams
+
+    g = torch.Generator().manual_seed(2)
+    ids = torch.randint(0, 95, (90,), generator=g).tolist()          # 90 tokens > the 64-token step budget
+    got = llm.prompt_logprobs([ids, ids[:7]], top=3)
+    assert got[0][0] is None and len(got[0]) == 90 and len(got[1]) == 7
+    assert [e["token_id"] for e in got[0][1:]] == ids[1:]
+    for k in (1, 5, 63, 64, 65, 89):                                  # around the chunk boundary too
+        o = llm.generate([ids[:k]], SamplingParams(max_tokens=1, logprobs=1024, ignore_eos=True))[0]
+        want = dict(o.outputs[0].logprobs[0]["top"])[ids[k]]
+        assert abs(got[0][k]["logprob"] - want) < 1e-4, (k, got[0][k], want)
+        assert len(got[0][k]["top"]) == 3 and got[0][k]["top"][0][1] >= got[0][k]["logprob"] - 1e-6
+    assert abs(got[1][3]["logprob"] - got[0][3]["logprob"]) < 1e-4

@@ -524,6 +524,56 @@ class LLM:
                 break
         return [merged(g) for g in groups]
 
+    def beam_search(self, prompts: Union[str, Sequence], beam_width: int = 4, max_tokens: int = 16,
+                    length_penalty: float = 1.0, ignore_eos: bool = False) -> list:
+        """Beam search per prompt: every round extends all live beams by one token (one batched ``generate`` call
+        with ``max_tokens=1`` and the ``2 * beam_width`` most likely continuations; the prompt and the shared beam
+        prefixes are served from the prefix cache when it is on), keeps the ``beam_width`` best by cumulative
+        log-probability, and moves beams that produced the end-of-sequence token to the finished pool.  Returns, per
+        prompt, ``[{"token_ids", "text", "cum_logprob", "score"}, ...]`` best first; ``score`` is the cumulative
+        log-probability over ``len ** length_penalty``.  (Upstream's ``LLM.beam_search`` contract.)"""
+        if isinstance(prompts, str) or (prompts and isinstance(prompts[0], int)):
+            prompts = [prompts]
+        eos = self.engine.cfg.model.eos_token_id
+        results = []
+        sp = SamplingParams(max_tokens=1, temperature=0.0, logprobs=2 * beam_width, ignore_eos=True)
+
+        def score(cum: float, n: int) -> float:
+            return cum / (max(n, 1) ** length_penalty)
+
+        for p in prompts:
+            base, _ = self._to_ids(p)
+            live = [([], 0.0)]                       # (generated tokens, cumulative log-probability)
+            finished = []
+            for _ in range(max_tokens):
+                if not live:
+                    break
+                outs = self.generate([list(base) + toks for toks, _ in live], sp)
+                cand = []
+                for (toks, cum), o in zip(live, outs):
+                    for t, lp in o.outputs[0].logprobs[0]["top"]:
+                        cand.append((toks + [t], cum + lp))
+                cand.sort(key=lambda c: -c[1])
+                live = []
+                for toks, cum in cand:
+                    if not ignore_eos and eos is not None and toks[-1] == eos:
+                        finished.append((toks, cum))
+                    else:
+                        live.append((toks, cum))
+                    if len(live) >= beam_width:
+                        break
+                # a finished beam that already beats every live one cannot be overtaken (log-probabilities only fall)
+                if finished and live and len(finished) >= beam_width and \
+                        max(score(c, len(t)) for t, c in finished) >= max(score(c, len(t)) for t, c in live) \
+                        and length_penalty <= 1.0:
+                    break
+            pool = finished + live
+            pool.sort(key=lambda b: -score(b[1], len(b[0])))
+            tok = self.tokenizer
+            results.append([{"token_ids": t, "text": tok.decode(t, skip_special_tokens=True) if tok is not None else None,
+                             "cum_logprob": c, "score": score(c, len(t))} for t, c in pool[:beam_width]])
+        return results
+
     # ------------------------------------------------------------------ chat / pooling / scoring
     def chat(self, messages, sampling_params: Optional[SamplingParams] = None,
              add_generation_prompt: bool = True) -> list[RequestOutput]:
@@ -596,6 +646,38 @@ class LLM:
         return torch.nn.functional.normalize(e, dim=-1) if normalize else e
 
     encode = embed
+
+    def prompt_logprobs(self, prompts: Union[str, Sequence], top: int = 0) -> list:
+        """Log-probability the model assigns to every prompt token given the tokens before it (the ``prompt_logprobs``
+        of upstream's sampling parameters; what perplexity / scoring harnesses read).  Per prompt a list with one
+        entry per position: ``None`` for the first token, then ``{"token_id", "logprob", "top": [(id, lp), ...]}``.
+        The hidden states of every prefill chunk go through the LM head as they are computed, so nothing of size
+        ``[prompt, vocab]`` is kept."""
+        if isinstance(prompts, str) or (prompts and isinstance(prompts[0], int)):
+            prompts = [prompts]
+        ids = [self._to_ids(p)[0] for p in prompts]
+        out: list = [[None] for _ in ids]
+        pos = [0] * len(ids)
+        model = self.engine.runner.model
+
+        def visit(i, rows, is_last):
+            n0, toks = pos[i], ids[i]
+            n = min(rows.shape[0], len(toks) - 1 - n0)          # row j predicts token n0 + j + 1
+            pos[i] = n0 + rows.shape[0]
+            if n <= 0:
+                return
+            lp = torch.log_softmax(model.compute_logits(rows[:n]).float(), dim=-1)
+            nxt = torch.as_tensor(toks[n0 + 1: n0 + 1 + n], dtype=torch.int64, device=lp.device)
+            chosen = lp.gather(1, nxt[:, None])[:, 0].cpu().tolist()
+            tv, ti = (lp.topk(min(top, lp.shape[1]), dim=-1) if top > 0 else (None, None))
+            tv = tv.cpu().tolist() if tv is not None else None
+            ti = ti.cpu().tolist() if ti is not None else None
+            for j in range(n):
+                out[i].append({"token_id": toks[n0 + 1 + j], "logprob": float(chosen[j]),
+                               "top": [(int(a), float(b)) for a, b in zip(ti[j], tv[j])] if top > 0 else []})
+
+        self._run_capturing(ids, visit)
+        return out
 
     def score(self, text_1: Union[str, Sequence], text_2: Union[str, Sequence], pooling: str = "last") -> list[float]:
         """Cosine similarity of the embeddings of ``text_1`` (one prompt, or one per pair) and every ``text_2``."""
