@@ -245,3 +245,65 @@ def test_chat_with_tools_and_reasoning_parsers():
         assert code == 400 and "unknown function" in text
     finally:
         allm.shutdown()
+
+
+def test_pooling_and_admin_endpoints(client_app):
+    """Embeddings / score / rerank / classify run on the engine thread while the server keeps generating; the
+    answers equal the offline API."""
+    pytest.importorskip("httpx")
+    allm, app = client_app
+    llm = allm.llm
+    texts = ["hello world", "another sentence here", "hello world"]
+    code, text = _call(app, "POST", "/v1/embeddings", {"input": texts})
+    res = json.loads(text)
+    assert code == 200 and [d["index"] for d in res["data"]] == [0, 1, 2]
+    emb = torch.tensor([d["embedding"] for d in res["data"]])
+    assert emb.shape == (3, 64) and torch.allclose(emb.norm(dim=-1), torch.ones(3), atol=1e-4)
+    assert torch.allclose(emb[0], emb[2], atol=1e-5) and not torch.allclose(emb[0], emb[1], atol=1e-3)
+    assert res["usage"]["prompt_tokens"] == sum(len(llm.tokenizer.encode(t)) for t in texts)
+    code, text = _call(app, "POST", "/v1/embeddings", {"input": "hello world", "dimensions": 16, "encoding_format": "base64"})
+    import base64
+
+    import numpy as np
+    small = np.frombuffer(base64.b64decode(json.loads(text)["data"][0]["embedding"]), dtype=np.float32)
+    assert small.shape == (16,) and abs(float(np.linalg.norm(small)) - 1.0) < 1e-4
+    code, text = _call(app, "POST", "/score", {"text_1": "hello world", "text_2": ["hello world", "zzz qqq"]})
+    sc = [d["score"] for d in json.loads(text)["data"]]
+    assert code == 200 and abs(sc[0] - 1.0) < 1e-4 and sc[1] < sc[0]
+    code, text = _call(app, "POST", "/v1/rerank", {"query": "hello world", "documents": ["zzz qqq", "hello world", "abc"],
+                                                   "top_n": 2})
+    rr = json.loads(text)["results"]
+    assert code == 200 and len(rr) == 2 and rr[0]["index"] == 1 and rr[0]["document"]["text"] == "hello world"
+    assert rr[0]["relevance_score"] >= rr[1]["relevance_score"]
+    code, text = _call(app, "POST", "/classify", {"input": ["good", "bad"], "class_token_ids": [5, 9, 11]})
+    cl = json.loads(text)["data"]
+    assert code == 200 and len(cl) == 2 and abs(sum(cl[0]["probs"]) - 1.0) < 1e-4 and cl[0]["num_classes"] == 3
+    assert _call(app, "POST", "/classify", {"input": "x", "class_token_ids": [1]})[0] == 400
+    assert _call(app, "POST", "/v1/embeddings", {"input": []})[0] == 400
+    assert json.loads(_call(app, "GET", "/version")[1])["version"]
+    assert _call(app, "GET", "/ping")[0] == 200
+    assert _call(app, "POST", "/reset_prefix_cache")[0] == 200
+    assert _call(app, "POST", "/v1/load_lora_adapter", {"lora_name": "a", "lora_path": "/x"})[0] == 400   # no --enable-lora
+    assert _call(app, "POST", "/v1/unload_lora_adapter", {"lora_name": "nope"})[0] == 404
+
+
+def test_embeddings_while_generating(client_app):
+    """A generation request that is in flight when an embedding call takes the engine still finishes with the same
+    tokens."""
+    pytest.importorskip("httpx")
+    import httpx
+
+    allm, app = client_app
+    body = {"prompt": "the quick brown fox", "max_tokens": 40}
+    want = json.loads(_call(app, "POST", "/v1/completions", body)[1])["choices"][0]["token_ids"]
+
+    async def go():
+        transport = httpx.ASGITransport(app=app)
+        async with httpx.AsyncClient(transport=transport, base_url="http://test") as c:
+            gen = asyncio.create_task(c.post("/v1/completions", json=body))
+            await asyncio.sleep(0.02)
+            embs = await asyncio.gather(*[c.post("/v1/embeddings", json={"input": ["abc def", "ghi"]}) for _ in range(3)])
+            return await gen, embs
+    gen, embs = asyncio.run(go())
+    assert gen.status_code == 200 and json.loads(gen.text)["choices"][0]["token_ids"] == want
+    assert all(e.status_code == 200 and len(json.loads(e.text)["data"]) == 2 for e in embs)

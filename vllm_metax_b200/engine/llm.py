@@ -453,6 +453,7 @@ class LLM:
         self.config = cfg
         self.engine = LLMEngine(cfg, tokenizer or tok)
         self.tokenizer = self.engine.tokenizer
+        self.foreign_finished: list = []       # see _run_capturing
 
     # ------------------------------------------------------------------ generate
     def _to_ids(self, p) -> tuple[list[int], Optional[str]]:
@@ -617,7 +618,9 @@ class LLM:
         use_graphs, runner.use_graphs = runner.use_graphs, False      # every step must expose its hidden states
         try:
             while any(r in self.engine.requests for r in rid_to_idx):
-                self.engine.step()
+                for r in self.engine.step():
+                    if r.request_id not in rid_to_idx:        # a generation request of a serving front end that
+                        self.foreign_finished.append(r)       # finished during these steps: handed back to it
         finally:
             runner.execute, runner.keep_hidden, runner.use_graphs = orig, prev_keep, use_graphs
 

@@ -57,6 +57,7 @@ class AsyncLLM:
         self.histograms = latency_histograms()
         self._inbox: list[tuple] = []
         self._aborts: list[str] = []
+        self._calls: list[tuple] = []          # (callable, future, loop): work that must run on the engine thread
         self._lock = threading.Lock()
         self._wake = threading.Event()
         self._streams: dict[str, _Stream] = {}
@@ -96,6 +97,18 @@ class AsyncLLM:
                     self.metrics["prompt_tokens"] += len(ids)
                 except BaseException as e:
                     self._post(st, StreamChunk(rid, [], [], None, True, "error", error=e))
+            with self._lock:
+                calls, self._calls = self._calls, []
+            for fn, fut, loop in calls:
+                # e.g. embeddings: the call steps the engine itself until its own requests are done; generation
+                # requests that finish meanwhile come back through ``llm.foreign_finished``
+                try:
+                    res, exc = fn(), None
+                except BaseException as e:  # noqa: BLE001
+                    res, exc = None, e
+                loop.call_soon_threadsafe(self._resolve, fut, res, exc)
+                foreign, self.llm.foreign_finished = self.llm.foreign_finished, []
+                self._dispatch(foreign)
             if not eng.has_unfinished_requests() or eng.scheduler.paused:
                 self._wake.wait(timeout=0.05)
                 self._wake.clear()
@@ -105,52 +118,79 @@ class AsyncLLM:
             except BaseException as e:
                 self._fail_all(e if isinstance(e, EngineDeadError) else EngineDeadError(repr(e)))
                 continue
-            now = time.perf_counter()
-            done = {r.request_id: r for r in finished}
-            for rid, st in list(self._streams.items()):
-                r = done.get(rid) or eng.requests.get(rid)
-                if r is None:
-                    continue
-                n = len(r.output_token_ids)
-                fin = rid in done
-                if n == st.sent and not fin:
-                    continue
-                if st.t_first is None and n > 0:
-                    st.t_first = now
-                    self.metrics["ttft_sum"] += now - st.t_arrival
-                    self.metrics["ttft_count"] += 1
-                    self.histograms["ttft"].observe(now - st.t_arrival)
-                elif n > st.sent and st.t_last is not None:
-                    for _ in range(n - st.sent):
-                        self.histograms["itl"].observe((now - st.t_last) / (n - st.sent))
-                if n > st.sent:
-                    st.t_last = now
-                new = list(r.output_token_ids[st.sent:n])
-                self.metrics["generated_tokens"] += len(new)
-                st.sent = n
-                out = eng.make_output(r) if fin else None
-                if out is not None:
-                    text = out.outputs[0].text
-                elif r.stop_checker is not None:
-                    # hold back what could still turn out to be the beginning of a stop string
-                    t, hold = r.stop_checker.text, r.stop_checker.max_len - 1
-                    text = t[: max(0, len(t) - hold)] if hold > 0 else t
-                else:
-                    text = (eng.tokenizer.decode(r.output_token_ids, skip_special_tokens=r.params.skip_special_tokens)
-                            if eng.tokenizer else None)
-                self._post(st, StreamChunk(rid, new, list(r.output_token_ids), text, fin,
-                                           out.outputs[0].finish_reason if out else None, len(r.prompt_token_ids),
-                                           ttft=None if st.t_first is None else st.t_first - st.t_arrival,
-                                           logprobs=list(r.logprobs) if r.params.logprobs is not None else None))
-                if fin:
-                    self.metrics["requests_finished"] += 1
-                    self.histograms["e2e"].observe(now - st.t_arrival)
-                    if self.tracer is not None:
-                        self.tracer.finish(rid, arrival_wall=st.wall_arrival, t_arrival=st.t_arrival, t_first=st.t_first,
-                                           t_end=now, prompt_tokens=len(r.prompt_token_ids), completion_tokens=n,
-                                           params=st.params, finish_reason=out.outputs[0].finish_reason,
-                                           traceparent=st.traceparent, cached_tokens=r.num_cached_tokens)
-                    del self._streams[rid]
+            self._dispatch(finished)
+
+    @staticmethod
+    def _resolve(fut, res, exc) -> None:
+        if fut.cancelled():
+            return
+        if exc is not None:
+            fut.set_exception(exc)
+        else:
+            fut.set_result(res)
+
+    def _dispatch(self, finished) -> None:
+        """Post the new tokens of every stream (and the final chunk of the requests in ``finished``)."""
+        eng = self.engine
+        now = time.perf_counter()
+        done = {r.request_id: r for r in finished}
+        for rid, st in list(self._streams.items()):
+            r = done.get(rid) or eng.requests.get(rid)
+            if r is None:
+                continue
+            n = len(r.output_token_ids)
+            fin = rid in done
+            if n == st.sent and not fin:
+                continue
+            if st.t_first is None and n > 0:
+                st.t_first = now
+                self.metrics["ttft_sum"] += now - st.t_arrival
+                self.metrics["ttft_count"] += 1
+                self.histograms["ttft"].observe(now - st.t_arrival)
+            elif n > st.sent and st.t_last is not None:
+                for _ in range(n - st.sent):
+                    self.histograms["itl"].observe((now - st.t_last) / (n - st.sent))
+            if n > st.sent:
+                st.t_last = now
+            new = list(r.output_token_ids[st.sent:n])
+            self.metrics["generated_tokens"] += len(new)
+            st.sent = n
+            out = eng.make_output(r) if fin else None
+            if out is not None:
+                text = out.outputs[0].text
+            elif r.stop_checker is not None:
+                # hold back what could still turn out to be the beginning of a stop string
+                t, hold = r.stop_checker.text, r.stop_checker.max_len - 1
+                text = t[: max(0, len(t) - hold)] if hold > 0 else t
+            else:
+                text = (eng.tokenizer.decode(r.output_token_ids, skip_special_tokens=r.params.skip_special_tokens)
+                        if eng.tokenizer else None)
+            self._post(st, StreamChunk(rid, new, list(r.output_token_ids), text, fin,
+                                       out.outputs[0].finish_reason if out else None, len(r.prompt_token_ids),
+                                       ttft=None if st.t_first is None else st.t_first - st.t_arrival,
+                                       logprobs=list(r.logprobs) if r.params.logprobs is not None else None))
+            if fin:
+                self.metrics["requests_finished"] += 1
+                self.histograms["e2e"].observe(now - st.t_arrival)
+                if self.tracer is not None:
+                    self.tracer.finish(rid, arrival_wall=st.wall_arrival, t_arrival=st.t_arrival, t_first=st.t_first,
+                                       t_end=now, prompt_tokens=len(r.prompt_token_ids), completion_tokens=n,
+                                       params=st.params, finish_reason=out.outputs[0].finish_reason,
+                                       traceparent=st.traceparent, cached_tokens=r.num_cached_tokens)
+                del self._streams[rid]
+
+
+    async def call(self, fn):
+        """Run ``fn()`` on the engine thread between two steps and return its result (pooling requests, anything that
+        drives the engine itself)."""
+        if self.engine.dead is not None:
+            raise EngineDeadError(str(self.engine.dead))
+        loop = asyncio.get_running_loop()
+        fut = loop.create_future()
+        with self._lock:
+            self._calls.append((fn, fut, loop))
+        self._wake.set()
+        return await fut
 
     # ------------------------------------------------------------------ coroutine API
     async def generate(self, prompt_token_ids: Sequence[int], params: SamplingParams, request_id: Optional[str] = None,

@@ -12,6 +12,8 @@ import asyncio
 import json
 import time
 import uuid
+
+import torch
 from typing import Any, Optional
 
 from ..engine.llm import EngineDeadError
@@ -414,6 +416,146 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
             yield "data: [DONE]\n\n"
 
         return StreamingResponse(sse(), media_type="text/event-stream")
+
+    # ---- pooling endpoints: embeddings, similarity scores, re-ranking (they drive the engine from its own thread)
+    def many(x) -> list:
+        """``str | [int] -> [x]``; ``[str] | [[int]]`` stay lists."""
+        if isinstance(x, str) or (isinstance(x, list) and x and isinstance(x[0], int)):
+            return [x]
+        if not isinstance(x, list) or not x:
+            raise ValueError("input must be a string, a list of strings, or token ids")
+        return list(x)
+
+    def count_tokens(items: list) -> int:
+        return sum(len(encode(i)[0]) for i in items)
+
+    @app.post("/v1/embeddings")
+    async def embeddings(req: Request):
+        body = await req.json()
+        try:
+            items = many(body.get("input"))
+            ntok = count_tokens(items)
+            pooling = body.get("pooling", "last")
+            normalize = bool(body.get("normalize", True))
+            emb = await allm.call(lambda: llm.embed(items, pooling=pooling, normalize=normalize))
+        except EngineDeadError as e:
+            return err(500, str(e), "engine_dead")
+        except Exception as e:  # noqa: BLE001
+            return err(400, str(e))
+        dims = body.get("dimensions")
+        if dims:                                   # matryoshka-style truncation + renormalisation
+            emb = torch.nn.functional.normalize(emb[:, : int(dims)], dim=-1) if normalize else emb[:, : int(dims)]
+        if body.get("encoding_format") == "base64":
+            import base64
+
+            import numpy as np
+
+            data = [base64.b64encode(np.asarray(e, dtype=np.float32).tobytes()).decode() for e in emb.tolist()]
+        else:
+            data = emb.tolist()
+        return {"id": "embd-" + uuid.uuid4().hex[:16], "object": "list", "model": served_model_name,
+                "data": [{"object": "embedding", "index": i, "embedding": e} for i, e in enumerate(data)],
+                "usage": {"prompt_tokens": ntok, "total_tokens": ntok}}
+
+    async def score_impl(body: dict):
+        t1 = body.get("text_1", body.get("query"))
+        t2 = body.get("text_2", body.get("documents"))
+        if t1 is None or t2 is None:
+            raise ValueError("text_1 and text_2 (or query and documents) are required")
+        one = isinstance(t1, str) or (isinstance(t1, list) and t1 and isinstance(t1[0], int))
+        docs = many(t2)
+        scores = await allm.call(lambda: llm.score(t1 if one else list(t1), docs))
+        return docs, [float(x) for x in scores], count_tokens(docs) + count_tokens([t1] if one else list(t1))
+
+    @app.post("/score")
+    @app.post("/v1/score")
+    async def score(req: Request):
+        try:
+            docs, scores, ntok = await score_impl(await req.json())
+        except EngineDeadError as e:
+            return err(500, str(e), "engine_dead")
+        except Exception as e:  # noqa: BLE001
+            return err(400, str(e))
+        return {"id": "score-" + uuid.uuid4().hex[:16], "object": "list", "model": served_model_name,
+                "data": [{"index": i, "object": "score", "score": x} for i, x in enumerate(scores)],
+                "usage": {"prompt_tokens": ntok, "total_tokens": ntok}}
+
+    @app.post("/rerank")
+    @app.post("/v1/rerank")
+    @app.post("/v2/rerank")
+    async def rerank(req: Request):
+        body = await req.json()
+        try:
+            docs, scores, ntok = await score_impl(body)
+        except EngineDeadError as e:
+            return err(500, str(e), "engine_dead")
+        except Exception as e:  # noqa: BLE001
+            return err(400, str(e))
+        order = sorted(range(len(docs)), key=lambda i: -scores[i])[: int(body.get("top_n") or len(docs))]
+        return {"id": "rerank-" + uuid.uuid4().hex[:16], "model": served_model_name,
+                "usage": {"total_tokens": ntok},
+                "results": [{"index": i, "document": {"text": docs[i] if isinstance(docs[i], str) else None},
+                             "relevance_score": scores[i]} for i in order]}
+
+    @app.post("/classify")
+    async def classify(req: Request):
+        """``class_token_ids``: the token whose logit stands for each class (label-token classification); answers the
+        softmax over them for every input."""
+        body = await req.json()
+        try:
+            items = many(body.get("input"))
+            ids = [int(t) for t in body.get("class_token_ids") or []]
+            if len(ids) < 2:
+                raise ValueError("class_token_ids needs at least two token ids")
+            probs = await allm.call(lambda: llm.classify(items, ids))
+        except EngineDeadError as e:
+            return err(500, str(e), "engine_dead")
+        except Exception as e:  # noqa: BLE001
+            return err(400, str(e))
+        return {"id": "classify-" + uuid.uuid4().hex[:16], "object": "list", "model": served_model_name,
+                "data": [{"index": i, "label": int(torch.as_tensor(p).argmax()), "probs": [float(x) for x in p],
+                          "num_classes": len(ids)} for i, p in enumerate(probs.tolist())]}
+
+    # ---- administration -------------------------------------------------------------------------------------------
+    @app.get("/version")
+    async def version():
+        from ..version import __version__
+
+        return {"version": __version__}
+
+    @app.get("/ping")
+    @app.post("/ping")
+    async def ping():
+        if llm.engine.dead is not None:
+            return err(500, str(llm.engine.dead), "engine_dead")
+        return {}
+
+    @app.post("/reset_prefix_cache")
+    async def reset_prefix_cache():
+        n = await allm.call(lambda: llm.engine.kv.reset_prefix_cache())
+        return {"status": "ok", "blocks_dropped": int(n or 0)}
+
+    @app.post("/v1/load_lora_adapter")
+    async def load_lora_adapter(req: Request):
+        body = await req.json()
+        name, path = body.get("lora_name"), body.get("lora_path")
+        if not name or not path:
+            return err(400, "lora_name and lora_path are required")
+        if getattr(llm.engine.runner, "lora", None) is None:
+            return err(400, "the server was started without --enable-lora")
+        from ..lora import LoRARequest
+
+        next_id = 1 + max([getattr(r, "lora_int_id", 0) for r in lora_modules.values()] + [0])
+        lora_modules[name] = LoRARequest(name, next_id, path)
+        return {"status": "ok", "lora_name": name}
+
+    @app.post("/v1/unload_lora_adapter")
+    async def unload_lora_adapter(req: Request):
+        name = (await req.json()).get("lora_name")
+        if name not in lora_modules:
+            return err(404, f"adapter {name!r} is not loaded", "model_not_found")
+        del lora_modules[name]
+        return {"status": "ok", "lora_name": name}
 
     @app.post("/v1/completions")
     async def completions(req: Request):
