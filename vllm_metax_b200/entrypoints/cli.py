@@ -19,6 +19,8 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--port", type=int, default=8000)
     s.add_argument("--served-model-name", default=None)
     s.add_argument("--tensor-parallel-size", "-tp", type=int, default=1)
+    s.add_argument("--data-parallel-size", "-dp", type=int, default=1,
+                   help="N single-GPU engine servers on ports port+1.. behind one balancing front on --port")
     s.add_argument("--dtype", default="bfloat16")
     s.add_argument("--kv-cache-dtype", default="auto")
     s.add_argument("--max-model-len", type=int, default=4096)
@@ -111,6 +113,14 @@ def main(argv=None) -> int:
                           "total_tok_s": (n_out + args.input_len * len(outs)) / dt}))
         return 0
     # serve
+    if getattr(args, "data_parallel_size", 1) > 1:
+        if args.tensor_parallel_size > 1:
+            raise SystemExit("--data-parallel-size replicas are single-GPU processes; for tensor-parallel replicas "
+                             "start one torchrun server per group and balance in front of them")
+        from .dp_front import run_front
+
+        return run_front(list(argv if argv is not None else sys.argv[1:]), args.host, args.port, args.data_parallel_size,
+                         on_gpu=args.device != "cpu")
     import uvicorn
 
     from ..parallel import state as ps
