@@ -12,6 +12,7 @@ backend builds its metadata from (vllm_metax/v1/attention/backends/flash_attn.py
 from __future__ import annotations
 
 import contextlib
+import threading
 from dataclasses import dataclass, field
 from typing import Any, Optional
 
@@ -57,30 +58,34 @@ class ForwardContext:
     extra: dict = field(default_factory=dict)
 
 
-_CTX: Optional[ForwardContext] = None
+class _Local(threading.local):
+    ctx: Optional[ForwardContext] = None
+
+
+_LOCAL = _Local()        # per thread: engines of one process that step on different threads do not see each other's step
 
 
 def get_forward_context() -> ForwardContext:
-    assert _CTX is not None, "forward context not set"
-    return _CTX
+    ctx = _LOCAL.ctx
+    assert ctx is not None, "forward context not set"
+    return ctx
 
 
 @contextlib.contextmanager
 def set_forward_context(ctx: ForwardContext):
-    global _CTX
-    prev = _CTX
-    _CTX = ctx
+    prev = _LOCAL.ctx
+    _LOCAL.ctx = ctx
     try:
         yield
     finally:
-        _CTX = prev
+        _LOCAL.ctx = prev
 
 
 def merge_multimodal_embeddings(h: torch.Tensor) -> torch.Tensor:
     """Overwrite the rows of image / audio placeholder tokens with the encoder's projected features (called by the text
     decoders right after their embedding lookup; a no-op for text-only steps).  The runner lists the rows of this
     step's chunk in ``extra["mm_rows"]`` and their features, in the same order, in ``extra["mm_embeds"]``."""
-    ctx = _CTX
+    ctx = _LOCAL.ctx
     md = ctx.attn_metadata if ctx is not None else None
     if md is None or "mm_embeds" not in md.extra:
         return h
