@@ -1,6 +1,7 @@
 """OpenAI-compatible server over a tiny random model on CPU (in-process ASGI client, no sockets)."""
 import asyncio
 import json
+import os
 
 import pytest
 import torch
@@ -307,3 +308,58 @@ def test_embeddings_while_generating(client_app):
     gen, embs = asyncio.run(go())
     assert gen.status_code == 200 and json.loads(gen.text)["choices"][0]["token_ids"] == want
     assert all(e.status_code == 200 and len(json.loads(e.text)["data"]) == 2 for e in embs)
+
+
+def test_chat_templates():
+    """The shipped Jinja templates render conversations (with tools, tool calls and tool results), and a server
+    started with one uses it instead of the tokenizer's."""
+    from vllm_metax_b200.entrypoints.openai_server import load_chat_template, render_chat
+
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "chat_templates")
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "weather in Paris?"}]
+    chatml = load_chat_template(os.path.join(root, "chatml.jinja"))
+    text = render_chat(None, msgs, chat_template=chatml)
+    assert text == "<|im_start|>system\nbe brief<|im_end|>\n<|im_start|>user\nweather in Paris?<|im_end|>\n<|im_start|>assistant\n"
+    assert render_chat(None, msgs, add_generation_prompt=False, chat_template=chatml).endswith("Paris?<|im_end|>\n")
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {"type": "object",
+                                                                                   "properties": {"city": {"type": "string"}}}}}]
+    convo = msgs + [{"role": "assistant", "content": "", "tool_calls": [
+        {"type": "function", "function": {"name": "get_weather", "arguments": {"city": "Paris"}}}]},
+        {"role": "tool", "content": "18 C"}]
+    hermes = render_chat(None, convo, tools=tools, chat_template=load_chat_template(os.path.join(root, "hermes_tools.jinja")))
+    assert '"name": "get_weather"' in hermes and "<tools>" in hermes and "<tool_response>\n18 C\n</tool_response>" in hermes
+    assert '<tool_call>\n{"name": "get_weather", "arguments": {"city": "Paris"}}\n</tool_call>' in hermes
+    from vllm_metax_b200.entrypoints.parsers import parse_hermes
+    call = parse_hermes(hermes[hermes.index("<|im_start|>assistant"):hermes.index("<|im_start|>user\n<tool_response>")]).tool_calls[0]
+    assert call.name == "get_weather" and json.loads(call.arguments) == {"city": "Paris"}      # what it renders, the parser reads
+    llama = render_chat(type("T", (), {"bos_token": "<|begin_of_text|>", "eos_token": ""})(), convo, tools=tools,
+                        chat_template=load_chat_template(os.path.join(root, "llama3_json_tools.jinja")))
+    assert llama.startswith("<|begin_of_text|><|start_header_id|>system<|end_header_id|>")
+    assert '{"name": "get_weather", "parameters": {"city": "Paris"}}<|eot_id|>' in llama
+    assert llama.endswith("<|start_header_id|>assistant<|end_header_id|>\n\n")
+    with pytest.raises(ValueError):
+        load_chat_template("no-such-file")
+    inline = load_chat_template("{% for m in messages %}[{{ m['role'] }}]{{ m['content'] }}{% endfor %}")
+    assert render_chat(None, msgs, chat_template=inline) == "[system]be brief[user]weather in Paris?"
+
+
+def test_server_uses_its_chat_template(client_app):
+    pytest.importorskip("httpx")
+    allm, _ = client_app
+    seen = {}
+    tok = allm.engine.tokenizer
+    orig = tok.encode
+
+    def spy(text, *a, **kw):
+        seen["text"] = text
+        return orig(text)
+    tok.encode = spy
+    try:
+        app = build_app(allm, "toy", chat_template="{% for m in messages %}<{{ m['role'] }}>{{ m['content'] }}{% endfor %}<bot>")
+        code, _ = _call(app, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3})
+        assert code == 200 and seen["text"] == "<user>hi<bot>"
+        code, _ = _call(app, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3,
+                                                              "chat_template": "{{ messages[0]['content'] }}!"})
+        assert code == 200 and seen["text"] == "hi!"
+    finally:
+        tok.encode = orig

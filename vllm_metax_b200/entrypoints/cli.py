@@ -44,6 +44,8 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--enable-auto-tool-choice", action="store_true", help="accepted for command-line compatibility: "
                    "tool_choice=auto is served whenever a tool-call parser is set")
     s.add_argument("--reasoning-parser", default=None, help="deepseek_r1 | qwen3 | glm45 | step3")
+    s.add_argument("--chat-template", default=None, help="Jinja chat template: a file (examples/chat_templates/) or "
+                   "the template text; replaces the tokenizer's own")
     s.add_argument("--kv-transfer-config", default=None, help="JSON, e.g. '{\"kv_connector\": \"SharedStorageConnector\", "
                    "\"kv_role\": \"kv_producer\", \"kv_connector_extra_config\": {\"shared_storage_path\": \"/dev/shm/kv\"}}'")
     b = sub.add_parser("bench", help="offline throughput / latency run (same engine, no HTTP)")
@@ -137,7 +139,8 @@ def main(argv=None) -> int:
 
     name = args.served_model_name or str(args.model)
     app = build_app(AsyncLLM(llm, RequestTracer.from_endpoint(args.otlp_traces_endpoint, name)), name, loras,
-                    tool_call_parser=args.tool_call_parser, reasoning_parser=args.reasoning_parser)
+                    tool_call_parser=args.tool_call_parser, reasoning_parser=args.reasoning_parser,
+                    chat_template=args.chat_template)
     uvicorn.run(app, host=args.host, port=args.port, log_level="info")
     return 0
 

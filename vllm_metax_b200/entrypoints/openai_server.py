@@ -72,7 +72,46 @@ def sampling_from_request(body: dict, default_max_tokens: int = 16) -> SamplingP
     return SamplingParams(**kw)
 
 
-def render_chat(tokenizer, messages: list[dict], add_generation_prompt: bool = True, tools: Optional[list] = None) -> str:
+def load_chat_template(arg: Optional[str]) -> Optional[str]:
+    """``--chat-template``: a file with a Jinja template, or the template text itself."""
+    if not arg:
+        return None
+    import os
+
+    if os.path.exists(arg):
+        with open(arg) as f:
+            return f.read()
+    if "{{" in arg or "{%" in arg:
+        return arg
+    raise ValueError(f"chat template {arg!r} is neither a file nor template text")
+
+
+_TEMPLATE_CACHE: dict = {}
+
+
+def _compile_template(text: str):
+    """Jinja in a sandbox, with the conventions chat templates rely on (``raise_exception``, ``tojson``,
+    whitespace control as in the tokenizers' own renderer)."""
+    t = _TEMPLATE_CACHE.get(text)
+    if t is None:
+        from jinja2.sandbox import ImmutableSandboxedEnvironment
+
+        def raise_exception(msg):
+            raise ValueError(f"chat template: {msg}")
+
+        env = ImmutableSandboxedEnvironment(trim_blocks=True, lstrip_blocks=True)
+        env.globals["raise_exception"] = raise_exception
+        env.filters["tojson"] = lambda x, **kw: json.dumps(x, ensure_ascii=False, **{k: v for k, v in kw.items() if k == "indent"})
+        t = _TEMPLATE_CACHE[text] = env.from_string(text)
+    return t
+
+
+def render_chat(tokenizer, messages: list[dict], add_generation_prompt: bool = True, tools: Optional[list] = None,
+                chat_template: Optional[str] = None) -> str:
+    if chat_template:        # the server's own template wins over the tokenizer's
+        return _compile_template(chat_template).render(
+            messages=messages, tools=tools or None, add_generation_prompt=add_generation_prompt,
+            bos_token=getattr(tokenizer, "bos_token", None) or "", eos_token=getattr(tokenizer, "eos_token", None) or "")
     if tokenizer is not None and getattr(tokenizer, "chat_template", None):
         kw = {"tools": tools} if tools else {}
         return tokenizer.apply_chat_template(messages, tokenize=False, add_generation_prompt=add_generation_prompt, **kw)
@@ -140,13 +179,15 @@ def format_logprobs(entries: Optional[list], tokenizer, chat: bool, start: int =
 
 
 def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_modules: Optional[dict] = None,
-              tool_call_parser: Optional[str] = None, reasoning_parser: Optional[str] = None):
+              tool_call_parser: Optional[str] = None, reasoning_parser: Optional[str] = None,
+              chat_template: Optional[str] = None):
     """``lora_modules``: adapter name -> ``LoRARequest``; a request whose ``model`` field names one runs with it.
     ``tool_call_parser`` / ``reasoning_parser``: names from ``entrypoints/parsers.py``; with them chat answers carry
     ``message.tool_calls`` / ``message.reasoning_content``."""
     from .parsers import get_reasoning_parser, get_tool_parser, parse_chat_output
 
     lora_modules = dict(lora_modules or {})
+    chat_template = load_chat_template(chat_template)       # file or text; None: the tokenizer's own template
     tool_parser, think_parser = get_tool_parser(tool_call_parser), get_reasoning_parser(reasoning_parser)
     from fastapi import FastAPI, Request
     from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
@@ -307,7 +348,8 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
                 return err(400, "tool_choice needs the server to be started with --tool-call-parser")
             if chat:
                 messages, images = split_images(body.get("messages") or [])
-                text = render_chat(tok, messages, tools=tools)
+                text = render_chat(tok, messages, tools=tools,
+                                   chat_template=body.get("chat_template") or chat_template)
                 if images:
                     ids, prompt = encode_with_images(text, len(images)), text
                 else:
