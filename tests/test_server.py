@@ -363,3 +363,38 @@ def test_server_uses_its_chat_template(client_app):
         assert code == 200 and seen["text"] == "hi!"
     finally:
         tok.encode = orig
+
+
+def test_completions_with_several_prompts_and_echo(client_app):
+    """Batch prompts give one choice per (prompt, sample); ``echo`` + ``logprobs`` + ``max_tokens: 0`` scores the
+    prompt itself - the way evaluation harnesses ask for the log-likelihood of a continuation."""
+    pytest.importorskip("httpx")
+    allm, app = client_app
+    llm = allm.llm
+    code, text = _call(app, "POST", "/v1/completions", {"prompt": ["hello", "bye now"], "max_tokens": 4, "n": 2,
+                                                        "temperature": 1.0, "seed": 5})
+    res = json.loads(text)
+    assert code == 200 and [c["index"] for c in res["choices"]] == [0, 1, 2, 3]
+    one = json.loads(_call(app, "POST", "/v1/completions", {"prompt": "bye now", "max_tokens": 4, "n": 2,
+                                                            "temperature": 1.0, "seed": 5})[1])
+    assert [c["token_ids"] for c in res["choices"][2:]] == [c["token_ids"] for c in one["choices"]]
+    assert res["usage"]["completion_tokens"] == 16
+    # scoring: prompt log-probabilities through the server equal the offline API
+    prompt = "the quick brown fox"
+    ids = llm.tokenizer.encode(prompt)
+    want = llm.prompt_logprobs([ids], top=2)[0]
+    code, text = _call(app, "POST", "/v1/completions", {"prompt": prompt, "max_tokens": 0, "echo": True, "logprobs": 2})
+    ch = json.loads(text)["choices"][0]
+    assert code == 200 and ch["text"] == prompt and ch["token_ids"] == []
+    lp = ch["logprobs"]
+    assert lp["token_logprobs"][0] is None and len(lp["token_logprobs"]) == len(ids)
+    assert all(abs(a - b["logprob"]) < 1e-5 for a, b in zip(lp["token_logprobs"][1:], want[1:]))
+    assert lp["top_logprobs"][0] is None and len(lp["top_logprobs"][1]) == 2
+    assert lp["text_offset"][:3] == [0, 1, 2]
+    # echo with a continuation: prompt text in front, prompt + completion log-probabilities
+    code, text = _call(app, "POST", "/v1/completions", {"prompt": prompt, "max_tokens": 3, "echo": True, "logprobs": 1})
+    ch = json.loads(text)["choices"][0]
+    assert ch["text"].startswith(prompt) and len(ch["text"]) == len(prompt) + 3
+    assert len(ch["logprobs"]["token_logprobs"]) == len(ids) + 3
+    assert _call(app, "POST", "/v1/completions", {"prompt": ["a", "b"], "stream": True})[0] == 400
+    assert _call(app, "POST", "/v1/completions", {"prompt": "a", "max_tokens": 0})[0] in (200, 400)

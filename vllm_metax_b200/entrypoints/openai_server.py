@@ -599,9 +599,90 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
         del lora_modules[name]
         return {"status": "ok", "lora_name": name}
 
+    async def serve_batch(body: dict, traceparent: Optional[str] = None):
+        """``/v1/completions`` with several prompts and / or ``echo`` (non-streaming): choice ``i * n + j`` is sample j
+        of prompt i.  ``echo`` puts the prompt in front of the text and, with ``logprobs``, the log-probability of every
+        prompt token in front of the completion's (first token: null) - what evaluation harnesses use to score a
+        continuation; ``max_tokens: 0`` then generates nothing."""
+        try:
+            raw = body.get("prompt", "")
+            single = isinstance(raw, str) or (isinstance(raw, list) and raw and isinstance(raw[0], int))
+            items = [raw] if single else list(raw)
+            if not items:
+                raise ValueError("prompt is empty")
+            enc = [encode(p) for p in items]
+            echo = bool(body.get("echo"))
+            no_gen = body.get("max_tokens") == 0
+            if no_gen and not echo:
+                raise ValueError("max_tokens = 0 needs echo")
+            params = sampling_from_request(dict(body, max_tokens=1) if no_gen else body, default_max_tokens=16)
+            model_name = body.get("model")
+            if model_name in lora_modules:
+                params._lora_request = lora_modules[model_name]
+            elif model_name not in (None, "", served_model_name):
+                return err(404, f"model {model_name!r} is not served (adapters: {sorted(lora_modules)})", "model_not_found")
+            limit = llm.engine.cfg.scheduler.max_model_len
+            for ids, _ in enc:
+                if len(ids) + params.max_tokens > limit:
+                    raise ValueError(f"prompt ({len(ids)}) + max_tokens ({params.max_tokens}) exceeds max_model_len")
+        except Exception as e:  # noqa: BLE001
+            return err(400, str(e))
+        n_samples = max(1, int(body.get("n") or 1))
+        rid = "cmpl-" + uuid.uuid4().hex[:16]
+        import copy
+
+        def p_for(j: int):
+            p_j = copy.copy(params)
+            if n_samples > 1:
+                p_j.seed = None if params.seed is None else params.seed + j
+            if hasattr(params, "_lora_request"):
+                p_j._lora_request = params._lora_request
+            return p_j
+
+        try:
+            lasts = await asyncio.gather(*[run_one(ids, text, p_for(j), f"{rid}-{i}-{j}", traceparent)
+                                           for i, (ids, text) in enumerate(enc) for j in range(n_samples)])
+            plp = None
+            if echo and params.logprobs is not None:
+                k = int(params.logprobs)
+                plp = await allm.call(lambda: llm.prompt_logprobs([ids for ids, _ in enc], top=k))
+        except EngineDeadError as e:
+            return err(500, str(e), "engine_dead")
+        choices, completion_tokens = [], 0
+        for i, (ids, text) in enumerate(enc):
+            ptext = text if text is not None else (tok.decode(ids) if tok is not None else "")
+            for j in range(n_samples):
+                last = lasts[i * n_samples + j]
+                gen_text = "" if no_gen else (last.text or "")
+                gen_ids = [] if no_gen else last.token_ids
+                gen_lp = [] if no_gen else (last.logprobs or [])
+                completion_tokens += len(gen_ids)
+                lp_obj = None
+                if params.logprobs is not None:
+                    entries = (plp[i] if plp is not None else []) + list(gen_lp)
+                    real = [e for e in entries if e is not None]
+                    lp_obj = format_logprobs(real, tok, False)
+                    if plp is not None and lp_obj is not None:           # the first prompt token has no prediction
+                        first = tok.decode([ids[0]]) if tok is not None else f"token_id:{ids[0]}"
+                        lp_obj = {"tokens": [first] + lp_obj["tokens"], "token_logprobs": [None] + lp_obj["token_logprobs"],
+                                  "top_logprobs": [None] + lp_obj["top_logprobs"],
+                                  "text_offset": [0] + [o + len(first) for o in lp_obj["text_offset"]]}
+                choices.append({"index": i * n_samples + j, "text": (ptext if echo else "") + gen_text,
+                                "token_ids": gen_ids, "logprobs": lp_obj,
+                                "finish_reason": "length" if no_gen else last.finish_reason})
+        return {"id": rid, "object": "text_completion", "created": int(time.time()), "model": served_model_name,
+                "choices": choices, "usage": usage(sum(len(ids) for ids, _ in enc), completion_tokens)}
+
     @app.post("/v1/completions")
     async def completions(req: Request):
-        return await serve(await req.json(), chat=False, traceparent=req.headers.get("traceparent"))
+        body = await req.json()
+        raw = body.get("prompt")
+        several = isinstance(raw, list) and len(raw) > 1 and not isinstance(raw[0], int)
+        if several or body.get("echo"):
+            if body.get("stream"):
+                return err(400, "several prompts / echo are served for non-streaming requests only")
+            return await serve_batch(body, req.headers.get("traceparent"))
+        return await serve(body, chat=False, traceparent=req.headers.get("traceparent"))
 
     @app.post("/v1/chat/completions")
     async def chat_completions(req: Request):
