@@ -115,3 +115,27 @@ def test_chat_builds_a_prompt(llm):
         assert out[0].prompt == "user: hi\nassistant:" and len(out[0].outputs[0].token_ids) == 2
     finally:
         llm.tokenizer = None
+
+
+def test_environment_switches(tmp_path, monkeypatch):
+    """The switches of envs.py that act outside the kernels: the precision-dump directory makes every engine record
+    its module outputs, the build target can be 'empty', the grouped top-k switch selects the unfused statement."""
+    import json as _json
+
+    from vllm_metax_b200 import LLM, SamplingParams, _build, envs
+    from vllm_metax_b200.utils.precision_dump import load_dump
+
+    monkeypatch.setenv("B200_PRECISION_DUMP_DIR", str(tmp_path))
+    assert envs.B200_PRECISION_DUMP_DIR == str(tmp_path)
+    from tests.test_e2e_plumbing import tiny_cfg
+
+    llm = LLM(tiny_cfg(), device="cpu", block_size=16, max_model_len=64, max_num_seqs=2, max_num_batched_tokens=32,
+              num_gpu_blocks=16)
+    llm.generate([[1, 2, 3, 4]], SamplingParams(max_tokens=2))
+    llm._precision_dump.__exit__()
+    recs = load_dump(str(tmp_path / "dump_rank0.jsonl"))
+    assert len(recs) > 10 and any("layers" in k[0] for k in recs)
+    monkeypatch.setenv("B200_TARGET_DEVICE", "empty")
+    assert _build.build() is None
+    monkeypatch.setenv("B200_USE_FUSED_GROUPED_TOPK", "0")
+    assert not envs.B200_USE_FUSED_GROUPED_TOPK

@@ -9,7 +9,13 @@ Two ways in:
   (``vllm.platform_plugins`` / ``vllm.general_plugins``), mirroring
   vllm_metax/__init__.py:7-38.
 """
+import logging as _logging
+import os as _os
+
 from .version import __version__  # noqa: F401
+
+# B200_LOG_LEVEL: level of the package's loggers (DEBUG / INFO / WARNING / ...)
+_logging.getLogger(__name__).setLevel(getattr(_logging, _os.environ.get("B200_LOG_LEVEL", "INFO").upper(), _logging.INFO))
 
 
 def collect_env() -> None:

@@ -21,6 +21,7 @@ import subprocess
 import sys
 import sysconfig
 from pathlib import Path
+from typing import Optional
 
 ROOT = Path(__file__).resolve().parent
 CSRC = ROOT / "csrc"
@@ -55,7 +56,11 @@ def sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
 
-def build(verbose: bool = False, force: bool = False) -> Path:
+def build(verbose: bool = False, force: bool = False) -> Optional[Path]:
+    """Compile ``csrc/*.cu`` for sm_100a and link ``_b200_C.so`` in-tree.  ``B200_TARGET_DEVICE=empty`` skips the
+    native build (a CPU-only checkout that runs the PyTorch reference ops; the reference's ``VLLM_TARGET_DEVICE``)."""
+    if os.environ.get("B200_TARGET_DEVICE", "cuda").lower() in ("empty", "cpu"):
+        return None
     import torch
     from torch.utils.cpp_extension import include_paths, library_paths
 

@@ -563,8 +563,10 @@ def topk_gating(gating, topk: int, renormalize: bool, scoring: str = "softmax", 
 
 def grouped_topk(gating, topk: int, renormalize: bool, num_expert_group: int, topk_group: int,
                  scoring_func: str = "sigmoid", bias=None, routed_scaling_factor: float = 1.0):
-    """Parity: vllm_metax/_custom_ops.py:206-238 (grouped_topk)."""
-    if _use_cuda(gating):
+    """Parity: vllm_metax/_custom_ops.py:206-238 (grouped_topk).  ``B200_USE_FUSED_GROUPED_TOPK=0`` takes the unfused
+    PyTorch statement on the device instead of the kernel (the reference's ``MACA_VLLM_USE_FUSED_GROUPED_TOPK``-style
+    switch for bisecting routing differences)."""
+    if _use_cuda(gating) and envs.B200_USE_FUSED_GROUPED_TOPK:
         T = gating.shape[0]
         w = torch.empty(T, topk, dtype=torch.float32, device=gating.device)
         ids = torch.empty(T, topk, dtype=torch.int32, device=gating.device)

@@ -9,6 +9,7 @@ reference's examples use them (examples/features/{sleep,pause_resume,profiling})
 from __future__ import annotations
 
 import itertools
+import os
 import time
 from typing import Any, Iterable, Optional, Sequence, Union
 
@@ -454,6 +455,23 @@ class LLM:
         self.engine = LLMEngine(cfg, tokenizer or tok)
         self.tokenizer = self.engine.tokenizer
         self.foreign_finished: list = []       # see _run_capturing
+        # B200_PRECISION_DUMP_DIR: record statistics of every module output of this engine's forwards into
+        # <dir>/dump_rank<r>.jsonl (utils/precision_dump.py; compare two runs with compare_dumps)
+        from .. import envs
+
+        self._precision_dump = None
+        if envs.B200_PRECISION_DUMP_DIR:
+            from ..parallel import state as ps
+            from ..utils.precision_dump import PrecisionDump
+
+            os.makedirs(envs.B200_PRECISION_DUMP_DIR, exist_ok=True)
+            path = os.path.join(envs.B200_PRECISION_DUMP_DIR, f"dump_rank{ps.global_rank()}.jsonl")
+            self._precision_dump = PrecisionDump(self.engine.runner.model, path)
+            self._precision_dump.__enter__()
+            import atexit
+
+            atexit.register(self._precision_dump.__exit__)     # flush and close the file when the process ends
+            self.engine.runner.use_graphs = False          # module hooks do not run inside a replayed graph
 
     # ------------------------------------------------------------------ generate
     def _to_ids(self, p) -> tuple[list[int], Optional[str]]:
