@@ -67,3 +67,56 @@ def test_dp_attention_with_shared_experts_matches_single_process(tmp_path, world
         assert toks == want[replica], (rank, replica, toks, want[replica])
         padded += pad if replica == 1 else 0
     assert padded > 0          # the short replica kept stepping with padding tokens
+
+
+def _sp_worker(rank, world, port, path, prompts, q):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), B200_FUSED_TP_COLLECTIVES="0")
+    try:
+        from vllm_metax_b200 import LLM, SamplingParams
+
+        llm = LLM(path, device="cpu", tensor_parallel_size=world, block_size=16, max_model_len=128, max_num_seqs=4,
+                  max_num_batched_tokens=32, num_gpu_blocks=64, dtype=torch.float32, use_sequence_parallel_moe=True,
+                  all2all_backend="allgather_reducescatter")
+        moe = llm.engine.runner.model.model.layers["0"].mlp.experts
+        assert moe.sequence_parallel(torch.zeros(4, 128)) and not moe._nvlink_exchange(torch.zeros(4, 128))
+        outs = llm.generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True))
+        q.put((rank, [o.outputs[0].token_ids for o in outs], getattr(moe, "_agrs", None) is not None))
+    except BaseException as e:
+        q.put((rank, repr(e), False))
+        raise
+
+
+def test_sequence_parallel_moe_inside_one_replica(tmp_path):
+    """``use_sequence_parallel_moe`` with the collectives backend: every tensor-parallel rank routes its share of the
+    tokens, all-gather / reduce-scatter move the rows; same tokens as one process."""
+    from vllm_metax_b200 import LLM, SamplingParams
+
+    torch.manual_seed(0)
+    cfg = tf.Qwen3MoeConfig(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                            num_attention_heads=4, num_key_value_heads=2, head_dim=32, max_position_embeddings=256,
+                            rms_norm_eps=1e-6, tie_word_embeddings=False, num_experts=8, num_experts_per_tok=2,
+                            moe_intermediate_size=64, decoder_sparse_step=1, norm_topk_prob=True, mlp_only_layers=[])
+    path = str(tmp_path / "ckpt")
+    tf.Qwen3MoeForCausalLM(cfg).save_pretrained(path)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (21, 50, 7)]
+    ref = LLM(path, device="cpu", block_size=16, max_model_len=128, max_num_seqs=4, max_num_batched_tokens=32,
+              num_gpu_blocks=64, dtype=torch.float32)
+    want = [o.outputs[0].token_ids for o in ref.generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True))]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29650 + (os.getpid() % 40)
+    procs = [ctx.Process(target=_sp_worker, args=(r, 2, port, path, prompts, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=300) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, toks, used in got:
+        assert toks == want, (rank, toks, want)
+        assert used                                            # the exchange path ran, not the local filter
+    with pytest.raises(ValueError):
+        from vllm_metax_b200.parallel import state as ps
+        ps.set_moe_parallel(True, "naive")

@@ -279,11 +279,16 @@ class ParallelConfig:
     tensor_parallel_size: int = 1
     pipeline_parallel_size: int = 1
     data_parallel_size: int = 1
+    # accepted for command-line compatibility: the experts of a MoE model are always sharded over the ranks of the
+    # tensor-parallel group (and over all replicas with data_parallel_size > 1)
     enable_expert_parallel: bool = False
     decode_context_parallel_size: int = 1
     prefill_context_parallel_size: int = 1
+    # sequence-parallel MoE inside one replica: every rank routes 1 / tp of the tokens and the rows are exchanged
+    # (layers/fused_moe.py:_forward_sp) instead of every rank running its experts on all tokens; the exchange runs
+    # over the NVLink dispatch / combine kernels ("fused_nvlink") or all-gather / reduce-scatter collectives
     use_sequence_parallel_moe: bool = False
-    all2all_backend: str = "fused_nvlink"      # fused_nvlink | allgather_reducescatter | naive
+    all2all_backend: str = "fused_nvlink"      # fused_nvlink | allgather_reducescatter
     # expert-parallel load balancing (parallel/eplb.py): redundant expert slots, re-placement every
     # eplb_step_interval engine steps from the routing statistics of the last eplb_window steps
     enable_eplb: bool = False
@@ -303,10 +308,6 @@ class SchedulerConfig:
     max_num_batched_tokens: int = 8192
     max_model_len: int = 4096
     enable_chunked_prefill: bool = True
-    # Number of decode iterations run back to back on the device (device-side
-    # advance of positions/slots) before the host looks at the sampled tokens.
-    num_scheduler_steps: int = 1
-    policy: str = "fcfs"
 
 
 @dataclass

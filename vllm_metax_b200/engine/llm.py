@@ -424,7 +424,8 @@ class LLM:
                  enable_lora: bool = False, max_loras: int = 4, max_lora_rank: int = 64,
                  kv_transfer_config: Optional[dict] = None, decode_context_parallel_size: int = 1,
                  prefill_context_parallel_size: int = 1, enable_eplb: bool = False, num_redundant_experts: int = 0,
-                 eplb_step_interval: int = 3000, eplb_window: int = 1000):
+                 eplb_step_interval: int = 3000, eplb_window: int = 1000, use_sequence_parallel_moe: bool = False,
+                 all2all_backend: str = "fused_nvlink"):
         overrides = {"seed": seed}
         if enable_lora:
             overrides.update(enable_lora=True, max_loras=max_loras, max_lora_rank=max_lora_rank)
@@ -444,7 +445,9 @@ class LLM:
                                     enable_expert_parallel, decode_context_parallel_size,
                                     prefill_context_parallel_size, enable_eplb=enable_eplb,
                                     num_redundant_experts=num_redundant_experts,
-                                    eplb_step_interval=eplb_step_interval, eplb_window=eplb_window),
+                                    eplb_step_interval=eplb_step_interval, eplb_window=eplb_window,
+                                    use_sequence_parallel_moe=use_sequence_parallel_moe,
+                                    all2all_backend=all2all_backend),
             scheduler=SchedulerConfig(max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens,
                                       max_model_len=max_model_len, enable_chunked_prefill=enable_chunked_prefill),
             device=device, enforce_eager=enforce_eager, load_format=load_format,

@@ -55,6 +55,7 @@ class ModelRunner:
         self.is_cuda = self.device.type == "cuda"
         torch.manual_seed(cfg.model.seed)
         ps.set_eplb(par.enable_eplb, par.num_redundant_experts)
+        ps.set_moe_parallel(par.use_sequence_parallel_moe, par.all2all_backend)
         with torch.no_grad():
             self.model = build_model(cfg, self.device)
         self.eplb = None

@@ -84,6 +84,7 @@ class FusedMoE(nn.Module):
         self.ep = self.ep_group.world_size
         self.ep_rank = self.ep_group.rank_in_group
         # load balancing: num_physical = num_experts + redundant slots; hot experts live in several slots
+        self._sp_config = ps.moe_sequence_parallel()
         self.eplb = ps.eplb_enabled()
         self.num_physical = num_experts + (ps.num_redundant_experts() if self.eplb else 0)
         assert self.num_physical % self.ep == 0, "number of expert slots must divide over the EP ranks"
@@ -239,8 +240,7 @@ class FusedMoE(nn.Module):
             ids = torch.empty(0, self.top_k, dtype=torch.int32, device=x.device)
         mine_x = x[lo: lo + n].contiguous()
         qm = self.quant_method
-        nvlink = (x.is_cuda and envs.B200_MOE_A2A and H % 128 == 0
-                  and (qm is None or hasattr(qm, "apply_sorted")))
+        nvlink = self._nvlink_exchange(x)
         if nvlink:
             mgr = getattr(self, "_a2a", None)
             # replicas step with different token counts: the receive slots are sized once, for the largest step
@@ -268,15 +268,24 @@ class FusedMoE(nn.Module):
             y = y + ps.tensor_model_parallel_all_reduce(shared_out)
         return y
 
+    def _nvlink_exchange(self, x: torch.Tensor) -> bool:
+        """Whether the token exchange runs over the NVLink dispatch / combine kernels: asked for by ``B200_MOE_A2A=1``
+        or by ``use_sequence_parallel_moe`` with ``all2all_backend="fused_nvlink"``, on CUDA tensors whose rows the
+        kernels take (hidden a multiple of 128; experts bf16 or a quantisation method with a sorted-rows entry)."""
+        qm = self.quant_method
+        want = bool(envs.B200_MOE_A2A) or (self._sp_config and ps.all2all_backend() == "fused_nvlink")
+        return bool(want and x.is_cuda and x.shape[1] % 128 == 0 and (qm is None or hasattr(qm, "apply_sorted")))
+
     def sequence_parallel(self, x: torch.Tensor) -> bool:
-        """Whether ``forward_reduced`` exchanges tokens (always with several replicas; opt-in inside one replica)."""
+        """Whether ``forward_reduced`` exchanges tokens (always with several replicas; opt-in inside one replica:
+        ``B200_MOE_A2A=1`` for the NVLink kernels, or ``use_sequence_parallel_moe`` with either backend)."""
         if self.ep == 1:
             return False
         if self.dp > 1:
             return True
-        qm = self.quant_method
-        return bool(x.is_cuda and envs.B200_MOE_A2A and x.shape[1] % 128 == 0
-                    and (qm is None or hasattr(qm, "apply_sorted")))
+        if self._sp_config:
+            return True
+        return self._nvlink_exchange(x)
 
     def forward_reduced(self, x: torch.Tensor, router_logits: torch.Tensor,
                         shared_out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -285,6 +285,26 @@ def set_eplb(enabled: bool, num_redundant_experts: int = 0) -> None:
     _NUM_REDUNDANT_EXPERTS = int(num_redundant_experts) if enabled else 0
 
 
+_MOE_SEQUENCE_PARALLEL = False
+_ALL2ALL_BACKEND = "fused_nvlink"
+
+
+def set_moe_parallel(sequence_parallel: bool, all2all_backend: str = "fused_nvlink") -> None:
+    """How the MoE layers built from now on exchange tokens inside one replica (``ParallelConfig``)."""
+    global _MOE_SEQUENCE_PARALLEL, _ALL2ALL_BACKEND
+    if all2all_backend not in ("fused_nvlink", "allgather_reducescatter"):
+        raise ValueError(f"unknown all2all_backend {all2all_backend!r}")
+    _MOE_SEQUENCE_PARALLEL, _ALL2ALL_BACKEND = bool(sequence_parallel), all2all_backend
+
+
+def moe_sequence_parallel() -> bool:
+    return _MOE_SEQUENCE_PARALLEL
+
+
+def all2all_backend() -> str:
+    return _ALL2ALL_BACKEND
+
+
 def eplb_enabled() -> bool:
     return _EPLB_ENABLED
 
