@@ -270,8 +270,7 @@ class CacheConfig:
     num_gpu_blocks: Optional[int] = None       # None: derived from gpu_memory_utilization
     gpu_memory_utilization: float = 0.88
     kv_cache_dtype: str = "auto"               # auto | bfloat16 | float16 | fp8 | int8_per_token_head | fp8_per_token_head | fp8_ds_mla | turboquant_{k8v4,4bit_nc,k3v4_nc,3bit_nc}
-    enable_prefix_caching: bool = False
-    swap_space_gb: float = 0.0
+    enable_prefix_caching: bool = False      # (pre-empted requests are recomputed; there is no CPU swap space)
 
 
 @dataclass
