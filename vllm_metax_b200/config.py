@@ -307,6 +307,9 @@ class SchedulerConfig:
     max_num_batched_tokens: int = 8192
     max_model_len: int = 4096
     enable_chunked_prefill: bool = True
+    # "fcfs": arrival order.  "priority": a smaller ``priority`` value is admitted first (ties by arrival) and is
+    # pre-empted last.
+    policy: str = "fcfs"
 
 
 @dataclass

@@ -125,7 +125,8 @@ class LLMEngine:
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
                     request_id: Optional[str] = None, prompt: Optional[str] = None,
-                    arrival_time: Optional[float] = None, lora_request=None, multi_modal_data: Optional[dict] = None) -> str:
+                    arrival_time: Optional[float] = None, lora_request=None, multi_modal_data: Optional[dict] = None,
+                    priority: int = 0) -> str:
         if self.dead is not None:
             raise EngineDeadError(str(self.dead))
         rid = request_id or f"req-{next(self._ids)}"
@@ -147,6 +148,7 @@ class LLMEngine:
 
             req.stop_checker = StopStringChecker(self.tokenizer, list(params.stop), params.include_stop_str_in_output,
                                                  params.skip_special_tokens)
+        req.priority = int(priority or getattr(params, "_priority", 0) or 0)
         if mm is not None:
             req.mm_embeds, req.mm_positions, req.mm_hash = mm[:3]
             if len(mm) > 3 and mm[3]:
@@ -425,7 +427,7 @@ class LLM:
                  kv_transfer_config: Optional[dict] = None, decode_context_parallel_size: int = 1,
                  prefill_context_parallel_size: int = 1, enable_eplb: bool = False, num_redundant_experts: int = 0,
                  eplb_step_interval: int = 3000, eplb_window: int = 1000, use_sequence_parallel_moe: bool = False,
-                 all2all_backend: str = "fused_nvlink"):
+                 all2all_backend: str = "fused_nvlink", scheduling_policy: str = "fcfs"):
         overrides = {"seed": seed}
         if enable_lora:
             overrides.update(enable_lora=True, max_loras=max_loras, max_lora_rank=max_lora_rank)
@@ -449,7 +451,8 @@ class LLM:
                                     use_sequence_parallel_moe=use_sequence_parallel_moe,
                                     all2all_backend=all2all_backend),
             scheduler=SchedulerConfig(max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens,
-                                      max_model_len=max_model_len, enable_chunked_prefill=enable_chunked_prefill),
+                                      max_model_len=max_model_len, enable_chunked_prefill=enable_chunked_prefill,
+                                      policy=scheduling_policy),
             device=device, enforce_eager=enforce_eager, load_format=load_format,
             additional_config=dict(additional_config or {},
                                    **({"speculative_config": speculative_config} if speculative_config else {}),

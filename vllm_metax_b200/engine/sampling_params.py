@@ -106,7 +106,7 @@ class Request:
     __slots__ = ("request_id", "prompt_token_ids", "params", "output_token_ids", "status", "block_ids",
                  "num_computed_tokens", "arrival_time", "first_token_time", "finish_time", "token_times",
                  "eos_token_id", "num_cached_tokens", "logprobs", "prompt", "_hashes", "spec_token_ids", "lora_request", "mm_embeds", "mm_positions", "mm_hash", "_sample_rng", "finishing", "mrope_positions", "mrope_delta", "stop_checker", "stop_reason",
-                 "parent_id", "sample_index")
+                 "parent_id", "sample_index", "priority")
 
     def __init__(self, request_id: str, prompt_token_ids: list[int], params: SamplingParams,
                  eos_token_id: Optional[int] = None, prompt: Optional[str] = None,
@@ -117,6 +117,7 @@ class Request:
         self.stop_reason = None                # the stop string / stop token id that ended the request
         self.parent_id = None                  # n > 1: the id the samples are reported under ...
         self.sample_index = 0                  # ... and this sample's index
+        self.priority = 0                      # scheduling policy "priority": smaller runs first
         self.finishing = False                 # its last token (by length) is being computed: not scheduled again
         self.mrope_positions = None            # [3, prompt] multimodal rotary position streams (Qwen2-VL family) ...
         self.mrope_delta = 0                   # ... and the offset of generated tokens' stream value from their position

@@ -72,6 +72,20 @@ class Scheduler:
             req.params.max_tokens = max(1, self.cfg.max_model_len - req.num_prompt_tokens)
         if req.num_prompt_tokens >= self.cfg.max_model_len:
             raise ValueError(f"prompt of {req.num_prompt_tokens} tokens exceeds max_model_len {self.cfg.max_model_len}")
+        if self.cfg.policy == "priority":
+            self._enqueue_by_priority(req)
+        else:
+            self.waiting.append(req)
+
+    def _enqueue_by_priority(self, req: Request, front_of_equals: bool = False) -> None:
+        """Keep ``waiting`` sorted by (priority, arrival); a pre-empted request goes in front of its equals."""
+        key = (req.priority, req.arrival_time)
+        i = 0
+        for i, other in enumerate(self.waiting):          # queues are short next to a step's cost
+            ok = (other.priority, other.arrival_time)
+            if ok > key or (front_of_equals and other.priority == req.priority):
+                self.waiting.insert(i, req)
+                return
         self.waiting.append(req)
 
     def abort(self, request_id: str) -> bool:
@@ -98,7 +112,10 @@ class Scheduler:
 
     # ------------------------------------------------------------------ scheduling
     def _preempt_one(self, out: SchedulerOutput, keep: Request) -> bool:
-        for victim in reversed(self.running):
+        order = reversed(self.running)
+        if self.cfg.policy == "priority":     # the least important request goes first, the latest among equals
+            order = sorted(self.running, key=lambda r: (-r.priority, -r.arrival_time))
+        for victim in order:
             if victim is keep or victim.request_id in self.in_flight:
                 continue
             self.running.remove(victim)
@@ -106,7 +123,10 @@ class Scheduler:
             self.kv.free(victim)
             victim.num_computed_tokens = 0
             victim.status = RequestStatus.PREEMPTED
-            self.waiting.appendleft(victim)
+            if self.cfg.policy == "priority":
+                self._enqueue_by_priority(victim, front_of_equals=True)
+            else:
+                self.waiting.appendleft(victim)
             out.preempted.append(victim)
             self.num_preemptions += 1
             return True

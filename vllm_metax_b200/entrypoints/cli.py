@@ -30,6 +30,8 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--block-size", type=int, default=64)
     s.add_argument("--load-format", default="auto", choices=["auto", "dummy", "safetensors", "sharded_state"])
     s.add_argument("--enable-prefix-caching", action="store_true")
+    s.add_argument("--scheduling-policy", default="fcfs", choices=["fcfs", "priority"],
+                   help="priority: requests carry a 'priority' (smaller first) and the least important is pre-empted first")
     s.add_argument("--enable-sleep-mode", action="store_true")
     s.add_argument("--enforce-eager", action="store_true")
     s.add_argument("--device", default="cuda")
@@ -76,7 +78,8 @@ def make_llm(args):
 
     kw = dict(tensor_parallel_size=args.tensor_parallel_size, load_format=args.load_format, device=args.device)
     for name in ("max_model_len", "max_num_seqs", "max_num_batched_tokens", "gpu_memory_utilization", "block_size",
-                 "enable_prefix_caching", "enable_sleep_mode", "enforce_eager", "kv_cache_dtype", "seed"):
+                 "enable_prefix_caching", "enable_sleep_mode", "enforce_eager", "kv_cache_dtype", "seed",
+                 "scheduling_policy"):
         if hasattr(args, name):
             kw[name] = getattr(args, name)
     if getattr(args, "enable_lora", False):

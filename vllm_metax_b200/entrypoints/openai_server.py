@@ -69,7 +69,10 @@ def sampling_from_request(body: dict, default_max_tokens: int = 16) -> SamplingP
     fields = getattr(SamplingParams, "__dataclass_fields__", None)
     if fields is not None:
         kw = {k: v for k, v in kw.items() if k in fields}
-    return SamplingParams(**kw)
+    sp = SamplingParams(**kw)
+    if body.get("priority"):
+        sp._priority = int(body["priority"])        # scheduling policy "priority": smaller is served first
+    return sp
 
 
 def load_chat_template(arg: Optional[str]) -> Optional[str]:
