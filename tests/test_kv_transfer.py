@@ -123,3 +123,32 @@ def test_block_store_is_bounded_lru():
     st.get("h2")
     st.put("h4", bytes(100))
     assert st.has("h2") and not st.has("h3")
+
+
+def test_host_offload_tier_in_one_engine():
+    """kv_both on the host-memory connector: a prompt seen before is attached from host memory (the device-side
+    prefix cache is off), shared prefixes hit, tokens do not change, and a bounded store evicts the oldest blocks."""
+    from vllm_metax_b200 import LLM, SamplingParams
+
+    g = torch.Generator().manual_seed(3)
+    base = torch.randint(0, 1024, (80,), generator=g).tolist()
+    prompts = [base, base[:48] + torch.randint(0, 1024, (20,), generator=g).tolist()]
+    sp = SamplingParams(max_tokens=6, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in LLM(tiny_cfg(), **KW).generate(prompts, sp)]
+    cfg = {"kv_connector": "OffloadingConnector", "kv_role": "kv_both",
+           "kv_connector_extra_config": {"cpu_bytes_to_use": 1 << 30}}
+    llm = LLM(tiny_cfg(), kv_transfer_config=cfg, **KW)
+    first = llm.generate([prompts[0]], sp)
+    assert first[0].outputs[0].token_ids == want[0] and first[0].num_cached_tokens == 0
+    assert llm.engine.kv_connector.stats["blocks_saved"] == 80 // 16
+    outs = llm.generate(prompts, sp)                              # the same prompt again, and one sharing 48 tokens
+    assert [o.outputs[0].token_ids for o in outs] == want
+    assert [o.num_cached_tokens for o in outs] == [64, 48]        # (80 - 1) // 16 * 16 and the shared 3 blocks
+    assert llm.engine.stats["kv_external_tokens"] == 64 + 48
+    # a store that holds about two blocks: old blocks fall out, loads stop at the first gap, tokens stay right
+    blob = len(llm.engine.kv_connector._pack(0))
+    small = LLM(tiny_cfg(), kv_transfer_config=dict(cfg, kv_connector_extra_config={"cpu_bytes_to_use": 2 * blob + 8}), **KW)
+    small.generate([prompts[0]], sp)
+    assert len(small.engine.kv_connector.store.blobs) == 2
+    again = small.generate([prompts[0]], sp)[0]
+    assert again.outputs[0].token_ids == want[0] and again.num_cached_tokens == 0      # the first block is gone

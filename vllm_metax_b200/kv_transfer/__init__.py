@@ -5,7 +5,8 @@ has processed, a decode engine pulls them instead of recomputing the prompt.
                                    "kv_connector_extra_config": {"shared_storage_path": "/dev/shm/kv"}})
 
 ``KVConnector`` is the interface; ``NetworkKVConnector`` (``network.py``) serves the blocks from the producer's memory
-over TCP; ``SharedStorageConnector`` keeps one file per KV block, addressed by the chained
+over TCP; ``HostOffloadConnector`` (``host_offload.py``) is the single-engine form, a host-memory tier behind the
+device's prefix cache; ``SharedStorageConnector`` keeps one file per KV block, addressed by the chained
 hash of the tokens up to and including that block, so any shared prompt prefix is found.  A block that is missing
 or fails its checksum ends the load there: the scheduler recomputes the rest and counts the failure.
 Parity: the disaggregated-prefill examples of the reference (examples/disaggregated/* and
@@ -13,7 +14,9 @@ kv_load_failure_recovery_offline/README.md:1-30 in its tree) and ``Platform.inse
 ``swap_out_blocks_to_host`` (vllm_metax/platform.py:619-640).
 """
 from .base import KVConnector, KVTransferConfig, make_connector
+from .host_offload import HostOffloadConnector
 from .network import NetworkKVConnector
 from .shared_storage import SharedStorageConnector
 
-__all__ = ["KVConnector", "KVTransferConfig", "NetworkKVConnector", "SharedStorageConnector", "make_connector"]
+__all__ = ["HostOffloadConnector", "KVConnector", "KVTransferConfig", "NetworkKVConnector", "SharedStorageConnector",
+           "make_connector"]

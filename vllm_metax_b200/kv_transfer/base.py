@@ -52,11 +52,13 @@ class KVConnector:
 def make_connector(config: Optional[KVTransferConfig], runner) -> Optional[KVConnector]:
     if config is None:
         return None
+    from .host_offload import HostOffloadConnector
     from .network import NetworkKVConnector
     from .shared_storage import SharedStorageConnector
 
     kinds = {"SharedStorageConnector": SharedStorageConnector, "NetworkKVConnector": NetworkKVConnector,
-             "P2pNcclConnector": NetworkKVConnector}      # upstream's name for "pull blocks from the prefill engine"
+             "P2pNcclConnector": NetworkKVConnector,      # upstream's name for "pull blocks from the prefill engine"
+             "OffloadingConnector": HostOffloadConnector, "HostOffloadConnector": HostOffloadConnector}
     if config.kv_connector not in kinds:
         raise ValueError(f"unknown kv_connector {config.kv_connector!r}; available: {', '.join(kinds)}")
     return kinds[config.kv_connector](config, runner)
