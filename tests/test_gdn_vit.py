@@ -46,6 +46,48 @@ def test_gdn_reference_properties():
     assert torch.equal(s1[1], state[1])                                   # an unused slot is untouched
 
 
+@pytest.mark.parametrize("lens,chunk", [((5, 1, 33), 64), ((200, 64, 129), 64), ((70, 3, 17), 16)])
+def test_gdn_chunked_form_equals_the_recurrence(lens, chunk):
+    """The matrix form over chunks (what prefill uses when switched on) against the token-by-token recurrence:
+    sequences shorter than, equal to and not a multiple of the chunk, initial states, stored final states."""
+    from vllm_metax_b200.ops.gdn import gated_delta_rule_chunked, gated_delta_rule_ref
+
+    q, k, v, g, beta, qsl, state, idx, has = _gdn_case(torch.float32, seed=4, lens=lens)
+    s_ref, s_chk = state.clone(), state.clone()
+    want = gated_delta_rule_ref(q, k, v, g, beta, qsl, s_ref, idx, has)
+    got = gated_delta_rule_chunked(q, k, v, g, beta, qsl, s_chk, idx, has, chunk=chunk)
+    torch.testing.assert_close(got, want, rtol=2e-4, atol=2e-4)
+    torch.testing.assert_close(s_chk, s_ref, rtol=2e-4, atol=2e-4)
+    assert torch.equal(s_chk[1], state[1])
+    # strong decay and beta = 1 (the stiffest case for the triangular solve)
+    g2, b2 = g * 8, torch.ones_like(beta)
+    s_ref, s_chk = state.clone(), state.clone()
+    want = gated_delta_rule_ref(q, k, v, g2, b2, qsl, s_ref, idx, has)
+    got = gated_delta_rule_chunked(q, k, v, g2, b2, qsl, s_chk, idx, has, chunk=chunk)
+    torch.testing.assert_close(got, want, rtol=5e-4, atol=5e-4)
+
+
+def test_gdn_dispatch_takes_the_chunked_form_when_switched_on(monkeypatch):
+    from vllm_metax_b200.ops import gdn
+
+    q, k, v, g, beta, qsl, state, idx, has = _gdn_case(torch.float32, seed=2, lens=(300, 2, 40))
+    calls = []
+    real = gdn.gated_delta_rule_chunked
+    monkeypatch.setattr(gdn, "gated_delta_rule_chunked", lambda *a, **kw: (calls.append(1), real(*a, **kw))[1])
+    s0 = state.clone()
+    want = gdn.gated_delta_rule(q, k, v, g, beta, qsl, s0, idx, has)
+    assert not calls
+    monkeypatch.setenv("B200_GDN_CHUNKED", "1")
+    s1 = state.clone()
+    got = gdn.gated_delta_rule(q, k, v, g, beta, qsl, s1, idx, has)
+    assert calls == [1]
+    torch.testing.assert_close(got, want, rtol=2e-4, atol=2e-4)
+    torch.testing.assert_close(s1, s0, rtol=2e-4, atol=2e-4)
+    short = torch.tensor([0, 5, 6, 39], dtype=torch.int32)                # no long chunk in the batch: recurrent
+    gdn.gated_delta_rule(q[:39], k[:39], v[:39], g[:39], beta[:39], short, state.clone(), idx, has)
+    assert calls == [1]
+
+
 @gpu
 def test_gdn_kernel_matches_reference():
     from vllm_metax_b200.ops.gdn import gated_delta_rule, gated_delta_rule_ref

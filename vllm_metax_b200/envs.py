@@ -54,6 +54,10 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # attend that prefix once for the whole step.  Taken when prefix_tokens * (requests - 1) reaches the threshold.
     "B200_CASCADE_ATTENTION": _flag("B200_CASCADE_ATTENTION", "1"),
     "B200_CASCADE_MIN_SAVED_TOKENS": _int("B200_CASCADE_MIN_SAVED_TOKENS", 131072),
+    # Gated delta rule (Qwen3-Next): prompt chunks of at least MIN_TOKENS tokens take the chunked matrix form
+    # (ops/gdn.py:gated_delta_rule_chunked, PyTorch products) instead of the recurrent kernel.  0 = always recurrent.
+    "B200_GDN_CHUNKED": _flag("B200_GDN_CHUNKED", "0"),
+    "B200_GDN_CHUNKED_MIN_TOKENS": _int("B200_GDN_CHUNKED_MIN_TOKENS", 256),
     # Absorbed-MLA decode on tcgen05 (csrc/mla_decode_tcgen05.cu) for dense 16-bit caches from 64 heads per rank up;
     # 0 = the mma.sync kernel unless a call asks for the tcgen05 one.
     "B200_MLA_TCGEN05": _flag("B200_MLA_TCGEN05", "0"),
