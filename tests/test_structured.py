@@ -136,3 +136,32 @@ def test_schema_to_regex_optional_refs_alternatives():
     import pytest as _pytest
     with _pytest.raises(NotImplementedError):           # unbounded recursion is refused, not silently truncated
         schema_to_regex(tree)
+
+
+@pytest.mark.parametrize("lo,hi", [(0, 9), (1, 100), (17, 342), (95, 1003), (-20, 15), (-250, -13), (0, 0), (7, 7),
+                                   (1000, 99999), (None, 42), (5, None), (-3, None), (None, -11)])
+def test_integer_range_regex_is_exact(lo, hi):
+    from vllm_metax_b200.engine.structured import integer_range_regex
+
+    rx = regex.compile(integer_range_regex(lo, hi))
+    a = (lo if lo is not None else -1500) - 30
+    b = (hi if hi is not None else 1500) + 30
+    for v in list(range(a, b + 1)) + [10 ** 6, -10 ** 6, 123456]:
+        want = (lo is None or v >= lo) and (hi is None or v <= hi)
+        assert bool(rx.fullmatch(str(v))) == want, (lo, hi, v)
+    assert not rx.fullmatch("007") and not rx.fullmatch("-0") and not rx.fullmatch("1.0")
+
+
+def test_schema_ranges_and_all_of():
+    from vllm_metax_b200.engine.structured import schema_to_regex
+
+    rx = schema_to_regex({"type": "object", "properties": {"age": {"type": "integer", "minimum": 1, "maximum": 120},
+                                                          "n": {"type": "integer", "exclusiveMinimum": 0}}})
+    assert regex.fullmatch(rx, '{"age": 120, "n": 1}') and regex.fullmatch(rx, '{"age": 1, "n": 99999}')
+    assert not regex.fullmatch(rx, '{"age": 121, "n": 1}') and not regex.fullmatch(rx, '{"age": 5, "n": 0}')
+    merged = schema_to_regex({"$defs": {"base": {"type": "object", "properties": {"id": {"type": "integer"}}, "required": ["id"]}},
+                              "allOf": [{"$ref": "#/$defs/base"},
+                                        {"properties": {"name": {"type": "string"}}, "required": ["name"]}]})
+    assert regex.fullmatch(merged, '{"id": 3, "name": "x"}') and not regex.fullmatch(merged, '{"id": 3}')
+    with pytest.raises(NotImplementedError):
+        schema_to_regex({"allOf": [{"properties": {"a": {"type": "string"}}}, {"properties": {"a": {"type": "integer"}}}]})

@@ -99,11 +99,113 @@ def _any_json(depth: int) -> str:
     return f"(?:{scalar}|{arr}|{obj})"
 
 
+def _range_nonneg(lo: int, hi: int) -> list:
+    """Alternatives (regex pieces without leading zeros) that together match exactly the integers lo..hi, 0 <= lo <= hi:
+    the range is cut at the boundaries where the number of digits or a leading prefix changes."""
+    if lo > hi:
+        return []
+    slo, shi = str(lo), str(hi)
+    if len(slo) < len(shi):                       # split by digit count
+        return _range_nonneg(lo, 10 ** len(slo) - 1) + _range_nonneg(10 ** len(slo), hi)
+    if lo == hi:
+        return [slo]
+    n = len(slo)
+    if n == 1:
+        return [f"[{slo}-{shi}]"]
+    if slo[0] == shi[0]:                          # common first digit
+        return [slo[0] + (t if len(ts) == 1 else f"(?:{t})") for ts in [_range_same_len(slo[1:], shi[1:])]
+                for t in ["|".join(ts)]]
+    out = []
+    # first digit of lo with the rest >= lo's rest, full middle digits, first digit of hi with the rest <= hi's rest
+    rest_lo = _range_same_len(slo[1:], "9" * (n - 1))
+    out.append(slo[0] + (rest_lo[0] if len(rest_lo) == 1 else "(?:" + "|".join(rest_lo) + ")"))
+    if int(shi[0]) - int(slo[0]) > 1:
+        a, b = int(slo[0]) + 1, int(shi[0]) - 1
+        out.append((f"[{a}-{b}]" if a != b else str(a)) + (f"[0-9]{{{n - 1}}}" if n - 1 > 1 else "[0-9]"))
+    rest_hi = _range_same_len("0" * (n - 1), shi[1:])
+    out.append(shi[0] + (rest_hi[0] if len(rest_hi) == 1 else "(?:" + "|".join(rest_hi) + ")"))
+    return out
+
+
+def _range_same_len(slo: str, shi: str) -> list:
+    """Like ``_range_nonneg`` for digit STRINGS of equal length that may start with zeros (the tail of a number)."""
+    n = len(slo)
+    if slo == shi:
+        return [slo]
+    if n == 1:
+        return [f"[{slo}-{shi}]"]
+    if slo == "0" * n and shi == "9" * n:
+        return [f"[0-9]{{{n}}}"]
+    if slo[0] == shi[0]:
+        ts = _range_same_len(slo[1:], shi[1:])
+        return [slo[0] + (ts[0] if len(ts) == 1 else "(?:" + "|".join(ts) + ")")]
+    out = []
+    ts = _range_same_len(slo[1:], "9" * (n - 1))
+    out.append(slo[0] + (ts[0] if len(ts) == 1 else "(?:" + "|".join(ts) + ")"))
+    if int(shi[0]) - int(slo[0]) > 1:
+        a, b = int(slo[0]) + 1, int(shi[0]) - 1
+        out.append((f"[{a}-{b}]" if a != b else str(a)) + (f"[0-9]{{{n - 1}}}" if n - 1 > 1 else "[0-9]"))
+    ts = _range_same_len("0" * (n - 1), shi[1:])
+    out.append(shi[0] + (ts[0] if len(ts) == 1 else "(?:" + "|".join(ts) + ")"))
+    return out
+
+
+def integer_range_regex(lo, hi) -> str:
+    """Regex for the JSON integers in ``[lo, hi]``; either bound may be None (open).  Open ranges are bounded by digit
+    count only where a bound exists: ``lo = 5`` gives 5..9 and every longer number."""
+    alts = []
+    if lo is None and hi is None:
+        return _JSON_INT
+    if hi is None:                                 # lo .. infinity
+        if lo <= 0:
+            neg = _range_nonneg(1, -lo) if lo < 0 else []
+            alts += ["-" + a for a in neg] + ["0", "[1-9][0-9]*"]
+        else:
+            d = len(str(lo))
+            alts += _range_nonneg(lo, 10 ** d - 1) + [f"[1-9][0-9]{{{d},}}"]
+    elif lo is None:                               # -infinity .. hi
+        if hi >= 0:
+            alts += ["-[1-9][0-9]*"] + _range_nonneg(0, hi)
+        else:
+            d = len(str(-hi))
+            alts += ["-" + a for a in _range_nonneg(-hi, 10 ** d - 1)] + [f"-[1-9][0-9]{{{d},}}"]
+    else:
+        if lo > hi:
+            raise ValueError(f"empty integer range [{lo}, {hi}]")
+        if lo < 0:
+            alts += ["-" + a for a in _range_nonneg(max(1, -hi), -lo)]
+        if hi >= 0:
+            alts += _range_nonneg(max(lo, 0), hi)
+    return "(?:" + "|".join(alts) + ")"
+
+
+def _merge_all_of(parts: list) -> dict:
+    """``allOf`` of object-like sub-schemas -> one schema: properties are united (a name listed twice must agree),
+    ``required`` lists are united, other keywords must not conflict."""
+    out: dict = {}
+    for p in parts:
+        for k, v in p.items():
+            if k == "properties":
+                props = out.setdefault("properties", {})
+                for name, sub in v.items():
+                    if name in props and props[name] != sub:
+                        raise NotImplementedError(f"allOf: property {name!r} is constrained twice")
+                    props[name] = sub
+            elif k == "required":
+                out["required"] = list(dict.fromkeys(out.get("required", []) + list(v)))
+            elif k in out and out[k] != v:
+                raise NotImplementedError(f"allOf: conflicting {k!r}")
+            else:
+                out[k] = v
+    return out
+
+
 def schema_to_regex(schema, _root=None, _depth: int = 0) -> str:
     """Regular expression for the JSON documents of a schema.
 
     Supported: ``type`` (one or a list of) string / integer / number / boolean / null / array / object; ``enum`` /
-    ``const``; ``anyOf`` / ``oneOf`` (alternation) and single-element ``allOf``; local ``$ref`` into ``$defs`` /
+    ``const``; integers with ``minimum`` / ``maximum`` / ``exclusiveMinimum`` / ``exclusiveMaximum``; ``anyOf`` /
+    ``oneOf`` (alternation); ``allOf`` (one part, or object parts whose properties / required lists are merged); local ``$ref`` into ``$defs`` /
     ``definitions`` (recursive schemas are unrolled three levels); strings with ``minLength`` / ``maxLength`` /
     ``pattern`` / ``format`` (date-time, date, time, uuid); arrays with ``items`` / ``prefixItems`` / ``minItems`` /
     ``maxItems``; objects with ``properties`` in their listed order, where ``required`` (when present) says which may be
@@ -141,9 +243,16 @@ def schema_to_regex(schema, _root=None, _depth: int = 0) -> str:
                 raise NotImplementedError("no usable alternative")
             return "(?:" + "|".join(alts) + ")"
     if "allOf" in schema:
-        if len(schema["allOf"]) != 1:
-            raise NotImplementedError("allOf with several sub-schemas")
-        return rec(schema["allOf"][0])
+        parts = []
+        for sub in schema["allOf"]:                # resolve references so that the parts can be merged
+            while "$ref" in sub and set(sub) == {"$ref"} and sub["$ref"].startswith("#/"):
+                node = root
+                for part in sub["$ref"][2:].split("/"):
+                    node = node[part.replace("~1", "/").replace("~0", "~")]
+                sub = node
+            parts.append(sub)
+        rest = {k: v for k, v in schema.items() if k != "allOf"}
+        return rec(parts[0] if len(parts) == 1 and not rest else _merge_all_of(parts + ([rest] if rest else [])))
     if "enum" in schema:
         return "(?:" + "|".join(re.escape(json.dumps(v)) for v in schema["enum"]) + ")"
     if "const" in schema:
@@ -166,6 +275,15 @@ def schema_to_regex(schema, _root=None, _depth: int = 0) -> str:
             return f'"{_STR_CHAR}{{{lo},{"" if hi is None else int(hi)}}}"'
         return _JSON_STRING
     if t == "integer":
+        import math
+
+        lo, hi = schema.get("minimum"), schema.get("maximum")
+        if schema.get("exclusiveMinimum") is not None:
+            lo = max(lo, schema["exclusiveMinimum"] + 1) if lo is not None else math.floor(schema["exclusiveMinimum"]) + 1
+        if schema.get("exclusiveMaximum") is not None:
+            hi = min(hi, schema["exclusiveMaximum"] - 1) if hi is not None else math.ceil(schema["exclusiveMaximum"]) - 1
+        if lo is not None or hi is not None:
+            return integer_range_regex(None if lo is None else math.ceil(lo), None if hi is None else math.floor(hi))
         return _JSON_INT
     if t == "number":
         return _JSON_NUMBER
