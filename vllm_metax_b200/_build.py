@@ -87,9 +87,24 @@ def build(verbose: bool = False, force: bool = False) -> Optional[Path]:
                      "-DTORCH_EXTENSION_NAME=_b200_C", *inc, "-I", str(CSRC), "-c", str(bind_src), "-o", str(bind_obj)])
     if jobs:
         workers = int(os.environ.get("MAX_JOBS", "0")) or min(8, os.cpu_count() or 4)
+        import json
+        import time
+
+        def timed(job):
+            t0 = time.perf_counter()
+            _run(job)
+            return os.path.basename(job[-1]), time.perf_counter() - t0
+
+        times_file = OBJ / "build_times.json"
+        try:
+            times = json.loads(times_file.read_text())
+        except (OSError, ValueError):
+            times = {}
         with cf.ThreadPoolExecutor(workers) as ex:
-            for fut in [ex.submit(_run, j) for j in jobs]:
-                fut.result()
+            for fut in [ex.submit(timed, j) for j in jobs]:
+                unit, dt = fut.result()
+                times[unit] = round(dt, 2)
+        times_file.write_text(json.dumps(times, indent=1, sort_keys=True))
         if verbose:
             print(f"[b200 build] compiled {len(jobs)} translation units")
     if force or jobs or not LIB.exists():
@@ -115,6 +130,25 @@ def build_cumem(verbose: bool = False, force: bool = False) -> Path | None:
     return CUMEM_LIB
 
 
+def report_build_times() -> str:
+    """Seconds each translation unit took the last time it was compiled, slowest first (what to split or to look
+    at when the build gets slow; the reference's tools/report_build_time_ninja.py for its ninja logs)."""
+    import json
+
+    try:
+        times = json.loads((OBJ / "build_times.json").read_text())
+    except (OSError, ValueError):
+        return "no build recorded yet: run python -m vllm_metax_b200._build --force"
+    rows = sorted(times.items(), key=lambda kv: -kv[1])
+    width = max(len(k) for k in times)
+    total = sum(times.values())
+    lines = [f"{'unit':<{width}}  seconds  share"] + [f"{k:<{width}}  {v:7.2f}  {v / total:5.1%}" for k, v in rows]
+    return "\n".join(lines + [f"{'total (cpu-seconds over all workers)':<{width}}  {total:7.2f}"])
+
+
 if __name__ == "__main__":
-    build(verbose=True, force="--force" in sys.argv)
-    print(LIB)
+    if "--report" in sys.argv:
+        print(report_build_times())
+    else:
+        build(verbose=True, force="--force" in sys.argv)
+        print(LIB)
