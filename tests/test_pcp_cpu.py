@@ -84,3 +84,48 @@ def test_pcp_matches_single_process(tmp_path, world, tp):
             assert got[r] == want, (r, got[r], want)
         else:      # tensor-parallel sums differ in the last bits: the seeded request is greedy in this case
             assert got[r][0] == want[0] and got[r][1] == want[1] and got[r][3] == want[3], (r, got[r], want)
+
+
+def _mla_worker(rank, world, port, arch_kw, prompts, q):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), B200_FUSED_TP_COLLECTIVES="0")
+    try:
+        from tests.test_deepseek import ds_cfg
+        from vllm_metax_b200 import LLM, SamplingParams
+
+        llm = LLM(ds_cfg(**arch_kw), device="cpu", prefill_context_parallel_size=world, block_size=16,
+                  max_model_len=128, max_num_seqs=4, max_num_batched_tokens=32, num_gpu_blocks=64)
+        assert llm.engine.runner.pcp == world
+        outs = llm.generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True))
+        q.put((rank, [o.outputs[0].token_ids for o in outs]))
+    except BaseException as e:
+        q.put((rank, repr(e)))
+        raise
+
+
+@pytest.mark.parametrize("sparse", [False, True])
+def test_pcp_mla_matches_single_process(sparse):
+    """DeepSeek-V3 (MLA) and V3.2 (MLA + sparse-attention indexer, top-k smaller than the context) with two model
+    copies: latent rows and index keys are exchanged and written into both caches; chunked prefill, mixed steps and
+    decode give the single-process tokens."""
+    from tests.test_deepseek import ds_cfg
+    from vllm_metax_b200 import LLM, SamplingParams
+
+    arch_kw = dict(architecture="DeepseekV32ForCausalLM", index_n_heads=16, index_head_dim=128, index_topk=24) if sparse else {}
+    g = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (21, 77, 1, 40)]
+    ref_llm = LLM(ds_cfg(**arch_kw), device="cpu", block_size=16, max_model_len=128, max_num_seqs=4,
+                  max_num_batched_tokens=32, num_gpu_blocks=64)
+    want = [o.outputs[0].token_ids for o in ref_llm.generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True))]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29550 + (os.getpid() % 40) + (50 if sparse else 0)
+    procs = [ctx.Process(target=_mla_worker, args=(r, 2, port, arch_kw, prompts, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=300) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, toks in got:
+        assert toks == want, (rank, toks, want)

@@ -94,8 +94,9 @@ class ModelRunner:
         self.uses_mrope = bool(getattr(self.model, "uses_mrope", False))
         # prefill context parallel: full model copies that split the tokens of every prefill chunk (parallel/pcp.py)
         self.pcp = ps.get_pcp_group().world_size
-        if self.pcp > 1 and (cfg.model.is_mla or self.dcp > 1):
-            raise ValueError("prefill context parallelism serves GQA models with an unsplit cache")
+        if self.pcp > 1 and (self.dcp > 1 or getattr(cfg.model, "compress_ratios", None) is not None):
+            raise ValueError("prefill context parallelism serves GQA and MLA models with an unsplit cache "
+                             "(not combined with decode context parallelism or the DeepSeek-V4 compressed caches)")
         # pipeline parallel with overlapped steps: asynchronous stage-to-stage transfers and one token buffer per
         # step in flight
         import collections

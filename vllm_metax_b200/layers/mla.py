@@ -78,7 +78,18 @@ class MLAAttention(nn.Module):
         md = ctx.attn_metadata
         cache = ctx.kv_caches[self.layer_idx]["mla"]
         T, H = q.shape[0], self.num_heads
-        ops.concat_and_cache_mla(kv_c, k_pe, cache, md.slot_mapping)
+        pcp_slots = md.extra.get("pcp_slots_all")
+        if pcp_slots is not None:
+            # prefill context parallel: this copy computed a slice of every chunk; the copies exchange their latent
+            # rows and each writes all of them into its own (replicated) cache, after which the slice is an ordinary
+            # request of length "end of the slice" for the kernels below - parallel/pcp.py
+            from ..parallel import state as ps
+
+            g, sizes = ps.get_pcp_group(), md.extra["pcp_sizes"]
+            ops.concat_and_cache_mla(g.all_gatherv(kv_c.contiguous(), sizes), g.all_gatherv(k_pe.contiguous(), sizes),
+                                     cache, pcp_slots)
+        else:
+            ops.concat_and_cache_mla(kv_c, k_pe, cache, md.slot_mapping)
         if "dcp_ctx_lens" in md.extra:
             return self._forward_dcp(q, kv_c, k_pe, kv_b_proj, topk_indices, md, cache)
         nd, ndt = md.num_decodes, md.num_decode_tokens
@@ -167,7 +178,14 @@ def sparse_attn_indexer(q_fp8: torch.Tensor, weights: torch.Tensor, k: torch.Ten
     ``k [T, 128]`` (bf16).  Returns int32 ``[T, topk]`` per-request positions, -1 padded.
     """
     md = get_forward_context().attn_metadata
-    ops.indexer_k_quant_and_cache(k, idx_cache, md.slot_mapping, block_size)
+    pcp_slots = md.extra.get("pcp_slots_all")
+    if pcp_slots is not None:       # prefill context parallel: the index keys of all copies go into every copy's cache
+        from ..parallel import state as ps
+
+        k_all = ps.get_pcp_group().all_gatherv(k.contiguous(), md.extra["pcp_sizes"])
+        ops.indexer_k_quant_and_cache(k_all, idx_cache, pcp_slots, block_size)
+    else:
+        ops.indexer_k_quant_and_cache(k, idx_cache, md.slot_mapping, block_size)
     if "dcp_ctx_lens" in md.extra:
         return _sparse_attn_indexer_dcp(q_fp8, weights, idx_cache, topk, block_size, md)
     return ops.indexer_topk(q_fp8, weights, idx_cache, md.block_table, md.seq_lens, md.query_start_loc, topk,

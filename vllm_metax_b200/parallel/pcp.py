@@ -14,8 +14,8 @@ identically on all copies.  The request's last token of a chunk lives on the las
 the tokens (``engine/model_runner.py``).
 
 The reference takes PCP from upstream (``pcp_world_size`` in its attention metadata builders,
-vllm_metax/v1/attention/backends/flash_attn.py:246-325 and mla_attention.py:2142-2297); this is the GQA form of it with
-a replicated cache.
+vllm_metax/v1/attention/backends/flash_attn.py:246-325 and mla_attention.py:2142-2297); this is the form with a replicated cache, for GQA caches (``layers/attention.py``) and for the MLA latent cache and
+the sparse indexer's key cache (``layers/mla.py``).
 """
 from __future__ import annotations
 
