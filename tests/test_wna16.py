@@ -136,6 +136,64 @@ def test_quantised_model_generates_cpu(quant, qc):
     assert len(out[0].outputs[0].token_ids) == 4
 
 
+def test_w4a8_int8_activation_experts_cpu():
+    """compressed-tensors W4 (channel-wise) + dynamic int8 activations: the nibbles become int8 weights at load and
+    the experts run as W8A8; against the dequantised-weight fp32 MoE (the only difference left is the activation
+    rounding)."""
+    from vllm_metax_b200.layers.fused_moe import FusedMoE, reference_moe
+    from vllm_metax_b200.quantization.int8 import W4A8Int8MoEMethod
+    from vllm_metax_b200.quantization.wna16 import CompressedTensorsConfig
+
+    qc = CompressedTensorsConfig({"format": "pack-quantized", "config_groups": {"g0": {
+        "weights": {"num_bits": 4, "symmetric": True, "strategy": "channel", "group_size": None},
+        "input_activations": {"num_bits": 8, "dynamic": True, "symmetric": True, "strategy": "token"}}}})
+    method = qc.get_moe_method("model.layers.0.mlp.experts")
+    assert isinstance(method, W4A8Int8MoEMethod)
+    grouped = CompressedTensorsConfig({"format": "pack-quantized", "config_groups": {"g0": {
+        "weights": {"num_bits": 4, "symmetric": True, "strategy": "group", "group_size": 64},
+        "input_activations": {"num_bits": 8, "dynamic": True}}}})
+    assert not isinstance(grouped.get_moe_method("x"), W4A8Int8MoEMethod)       # group scales: weight-only kernel
+
+    torch.manual_seed(7)
+    E, H, I, k = 4, 64, 32, 2
+    moe = FusedMoE(E, k, H, I, dtype=torch.float32, quant_method=method)
+    deq = {}
+    for e in range(E):
+        for shard, (n, kk) in (("w1", (I, H)), ("w3", (I, H)), ("w2", (H, I))):
+            w = torch.randn(n, kk) * 0.2
+            scale = w.abs().amax(1, keepdim=True) / 7
+            q = torch.clamp(torch.round(w / scale), -8, 7)
+            deq[(e, shard)] = q * scale
+            packed = W.pack_int32((q + 8).to(torch.int32), 4, 1)
+            assert moe.load_expert_tensor(e, shard, "weight_shape", torch.tensor([n, kk]))
+            moe.load_expert_tensor(e, shard, "weight_packed", packed)
+            moe.load_expert_tensor(e, shard, "weight_scale", scale.to(torch.bfloat16).float())
+            deq[(e, shard)] = q * scale.to(torch.bfloat16).float()
+    assert moe.w13_weight.dtype == torch.int8 and int(moe.w13_weight.min()) >= -8 and int(moe.w13_weight.max()) <= 7
+    x = torch.randn(24, H)
+    logits = torch.randn(24, E)
+    got = moe.forward_reduced(x, logits)
+    w13 = torch.stack([torch.stack([deq[(e, "w1")], deq[(e, "w3")]], 1).reshape(2 * I, H) for e in range(E)])   # interleaved
+    w2 = torch.stack([deq[(e, "w2")] for e in range(E)])
+    wts, ids = moe.route(logits)
+    want = reference_moe(x, w13, w2, wts, ids)
+    assert cos_diff(got, want) < 2e-3
+
+
+def test_w4a8_checkpoint_config_generates_cpu():
+    qc = {"quant_method": "compressed-tensors", "format": "pack-quantized", "config_groups": {"g0": {
+        "weights": {"num_bits": 4, "symmetric": True, "strategy": "channel", "group_size": None},
+        "input_activations": {"num_bits": 8, "dynamic": True, "symmetric": True, "strategy": "token"}}},
+        "ignore": ["re:.*self_attn.*", "lm_head", "re:.*mlp.gate$"]}
+    cfg = _tiny_moe_cfg(quantization="compressed-tensors", quant_config=qc)
+    llm = LLM(cfg, device="cpu", load_format="dummy", num_gpu_blocks=32, block_size=16, seed=0)
+    from vllm_metax_b200.quantization.int8 import W4A8Int8MoEMethod
+
+    assert isinstance(llm.engine.runner.model.model.layers["0"].mlp.experts.quant_method, W4A8Int8MoEMethod)
+    out = llm.generate([[1, 2, 3, 4, 5]], SamplingParams(max_tokens=4, temperature=0.0))
+    assert len(out[0].outputs[0].token_ids) == 4
+
+
 # ----------------------------------------------------------------------------- GPU kernels
 @gpu
 @pytest.mark.parametrize("M,N,K,g", [(1, 256, 256, 128), (7, 4096, 4096, 128), (48, 1536, 2048, 64), (100, 512, 1024, 32),

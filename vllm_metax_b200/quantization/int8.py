@@ -102,6 +102,38 @@ class Int8MoEMethod:
         return ops.moe_combine(y, topk_weights, inv, T, shared_out)
 
 
+class W4A8Int8MoEMethod(Int8MoEMethod):
+    """Experts with 4-bit channel-wise weights and dynamic per-token int8 activations (compressed-tensors
+    ``pack-quantized`` weights + 8-bit ``input_activations``): the nibbles are expanded to int8 values in [-8, 7] as
+    they are loaded and the layer then IS a W8A8 layer - int8 activations x int8 weights on the ``kind::i8`` tensor
+    cores, per-token x per-channel scales in the epilogue.  Weights take one byte per value in memory (twice the
+    checkpoint), which buys the integer tensor-core rate; group-wise 4-bit weights stay on the weight-only kernel
+    (``WNA16MoEMethod``), whose group scales the W8A8 epilogue cannot apply.
+    Parity: vllm_metax/registry/quant_config/compressed_tensors_moe/compressed_tensors_moe_w4a8_int4.py:33-459."""
+
+    def __init__(self, bits: int = 4):
+        self.bits = bits
+        self._staging: dict = {}
+
+    def load_expert_tensor(self, layer, e: int, shard: str, kind: str, tensor: torch.Tensor) -> None:
+        if kind not in ("weight_packed", "weight_scale"):
+            return                                        # weight_shape and friends carry nothing the layer needs
+        st = self._staging.setdefault((e, shard), {})
+        st[kind] = tensor
+        if len(st) < 2:
+            return
+        del self._staging[(e, shard)]
+        from .wna16 import unpack_int32
+
+        q = unpack_int32(st["weight_packed"], self.bits, 1).to(torch.int16) - (1 << (self.bits - 1))   # [N, K] signed
+        scale = st["weight_scale"].float().reshape(q.shape[0], -1)
+        if scale.shape[1] != 1:
+            raise ValueError("W4A8 with int8 activations needs channel-wise weight scales (one per output row)")
+        w, s_ = (layer.w2_weight, layer.w2_weight_scale) if shard == "w2" else (layer.w13_weight, layer.w13_weight_scale)
+        self.load_expert_weight(layer, w, q.to(torch.int8), e, shard)
+        self.load_expert_weight(layer, s_, scale, e, shard)
+
+
 class Int8Config:
     """``{"quant_method": "w8a8_int8", "activation_scheme": "dynamic" | "static", "symmetric": true}``."""
 

@@ -418,6 +418,10 @@ class CompressedTensorsConfig:
             from .int8 import Int8MoEMethod
 
             return Int8MoEMethod()
+        if self.bits == 4 and self.act_bits == 8 and self.sym and (self.group in (-1, None) or self.strategy == "channel"):
+            from .int8 import W4A8Int8MoEMethod      # channel-wise W4 + int8 activations: the integer tensor-core path
+
+            return W4A8Int8MoEMethod(self.bits)
         return WNA16MoEMethod("ct", self.bits, self.group, self.sym, act_int8=self.act_bits == 8)
 
 
