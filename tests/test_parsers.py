@@ -1,6 +1,8 @@
 """Tool-call and reasoning parsers of the chat endpoint, and the OpenAI ``logprobs`` objects."""
 import json
 
+import pytest
+
 from vllm_metax_b200.entrypoints.openai_server import format_logprobs
 from vllm_metax_b200.entrypoints.parsers import (get_reasoning_parser, get_tool_parser, parse_chat_output,
                                                  parse_deepseek_v3, parse_hermes, parse_llama3_json, parse_mistral,
@@ -71,3 +73,45 @@ def test_logprobs_objects():
     ch = format_logprobs(entries, Tok(), chat=True, start=1)
     assert len(ch["content"]) == 1 and ch["content"][0]["token"] == "aaa" and len(ch["content"][0]["top_logprobs"]) == 2
     assert format_logprobs(None, Tok(), chat=True) is None
+
+
+@pytest.mark.parametrize("name,text,want", [
+    ("deepseek_v31", 'ok<｜tool▁calls▁begin｜><｜tool▁call▁begin｜>get_weather<｜tool▁sep｜>{"city": "Paris"}<｜tool▁call▁end｜>'
+                     '<｜tool▁call▁begin｜>add<｜tool▁sep｜>{"a": 1, "b": 2}<｜tool▁call▁end｜><｜tool▁calls▁end｜>',
+     [("get_weather", {"city": "Paris"}), ("add", {"a": 1, "b": 2})]),
+    ("granite", '<|tool_call|>[{"name": "get_weather", "arguments": {"city": "Paris"}}]', [("get_weather", {"city": "Paris"})]),
+    ("granite-20b-fc", '<function_call> {"name": "f", "arguments": {"x": 1}}\n<function_call> {"name": "g", "arguments": {}}',
+     [("f", {"x": 1}), ("g", {})]),
+    ("phi4_mini_json", 'functools[{"name": "f", "arguments": {"x": [1, 2]}}]', [("f", {"x": [1, 2]})]),
+    ("minimax", 'thinking\n<tool_calls>\n{"name": "f", "arguments": {"x": 1}}\n{"name": "g", "arguments": {"y": "z"}}\n</tool_calls>',
+     [("f", {"x": 1}), ("g", {"y": "z"})]),
+    ("hunyuan_a13b", '<tool_calls>[{"name": "f", "arguments": {"x": 1}}]</tool_calls>', [("f", {"x": 1})]),
+    ("internlm", 'Let me check.<|action_start|><|plugin|>\n{"name": "f", "parameters": {"q": "a b"}}<|action_end|>',
+     [("f", {"q": "a b"})]),
+    ("xlam", '```json\n[{"name": "f", "arguments": {"x": 1}}]\n```', [("f", {"x": 1})]),
+    ("xlam", '<think>hm</think>[{"name": "f", "arguments": {"x": 1}}]', [("f", {"x": 1})]),
+    ("kimi_k2", '<|tool_calls_section_begin|><|tool_call_begin|>functions.get_weather:0<|tool_call_argument_begin|>'
+                '{"city": "Paris"}<|tool_call_end|><|tool_calls_section_end|>', [("get_weather", {"city": "Paris"})]),
+    ("qwen3_coder", 'Sure.\n<tool_call>\n<function=get_weather>\n<parameter=city>\nParis\n</parameter>\n<parameter=days>\n3\n'
+                    '</parameter>\n</function>\n</tool_call>', [("get_weather", {"city": "Paris", "days": 3})]),
+    ("glm45", '<tool_call>get_weather\n<arg_key>city</arg_key>\n<arg_value>Paris</arg_value>\n<arg_key>metric</arg_key>\n'
+              '<arg_value>true</arg_value>\n</tool_call>', [("get_weather", {"city": "Paris", "metric": True})]),
+])
+def test_more_tool_formats(name, text, want):
+    import json as _json
+
+    from vllm_metax_b200.entrypoints.parsers import get_tool_parser
+
+    msg = get_tool_parser(name)(text)
+    assert [(c.name, _json.loads(c.arguments)) for c in msg.tool_calls] == want
+    plain = get_tool_parser(name)("just an answer, no call")
+    assert plain.tool_calls == [] and plain.content == "just an answer, no call"
+
+
+def test_tool_parsers_keep_leading_text():
+    from vllm_metax_b200.entrypoints.parsers import get_tool_parser
+
+    assert get_tool_parser("internlm")('Let me check.<|action_start|><|plugin|>{"name": "f", "parameters": {}}<|action_end|>').content == "Let me check."
+    assert get_tool_parser("qwen3_coder")("Sure.\n<tool_call>\n<function=f>\n</function>\n</tool_call>").content == "Sure."
+    assert get_tool_parser("kimi_k2")('x<|tool_calls_section_begin|><|tool_call_begin|>functions.f:1<|tool_call_argument_begin|>{}'
+                                      '<|tool_call_end|><|tool_calls_section_end|>').tool_calls[0].id == "functions.f:1"

@@ -42,7 +42,9 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--max-lora-rank", type=int, default=64)
     s.add_argument("--lora-modules", nargs="*", default=[], metavar="NAME=PATH", help="PEFT adapters served under NAME")
     s.add_argument("--tool-call-parser", default=None,
-                   help="hermes | qwen | llama3_json | llama4_json | mistral | deepseek_v3 | pythonic")
+                   help="hermes | qwen | llama3_json | llama4_json | llama4_pythonic | mistral | deepseek_v3 | deepseek_v31 | "
+                        "pythonic | granite | granite-20b-fc | internlm | phi4_mini_json | minimax | hunyuan_a13b | jamba | "
+                        "xlam | kimi_k2 | qwen3_coder | glm45")
     s.add_argument("--enable-auto-tool-choice", action="store_true", help="accepted for command-line compatibility: "
                    "tool_choice=auto is served whenever a tool-call parser is set")
     s.add_argument("--reasoning-parser", default=None, help="deepseek_r1 | qwen3 | glm45 | step3")

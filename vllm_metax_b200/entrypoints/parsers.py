@@ -11,6 +11,13 @@ Tool-call formats:
   mistral      ``[TOOL_CALLS] [{"name": ..., "arguments": {...}}, ...]``
   deepseek_v3  ``<｜tool▁call▁begin｜>function<｜tool▁sep｜>NAME\\n```json\\n{...}\\n```<｜tool▁call▁end｜>``
   pythonic     ``[get_weather(city="Paris"), other(x=1)]``
+  deepseek_v31 ``<｜tool▁call▁begin｜>NAME<｜tool▁sep｜>{...}<｜tool▁call▁end｜>``
+  granite / granite-20b-fc / phi4_mini_json / minimax / hunyuan_a13b / jamba / internlm / xlam
+               a JSON list (or objects) of calls after the model's marker (``<|tool_call|>``, ``<function_call>``,
+               ``functools``, ``<tool_calls>...</tool_calls>``, ``<|action_start|><|plugin|>``, a bare / fenced list)
+  kimi_k2      ``<|tool_call_begin|>functions.NAME:IDX<|tool_call_argument_begin|>{...}<|tool_call_end|>``
+  qwen3_coder  ``<tool_call><function=NAME><parameter=KEY>VALUE</parameter></function></tool_call>``
+  glm45        ``<tool_call>NAME <arg_key>K</arg_key><arg_value>V</arg_value></tool_call>``
 Reasoning formats:
   deepseek_r1 / qwen3   ``<think> ... </think>`` before the answer (the opening tag may be part of the prompt)
 
@@ -164,9 +171,131 @@ def parse_pythonic(text: str) -> ParsedMessage:
     return ParsedMessage(None, calls)
 
 
+def _calls_from_json_list(blob: str) -> list:
+    """Tool calls from text that holds a JSON list (or consecutive JSON objects) of ``{"name", "arguments" | "parameters"}``."""
+    calls = []
+    for _, _, val in _json_objects(blob):
+        for obj in (val if isinstance(val, list) else [val]):
+            c = _call_from_obj(obj)
+            if c is not None:
+                calls.append(c)
+    return calls
+
+
+def _tagged_json_parser(open_tag: str, close_tag: Optional[str]):
+    """Formats that put a JSON list / objects of calls after ``open_tag`` (up to ``close_tag`` when there is one)."""
+    def parse(text: str) -> ParsedMessage:
+        if open_tag not in text:
+            return ParsedMessage(text)
+        head, tail = text.split(open_tag, 1)
+        if close_tag and close_tag in tail:
+            tail = tail.split(close_tag, 1)[0]
+        calls = _calls_from_json_list(tail)
+        return ParsedMessage(head.strip() or None, calls) if calls else ParsedMessage(text)
+    return parse
+
+
+parse_granite = _tagged_json_parser("<|tool_call|>", None)                       # <|tool_call|>[{...}, ...]
+parse_granite_20b_fc = _tagged_json_parser("<function_call>", None)              # <function_call> {...}
+parse_phi4_mini_json = _tagged_json_parser("functools", None)                    # functools[{...}, ...]
+parse_minimax = _tagged_json_parser("<tool_calls>", "</tool_calls>")             # one JSON object per line
+parse_hunyuan_a13b = _tagged_json_parser("<tool_calls>", "</tool_calls>")        # a JSON list
+parse_jamba = _tagged_json_parser("<tool_calls>", "</tool_calls>")
+
+
+def parse_internlm(text: str) -> ParsedMessage:
+    """``...<|action_start|><|plugin|>{"name": ..., "parameters": {...}}<|action_end|>``"""
+    m = re.search(r"<\|action_start\|>\s*<\|plugin\|>(.*?)(?:<\|action_end\|>|$)", text, flags=re.S)
+    if not m:
+        return ParsedMessage(text)
+    calls = _calls_from_json_list(m.group(1))
+    return ParsedMessage(text[:m.start()].strip() or None, calls) if calls else ParsedMessage(text)
+
+
+def parse_xlam(text: str) -> ParsedMessage:
+    """A JSON list of calls, bare, inside a ```json fence, after ``</think>`` or after ``[TOOL_CALLS]``."""
+    body = text.split("</think>", 1)[1] if "</think>" in text else text
+    body = body.split("[TOOL_CALLS]", 1)[1] if "[TOOL_CALLS]" in body else body
+    fence = re.search(r"```(?:json)?\s*(.*?)```", body, flags=re.S)
+    blob = (fence.group(1) if fence else body).strip()
+    if not blob.startswith("["):
+        return ParsedMessage(text)
+    calls = _calls_from_json_list(blob)
+    lead = body[:fence.start()].strip() if fence else None
+    return ParsedMessage(lead or None, calls) if calls else ParsedMessage(text)
+
+
+_KIMI_CALL = re.compile(r"<\|tool_call_begin\|>\s*(?P<id>[^<\s]+)\s*<\|tool_call_argument_begin\|>\s*(?P<args>.*?)\s*"
+                        r"<\|tool_call_end\|>", re.S)
+
+
+def parse_kimi_k2(text: str) -> ParsedMessage:
+    """``<|tool_calls_section_begin|><|tool_call_begin|>functions.NAME:IDX<|tool_call_argument_begin|>{...}
+    <|tool_call_end|><|tool_calls_section_end|>``"""
+    calls = []
+    for m in _KIMI_CALL.finditer(text):
+        ident = m.group("id")
+        name = ident.split(":", 1)[0]
+        name = name.split(".", 1)[1] if name.startswith("functions.") else name
+        calls.append(ToolCall(name, _args_text(m.group("args")), id=ident))
+    if not calls:
+        return ParsedMessage(text)
+    return ParsedMessage(text.split("<|tool_calls_section_begin|>", 1)[0].strip() or None, calls)
+
+
+_DS31_CALL = re.compile(r"<｜tool▁call▁begin｜>(?P<name>.*?)<｜tool▁sep｜>(?P<args>.*?)<｜tool▁call▁end｜>", re.S)
+
+
+def parse_deepseek_v31(text: str) -> ParsedMessage:
+    """``<｜tool▁calls▁begin｜><｜tool▁call▁begin｜>NAME<｜tool▁sep｜>{...}<｜tool▁call▁end｜><｜tool▁calls▁end｜>``"""
+    calls = [ToolCall(m.group("name").strip(), _args_text(m.group("args").strip())) for m in _DS31_CALL.finditer(text)]
+    if not calls:
+        return ParsedMessage(text)
+    return ParsedMessage(text.split("<｜tool▁calls▁begin｜>", 1)[0].strip() or None, calls)
+
+
+def _typed(value: str):
+    """Parameter text of the XML-style formats: JSON where it parses (numbers, booleans, objects), else the string."""
+    v = value.strip("\n")
+    try:
+        return json.loads(v)
+    except ValueError:
+        return v
+
+
+def parse_qwen3_coder(text: str) -> ParsedMessage:
+    """``<tool_call><function=NAME><parameter=KEY>VALUE</parameter>...</function></tool_call>``"""
+    calls = []
+    for fm in re.finditer(r"<function=([^>\s]+)>(.*?)(?:</function>|$)", text, flags=re.S):
+        args = {pm.group(1): _typed(pm.group(2))
+                for pm in re.finditer(r"<parameter=([^>\s]+)>(.*?)(?:</parameter>|(?=<parameter=)|$)", fm.group(2), flags=re.S)}
+        calls.append(ToolCall(fm.group(1), json.dumps(args, ensure_ascii=False)))
+    if not calls:
+        return ParsedMessage(text)
+    head = re.split(r"<tool_call>|<function=", text, maxsplit=1)[0]
+    return ParsedMessage(head.strip() or None, calls)
+
+
+def parse_glm45(text: str) -> ParsedMessage:
+    """``<tool_call>NAME\n<arg_key>K</arg_key>\n<arg_value>V</arg_value>...</tool_call>``"""
+    calls = []
+    for m in re.finditer(r"<tool_call>\s*([^\n<]+)\s*(.*?)\s*(?:</tool_call>|$)", text, flags=re.S):
+        keys = re.findall(r"<arg_key>(.*?)</arg_key>", m.group(2), flags=re.S)
+        vals = re.findall(r"<arg_value>(.*?)</arg_value>", m.group(2), flags=re.S)
+        calls.append(ToolCall(m.group(1).strip(), json.dumps({k.strip(): _typed(v) for k, v in zip(keys, vals)},
+                                                             ensure_ascii=False)))
+    if not calls:
+        return ParsedMessage(text)
+    return ParsedMessage(text.split("<tool_call>", 1)[0].strip() or None, calls)
+
+
 TOOL_PARSERS: dict[str, Callable[[str], ParsedMessage]] = {
     "hermes": parse_hermes, "qwen": parse_hermes, "llama3_json": parse_llama3_json, "llama4_json": parse_llama3_json,
     "mistral": parse_mistral, "deepseek_v3": parse_deepseek_v3, "pythonic": parse_pythonic,
+    "llama4_pythonic": parse_pythonic, "deepseek_v31": parse_deepseek_v31, "granite": parse_granite,
+    "granite-20b-fc": parse_granite_20b_fc, "internlm": parse_internlm, "phi4_mini_json": parse_phi4_mini_json,
+    "minimax": parse_minimax, "hunyuan_a13b": parse_hunyuan_a13b, "jamba": parse_jamba, "xlam": parse_xlam,
+    "kimi_k2": parse_kimi_k2, "qwen3_coder": parse_qwen3_coder, "qwen3_xml": parse_qwen3_coder, "glm45": parse_glm45,
 }
 
 
