@@ -115,3 +115,12 @@ def test_tool_parsers_keep_leading_text():
     assert get_tool_parser("qwen3_coder")("Sure.\n<tool_call>\n<function=f>\n</function>\n</tool_call>").content == "Sure."
     assert get_tool_parser("kimi_k2")('x<|tool_calls_section_begin|><|tool_call_begin|>functions.f:1<|tool_call_argument_begin|>{}'
                                       '<|tool_call_end|><|tool_calls_section_end|>').tool_calls[0].id == "functions.f:1"
+
+
+def test_more_reasoning_formats():
+    from vllm_metax_b200.entrypoints.parsers import get_reasoning_parser
+
+    assert get_reasoning_parser("mistral")("[THINK]step 1[/THINK]42") == ("step 1", "42")
+    assert get_reasoning_parser("granite")("Here is my thought process: a then b. Here is my response: yes") == ("a then b.", "yes")
+    assert get_reasoning_parser("granite")("plain") == (None, "plain")
+    assert get_reasoning_parser("hunyuan_a13b")("<think>hm</think>\n<answer>\nyes\n</answer>") == ("hm", "yes")

@@ -47,7 +47,7 @@ def build_parser() -> argparse.ArgumentParser:
                         "xlam | kimi_k2 | qwen3_coder | glm45")
     s.add_argument("--enable-auto-tool-choice", action="store_true", help="accepted for command-line compatibility: "
                    "tool_choice=auto is served whenever a tool-call parser is set")
-    s.add_argument("--reasoning-parser", default=None, help="deepseek_r1 | qwen3 | glm45 | step3")
+    s.add_argument("--reasoning-parser", default=None, help="deepseek_r1 | qwen3 | glm45 | step3 | mistral | granite | hunyuan_a13b")
     s.add_argument("--chat-template", default=None, help="Jinja chat template: a file (examples/chat_templates/) or "
                    "the template text; replaces the tokenizer's own")
     s.add_argument("--kv-transfer-config", default=None, help="JSON, e.g. '{\"kv_connector\": \"SharedStorageConnector\", "

@@ -316,8 +316,32 @@ def split_think(text: str, open_tag: str = "<think>", close_tag: str = "</think>
     return None, text
 
 
+def split_mistral_think(text: str, finished: bool = True):
+    """Magistral: ``[THINK] ... [/THINK]answer``."""
+    return split_think(text, "[THINK]", "[/THINK]", finished)
+
+
+def split_granite(text: str, finished: bool = True):
+    """Granite 3.2: ``Here is my thought process: ... Here is my response: ...`` (either phrase may start with
+    "Here's")."""
+    m = re.search(r"Here(?: is|'s) my thought process:(.*?)(?:Here(?: is|'s) my response:(.*))?$", text, flags=re.S)
+    if not m:
+        return None, text
+    return (m.group(1).strip() or None), ((m.group(2) or "").strip() or None)
+
+
+def split_hunyuan(text: str, finished: bool = True):
+    """Hunyuan-A13B: ``<think>...</think><answer>...</answer>``."""
+    reasoning, answer = split_think(text, finished=finished)
+    if answer:
+        m = re.search(r"<answer>\s*(.*?)\s*(?:</answer>|$)", answer, flags=re.S)
+        answer = m.group(1) if m else answer
+    return reasoning, answer or None
+
+
 REASONING_PARSERS: dict[str, Callable] = {
     "deepseek_r1": split_think, "qwen3": split_think, "glm45": split_think, "step3": split_think,
+    "mistral": split_mistral_think, "granite": split_granite, "hunyuan_a13b": split_hunyuan,
 }
 
 
