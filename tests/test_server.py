@@ -398,3 +398,22 @@ def test_completions_with_several_prompts_and_echo(client_app):
     assert len(ch["logprobs"]["token_logprobs"]) == len(ids) + 3
     assert _call(app, "POST", "/v1/completions", {"prompt": ["a", "b"], "stream": True})[0] == 400
     assert _call(app, "POST", "/v1/completions", {"prompt": "a", "max_tokens": 0})[0] in (200, 400)
+
+
+def test_responses_route(client_app):
+    pytest.importorskip("httpx")
+    allm, app = client_app
+    code, text = _call(app, "POST", "/v1/responses", {"input": "hi there", "instructions": "be brief", "max_output_tokens": 5})
+    res = json.loads(text)
+    assert code == 200 and res["object"] == "response" and res["status"] == "incomplete"
+    msg = [o for o in res["output"] if o["type"] == "message"][0]
+    assert msg["content"][0]["type"] == "output_text" and msg["content"][0]["text"] == res["output_text"]
+    assert res["usage"]["output_tokens"] == 5 and res["usage"]["input_tokens"] > 0
+    chat = json.loads(_call(app, "POST", "/v1/chat/completions", {"messages": [
+        {"role": "system", "content": "be brief"}, {"role": "user", "content": "hi there"}], "max_tokens": 5})[1])
+    assert chat["choices"][0]["message"]["content"] == res["output_text"]          # the same request underneath
+    code, text = _call(app, "POST", "/v1/responses", {"input": [
+        {"role": "user", "content": [{"type": "input_text", "text": "hi "}, {"type": "input_text", "text": "there"}]}],
+        "instructions": "be brief", "max_output_tokens": 5})
+    assert json.loads(text)["output_text"] == res["output_text"]
+    assert _call(app, "POST", "/v1/responses", {"input": "x", "stream": True})[0] == 400

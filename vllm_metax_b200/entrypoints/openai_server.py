@@ -462,6 +462,58 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
 
         return StreamingResponse(sse(), media_type="text/event-stream")
 
+    # ---- Responses API (non-streaming subset): the chat path under another envelope
+    @app.post("/v1/responses")
+    async def responses(req: Request):
+        """``input``: a string or a list of ``{"role", "content"}`` items (content a string or a list of
+        ``input_text`` / ``output_text`` parts); ``instructions`` becomes the system turn.  Answers one ``message``
+        output item (plus a ``reasoning`` item and ``function_call`` items when the parsers find them)."""
+        body = await req.json()
+        if body.get("stream"):
+            return err(400, "the responses route is served without streaming; use /v1/chat/completions to stream")
+        inp = body.get("input", "")
+        messages = []
+        if body.get("instructions"):
+            messages.append({"role": "system", "content": str(body["instructions"])})
+        if isinstance(inp, str):
+            messages.append({"role": "user", "content": inp})
+        else:
+            for item in inp:
+                c = item.get("content", "")
+                if isinstance(c, list):
+                    c = "".join(p.get("text", "") for p in c if p.get("type") in ("input_text", "output_text", "text"))
+                messages.append({"role": item.get("role", "user"), "content": c})
+        chat_body = {k: v for k, v in body.items() if k in ("temperature", "top_p", "seed", "model", "stop", "top_k")}
+        chat_body.update(messages=messages, max_tokens=body.get("max_output_tokens") or 256)
+        tools = [t for t in (body.get("tools") or []) if t.get("type") == "function"]
+        if tools:       # Responses puts name / parameters at the top level of a tool
+            chat_body["tools"] = [{"type": "function", "function": {k: t[k] for k in ("name", "description", "parameters")
+                                                                  if k in t}} for t in tools]
+            if body.get("tool_choice") in ("auto", "none"):
+                chat_body["tool_choice"] = body["tool_choice"]
+        out = await serve(chat_body, chat=True, traceparent=req.headers.get("traceparent"))
+        if not isinstance(out, dict):
+            return out                                       # an error response
+        msg = out["choices"][0]["message"]
+        items = []
+        if msg.get("reasoning_content"):
+            items.append({"type": "reasoning", "id": "rs_" + uuid.uuid4().hex[:16],
+                          "summary": [{"type": "summary_text", "text": msg["reasoning_content"]}]})
+        for c in msg.get("tool_calls") or []:
+            items.append({"type": "function_call", "id": "fc_" + uuid.uuid4().hex[:16], "call_id": c["id"],
+                          "name": c["function"]["name"], "arguments": c["function"]["arguments"], "status": "completed"})
+        if msg.get("content") is not None or not items:
+            items.append({"type": "message", "id": "msg_" + uuid.uuid4().hex[:16], "role": "assistant", "status": "completed",
+                          "content": [{"type": "output_text", "text": msg.get("content") or "", "annotations": []}]})
+        u = out["usage"]
+        finish = out["choices"][0]["finish_reason"]
+        return {"id": "resp_" + uuid.uuid4().hex[:16], "object": "response", "created_at": out["created"],
+                "model": out["model"], "status": "completed" if finish != "length" else "incomplete",
+                "incomplete_details": {"reason": "max_output_tokens"} if finish == "length" else None,
+                "output": items, "output_text": msg.get("content") or "",
+                "usage": {"input_tokens": u["prompt_tokens"], "output_tokens": u["completion_tokens"],
+                          "total_tokens": u["total_tokens"]}}
+
     # ---- pooling endpoints: embeddings, similarity scores, re-ranking (they drive the engine from its own thread)
     def many(x) -> list:
         """``str | [int] -> [x]``; ``[str] | [[int]]`` stay lists."""
