@@ -334,3 +334,52 @@ def test_qwen2_5_vl_matches_hugging_face(tmp_path):
                           mm_token_type_ids=torch.tensor([[1 if t == QV_IMG else 0 for t in ids]]),
                           max_new_tokens=6, do_sample=False, eos_token_id=None, pad_token_id=0)
     assert got == out[0, len(ids):].tolist()
+
+
+def test_llava_next_matches_hugging_face(tmp_path):
+    """Any-resolution LLaVA: base image + tile grid, unpadded feature map, newline column; wide, tall and small
+    images (different grids and different token counts) against Hugging Face's model on the same pixel tensors."""
+    from vllm_metax_b200 import LLM, SamplingParams
+    from vllm_metax_b200.models.llava import select_best_resolution
+
+    torch.manual_seed(0)
+    vc = tf.CLIPVisionConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4,
+                             image_size=28, patch_size=14, projection_dim=32)
+    tc = tf.LlamaConfig(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2, max_position_embeddings=256)
+    pins = [[28, 56], [56, 28], [56, 56], [28, 84], [84, 28]]
+    c = tf.LlavaNextConfig(vision_config=vc, text_config=tc, image_token_index=IMG_TOK, vision_feature_layer=-2,
+                           vision_feature_select_strategy="default", image_grid_pinpoints=pins, image_seq_length=4)
+    hf = tf.LlavaNextForConditionalGeneration(c).eval().float()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.dim() == 1:
+                p.add_(0.1 * torch.randn_like(p))
+            else:
+                p.mul_(3.0)
+    hf.save_pretrained(str(tmp_path))
+    llm = LLM(str(tmp_path), dtype="float32", device="cpu", max_model_len=160, num_gpu_blocks=40, block_size=16,
+              max_num_batched_tokens=24)
+    model = llm.engine.runner.model
+    assert type(model).__name__ == "LlavaNextForConditionalGeneration" and float(model.image_newline.abs().sum()) > 0
+    g = torch.Generator().manual_seed(2)
+    sp = SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True)
+    for hw in [(30, 100), (90, 40), (50, 50), (20, 20)]:
+        ch, cw = select_best_resolution(hw, [tuple(p) for p in pins])
+        tiles = 1 + (ch // 28) * (cw // 28)
+        pixels = torch.randn(1, tiles, 3, 28, 28, generator=g)
+        sizes = torch.tensor([list(hw)])
+        with torch.no_grad():       # Hugging Face checks the count itself: a wrong one fails its generate call below
+            n_tok = model.pack_features(model.embed_multimodal(pixels[0]), hw).shape[0]
+        ids = [5, 9] + [IMG_TOK] * n_tok + [33, 100, 7, 8]
+        with torch.no_grad():
+            want = hf.generate(input_ids=torch.tensor([ids]), pixel_values=pixels, image_sizes=sizes, max_new_tokens=5,
+                               do_sample=False, eos_token_id=None, pad_token_id=0)[0, len(ids):].tolist()
+        out = llm.generate([{"prompt_token_ids": [5, 9, IMG_TOK, 33, 100, 7, 8],
+                             "multi_modal_data": {"pixel_values": pixels, "image_sizes": sizes}}], sp)
+        assert len(out[0].prompt_token_ids) == len(ids), (hw, n_tok)
+        assert list(out[0].outputs[0].token_ids) == want, hw
+    # raw images go through this package's own tiling
+    img = torch.randint(0, 255, (3, 40, 100), dtype=torch.uint8)
+    out = llm.generate([{"prompt_token_ids": [1, IMG_TOK, 3], "multi_modal_data": {"image": img}}], sp)
+    assert len(out[0].outputs[0].token_ids) == 5

@@ -41,6 +41,7 @@ _MODELS: dict[str, tuple[str, str]] = {
     "ChatGLMModel": ("llama_family", "ChatGLMModel"),
     "ChatGLMForConditionalGeneration": ("llama_family", "ChatGLMModel"),
     "LlavaForConditionalGeneration": ("llava", "LlavaForConditionalGeneration"),
+    "LlavaNextForConditionalGeneration": ("llava", "LlavaNextForConditionalGeneration"),
     "Qwen2VLForConditionalGeneration": ("qwen2_vl", "Qwen2VLForConditionalGeneration"),
     "Qwen2_5_VLForConditionalGeneration": ("qwen2_vl", "Qwen2_5_VLForConditionalGeneration"),
     "InternVLForConditionalGeneration": ("internvl", "InternVLForConditionalGeneration"),

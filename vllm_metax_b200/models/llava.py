@@ -188,3 +188,134 @@ class LlavaForConditionalGeneration(nn.Module):
             lm.lm_head.weight.data.copy_(lm.model.embed_tokens.weight.data)
         loaded |= {f"language_model.{n}" for n in got}
         return loaded
+
+
+# ------------------------------------------------------------------------------------------ LLaVA-NeXT (any resolution)
+def select_best_resolution(original_hw: tuple, candidates: list) -> tuple:
+    """The candidate ``(height, width)`` that keeps most of the image's pixels after an aspect-preserving resize, and
+    among equals wastes the least canvas (the rule LLaVA-NeXT's processor and model both apply)."""
+    oh, ow = original_hw
+    best, best_eff, best_waste = None, 0, float("inf")
+    for h, w in candidates:
+        scale = min(w / ow, h / oh)
+        eff = min(int(ow * scale) * int(oh * scale), ow * oh)
+        waste = w * h - eff
+        if eff > best_eff or (eff == best_eff and waste < best_waste):
+            best, best_eff, best_waste = (h, w), eff, waste
+    return best
+
+
+def unpad_features(x: torch.Tensor, original_hw: tuple) -> torch.Tensor:
+    """``x [C, H, W]`` is the feature map of an image that was resized with its aspect ratio kept and padded to the
+    canvas: cut the rows (or columns) that only saw padding."""
+    oh, ow = original_hw
+    H, W = x.shape[1:]
+    if ow / oh > W / H:
+        new_h = int(round(oh * (W / ow), 7))
+        pad = (H - new_h) // 2
+        return x[:, pad: H - pad, :]
+    new_w = int(round(ow * (H / oh), 7))
+    pad = (W - new_w) // 2
+    return x[:, :, pad: W - pad]
+
+
+class LlavaNextForConditionalGeneration(LlavaForConditionalGeneration):
+    """LLaVA-NeXT (1.6): the image is shown to the CLIP tower once whole (resized to the tower's square) and once as
+    a grid of tower-sized tiles cut from the best-fitting canvas of ``image_grid_pinpoints``; the tile features are
+    laid out as one feature map, the padding rows / columns are cut, a learned ``image_newline`` vector ends every
+    row, and base + grid features replace the prompt's placeholder run.  The number of image tokens therefore depends
+    on the image size."""
+
+    renames = LlavaForConditionalGeneration.renames + [(r"^model\.image_newline$", "image_newline")]
+
+    def __init__(self, cfg: ModelConfig):
+        super().__init__(cfg)
+        hf = cfg.hf_config
+        self.pinpoints = [tuple(p) for p in hf.get("image_grid_pinpoints",
+                                                   [[336, 672], [672, 336], [672, 672], [1008, 336], [336, 1008]])]
+        self.image_newline = nn.Parameter(torch.zeros(cfg.hidden_size, dtype=cfg.dtype), requires_grad=False)
+
+    # ---- preprocessing: one image -> [1 + tiles, 3, S, S] and its original (h, w) --------------------------------
+    def tiles_of(self, image) -> tuple:
+        S = self.vision_tower.size
+        if not isinstance(image, torch.Tensor):
+            import numpy as np
+
+            image = torch.from_numpy(np.asarray(image.convert("RGB"))).permute(2, 0, 1)
+        x = image.float() / (255.0 if image.dtype == torch.uint8 else 1.0)
+        oh, ow = x.shape[1:]
+        ch, cw = select_best_resolution((oh, ow), self.pinpoints)
+        import math
+
+        if cw / ow < ch / oh:                     # the width binds: fill it, round the height up
+            nw, nh = cw, min(math.ceil(oh * (cw / ow)), ch)
+        else:
+            nh, nw = ch, min(math.ceil(ow * (ch / oh)), cw)
+        resized = F.interpolate(x[None], size=(nh, nw), mode="bicubic", align_corners=False)[0].clamp(0, 1)
+        canvas = torch.zeros(3, ch, cw)
+        top, left = (ch - nh) // 2, (cw - nw) // 2
+        canvas[:, top: top + nh, left: left + nw] = resized
+        tiles = canvas.unfold(1, S, S).unfold(2, S, S).permute(1, 2, 0, 3, 4).reshape(-1, 3, S, S)   # row-major grid
+        base = F.interpolate(x[None], size=(S, S), mode="bicubic", align_corners=False)[0].clamp(0, 1)
+        mean = torch.tensor([0.48145466, 0.4578275, 0.40821073]).view(1, 3, 1, 1)
+        std = torch.tensor([0.26862954, 0.26130258, 0.27577711]).view(1, 3, 1, 1)
+        return (torch.cat([base[None], tiles]) - mean) / std, (oh, ow)
+
+    # ---- features of one image: [tokens, hidden] ------------------------------------------------------------------
+    def pack_features(self, feats: torch.Tensor, original_hw: tuple) -> torch.Tensor:
+        """``feats [1 + tiles, per, hidden]`` (projected tower outputs of the whole image and of the tiles)."""
+        S, side = self.vision_tower.size, int(round(feats.shape[1] ** 0.5))
+        newline = self.image_newline.to(feats.dtype)
+        if feats.shape[0] == 1:
+            return torch.cat([feats[0], newline[None]])
+        ch, cw = select_best_resolution(original_hw, self.pinpoints)
+        gh, gw = ch // S, cw // S
+        grid = feats[1:].reshape(gh, gw, side, side, -1).permute(4, 0, 2, 1, 3).reshape(-1, gh * side, gw * side)
+        grid = unpad_features(grid, original_hw)
+        grid = torch.cat([grid, newline[:, None, None].expand(-1, grid.shape[1], 1)], dim=-1)
+        return torch.cat([feats[0], grid.flatten(1).transpose(0, 1)])
+
+    @torch.no_grad()
+    def encode_request(self, prompt_token_ids: list, mm: dict, device):
+        """``mm``: ``{"image": image | [images]}`` (PIL / ``[3, H, W]`` tensors), or the processor's outputs
+        ``{"pixel_values": [n, 1 + tiles, 3, S, S] (zero-padded tiles allowed), "image_sizes": [n, 2]}``.  The prompt
+        holds one placeholder per image or the already expanded runs."""
+        import hashlib
+
+        import numpy as np
+
+        if "pixel_values" in mm:
+            sizes = [tuple(int(v) for v in s) for s in torch.as_tensor(mm["image_sizes"]).tolist()]
+            S = self.vision_tower.size
+            stacks = []
+            for pv, hw in zip(mm["pixel_values"], sizes):
+                ch, cw = select_best_resolution(hw, self.pinpoints)
+                stacks.append(pv[: 1 + (ch // S) * (cw // S)])           # drop the batch padding tiles
+        else:
+            imgs = mm["image"] if isinstance(mm["image"], (list, tuple)) else [mm["image"]]
+            stacks, sizes = zip(*[self.tiles_of(im) for im in imgs])
+        per_image = []
+        for st, hw in zip(stacks, sizes):
+            f = self.embed_multimodal(st.to(device=device, dtype=self.image_newline.dtype))
+            per_image.append(self.pack_features(f, hw))
+        tok = self.image_token_id
+        runs, ids = [], []
+        count = sum(1 for t in prompt_token_ids if t == tok)
+        if count == len(per_image):                                      # one placeholder per image: expand
+            k = 0
+            for t in prompt_token_ids:
+                if t == tok:
+                    ids.extend([tok] * per_image[k].shape[0])
+                    k += 1
+                else:
+                    ids.append(t)
+        elif count == sum(f.shape[0] for f in per_image):
+            ids = list(prompt_token_ids)
+        else:
+            raise ValueError(f"prompt has {count} image placeholder tokens; the images need "
+                             f"{[int(f.shape[0]) for f in per_image]}")
+        pos = np.asarray([i for i, t in enumerate(ids) if t == tok], dtype=np.int64)
+        h = hashlib.sha256()
+        for st in stacks:
+            h.update(st.detach().float().cpu().numpy().tobytes())
+        return ids, (torch.cat(per_image), pos, h.hexdigest()[:16]), None
