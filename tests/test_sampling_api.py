@@ -205,3 +205,48 @@ def test_prompt_logprobs_match_step_by_step_scoring(llm):
         assert abs(got[0][k]["logprob"] - want) < 1e-4, (k, got[0][k], want)
         assert len(got[0][k]["top"]) == 3 and got[0][k]["top"][0][1] >= got[0][k]["logprob"] - 1e-6
     assert abs(got[1][3]["logprob"] - got[0][3]["logprob"]) < 1e-4
+
+
+def test_incremental_detokenizer_equals_full_decode():
+    """A byte-level BPE tokenizer with a small vocabulary (multi-byte characters are split over several tokens):
+    feeding the tokens a few at a time gives exactly the text of one full decode, never shows a broken character,
+    and the final flush emits a trailing incomplete one the way the full decode does."""
+    import random
+
+    tokenizers = pytest.importorskip("tokenizers")
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+
+    from vllm_metax_b200.engine.sampling_params import IncrementalDetokenizer
+
+    tok = Tokenizer(models.BPE(unk_token=None))
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tok.decoder = decoders.ByteLevel()
+    corpus = ["the quick brown fox jumps over the lazy dog ", "héllo wörld çà et là ", "中文 测试 文本 ", "emoji 😀 🎉 ok "] * 5
+    tok.train_from_iterator(corpus, trainers.BpeTrainer(vocab_size=300, initial_alphabet=pre_tokenizers.ByteLevel.alphabet(),
+                                                        show_progress=False))
+
+    class Wrap:                                  # the decode signature the engine uses
+        def decode(self, ids, skip_special_tokens=True):
+            return tok.decode(list(ids), skip_special_tokens=skip_special_tokens)
+
+    rng = random.Random(0)
+    pieces = ["the lazy dog", " héllo", " 中文测试", " 😀🎉", " wörld", " fox", "文本", " çà"]
+    for trial in range(20):
+        text = "".join(rng.choice(pieces) for _ in range(12))
+        ids = tok.encode(text).ids
+        assert len(ids) > len(text) // 3                       # the vocabulary really splits characters
+        d = IncrementalDetokenizer(Wrap())
+        i, seen = 0, ""
+        while i < len(ids):
+            i = min(len(ids), i + rng.randint(1, 3))
+            d.step(ids[:i])
+            assert "�" not in d.text and d.text.startswith(seen)
+            seen = d.text
+        d.finish(ids)
+        assert d.text == tok.decode(ids) == text
+        cut = ids[: len(ids) - 1]                              # may end inside a character
+        d2 = IncrementalDetokenizer(Wrap())
+        for j in range(1, len(cut) + 1):
+            d2.step(cut[:j])
+        d2.finish(cut)
+        assert d2.text == tok.decode(cut)

@@ -198,35 +198,57 @@ class Request:
             self.status = RequestStatus.FINISHED_LENGTH
 
 
-class StopStringChecker:
-    """Incremental detokeniser + stop-string search for one request.  ``step`` is called after every new token with
-    the whole output; it decodes only the tokens since the last stable boundary (a token sequence can end inside a
-    multi-byte character, which decodes to U+FFFD until the rest arrives) and searches the tail of the text.  On a
-    hit, ``text`` is cut before the stop string (after it with ``include``)."""
+class IncrementalDetokenizer:
+    """Text of a growing token sequence without decoding it again from the start.  ``step(ids)`` decodes only the
+    tokens since the last stable boundary, with the tokens of the previous step as context (so that tokenizers which
+    treat the first token of a call differently - a leading space, for one - give the same text as one full decode),
+    and holds tokens back while they end inside a multi-byte character (they decode to U+FFFD until the rest
+    arrives).  ``finish(ids)`` emits whatever is still held back."""
 
-    def __init__(self, tokenizer, stops: list, include: bool = False, skip_special_tokens: bool = True):
-        self.tok, self.stops, self.include, self.skip = tokenizer, [s for s in stops if s], include, skip_special_tokens
-        self.max_len = max((len(s) for s in self.stops), default=0)
+    def __init__(self, tokenizer, skip_special_tokens: bool = True):
+        self.tok, self.skip = tokenizer, skip_special_tokens
         self.text = ""
-        self.prefix = 0          # tokens before this offset are fully emitted
-        self.read = 0            # tokens before this offset have been decoded as context
-        self.hit: Optional[str] = None
+        self.prefix = 0          # tokens before this offset are fully emitted ...
+        self.read = 0            # ... and tokens [prefix, read) are the context of the next decode
 
     def _decode(self, ids) -> str:
         return self.tok.decode(list(ids), skip_special_tokens=self.skip)
 
+    def step(self, output_token_ids: list, final: bool = False) -> str:
+        ids = output_token_ids
+        if len(ids) <= self.read:
+            return ""
+        before = self._decode(ids[self.prefix:self.read]) if self.read > self.prefix else ""
+        now = self._decode(ids[self.prefix:])
+        if not final and (len(now) <= len(before) or now.endswith("\ufffd")):
+            return ""                     # nothing printable yet (incomplete character): wait for more tokens
+        delta = now[len(before):]
+        self.prefix, self.read = self.read, len(ids)
+        self.text += delta
+        return delta
+
+    def finish(self, output_token_ids: list) -> str:
+        return self.step(output_token_ids, final=True)
+
+
+class StopStringChecker:
+    """Stop-string search on the incrementally detokenised output of one request.  ``step`` is called after every new
+    token with the whole output and searches the tail of the text.  On a hit, ``text`` is cut before the stop string
+    (after it with ``include``)."""
+
+    def __init__(self, tokenizer, stops: list, include: bool = False, skip_special_tokens: bool = True):
+        self.detok = IncrementalDetokenizer(tokenizer, skip_special_tokens)
+        self.stops, self.include = [s for s in stops if s], include
+        self.max_len = max((len(s) for s in self.stops), default=0)
+        self.text = ""
+        self.hit: Optional[str] = None
+
     def step(self, output_token_ids: list) -> Optional[str]:
         if self.hit is not None:
             return self.hit
-        ids = output_token_ids
-        if len(ids) <= self.read:
+        delta = self.detok.step(output_token_ids)
+        if not delta:
             return None
-        before = self._decode(ids[self.prefix:self.read]) if self.read > self.prefix else ""
-        now = self._decode(ids[self.prefix:])
-        if len(now) <= len(before) or now.endswith("\ufffd"):
-            return None                       # nothing printable yet (incomplete character): wait for more tokens
-        delta = now[len(before):]
-        self.prefix, self.read = self.read, len(ids)
         start = max(0, len(self.text) - self.max_len + 1)
         self.text += delta
         best = None

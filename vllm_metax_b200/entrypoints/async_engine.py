@@ -44,6 +44,7 @@ class _Stream:
     wall_arrival: float = field(default_factory=time.time)
     traceparent: Optional[str] = None
     params: Optional[SamplingParams] = None
+    detok: Optional[object] = None                 # IncrementalDetokenizer of this stream's text
 
 
 class AsyncLLM:
@@ -156,15 +157,23 @@ class AsyncLLM:
             self.metrics["generated_tokens"] += len(new)
             st.sent = n
             out = eng.make_output(r) if fin else None
-            if out is not None:
-                text = out.outputs[0].text
-            elif r.stop_checker is not None:
-                # hold back what could still turn out to be the beginning of a stop string
-                t, hold = r.stop_checker.text, r.stop_checker.max_len - 1
-                text = t[: max(0, len(t) - hold)] if hold > 0 else t
+            if r.stop_checker is not None:
+                if fin:
+                    text = out.outputs[0].text
+                else:     # hold back what could still turn out to be the beginning of a stop string
+                    t, hold = r.stop_checker.text, r.stop_checker.max_len - 1
+                    text = t[: max(0, len(t) - hold)] if hold > 0 else t
+            elif eng.tokenizer is None:
+                text = None
             else:
-                text = (eng.tokenizer.decode(r.output_token_ids, skip_special_tokens=r.params.skip_special_tokens)
-                        if eng.tokenizer else None)
+                # one incremental decode per step and stream (decoding the whole output every step would grow
+                # quadratically with its length, on the thread that launches the engine's steps)
+                if st.detok is None:
+                    from ..engine.sampling_params import IncrementalDetokenizer
+
+                    st.detok = IncrementalDetokenizer(eng.tokenizer, r.params.skip_special_tokens)
+                st.detok.step(r.output_token_ids, final=fin)
+                text = st.detok.text
             self._post(st, StreamChunk(rid, new, list(r.output_token_ids), text, fin,
                                        out.outputs[0].finish_reason if out else None, len(r.prompt_token_ids),
                                        ttft=None if st.t_first is None else st.t_first - st.t_arrival,
