@@ -139,3 +139,35 @@ def test_environment_switches(tmp_path, monkeypatch):
     assert _build.build() is None
     monkeypatch.setenv("B200_USE_FUSED_GROUPED_TOPK", "0")
     assert not envs.B200_USE_FUSED_GROUPED_TOPK
+
+
+def test_batch_invariant_switch_pins_the_batch_dependent_choices():
+    """B200_BATCH_INVARIANT=1 (checked in a fresh interpreter: the switch is read once): unsplit decode attention, the
+    native GEMM dispatcher's split-K / stream-K / pair switches off, cascade attention and fused collectives off; and
+    a request generates the same tokens alone and inside a batch."""
+    import subprocess
+    import sys
+
+    code = '''
+import os, json, torch
+import vllm_metax_b200 as pkg
+from vllm_metax_b200 import _custom_ops as ops, LLM, SamplingParams
+from tests.test_e2e_plumbing import tiny_cfg
+assert ops.batch_invariant()
+assert ops.decode_num_splits(1, 1, 100000) == 1 and ops.decode_num_splits(3, 8, 4096) == 1
+assert all(os.environ[k] == "0" for k in ("B200_GEMM_STREAMK", "B200_GEMM_SPLITK", "B200_GEMM_PAIR",
+                                          "B200_FUSED_TP_COLLECTIVES", "B200_CASCADE_ATTENTION", "B200_CUSTOM_ALLREDUCE"))
+llm = LLM(tiny_cfg(), device="cpu", block_size=16, max_model_len=128, max_num_seqs=8, max_num_batched_tokens=64, num_gpu_blocks=64)
+g = torch.Generator().manual_seed(0)
+prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (30, 9, 50, 17)]
+sp = SamplingParams(max_tokens=6, ignore_eos=True)
+alone = [llm.generate([p], sp)[0].outputs[0].token_ids for p in prompts]
+together = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+print("RESULT", json.dumps(alone == together))
+'''
+    env = dict(os.environ, B200_BATCH_INVARIANT="1", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=ROOT, env=env, timeout=300)
+    assert r.returncode == 0 and "RESULT true" in r.stdout, (r.stdout[-500:], r.stderr[-1500:])
+    from vllm_metax_b200 import _custom_ops as ops
+
+    assert not ops.batch_invariant() and ops.decode_num_splits(1, 1, 100000) > 1       # off by default

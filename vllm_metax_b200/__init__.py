@@ -18,6 +18,12 @@ from .version import __version__  # noqa: F401
 _logging.getLogger(__name__).setLevel(getattr(_logging, _os.environ.get("B200_LOG_LEVEL", "INFO").upper(), _logging.INFO))
 
 
+if _os.environ.get("B200_BATCH_INVARIANT", "0") not in ("", "0"):
+    from . import _custom_ops as _ops      # pins the dependent switches before anything reads them
+
+    _ops.batch_invariant()
+
+
 def collect_env() -> None:
     from .collect_env import main
 

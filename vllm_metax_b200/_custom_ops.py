@@ -106,6 +106,8 @@ def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
         if _tc_gemm is None:
             _tc_gemm = bool(envs.B200_TCGEN05_GEMM)
         if _tc_gemm:
+            if force_bn == 0 and batch_invariant():
+                force_bn = 128                 # one tile shape for every token count
             torch.ops.b200.gemm(out, a, w, bias, residual, force_bn, 0)
         else:  # debug switch only: library GEMM
             torch.addmm(bias, a, w.t(), out=out) if bias is not None else torch.mm(a, w.t(), out=out)
@@ -129,7 +131,7 @@ def gemm_silu_mul(a: torch.Tensor, w_interleaved: torch.Tensor, bias: Optional[t
     if _use_cuda(a) and a.dtype in (torch.bfloat16, torch.float16):
         if out is None:
             out = torch.empty(a.shape[0], w_interleaved.shape[0] // 2, dtype=a.dtype, device=a.device)
-        torch.ops.b200.gemm(out, a, w_interleaved, bias, None, 0, 1)
+        torch.ops.b200.gemm(out, a, w_interleaved, bias, None, 128 if batch_invariant() else 0, 1)
         return out
     y = ref.gemm(a, w_interleaved, bias)
     r = (torch.nn.functional.silu(y[:, 0::2].float()) * y[:, 1::2].float()).to(a.dtype)
@@ -359,8 +361,26 @@ def _decode_workspace(device, numel: int) -> torch.Tensor:
     return ws
 
 
+def batch_invariant() -> bool:
+    """``B200_BATCH_INVARIANT=1``: see envs.py.  The first call also pins the switches the native GEMM dispatcher reads
+    from the environment (it caches them at its first launch)."""
+    global _batch_invariant
+    if _batch_invariant is None:
+        _batch_invariant = bool(envs.B200_BATCH_INVARIANT)
+        if _batch_invariant:
+            for name in ("B200_GEMM_STREAMK", "B200_GEMM_SPLITK", "B200_GEMM_PAIR", "B200_FUSED_TP_COLLECTIVES",
+                         "B200_CASCADE_ATTENTION", "B200_CUSTOM_ALLREDUCE"):
+                os.environ[name] = "0"
+    return _batch_invariant
+
+
+_batch_invariant: Optional[bool] = None
+
+
 def decode_num_splits(batch: int, num_kv_heads: int, max_seq_len: int, row_tiles: int = 1, sms: int = 148) -> int:
     """Enough KV splits to give every SM a CTA, never finer than 256 tokens per split."""
+    if batch_invariant():
+        return 1                               # the split count follows the batch size: one pass per sequence instead
     ctas = max(1, batch * num_kv_heads * row_tiles)
     if ctas >= sms:
         return 1
@@ -858,6 +878,8 @@ def mla_decode(q, mla_cache, block_table, seq_lens, scale, *, query_start_loc=No
         if impl == 0 and not envs.B200_MLA_TCGEN05:
             impl = 1
         out = torch.empty(T, H, 512, dtype=q.dtype, device=q.device) if out is None else out
+        if num_splits <= 0 and batch_invariant():
+            num_splits = 1
         if num_splits <= 0:
             # heads per CTA as chosen by the kernel launcher (csrc/mla_decode.cu:mla_decode_heads_per_cta)
             hpc = 16 if H <= 16 else (32 if (H <= 32 or mla_cache.dtype == torch.uint8) else 64)

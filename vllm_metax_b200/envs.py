@@ -54,6 +54,11 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # attend that prefix once for the whole step.  Taken when prefix_tokens * (requests - 1) reaches the threshold.
     "B200_CASCADE_ATTENTION": _flag("B200_CASCADE_ATTENTION", "1"),
     "B200_CASCADE_MIN_SAVED_TOKENS": _int("B200_CASCADE_MIN_SAVED_TOKENS", 131072),
+    # Batch-invariant execution (the reference's VLLM_BATCH_INVARIANT, vllm_metax/v1/attention/backends/flash_attn.py:1063,
+    # 1145): a request's tokens must not depend on what else is in its step.  Every reduction whose order follows the
+    # batch is pinned: decode attention and MLA decode run unsplit, GEMMs take one fixed tile shape without split-K /
+    # stream-K / CTA pairs / operand swap, cascade attention and the fused tensor-parallel collectives are off.
+    "B200_BATCH_INVARIANT": _flag("B200_BATCH_INVARIANT", "0"),
     # Gated delta rule (Qwen3-Next): prompt chunks of at least MIN_TOKENS tokens take the chunked matrix form
     # (ops/gdn.py:gated_delta_rule_chunked, PyTorch products) instead of the recurrent kernel.  0 = always recurrent.
     "B200_GDN_CHUNKED": _flag("B200_GDN_CHUNKED", "0"),
