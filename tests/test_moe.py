@@ -130,3 +130,21 @@ def test_qwen3_moe_gpu_tracks_cpu(kernel_status_ok):
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (70, 130)]
     lockstep(cpu, gpu_llm, prompts, steps=4, tol=2e-2)
+
+
+def test_moe_chunked_over_tokens_equals_one_pass(monkeypatch):
+    """B200_FUSED_MOE_CHUNK_SIZE: a long step goes through the experts in pieces with the same result."""
+    import torch
+
+    from vllm_metax_b200.layers.fused_moe import FusedMoE
+
+    torch.manual_seed(0)
+    moe = FusedMoE(8, 2, 32, 16, dtype=torch.float32)
+    moe.w13_weight.data.normal_(0, 0.2)
+    moe.w2_weight.data.normal_(0, 0.2)
+    x, logits, shared = torch.randn(70, 32), torch.randn(70, 8), torch.randn(70, 32)
+    want = moe.forward(x, logits, shared)
+    monkeypatch.setenv("B200_FUSED_MOE_CHUNK_SIZE", "16")
+    torch.testing.assert_close(moe.forward(x, logits, shared), want, rtol=1e-5, atol=1e-5)
+    monkeypatch.setenv("B200_FUSED_MOE_CHUNK_SIZE", "0")
+    torch.testing.assert_close(moe.forward(x, logits, None), moe.forward(x, logits, shared) - shared, rtol=1e-5, atol=1e-5)

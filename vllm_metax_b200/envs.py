@@ -77,6 +77,9 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # Sequence-parallel MoE through the NVLink dispatch / combine kernels instead of experts-on-all-tokens + all-reduce.
     "B200_MOE_A2A": _flag("B200_MOE_A2A", "0"),
     # Pack topk weights/ids/scales into one tensor for the AG/RS dispatch.
+    # Tokens per pass through the expert kernels (bounds the expert-sorted workspace of a MoE layer on very long steps;
+    # the reference's VLLM_FUSED_MOE_CHUNK_SIZE).  0 = never split.
+    "B200_FUSED_MOE_CHUNK_SIZE": _int("B200_FUSED_MOE_CHUNK_SIZE", 32768),
     "B200_OPTIMIZED_DP_ALL2ALL": _flag("B200_OPTIMIZED_DP_ALL2ALL", "1"),
     "B200_SUPPORTS_FP8": _flag("B200_SUPPORTS_FP8", "1"),
     "B200_USE_FUSED_GROUPED_TOPK": _flag("B200_USE_FUSED_GROUPED_TOPK", "1"),

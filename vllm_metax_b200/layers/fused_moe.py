@@ -305,10 +305,21 @@ class FusedMoE(nn.Module):
         if self.reduce_results and self.sequence_parallel(x):
             return self._forward_sp(x, router_logits, shared_out)
         w, ids = self.route(router_logits)
-        if self.quant_method is not None:
-            y = self.quant_method.apply(self, x, w, ids, shared_out)
+
+        def experts(xs, ws, idss, shared):
+            if self.quant_method is not None:
+                return self.quant_method.apply(self, xs, ws, idss, shared)
+            return fused_experts(xs, self.w13_weight, self.w2_weight, ws, idss, self.num_local, self.expert_map, shared)
+
+        chunk = int(envs.B200_FUSED_MOE_CHUNK_SIZE)
+        T = x.shape[0]
+        if chunk > 0 and T > chunk:
+            # the expert-sorted copies of the rows ([T * top_k + padding, hidden] and [.., 2 * intermediate]) are the
+            # layer's workspace: very long steps go through it in pieces
+            y = torch.cat([experts(x[i: i + chunk], w[i: i + chunk], ids[i: i + chunk],
+                                   None if shared_out is None else shared_out[i: i + chunk]) for i in range(0, T, chunk)])
         else:
-            y = fused_experts(x, self.w13_weight, self.w2_weight, w, ids, self.num_local, self.expert_map, shared_out)
+            y = experts(x, w, ids, shared_out)
         if self.reduce_results and self.ep > 1:
             y = ps.tensor_model_parallel_all_reduce(y)
         return y
