@@ -242,3 +242,19 @@ def test_indexer_bf16_variant_gpu(kernel_status_ok):
             torch.testing.assert_close(mine[fin], lg[fin], rtol=2e-2, atol=5e-2)
             assert set(got[t].cpu().tolist()) - {-1} == set(want[t].tolist()) - {-1} or lim > 64
             t += 1
+
+
+def test_deepseek_graph_under_another_architecture_name_cpu():
+    """A checkpoint whose config names its own architecture but is the DeepSeek-V3 graph (MLA fields + a model type of
+    that lineage) is served by the DeepSeek class."""
+    d = dict(architectures=["JoyAILLMFlashForCausalLM"], model_type="joyai_llm_flash", vocab_size=512, hidden_size=128,
+             intermediate_size=256, num_hidden_layers=2, num_attention_heads=4, q_lora_rank=48, kv_lora_rank=512,
+             qk_nope_head_dim=32, qk_rope_head_dim=64, v_head_dim=32, n_routed_experts=8, num_experts_per_tok=2,
+             moe_intermediate_size=64, n_shared_experts=1, n_group=2, topk_group=1, first_k_dense_replace=1,
+             max_position_embeddings=256, torch_dtype="float32")
+    mc = ModelConfig.from_hf_dict(d)
+    assert mc.architecture == "DeepseekV3ForCausalLM" and mc.is_mla and mc.scoring_func == "sigmoid"
+    out = LLM(mc, device="cpu", **KW).generate([[1, 2, 3, 4]], SamplingParams(max_tokens=3, ignore_eos=True))
+    assert len(out[0].outputs[0].token_ids) == 3
+    other = ModelConfig.from_hf_dict(dict(d, model_type="something_else", architectures=["LlamaForCausalLM"]))
+    assert other.architecture == "LlamaForCausalLM"

@@ -79,6 +79,10 @@ def _canonical_hf_keys(d: dict) -> dict:
     return d
 
 
+_DEEPSEEK_V3_MODEL_TYPES = ("joyai_llm_flash", "kimi_k2", "AXK1", "pangu_ultra_moe", "glm4_moe_lite", "longcat_flash",
+                            "deepseek_v3", "deepseek_v2")
+
+
 @dataclass
 class ModelConfig:
     architecture: str = "LlamaForCausalLM"
@@ -190,6 +194,14 @@ class ModelConfig:
         d = _canonical_hf_keys(d)
         archs = d.get("architectures") or ["LlamaForCausalLM"]
         arch = archs[0]
+        # checkpoints that are the DeepSeek-V3 graph (MLA + routed experts) under an architecture name of their own:
+        # served by that model class (the reference marks the same model types as MLA models,
+        # vllm_metax/patch/enhancement/joyai_support/model_arch_config_convertor.py:22-47)
+        from .models import _MODELS
+
+        if arch not in _MODELS and d.get("kv_lora_rank") is not None and \
+                d.get("model_type") in _DEEPSEEK_V3_MODEL_TYPES:
+            arch = "DeepseekV3ForCausalLM"
         # DeepSeek-V3 lineage: sigmoid scores + bias-corrected grouped top-k even when the config (HF-native exports)
         # does not spell it out
         v3_routing = any(t in arch for t in ("DeepseekV3", "DeepseekV32", "GlmMoeDsa", "DeepseekV4", "Glm4Moe"))
