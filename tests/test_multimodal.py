@@ -383,3 +383,67 @@ def test_llava_next_matches_hugging_face(tmp_path):
     img = torch.randint(0, 255, (3, 40, 100), dtype=torch.uint8)
     out = llm.generate([{"prompt_token_ids": [1, IMG_TOK, 3], "multi_modal_data": {"image": img}}], sp)
     assert len(out[0].outputs[0].token_ids) == 5
+
+
+@pytest.mark.parametrize("chunk", [64, 7])
+def test_qwen3_vl_matches_hugging_face(tmp_path, chunk):
+    """Qwen3-VL: interpolated position embeddings, interleaved M-RoPE, DeepStack features added after the first
+    decoder layers - across chunked prefill (the image run is split between steps) against Hugging Face."""
+    from vllm_metax_b200 import LLM, SamplingParams
+
+    torch.manual_seed(0)
+    c = tf.Qwen3VLConfig(
+        text_config=dict(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=32, max_position_embeddings=256, tie_word_embeddings=False,
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [6, 5, 5],
+                                          "mrope_interleaved": True}),
+        vision_config=dict(depth=3, hidden_size=64, intermediate_size=96, out_hidden_size=128, num_heads=4, in_channels=3,
+                           patch_size=8, spatial_merge_size=2, temporal_patch_size=2, num_position_embeddings=36,
+                           deepstack_visual_indexes=[0, 1]),
+        image_token_id=QV_IMG, video_token_id=503, vision_start_token_id=QV_START, vision_end_token_id=QV_END,
+        tie_word_embeddings=False)
+    hf = tf.Qwen3VLForConditionalGeneration(c).eval().float()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.dim() == 1:
+                p.add_(0.1 * torch.randn_like(p))
+            else:
+                p.mul_(2.0)
+    hf.save_pretrained(str(tmp_path))
+    llm = LLM(str(tmp_path), dtype="float32", device="cpu", max_model_len=128, num_gpu_blocks=32, block_size=16,
+              max_num_batched_tokens=chunk)
+    model = llm.engine.runner.model
+    assert type(model).__name__ == "Qwen3VLForConditionalGeneration" and model.language_model.model.takes_deepstack
+    g = torch.Generator().manual_seed(1)
+    grid_a, grid_b = (1, 4, 6), (1, 2, 4)
+    dim = 3 * 2 * 8 * 8
+    pa, pb = torch.randn(24, dim, generator=g), torch.randn(8, dim, generator=g)
+    one = [5, 9, QV_START] + [QV_IMG] * 6 + [QV_END, 33, 100, 7, 8, 200, 31]
+    two = [3, QV_START] + [QV_IMG] * 6 + [QV_END, 40, QV_START] + [QV_IMG] * 2 + [QV_END, 60, 61, 62]
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    outs = llm.generate([
+        {"prompt_token_ids": one, "multi_modal_data": {"pixel_values": pa, "image_grid_thw": [grid_a]}},
+        {"prompt_token_ids": two, "multi_modal_data": {"pixel_values": torch.cat([pa, pb]), "image_grid_thw": [grid_a, grid_b]}},
+        {"prompt_token_ids": [5, 9, 33, 100, 7]},
+    ], sp)
+    got = [list(o.outputs[0].token_ids) for o in outs]
+
+    def want(ids, pixels=None, grids=None):
+        kw = {} if pixels is None else dict(pixel_values=pixels, image_grid_thw=torch.tensor(grids),
+                                            mm_token_type_ids=torch.tensor([[1 if t == QV_IMG else 0 for t in ids]]))
+        with torch.no_grad():
+            out = hf.generate(input_ids=torch.tensor([ids]), max_new_tokens=6, do_sample=False, eos_token_id=None,
+                              pad_token_id=0, **kw)
+        return out[0, len(ids):].tolist()
+
+    assert got[0] == want(one, pa, [grid_a])
+    assert got[1] == want(two, torch.cat([pa, pb]), [grid_a, grid_b])
+    assert got[2] == want([5, 9, 33, 100, 7])
+
+
+def test_mrope_frequency_streams():
+    from vllm_metax_b200.models.qwen2_vl import mrope_stream_of_frequency
+
+    assert mrope_stream_of_frequency([2, 3, 3], 8, False) == [0, 0, 1, 1, 1, 2, 2, 2]
+    assert mrope_stream_of_frequency([6, 5, 5], 16, True) == [0, 1, 2] * 5 + [0]
+    assert mrope_stream_of_frequency([24, 20, 20], 64, True)[58:] == [1, 2, 0, 0, 0, 0]

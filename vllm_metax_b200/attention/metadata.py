@@ -89,4 +89,9 @@ def merge_multimodal_embeddings(h: torch.Tensor) -> torch.Tensor:
     md = ctx.attn_metadata if ctx is not None else None
     if md is None or "mm_embeds" not in md.extra:
         return h
-    return h.index_copy_(0, md.extra["mm_rows"], md.extra["mm_embeds"].to(h.dtype))
+    emb = md.extra["mm_embeds"]
+    H = h.shape[1]
+    if emb.shape[1] > H:          # DeepStack models: the wider rows carry extra feature levels for the first layers
+        md.extra["mm_deepstack"] = emb[:, H:].reshape(emb.shape[0], -1, H)
+        emb = emb[:, :H]
+    return h.index_copy_(0, md.extra["mm_rows"], emb.to(h.dtype))

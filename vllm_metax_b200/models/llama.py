@@ -23,7 +23,7 @@ import torch.nn as nn
 
 from .. import _custom_ops as ops
 from ..config import ModelConfig
-from ..attention.metadata import merge_multimodal_embeddings
+from ..attention.metadata import get_forward_context, merge_multimodal_embeddings
 from ..layers.attention import Attention
 from ..layers.basic import ParallelLMHead, RMSNorm, SiluAndMul, VocabParallelEmbedding, get_rope
 from ..layers.linear import GateUpSiluLinear, MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear
@@ -103,7 +103,8 @@ class LlamaAttention(nn.Module):
             pos3 = get_forward_context().attn_metadata.extra.get("mrope_positions")
             if pos3 is None:
                 pos3 = positions[None, :].expand(3, -1)
-            q, k = apply_mrope(q, k, pos3, self.rope.cos_sin_cache, sections, self.head_dim)
+            q, k = apply_mrope(q, k, pos3, self.rope.cos_sin_cache, sections, self.head_dim,
+                               getattr(self, "mrope_interleaved", False))
             return self.attn(q, k, v.contiguous(), positions, None)
         return self.attn(q, k, v, positions, self.rope)
 
@@ -176,14 +177,22 @@ class LlamaModel(nn.Module):
     def forward(self, input_ids, positions, intermediate: Optional[dict] = None):
         # large token counts: GEMM + reduce + norm as one NVLink kernel; small ones (decode steps): the split-K GEMMs
         # of the single-GPU path + the peer-store all-reduce are faster than a 128x256-tile kernel on a few tiles
-        if getattr(self, "fused_ar", None) is not None and input_ids.shape[0] >= getattr(self, "fused_min_tokens", 0):
+        deep_rows, md = None, None
+        if getattr(self, "takes_deepstack", False):       # Qwen3-VL: extra visual feature levels for the first layers
+            md = get_forward_context().attn_metadata
+            deep_rows = md.extra.get("mm_rows")
+        if getattr(self, "fused_ar", None) is not None and input_ids.shape[0] >= getattr(self, "fused_min_tokens", 0) \
+                and deep_rows is None:
             return self.forward_fused_tp(input_ids, positions)
         if self.embed_tokens is not None:
             h, residual = merge_multimodal_embeddings(self.embed_tokens(input_ids)), None
         else:
             h, residual = intermediate["hidden_states"], intermediate["residual"]
+        deep = md.extra.get("mm_deepstack") if deep_rows is not None else None     # [N, levels, hidden] (DeepStack)
         for i in range(self.start_layer, self.end_layer):
             h, residual = self.layers[str(i)](positions, h, residual)
+            if deep is not None and i < deep.shape[1]:
+                h.index_add_(0, deep_rows, deep[:, i].to(h.dtype))       # level i joins the stream after layer i
         if self.norm is None:
             return {"hidden_states": h, "residual": residual}
         h, _ = self.norm(h, residual)

@@ -36,19 +36,35 @@ from ..layers.linear import ReplicatedLinear
 from ..layers.mm_encoder_attention import encoder_attention
 
 
+def mrope_stream_of_frequency(sections, half: int, interleaved: bool) -> list:
+    """Which of the three position streams (0 = temporal, 1 = height, 2 = width) turns frequency pair j.  Chunked
+    (Qwen2-VL): the first ``sections[0]`` pairs are temporal, the next height, the rest width.  Interleaved
+    (Qwen3-VL): pairs 1, 4, 7, ... below ``3 * sections[1]`` are height, pairs 2, 5, 8, ... below ``3 * sections[2]``
+    width, everything else temporal."""
+    if not interleaved:
+        out = [0] * sections[0] + [1] * sections[1] + [2] * sections[2]
+        assert len(out) == half, "mrope_section must cover half of the head dimension"
+        return out
+    out = [0] * half
+    for j in range(half):
+        if j % 3 == 1 and j < 3 * sections[1]:
+            out[j] = 1
+        elif j % 3 == 2 and j < 3 * sections[2]:
+            out[j] = 2
+    return out
+
+
 def apply_mrope(q: torch.Tensor, k: torch.Tensor, pos3: torch.Tensor, cos_sin_cache: torch.Tensor, sections,
-                head_dim: int) -> tuple[torch.Tensor, torch.Tensor]:
-    """NeoX rotation of ``q [T, Hq * D]`` / ``k [T, Hkv * D]`` where frequency pair j turns with position stream
-    ``section_of(j)`` of ``pos3 [3, T]``.  ``cos_sin_cache [max_pos, D]`` = ``[cos(D/2) | sin(D/2)]``."""
+                head_dim: int, interleaved: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+    """NeoX rotation of ``q [T, Hq * D]`` / ``k [T, Hkv * D]`` where frequency pair j turns with the position stream
+    ``mrope_stream_of_frequency`` names, taken from ``pos3 [3, T]``.  ``cos_sin_cache [max_pos, D]`` =
+    ``[cos(D/2) | sin(D/2)]``."""
     half = head_dim // 2
     cs = cos_sin_cache.index_select(0, pos3.reshape(-1).long()).view(3, -1, head_dim).float()      # [3, T, D]
-    cos_parts, sin_parts, o = [], [], 0
-    for i, n in enumerate(sections):
-        cos_parts.append(cs[i, :, o:o + n])
-        sin_parts.append(cs[i, :, half + o: half + o + n])
-        o += n
-    assert o == half, "mrope_section must cover half of the head dimension"
-    cos, sin = torch.cat(cos_parts, -1)[:, None, :], torch.cat(sin_parts, -1)[:, None, :]            # [T, 1, D/2]
+    sel = torch.as_tensor(mrope_stream_of_frequency(list(sections), half, interleaved), device=cs.device)
+    j = torch.arange(half, device=cs.device)
+    cos = cs[sel, :, j].transpose(0, 1)[:, None, :]                                               # [T, 1, D/2]
+    sin = cs[sel, :, half + j].transpose(0, 1)[:, None, :]
 
     def rot(x):
         T = x.shape[0]
@@ -155,6 +171,7 @@ class Qwen2VisionTower(nn.Module):
 class Qwen2VLForConditionalGeneration(nn.Module):
     is_multimodal = True
     uses_mrope = True
+    image_mean, image_std = (0.48145466, 0.4578275, 0.40821073), (0.26862954, 0.26130258, 0.27577711)    # CLIP statistics
     renames = [(r"^model\.language_model\.", "language_model.model."), (r"^model\.visual\.", "visual."),
                (r"^lm_head\.", "language_model.lm_head."), (r"^model\.(?!language_model|visual)", "language_model.model."),
                (r"^visual\.patch_embed\.proj\.", "visual.patch_embed."),
@@ -189,8 +206,7 @@ class Qwen2VLForConditionalGeneration(nn.Module):
         H = max(unit, round(x.shape[1] / unit) * unit)
         W = max(unit, round(x.shape[2] / unit) * unit)
         x = F.interpolate(x[None], size=(H, W), mode="bicubic", align_corners=False)[0].clamp(0, 1)
-        mean = torch.tensor([0.48145466, 0.4578275, 0.40821073]).view(3, 1, 1)
-        std = torch.tensor([0.26862954, 0.26130258, 0.27577711]).view(3, 1, 1)
+        mean, std = torch.tensor(self.image_mean).view(3, 1, 1), torch.tensor(self.image_std).view(3, 1, 1)
         x = ((x - mean) / std)[None].repeat(v.tpatch, 1, 1, 1)                       # [tp, 3, H, W]
         gh, gw, m, p = H // v.patch, W // v.patch, v.merge, v.patch
         x = x.reshape(1, v.tpatch, 3, gh // m, m, p, gw // m, m, p).permute(0, 3, 6, 4, 7, 2, 1, 5, 8)
@@ -378,3 +394,126 @@ class Qwen2_5_VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
         self.mrope_section = list(rp.get("mrope_section") or [cfg.head_dim // 2 - 2 * (cfg.head_dim // 6)] + [cfg.head_dim // 6] * 2)
         for layer in self.language_model.model.layers.values():
             layer.self_attn.mrope_section = self.mrope_section
+
+
+# ------------------------------------------------------------------------------------------------------ Qwen3-VL
+class Qwen3VisionTower(nn.Module):
+    """Qwen3-VL vision tower: patch projection with bias, learned position embeddings on a fixed square grid that are
+    bilinearly interpolated to the image's patch grid, the Qwen2-VL blocks (LayerNorm, 2-D rotary, GELU MLP), a merger,
+    and DeepStack mergers that turn the hidden states after chosen blocks into extra features for the first decoder
+    layers."""
+
+    def __init__(self, vc: dict, dtype):
+        super().__init__()
+        self.embed, self.heads = vc["hidden_size"], vc["num_heads"]
+        self.patch, self.merge, self.tpatch = vc.get("patch_size", 16), vc.get("spatial_merge_size", 2), vc.get("temporal_patch_size", 2)
+        self.in_ch = vc.get("in_channels", 3)
+        self.patch_dim = self.in_ch * self.tpatch * self.patch * self.patch
+        self.patch_embed = ReplicatedLinear(self.patch_dim, self.embed, True, dtype)
+        self.side = int(round(vc["num_position_embeddings"] ** 0.5))
+        self.pos_embed = nn.Parameter(torch.zeros(vc["num_position_embeddings"], self.embed, dtype=dtype), requires_grad=False)
+        self.blocks = nn.ModuleList([Qwen2VisionBlock(self.embed, self.heads, vc["intermediate_size"],
+                                                      vc.get("hidden_act", "gelu_pytorch_tanh"), dtype)
+                                     for _ in range(vc["depth"])])
+        unit = self.embed * self.merge * self.merge
+        self.deepstack_indexes = list(vc.get("deepstack_visual_indexes") or [])
+
+        def merger(norm_dim):
+            return nn.ModuleDict({"norm": LayerNorm(norm_dim, 1e-6, dtype), "fc1": ReplicatedLinear(unit, unit, True, dtype),
+                                  "fc2": ReplicatedLinear(unit, vc["out_hidden_size"], True, dtype)})
+
+        self.merger = merger(self.embed)
+        self.deepstack_mergers = nn.ModuleList([merger(unit) for _ in self.deepstack_indexes])
+
+    _angles = Qwen2VisionTower._angles
+
+    def _pos(self, grids: list, device) -> torch.Tensor:
+        """Position embeddings of every patch, in the tower's patch order (merge blocks of ``m x m`` neighbours)."""
+        S, m, out = self.side, self.merge, []
+        table = self.pos_embed.float()
+        for t, h, w in grids:
+            ys, xs = torch.linspace(0, S - 1, h, device=device), torch.linspace(0, S - 1, w, device=device)
+            y0, x0 = ys.long(), xs.long()
+            y1, x1 = (y0 + 1).clamp(max=S - 1), (x0 + 1).clamp(max=S - 1)
+            dy, dx = (ys - y0)[:, None, None], (xs - x0)[None, :, None]
+            g = lambda yy, xx: table[(yy[:, None] * S + xx[None, :])]                       # [h, w, embed]
+            e = g(y0, x0) * (1 - dy) * (1 - dx) + g(y0, x1) * (1 - dy) * dx + g(y1, x0) * dy * (1 - dx) + g(y1, x1) * dy * dx
+            e = e.reshape(h // m, m, w // m, m, -1).permute(0, 2, 1, 3, 4).reshape(h * w, -1)
+            out.append(e.repeat(t, 1))
+        return torch.cat(out)
+
+    def _merge(self, mod, x: torch.Tensor, post_shuffle: bool) -> torch.Tensor:
+        unit = self.embed * self.merge * self.merge
+        x = mod["norm"](x.reshape(-1, unit)) if post_shuffle else mod["norm"](x).reshape(-1, unit)
+        return mod["fc2"](F.gelu(mod["fc1"](x)))
+
+    def forward(self, patches: torch.Tensor, grids: list):
+        """``patches [N, patch_dim]`` -> ``(features [N / merge^2, hidden_text], [DeepStack features, same shape])``."""
+        x = self.patch_embed(patches.to(self.patch_embed.weight.dtype))
+        x = x + self._pos(grids, x.device).to(x.dtype)
+        ang = self._angles(grids, x.device)
+        emb = torch.cat([ang, ang], -1)
+        cos, sin = emb.cos(), emb.sin()
+        frames = [h * w for t, h, w in grids for _ in range(t)]
+        cu = torch.tensor([0] + list(np.cumsum(frames)), dtype=torch.int32, device=x.device)
+        deep = []
+        for i, blk in enumerate(self.blocks):
+            x = blk(x, cos, sin, cu, max(frames))
+            if i in self.deepstack_indexes:
+                deep.append(self._merge(self.deepstack_mergers[self.deepstack_indexes.index(i)], x, True))
+        return self._merge(self.merger, x, False), deep
+
+
+class Qwen3VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
+    """Qwen3-VL: Qwen3 decoder (per-head q / k norms) with interleaved M-RoPE, the tower above, and DeepStack - the
+    features taken after chosen vision blocks are added to the hidden states of the image tokens after the first
+    decoder layers.  The engine carries them beside the image features (one wider row per image token) and the
+    decoder's layer loop adds level i after layer i (``attention/metadata.py:merge_multimodal_embeddings``)."""
+
+    renames = [(r"^model\.language_model\.", "language_model.model."), (r"^model\.visual\.", "visual."),
+               (r"^lm_head\.", "language_model.lm_head."), (r"^model\.(?!language_model|visual)", "language_model.model."),
+               (r"^visual\.patch_embed\.proj\.", "visual.patch_embed."), (r"^visual\.pos_embed\.weight$", "visual.pos_embed"),
+               (r"^visual\.blocks\.(\d+)\.attn\.", r"visual.blocks.\1."),
+               (r"^visual\.blocks\.(\d+)\.mlp\.linear_fc([12])\.", r"visual.blocks.\1.fc\2."),
+               (r"^visual\.merger\.linear_fc([12])\.", r"visual.merger.fc\1."),
+               (r"^visual\.deepstack_merger_list\.(\d+)\.linear_fc([12])\.", r"visual.deepstack_mergers.\1.fc\2."),
+               (r"^visual\.deepstack_merger_list\.(\d+)\.norm\.", r"visual.deepstack_mergers.\1.norm.")]
+
+    def __init__(self, cfg: ModelConfig):
+        nn.Module.__init__(self)
+        from . import get_model_class
+
+        self.cfg = cfg
+        hf = cfg.hf_config
+        self.image_token_id = int(hf.get("image_token_id", 151655))
+        self.visual = Qwen3VisionTower(hf["vision_config"], cfg.dtype)
+        self.language_model = get_model_class("Qwen3ForCausalLM")(cfg)
+        tc = hf.get("text_config", hf)
+        rp = tc.get("rope_parameters") or tc.get("rope_scaling") or hf.get("rope_scaling") or {}
+        self.mrope_section = list(rp.get("mrope_section") or [24, 20, 20])
+        for layer in self.language_model.model.layers.values():
+            layer.self_attn.mrope_section = self.mrope_section
+            layer.self_attn.mrope_interleaved = bool(rp.get("mrope_interleaved", True))
+        self.language_model.model.takes_deepstack = bool(self.visual.deepstack_indexes)
+
+    image_mean, image_std = (0.5, 0.5, 0.5), (0.5, 0.5, 0.5)          # this family's image processor
+
+    @torch.no_grad()
+    def encode_request(self, prompt_token_ids: list, mm: dict, device):
+        orig = self.visual.forward
+        deep_box = []
+
+        def tower(patches, grids):                 # the parent's request logic with this tower's two outputs
+            feats, deep = orig(patches, grids)
+            deep_box.append(deep)
+            return feats
+
+        self.visual.forward = tower
+        try:
+            ids, (feats, pos, digest), extras = super().encode_request(prompt_token_ids, mm, device)
+        finally:
+            self.visual.forward = orig
+        deep = deep_box[0]
+        if deep:                                    # [N, hidden * (1 + levels)]: features | level 0 | level 1 | ...
+            feats = torch.cat([feats] + deep, dim=-1)
+        return ids, (feats, pos, digest), extras
