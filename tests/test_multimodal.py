@@ -447,3 +447,50 @@ def test_mrope_frequency_streams():
     assert mrope_stream_of_frequency([2, 3, 3], 8, False) == [0, 0, 1, 1, 1, 2, 2, 2]
     assert mrope_stream_of_frequency([6, 5, 5], 16, True) == [0, 1, 2] * 5 + [0]
     assert mrope_stream_of_frequency([24, 20, 20], 64, True)[58:] == [1, 2, 0, 0, 0, 0]
+
+
+def test_qwen3_vl_moe_matches_hugging_face(tmp_path):
+    """The same tower, M-RoPE and DeepStack over the mixture-of-experts decoder; stacked expert tensors of the
+    checkpoint are split per expert at load."""
+    from vllm_metax_b200 import LLM, SamplingParams
+
+    torch.manual_seed(0)
+    c = tf.Qwen3VLMoeConfig(
+        text_config=dict(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=32, max_position_embeddings=256, num_experts=4, num_experts_per_tok=2,
+                         moe_intermediate_size=64, decoder_sparse_step=1, mlp_only_layers=[], tie_word_embeddings=False,
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [6, 5, 5],
+                                          "mrope_interleaved": True}),
+        vision_config=dict(depth=2, hidden_size=64, intermediate_size=96, out_hidden_size=128, num_heads=4, in_channels=3,
+                           patch_size=8, spatial_merge_size=2, temporal_patch_size=2, num_position_embeddings=36,
+                           deepstack_visual_indexes=[0, 1]),
+        image_token_id=QV_IMG, video_token_id=503, vision_start_token_id=QV_START, vision_end_token_id=QV_END,
+        tie_word_embeddings=False)
+    hf = tf.Qwen3VLMoeForConditionalGeneration(c).eval().float()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.dim() == 1:
+                p.add_(0.1 * torch.randn_like(p))
+            elif p.dim() == 3:
+                p.normal_(0, 0.15)                       # stacked experts (left uninitialised by the constructor)
+            else:
+                p.mul_(2.0)
+    hf.save_pretrained(str(tmp_path))
+    llm = LLM(str(tmp_path), dtype="float32", device="cpu", max_model_len=128, num_gpu_blocks=32, block_size=16,
+              max_num_batched_tokens=9)
+    assert type(llm.engine.runner.model).__name__ == "Qwen3VLMoeForConditionalGeneration"
+    g = torch.Generator().manual_seed(3)
+    grid = (1, 4, 4)
+    px = torch.randn(16, 3 * 2 * 8 * 8, generator=g)
+    ids = [5, 9, QV_START] + [QV_IMG] * 4 + [QV_END, 33, 100, 7, 8, 200, 31]
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    got = llm.generate([{"prompt_token_ids": ids, "multi_modal_data": {"pixel_values": px, "image_grid_thw": [grid]}},
+                        {"prompt_token_ids": [5, 9, 33, 100, 7]}], sp)
+    with torch.no_grad():
+        want = hf.generate(input_ids=torch.tensor([ids]), max_new_tokens=6, do_sample=False, eos_token_id=None, pad_token_id=0,
+                           pixel_values=px, image_grid_thw=torch.tensor([grid]),
+                           mm_token_type_ids=torch.tensor([[1 if t == QV_IMG else 0 for t in ids]]))[0, len(ids):].tolist()
+        text = hf.generate(input_ids=torch.tensor([[5, 9, 33, 100, 7]]), max_new_tokens=6, do_sample=False, eos_token_id=None,
+                           pad_token_id=0)[0, 5:].tolist()
+    assert list(got[0].outputs[0].token_ids) == want
+    assert list(got[1].outputs[0].token_ids) == text

@@ -45,6 +45,7 @@ _MODELS: dict[str, tuple[str, str]] = {
     "Qwen2VLForConditionalGeneration": ("qwen2_vl", "Qwen2VLForConditionalGeneration"),
     "Qwen2_5_VLForConditionalGeneration": ("qwen2_vl", "Qwen2_5_VLForConditionalGeneration"),
     "Qwen3VLForConditionalGeneration": ("qwen2_vl", "Qwen3VLForConditionalGeneration"),
+    "Qwen3VLMoeForConditionalGeneration": ("qwen2_vl", "Qwen3VLMoeForConditionalGeneration"),
     "InternVLForConditionalGeneration": ("internvl", "InternVLForConditionalGeneration"),
     "InternVLChatModel": ("internvl", "InternVLChatModel"),
     "MambaForCausalLM": ("mamba", "MambaForCausalLM"),

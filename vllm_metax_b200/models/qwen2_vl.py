@@ -487,7 +487,7 @@ class Qwen3VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
         hf = cfg.hf_config
         self.image_token_id = int(hf.get("image_token_id", 151655))
         self.visual = Qwen3VisionTower(hf["vision_config"], cfg.dtype)
-        self.language_model = get_model_class("Qwen3ForCausalLM")(cfg)
+        self.language_model = get_model_class(self.decoder_arch)(cfg)
         tc = hf.get("text_config", hf)
         rp = tc.get("rope_parameters") or tc.get("rope_scaling") or hf.get("rope_scaling") or {}
         self.mrope_section = list(rp.get("mrope_section") or [24, 20, 20])
@@ -497,6 +497,7 @@ class Qwen3VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
         self.language_model.model.takes_deepstack = bool(self.visual.deepstack_indexes)
 
     image_mean, image_std = (0.5, 0.5, 0.5), (0.5, 0.5, 0.5)          # this family's image processor
+    decoder_arch = "Qwen3ForCausalLM"
 
     @torch.no_grad()
     def encode_request(self, prompt_token_ids: list, mm: dict, device):
@@ -517,3 +518,28 @@ class Qwen3VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
         if deep:                                    # [N, hidden * (1 + levels)]: features | level 0 | level 1 | ...
             feats = torch.cat([feats] + deep, dim=-1)
         return ids, (feats, pos, digest), extras
+
+
+class Qwen3VLMoeForConditionalGeneration(Qwen3VLForConditionalGeneration):
+    """Qwen3-VL-MoE: the Qwen3-VL tower, M-RoPE and DeepStack over the Qwen3-MoE decoder.  Checkpoints keep the experts
+    of a layer in two stacked tensors (``experts.gate_up_proj [E, 2I, H]``: gate rows then up rows;
+    ``experts.down_proj [E, H, I]``); they are handed to the expert-parallel loader one expert at a time."""
+
+    decoder_arch = "Qwen3MoeForCausalLM"
+
+    def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]) -> set[str]:
+        def per_expert():
+            for name, w in weights:
+                if name.endswith(".mlp.experts.gate_up_proj"):
+                    base, inter = name[: -len("gate_up_proj")], w.shape[1] // 2
+                    for e in range(w.shape[0]):
+                        yield f"{base}{e}.gate_proj.weight", w[e, :inter]
+                        yield f"{base}{e}.up_proj.weight", w[e, inter:]
+                elif name.endswith(".mlp.experts.down_proj"):
+                    base = name[: -len("down_proj")]
+                    for e in range(w.shape[0]):
+                        yield f"{base}{e}.down_proj.weight", w[e]
+                else:
+                    yield name, w
+
+        return super().load_weights(per_expert())
