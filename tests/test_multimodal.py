@@ -494,3 +494,58 @@ def test_qwen3_vl_moe_matches_hugging_face(tmp_path):
                            pad_token_id=0)[0, 5:].tolist()
     assert list(got[0].outputs[0].token_ids) == want
     assert list(got[1].outputs[0].token_ids) == text
+
+
+@pytest.mark.parametrize("chunk", [64, 7])
+def test_glm4v_matches_hugging_face(tmp_path, chunk):
+    """GLM-4.1V: bicubically sampled position embeddings, RMSNorm / SwiGLU vision blocks, convolutional patch merge,
+    gated merger; GLM-4 decoder with M-RoPE over the rotated half of every head in adjacent pairs."""
+    from vllm_metax_b200 import LLM, SamplingParams
+
+    torch.manual_seed(0)
+    c = tf.Glm4vConfig(
+        text_config=dict(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=32, max_position_embeddings=256, tie_word_embeddings=False,
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [2, 3, 3],
+                                          "partial_rotary_factor": 0.5}),
+        vision_config=dict(depth=2, hidden_size=64, intermediate_size=96, out_hidden_size=128, num_heads=4, in_channels=3,
+                           patch_size=8, spatial_merge_size=2, temporal_patch_size=2, image_size=48, attention_bias=False),
+        image_token_id=QV_IMG, video_token_id=503, image_start_token_id=QV_START, image_end_token_id=QV_END,
+        tie_word_embeddings=False)
+    hf = tf.Glm4vForConditionalGeneration(c).eval().float()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.dim() == 1:
+                p.add_(0.1 * torch.randn_like(p))
+            else:
+                p.mul_(2.0)
+    hf.save_pretrained(str(tmp_path))
+    llm = LLM(str(tmp_path), dtype="float32", device="cpu", max_model_len=128, num_gpu_blocks=32, block_size=16,
+              max_num_batched_tokens=chunk)
+    assert type(llm.engine.runner.model).__name__ == "Glm4vForConditionalGeneration" and llm.engine.runner.uses_mrope
+    g = torch.Generator().manual_seed(1)
+    grid_a, grid_b = (1, 4, 6), (1, 2, 4)
+    dim = 3 * 2 * 8 * 8
+    pa, pb = torch.randn(24, dim, generator=g), torch.randn(8, dim, generator=g)
+    one = [5, 9, QV_START] + [QV_IMG] * 6 + [QV_END, 33, 100, 7, 8, 200, 31]
+    two = [3, QV_START] + [QV_IMG] * 6 + [QV_END, 40, QV_START] + [QV_IMG] * 2 + [QV_END, 60, 61, 62]
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    outs = llm.generate([
+        {"prompt_token_ids": one, "multi_modal_data": {"pixel_values": pa, "image_grid_thw": [grid_a]}},
+        {"prompt_token_ids": two, "multi_modal_data": {"pixel_values": torch.cat([pa, pb]), "image_grid_thw": [grid_a, grid_b]}},
+        {"prompt_token_ids": [5, 9, 33, 100, 7]},
+    ], sp)
+    got = [list(o.outputs[0].token_ids) for o in outs]
+
+    def want(ids, pixels=None, grids=None):
+        kw = {} if pixels is None else dict(pixel_values=pixels, image_grid_thw=torch.tensor(grids),
+                                            mm_token_type_ids=torch.tensor([[1 if t == QV_IMG else 0 for t in ids]]))
+        with torch.no_grad():
+            out = hf.generate(input_ids=torch.tensor([ids]), max_new_tokens=6, do_sample=False, eos_token_id=None,
+                              pad_token_id=0, **kw)
+        return out[0, len(ids):].tolist()
+
+    assert got[0] == want(one, pa, [grid_a])
+    assert got[1] == want(two, torch.cat([pa, pb]), [grid_a, grid_b])
+    assert got[2] == want([5, 9, 33, 100, 7])
+    assert len(set(got[0])) > 1 or len(set(got[1])) > 1           # not a degenerate constant continuation

@@ -44,6 +44,7 @@ _MODELS: dict[str, tuple[str, str]] = {
     "LlavaNextForConditionalGeneration": ("llava", "LlavaNextForConditionalGeneration"),
     "Qwen2VLForConditionalGeneration": ("qwen2_vl", "Qwen2VLForConditionalGeneration"),
     "Qwen2_5_VLForConditionalGeneration": ("qwen2_vl", "Qwen2_5_VLForConditionalGeneration"),
+    "Glm4vForConditionalGeneration": ("qwen2_vl", "Glm4vForConditionalGeneration"),
     "Qwen3VLForConditionalGeneration": ("qwen2_vl", "Qwen3VLForConditionalGeneration"),
     "Qwen3VLMoeForConditionalGeneration": ("qwen2_vl", "Qwen3VLMoeForConditionalGeneration"),
     "InternVLForConditionalGeneration": ("internvl", "InternVLForConditionalGeneration"),

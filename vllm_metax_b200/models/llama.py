@@ -104,7 +104,7 @@ class LlamaAttention(nn.Module):
             if pos3 is None:
                 pos3 = positions[None, :].expand(3, -1)
             q, k = apply_mrope(q, k, pos3, self.rope.cos_sin_cache, sections, self.head_dim,
-                               getattr(self, "mrope_interleaved", False))
+                               getattr(self, "mrope_interleaved", False), self.rope.is_neox)
             return self.attn(q, k, v.contiguous(), positions, None)
         return self.attn(q, k, v, positions, self.rope)
 

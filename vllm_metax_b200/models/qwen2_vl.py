@@ -55,24 +55,32 @@ def mrope_stream_of_frequency(sections, half: int, interleaved: bool) -> list:
 
 
 def apply_mrope(q: torch.Tensor, k: torch.Tensor, pos3: torch.Tensor, cos_sin_cache: torch.Tensor, sections,
-                head_dim: int, interleaved: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
-    """NeoX rotation of ``q [T, Hq * D]`` / ``k [T, Hkv * D]`` where frequency pair j turns with the position stream
-    ``mrope_stream_of_frequency`` names, taken from ``pos3 [3, T]``.  ``cos_sin_cache [max_pos, D]`` =
-    ``[cos(D/2) | sin(D/2)]``."""
-    half = head_dim // 2
-    cs = cos_sin_cache.index_select(0, pos3.reshape(-1).long()).view(3, -1, head_dim).float()      # [3, T, D]
+                head_dim: int, interleaved: bool = False, is_neox: bool = True) -> tuple[torch.Tensor, torch.Tensor]:
+    """Rotation of ``q [T, Hq * D]`` / ``k [T, Hkv * D]`` where frequency pair j turns with the position stream
+    ``mrope_stream_of_frequency`` names, taken from ``pos3 [3, T]``.  ``cos_sin_cache [max_pos, R]`` =
+    ``[cos(R/2) | sin(R/2)]`` with ``R <= D`` rotated dimensions (the rest of a head passes through); pairs are
+    (j, j + R/2) in NeoX style and (2j, 2j + 1) otherwise."""
+    rot = cos_sin_cache.shape[1]
+    half = rot // 2
+    cs = cos_sin_cache.index_select(0, pos3.reshape(-1).long()).view(3, -1, rot).float()           # [3, T, R]
     sel = torch.as_tensor(mrope_stream_of_frequency(list(sections), half, interleaved), device=cs.device)
     j = torch.arange(half, device=cs.device)
-    cos = cs[sel, :, j].transpose(0, 1)[:, None, :]                                               # [T, 1, D/2]
+    cos = cs[sel, :, j].transpose(0, 1)[:, None, :]                                               # [T, 1, R/2]
     sin = cs[sel, :, half + j].transpose(0, 1)[:, None, :]
 
-    def rot(x):
+    def turn(x):
         T = x.shape[0]
         x3 = x.reshape(T, -1, head_dim).float()
-        a, b = x3[..., :half], x3[..., half:]
-        return torch.cat([a * cos - b * sin, b * cos + a * sin], -1).to(x.dtype).reshape(T, -1)
+        xr, rest = x3[..., :rot], x3[..., rot:]
+        if is_neox:
+            a, b = xr[..., :half], xr[..., half:]
+            out = torch.cat([a * cos - b * sin, b * cos + a * sin], -1)
+        else:
+            a, b = xr[..., 0::2], xr[..., 1::2]
+            out = torch.stack([a * cos - b * sin, b * cos + a * sin], -1).flatten(-2)
+        return torch.cat([out, rest], -1).to(x.dtype).reshape(T, -1)
 
-    return rot(q), rot(k)
+    return turn(q), turn(k)
 
 
 def mrope_prompt_positions(ids: list, grids: list, image_token_id: int, merge: int) -> tuple[np.ndarray, int]:
@@ -543,3 +551,135 @@ class Qwen3VLMoeForConditionalGeneration(Qwen3VLForConditionalGeneration):
                     yield name, w
 
         return super().load_weights(per_expert())
+
+
+# ------------------------------------------------------------------------------------------------------ GLM-4.1V
+class Glm4vVisionBlock(nn.Module):
+    """RMSNorm, fused qkv (optional bias) + bias-free projection, 2-D rotary, bias-free SwiGLU MLP."""
+
+    def __init__(self, dim: int, heads: int, inter: int, eps: float, qkv_bias: bool, dtype):
+        super().__init__()
+        from ..layers.basic import RMSNorm
+
+        self.heads, self.hd = heads, dim // heads
+        self.norm1, self.norm2 = RMSNorm(dim, eps, dtype), RMSNorm(dim, eps, dtype)
+        self.qkv = ReplicatedLinear(dim, 3 * dim, qkv_bias, dtype)
+        self.proj = ReplicatedLinear(dim, dim, False, dtype)
+        self.gate_proj, self.up_proj = ReplicatedLinear(dim, inter, False, dtype), ReplicatedLinear(dim, inter, False, dtype)
+        self.down_proj = ReplicatedLinear(inter, dim, False, dtype)
+
+    def forward(self, x, cos, sin, cu, max_tokens: int):
+        N, dim = x.shape
+        qkv = self.qkv(self.norm1(x)).reshape(N, 3, self.heads, self.hd)
+        q, k, v = qkv[:, 0], qkv[:, 1], qkv[:, 2]
+
+        def rot(t):
+            tf_ = t.float()
+            a, b = tf_[..., : self.hd // 2], tf_[..., self.hd // 2:]
+            return (tf_ * cos[:, None, :] + torch.cat([-b, a], -1) * sin[:, None, :]).to(t.dtype)
+
+        a = encoder_attention(rot(q).contiguous(), rot(k).contiguous(), v.contiguous(), cu, max_tokens)
+        x = x + self.proj(a.reshape(N, dim))
+        y = self.norm2(x)
+        return x + self.down_proj(F.silu(self.gate_proj(y)) * self.up_proj(y))
+
+
+class Glm4vVisionTower(nn.Module):
+    """GLM-4.1V tower: patch projection, RMSNorm, learned position embeddings sampled bicubically at every patch
+    centre, RMSNorm / SwiGLU blocks with 2-D rotary, a strided convolution that merges ``m x m`` patches, and a gated
+    merger MLP."""
+
+    def __init__(self, vc: dict, dtype):
+        super().__init__()
+        from ..layers.basic import RMSNorm
+
+        self.embed, self.heads = vc["hidden_size"], vc["num_heads"]
+        self.patch, self.merge, self.tpatch = vc.get("patch_size", 14), vc.get("spatial_merge_size", 2), vc.get("temporal_patch_size", 2)
+        self.in_ch = vc.get("in_channels", 3)
+        self.patch_dim = self.in_ch * self.tpatch * self.patch * self.patch
+        eps = vc.get("rms_norm_eps", 1e-5)
+        out = vc["out_hidden_size"]
+        self.patch_embed = ReplicatedLinear(self.patch_dim, self.embed, True, dtype)
+        self.post_conv_layernorm = RMSNorm(self.embed, eps, dtype)
+        self.side = vc.get("image_size", 336) // self.patch
+        self.position_embedding = nn.Parameter(torch.zeros(self.side * self.side, self.embed, dtype=dtype), requires_grad=False)
+        self.blocks = nn.ModuleList([Glm4vVisionBlock(self.embed, self.heads, out, eps, bool(vc.get("attention_bias", False)), dtype)
+                                     for _ in range(vc["depth"])])
+        self.post_layernorm = RMSNorm(self.embed, eps, dtype)
+        self.downsample = ReplicatedLinear(self.embed * self.merge * self.merge, out, True, dtype)     # the strided conv
+        self.merger_proj = ReplicatedLinear(out, out, False, dtype)
+        self.merger_norm = LayerNorm(out, 1e-5, dtype)
+        inter = vc["intermediate_size"]
+        self.merger_gate, self.merger_up = ReplicatedLinear(out, inter, False, dtype), ReplicatedLinear(out, inter, False, dtype)
+        self.merger_down = ReplicatedLinear(inter, out, False, dtype)
+
+    _angles = Qwen2VisionTower._angles
+
+    def _pos(self, grids: list, device) -> torch.Tensor:
+        S, m = self.side, self.merge
+        table = self.position_embedding.float().view(S, S, -1).permute(2, 0, 1)[None]            # [1, C, S, S]
+        out = []
+        for t, h, w in grids:
+            hp = torch.arange(h, device=device)[:, None].expand(h, w).reshape(h // m, m, w // m, m).permute(0, 2, 1, 3).flatten()
+            wp = torch.arange(w, device=device)[None, :].expand(h, w).reshape(h // m, m, w // m, m).permute(0, 2, 1, 3).flatten()
+            gx, gy = ((wp.float() + 0.5) / w) * 2 - 1, ((hp.float() + 0.5) / h) * 2 - 1
+            grid = torch.stack([gx, gy], -1)[None, :, None, :]                                     # [1, N, 1, 2]
+            e = F.grid_sample(table, grid, mode="bicubic", align_corners=False, padding_mode="border")
+            out.append(e[0, :, :, 0].transpose(0, 1).repeat(t, 1))
+        return torch.cat(out)
+
+    def forward(self, patches: torch.Tensor, grids: list) -> torch.Tensor:
+        x = self.post_conv_layernorm(self.patch_embed(patches.to(self.patch_embed.weight.dtype)))
+        ang = self._angles(grids, x.device)
+        emb = torch.cat([ang, ang], -1)
+        cos, sin = emb.cos(), emb.sin()
+        x = x + self._pos(grids, x.device).to(x.dtype)
+        frames = [h * w for t, h, w in grids for _ in range(t)]
+        cu = torch.tensor([0] + list(np.cumsum(frames)), dtype=torch.int32, device=x.device)
+        for blk in self.blocks:
+            x = blk(x, cos, sin, cu, max(frames))
+        x = self.post_layernorm(x)
+        m = self.merge
+        x = x.reshape(-1, m, m, self.embed).permute(0, 3, 1, 2).reshape(-1, self.embed * m * m)     # conv input order
+        x = self.downsample(x)
+        x = F.gelu(self.merger_norm(self.merger_proj(x)))
+        return self.merger_down(F.silu(self.merger_gate(x)) * self.merger_up(x))
+
+
+class Glm4vForConditionalGeneration(Qwen2VLForConditionalGeneration):
+    """GLM-4.1V: the tower above over the GLM-4 decoder (extra norms after each branch, half of every head rotated in
+    adjacent pairs) with M-RoPE in the chunked layout."""
+
+    image_mean, image_std = (0.48145466, 0.4578275, 0.40821073), (0.26862954, 0.26130258, 0.27577711)
+    renames = [(r"^model\.language_model\.", "language_model.model."), (r"^model\.visual\.", "visual."),
+               (r"^lm_head\.", "language_model.lm_head."), (r"^model\.(?!language_model|visual)", "language_model.model."),
+               (r"^visual\.patch_embed\.proj\.", "visual.patch_embed."),
+               (r"^visual\.embeddings\.position_embedding\.weight$", "visual.position_embedding"),
+               (r"^visual\.blocks\.(\d+)\.attn\.", r"visual.blocks.\1."), (r"^visual\.blocks\.(\d+)\.mlp\.", r"visual.blocks.\1."),
+               (r"^visual\.merger\.proj\.", "visual.merger_proj."), (r"^visual\.merger\.post_projection_norm\.", "visual.merger_norm."),
+               (r"^visual\.merger\.(gate|up|down)_proj\.", r"visual.merger_\1.")]
+
+    def __init__(self, cfg: ModelConfig):
+        nn.Module.__init__(self)
+        from . import get_model_class
+
+        self.cfg = cfg
+        hf = cfg.hf_config
+        self.image_token_id = int(hf.get("image_token_id", 151343))
+        self.visual = Glm4vVisionTower(hf["vision_config"], cfg.dtype)
+        cfg.attention_bias = True                          # this family's q / k / v projections always carry a bias
+        self.language_model = get_model_class("Glm4ForCausalLM")(cfg)
+        tc = hf.get("text_config", hf)
+        rp = tc.get("rope_parameters") or tc.get("rope_scaling") or hf.get("rope_scaling") or {}
+        self.mrope_section = list(rp.get("mrope_section") or [8, 12, 12])
+        for layer in self.language_model.model.layers.values():
+            layer.self_attn.mrope_section = self.mrope_section
+
+    def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]) -> set[str]:
+        def conv_as_linear():
+            for name, w in weights:
+                if name.endswith("visual.downsample.weight"):          # [out, C, m, m] strided convolution
+                    w = w.reshape(w.shape[0], -1)
+                yield name, w
+
+        return super().load_weights(conv_as_linear())
