@@ -549,3 +549,52 @@ def test_glm4v_matches_hugging_face(tmp_path, chunk):
     assert got[1] == want(two, torch.cat([pa, pb]), [grid_a, grid_b])
     assert got[2] == want([5, 9, 33, 100, 7])
     assert len(set(got[0])) > 1 or len(set(got[1])) > 1           # not a degenerate constant continuation
+
+
+def test_glm4v_moe_matches_hugging_face(tmp_path):
+    """GLM-4.5V: the GLM-4.1V tower over the GLM-4.5 mixture-of-experts decoder (sigmoid routing with bias correction,
+    shared expert, a dense first layer), stacked expert tensors split at load."""
+    from vllm_metax_b200 import LLM, SamplingParams
+
+    torch.manual_seed(0)
+    c = tf.Glm4vMoeConfig(
+        text_config=dict(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=32, max_position_embeddings=256, tie_word_embeddings=False,
+                         n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=64, n_shared_experts=1, n_group=1,
+                         topk_group=1, first_k_dense_replace=1, norm_topk_prob=True, routed_scaling_factor=1.0,
+                         use_qk_norm=False,
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [2, 3, 3],
+                                          "partial_rotary_factor": 0.5}),
+        vision_config=dict(depth=2, hidden_size=64, intermediate_size=96, out_hidden_size=128, num_heads=4, in_channels=3,
+                           patch_size=8, spatial_merge_size=2, temporal_patch_size=2, image_size=48, attention_bias=False),
+        image_token_id=QV_IMG, video_token_id=503, image_start_token_id=QV_START, image_end_token_id=QV_END,
+        tie_word_embeddings=False)
+    hf = tf.Glm4vMoeForConditionalGeneration(c).eval().float()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.dim() == 1:
+                p.add_(0.1 * torch.randn_like(p))
+            elif p.dim() == 3:
+                p.normal_(0, 0.15)
+            else:
+                p.mul_(2.0)
+    hf.save_pretrained(str(tmp_path))
+    llm = LLM(str(tmp_path), dtype="float32", device="cpu", max_model_len=128, num_gpu_blocks=32, block_size=16,
+              max_num_batched_tokens=9)
+    assert type(llm.engine.runner.model).__name__ == "Glm4vMoeForConditionalGeneration"
+    assert llm.engine.cfg.model.scoring_func == "sigmoid"
+    g = torch.Generator().manual_seed(1)
+    grid = (1, 4, 6)
+    px = torch.randn(24, 3 * 2 * 8 * 8, generator=g)
+    ids = [5, 9, QV_START] + [QV_IMG] * 6 + [QV_END, 33, 100, 7, 8, 200, 31]
+    sp = SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True)
+    got = llm.generate([{"prompt_token_ids": ids, "multi_modal_data": {"pixel_values": px, "image_grid_thw": [grid]}},
+                        {"prompt_token_ids": [5, 9, 33, 100, 7]}], sp)
+    with torch.no_grad():
+        want = hf.generate(input_ids=torch.tensor([ids]), max_new_tokens=5, do_sample=False, eos_token_id=None, pad_token_id=0,
+                           pixel_values=px, image_grid_thw=torch.tensor([grid]),
+                           mm_token_type_ids=torch.tensor([[1 if t == QV_IMG else 0 for t in ids]]))[0, len(ids):].tolist()
+        text = hf.generate(input_ids=torch.tensor([[5, 9, 33, 100, 7]]), max_new_tokens=5, do_sample=False, eos_token_id=None,
+                           pad_token_id=0)[0, 5:].tolist()
+    assert list(got[0].outputs[0].token_ids) == want
+    assert list(got[1].outputs[0].token_ids) == text

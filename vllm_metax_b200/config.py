@@ -204,7 +204,9 @@ class ModelConfig:
             arch = "DeepseekV3ForCausalLM"
         # DeepSeek-V3 lineage: sigmoid scores + bias-corrected grouped top-k even when the config (HF-native exports)
         # does not spell it out
-        v3_routing = any(t in arch for t in ("DeepseekV3", "DeepseekV32", "GlmMoeDsa", "DeepseekV4", "Glm4Moe"))
+        # (vision-language wrappers follow the rules of their decoder)
+        rule_arch = {"Glm4vMoeForConditionalGeneration": "Glm4MoeForCausalLM"}.get(arch, arch)
+        v3_routing = any(t in rule_arch for t in ("DeepseekV3", "DeepseekV32", "GlmMoeDsa", "DeepseekV4", "Glm4Moe"))
         kw: dict[str, Any] = dict(
             hf_config=dict(raw),
             partial_rotary_factor=float(d.get("partial_rotary_factor", 1.0) or 1.0),

@@ -45,6 +45,7 @@ _MODELS: dict[str, tuple[str, str]] = {
     "Qwen2VLForConditionalGeneration": ("qwen2_vl", "Qwen2VLForConditionalGeneration"),
     "Qwen2_5_VLForConditionalGeneration": ("qwen2_vl", "Qwen2_5_VLForConditionalGeneration"),
     "Glm4vForConditionalGeneration": ("qwen2_vl", "Glm4vForConditionalGeneration"),
+    "Glm4vMoeForConditionalGeneration": ("qwen2_vl", "Glm4vMoeForConditionalGeneration"),
     "Qwen3VLForConditionalGeneration": ("qwen2_vl", "Qwen3VLForConditionalGeneration"),
     "Qwen3VLMoeForConditionalGeneration": ("qwen2_vl", "Qwen3VLMoeForConditionalGeneration"),
     "InternVLForConditionalGeneration": ("internvl", "InternVLForConditionalGeneration"),

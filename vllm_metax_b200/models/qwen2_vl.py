@@ -536,21 +536,24 @@ class Qwen3VLMoeForConditionalGeneration(Qwen3VLForConditionalGeneration):
     decoder_arch = "Qwen3MoeForCausalLM"
 
     def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]) -> set[str]:
-        def per_expert():
-            for name, w in weights:
-                if name.endswith(".mlp.experts.gate_up_proj"):
-                    base, inter = name[: -len("gate_up_proj")], w.shape[1] // 2
-                    for e in range(w.shape[0]):
-                        yield f"{base}{e}.gate_proj.weight", w[e, :inter]
-                        yield f"{base}{e}.up_proj.weight", w[e, inter:]
-                elif name.endswith(".mlp.experts.down_proj"):
-                    base = name[: -len("down_proj")]
-                    for e in range(w.shape[0]):
-                        yield f"{base}{e}.down_proj.weight", w[e]
-                else:
-                    yield name, w
+        return super().load_weights(split_stacked_experts(weights))
 
-        return super().load_weights(per_expert())
+
+def split_stacked_experts(weights):
+    """``experts.gate_up_proj [E, 2I, H]`` / ``experts.down_proj [E, H, I]`` -> the per-expert tensor names the
+    expert-parallel loaders take (gate rows first, then up rows)."""
+    for name, w in weights:
+        if name.endswith(".mlp.experts.gate_up_proj"):
+            base, inter = name[: -len("gate_up_proj")], w.shape[1] // 2
+            for e in range(w.shape[0]):
+                yield f"{base}{e}.gate_proj.weight", w[e, :inter]
+                yield f"{base}{e}.up_proj.weight", w[e, inter:]
+        elif name.endswith(".mlp.experts.down_proj"):
+            base = name[: -len("down_proj")]
+            for e in range(w.shape[0]):
+                yield f"{base}{e}.down_proj.weight", w[e]
+        else:
+            yield name, w
 
 
 # ------------------------------------------------------------------------------------------------------ GLM-4.1V
@@ -651,6 +654,7 @@ class Glm4vForConditionalGeneration(Qwen2VLForConditionalGeneration):
     adjacent pairs) with M-RoPE in the chunked layout."""
 
     image_mean, image_std = (0.48145466, 0.4578275, 0.40821073), (0.26862954, 0.26130258, 0.27577711)
+    decoder_arch = "Glm4ForCausalLM"
     renames = [(r"^model\.language_model\.", "language_model.model."), (r"^model\.visual\.", "visual."),
                (r"^lm_head\.", "language_model.lm_head."), (r"^model\.(?!language_model|visual)", "language_model.model."),
                (r"^visual\.patch_embed\.proj\.", "visual.patch_embed."),
@@ -667,8 +671,9 @@ class Glm4vForConditionalGeneration(Qwen2VLForConditionalGeneration):
         hf = cfg.hf_config
         self.image_token_id = int(hf.get("image_token_id", 151343))
         self.visual = Glm4vVisionTower(hf["vision_config"], cfg.dtype)
-        cfg.attention_bias = True                          # this family's q / k / v projections always carry a bias
-        self.language_model = get_model_class("Glm4ForCausalLM")(cfg)
+        if self.decoder_arch == "Glm4ForCausalLM":
+            cfg.attention_bias = True                      # GLM-4.1V's q / k / v projections always carry a bias
+        self.language_model = get_model_class(self.decoder_arch)(cfg)
         tc = hf.get("text_config", hf)
         rp = tc.get("rope_parameters") or tc.get("rope_scaling") or hf.get("rope_scaling") or {}
         self.mrope_section = list(rp.get("mrope_section") or [8, 12, 12])
@@ -683,3 +688,13 @@ class Glm4vForConditionalGeneration(Qwen2VLForConditionalGeneration):
                 yield name, w
 
         return super().load_weights(conv_as_linear())
+
+
+class Glm4vMoeForConditionalGeneration(Glm4vForConditionalGeneration):
+    """GLM-4.5V: the GLM-4.1V tower and M-RoPE over the GLM-4.5 mixture-of-experts decoder (NeoX-style rotation of
+    half of each head; stacked expert tensors are split per expert at load)."""
+
+    decoder_arch = "Glm4MoeForCausalLM"
+
+    def load_weights(self, weights: Iterable[tuple[str, torch.Tensor]]) -> set[str]:
+        return super().load_weights(split_stacked_experts(weights))
