@@ -50,6 +50,7 @@ _MODELS: dict[str, tuple[str, str]] = {
     "Qwen3VLMoeForConditionalGeneration": ("qwen2_vl", "Qwen3VLMoeForConditionalGeneration"),
     "InternVLForConditionalGeneration": ("internvl", "InternVLForConditionalGeneration"),
     "InternVLChatModel": ("internvl", "InternVLChatModel"),
+    "InternS1ForConditionalGeneration": ("internvl", "InternVLForConditionalGeneration"),    # the same graph, other decoder
     "MambaForCausalLM": ("mamba", "MambaForCausalLM"),
     "Qwen3NextForCausalLM": ("qwen3_next", "Qwen3NextForCausalLM"),
     "Glm4MoeForCausalLM": ("moe_family", "Glm4MoeForCausalLM"),
