@@ -598,3 +598,52 @@ def test_glm4v_moe_matches_hugging_face(tmp_path):
                            pad_token_id=0)[0, 5:].tolist()
     assert list(got[0].outputs[0].token_ids) == want
     assert list(got[1].outputs[0].token_ids) == text
+
+
+def test_llava_onevision_matches_hugging_face(tmp_path):
+    """LLaVA-OneVision: SigLIP tower (no class token), any-resolution packing, and the bilinear shrink of feature maps
+    larger than ``anyres_max_N`` tower images (forced here with N = 1)."""
+    from vllm_metax_b200 import LLM, SamplingParams
+    from vllm_metax_b200.models.llava import select_best_resolution
+
+    torch.manual_seed(0)
+    vc = tf.SiglipVisionConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4,
+                               image_size=28, patch_size=14)
+    tc = tf.Qwen2Config(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2, max_position_embeddings=256, tie_word_embeddings=False)
+    pins = [[28, 56], [56, 28], [56, 56], [28, 84], [84, 28]]
+    c = tf.LlavaOnevisionConfig(vision_config=vc, text_config=tc, image_token_index=IMG_TOK, vision_feature_layer=-1,
+                                vision_feature_select_strategy="full", image_grid_pinpoints=pins,
+                                vision_aspect_ratio="anyres_max_1", tie_word_embeddings=False)
+    hf = tf.LlavaOnevisionForConditionalGeneration(c).eval().float()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.dim() == 1:
+                p.add_(0.1 * torch.randn_like(p))
+            else:
+                p.mul_(3.0)
+    hf.save_pretrained(str(tmp_path))
+    llm = LLM(str(tmp_path), dtype="float32", device="cpu", max_model_len=160, num_gpu_blocks=40, block_size=16,
+              max_num_batched_tokens=24)
+    model = llm.engine.runner.model
+    assert type(model).__name__ == "LlavaOnevisionForConditionalGeneration" and model.max_tiles == 1
+    g = torch.Generator().manual_seed(2)
+    sp = SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True)
+    shrunk = 0
+    for hw in [(30, 100), (90, 40), (50, 50), (20, 20)]:
+        ch, cw = select_best_resolution(hw, [tuple(p) for p in pins])
+        tiles = 1 + (ch // 28) * (cw // 28)
+        pixels = torch.randn(1, tiles, 3, 28, 28, generator=g)
+        sizes = torch.tensor([list(hw)])
+        with torch.no_grad():
+            n_tok = model.pack_features(model.embed_multimodal(pixels[0]), hw).shape[0]
+        shrunk += n_tok < 4 + (ch // 14) * (cw // 14 + 1) - 8                     # fewer tokens than the unshrunk map
+        ids = [5, 9] + [IMG_TOK] * n_tok + [33, 100, 7, 8]
+        with torch.no_grad():
+            want = hf.generate(input_ids=torch.tensor([ids]), pixel_values=pixels, image_sizes=sizes, max_new_tokens=5,
+                               do_sample=False, eos_token_id=None, pad_token_id=0)[0, len(ids):].tolist()
+        out = llm.generate([{"prompt_token_ids": [5, 9, IMG_TOK, 33, 100, 7, 8],
+                             "multi_modal_data": {"pixel_values": pixels, "image_sizes": sizes}}], sp)
+        assert len(out[0].prompt_token_ids) == len(ids), (hw, n_tok)
+        assert list(out[0].outputs[0].token_ids) == want, hw
+    assert shrunk >= 1                                                            # the shrink path was exercised

@@ -42,6 +42,7 @@ _MODELS: dict[str, tuple[str, str]] = {
     "ChatGLMForConditionalGeneration": ("llama_family", "ChatGLMModel"),
     "LlavaForConditionalGeneration": ("llava", "LlavaForConditionalGeneration"),
     "LlavaNextForConditionalGeneration": ("llava", "LlavaNextForConditionalGeneration"),
+    "LlavaOnevisionForConditionalGeneration": ("llava", "LlavaOnevisionForConditionalGeneration"),
     "Qwen2VLForConditionalGeneration": ("qwen2_vl", "Qwen2VLForConditionalGeneration"),
     "Qwen2_5_VLForConditionalGeneration": ("qwen2_vl", "Qwen2_5_VLForConditionalGeneration"),
     "Glm4vForConditionalGeneration": ("qwen2_vl", "Glm4vForConditionalGeneration"),

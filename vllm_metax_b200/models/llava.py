@@ -257,8 +257,8 @@ class LlavaNextForConditionalGeneration(LlavaForConditionalGeneration):
         canvas[:, top: top + nh, left: left + nw] = resized
         tiles = canvas.unfold(1, S, S).unfold(2, S, S).permute(1, 2, 0, 3, 4).reshape(-1, 3, S, S)   # row-major grid
         base = F.interpolate(x[None], size=(S, S), mode="bicubic", align_corners=False)[0].clamp(0, 1)
-        mean = torch.tensor([0.48145466, 0.4578275, 0.40821073]).view(1, 3, 1, 1)
-        std = torch.tensor([0.26862954, 0.26130258, 0.27577711]).view(1, 3, 1, 1)
+        mean = torch.tensor(getattr(self, "image_mean", (0.48145466, 0.4578275, 0.40821073))).view(1, 3, 1, 1)
+        std = torch.tensor(getattr(self, "image_std", (0.26862954, 0.26130258, 0.27577711))).view(1, 3, 1, 1)
         return (torch.cat([base[None], tiles]) - mean) / std, (oh, ow)
 
     # ---- features of one image: [tokens, hidden] ------------------------------------------------------------------
@@ -319,3 +319,81 @@ class LlavaNextForConditionalGeneration(LlavaForConditionalGeneration):
         for st in stacks:
             h.update(st.detach().float().cpu().numpy().tobytes())
         return ids, (torch.cat(per_image), pos, h.hexdigest()[:16]), None
+
+
+# ------------------------------------------------------------------------------------------ LLaVA-OneVision (SigLIP tower)
+class SiglipVisionTower(nn.Module):
+    """SigLIP vision encoder as the LLaVA-OneVision family uses it: patch projection with bias, learned position
+    embeddings, no class token and no norm before the encoder; the features are the output of the last kept layer."""
+
+    def __init__(self, vc: dict, dtype, num_layers: int):
+        super().__init__()
+        hid, self.patch, self.size = vc["hidden_size"], vc["patch_size"], vc["image_size"]
+        self.grid = self.size // self.patch
+        self.tokens = self.grid * self.grid
+        eps = vc.get("layer_norm_eps", 1e-6)
+        self.patch_embedding = nn.Parameter(torch.zeros(hid, 3 * self.patch * self.patch, dtype=dtype), requires_grad=False)
+        self.patch_bias = nn.Parameter(torch.zeros(hid, dtype=dtype), requires_grad=False)
+        self.position_embedding = nn.Parameter(torch.zeros(self.tokens, hid, dtype=dtype), requires_grad=False)
+        self.layers = nn.ModuleList([ClipEncoderLayer(hid, vc["intermediate_size"], vc["num_attention_heads"], eps,
+                                                      vc.get("hidden_act", "gelu_pytorch_tanh"), dtype) for _ in range(num_layers)])
+
+    def forward(self, pixels: torch.Tensor) -> torch.Tensor:
+        n, p, g = pixels.shape[0], self.patch, self.grid
+        dt = self.patch_embedding.dtype
+        x = pixels.to(dt).reshape(n, 3, g, p, g, p).permute(0, 2, 4, 1, 3, 5).reshape(n * g * g, 3 * p * p)
+        x = (F.linear(x, self.patch_embedding, self.patch_bias).reshape(n, g * g, -1) + self.position_embedding).reshape(n * self.tokens, -1)
+        cu = torch.arange(0, (n + 1) * self.tokens, self.tokens, dtype=torch.int32, device=x.device)
+        for layer in self.layers:
+            x = layer(x, cu, self.tokens)
+        return x.reshape(n, self.tokens, -1)
+
+
+class LlavaOnevisionForConditionalGeneration(LlavaNextForConditionalGeneration):
+    """LLaVA-OneVision: the any-resolution packing of LLaVA-NeXT over a SigLIP tower (all of its tokens are image
+    tokens), with one more step - a feature map that would exceed ``anyres_max_N`` tower images' worth of tokens is
+    shrunk bilinearly before the newline column is added."""
+
+    renames = LlavaNextForConditionalGeneration.renames + [
+        (r"^vision_tower\.vision_model\.embeddings\.patch_embedding\.bias$", "vision_tower.patch_bias"),
+        (r"^vision_tower\.vision_model\.post_layernorm\..*$", "vision_tower.unused_post_layernorm"),
+        (r"^vision_tower\.vision_model\.head\..*$", "vision_tower.unused_head")]
+
+    def __init__(self, cfg: ModelConfig):
+        super().__init__(cfg)
+        hf = cfg.hf_config
+        vc = hf["vision_config"]
+        layer = hf.get("vision_feature_layer", -1)
+        total = vc["num_hidden_layers"]
+        keep = total + layer + 1 if layer < 0 else layer
+        self.select = hf.get("vision_feature_select_strategy", "full")
+        self.vision_tower = SiglipVisionTower(vc, cfg.dtype, keep)
+        self.tokens_per_image = self.vision_tower.tokens
+        self.max_tiles = int(str(hf.get("vision_aspect_ratio", "anyres_max_9")).replace("anyres_max_", ""))
+        self.image_mean, self.image_std = (0.5, 0.5, 0.5), (0.5, 0.5, 0.5)
+
+    @torch.no_grad()
+    def embed_multimodal(self, pixel_values: torch.Tensor) -> torch.Tensor:
+        feats = self.vision_tower(pixel_values)                          # every token is an image token (no class token)
+        n, t, hv = feats.shape
+        x = self.multi_modal_projector["linear_1"](feats.reshape(n * t, hv))
+        x = self.multi_modal_projector["linear_2"](ops.activation(x, self.proj_act))
+        return x.reshape(n, t, -1)
+
+    def pack_features(self, feats: torch.Tensor, original_hw: tuple) -> torch.Tensor:
+        import math
+
+        S, side = self.vision_tower.size, int(round(feats.shape[1] ** 0.5))
+        newline = self.image_newline.to(feats.dtype)
+        if feats.shape[0] == 1:
+            return torch.cat([feats[0], newline[None]])
+        ch, cw = select_best_resolution(original_hw, self.pinpoints)
+        gh, gw = ch // S, cw // S
+        grid = feats[1:].reshape(gh, gw, side, side, -1).permute(4, 0, 2, 1, 3).reshape(-1, gh * side, gw * side)
+        grid = unpad_features(grid, original_hw)
+        _, H, W = grid.shape
+        ratio = math.sqrt(H * W / (self.max_tiles * side * side))
+        if ratio > 1.1:
+            grid = F.interpolate(grid[None].float(), [int(H // ratio), int(W // ratio)], mode="bilinear")[0].to(feats.dtype)
+        grid = torch.cat([grid, newline[:, None, None].expand(-1, grid.shape[1], 1)], dim=-1)
+        return torch.cat([feats[0], grid.flatten(1).transpose(0, 1)])
