@@ -647,3 +647,32 @@ def test_llava_onevision_matches_hugging_face(tmp_path):
         assert len(out[0].prompt_token_ids) == len(ids), (hw, n_tok)
         assert list(out[0].outputs[0].token_ids) == want, hw
     assert shrunk >= 1                                                            # the shrink path was exercised
+
+
+def test_qwen2_vl_video_matches_hugging_face(tmp_path):
+    """A video (three temporal patches) and an image in one prompt: the video's tokens take the video placeholder, the
+    temporal stream of M-RoPE advances per temporal patch."""
+    from vllm_metax_b200 import LLM, SamplingParams
+
+    hf = _hf_qwen2vl(tmp_path)
+    llm = LLM(str(tmp_path), dtype="float32", device="cpu", max_model_len=128, num_gpu_blocks=32, block_size=16,
+              max_num_batched_tokens=11)
+    VID = 503
+    g = torch.Generator().manual_seed(4)
+    vgrid, igrid = (3, 2, 4), (1, 4, 6)                       # 3 x (1 x 2) = 6 video tokens; 6 image tokens
+    pv, pi = torch.randn(24, 1176, generator=g), torch.randn(24, 1176, generator=g)
+    ids = [5, QV_START] + [VID] * 6 + [QV_END, 40, QV_START] + [QV_IMG] * 6 + [QV_END, 60, 61]
+    short = [5, QV_START, VID, QV_END, 40, QV_START, QV_IMG, QV_END, 60, 61]
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    mm = {"pixel_values": pi, "image_grid_thw": [igrid], "pixel_values_videos": pv, "video_grid_thw": [vgrid]}
+    got = llm.generate([{"prompt_token_ids": ids, "multi_modal_data": mm},
+                        {"prompt_token_ids": short, "multi_modal_data": mm}], sp)
+    tt = torch.tensor([[1 if t == QV_IMG else (2 if t == VID else 0) for t in ids]])
+    with torch.no_grad():
+        want = hf.generate(input_ids=torch.tensor([ids]), max_new_tokens=6, do_sample=False, eos_token_id=None, pad_token_id=0,
+                           pixel_values=pi, image_grid_thw=torch.tensor([igrid]), pixel_values_videos=pv,
+                           video_grid_thw=torch.tensor([vgrid]), mm_token_type_ids=tt)[0, len(ids):].tolist()
+    assert list(got[0].outputs[0].token_ids) == want
+    assert list(got[1].outputs[0].token_ids) == want and len(got[1].prompt_token_ids) == len(ids)
+    with pytest.raises(ValueError):
+        llm.generate([{"prompt_token_ids": [5, VID, VID, VID, 6], "multi_modal_data": mm}], sp)

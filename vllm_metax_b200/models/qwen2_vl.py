@@ -22,7 +22,7 @@ from __future__ import annotations
 
 import hashlib
 import re
-from typing import Iterable
+from typing import Iterable, Optional
 
 import numpy as np
 import torch
@@ -83,14 +83,20 @@ def apply_mrope(q: torch.Tensor, k: torch.Tensor, pos3: torch.Tensor, cos_sin_ca
     return turn(q), turn(k)
 
 
-def mrope_prompt_positions(ids: list, grids: list, image_token_id: int, merge: int) -> tuple[np.ndarray, int]:
+def mrope_prompt_positions(ids: list, grids, image_token_id: int, merge: int, video_token_id: Optional[int] = None,
+                           video_grids: Optional[list] = None) -> tuple[np.ndarray, int]:
     """``[3, len(ids)]`` position streams of a prompt whose images (in order) have the ``(t, h, w)`` patch grids
-    ``grids``, and the offset that turns the ordinary position of a generated token into its (common) stream value."""
+    ``grids`` (and whose videos, runs of ``video_token_id``, have ``video_grids``), and the offset that turns the
+    ordinary position of a generated token into its (common) stream value."""
     pos = np.zeros((3, len(ids)), dtype=np.int64)
-    nxt, i, g = 0, 0, 0
+    queues = {image_token_id: list(grids)}
+    if video_token_id is not None:
+        queues[video_token_id] = list(video_grids or [])
+    nxt, i = 0, 0
     while i < len(ids):
-        if ids[i] == image_token_id and g < len(grids):
-            t, h, w = grids[g]
+        q = queues.get(ids[i])
+        if q:
+            t, h, w = q.pop(0)
             gh, gw = h // merge, w // merge
             n = t * gh * gw
             tt = np.repeat(np.arange(t), gh * gw)
@@ -99,7 +105,6 @@ def mrope_prompt_positions(ids: list, grids: list, image_token_id: int, merge: i
             pos[:, i:i + n] = np.stack([tt, hh, ww]) + nxt
             nxt += max(t, gh, gw)
             i += n
-            g += 1
         else:
             pos[:, i] = nxt
             nxt += 1
@@ -179,6 +184,8 @@ class Qwen2VisionTower(nn.Module):
 class Qwen2VLForConditionalGeneration(nn.Module):
     is_multimodal = True
     uses_mrope = True
+    supports_video = True         # Qwen2-VL's video positions advance one step per temporal patch, like its images
+    video_token_id = -1
     image_mean, image_std = (0.48145466, 0.4578275, 0.40821073), (0.26862954, 0.26130258, 0.27577711)    # CLIP statistics
     renames = [(r"^model\.language_model\.", "language_model.model."), (r"^model\.visual\.", "visual."),
                (r"^lm_head\.", "language_model.lm_head."), (r"^model\.(?!language_model|visual)", "language_model.model."),
@@ -194,6 +201,7 @@ class Qwen2VLForConditionalGeneration(nn.Module):
         self.cfg = cfg
         hf = cfg.hf_config
         self.image_token_id = int(hf.get("image_token_id", 151655))
+        self.video_token_id = int(hf.get("video_token_id", 151656))
         self.visual = Qwen2VisionTower(hf["vision_config"], cfg.dtype)
         self.language_model = get_model_class("Qwen2ForCausalLM")(cfg)
         tc = hf.get("text_config", hf)
@@ -223,35 +231,82 @@ class Qwen2VLForConditionalGeneration(nn.Module):
     @torch.no_grad()
     def encode_request(self, prompt_token_ids: list, mm: dict, device):
         """Everything the engine needs for one request: the prompt with its placeholder runs expanded, the projected
-        image features with the prompt positions they replace, a content hash, and the M-RoPE streams of the prompt."""
+        image (and video) features with the prompt positions they replace, a content hash, and the M-RoPE streams of
+        the prompt.  Videos come pre-processed: ``pixel_values_videos`` + ``video_grid_thw`` (``t`` temporal patches per
+        video), their placeholder is the model's video token."""
         if "pixel_values" in mm:
             patches, grids = mm["pixel_values"], [tuple(int(x) for x in g) for g in mm["image_grid_thw"]]
-        else:
+        elif "image" in mm:
             imgs = mm["image"] if isinstance(mm["image"], (list, tuple)) else [mm["image"]]
             pg = [self.patchify(im) for im in imgs]
             patches, grids = torch.cat([p for p, _ in pg]), [g for _, g in pg]
-        feats = self.visual(patches.to(device), grids)
-        m2 = self.visual.merge ** 2
-        per = [t * h * w // m2 for t, h, w in grids]
-        tok = self.image_token_id
-        runs = [r for r in re.finditer(r"(?:%d,)+" % tok, ",".join(map(str, prompt_token_ids)) + ",")]
-        lens = [r.group(0).count(",") for r in runs]
-        if lens == per:
-            ids = list(prompt_token_ids)
-        elif len(lens) == len(per) and all(n == 1 for n in lens):          # one placeholder per image: expand
-            ids, g = [], 0
-            for t in prompt_token_ids:
-                if t == tok:
-                    ids.extend([tok] * per[g])
-                    g += 1
-                else:
-                    ids.append(t)
         else:
-            raise ValueError(f"prompt has image placeholder runs of {lens} tokens for images of {per} tokens")
-        pos = np.asarray([i for i, t in enumerate(ids) if t == tok], dtype=np.int64)
-        digest = hashlib.sha256(patches.detach().float().cpu().numpy().tobytes()).hexdigest()[:16]
-        table, delta = mrope_prompt_positions(ids, grids, tok, self.visual.merge)
-        return ids, (feats, pos, digest), {"mrope_positions": table, "mrope_delta": delta}
+            patches, grids = None, []
+        vpatches, vgrids = mm.get("pixel_values_videos"), [tuple(int(x) for x in g) for g in mm.get("video_grid_thw", [])]
+        vtok = self.video_token_id if vgrids else None
+        if vgrids and not self.supports_video:
+            raise ValueError(f"{type(self).__name__} takes images only")
+        m2 = self.visual.merge ** 2
+        tok = self.image_token_id
+        kinds = {tok: (patches, grids)}
+        if vtok is not None:
+            kinds[vtok] = (vpatches, vgrids)
+        feats_by, per_by = {}, {}
+        for t_id, (px, gr) in kinds.items():
+            if gr:
+                feats_by[t_id] = self.visual(px.to(device), gr)
+                per_by[t_id] = [t * h * w // m2 for t, h, w in gr]
+            else:
+                feats_by[t_id], per_by[t_id] = None, []
+        # expand single placeholders / check the expanded runs, for either kind of token
+        ids, used = [], {k: 0 for k in kinds}
+        i, n_ids = 0, len(prompt_token_ids)
+        while i < n_ids:
+            t_id = prompt_token_ids[i]
+            if t_id in kinds:
+                j = i
+                while j < n_ids and prompt_token_ids[j] == t_id:
+                    j += 1
+                run = j - i
+                k = used[t_id]
+                per = per_by[t_id]
+                total, kk = 0, k
+                while kk < len(per) and total < run:                   # expanded items back to back (usually one)
+                    total += per[kk]
+                    kk += 1
+                if total == run:
+                    ids.extend([t_id] * run)
+                    used[t_id] = kk
+                elif k + run <= len(per):                              # `run` single placeholders: expand each
+                    for r in range(run):
+                        ids.extend([t_id] * per[k + r])
+                    used[t_id] += run
+                else:
+                    raise ValueError(f"prompt has a placeholder run of {run} tokens; the inputs need {per[k:]}")
+                i = j
+            else:
+                ids.append(t_id)
+                i += 1
+        for t_id, per in per_by.items():
+            if used[t_id] != len(per):
+                raise ValueError(f"prompt has placeholders for {used[t_id]} of {len(per)} visual inputs")
+        # features in prompt order
+        arr = np.asarray(ids)
+        pos = np.nonzero(np.isin(arr, list(kinds)))[0].astype(np.int64)
+        if vtok is None:
+            feats = feats_by[tok]
+        else:
+            width = next(f.shape[1] for f in feats_by.values() if f is not None)
+            feats = torch.empty(len(pos), width, dtype=next(f.dtype for f in feats_by.values() if f is not None), device=device)
+            for t_id, f in feats_by.items():
+                if f is not None:
+                    feats[torch.from_numpy(arr[pos] == t_id).to(device)] = f
+        h = hashlib.sha256()
+        for px in (patches, vpatches):
+            if px is not None:
+                h.update(px.detach().float().cpu().numpy().tobytes())
+        table, delta = mrope_prompt_positions(ids, grids, tok, self.visual.merge, vtok, vgrids)
+        return ids, (feats, pos, h.hexdigest()[:16]), {"mrope_positions": table, "mrope_delta": delta}
 
     # ---- engine interface: the text decoder's ---------------------------------------------------------------------
     def num_kv_layers(self) -> int:
@@ -386,6 +441,7 @@ class Qwen25VisionTower(Qwen2VisionTower):
 
 
 class Qwen2_5_VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
+    supports_video = False        # (its video positions scale with the sampling rate: not built)
     renames = Qwen2VLForConditionalGeneration.renames
 
     def __init__(self, cfg: ModelConfig):
@@ -506,6 +562,7 @@ class Qwen3VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
 
     image_mean, image_std = (0.5, 0.5, 0.5), (0.5, 0.5, 0.5)          # this family's image processor
     decoder_arch = "Qwen3ForCausalLM"
+    supports_video = False        # (its videos are frame groups separated by timestamp text: not built)
 
     @torch.no_grad()
     def encode_request(self, prompt_token_ids: list, mm: dict, device):
@@ -655,6 +712,7 @@ class Glm4vForConditionalGeneration(Qwen2VLForConditionalGeneration):
 
     image_mean, image_std = (0.48145466, 0.4578275, 0.40821073), (0.26862954, 0.26130258, 0.27577711)
     decoder_arch = "Glm4ForCausalLM"
+    supports_video = False
     renames = [(r"^model\.language_model\.", "language_model.model."), (r"^model\.visual\.", "visual."),
                (r"^lm_head\.", "language_model.lm_head."), (r"^model\.(?!language_model|visual)", "language_model.model."),
                (r"^visual\.patch_embed\.proj\.", "visual.patch_embed."),
