@@ -84,26 +84,30 @@ def apply_mrope(q: torch.Tensor, k: torch.Tensor, pos3: torch.Tensor, cos_sin_ca
 
 
 def mrope_prompt_positions(ids: list, grids, image_token_id: int, merge: int, video_token_id: Optional[int] = None,
-                           video_grids: Optional[list] = None) -> tuple[np.ndarray, int]:
+                           video_grids: Optional[list] = None, video_t_scale: Optional[list] = None) -> tuple[np.ndarray, int]:
     """``[3, len(ids)]`` position streams of a prompt whose images (in order) have the ``(t, h, w)`` patch grids
     ``grids`` (and whose videos, runs of ``video_token_id``, have ``video_grids``), and the offset that turns the
-    ordinary position of a generated token into its (common) stream value."""
+    ordinary position of a generated token into its (common) stream value.  ``video_t_scale[i]``: how far the
+    temporal stream advances per temporal patch of video i (1 = one step, as for Qwen2-VL; Qwen2.5-VL uses seconds per
+    patch x position steps per second)."""
     pos = np.zeros((3, len(ids)), dtype=np.int64)
-    queues = {image_token_id: list(grids)}
+    queues = {image_token_id: [(g, 1.0) for g in grids]}
     if video_token_id is not None:
-        queues[video_token_id] = list(video_grids or [])
+        scales = list(video_t_scale or [1.0] * len(video_grids or []))
+        queues[video_token_id] = list(zip(video_grids or [], scales))
     nxt, i = 0, 0
     while i < len(ids):
         q = queues.get(ids[i])
         if q:
-            t, h, w = q.pop(0)
+            (t, h, w), scale = q.pop(0)
             gh, gw = h // merge, w // merge
             n = t * gh * gw
-            tt = np.repeat(np.arange(t), gh * gw)
+            steps = np.floor(np.arange(t) * scale).astype(np.int64)
+            tt = np.repeat(steps, gh * gw)
             hh = np.tile(np.repeat(np.arange(gh), gw), t)
             ww = np.tile(np.arange(gw), t * gh)
             pos[:, i:i + n] = np.stack([tt, hh, ww]) + nxt
-            nxt += max(t, gh, gw)
+            nxt += int(max(steps[-1], gh - 1, gw - 1)) + 1
             i += n
         else:
             pos[:, i] = nxt
@@ -185,7 +189,10 @@ class Qwen2VLForConditionalGeneration(nn.Module):
     is_multimodal = True
     uses_mrope = True
     supports_video = True         # Qwen2-VL's video positions advance one step per temporal patch, like its images
-    video_token_id = -1
+
+    @property
+    def video_token_id(self) -> int:
+        return int(self.cfg.hf_config.get("video_token_id", 151656))
     image_mean, image_std = (0.48145466, 0.4578275, 0.40821073), (0.26862954, 0.26130258, 0.27577711)    # CLIP statistics
     renames = [(r"^model\.language_model\.", "language_model.model."), (r"^model\.visual\.", "visual."),
                (r"^lm_head\.", "language_model.lm_head."), (r"^model\.(?!language_model|visual)", "language_model.model."),
@@ -201,7 +208,6 @@ class Qwen2VLForConditionalGeneration(nn.Module):
         self.cfg = cfg
         hf = cfg.hf_config
         self.image_token_id = int(hf.get("image_token_id", 151655))
-        self.video_token_id = int(hf.get("video_token_id", 151656))
         self.visual = Qwen2VisionTower(hf["vision_config"], cfg.dtype)
         self.language_model = get_model_class("Qwen2ForCausalLM")(cfg)
         tc = hf.get("text_config", hf)
@@ -305,8 +311,13 @@ class Qwen2VLForConditionalGeneration(nn.Module):
         for px in (patches, vpatches):
             if px is not None:
                 h.update(px.detach().float().cpu().numpy().tobytes())
-        table, delta = mrope_prompt_positions(ids, grids, tok, self.visual.merge, vtok, vgrids)
+        table, delta = mrope_prompt_positions(ids, grids, tok, self.visual.merge, vtok, vgrids,
+                                              self.video_t_scale(mm, len(vgrids)) if vgrids else None)
         return ids, (feats, pos, h.hexdigest()[:16]), {"mrope_positions": table, "mrope_delta": delta}
+
+    def video_t_scale(self, mm: dict, n: int) -> list:
+        """Temporal-stream advance per temporal patch of each video."""
+        return [1.0] * n
 
     # ---- engine interface: the text decoder's ---------------------------------------------------------------------
     def num_kv_layers(self) -> int:
@@ -441,7 +452,8 @@ class Qwen25VisionTower(Qwen2VisionTower):
 
 
 class Qwen2_5_VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
-    supports_video = False        # (its video positions scale with the sampling rate: not built)
+    supports_video = False        # (its video positions follow the sampling rate: not built)
+
     renames = Qwen2VLForConditionalGeneration.renames
 
     def __init__(self, cfg: ModelConfig):
