@@ -258,3 +258,37 @@ def test_deepseek_graph_under_another_architecture_name_cpu():
     assert len(out[0].outputs[0].token_ids) == 3
     other = ModelConfig.from_hf_dict(dict(d, model_type="something_else", architectures=["LlamaForCausalLM"]))
     assert other.architecture == "LlamaForCausalLM"
+
+
+def test_mla_tcgen05_tiling_arithmetic_cpu():
+    """The index arithmetic of csrc/mla_decode_tcgen05.cu restated: for every visible length, split count and page
+    size the kernel serves, the 32-token tiles of all splits cover the visible positions exactly once, no tile
+    straddles a page, every tile holds at least one visible position, and TMA coordinates stay 16-byte aligned."""
+    import random
+
+    BN = 32
+    rng = random.Random(0)
+    for _ in range(2000):
+        block_size = rng.choice([32, 64, 128, 256])
+        max_blocks = rng.randint(1, 40)
+        lim = min(rng.randint(-3, max_blocks * block_size + 40), max_blocks * block_size)      # the kernel clamps to the table
+        splits = rng.randint(1, 9)
+        tiles_total = (lim + BN - 1) // BN if lim > 0 else 0
+        per = (tiles_total + splits - 1) // splits
+        seen = []
+        for s in range(splits):
+            begin = s * per
+            n = max(0, min(tiles_total, begin + per) - begin)
+            for j in range(n):
+                tok0 = (begin + j) * BN
+                page_index, off = tok0 // block_size, tok0 % block_size
+                assert page_index < max_blocks and off + BN <= block_size          # inside the table, inside one page
+                assert tok0 < lim                                                  # at least one visible position
+                seen.extend(range(tok0, min(tok0 + BN, lim)))
+        assert seen == list(range(max(lim, 0)))
+    # TMA: innermost coordinate c * 64 elements of 2 bytes = multiples of 128 bytes; boxes of 64 elements = 128 bytes
+    assert all((c * 64 * 2) % 16 == 0 for c in range(9)) and (64 * 2) % 16 == 0 and (576 * 2) % 16 == 0
+    # shared memory: Q tile + two cache stages + barriers fit the 227 KB limit with the 1024-byte alignment slack
+    assert 128 * 576 * 2 + 2 * 32 * 576 * 2 + 10 * 8 + 16 + 1024 <= 232448
+    # tensor memory: two score buffers of 32 fp32 columns and 256 output columns fit 512 columns
+    assert 2 * 32 + 256 <= 512
