@@ -139,3 +139,50 @@ def test_front_balances_relays_and_scales():
             await r.client.aclose()
 
     asyncio.run(go())
+
+
+def test_front_with_real_replica_processes():
+    """``b200-serve serve ... --data-parallel-size 2`` on CPU: two engine server processes behind the front, requests
+    answered through it, one replica retired on request, everything gone after the front is terminated."""
+    import subprocess
+    import time
+
+    port = 18100 + (os.getpid() % 500) * 3
+    cfg = json.dumps({"architecture": "LlamaForCausalLM", "vocab_size": 256, "hidden_size": 64, "intermediate_size": 128,
+                      "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16,
+                      "max_position_embeddings": 256})
+    front = subprocess.Popen([sys.executable, "-m", "vllm_metax_b200.entrypoints.cli", "serve", cfg, "--device", "cpu",
+                              "--load-format", "dummy", "--dtype", "float32", "--port", str(port), "--host", "127.0.0.1",
+                              "--data-parallel-size", "2", "--max-model-len", "128", "--block-size", "16"],
+                             cwd=ROOT, stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+    base = f"http://127.0.0.1:{port}"
+    try:
+        deadline = time.monotonic() + 240
+        healthy = None
+        while time.monotonic() < deadline and front.poll() is None:
+            try:
+                r = httpx.get(base + "/health", timeout=2)
+                if r.status_code == 200:
+                    healthy = r.json()
+                    break
+            except httpx.HTTPError:
+                pass
+            time.sleep(1)
+        assert healthy == {"replicas": 2, "healthy": 2}, (healthy, front.poll())
+        outs = [httpx.post(base + "/v1/completions", json={"prompt": [1, 2, 3, 4], "max_tokens": 5}, timeout=120) for _ in range(4)]
+        assert all(o.status_code == 200 for o in outs)
+        assert len({tuple(o.json()["choices"][0]["token_ids"]) for o in outs}) == 1           # same model on every replica
+        assert {o.headers["x-data-parallel-rank"] for o in outs} == {"0", "1"}                # ties go to the idler one
+        r = httpx.post(base + "/scale_elastic_ep", json={"new_data_parallel_size": 1}, timeout=120)
+        assert r.json() == {"data_parallel_size": 1, "previous": 2}
+        assert httpx.get(base + "/health", timeout=5).json() == {"replicas": 1, "healthy": 1}
+        assert httpx.post(base + "/v1/completions", json={"prompt": [1, 2, 3, 4], "max_tokens": 5}, timeout=120).status_code == 200
+    finally:
+        front.terminate()                     # the front ends the replica processes it started
+        try:
+            front.wait(timeout=60)
+        except subprocess.TimeoutExpired:
+            front.kill()
+    for p in (port + 1, port + 2):            # nothing is left listening on the replicas' ports
+        with pytest.raises(httpx.HTTPError):
+            httpx.get(f"http://127.0.0.1:{p}/health", timeout=2)

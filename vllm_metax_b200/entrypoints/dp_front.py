@@ -263,10 +263,27 @@ def run_front(argv: list, host: str, port: int, dp: int, devices_per_replica: in
             for r in list(front.replicas):
                 await retire(r)
 
+    # The HTTP server restores the previous handlers when it stops and raises the signal it caught again; the default
+    # action would end this process before the replicas are retired.  A handler that raises SystemExit lets the
+    # ``finally`` blocks run.
+    import signal
+
+    def leave(signum, _frame):
+        raise SystemExit(128 + signum)
+
+    for sig in (signal.SIGTERM, signal.SIGINT):
+        signal.signal(sig, leave)
     try:
         asyncio.run(main())
+    except SystemExit:
+        pass
     finally:
-        for proc in procs.values():          # exactly the processes started above
-            if proc.poll() is None:
-                proc.terminate()
+        left = [proc for proc in procs.values() if proc.poll() is None]      # exactly the processes started above
+        for proc in left:
+            proc.terminate()
+        for proc in left:
+            try:
+                proc.wait(timeout=30)
+            except subprocess.TimeoutExpired:
+                proc.kill()
     return 0
