@@ -417,3 +417,66 @@ def test_responses_route(client_app):
         "instructions": "be brief", "max_output_tokens": 5})
     assert json.loads(text)["output_text"] == res["output_text"]
     assert _call(app, "POST", "/v1/responses", {"input": "x", "stream": True})[0] == 400
+
+
+def test_response_format_and_chat_rendering_options(client_app):
+    """``response_format`` maps onto JSON-guided decoding; ``continue_final_message``, ``add_generation_prompt`` and
+    ``chat_template_kwargs`` reach the template; ``/pooling`` and ``/server_info`` answer."""
+    from vllm_metax_b200.entrypoints.openai_server import load_chat_template, render_chat
+
+    schema = {"type": "object", "properties": {"a": {"type": "integer"}}, "required": ["a"]}
+    assert sampling_from_request({"response_format": {"type": "json_object"}}).guided_json == {"type": "object"}
+    assert sampling_from_request({"response_format": {"type": "json_schema",
+                                                      "json_schema": {"name": "x", "schema": schema}}}).guided_json == schema
+    assert sampling_from_request({"response_format": {"type": "text"}}).guided_json is None
+    assert sampling_from_request({"guided_regex": "a+", "response_format": {"type": "json_object"}}).guided_json is None
+    with pytest.raises(ValueError):
+        sampling_from_request({"response_format": {"type": "structural_tag"}})
+    with pytest.raises(ValueError):
+        sampling_from_request({"guided_grammar": "root ::= 'a'"})
+
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "chat_templates")
+    chatml = load_chat_template(os.path.join(root, "chatml.jinja"))
+    msgs = [{"role": "user", "content": "count"}, {"role": "assistant", "content": "one, two,"}]
+    text = render_chat(None, msgs, chat_template=chatml, continue_final_message=True)
+    assert text == "<|im_start|>user\ncount<|im_end|>\n<|im_start|>assistant\none, two,"          # the turn stays open
+    with pytest.raises(ValueError):
+        render_chat(None, msgs[:1], chat_template=chatml, continue_final_message=True)          # a user turn cannot be continued
+    think = "{{ messages[0]['content'] }}{% if enable_thinking %}<think>{% endif %}"
+    assert render_chat(None, msgs, chat_template=think, template_kwargs={"enable_thinking": True}) == "count<think>"
+    assert render_chat(None, msgs, chat_template=think, template_kwargs={"enable_thinking": False}) == "count"
+
+    pytest.importorskip("httpx")
+    allm, app = client_app
+    seen = {}
+    tok = allm.engine.tokenizer
+    orig = tok.encode
+
+    def spy(text, *a, **kw):
+        seen["text"] = text
+        return orig(text)
+    tok.encode = spy
+    try:
+        code, _ = _call(app, "POST", "/v1/chat/completions", {"messages": msgs, "max_tokens": 3, "chat_template": chatml,
+                                                              "continue_final_message": True, "add_generation_prompt": False})
+        assert code == 200 and seen["text"].endswith("<|im_start|>assistant\none, two,")
+        code, _ = _call(app, "POST", "/v1/chat/completions", {"messages": msgs[:1], "max_tokens": 3, "chat_template": think,
+                                                              "chat_template_kwargs": {"enable_thinking": True}})
+        assert code == 200 and seen["text"] == "count<think>"
+        code, _ = _call(app, "POST", "/v1/chat/completions", {"messages": msgs[:1], "max_tokens": 3, "chat_template": chatml,
+                                                              "add_generation_prompt": False})
+        assert code == 200 and seen["text"].endswith("count<|im_end|>\n")
+        code, text = _call(app, "POST", "/v1/chat/completions", {"messages": msgs[:1], "max_tokens": 3,
+                                                                 "response_format": {"type": "nope"}})
+        assert code == 400 and "response_format" in text
+    finally:
+        tok.encode = orig
+    code, text = _call(app, "POST", "/pooling", {"input": ["hello", "wor"]})
+    out = json.loads(text)
+    assert code == 200 and [d["object"] for d in out["data"]] == ["pooling", "pooling"] and len(out["data"][0]["data"]) == 64
+    code, emb = _call(app, "POST", "/v1/embeddings", {"input": ["hello"], "normalize": False})
+    torch.testing.assert_close(torch.tensor(out["data"][0]["data"]), torch.tensor(json.loads(emb)["data"][0]["embedding"]))
+    assert _call(app, "POST", "/pooling", {"input": "x", "task": "token_classify"})[0] == 400
+    code, text = _call(app, "GET", "/server_info")
+    info = json.loads(text)
+    assert code == 200 and info["served_model_name"] == "toy" and info["config"]["scheduler"]["max_model_len"] == 256

@@ -62,6 +62,21 @@ def sampling_from_request(body: dict, default_max_tokens: int = 16) -> SamplingP
     for name in ("guided_regex", "guided_json"):
         if body.get(name) is not None or so.get(name[7:]) is not None:
             kw[name] = body.get(name) if body.get(name) is not None else so.get(name[7:])
+    rf = body.get("response_format")
+    if isinstance(rf, dict) and "guided_json" not in kw and "guided_regex" not in kw and "guided_choice" not in kw:
+        kind = rf.get("type")
+        if kind == "json_object":                 # any JSON object
+            kw["guided_json"] = {"type": "object"}
+        elif kind == "json_schema":               # {"type": "json_schema", "json_schema": {"name": ..., "schema": {...}}}
+            js = rf.get("json_schema") or {}
+            schema = js.get("schema", js.get("json_schema"))
+            if not isinstance(schema, (dict, str)):
+                raise ValueError("response_format.json_schema needs a 'schema' object")
+            kw["guided_json"] = schema
+        elif kind not in (None, "text"):
+            raise ValueError(f"response_format type {kind!r} is not served (text, json_object, json_schema)")
+    if body.get("guided_grammar") is not None or so.get("grammar") is not None:
+        raise ValueError("grammar-guided decoding is not served; use guided_regex, guided_json or guided_choice")
     if body.get("allowed_token_ids"):
         kw["allowed_token_ids"] = [int(t) for t in body["allowed_token_ids"]]
     if body.get("logit_bias"):
@@ -110,14 +125,34 @@ def _compile_template(text: str):
 
 
 def render_chat(tokenizer, messages: list[dict], add_generation_prompt: bool = True, tools: Optional[list] = None,
-                chat_template: Optional[str] = None) -> str:
+                chat_template: Optional[str] = None, continue_final_message: bool = False,
+                template_kwargs: Optional[dict] = None) -> str:
+    """``continue_final_message``: the last message is an unfinished assistant turn; the prompt ends inside it (the
+    template's end-of-turn text after that message is cut) and no generation prompt is added.  ``template_kwargs``
+    are extra variables for the template (``enable_thinking`` and the like)."""
+    if continue_final_message:
+        if add_generation_prompt and messages and messages[-1].get("role") == "assistant":
+            add_generation_prompt = False
+        if add_generation_prompt:
+            raise ValueError("continue_final_message and add_generation_prompt exclude each other")
+        if not messages or not isinstance(messages[-1].get("content"), str):
+            raise ValueError("continue_final_message needs a final message with text content")
+        full = render_chat(tokenizer, messages, False, tools, chat_template, False, template_kwargs)
+        tail = messages[-1]["content"].rstrip()
+        at = full.rfind(tail)
+        if at < 0:
+            raise ValueError("the chat template does not reproduce the final message's text; cannot continue it")
+        return full[: at + len(tail)]
+    extra = {k: v for k, v in (template_kwargs or {}).items()
+             if k not in ("messages", "tools", "add_generation_prompt", "bos_token", "eos_token", "tokenize")}
     if chat_template:        # the server's own template wins over the tokenizer's
         return _compile_template(chat_template).render(
-            messages=messages, tools=tools or None, add_generation_prompt=add_generation_prompt,
+            **extra, messages=messages, tools=tools or None, add_generation_prompt=add_generation_prompt,
             bos_token=getattr(tokenizer, "bos_token", None) or "", eos_token=getattr(tokenizer, "eos_token", None) or "")
     if tokenizer is not None and getattr(tokenizer, "chat_template", None):
         kw = {"tools": tools} if tools else {}
-        return tokenizer.apply_chat_template(messages, tokenize=False, add_generation_prompt=add_generation_prompt, **kw)
+        return tokenizer.apply_chat_template(messages, tokenize=False, add_generation_prompt=add_generation_prompt,
+                                             **kw, **extra)
     if tools:      # no template: list the functions in a system turn, Hermes style
         listing = "\n".join(json.dumps(t.get("function", t)) for t in tools)
         messages = [{"role": "system", "content": "You may call these functions by answering "
@@ -352,7 +387,10 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
             if chat:
                 messages, images = split_images(body.get("messages") or [])
                 text = render_chat(tok, messages, tools=tools,
-                                   chat_template=body.get("chat_template") or chat_template)
+                                   add_generation_prompt=bool(body.get("add_generation_prompt", True)),
+                                   chat_template=body.get("chat_template") or chat_template,
+                                   continue_final_message=bool(body.get("continue_final_message", False)),
+                                   template_kwargs=body.get("chat_template_kwargs"))
                 if images:
                     ids, prompt = encode_with_images(text, len(images)), text
                 else:
@@ -554,6 +592,26 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
                 "data": [{"object": "embedding", "index": i, "embedding": e} for i, e in enumerate(data)],
                 "usage": {"prompt_tokens": ntok, "total_tokens": ntok}}
 
+    @app.post("/pooling")
+    async def pooling_route(req: Request):
+        """The pooled hidden state of every input, not normalised unless asked; ``task``: ``embed`` (default; one
+        vector per input) or ``token_embed`` is not served."""
+        body = await req.json()
+        if body.get("task", "embed") not in ("embed", "encode"):
+            return err(400, f"pooling task {body.get('task')!r} is not served (embed)")
+        try:
+            items = many(body.get("input"))
+            ntok = count_tokens(items)
+            emb = await allm.call(lambda: llm.embed(items, pooling=body.get("pooling", "last"),
+                                                    normalize=bool(body.get("normalize", False))))
+        except EngineDeadError as e:
+            return err(500, str(e), "engine_dead")
+        except Exception as e:  # noqa: BLE001
+            return err(400, str(e))
+        return {"id": "pool-" + uuid.uuid4().hex[:16], "object": "list", "model": served_model_name,
+                "data": [{"object": "pooling", "index": i, "data": e} for i, e in enumerate(emb.tolist())],
+                "usage": {"prompt_tokens": ntok, "total_tokens": ntok}}
+
     async def score_impl(body: dict):
         t1 = body.get("text_1", body.get("query"))
         t2 = body.get("text_2", body.get("documents"))
@@ -619,6 +677,31 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
         from ..version import __version__
 
         return {"version": __version__}
+
+    @app.get("/server_info")
+    async def server_info():
+        """The engine's resolved configuration (what upstream's development endpoint of this name answers)."""
+        import dataclasses
+
+        def plain(v):
+            if dataclasses.is_dataclass(v) and not isinstance(v, type):
+                return {f.name: plain(getattr(v, f.name)) for f in dataclasses.fields(v)}
+            if isinstance(v, (list, tuple)):
+                return [plain(x) for x in v]
+            if isinstance(v, dict):
+                return {str(k): plain(x) for k, x in v.items()}
+            return v if isinstance(v, (int, float, str, bool, type(None))) else str(v)
+
+        cfg = llm.engine.cfg
+        out = {name: plain(getattr(cfg, name)) for name in ("parallel", "scheduler", "cache") if hasattr(cfg, name)}
+        m = getattr(cfg, "model", None)
+        if m is not None:
+            out["model"] = {k: plain(getattr(m, k)) for k in ("architecture", "dtype", "num_hidden_layers", "hidden_size",
+                                                                "num_attention_heads", "num_key_value_heads", "vocab_size",
+                                                                "max_position_embeddings") if hasattr(m, k)}
+        from ..version import __version__
+
+        return {"version": __version__, "served_model_name": served_model_name, "config": out}
 
     @app.get("/ping")
     @app.post("/ping")
