@@ -165,3 +165,23 @@ def test_schema_ranges_and_all_of():
     assert regex.fullmatch(merged, '{"id": 3, "name": "x"}') and not regex.fullmatch(merged, '{"id": 3}')
     with pytest.raises(NotImplementedError):
         schema_to_regex({"allOf": [{"properties": {"a": {"type": "string"}}}, {"properties": {"a": {"type": "integer"}}}]})
+
+
+def test_open_values_nest_to_any_depth():
+    """A schema that leaves a value open (``{}``, an object without properties, an array without ``items``) accepts
+    JSON of any nesting depth through one recursive definition; partial matching follows it too."""
+    from vllm_metax_b200.engine.structured import schema_to_regex
+
+    rx = regex.compile(schema_to_regex({"type": "object"}))
+    deep = '{"a": {"b": [1, "x", null, {"q": [[[{"r": {"s": []}}]]]}]}, "c": true}'
+    assert rx.fullmatch(deep)
+    assert not rx.fullmatch("[1]") and not rx.fullmatch('{"a"}') and not rx.fullmatch('{"a": [1,]}')
+    m = rx.fullmatch(deep[:40], partial=True)
+    assert m is not None and m.partial
+    assert rx.fullmatch('{"a": 1}}', partial=True) is None
+    mixed = regex.compile(schema_to_regex({"type": "object", "properties": {"k": {"type": "string"}, "meta": {},
+                                                                           "tags": {"type": "array"}}}))
+    assert mixed.fullmatch('{"k": "v", "meta": {"x": [1, {"y": null}]}, "tags": [[1], "a"]}')
+    assert not mixed.fullmatch('{"k": 3, "meta": 1, "tags": []}')
+    closed = schema_to_regex({"type": "object", "properties": {"k": {"type": "string"}}})
+    assert "(?(DEFINE)" not in closed                       # nothing open: no definition in front

@@ -99,6 +99,15 @@ def _any_json(depth: int) -> str:
     return f"(?:{scalar}|{arr}|{obj})"
 
 
+# Any JSON value as a recursive group (the ``regex`` module follows ``(?&name)`` calls, also in partial matching).
+_ANY_JSON_REF = "(?&jv)"
+_ANY_JSON_DEFINE = (
+    rf"(?(DEFINE)(?<jv>{_JSON_STRING}|{_JSON_NUMBER}|true|false|null"
+    rf"|\[{_JSON_WS}(?:(?&jv)(?:,{_JSON_WS}(?&jv))*)?{_JSON_WS}\]"
+    rf"|\{{{_JSON_WS}(?:{_JSON_STRING}:{_JSON_WS}(?&jv)(?:,{_JSON_WS}{_JSON_STRING}:{_JSON_WS}(?&jv))*)?{_JSON_WS}\}}))"
+)
+
+
 def _range_nonneg(lo: int, hi: int) -> list:
     """Alternatives (regex pieces without leading zeros) that together match exactly the integers lo..hi, 0 <= lo <= hi:
     the range is cut at the boundaries where the number of digits or a leading prefix changes."""
@@ -200,7 +209,7 @@ def _merge_all_of(parts: list) -> dict:
     return out
 
 
-def schema_to_regex(schema, _root=None, _depth: int = 0) -> str:
+def _schema_to_regex(schema, _root=None, _depth: int = 0) -> str:
     """Regular expression for the JSON documents of a schema.
 
     Supported: ``type`` (one or a list of) string / integer / number / boolean / null / array / object; ``enum`` /
@@ -210,7 +219,7 @@ def schema_to_regex(schema, _root=None, _depth: int = 0) -> str:
     ``pattern`` / ``format`` (date-time, date, time, uuid); arrays with ``items`` / ``prefixItems`` / ``minItems`` /
     ``maxItems``; objects with ``properties`` in their listed order, where ``required`` (when present) says which may be
     left out - without a ``required`` list every listed property is produced; an object or schema that leaves its
-    content open accepts any JSON value nested up to two levels.  Anything else raises."""
+    content open accepts any JSON value, nested to any depth.  Anything else raises."""
     import json
     import re
 
@@ -218,8 +227,8 @@ def schema_to_regex(schema, _root=None, _depth: int = 0) -> str:
         schema = json.loads(schema)
     root = schema if _root is None else _root
     if schema is True or schema == {}:
-        return _any_json(2)
-    rec = lambda sub: schema_to_regex(sub, root, _depth)
+        return _ANY_JSON_REF
+    rec = lambda sub: _schema_to_regex(sub, root, _depth)
     if "$ref" in schema:
         ref = schema["$ref"]
         if not ref.startswith("#/"):
@@ -229,7 +238,7 @@ def schema_to_regex(schema, _root=None, _depth: int = 0) -> str:
         node = root
         for part in ref[2:].split("/"):
             node = node[part.replace("~1", "/").replace("~0", "~")]
-        return schema_to_regex(node, root, _depth + 1)
+        return _schema_to_regex(node, root, _depth + 1)
     for key in ("anyOf", "oneOf"):
         if key in schema:
             alts = []
@@ -295,7 +304,7 @@ def schema_to_regex(schema, _root=None, _depth: int = 0) -> str:
         if "prefixItems" in schema:
             items = [rec(sub) for sub in schema["prefixItems"]]
             return rf"\[{_JSON_WS}" + f",{_JSON_WS}".join(items) + rf"{_JSON_WS}\]"
-        item = rec(schema["items"]) if schema.get("items") not in (None, True) else _any_json(1)
+        item = rec(schema["items"]) if schema.get("items") not in (None, True) else _ANY_JSON_REF
         lo, hi = int(schema.get("minItems", 0)), schema.get("maxItems")
         more = f"(?:,{_JSON_WS}{item})"
         if hi is None:
@@ -310,7 +319,7 @@ def schema_to_regex(schema, _root=None, _depth: int = 0) -> str:
             if schema.get("additionalProperties") in (None, False) and "additionalProperties" in schema:
                 return r"\{" + _JSON_WS + r"\}"
             extra = schema.get("additionalProperties")
-            val = rec(extra) if isinstance(extra, dict) and extra else _any_json(1)
+            val = rec(extra) if isinstance(extra, dict) and extra else _ANY_JSON_REF
             member = f"{_JSON_STRING}:{_JSON_WS}{val}"
             return rf"\{{{_JSON_WS}(?:{member}(?:,{_JSON_WS}{member})*)?{_JSON_WS}\}}"
         names = list(props)
@@ -330,8 +339,16 @@ def schema_to_regex(schema, _root=None, _depth: int = 0) -> str:
             body = "(?:" + "|".join(alts) + ")?"
         return r"\{" + _JSON_WS + body + _JSON_WS + r"\}"
     if t is None:
-        return _any_json(2)
+        return _ANY_JSON_REF
     raise NotImplementedError(f"JSON schema construct not supported for guided decoding: {schema!r}")
+
+
+def schema_to_regex(schema) -> str:
+    """Pattern (``regex`` module syntax) for the JSON documents of ``schema``; see :func:`_schema_to_regex` for the
+    supported subset.  Values the schema leaves open refer to one recursive definition of "any JSON value" that is
+    placed in front of the pattern, so they nest to any depth at no cost in pattern size."""
+    body = _schema_to_regex(schema)
+    return (_ANY_JSON_DEFINE + body) if _ANY_JSON_REF in body else body
 
 
 class RegexGuide:
