@@ -133,9 +133,13 @@ def test_schema_to_regex_optional_refs_alternatives():
     tree = {"$defs": {"N": {"type": "object", "properties": {"v": {"type": "integer"},
                                                                 "kids": {"type": "array", "items": {"$ref": "#/$defs/N"}}},
                             "required": ["v"]}}, "$ref": "#/$defs/N"}
+    # a recursive definition is one named group that calls itself: exact at any depth
+    assert ok(tree, '{"v": 1, "kids": [{"v": 2, "kids": [{"v": 3, "kids": [{"v": 4, "kids": [{"v": 5}]}]}]}, {"v": 6}]}')
+    assert not ok(tree, '{"v": 1, "kids": [{"v": 2, "kids": [{"v": "x"}]}]}')
+    assert regex.fullmatch(schema_to_regex(tree), '{"v": 1, "kids": [{"v": 2, "ki', partial=True)
     import pytest as _pytest
-    with _pytest.raises(NotImplementedError):           # unbounded recursion is refused, not silently truncated
-        schema_to_regex(tree)
+    with _pytest.raises(NotImplementedError):
+        schema_to_regex({"$defs": {"A": {"$ref": "#/$defs/A"}}, "$ref": "#/$defs/A"})
 
 
 @pytest.mark.parametrize("lo,hi", [(0, 9), (1, 100), (17, 342), (95, 1003), (-20, 15), (-250, -13), (0, 0), (7, 7),

@@ -209,13 +209,22 @@ def _merge_all_of(parts: list) -> dict:
     return out
 
 
-def _schema_to_regex(schema, _root=None, _depth: int = 0) -> str:
+class _RefContext:
+    """The document ``$ref`` pointers resolve in, and the named group of every definition referenced so far."""
+
+    def __init__(self, root):
+        self.root = root
+        self.names: dict = {}       # "#/$defs/N" -> group name
+        self.defs: dict = {}        # group name -> pattern
+
+
+def _schema_to_regex(schema, _root=None) -> str:
     """Regular expression for the JSON documents of a schema.
 
     Supported: ``type`` (one or a list of) string / integer / number / boolean / null / array / object; ``enum`` /
     ``const``; integers with ``minimum`` / ``maximum`` / ``exclusiveMinimum`` / ``exclusiveMaximum``; ``anyOf`` /
     ``oneOf`` (alternation); ``allOf`` (one part, or object parts whose properties / required lists are merged); local ``$ref`` into ``$defs`` /
-    ``definitions`` (recursive schemas are unrolled three levels); strings with ``minLength`` / ``maxLength`` /
+    ``definitions`` (each referenced definition becomes a named group, so recursive schemas are exact); strings with ``minLength`` / ``maxLength`` /
     ``pattern`` / ``format`` (date-time, date, time, uuid); arrays with ``items`` / ``prefixItems`` / ``minItems`` /
     ``maxItems``; objects with ``properties`` in their listed order, where ``required`` (when present) says which may be
     left out - without a ``required`` list every listed property is produced; an object or schema that leaves its
@@ -225,29 +234,30 @@ def _schema_to_regex(schema, _root=None, _depth: int = 0) -> str:
 
     if isinstance(schema, str):
         schema = json.loads(schema)
-    root = schema if _root is None else _root
+    ctx = _root if _root is not None else _RefContext(schema)
+    root = ctx.root
     if schema is True or schema == {}:
         return _ANY_JSON_REF
-    rec = lambda sub: _schema_to_regex(sub, root, _depth)
+    rec = lambda sub: _schema_to_regex(sub, ctx)
     if "$ref" in schema:
         ref = schema["$ref"]
         if not ref.startswith("#/"):
             raise NotImplementedError(f"only local $ref is supported: {ref!r}")
-        if _depth >= 3:
-            raise NotImplementedError("recursive $ref deeper than three levels")
-        node = root
-        for part in ref[2:].split("/"):
-            node = node[part.replace("~1", "/").replace("~0", "~")]
-        return _schema_to_regex(node, root, _depth + 1)
+        if ref not in ctx.names:                   # one named group per referenced definition; recursion is a group call
+            name = ctx.names[ref] = f"r{len(ctx.names)}"
+            node = root
+            for part in ref[2:].split("/"):
+                node = node[part.replace("~1", "/").replace("~0", "~")]
+            body = _schema_to_regex(node, ctx)
+            if body == f"(?&{name})":
+                raise NotImplementedError(f"$ref {ref!r} refers only to itself")
+            ctx.defs[name] = body
+        return f"(?&{ctx.names[ref]})"
     for key in ("anyOf", "oneOf"):
         if key in schema:
             alts = []
             for sub in schema[key]:
-                try:
-                    alts.append(rec(sub))
-                except NotImplementedError:
-                    if _depth < 3:
-                        raise
+                alts.append(rec(sub))
             if not alts:
                 raise NotImplementedError("no usable alternative")
             return "(?:" + "|".join(alts) + ")"
@@ -347,8 +357,17 @@ def schema_to_regex(schema) -> str:
     """Pattern (``regex`` module syntax) for the JSON documents of ``schema``; see :func:`_schema_to_regex` for the
     supported subset.  Values the schema leaves open refer to one recursive definition of "any JSON value" that is
     placed in front of the pattern, so they nest to any depth at no cost in pattern size."""
-    body = _schema_to_regex(schema)
-    return (_ANY_JSON_DEFINE + body) if _ANY_JSON_REF in body else body
+    import json
+
+    if isinstance(schema, str):
+        schema = json.loads(schema)
+    ctx = _RefContext(schema)
+    body = _schema_to_regex(schema, ctx)
+    groups = "".join(f"(?<{name}>{sub})" for name, sub in ctx.defs.items())
+    head = f"(?(DEFINE){groups})" if groups else ""
+    if _ANY_JSON_REF in body or _ANY_JSON_REF in groups:
+        head = _ANY_JSON_DEFINE + head
+    return head + body
 
 
 class RegexGuide:
