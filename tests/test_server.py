@@ -432,8 +432,8 @@ def test_response_format_and_chat_rendering_options(client_app):
     assert sampling_from_request({"guided_regex": "a+", "response_format": {"type": "json_object"}}).guided_json is None
     with pytest.raises(ValueError):
         sampling_from_request({"response_format": {"type": "structural_tag"}})
-    with pytest.raises(ValueError):
-        sampling_from_request({"guided_grammar": "root ::= 'a'"})
+    assert sampling_from_request({"guided_grammar": 'root ::= "a"+'}).guided_grammar == 'root ::= "a"+'
+    assert sampling_from_request({"structured_outputs": {"grammar": 'root ::= "b"'}}).guided_grammar == 'root ::= "b"'
 
     root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "chat_templates")
     chatml = load_chat_template(os.path.join(root, "chatml.jinja"))

@@ -189,3 +189,64 @@ def test_open_values_nest_to_any_depth():
     assert not mixed.fullmatch('{"k": 3, "meta": 1, "tags": []}')
     closed = schema_to_regex({"type": "object", "properties": {"k": {"type": "string"}}})
     assert "(?(DEFINE)" not in closed                       # nothing open: no definition in front
+
+
+_SQL = r'''
+# a tiny query language
+root   ::= "SELECT " column (", " column){0,2} " FROM " table (" WHERE " cond)? ";"
+column ::= "name" | "age" | "id"
+table  ::= [a-z_]{1,8}
+cond   ::= column " " op " " value
+op     ::= "=" | "<" | ">" | "<="
+value  ::= [0-9]{1,3} | "'" [^'\n]{0,6} "'"
+'''
+
+_ARITH = r'''
+root ::= expr
+expr ::= term (ws [-+] ws term)*
+term ::= factor (ws [*/] ws factor)*
+factor ::= number | "(" ws expr ws ")"
+number ::= "-"? [0-9]+ ("." [0-9]+)?
+ws ::= " "*
+'''
+
+
+def test_grammar_to_pattern():
+    from vllm_metax_b200.engine.grammar import grammar_to_regex
+
+    sql = regex.compile(grammar_to_regex(_SQL))
+    assert sql.fullmatch("SELECT name FROM users;") and sql.fullmatch("SELECT name, age FROM t WHERE id <= 120;")
+    assert sql.fullmatch("SELECT id FROM t WHERE name = 'bob #';")          # '#' inside a class or string is no comment
+    assert not sql.fullmatch("SELECT foo FROM t;") and not sql.fullmatch("SELECT name FROM t WHERE id = 1234;")
+    assert sql.fullmatch("SELECT name, a", partial=True) and sql.fullmatch("SELECT x", partial=True) is None
+    arith = regex.compile(grammar_to_regex(_ARITH))                         # nesting: a context-free language
+    assert arith.fullmatch("1 + 2 * (3 - 4.5)") and arith.fullmatch("((((1))))")
+    assert not arith.fullmatch("(1 + ") and arith.fullmatch("(1 + ", partial=True)
+    assert arith.fullmatch("1 + + 2", partial=True) is None and arith.fullmatch("(1 + 2))", partial=True) is None
+    esc = regex.compile(grammar_to_regex('root ::= "a\\"b\\n" [\\]x-z]+ "\\x41\\u00e9" other-rule\nother-rule ::= .'))
+    assert esc.fullmatch('a"b\n]zy' + "Aé" + "\n") and not esc.fullmatch('a"b\n]w' + "Aé!")
+    with pytest.raises(NotImplementedError, match="left-recursive"):
+        grammar_to_regex('root ::= expr\nexpr ::= expr "+" [0-9] | [0-9]')
+    with pytest.raises(NotImplementedError, match="left-recursive"):     # hidden behind a rule that can be empty
+        grammar_to_regex('root ::= ws root "x" | "y"\nws ::= " "*')
+    for bad in ('root ::= foo', 'x ::= "a"', 'root ::= "a" )', 'root ::= "a', 'root ::= [a-z', 'root ::= "a"{3,1}',
+                'root ::= "a"\nroot ::= "b"', 'nothing here'):
+        with pytest.raises(ValueError):
+            grammar_to_regex(bad)
+
+
+@pytest.mark.parametrize("temperature", [0.0, 0.9])
+def test_guided_grammar(llm, temperature):
+    from vllm_metax_b200 import SamplingParams
+    from vllm_metax_b200.engine.grammar import grammar_to_regex
+
+    sp = SamplingParams(max_tokens=80, temperature=temperature, seed=3, guided_grammar=_SQL)
+    rx = regex.compile(grammar_to_regex(_SQL))
+    for o in llm.generate(["q1", "another"], sp):
+        out = o.outputs[0]
+        assert rx.fullmatch(out.text, partial=True), out.text
+        assert out.finish_reason == "stop" and rx.fullmatch(out.text), out.text    # every repetition is bounded: it must end
+    o = llm.generate(["calc"], SamplingParams(max_tokens=24, temperature=temperature, seed=5, guided_grammar=_ARITH))[0].outputs[0]
+    assert regex.fullmatch(grammar_to_regex(_ARITH), o.text, partial=True), o.text
+    with pytest.raises(ValueError):
+        llm.generate(["x"], SamplingParams(guided_grammar=_SQL, guided_regex="a+"))

@@ -135,7 +135,7 @@ class LLMEngine:
             multi_modal_data = getattr(params, "_multi_modal_data", None)   # set by front ends that only pass params through
         if multi_modal_data:
             prompt_token_ids, mm = self.runner.encode_multimodal(list(prompt_token_ids), multi_modal_data)
-        if params is not None and (params.constrained or params.guided_regex is not None or params.guided_json is not None):
+        if params is not None and params.constrained:
             params.prepare(self.tokenizer)
         if params is not None and params.truncate_prompt_tokens:
             prompt_token_ids = list(prompt_token_ids)[-int(params.truncate_prompt_tokens):]

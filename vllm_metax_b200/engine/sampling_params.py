@@ -34,13 +34,22 @@ class SamplingParams:
     guided_choice: Optional[list] = None        # alternatives: token-id lists, or strings with a tokenizer attached
     guided_regex: Optional[str] = None
     guided_json: Optional[object] = None
+    guided_grammar: Optional[str] = None        # GBNF / EBNF text with a ``root`` rule (engine/grammar.py)
 
     def prepare(self, tokenizer=None) -> "SamplingParams":
         """Resolve the constraint once per request (builds the token trie of ``guided_choice``)."""
-        if (self.guided_regex is not None or self.guided_json is not None) and getattr(self, "_guide", None) is None:
+        if ((self.guided_regex is not None or self.guided_json is not None or self.guided_grammar is not None)
+                and getattr(self, "_guide", None) is None):
             from .structured import RegexGuide, schema_to_regex
 
-            pattern = self.guided_regex if self.guided_regex is not None else schema_to_regex(self.guided_json)
+            if sum(x is not None for x in (self.guided_regex, self.guided_json, self.guided_grammar)) > 1:
+                raise ValueError("give one of guided_regex, guided_json, guided_grammar")
+            if self.guided_grammar is not None:
+                from .grammar import grammar_to_regex
+
+                pattern = grammar_to_regex(self.guided_grammar)
+            else:
+                pattern = self.guided_regex if self.guided_regex is not None else schema_to_regex(self.guided_json)
             self._guide = RegexGuide(pattern, tokenizer)
         if self.guided_choice is not None and getattr(self, "_trie", None) is None:
             from .structured import TokenTrie, resolve_choices
@@ -76,7 +85,8 @@ class SamplingParams:
     @property
     def constrained(self) -> bool:
         return (bool(self.allowed_token_ids) or bool(self.logit_bias) or self.guided_choice is not None
-                or self.guided_regex is not None or self.guided_json is not None or bool(self.bad_words))
+                or self.guided_regex is not None or self.guided_json is not None or self.guided_grammar is not None
+                or bool(self.bad_words))
 
     @property
     def greedy(self) -> bool:

@@ -59,11 +59,11 @@ def sampling_from_request(body: dict, default_max_tokens: int = 16) -> SamplingP
     choice = body.get("guided_choice") or so.get("choice")
     if choice:
         kw["guided_choice"] = list(choice)
-    for name in ("guided_regex", "guided_json"):
+    for name in ("guided_regex", "guided_json", "guided_grammar"):
         if body.get(name) is not None or so.get(name[7:]) is not None:
             kw[name] = body.get(name) if body.get(name) is not None else so.get(name[7:])
     rf = body.get("response_format")
-    if isinstance(rf, dict) and "guided_json" not in kw and "guided_regex" not in kw and "guided_choice" not in kw:
+    if isinstance(rf, dict) and not any(k in kw for k in ("guided_json", "guided_regex", "guided_choice", "guided_grammar")):
         kind = rf.get("type")
         if kind == "json_object":                 # any JSON object
             kw["guided_json"] = {"type": "object"}
@@ -75,8 +75,6 @@ def sampling_from_request(body: dict, default_max_tokens: int = 16) -> SamplingP
             kw["guided_json"] = schema
         elif kind not in (None, "text"):
             raise ValueError(f"response_format type {kind!r} is not served (text, json_object, json_schema)")
-    if body.get("guided_grammar") is not None or so.get("grammar") is not None:
-        raise ValueError("grammar-guided decoding is not served; use guided_regex, guided_json or guided_choice")
     if body.get("allowed_token_ids"):
         kw["allowed_token_ids"] = [int(t) for t in body["allowed_token_ids"]]
     if body.get("logit_bias"):
