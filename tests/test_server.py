@@ -240,8 +240,6 @@ def test_chat_with_tools_and_reasoning_parsers():
         code, text = _call(app, "POST", "/v1/chat/completions", dict(body, stream=True))
         assert code == 200 and text.count("data: ") == 2 and "[DONE]" in text     # one parsed chunk + the terminator
         plain = build_app(allm, "toy")
-        code, text = _call(plain, "POST", "/v1/chat/completions", dict(body, tool_choice="required"))
-        assert code == 400 and "tool-call-parser" in text
         code, text = _call(plain, "POST", "/v1/chat/completions", dict(body, tool_choice={"type": "function", "function": {"name": "nope"}}))
         assert code == 400 and "unknown function" in text
     finally:
@@ -480,3 +478,52 @@ def test_response_format_and_chat_rendering_options(client_app):
     code, text = _call(app, "GET", "/server_info")
     info = json.loads(text)
     assert code == 200 and info["served_model_name"] == "toy" and info["config"]["scheduler"]["max_model_len"] == 256
+
+
+def test_tool_choice_required_and_named_are_served_by_guided_json():
+    """``tool_choice="required"`` constrains the answer to a JSON list of calls of the offered functions, a named
+    function to its arguments; neither needs a tool-call parser.  (Character-level tokenizer: the random model can
+    spell JSON.)"""
+    pytest.importorskip("httpx")
+    from tests.test_structured import CHARS
+    from tests.test_structured import CharTokenizer as _Chars
+
+    class CharTokenizer(_Chars):
+        def encode(self, text, add_special_tokens=True):           # the chat rendering has newlines
+            return [CHARS.index(c) if c in CHARS else 0 for c in text][-200:]
+
+    cfg = ModelConfig(architecture="LlamaForCausalLM", vocab_size=256, hidden_size=64, intermediate_size=128,
+                      num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                      max_position_embeddings=512, dtype=torch.float32)
+    llm = LLM(cfg, device="cpu", load_format="dummy", num_gpu_blocks=96, block_size=16, max_model_len=512,
+              tokenizer=CharTokenizer(), seed=0)
+    allm = AsyncLLM(llm)
+    try:
+        app = build_app(allm, "toy")
+        tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {
+                      "type": "object", "properties": {"city": {"enum": ["Paris", "Rome"]}, "days": {"type": "integer", "minimum": 1, "maximum": 7}}}}},
+                 {"type": "function", "function": {"name": "get_time", "parameters": {
+                      "type": "object", "properties": {"zone": {"enum": ["UTC", "CET"]}}}}}]
+        body = {"messages": [{"role": "user", "content": "weather?"}], "max_tokens": 200, "tools": tools,
+                "temperature": 0.8, "seed": 2}
+        code, text = _call(app, "POST", "/v1/chat/completions", dict(body, tool_choice="required"))
+        assert code == 200, text
+        choice = json.loads(text)["choices"][0]
+        calls = choice["message"].get("tool_calls")
+        if choice["finish_reason"] == "length":           # an unbounded list may outlast the limit: content, no calls
+            assert not calls
+        else:
+            assert calls and choice["finish_reason"] == "tool_calls" and choice["message"]["content"] is None
+            for c in calls:
+                args = json.loads(c["function"]["arguments"])
+                if c["function"]["name"] == "get_weather":
+                    assert args["city"] in ("Paris", "Rome") and 1 <= args["days"] <= 7
+                else:
+                    assert c["function"]["name"] == "get_time" and args["zone"] in ("UTC", "CET")
+        code, text = _call(app, "POST", "/v1/chat/completions",
+                           dict(body, tool_choice={"type": "function", "function": {"name": "get_time"}}))
+        assert code == 200, text
+        call = json.loads(text)["choices"][0]["message"]["tool_calls"][0]["function"]
+        assert call["name"] == "get_time" and json.loads(call["arguments"])["zone"] in ("UTC", "CET")
+    finally:
+        allm.shutdown()

@@ -380,6 +380,13 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
                 if spec is None:
                     return err(400, f"tool_choice names an unknown function {forced_tool!r}")
                 body = dict(body, guided_json=spec.get("parameters") or {"type": "object"})   # the answer IS the arguments
+            if tools and tool_choice == "required":              # at least one call: the answer is a JSON list of calls
+                one = [{"type": "object", "required": ["name", "parameters"],
+                        "properties": {"name": {"const": t.get("function", t).get("name")},
+                                       "parameters": t.get("function", t).get("parameters") or {"type": "object"}}}
+                       for t in tools]
+                forced_tool = True
+                body = dict(body, guided_json={"type": "array", "minItems": 1, "items": {"anyOf": one}})
             if tools and tool_parser is None and forced_tool is None and tool_choice != "auto":
                 return err(400, "tool_choice needs the server to be started with --tool-call-parser")
             if chat:
@@ -436,7 +443,7 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
                 finish = last.finish_reason
                 if msg.tool_calls:
                     message["tool_calls"] = [c.to_openai() for c in msg.tool_calls]
-                    finish = "tool_calls" if forced_tool is None else finish
+                    finish = "tool_calls" if forced_tool in (None, True) else finish
                 return {"index": i, "message": message, "finish_reason": finish,
                         "logprobs": format_logprobs(last.logprobs, tok, True)}
             return {"index": i, "text": text, "token_ids": last.token_ids,
@@ -479,7 +486,7 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
                         finish = chunk.finish_reason
                         if msg.tool_calls:
                             d["tool_calls"] = [c.to_openai(i) for i, c in enumerate(msg.tool_calls)]
-                            finish = "tool_calls" if forced_tool is None else finish
+                            finish = "tool_calls" if forced_tool in (None, True) else finish
                         ch = {"index": 0, "delta": d, "finish_reason": finish,
                               "logprobs": format_logprobs(chunk.logprobs, tok, True)}
                     elif chat:

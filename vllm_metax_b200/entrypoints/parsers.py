@@ -364,11 +364,19 @@ def get_reasoning_parser(name: Optional[str]):
 def parse_chat_output(text: str, tool_parser=None, reasoning_parser=None, tools_requested: bool = False,
                       forced_tool: Optional[str] = None) -> ParsedMessage:
     """Reasoning first, then tool calls in what remains.  ``forced_tool``: ``tool_choice`` named one function and the
-    output was constrained to its arguments - the whole answer is that call."""
+    output was constrained to its arguments - the whole answer is that call.  ``forced_tool=True``:
+    ``tool_choice="required"``, the output was constrained to a JSON list ``[{"name": ..., "parameters": {...}}, ...]``
+    (a list cut off by the token limit is answered as plain content)."""
     reasoning = None
     if reasoning_parser is not None:
         reasoning, text = reasoning_parser(text)
         text = text or ""
+    if forced_tool is True:
+        try:
+            calls = json.loads(text)
+            return ParsedMessage(None, [ToolCall(c["name"], json.dumps(c.get("parameters", {}))) for c in calls], reasoning)
+        except (ValueError, KeyError, TypeError):
+            return ParsedMessage(text or None, [], reasoning)
     if forced_tool:
         return ParsedMessage(None, [ToolCall(forced_tool, _args_text(text.strip() or "{}"))], reasoning)
     msg = tool_parser(text) if (tool_parser is not None and tools_requested) else ParsedMessage(text or None)
