@@ -250,3 +250,22 @@ def test_incremental_detokenizer_equals_full_decode():
             d2.step(cut[:j])
         d2.finish(cut)
         assert d2.text == tok.decode(cut)
+
+
+def test_best_of_returns_the_most_likely_samples(llm):
+    """``best_of=6, n=2``: six seeded samples run, the two with the best cumulative log-probability come back (they are
+    among the six that ``n=6`` gives for the same seed, in order of likelihood); log-probabilities are only returned
+    when asked for."""
+    from vllm_metax_b200 import SamplingParams
+
+    kw = dict(max_tokens=10, temperature=1.0, seed=5, ignore_eos=True)
+    all6 = llm.generate(["Q: ok?"], SamplingParams(n=6, logprobs=0, **kw))[0].outputs
+    score = lambda c: sum(e["logprob"] for e in c.logprobs)
+    want = sorted(all6, key=lambda c: -score(c))[:2]
+    best = llm.generate(["Q: ok?"], SamplingParams(n=2, best_of=6, **kw))[0].outputs
+    assert [c.token_ids for c in best] == [c.token_ids for c in want]
+    assert [c.index for c in best] == [0, 1] and all(c.logprobs is None for c in best)
+    with_lp = llm.generate(["Q: ok?"], SamplingParams(n=1, best_of=6, logprobs=2, **kw))[0].outputs
+    assert len(with_lp) == 1 and with_lp[0].token_ids == want[0].token_ids and len(with_lp[0].logprobs[0]["top"]) == 2
+    plain = llm.generate(["Q: ok?"], SamplingParams(n=2, best_of=2, **kw))[0].outputs       # best_of == n: nothing to rank
+    assert [c.token_ids for c in plain] == [c.token_ids for c in all6[:2]]

@@ -527,3 +527,11 @@ def test_tool_choice_required_and_named_are_served_by_guided_json():
         assert call["name"] == "get_time" and json.loads(call["arguments"])["zone"] in ("UTC", "CET")
     finally:
         allm.shutdown()
+
+
+def test_best_of_is_refused_by_the_server(client_app):
+    pytest.importorskip("httpx")
+    _, app = client_app
+    code, text = _call(app, "POST", "/v1/completions", {"prompt": "hi", "max_tokens": 3, "n": 1, "best_of": 4})
+    assert code == 400 and "best_of" in text
+    assert _call(app, "POST", "/v1/completions", {"prompt": "hi", "max_tokens": 3, "n": 2, "best_of": 2})[0] == 200

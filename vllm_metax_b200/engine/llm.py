@@ -505,24 +505,29 @@ class LLM:
         import copy
 
         groups: list[list[str]] = []          # per prompt: the request ids of its sp.n samples
+        first_params: dict = {}               # first request id of a group -> the caller's SamplingParams
         reqs: dict[str, Request] = {}
         loras = lora_request if isinstance(lora_request, (list, tuple)) else [lora_request] * n
         for p, sp, lr in zip(prompts, sps, loras):
             ids, text = self._to_ids(p)
             mm = p.get("multi_modal_data") if isinstance(p, dict) else None       # {"image": tensor | PIL | list}
-            k = max(1, int(getattr(sp, "n", 1) or 1))
+            keep = max(1, int(getattr(sp, "n", 1) or 1))
+            k = max(keep, int(getattr(sp, "best_of", None) or 0))
             rids = []
             for i in range(k):
                 spi = copy.copy(sp)
                 if k > 1:       # independent samples of one prompt (they share its cached prefix when that is on)
-                    spi.n = 1
+                    spi.n, spi.best_of = 1, None
                     spi.seed = None if sp.seed is None else sp.seed + i
+                if k > keep and spi.logprobs is None:
+                    spi.logprobs = 0            # the chosen tokens' log-probabilities rank the samples
                 rid = self.engine.add_request(ids, spi, prompt=text, arrival_time=now, lora_request=lr,
                                               multi_modal_data=mm)
                 reqs[rid] = self.engine.requests[rid]
                 reqs[rid].sample_index = i
                 rids.append(rid)
             groups.append(rids)
+            first_params[rids[0]] = sp
         total = len(reqs)
 
         def merged(rids: list[str]) -> RequestOutput:
@@ -531,6 +536,15 @@ class LLM:
             for o in outs[1:]:
                 first.outputs.extend(o.outputs)
                 first.finished = first.finished and o.finished
+            sp0 = first_params[rids[0]]
+            keep = max(1, int(getattr(sp0, "n", 1) or 1))
+            if len(first.outputs) > keep:        # best_of: the ``n`` samples with the best cumulative log-probability
+                ranked = sorted(first.outputs, key=lambda c: -sum(e["logprob"] for e in (c.logprobs or [])))[:keep]
+                for i, c in enumerate(ranked):
+                    c.index = i
+                    if sp0.logprobs is None:
+                        c.logprobs = None
+                first.outputs = ranked
             return first
 
         done: dict[str, Request] = {}

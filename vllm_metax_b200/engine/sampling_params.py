@@ -23,6 +23,7 @@ class SamplingParams:
     min_tokens: int = 0
     logprobs: Optional[int] = None
     n: int = 1                                  # completions per prompt (independent samples; seed + i when seeded)
+    best_of: Optional[int] = None               # sample this many (>= n), return the n with the best cumulative log-probability
     stop: list = field(default_factory=list)    # stop STRINGS: generation ends when the output text contains one
     include_stop_str_in_output: bool = False
     bad_words: list = field(default_factory=list)   # strings (need a tokenizer) or token-id lists never to be produced

@@ -420,6 +420,8 @@ def build_app(allm: AsyncLLM, served_model_name: str = "b200-model", lora_module
         n_samples = max(1, int(body.get("n") or 1))
         if n_samples > 1 and body.get("stream"):
             return err(400, "n > 1 is served for non-streaming requests only")
+        if int(body.get("best_of") or 0) > n_samples:
+            return err(400, "best_of > n is served by the offline API (SamplingParams.best_of), not by this server")
 
         def sample_params(i: int):
             if n_samples == 1:
